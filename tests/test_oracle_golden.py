@@ -1,0 +1,127 @@
+"""The CPU oracle against vectors it did not produce: the reference's I2_S fixtures, gguf-py, and the reference's own
+I2_S CPU kernel (tests/golden/make_golden.py says how each file was made)."""
+import hashlib
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oracle
+from conftest import GOLDEN
+
+
+def _g(name):
+    return os.path.join(GOLDEN, name)
+
+
+META = json.load(open(_g("golden_meta.json")))
+
+
+def test_fixture_hashes():
+    for name, want in META["sha256"].items():
+        assert hashlib.sha256(open(_g(name), "rb").read()).hexdigest() == want
+
+
+def test_i2s_upstream_fixture_decodes_to_expected_f32():
+    # tests/test_phase0_i2s_proof.c subtest 7.1: 64 B payload = 256 weights, scale in the 32 B trailer
+    raw = np.fromfile(_g("fixture_i2s_upstream.bin"), np.uint8)
+    assert raw.size == 96
+    scale = float(raw[64:68].view(np.float32)[0])
+    assert scale == META["fixture_i2s_upstream_scale"]
+    rc, w = oracle.dequantize_i2_s(raw[:64], scale, 256)
+    assert rc == 0
+    want = np.fromfile(_g("expected_i2s_upstream_f32.bin"), np.float32)
+    assert np.array_equal(w.view(np.uint32), want.view(np.uint32))
+    neg, zero, pos = (w < 0).sum(), (w == 0).sum(), (w > 0).sum()
+    assert [neg, zero, pos] == META["upstream_counts_neg_zero_pos"]
+
+
+def test_i2s_gguf_slice():
+    # subtest 7.2: block 0 (32 B) of blk.0.attn_v.weight + its 32 B scale trailer
+    raw = np.fromfile(_g("gguf_slice_blk0_v.bin"), np.uint8)
+    assert raw.size == 64
+    scale = float(raw[32:36].view(np.float32)[0])
+    assert abs(scale - META["gguf_slice_scale"]) < 1e-6
+    rc, w = oracle.dequantize_i2_s(raw[:32], scale, 128)
+    assert rc == 0
+    assert [(w < 0).sum(), (w == 0).sum(), (w > 0).sum()] == META["gguf_slice_counts_neg_zero_pos"]
+    assert set(np.unique(w)) <= {-np.float32(scale), 0.0, np.float32(scale)}
+
+
+def test_i2s_boundaries_and_truncation():
+    # boundary n (not a multiple of 128) and truncated input, as the reference's decoder gates
+    raw = np.fromfile(_g("fixture_i2s_upstream.bin"), np.uint8)
+    rc, full = oracle.dequantize_i2_s(raw[:64], 1.0, 256)
+    for n in (0, 1, 31, 32, 33, 127, 128, 129, 255):
+        rc, w = oracle.dequantize_i2_s(raw[:64], 1.0, n)
+        assert rc == 0 and np.array_equal(w, full[:n])
+    rc, _ = oracle.dequantize_i2_s(raw[:32], 1.0, 129)
+    assert rc == -3
+    rc, _ = oracle.dequantize_i2_s(raw[:64], 1.0, -1)
+    assert rc == -2
+
+
+def test_fp16_conversions_match_numpy():
+    z = np.load(_g("fp16.npz"))
+    f32, f16 = z["f32"], z["f16"]
+    got = np.array([oracle.fp32_to_fp16(v) for v in f32], np.uint16)
+    assert np.array_equal(got, f16)
+    allh = np.arange(65536, dtype=np.uint16)
+    wide = allh.view(np.float16).astype(np.float32)
+    mine = np.array([oracle.fp16_to_fp32(h) for h in allh], np.float32)
+    ok = np.isnan(wide) | (wide.view(np.uint32) == mine.view(np.uint32))
+    assert ok.all()
+    assert np.isnan(mine[np.isnan(wide)]).all()
+
+
+def test_q8_0_q4_0_against_gguf_py():
+    z = np.load(_g("gguf_q8_0_q4_0.npz"))
+    x = z["x"]
+    # gguf-py rounds half away from zero ("bit-exact with the reference implementation in ggml-quants.c")
+    assert np.array_equal(oracle.quantize_q8_0(x, oracle.ROUND_TIES_AWAY), z["q8_0"])
+    assert np.array_equal(oracle.quantize_q4_0(x), z["q4_0"])
+    assert np.array_equal(oracle.dequantize_q8_0(z["q8_0"]).view(np.uint32), z["deq_q8_0"].view(np.uint32))
+    assert np.array_equal(oracle.dequantize_q4_0(z["q4_0"]).view(np.uint32), z["deq_q4_0"].view(np.uint32))
+    # the nearest-even convention differs from ties-away only on exact .5 values; row 5 was built to contain some
+    even = oracle.quantize_q8_0(x, oracle.ROUND_NEAREST_EVEN)
+    diff_rows = np.unique(np.nonzero(even != z["q8_0"])[0])
+    assert 5 in diff_rows
+    d = even.view(np.int8).astype(np.int16) - z["q8_0"].view(np.int8).astype(np.int16)
+    assert np.abs(d).max() <= 1
+
+
+def test_q4_K_dequant_against_gguf_py():
+    z = np.load(_g("gguf_q4_K.npz"))
+    got = oracle.dequantize_q4_K(z["q4_K"]).reshape(-1)
+    assert np.array_equal(got.view(np.uint32), z["deq"].view(np.uint32))
+
+
+def test_i2s_dot_against_reference_cpu_kernel():
+    z = np.load(_g("i2s_ref_kernel.npz"))
+    packed, act, out = z["packed"], z["act"], z["out"]
+    N, K = packed.shape[0], packed.shape[1] * 4
+    M = act.shape[0]
+    y, acc = oracle.mul_mat_i2_s_i8(packed, 1.0, act, np.ones(M, np.float32), M, N, K)
+    assert np.array_equal(acc.astype(np.float32), out)
+    assert np.array_equal(y, out)
+    # code 3 contributes +2 in the dot kernel (and 0.0 in the dequantizer)
+    one = np.full((1, 32), 0xFF, np.uint8)
+    a = np.ones((1, 128), np.int8)
+    _, acc = oracle.mul_mat_i2_s_i8(one, 1.0, a, np.ones(1, np.float32), 1, 1, 128)
+    assert acc[0, 0] == 256
+
+
+@pytest.mark.skipif(not oracle.ref_available(), reason="oracle/_ref is built only where the reference tree exists")
+def test_i2s_live_reference_kernel():
+    rng = np.random.default_rng(7)
+    N, K = 64, 2560
+    w = rng.standard_normal((N, K)).astype(np.float32)
+    packed, scale = oracle.quantize_i2_s(w)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    q, dq, sm = oracle.quantize_i8_token(x)
+    ref = oracle.ref_vec_dot_i2_i8_s(packed, q[0], N, K)
+    y, acc = oracle.mul_mat_i2_s_i8(packed, scale, q, dq, 1, N, K)
+    assert np.array_equal(acc[0].astype(np.float32), ref)
+    total = np.float32(dq[0]) * np.float32(scale)
+    assert np.array_equal(y[0], ref * total)
