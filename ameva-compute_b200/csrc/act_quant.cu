@@ -1,0 +1,285 @@
+// On-the-fly activation quantization: fp32 rows -> int8 with per-32 (Q8_0), per-256 (Q8_K) or per-token (BitNet) scales.
+// Results are bit-equal to the CPU quantizers: every fp32 expression below is written so that it rounds once, in the
+// same place as ggml's reference code (IEEE division and multiplication, no fused multiply-add on the rounding path).
+//
+// Reference kernels replaced:
+//   ameva_quant_a8   adapters/llama/ggml-ameva/shaders/ameva_quant_a8.comp:32-79   (per-32)
+//   ameva_quant_a8b  adapters/llama/ggml-ameva/shaders/ameva_quant_a8b.comp:34-71  (per-256)
+//   bitnet_norm_q8   src/shaders/bitnet_norm_q8.comp:51-123                        (norm + per-token absmax)
+#include <cstring>
+
+#include "common.cuh"
+
+namespace amv {
+
+// ---------------------------------------------------------------------------------------------------------------------
+// per-32: 8 lanes per unit, one float4 each (128 B coalesced per unit, 4 units per warp).
+//   d = amax / 127 (f32); id = d ? 1/d : 0; q = clamp(round(x*id), +-127); stored d = fp16(d) (what the dot uses).
+//   round_mode 0 = ties-to-even (reference shaders, ggml SIMD quantizers), 1 = ties-away (ggml quantize_row_q8_0_ref).
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
+                                                         uint32_t* __restrict__ ad, uint32_t M, uint32_t K,
+                                                         uint32_t src_stride, uint32_t round_mode) {
+    const uint32_t U = K >> 5;
+    const uint64_t total = (uint64_t)M * U;
+    const uint64_t gi = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;  // unit index
+    const uint32_t sub = threadIdx.x & 7u;
+    const bool live = gi < total;
+    const uint32_t m = live ? (uint32_t)(gi / U) : 0u;
+    const uint32_t u = live ? (uint32_t)(gi - (uint64_t)m * U) : 0u;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) x = *reinterpret_cast<const float4*>(src + (size_t)m * src_stride + 32u * u + 4u * sub);
+    float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d = __fdiv_rn(amax, 127.0f);
+    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
+    int q[4];
+    const float v[4] = {__fmul_rn(x.x, id), __fmul_rn(x.y, id), __fmul_rn(x.z, id), __fmul_rn(x.w, id)};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int r = round_mode ? (int)roundf(v[i]) : __float2int_rn(v[i]);
+        q[i] = max(-127, min(127, r));
+    }
+    int s = q[0] + q[1] + q[2] + q[3];
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (live) {
+        const uint32_t w = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) |
+                           ((uint32_t)(q[3] & 0xFF) << 24);
+        reinterpret_cast<uint32_t*>(aq + (size_t)m * K + 32u * u)[sub] = w;
+        if (sub == 0) ad[(size_t)m * U + u] = (uint32_t)f2h(d) | ((uint32_t)(s & 0xFFFF) << 16);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// per-256: one warp per block, 8 consecutive elements per lane.
+//   mode 0 (ggml quantize_row_q8_K_ref): max = signed element of largest magnitude (first on ties),
+//          iscale = -127/max, q = min(127, nearest_int(iscale*x)), d = 1/iscale; amax == 0 -> d = 0, q = 0.
+//   mode 1 (ameva_quant_a8b.comp): d = amax/127, q = clamp(roundEven(x * (1/d)), +-127).
+//   bsums[j] = sum of q over elements 16j..16j+15.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
+                                                         uint8_t* __restrict__ ab, uint32_t M, uint32_t K,
+                                                         uint32_t src_stride, uint32_t mode) {
+    const uint32_t B = K >> 8;
+    const uint64_t total = (uint64_t)M * B;
+    const uint64_t gi = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const uint32_t lane = threadIdx.x & 31u;
+    if (gi >= total) return;  // whole warps leave together
+    const uint32_t m = (uint32_t)(gi / B);
+    const uint32_t b = (uint32_t)(gi - (uint64_t)m * B);
+    const float* p = src + (size_t)m * src_stride + 256u * b + 8u * lane;
+    const float4 x0 = *reinterpret_cast<const float4*>(p);
+    const float4 x1 = *reinterpret_cast<const float4*>(p + 4);
+    const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    float amax = 0.0f, mx = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float ax = fabsf(x[i]);
+        if (ax > amax) {
+            amax = ax;
+            mx = x[i];
+        }
+    }
+    // the first element of largest magnitude wins: lower lanes hold lower indices, so on equal magnitude keep the
+    // value that came from the lower lane
+    uint32_t owner = lane;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
+        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
+        const uint32_t oo = __shfl_xor_sync(0xffffffffu, owner, o);
+        if (oa > amax || (oa == amax && oo < owner)) {
+            amax = oa;
+            mx = om;
+            owner = oo;
+        }
+    }
+    int q[8];
+    float d;
+    if (amax == 0.0f) {
+        d = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = 0;
+    } else if (mode == 0u) {
+        const float iscale = __fdiv_rn(-127.0f, mx);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = min(127, __float2int_rn(__fmul_rn(iscale, x[i])));
+        d = __fdiv_rn(1.0f, iscale);
+    } else {
+        d = __fdiv_rn(amax, 127.0f);
+        const float id = __fdiv_rn(1.0f, d);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = max(-127, min(127, __float2int_rn(__fmul_rn(x[i], id))));
+    }
+    int s = 0;
+    uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        s += q[i] + q[i + 4];
+        w0 |= (uint32_t)(q[i] & 0xFF) << (8 * i);
+        w1 |= (uint32_t)(q[i + 4] & 0xFF) << (8 * i);
+    }
+    *reinterpret_cast<uint2*>(aq + (size_t)m * K + 256u * b + 8u * lane) = make_uint2(w0, w1);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);  // lanes 2j, 2j+1 -> 16-element group j
+    uint8_t* blk = ab + ((size_t)m * B + b) * kABBytes;
+    if ((lane & 1u) == 0u) reinterpret_cast<int16_t*>(blk)[lane >> 1] = (int16_t)s;
+    if (lane == 0) {
+        *reinterpret_cast<float*>(blk + 32) = d;
+        *reinterpret_cast<uint32_t*>(blk + 36) = 0u;
+        *reinterpret_cast<uint2*>(blk + 40) = make_uint2(0u, 0u);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// BitNet stage before an I2_S projection, one CTA of 256 per token row (grid.x = rows; the reference runs one row).
+//   h = a (mode 0) | relu(a)^2 * b (mode 1) | silu(a) * b (mode 2); y = do_norm ? (h * rms_scale) * w : h
+//   qs = 127 / max(|y|max, 1e-7); q = clamp(round_half_away(y*qs), +-127); act[0] = bits(1/qs), act[1] = sum(q);
+//   qeo = even/odd split of q+128 (kept for hosts that still bind it).
+// Rows are dim apart in a, b, y; dim/4 words apart in q; 2 words apart in act; dim/4 uvec2 apart in qeo; w is shared.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_reduce_256(float v, float* red, bool is_max) {
+    v = is_max ? warp_max(v) : warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+    return r;
+}
+
+__global__ void __launch_bounds__(256) bitnet_norm_q8_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                                                             const float* __restrict__ w, float* __restrict__ y,
+                                                             uint32_t* __restrict__ q, uint32_t* __restrict__ act,
+                                                             uint2* __restrict__ qeo, uint32_t dim, float eps,
+                                                             uint32_t mode, uint32_t do_norm) {
+    __shared__ float red[8];
+    __shared__ int redi[8];
+    const uint32_t row = blockIdx.x, t = threadIdx.x, words = dim >> 2;
+    a += (size_t)row * dim;
+    if (mode != 0u) b += (size_t)row * dim;
+    y += (size_t)row * dim;
+    q += (size_t)row * words;
+    act += 2u * row;
+    if (qeo) qeo += (size_t)row * words;
+
+    float ss = 0.0f;
+    for (uint32_t wi = t; wi < words; wi += 256u) {
+        const float4 g = *reinterpret_cast<const float4*>(a + 4u * wi);
+        float h[4] = {g.x, g.y, g.z, g.w};
+        if (mode != 0u) {
+            const float4 e = *reinterpret_cast<const float4*>(b + 4u * wi);
+            const float ev[4] = {e.x, e.y, e.z, e.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                if (mode == 1u) {
+                    const float r = h[k] > 0.0f ? h[k] : 0.0f;
+                    h[k] = __fmul_rn(__fmul_rn(r, r), ev[k]);
+                } else {
+                    h[k] = __fmul_rn(__fdiv_rn(h[k], 1.0f + expf(-h[k])), ev[k]);
+                }
+            }
+        }
+        *reinterpret_cast<float4*>(y + 4u * wi) = make_float4(h[0], h[1], h[2], h[3]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) ss = fmaf(h[k], h[k], ss);
+    }
+    const float tot = block_reduce_256(ss, red, false);
+    const float scale = __fdiv_rn(1.0f, sqrtf(__fdiv_rn(tot, (float)dim) + eps));
+
+    float amax = 0.0f;
+    for (uint32_t wi = t; wi < words; wi += 256u) {  // every thread re-reads only the words it wrote
+        float4 v = *reinterpret_cast<const float4*>(y + 4u * wi);
+        if (do_norm != 0u) {
+            const float4 g = *reinterpret_cast<const float4*>(w + 4u * wi);
+            v.x = __fmul_rn(__fmul_rn(v.x, scale), g.x);
+            v.y = __fmul_rn(__fmul_rn(v.y, scale), g.y);
+            v.z = __fmul_rn(__fmul_rn(v.z, scale), g.z);
+            v.w = __fmul_rn(__fmul_rn(v.w, scale), g.w);
+            *reinterpret_cast<float4*>(y + 4u * wi) = v;
+        }
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    const float qs = __fdiv_rn(127.0f, fmaxf(block_reduce_256(amax, red, true), 1e-7f));
+
+    int qsum = 0;
+    for (uint32_t wi = t; wi < words; wi += 256u) {
+        const float4 v4 = *reinterpret_cast<const float4*>(y + 4u * wi);
+        const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+        uint32_t packed = 0, u[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int iv = max(-127, min(127, (int)roundf(__fmul_rn(v[k], qs))));
+            packed |= (uint32_t)(iv & 0xFF) << (8 * k);
+            qsum += iv;
+            u[k] = (uint32_t)(iv + 128);
+        }
+        q[wi] = packed;
+        if (qeo) qeo[wi] = make_uint2((u[0] << 16) | u[2], (u[1] << 16) | u[3]);
+    }
+    qsum = warp_sum_i(qsum);
+    if ((t & 31u) == 0) redi[t >> 5] = qsum;
+    __syncthreads();
+    if (t == 0) {
+        int s = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += redi[i];
+        act[0] = __float_as_uint(__fdiv_rn(1.0f, qs));
+        act[1] = (uint32_t)s;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------------------------------
+// ameva_quant_a8: bindings 0 src f32, 1 AQ, 2 AD; push {M, K, src_stride (floats), round_mode}
+AcResult launch_quant_a8(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], round_mode = a.push[3];
+    if (M == 0 || K == 0 || (K & 31u) || stride < K || (stride & 3u) || round_mode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t U = K >> 5;
+    if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || a.range[1] < (uint64_t)M * K || a.range[2] < (uint64_t)M * U * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    const uint64_t threads = (uint64_t)M * U * 8u;
+    const uint64_t blocks = (threads + 255u) / 256u;
+    if (blocks > 0x7FFFFFFFull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
+    quant_q8_0_kernel<<<(unsigned)blocks, 256, 0, a.stream>>>((const float*)a.ptr[0], (int8_t*)a.ptr[1],
+                                                              (uint32_t*)a.ptr[2], M, K, stride, round_mode);
+    return check_launch();
+}
+
+// ameva_quant_a8b: bindings 0 src f32, 1 AQ, 2 AB; push {M, K, src_stride (floats), mode}
+AcResult launch_quant_a8b(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], mode = a.push[3];
+    if (M == 0 || K == 0 || (K & 255u) || stride < K || (stride & 3u) || mode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t B = K >> 8;
+    if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || a.range[1] < (uint64_t)M * K ||
+        a.range[2] < (uint64_t)M * B * kABBytes)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    const uint64_t blocks = ((uint64_t)M * B * 32u + 255u) / 256u;
+    if (blocks > 0x7FFFFFFFull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
+    quant_q8_K_kernel<<<(unsigned)blocks, 256, 0, a.stream>>>((const float*)a.ptr[0], (int8_t*)a.ptr[1],
+                                                              (uint8_t*)a.ptr[2], M, K, stride, mode);
+    return check_launch();
+}
+
+// bitnet_norm_q8: bindings 0 a, 1 b, 2 w, 3 y, 4 q, 5 act, 6 qeo; push {dim, eps_bits, mode, do_norm}; grid.x = rows
+// (argument contract of src/shaders/bitnet_norm_q8.comp:20-44, extended from one row to grid.x rows).
+AcResult launch_bitnet_norm_q8(const LaunchArgs& a) {
+    const uint32_t dim = a.push[0], mode = a.push[2], do_norm = a.push[3], rows = a.grid.x;
+    if (dim == 0 || (dim & 3u) || mode > 2u || a.grid.y != 1 || a.grid.z != 1) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t need = (uint64_t)rows * dim * 4u;
+    if (a.range[0] < need || (mode != 0u && a.range[1] < need) || (do_norm && a.range[2] < (uint64_t)dim * 4u) ||
+        a.range[3] < need || a.range[4] < (uint64_t)rows * dim || a.range[5] < (uint64_t)rows * 8u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    uint2* qeo = a.range[6] >= (uint64_t)rows * dim * 2u ? (uint2*)a.ptr[6] : nullptr;
+    float eps;
+    memcpy(&eps, &a.push[1], 4);
+    bitnet_norm_q8_kernel<<<rows, 256, 0, a.stream>>>((const float*)a.ptr[0], (const float*)a.ptr[1],
+                                                      (const float*)a.ptr[2], (float*)a.ptr[3], (uint32_t*)a.ptr[4],
+                                                      (uint32_t*)a.ptr[5], qeo, dim, eps, mode, do_norm);
+    return check_launch();
+}
+
+}  // namespace amv

@@ -1,0 +1,114 @@
+// Shared device helpers and the launcher contract of the built-in kernel registry (sm_100a only).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/ac_runtime_b200.h"
+
+namespace amv {
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Launcher contract. A dispatch hands the launcher the device address and byte range of every binding (base + offset of
+// the bound range), the push constants zero-padded to the kernel's declared size, the caller's grid, and the context's
+// device status words. Launchers validate shapes and ranges and return an AcResult: they never fall back to another
+// implementation.
+// ---------------------------------------------------------------------------------------------------------------------
+struct LaunchArgs {
+    cudaStream_t stream;
+    uint32_t binding_count;
+    void* ptr[16];
+    uint64_t range[16];
+    uint32_t push[32];
+    AcDim3 grid;
+    uint32_t* status;  // 4 device words owned by the context: [0] error code, [1] detail, [2..3] reserved
+    int sm_count;
+};
+
+typedef AcResult (*LaunchFn)(const LaunchArgs&);
+
+struct KernelEntry {
+    const char* name;
+    uint32_t binding_count;
+    uint32_t push_bytes;
+    AcDim3 local_size;
+    LaunchFn launch;
+};
+
+const KernelEntry* find_kernel(const char* name);
+uint32_t kernel_count();
+const KernelEntry* kernel_at(uint32_t i);
+
+inline AcResult check_launch() {
+    return cudaGetLastError() == cudaSuccess ? AC_SUCCESS : AC_ERR_INVALID_WORK_GROUP_SIZE;
+}
+
+// Device status codes written by kernels that give up on a bounded wait (never a trap).
+enum : uint32_t { DEV_STATUS_OK = 0, DEV_STATUS_WAIT_TIMEOUT = 1, DEV_STATUS_BAD_INDEX = 2 };
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------------------------------------
+// Loads. Weights are streamed exactly once, so they bypass L1 (which is left to the activation vector every warp of the
+// SM re-reads).
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+struct __align__(32) u32x8 {
+    uint32_t v[8];
+};
+__device__ __forceinline__ u32x8 ld_stream_u8(const void* p) {  // 256-bit load (sm_100)
+    u32x8 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]), "=r"(r.v[6]),
+                   "=r"(r.v[7])
+                 : "l"(p));
+    return r;
+}
+__device__ __forceinline__ uint16_t ld_stream_u16(const void* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 ld_cached_u4(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ uint16_t f2h(float f) { return __half_as_ushort(__float2half_rn(f)); }
+
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) { return __dp4a((int)a, (int)b, c); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+#endif  // __CUDACC__
+
+// Layout constants shared by host packer and kernels.
+// Device weight layout ("regions"): the quant payloads of all blocks first (padded to a multiple of 64 bytes), then the
+// scale fields of all blocks, both in block order (row-major over [N][K/blk]).
+//   Q4_0: Q 16 B/unit, S 2 B/unit (fp16 d)             Q8_0: Q 32 B/unit, S 2 B/unit
+//   Q4_K: Q 128 B/block, S 16 B/block (d, dmin, scales[12])   I2_S: unchanged (already dense: K/4 bytes per row)
+constexpr int kQ40QBytes = 16, kQ80QBytes = 32, kQ4KQBytes = 128, kQ4KSBytes = 16;
+// Quantized-activation scratch:
+//   per-32  : AQ int8 [M][K];  AD uint32 [M][K/32]  = fp16 d bits | int16 sum(q) << 16
+//   per-256 : AQ int8 [M][K];  AB 48 B  [M][K/256]  = int16 bsums[16] @0, float d @32, 12 B pad
+//   per-token: AQ int8 [M][K]; ACT uint32 [M][2]    = bits of 1/scale, sum(q)
+constexpr int kABBytes = 48;
+
+}  // namespace amv

@@ -1,0 +1,462 @@
+// Decode GEMV (M <= 8 activation rows) over block-quantized weights: an HBM-streaming kernel family.
+//
+// One warp owns R consecutive weight rows. Its lanes walk the row in 16-byte (Q4_0, Q4_K, I2_S) or 32-byte (Q8_0) chunks,
+// lane-contiguous so every warp-wide load covers 512 / 1024 contiguous bytes; UN chunks per row are requested before
+// the first is used, which keeps R*UN independent 128/256-bit loads in flight per lane. Weights bypass L1; the int8
+// activations (K bytes per row, re-read by every warp) are served from L1. The integer part is exact (__dp4a into
+// int32 per block); scales are applied in fp32 per block and lane partials are combined with warp shuffles.
+//
+// Reference kernels replaced: adapters/llama/ggml-ameva/shaders/ameva_mmvq.comp:73-179 (per-32 int8 GEMV),
+// ameva_mmvqb.comp (per-256), src/shaders/bitnet_gemv_i2_s.comp:84-149; product formulas of ameva_mmq.comp:8-12 and
+// ameva_mmqb.comp:10-16. With DUMP the exact per-block int32 sums are also written (parity evidence; not a fast path).
+#include <cstring>
+
+#include "common.cuh"
+
+namespace amv {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = kGemvThreads / 32;
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Q4_0 x Q8_0.  Q: uint4 [N][U] (byte j: element j low nibble, element j+16 high nibble), S: fp16 [N][U].
+// block: isum = sum nib*q - 8*sum(q); y += float(isum) * d_w * d_a
+// ---------------------------------------------------------------------------------------------------------------------
+template <int M, int R, bool DUMP>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
+                 const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
+                 uint32_t K, uint32_t dst_stride) {
+    constexpr int UN = M <= 2 ? 4 : 2;
+    const uint32_t U = K >> 5;
+    const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row0 = warp * R;
+    if (row0 >= N) return;
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+    size_t rbase[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) rbase[r] = (size_t)min(row0 + r, N - 1) * U;
+
+    for (uint32_t u0 = lane; u0 < U; u0 += 32 * UN) {
+        uint4 wq[UN][R];
+        uint16_t ws[UN][R];
+#pragma unroll
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t u = u0 + 32 * i;
+            if (u < U) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    wq[i][r] = ld_stream_u4(Q + rbase[r] + u);
+                    ws[i][r] = ld_stream_u16(S + rbase[r] + u);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t u = u0 + 32 * i;
+            if (u < U) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const int8_t* ap = AQ + (size_t)m * K + 32u * u;
+                    const uint4 a0 = ld_cached_u4(ap), a1 = ld_cached_u4(ap + 16);
+                    const uint32_t adw = __ldg(AD + (size_t)m * U + u);
+                    const float da = h2f((uint16_t)(adw & 0xFFFFu));
+                    const int sa = (int)(int16_t)(adw >> 16);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const uint4 w = wq[i][r];
+                        int s = 0;
+                        s = dp4a_ss(w.x & 0x0F0F0F0Fu, a0.x, s);
+                        s = dp4a_ss(w.y & 0x0F0F0F0Fu, a0.y, s);
+                        s = dp4a_ss(w.z & 0x0F0F0F0Fu, a0.z, s);
+                        s = dp4a_ss(w.w & 0x0F0F0F0Fu, a0.w, s);
+                        s = dp4a_ss((w.x >> 4) & 0x0F0F0F0Fu, a1.x, s);
+                        s = dp4a_ss((w.y >> 4) & 0x0F0F0F0Fu, a1.y, s);
+                        s = dp4a_ss((w.z >> 4) & 0x0F0F0F0Fu, a1.z, s);
+                        s = dp4a_ss((w.w >> 4) & 0x0F0F0F0Fu, a1.w, s);
+                        s -= 8 * sa;
+                        if (DUMP && row0 + r < N) sums[((size_t)m * N + row0 + r) * U + u] = s;
+                        acc[r][m] += (float)s * h2f(ws[i][r]) * da;
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float v = warp_sum(acc[r][m]);
+            if (lane == 0 && row0 + r < N) dst[(size_t)m * dst_stride + row0 + r] = v;
+        }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Q8_0 x Q8_0.  Q: 32 int8 per unit (256-bit loads), S: fp16 [N][U].  y += float(isum) * (d_w * d_a)
+// ---------------------------------------------------------------------------------------------------------------------
+template <int M, int R, bool DUMP>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
+                 const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
+                 uint32_t K, uint32_t dst_stride) {
+    constexpr int UN = M <= 2 ? 2 : 1;
+    const uint32_t U = K >> 5;
+    const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row0 = warp * R;
+    if (row0 >= N) return;
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+    size_t rbase[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) rbase[r] = (size_t)min(row0 + r, N - 1) * U;
+
+    for (uint32_t u0 = lane; u0 < U; u0 += 32 * UN) {
+        u32x8 wq[UN][R];
+        uint16_t ws[UN][R];
+#pragma unroll
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t u = u0 + 32 * i;
+            if (u < U) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    wq[i][r] = ld_stream_u8(Q + rbase[r] + u);
+                    ws[i][r] = ld_stream_u16(S + rbase[r] + u);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t u = u0 + 32 * i;
+            if (u < U) {
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const int8_t* ap = AQ + (size_t)m * K + 32u * u;
+                    const uint4 a0 = ld_cached_u4(ap), a1 = ld_cached_u4(ap + 16);
+                    const float da = h2f((uint16_t)(__ldg(AD + (size_t)m * U + u) & 0xFFFFu));
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const u32x8& w = wq[i][r];
+                        int s = 0;
+                        s = dp4a_ss(w.v[0], a0.x, s);
+                        s = dp4a_ss(w.v[1], a0.y, s);
+                        s = dp4a_ss(w.v[2], a0.z, s);
+                        s = dp4a_ss(w.v[3], a0.w, s);
+                        s = dp4a_ss(w.v[4], a1.x, s);
+                        s = dp4a_ss(w.v[5], a1.y, s);
+                        s = dp4a_ss(w.v[6], a1.z, s);
+                        s = dp4a_ss(w.v[7], a1.w, s);
+                        if (DUMP && row0 + r < N) sums[((size_t)m * N + row0 + r) * U + u] = s;
+                        acc[r][m] += (float)s * (h2f(ws[i][r]) * da);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float v = warp_sum(acc[r][m]);
+            if (lane == 0 && row0 + r < N) dst[(size_t)m * dst_stride + row0 + r] = v;
+        }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Q4_K x Q8_K.  Q: 128 B per 256-block (8 chunks of 16 B), S: 16 B per block (fp16 d, fp16 dmin, scales[12]).
+// Chunk cc of a block: bytes qs[16cc..16cc+15] = 64-group k = cc/2, half h = cc%2; low nibbles are elements
+// 16h..16h+15 of sub-block 2k, high nibbles the same elements of sub-block 2k+1.
+//   lane integer part: isum = sc[2k]*dot_lo + sc[2k+1]*dot_hi;  mpart = m[2k]*bsums[4k+h] + m[2k+1]*bsums[4k+2+h]
+//   y += (d*d_a)*float(isum) - (dmin*d_a)*float(mpart)          (block-integer form, ameva_mmqb.comp:10-16)
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void q4k_scale_min(const uint4& s, uint32_t j, uint32_t& sc, uint32_t& mn) {
+    // get_scale_min_k4 on the 12 scale bytes held in s.y, s.z, s.w (bytes 0-3, 4-7, 8-11)
+    const uint32_t k = 8u * (j & 3u);
+    const uint32_t b0 = (s.y >> k) & 0xFFu, b1 = (s.z >> k) & 0xFFu, b2 = (s.w >> k) & 0xFFu;
+    if (j < 4u) {
+        sc = b0 & 63u;
+        mn = b1 & 63u;
+    } else {
+        sc = (b2 & 0xFu) | ((b0 >> 6) << 4);
+        mn = (b2 >> 4) | ((b1 >> 6) << 4);
+    }
+}
+
+template <int M, int R, bool DUMP>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_q4_K_kernel(const uint4* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
+                 const uint8_t* __restrict__ AB, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
+                 uint32_t K, uint32_t dst_stride) {
+    constexpr int UN = M <= 2 ? 4 : 2;
+    const uint32_t B = K >> 8, C = K >> 5;  // blocks and 16-byte chunks per row
+    const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row0 = warp * R;
+    if (row0 >= N) return;
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+    size_t rblk[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) rblk[r] = (size_t)min(row0 + r, N - 1) * B;
+
+    for (uint32_t c0 = lane; c0 < C; c0 += 32 * UN) {
+        uint4 wq[UN][R], wsc[UN][R];
+#pragma unroll
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t c = c0 + 32 * i;
+            if (c < C) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    wq[i][r] = ld_stream_u4(Q + rblk[r] * 8u + c);
+                    wsc[i][r] = ld_cached_u4(S + rblk[r] + (c >> 3));  // shared by the 8 lanes of the block
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t c = c0 + 32 * i;
+            if (c < C) {
+                const uint32_t b = c >> 3, cc = c & 7u, k = cc >> 1, h = cc & 1u;
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const int8_t* ap = AQ + (size_t)m * K + 256u * b + 64u * k + 16u * h;
+                    const uint4 alo = ld_cached_u4(ap), ahi = ld_cached_u4(ap + 32);
+                    const uint8_t* ab = AB + ((size_t)m * B + b) * kABBytes;
+                    const uint2 bs = __ldg(reinterpret_cast<const uint2*>(ab + 8u * k));
+                    const float da = __ldg(reinterpret_cast<const float*>(ab + 32));
+                    const int bs_lo = (int)(int16_t)(h ? (bs.x >> 16) : (bs.x & 0xFFFFu));
+                    const int bs_hi = (int)(int16_t)(h ? (bs.y >> 16) : (bs.y & 0xFFFFu));
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const uint4 w = wq[i][r];
+                        int dlo = 0, dhi = 0;
+                        dlo = dp4a_ss(w.x & 0x0F0F0F0Fu, alo.x, dlo);
+                        dlo = dp4a_ss(w.y & 0x0F0F0F0Fu, alo.y, dlo);
+                        dlo = dp4a_ss(w.z & 0x0F0F0F0Fu, alo.z, dlo);
+                        dlo = dp4a_ss(w.w & 0x0F0F0F0Fu, alo.w, dlo);
+                        dhi = dp4a_ss((w.x >> 4) & 0x0F0F0F0Fu, ahi.x, dhi);
+                        dhi = dp4a_ss((w.y >> 4) & 0x0F0F0F0Fu, ahi.y, dhi);
+                        dhi = dp4a_ss((w.z >> 4) & 0x0F0F0F0Fu, ahi.z, dhi);
+                        dhi = dp4a_ss((w.w >> 4) & 0x0F0F0F0Fu, ahi.w, dhi);
+                        uint32_t sc0, mn0, sc1, mn1;
+                        q4k_scale_min(wsc[i][r], 2u * k, sc0, mn0);
+                        q4k_scale_min(wsc[i][r], 2u * k + 1u, sc1, mn1);
+                        const int isum = (int)sc0 * dlo + (int)sc1 * dhi;
+                        const int mpart = (int)mn0 * bs_lo + (int)mn1 * bs_hi;
+                        if (DUMP) {  // the 8 lanes of a block are an aligned lane group
+                            int t0 = isum, t1 = mpart;
+                            const uint32_t gmask = 0xFFu << (lane & 24u);  // C % 8 == 0: the group is in or out whole
+#pragma unroll
+                            for (int o = 1; o < 8; o <<= 1) {
+                                t0 += __shfl_xor_sync(gmask, t0, o);
+                                t1 += __shfl_xor_sync(gmask, t1, o);
+                            }
+                            if (cc == 0 && row0 + r < N) {
+                                int32_t* o = sums + (((size_t)m * N + row0 + r) * B + b) * 2u;
+                                o[0] = t0;
+                                o[1] = t1;
+                            }
+                        }
+                        const float d = h2f((uint16_t)(wsc[i][r].x & 0xFFFFu)), dmin = h2f((uint16_t)(wsc[i][r].x >> 16));
+                        acc[r][m] += (d * da) * (float)isum - (dmin * da) * (float)mpart;
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const float v = warp_sum(acc[r][m]);
+            if (lane == 0 && row0 + r < N) dst[(size_t)m * dst_stride + row0 + r] = v;
+        }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// I2_S x int8 (BitNet).  W: K/4 bytes per row; 16-byte chunk c = half hh = c%2 of 128-block b = c/2. Word w of the
+// chunk, group g: codes = (word >> (6-2g)) & 0x03030303 meet the activation word of elements b*128 + g*32 + 16hh + 4w.
+//   total = sum code*q - sum q (exact int32);  y = float(total) * (act_dequant * w_scale)  [+ y_old when ACC]
+// ---------------------------------------------------------------------------------------------------------------------
+template <int M, int R, bool ACC>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_i2_s_kernel(const uint4* __restrict__ W, const int8_t* __restrict__ AQ, float* __restrict__ dst,
+                 const uint32_t* __restrict__ ACT, uint32_t N, uint32_t K, float w_scale, uint32_t dst_stride,
+                 uint32_t aq_stride) {
+    constexpr int UN = M <= 2 ? 4 : 2;
+    const uint32_t C = K >> 6;  // 16-byte chunks per row
+    const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    const uint32_t row0 = warp * R;
+    if (row0 >= N) return;
+    int acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0;
+    size_t rbase[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) rbase[r] = (size_t)min(row0 + r, N - 1) * C;
+
+    for (uint32_t c0 = lane; c0 < C; c0 += 32 * UN) {
+        uint4 wq[UN][R];
+#pragma unroll
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t c = c0 + 32 * i;
+            if (c < C) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) wq[i][r] = ld_stream_u4(W + rbase[r] + c);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < UN; ++i) {
+            const uint32_t c = c0 + 32 * i;
+            if (c < C) {
+                const uint32_t b = c >> 1, hh = c & 1u;
+#pragma unroll
+                for (int m = 0; m < M; ++m) {
+                    const int8_t* ap = AQ + (size_t)m * aq_stride + 128u * b + 16u * hh;
+                    uint4 ag[4];
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) ag[g] = ld_cached_u4(ap + 32 * g);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const uint4 w = wq[i][r];
+                        int s = acc[r][m];
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            const int sh = 6 - 2 * g;
+                            s = dp4a_ss((w.x >> sh) & 0x03030303u, ag[g].x, s);
+                            s = dp4a_ss((w.y >> sh) & 0x03030303u, ag[g].y, s);
+                            s = dp4a_ss((w.z >> sh) & 0x03030303u, ag[g].z, s);
+                            s = dp4a_ss((w.w >> sh) & 0x03030303u, ag[g].w, s);
+                        }
+                        acc[r][m] = s;
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const int tot = warp_sum_i(acc[r][m]);
+            if (lane == 0 && row0 + r < N) {
+                const int sum = tot - (int)__ldg(ACT + 2 * m + 1);
+                const float total_scale = __fmul_rn(__uint_as_float(__ldg(ACT + 2 * m)), w_scale);
+                const float v = __fmul_rn((float)sum, total_scale);
+                float* o = dst + (size_t)m * dst_stride + row0 + r;
+                *o = ACC ? __fadd_rn(*o, v) : v;
+            }
+        }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// launchers
+// ---------------------------------------------------------------------------------------------------------------------
+template <int R>
+static inline unsigned gemv_blocks(uint32_t N) {
+    const uint32_t warps = (N + R - 1) / R;
+    return (warps + kGemvWarps - 1) / kGemvWarps;
+}
+
+#define AMV_GEMV_CASE(KERNEL, MM, RR, DUMPV, ...)                                                   \
+    case MM:                                                                                        \
+        KERNEL<MM, RR, DUMPV><<<gemv_blocks<RR>(N), kGemvThreads, 0, a.stream>>>(__VA_ARGS__);       \
+        break;
+
+#define AMV_GEMV_SWITCH(KERNEL, DUMPV, ...)                   \
+    switch (M) {                                              \
+        AMV_GEMV_CASE(KERNEL, 1, 2, DUMPV, __VA_ARGS__)       \
+        AMV_GEMV_CASE(KERNEL, 2, 2, DUMPV, __VA_ARGS__)       \
+        AMV_GEMV_CASE(KERNEL, 3, 4, DUMPV, __VA_ARGS__)       \
+        AMV_GEMV_CASE(KERNEL, 4, 4, DUMPV, __VA_ARGS__)       \
+        AMV_GEMV_CASE(KERNEL, 5, 4, DUMPV, __VA_ARGS__)       \
+        AMV_GEMV_CASE(KERNEL, 6, 4, DUMPV, __VA_ARGS__)       \
+        AMV_GEMV_CASE(KERNEL, 7, 4, DUMPV, __VA_ARGS__)       \
+        AMV_GEMV_CASE(KERNEL, 8, 4, DUMPV, __VA_ARGS__)       \
+        default:                                              \
+            return AC_ERR_INVALID_SHAPE;                      \
+    }
+
+// ameva_mmvq_q4_0 / ameva_mmvq_q8_0 [_dump]:
+//   bindings 0 Q, 1 S, 2 AQ, 3 AD, 4 dst f32 [M][dst_stride] (, 5 block sums int32 [M][N][K/32])
+//   push {M (1..8), N, K, dst_stride}
+template <int QBYTES, bool DUMP>
+static AcResult launch_mmvq32(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
+    if (N == 0 || K == 0 || (K & 31u) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t U = K >> 5;
+    if (a.range[0] < (uint64_t)N * U * QBYTES || a.range[1] < (uint64_t)N * U * 2u || a.range[2] < (uint64_t)M * K ||
+        a.range[3] < (uint64_t)M * U * 4u || a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u ||
+        (DUMP && a.range[5] < (uint64_t)M * N * U * 4u))
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    int32_t* sums = DUMP ? (int32_t*)a.ptr[5] : nullptr;
+    if (QBYTES == kQ40QBytes) {
+        AMV_GEMV_SWITCH(gemv_q4_0_kernel, DUMP, (const uint4*)a.ptr[0], (const uint16_t*)a.ptr[1],
+                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride)
+    } else {
+        AMV_GEMV_SWITCH(gemv_q8_0_kernel, DUMP, (const u32x8*)a.ptr[0], (const uint16_t*)a.ptr[1],
+                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride)
+    }
+    return check_launch();
+}
+AcResult launch_mmvq_q4_0(const LaunchArgs& a) { return launch_mmvq32<kQ40QBytes, false>(a); }
+AcResult launch_mmvq_q4_0_dump(const LaunchArgs& a) { return launch_mmvq32<kQ40QBytes, true>(a); }
+AcResult launch_mmvq_q8_0(const LaunchArgs& a) { return launch_mmvq32<kQ80QBytes, false>(a); }
+AcResult launch_mmvq_q8_0_dump(const LaunchArgs& a) { return launch_mmvq32<kQ80QBytes, true>(a); }
+
+// ameva_mmvqb_q4_K [_dump]:
+//   bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 dst (, 5 block sums int32 [M][N][K/256][2]);  push {M (1..8), N, K, dst_stride}
+template <bool DUMP>
+static AcResult launch_mmvqb(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
+    if (N == 0 || K == 0 || (K & 255u) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t B = K >> 8;
+    if (a.range[0] < (uint64_t)N * B * kQ4KQBytes || a.range[1] < (uint64_t)N * B * kQ4KSBytes ||
+        a.range[2] < (uint64_t)M * K || a.range[3] < (uint64_t)M * B * kABBytes ||
+        a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u || (DUMP && a.range[5] < (uint64_t)M * N * B * 8u))
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    int32_t* sums = DUMP ? (int32_t*)a.ptr[5] : nullptr;
+    AMV_GEMV_SWITCH(gemv_q4_K_kernel, DUMP, (const uint4*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2],
+                    (const uint8_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride)
+    return check_launch();
+}
+AcResult launch_mmvqb_q4_K(const LaunchArgs& a) { return launch_mmvqb<false>(a); }
+AcResult launch_mmvqb_q4_K_dump(const LaunchArgs& a) { return launch_mmvqb<true>(a); }
+
+// bitnet_gemv_i2_s_<l32w1|l16w2|l8w4>[_acc]  (argument contract of src/shaders/bitnet_gemv_i2_s.comp:45-80):
+//   bindings 0 packed weights, 1 int8 activations, 2 out f32, 3 act[2] per row {bits of dequant, sum q}
+//   push {in_dim (%128), out_dim, weight_scale_bits, output_offset_words, rows (0 or absent = 1), out_stride (0 =
+//   out_dim)}: the last two extend the reference's single-vector contract to M <= 8 token rows (activation rows in_dim
+//   bytes apart, act 2 words apart, outputs out_stride floats apart).
+template <bool ACC>
+static AcResult launch_i2s(const LaunchArgs& a) {
+    const uint32_t K = a.push[0], N = a.push[1], off = a.push[3];
+    const uint32_t M = a.push[4] ? a.push[4] : 1u, dst_stride = a.push[5] ? a.push[5] : N;
+    if (M > 8) return AC_ERR_INVALID_SHAPE;
+    if (K == 0 || (K & 127u) || N == 0 || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    if (a.range[0] < (uint64_t)N * (K >> 2) || a.range[1] < (uint64_t)M * K ||
+        a.range[2] < ((uint64_t)off + (uint64_t)(M - 1) * dst_stride + N) * 4u || a.range[3] < (uint64_t)M * 8u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    float w_scale;
+    memcpy(&w_scale, &a.push[2], 4);
+    float* dst = (float*)a.ptr[2] + off;
+    AMV_GEMV_SWITCH(gemv_i2_s_kernel, ACC, (const uint4*)a.ptr[0], (const int8_t*)a.ptr[1], dst,
+                    (const uint32_t*)a.ptr[3], N, K, w_scale, dst_stride, K)
+    return check_launch();
+}
+AcResult launch_bitnet_gemv_i2_s(const LaunchArgs& a) { return launch_i2s<false>(a); }
+AcResult launch_bitnet_gemv_i2_s_acc(const LaunchArgs& a) { return launch_i2s<true>(a); }
+
+}  // namespace amv

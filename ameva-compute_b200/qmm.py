@@ -1,0 +1,266 @@
+"""Host side of the quantized MUL_MAT path: weight upload into the device layout, the shape contract, the choice of
+kernel by M, and the dispatch sequence (activation quantize -> GEMV / GEMM) recorded into an ac_runtime batch.
+
+Mirrors, for this path only, what the reference's ggml plugin does on the host
+(adapters/llama/ggml-ameva/ggml-ameva.cpp: ``mul_mat_qmm_reason`` :1326-1377, ``ameva_mmq_plan`` :2486-2503,
+``enc_mul_mat`` :3607-3804, ``enc_mul_mat_mmq`` :2540, ``enc_mul_mat_mmvq`` :2704; weight repack on upload,
+ggml-ameva-buffer.cpp:300-330, 390-416) and the BitNet engine's ``RecordNormQ8`` / ``RecordGemv``
+(adapters/bitnet/src/core/ac_bitnet_engine.cpp:253-288). Anything the kernels cannot run is refused with a reason
+(``MulMatUnsupported``): there is no CPU path behind this module.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import numpy as np
+
+from . import runtime as rt
+
+GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_I2_S = 2, 8, 12, 36
+TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s"}
+BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128}
+Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128}   # payload bytes per block
+S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16}      # scale bytes per block
+GEMV_MAX_M = 8   # decode GEMV serves M <= 8 (ggml-ameva.cpp:3607-3804 sends 2 <= M < 8 to the GEMV family as well)
+AB_BYTES = 48
+
+ROUND_NEAREST_EVEN, ROUND_TIES_AWAY = 0, 1
+Q8K_GGML, Q8K_AMEVA = 0, 1
+
+
+class MulMatUnsupported(Exception):
+    """The op is outside the contract; the message is the reason (the reference logs it once per (op, type, reason))."""
+
+
+def unsupported_reason(ggml_type: int, M: int, N: int, K: int) -> Optional[str]:
+    """Shape contract (mul_mat_qmm_reason, ggml-ameva.cpp:1326-1377, narrowed to the four types built here)."""
+    if ggml_type not in TYPE_NAMES:
+        return f"weight type {ggml_type} not built"
+    if M <= 0 or N <= 0 or K <= 0:
+        return "empty operand"
+    if K % BLOCK[ggml_type]:
+        return f"K={K} is not a multiple of the {TYPE_NAMES[ggml_type]} block ({BLOCK[ggml_type]})"
+    if K % 4 or (K * 4) % 16:
+        return "activation rows must be 16-byte aligned"
+    if N * K >= 2 ** 32 or M * max(N, K) >= 2 ** 32:
+        return "32-bit indexing"
+    return None
+
+
+@dataclass
+class WeightView:
+    """Rows [row0, row0 + rows) of an uploaded weight (what a rank of a row-sharded projection owns)."""
+    weight: "QuantWeight"
+    row0: int
+    rows: int
+
+
+class QuantWeight:
+    """A weight matrix [N][K] in the device layout. ``from_ggml`` repacks ggml blocks on upload; ``to_ggml`` returns the
+    uploaded bytes exactly, whole or by row range (read-back guarantee of tests/ameva_qmm_check.cpp:184-196)."""
+
+    def __init__(self, ctx: rt.Context, ggml_type: int, N: int, K: int, buf: rt.Buffer, s_off: int,
+                 scale: float = 1.0) -> None:
+        self.ctx, self.type, self.N, self.K, self.buf, self.s_off, self.scale = ctx, ggml_type, N, K, buf, s_off, scale
+
+    @classmethod
+    def from_ggml(cls, ctx: rt.Context, ggml_type: int, blocks: np.ndarray, N: int, K: int,
+                  scale: float = 1.0) -> "QuantWeight":
+        why = unsupported_reason(ggml_type, 1, N, K)
+        if why:
+            raise MulMatUnsupported(why)
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        if blocks.size != rt.ggml_nbytes(ggml_type, N, K):
+            raise MulMatUnsupported(f"expected {rt.ggml_nbytes(ggml_type, N, K)} bytes of ggml blocks, got {blocks.size}")
+        total, s_off = rt.device_layout(ggml_type, N, K)
+        dev = rt.repack_to_device(ggml_type, blocks, N, K)
+        return cls(ctx, ggml_type, N, K, ctx.buffer(total, dev), s_off, scale)
+
+    def to_ggml(self, row0: int = 0, rows: Optional[int] = None) -> np.ndarray:
+        rows = self.N - row0 if rows is None else rows
+        nblk_row = self.K // BLOCK[self.type]
+        if self.type == GGML_TYPE_I2_S:
+            return self.buf.read(np.uint8, rows * self.K // 4, row0 * self.K // 4)
+        qb, sb = Q_BYTES[self.type], S_BYTES[self.type]
+        q = self.buf.read(np.uint8, rows * nblk_row * qb, row0 * nblk_row * qb)
+        s = self.buf.read(np.uint8, rows * nblk_row * sb, self.s_off + row0 * nblk_row * sb)
+        pad = (-q.size) % 64   # the codec expects the payload region padded to 64 bytes before the scales
+        dev = np.concatenate([q, np.zeros(pad, np.uint8), s])
+        return rt.repack_from_device(self.type, dev, rows, self.K)
+
+    def view(self, row0: int, rows: int) -> WeightView:
+        if row0 < 0 or rows <= 0 or row0 + rows > self.N:
+            raise MulMatUnsupported("row range outside the weight")
+        return WeightView(self, row0, rows)
+
+    def destroy(self) -> None:
+        self.buf.destroy()
+
+
+def _bindings_for(view: WeightView):
+    """(Q binding, S binding) of a row range; offsets must meet the runtime's 64-byte binding alignment."""
+    w = view.weight
+    nblk_row = w.K // BLOCK[w.type]
+    if w.type == GGML_TYPE_I2_S:
+        off = view.row0 * w.K // 4
+        if off % 64:
+            raise MulMatUnsupported("row range does not start on a 64-byte boundary")
+        return (w.buf, off, view.rows * w.K // 4), None
+    qb, sb = Q_BYTES[w.type], S_BYTES[w.type]
+    qo, so = view.row0 * nblk_row * qb, w.s_off + view.row0 * nblk_row * sb
+    if qo % 64 or so % 64:
+        raise MulMatUnsupported("row range does not start on a 64-byte boundary of the payload / scale regions")
+    return (w.buf, qo, view.rows * nblk_row * qb), (w.buf, so, view.rows * nblk_row * sb)
+
+
+class MulMat:
+    """dst[M][N] (fp32) = activations[M][K] (fp32) x weight[N][K]^T for one weight (or row range) and a maximum M.
+
+    Owns the scratch the path needs (quantized activations and their scales), sized once for ``max_m``; ``record``
+    appends the dispatch sequence to a batch; ``run`` is record + submit + wait. ``path`` reports which kernels ran.
+    """
+
+    def __init__(self, ctx: rt.Context, weight, max_m: int, *, round_mode: int = ROUND_NEAREST_EVEN,
+                 q8k_mode: int = Q8K_GGML, dump_block_sums: bool = False) -> None:
+        self.ctx = ctx
+        self.view = weight if isinstance(weight, WeightView) else weight.view(0, weight.N)
+        w = self.view.weight
+        why = unsupported_reason(w.type, max_m, self.view.rows, w.K)
+        if why:
+            raise MulMatUnsupported(why)
+        self.type, self.N, self.K, self.max_m = w.type, self.view.rows, w.K, max_m
+        self.round_mode, self.q8k_mode, self.dump = round_mode, q8k_mode, dump_block_sums
+        self.qbind, self.sbind = _bindings_for(self.view)
+        K = self.K
+        self.aq = ctx.buffer(max_m * K)
+        if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
+            self.ad = ctx.buffer(max_m * (K // 32) * 4)
+        elif self.type == GGML_TYPE_Q4_K:
+            self.ad = ctx.buffer(max_m * (K // 256) * AB_BYTES)
+        else:
+            self.ad = ctx.buffer(max_m * 8)
+            self.y = ctx.buffer(max_m * K * 4)     # bitnet_norm_q8 writes the fp32 activations it quantized
+            self.qeo = ctx.buffer(64)              # emulated-dot operand: not produced (range too small on purpose)
+        self.sums = None
+        self.path = ""
+
+    # -- scratch accounting (graph_compute reserves the max over nodes, ggml-ameva.cpp:5382-5422)
+    def scratch_bytes(self) -> int:
+        return self.aq.size_bytes + self.ad.size_bytes
+
+    def _sum_shape(self, M: int):
+        if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
+            return (M, self.N, self.K // 32)
+        if self.type == GGML_TYPE_Q4_K:
+            return (M, self.N, self.K // 256, 2)
+        return None
+
+    def record(self, batch: rt.Batch, x: rt.Buffer, dst: rt.Buffer, M: int, *, x_offset: int = 0, dst_offset: int = 0,
+               dst_stride: Optional[int] = None, quantize: bool = True) -> None:
+        """x: fp32 [M][K] at byte x_offset; dst: fp32 rows dst_stride floats apart at byte dst_offset."""
+        if M <= 0 or M > self.max_m:
+            raise MulMatUnsupported(f"M={M} outside 1..{self.max_m}")
+        ctx, K, N = self.ctx, self.K, self.N
+        dst_stride = N if dst_stride is None else dst_stride
+        t = self.type
+        if quantize:
+            if t in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
+                batch.dispatch(ctx.kernel("ameva_quant_a8"), [(x, x_offset), self.aq, self.ad],
+                               [M, K, K, self.round_mode], ((M * (K // 32) * 8 + 255) // 256, 1, 1))
+            elif t == GGML_TYPE_Q4_K:
+                batch.dispatch(ctx.kernel("ameva_quant_a8b"), [(x, x_offset), self.aq, self.ad],
+                               [M, K, K, self.q8k_mode], ((M * (K // 256) * 32 + 255) // 256, 1, 1))
+            else:
+                batch.dispatch(ctx.kernel("bitnet_norm_q8"),
+                               [(x, x_offset), (x, x_offset), (x, x_offset), self.y, self.aq, self.ad, self.qeo],
+                               [K, 0, 0, 0], (M, 1, 1))
+            batch.barrier()
+        if self.dump:
+            shp = self._sum_shape(M)
+            if shp is not None and self.sums is None:
+                self.sums = ctx.buffer(int(np.prod(self._sum_shape(self.max_m))) * 4)
+        # kernel choice by M (ameva_mmq_plan / enc_mul_mat): M <= 8 -> streaming GEMV; larger M -> chunks of 8 through the
+        # same exact dp4a kernels until the tensor-core GEMM takes over
+        self.path = "mmvq" if M <= GEMV_MAX_M else "mmvq-chunks"
+        for m0 in range(0, M, GEMV_MAX_M):
+            mc = min(GEMV_MAX_M, M - m0)
+            d_off = dst_offset + m0 * dst_stride * 4
+            if t == GGML_TYPE_I2_S:
+                name = "bitnet_gemv_i2_s_l32w1"
+                push = [K, N, int(np.float32(self.view.weight.scale).view(np.uint32)), 0, mc, dst_stride]
+                binds = [self.qbind, (self.aq, m0 * K), (dst, d_off), (self.ad, m0 * 8)]
+            else:
+                fam = "ameva_mmvqb" if t == GGML_TYPE_Q4_K else "ameva_mmvq"
+                name = f"{fam}_{TYPE_NAMES[t]}" + ("_dump" if self.dump else "")
+                push = [mc, N, K, dst_stride]
+                per_row = (K // 32) * 4 if t != GGML_TYPE_Q4_K else (K // 256) * AB_BYTES
+                binds = [self.qbind, self.sbind, (self.aq, m0 * K), (self.ad, m0 * per_row), (dst, d_off)]
+                if self.dump:
+                    per_m = int(np.prod(self._sum_shape(1))) * 4
+                    binds.append((self.sums, m0 * per_m))
+            for b in binds:
+                if isinstance(b, tuple) and b[1] % 64:
+                    raise MulMatUnsupported(f"binding offset {b[1]} of {name} is not 64-byte aligned")
+            batch.dispatch(ctx.kernel(name), binds, push, ((N + 15) // 16, 1, 1))
+
+    def run(self, x: rt.Buffer, dst: rt.Buffer, M: int, **kw) -> float:
+        """Record, submit, wait. Returns the GPU time of the batch in microseconds."""
+        batch = self.ctx.batch(64)
+        try:
+            self.record(batch, x, dst, M, **kw)
+            ev = batch.submit()
+            try:
+                ev.wait()
+                return ev.gpu_duration_us()
+            finally:
+                ev.destroy()
+        finally:
+            batch.destroy()
+
+    def read_block_sums(self, M: int) -> np.ndarray:
+        shp = self._sum_shape(M)
+        return self.sums.read(np.int32, int(np.prod(shp))).reshape(shp)
+
+    def read_quantized(self, M: int):
+        """The activation scratch of the last run, in oracle-comparable form."""
+        K = self.K
+        q = self.aq.read(np.int8, M * K).reshape(M, K)
+        if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
+            ad = self.ad.read(np.uint32, M * (K // 32)).reshape(M, K // 32)
+            return q, (ad & 0xFFFF).astype(np.uint16), (ad >> 16).astype(np.uint16).view(np.int16)
+        if self.type == GGML_TYPE_Q4_K:
+            ab = self.ad.read(np.uint8, M * (K // 256) * AB_BYTES).reshape(M, K // 256, AB_BYTES)
+            bsums = np.ascontiguousarray(ab[:, :, :32]).view(np.int16)
+            d = np.ascontiguousarray(ab[:, :, 32:36]).view(np.float32)[..., 0]
+            return q, d, bsums
+        act = self.ad.read(np.uint32, M * 2).reshape(M, 2)
+        return q, act[:, 0].copy().view(np.float32), act[:, 1].copy().view(np.int32)
+
+    def destroy(self) -> None:
+        for name in ("aq", "ad", "y", "qeo", "sums"):
+            b = getattr(self, name, None)
+            if b is not None:
+                b.destroy()
+
+
+def q8_0_blocks_from_scratch(q: np.ndarray, d_bits: np.ndarray) -> np.ndarray:
+    """Reassembles ggml Q8_0 block bytes (fp16 d + 32 int8) from the SoA scratch, for byte comparison with a CPU
+    quantizer."""
+    M, K = q.shape
+    U = K // 32
+    out = np.empty((M, U, 34), np.uint8)
+    out[:, :, 0:2] = d_bits.astype(np.uint16).reshape(M, U, 1).view(np.uint8)
+    out[:, :, 2:] = q.reshape(M, U, 32).view(np.uint8)
+    return out.reshape(M, U * 34)
+
+
+def q8_K_blocks_from_scratch(q: np.ndarray, d: np.ndarray, bsums: np.ndarray) -> np.ndarray:
+    """Reassembles ggml Q8_K block bytes (float d, 256 int8, 16 int16 bsums) from the SoA scratch."""
+    M, K = q.shape
+    B = K // 256
+    out = np.empty((M, B, 292), np.uint8)
+    out[:, :, 0:4] = d.astype(np.float32).reshape(M, B, 1).view(np.uint8)
+    out[:, :, 4:260] = q.reshape(M, B, 256).view(np.uint8)
+    out[:, :, 260:] = np.ascontiguousarray(bsums.reshape(M, B, 16)).view(np.uint8)
+    return out.reshape(M, B * 292)

@@ -1,0 +1,339 @@
+/*
+ * C ABI of the B200 runtime library (libac_runtime_b200.so): the opaque-handle runtime interface of
+ * uno-km/ameva-compute (include/ac_runtime.h, include/ac_base.h, include/ac_error.h, ABI 2.3) served by a CUDA backend.
+ *
+ * A host built against the reference's own headers links or dlopens this library unchanged: every struct below has the
+ * field order, sizes and offsets of docs/abi/ac_runtime_layout.txt, every enumerator the reference's value, every
+ * function the reference's name and signature. Differences, all additive (ABI minor 2.4):
+ *   - AC_BACKEND_CUDA (3) is the only backend kind this library creates contexts for; Vulkan / OpenCL kinds are refused
+ *     with AC_ERR_BACKEND_UNAVAILABLE;
+ *   - kernels are built in: ac_runtime_kernel_create / _create_from_source resolve metadata->kernel_name in the
+ *     library's registry and ignore the SPIR-V / OpenCL C blob; an unknown name is AC_ERR_KERNEL_NOT_FOUND (there is no
+ *     fallback of any kind); ac_runtime_kernel_create_builtin is the short form;
+ *   - buffers are device memory (cudaMalloc): host access only through ac_runtime_buffer_write / read / fill, exactly
+ *     like the reference's OpenCL backend (mapped-pointer calls return AC_ERR_BUFFER_NOT_MAPPED);
+ *   - dispatches of a context run in recording order on one CUDA stream, so batch barriers are implied.
+ * Each declaration cites the reference interface it replaces (file:line inside uno-km/ameva-compute).
+ */
+#ifndef AC_RUNTIME_B200_H
+#define AC_RUNTIME_B200_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- versioning: include/ac_base.h:28-46 ------------------------------------------------------------------------- */
+#define AC_ABI_VERSION_MAJOR 2u
+#define AC_ABI_VERSION_MINOR 4u /* 2.4 = 2.3 + AC_BACKEND_CUDA + ac_runtime_kernel_create_builtin + ac_b200_* */
+#define AC_ABI_VERSION_PATCH 0u
+#define AC_ABI_VERSION 0x00020400u
+#define AC_ABI_MIN_MINOR 1u
+#define AC_ABI_COMPATIBLE(v)                                                                                      \
+    ((((v) >> 16) == AC_ABI_VERSION_MAJOR) && ((((v) >> 8) & 0xFFu) >= AC_ABI_MIN_MINOR) &&                       \
+     ((((v) >> 8) & 0xFFu) <= AC_ABI_VERSION_MINOR) && (((v)&0xFFu) == 0u))
+
+/* ---- backend kinds: include/ac_base.h:51-55 ---------------------------------------------------------------------- */
+typedef uint32_t AcBackendKind;
+#define AC_BACKEND_UNKNOWN ((AcBackendKind)0u)
+#define AC_BACKEND_VULKAN ((AcBackendKind)1u)
+#define AC_BACKEND_OPENCL ((AcBackendKind)2u)
+#define AC_BACKEND_CUDA ((AcBackendKind)3u)
+
+/* ---- result codes: include/ac_base.h:92-139 (values are ABI) ----------------------------------------------------- */
+typedef enum {
+    AC_SUCCESS = 0,
+    AC_ERR_INVALID_CONTEXT = -101,
+    AC_ERR_DRIVER_NOT_FOUND = -102,
+    AC_ERR_DRIVER_SYMBOL_MISSING = -103,
+    AC_ERR_DEVICE_NOT_SUPPORTED = -104,
+    AC_ERR_DRIVER_INIT_FAILED = -105,
+    AC_ERR_INVALID_ARGUMENT = -106,
+    AC_ERR_CONTEXT_MISMATCH = -107,
+    AC_ERR_FEATURE_NOT_SUPPORTED = -108,
+    AC_ERR_INVALID_SHAPE = -109,
+    AC_ERR_ABI_MISMATCH = -110,
+    AC_ERR_BACKEND_UNAVAILABLE = -111,
+    AC_ERR_OUT_OF_HOST_MEMORY = -201,
+    AC_ERR_OUT_OF_DEVICE_MEMORY = -202,
+    AC_ERR_BUFFER_ALIGNMENT_INVALID = -203,
+    AC_ERR_BUFFER_NOT_MAPPED = -204,
+    AC_ERR_NULL_POINTER = -205,
+    AC_ERR_INVALID_BUFFER_SIZE = -206,
+    AC_ERR_KERNEL_BUILD_FAILED = -301,
+    AC_ERR_KERNEL_NOT_FOUND = -302,
+    AC_ERR_KERNEL_ARG_INVALID = -303,
+    AC_ERR_BINARY_CORRUPTED = -304,
+    AC_ERR_INVALID_WORK_GROUP_SIZE = -401,
+    AC_ERR_INVALID_WORK_ITEM_DIMS = -402,
+    AC_ERR_MALI_INFINITE_LOOP_DETECTED = -403,
+    AC_ERR_ADRENO_UNSAFE_SUBGROUP_OP = -404,
+    AC_ERR_LAUNCH_TIMEOUT = -405,
+    AC_ERR_DEVICE_BUSY = -406,
+    AC_ERR_RESOURCE_IN_USE = -407,
+    AC_ERR_NAN_OR_INF_DETECTED = -501,
+    AC_ERR_NUMERICAL_OVERFLOW = -502,
+    AC_ERR_DRIVER_CRASH_OR_LOST = -601,
+    AC_ERR_OS_PROCESS_KILL_SIGNAL = -602,
+    AC_ERR_THERMAL_THROTTLING_TRIPPED = -603
+} AcResult;
+
+/* ---- small shared types: include/ac_base.h:60-84, 165-169 -------------------------------------------------------- */
+typedef struct { uint32_t x, y, z; } AcDim3;
+typedef uint32_t AcSpecConstantType;
+typedef struct { uint32_t constant_id; AcSpecConstantType type; uint32_t value_bits; } AcSpecConstant;
+typedef struct {
+    uint32_t constant_id;
+    AcSpecConstantType type;
+    uint32_t default_value_bits, min_value_bits, max_value_bits;
+    uint32_t overrides_local_size_axis;
+} AcSpecConstantSchemaEntry;
+
+/* ---- opaque handles: include/ac_runtime.h:42-45, 389 ------------------------------------------------------------- */
+typedef struct AcContext AcContext;
+typedef struct AcBuffer AcBuffer;
+typedef struct AcKernel AcKernel;
+typedef struct AcEvent AcEvent;
+typedef struct AcCommandBatch AcCommandBatch;
+
+/* ---- flags: include/ac_runtime.h:54-71, 458-465, 638 ------------------------------------------------------------- */
+typedef uint32_t AcBufferUsageFlags;
+#define AC_BUFFER_USAGE_STORAGE (1u << 0)
+#define AC_BUFFER_USAGE_TRANSFER_SRC (1u << 1)
+#define AC_BUFFER_USAGE_TRANSFER_DST (1u << 2)
+#define AC_BUFFER_USAGE_UNIFORM (1u << 3)
+typedef uint32_t AcShaderStage;
+#define AC_STAGE_COMPUTE ((AcShaderStage)(1u << 5))
+typedef uint32_t AcRuntimeBindingType;
+#define AC_RUNTIME_BINDING_STORAGE_BUFFER ((AcRuntimeBindingType)0u)
+#define AC_RUNTIME_BINDING_UNIFORM_BUFFER ((AcRuntimeBindingType)1u)
+#define AC_BATCH_MAX_DISPATCHES 65536u
+#define AC_BATCH_FLAG_EXPLICIT_BARRIERS (1u << 0)
+#define AC_BATCH_FLAG_TIMESTAMPS (1u << 1)
+#define AC_BATCH_FLAG_DISPATCH_TIMESTAMPS (1u << 2)
+#define AC_KERNEL_SOURCE_BINDING_RANGES (1u << 0)
+#define AC_PIPELINE_IDENTITY_SHA256_HEX_SIZE 65u
+
+/* ---- descriptors: include/ac_runtime.h:76-149, 467-515, 640-648 -------------------------------------------------- */
+typedef struct { uint32_t binding_index; AcRuntimeBindingType binding_type; AcShaderStage stage_flags; } AcRuntimeBindingDesc;
+
+typedef struct {
+    const char* kernel_name; /* the registry key on this backend */
+    const char* entry_point;
+    uint32_t binding_count;
+    const AcRuntimeBindingDesc* bindings;
+    size_t push_constant_size;
+    AcDim3 local_size;
+    uint32_t required_features;
+    const char* expected_spirv_sha256; /* not used by this backend */
+    uint32_t specialization_schema_count;
+    const AcSpecConstantSchemaEntry* specialization_schemas;
+} AcKernelRuntimeMetadata;
+
+typedef struct { uint32_t abi_version, struct_size; AcBackendKind backend_kind; uint32_t flags; } AcContextDesc;
+
+typedef struct {
+    uint32_t abi_version, struct_size;
+    size_t size_bytes;
+    AcBufferUsageFlags usage;
+    uint32_t force_non_coherent;
+} AcBufferDesc;
+
+typedef struct {
+    uint32_t abi_version, struct_size;
+    const uint32_t* spirv_code; /* ignored (may be NULL) */
+    size_t code_size_bytes;     /* ignored */
+    const AcKernelRuntimeMetadata* metadata;
+    uint32_t specialization_count;
+    const AcSpecConstant* specializations;
+} AcKernelDesc;
+
+typedef struct {
+    uint32_t abi_version, struct_size;
+    const char* source; /* ignored (may be NULL) */
+    size_t source_size;
+    const char* build_options;
+    const AcKernelRuntimeMetadata* metadata;
+    uint32_t flags;
+} AcKernelSourceDesc;
+
+typedef struct {
+    uint32_t abi_version, struct_size;
+    AcKernel* kernel;
+    AcBuffer** buffers;
+    uint32_t buffer_count;
+    const void* push_constants;
+    size_t push_constants_size;
+    AcDim3 grid_dim;
+} AcLaunchDesc;
+
+typedef struct { uint32_t abi_version, struct_size, max_dispatches, flags; } AcBatchDesc;
+typedef struct { AcBuffer* buffer; uint64_t offset, range; } AcBufferBinding;
+
+typedef struct {
+    uint32_t abi_version, struct_size;
+    uint32_t dispatches, barriers, elided_barriers, flushes;
+    uint64_t descriptor_cache_hits, descriptor_cache_misses;
+} AcBatchStats;
+
+typedef struct {
+    uint32_t abi_version, struct_size;
+    uint64_t max_storage_buffer_range;
+    uint64_t min_storage_buffer_offset_alignment;
+    uint64_t max_memory_allocation_size;
+    uint32_t max_compute_workgroup_count[3];
+    uint32_t max_compute_workgroup_size[3];
+    uint32_t max_compute_workgroup_invocations;
+    uint32_t max_compute_shared_memory_size;
+    uint32_t max_push_constants_size;
+    uint32_t subgroup_size;
+    uint32_t timestamps_supported;
+    float timestamp_period_ns;
+    uint32_t integer_dot_product;             /* appended in 2.3: filled only when struct_size covers them */
+    uint32_t integer_dot_product_accelerated;
+} AcDeviceLimits;
+
+/* ---- error state: include/ac_error.h:26-49 ----------------------------------------------------------------------- */
+typedef enum AmevaBackendOpKind {
+    AMEVA_BACKEND_OP_NONE = 0,
+    AMEVA_BACKEND_OP_BUFFER_ALLOC,
+    AMEVA_BACKEND_OP_BUFFER_FREE,
+    AMEVA_BACKEND_OP_BUFFER_MAP,
+    AMEVA_BACKEND_OP_BUFFER_UNMAP,
+    AMEVA_BACKEND_OP_COPY_HTOD,
+    AMEVA_BACKEND_OP_COPY_DTOH,
+    AMEVA_BACKEND_OP_DISPATCH,
+    AMEVA_BACKEND_OP_SYNC
+} AmevaBackendOpKind;
+
+typedef struct AmevaBackendErrorState {
+    uint64_t generation;
+    int32_t first_error;
+    AmevaBackendOpKind operation;
+    size_t offset, requested_bytes, capacity_bytes;
+} AmevaBackendErrorState;
+#define AC_GLOBAL_CONTEXT_ID 0ULL
+
+/* ================================================================================================================== */
+/* Entry points. Every out-pointer is NULLed on entry and assigned only on success (include/ac_runtime.h:14).        */
+/* ================================================================================================================== */
+
+/* include/ac_runtime.h:612 */
+uint32_t ac_runtime_abi_version(void);
+
+/* contexts — include/ac_runtime.h:162-186, 536-539, 651; destroy refuses with AC_ERR_RESOURCE_IN_USE while buffers,
+ * kernels, events or batches live (src/runtime/ac_runtime.cpp:161-172). One CUDA device + one stream per context; the
+ * device is cudaGetDevice() of the calling thread at creation (a rank selects its GPU before creating the context). */
+AcResult ac_runtime_context_create(const AcContextDesc* desc, AcContext** out_ctx);
+AcResult ac_runtime_context_destroy(AcContext* ctx);
+AcResult ac_runtime_context_get_device_name(const AcContext* ctx, char* out_name, size_t max_len);
+AcResult ac_runtime_context_get_limits(const AcContext* ctx, AcDeviceLimits* out_limits);
+AcResult ac_runtime_context_get_backend_kind(const AcContext* ctx, AcBackendKind* out_kind);
+
+/* buffers — include/ac_runtime.h:200-264, 663-675 */
+AcResult ac_runtime_buffer_create(AcContext* ctx, const AcBufferDesc* desc, AcBuffer** out_buf);
+AcResult ac_runtime_buffer_destroy(AcBuffer* buf);
+AcResult ac_runtime_buffer_get_mapped_ptr(const AcBuffer* buf, void** out_ptr); /* AC_ERR_BUFFER_NOT_MAPPED */
+AcResult ac_runtime_buffer_get_size(const AcBuffer* buf, size_t* out_size);
+AcResult ac_runtime_buffer_get_allocation_size(const AcBuffer* buf, size_t* out_alloc_size);
+AcResult ac_runtime_buffer_is_coherent(const AcBuffer* buf, uint32_t* out_is_coherent); /* AC_ERR_BUFFER_NOT_MAPPED */
+AcResult ac_runtime_buffer_flush(AcBuffer* buf, size_t offset, size_t size_bytes);      /* AC_ERR_BUFFER_NOT_MAPPED */
+AcResult ac_runtime_buffer_invalidate(AcBuffer* buf, size_t offset, size_t size_bytes); /* AC_ERR_BUFFER_NOT_MAPPED */
+AcResult ac_runtime_buffer_write(AcBuffer* buf, size_t offset, const void* src, size_t size_bytes);
+AcResult ac_runtime_buffer_read(AcBuffer* buf, size_t offset, void* dst, size_t size_bytes);
+AcResult ac_runtime_buffer_fill(AcBuffer* buf, size_t offset, size_t size_bytes, uint8_t value);
+AcResult ac_runtime_buffer_get_address(const AcBuffer* buf, void** out_address); /* the device address */
+
+/* kernels — include/ac_runtime.h:278-332, 657. Validation kept from src/runtime/ac_runtime.cpp:586-660: non-empty
+ * kernel_name and entry_point, non-zero local size, push <= 128 B, <= 16 bindings of compute stage and storage/uniform
+ * type with distinct indices; plus binding_count and push size must match the registry entry
+ * (AC_ERR_KERNEL_ARG_INVALID). */
+AcResult ac_runtime_kernel_create(AcContext* ctx, const AcKernelDesc* desc, AcKernel** out_kernel);
+AcResult ac_runtime_kernel_create_from_source(AcContext* ctx, const AcKernelSourceDesc* desc, AcKernel** out_kernel);
+AcResult ac_runtime_kernel_destroy(AcKernel* kernel);
+AcResult ac_runtime_kernel_get_pipeline_identity(const AcKernel* kernel, char* out_hex, size_t out_hex_size);
+AcResult ac_runtime_kernel_get_effective_local_size(const AcKernel* kernel, AcDim3* out_local_size);
+AcResult ac_runtime_kernel_get_push_constant_size(const AcKernel* kernel, size_t* out_size);
+
+/* dispatch and events — include/ac_runtime.h:348-383. out_event == NULL blocks until the GPU finished. */
+AcResult ac_runtime_dispatch(AcContext* ctx, const AcLaunchDesc* desc, AcEvent** out_event);
+AcResult ac_runtime_event_wait(AcEvent* event, uint64_t timeout_ns); /* AC_ERR_LAUNCH_TIMEOUT when the deadline passes */
+AcResult ac_runtime_event_get_timing(AcEvent* event, uint64_t* out_wall_latency_ns, uint64_t* out_gpu_duration_ns);
+AcResult ac_runtime_event_destroy(AcEvent* event);
+
+/* batches — include/ac_runtime.h:398-451, 544-602 */
+AcResult ac_runtime_batch_begin(AcContext* context, AcCommandBatch** out_batch);
+AcResult ac_runtime_batch_begin_ex(AcContext* context, const AcBatchDesc* desc, AcCommandBatch** out_batch);
+AcResult ac_runtime_batch_dispatch(AcCommandBatch* batch, AcKernel* kernel, const AcLaunchDesc* launch,
+                                   AcEvent** out_event);
+AcResult ac_runtime_batch_dispatch_bindings(AcCommandBatch* batch, AcKernel* kernel, const AcBufferBinding* bindings,
+                                            uint32_t binding_count, const void* push_constants,
+                                            size_t push_constants_size, AcDim3 grid_dim);
+AcResult ac_runtime_batch_barrier(AcCommandBatch* batch);
+AcResult ac_runtime_batch_flush(AcCommandBatch* batch);
+AcResult ac_runtime_batch_submit(AcCommandBatch* batch, AcEvent** out_completion_event);
+AcResult ac_runtime_batch_abort(AcCommandBatch* batch);
+void ac_runtime_batch_destroy(AcCommandBatch* batch);
+AcResult ac_runtime_batch_get_dispatch_times(const AcCommandBatch* batch, uint64_t* out_ns, uint32_t capacity,
+                                             uint32_t* out_count);
+AcResult ac_runtime_batch_get_stats(const AcCommandBatch* batch, AcBatchStats* out_stats);
+
+/* pipeline cache — include/ac_runtime.h:524-531. Kernels are precompiled: the cache is empty (size 0), merge accepts
+ * only an empty blob. */
+AcResult ac_runtime_pipeline_cache_merge(AcContext* ctx, const void* data, size_t size);
+AcResult ac_runtime_pipeline_cache_get_data(AcContext* ctx, void* data, size_t* inout_size);
+
+/* error state — include/ac_error.h:55-82, semantics of src/runtime/ac_error.cpp:30-93 (first error wins per generation) */
+void ac_runtime_set_error(int32_t error_code, AmevaBackendOpKind op, size_t offset, size_t requested_bytes,
+                          size_t capacity_bytes);
+AmevaBackendErrorState ac_runtime_get_error_state(void);
+int32_t ac_runtime_consume_error(void);
+uint64_t ac_runtime_advance_generation(void);
+uint64_t ac_runtime_get_generation(void);
+void ac_runtime_reset_error_state(void);
+void ac_runtime_set_error_ctx(uint64_t context_id, int32_t error_code, AmevaBackendOpKind op, size_t offset,
+                              size_t requested_bytes, size_t capacity_bytes);
+AmevaBackendErrorState ac_runtime_get_error_state_ctx(uint64_t context_id);
+int32_t ac_runtime_consume_error_ctx(uint64_t context_id);
+uint64_t ac_runtime_advance_generation_ctx(uint64_t context_id);
+uint64_t ac_runtime_get_generation_ctx(uint64_t context_id);
+void ac_runtime_reset_error_state_ctx(uint64_t context_id);
+
+/* ================================================================================================================== */
+/* 2.4 additions (no counterpart in the reference unless a citation says which code they stand in for)               */
+/* ================================================================================================================== */
+
+/* Short form of kernel creation: the registry entry supplies binding count, push size and local size. */
+AcResult ac_runtime_kernel_create_builtin(AcContext* ctx, const char* kernel_name, AcKernel** out_kernel);
+/* Registry enumeration: number of built-in kernels and the name of entry i (NULL when out of range). */
+uint32_t ac_b200_kernel_count(void);
+const char* ac_b200_kernel_name(uint32_t index);
+/* The context's CUDA stream (a cudaStream_t), for callers that time or order their own work against it. */
+AcResult ac_b200_context_get_stream(const AcContext* ctx, void** out_stream);
+/* Wrap device memory owned by the caller (e.g. a framework allocator) as a buffer; destroy does not free it. */
+AcResult ac_b200_buffer_import(AcContext* ctx, void* device_ptr, size_t size_bytes, AcBuffer** out_buf);
+/* Asynchronous host->device / device->host copies on the context's stream (pinned host memory for true overlap);
+ * ordered with the context's dispatches, complete after ac_b200_context_synchronize or a later event wait. */
+AcResult ac_b200_buffer_write_async(AcBuffer* buf, size_t offset, const void* src, size_t size_bytes);
+AcResult ac_b200_buffer_read_async(AcBuffer* buf, size_t offset, void* dst, size_t size_bytes);
+AcResult ac_b200_context_synchronize(AcContext* ctx);
+
+/* Weight codec: ggml block bytes <-> the device region layout the kernels read. Stands in for the reference's CPU
+ * repack codec (adapters/llama/ggml-ameva/ggml-ameva-repack.cpp:82-247, ggml-ameva-buffer.cpp:300-330). type is the
+ * ggml type id (2 = Q4_0, 8 = Q8_0, 12 = Q4_K, 36 = I2_S). The device layout is the quant payloads of all blocks, padded
+ * to a multiple of 64 bytes, then the scale fields of all blocks; ac_b200_device_layout reports its total size and the
+ * byte offset of the scale region (I2_S: rows*k/4 bytes, copied unchanged, scale offset = end of payload). Host-side,
+ * pure functions. */
+AcResult ac_b200_device_layout(uint32_t ggml_type, uint64_t rows, uint64_t k, uint64_t* out_total_bytes,
+                               uint64_t* out_scale_offset);
+AcResult ac_b200_repack_to_device(uint32_t ggml_type, const void* ggml_blocks, uint64_t rows, uint64_t k, void* dst);
+AcResult ac_b200_repack_from_device(uint32_t ggml_type, const void* device_layout, uint64_t rows, uint64_t k,
+                                    void* ggml_blocks);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AC_RUNTIME_B200_H */

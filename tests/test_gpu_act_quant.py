@@ -1,0 +1,150 @@
+"""Activation quantizers on the GPU, through the C ABI, byte-compared with the CPU oracle (bit-exact is the bar)."""
+import numpy as np
+import pytest
+
+import oracle
+from conftest import load_pkg
+
+pytestmark = pytest.mark.gpu
+pkg = load_pkg()
+rt, qmm = pkg.runtime, pkg.qmm
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = rt.init()
+    yield c
+    c.destroy()
+
+
+def _acts(M, K, seed):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    if M >= 4:
+        x[1] = 0.0                                   # all-zero row: d = 0, q = 0
+        x[2, :32] = 0.0                              # zero block inside a live row
+        x[3, :32] = (np.arange(32, dtype=np.float32) - 15.0) * 0.5 + 0.25   # exact .5 ties with d = 0.5
+        x[3, 0] = -63.5
+    return x
+
+
+def count_ties_per32(x):
+    x = x.reshape(x.shape[0], -1, 32)
+    d = np.abs(x).max(axis=2, keepdims=True) / np.float32(127.0)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        v = np.where(d != 0, x * (np.float32(1.0) / d), 0).astype(np.float32)
+    return int((np.abs(v - np.trunc(v)) == 0.5).sum())
+
+
+@pytest.mark.parametrize("M,K", [(1, 4096), (1, 32), (5, 96), (37, 1024), (512, 4096), (8, 11008)])
+@pytest.mark.parametrize("round_mode", [0, 1])
+def test_quant_a8_matches_q8_0_bytes(ctx, M, K, round_mode):
+    x = _acts(M, K, 10 + M)
+    xb, aq, ad = ctx.buffer(data=x), ctx.buffer(M * K), ctx.buffer(M * (K // 32) * 4)
+    k = ctx.kernel("ameva_quant_a8")
+    ctx.dispatch(k, [xb, aq, ad], [M, K, K, round_mode], ((M * (K // 32) * 8 + 255) // 256, 1, 1))
+    q = aq.read(np.int8).reshape(M, K)
+    adw = ad.read(np.uint32).reshape(M, K // 32)
+    got = qmm.q8_0_blocks_from_scratch(q, (adw & 0xFFFF).astype(np.uint16))
+    want = oracle.quantize_q8_0(x, round_mode)
+    assert np.array_equal(got, want), f"ties in input: {count_ties_per32(x)}"
+    sums = (adw >> 16).astype(np.uint16).view(np.int16)
+    assert np.array_equal(sums, q.reshape(M, K // 32, 32).sum(axis=2).astype(np.int16))
+    for b in (xb, aq, ad):
+        b.destroy()
+
+
+def test_quant_a8_rounding_modes_differ_only_on_ties(ctx):
+    x = _acts(8, 256, 5)
+    assert count_ties_per32(x) > 0
+    outs = []
+    for mode in (0, 1):
+        xb, aq, ad = ctx.buffer(data=x), ctx.buffer(x.size), ctx.buffer(8 * 8 * 4)
+        ctx.dispatch(ctx.kernel("ameva_quant_a8"), [xb, aq, ad], [8, 256, 256, mode], (2, 1, 1))
+        outs.append(aq.read(np.int8).astype(np.int16))
+        for b in (xb, aq, ad):
+            b.destroy()
+    d = outs[0] - outs[1]
+    assert np.abs(d).max() == 1 and (d != 0).sum() <= count_ties_per32(x)
+
+
+@pytest.mark.parametrize("M,K", [(1, 256), (1, 4096), (3, 11008), (8, 8192), (64, 2048), (512, 4096)])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_quant_a8b_matches_q8_K_bytes(ctx, M, K, mode):
+    x = _acts(M, K, 20 + M)
+    if M >= 3:
+        x[2, 256 - 3] = -np.abs(x[2, :256]).max() * 2   # a block whose max is negative and late
+        x[2, 5] = -x[2, 256 - 3]                        # equal magnitude, opposite sign, earlier: it must win
+    xb, aq, ab = ctx.buffer(data=x), ctx.buffer(M * K), ctx.buffer(M * (K // 256) * 48)
+    ctx.dispatch(ctx.kernel("ameva_quant_a8b"), [xb, aq, ab], [M, K, K, mode], ((M * (K // 256) * 32 + 255) // 256, 1, 1))
+    q = aq.read(np.int8).reshape(M, K)
+    raw = ab.read(np.uint8).reshape(M, K // 256, 48)
+    bsums = np.ascontiguousarray(raw[:, :, :32]).view(np.int16)
+    d = np.ascontiguousarray(raw[:, :, 32:36]).view(np.float32)[..., 0]
+    got = qmm.q8_K_blocks_from_scratch(q, d, bsums)
+    want = oracle.quantize_q8_K(x, mode)
+    assert np.array_equal(got, want)
+    for b in (xb, aq, ab):
+        b.destroy()
+
+
+@pytest.mark.parametrize("M,K", [(1, 2560), (1, 6912), (128, 2560), (7, 128)])
+def test_bitnet_norm_q8_plain_quantize_matches_cpu(ctx, M, K):
+    """mode 0, do_norm 0: the stage is quantize_activation_int8 (llama_bitnet_core.cpp:914-926): bit-exact q, factor, sum."""
+    x = _acts(M, K, 30 + M)
+    xb, y, q, act, qeo = ctx.buffer(data=x), ctx.buffer(x.nbytes), ctx.buffer(M * K), ctx.buffer(M * 8), ctx.buffer(M * K * 2)
+    ctx.dispatch(ctx.kernel("bitnet_norm_q8", 7, 16, (256, 1, 1)), [xb, xb, xb, y, q, act, qeo], [K, 0, 0, 0], (M, 1, 1))
+    wq, wdq, wsum = oracle.quantize_i8_token(x)
+    assert np.array_equal(q.read(np.int8).reshape(M, K), wq)
+    a = act.read(np.uint32).reshape(M, 2)
+    assert np.array_equal(a[:, 0].copy().view(np.float32).view(np.uint32), wdq.view(np.uint32))
+    assert np.array_equal(a[:, 1].copy().view(np.int32), wsum)
+    assert np.array_equal(y.read(np.float32).reshape(M, K), x)
+    # the emulated-dot operand pairs (q0+128)<<16 | (q2+128), (q1+128)<<16 | (q3+128)
+    eo = qeo.read(np.uint32).reshape(M, K // 4, 2)
+    u = (wq.astype(np.int32) + 128).reshape(M, K // 4, 4)
+    assert np.array_equal(eo[..., 0], (u[..., 0] << 16) | u[..., 2])
+    assert np.array_equal(eo[..., 1], (u[..., 1] << 16) | u[..., 3])
+    for b in (xb, y, q, act, qeo):
+        b.destroy()
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_bitnet_norm_q8_norm_modes(ctx, mode):
+    """With the norm on, y is checked against a float64 statement to fp32 tolerance (the reduction order differs from
+    the CPU loop), and q must be the exact CPU quantization of the y the GPU produced."""
+    K, eps = 2560, 1e-5
+    rng = np.random.default_rng(40 + mode)
+    a, b = rng.standard_normal((2, K)).astype(np.float32), rng.standard_normal((2, K)).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    ab_, bb, wb = ctx.buffer(data=a), ctx.buffer(data=b), ctx.buffer(data=w)
+    y, q, act, qeo = ctx.buffer(a.nbytes), ctx.buffer(2 * K), ctx.buffer(16), ctx.buffer(64)
+    ctx.dispatch(ctx.kernel("bitnet_norm_q8"), [ab_, bb, wb, y, q, act, qeo],
+                 [K, int(np.float32(eps).view(np.uint32)), mode, 1], (2, 1, 1))
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    h = a64 if mode == 0 else (np.maximum(a64, 0) ** 2 * b64 if mode == 1 else a64 / (1 + np.exp(-a64)) * b64)
+    want = h / np.sqrt((h * h).mean(axis=1, keepdims=True) + eps) * w
+    got = y.read(np.float32).reshape(2, K)
+    assert np.allclose(got, want, rtol=2e-5, atol=1e-6)
+    wq, wdq, wsum = oracle.quantize_i8_token(got)
+    assert np.array_equal(q.read(np.int8).reshape(2, K), wq)
+    av = act.read(np.uint32).reshape(2, 2)
+    assert np.array_equal(av[:, 0].copy().view(np.float32), wdq) and np.array_equal(av[:, 1].copy().view(np.int32), wsum)
+    for x in (ab_, bb, wb, y, q, act, qeo):
+        x.destroy()
+
+
+def test_quant_argument_errors_are_explicit(ctx):
+    xb, aq, ad = ctx.buffer(4096), ctx.buffer(1024), ctx.buffer(128)
+    k = ctx.kernel("ameva_quant_a8")
+    with pytest.raises(rt.AmevaComputeError) as e:
+        ctx.dispatch(k, [xb, aq, ad], [1, 48, 48, 0])          # K not a multiple of 32
+    assert e.value.code == rt.AC_ERR_KERNEL_ARG_INVALID
+    with pytest.raises(rt.AmevaComputeError) as e:
+        ctx.dispatch(k, [xb, aq, ad], [4, 1024, 1024, 0])      # source buffer too small for 4 rows
+    assert e.value.code == rt.AC_ERR_INVALID_BUFFER_SIZE
+    with pytest.raises(rt.AmevaComputeError) as e:
+        ctx.dispatch(k, [xb, aq], [1, 1024, 1024, 0])          # wrong binding count
+    assert e.value.code == rt.AC_ERR_KERNEL_ARG_INVALID
+    for b in (xb, aq, ad):
+        b.destroy()

@@ -1,0 +1,186 @@
+"""Decode GEMV (M <= 8) on the GPU through the C ABI against the CPU oracle: exact per-block int32 sums, bit-equal
+activation quantization, fp32 outputs within max normalised error 1e-3 (the stated tolerance of the path)."""
+import numpy as np
+import pytest
+
+import oracle
+from conftest import load_pkg
+from helpers import I2_S, Q4_0, Q4_K, Q8_0, dequantize, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+
+pytestmark = pytest.mark.gpu
+pkg = load_pkg()
+rt, qmm = pkg.runtime, pkg.qmm
+TOL = 1e-3          # max |y - y_ref| / max |y_ref|
+STRICT_TOL = 1e-4   # per element against sum_k |w*x| in float64 (the reference's gate form, tests/ameva_qmm_check.cpp:205-217)
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = rt.init()
+    yield c
+    c.destroy()
+
+
+def run_case(ctx, t, M, N, K, seed=0, dump=True, check_strict=True):
+    blocks, scale = make_weights(t, N, K, seed)
+    x = make_acts(M, K, seed + 1)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    mm = qmm.MulMat(ctx, w, M, dump_block_sums=dump and t != I2_S)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    dst.fill(0xFF)
+    mm.run(xb, dst, M)
+    y = dst.read(np.float32).reshape(M, N)
+    want, sums, aq = oracle_mul_mat(t, blocks, scale, x, N, K)
+    # 1. activation quantization: bytes equal
+    if t in (Q4_0, Q8_0):
+        q, dbits, _ = mm.read_quantized(M)
+        assert np.array_equal(qmm.q8_0_blocks_from_scratch(q, dbits), aq)
+    elif t == Q4_K:
+        q, d, bs = mm.read_quantized(M)
+        assert np.array_equal(qmm.q8_K_blocks_from_scratch(q, d, bs), aq)
+    else:
+        q, dq, sm = mm.read_quantized(M)
+        assert np.array_equal(q, aq[0]) and np.array_equal(dq, aq[1]) and np.array_equal(sm, aq[2])
+    # 2. exact integer sums
+    if t == I2_S:
+        assert np.array_equal(y, want), "I2_S outputs are exact integers times one fp32 scale: bit-equal"
+    elif dump:
+        assert np.array_equal(mm.read_block_sums(M), sums)
+    # 3. fp32 outputs
+    assert np.isfinite(y).all()
+    err = max_normalised_error(y, want)
+    assert err <= TOL, err
+    if check_strict:
+        ref64, norm = oracle.mul_mat_f64(dequantize(t, blocks, scale, N, K), _dequant_acts(t, aq, M, K))
+        rel = np.max(np.abs(y - ref64) / np.maximum(norm, 1e-30))
+        assert rel <= STRICT_TOL, rel
+    # 4. weights read back as the uploaded ggml bytes, whole and a partial row range
+    if N >= 3:
+        assert np.array_equal(w.to_ggml(), np.asarray(blocks).reshape(-1))
+    for b in (xb, dst):
+        b.destroy()
+    mm.destroy()
+    w.destroy()
+    return err
+
+
+def _dequant_acts(t, aq, M, K):
+    if t in (Q4_0, Q8_0):
+        return oracle.dequantize_q8_0(aq).reshape(M, K)
+    if t == Q4_K:
+        return oracle.dequantize_q8_K(aq).reshape(M, K)
+    q, dq, _ = aq
+    return q.astype(np.float32) * dq[:, None]
+
+
+SMALL = [(1, 1, 256), (1, 3, 256), (2, 17, 512), (3, 64, 1024), (4, 130, 768), (5, 33, 2048), (7, 250, 256), (8, 96, 4096)]
+
+
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
+@pytest.mark.parametrize("M,N,K", SMALL)
+def test_gemv_small_shapes(ctx, t, M, N, K):
+    run_case(ctx, t, M, N, K, seed=M * 7 + N)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 128), (1, 5, 384), (2, 64, 2560), (8, 130, 1280), (3, 640, 2560)])
+def test_gemv_i2s_small_shapes(ctx, M, N, K):
+    run_case(ctx, I2_S, M, N, K, seed=M + N)
+
+
+@pytest.mark.parametrize("t,K", [(Q4_0, 32), (Q4_0, 96), (Q8_0, 32), (Q8_0, 160)])
+def test_gemv_k_not_multiple_of_lane_span(ctx, t, K):
+    run_case(ctx, t, 2, 9, K, seed=K)
+
+
+def test_config1_q4_0_decode_full_size(ctx):
+    """Configuration 1: W 4096 x 4096 Q4_0, M = 1, seed 0."""
+    run_case(ctx, Q4_0, 1, 4096, 4096, seed=0)
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (11008, 4096), (4096, 11008)])
+@pytest.mark.parametrize("M", [1, 8])
+def test_config3_q4_K_llama7b_shapes(ctx, M, N, K):
+    run_case(ctx, Q4_K, M, N, K, seed=3, check_strict=(M == 1))
+
+
+@pytest.mark.parametrize("N,K", [(2560, 2560), (640, 2560), (6912, 2560), (2560, 6912)])
+def test_config4_bitnet_shapes_decode(ctx, N, K):
+    run_case(ctx, I2_S, 1, N, K, seed=4, check_strict=False)
+
+
+def test_config5_q4_K_70b_ffn_decode(ctx):
+    run_case(ctx, Q4_K, 1, 28672, 8192, seed=5, check_strict=False)
+    run_case(ctx, Q4_K, 1, 8192, 28672, seed=6, check_strict=False)
+
+
+def test_q8_0_decode_11008x4096(ctx):
+    run_case(ctx, Q8_0, 1, 11008, 4096, seed=2)
+    run_case(ctx, Q8_0, 8, 11008, 4096, seed=2, check_strict=False)
+
+
+def test_i2s_reference_contract_single_vector_and_acc(ctx):
+    """The argument contract of the reference's bitnet_gemv_i2_s (4 bindings, 16 bytes of push constants, one vector;
+    `_acc` adds into the output): what adapters/bitnet/src/core/ac_bitnet_engine.cpp:280-288 records."""
+    N, K = 640, 2560
+    blocks, scale = make_weights(I2_S, N, K, 9)
+    x = make_acts(1, K, 10)
+    q, dq, sm = oracle.quantize_i8_token(x)
+    want, _ = oracle.mul_mat_i2_s_i8(blocks, scale, q, dq, 1, N, K)
+    wb, qb = ctx.buffer(data=blocks), ctx.buffer(data=q)
+    act = ctx.buffer(data=np.array([dq.view(np.uint32)[0], np.uint32(sm[0] & 0xFFFFFFFF)], np.uint32))
+    out = ctx.buffer((N + 64) * 4)
+    out.fill(0)
+    push = [K, N, int(np.float32(scale).view(np.uint32)), 64]           # output_offset_words = 64
+    for name in ("bitnet_gemv_i2_s_l32w1", "bitnet_gemv_i2_s_l16w2", "bitnet_gemv_i2_s_l8w4"):
+        k = ctx.kernel(name, 4, 16, (32, 4, 1))                           # the reference's metadata: 16 B of push
+        ctx.dispatch(k, [wb, qb, out, act], push, ((N + 3) // 4, 1, 1))
+        got = out.read(np.float32)
+        assert np.array_equal(got[64:], want[0]) and not got[:64].any()
+    res = np.random.default_rng(1).standard_normal(N + 64).astype(np.float32)
+    out.write(res)
+    ctx.dispatch(ctx.kernel("bitnet_gemv_i2_s_l32w1_acc", 4, 16, (32, 4, 1)), [wb, qb, out, act], push, ((N + 3) // 4, 1, 1))
+    assert np.array_equal(out.read(np.float32)[64:], res[64:] + want[0])   # two separate roundings, as the CPU path
+    for b in (wb, qb, act, out):
+        b.destroy()
+
+
+def test_row_range_view_matches_full(ctx):
+    """A rank of a row-sharded projection binds rows [r0, r0+n) of the uploaded weight (the reference's VIEW placement,
+    tests/ameva_qmm_check.cpp:103-127)."""
+    N, K, M = 512, 1024, 2
+    for t in (Q4_0, Q8_0, Q4_K, I2_S):
+        blocks, scale = make_weights(t, N, K, 11)
+        x = make_acts(M, K, 12)
+        w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+        want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K)
+        xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+        for r0, n in ((0, 256), (256, 256)):
+            mm = qmm.MulMat(ctx, w.view(r0, n), M)
+            mm.run(xb, dst, M, dst_offset=r0 * 4, dst_stride=N)
+            mm.destroy()
+            part = w.to_ggml(r0, n)
+            per_row = blocks.reshape(N, -1).shape[1]
+            assert np.array_equal(part, blocks.reshape(N, -1)[r0:r0 + n].reshape(-1)), (t, r0, per_row)
+        y = dst.read(np.float32).reshape(M, N)
+        assert max_normalised_error(y, want) <= TOL
+        for b in (xb, dst):
+            b.destroy()
+        w.destroy()
+
+
+def test_unsupported_is_an_explicit_error_not_a_fallback(ctx):
+    with pytest.raises(qmm.MulMatUnsupported):
+        qmm.QuantWeight.from_ggml(ctx, 14, np.zeros(210, np.uint8), 1, 256)        # Q6_K: not built
+    with pytest.raises(rt.AmevaComputeError) as e:
+        ctx.kernel("ameva_mmvq_q6_K")
+    assert e.value.code == rt.AC_ERR_KERNEL_NOT_FOUND
+    blocks, _ = make_weights(Q4_0, 8, 256, 0)
+    w = qmm.QuantWeight.from_ggml(ctx, Q4_0, blocks, 8, 256)
+    k = ctx.kernel("ameva_mmvq_q4_0")
+    bufs = [w.buf, w.buf, ctx.buffer(256 * 9), ctx.buffer(8 * 9 * 4), ctx.buffer(8 * 9 * 4)]
+    with pytest.raises(rt.AmevaComputeError) as e:
+        ctx.dispatch(k, bufs, [9, 8, 256, 8])                                         # M = 9 is not a GEMV shape
+    assert e.value.code == rt.AC_ERR_INVALID_SHAPE
+    for b in bufs[2:]:
+        b.destroy()
+    w.destroy()
