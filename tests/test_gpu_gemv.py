@@ -127,7 +127,7 @@ def test_i2s_reference_contract_single_vector_and_acc(ctx):
     q, dq, sm = oracle.quantize_i8_token(x)
     want, _ = oracle.mul_mat_i2_s_i8(blocks, scale, q, dq, 1, N, K)
     wb, qb = ctx.buffer(data=blocks), ctx.buffer(data=q)
-    act = ctx.buffer(data=np.array([dq.view(np.uint32)[0], np.uint32(sm[0] & 0xFFFFFFFF)], np.uint32))
+    act = ctx.buffer(data=np.array([dq.view(np.uint32)[0], sm.view(np.uint32)[0]], np.uint32))
     out = ctx.buffer((N + 64) * 4)
     out.fill(0)
     push = [K, N, int(np.float32(scale).view(np.uint32)), 64]           # output_offset_words = 64
