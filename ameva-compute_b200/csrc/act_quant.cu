@@ -17,9 +17,10 @@ namespace amv {
 //   d = amax / 127 (f32); id = d ? 1/d : 0; q = clamp(round(x*id), +-127); stored d = fp16(d) (what the dot uses).
 //   round_mode 0 = ties-to-even (reference shaders, ggml SIMD quantizers), 1 = ties-away (ggml quantize_row_q8_0_ref).
 // ---------------------------------------------------------------------------------------------------------------------
+template <bool WRITE_H>
 __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
-                                                         uint32_t* __restrict__ ad, uint32_t M, uint32_t K,
-                                                         uint32_t src_stride, uint32_t round_mode) {
+                                                         uint32_t* __restrict__ ad, __half* __restrict__ ah, uint32_t M,
+                                                         uint32_t K, uint32_t src_stride, uint32_t round_mode) {
     const uint32_t U = K >> 5;
     const uint64_t total = (uint64_t)M * U;
     const uint64_t gi = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;  // unit index
@@ -49,6 +50,15 @@ __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict
                            ((uint32_t)(q[3] & 0xFF) << 24);
         reinterpret_cast<uint32_t*>(aq + (size_t)m * K + 32u * u)[sub] = w;
         if (sub == 0) ad[(size_t)m * U + u] = (uint32_t)f2h(d) | ((uint32_t)(s & 0xFFFF) << 16);
+        if (WRITE_H) {   // the tensor-core operand: fp16(q * d) with d the fp16-rounded scale the dot product uses
+            const float dh = h2f(f2h(d));
+            const __half2 h01 = __floats2half2_rn((float)q[0] * dh, (float)q[1] * dh);
+            const __half2 h23 = __floats2half2_rn((float)q[2] * dh, (float)q[3] * dh);
+            uint2 o;
+            o.x = *reinterpret_cast<const uint32_t*>(&h01);
+            o.y = *reinterpret_cast<const uint32_t*>(&h23);
+            *reinterpret_cast<uint2*>(ah + (size_t)m * K + 32u * u + 4u * sub) = o;
+        }
     }
 }
 
@@ -59,9 +69,10 @@ __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict
 //   mode 1 (ameva_quant_a8b.comp): d = amax/127, q = clamp(roundEven(x * (1/d)), +-127).
 //   bsums[j] = sum of q over elements 16j..16j+15.
 // ---------------------------------------------------------------------------------------------------------------------
+template <bool WRITE_H>
 __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
-                                                         uint8_t* __restrict__ ab, uint32_t M, uint32_t K,
-                                                         uint32_t src_stride, uint32_t mode) {
+                                                         uint8_t* __restrict__ ab, __half* __restrict__ ah, uint32_t M,
+                                                         uint32_t K, uint32_t src_stride, uint32_t mode) {
     const uint32_t B = K >> 8;
     const uint64_t total = (uint64_t)M * B;
     const uint64_t gi = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -122,6 +133,15 @@ __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict
         w1 |= (uint32_t)(q[i + 4] & 0xFF) << (8 * i);
     }
     *reinterpret_cast<uint2*>(aq + (size_t)m * K + 256u * b + 8u * lane) = make_uint2(w0, w1);
+    if (WRITE_H) {   // the tensor-core operand: fp16(q * d)
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __half2 hh = __floats2half2_rn((float)q[2 * i] * d, (float)q[2 * i + 1] * d);
+            o[i] = *reinterpret_cast<const uint32_t*>(&hh);
+        }
+        *reinterpret_cast<uint4*>(ah + (size_t)m * K + 256u * b + 8u * lane) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
     s += __shfl_xor_sync(0xffffffffu, s, 1);  // lanes 2j, 2j+1 -> 16-element group j
     uint8_t* blk = ab + ((size_t)m * B + b) * kABBytes;
     if ((lane & 1u) == 0u) reinterpret_cast<int16_t*>(blk)[lane >> 1] = (int16_t)s;
@@ -235,34 +255,45 @@ __global__ void __launch_bounds__(256) bitnet_norm_q8_kernel(const float* __rest
 // launchers
 // ---------------------------------------------------------------------------------------------------------------------
 // ameva_quant_a8: bindings 0 src f32, 1 AQ, 2 AD; push {M, K, src_stride (floats), round_mode}
-AcResult launch_quant_a8(const LaunchArgs& a) {
+// ameva_quant_a8_f16: the same plus binding 3 AH, fp16 [M][K] = fp16(q * d), the activation operand of ameva_mmtc_*
+template <bool WRITE_H>
+static AcResult launch_quant_a8_t(const LaunchArgs& a) {
     const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], round_mode = a.push[3];
     if (M == 0 || K == 0 || (K & 31u) || stride < K || (stride & 3u) || round_mode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
     const uint64_t U = K >> 5;
-    if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || a.range[1] < (uint64_t)M * K || a.range[2] < (uint64_t)M * U * 4u)
+    if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || a.range[1] < (uint64_t)M * K ||
+        a.range[2] < (uint64_t)M * U * 4u || (WRITE_H && a.range[3] < (uint64_t)M * K * 2u))
         return AC_ERR_INVALID_BUFFER_SIZE;
     const uint64_t threads = (uint64_t)M * U * 8u;
     const uint64_t blocks = (threads + 255u) / 256u;
     if (blocks > 0x7FFFFFFFull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    quant_q8_0_kernel<<<(unsigned)blocks, 256, 0, a.stream>>>((const float*)a.ptr[0], (int8_t*)a.ptr[1],
-                                                              (uint32_t*)a.ptr[2], M, K, stride, round_mode);
+    quant_q8_0_kernel<WRITE_H><<<(unsigned)blocks, 256, 0, a.stream>>>(
+        (const float*)a.ptr[0], (int8_t*)a.ptr[1], (uint32_t*)a.ptr[2], WRITE_H ? (__half*)a.ptr[3] : nullptr, M, K,
+        stride, round_mode);
     return check_launch();
 }
+AcResult launch_quant_a8(const LaunchArgs& a) { return launch_quant_a8_t<false>(a); }
+AcResult launch_quant_a8_f16(const LaunchArgs& a) { return launch_quant_a8_t<true>(a); }
 
 // ameva_quant_a8b: bindings 0 src f32, 1 AQ, 2 AB; push {M, K, src_stride (floats), mode}
-AcResult launch_quant_a8b(const LaunchArgs& a) {
+// ameva_quant_a8b_f16: the same plus binding 3 AH, fp16 [M][K] = fp16(q * d)
+template <bool WRITE_H>
+static AcResult launch_quant_a8b_t(const LaunchArgs& a) {
     const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], mode = a.push[3];
     if (M == 0 || K == 0 || (K & 255u) || stride < K || (stride & 3u) || mode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
     const uint64_t B = K >> 8;
     if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || a.range[1] < (uint64_t)M * K ||
-        a.range[2] < (uint64_t)M * B * kABBytes)
+        a.range[2] < (uint64_t)M * B * kABBytes || (WRITE_H && a.range[3] < (uint64_t)M * K * 2u))
         return AC_ERR_INVALID_BUFFER_SIZE;
     const uint64_t blocks = ((uint64_t)M * B * 32u + 255u) / 256u;
     if (blocks > 0x7FFFFFFFull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    quant_q8_K_kernel<<<(unsigned)blocks, 256, 0, a.stream>>>((const float*)a.ptr[0], (int8_t*)a.ptr[1],
-                                                              (uint8_t*)a.ptr[2], M, K, stride, mode);
+    quant_q8_K_kernel<WRITE_H><<<(unsigned)blocks, 256, 0, a.stream>>>(
+        (const float*)a.ptr[0], (int8_t*)a.ptr[1], (uint8_t*)a.ptr[2], WRITE_H ? (__half*)a.ptr[3] : nullptr, M, K,
+        stride, mode);
     return check_launch();
 }
+AcResult launch_quant_a8b(const LaunchArgs& a) { return launch_quant_a8b_t<false>(a); }
+AcResult launch_quant_a8b_f16(const LaunchArgs& a) { return launch_quant_a8b_t<true>(a); }
 
 // bitnet_norm_q8: bindings 0 a, 1 b, 2 w, 3 y, 4 q, 5 act, 6 qeo; push {dim, eps_bits, mode, do_norm}; grid.x = rows
 // (argument contract of src/shaders/bitnet_norm_q8.comp:20-44, extended from one row to grid.x rows).

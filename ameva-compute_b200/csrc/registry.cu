@@ -15,7 +15,13 @@ namespace amv {
 
 AcResult launch_quant_a8(const LaunchArgs&);
 AcResult launch_quant_a8b(const LaunchArgs&);
+AcResult launch_quant_a8_f16(const LaunchArgs&);
+AcResult launch_quant_a8b_f16(const LaunchArgs&);
 AcResult launch_bitnet_norm_q8(const LaunchArgs&);
+AcResult launch_mmtc_q4_0(const LaunchArgs&);
+AcResult launch_mmtc_q8_0(const LaunchArgs&);
+AcResult launch_mmtc_q4_K(const LaunchArgs&);
+AcResult launch_bitnet_gemm_i2_s(const LaunchArgs&);
 AcResult launch_mmvq_q4_0(const LaunchArgs&);
 AcResult launch_mmvq_q4_0_dump(const LaunchArgs&);
 AcResult launch_mmvq_q8_0(const LaunchArgs&);
@@ -28,7 +34,13 @@ AcResult launch_bitnet_gemv_i2_s_acc(const LaunchArgs&);
 static const KernelEntry kTable[] = {
     {"ameva_quant_a8", 3, 16, {256, 1, 1}, launch_quant_a8},
     {"ameva_quant_a8b", 3, 16, {256, 1, 1}, launch_quant_a8b},
+    {"ameva_quant_a8_f16", 4, 16, {256, 1, 1}, launch_quant_a8_f16},
+    {"ameva_quant_a8b_f16", 4, 16, {256, 1, 1}, launch_quant_a8b_f16},
     {"bitnet_norm_q8", 7, 16, {256, 1, 1}, launch_bitnet_norm_q8},
+    {"ameva_mmtc_q4_0", 4, 16, {320, 1, 1}, launch_mmtc_q4_0},
+    {"ameva_mmtc_q8_0", 4, 16, {320, 1, 1}, launch_mmtc_q8_0},
+    {"ameva_mmtc_q4_K", 4, 16, {320, 1, 1}, launch_mmtc_q4_K},
+    {"bitnet_gemm_i2_s", 4, 20, {320, 1, 1}, launch_bitnet_gemm_i2_s},
     {"ameva_mmvq_q4_0", 5, 16, {256, 1, 1}, launch_mmvq_q4_0},
     {"ameva_mmvq_q4_0_dump", 6, 16, {256, 1, 1}, launch_mmvq_q4_0_dump},
     {"ameva_mmvq_q8_0", 5, 16, {256, 1, 1}, launch_mmvq_q8_0},

@@ -122,7 +122,7 @@ class MulMat:
     """
 
     def __init__(self, ctx: rt.Context, weight, max_m: int, *, round_mode: int = ROUND_NEAREST_EVEN,
-                 q8k_mode: int = Q8K_GGML, dump_block_sums: bool = False) -> None:
+                 q8k_mode: int = Q8K_GGML, dump_block_sums: bool = False, exact: bool = False) -> None:
         self.ctx = ctx
         self.view = weight if isinstance(weight, WeightView) else weight.view(0, weight.N)
         w = self.view.weight
@@ -131,6 +131,9 @@ class MulMat:
             raise MulMatUnsupported(why)
         self.type, self.N, self.K, self.max_m = w.type, self.view.rows, w.K, max_m
         self.round_mode, self.q8k_mode, self.dump = round_mode, q8k_mode, dump_block_sums
+        # exact = keep every M on the dp4a kernels (exact per-block int32 sums); otherwise M > 8 runs on tensor cores
+        self.exact = exact or dump_block_sums
+        self.tc_ok = self.K % (128 if self.type == GGML_TYPE_I2_S else 64) == 0
         self.qbind, self.sbind = _bindings_for(self.view)
         K = self.K
         self.aq = ctx.buffer(max_m * K)
@@ -142,12 +145,15 @@ class MulMat:
             self.ad = ctx.buffer(max_m * 8)
             self.y = ctx.buffer(max_m * K * 4)     # bitnet_norm_q8 writes the fp32 activations it quantized
             self.qeo = ctx.buffer(64)              # emulated-dot operand: not produced (range too small on purpose)
+        self.ah = None
+        if max_m > GEMV_MAX_M and not self.exact and self.tc_ok and self.type != GGML_TYPE_I2_S:
+            self.ah = ctx.buffer(max_m * K * 2)    # fp16(q * d): the activation operand of the tensor-core GEMM
         self.sums = None
         self.path = ""
 
     # -- scratch accounting (graph_compute reserves the max over nodes, ggml-ameva.cpp:5382-5422)
     def scratch_bytes(self) -> int:
-        return self.aq.size_bytes + self.ad.size_bytes
+        return self.aq.size_bytes + self.ad.size_bytes + (self.ah.size_bytes if self.ah else 0)
 
     def _sum_shape(self, M: int):
         if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
@@ -164,12 +170,15 @@ class MulMat:
         ctx, K, N = self.ctx, self.K, self.N
         dst_stride = N if dst_stride is None else dst_stride
         t = self.type
+        use_tc = M > GEMV_MAX_M and not self.exact and self.tc_ok
         if quantize:
             if t in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
-                batch.dispatch(ctx.kernel("ameva_quant_a8"), [(x, x_offset), self.aq, self.ad],
+                binds = [(x, x_offset), self.aq, self.ad] + ([self.ah] if use_tc else [])
+                batch.dispatch(ctx.kernel("ameva_quant_a8_f16" if use_tc else "ameva_quant_a8"), binds,
                                [M, K, K, self.round_mode], ((M * (K // 32) * 8 + 255) // 256, 1, 1))
             elif t == GGML_TYPE_Q4_K:
-                batch.dispatch(ctx.kernel("ameva_quant_a8b"), [(x, x_offset), self.aq, self.ad],
+                binds = [(x, x_offset), self.aq, self.ad] + ([self.ah] if use_tc else [])
+                batch.dispatch(ctx.kernel("ameva_quant_a8b_f16" if use_tc else "ameva_quant_a8b"), binds,
                                [M, K, K, self.q8k_mode], ((M * (K // 256) * 32 + 255) // 256, 1, 1))
             else:
                 batch.dispatch(ctx.kernel("bitnet_norm_q8"),
@@ -180,8 +189,19 @@ class MulMat:
             shp = self._sum_shape(M)
             if shp is not None and self.sums is None:
                 self.sums = ctx.buffer(int(np.prod(self._sum_shape(self.max_m))) * 4)
-        # kernel choice by M (ameva_mmq_plan / enc_mul_mat): M <= 8 -> streaming GEMV; larger M -> chunks of 8 through the
-        # same exact dp4a kernels until the tensor-core GEMM takes over
+        # kernel choice by M (ameva_mmq_plan / enc_mul_mat): M <= 8 -> streaming GEMV; larger M -> tcgen05 GEMM; the exact
+        # mode (and K that is not a whole number of 128-byte operand rows) walks larger M in chunks of 8 through the GEMV
+        if use_tc:
+            self.path = "mmtc"
+            grid = ((M + 255) // 256, (N + 127) // 128, 1)
+            if t == GGML_TYPE_I2_S:
+                push = [M, N, K, dst_stride, int(np.float32(self.view.weight.scale).view(np.uint32))]
+                batch.dispatch(ctx.kernel("bitnet_gemm_i2_s"), [self.qbind, self.aq, (dst, dst_offset), self.ad], push,
+                               grid)
+            else:
+                batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}"),
+                               [self.qbind, self.sbind, self.ah, (dst, dst_offset)], [M, N, K, dst_stride], grid)
+            return
         self.path = "mmvq" if M <= GEMV_MAX_M else "mmvq-chunks"
         for m0 in range(0, M, GEMV_MAX_M):
             mc = min(GEMV_MAX_M, M - m0)
@@ -238,7 +258,7 @@ class MulMat:
         return q, act[:, 0].copy().view(np.float32), act[:, 1].copy().view(np.int32)
 
     def destroy(self) -> None:
-        for name in ("aq", "ad", "y", "qeo", "sums"):
+        for name in ("aq", "ad", "ah", "y", "qeo", "sums"):
             b = getattr(self, name, None)
             if b is not None:
                 b.destroy()

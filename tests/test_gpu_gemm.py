@@ -1,0 +1,127 @@
+"""Prefill GEMM (M > 8) on the tensor cores through the C ABI against the CPU oracle.
+
+Q4_0 / Q8_0 / Q4_K run with fp16 operands and fp32 accumulation: the gate is the path's stated tolerance, max normalised
+error <= 1e-3 against the oracle (which accumulates the exact per-block integer sums). I2_S runs on the int8 tensor path
+with an int32 accumulator over the whole K: outputs must be bit-equal to the CPU result. The exact per-block sums at
+M > 8 are checked on the dp4a path (`exact=True`), which is what serves callers that need them."""
+import numpy as np
+import pytest
+
+import oracle
+from conftest import load_pkg
+from helpers import I2_S, Q4_0, Q4_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+
+pytestmark = pytest.mark.gpu
+pkg = load_pkg()
+rt, qmm = pkg.runtime, pkg.qmm
+TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = rt.init()
+    yield c
+    c.destroy()
+
+
+def run_gemm(ctx, t, M, N, K, seed=0, exact=False, rows_checked=None):
+    blocks, scale = make_weights(t, N, K, seed)
+    x = make_acts(M, K, seed + 1)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    mm = qmm.MulMat(ctx, w, M, exact=exact, dump_block_sums=exact and t != I2_S)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    dst.fill(0xFF)
+    mm.run(xb, dst, M)
+    y = dst.read(np.float32).reshape(M, N)
+    assert mm.path == ("mmvq-chunks" if exact else "mmtc")
+    # oracle on all rows, or on a seeded subset of weight rows when the full product would take too long on the CPU
+    if rows_checked is None:
+        want, sums, aq = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=exact)
+        got = y
+    else:
+        idx = np.sort(np.random.default_rng(seed).choice(N, rows_checked, replace=False))
+        sub = np.ascontiguousarray(np.asarray(blocks).reshape(N, -1)[idx])
+        want, sums, aq = oracle_mul_mat(t, sub, scale, x, rows_checked, K, want_sums=False)
+        got = y[:, idx]
+    assert np.isfinite(y).all()
+    if t == I2_S:
+        assert np.array_equal(got, want)
+    else:
+        err = max_normalised_error(got, want)
+        assert err <= TOL, err
+        if exact:
+            assert np.array_equal(mm.read_block_sums(M), sums)
+    # activation quantization stays bit-exact on this path too
+    if t in (Q4_0, Q8_0):
+        q, dbits, _ = mm.read_quantized(M)
+        assert np.array_equal(qmm.q8_0_blocks_from_scratch(q, dbits), aq)
+    elif t == Q4_K:
+        q, d, bs = mm.read_quantized(M)
+        assert np.array_equal(qmm.q8_K_blocks_from_scratch(q, d, bs), aq)
+    for b in (xb, dst):
+        b.destroy()
+    mm.destroy()
+    w.destroy()
+    return None if t == I2_S else max_normalised_error(got, want)
+
+
+@pytest.mark.parametrize("t", [Q8_0, Q4_0, Q4_K])
+@pytest.mark.parametrize("M,N,K", [(16, 128, 256), (9, 64, 512), (33, 130, 1024), (128, 256, 2048), (257, 384, 512),
+                                   (512, 129, 768)])
+def test_gemm_tc_small(ctx, t, M, N, K):
+    if t == Q4_K and K % 256:
+        K = (K // 256 + 1) * 256
+    run_gemm(ctx, t, M, N, K, seed=M + N)
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 128, 128), (128, 640, 2560), (100, 130, 1280), (300, 256, 384)])
+def test_gemm_i2s_bit_exact(ctx, M, N, K):
+    run_gemm(ctx, I2_S, M, N, K, seed=M)
+
+
+@pytest.mark.parametrize("t", [Q8_0, Q4_0, Q4_K])
+def test_exact_path_block_sums_at_prefill_m(ctx, t):
+    run_gemm(ctx, t, 24, 96, 512, seed=5, exact=True)
+
+
+def test_config2_q8_0_prefill_full_size(ctx):
+    """Configuration 2: W 11008 x 4096 Q8_0, M = 512; oracle on 384 seeded weight rows x all 512 tokens."""
+    err = run_gemm(ctx, Q8_0, 512, 11008, 4096, seed=0, rows_checked=384)
+    print("config 2 max normalised error", err)
+
+
+@pytest.mark.parametrize("N,K", [(4096, 4096), (11008, 4096), (4096, 11008)])
+def test_config3_q4_K_prefill(ctx, N, K):
+    run_gemm(ctx, Q4_K, 512, N, K, seed=3, rows_checked=192)
+
+
+@pytest.mark.parametrize("N,K", [(2560, 2560), (640, 2560), (6912, 2560), (2560, 6912)])
+def test_config4_bitnet_prefill_m128(ctx, N, K):
+    run_gemm(ctx, I2_S, 128, N, K, seed=4, rows_checked=min(N, 512))
+
+
+def test_config5_q4_K_70b_prefill_m2048(ctx):
+    run_gemm(ctx, Q4_K, 2048, 28672, 8192, seed=5, rows_checked=48)
+
+
+def test_gemm_linearity_property_full_size(ctx):
+    """Size-independent property at configuration-2 size: the GEMM of one-hot-scaled activations picks out dequantized
+    weights (the reference's KAT form, tests/test_phase4_runtime_abi.cpp:593-697): x = e_k * 127 quantizes exactly
+    (d = 1, q = 127), so y[m][n] = 127 * w[n][k] up to the fp16 operand rounding."""
+    N, K, M = 11008, 4096, 16
+    blocks, scale = make_weights(Q8_0, N, K, 1)
+    wf = oracle.dequantize_q8_0(blocks).reshape(N, K)
+    x = np.zeros((M, K), np.float32)
+    ks = np.random.default_rng(2).choice(K, M, replace=False)
+    x[np.arange(M), ks] = 127.0
+    w = qmm.QuantWeight.from_ggml(ctx, Q8_0, blocks, N, K)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    mm.run(xb, dst, M)
+    y = dst.read(np.float32).reshape(M, N)
+    want = 127.0 * wf[:, ks].T
+    assert np.max(np.abs(y - want)) <= 2e-3 * np.max(np.abs(want))
+    for b in (xb, dst):
+        b.destroy()
+    mm.destroy()
+    w.destroy()
