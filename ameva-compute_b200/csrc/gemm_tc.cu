@@ -289,7 +289,7 @@ template <int TYPE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const uint8_t* __restrict__ Q, const uint8_t* __restrict__ S,
                float* __restrict__ dst, const uint32_t* __restrict__ ACT, uint32_t M, uint32_t N, uint32_t K,
-               uint32_t dst_stride, float w_scale, uint32_t* status) {
+               uint32_t dst_stride, float w_scale, uint32_t diag, uint32_t* status) {
     constexpr bool INT8 = TYPE == T_I2_S;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -329,6 +329,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const uint8_t* __res
             for (uint32_t kb = 0; kb < KB; ++kb, ++issued) {
                 const uint32_t s = kb % kStages, ph = (kb / kStages) & 1u;
                 if (!mbar_wait(empty + 8u * s, ph ^ 1u, ctl, status, 0x100u | s)) break;
+                if (diag & 2u) {   // diagnostic: no activation traffic
+                    mbar_arrive(full_b + 8u * s);
+                    continue;
+                }
                 mbar_arrive_expect_tx(full_b + 8u * s, kBBytes);
                 tma_load_2d(smem_u32(sB + s * kBBytes), &act_map, full_b + 8u * s, (int)(kb * block_k<TYPE>()),
                             (int)m0);
@@ -351,9 +355,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const uint8_t* __res
                 tc_fence_after();
                 const uint64_t da = make_smem_desc(smem_u32(sA + s * kABytes));
                 const uint64_t db = make_smem_desc(smem_u32(sB + s * kBBytes));
+                if (!(diag & 4u)) {
 #pragma unroll
-                for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: +2 in the 16-byte address field
-                    umma<INT8>(tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0u);
+                    for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: +2 in the 16-byte address field
+                        umma<INT8>(tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0u);
+                }
                 umma_commit(empty + 8u * s);
             }
             umma_commit(accum);
@@ -377,7 +383,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const uint8_t* __res
                     const uint32_t s = kb % kStages, ph = (kb / kStages) & 1u;
                     ok = mbar_wait(empty + 8u * s, ph ^ 1u, ctl, status, 0x400u | s);
                     if (ok) {
-                        dequant_store<TYPE>(cur, sA + s * kABytes + r * kRowBytes, r, h, kb);
+                        if (!(diag & 1u)) dequant_store<TYPE>(cur, sA + s * kABytes + r * kRowBytes, r, h, kb);
                         fence_async_smem();
                         mbar_arrive(full_a + 8u * s);
                     }
@@ -398,7 +404,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const uint8_t* __res
 #pragma unroll
                 for (uint32_t j = 0; j < 32; ++j) {
                     const uint32_t m = m0 + c * 32u + j;
-                    if (m < M && out_row < N) {
+                    if (m < M && out_row < N && !(diag & 8u)) {
                         float y;
                         if (INT8) {
                             const float total_scale = __fmul_rn(__uint_as_float(__ldg(ACT + 2u * m)), w_scale);
@@ -439,7 +445,7 @@ static EncodeTiledFn encode_fn() {
 template <int TYPE>
 static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, void* act, uint64_t act_range, void* dstp,
                        uint64_t dst_range, const void* actscale, uint32_t M, uint32_t N, uint32_t K,
-                       uint32_t dst_stride, float w_scale) {
+                       uint32_t dst_stride, float w_scale, uint32_t diag) {
     constexpr uint32_t BK = block_k<TYPE>();
     constexpr uint32_t esz = TYPE == T_I2_S ? 1u : 2u;
     if (M == 0 || N == 0 || K == 0 || (K % BK) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
@@ -471,14 +477,16 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, void
     if (grid.y > 65535u) return AC_ERR_INVALID_WORK_ITEM_DIMS;
     gemm_tc_kernel<TYPE><<<grid, kThreads, kSmemBytes, a.stream>>>(map, (const uint8_t*)Qp, (const uint8_t*)Sp,
                                                                    (float*)dstp, (const uint32_t*)actscale, M, N, K,
-                                                                   dst_stride, w_scale, a.status);
+                                                                   dst_stride, w_scale, diag, a.status);
     return check_launch();
 }
 
 }  // namespace tc
 
 // ameva_mmtc_<q4_0|q8_0|q4_K>: bindings 0 Q, 1 S, 2 AH (fp16 activations [M][K], written by ameva_quant_a8_f16 /
-// ameva_quant_a8b_f16), 3 dst f32 [M][dst_stride];  push {M, N, K, dst_stride}
+// ameva_quant_a8b_f16), 3 dst f32 [M][dst_stride];  push {M, N, K, dst_stride, diag}
+// diag (0 in production; results are meaningless otherwise) switches one pipeline stage off for profiling:
+// 1 = no weight dequantization, 2 = no activation TMA, 4 = no MMA, 8 = no output stores.
 template <int TYPE, uint32_t QB, uint32_t SB, uint32_t BLK>
 static AcResult launch_mmtc(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
@@ -486,14 +494,14 @@ static AcResult launch_mmtc(const LaunchArgs& a) {
     const uint64_t nblk = (uint64_t)N * (K / BLK);
     if (a.range[0] < nblk * QB || a.range[1] < nblk * SB) return AC_ERR_INVALID_BUFFER_SIZE;
     return tc::launch<TYPE>(a, a.ptr[0], a.ptr[1], a.ptr[2], a.range[2], a.ptr[3], a.range[3], nullptr, M, N, K,
-                            dst_stride, 1.0f);
+                            dst_stride, 1.0f, a.push[4]);
 }
 AcResult launch_mmtc_q4_0(const LaunchArgs& a) { return launch_mmtc<tc::T_Q4_0, 16, 2, 32>(a); }
 AcResult launch_mmtc_q8_0(const LaunchArgs& a) { return launch_mmtc<tc::T_Q8_0, 32, 2, 32>(a); }
 AcResult launch_mmtc_q4_K(const LaunchArgs& a) { return launch_mmtc<tc::T_Q4_K, 128, 16, 256>(a); }
 
 // bitnet_gemm_i2_s: bindings 0 packed weights, 1 int8 activations [M][K], 2 dst f32 [M][dst_stride], 3 act[2] per row
-// {bits of dequant, sum q};  push {M, N, K, dst_stride, weight_scale_bits}
+// {bits of dequant, sum q};  push {M, N, K, dst_stride, weight_scale_bits, diag}
 AcResult launch_bitnet_gemm_i2_s(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
     if (K == 0 || (K & 127u)) return AC_ERR_KERNEL_ARG_INVALID;
@@ -501,7 +509,7 @@ AcResult launch_bitnet_gemm_i2_s(const LaunchArgs& a) {
     float w_scale;
     memcpy(&w_scale, &a.push[4], 4);
     return tc::launch<tc::T_I2_S>(a, a.ptr[0], nullptr, a.ptr[1], a.range[1], a.ptr[2], a.range[2], a.ptr[3], M, N, K,
-                                  dst_stride, w_scale);
+                                  dst_stride, w_scale, a.push[5]);
 }
 
 }  // namespace amv

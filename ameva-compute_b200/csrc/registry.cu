@@ -37,10 +37,10 @@ static const KernelEntry kTable[] = {
     {"ameva_quant_a8_f16", 4, 16, {256, 1, 1}, launch_quant_a8_f16},
     {"ameva_quant_a8b_f16", 4, 16, {256, 1, 1}, launch_quant_a8b_f16},
     {"bitnet_norm_q8", 7, 16, {256, 1, 1}, launch_bitnet_norm_q8},
-    {"ameva_mmtc_q4_0", 4, 16, {320, 1, 1}, launch_mmtc_q4_0},
-    {"ameva_mmtc_q8_0", 4, 16, {320, 1, 1}, launch_mmtc_q8_0},
-    {"ameva_mmtc_q4_K", 4, 16, {320, 1, 1}, launch_mmtc_q4_K},
-    {"bitnet_gemm_i2_s", 4, 20, {320, 1, 1}, launch_bitnet_gemm_i2_s},
+    {"ameva_mmtc_q4_0", 4, 20, {320, 1, 1}, launch_mmtc_q4_0},
+    {"ameva_mmtc_q8_0", 4, 20, {320, 1, 1}, launch_mmtc_q8_0},
+    {"ameva_mmtc_q4_K", 4, 20, {320, 1, 1}, launch_mmtc_q4_K},
+    {"bitnet_gemm_i2_s", 4, 24, {320, 1, 1}, launch_bitnet_gemm_i2_s},
     {"ameva_mmvq_q4_0", 5, 16, {256, 1, 1}, launch_mmvq_q4_0},
     {"ameva_mmvq_q4_0_dump", 6, 16, {256, 1, 1}, launch_mmvq_q4_0_dump},
     {"ameva_mmvq_q8_0", 5, 16, {256, 1, 1}, launch_mmvq_q8_0},

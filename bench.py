@@ -222,8 +222,8 @@ def metric_name(name):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -283,12 +283,21 @@ def main():
     def gpu_steps(n, first, flags=0):
         """n steps on the device; returns (gpu seconds by CUDA events on the runtime's stream, batch)."""
         if world == 1:
-            batch = ctx.batch(max(64, n * 80), flags)
-            record_steps(batch, n, first)
-            ev = batch.submit()
-            ev.wait(600_000_000_000)
-            gpu_s = ev.timing()[1] / 1e9
-            ev.destroy()
+            per_batch = n if flags else max(1, min(n, 60000 // 70))   # a batch holds at most 65536 dispatches
+            gpu_s, done, batch = 0.0, 0, None
+            pending = []
+            while done < n:   # every batch is recorded and submitted before the first wait: the GPU never idles
+                cnt = min(per_batch, n - done)
+                batch = ctx.batch(max(64, cnt * 70), flags)
+                record_steps(batch, cnt, first + done)
+                pending.append((batch, batch.submit()))
+                done += cnt
+            for bt, ev in pending:
+                ev.wait(600_000_000_000)
+                gpu_s += ev.timing()[1] / 1e9
+                ev.destroy()
+                if bt is not batch:
+                    bt.destroy()
             return gpu_s, batch
         # sharded: every step is compute on the runtime's stream, then the all-gather and the permute, in stream order
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
