@@ -133,6 +133,7 @@ EXPORTED_SYMBOLS = [
     "ac_b200_kernel_count", "ac_b200_kernel_name", "ac_b200_context_get_stream", "ac_b200_buffer_import",
     "ac_b200_buffer_write_async", "ac_b200_buffer_read_async", "ac_b200_context_synchronize",
     "ac_b200_device_layout", "ac_b200_repack_to_device", "ac_b200_repack_from_device",
+    "ac_b200_mul_mat_q4_0_static",
 ]
 
 _lib = None
@@ -210,6 +211,7 @@ def load_library() -> C.CDLL:
         "ac_b200_buffer_read_async": (C.c_int, [vp, sz, vp, sz]),
         "ac_b200_context_synchronize": (C.c_int, [vp]),
         "ac_b200_device_layout": (C.c_int, [u32, u64, u64, P(u64), P(u64)]),
+        "ac_b200_mul_mat_q4_0_static": (C.c_int, [vp, vp, vp, vp, u32, vp, u32, u32, u32, u32, u32]),
         "ac_b200_repack_to_device": (C.c_int, [u32, vp, u64, u64, vp]),
         "ac_b200_repack_from_device": (C.c_int, [u32, vp, u64, u64, vp]),
     }

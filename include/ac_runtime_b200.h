@@ -333,6 +333,20 @@ AcResult ac_b200_repack_to_device(uint32_t ggml_type, const void* ggml_blocks, u
 AcResult ac_b200_repack_from_device(uint32_t ggml_type, const void* device_layout, uint64_t rows, uint64_t k,
                                     void* ggml_blocks);
 
+/* Decode mul_mat for callers that cannot allocate. No counterpart in the reference.
+ * Q4_0 weights (device layout: w_payload 16 bytes and w_scales one fp16 per 32 weights, row-major over [N][K/32]) times
+ * fp32 activations x[M][K], quantized per 32 values on the fly, into dst[M][N] (fp32). The scratch for the quantized
+ * activations is a fixed array inside the library's GPU module, so the call performs no device allocation of any kind:
+ * meant for hosts that must not allocate where they call from (real-time callbacks, fixed-budget plugins, sandboxes
+ * that forbid allocation after start-up). Limits: M <= 8 and K <= 32768, otherwise AC_ERR_INVALID_SHAPE; the array
+ * (294 912 bytes) stays resident on every GPU that loads the library. All pointers are device addresses on the current
+ * device; the work is enqueued on `stream` (cudaStream_t, NULL = default stream) and not waited for. The first call on a
+ * device also looks the array up and should come before any stream capture. Every call reuses the same array, so calls
+ * whose GPU work may overlap must be serialised by the caller. */
+AcResult ac_b200_mul_mat_q4_0_static(void* stream, const void* w_payload, const void* w_scales, const float* x,
+                                     uint32_t x_stride, float* dst, uint32_t dst_stride, uint32_t M, uint32_t N,
+                                     uint32_t K, uint32_t round_mode);
+
 #ifdef __cplusplus
 }
 #endif
