@@ -307,7 +307,7 @@ def main():
                 batch = ctx.batch(128, 0)
                 record_steps(batch, 1, first + i)
                 batch.flush()
-                dist.all_gather_into_tensor(gathered_t, out_local_t)
+                dist.all_gather_into_tensor(gathered_t.view(world * M, pad), out_local_t)
                 shard.assemble(gathered_t, parts, M, N, out_full_t)
                 batch_keep.append(batch)
             end.record()
