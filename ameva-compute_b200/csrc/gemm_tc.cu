@@ -2,16 +2,20 @@
 //
 //   dst[m][n] = sum_k W[n][k] * A[m][k]        W: N x K block-quantized, A: M x K quantized on the fly
 //
-// One CTA computes a 128 (weight rows) x <=256 (tokens) output tile, walking K in blocks of one 128-byte swizzle row:
-//   warps 0-7  dequantize the CTA's 128 weight rows from the packed device layout straight into the K-major,
-//              128B-swizzled shared-memory image tcgen05.mma reads (fp16 for Q4_0 / Q8_0 / Q4_K with the block scales
-//              folded in, one rounding; int8 ternary values for I2_S), a PD-deep register prefetch hiding the global
-//              latency; afterwards they are the epilogue (tcgen05.ld -> coalesced fp32 stores);
+// One CTA computes a 128 (weight rows) x T (tokens, T <= 256 chosen by the host to balance the waves over the SMs)
+// output tile, walking K in blocks of one 128-byte swizzle row (64 fp16 or 128 int8 elements):
+//   warp 10    streams the CTA's packed weight rows with TMA, one box of 128 rows per K block, into a deep ring of raw
+//              stages (and the block scales once per 256 weights into their own small ring);
+//   warps 0-7  dequantize a raw stage in shared memory into the K-major, 128B-swizzled operand image tcgen05.mma reads
+//              (fp16 with the block scales folded in, one rounding, for Q4_0 / Q8_0 / Q4_K; int8 ternary values for
+//              I2_S); after the last K block they are the epilogue: tcgen05.ld, then every warp sends its 32 x 32
+//              pieces out through a 4 KB staging buffer and a TMA store (plain coalesced stores when the output is
+//              not 16-byte aligned);
 //   warp 8     streams the activation tile with TMA (2-D tensor map, 128B swizzle) into the other operand's stages;
 //   warp 9     allocates TMEM and issues the MMAs (one elected thread), releasing stages through tcgen05.commit.
 // Stages are handed over with mbarriers; every wait is bounded by a cycle budget, after which the CTA records
 // DEV_STATUS_WAIT_TIMEOUT in the context's status words, stops, frees its TMEM and returns (the host turns it into
-// AC_ERR_LAUNCH_TIMEOUT).
+// AC_ERR_LAUNCH_TIMEOUT). No TMA load carries a cluster qualifier beyond its own CTA.
 //
 // Numerics: Q4_0 / Q8_0 / Q4_K run kind::f16 (fp16 operands, fp32 accumulation): weights are fp16(dequantized value),
 // activations fp16(q * d) written by the quantize kernel, so each product carries two 2^-12 relative roundings and the
@@ -30,19 +34,28 @@ namespace amv {
 namespace tc {
 
 constexpr int kRows = 128;          // weight rows per CTA (UMMA M)
-constexpr int kTokMax = 256;        // tokens per CTA (UMMA N, multiple of 16)
-constexpr int kStages = 4;
+constexpr int kTokMax = 256;        // tokens per CTA at most (UMMA N, multiple of 16)
 constexpr int kRowBytes = 128;      // bytes of one operand row per K block (the swizzle span)
 constexpr int kDequantThreads = 256;
-constexpr int kThreads = 320;       // 8 dequant/epilogue warps + TMA warp + MMA warp
-constexpr int kPrefetch = 4;        // K blocks of packed weights held in registers ahead of use
-constexpr uint32_t kABytes = kRows * kRowBytes;     // 16 KB
-constexpr uint32_t kBBytes = kTokMax * kRowBytes;   // 32 KB
-constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kSmemBytes = 1024 + kStages * (kABytes + kBBytes) + 256;
+constexpr int kThreads = 352;       // 8 dequant/epilogue warps + activation TMA warp + MMA warp + weight TMA warp
+constexpr int kMaxStages = 6;
+constexpr int kScaleSlots = 3;
+constexpr uint32_t kABytes = kRows * kRowBytes;     // 16 KB per operand stage of weights
+constexpr uint32_t kScaleBytes = kRows * 16;        // 2 KB: 16 bytes of scales per row per 256 weights
+constexpr uint32_t kSmemLimit = 227 * 1024;
 constexpr long long kWaitCycles = 2000000000ll;     // about one second
 
 enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_I2_S = 36 };
+
+template <int TYPE>
+struct Cfg {
+    static constexpr bool kInt8 = TYPE == T_I2_S;
+    static constexpr bool kScales = TYPE != T_I2_S;
+    static constexpr uint32_t kBlockK = kInt8 ? 128u : 64u;                 // K elements per K block
+    static constexpr uint32_t kRawRow = TYPE == T_Q8_0 ? 64u : 32u;         // packed bytes per row per K block
+    static constexpr uint32_t kRawBytes = kRows * kRawRow;
+    static constexpr uint32_t kRawSlots = TYPE == T_Q8_0 ? 6u : 8u;
+};
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -140,6 +153,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
         "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(src_smem), "r"(c0), "r"(c1)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
     asm volatile(
@@ -155,57 +174,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// ---- packed weights of one (row, half K-block): what a dequant thread prefetches ------------------------------------
-template <int TYPE>
-struct Raw;
-template <>
-struct Raw<T_Q8_0> {
-    u32x8 q;
-    uint16_t d;
-};
-template <>
-struct Raw<T_Q4_0> {
-    uint4 q;
-    uint16_t d;
-};
-template <>
-struct Raw<T_Q4_K> {
-    u32x8 q;
-    uint4 s;
-};
-template <>
-struct Raw<T_I2_S> {
-    u32x8 q;
-};
-
-// K elements per K block: 64 fp16 or 128 int8 (one 128-byte row).
-template <int TYPE>
-__host__ __device__ constexpr uint32_t block_k() {
-    return TYPE == T_I2_S ? 128u : 64u;
-}
-
-template <int TYPE>
-__device__ __forceinline__ Raw<TYPE> load_raw(const uint8_t* Q, const uint8_t* S, size_t row, uint32_t K, uint32_t kb,
-                                               uint32_t h) {
-    Raw<TYPE> r;
-    if constexpr (TYPE == T_Q8_0) {
-        const size_t u = row * (K >> 5) + 2u * kb + h;
-        r.q = ld_stream_u8(Q + u * 32u);
-        r.d = ld_stream_u16(S + u * 2u);
-    } else if constexpr (TYPE == T_Q4_0) {
-        const size_t u = row * (K >> 5) + 2u * kb + h;
-        r.q = ld_stream_u4(Q + u * 16u);
-        r.d = ld_stream_u16(S + u * 2u);
-    } else if constexpr (TYPE == T_Q4_K) {
-        const size_t b = row * (K >> 8) + (kb >> 2);
-        r.q = *reinterpret_cast<const u32x8*>(Q + b * 128u + (kb & 3u) * 32u);   // both halves read it: keep it in L1
-        r.s = ld_cached_u4(S + b * 16u);
-    } else {
-        r.q = *reinterpret_cast<const u32x8*>(Q + row * (K >> 2) + kb * 32u);
-    }
-    return r;
-}
-
 __device__ __forceinline__ uint32_t pack_h2(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
 // 4 packed byte values (0..255) + the fp16 magic 1024: two half2 holding 1024 + b0, 1024 + b1 and 1024 + b2, 1024 + b3.
@@ -215,29 +183,48 @@ __device__ __forceinline__ void bytes_to_h2(uint32_t x, __half2& lo, __half2& hi
     hi = *reinterpret_cast<const __half2*>(&b);
 }
 
-// Converts the raw data of (row r, half h) into its 64 bytes of the operand row and stores them swizzled.
+// 16-byte chunk c of operand row r lives at chunk position c ^ (r % 8) (the 128-byte swizzle).
+__device__ __forceinline__ void store_chunk(uint8_t* stage, uint32_t r, uint32_t c, uint4 v) {
+    reinterpret_cast<uint4*>(stage + r * kRowBytes)[c ^ (r & 7u)] = v;
+}
+
+// ---- dequantization of one raw stage (128 rows x one K block) into an operand stage -----------------------------------
+// Every thread reads 16 contiguous bytes; consecutive lanes read consecutive 16-byte pieces of the raw stage, so the
+// shared-memory reads are conflict free, and a quarter-warp's eight stores land on eight different chunk positions.
 template <int TYPE>
-__device__ __forceinline__ void dequant_store(const Raw<TYPE>& raw, uint8_t* stage_row, uint32_t r, uint32_t h,
+__device__ __forceinline__ void dequant_stage(const uint8_t* raw, const uint8_t* sc, uint8_t* stage, uint32_t t,
                                               uint32_t kb) {
-    uint4 out[4];
     if constexpr (TYPE == T_Q8_0) {
-        const __half2 d2 = __half2half2(__ushort_as_half(raw.d));
-        const __half2 bias = __float2half2_rn(1152.0f);   // 1024 (magic) + 128 (the bytes are q + 128)
-        uint32_t* o = reinterpret_cast<uint32_t*>(out);
+        // raw: 64 B per row (2 units of 32 int8); sc: 16 B per row = 8 fp16 scales of the 8 units of this 256-group
+        const __half2 bias = __float2half2_rn(1152.0f);   // 1024 (magic) + 128 (bytes are q + 128 after the xor)
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            __half2 lo, hi;
-            bytes_to_h2(raw.q.v[w] ^ 0x80808080u, lo, hi);
-            o[2 * w] = pack_h2(__hmul2(__hsub2(lo, bias), d2));
-            o[2 * w + 1] = pack_h2(__hmul2(__hsub2(hi, bias), d2));
+        for (uint32_t pass = 0; pass < 2; ++pass) {
+            const uint32_t task = t + pass * kDequantThreads, r = task >> 2, c = task & 3u;
+            const uint4 q = *reinterpret_cast<const uint4*>(raw + task * 16u);
+            const __half d = *reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + (c >> 1)) * 2u);
+            const __half2 d2 = __half2half2(d);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __half2 lo, hi;
+                bytes_to_h2(w[i] ^ 0x80808080u, lo, hi);
+                o[2 * i] = pack_h2(__hmul2(__hsub2(lo, bias), d2));
+                o[2 * i + 1] = pack_h2(__hmul2(__hsub2(hi, bias), d2));
+            }
+            store_chunk(stage, r, 2u * c, make_uint4(o[0], o[1], o[2], o[3]));
+            store_chunk(stage, r, 2u * c + 1u, make_uint4(o[4], o[5], o[6], o[7]));
         }
     } else if constexpr (TYPE == T_Q4_0) {
-        const __half2 d2 = __half2half2(__ushort_as_half(raw.d));
+        // raw: 32 B per row (2 units of 16 B: byte j = weight j low nibble, weight j + 16 high nibble)
+        const uint32_t r = t >> 1, u = t & 1u;
+        const uint4 q = *reinterpret_cast<const uint4*>(raw + t * 16u);
+        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + u) * 2u));
         const __half2 bias = __float2half2_rn(1032.0f);   // 1024 (magic) + 8 (the nibble offset)
-        const uint32_t w[4] = {raw.q.x, raw.q.y, raw.q.z, raw.q.w};
-        uint32_t* o = reinterpret_cast<uint32_t*>(out);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t o[16];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {   // low nibbles: elements 4i..4i+3; high nibbles: elements 16+4i..16+4i+3
+        for (int i = 0; i < 4; ++i) {   // low nibbles: weights 4i..4i+3; high nibbles: weights 16+4i..16+4i+3
             __half2 lo, hi;
             bytes_to_h2(w[i] & 0x0F0F0F0Fu, lo, hi);
             o[2 * i] = pack_h2(__hmul2(__hsub2(lo, bias), d2));
@@ -246,116 +233,186 @@ __device__ __forceinline__ void dequant_store(const Raw<TYPE>& raw, uint8_t* sta
             o[8 + 2 * i] = pack_h2(__hmul2(__hsub2(lo, bias), d2));
             o[8 + 2 * i + 1] = pack_h2(__hmul2(__hsub2(hi, bias), d2));
         }
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i)
+            store_chunk(stage, r, 4u * u + i, make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]));
     } else if constexpr (TYPE == T_Q4_K) {
-        // sub-block j = 2 (kb % 4) + h: low (h = 0) or high (h = 1) nibbles of the 32 bytes; w = (d sc) q - (dmin m)
-        const uint32_t j = 2u * (kb & 3u) + h;
-        const uint32_t k8 = 8u * (j & 3u);
-        const uint32_t b0 = (raw.s.y >> k8) & 0xFFu, b1 = (raw.s.z >> k8) & 0xFFu, b2 = (raw.s.w >> k8) & 0xFFu;
-        const uint32_t sc = j < 4u ? (b0 & 63u) : ((b2 & 0xFu) | ((b0 >> 6) << 4));
-        const uint32_t mn = j < 4u ? (b1 & 63u) : ((b2 >> 4) | ((b1 >> 6) << 4));
-        const float dl = h2f((uint16_t)(raw.s.x & 0xFFFFu)) * (float)sc;
-        const float ml = h2f((uint16_t)(raw.s.x >> 16)) * (float)mn;
-        uint32_t* o = reinterpret_cast<uint32_t*>(out);
-#pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            const uint32_t x = (raw.q.v[w] >> (4u * h)) & 0x0F0F0F0Fu;
-            float f[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float q = __uint_as_float(0x4B000000u | ((x >> (8 * e)) & 0xFFu)) - 8388608.0f;   // exact
-                f[e] = fmaf(q, dl, -ml);
-            }
-            o[2 * w] = pack_h2(__floats2half2_rn(f[0], f[1]));
-            o[2 * w + 1] = pack_h2(__floats2half2_rn(f[2], f[3]));
+        // raw: 32 B per row = qs[32k' .. 32k'+31], k' = kb % 4: low nibbles are sub-block 2k', high nibbles 2k'+1;
+        // this thread holds bytes 16c .. 16c+15: weights 16c..16c+15 of both sub-blocks. w = (d sc) q - (dmin m).
+        const uint32_t r = t >> 1, c = t & 1u;
+        const uint4 q = *reinterpret_cast<const uint4*>(raw + t * 16u);
+        const uint4 s = *reinterpret_cast<const uint4*>(sc + r * 16u);
+        const uint32_t p16 = 16u * (kb & 1u);   // the byte pair (2k', 2k'+1) % 4 inside each scale word
+        const uint32_t a = (s.y >> p16) & 0xFFFFu, b = (s.z >> p16) & 0xFFFFu, e = (s.w >> p16) & 0xFFFFu;
+        uint32_t scp, mnp;                      // two 6-bit values each, one per byte
+        if ((kb & 3u) < 2u) {
+            scp = a & 0x3F3Fu;
+            mnp = b & 0x3F3Fu;
+        } else {
+            scp = (e & 0x0F0Fu) | ((a >> 2) & 0x3030u);
+            mnp = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
         }
-    } else {
-        // I2_S: chunk i of this half holds elements 64h + 16i .. +15 = group g = 2h + i/2, block bytes 16(i%2) .. +15
-        uint32_t* o = reinterpret_cast<uint32_t*>(out);
+        const float d = h2f((uint16_t)(s.x & 0xFFFFu)), dmin = h2f((uint16_t)(s.x >> 16));
+        const float dl0 = d * (float)(scp & 0xFFu), dl1 = d * (float)(scp >> 8);
+        const float ml0 = dmin * (float)(mnp & 0xFFu), ml1 = dmin * (float)(mnp >> 8);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t o[16];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const uint32_t sh = 6u - 2u * (2u * h + (uint32_t)(i >> 1));
 #pragma unroll
-            for (int w = 0; w < 4; ++w)
-                o[4 * i + w] = __vsub4((raw.q.v[4 * (i & 1) + w] >> sh) & 0x03030303u, 0x01010101u);
+            for (int hi = 0; hi < 2; ++hi) {
+                const uint32_t x = (w[i] >> (4 * hi)) & 0x0F0F0F0Fu;
+                const float dl = hi ? dl1 : dl0, ml = hi ? ml1 : ml0;
+                float f[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k)   // exact nibble -> float through the 2^23 magic, then one fma
+                    f[k] = fmaf(__uint_as_float(0x4B000000u | ((x >> (8 * k)) & 0xFFu)) - 8388608.0f, dl, -ml);
+                o[8 * hi + 2 * i] = pack_h2(__floats2half2_rn(f[0], f[1]));
+                o[8 * hi + 2 * i + 1] = pack_h2(__floats2half2_rn(f[2], f[3]));
+            }
+        }
+        store_chunk(stage, r, 2u * c, make_uint4(o[0], o[1], o[2], o[3]));
+        store_chunk(stage, r, 2u * c + 1u, make_uint4(o[4], o[5], o[6], o[7]));
+        store_chunk(stage, r, 4u + 2u * c, make_uint4(o[8], o[9], o[10], o[11]));
+        store_chunk(stage, r, 5u + 2u * c, make_uint4(o[12], o[13], o[14], o[15]));
+    } else {
+        // I2_S: raw 32 B per row = one 128-weight block; byte k holds weights k, 32+k, 64+k, 96+k in bits 7-6 .. 1-0.
+        // This thread holds bytes 16c .. 16c+15: for group g the weights 32g + 16c .. +15 = operand chunk 2g + c.
+        const uint32_t r = t >> 1, c = t & 1u;
+        const uint4 q = *reinterpret_cast<const uint4*>(raw + t * 16u);
+#pragma unroll
+        for (uint32_t g = 0; g < 4; ++g) {
+            const uint32_t sh = 6u - 2u * g;
+            store_chunk(stage, r, 2u * g + c,
+                        make_uint4(__vsub4((q.x >> sh) & 0x03030303u, 0x01010101u),
+                                   __vsub4((q.y >> sh) & 0x03030303u, 0x01010101u),
+                                   __vsub4((q.z >> sh) & 0x03030303u, 0x01010101u),
+                                   __vsub4((q.w >> sh) & 0x03030303u, 0x01010101u)));
         }
     }
-    uint4* rowp = reinterpret_cast<uint4*>(stage_row);
-#pragma unroll
-    for (uint32_t i = 0; i < 4; ++i) rowp[(4u * h + i) ^ (r & 7u)] = out[i];
 }
+
+struct Params {
+    float* dst;
+    const uint32_t* act;      // I2_S: {bits of 1/scale, sum q} per token row
+    uint32_t M, N, K, dst_stride;
+    uint32_t tok_tile;        // T: tokens per CTA, multiple of 32, <= 256
+    uint32_t stages;          // operand stages (3..6)
+    uint32_t tmem_cols;       // power of two >= T
+    uint32_t tma_store;       // 1: epilogue through shared memory + TMA store
+    float w_scale;
+    uint32_t diag;
+    uint32_t* status;
+};
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
 template <int TYPE>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const uint8_t* __restrict__ Q, const uint8_t* __restrict__ S,
-               float* __restrict__ dst, const uint32_t* __restrict__ ACT, uint32_t M, uint32_t N, uint32_t K,
-               uint32_t dst_stride, float w_scale, uint32_t diag, uint32_t* status) {
-    constexpr bool INT8 = TYPE == T_I2_S;
+gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap raw_map,
+               const __grid_constant__ CUtensorMap scale_map, const __grid_constant__ CUtensorMap out_map,
+               const Params p) {
+    using C = Cfg<TYPE>;
+    constexpr bool INT8 = C::kInt8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    uint8_t* sA = base;
-    uint8_t* sB = base + kStages * kABytes;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + kStages * kBBytes);
-    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 3 * kStages + 1);
-    const uint32_t full_a = smem_u32(bars), full_b = full_a + 8u * kStages, empty = full_b + 8u * kStages,
-                   accum = empty + 8u * kStages;
+    const uint32_t S = p.stages, T = p.tok_tile, b_bytes = T * kRowBytes;
+    uint8_t* sA = base;                               // S x 16 KB
+    uint8_t* sB = sA + S * kABytes;                   // S x T*128 B
+    uint8_t* sRaw = sB + S * b_bytes;                 // kRawSlots x kRawBytes
+    uint8_t* sSc = sRaw + C::kRawSlots * C::kRawBytes;   // kScaleSlots x 2 KB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sSc + kScaleSlots * kScaleBytes);
+    // barrier order: full_a[6] full_b[6] empty[6] raw_full[8] raw_empty[8] sc_full[3] sc_empty[3] accum
+    const uint32_t full_a = smem_u32(bars), full_b = full_a + 8u * kMaxStages, empty = full_b + 8u * kMaxStages,
+                   raw_full = empty + 8u * kMaxStages, raw_empty = raw_full + 8u * 8u, sc_full = raw_empty + 8u * 8u,
+                   sc_empty = sc_full + 8u * kScaleSlots, accum = sc_empty + 8u * kScaleSlots;
+    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 3 * kMaxStages + 16 + 2 * kScaleSlots + 1);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t m0 = blockIdx.x * kTokMax, n0 = blockIdx.y * kRows;
-    const uint32_t tokens = min((uint32_t)kTokMax, M - m0);
-    const uint32_t nt = (tokens + 15u) & ~15u;          // UMMA N
-    const uint32_t KB = K / block_k<TYPE>();
+    const uint32_t m0 = blockIdx.x * T, n0 = blockIdx.y * kRows;
+    const uint32_t KB = p.K / C::kBlockK;
+    uint32_t* status = p.status;
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < kStages; ++s) {
+        for (uint32_t s = 0; s < kMaxStages; ++s) {
             mbar_init(full_a + 8u * s, kDequantThreads);
             mbar_init(full_b + 8u * s, 1u);
             mbar_init(empty + 8u * s, 1u);
+        }
+        for (uint32_t s = 0; s < 8u; ++s) {
+            mbar_init(raw_full + 8u * s, 1u);
+            mbar_init(raw_empty + 8u * s, kDequantThreads);
+        }
+        for (uint32_t s = 0; s < kScaleSlots; ++s) {
+            mbar_init(sc_full + 8u * s, 1u);
+            mbar_init(sc_empty + 8u * s, kDequantThreads);
         }
         mbar_init(accum, 1u);
         ctl->abort = 0u;
         fence_barrier_init();
     }
-    if (warp == 9) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    if (warp == 9) tmem_alloc(smem_u32(&ctl->tmem_base), p.tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
 
     if (warp == 8) {
-        // ---- TMA producer: activation rows m0 .. m0+255 (rows past M read as zero), K block kb ----
+        // ---- activation TMA: token rows m0 .. m0+T-1 (rows past M read as zero), K block kb ----
         if (lane == 0) {
             uint32_t issued = 0;
             for (uint32_t kb = 0; kb < KB; ++kb, ++issued) {
-                const uint32_t s = kb % kStages, ph = (kb / kStages) & 1u;
+                const uint32_t s = kb % S, ph = (kb / S) & 1u;
                 if (!mbar_wait(empty + 8u * s, ph ^ 1u, ctl, status, 0x100u | s)) break;
-                if (diag & 2u) {   // diagnostic: no activation traffic
+                if (p.diag & 2u) {   // diagnostic: no activation traffic
                     mbar_arrive(full_b + 8u * s);
                     continue;
                 }
-                mbar_arrive_expect_tx(full_b + 8u * s, kBBytes);
-                tma_load_2d(smem_u32(sB + s * kBBytes), &act_map, full_b + 8u * s, (int)(kb * block_k<TYPE>()),
-                            (int)m0);
+                mbar_arrive_expect_tx(full_b + 8u * s, b_bytes);
+                tma_load_2d(smem_u32(sB + s * b_bytes), &act_map, full_b + 8u * s, (int)(kb * C::kBlockK), (int)m0);
             }
-            if (ctl->abort) {   // let the copies already requested land before the CTA leaves
-                for (uint32_t i = issued > kStages ? issued - kStages : 0; i < issued; ++i)
-                    mbar_wait(full_b + 8u * (i % kStages), (i / kStages) & 1u, ctl, status, 0x180u);
+            if (ctl->abort && !(p.diag & 2u)) {   // let the copies already requested land before the CTA leaves
+                for (uint32_t i = issued > S ? issued - S : 0; i < issued; ++i)
+                    mbar_wait(full_b + 8u * (i % S), (i / S) & 1u, ctl, status, 0x180u);
+            }
+        }
+    } else if (warp == 10) {
+        // ---- packed-weight TMA: rows n0 .. n0+127 (rows past N read as zero), raw bytes of K block kb; the scales of
+        //      a 256-weight group once per 4 K blocks ----
+        if (lane == 0) {
+            uint32_t issued = 0;
+            for (uint32_t kb = 0; kb < KB; ++kb, ++issued) {
+                if (C::kScales && (kb & 3u) == 0u) {
+                    const uint32_t g = kb >> 2, ss = g % kScaleSlots;
+                    if (!mbar_wait(sc_empty + 8u * ss, ((g / kScaleSlots) & 1u) ^ 1u, ctl, status, 0x600u | ss)) break;
+                    mbar_arrive_expect_tx(sc_full + 8u * ss, kScaleBytes);
+                    tma_load_2d(smem_u32(sSc + ss * kScaleBytes), &scale_map, sc_full + 8u * ss, (int)(g * 16u), (int)n0);
+                }
+                const uint32_t rs = kb % C::kRawSlots;
+                if (!mbar_wait(raw_empty + 8u * rs, ((kb / C::kRawSlots) & 1u) ^ 1u, ctl, status, 0x700u | rs)) break;
+                mbar_arrive_expect_tx(raw_full + 8u * rs, C::kRawBytes);
+                tma_load_2d(smem_u32(sRaw + rs * C::kRawBytes), &raw_map, raw_full + 8u * rs, (int)(kb * C::kRawRow),
+                            (int)n0);
+            }
+            if (ctl->abort) {
+                for (uint32_t i = issued > C::kRawSlots ? issued - C::kRawSlots : 0; i < issued; ++i)
+                    mbar_wait(raw_full + 8u * (i % C::kRawSlots), (i / C::kRawSlots) & 1u, ctl, status, 0x780u);
             }
         }
     } else if (warp == 9) {
         // ---- MMA issuer ----
         if (lane == 0) {
-            const uint32_t idesc = INT8 ? make_idesc(2u, 1u, nt) : make_idesc(1u, 0u, nt);
-            bool ok = true;
-            for (uint32_t kb = 0; kb < KB && ok; ++kb) {
-                const uint32_t s = kb % kStages, ph = (kb / kStages) & 1u;
-                ok = mbar_wait(full_a + 8u * s, ph, ctl, status, 0x200u | s) &&
-                     mbar_wait(full_b + 8u * s, ph, ctl, status, 0x300u | s);
-                if (!ok) break;
+            const uint32_t idesc = INT8 ? make_idesc(2u, 1u, T) : make_idesc(1u, 0u, T);
+            for (uint32_t kb = 0; kb < KB; ++kb) {
+                const uint32_t s = kb % S, ph = (kb / S) & 1u;
+                if (!mbar_wait(full_a + 8u * s, ph, ctl, status, 0x200u | s) ||
+                    !mbar_wait(full_b + 8u * s, ph, ctl, status, 0x300u | s)) {
+                    ctl->abort = 1u;   // visible to whoever passes the accumulator barrier below
+                    break;
+                }
                 tc_fence_after();
                 const uint64_t da = make_smem_desc(smem_u32(sA + s * kABytes));
-                const uint64_t db = make_smem_desc(smem_u32(sB + s * kBBytes));
-                if (!(diag & 4u)) {
+                const uint64_t db = make_smem_desc(smem_u32(sB + s * b_bytes));
+                if (!(p.diag & 4u)) {
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: +2 in the 16-byte address field
                         umma<INT8>(tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0u);
@@ -365,62 +422,68 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const uint8_t* __res
             umma_commit(accum);
         }
     } else {
-        // ---- weight dequantization: thread (r, h) owns half h of row r in every K block ----
-        const uint32_t t = threadIdx.x, r = t & 127u, h = t >> 7;
-        const size_t row = min(n0 + r, N - 1u);
-        Raw<TYPE> raw[kPrefetch];
-#pragma unroll
-        for (uint32_t i = 0; i < kPrefetch; ++i)
-            if (i < KB) raw[i] = load_raw<TYPE>(Q, S, row, K, i, h);
+        // ---- weight dequantization: raw stage -> operand stage ----
+        const uint32_t t = threadIdx.x;
         bool ok = true;
-        for (uint32_t kb0 = 0; kb0 < KB && ok; kb0 += kPrefetch) {
-#pragma unroll
-            for (uint32_t i = 0; i < kPrefetch; ++i) {
-                const uint32_t kb = kb0 + i;
-                if (kb < KB && ok) {
-                    const Raw<TYPE> cur = raw[i];
-                    if (kb + kPrefetch < KB) raw[i] = load_raw<TYPE>(Q, S, row, K, kb + kPrefetch, h);
-                    const uint32_t s = kb % kStages, ph = (kb / kStages) & 1u;
-                    ok = mbar_wait(empty + 8u * s, ph ^ 1u, ctl, status, 0x400u | s);
-                    if (ok) {
-                        if (!(diag & 1u)) dequant_store<TYPE>(cur, sA + s * kABytes + r * kRowBytes, r, h, kb);
-                        fence_async_smem();
-                        mbar_arrive(full_a + 8u * s);
-                    }
-                }
-            }
+        for (uint32_t kb = 0; kb < KB && ok; ++kb) {
+            const uint32_t s = kb % S, rs = kb % C::kRawSlots, g = kb >> 2, ss = g % kScaleSlots;
+            if (C::kScales && (kb & 3u) == 0u)
+                ok = mbar_wait(sc_full + 8u * ss, (g / kScaleSlots) & 1u, ctl, status, 0x800u | ss);
+            ok = ok && mbar_wait(raw_full + 8u * rs, (kb / C::kRawSlots) & 1u, ctl, status, 0x900u | rs) &&
+                 mbar_wait(empty + 8u * s, ((kb / S) & 1u) ^ 1u, ctl, status, 0x400u | s);
+            if (!ok) break;
+            if (!(p.diag & 1u))
+                dequant_stage<TYPE>(sRaw + rs * C::kRawBytes, sSc + ss * kScaleBytes, sA + s * kABytes, t, kb);
+            fence_async_smem();
+            mbar_arrive(full_a + 8u * s);
+            mbar_arrive(raw_empty + 8u * rs);
+            if (C::kScales && (kb & 3u) == 3u) mbar_arrive(sc_empty + 8u * ss);
         }
-        // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows), 32-column chunks w / 4, w / 4 + 2, ... ----
-        ok = ok && mbar_wait(accum, 0u, ctl, status, 0x500u);
+        // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows), 32-column chunks w / 4, w / 4 + 2, ... and
+        //      sends each 32 x 32 piece out through its own 4 KB staging buffer and TMA store (no CTA-wide sync) ----
+        ok = ok && mbar_wait(accum, 0u, ctl, status, 0x500u) && !ctl->abort;
         __syncwarp();
         const bool all_ok = __all_sync(0xffffffffu, ok);
         if (all_ok) {
             tc_fence_after();
             const uint32_t q4 = warp & 3u, half = warp >> 2;
             const uint32_t out_row = n0 + q4 * 32u + lane;
-            for (uint32_t c = half; c * 32u < nt; c += 2u) {
+            float* stage_out = reinterpret_cast<float*>(base) + warp * 1024u;   // every pipeline stage is idle now
+            for (uint32_t c = half; c * 32u < T; c += 2u) {
                 uint32_t v[32];
                 tmem_ld32(tmem + ((q4 * 32u) << 16) + c * 32u, v);
 #pragma unroll
                 for (uint32_t j = 0; j < 32; ++j) {
                     const uint32_t m = m0 + c * 32u + j;
-                    if (m < M && out_row < N && !(diag & 8u)) {
-                        float y;
-                        if (INT8) {
-                            const float total_scale = __fmul_rn(__uint_as_float(__ldg(ACT + 2u * m)), w_scale);
-                            y = __fmul_rn((float)(int)v[j], total_scale);
-                        } else {
-                            y = __uint_as_float(v[j]);
-                        }
-                        dst[(size_t)m * dst_stride + out_row] = y;
+                    float y;
+                    if (INT8) {
+                        const float total_scale =
+                            __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
+                        y = __fmul_rn((float)(int)v[j], total_scale);
+                    } else {
+                        y = __uint_as_float(v[j]);
                     }
+                    if (p.tma_store)
+                        stage_out[j * 32u + lane] = y;
+                    else if (m < p.M && out_row < p.N && !(p.diag & 8u))
+                        p.dst[(size_t)m * p.dst_stride + out_row] = y;
+                }
+                if (p.tma_store && !(p.diag & 8u)) {
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {   // rows past M and columns past N are clipped by the tensor map
+                        tma_store_2d(&out_map, smem_u32(stage_out), (int)(n0 + q4 * 32u), (int)(m0 + c * 32u));
+                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // buffer reusable
+                    }
+                    __syncwarp();
                 }
             }
+            if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem, kTmemCols);
+    if (warp == 9) tmem_dealloc(tmem, p.tmem_cols);
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------
@@ -442,51 +505,123 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+static bool encode_2d(EncodeTiledFn enc, CUtensorMap* map, CUtensorMapDataType dt, uint32_t esz, const void* ptr,
+                      uint64_t inner, uint64_t rows, uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows,
+                      CUtensorMapSwizzle sw) {
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    (void)esz;
+    return enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Token tile: split M into j tiles of T = ceil(M / j) rounded up to 32 and take the j with the fewest token-columns
+// per SM over all waves (a fixed per-tile cost stands for prologue + epilogue), preferring the larger tile on ties.
+static uint32_t choose_tok_tile(uint32_t M, uint32_t row_tiles, int sm_count) {
+    uint32_t best_t = 0;
+    uint64_t best_cost = ~0ull;
+    for (uint32_t j = (M + kTokMax - 1) / kTokMax; j <= 16; ++j) {
+        const uint32_t t = (((M + j - 1) / j) + 31u) & ~31u;
+        if (t > (uint32_t)kTokMax || t < 32u) continue;
+        const uint32_t tiles = row_tiles * ((M + t - 1) / t);
+        const uint64_t waves = (tiles + sm_count - 1) / sm_count;
+        const uint64_t cost = waves * (t + 48u);
+        if (cost < best_cost) {
+            best_cost = cost;
+            best_t = t;
+        }
+        if (t == 32u) break;
+    }
+    return best_t ? best_t : (uint32_t)kTokMax;
+}
+
 template <int TYPE>
-static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, void* act, uint64_t act_range, void* dstp,
-                       uint64_t dst_range, const void* actscale, uint32_t M, uint32_t N, uint32_t K,
+static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, const void* act, uint64_t act_range,
+                       void* dstp, uint64_t dst_range, const void* actscale, uint32_t M, uint32_t N, uint32_t K,
                        uint32_t dst_stride, float w_scale, uint32_t diag) {
-    constexpr uint32_t BK = block_k<TYPE>();
-    constexpr uint32_t esz = TYPE == T_I2_S ? 1u : 2u;
-    if (M == 0 || N == 0 || K == 0 || (K % BK) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
-    if (TYPE == T_Q4_K && (K & 255u)) return AC_ERR_KERNEL_ARG_INVALID;
+    using C = Cfg<TYPE>;
+    constexpr uint32_t esz = C::kInt8 ? 1u : 2u;
+    if (M == 0 || N == 0 || K == 0 || (K % C::kBlockK) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    if (C::kScales && (K & 255u)) return AC_ERR_KERNEL_ARG_INVALID;   // scale rows must be whole 16-byte groups
     if (act_range < (uint64_t)M * K * esz || dst_range < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
         return AC_ERR_INVALID_BUFFER_SIZE;
-    if (((uintptr_t)act & 15u) || (((uint64_t)K * esz) & 15u)) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    if (((uintptr_t)act & 15u) || ((uintptr_t)Qp & 15u) || (C::kScales && ((uintptr_t)Sp & 15u)))
+        return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return AC_ERR_DRIVER_SYMBOL_MISSING;
-    CUtensorMap map;
-    const cuuint64_t dims[2] = {K, M};
-    const cuuint64_t strides[1] = {(cuuint64_t)K * esz};
-    const cuuint32_t box[2] = {BK, (cuuint32_t)kTokMax};
-    const cuuint32_t estr[2] = {1, 1};
-    if (enc(&map, TYPE == T_I2_S ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act, dims,
-            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+
+    Params p;
+    memset(&p, 0, sizeof(p));
+    p.dst = (float*)dstp;
+    p.act = (const uint32_t*)actscale;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.dst_stride = dst_stride;
+    p.w_scale = w_scale;
+    p.diag = diag & 15u;
+    p.status = a.status;
+    const uint32_t row_tiles = (N + kRows - 1) / kRows;
+    const uint32_t forced = diag >> 8;   // diagnostic: bits 8.. force the token tile
+    p.tok_tile = forced ? forced : choose_tok_tile(M, row_tiles, a.sm_count > 0 ? a.sm_count : 148);
+    if (p.tok_tile == 0 || p.tok_tile > (uint32_t)kTokMax || (p.tok_tile & 31u)) return AC_ERR_KERNEL_ARG_INVALID;
+    p.tmem_cols = 32;
+    while (p.tmem_cols < p.tok_tile) p.tmem_cols <<= 1;
+    p.tma_store = ((dst_stride & 3u) == 0u && ((uintptr_t)dstp & 15u) == 0u) ? 1u : 0u;
+
+    const uint32_t fixed = 1024u + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + 512u;
+    const uint32_t per_stage = kABytes + p.tok_tile * kRowBytes;
+    uint32_t stages = (kSmemLimit - fixed) / per_stage;
+    if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
+    if (stages < 3u) return AC_ERR_INVALID_WORK_GROUP_SIZE;
+    p.stages = stages;
+    const uint32_t smem_bytes = fixed + stages * per_stage;
+
+    CUtensorMap act_map, raw_map, scale_map, out_map;
+    const uint64_t row_bytes = (uint64_t)(K / C::kBlockK) * C::kRawRow;
+    if (!encode_2d(enc, &act_map, C::kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, esz, act,
+                   K, M, (uint64_t)K * esz, C::kBlockK, p.tok_tile, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_2d(enc, &raw_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Qp, row_bytes, N, row_bytes, C::kRawRow, kRows,
+                   CU_TENSOR_MAP_SWIZZLE_NONE))
         return AC_ERR_INVALID_ARGUMENT;
+    if (C::kScales) {
+        const uint64_t srow = (uint64_t)(K >> 8) * 16u;   // 16 bytes of scales per 256 weights
+        if (!encode_2d(enc, &scale_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Sp, srow, N, srow, 16, kRows,
+                       CU_TENSOR_MAP_SWIZZLE_NONE))
+            return AC_ERR_INVALID_ARGUMENT;
+    } else {
+        scale_map = raw_map;
+    }
+    if (p.tma_store) {
+        if (!encode_2d(enc, &out_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dstp, N, M, (uint64_t)dst_stride * 4u, 32, 32,
+                       CU_TENSOR_MAP_SWIZZLE_NONE))
+            return AC_ERR_INVALID_ARGUMENT;
+    } else {
+        out_map = raw_map;
+    }
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes) !=
+        if (cudaFuncSetAttribute(gemm_tc_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit) !=
             cudaSuccess) {
             cudaGetLastError();
             return AC_ERR_INVALID_WORK_GROUP_SIZE;
         }
         attr_set = true;
     }
-    const dim3 grid((M + kTokMax - 1) / kTokMax, (N + kRows - 1) / kRows);
+    const dim3 grid((M + p.tok_tile - 1) / p.tok_tile, row_tiles);
     if (grid.y > 65535u) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    gemm_tc_kernel<TYPE><<<grid, kThreads, kSmemBytes, a.stream>>>(map, (const uint8_t*)Qp, (const uint8_t*)Sp,
-                                                                   (float*)dstp, (const uint32_t*)actscale, M, N, K,
-                                                                   dst_stride, w_scale, diag, a.status);
+    gemm_tc_kernel<TYPE><<<grid, kThreads, smem_bytes, a.stream>>>(act_map, raw_map, scale_map, out_map, p);
     return check_launch();
 }
 
 }  // namespace tc
 
 // ameva_mmtc_<q4_0|q8_0|q4_K>: bindings 0 Q, 1 S, 2 AH (fp16 activations [M][K], written by ameva_quant_a8_f16 /
-// ameva_quant_a8b_f16), 3 dst f32 [M][dst_stride];  push {M, N, K, dst_stride, diag}
+// ameva_quant_a8b_f16), 3 dst f32 [M][dst_stride];  push {M, N, K (% 256), dst_stride, diag}
 // diag (0 in production; results are meaningless otherwise) switches one pipeline stage off for profiling:
-// 1 = no weight dequantization, 2 = no activation TMA, 4 = no MMA, 8 = no output stores.
+// 1 = no weight dequantization, 2 = no activation TMA, 4 = no MMA, 8 = no output stores; bits 8.. force the token tile.
 template <int TYPE, uint32_t QB, uint32_t SB, uint32_t BLK>
 static AcResult launch_mmtc(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
@@ -501,7 +636,7 @@ AcResult launch_mmtc_q8_0(const LaunchArgs& a) { return launch_mmtc<tc::T_Q8_0, 
 AcResult launch_mmtc_q4_K(const LaunchArgs& a) { return launch_mmtc<tc::T_Q4_K, 128, 16, 256>(a); }
 
 // bitnet_gemm_i2_s: bindings 0 packed weights, 1 int8 activations [M][K], 2 dst f32 [M][dst_stride], 3 act[2] per row
-// {bits of dequant, sum q};  push {M, N, K, dst_stride, weight_scale_bits, diag}
+// {bits of dequant, sum q};  push {M, N, K (% 128), dst_stride, weight_scale_bits, diag}
 AcResult launch_bitnet_gemm_i2_s(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
     if (K == 0 || (K & 127u)) return AC_ERR_KERNEL_ARG_INVALID;

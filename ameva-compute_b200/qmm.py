@@ -133,7 +133,8 @@ class MulMat:
         self.round_mode, self.q8k_mode, self.dump = round_mode, q8k_mode, dump_block_sums
         # exact = keep every M on the dp4a kernels (exact per-block int32 sums); otherwise M > 8 runs on tensor cores
         self.exact = exact or dump_block_sums
-        self.tc_ok = self.K % (128 if self.type == GGML_TYPE_I2_S else 64) == 0
+        # the GEMM stages weights and scales with TMA: whole 128-byte operand rows, whole 16-byte scale groups per row
+        self.tc_ok = self.K % (128 if self.type == GGML_TYPE_I2_S else 256) == 0
         self.qbind, self.sbind = _bindings_for(self.view)
         K = self.K
         self.aq = ctx.buffer(max_m * K)
