@@ -3,16 +3,18 @@
 //   dst[m][n] = sum_k W[n][k] * A[m][k]        W: N x K block-quantized, A: M x K quantized on the fly
 //
 // One CTA computes a 128 (weight rows) x T (tokens, T <= 256 chosen by the host to balance the waves over the SMs)
-// output tile, walking K in blocks of one 128-byte swizzle row (64 fp16 or 128 int8 elements):
-//   warp 10    streams the CTA's packed weight rows with TMA, one box of 128 rows per K block, into a deep ring of raw
-//              stages (and the block scales once per 256 weights into their own small ring);
-//   warps 0-7  dequantize a raw stage in shared memory into the K-major, 128B-swizzled operand image tcgen05.mma reads
-//              (fp16 with the block scales folded in, one rounding, for Q4_0 / Q8_0 / Q4_K; int8 ternary values for
-//              I2_S); after the last K block they are the epilogue: tcgen05.ld, then every warp sends its 32 x 32
-//              pieces out through a 4 KB staging buffer and a TMA store (plain coalesced stores when the output is
-//              not 16-byte aligned);
-//   warp 8     streams the activation tile with TMA (2-D tensor map, 128B swizzle) into the other operand's stages;
-//   warp 9     allocates TMEM and issues the MMAs (one elected thread), releasing stages through tcgen05.commit.
+// output tile, walking K in blocks of 64 fp16 / 128 int8 elements (one 128-byte swizzle row of the activation operand):
+//   warp 18     streams the CTA's packed weight rows with TMA, boxes of 128 rows x 128 contiguous bytes (2 or 4 K
+//               blocks, 128B-swizzled), into a ring of raw stages, and the block scales once per 256 weights;
+//   warps 0-15  (two groups of eight taking alternate K blocks) dequantize: each thread owns one weight row = one TMEM
+//               lane and half a K block, converts it in registers (fp16 with the block scales folded in, one rounding,
+//               for Q4_0 / Q8_0 / Q4_K; int8 ternary values for I2_S) and writes it with tcgen05.st into a ring of
+//               tensor-memory operand stages: the weight operand never touches shared memory. After the last K block
+//               the same warps are the epilogue: tcgen05.ld, then every warp sends its 32 x 32 pieces out through a
+//               4 KB staging buffer and a TMA store (plain coalesced stores when the output is not 16-byte aligned);
+//   warp 16     streams the activation tile with TMA (2-D tensor map, 128B swizzle) into shared-memory stages;
+//   warp 17     allocates TMEM and issues the MMAs (one elected thread; A from tensor memory, B from shared memory),
+//               releasing stages through tcgen05.commit.
 // Stages are handed over with mbarriers; every wait is bounded by a cycle budget, after which the CTA records
 // DEV_STATUS_WAIT_TIMEOUT in the context's status words, stops, frees its TMEM and returns (the host turns it into
 // AC_ERR_LAUNCH_TIMEOUT). No TMA load carries a cluster qualifier beyond its own CTA.
@@ -36,11 +38,17 @@ namespace tc {
 constexpr int kRows = 128;          // weight rows per CTA (UMMA M)
 constexpr int kTokMax = 256;        // tokens per CTA at most (UMMA N, multiple of 16)
 constexpr int kRowBytes = 128;      // bytes of one operand row per K block (the swizzle span)
-constexpr int kDequantThreads = 256;
-constexpr int kThreads = 352;       // 8 dequant/epilogue warps + activation TMA warp + MMA warp + weight TMA warp
-constexpr int kMaxStages = 6;
+constexpr int kDequantThreads = 256;   // threads that convert one K block (one dequant group)
+constexpr int kGroupWarps = kDequantThreads / 32;      // one elected arrival per warp on the stage barriers
+constexpr int kDequantGroups = 2;       // two groups take alternate K blocks, so each has two MMA periods per block
+constexpr int kDequantWarps = kGroupWarps * kDequantGroups;
+constexpr int kThreads = (kDequantWarps + 3) * 32;   // dequant/epilogue warps + activation TMA, MMA, weight TMA warps
+constexpr int kWarpAct = kDequantWarps, kWarpMma = kDequantWarps + 1, kWarpRaw = kDequantWarps + 2;
+constexpr int kMaxStages = 6;        // activation stages in shared memory
+constexpr int kMaxAStages = 8;       // weight stages in tensor memory (32 columns each, after the accumulator)
+constexpr uint32_t kTmemCols = 512;  // 256 accumulator columns + 8 x 32 operand columns
 constexpr int kScaleSlots = 3;
-constexpr uint32_t kABytes = kRows * kRowBytes;     // 16 KB per operand stage of weights
+constexpr uint32_t kEpilogueBytes = kDequantWarps * 4096u;   // one 32 x 32 fp32 staging buffer per epilogue warp
 constexpr uint32_t kScaleBytes = kRows * 16;        // 2 KB: 16 bytes of scales per row per 256 weights
 constexpr uint32_t kSmemLimit = 227 * 1024;
 constexpr long long kWaitCycles = 2000000000ll;     // about one second
@@ -53,8 +61,11 @@ struct Cfg {
     static constexpr bool kScales = TYPE != T_I2_S;
     static constexpr uint32_t kBlockK = kInt8 ? 128u : 64u;                 // K elements per K block
     static constexpr uint32_t kRawRow = TYPE == T_Q8_0 ? 64u : 32u;         // packed bytes per row per K block
-    static constexpr uint32_t kRawBytes = kRows * kRawRow;
-    static constexpr uint32_t kRawSlots = TYPE == T_Q8_0 ? 6u : 8u;
+    // A raw stage is one TMA box of 128 rows x 128 contiguous bytes (a full L2 line per row, 128B-swizzled in shared
+    // memory): kGroup K blocks of packed weights.
+    static constexpr uint32_t kGroup = 128u / kRawRow;
+    static constexpr uint32_t kRawBytes = kRows * 128u;
+    static constexpr uint32_t kRawSlots = TYPE == T_Q8_0 ? 4u : 3u;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------------------------
@@ -101,6 +112,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
     return true;
 }
 
+// Position in a ring of n slots: slot index and the parity of the current pass (no divisions in the K loop).
+struct Ring {
+    uint32_t idx, phase, n;
+    __device__ __forceinline__ Ring(uint32_t slots) : idx(0u), phase(0u), n(slots) {}
+    __device__ __forceinline__ void advance() {
+        if (++idx == n) {
+            idx = 0u;
+            phase ^= 1u;
+        }
+    }
+};
+
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -146,6 +169,36 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
     }
 }
 
+// The same with the A operand read from tensor memory (the dequantized weight stage) instead of shared memory.
+template <bool INT8>
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t acc) {
+    if (INT8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc)
+            : "memory");
+    }
+}
+
+// 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+        "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
@@ -183,46 +236,36 @@ __device__ __forceinline__ void bytes_to_h2(uint32_t x, __half2& lo, __half2& hi
     hi = *reinterpret_cast<const __half2*>(&b);
 }
 
-// 16-byte chunk c of operand row r lives at chunk position c ^ (r % 8) (the 128-byte swizzle).
-__device__ __forceinline__ void store_chunk(uint8_t* stage, uint32_t r, uint32_t c, uint4 v) {
-    reinterpret_cast<uint4*>(stage + r * kRowBytes)[c ^ (r & 7u)] = v;
+// 16-byte chunk c of row r of a raw stage (128 rows x 128 bytes, written by TMA with the 128-byte swizzle).
+__device__ __forceinline__ uint4 raw_chunk(const uint8_t* raw, uint32_t r, uint32_t c) {
+    return reinterpret_cast<const uint4*>(raw + r * 128u)[c ^ (r & 7u)];
 }
 
-// ---- dequantization of one raw stage (128 rows x one K block) into an operand stage -----------------------------------
-// Every thread reads 16 contiguous bytes; consecutive lanes read consecutive 16-byte pieces of the raw stage, so the
-// shared-memory reads are conflict free, and a quarter-warp's eight stores land on eight different chunk positions.
+// ---- dequantization of (row r, half h) of one K block: 32 fp16 (or 64 int8) values = 16 TMEM columns -----------------
+// The lanes of a warp are 32 consecutive rows reading the same chunk index, which the swizzle spreads over all banks.
 template <int TYPE>
-__device__ __forceinline__ void dequant_stage(const uint8_t* raw, const uint8_t* sc, uint8_t* stage, uint32_t t,
-                                              uint32_t kb) {
+__device__ __forceinline__ void dequant_half(const uint8_t* raw, const uint8_t* sc, uint32_t r, uint32_t h, uint32_t kb,
+                                             uint32_t* o) {
     if constexpr (TYPE == T_Q8_0) {
-        // raw: 64 B per row (2 units of 32 int8); sc: 16 B per row = 8 fp16 scales of the 8 units of this 256-group
+        // raw row: 2 K blocks x 64 B; this half: 32 int8 = chunks 4 (kb % 2) + 2h, +1; scale of unit 2 (kb % 4) + h
+        const uint32_t c0 = 4u * (kb & 1u) + 2u * h;
+        const uint4 q0 = raw_chunk(raw, r, c0), q1 = raw_chunk(raw, r, c0 + 1u);
+        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + h) * 2u));
         const __half2 bias = __float2half2_rn(1152.0f);   // 1024 (magic) + 128 (bytes are q + 128 after the xor)
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-        for (uint32_t pass = 0; pass < 2; ++pass) {
-            const uint32_t task = t + pass * kDequantThreads, r = task >> 2, c = task & 3u;
-            const uint4 q = *reinterpret_cast<const uint4*>(raw + task * 16u);
-            const __half d = *reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + (c >> 1)) * 2u);
-            const __half2 d2 = __half2half2(d);
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-            uint32_t o[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                __half2 lo, hi;
-                bytes_to_h2(w[i] ^ 0x80808080u, lo, hi);
-                o[2 * i] = pack_h2(__hmul2(__hsub2(lo, bias), d2));
-                o[2 * i + 1] = pack_h2(__hmul2(__hsub2(hi, bias), d2));
-            }
-            store_chunk(stage, r, 2u * c, make_uint4(o[0], o[1], o[2], o[3]));
-            store_chunk(stage, r, 2u * c + 1u, make_uint4(o[4], o[5], o[6], o[7]));
+        for (int i = 0; i < 8; ++i) {
+            __half2 lo, hi;
+            bytes_to_h2(w[i] ^ 0x80808080u, lo, hi);
+            o[2 * i] = pack_h2(__hmul2(__hsub2(lo, bias), d2));
+            o[2 * i + 1] = pack_h2(__hmul2(__hsub2(hi, bias), d2));
         }
     } else if constexpr (TYPE == T_Q4_0) {
-        // raw: 32 B per row (2 units of 16 B: byte j = weight j low nibble, weight j + 16 high nibble)
-        const uint32_t r = t >> 1, u = t & 1u;
-        const uint4 q = *reinterpret_cast<const uint4*>(raw + t * 16u);
-        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + u) * 2u));
+        // raw row: 4 K blocks x 32 B; this half: one unit of 16 B (byte j = weight j low nibble, weight j + 16 high)
+        const uint4 q = raw_chunk(raw, r, 2u * (kb & 3u) + h);
+        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + h) * 2u));
         const __half2 bias = __float2half2_rn(1032.0f);   // 1024 (magic) + 8 (the nibble offset)
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-        uint32_t o[16];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {   // low nibbles: weights 4i..4i+3; high nibbles: weights 16+4i..16+4i+3
             __half2 lo, hi;
@@ -233,14 +276,11 @@ __device__ __forceinline__ void dequant_stage(const uint8_t* raw, const uint8_t*
             o[8 + 2 * i] = pack_h2(__hmul2(__hsub2(lo, bias), d2));
             o[8 + 2 * i + 1] = pack_h2(__hmul2(__hsub2(hi, bias), d2));
         }
-#pragma unroll
-        for (uint32_t i = 0; i < 4; ++i)
-            store_chunk(stage, r, 4u * u + i, make_uint4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]));
     } else if constexpr (TYPE == T_Q4_K) {
-        // raw: 32 B per row = qs[32k' .. 32k'+31], k' = kb % 4: low nibbles are sub-block 2k', high nibbles 2k'+1;
-        // this thread holds bytes 16c .. 16c+15: weights 16c..16c+15 of both sub-blocks. w = (d sc) q - (dmin m).
-        const uint32_t r = t >> 1, c = t & 1u;
-        const uint4 q = *reinterpret_cast<const uint4*>(raw + t * 16u);
+        // raw row: one 256-block = 4 K blocks x 32 B; K block k' = kb % 4 is qs[32k' .. 32k'+31]: low nibbles are
+        // sub-block 2k' (half 0 of the K block), high nibbles sub-block 2k'+1 (half 1). w = (d sc) q - (dmin m).
+        const uint32_t c0 = 2u * (kb & 3u);
+        const uint4 q0 = raw_chunk(raw, r, c0), q1 = raw_chunk(raw, r, c0 + 1u);
         const uint4 s = *reinterpret_cast<const uint4*>(sc + r * 16u);
         const uint32_t p16 = 16u * (kb & 1u);   // the byte pair (2k', 2k'+1) % 4 inside each scale word
         const uint32_t a = (s.y >> p16) & 0xFFFFu, b = (s.z >> p16) & 0xFFFFu, e = (s.w >> p16) & 0xFFFFu;
@@ -252,42 +292,30 @@ __device__ __forceinline__ void dequant_stage(const uint8_t* raw, const uint8_t*
             scp = (e & 0x0F0Fu) | ((a >> 2) & 0x3030u);
             mnp = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
         }
-        const float d = h2f((uint16_t)(s.x & 0xFFFFu)), dmin = h2f((uint16_t)(s.x >> 16));
-        const float dl0 = d * (float)(scp & 0xFFu), dl1 = d * (float)(scp >> 8);
-        const float ml0 = dmin * (float)(mnp & 0xFFu), ml1 = dmin * (float)(mnp >> 8);
-        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-        uint32_t o[16];
+        const float dl = h2f((uint16_t)(s.x & 0xFFFFu)) * (float)((scp >> (8u * h)) & 0xFFu);
+        const float ml = h2f((uint16_t)(s.x >> 16)) * (float)((mnp >> (8u * h)) & 0xFFu);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t x = (w[i] >> (4u * h)) & 0x0F0F0F0Fu;
+            float f[4];
 #pragma unroll
-            for (int hi = 0; hi < 2; ++hi) {
-                const uint32_t x = (w[i] >> (4 * hi)) & 0x0F0F0F0Fu;
-                const float dl = hi ? dl1 : dl0, ml = hi ? ml1 : ml0;
-                float f[4];
-#pragma unroll
-                for (int k = 0; k < 4; ++k)   // exact nibble -> float through the 2^23 magic, then one fma
-                    f[k] = fmaf(__uint_as_float(0x4B000000u | ((x >> (8 * k)) & 0xFFu)) - 8388608.0f, dl, -ml);
-                o[8 * hi + 2 * i] = pack_h2(__floats2half2_rn(f[0], f[1]));
-                o[8 * hi + 2 * i + 1] = pack_h2(__floats2half2_rn(f[2], f[3]));
-            }
+            for (int k = 0; k < 4; ++k)   // exact nibble -> float through the 2^23 magic, then one fma
+                f[k] = fmaf(__uint_as_float(0x4B000000u | ((x >> (8 * k)) & 0xFFu)) - 8388608.0f, dl, -ml);
+            o[2 * i] = pack_h2(__floats2half2_rn(f[0], f[1]));
+            o[2 * i + 1] = pack_h2(__floats2half2_rn(f[2], f[3]));
         }
-        store_chunk(stage, r, 2u * c, make_uint4(o[0], o[1], o[2], o[3]));
-        store_chunk(stage, r, 2u * c + 1u, make_uint4(o[4], o[5], o[6], o[7]));
-        store_chunk(stage, r, 4u + 2u * c, make_uint4(o[8], o[9], o[10], o[11]));
-        store_chunk(stage, r, 5u + 2u * c, make_uint4(o[12], o[13], o[14], o[15]));
     } else {
-        // I2_S: raw 32 B per row = one 128-weight block; byte k holds weights k, 32+k, 64+k, 96+k in bits 7-6 .. 1-0.
-        // This thread holds bytes 16c .. 16c+15: for group g the weights 32g + 16c .. +15 = operand chunk 2g + c.
-        const uint32_t r = t >> 1, c = t & 1u;
-        const uint4 q = *reinterpret_cast<const uint4*>(raw + t * 16u);
+        // I2_S: raw row: 4 K blocks x 32 B; byte k of a block holds weights k, 32+k, 64+k, 96+k in bits 7-6 .. 1-0.
+        // Half h holds groups 2h and 2h+1: weights 64h .. 64h+63 as 16 words of four int8.
+        const uint32_t c0 = 2u * (kb & 3u);
+        const uint4 q0 = raw_chunk(raw, r, c0), q1 = raw_chunk(raw, r, c0 + 1u);
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
-        for (uint32_t g = 0; g < 4; ++g) {
-            const uint32_t sh = 6u - 2u * g;
-            store_chunk(stage, r, 2u * g + c,
-                        make_uint4(__vsub4((q.x >> sh) & 0x03030303u, 0x01010101u),
-                                   __vsub4((q.y >> sh) & 0x03030303u, 0x01010101u),
-                                   __vsub4((q.z >> sh) & 0x03030303u, 0x01010101u),
-                                   __vsub4((q.w >> sh) & 0x03030303u, 0x01010101u)));
+        for (uint32_t g = 0; g < 2; ++g) {
+            const uint32_t sh = 6u - 2u * (2u * h + g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[8 * g + i] = __vsub4((w[i] >> sh) & 0x03030303u, 0x01010101u);
         }
     }
 }
@@ -297,13 +325,19 @@ struct Params {
     const uint32_t* act;      // I2_S: {bits of 1/scale, sum q} per token row
     uint32_t M, N, K, dst_stride;
     uint32_t tok_tile;        // T: tokens per CTA, multiple of 32, <= 256
-    uint32_t stages;          // operand stages (3..6)
-    uint32_t tmem_cols;       // power of two >= T
+    uint32_t b_stages;        // activation operand stages in shared memory (3..6)
+    uint32_t a_stages;        // weight operand stages in tensor memory (2..8), 32 columns each, after the accumulator
     uint32_t tma_store;       // 1: epilogue through shared memory + TMA store
     float w_scale;
     uint32_t diag;
     uint32_t* status;
 };
+
+// Diagnostic timeline (diag bit 4): CTA (0,0) writes SM clock stamps into the output buffer instead of results.
+__device__ __forceinline__ void trace(const Params& p, uint32_t slot) {
+    if ((p.diag & 16u) && blockIdx.x == 0 && blockIdx.y == 0)
+        reinterpret_cast<long long*>(p.dst)[slot] = clock64();
+}
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
 template <int TYPE>
@@ -315,143 +349,193 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     constexpr bool INT8 = C::kInt8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const uint32_t S = p.stages, T = p.tok_tile, b_bytes = T * kRowBytes;
-    uint8_t* sA = base;                               // S x 16 KB
-    uint8_t* sB = sA + S * kABytes;                   // S x T*128 B
-    uint8_t* sRaw = sB + S * b_bytes;                 // kRawSlots x kRawBytes
-    uint8_t* sSc = sRaw + C::kRawSlots * C::kRawBytes;   // kScaleSlots x 2 KB
+    const uint32_t S = p.b_stages, SA = p.a_stages, T = p.tok_tile, b_bytes = T * kRowBytes;
+    uint8_t* sB = base;                                               // S x T*128 B (>= 64 KB: epilogue staging)
+    uint8_t* sRaw = sB + max(S * b_bytes, kEpilogueBytes);            // kRawSlots x 16 KB
+    uint8_t* sSc = sRaw + C::kRawSlots * C::kRawBytes;                // kScaleSlots x 2 KB
     uint64_t* bars = reinterpret_cast<uint64_t*>(sSc + kScaleSlots * kScaleBytes);
-    // barrier order: full_a[6] full_b[6] empty[6] raw_full[8] raw_empty[8] sc_full[3] sc_empty[3] accum
-    const uint32_t full_a = smem_u32(bars), full_b = full_a + 8u * kMaxStages, empty = full_b + 8u * kMaxStages,
-                   raw_full = empty + 8u * kMaxStages, raw_empty = raw_full + 8u * 8u, sc_full = raw_empty + 8u * 8u,
-                   sc_empty = sc_full + 8u * kScaleSlots, accum = sc_empty + 8u * kScaleSlots;
-    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 3 * kMaxStages + 16 + 2 * kScaleSlots + 1);
+    const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8u * 8u, full_b = empty_a + 8u * 8u,
+                   empty_b = full_b + 8u * 6u, raw_full = empty_b + 8u * 6u, raw_empty = raw_full + 8u * 4u,
+                   sc_full = raw_empty + 8u * 4u, sc_empty = sc_full + 8u * 3u, accum = sc_empty + 8u * 3u;
+    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 43);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t m0 = blockIdx.x * T, n0 = blockIdx.y * kRows;
     const uint32_t KB = p.K / C::kBlockK;
+    // Every CTA walks K from its own starting block (a multiple of 4 blocks = one scale group) and wraps around: at any
+    // moment the CTAs of a wave read different activation lines, instead of all of them hitting the same L2 lines.
+    const uint32_t rot = (KB & 3u) ? 0u : 4u * ((blockIdx.y * 5u + blockIdx.x * 3u) % (KB >> 2));
     uint32_t* status = p.status;
+    if (threadIdx.x == 0) trace(p, 0);
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < kMaxStages; ++s) {
-            mbar_init(full_a + 8u * s, kDequantThreads);
-            mbar_init(full_b + 8u * s, 1u);
-            mbar_init(empty + 8u * s, 1u);
-        }
         for (uint32_t s = 0; s < 8u; ++s) {
+            mbar_init(full_a + 8u * s, kGroupWarps);
+            mbar_init(empty_a + 8u * s, 1u);
+        }
+        for (uint32_t s = 0; s < 6u; ++s) {
+            mbar_init(full_b + 8u * s, 1u);
+            mbar_init(empty_b + 8u * s, 1u);
+        }
+        for (uint32_t s = 0; s < 4u; ++s) {
             mbar_init(raw_full + 8u * s, 1u);
-            mbar_init(raw_empty + 8u * s, kDequantThreads);
+            mbar_init(raw_empty + 8u * s, kDequantWarps);
         }
         for (uint32_t s = 0; s < kScaleSlots; ++s) {
             mbar_init(sc_full + 8u * s, 1u);
-            mbar_init(sc_empty + 8u * s, kDequantThreads);
+            mbar_init(sc_empty + 8u * s, kDequantWarps);
         }
         mbar_init(accum, 1u);
         ctl->abort = 0u;
         fence_barrier_init();
     }
-    if (warp == 9) tmem_alloc(smem_u32(&ctl->tmem_base), p.tmem_cols);
+    if (warp == kWarpMma) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem = ctl->tmem_base;
+    const uint32_t tmem = ctl->tmem_base;       // accumulator: columns 0 .. T-1
+    const uint32_t tmem_a = tmem + kTokMax;     // weight operand stages: 32 columns each
+    if (threadIdx.x == 0) trace(p, 1);
 
-    if (warp == 8) {
+    if (warp == kWarpAct) {
         // ---- activation TMA: token rows m0 .. m0+T-1 (rows past M read as zero), K block kb ----
         if (lane == 0) {
-            uint32_t issued = 0;
-            for (uint32_t kb = 0; kb < KB; ++kb, ++issued) {
-                const uint32_t s = kb % S, ph = (kb / S) & 1u;
-                if (!mbar_wait(empty + 8u * s, ph ^ 1u, ctl, status, 0x100u | s)) break;
+            Ring st(S);
+            uint32_t kb = 0;
+            for (; kb < KB; ++kb, st.advance()) {
+                if (!mbar_wait(empty_b + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x100u | st.idx)) break;
                 if (p.diag & 2u) {   // diagnostic: no activation traffic
-                    mbar_arrive(full_b + 8u * s);
+                    mbar_arrive(full_b + 8u * st.idx);
                     continue;
                 }
-                mbar_arrive_expect_tx(full_b + 8u * s, b_bytes);
-                tma_load_2d(smem_u32(sB + s * b_bytes), &act_map, full_b + 8u * s, (int)(kb * C::kBlockK), (int)m0);
+                trace(p, 900u + kb);
+                mbar_arrive_expect_tx(full_b + 8u * st.idx, b_bytes);
+                const uint32_t kbr = kb + rot < KB ? kb + rot : kb + rot - KB;
+                tma_load_2d(smem_u32(sB + st.idx * b_bytes), &act_map, full_b + 8u * st.idx, (int)(kbr * C::kBlockK),
+                            (int)m0);
             }
             if (ctl->abort && !(p.diag & 2u)) {   // let the copies already requested land before the CTA leaves
-                for (uint32_t i = issued > S ? issued - S : 0; i < issued; ++i)
+                for (uint32_t i = kb > S ? kb - S : 0; i < kb; ++i)
                     mbar_wait(full_b + 8u * (i % S), (i / S) & 1u, ctl, status, 0x180u);
             }
         }
-    } else if (warp == 10) {
-        // ---- packed-weight TMA: rows n0 .. n0+127 (rows past N read as zero), raw bytes of K block kb; the scales of
-        //      a 256-weight group once per 4 K blocks ----
+    } else if (warp == kWarpRaw) {
+        // ---- packed-weight TMA: rows n0 .. n0+127 (rows past N read as zero), one 128-byte-per-row box per kGroup K
+        //      blocks; the scales of a 256-weight group once per 4 K blocks ----
         if (lane == 0) {
-            uint32_t issued = 0;
-            for (uint32_t kb = 0; kb < KB; ++kb, ++issued) {
+            Ring rr(C::kRawSlots), sr(kScaleSlots);
+            uint32_t groups = 0, sgroups = 0;
+            bool ok = true;
+            for (uint32_t kb = 0; kb < KB && ok; ++kb) {
                 if (C::kScales && (kb & 3u) == 0u) {
-                    const uint32_t g = kb >> 2, ss = g % kScaleSlots;
-                    if (!mbar_wait(sc_empty + 8u * ss, ((g / kScaleSlots) & 1u) ^ 1u, ctl, status, 0x600u | ss)) break;
-                    mbar_arrive_expect_tx(sc_full + 8u * ss, kScaleBytes);
-                    tma_load_2d(smem_u32(sSc + ss * kScaleBytes), &scale_map, sc_full + 8u * ss, (int)(g * 16u), (int)n0);
+                    ok = mbar_wait(sc_empty + 8u * sr.idx, sr.phase ^ 1u, ctl, status, 0x600u | sr.idx);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(sc_full + 8u * sr.idx, kScaleBytes);
+                    tma_load_2d(smem_u32(sSc + sr.idx * kScaleBytes), &scale_map, sc_full + 8u * sr.idx,
+                                (int)(((sgroups + (rot >> 2)) % ((KB + 3u) >> 2)) * 16u), (int)n0);
+                    ++sgroups;
+                    sr.advance();
                 }
-                const uint32_t rs = kb % C::kRawSlots;
-                if (!mbar_wait(raw_empty + 8u * rs, ((kb / C::kRawSlots) & 1u) ^ 1u, ctl, status, 0x700u | rs)) break;
-                mbar_arrive_expect_tx(raw_full + 8u * rs, C::kRawBytes);
-                tma_load_2d(smem_u32(sRaw + rs * C::kRawBytes), &raw_map, raw_full + 8u * rs, (int)(kb * C::kRawRow),
-                            (int)n0);
+                if ((kb & (C::kGroup - 1u)) == 0u) {
+                    ok = mbar_wait(raw_empty + 8u * rr.idx, rr.phase ^ 1u, ctl, status, 0x700u | rr.idx);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(raw_full + 8u * rr.idx, C::kRawBytes);
+                    tma_load_2d(smem_u32(sRaw + rr.idx * C::kRawBytes), &raw_map, raw_full + 8u * rr.idx,
+                                (int)(((groups + rot / C::kGroup) % ((KB + C::kGroup - 1u) / C::kGroup)) * 128u), (int)n0);
+                    trace(p, 530u + groups);
+                    ++groups;
+                    rr.advance();
+                }
             }
             if (ctl->abort) {
-                for (uint32_t i = issued > C::kRawSlots ? issued - C::kRawSlots : 0; i < issued; ++i)
+                for (uint32_t i = groups > C::kRawSlots ? groups - C::kRawSlots : 0; i < groups; ++i)
                     mbar_wait(raw_full + 8u * (i % C::kRawSlots), (i / C::kRawSlots) & 1u, ctl, status, 0x780u);
             }
         }
-    } else if (warp == 9) {
-        // ---- MMA issuer ----
+    } else if (warp == kWarpMma) {
+        // ---- MMA issuer: A from tensor memory (stage sa), B from shared memory (stage sb) ----
         if (lane == 0) {
             const uint32_t idesc = INT8 ? make_idesc(2u, 1u, T) : make_idesc(1u, 0u, T);
-            for (uint32_t kb = 0; kb < KB; ++kb) {
-                const uint32_t s = kb % S, ph = (kb / S) & 1u;
-                if (!mbar_wait(full_a + 8u * s, ph, ctl, status, 0x200u | s) ||
-                    !mbar_wait(full_b + 8u * s, ph, ctl, status, 0x300u | s)) {
+            Ring sa(SA), sb(S);
+            for (uint32_t kb = 0; kb < KB; ++kb, sa.advance(), sb.advance()) {
+                if (!mbar_wait(full_a + 8u * sa.idx, sa.phase, ctl, status, 0x200u | sa.idx) ||
+                    !mbar_wait(full_b + 8u * sb.idx, sb.phase, ctl, status, 0x300u | sb.idx)) {
                     ctl->abort = 1u;   // visible to whoever passes the accumulator barrier below
                     break;
                 }
+                trace(p, 2u + kb);
                 tc_fence_after();
-                const uint64_t da = make_smem_desc(smem_u32(sA + s * kABytes));
-                const uint64_t db = make_smem_desc(smem_u32(sB + s * b_bytes));
+                const uint64_t db = make_smem_desc(smem_u32(sB + sb.idx * b_bytes));
+                const uint32_t ta = tmem_a + sa.idx * 32u;
                 if (!(p.diag & 4u)) {
 #pragma unroll
-                    for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: +2 in the 16-byte address field
-                        umma<INT8>(tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0u);
+                    for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: 8 TMEM columns / +2 desc units
+                        umma_ts<INT8>(tmem, ta + 8u * k, db + 2u * k, idesc, (kb | k) != 0u);
                 }
-                umma_commit(empty + 8u * s);
+                umma_commit(empty_a + 8u * sa.idx);
+                umma_commit(empty_b + 8u * sb.idx);
+                trace(p, 130u + kb);
             }
             umma_commit(accum);
         }
     } else {
-        // ---- weight dequantization: raw stage -> operand stage ----
-        const uint32_t t = threadIdx.x;
+        // ---- weight dequantization: raw stage -> tensor-memory operand stage. Group dg converts the K blocks with
+        //      kb % 2 == dg; in a group, warp w owns TMEM lanes (rows) 32 (w % 4) .. +31 and half w / 4 of the K block ----
+        const uint32_t dg = threadIdx.x / kDequantThreads, wg = warp & (kGroupWarps - 1u);
+        const uint32_t q4 = wg & 3u, h = wg >> 2, r = q4 * 32u + lane;
         bool ok = true;
+        Ring sa(SA), rr(C::kRawSlots), sr(kScaleSlots);
         for (uint32_t kb = 0; kb < KB && ok; ++kb) {
-            const uint32_t s = kb % S, rs = kb % C::kRawSlots, g = kb >> 2, ss = g % kScaleSlots;
-            if (C::kScales && (kb & 3u) == 0u)
-                ok = mbar_wait(sc_full + 8u * ss, (g / kScaleSlots) & 1u, ctl, status, 0x800u | ss);
-            ok = ok && mbar_wait(raw_full + 8u * rs, (kb / C::kRawSlots) & 1u, ctl, status, 0x900u | rs) &&
-                 mbar_wait(empty + 8u * s, ((kb / S) & 1u) ^ 1u, ctl, status, 0x400u | s);
-            if (!ok) break;
-            if (!(p.diag & 1u))
-                dequant_stage<TYPE>(sRaw + rs * C::kRawBytes, sSc + ss * kScaleBytes, sA + s * kABytes, t, kb);
-            fence_async_smem();
-            mbar_arrive(full_a + 8u * s);
-            mbar_arrive(raw_empty + 8u * rs);
-            if (C::kScales && (kb & 3u) == 3u) mbar_arrive(sc_empty + 8u * ss);
+            const uint32_t raw_last = min((kb | (C::kGroup - 1u)), KB - 1u);   // last K block of this raw / scale group
+            const uint32_t sc_last = min((kb | 3u), KB - 1u);
+            if ((kb & 1u) == dg) {
+                const bool tr = (threadIdx.x & (kDequantThreads - 1u)) == 0u;
+                if (tr) trace(p, 1024u + kb);
+                if (C::kScales) ok = mbar_wait(sc_full + 8u * sr.idx, sr.phase, ctl, status, 0x800u | sr.idx);
+                if (tr) trace(p, 650u + kb);
+                ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x900u | rr.idx);
+                if (tr) trace(p, 780u + kb);
+                ok = ok && mbar_wait(empty_a + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx);
+                if (!ok) break;
+                if (tr) trace(p, 260u + kb);
+                tc_fence_after();
+                uint32_t o[16];
+                if (!(p.diag & 1u)) {
+                    dequant_half<TYPE>(sRaw + rr.idx * C::kRawBytes, sSc + sr.idx * kScaleBytes, r, h, kb, o);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) o[i] = 0u;
+                }
+                if (tr) trace(p, 1280u + kb);
+                tmem_st16(tmem_a + ((q4 * 32u) << 16) + sa.idx * 32u + h * 16u, o);
+                if (tr) trace(p, 1408u + kb);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(full_a + 8u * sa.idx);
+                    if (kb + 2u > raw_last) mbar_arrive(raw_empty + 8u * rr.idx);      // my last block of the raw stage
+                    if (C::kScales && kb + 2u > sc_last) mbar_arrive(sc_empty + 8u * sr.idx);
+                    if (tr) trace(p, 390u + kb);
+                }
+            }
+            sa.advance();
+            if (kb == raw_last) rr.advance();
+            if (C::kScales && kb == sc_last) sr.advance();
         }
-        // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows), 32-column chunks w / 4, w / 4 + 2, ... and
-        //      sends each 32 x 32 piece out through its own 4 KB staging buffer and TMA store (no CTA-wide sync) ----
+        // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows) and the 32-column chunks w / 4, w / 4 + 4,
+        //      ..., and sends each 32 x 32 piece out through its own 4 KB staging buffer and a TMA store ----
         ok = ok && mbar_wait(accum, 0u, ctl, status, 0x500u) && !ctl->abort;
+        if (threadIdx.x == 0) trace(p, 520);
         __syncwarp();
         const bool all_ok = __all_sync(0xffffffffu, ok);
         if (all_ok) {
             tc_fence_after();
-            const uint32_t q4 = warp & 3u, half = warp >> 2;
-            const uint32_t out_row = n0 + q4 * 32u + lane;
-            float* stage_out = reinterpret_cast<float*>(base) + warp * 1024u;   // every pipeline stage is idle now
-            for (uint32_t c = half; c * 32u < T; c += 2u) {
+            const uint32_t eq = warp & 3u, cq = warp >> 2;   // TMEM lane quarter, column-chunk phase
+            const uint32_t out_row = n0 + eq * 32u + lane;
+            float* stage_out = reinterpret_cast<float*>(base) + warp * 1024u;   // the activation stages are idle now
+            for (uint32_t c = cq; c * 32u < T; c += kDequantWarps / 4) {
                 uint32_t v[32];
-                tmem_ld32(tmem + ((q4 * 32u) << 16) + c * 32u, v);
+                tmem_ld32(tmem + ((eq * 32u) << 16) + c * 32u, v);
 #pragma unroll
                 for (uint32_t j = 0; j < 32; ++j) {
                     const uint32_t m = m0 + c * 32u + j;
@@ -472,18 +556,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {   // rows past M and columns past N are clipped by the tensor map
-                        tma_store_2d(&out_map, smem_u32(stage_out), (int)(n0 + q4 * 32u), (int)(m0 + c * 32u));
+                        tma_store_2d(&out_map, smem_u32(stage_out), (int)(n0 + eq * 32u), (int)(m0 + c * 32u));
                         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // buffer reusable
                     }
                     __syncwarp();
                 }
             }
             if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            if (threadIdx.x == 0) trace(p, 521);
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem, p.tmem_cols);
+    if (warp == kWarpMma) tmem_dealloc(tmem, kTmemCols);
+    if (threadIdx.x == 0) trace(p, 522);
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------
@@ -561,30 +647,30 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     p.K = K;
     p.dst_stride = dst_stride;
     p.w_scale = w_scale;
-    p.diag = diag & 15u;
+    p.diag = diag & 31u;
     p.status = a.status;
     const uint32_t row_tiles = (N + kRows - 1) / kRows;
     const uint32_t forced = diag >> 8;   // diagnostic: bits 8.. force the token tile
     p.tok_tile = forced ? forced : choose_tok_tile(M, row_tiles, a.sm_count > 0 ? a.sm_count : 148);
     if (p.tok_tile == 0 || p.tok_tile > (uint32_t)kTokMax || (p.tok_tile & 31u)) return AC_ERR_KERNEL_ARG_INVALID;
-    p.tmem_cols = 32;
-    while (p.tmem_cols < p.tok_tile) p.tmem_cols <<= 1;
     p.tma_store = ((dst_stride & 3u) == 0u && ((uintptr_t)dstp & 15u) == 0u) ? 1u : 0u;
 
     const uint32_t fixed = 1024u + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + 512u;
-    const uint32_t per_stage = kABytes + p.tok_tile * kRowBytes;
+    const uint32_t per_stage = p.tok_tile * kRowBytes;
     uint32_t stages = (kSmemLimit - fixed) / per_stage;
     if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
     if (stages < 3u) return AC_ERR_INVALID_WORK_GROUP_SIZE;
-    p.stages = stages;
-    const uint32_t smem_bytes = fixed + stages * per_stage;
+    p.b_stages = stages;
+    p.a_stages = kMaxAStages;
+    const uint32_t stage_area = stages * per_stage > kEpilogueBytes ? stages * per_stage : kEpilogueBytes;
+    const uint32_t smem_bytes = fixed + stage_area;
 
     CUtensorMap act_map, raw_map, scale_map, out_map;
     const uint64_t row_bytes = (uint64_t)(K / C::kBlockK) * C::kRawRow;
     if (!encode_2d(enc, &act_map, C::kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, esz, act,
                    K, M, (uint64_t)K * esz, C::kBlockK, p.tok_tile, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        !encode_2d(enc, &raw_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Qp, row_bytes, N, row_bytes, C::kRawRow, kRows,
-                   CU_TENSOR_MAP_SWIZZLE_NONE))
+        !encode_2d(enc, &raw_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Qp, row_bytes, N, row_bytes, 128, kRows,
+                   CU_TENSOR_MAP_SWIZZLE_128B))
         return AC_ERR_INVALID_ARGUMENT;
     if (C::kScales) {
         const uint64_t srow = (uint64_t)(K >> 8) * 16u;   // 16 bytes of scales per 256 weights

@@ -408,7 +408,10 @@ def main():
             "metric": metric_name(name), "value": unit_value(unit, t, M, N, K, gpu_s / args.steps), "unit": unit,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": gpu_s / args.steps * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "int8 dot (dp4a), fp32 scale-accumulate", "data": "synthetic",
+            "dtype": {"mmtc": "int8 (tcgen05 kind::i8, int32 accumulate)" if t == I2_S else
+                      "f16 (tcgen05 kind::f16 on dequantized fp16 operands, fp32 accumulate in TMEM)"}.get(
+                          mms[0].path, "int8 (dp4a, int32 per block, fp32 scale-accumulate)"),
+            "data": "synthetic",
             "config": {"workload": f"{name}: {desc}", "M": M, "N": N, "K": K,
                        "l2": f"rotating pool of {pool_n} weight copies ({pool_n * shard_bytes / 1e6:.0f} MB > L2) per rank",
                        "parallelism": "single GPU" if world == 1 else f"weight rows sharded over {world} ranks, "
