@@ -97,16 +97,22 @@ struct Ctl {             // shared control words
     volatile uint32_t abort;
 };
 
-// Bounded wait: false when the CTA is aborting (this or another thread ran out of budget).
+// Bounded wait: false when the CTA is aborting (this or another thread ran out of budget). Waiters other than the MMA
+// issuer back off between polls (BACKOFF): a spinning warp takes issue slots from the warps that share its scheduler.
+template <bool BACKOFF = true>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t* status, uint32_t tag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
+    uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if (ctl->abort) return false;
-        if (clock64() - t0 > kWaitCycles) {
-            ctl->abort = 1u;
-            if (atomicCAS(status, DEV_STATUS_OK, DEV_STATUS_WAIT_TIMEOUT) == DEV_STATUS_OK) status[1] = tag;
-            return false;
+        if (BACKOFF) __nanosleep(64);
+        if ((++spins & 63u) == 0u) {
+            if (ctl->abort) return false;
+            if (clock64() - t0 > kWaitCycles) {
+                ctl->abort = 1u;
+                if (atomicCAS(status, DEV_STATUS_OK, DEV_STATUS_WAIT_TIMEOUT) == DEV_STATUS_OK) status[1] = tag;
+                return false;
+            }
         }
     }
     return true;
@@ -325,8 +331,7 @@ struct Params {
     const uint32_t* act;      // I2_S: {bits of 1/scale, sum q} per token row
     uint32_t M, N, K, dst_stride;
     uint32_t tok_tile;        // T: tokens per CTA, multiple of 32, <= 256
-    uint32_t b_stages;        // activation operand stages in shared memory (3..6)
-    uint32_t a_stages;        // weight operand stages in tensor memory (2..8), 32 columns each, after the accumulator
+    uint32_t b_stages;        // pipeline stages (3..6): activations in shared memory, weights in 32 TMEM columns each
     uint32_t tma_store;       // 1: epilogue through shared memory + TMA store
     float w_scale;
     uint32_t diag;
@@ -349,15 +354,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     constexpr bool INT8 = C::kInt8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const uint32_t S = p.b_stages, SA = p.a_stages, T = p.tok_tile, b_bytes = T * kRowBytes;
+    const uint32_t S = p.b_stages, T = p.tok_tile, b_bytes = T * kRowBytes;
     uint8_t* sB = base;                                               // S x T*128 B (>= 64 KB: epilogue staging)
     uint8_t* sRaw = sB + max(S * b_bytes, kEpilogueBytes);            // kRawSlots x 16 KB
     uint8_t* sSc = sRaw + C::kRawSlots * C::kRawBytes;                // kScaleSlots x 2 KB
     uint64_t* bars = reinterpret_cast<uint64_t*>(sSc + kScaleSlots * kScaleBytes);
-    const uint32_t full_a = smem_u32(bars), empty_a = full_a + 8u * 8u, full_b = empty_a + 8u * 8u,
-                   empty_b = full_b + 8u * 6u, raw_full = empty_b + 8u * 6u, raw_empty = raw_full + 8u * 4u,
-                   sc_full = raw_empty + 8u * 4u, sc_empty = sc_full + 8u * 3u, accum = sc_empty + 8u * 3u;
-    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 43);
+    // full[s]: the eight arrivals of the dequant group that wrote TMEM stage s + the activation TMA's arrival and bytes
+    // for shared-memory stage s; empty[s]: one tcgen05.commit when the MMAs that read stage s have finished.
+    const uint32_t full = smem_u32(bars), empty = full + 8u * 6u, raw_full = empty + 8u * 6u,
+                   raw_empty = raw_full + 8u * 4u, sc_full = raw_empty + 8u * 4u, sc_empty = sc_full + 8u * 3u,
+                   accum = sc_empty + 8u * 3u;
+    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 27);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t m0 = blockIdx.x * T, n0 = blockIdx.y * kRows;
@@ -369,13 +376,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     if (threadIdx.x == 0) trace(p, 0);
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < 8u; ++s) {
-            mbar_init(full_a + 8u * s, kGroupWarps);
-            mbar_init(empty_a + 8u * s, 1u);
-        }
         for (uint32_t s = 0; s < 6u; ++s) {
-            mbar_init(full_b + 8u * s, 1u);
-            mbar_init(empty_b + 8u * s, 1u);
+            mbar_init(full + 8u * s, kGroupWarps + 1u);
+            mbar_init(empty + 8u * s, 1u);
         }
         for (uint32_t s = 0; s < 4u; ++s) {
             mbar_init(raw_full + 8u * s, 1u);
@@ -403,20 +406,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             Ring st(S);
             uint32_t kb = 0;
             for (; kb < KB; ++kb, st.advance()) {
-                if (!mbar_wait(empty_b + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x100u | st.idx)) break;
+                if (!mbar_wait(empty + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x100u | st.idx)) break;
                 if (p.diag & 2u) {   // diagnostic: no activation traffic
-                    mbar_arrive(full_b + 8u * st.idx);
+                    mbar_arrive(full + 8u * st.idx);
                     continue;
                 }
                 trace(p, 900u + kb);
-                mbar_arrive_expect_tx(full_b + 8u * st.idx, b_bytes);
+                mbar_arrive_expect_tx(full + 8u * st.idx, b_bytes);
                 const uint32_t kbr = kb + rot < KB ? kb + rot : kb + rot - KB;
-                tma_load_2d(smem_u32(sB + st.idx * b_bytes), &act_map, full_b + 8u * st.idx, (int)(kbr * C::kBlockK),
+                tma_load_2d(smem_u32(sB + st.idx * b_bytes), &act_map, full + 8u * st.idx, (int)(kbr * C::kBlockK),
                             (int)m0);
             }
             if (ctl->abort && !(p.diag & 2u)) {   // let the copies already requested land before the CTA leaves
                 for (uint32_t i = kb > S ? kb - S : 0; i < kb; ++i)
-                    mbar_wait(full_b + 8u * (i % S), (i / S) & 1u, ctl, status, 0x180u);
+                    mbar_wait(full + 8u * (i % S), (i / S) & 1u, ctl, status, 0x180u);
             }
         }
     } else if (warp == kWarpRaw) {
@@ -456,24 +459,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         // ---- MMA issuer: A from tensor memory (stage sa), B from shared memory (stage sb) ----
         if (lane == 0) {
             const uint32_t idesc = INT8 ? make_idesc(2u, 1u, T) : make_idesc(1u, 0u, T);
-            Ring sa(SA), sb(S);
-            for (uint32_t kb = 0; kb < KB; ++kb, sa.advance(), sb.advance()) {
-                if (!mbar_wait(full_a + 8u * sa.idx, sa.phase, ctl, status, 0x200u | sa.idx) ||
-                    !mbar_wait(full_b + 8u * sb.idx, sb.phase, ctl, status, 0x300u | sb.idx)) {
+            Ring st(S);
+            for (uint32_t kb = 0; kb < KB; ++kb, st.advance()) {
+                if (!mbar_wait<false>(full + 8u * st.idx, st.phase, ctl, status, 0x200u | st.idx)) {
                     ctl->abort = 1u;   // visible to whoever passes the accumulator barrier below
                     break;
                 }
                 trace(p, 2u + kb);
                 tc_fence_after();
-                const uint64_t db = make_smem_desc(smem_u32(sB + sb.idx * b_bytes));
-                const uint32_t ta = tmem_a + sa.idx * 32u;
+                const uint64_t db = make_smem_desc(smem_u32(sB + st.idx * b_bytes));
+                const uint32_t ta = tmem_a + st.idx * 32u;
                 if (!(p.diag & 4u)) {
 #pragma unroll
                     for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: 8 TMEM columns / +2 desc units
                         umma_ts<INT8>(tmem, ta + 8u * k, db + 2u * k, idesc, (kb | k) != 0u);
                 }
-                umma_commit(empty_a + 8u * sa.idx);
-                umma_commit(empty_b + 8u * sb.idx);
+                umma_commit(empty + 8u * st.idx);
                 trace(p, 130u + kb);
             }
             umma_commit(accum);
@@ -484,7 +485,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         const uint32_t dg = threadIdx.x / kDequantThreads, wg = warp & (kGroupWarps - 1u);
         const uint32_t q4 = wg & 3u, h = wg >> 2, r = q4 * 32u + lane;
         bool ok = true;
-        Ring sa(SA), rr(C::kRawSlots), sr(kScaleSlots);
+        Ring sa(S), rr(C::kRawSlots), sr(kScaleSlots);
         for (uint32_t kb = 0; kb < KB && ok; ++kb) {
             const uint32_t raw_last = min((kb | (C::kGroup - 1u)), KB - 1u);   // last K block of this raw / scale group
             const uint32_t sc_last = min((kb | 3u), KB - 1u);
@@ -495,7 +496,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 if (tr) trace(p, 650u + kb);
                 ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x900u | rr.idx);
                 if (tr) trace(p, 780u + kb);
-                ok = ok && mbar_wait(empty_a + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx);
+                ok = ok && mbar_wait(empty + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx);
                 if (!ok) break;
                 if (tr) trace(p, 260u + kb);
                 tc_fence_after();
@@ -512,7 +513,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
-                    mbar_arrive(full_a + 8u * sa.idx);
+                    mbar_arrive(full + 8u * sa.idx);
                     if (kb + 2u > raw_last) mbar_arrive(raw_empty + 8u * rr.idx);      // my last block of the raw stage
                     if (C::kScales && kb + 2u > sc_last) mbar_arrive(sc_empty + 8u * sr.idx);
                     if (tr) trace(p, 390u + kb);
@@ -661,7 +662,6 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
     if (stages < 3u) return AC_ERR_INVALID_WORK_GROUP_SIZE;
     p.b_stages = stages;
-    p.a_stages = kMaxAStages;
     const uint32_t stage_area = stages * per_stage > kEpilogueBytes ? stages * per_stage : kEpilogueBytes;
     const uint32_t smem_bytes = fixed + stage_area;
 

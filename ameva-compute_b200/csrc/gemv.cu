@@ -169,32 +169,20 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// Q4_K x Q8_K.  Q: 128 B per 256-block (8 chunks of 16 B), S: 16 B per block (fp16 d, fp16 dmin, scales[12]).
-// Chunk cc of a block: bytes qs[16cc..16cc+15] = 64-group k = cc/2, half h = cc%2; low nibbles are elements
-// 16h..16h+15 of sub-block 2k, high nibbles the same elements of sub-block 2k+1.
-//   lane integer part: isum = sc[2k]*dot_lo + sc[2k+1]*dot_hi;  mpart = m[2k]*bsums[4k+h] + m[2k+1]*bsums[4k+2+h]
+// Q4_K x Q8_K.  Q: 128 B per 256-block, S: 16 B per block (fp16 d, fp16 dmin, scales[12]).
+// A lane takes a 32-byte chunk = qs[32k .. 32k+31] of a block (k = 0..3): the low nibbles are the 32 weights of
+// sub-block 2k, the high nibbles those of sub-block 2k+1, and the matching activations are 64 contiguous int8.
+//   lane integer part: isum = sc[2k]*dot_lo + sc[2k+1]*dot_hi;  mpart = m[2k]*bsum(2k) + m[2k+1]*bsum(2k+1)
 //   y += (d*d_a)*float(isum) - (dmin*d_a)*float(mpart)          (block-integer form, ameva_mmqb.comp:10-16)
+// The four lanes of a block are an aligned lane group (DUMP reduces over them).
 // ---------------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ void q4k_scale_min(const uint4& s, uint32_t j, uint32_t& sc, uint32_t& mn) {
-    // get_scale_min_k4 on the 12 scale bytes held in s.y, s.z, s.w (bytes 0-3, 4-7, 8-11)
-    const uint32_t k = 8u * (j & 3u);
-    const uint32_t b0 = (s.y >> k) & 0xFFu, b1 = (s.z >> k) & 0xFFu, b2 = (s.w >> k) & 0xFFu;
-    if (j < 4u) {
-        sc = b0 & 63u;
-        mn = b1 & 63u;
-    } else {
-        sc = (b2 & 0xFu) | ((b0 >> 6) << 4);
-        mn = (b2 >> 4) | ((b1 >> 6) << 4);
-    }
-}
-
 template <int M, int R, bool DUMP>
 __global__ void __launch_bounds__(kGemvThreads)
-gemv_q4_K_kernel(const uint4* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
+gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
                  const uint8_t* __restrict__ AB, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
                  uint32_t K, uint32_t dst_stride) {
-    constexpr int UN = M <= 2 ? 4 : 2;
-    const uint32_t B = K >> 8, C = K >> 5;  // blocks and 16-byte chunks per row
+    constexpr int UN = M <= 2 ? 2 : 1;
+    const uint32_t B = K >> 8, C = K >> 6;  // blocks and 32-byte chunks per row
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
@@ -203,20 +191,26 @@ gemv_q4_K_kernel(const uint4* __restrict__ Q, const uint4* __restrict__ S, const
     for (int r = 0; r < R; ++r)
 #pragma unroll
         for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
-    size_t rblk[R];
+    const u32x8* qrow[R];
+    const uint4* srow[R];
 #pragma unroll
-    for (int r = 0; r < R; ++r) rblk[r] = (size_t)min(row0 + r, N - 1) * B;
+    for (int r = 0; r < R; ++r) {
+        const size_t blk = (size_t)min(row0 + r, N - 1) * B;
+        qrow[r] = Q + blk * 4u;
+        srow[r] = S + blk;
+    }
 
     for (uint32_t c0 = lane; c0 < C; c0 += 32 * UN) {
-        uint4 wq[UN][R], wsc[UN][R];
+        u32x8 wq[UN][R];
+        uint4 wsc[UN][R];
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t c = c0 + 32 * i;
             if (c < C) {
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    wq[i][r] = ld_stream_u4(Q + rblk[r] * 8u + c);
-                    wsc[i][r] = ld_cached_u4(S + rblk[r] + (c >> 3));  // shared by the 8 lanes of the block
+                    wq[i][r] = ld_stream_u8(qrow[r] + c);
+                    wsc[i][r] = ld_cached_u4(srow[r] + (c >> 2));  // shared by the 4 lanes of the block
                 }
             }
         }
@@ -224,49 +218,62 @@ gemv_q4_K_kernel(const uint4* __restrict__ Q, const uint4* __restrict__ S, const
         for (int i = 0; i < UN; ++i) {
             const uint32_t c = c0 + 32 * i;
             if (c < C) {
-                const uint32_t b = c >> 3, cc = c & 7u, k = cc >> 1, h = cc & 1u;
+                const uint32_t b = c >> 2, k = c & 3u;
+                const uint32_t p16 = 16u * (k & 1u);
+                // scales / mins of sub-blocks 2k, 2k+1 and the two fp16 block scales, per row
+                int sc0[R], sc1[R], mn0[R], mn1[R];
+                float dw[R], dminw[R];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const uint4 s = wsc[i][r];
+                    const uint32_t a = (s.y >> p16) & 0xFFFFu, bb = (s.z >> p16) & 0xFFFFu, e = (s.w >> p16) & 0xFFFFu;
+                    const uint32_t scp = k < 2u ? (a & 0x3F3Fu) : ((e & 0x0F0Fu) | ((a >> 2) & 0x3030u));
+                    const uint32_t mnp = k < 2u ? (bb & 0x3F3Fu) : (((e >> 4) & 0x0F0Fu) | ((bb >> 2) & 0x3030u));
+                    sc0[r] = (int)(scp & 0xFFu);
+                    sc1[r] = (int)(scp >> 8);
+                    mn0[r] = (int)(mnp & 0xFFu);
+                    mn1[r] = (int)(mnp >> 8);
+                    dw[r] = h2f((uint16_t)(s.x & 0xFFFFu));
+                    dminw[r] = h2f((uint16_t)(s.x >> 16));
+                }
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
-                    const int8_t* ap = AQ + (size_t)m * K + 256u * b + 64u * k + 16u * h;
-                    const uint4 alo = ld_cached_u4(ap), ahi = ld_cached_u4(ap + 32);
+                    const int8_t* ap = AQ + (size_t)m * K + 64u * c;
+                    const uint4 a0 = ld_cached_u4(ap), a1 = ld_cached_u4(ap + 16), a2 = ld_cached_u4(ap + 32),
+                                a3 = ld_cached_u4(ap + 48);
                     const uint8_t* ab = AB + ((size_t)m * B + b) * kABBytes;
-                    const uint2 bs = __ldg(reinterpret_cast<const uint2*>(ab + 8u * k));
+                    const uint2 bs = __ldg(reinterpret_cast<const uint2*>(ab + 8u * k));   // bsums[4k .. 4k+3]
                     const float da = __ldg(reinterpret_cast<const float*>(ab + 32));
-                    const int bs_lo = (int)(int16_t)(h ? (bs.x >> 16) : (bs.x & 0xFFFFu));
-                    const int bs_hi = (int)(int16_t)(h ? (bs.y >> 16) : (bs.y & 0xFFFFu));
+                    const int bs_lo = (int)(int16_t)(bs.x & 0xFFFFu) + (int)(int16_t)(bs.x >> 16);
+                    const int bs_hi = (int)(int16_t)(bs.y & 0xFFFFu) + (int)(int16_t)(bs.y >> 16);
+                    const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                    const uint32_t ah[8] = {a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
 #pragma unroll
                     for (int r = 0; r < R; ++r) {
-                        const uint4 w = wq[i][r];
                         int dlo = 0, dhi = 0;
-                        dlo = dp4a_ss(w.x & 0x0F0F0F0Fu, alo.x, dlo);
-                        dlo = dp4a_ss(w.y & 0x0F0F0F0Fu, alo.y, dlo);
-                        dlo = dp4a_ss(w.z & 0x0F0F0F0Fu, alo.z, dlo);
-                        dlo = dp4a_ss(w.w & 0x0F0F0F0Fu, alo.w, dlo);
-                        dhi = dp4a_ss((w.x >> 4) & 0x0F0F0F0Fu, ahi.x, dhi);
-                        dhi = dp4a_ss((w.y >> 4) & 0x0F0F0F0Fu, ahi.y, dhi);
-                        dhi = dp4a_ss((w.z >> 4) & 0x0F0F0F0Fu, ahi.z, dhi);
-                        dhi = dp4a_ss((w.w >> 4) & 0x0F0F0F0Fu, ahi.w, dhi);
-                        uint32_t sc0, mn0, sc1, mn1;
-                        q4k_scale_min(wsc[i][r], 2u * k, sc0, mn0);
-                        q4k_scale_min(wsc[i][r], 2u * k + 1u, sc1, mn1);
-                        const int isum = (int)sc0 * dlo + (int)sc1 * dhi;
-                        const int mpart = (int)mn0 * bs_lo + (int)mn1 * bs_hi;
-                        if (DUMP) {  // the 8 lanes of a block are an aligned lane group
-                            int t0 = isum, t1 = mpart;
-                            const uint32_t gmask = 0xFFu << (lane & 24u);  // C % 8 == 0: the group is in or out whole
 #pragma unroll
-                            for (int o = 1; o < 8; o <<= 1) {
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t w = wq[i][r].v[j];
+                            dlo = dp4a_ss(w & 0x0F0F0F0Fu, al[j], dlo);
+                            dhi = dp4a_ss((w >> 4) & 0x0F0F0F0Fu, ah[j], dhi);
+                        }
+                        const int isum = sc0[r] * dlo + sc1[r] * dhi;
+                        const int mpart = mn0[r] * bs_lo + mn1[r] * bs_hi;
+                        if (DUMP) {
+                            int t0 = isum, t1 = mpart;
+                            const uint32_t gmask = 0xFu << (lane & 28u);  // C % 4 == 0: the group is in or out whole
+#pragma unroll
+                            for (int o = 1; o < 4; o <<= 1) {
                                 t0 += __shfl_xor_sync(gmask, t0, o);
                                 t1 += __shfl_xor_sync(gmask, t1, o);
                             }
-                            if (cc == 0 && row0 + r < N) {
+                            if (k == 0 && row0 + r < N) {
                                 int32_t* o = sums + (((size_t)m * N + row0 + r) * B + b) * 2u;
                                 o[0] = t0;
                                 o[1] = t1;
                             }
                         }
-                        const float d = h2f((uint16_t)(wsc[i][r].x & 0xFFFFu)), dmin = h2f((uint16_t)(wsc[i][r].x >> 16));
-                        acc[r][m] += (d * da) * (float)isum - (dmin * da) * (float)mpart;
+                        acc[r][m] += (dw[r] * da) * (float)isum - (dminw[r] * da) * (float)mpart;
                     }
                 }
             }
@@ -428,7 +435,7 @@ static AcResult launch_mmvqb(const LaunchArgs& a) {
         a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u || (DUMP && a.range[5] < (uint64_t)M * N * B * 8u))
         return AC_ERR_INVALID_BUFFER_SIZE;
     int32_t* sums = DUMP ? (int32_t*)a.ptr[5] : nullptr;
-    AMV_GEMV_SWITCH(gemv_q4_K_kernel, DUMP, (const uint4*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2],
+    AMV_GEMV_SWITCH(gemv_q4_K_kernel, DUMP, (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2],
                     (const uint8_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride)
     return check_launch();
 }
