@@ -326,6 +326,12 @@ __device__ __forceinline__ void dequant_half(const uint8_t* raw, const uint8_t* 
     }
 }
 
+// Output tensor maps: the local destination first, then the same range of the other ranks' output buffers (peer
+// memory over NVLink) when the kernel also performs the output exchange of a row-sharded mul_mat.
+struct OutMaps {
+    CUtensorMap m[8];
+};
+
 struct Params {
     float* dst;
     const uint32_t* act;      // I2_S: {bits of 1/scale, sum q} per token row
@@ -333,6 +339,7 @@ struct Params {
     uint32_t tok_tile;        // T: tokens per CTA, multiple of 32, <= 256
     uint32_t b_stages;        // pipeline stages (3..6): activations in shared memory, weights in 32 TMEM columns each
     uint32_t tma_store;       // 1: epilogue through shared memory + TMA store
+    uint32_t n_out;           // destinations (1 = local only; up to 8 with peers)
     float w_scale;
     uint32_t diag;
     uint32_t* status;
@@ -348,7 +355,7 @@ __device__ __forceinline__ void trace(const Params& p, uint32_t slot) {
 template <int TYPE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap raw_map,
-               const __grid_constant__ CUtensorMap scale_map, const __grid_constant__ CUtensorMap out_map,
+               const __grid_constant__ CUtensorMap scale_map, const __grid_constant__ OutMaps out_maps,
                const Params p) {
     using C = Cfg<TYPE>;
     constexpr bool INT8 = C::kInt8;
@@ -557,7 +564,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) {   // rows past M and columns past N are clipped by the tensor map
-                        tma_store_2d(&out_map, smem_u32(stage_out), (int)(n0 + eq * 32u), (int)(m0 + c * 32u));
+                        for (uint32_t o = 0; o < p.n_out; ++o)   // the same piece to every rank's output
+                            tma_store_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u), (int)(m0 + c * 32u));
                         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // buffer reusable
                     }
                     __syncwarp();
@@ -627,7 +635,8 @@ static uint32_t choose_tok_tile(uint32_t M, uint32_t row_tiles, int sm_count) {
 template <int TYPE>
 static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, const void* act, uint64_t act_range,
                        void* dstp, uint64_t dst_range, const void* actscale, uint32_t M, uint32_t N, uint32_t K,
-                       uint32_t dst_stride, float w_scale, uint32_t diag) {
+                       uint32_t dst_stride, float w_scale, uint32_t diag, uint32_t n_peers = 0,
+                       void* const* peer_dst = nullptr, const uint64_t* peer_range = nullptr) {
     using C = Cfg<TYPE>;
     constexpr uint32_t esz = C::kInt8 ? 1u : 2u;
     if (M == 0 || N == 0 || K == 0 || (K % C::kBlockK) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
@@ -665,7 +674,9 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     const uint32_t stage_area = stages * per_stage > kEpilogueBytes ? stages * per_stage : kEpilogueBytes;
     const uint32_t smem_bytes = fixed + stage_area;
 
-    CUtensorMap act_map, raw_map, scale_map, out_map;
+    CUtensorMap act_map, raw_map, scale_map;
+    OutMaps out_maps;
+    memset(&out_maps, 0, sizeof(out_maps));
     const uint64_t row_bytes = (uint64_t)(K / C::kBlockK) * C::kRawRow;
     if (!encode_2d(enc, &act_map, C::kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, esz, act,
                    K, M, (uint64_t)K * esz, C::kBlockK, p.tok_tile, CU_TENSOR_MAP_SWIZZLE_128B) ||
@@ -680,12 +691,22 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     } else {
         scale_map = raw_map;
     }
-    if (p.tma_store) {
-        if (!encode_2d(enc, &out_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dstp, N, M, (uint64_t)dst_stride * 4u, 32, 32,
-                       CU_TENSOR_MAP_SWIZZLE_NONE))
-            return AC_ERR_INVALID_ARGUMENT;
-    } else {
-        out_map = raw_map;
+    p.n_out = 1u + n_peers;
+    if (n_peers) {   // the exchange goes through TMA stores: every destination must qualify
+        if (n_peers > 7u || !p.tma_store) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+        for (uint32_t i = 0; i < n_peers; ++i)
+            if (((uintptr_t)peer_dst[i] & 15u) || peer_range[i] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
+                return AC_ERR_INVALID_BUFFER_SIZE;
+    }
+    for (uint32_t o = 0; o < 8u; ++o) {
+        void* d = o == 0 ? dstp : (o <= n_peers ? peer_dst[o - 1] : dstp);
+        if (p.tma_store) {
+            if (!encode_2d(enc, &out_maps.m[o], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, N, M, (uint64_t)dst_stride * 4u,
+                           32, 32, CU_TENSOR_MAP_SWIZZLE_NONE))
+                return AC_ERR_INVALID_ARGUMENT;
+        } else {
+            out_maps.m[o] = raw_map;
+        }
     }
     static bool attr_set = false;
     if (!attr_set) {
@@ -698,7 +719,7 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     }
     const dim3 grid((M + p.tok_tile - 1) / p.tok_tile, row_tiles);
     if (grid.y > 65535u) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    gemm_tc_kernel<TYPE><<<grid, kThreads, smem_bytes, a.stream>>>(act_map, raw_map, scale_map, out_map, p);
+    gemm_tc_kernel<TYPE><<<grid, kThreads, smem_bytes, a.stream>>>(act_map, raw_map, scale_map, out_maps, p);
     return check_launch();
 }
 
@@ -717,6 +738,21 @@ static AcResult launch_mmtc(const LaunchArgs& a) {
     return tc::launch<TYPE>(a, a.ptr[0], a.ptr[1], a.ptr[2], a.range[2], a.ptr[3], a.range[3], nullptr, M, N, K,
                             dst_stride, 1.0f, a.push[4]);
 }
+// ameva_mmtc_<type>_mp: the same with the output exchange of a row-sharded mul_mat fused into the epilogue: bindings
+// 0 Q, 1 S, 2 AH, 3 local dst, 4..10 the same range of up to seven peers' outputs (unused slots repeat binding 3);
+// push {M, N, K, dst_stride, diag, n_peers}. Every tile is sent with one TMA store per destination.
+template <int TYPE, uint32_t QB, uint32_t SB, uint32_t BLK>
+static AcResult launch_mmtc_mp(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3], n_peers = a.push[5];
+    if (K == 0 || (K % BLK) || n_peers > 7u) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t nblk = (uint64_t)N * (K / BLK);
+    if (a.range[0] < nblk * QB || a.range[1] < nblk * SB) return AC_ERR_INVALID_BUFFER_SIZE;
+    return tc::launch<TYPE>(a, a.ptr[0], a.ptr[1], a.ptr[2], a.range[2], a.ptr[3], a.range[3], nullptr, M, N, K,
+                            dst_stride, 1.0f, a.push[4], n_peers, &a.ptr[4], &a.range[4]);
+}
+AcResult launch_mmtc_q4_0_mp(const LaunchArgs& a) { return launch_mmtc_mp<tc::T_Q4_0, 16, 2, 32>(a); }
+AcResult launch_mmtc_q8_0_mp(const LaunchArgs& a) { return launch_mmtc_mp<tc::T_Q8_0, 32, 2, 32>(a); }
+AcResult launch_mmtc_q4_K_mp(const LaunchArgs& a) { return launch_mmtc_mp<tc::T_Q4_K, 128, 16, 256>(a); }
 AcResult launch_mmtc_q4_0(const LaunchArgs& a) { return launch_mmtc<tc::T_Q4_0, 16, 2, 32>(a); }
 AcResult launch_mmtc_q8_0(const LaunchArgs& a) { return launch_mmtc<tc::T_Q8_0, 32, 2, 32>(a); }
 AcResult launch_mmtc_q4_K(const LaunchArgs& a) { return launch_mmtc<tc::T_Q4_K, 128, 16, 256>(a); }

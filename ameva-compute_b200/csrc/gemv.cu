@@ -18,6 +18,13 @@ namespace amv {
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / 32;
 
+// Destinations of an output row: the local buffer first, then the same range of the other ranks' outputs (peer memory
+// over NVLink) when the kernel also performs the output exchange of a row-sharded mul_mat.
+struct DstList {
+    float* p[8];
+    uint32_t n;
+};
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Q4_0 x Q8_0.  Q: uint4 [N][U] (byte j: element j low nibble, element j+16 high nibble), S: fp16 [N][U].
 // block: isum = sum nib*q - 8*sum(q); y += float(isum) * d_w * d_a
@@ -179,8 +186,8 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
 template <int M, int R, bool DUMP>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
-                 const uint8_t* __restrict__ AB, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
-                 uint32_t K, uint32_t dst_stride) {
+                 const uint8_t* __restrict__ AB, const DstList dl, int32_t* __restrict__ sums, uint32_t N, uint32_t K,
+                 uint32_t dst_stride) {
     constexpr int UN = M <= 2 ? 2 : 1;
     const uint32_t B = K >> 8, C = K >> 6;  // blocks and 32-byte chunks per row
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
@@ -284,7 +291,8 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const float v = warp_sum(acc[r][m]);
-            if (lane == 0 && row0 + r < N) dst[(size_t)m * dst_stride + row0 + r] = v;
+            if (lane == 0 && row0 + r < N)
+                for (uint32_t o = 0; o < dl.n; ++o) dl.p[o][(size_t)m * dst_stride + row0 + r] = v;
         }
 }
 
@@ -424,23 +432,34 @@ AcResult launch_mmvq_q8_0_dump(const LaunchArgs& a) { return launch_mmvq32<kQ80Q
 
 // ameva_mmvqb_q4_K [_dump]:
 //   bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 dst (, 5 block sums int32 [M][N][K/256][2]);  push {M (1..8), N, K, dst_stride}
-template <bool DUMP>
+template <bool DUMP, bool PEERS>
 static AcResult launch_mmvqb(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    const uint32_t n_peers = PEERS ? a.push[4] : 0u;
     if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
-    if (N == 0 || K == 0 || (K & 255u) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
-    const uint64_t B = K >> 8;
+    if (N == 0 || K == 0 || (K & 255u) || dst_stride < N || n_peers > 7u) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t B = K >> 8, need = ((uint64_t)(M - 1) * dst_stride + N) * 4u;
     if (a.range[0] < (uint64_t)N * B * kQ4KQBytes || a.range[1] < (uint64_t)N * B * kQ4KSBytes ||
-        a.range[2] < (uint64_t)M * K || a.range[3] < (uint64_t)M * B * kABBytes ||
-        a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u || (DUMP && a.range[5] < (uint64_t)M * N * B * 8u))
+        a.range[2] < (uint64_t)M * K || a.range[3] < (uint64_t)M * B * kABBytes || a.range[4] < need ||
+        (DUMP && a.range[5] < (uint64_t)M * N * B * 8u))
         return AC_ERR_INVALID_BUFFER_SIZE;
+    DstList dl;
+    dl.n = 1u + n_peers;
+    dl.p[0] = (float*)a.ptr[4];
+    for (uint32_t i = 0; i < 7u; ++i) {
+        dl.p[1 + i] = i < n_peers ? (float*)a.ptr[5 + i] : nullptr;
+        if (i < n_peers && a.range[5 + i] < need) return AC_ERR_INVALID_BUFFER_SIZE;
+    }
     int32_t* sums = DUMP ? (int32_t*)a.ptr[5] : nullptr;
     AMV_GEMV_SWITCH(gemv_q4_K_kernel, DUMP, (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2],
-                    (const uint8_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride)
+                    (const uint8_t*)a.ptr[3], dl, sums, N, K, dst_stride)
     return check_launch();
 }
-AcResult launch_mmvqb_q4_K(const LaunchArgs& a) { return launch_mmvqb<false>(a); }
-AcResult launch_mmvqb_q4_K_dump(const LaunchArgs& a) { return launch_mmvqb<true>(a); }
+AcResult launch_mmvqb_q4_K(const LaunchArgs& a) { return launch_mmvqb<false, false>(a); }
+AcResult launch_mmvqb_q4_K_dump(const LaunchArgs& a) { return launch_mmvqb<true, false>(a); }
+// ameva_mmvqb_q4_K_mp: bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 local dst, 5..11 the same range of up to seven peers' outputs
+// (unused slots repeat binding 4); push {M, N, K, dst_stride, n_peers}: every output row is stored to every destination.
+AcResult launch_mmvqb_q4_K_mp(const LaunchArgs& a) { return launch_mmvqb<false, true>(a); }
 
 // bitnet_gemv_i2_s_<l32w1|l16w2|l8w4>[_acc]  (argument contract of src/shaders/bitnet_gemv_i2_s.comp:45-80):
 //   bindings 0 packed weights, 1 int8 activations, 2 out f32, 3 act[2] per row {bits of dequant, sum q}

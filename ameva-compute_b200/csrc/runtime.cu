@@ -53,6 +53,7 @@ struct AcBuffer {
     void* dptr;
     size_t size, alloc_size;
     bool owned;
+    bool ipc;   // opened from another process's allocation: closed, not freed, on destroy
     uint32_t retained;  // recorded in batches that have not completed
 };
 
@@ -433,6 +434,7 @@ AcResult ac_runtime_buffer_create(AcContext* ctx, const AcBufferDesc* desc, AcBu
     b->size = desc->size_bytes;
     b->alloc_size = alloc;
     b->owned = true;
+    b->ipc = false;
     b->retained = 0;
     ctx->live_buffers++;
     *out_buf = b;
@@ -453,6 +455,55 @@ AcResult ac_b200_buffer_import(AcContext* ctx, void* device_ptr, size_t size_byt
     b->dptr = device_ptr;
     b->size = b->alloc_size = size_bytes;
     b->owned = false;
+    b->ipc = false;
+    b->retained = 0;
+    ctx->live_buffers++;
+    *out_buf = b;
+    return AC_SUCCESS;
+}
+
+// Peer sharing between the ranks of one box (one process per GPU): the owner exports a 64-byte handle, the peers open
+// it and get a buffer whose device address is the owner's memory, reachable over NVLink.
+AcResult ac_b200_buffer_export_ipc(AcBuffer* buf, void* out_handle64) {
+    if (!buf_ok(buf)) return AC_ERR_INVALID_ARGUMENT;
+    if (!out_handle64) return AC_ERR_NULL_POINTER;
+    if (!buf->owned) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    DeviceGuard g(buf->ctx->device);
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, buf->dptr) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(buf->ctx, AC_ERR_DRIVER_INIT_FAILED, AMEVA_BACKEND_OP_BUFFER_MAP);
+    }
+    memcpy(out_handle64, &h, 64);
+    return AC_SUCCESS;
+}
+
+AcResult ac_b200_buffer_open_ipc(AcContext* ctx, const void* handle64, size_t size_bytes, AcBuffer** out_buf) {
+    if (!out_buf) return AC_ERR_NULL_POINTER;
+    *out_buf = nullptr;
+    if (!ctx_ok(ctx)) return AC_ERR_INVALID_CONTEXT;
+    if (!handle64) return AC_ERR_NULL_POINTER;
+    if (size_bytes == 0) return AC_ERR_INVALID_BUFFER_SIZE;
+    DeviceGuard g(ctx->device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess || !p) {
+        cudaGetLastError();
+        return fail(ctx, AC_ERR_DRIVER_INIT_FAILED, AMEVA_BACKEND_OP_BUFFER_MAP);
+    }
+    AcBuffer* b = new (std::nothrow) AcBuffer();
+    if (!b) {
+        cudaIpcCloseMemHandle(p);
+        return AC_ERR_OUT_OF_HOST_MEMORY;
+    }
+    b->magic = kMagicBuf;
+    b->ctx = ctx;
+    b->dptr = p;
+    b->size = b->alloc_size = size_bytes;
+    b->owned = false;
+    b->ipc = true;
     b->retained = 0;
     ctx->live_buffers++;
     *out_buf = b;
@@ -467,6 +518,9 @@ AcResult ac_runtime_buffer_destroy(AcBuffer* buf) {
     if (buf->owned) {
         cudaStreamSynchronize(ctx->stream);  // a dispatch still in flight may reference it
         cudaFree(buf->dptr);
+    } else if (buf->ipc) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaIpcCloseMemHandle(buf->dptr);
     }
     ctx->live_buffers--;
     buf->magic = kMagicDead;

@@ -164,8 +164,12 @@ class MulMat:
         return None
 
     def record(self, batch: rt.Batch, x: rt.Buffer, dst: rt.Buffer, M: int, *, x_offset: int = 0, dst_offset: int = 0,
-               dst_stride: Optional[int] = None, quantize: bool = True) -> None:
-        """x: fp32 [M][K] at byte x_offset; dst: fp32 rows dst_stride floats apart at byte dst_offset."""
+               dst_stride: Optional[int] = None, quantize: bool = True, peers=None) -> None:
+        """x: fp32 [M][K] at byte x_offset; dst: fp32 rows dst_stride floats apart at byte dst_offset.
+
+        peers: buffers of other ranks (opened with Context.open_ipc) that receive the same output range at the same
+        offset and stride: the kernel's epilogue stores every tile to the local dst and to each peer, which is the
+        output exchange of a row-sharded projection fused into the mul_mat (no separate all-gather)."""
         if M <= 0 or M > self.max_m:
             raise MulMatUnsupported(f"M={M} outside 1..{self.max_m}")
         ctx, K, N = self.ctx, self.K, self.N
@@ -192,9 +196,21 @@ class MulMat:
                 self.sums = ctx.buffer(int(np.prod(self._sum_shape(self.max_m))) * 4)
         # kernel choice by M (ameva_mmq_plan / enc_mul_mat): M <= 8 -> streaming GEMV; larger M -> tcgen05 GEMM; the exact
         # mode (and K that is not a whole number of 128-byte operand rows) walks larger M in chunks of 8 through the GEMV
+        peers = list(peers or [])
+        if len(peers) > 7:
+            raise MulMatUnsupported("at most 7 peers")
+        if peers and (t == GGML_TYPE_I2_S or (not use_tc and (t != GGML_TYPE_Q4_K or M > GEMV_MAX_M))):
+            raise MulMatUnsupported("the fused peer exchange is built for the tensor-core GEMM and the Q4_K GEMV")
         if use_tc:
             self.path = "mmtc"
             grid = ((M + 255) // 256, (N + 127) // 128, 1)
+            if peers:
+                self.path = "mmtc+peer-stores"
+                outs = [(dst, dst_offset)] + [(pb, dst_offset) for pb in peers]
+                outs += [(dst, dst_offset)] * (8 - len(outs))
+                batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}_mp"), [self.qbind, self.sbind, self.ah] + outs,
+                               [M, N, K, dst_stride, 0, len(peers)], grid)
+                return
             if t == GGML_TYPE_I2_S:
                 push = [M, N, K, dst_stride, int(np.float32(self.view.weight.scale).view(np.uint32))]
                 batch.dispatch(ctx.kernel("bitnet_gemm_i2_s"), [self.qbind, self.aq, (dst, dst_offset), self.ad], push,
@@ -204,6 +220,13 @@ class MulMat:
                                [self.qbind, self.sbind, self.ah, (dst, dst_offset)], [M, N, K, dst_stride], grid)
             return
         self.path = "mmvq" if M <= GEMV_MAX_M else "mmvq-chunks"
+        if peers:
+            self.path = "mmvq+peer-stores"
+            outs = [(dst, dst_offset)] + [(pb, dst_offset) for pb in peers]
+            outs += [(dst, dst_offset)] * (8 - len(outs))
+            batch.dispatch(ctx.kernel("ameva_mmvqb_q4_K_mp"), [self.qbind, self.sbind, self.aq, self.ad] + outs,
+                           [M, N, K, dst_stride, len(peers)], ((N + 15) // 16, 1, 1))
+            return
         for m0 in range(0, M, GEMV_MAX_M):
             mc = min(GEMV_MAX_M, M - m0)
             d_off = dst_offset + m0 * dst_stride * 4
@@ -285,3 +308,46 @@ def q8_K_blocks_from_scratch(q: np.ndarray, d: np.ndarray, bsums: np.ndarray) ->
     out[:, :, 4:260] = q.reshape(M, B, 256).view(np.uint8)
     out[:, :, 260:] = np.ascontiguousarray(bsums.reshape(M, B, 16)).view(np.uint8)
     return out.reshape(M, B * 292)
+
+
+class PeerExchange:
+    """The output side of a row-sharded mul_mat on the ranks of one box (one process per GPU).
+
+    Every rank owns a full [M][N] fp32 output and a small flag array, both exported to the other ranks
+    (``handles()`` -> exchange with any out-of-band channel -> ``connect()``). ``MulMat.record(..., peers=ex.peers)``
+    then stores each rank's rows into every rank's output, and ``record_barrier`` appends the cross-GPU barrier after
+    which the local output is complete. No collective library is involved in the data path."""
+
+    def __init__(self, ctx: rt.Context, rank: int, world: int, out_bytes: int) -> None:
+        if not 2 <= world <= 8 or not 0 <= rank < world:
+            raise MulMatUnsupported("PeerExchange needs 2..8 ranks")
+        self.ctx, self.rank, self.world = ctx, rank, world
+        self.out = ctx.buffer(out_bytes)
+        self.flags = ctx.buffer(256)
+        self.flags.fill(0)
+        self.epoch = 0
+        self.peer_out, self.peer_flags = {}, {}
+
+    def handles(self):
+        return (self.out.export_ipc(), self.flags.export_ipc(), self.out.size_bytes)
+
+    def connect(self, all_handles) -> None:
+        """all_handles[r] = handles() of rank r."""
+        for r, (oh, fh, nbytes) in enumerate(all_handles):
+            if r != self.rank:
+                self.peer_out[r] = self.ctx.open_ipc(oh, nbytes)
+                self.peer_flags[r] = self.ctx.open_ipc(fh, 256)
+
+    @property
+    def peers(self):
+        return [self.peer_out[r] for r in sorted(self.peer_out)]
+
+    def record_barrier(self, batch: rt.Batch) -> None:
+        self.epoch += 1
+        slots = [self.flags if r == self.rank or r >= self.world else self.peer_flags[r] for r in range(8)]
+        batch.dispatch(self.ctx.kernel("ameva_peer_barrier"), slots, [self.rank, self.world, self.epoch], (1, 1, 1))
+
+    def destroy(self) -> None:
+        for b in list(self.peer_out.values()) + list(self.peer_flags.values()) + [self.out, self.flags]:
+            b.destroy()
+        self.peer_out, self.peer_flags = {}, {}

@@ -131,7 +131,7 @@ EXPORTED_SYMBOLS = [
     "ac_runtime_get_error_state_ctx", "ac_runtime_consume_error_ctx", "ac_runtime_advance_generation_ctx",
     "ac_runtime_get_generation_ctx", "ac_runtime_reset_error_state_ctx", "ac_runtime_kernel_create_builtin",
     "ac_b200_kernel_count", "ac_b200_kernel_name", "ac_b200_context_get_stream", "ac_b200_buffer_import",
-    "ac_b200_buffer_write_async", "ac_b200_buffer_read_async", "ac_b200_context_synchronize",
+    "ac_b200_buffer_export_ipc", "ac_b200_buffer_open_ipc", "ac_b200_buffer_write_async", "ac_b200_buffer_read_async", "ac_b200_context_synchronize",
     "ac_b200_device_layout", "ac_b200_repack_to_device", "ac_b200_repack_from_device",
     "ac_b200_mul_mat_q4_0_static",
 ]
@@ -207,6 +207,8 @@ def load_library() -> C.CDLL:
         "ac_b200_kernel_name": (C.c_char_p, [u32]),
         "ac_b200_context_get_stream": (C.c_int, [vp, P(vp)]),
         "ac_b200_buffer_import": (C.c_int, [vp, vp, sz, P(vp)]),
+        "ac_b200_buffer_export_ipc": (C.c_int, [vp, vp]),
+        "ac_b200_buffer_open_ipc": (C.c_int, [vp, vp, sz, P(vp)]),
         "ac_b200_buffer_write_async": (C.c_int, [vp, sz, vp, sz]),
         "ac_b200_buffer_read_async": (C.c_int, [vp, sz, vp, sz]),
         "ac_b200_context_synchronize": (C.c_int, [vp]),
@@ -292,6 +294,12 @@ class Buffer:
 
     def read_async(self, host, nbytes: int, offset: int = 0) -> None:
         _check(load_library().ac_b200_buffer_read_async(self._h, offset, _host_ptr(host), nbytes), "read_async")
+
+    def export_ipc(self) -> bytes:
+        """64-byte handle another rank of the same box opens with Context.open_ipc."""
+        h = C.create_string_buffer(64)
+        _check(load_library().ac_b200_buffer_export_ipc(self._h, h), "buffer_export_ipc")
+        return h.raw
 
     def fill(self, value: int = 0, offset: int = 0, size: Optional[int] = None) -> None:
         n = self.size_bytes - offset if size is None else size
@@ -437,6 +445,12 @@ class Context:
     def import_buffer(self, device_ptr: int, size_bytes: int) -> Buffer:
         out = C.c_void_p()
         _check(load_library().ac_b200_buffer_import(self._h, device_ptr, size_bytes, C.byref(out)), "buffer_import")
+        return Buffer(self, out.value, size_bytes)
+
+    def open_ipc(self, handle: bytes, size_bytes: int) -> Buffer:
+        out = C.c_void_p()
+        hb = C.create_string_buffer(handle, 64)
+        _check(load_library().ac_b200_buffer_open_ipc(self._h, hb, size_bytes, C.byref(out)), "buffer_open_ipc")
         return Buffer(self, out.value, size_bytes)
 
     def kernel(self, name: str, binding_count: Optional[int] = None, push_constant_size: Optional[int] = None,

@@ -14,8 +14,10 @@ through the same public API with host buffers (pinned), the host->device copy of
 copy of the result inside the timed region.
 
 With N > 1 (launched by torch.distributed.run) the weight rows are sharded over the ranks (strong scaling: the total
-work is fixed), every rank runs the single-GPU kernels on its slice and the fp32 output is assembled with an NCCL
-all-gather inside the timed region.
+work is fixed). Every rank owns a full [M][N] output shared with the other ranks over CUDA IPC; the mul_mat's epilogue
+stores the rank's rows into every rank's output over NVLink and a flag barrier kernel closes the step, so the exchange
+is part of this library's kernels and of the timed region. Kernels without that epilogue (I2_S, Q4_0/Q8_0 GEMV) fall
+back to an NCCL all-gather of the fp32 output plus a permute, also inside the timed region.
 
 `--impl reference` times the CPU implementation of the same path (the oracle: a C restatement of the ggml CPU
 arithmetic, or for I2_S the reference's own CPU kernel) on the host cores, on a bounded sample of the workload.
@@ -56,6 +58,9 @@ WORKLOADS = {
     "cfg5-up-m2048": (Q4_K, 2048, 28672, 8192, 0.01, "Q4_K x Q8_K 28672x8192 M=2048"),
 }
 L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures summarised under
+# profiles/ (bytes)
+TRAFFIC = {"cfg2": 53424896, "cfg5-up-m1": 136504320}
 GEMV_MAX_M = 8
 
 
@@ -263,26 +268,49 @@ def main():
     pool_n = max(2, min(64, -(-2 * L2_BYTES // max(shard_bytes, 1)) + 1))
     weights = [qmm.QuantWeight.from_ggml(ctx, t, my_blocks, rows, K, scale) for _ in range(pool_n)]
     mms = [qmm.MulMat(ctx, w, M) for w in weights]
-    # scratch is per MulMat here only because each owns it; share one set to keep the activation side identical
     x_dev = ctx.buffer(data=x)
-    out_local_t = torch.empty((M, pad), dtype=torch.float32, device="cuda")
-    out_local = ctx.import_buffer(out_local_t.data_ptr(), out_local_t.numel() * 4)
-    gathered_t = torch.empty((world, M, pad), dtype=torch.float32, device="cuda") if world > 1 else None
-    out_full_t = torch.empty((M, N), dtype=torch.float32, device="cuda") if world > 1 else None
+
+    # Output exchange of the sharded run. "peer": every rank owns a full [M][N] output; the mul_mat's epilogue stores
+    # its rows into every rank's output over NVLink and a flag barrier closes the step (all inside this library's
+    # kernels). "allgather": [M][rows] shards + NCCL all-gather + permute, for the kernels without the fused epilogue.
+    tc_path = M > GEMV_MAX_M and mms[0].tc_ok
+    exchange = "none"
+    if world > 1:
+        exchange = "peer" if (t != I2_S and (tc_path or (t == Q4_K and M <= GEMV_MAX_M))) else "allgather"
+    ex = None
+    if exchange == "peer":
+        ex = qmm.PeerExchange(ctx, rank, world, M * N * 4)
+        handles = [None] * world
+        dist.all_gather_object(handles, ex.handles())
+        ex.connect(handles)
+        out_buf, out_off, out_stride, out_cols = ex.out, row0 * 4, N, N
+    else:
+        out_buf, out_off, out_stride, out_cols = ctx.buffer(M * pad * 4), 0, pad, pad
+    gathered_t = out_full_t = out_local_t = None
+    if exchange == "allgather":
+        out_local_t = torch.empty((M, pad), dtype=torch.float32, device="cuda")
+        out_buf.destroy()
+        out_buf = ctx.import_buffer(out_local_t.data_ptr(), out_local_t.numel() * 4)
+        gathered_t = torch.empty((world, M, pad), dtype=torch.float32, device="cuda")
+        out_full_t = torch.empty((M, N), dtype=torch.float32, device="cuda")
 
     launches_per_step = [0]
+    batch_keep = []
 
     def record_steps(batch, n, first):
         for i in range(n):
             mm = mms[(first + i) % pool_n]
             before = batch.stats().dispatches if i == 0 else None
-            mm.record(batch, x_dev, out_local, M, dst_stride=pad)
+            mm.record(batch, x_dev, out_buf, M, dst_offset=out_off, dst_stride=out_stride,
+                      peers=ex.peers if ex else None)
+            if ex:
+                ex.record_barrier(batch)
             if i == 0:
                 launches_per_step[0] = batch.stats().dispatches - before
 
     def gpu_steps(n, first, flags=0):
-        """n steps on the device; returns (gpu seconds by CUDA events on the runtime's stream, batch)."""
-        if world == 1:
+        """n steps on the device; returns (gpu seconds by CUDA events on the runtime's stream, last batch)."""
+        if exchange != "allgather":
             per_batch = n if flags else max(1, min(n, 60000 // 70))   # a batch holds at most 65536 dispatches
             gpu_s, done, batch = 0.0, 0, None
             pending = []
@@ -299,7 +327,7 @@ def main():
                 if bt is not batch:
                     bt.destroy()
             return gpu_s, batch
-        # sharded: every step is compute on the runtime's stream, then the all-gather and the permute, in stream order
+        # all-gather exchange: compute on the runtime's stream, then the NCCL all-gather and the permute, in stream order
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(ext_stream):
             start.record()
@@ -312,12 +340,10 @@ def main():
                 batch_keep.append(batch)
             end.record()
             end.synchronize()
-        for b in batch_keep:
-            b.destroy()
+        for b_ in batch_keep:
+            b_.destroy()
         batch_keep.clear()
         return start.elapsed_time(end) / 1e3, None
-
-    batch_keep = []
 
     def barrier():
         if dist is not None:
@@ -356,27 +382,32 @@ def main():
         if unit == "TFLOP/s":
             ach = 2.0 * M * N * K / (main_ns * 1e-9) / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
-                    "frac": ach / pk["tflops"], "traffic": None,
+                    "frac": ach / pk["tflops"], "traffic": TRAFFIC.get(name),
                     "peak_source": pk["source"] + " bf16 burst", "kernel_us": main_ns / 1e3, "quant_us": quant_ns / 1e3}
         else:
             ach = algorithmic_bytes(t, M, N, K) / (main_ns * 1e-9) / 1e9
             roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
-                    "traffic": None, "peak_source": pk["source"] + " copy", "kernel_us": main_ns / 1e3,
+                    "traffic": TRAFFIC.get(name), "peak_source": pk["source"] + " copy", "kernel_us": main_ns / 1e3,
                     "quant_us": quant_ns / 1e3}
 
     # end to end through the public API with host buffers: H2D of the activations, compute, D2H of the result, per step
     x_pin = torch.from_numpy(x).pin_memory()
-    y_pin = torch.empty((M, pad), dtype=torch.float32).pin_memory()
+    d2h_bytes = M * out_cols * 4
+    y_pin = torch.empty((M, out_cols), dtype=torch.float32).pin_memory()
     e2e_steps = args.steps
 
     def e2e_run(n, first):
-        for i in range(n):
-            x_dev.write_async(x_pin.data_ptr(), x.nbytes)
-            batch = ctx.batch(128, 0)
-            mms[(first + i) % pool_n].record(batch, x_dev, out_local, M, dst_stride=pad)
-            batch.flush()
-            batch_keep.append(batch)
-            out_local.read_async(y_pin.data_ptr(), M * pad * 4)
+        with torch.cuda.stream(ext_stream):
+            for i in range(n):
+                x_dev.write_async(x_pin.data_ptr(), x.nbytes)
+                batch = ctx.batch(128, 0)
+                record_steps(batch, 1, first + i)
+                batch.flush()
+                batch_keep.append(batch)
+                if exchange == "allgather":
+                    dist.all_gather_into_tensor(gathered_t.view(world * M, pad), out_local_t)
+                    shard.assemble(gathered_t, parts, M, N, out_full_t)
+                out_buf.read_async(y_pin.data_ptr(), d2h_bytes)
         ctx.synchronize()
         for bb in batch_keep:
             bb.destroy()
@@ -394,33 +425,46 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         e2e_s = float(tt.item())
 
-    # parity spot check of what was timed (rank 0, first token rows of its shard) so a wrong kernel cannot post a number
+    # parity spot check of what was timed (rank 0): first token rows x a sample of weight rows of the first and, when
+    # sharded with the peer exchange, also of the last rank's shard, so a wrong kernel or exchange cannot post a number
     check = None
     if rank == 0 and rows:
         from helpers import max_normalised_error, oracle_mul_mat
         ms, ns = min(M, 4), min(rows, 512)
-        want, _, _ = oracle_mul_mat(t, my_blocks[:ns], scale, x[:ms], ns, K, want_sums=False)
-        got = y_pin.numpy()[:ms, :ns]
-        check = max_normalised_error(got, want)
+        got_all = y_pin.numpy()
+        spans = [(row0, ns, 0 if exchange != "peer" else row0)]
+        if exchange == "peer":
+            lr0, lrows = parts[-1]
+            spans.append((lr0, min(lrows, 256), lr0))
+        check = 0.0
+        allb = blocks.reshape(N, per_row)
+        for g_row0, g_n, col0 in spans:
+            want, _, _ = oracle_mul_mat(t, np.ascontiguousarray(allb[g_row0:g_row0 + g_n]), scale, x[:ms], g_n, K,
+                                        want_sums=False)
+            check = max(check, max_normalised_error(got_all[:ms, col0:col0 + g_n], want))
 
     if rank == 0:
+        par = {"none": "single GPU",
+               "peer": f"weight rows sharded over {world} ranks; the GEMM/GEMV epilogue stores each rank's rows into every "
+                       "rank's [M][N] output over NVLink (peer memory) and a flag barrier kernel closes every step; no "
+                       "collective library in the data path",
+               "allgather": f"weight rows sharded over {world} ranks, NCCL all-gather of the fp32 output + permute inside "
+                            "the timed region"}[exchange]
         line = {
             "metric": metric_name(name), "value": unit_value(unit, t, M, N, K, gpu_s / args.steps), "unit": unit,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": gpu_s / args.steps * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": {"mmtc": "int8 (tcgen05 kind::i8, int32 accumulate)" if t == I2_S else
                       "f16 (tcgen05 kind::f16 on dequantized fp16 operands, fp32 accumulate in TMEM)"}.get(
-                          mms[0].path, "int8 (dp4a, int32 per block, fp32 scale-accumulate)"),
+                          mms[0].path.split("+")[0], "int8 (dp4a, int32 per block, fp32 scale-accumulate)"),
             "data": "synthetic",
             "config": {"workload": f"{name}: {desc}", "M": M, "N": N, "K": K,
                        "l2": f"rotating pool of {pool_n} weight copies ({pool_n * shard_bytes / 1e6:.0f} MB > L2) per rank",
-                       "parallelism": "single GPU" if world == 1 else f"weight rows sharded over {world} ranks, "
-                       "NCCL all-gather of the fp32 output + permute inside the timed region",
-                       "path": mms[0].path},
+                       "parallelism": par, "path": mms[0].path},
             "wall_ms_per_step": wall_s / args.steps * 1e3,
             "gpu_launches": launches_per_step[0] * args.steps,
             "e2e": {"value": unit_value(unit, t, M, N, K, e2e_s / e2e_steps), "unit": unit,
-                    "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(M * pad * 4),
+                    "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(d2h_bytes),
                     "ms_per_step": e2e_s / e2e_steps * 1e3},
             "clocks": clocks,
             "parity_max_normalised_error": check,
@@ -429,17 +473,24 @@ def main():
             line["roofline"] = roof
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = run_cpu_baseline(t, M, N, K, blocks, scale, x, unit)
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
 
+    if dist is not None:   # nobody unmaps a buffer a peer may still be writing; and never hang after the line is out
+        threading.Timer(60.0, lambda: os._exit(0)).start()
+        barrier()
     for mm in mms:
         mm.destroy()
     for w in weights:
         w.destroy()
-    for bfr in (x_dev, out_local):
-        bfr.destroy()
+    x_dev.destroy()
+    if ex:
+        ex.destroy()
+    else:
+        out_buf.destroy()
     ctx.destroy()
     if dist is not None:
         dist.destroy_process_group()
+        os._exit(0)
 
 
 if __name__ == "__main__":

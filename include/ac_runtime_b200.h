@@ -315,6 +315,12 @@ const char* ac_b200_kernel_name(uint32_t index);
 AcResult ac_b200_context_get_stream(const AcContext* ctx, void** out_stream);
 /* Wrap device memory owned by the caller (e.g. a framework allocator) as a buffer; destroy does not free it. */
 AcResult ac_b200_buffer_import(AcContext* ctx, void* device_ptr, size_t size_bytes, AcBuffer** out_buf);
+/* Sharing a buffer between the ranks of one box (one process per GPU): the owner exports a 64-byte handle
+ * (cudaIpcMemHandle_t), a peer opens it and gets a buffer backed by the owner's device memory, reached over NVLink.
+ * Used for the fused output exchange of the row-sharded mul_mat (every rank stores its rows into every rank's output).
+ * No counterpart in the reference, which is single-device (adapters/llama/ggml-ameva/ggml-ameva-device.cpp:367-370). */
+AcResult ac_b200_buffer_export_ipc(AcBuffer* buf, void* out_handle64);
+AcResult ac_b200_buffer_open_ipc(AcContext* ctx, const void* handle64, size_t size_bytes, AcBuffer** out_buf);
 /* Asynchronous host->device / device->host copies on the context's stream (pinned host memory for true overlap);
  * ordered with the context's dispatches, complete after ac_b200_context_synchronize or a later event wait. */
 AcResult ac_b200_buffer_write_async(AcBuffer* buf, size_t offset, const void* src, size_t size_bytes);

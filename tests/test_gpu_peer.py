@@ -1,0 +1,145 @@
+"""The fused peer-store epilogue of the row-sharded mul_mat and the cross-GPU flag barrier, on ONE GPU.
+
+A second buffer of the same device stands in for the peer rank's output: the `_mp` kernels must leave the same bytes in
+the local and in every "peer" output, equal to the single-destination kernel's. Two shards written into one [M][N]
+output must reproduce the unsharded product. The barrier kernel is exercised without a second waiting kernel: the
+"other rank's" flag word is written by the host before the launch (pass), or never (the bounded wait runs out after about
+a second and the host reads AC_ERR_LAUNCH_TIMEOUT; the context stays usable)."""
+import numpy as np
+import pytest
+
+from conftest import load_pkg
+from helpers import Q4_0, Q4_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+
+pytestmark = pytest.mark.gpu
+pkg = load_pkg()
+rt, qmm, shard = pkg.runtime, pkg.qmm, pkg.shard
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = rt.init()
+    yield c
+    c.destroy()
+
+
+def sharded_into_full(ctx, t, M, N, K, world, n_peer_bufs):
+    """Every 'rank' computes its row slice and stores it into the local [M][N] output and n_peer_bufs stand-ins."""
+    blocks, scale = make_weights(t, N, K, 3)
+    x = make_acts(M, K, 4)
+    per_row = np.asarray(blocks).reshape(N, -1)
+    xb = ctx.buffer(data=x)
+    outs = [ctx.buffer(M * N * 4) for _ in range(1 + n_peer_bufs)]
+    for o in outs:
+        o.fill(0xFF)
+    path = None
+    for row0, rows in shard.partition_rows(N, world):
+        if rows == 0:
+            continue
+        w = qmm.QuantWeight.from_ggml(ctx, t, np.ascontiguousarray(per_row[row0:row0 + rows]), rows, K, scale)
+        mm = qmm.MulMat(ctx, w, M)
+        mm.run(xb, outs[0], M, dst_offset=row0 * 4, dst_stride=N, peers=outs[1:])
+        path = mm.path
+        mm.destroy()
+        w.destroy()
+    ys = [o.read(np.float32).reshape(M, N) for o in outs]
+    for b in outs + [xb]:
+        b.destroy()
+    want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+    return ys, want, path
+
+
+@pytest.mark.parametrize("t", [Q8_0, Q4_0, Q4_K])
+@pytest.mark.parametrize("M,N,K,world,npeer", [(64, 512, 512, 2, 1), (100, 640, 1024, 4, 3), (33, 384, 256, 3, 7)])
+def test_gemm_peer_stores(ctx, t, M, N, K, world, npeer):
+    ys, want, path = sharded_into_full(ctx, t, M, N, K, world, npeer)
+    assert path == "mmtc+peer-stores"
+    assert np.isfinite(ys[0]).all()
+    assert max_normalised_error(ys[0], want) <= 1e-3
+    for y in ys[1:]:
+        assert np.array_equal(y.view(np.uint32), ys[0].view(np.uint32))
+
+
+@pytest.mark.parametrize("M,N,K,world,npeer", [(1, 512, 512, 2, 1), (8, 640, 1024, 4, 3), (3, 272, 256, 2, 7)])
+def test_gemv_q4k_peer_stores(ctx, M, N, K, world, npeer):
+    ys, want, path = sharded_into_full(ctx, Q4_K, M, N, K, world, npeer)
+    assert path == "mmvq+peer-stores"
+    assert max_normalised_error(ys[0], want) <= 1e-3
+    for y in ys[1:]:
+        assert np.array_equal(y.view(np.uint32), ys[0].view(np.uint32))
+
+
+def test_peer_stores_match_single_destination(ctx):
+    t, M, N, K = Q8_0, 96, 256, 512
+    blocks, scale = make_weights(t, N, K, 5)
+    x = make_acts(M, K, 6)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, a, b, c = ctx.buffer(data=x), ctx.buffer(M * N * 4), ctx.buffer(M * N * 4), ctx.buffer(M * N * 4)
+    mm.run(xb, a, M)
+    mm.run(xb, b, M, peers=[c])
+    ya, yb, yc = (v.read(np.uint32) for v in (a, b, c))
+    assert np.array_equal(ya, yb) and np.array_equal(ya, yc)
+    for v in (xb, a, b, c):
+        v.destroy()
+    mm.destroy()
+    w.destroy()
+
+
+def _barrier(ctx, flags_local, flags_other, rank, world, epoch):
+    batch = ctx.batch(8)
+    slots = [flags_local if r == rank or r >= world else flags_other for r in range(8)]
+    batch.dispatch(ctx.kernel("ameva_peer_barrier"), slots, [rank, world, epoch], (1, 1, 1))
+    ev = batch.submit()
+    try:
+        ev.wait(10_000_000_000)
+    finally:
+        ev.destroy()
+        batch.destroy()
+
+
+def test_peer_barrier_publishes_and_passes(ctx):
+    mine, other = ctx.buffer(256), ctx.buffer(256)
+    mine.fill(0)
+    other.fill(0)
+    w = np.zeros(64, np.uint32)
+    w[1] = 7                      # "rank 1" already published epoch 7 into rank 0's array
+    mine.write(w)
+    _barrier(ctx, mine, other, 0, 2, 7)
+    assert other.read(np.uint32)[0] == 7      # rank 0 published into the other rank's array, word [0]
+    assert mine.read(np.uint32)[0] == 7       # ... and into its own
+    # an older epoch is already satisfied by a newer published value
+    _barrier(ctx, mine, other, 0, 2, 6)
+    mine.destroy()
+    other.destroy()
+
+
+def test_peer_barrier_argument_checks(ctx):
+    mine, small = ctx.buffer(256), ctx.buffer(64)
+    batch = ctx.batch(8)
+    k = ctx.kernel("ameva_peer_barrier")
+    for push in ([0, 1, 1], [2, 2, 1], [0, 9, 1]):
+        with pytest.raises(rt.AmevaComputeError):
+            batch.dispatch(k, [mine] * 8, push, (1, 1, 1))
+            batch.submit().wait()
+    batch.destroy()
+    mine.destroy()
+    small.destroy()
+
+
+def test_peer_barrier_wait_runs_out(ctx):
+    """Nothing sets the other rank's word: the kernel gives up after its bounded wait and reports it."""
+    mine, other = ctx.buffer(256), ctx.buffer(256)
+    mine.fill(0)
+    other.fill(0)
+    with pytest.raises(rt.AmevaComputeError) as e:
+        _barrier(ctx, mine, other, 0, 2, 1)
+    assert e.value.code == -405   # AC_ERR_LAUNCH_TIMEOUT
+    # the context is still usable
+    mine.fill(0)
+    w = np.zeros(64, np.uint32)
+    w[1] = 2
+    mine.write(w)
+    _barrier(ctx, mine, other, 0, 2, 2)
+    mine.destroy()
+    other.destroy()
