@@ -24,6 +24,8 @@ struct LaunchArgs {
     AcDim3 grid;
     uint32_t* status;  // 4 device words owned by the context: [0] error code, [1] detail, [2..3] reserved
     int sm_count;
+    uint32_t* workspace;      // device words owned by the context, zero between launches (cross-CTA sequence flags)
+    uint64_t workspace_bytes;
 };
 
 typedef AcResult (*LaunchFn)(const LaunchArgs&);

@@ -38,17 +38,17 @@ namespace tc {
 constexpr int kRows = 128;          // weight rows per CTA (UMMA M)
 constexpr int kTokMax = 256;        // tokens per CTA at most (UMMA N, multiple of 16)
 constexpr int kRowBytes = 128;      // bytes of one operand row per K block (the swizzle span)
-constexpr int kDequantThreads = 256;   // threads that convert one K block (one dequant group)
+constexpr int kDequantThreads = 128;   // threads that convert one K block (one dequant group): one weight row each
 constexpr int kGroupWarps = kDequantThreads / 32;      // one elected arrival per warp on the stage barriers
-constexpr int kDequantGroups = 2;       // two groups take alternate K blocks, so each has two MMA periods per block
+constexpr int kDequantGroups = 4;       // the groups take K blocks in turn, so each has four MMA periods per block
 constexpr int kDequantWarps = kGroupWarps * kDequantGroups;
 constexpr int kThreads = (kDequantWarps + 3) * 32;   // dequant/epilogue warps + activation TMA, MMA, weight TMA warps
 constexpr int kWarpAct = kDequantWarps, kWarpMma = kDequantWarps + 1, kWarpRaw = kDequantWarps + 2;
-constexpr int kMaxStages = 6;        // activation stages in shared memory
+constexpr int kMaxStages = 8;        // activation stages in shared memory (= weight stages in tensor memory)
 constexpr int kMaxAStages = 8;       // weight stages in tensor memory (32 columns each, after the accumulator)
 constexpr uint32_t kTmemCols = 512;  // 256 accumulator columns + 8 x 32 operand columns
 constexpr int kScaleSlots = 3;
-constexpr uint32_t kEpilogueBytes = kDequantWarps * 4096u;   // one 32 x 32 fp32 staging buffer per epilogue warp
+constexpr uint32_t kEpilogueBytes = kDequantWarps * 2048u;   // one 32 x 16 fp32 staging buffer per epilogue warp
 constexpr uint32_t kScaleBytes = kRows * 16;        // 2 KB: 16 bytes of scales per row per 256 weights
 constexpr uint32_t kSmemLimit = 227 * 1024;
 constexpr long long kWaitCycles = 2000000000ll;     // about one second
@@ -135,16 +135,61 @@ __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarr
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// ---- CTA pairs (PAIR): two CTAs of a cluster on neighbouring SMs run one 256-row MMA together -----------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster (shared::cluster window).
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+// What is handed over with this arrival is tensor memory already written (tcgen05.wait::st), not shared or global
+// memory, so the arrival carries no cluster-scope release fence (which would stall the arriving thread every K block).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// With PAIR the warp of the same index in both CTAs executes these, and both get the same TMEM address.
+template <bool PAIR>
 __device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (PAIR) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
 }
+template <bool PAIR>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    if (PAIR)
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+    else
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
 }
+// One arrival on `bar` when the MMAs issued so far have finished; with PAIR on the barrier at that offset in both CTAs.
+template <bool PAIR>
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    if (PAIR) {
+        const uint16_t both = 3;
+        asm volatile(
+            "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                bar),
+            "h"(both)
+            : "memory");
+    } else {
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                     : "memory");
+    }
 }
 
 // Shared-memory matrix descriptor of a K-major operand tile whose rows are one 128-byte swizzle span: 8-row groups
@@ -153,36 +198,35 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
 }
 
-// Instruction descriptor: D format (bits 4-5), A/B formats (7-9, 10-12), both K-major, N >> 3 at bit 17, M >> 4 at 24.
-__host__ __device__ constexpr uint32_t make_idesc(uint32_t d_fmt, uint32_t ab_fmt, uint32_t n) {
-    return (d_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((n >> 3) << 17) | ((uint32_t)(kRows >> 4) << 24);
+// Instruction descriptor: D format (bits 4-5), A/B formats (7-9, 10-12), both K-major, N >> 3 at bit 17, M >> 4 at 24
+// (M = 128 rows for one CTA, 256 for a CTA pair).
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t d_fmt, uint32_t ab_fmt, uint32_t n, uint32_t m) {
+    return (d_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
-template <bool INT8>
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
-    if (INT8) {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
-            : "memory");
-    } else {
-        asm volatile(
-            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
-            : "memory");
-    }
-}
-
-// The same with the A operand read from tensor memory (the dequantized weight stage) instead of shared memory.
-template <bool INT8>
+// MMA with the A operand read from tensor memory (the dequantized weight stage) and B from shared memory. With
+// PAIR one thread of the even CTA issues it for both: each CTA's tensor core multiplies its own 128 weight rows (its own
+// TMEM) with all the tokens, reading the first half of the token rows from the even CTA's shared memory and the second
+// half from the odd CTA's, at the same shared-memory offset.
+template <bool INT8, bool PAIR>
 __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
                                         uint32_t acc) {
-    if (INT8) {
+    if (INT8 && PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc)
+            : "memory");
+    } else if (INT8) {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc)
+            : "memory");
+    } else if (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
             "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc)
             : "memory");
     } else {
@@ -192,6 +236,25 @@ __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64
             "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(acc)
             : "memory");
     }
+}
+
+// 32 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // 16 consecutive 32-bit columns of this thread's TMEM lane.
@@ -211,6 +274,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const CUtensorMap
             dst_smem),
         "l"(map), "r"(bar), "r"(c0), "r"(c1)
         : "memory");
+}
+// Load issued by either CTA of a pair whose completion bytes are counted on a barrier of the even CTA (`bar` is an
+// address in the shared::cluster window); the data lands in the issuing CTA's own shared memory.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtensorMap* map, uint32_t bar, int c0,
+                                                 int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+        "[%2];" ::"r"(dst_smem),
+        "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+// The same box added to global memory (fp32 add performed at the memory side).
+__device__ __forceinline__ void tma_add_2d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(src_smem), "r"(c0), "r"(c1)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src_smem, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
@@ -336,10 +416,13 @@ struct Params {
     float* dst;
     const uint32_t* act;      // I2_S: {bits of 1/scale, sum q} per token row
     uint32_t M, N, K, dst_stride;
-    uint32_t tok_tile;        // T: tokens per CTA, multiple of 32, <= 256
-    uint32_t b_stages;        // pipeline stages (3..6): activations in shared memory, weights in 32 TMEM columns each
+    uint32_t tok_tile;        // T: tokens per CTA (per CTA pair), multiple of 32, <= 256
+    uint32_t b_stages;        // pipeline stages (4..8): activations in shared memory, weights in 32 TMEM columns each
     uint32_t tma_store;       // 1: epilogue through shared memory + TMA store
     uint32_t n_out;           // destinations (1 = local only; up to 8 with peers)
+    uint32_t tiles, row_units;   // output tiles; units of 128 (256 for a CTA pair) weight rows across N
+    uint32_t iters, units;    // K blocks per unit in the linear (tile, K block) space; number of units launched
+    uint32_t* flags;          // per (tile, CTA of the pair, epilogue warp) sequence words, zero between launches
     float w_scale;
     uint32_t diag;
     uint32_t* status;
@@ -351,8 +434,54 @@ __device__ __forceinline__ void trace(const Params& p, uint32_t slot) {
         reinterpret_cast<long long*>(p.dst)[slot] = clock64();
 }
 
+// With the same bit every CTA also records the global nanosecond timer at its start and end (slots 2048 + 2 cta, + 1).
+__device__ __forceinline__ void trace_cta(const Params& p, uint32_t which) {
+    if (p.diag & 16u) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        reinterpret_cast<unsigned long long*>(p.dst)[2048u + 2u * (blockIdx.y * gridDim.x + blockIdx.x) + which] = t;
+    }
+}
+
+// ---- work decomposition ---------------------------------------------------------------------------------------------
+// An output tile is 128 weight rows (256 for a CTA pair) x T tokens; tile t covers token tile t / row_units and row unit
+// t % row_units. The K blocks of all tiles form one linear iteration space of tiles * KB steps that is cut into equal
+// ranges of `iters` steps (a multiple of 4), one per unit (a CTA or a CTA pair): a unit walks its range tile by tile
+// ("segments"). With iters == KB every unit computes exactly one tile; otherwise the units are all resident at once
+// and a tile cut by a range boundary is produced by several units, whose partial sums are combined in the output
+// itself in a fixed order (descending K): the segment that ends the tile stores, every other one waits for a per-tile
+// sequence flag and then adds with a TMA reduction, so the result does not depend on timing.
+struct Seg {
+    uint32_t tile, kb0, kb1;
+};
+__device__ __forceinline__ bool next_seg(uint32_t& it, uint32_t it_end, uint32_t KB, Seg& s) {
+    if (it >= it_end) return false;
+    s.tile = it / KB;
+    s.kb0 = it - s.tile * KB;
+    s.kb1 = min(KB, s.kb0 + (it_end - it));
+    it += s.kb1 - s.kb0;
+    return true;
+}
+
+// Bounded wait for a sequence flag written by another CTA of the same launch.
+__device__ __forceinline__ bool flag_wait(const uint32_t* flag, uint32_t want, Ctl* ctl, uint32_t* status, uint32_t tag) {
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v == want) return true;
+        if (ctl->abort) return false;
+        if (clock64() - t0 > kWaitCycles) {
+            ctl->abort = 1u;
+            if (atomicCAS(status, DEV_STATUS_OK, DEV_STATUS_WAIT_TIMEOUT) == DEV_STATUS_OK) status[1] = tag;
+            return false;
+        }
+        __nanosleep(200);
+    }
+}
+
 // ---- the kernel -----------------------------------------------------------------------------------------------------
-template <int TYPE>
+template <int TYPE, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap raw_map,
                const __grid_constant__ CUtensorMap scale_map, const __grid_constant__ OutMaps out_maps,
@@ -361,100 +490,143 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     constexpr bool INT8 = C::kInt8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-    const uint32_t S = p.b_stages, T = p.tok_tile, b_bytes = T * kRowBytes;
-    uint8_t* sB = base;                                               // S x T*128 B (>= 64 KB: epilogue staging)
-    uint8_t* sRaw = sB + max(S * b_bytes, kEpilogueBytes);            // kRawSlots x 16 KB
+    // PAIR: blockIdx.x and blockIdx.x ^ 1 form a cluster (one unit); they share the token tile (each stages half of its
+    // rows) and own the two 128-row halves of the tile. The even CTA (rank 0) issues the MMAs and owns the full[] and
+    // acc_empty barriers.
+    const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+    const uint32_t unit = PAIR ? blockIdx.x >> 1 : blockIdx.x;
+    const uint32_t S = p.b_stages, T = p.tok_tile, Th = PAIR ? T / 2u : T, b_bytes = Th * kRowBytes;
+    uint8_t* sB = base;                                               // S x Th*128 B activation stages
+    uint8_t* sOut = sB + S * b_bytes;                                 // 16 x 2 KB epilogue staging
+    uint8_t* sRaw = sOut + kEpilogueBytes;                            // kRawSlots x 16 KB
     uint8_t* sSc = sRaw + C::kRawSlots * C::kRawBytes;                // kScaleSlots x 2 KB
     uint64_t* bars = reinterpret_cast<uint64_t*>(sSc + kScaleSlots * kScaleBytes);
-    // full[s]: the eight arrivals of the dequant group that wrote TMEM stage s + the activation TMA's arrival and bytes
-    // for shared-memory stage s; empty[s]: one tcgen05.commit when the MMAs that read stage s have finished.
-    const uint32_t full = smem_u32(bars), empty = full + 8u * 6u, raw_full = empty + 8u * 6u,
+    // full[s]: the four arrivals of the dequant group that wrote TMEM stage s (of each CTA of a pair) + the activation
+    // TMA's arrival and bytes for shared-memory stage s; empty[s]: one tcgen05.commit when the MMAs that read stage s
+    // have finished (delivered to both CTAs of a pair); accum: the MMAs of a segment have finished; acc_empty: the
+    // epilogue warps have read the accumulator out.
+    const uint32_t full = smem_u32(bars), empty = full + 8u * 8u, raw_full = empty + 8u * 8u,
                    raw_empty = raw_full + 8u * 4u, sc_full = raw_empty + 8u * 4u, sc_empty = sc_full + 8u * 3u,
-                   accum = sc_empty + 8u * 3u;
-    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 27);
+                   accum = sc_empty + 8u * 3u, acc_empty = accum + 8u;
+    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 32);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t m0 = blockIdx.x * T, n0 = blockIdx.y * kRows;
     const uint32_t KB = p.K / C::kBlockK;
-    // Every CTA walks K from its own starting block (a multiple of 4 blocks = one scale group) and wraps around: at any
-    // moment the CTAs of a wave read different activation lines, instead of all of them hitting the same L2 lines.
-    const uint32_t rot = (KB & 3u) ? 0u : 4u * ((blockIdx.y * 5u + blockIdx.x * 3u) % (KB >> 2));
+    {   // the carve-up above must fit the dynamic shared memory of this launch (the same in every CTA: uniform exit)
+        uint32_t dyn;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        const uint32_t need = (uint32_t)(reinterpret_cast<uint8_t*>(ctl + 1) - smem_raw);
+        if (need > dyn || S < (uint32_t)kDequantGroups || S > (uint32_t)kMaxStages || T > (uint32_t)kTokMax || (T & 31u)) {
+            if (threadIdx.x == 0 && atomicCAS(p.status, DEV_STATUS_OK, DEV_STATUS_BAD_INDEX) == DEV_STATUS_OK)
+                p.status[1] = 0xA00u | (need > dyn ? 1u : 2u);
+            return;
+        }
+    }
+    const uint32_t it_begin = unit * p.iters, it_end = min(it_begin + p.iters, p.tiles * KB);
     uint32_t* status = p.status;
-    if (threadIdx.x == 0) trace(p, 0);
+    if (threadIdx.x == 0) {
+        trace(p, 0);
+        trace_cta(p, 0);
+    }
 
     if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < 6u; ++s) {
-            mbar_init(full + 8u * s, kGroupWarps + 1u);
+        for (uint32_t s = 0; s < 8u; ++s) {
+            mbar_init(full + 8u * s, kGroupWarps * (PAIR ? 2u : 1u) + 1u);
             mbar_init(empty + 8u * s, 1u);
         }
         for (uint32_t s = 0; s < 4u; ++s) {
             mbar_init(raw_full + 8u * s, 1u);
-            mbar_init(raw_empty + 8u * s, kDequantWarps);
+            mbar_init(raw_empty + 8u * s, kGroupWarps * (C::kGroup < 4u ? C::kGroup : 4u));
         }
         for (uint32_t s = 0; s < kScaleSlots; ++s) {
             mbar_init(sc_full + 8u * s, 1u);
             mbar_init(sc_empty + 8u * s, kDequantWarps);
         }
         mbar_init(accum, 1u);
+        mbar_init(acc_empty, kDequantWarps * (PAIR ? 2u : 1u));
         ctl->abort = 0u;
         fence_barrier_init();
     }
-    if (warp == kWarpMma) tmem_alloc(smem_u32(&ctl->tmem_base), kTmemCols);
+    if (warp == kWarpMma) tmem_alloc<PAIR>(smem_u32(&ctl->tmem_base), kTmemCols);
     tc_fence_before();
-    __syncthreads();
+    if (PAIR)
+        cluster_sync();   // the peer's barriers are initialised before anything arrives on them
+    else
+        __syncthreads();
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;       // accumulator: columns 0 .. T-1
     const uint32_t tmem_a = tmem + kTokMax;     // weight operand stages: 32 columns each
     if (threadIdx.x == 0) trace(p, 1);
 
+    // Every tile walks K from its own starting block (a multiple of 4 blocks = one scale group) and wraps around, so
+    // that the units running at the same time read different activation lines instead of the same L2 lines.
+    auto rot_of = [&](uint32_t tile) -> uint32_t { return (KB & 3u) ? 0u : 4u * ((tile * 5u) % (KB >> 2)); };
+
     if (warp == kWarpAct) {
         // ---- activation TMA: token rows m0 .. m0+T-1 (rows past M read as zero), K block kb ----
         if (lane == 0) {
             Ring st(S);
-            uint32_t kb = 0;
-            for (; kb < KB; ++kb, st.advance()) {
-                if (!mbar_wait(empty + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x100u | st.idx)) break;
-                if (p.diag & 2u) {   // diagnostic: no activation traffic
-                    mbar_arrive(full + 8u * st.idx);
-                    continue;
+            Seg sg;
+            uint32_t it = it_begin, issued = 0;
+            bool ok = true;
+            while (ok && next_seg(it, it_end, KB, sg)) {
+                const uint32_t m0 = (sg.tile / p.row_units) * T, rot = rot_of(sg.tile);
+                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, st.advance()) {
+                    ok = mbar_wait(empty + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x100u | st.idx);
+                    if (!ok) break;
+                    if (p.diag & 2u) {   // diagnostic: no activation traffic
+                        if (rank == 0u) mbar_arrive(full + 8u * st.idx);
+                        continue;
+                    }
+                    trace(p, 900u + kb);
+                    const uint32_t kbr = kb + rot < KB ? kb + rot : kb + rot - KB;
+                    if (PAIR) {   // the even CTA expects both halves' bytes on its barrier; each CTA loads its own half
+                        if (rank == 0u) mbar_arrive_expect_tx(full + 8u * st.idx, 2u * b_bytes);
+                        tma_load_2d_pair(smem_u32(sB + st.idx * b_bytes), &act_map, map_to_cta(full + 8u * st.idx, 0u),
+                                         (int)(kbr * C::kBlockK), (int)(m0 + rank * Th));
+                    } else {
+                        mbar_arrive_expect_tx(full + 8u * st.idx, b_bytes);
+                        tma_load_2d(smem_u32(sB + st.idx * b_bytes), &act_map, full + 8u * st.idx,
+                                    (int)(kbr * C::kBlockK), (int)m0);
+                    }
+                    ++issued;
                 }
-                trace(p, 900u + kb);
-                mbar_arrive_expect_tx(full + 8u * st.idx, b_bytes);
-                const uint32_t kbr = kb + rot < KB ? kb + rot : kb + rot - KB;
-                tma_load_2d(smem_u32(sB + st.idx * b_bytes), &act_map, full + 8u * st.idx, (int)(kbr * C::kBlockK),
-                            (int)m0);
             }
-            if (ctl->abort && !(p.diag & 2u)) {   // let the copies already requested land before the CTA leaves
-                for (uint32_t i = kb > S ? kb - S : 0; i < kb; ++i)
+            if (ctl->abort && !(p.diag & 2u) && rank == 0u) {   // let the copies already requested land before leaving
+                for (uint32_t i = issued > S ? issued - S : 0; i < issued; ++i)
                     mbar_wait(full + 8u * (i % S), (i / S) & 1u, ctl, status, 0x180u);
             }
         }
     } else if (warp == kWarpRaw) {
         // ---- packed-weight TMA: rows n0 .. n0+127 (rows past N read as zero), one 128-byte-per-row box per kGroup K
-        //      blocks; the scales of a 256-weight group once per 4 K blocks ----
+        //      blocks; the scales of a 256-weight group once per 4 K blocks. Segments start on multiples of 4 blocks. ----
         if (lane == 0) {
             Ring rr(C::kRawSlots), sr(kScaleSlots);
-            uint32_t groups = 0, sgroups = 0;
+            Seg sg;
+            uint32_t it = it_begin, groups = 0;
             bool ok = true;
-            for (uint32_t kb = 0; kb < KB && ok; ++kb) {
-                if (C::kScales && (kb & 3u) == 0u) {
-                    ok = mbar_wait(sc_empty + 8u * sr.idx, sr.phase ^ 1u, ctl, status, 0x600u | sr.idx);
-                    if (!ok) break;
-                    mbar_arrive_expect_tx(sc_full + 8u * sr.idx, kScaleBytes);
-                    tma_load_2d(smem_u32(sSc + sr.idx * kScaleBytes), &scale_map, sc_full + 8u * sr.idx,
-                                (int)(((sgroups + (rot >> 2)) % ((KB + 3u) >> 2)) * 16u), (int)n0);
-                    ++sgroups;
-                    sr.advance();
-                }
-                if ((kb & (C::kGroup - 1u)) == 0u) {
-                    ok = mbar_wait(raw_empty + 8u * rr.idx, rr.phase ^ 1u, ctl, status, 0x700u | rr.idx);
-                    if (!ok) break;
-                    mbar_arrive_expect_tx(raw_full + 8u * rr.idx, C::kRawBytes);
-                    tma_load_2d(smem_u32(sRaw + rr.idx * C::kRawBytes), &raw_map, raw_full + 8u * rr.idx,
-                                (int)(((groups + rot / C::kGroup) % ((KB + C::kGroup - 1u) / C::kGroup)) * 128u), (int)n0);
-                    trace(p, 530u + groups);
-                    ++groups;
-                    rr.advance();
+            while (ok && next_seg(it, it_end, KB, sg)) {
+                const uint32_t n0 = ((sg.tile % p.row_units) * (PAIR ? 2u : 1u) + rank) * kRows, rot = rot_of(sg.tile);
+                for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb) {
+                    const uint32_t kbr = kb + rot < KB ? kb + rot : kb + rot - KB;
+                    if (C::kScales && (kb & 3u) == 0u) {
+                        ok = mbar_wait(sc_empty + 8u * sr.idx, sr.phase ^ 1u, ctl, status, 0x600u | sr.idx);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(sc_full + 8u * sr.idx, kScaleBytes);
+                        tma_load_2d(smem_u32(sSc + sr.idx * kScaleBytes), &scale_map, sc_full + 8u * sr.idx,
+                                    (int)((kbr >> 2) * 16u), (int)n0);
+                        sr.advance();
+                    }
+                    if ((kb & (C::kGroup - 1u)) == 0u) {
+                        ok = mbar_wait(raw_empty + 8u * rr.idx, rr.phase ^ 1u, ctl, status, 0x700u | rr.idx);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(raw_full + 8u * rr.idx, C::kRawBytes);
+                        tma_load_2d(smem_u32(sRaw + rr.idx * C::kRawBytes), &raw_map, raw_full + 8u * rr.idx,
+                                    (int)((kbr / C::kGroup) * 128u), (int)n0);
+                        trace(p, 530u + groups);
+                        ++groups;
+                        rr.advance();
+                    }
                 }
             }
             if (ctl->abort) {
@@ -463,122 +635,190 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             }
         }
     } else if (warp == kWarpMma) {
-        // ---- MMA issuer: A from tensor memory (stage sa), B from shared memory (stage sb) ----
-        if (lane == 0) {
-            const uint32_t idesc = INT8 ? make_idesc(2u, 1u, T) : make_idesc(1u, 0u, T);
+        // ---- MMA issuer: A from tensor memory (stage st), B from shared memory (stage st) ----
+        if (lane == 0 && rank == 0u) {
+            const uint32_t rows = PAIR ? 2u * kRows : kRows;
+            const uint32_t idesc = INT8 ? make_idesc(2u, 1u, T, rows) : make_idesc(1u, 0u, T, rows);
             Ring st(S);
-            for (uint32_t kb = 0; kb < KB; ++kb, st.advance()) {
-                if (!mbar_wait<false>(full + 8u * st.idx, st.phase, ctl, status, 0x200u | st.idx)) {
-                    ctl->abort = 1u;   // visible to whoever passes the accumulator barrier below
-                    break;
-                }
-                trace(p, 2u + kb);
-                tc_fence_after();
-                const uint64_t db = make_smem_desc(smem_u32(sB + st.idx * b_bytes));
-                const uint32_t ta = tmem_a + st.idx * 32u;
-                if (!(p.diag & 4u)) {
+            Seg sg;
+            uint32_t it = it_begin, nseg = 0;
+            bool ok = true;
+            while (ok && next_seg(it, it_end, KB, sg)) {
+                // the epilogue of the previous segment has read the accumulator out
+                if (nseg) ok = mbar_wait<false>(acc_empty, (nseg - 1u) & 1u, ctl, status, 0x280u);
+                for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb, st.advance()) {
+                    ok = mbar_wait<false>(full + 8u * st.idx, st.phase, ctl, status, 0x200u | st.idx);
+                    if (!ok) break;
+                    trace(p, 2u + kb);
+                    tc_fence_after();
+                    const uint64_t db = make_smem_desc(smem_u32(sB + st.idx * b_bytes));
+                    const uint32_t ta = tmem_a + st.idx * 32u;
+                    if (!(p.diag & 4u)) {
 #pragma unroll
-                    for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: 8 TMEM columns / +2 desc units
-                        umma_ts<INT8>(tmem, ta + 8u * k, db + 2u * k, idesc, (kb | k) != 0u);
+                        for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: 8 TMEM columns / +2 desc units
+                            umma_ts<INT8, PAIR>(tmem, ta + 8u * k, db + 2u * k, idesc, (uint32_t)(kb != sg.kb0 || k != 0u));
+                    }
+                    umma_commit<PAIR>(empty + 8u * st.idx);
+                    trace(p, 130u + kb);
                 }
-                umma_commit(empty + 8u * st.idx);
-                trace(p, 130u + kb);
+                if (!ok) ctl->abort = 1u;   // visible to whoever passes the accumulator barrier below
+                umma_commit<PAIR>(accum);
+                ++nseg;
             }
-            umma_commit(accum);
         }
     } else {
-        // ---- weight dequantization: raw stage -> tensor-memory operand stage. Group dg converts the K blocks with
-        //      kb % 2 == dg; in a group, warp w owns TMEM lanes (rows) 32 (w % 4) .. +31 and half w / 4 of the K block ----
-        const uint32_t dg = threadIdx.x / kDequantThreads, wg = warp & (kGroupWarps - 1u);
-        const uint32_t q4 = wg & 3u, h = wg >> 2, r = q4 * 32u + lane;
+        // The stage ring must be at least as deep as the number of groups: consecutive uses of a stage (K blocks kb, kb +
+        // S, kb + 2S) fall to different groups, and a parity wait only tells phases apart that are one step away. A group
+        // reaches K block kb + 2S after its own wait for the MMAs of kb + S - 4, which (in-order MMAs) covers kb when
+        // S >= 4; with a shallower ring it could pass its wait two phases early and overwrite a stage still in use.
+        // ---- weight dequantization: raw stage -> tensor-memory operand stage. Group g (four warps) converts the K
+        //      blocks with kb % 4 == g, so every group has four MMA periods per block; in a group, warp w owns TMEM lanes
+        //      (rows) 32 (w % 4) .. +31, one row and one whole K block per thread ----
+        const uint32_t g = warp >> 2, q4 = warp & 3u, r = q4 * 32u + lane;
+        const uint32_t eq = q4, cq = g;   // epilogue: TMEM lane quarter, column-chunk phase
+        const uint32_t full_remote = (PAIR && rank != 0u) ? map_to_cta(full, 0u) : 0u;
+        float* stage_out = reinterpret_cast<float*>(sOut) + warp * 512u;
         bool ok = true;
         Ring sa(S), rr(C::kRawSlots), sr(kScaleSlots);
-        for (uint32_t kb = 0; kb < KB && ok; ++kb) {
-            const uint32_t raw_last = min((kb | (C::kGroup - 1u)), KB - 1u);   // last K block of this raw / scale group
-            const uint32_t sc_last = min((kb | 3u), KB - 1u);
-            if ((kb & 1u) == dg) {
-                const bool tr = (threadIdx.x & (kDequantThreads - 1u)) == 0u;
-                if (tr) trace(p, 1024u + kb);
-                if (C::kScales) ok = mbar_wait(sc_full + 8u * sr.idx, sr.phase, ctl, status, 0x800u | sr.idx);
-                if (tr) trace(p, 650u + kb);
-                ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x900u | rr.idx);
-                if (tr) trace(p, 780u + kb);
-                ok = ok && mbar_wait(empty + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx);
-                if (!ok) break;
-                if (tr) trace(p, 260u + kb);
-                tc_fence_after();
-                uint32_t o[16];
-                if (!(p.diag & 1u)) {
-                    dequant_half<TYPE>(sRaw + rr.idx * C::kRawBytes, sSc + sr.idx * kScaleBytes, r, h, kb, o);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) o[i] = 0u;
-                }
-                if (tr) trace(p, 1280u + kb);
-                tmem_st16(tmem_a + ((q4 * 32u) << 16) + sa.idx * 32u + h * 16u, o);
-                if (tr) trace(p, 1408u + kb);
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(full + 8u * sa.idx);
-                    if (kb + 2u > raw_last) mbar_arrive(raw_empty + 8u * rr.idx);      // my last block of the raw stage
-                    if (C::kScales && kb + 2u > sc_last) mbar_arrive(sc_empty + 8u * sr.idx);
-                    if (tr) trace(p, 390u + kb);
-                }
-            }
-            sa.advance();
-            if (kb == raw_last) rr.advance();
-            if (C::kScales && kb == sc_last) sr.advance();
-        }
-        // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows) and the 32-column chunks w / 4, w / 4 + 4,
-        //      ..., and sends each 32 x 32 piece out through its own 4 KB staging buffer and a TMA store ----
-        ok = ok && mbar_wait(accum, 0u, ctl, status, 0x500u) && !ctl->abort;
-        if (threadIdx.x == 0) trace(p, 520);
-        __syncwarp();
-        const bool all_ok = __all_sync(0xffffffffu, ok);
-        if (all_ok) {
-            tc_fence_after();
-            const uint32_t eq = warp & 3u, cq = warp >> 2;   // TMEM lane quarter, column-chunk phase
-            const uint32_t out_row = n0 + eq * 32u + lane;
-            float* stage_out = reinterpret_cast<float*>(base) + warp * 1024u;   // the activation stages are idle now
-            for (uint32_t c = cq; c * 32u < T; c += kDequantWarps / 4) {
-                uint32_t v[32];
-                tmem_ld32(tmem + ((eq * 32u) << 16) + c * 32u, v);
-#pragma unroll
-                for (uint32_t j = 0; j < 32; ++j) {
-                    const uint32_t m = m0 + c * 32u + j;
-                    float y;
-                    if (INT8) {
-                        const float total_scale =
-                            __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
-                        y = __fmul_rn((float)(int)v[j], total_scale);
+        Seg sg;
+        uint32_t it = it_begin, nseg = 0;
+        while (ok && next_seg(it, it_end, KB, sg)) {
+            for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb) {
+                const uint32_t raw_last = min((kb | (C::kGroup - 1u)), sg.kb1 - 1u);   // last K block of this raw group
+                const uint32_t sc_last = min((kb | 3u), sg.kb1 - 1u);
+                if ((kb & 3u) == g) {
+                    const bool tr = threadIdx.x == 0u;
+                    if (tr) trace(p, 1024u + kb);
+                    if (C::kScales) ok = mbar_wait(sc_full + 8u * sr.idx, sr.phase, ctl, status, 0x800u | sr.idx);
+                    ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x900u | rr.idx);
+                    ok = ok && mbar_wait(empty + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx);
+                    if (!ok) break;
+                    if (tr) trace(p, 260u + kb);
+                    tc_fence_after();
+                    uint32_t o[32];
+                    if (!(p.diag & 1u)) {
+                        const uint8_t* raw = sRaw + rr.idx * C::kRawBytes;
+                        const uint8_t* sc = sSc + sr.idx * kScaleBytes;
+                        dequant_half<TYPE>(raw, sc, r, 0u, kb, o);
+                        dequant_half<TYPE>(raw, sc, r, 1u, kb, o + 16);
                     } else {
-                        y = __uint_as_float(v[j]);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = 0u;
                     }
-                    if (p.tma_store)
-                        stage_out[j * 32u + lane] = y;
-                    else if (m < p.M && out_row < p.N && !(p.diag & 8u))
-                        p.dst[(size_t)m * p.dst_stride + out_row] = y;
-                }
-                if (p.tma_store && !(p.diag & 8u)) {
-                    fence_async_smem();
+                    if (tr) trace(p, 1280u + kb);
+                    tmem_st32(tmem_a + ((q4 * 32u) << 16) + sa.idx * 32u, o);
+                    tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) {   // rows past M and columns past N are clipped by the tensor map
-                        for (uint32_t o = 0; o < p.n_out; ++o)   // the same piece to every rank's output
-                            tma_store_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u), (int)(m0 + c * 32u));
-                        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // buffer reusable
+                    if (lane == 0) {
+                        if (PAIR && rank != 0u)
+                            mbar_arrive_cluster(full_remote + 8u * sa.idx);
+                        else
+                            mbar_arrive(full + 8u * sa.idx);
+                        mbar_arrive(raw_empty + 8u * rr.idx);   // a group meets every raw / scale stage at most once
+                        if (C::kScales) mbar_arrive(sc_empty + 8u * sr.idx);
+                        if (tr) trace(p, 390u + kb);
                     }
-                    __syncwarp();
                 }
+                sa.advance();
+                if (kb == raw_last) rr.advance();
+                if (C::kScales && kb == sc_last) sr.advance();
             }
-            if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-            if (threadIdx.x == 0) trace(p, 521);
+            // ---- epilogue of the segment: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows) and the 16-column
+            //      chunks w / 4, w / 4 + 4, ..., and sends each 32 x 16 piece out through its own 2 KB staging buffer and
+            //      one TMA store (or TMA add, for a partial sum that is not the first of its tile) per destination ----
+            ok = ok && mbar_wait(accum, nseg & 1u, ctl, status, 0x500u) && !ctl->abort;
+            if (threadIdx.x == 0) trace(p, 520);
+            __syncwarp();
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                tc_fence_after();
+                const uint32_t m0 = (sg.tile / p.row_units) * T;
+                const uint32_t n0 = ((sg.tile % p.row_units) * (PAIR ? 2u : 1u) + rank) * kRows;
+                const uint32_t out_row = n0 + eq * 32u + lane;
+                // Partial sums: `later` = the segments of this tile with higher K, which come first in the fixed order.
+                const bool split = sg.kb1 - sg.kb0 != KB;
+                uint32_t later = 0;
+                uint32_t* flag = nullptr;
+                if (split) {
+                    const uint32_t g_end = sg.tile * KB + sg.kb1, t_end = (sg.tile + 1u) * KB;
+                    later = sg.kb1 == KB ? 0u : (t_end - 1u) / p.iters - g_end / p.iters + 1u;
+                    flag = p.flags + ((sg.tile * 2u + rank) * (uint32_t)kDequantWarps + warp);
+                    if (later) {
+                        if (lane == 0) ok = flag_wait(flag, later, ctl, status, 0x540u);
+                        ok = __all_sync(0xffffffffu, ok);
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                    }
+                }
+                for (uint32_t c = cq; c * 16u < T && ok; c += kDequantGroups) {
+                    uint32_t v[16];
+                    tmem_ld16(tmem + ((eq * 32u) << 16) + c * 16u, v);
+#pragma unroll
+                    for (uint32_t j = 0; j < 16; ++j) {
+                        const uint32_t m = m0 + c * 16u + j;
+                        float y;
+                        if (INT8) {
+                            const float total_scale =
+                                __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
+                            y = __fmul_rn((float)(int)v[j], total_scale);
+                        } else {
+                            y = __uint_as_float(v[j]);
+                        }
+                        if (p.tma_store)
+                            stage_out[j * 32u + lane] = y;
+                        else if (m < p.M && out_row < p.N && !(p.diag & 8u))
+                            p.dst[(size_t)m * p.dst_stride + out_row] = y;
+                    }
+                    if (p.tma_store && !(p.diag & 8u)) {
+                        fence_async_smem();
+                        __syncwarp();
+                        // rows past M and columns past N are clipped by the tensor map; a piece entirely outside is skipped
+                        if (lane == 0 && n0 + eq * 32u < p.N && m0 + c * 16u < p.M) {
+                            for (uint32_t o = 0; o < p.n_out; ++o) {   // the same piece to every rank's output
+                                if (later)
+                                    tma_add_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u),
+                                               (int)(m0 + c * 16u));
+                                else
+                                    tma_store_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u),
+                                                 (int)(m0 + c * 16u));
+                            }
+                            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // buffer reusable
+                        }
+                        __syncwarp();
+                    }
+                }
+                if (split && ok && lane == 0) {
+                    if (sg.kb0 != 0u) {   // hand the tile on to the next lower K range once these writes are done
+                        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                        __threadfence();
+                        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(later + 1u) : "memory");
+                    } else {
+                        *flag = 0u;       // the tile is complete: leave the flag as the next launch expects it
+                    }
+                }
+                if (threadIdx.x == 0) trace(p, 521);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {   // the accumulator may be overwritten by the next segment
+                if (PAIR && rank != 0u)
+                    mbar_arrive_cluster(map_to_cta(acc_empty, 0u));
+                else
+                    mbar_arrive(acc_empty);
+            }
+            ++nseg;
         }
+        if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     tc_fence_before();
-    __syncthreads();
-    if (warp == kWarpMma) tmem_dealloc(tmem, kTmemCols);
-    if (threadIdx.x == 0) trace(p, 522);
+    if (PAIR)
+        cluster_sync();   // neither CTA leaves (or frees TMEM) while the other may still reach its memory or barriers
+    else
+        __syncthreads();
+    if (warp == kWarpMma) tmem_dealloc<PAIR>(tmem, kTmemCols);
+    if (threadIdx.x == 0) {
+        trace(p, 522);
+        trace_cta(p, 1);
+    }
 }
 
 // ---- host side ------------------------------------------------------------------------------------------------------
@@ -612,16 +852,17 @@ static bool encode_2d(EncodeTiledFn enc, CUtensorMap* map, CUtensorMapDataType d
                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Token tile: split M into j tiles of T = ceil(M / j) rounded up to 32 and take the j with the fewest token-columns
-// per SM over all waves (a fixed per-tile cost stands for prologue + epilogue), preferring the larger tile on ties.
-static uint32_t choose_tok_tile(uint32_t M, uint32_t row_tiles, int sm_count) {
+// Token tile for one-tile-per-unit launches: split M into j tiles of T = ceil(M / j) rounded up to 32 and take the j
+// with the fewest token-columns per SM over all waves (a fixed per-tile cost stands for prologue + epilogue),
+// preferring the larger tile on ties.
+static uint32_t choose_tok_tile(uint32_t M, uint32_t row_units, int units_resident, uint32_t tok_max) {
     uint32_t best_t = 0;
     uint64_t best_cost = ~0ull;
-    for (uint32_t j = (M + kTokMax - 1) / kTokMax; j <= 16; ++j) {
+    for (uint32_t j = (M + tok_max - 1) / tok_max; j <= 16; ++j) {
         const uint32_t t = (((M + j - 1) / j) + 31u) & ~31u;
-        if (t > (uint32_t)kTokMax || t < 32u) continue;
-        const uint32_t tiles = row_tiles * ((M + t - 1) / t);
-        const uint64_t waves = (tiles + sm_count - 1) / sm_count;
+        if (t > tok_max || t < 32u) continue;
+        const uint32_t tiles = row_units * ((M + t - 1) / t);
+        const uint64_t waves = (tiles + units_resident - 1) / units_resident;
         const uint64_t cost = waves * (t + 48u);
         if (cost < best_cost) {
             best_cost = cost;
@@ -629,7 +870,45 @@ static uint32_t choose_tok_tile(uint32_t M, uint32_t row_tiles, int sm_count) {
         }
         if (t == 32u) break;
     }
-    return best_t ? best_t : (uint32_t)kTokMax;
+    return best_t ? best_t : tok_max;
+}
+
+// Units (CTAs, or CTA pairs) of the kernel that the device holds at once.
+template <int TYPE, bool PAIR>
+static int resident_units(uint32_t smem_bytes, int sm_count) {
+    static int cached = 0;
+    static uint32_t cached_smem = 0;
+    if (cached && cached_smem == smem_bytes) return cached;
+    int n = 0;
+    if (PAIR) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(2 * sm_count);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem_bytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_kernel<TYPE, true>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+    } else {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, gemm_tc_kernel<TYPE, false>, kThreads, smem_bytes) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            per_sm = 0;
+        }
+        n = per_sm * sm_count;
+    }
+    cached = n;
+    cached_smem = smem_bytes;
+    return n;
 }
 
 template <int TYPE>
@@ -647,6 +926,17 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
         return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return AC_ERR_DRIVER_SYMBOL_MISSING;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<TYPE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemLimit) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_tc_kernel<TYPE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemLimit) != cudaSuccess) {
+            cudaGetLastError();
+            return AC_ERR_INVALID_WORK_GROUP_SIZE;
+        }
+        attr_set = true;
+    }
 
     Params p;
     memset(&p, 0, sizeof(p));
@@ -657,29 +947,83 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     p.K = K;
     p.dst_stride = dst_stride;
     p.w_scale = w_scale;
-    p.diag = diag & 31u;
+    p.diag = diag & 31u;   // bits 5 (single CTAs) and 6 (one tile per unit) are host-side choices
     p.status = a.status;
-    const uint32_t row_tiles = (N + kRows - 1) / kRows;
-    const uint32_t forced = diag >> 8;   // diagnostic: bits 8.. force the token tile
-    p.tok_tile = forced ? forced : choose_tok_tile(M, row_tiles, a.sm_count > 0 ? a.sm_count : 148);
-    if (p.tok_tile == 0 || p.tok_tile > (uint32_t)kTokMax || (p.tok_tile & 31u)) return AC_ERR_KERNEL_ARG_INVALID;
+    p.flags = a.workspace;
     p.tma_store = ((dst_stride & 3u) == 0u && ((uintptr_t)dstp & 15u) == 0u) ? 1u : 0u;
+    p.n_out = 1u + n_peers;
+    if (n_peers) {   // the exchange goes through TMA stores: every destination must qualify
+        if (n_peers > 7u || !p.tma_store) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+        for (uint32_t i = 0; i < n_peers; ++i)
+            if (((uintptr_t)peer_dst[i] & 15u) || peer_range[i] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
+                return AC_ERR_INVALID_BUFFER_SIZE;
+    }
 
-    const uint32_t fixed = 1024u + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + 512u;
-    const uint32_t per_stage = p.tok_tile * kRowBytes;
-    uint32_t stages = (kSmemLimit - fixed) / per_stage;
-    if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
-    if (stages < 3u) return AC_ERR_INVALID_WORK_GROUP_SIZE;
-    p.b_stages = stages;
-    const uint32_t stage_area = stages * per_stage > kEpilogueBytes ? stages * per_stage : kEpilogueBytes;
-    const uint32_t smem_bytes = fixed + stage_area;
+    // CTA pairs whenever there are two row tiles to pair up (an odd last tile is paired with an empty one whose loads
+    // read zeros and whose stores are skipped); diag bit 5 forces single CTAs.
+    const bool pair = (N > (uint32_t)kRows) && !(diag & 32u);
+    const uint32_t unit_rows = pair ? 2u * kRows : kRows;
+    p.row_units = (N + unit_rows - 1) / unit_rows;
+    const uint32_t KB = K / C::kBlockK;
+    const int sm_count = a.sm_count > 0 ? a.sm_count : 148;
+    const uint32_t fixed = 1024u + kEpilogueBytes + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + 512u;
+
+    // K ranges cut across tiles ("stream" launch, all units resident at once) need the TMA path for the partial sums, a
+    // K that is whole scale groups, exact integer results left alone (I2_S scales per token after the sum), flag space,
+    // and the local output only. Otherwise one tile per unit, as many waves as it takes.
+    bool stream = p.tma_store && !C::kInt8 && (KB & 3u) == 0u && n_peers == 0u && !(diag & 64u) && a.workspace;
+    const uint32_t forced = diag >> 8;   // diagnostic: bits 8.. force the token tile
+    // A single CTA stages all the token rows of its tile itself: 128 of them keep the stage ring deep enough.
+    const uint32_t tok_max = pair ? (uint32_t)kTokMax : (uint32_t)kTokMax / 2u;
+    int resident = 0;
+    for (int attempt = 0; attempt < 2; ++attempt) {
+        if (forced) {
+            p.tok_tile = forced;
+        } else if (stream) {
+            const uint32_t j = (M + tok_max - 1) / tok_max;
+            p.tok_tile = (((M + j - 1) / j) + 31u) & ~31u;
+        } else {
+            p.tok_tile = choose_tok_tile(M, p.row_units, pair ? sm_count / 2 : sm_count, tok_max);
+        }
+        if (p.tok_tile == 0 || p.tok_tile > (uint32_t)kTokMax || (p.tok_tile & 31u)) return AC_ERR_KERNEL_ARG_INVALID;
+        const uint32_t per_stage = (pair ? p.tok_tile / 2u : p.tok_tile) * kRowBytes;
+        uint32_t stages = (kSmemLimit - fixed) / per_stage;
+        if (stages > (uint32_t)kMaxStages) stages = kMaxStages;
+        if (stages < (uint32_t)kDequantGroups) return AC_ERR_INVALID_WORK_GROUP_SIZE;   // ring depth >= groups (see the kernel)
+        p.b_stages = stages;
+        p.tiles = p.row_units * ((M + p.tok_tile - 1) / p.tok_tile);
+        p.iters = KB;
+        p.units = p.tiles;
+        if (!stream) break;
+        const uint32_t smem_try = fixed + stages * per_stage;
+        resident = pair ? resident_units<TYPE, true>(smem_try, sm_count) : resident_units<TYPE, false>(smem_try, sm_count);
+        const uint64_t total = (uint64_t)p.tiles * KB;
+        if (resident < 1 || (uint64_t)p.tiles * 2u * kDequantWarps * 4u > a.workspace_bytes || total > 0x7fffffffull) {
+            stream = false;   // once more, with the token tile of the one-tile-per-unit launch
+            continue;
+        }
+        if (p.tiles >= (uint32_t)resident) {
+            p.iters = (uint32_t)(((total + resident - 1) / resident + 3u) & ~3ull);
+        } else {
+            const uint32_t fit = (uint32_t)resident / p.tiles, split = fit < 4u ? fit : 4u;
+            p.iters = split >= 2u ? (((KB + split - 1) / split + 3u) & ~3u) : KB;
+        }
+        p.units = (uint32_t)((total + p.iters - 1) / p.iters);
+        if (p.iters != KB && p.units > (uint32_t)resident) {   // cannot happen by construction; never launch it
+            stream = false;
+            continue;
+        }
+        break;
+    }
+    const uint32_t tok_rows = pair ? p.tok_tile / 2u : p.tok_tile;   // token rows staged by one CTA
+    const uint32_t smem_bytes = fixed + p.b_stages * tok_rows * kRowBytes;
 
     CUtensorMap act_map, raw_map, scale_map;
     OutMaps out_maps;
     memset(&out_maps, 0, sizeof(out_maps));
     const uint64_t row_bytes = (uint64_t)(K / C::kBlockK) * C::kRawRow;
     if (!encode_2d(enc, &act_map, C::kInt8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, esz, act,
-                   K, M, (uint64_t)K * esz, C::kBlockK, p.tok_tile, CU_TENSOR_MAP_SWIZZLE_128B) ||
+                   K, M, (uint64_t)K * esz, C::kBlockK, tok_rows, CU_TENSOR_MAP_SWIZZLE_128B) ||
         !encode_2d(enc, &raw_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Qp, row_bytes, N, row_bytes, 128, kRows,
                    CU_TENSOR_MAP_SWIZZLE_128B))
         return AC_ERR_INVALID_ARGUMENT;
@@ -691,35 +1035,39 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     } else {
         scale_map = raw_map;
     }
-    p.n_out = 1u + n_peers;
-    if (n_peers) {   // the exchange goes through TMA stores: every destination must qualify
-        if (n_peers > 7u || !p.tma_store) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
-        for (uint32_t i = 0; i < n_peers; ++i)
-            if (((uintptr_t)peer_dst[i] & 15u) || peer_range[i] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
-                return AC_ERR_INVALID_BUFFER_SIZE;
-    }
     for (uint32_t o = 0; o < 8u; ++o) {
         void* d = o == 0 ? dstp : (o <= n_peers ? peer_dst[o - 1] : dstp);
         if (p.tma_store) {
             if (!encode_2d(enc, &out_maps.m[o], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, d, N, M, (uint64_t)dst_stride * 4u,
-                           32, 32, CU_TENSOR_MAP_SWIZZLE_NONE))
+                           32, 16, CU_TENSOR_MAP_SWIZZLE_NONE))
                 return AC_ERR_INVALID_ARGUMENT;
         } else {
             out_maps.m[o] = raw_map;
         }
     }
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit) !=
-            cudaSuccess) {
-            cudaGetLastError();
-            return AC_ERR_INVALID_WORK_GROUP_SIZE;
-        }
-        attr_set = true;
+    const uint64_t ctas = (uint64_t)p.units * (pair ? 2u : 1u);
+    if (ctas > 0x7fffffffull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = a.stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = pair ? 2 : 1;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = pair ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, true>, act_map, raw_map, scale_map,
+                                                    out_maps, p)
+                               : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, false>, act_map, raw_map, scale_map,
+                                                    out_maps, p);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return AC_ERR_INVALID_WORK_GROUP_SIZE;
     }
-    const dim3 grid((M + p.tok_tile - 1) / p.tok_tile, row_tiles);
-    if (grid.y > 65535u) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    gemm_tc_kernel<TYPE><<<grid, kThreads, smem_bytes, a.stream>>>(act_map, raw_map, scale_map, out_maps, p);
     return check_launch();
 }
 

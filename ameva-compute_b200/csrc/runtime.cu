@@ -43,6 +43,7 @@ struct AcContext {
     cudaDeviceProp prop;
     uint32_t* status_host;  // mapped pinned memory, 4 words
     uint32_t* status_dev;
+    uint32_t* workspace;    // kWorkspaceBytes of zeroed device memory for the kernels' cross-CTA flags
     uint32_t live_buffers, live_kernels, live_events, live_batches;
     uint64_t id;
 };
@@ -129,6 +130,8 @@ AcResult fail(AcContext* ctx, AcResult r, AmevaBackendOpKind op, size_t off = 0,
     return r;
 }
 
+constexpr size_t kWorkspaceBytes = 1u << 20;
+
 AcResult validate_grid(AcDim3 g) {
     if (g.x == 0 || g.y == 0 || g.z == 0) return AC_ERR_INVALID_WORK_ITEM_DIMS;
     if (g.x > kMaxGroupsAxis || g.y > kMaxGroupsAxis || g.z > kMaxGroupsAxis) return AC_ERR_INVALID_WORK_ITEM_DIMS;
@@ -143,6 +146,8 @@ AcResult take_device_status(AcContext* ctx) {
     if (code == DEV_STATUS_OK) return AC_SUCCESS;
     s[0] = 0;
     s[1] = 0;
+    // a kernel that gave up may have left sequence flags behind: clear them before the next launch
+    cudaMemsetAsync(ctx->workspace, 0, kWorkspaceBytes, ctx->stream);
     return code == DEV_STATUS_WAIT_TIMEOUT ? AC_ERR_LAUNCH_TIMEOUT : AC_ERR_KERNEL_ARG_INVALID;
 }
 
@@ -152,9 +157,10 @@ AcResult wait_cuda_event(AcContext* ctx, cudaEvent_t ev, uint64_t timeout_ns) {
     for (;;) {
         const cudaError_t q = cudaEventQuery(ev);
         if (q == cudaSuccess) return AC_SUCCESS;
-        if (q != cudaErrorNotReady) {
+        if (q != cudaErrorNotReady) {   // the CUDA error code travels in the error state's offset field
+            fprintf(stderr, "ac_runtime_b200: device error while waiting: %s\n", cudaGetErrorName(q));
             cudaGetLastError();
-            return fail(ctx, AC_ERR_DRIVER_CRASH_OR_LOST, AMEVA_BACKEND_OP_SYNC);
+            return fail(ctx, AC_ERR_DRIVER_CRASH_OR_LOST, AMEVA_BACKEND_OP_SYNC, (size_t)q);
         }
         if (now_ns() - t0 >= timeout_ns) return AC_ERR_LAUNCH_TIMEOUT;
         if (++spins > 2000) std::this_thread::sleep_for(std::chrono::microseconds(20));
@@ -175,6 +181,8 @@ AcResult launch_record(AcContext* ctx, const KernelEntry* e, uint32_t nbind, voi
     a.grid = grid;
     a.status = ctx->status_dev;
     a.sm_count = ctx->prop.multiProcessorCount;
+    a.workspace = ctx->workspace;
+    a.workspace_bytes = kWorkspaceBytes;
     return e->launch(a);
 }
 
@@ -335,8 +343,11 @@ AcResult ac_runtime_context_create(const AcContextDesc* desc, AcContext** out_ct
     }
     if (cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) != cudaSuccess ||
         cudaHostAlloc((void**)&c->status_host, 16, cudaHostAllocMapped) != cudaSuccess ||
-        cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0) != cudaSuccess) {
+        cudaHostGetDevicePointer((void**)&c->status_dev, c->status_host, 0) != cudaSuccess ||
+        cudaMalloc((void**)&c->workspace, kWorkspaceBytes) != cudaSuccess ||
+        cudaMemset(c->workspace, 0, kWorkspaceBytes) != cudaSuccess) {
         cudaGetLastError();
+        if (c->workspace) cudaFree(c->workspace);
         if (c->stream) cudaStreamDestroy(c->stream);
         if (c->status_host) cudaFreeHost(c->status_host);
         delete c;
@@ -359,6 +370,7 @@ AcResult ac_runtime_context_destroy(AcContext* ctx) {
     cudaStreamSynchronize(ctx->stream);
     cudaStreamDestroy(ctx->stream);
     cudaFreeHost(ctx->status_host);
+    cudaFree(ctx->workspace);
     ctx->magic = kMagicDead;
     delete ctx;
     return AC_SUCCESS;
