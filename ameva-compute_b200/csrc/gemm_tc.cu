@@ -100,9 +100,13 @@ struct Ctl {             // shared control words
 // Bounded wait: false when the CTA is aborting (this or another thread ran out of budget). Waiters other than the MMA
 // issuer back off between polls (BACKOFF): a spinning warp takes issue slots from the warps that share its scheduler.
 template <bool BACKOFF = true>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t* status, uint32_t tag) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t* status, uint32_t tag,
+                                          long long* waited = nullptr) {
     const long long t0 = clock64();
+    if (mbar_try_wait(bar, parity)) {
+        if (waited) *waited += clock64() - t0;
+        return true;
+    }
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if (BACKOFF) __nanosleep(64);
@@ -115,6 +119,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
             }
         }
     }
+    if (waited) *waited += clock64() - t0;   // diagnostic: cycles this thread spent blocked here
     return true;
 }
 
@@ -380,16 +385,21 @@ __device__ __forceinline__ void dequant_half(const uint8_t* raw, const uint8_t* 
         }
         const float dl = h2f((uint16_t)(s.x & 0xFFFFu)) * (float)((scp >> (8u * h)) & 0xFFu);
         const float ml = h2f((uint16_t)(s.x >> 16)) * (float)((mnp >> (8u * h)) & 0xFFu);
+        // One byte permute puts a nibble (as a byte 0..15) into mantissa bits 16..19 of the float 0x3F000000 = 0.5, which
+        // then reads 0.5 + q / 256. One fp32 fma gives q dl - ml to about 21 bits (the constant 128 dl costs three of the
+        // 24), and one rounding makes the fp16 operand.
+        const float sl = 256.0f * dl;
+        const float cl = -fmaf(128.0f, dl, ml);
         const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const uint32_t x = (w[i] >> (4u * h)) & 0x0F0F0F0Fu;
-            float f[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k)   // exact nibble -> float through the 2^23 magic, then one fma
-                f[k] = fmaf(__uint_as_float(0x4B000000u | ((x >> (8 * k)) & 0xFFu)) - 8388608.0f, dl, -ml);
-            o[2 * i] = pack_h2(__floats2half2_rn(f[0], f[1]));
-            o[2 * i + 1] = pack_h2(__floats2half2_rn(f[2], f[3]));
+            const float f0 = fmaf(__uint_as_float(__byte_perm(x, 0x3F000000u, 0x7044)), sl, cl);
+            const float f1 = fmaf(__uint_as_float(__byte_perm(x, 0x3F000000u, 0x7144)), sl, cl);
+            const float f2 = fmaf(__uint_as_float(__byte_perm(x, 0x3F000000u, 0x7244)), sl, cl);
+            const float f3 = fmaf(__uint_as_float(__byte_perm(x, 0x3F000000u, 0x7344)), sl, cl);
+            o[2 * i] = pack_h2(__floats2half2_rn(f0, f1));
+            o[2 * i + 1] = pack_h2(__floats2half2_rn(f2, f3));
         }
     } else {
         // I2_S: raw row: 4 K blocks x 32 B; byte k of a block holds weights k, 32+k, 64+k, 96+k in bits 7-6 .. 1-0.
@@ -432,6 +442,10 @@ struct Params {
 __device__ __forceinline__ void trace(const Params& p, uint32_t slot) {
     if ((p.diag & 16u) && blockIdx.x == 0 && blockIdx.y == 0)
         reinterpret_cast<long long*>(p.dst)[slot] = clock64();
+}
+
+__device__ __forceinline__ void trace_val(const Params& p, uint32_t slot, long long v) {
+    if ((p.diag & 16u) && blockIdx.x == 0 && blockIdx.y == 0) reinterpret_cast<long long*>(p.dst)[slot] = v;
 }
 
 // With the same bit every CTA also records the global nanosecond timer at its start and end (slots 2048 + 2 cta, + 1).
@@ -524,6 +538,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     }
     const uint32_t it_begin = unit * p.iters, it_end = min(it_begin + p.iters, p.tiles * KB);
     uint32_t* status = p.status;
+    const bool dg = (p.diag & 16u) != 0u;   // diagnostic run: account the cycles spent in barrier waits
     if (threadIdx.x == 0) {
         trace(p, 0);
         trace_cta(p, 0);
@@ -568,11 +583,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             Ring st(S);
             Seg sg;
             uint32_t it = it_begin, issued = 0;
+            long long w_empty = 0;
             bool ok = true;
             while (ok && next_seg(it, it_end, KB, sg)) {
                 const uint32_t m0 = (sg.tile / p.row_units) * T, rot = rot_of(sg.tile);
                 for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, st.advance()) {
-                    ok = mbar_wait(empty + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x100u | st.idx);
+                    ok = mbar_wait(empty + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x100u | st.idx, dg ? &w_empty : nullptr);
                     if (!ok) break;
                     if (p.diag & 2u) {   // diagnostic: no activation traffic
                         if (rank == 0u) mbar_arrive(full + 8u * st.idx);
@@ -592,6 +608,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     ++issued;
                 }
             }
+            trace_val(p, 1604u, w_empty);
             if (ctl->abort && !(p.diag & 2u) && rank == 0u) {   // let the copies already requested land before leaving
                 for (uint32_t i = issued > S ? issued - S : 0; i < issued; ++i)
                     mbar_wait(full + 8u * (i % S), (i / S) & 1u, ctl, status, 0x180u);
@@ -604,13 +621,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             Ring rr(C::kRawSlots), sr(kScaleSlots);
             Seg sg;
             uint32_t it = it_begin, groups = 0;
+            long long w_raw = 0, w_sc = 0;
             bool ok = true;
             while (ok && next_seg(it, it_end, KB, sg)) {
                 const uint32_t n0 = ((sg.tile % p.row_units) * (PAIR ? 2u : 1u) + rank) * kRows, rot = rot_of(sg.tile);
                 for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb) {
                     const uint32_t kbr = kb + rot < KB ? kb + rot : kb + rot - KB;
                     if (C::kScales && (kb & 3u) == 0u) {
-                        ok = mbar_wait(sc_empty + 8u * sr.idx, sr.phase ^ 1u, ctl, status, 0x600u | sr.idx);
+                        ok = mbar_wait(sc_empty + 8u * sr.idx, sr.phase ^ 1u, ctl, status, 0x600u | sr.idx, dg ? &w_sc : nullptr);
                         if (!ok) break;
                         mbar_arrive_expect_tx(sc_full + 8u * sr.idx, kScaleBytes);
                         tma_load_2d(smem_u32(sSc + sr.idx * kScaleBytes), &scale_map, sc_full + 8u * sr.idx,
@@ -618,7 +636,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                         sr.advance();
                     }
                     if ((kb & (C::kGroup - 1u)) == 0u) {
-                        ok = mbar_wait(raw_empty + 8u * rr.idx, rr.phase ^ 1u, ctl, status, 0x700u | rr.idx);
+                        ok = mbar_wait(raw_empty + 8u * rr.idx, rr.phase ^ 1u, ctl, status, 0x700u | rr.idx, dg ? &w_raw : nullptr);
                         if (!ok) break;
                         mbar_arrive_expect_tx(raw_full + 8u * rr.idx, C::kRawBytes);
                         tma_load_2d(smem_u32(sRaw + rr.idx * C::kRawBytes), &raw_map, raw_full + 8u * rr.idx,
@@ -629,6 +647,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     }
                 }
             }
+            trace_val(p, 1606u, w_raw);
+            trace_val(p, 1607u, w_sc);
             if (ctl->abort) {
                 for (uint32_t i = groups > C::kRawSlots ? groups - C::kRawSlots : 0; i < groups; ++i)
                     mbar_wait(raw_full + 8u * (i % C::kRawSlots), (i / C::kRawSlots) & 1u, ctl, status, 0x780u);
@@ -642,29 +662,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             Ring st(S);
             Seg sg;
             uint32_t it = it_begin, nseg = 0;
+            long long w_full = 0, w_acc = 0, w_issue = 0;
             bool ok = true;
             while (ok && next_seg(it, it_end, KB, sg)) {
                 // the epilogue of the previous segment has read the accumulator out
-                if (nseg) ok = mbar_wait<false>(acc_empty, (nseg - 1u) & 1u, ctl, status, 0x280u);
+                if (nseg) ok = mbar_wait<false>(acc_empty, (nseg - 1u) & 1u, ctl, status, 0x280u, dg ? &w_acc : nullptr);
                 for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb, st.advance()) {
-                    ok = mbar_wait<false>(full + 8u * st.idx, st.phase, ctl, status, 0x200u | st.idx);
+                    ok = mbar_wait<false>(full + 8u * st.idx, st.phase, ctl, status, 0x200u | st.idx, dg ? &w_full : nullptr);
                     if (!ok) break;
-                    trace(p, 2u + kb);
                     tc_fence_after();
                     const uint64_t db = make_smem_desc(smem_u32(sB + st.idx * b_bytes));
                     const uint32_t ta = tmem_a + st.idx * 32u;
+                    const long long ti = dg ? clock64() : 0;
                     if (!(p.diag & 4u)) {
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: 8 TMEM columns / +2 desc units
                             umma_ts<INT8, PAIR>(tmem, ta + 8u * k, db + 2u * k, idesc, (uint32_t)(kb != sg.kb0 || k != 0u));
                     }
                     umma_commit<PAIR>(empty + 8u * st.idx);
-                    trace(p, 130u + kb);
+                    if (dg) w_issue += clock64() - ti;
                 }
                 if (!ok) ctl->abort = 1u;   // visible to whoever passes the accumulator barrier below
                 umma_commit<PAIR>(accum);
                 ++nseg;
             }
+            trace_val(p, 1600u, w_full);
+            trace_val(p, 1601u, w_acc);
+            trace_val(p, 1602u, w_issue);
         }
     } else {
         // The stage ring must be at least as deep as the number of groups: consecutive uses of a stage (K blocks kb, kb +
@@ -682,6 +706,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         Ring sa(S), rr(C::kRawSlots), sr(kScaleSlots);
         Seg sg;
         uint32_t it = it_begin, nseg = 0;
+        long long w_sc = 0, w_raw = 0, w_empty = 0, w_accum = 0;
         while (ok && next_seg(it, it_end, KB, sg)) {
             for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb) {
                 const uint32_t raw_last = min((kb | (C::kGroup - 1u)), sg.kb1 - 1u);   // last K block of this raw group
@@ -689,9 +714,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 if ((kb & 3u) == g) {
                     const bool tr = threadIdx.x == 0u;
                     if (tr) trace(p, 1024u + kb);
-                    if (C::kScales) ok = mbar_wait(sc_full + 8u * sr.idx, sr.phase, ctl, status, 0x800u | sr.idx);
-                    ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x900u | rr.idx);
-                    ok = ok && mbar_wait(empty + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx);
+                    if (C::kScales) ok = mbar_wait(sc_full + 8u * sr.idx, sr.phase, ctl, status, 0x800u | sr.idx, dg ? &w_sc : nullptr);
+                    ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x900u | rr.idx, dg ? &w_raw : nullptr);
+                    ok = ok && mbar_wait(empty + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx, dg ? &w_empty : nullptr);
                     if (!ok) break;
                     if (tr) trace(p, 260u + kb);
                     tc_fence_after();
@@ -726,7 +751,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             // ---- epilogue of the segment: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows) and the 16-column
             //      chunks w / 4, w / 4 + 4, ..., and sends each 32 x 16 piece out through its own 2 KB staging buffer and
             //      one TMA store (or TMA add, for a partial sum that is not the first of its tile) per destination ----
-            ok = ok && mbar_wait(accum, nseg & 1u, ctl, status, 0x500u) && !ctl->abort;
+            ok = ok && mbar_wait(accum, nseg & 1u, ctl, status, 0x500u, dg ? &w_accum : nullptr) && !ctl->abort;
             if (threadIdx.x == 0) trace(p, 520);
             __syncwarp();
             ok = __all_sync(0xffffffffu, ok);
@@ -808,6 +833,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             ++nseg;
         }
         if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (lane == 0 && q4 == 0u) {
+            trace_val(p, 1610u + 4u * g, w_sc);
+            trace_val(p, 1611u + 4u * g, w_raw);
+            trace_val(p, 1612u + 4u * g, w_empty);
+            trace_val(p, 1613u + 4u * g, w_accum);
+        }
     }
     tc_fence_before();
     if (PAIR)

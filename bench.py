@@ -297,18 +297,18 @@ def main():
     launches_per_step = [0]
     batch_keep = []
 
-    def record_steps(batch, n, first):
+    def record_steps(batch, n, first, quantize=True):
         for i in range(n):
             mm = mms[(first + i) % pool_n]
             before = batch.stats().dispatches if i == 0 else None
-            mm.record(batch, x_dev, out_buf, M, dst_offset=out_off, dst_stride=out_stride,
+            mm.record(batch, x_dev, out_buf, M, dst_offset=out_off, dst_stride=out_stride, quantize=quantize,
                       peers=ex.peers if ex else None)
             if ex:
                 ex.record_barrier(batch)
-            if i == 0:
+            if i == 0 and quantize:
                 launches_per_step[0] = batch.stats().dispatches - before
 
-    def gpu_steps(n, first, flags=0):
+    def gpu_steps(n, first, flags=0, quantize=True):
         """n steps on the device; returns (gpu seconds by CUDA events on the runtime's stream, last batch)."""
         if exchange != "allgather":
             per_batch = n if flags else max(1, min(n, 60000 // 70))   # a batch holds at most 65536 dispatches
@@ -317,7 +317,7 @@ def main():
             while done < n:   # every batch is recorded and submitted before the first wait: the GPU never idles
                 cnt = min(per_batch, n - done)
                 batch = ctx.batch(max(64, cnt * 70), flags)
-                record_steps(batch, cnt, first + done)
+                record_steps(batch, cnt, first + done, quantize)
                 pending.append((batch, batch.submit()))
                 done += cnt
             for bt, ev in pending:
@@ -369,15 +369,16 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         gpu_s = float(tt.item())
 
-    # per-dispatch times of the dominant kernel (live, CUDA events after every dispatch on the launching stream)
+    # average launch duration of the dominant kernel, live: the mul_mat kernel(s) alone (activations already quantized
+    # by the steps above), the same rotation of weight copies, back to back on the launching stream between two CUDA
+    # events; the quantize kernel's share is the rest of a step
     roof = None
     if world == 1:
-        nprof = min(args.steps, 10)
-        _, pb = gpu_steps(nprof, args.warmup + args.steps, rt.AC_BATCH_FLAG_DISPATCH_TIMESTAMPS)
-        times = pb.dispatch_times_ns().astype(np.float64).reshape(nprof, -1)
+        nprof = args.steps
+        main_s, pb = gpu_steps(nprof, args.warmup + args.steps, 0, quantize=False)
         pb.destroy()
-        quant_ns = float(np.median(times[:, 0]))
-        main_ns = float(np.median(times[:, 1:].sum(axis=1)))   # the mul_mat kernel(s) of a step
+        main_ns = main_s / nprof * 1e9
+        quant_ns = max(0.0, gpu_s / args.steps * 1e9 - main_ns)
         pk = peaks()
         if unit == "TFLOP/s":
             ach = 2.0 * M * N * K / (main_ns * 1e-9) / 1e12
