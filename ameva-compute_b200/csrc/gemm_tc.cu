@@ -31,6 +31,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "sync_ptx.cuh"
 
 namespace amv {
 namespace tc {
@@ -51,7 +52,6 @@ constexpr int kScaleSlots = 3;
 constexpr uint32_t kEpilogueBytes = kDequantWarps * 2048u;   // one 32 x 16 fp32 staging buffer per epilogue warp
 constexpr uint32_t kScaleBytes = kRows * 16;        // 2 KB: 16 bytes of scales per row per 256 weights
 constexpr uint32_t kSmemLimit = 227 * 1024;
-constexpr long long kWaitCycles = 2000000000ll;     // about one second
 
 enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_I2_S = 36 };
 
@@ -68,75 +68,9 @@ struct Cfg {
     static constexpr uint32_t kRawSlots = TYPE == T_Q8_0 ? 4u : 3u;
 };
 
-// ---- PTX wrappers ---------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-
-struct Ctl {             // shared control words
-    uint32_t tmem_base;
-    volatile uint32_t abort;
-};
-
-// Bounded wait: false when the CTA is aborting (this or another thread ran out of budget). Waiters other than the MMA
-// issuer back off between polls (BACKOFF): a spinning warp takes issue slots from the warps that share its scheduler.
-template <bool BACKOFF = true>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t* status, uint32_t tag,
-                                          long long* waited = nullptr) {
-    const long long t0 = clock64();
-    if (mbar_try_wait(bar, parity)) {
-        if (waited) *waited += clock64() - t0;
-        return true;
-    }
-    uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
-        if (BACKOFF) __nanosleep(64);
-        if ((++spins & 63u) == 0u) {
-            if (ctl->abort) return false;
-            if (clock64() - t0 > kWaitCycles) {
-                ctl->abort = 1u;
-                if (atomicCAS(status, DEV_STATUS_OK, DEV_STATUS_WAIT_TIMEOUT) == DEV_STATUS_OK) status[1] = tag;
-                return false;
-            }
-        }
-    }
-    if (waited) *waited += clock64() - t0;   // diagnostic: cycles this thread spent blocked here
-    return true;
-}
-
-// Position in a ring of n slots: slot index and the parity of the current pass (no divisions in the K loop).
-struct Ring {
-    uint32_t idx, phase, n;
-    __device__ __forceinline__ Ring(uint32_t slots) : idx(0u), phase(0u), n(slots) {}
-    __device__ __forceinline__ void advance() {
-        if (++idx == n) {
-            idx = 0u;
-            phase ^= 1u;
-        }
-    }
-};
-
+// ---- PTX wrappers (barriers, bounded waits and ring counters come from sync_ptx.cuh) -----------------------------------
+using namespace ptx;
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 

@@ -122,8 +122,10 @@ class MulMat:
     """
 
     def __init__(self, ctx: rt.Context, weight, max_m: int, *, round_mode: int = ROUND_NEAREST_EVEN,
-                 q8k_mode: int = Q8K_GGML, dump_block_sums: bool = False, exact: bool = False) -> None:
+                 q8k_mode: int = Q8K_GGML, dump_block_sums: bool = False, exact: bool = False,
+                 streamed: bool = False) -> None:
         self.ctx = ctx
+        self.streamed = streamed   # M <= 8: stage the weight rows in shared memory by bulk copies (ameva_mmvs_*)
         self.view = weight if isinstance(weight, WeightView) else weight.view(0, weight.N)
         w = self.view.weight
         why = unsupported_reason(w.type, max_m, self.view.rows, w.K)
@@ -199,8 +201,13 @@ class MulMat:
         peers = list(peers or [])
         if len(peers) > 7:
             raise MulMatUnsupported("at most 7 peers")
-        if peers and (t == GGML_TYPE_I2_S or (not use_tc and (t != GGML_TYPE_Q4_K or M > GEMV_MAX_M))):
-            raise MulMatUnsupported("the fused peer exchange is built for the tensor-core GEMM and the Q4_K GEMV")
+        # The shared-memory-streamed GEMV carries the peer exchange for every scaled type; on one GPU the
+        # register-staged kernels measure faster (35 vs 45 us on 28672 x 8192 Q4_K), so it runs only on request.
+        streamed = (not use_tc and M <= GEMV_MAX_M and t != GGML_TYPE_I2_S and K % 256 == 0 and not self.dump
+                    and not self.exact and (self.streamed or bool(peers)))
+        if peers and not (use_tc and t != GGML_TYPE_I2_S) and not streamed:
+            raise MulMatUnsupported("the fused peer exchange is built for the tensor-core GEMM of the scaled types and "
+                                    "the streamed GEMV (K a multiple of 256)")
         if use_tc:
             self.path = "mmtc"
             grid = ((M + 255) // 256, (N + 127) // 128, 1)
@@ -219,14 +226,16 @@ class MulMat:
                 batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}"),
                                [self.qbind, self.sbind, self.ah, (dst, dst_offset)], [M, N, K, dst_stride], grid)
             return
-        self.path = "mmvq" if M <= GEMV_MAX_M else "mmvq-chunks"
-        if peers:
-            self.path = "mmvq+peer-stores"
+        if streamed:
+            # weight rows staged in shared memory by bulk copies, several stages ahead of the dot products; also carries
+            # the output exchange of a row-sharded projection (every output row stored to every rank)
+            self.path = "mmvs+peer-stores" if peers else "mmvs"
             outs = [(dst, dst_offset)] + [(pb, dst_offset) for pb in peers]
             outs += [(dst, dst_offset)] * (8 - len(outs))
-            batch.dispatch(ctx.kernel("ameva_mmvqb_q4_K_mp"), [self.qbind, self.sbind, self.aq, self.ad] + outs,
-                           [M, N, K, dst_stride, len(peers)], ((N + 15) // 16, 1, 1))
+            batch.dispatch(ctx.kernel(f"ameva_mmvs_{TYPE_NAMES[t]}"), [self.qbind, self.sbind, self.aq, self.ad] + outs,
+                           [M, N, K, dst_stride, len(peers), 0], ((N + 15) // 16, 1, 1))
             return
+        self.path = "mmvq" if M <= GEMV_MAX_M else "mmvq-chunks"
         for m0 in range(0, M, GEMV_MAX_M):
             mc = min(GEMV_MAX_M, M - m0)
             d_off = dst_offset + m0 * dst_stride * 4

@@ -16,7 +16,7 @@ copy of the result inside the timed region.
 With N > 1 (launched by torch.distributed.run) the weight rows are sharded over the ranks (strong scaling: the total
 work is fixed). Every rank owns a full [M][N] output shared with the other ranks over CUDA IPC; the mul_mat's epilogue
 stores the rank's rows into every rank's output over NVLink and a flag barrier kernel closes the step, so the exchange
-is part of this library's kernels and of the timed region. Kernels without that epilogue (I2_S, Q4_0/Q8_0 GEMV) fall
+is part of this library's kernels and of the timed region. Kernels without that epilogue (I2_S) fall
 back to an NCCL all-gather of the fp32 output plus a permute, also inside the timed region.
 
 `--impl reference` times the CPU implementation of the same path (the oracle: a C restatement of the ggml CPU
@@ -60,7 +60,7 @@ WORKLOADS = {
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (bytes)
-TRAFFIC = {"cfg2": 53424896, "cfg5-up-m1": 136504320}
+TRAFFIC = {"cfg2": 58067200, "cfg5-up-m1": 136173568}
 GEMV_MAX_M = 8
 
 
@@ -276,7 +276,7 @@ def main():
     tc_path = M > GEMV_MAX_M and mms[0].tc_ok
     exchange = "none"
     if world > 1:
-        exchange = "peer" if (t != I2_S and (tc_path or (t == Q4_K and M <= GEMV_MAX_M))) else "allgather"
+        exchange = "peer" if (t != I2_S and (tc_path or (M <= GEMV_MAX_M and K % 256 == 0))) else "allgather"
     ex = None
     if exchange == "peer":
         ex = qmm.PeerExchange(ctx, rank, world, M * N * 4)

@@ -21,15 +21,17 @@ def ctx():
     c.destroy()
 
 
-def run_case(ctx, t, M, N, K, seed=0, dump=True, check_strict=True):
+def run_case(ctx, t, M, N, K, seed=0, dump=True, check_strict=True, streamed=False):
     blocks, scale = make_weights(t, N, K, seed)
     x = make_acts(M, K, seed + 1)
     w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
-    mm = qmm.MulMat(ctx, w, M, dump_block_sums=dump and t != I2_S)
+    mm = qmm.MulMat(ctx, w, M, dump_block_sums=dump and t != I2_S, streamed=streamed)
     xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
     dst.fill(0xFF)
     mm.run(xb, dst, M)
     y = dst.read(np.float32).reshape(M, N)
+    # the shared-memory-streamed kernel runs on request, for the scaled types and K % 256 == 0, and never with the dump
+    assert mm.path == ("mmvs" if (streamed and t != I2_S and K % 256 == 0 and not dump) else "mmvq")
     want, sums, aq = oracle_mul_mat(t, blocks, scale, x, N, K)
     # 1. activation quantization: bytes equal
     if t in (Q4_0, Q8_0):
@@ -76,10 +78,19 @@ def _dequant_acts(t, aq, M, K):
 SMALL = [(1, 1, 256), (1, 3, 256), (2, 17, 512), (3, 64, 1024), (4, 130, 768), (5, 33, 2048), (7, 250, 256), (8, 96, 4096)]
 
 
+@pytest.mark.parametrize("mode", ["dump", "plain", "streamed"])
 @pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
 @pytest.mark.parametrize("M,N,K", SMALL)
-def test_gemv_small_shapes(ctx, t, M, N, K):
-    run_case(ctx, t, M, N, K, seed=M * 7 + N)
+def test_gemv_small_shapes(ctx, t, M, N, K, mode):
+    run_case(ctx, t, M, N, K, seed=M * 7 + N, dump=mode == "dump", streamed=mode == "streamed")
+
+
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 4352), (2, 1000, 8192), (4, 2500, 12288), (8, 300, 4096), (1, 9, 16384)])
+def test_gemv_streamed_k_segments_and_ragged_row_blocks(ctx, t, M, N, K):
+    """K longer than one stage (several segments per row, the last one shorter), N not a multiple of the row block."""
+    run_case(ctx, t, M, N, K, seed=N + K, dump=False, check_strict=(M <= 2), streamed=True)
+    run_case(ctx, t, M, N, K, seed=N + K, dump=False, check_strict=False)
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 1, 128), (1, 5, 384), (2, 64, 2560), (8, 130, 1280), (3, 640, 2560)])
@@ -92,15 +103,17 @@ def test_gemv_k_not_multiple_of_lane_span(ctx, t, K):
     run_case(ctx, t, 2, 9, K, seed=K)
 
 
-def test_config1_q4_0_decode_full_size(ctx):
+@pytest.mark.parametrize("mode", ["dump", "plain", "streamed"])
+def test_config1_q4_0_decode_full_size(ctx, mode):
     """Configuration 1: W 4096 x 4096 Q4_0, M = 1, seed 0."""
-    run_case(ctx, Q4_0, 1, 4096, 4096, seed=0)
+    run_case(ctx, Q4_0, 1, 4096, 4096, seed=0, dump=mode == "dump", streamed=mode == "streamed")
 
 
+@pytest.mark.parametrize("mode", ["dump", "plain", "streamed"])
 @pytest.mark.parametrize("N,K", [(4096, 4096), (11008, 4096), (4096, 11008)])
 @pytest.mark.parametrize("M", [1, 8])
-def test_config3_q4_K_llama7b_shapes(ctx, M, N, K):
-    run_case(ctx, Q4_K, M, N, K, seed=3, check_strict=(M == 1))
+def test_config3_q4_K_llama7b_shapes(ctx, M, N, K, mode):
+    run_case(ctx, Q4_K, M, N, K, seed=3, check_strict=(M == 1), dump=mode == "dump", streamed=mode == "streamed")
 
 
 @pytest.mark.parametrize("N,K", [(2560, 2560), (640, 2560), (6912, 2560), (2560, 6912)])
@@ -108,14 +121,17 @@ def test_config4_bitnet_shapes_decode(ctx, N, K):
     run_case(ctx, I2_S, 1, N, K, seed=4, check_strict=False)
 
 
-def test_config5_q4_K_70b_ffn_decode(ctx):
-    run_case(ctx, Q4_K, 1, 28672, 8192, seed=5, check_strict=False)
-    run_case(ctx, Q4_K, 1, 8192, 28672, seed=6, check_strict=False)
+@pytest.mark.parametrize("mode", ["dump", "plain", "streamed"])
+def test_config5_q4_K_70b_ffn_decode(ctx, mode):
+    run_case(ctx, Q4_K, 1, 28672, 8192, seed=5, check_strict=False, dump=mode == "dump", streamed=mode == "streamed")
+    run_case(ctx, Q4_K, 1, 8192, 28672, seed=6, check_strict=False, dump=mode == "dump", streamed=mode == "streamed")
 
 
 def test_q8_0_decode_11008x4096(ctx):
     run_case(ctx, Q8_0, 1, 11008, 4096, seed=2)
     run_case(ctx, Q8_0, 8, 11008, 4096, seed=2, check_strict=False)
+    run_case(ctx, Q8_0, 1, 11008, 4096, seed=2, dump=False)
+    run_case(ctx, Q8_0, 8, 11008, 4096, seed=2, check_strict=False, dump=False, streamed=True)
 
 
 def test_i2s_reference_contract_single_vector_and_acc(ctx):

@@ -60,10 +60,11 @@ def test_gemm_peer_stores(ctx, t, M, N, K, world, npeer):
         assert np.array_equal(y.view(np.uint32), ys[0].view(np.uint32))
 
 
+@pytest.mark.parametrize("t", [Q4_K, Q4_0, Q8_0])
 @pytest.mark.parametrize("M,N,K,world,npeer", [(1, 512, 512, 2, 1), (8, 640, 1024, 4, 3), (3, 272, 256, 2, 7)])
-def test_gemv_q4k_peer_stores(ctx, M, N, K, world, npeer):
-    ys, want, path = sharded_into_full(ctx, Q4_K, M, N, K, world, npeer)
-    assert path == "mmvq+peer-stores"
+def test_gemv_streamed_peer_stores(ctx, t, M, N, K, world, npeer):
+    ys, want, path = sharded_into_full(ctx, t, M, N, K, world, npeer)
+    assert path == "mmvs+peer-stores"
     assert max_normalised_error(ys[0], want) <= 1e-3
     for y in ys[1:]:
         assert np.array_equal(y.view(np.uint32), ys[0].view(np.uint32))
