@@ -87,7 +87,8 @@ struct BatchRecord {
 struct AcCommandBatch {
     uint32_t magic;
     AcContext* ctx;
-    enum State { RECORDING, SUBMITTED, ABORTED } state;
+    enum State { RECORDING, SUBMITTED, ABORTED, REPLAYABLE } state;
+    cudaGraphExec_t exec;   // REPLAYABLE: the recorded launches as an instantiated CUDA graph
     uint32_t max_dispatches, flags;
     std::vector<BatchRecord> records;
     size_t flushed;  // records already launched
@@ -865,6 +866,7 @@ AcResult ac_runtime_batch_begin_ex(AcContext* context, const AcBatchDesc* desc, 
     memset(&b->stats, 0, sizeof(b->stats));
     b->t_begin = b->t_end = nullptr;
     b->started = b->completed = false;
+    b->exec = nullptr;
     b->records.reserve(desc->max_dispatches < 256 ? desc->max_dispatches : 256);
     context->live_batches++;
     *out_batch = b;
@@ -1003,11 +1005,79 @@ AcResult ac_runtime_batch_abort(AcCommandBatch* batch) {
     return AC_SUCCESS;
 }
 
+// ---- replayable batches (no counterpart in the reference: its command batches are one-shot) ------------------------
+// ac_b200_batch_instantiate turns a recorded, not yet flushed batch into a CUDA graph of its launches (stream capture
+// of the same launchers, so every argument check still runs once); ac_b200_batch_replay enqueues that graph on the
+// context's stream any number of times. Launch-bound step sequences (decode GEMVs of a few microseconds) then cost one
+// graph launch instead of one host launch per kernel.
+AcResult ac_b200_batch_instantiate(AcCommandBatch* batch) {
+    if (!bat_ok(batch)) return AC_ERR_INVALID_ARGUMENT;
+    if (batch->state != AcCommandBatch::RECORDING || batch->flushed || batch->records.empty())
+        return AC_ERR_INVALID_ARGUMENT;
+    if (batch->flags & (AC_BATCH_FLAG_TIMESTAMPS | AC_BATCH_FLAG_DISPATCH_TIMESTAMPS)) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    AcContext* ctx = batch->ctx;
+    DeviceGuard g(ctx->device);
+    if (cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ctx, AC_ERR_FEATURE_NOT_SUPPORTED, AMEVA_BACKEND_OP_DISPATCH);
+    }
+    const AcResult r = flush_batch(batch);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    if (r != AC_SUCCESS || e != cudaSuccess || !graph) {
+        if (graph) cudaGraphDestroy(graph);
+        cudaGetLastError();
+        batch->state = AcCommandBatch::ABORTED;
+        batch->started = false;   // nothing ran
+        return r != AC_SUCCESS ? r : fail(ctx, AC_ERR_FEATURE_NOT_SUPPORTED, AMEVA_BACKEND_OP_DISPATCH);
+    }
+    const cudaError_t ie = cudaGraphInstantiate(&batch->exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) {
+        cudaGetLastError();
+        batch->exec = nullptr;
+        batch->state = AcCommandBatch::ABORTED;
+        batch->started = false;
+        return fail(ctx, AC_ERR_OUT_OF_DEVICE_MEMORY, AMEVA_BACKEND_OP_DISPATCH);
+    }
+    batch->state = AcCommandBatch::REPLAYABLE;
+    batch->started = false;
+    return AC_SUCCESS;
+}
+
+AcResult ac_b200_batch_replay(AcCommandBatch* batch, AcEvent** out_completion_event) {
+    if (out_completion_event) *out_completion_event = nullptr;
+    if (!bat_ok(batch)) return AC_ERR_INVALID_ARGUMENT;
+    if (batch->state != AcCommandBatch::REPLAYABLE || !batch->exec) return AC_ERR_INVALID_ARGUMENT;
+    AcContext* ctx = batch->ctx;
+    DeviceGuard g(ctx->device);
+    AcEvent* ev = nullptr;
+    AcResult r = make_event(ctx, true, &ev);
+    if (r != AC_SUCCESS) return r;
+    cudaEventRecord(ev->start, ctx->stream);
+    if (cudaGraphLaunch(batch->exec, ctx->stream) != cudaSuccess) {
+        cudaGetLastError();
+        free_event(ev);
+        return fail(ctx, AC_ERR_DRIVER_CRASH_OR_LOST, AMEVA_BACKEND_OP_DISPATCH);
+    }
+    cudaEventRecord(ev->end, ctx->stream);
+    batch->started = true;   // work of this batch may be in flight: destroy synchronizes
+    batch->stats.flushes++;
+    if (out_completion_event) {
+        *out_completion_event = ev;
+        return AC_SUCCESS;
+    }
+    r = ac_runtime_event_wait(ev, kBlockingWaitNs);
+    free_event(ev);
+    return r;
+}
+
 void ac_runtime_batch_destroy(AcCommandBatch* batch) {
     if (!bat_ok(batch)) return;
     AcContext* ctx = batch->ctx;
     DeviceGuard g(ctx->device);
     if (batch->started && !batch->completed) cudaStreamSynchronize(ctx->stream);  // launched work may still run
+    if (batch->exec) cudaGraphExecDestroy(batch->exec);
     release_records(batch);
     destroy_batch_events(batch);
     ctx->live_batches--;

@@ -131,7 +131,7 @@ EXPORTED_SYMBOLS = [
     "ac_runtime_get_error_state_ctx", "ac_runtime_consume_error_ctx", "ac_runtime_advance_generation_ctx",
     "ac_runtime_get_generation_ctx", "ac_runtime_reset_error_state_ctx", "ac_runtime_kernel_create_builtin",
     "ac_b200_kernel_count", "ac_b200_kernel_name", "ac_b200_context_get_stream", "ac_b200_buffer_import",
-    "ac_b200_buffer_export_ipc", "ac_b200_buffer_open_ipc", "ac_b200_buffer_write_async", "ac_b200_buffer_read_async", "ac_b200_context_synchronize",
+    "ac_b200_buffer_export_ipc", "ac_b200_buffer_open_ipc", "ac_b200_buffer_write_async", "ac_b200_buffer_read_async", "ac_b200_context_synchronize", "ac_b200_batch_instantiate", "ac_b200_batch_replay",
     "ac_b200_device_layout", "ac_b200_repack_to_device", "ac_b200_repack_from_device",
     "ac_b200_mul_mat_q4_0_static",
 ]
@@ -212,6 +212,8 @@ def load_library() -> C.CDLL:
         "ac_b200_buffer_write_async": (C.c_int, [vp, sz, vp, sz]),
         "ac_b200_buffer_read_async": (C.c_int, [vp, sz, vp, sz]),
         "ac_b200_context_synchronize": (C.c_int, [vp]),
+        "ac_b200_batch_instantiate": (C.c_int, [vp]),
+        "ac_b200_batch_replay": (C.c_int, [vp, C.POINTER(vp)]),
         "ac_b200_device_layout": (C.c_int, [u32, u64, u64, P(u64), P(u64)]),
         "ac_b200_mul_mat_q4_0_static": (C.c_int, [vp, vp, vp, vp, u32, vp, u32, u32, u32, u32, u32]),
         "ac_b200_repack_to_device": (C.c_int, [u32, vp, u64, u64, vp]),
@@ -379,6 +381,16 @@ class Batch:
     def submit(self) -> Event:
         out = C.c_void_p()
         _check(load_library().ac_runtime_batch_submit(self._h, C.byref(out)), "batch_submit")
+        return Event(out.value)
+
+    def instantiate(self) -> None:
+        """Turn the recorded (not yet flushed) dispatches into a CUDA graph; `replay` then enqueues it any number of
+        times. B200 extension: the reference's batches are one-shot."""
+        _check(load_library().ac_b200_batch_instantiate(self._h), "batch_instantiate")
+
+    def replay(self) -> Event:
+        out = C.c_void_p()
+        _check(load_library().ac_b200_batch_replay(self._h, C.byref(out)), "batch_replay")
         return Event(out.value)
 
     def dispatch_times_ns(self) -> np.ndarray:

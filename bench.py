@@ -232,6 +232,7 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-replay", action="store_true", help="one host launch per kernel instead of replayed batches")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     name = args.workload
@@ -308,8 +309,43 @@ def main():
             if i == 0 and quantize:
                 launches_per_step[0] = batch.stats().dispatches - before
 
+    # One GPU: the steps are replayed from instantiated batches (CUDA graphs of pool_n consecutive steps, one per weight
+    # copy), so that a step of a few microseconds is not bounded by one host launch per kernel; the timed region is
+    # bracketed by CUDA events on the runtime's stream.
+    use_replay = world == 1 and not args.no_replay
+    replay_cache = {}
+
+    def replay_batch(quantize):
+        if quantize not in replay_cache:
+            rb = ctx.batch(max(64, pool_n * 70), 0)
+            record_steps(rb, pool_n, 0, quantize)
+            rb.instantiate()
+            replay_cache[quantize] = rb
+        return replay_cache[quantize]
+
     def gpu_steps(n, first, flags=0, quantize=True):
         """n steps on the device; returns (gpu seconds by CUDA events on the runtime's stream, last batch)."""
+        if use_replay and not flags:
+            full, rem = divmod(n, pool_n)
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            rb = replay_batch(quantize) if full else None
+            tail = None
+            if rem:
+                tail = ctx.batch(max(64, rem * 70), 0)
+                record_steps(tail, rem, 0, quantize)
+            evs = []
+            with torch.cuda.stream(ext_stream):
+                start.record()
+                for _ in range(full):
+                    evs.append(rb.replay())
+                if tail:
+                    evs.append(tail.submit())
+                end.record()
+            for ev in evs:
+                ev.wait(600_000_000_000)
+                ev.destroy()
+            end.synchronize()
+            return start.elapsed_time(end) / 1e3, tail
         if exchange != "allgather":
             per_batch = n if flags else max(1, min(n, 60000 // 70))   # a batch holds at most 65536 dispatches
             gpu_s, done, batch = 0.0, 0, None
@@ -376,7 +412,8 @@ def main():
     if world == 1:
         nprof = args.steps
         main_s, pb = gpu_steps(nprof, args.warmup + args.steps, 0, quantize=False)
-        pb.destroy()
+        if pb:
+            pb.destroy()
         main_ns = main_s / nprof * 1e9
         quant_ns = max(0.0, gpu_s / args.steps * 1e9 - main_ns)
         pk = peaks()
@@ -461,7 +498,9 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"{name}: {desc}", "M": M, "N": N, "K": K,
                        "l2": f"rotating pool of {pool_n} weight copies ({pool_n * shard_bytes / 1e6:.0f} MB > L2) per rank",
-                       "parallelism": par, "path": mms[0].path},
+                       "parallelism": par, "path": mms[0].path,
+                       "launch": f"replayed batches (CUDA graphs of {pool_n} steps)" if use_replay else
+                                 "one host launch per kernel"},
             "wall_ms_per_step": wall_s / args.steps * 1e3,
             "gpu_launches": launches_per_step[0] * args.steps,
             "e2e": {"value": unit_value(unit, t, M, N, K, e2e_s / e2e_steps), "unit": unit,
@@ -479,6 +518,8 @@ def main():
     if dist is not None:   # nobody unmaps a buffer a peer may still be writing; and never hang after the line is out
         threading.Timer(60.0, lambda: os._exit(0)).start()
         barrier()
+    for rb in replay_cache.values():
+        rb.destroy()
     for mm in mms:
         mm.destroy()
     for w in weights:

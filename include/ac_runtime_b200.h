@@ -327,6 +327,16 @@ AcResult ac_b200_buffer_write_async(AcBuffer* buf, size_t offset, const void* sr
 AcResult ac_b200_buffer_read_async(AcBuffer* buf, size_t offset, void* dst, size_t size_bytes);
 AcResult ac_b200_context_synchronize(AcContext* ctx);
 
+/* Replayable batches. The reference's command batches are one-shot (include/ac_runtime.h:820-880); these two calls have
+ * no reference counterpart. ac_b200_batch_instantiate takes a batch that is recording and not yet flushed (without the
+ * timestamp flags) and turns its dispatches into an instantiated CUDA graph: every launcher runs once under stream
+ * capture, so argument checks and errors are those of a normal flush, and nothing executes yet. ac_b200_batch_replay
+ * enqueues the graph on the context's stream (any number of times, in stream order with everything else) and returns a
+ * completion event with GPU timing, or blocks when out_completion_event is NULL. The buffers and kernels of the batch
+ * stay retained until ac_runtime_batch_destroy. */
+AcResult ac_b200_batch_instantiate(AcCommandBatch* batch);
+AcResult ac_b200_batch_replay(AcCommandBatch* batch, AcEvent** out_completion_event);
+
 /* Weight codec: ggml block bytes <-> the device region layout the kernels read. Stands in for the reference's CPU
  * repack codec (adapters/llama/ggml-ameva/ggml-ameva-repack.cpp:82-247, ggml-ameva-buffer.cpp:300-330). type is the
  * ggml type id (2 = Q4_0, 8 = Q8_0, 12 = Q4_K, 36 = I2_S). The device layout is the quant payloads of all blocks, padded

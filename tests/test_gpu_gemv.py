@@ -200,3 +200,37 @@ def test_unsupported_is_an_explicit_error_not_a_fallback(ctx):
     for b in bufs[2:]:
         b.destroy()
     w.destroy()
+
+
+def test_replayed_batch_matches_one_shot_submit(ctx):
+    """A batch turned into a CUDA graph and replayed three times leaves the bytes a one-shot submit leaves; instantiating
+    a flushed or timestamped batch is refused."""
+    t, M, N, K = Q4_K, 2, 520, 1024
+    blocks, scale = make_weights(t, N, K, 11)
+    x = make_acts(M, K, 12)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, a, b = ctx.buffer(data=x), ctx.buffer(M * N * 4), ctx.buffer(M * N * 4)
+    mm.run(xb, a, M)
+    rb = ctx.batch(64)
+    mm.record(rb, xb, b, M)
+    rb.instantiate()
+    for _ in range(3):
+        b.fill(0xFF)
+        ev = rb.replay()
+        ev.wait()
+        assert ev.gpu_duration_us() > 0
+        ev.destroy()
+        assert np.array_equal(a.read(np.uint32), b.read(np.uint32))
+    with pytest.raises(rt.AmevaComputeError):
+        rb.submit()            # a replayable batch is not submitted the one-shot way
+    rb.destroy()
+    tb = ctx.batch(64, rt.AC_BATCH_FLAG_DISPATCH_TIMESTAMPS)
+    mm.record(tb, xb, b, M)
+    with pytest.raises(rt.AmevaComputeError):
+        tb.instantiate()
+    tb.destroy()
+    for v in (xb, a, b):
+        v.destroy()
+    mm.destroy()
+    w.destroy()
