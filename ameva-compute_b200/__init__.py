@@ -4,13 +4,14 @@
                kernels, dispatch, batches, events); the CUDA library is the only implementation: a missing library or
                kernel is an error, never a fallback.
     shard    - row partition of a projection over the GPUs of one box (plain arithmetic + the gather/permute step)
+    amuda    - ctypes mirror of the legacy amuda host API (libamuda_b200.so)
     qmm      - host side of MUL_MAT over Q4_0 / Q8_0 / Q4_K / I2_S weights: upload + repack, shape contract, kernel choice
                by M, dispatch sequence.
 
 The directory name carries the reference project's name (with its hyphen), so import it with
 ``importlib.import_module("ameva-compute_b200")``.
 """
-from . import qmm, runtime, shard  # noqa: F401
+from . import amuda, qmm, runtime, shard  # noqa: F401
 from .runtime import AmevaComputeError, init  # noqa: F401
 
-__all__ = ["runtime", "qmm", "shard", "init", "AmevaComputeError"]
+__all__ = ["runtime", "qmm", "shard", "amuda", "init", "AmevaComputeError"]

@@ -4,6 +4,7 @@
 
 Outputs (git-ignored, next to this file):
     libac_runtime_b200.so   the ac_runtime C ABI + every built-in kernel
+    libamuda_b200.so        the legacy amuda host API + ac_ops_bitnet_gemv_i2_s_exact
 """
 from __future__ import annotations
 
@@ -15,6 +16,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libac_runtime_b200.so")
+LEGACY_LIB = os.path.join(HERE, "libamuda_b200.so")
 
 RUNTIME_SOURCES = ["runtime.cu", "registry.cu", "act_quant.cu", "gemv.cu", "gemv_bulk.cu", "gemm_tc.cu", "noalloc.cu", "peer_sync.cu"]
 NVCC_FLAGS = [
@@ -61,6 +63,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if force or procs or _stale(LIB, objs):
         cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB] + objs
         subprocess.run(cmd, check=True)
+    # the legacy host API is a library of its own: its type names collide with the opaque handles of the ac_runtime ABI
+    shim = os.path.join(CSRC, "amuda_shim.cu")
+    if force or _stale(LEGACY_LIB, [shim, os.path.join(ROOT, "include", "amuda_b200.h")]):
+        cmd = [_nvcc()] + NVCC_FLAGS + ["-shared", shim, "-o", LEGACY_LIB]
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0 or verbose:
+            sys.stderr.write(f"--- nvcc amuda_shim.cu ---\n{r.stdout}\n")
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed")
     return LIB
 
 

@@ -352,9 +352,9 @@ class PeerExchange:
         return [self.peer_out[r] for r in sorted(self.peer_out)]
 
     def record_barrier(self, batch: rt.Batch) -> None:
-        self.epoch += 1
+        """The kernel counts its own uses (epoch 0), so a recorded step can be replayed."""
         slots = [self.flags if r == self.rank or r >= self.world else self.peer_flags[r] for r in range(8)]
-        batch.dispatch(self.ctx.kernel("ameva_peer_barrier"), slots, [self.rank, self.world, self.epoch], (1, 1, 1))
+        batch.dispatch(self.ctx.kernel("ameva_peer_barrier"), slots, [self.rank, self.world, 0], (1, 1, 1))
 
     def destroy(self) -> None:
         for b in list(self.peer_out.values()) + list(self.peer_flags.values()) + [self.out, self.flags]:

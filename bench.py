@@ -309,10 +309,11 @@ def main():
             if i == 0 and quantize:
                 launches_per_step[0] = batch.stats().dispatches - before
 
-    # One GPU: the steps are replayed from instantiated batches (CUDA graphs of pool_n consecutive steps, one per weight
-    # copy), so that a step of a few microseconds is not bounded by one host launch per kernel; the timed region is
-    # bracketed by CUDA events on the runtime's stream.
-    use_replay = world == 1 and not args.no_replay
+    # The steps are replayed from instantiated batches (CUDA graphs of pool_n consecutive steps, one per weight copy;
+    # with peers each step ends in the flag barrier kernel, which counts its own epochs), so that a step of a few
+    # microseconds is not bounded by one host launch per kernel; the timed region is bracketed by CUDA events on the
+    # runtime's stream.
+    use_replay = exchange != "allgather" and not args.no_replay
     replay_cache = {}
 
     def replay_batch(quantize):

@@ -146,3 +146,24 @@ def test_peer_barrier_wait_runs_out(ctx):
     _barrier(ctx, mine, other, 0, 2, 2)
     mine.destroy()
     other.destroy()
+
+
+def test_peer_barrier_counts_its_own_epochs(ctx):
+    """Epoch 0: the kernel numbers its uses itself (word 16 of the own array), which is what a replayed step needs."""
+    mine, other, small = ctx.buffer(256), ctx.buffer(256), ctx.buffer(64)
+    mine.fill(0)
+    other.fill(0)
+    w = np.zeros(64, np.uint32)
+    w[1] = 5                      # "rank 1" is already at epoch 5
+    mine.write(w)
+    for n in (1, 2, 3):
+        _barrier(ctx, mine, other, 0, 2, 0)
+        assert mine.read(np.uint32)[16] == n
+        assert other.read(np.uint32)[0] == n
+    batch = ctx.batch(8)
+    with pytest.raises(rt.AmevaComputeError):   # a flag array must hold the counter word too
+        batch.dispatch(ctx.kernel("ameva_peer_barrier"), [mine, small] + [mine] * 6, [0, 2, 0], (1, 1, 1))
+        batch.submit().wait()
+    batch.destroy()
+    for b in (mine, other, small):
+        b.destroy()
