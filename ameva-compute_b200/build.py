@@ -5,6 +5,9 @@
 Outputs (git-ignored, next to this file):
     libac_runtime_b200.so   the ac_runtime C ABI + every built-in kernel
     libamuda_b200.so        the legacy amuda host API + ac_ops_bitnet_gemv_i2_s_exact
+    libggml-ameva-b200.so   the ggml backend plugin, only where ggml's headers are available (GGML_INCLUDE_DIR, or the
+                            headers vendored by a checkout of the reference); with it the test harness
+                            tests/ggml_shim/_build/driver
 """
 from __future__ import annotations
 
@@ -75,5 +78,37 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+GGML_PLUGIN = os.path.join(HERE, "libggml-ameva-b200.so")
+GGML_DRIVER = os.path.join(ROOT, "tests", "ggml_shim", "_build", "driver")
+
+
+def ggml_include_dir():
+    for cand in (os.environ.get("GGML_INCLUDE_DIR"), "/root/reference/include/ggml"):
+        if cand and os.path.exists(os.path.join(cand, "ggml-backend-impl.h")):
+            return cand
+    return None
+
+
+def build_ggml_plugin(force: bool = False):
+    """Compiles the ggml backend plugin and its test harness against the host application's ggml headers. Returns the
+    plugin path, or None when no ggml headers are around (prebuilt binaries, if any, are left alone)."""
+    inc = ggml_include_dir()
+    if not inc:
+        return None
+    src = os.path.join(HERE, "ggml_plugin", "ggml_ameva_b200.cpp")
+    drv = os.path.join(ROOT, "tests", "ggml_shim", "driver.cpp")
+    cxx = "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"
+    if force or _stale(GGML_PLUGIN, [src, LIB, os.path.join(ROOT, "include", "ac_runtime_b200.h")]):
+        subprocess.run([cxx, "-std=c++17", "-fPIC", "-shared", "-O2", "-Wall", "-I", inc, src, "-o", GGML_PLUGIN,
+                        "-L", HERE, "-lac_runtime_b200", "-Wl,-rpath,$ORIGIN"], check=True)
+    os.makedirs(os.path.dirname(GGML_DRIVER), exist_ok=True)
+    if force or _stale(GGML_DRIVER, [drv, GGML_PLUGIN]):
+        subprocess.run([cxx, "-std=c++17", "-O1", "-Wall", "-I", inc, drv, "-o", GGML_DRIVER, "-L", HERE,
+                        "-lggml-ameva-b200", "-lac_runtime_b200", "-Wl,-rpath,$ORIGIN/../../../ameva-compute_b200"],
+                       check=True)
+    return GGML_PLUGIN
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_ggml_plugin(force="--force" in sys.argv) or "ggml plugin: no ggml headers (set GGML_INCLUDE_DIR)")
