@@ -1,5 +1,6 @@
 // Shared device helpers and the launcher contract of the built-in kernel registry (sm_100a only).
 #pragma once
+#include <cstring>
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -50,6 +51,33 @@ inline AcResult check_launch() {
 enum : uint32_t { DEV_STATUS_OK = 0, DEV_STATUS_WAIT_TIMEOUT = 1, DEV_STATUS_BAD_INDEX = 2 };
 
 #ifdef __CUDACC__
+// ---------------------------------------------------------------------------------------------------------------------
+// Programmatic dependent launch. The activation-quantize kernels let the next kernel of the stream be scheduled as soon
+// as all their CTAs have started (pdl_trigger); the mul_mat kernels are launched with the matching attribute
+// (launch_pdl) and call pdl_wait before they touch memory: it returns when the preceding grid has completed and its
+// writes are visible, so only launch latency and set-up overlap. After a kernel that never triggers, or a copy, the
+// dependent simply starts when that work is done.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Loads. Weights are streamed exactly once, so they bypass L1 (which is left to the activation vector every warp of the
 // SM re-reads).

@@ -505,6 +505,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;       // accumulator: columns 0 .. T-1
     const uint32_t tmem_a = tmem + kTokMax;     // weight operand stages: 32 columns each
+    pdl_wait();   // everything above overlapped the tail of the preceding kernel (the activation quantize)
     if (threadIdx.x == 0) trace(p, 1);
 
     // Every tile walks K from its own starting block (a multiple of 4 blocks = one scale group) and wraps around, so
@@ -1018,13 +1019,15 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem_bytes;
     cfg.stream = a.stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = pair ? 2 : 1;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = pair ? 2 : 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // see pdl_wait in the kernel
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
     const cudaError_t e = pair ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, true>, act_map, raw_map, scale_map,
                                                     out_maps, p)
                                : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, false>, act_map, raw_map, scale_map,

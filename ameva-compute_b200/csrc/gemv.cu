@@ -39,6 +39,7 @@ gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, co
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
+    pdl_wait();   // the quantized activations come from the preceding kernel
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -115,6 +116,7 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
+    pdl_wait();   // the quantized activations come from the preceding kernel
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -193,6 +195,7 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
+    pdl_wait();   // the quantized activations come from the preceding kernel
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -311,6 +314,7 @@ gemv_i2_s_kernel(const uint4* __restrict__ W, const int8_t* __restrict__ AQ, flo
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
+    pdl_wait();   // the quantized activations come from the preceding kernel
     int acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -385,7 +389,7 @@ static inline unsigned gemv_blocks(uint32_t N) {
 
 #define AMV_GEMV_CASE(KERNEL, MM, RR, DUMPV, ...)                                                   \
     case MM:                                                                                        \
-        KERNEL<MM, RR, DUMPV><<<gemv_blocks<RR>(N), kGemvThreads, 0, a.stream>>>(__VA_ARGS__);       \
+        launch_pdl(KERNEL<MM, RR, DUMPV>, dim3(gemv_blocks<RR>(N)), dim3(kGemvThreads), 0, a.stream, __VA_ARGS__); \
         break;
 
 #define AMV_GEMV_SWITCH(KERNEL, DUMPV, ...)                   \
@@ -455,13 +459,13 @@ static AcResult launch_mmvqb(const LaunchArgs& a) {
         // Measured on the 28672 x 8192 and 8192 x 28672 projections: one 32-byte chunk per row in flight per lane at 63
         // registers (four blocks = 32 warps per SM) beats two chunks at 96 registers (two blocks): 35 vs 39 us.
         if (M == 1u)
-            gemv_q4_K_kernel<1, 2, false, 1, 4><<<gemv_blocks<2>(N), kGemvThreads, 0, a.stream>>>(
-                (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3], dl,
-                sums, N, K, dst_stride);
+            launch_pdl(gemv_q4_K_kernel<1, 2, false, 1, 4>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
+                       (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
+                       dl, sums, N, K, dst_stride);
         else
-            gemv_q4_K_kernel<2, 2, false, 1, 3><<<gemv_blocks<2>(N), kGemvThreads, 0, a.stream>>>(
-                (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3], dl,
-                sums, N, K, dst_stride);
+            launch_pdl(gemv_q4_K_kernel<2, 2, false, 1, 3>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
+                       (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
+                       dl, sums, N, K, dst_stride);
         return check_launch();
     }
     AMV_GEMV_SWITCH(gemv_q4_K_kernel, DUMP, (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2],

@@ -213,6 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
         fence_barrier_init();
     }
     __syncthreads();
+    pdl_wait();   // the quantized activations come from the preceding kernel
     if (p.act_smem && threadIdx.x == 0) {   // one copy each for the quantized activations and their scales
         mbar_arrive_expect_tx(act_bar, p.aq_bytes + p.ad_bytes);
         bulk_load(smem_u32(s_aq), p.AQ, p.aq_bytes, act_bar);
@@ -335,7 +336,7 @@ static AcResult launch_one(const LaunchArgs& a, Params& p) {
     const uint32_t NB = (p.N + RB - 1) / RB;
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
     const uint32_t grid = NB < sms ? NB : sms;
-    gemv_bulk_kernel<TYPE, M, R><<<grid, kThreads, smem_bytes, a.stream>>>(p);
+    launch_pdl(gemv_bulk_kernel<TYPE, M, R>, dim3(grid), dim3(kThreads), smem_bytes, a.stream, p);
     return check_launch();
 }
 
