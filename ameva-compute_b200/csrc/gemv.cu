@@ -457,7 +457,9 @@ static AcResult launch_mmvqb(const LaunchArgs& a) {
     int32_t* sums = DUMP ? (int32_t*)a.ptr[5] : nullptr;
     if (!DUMP && M <= 2u) {
         // Measured on the 28672 x 8192 and 8192 x 28672 projections: one 32-byte chunk per row in flight per lane at 63
-        // registers (four blocks = 32 warps per SM) beats two chunks at 96 registers (two blocks): 35 vs 39 us.
+        // registers (four blocks = 32 warps per SM) beats two chunks at 96 registers (two blocks): 34.3 vs 39 us. Staging
+        // the stream through shared memory was also tried and is slower on this kernel: cp.async prefetch four steps
+        // ahead 41 us, bulk copies into a persistent CTA (gemv_bulk.cu) 45 us.
         if (M == 1u)
             launch_pdl(gemv_q4_K_kernel<1, 2, false, 1, 4>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
                        (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
