@@ -25,6 +25,20 @@ struct DstList {
     uint32_t n;
 };
 
+// Fused consumer of a one-row product (the reference's AmevaEpilogue, ggml-ameva.cpp:2272-2279, applied as in
+// shaders/ameva_mmvq.comp:158-176): besides dst[n] = v the kernel writes out[n] = v + e[n] (mode 1), silu(v) * e[n]
+// (mode 2: the product is the gate) or silu(e[n]) * v (mode 3: the product is the up projection). mode 0: nothing.
+struct Epi {
+    const float* e;
+    float* out;
+    uint32_t mode;
+};
+__device__ __forceinline__ float epilogue_value(uint32_t mode, float v, float e) {
+    if (mode == 1u) return v + e;
+    if (mode == 2u) return (v / (1.0f + expf(-v))) * e;
+    return (e / (1.0f + expf(-e))) * v;
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Q4_0 x Q8_0.  Q: uint4 [N][U] (byte j: element j low nibble, element j+16 high nibble), S: fp16 [N][U].
 // block: isum = sum nib*q - 8*sum(q); y += float(isum) * d_w * d_a
@@ -33,7 +47,7 @@ template <int M, int R, bool DUMP>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
                  const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
-                 uint32_t K, uint32_t dst_stride) {
+                 uint32_t K, uint32_t dst_stride, const Epi ep) {
     constexpr int UN = M <= 2 ? 4 : 2;
     const uint32_t U = K >> 5;
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
@@ -99,7 +113,10 @@ gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, co
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const float v = warp_sum(acc[r][m]);
-            if (lane == 0 && row0 + r < N) dst[(size_t)m * dst_stride + row0 + r] = v;
+            if (lane == 0 && row0 + r < N) {
+                dst[(size_t)m * dst_stride + row0 + r] = v;
+                if (M == 1 && ep.mode) ep.out[row0 + r] = epilogue_value(ep.mode, v, __ldg(ep.e + row0 + r));
+            }
         }
 }
 
@@ -110,7 +127,7 @@ template <int M, int R, bool DUMP>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
                  const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
-                 uint32_t K, uint32_t dst_stride) {
+                 uint32_t K, uint32_t dst_stride, const Epi ep) {
     constexpr int UN = M <= 2 ? 2 : 1;
     const uint32_t U = K >> 5;
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
@@ -173,7 +190,10 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const float v = warp_sum(acc[r][m]);
-            if (lane == 0 && row0 + r < N) dst[(size_t)m * dst_stride + row0 + r] = v;
+            if (lane == 0 && row0 + r < N) {
+                dst[(size_t)m * dst_stride + row0 + r] = v;
+                if (M == 1 && ep.mode) ep.out[row0 + r] = epilogue_value(ep.mode, v, __ldg(ep.e + row0 + r));
+            }
         }
 }
 
@@ -189,7 +209,7 @@ template <int M, int R, bool DUMP, int UNV = 0, int MINB = 1>
 __global__ void __launch_bounds__(kGemvThreads, MINB)
 gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
                  const uint8_t* __restrict__ AB, const DstList dl, int32_t* __restrict__ sums, uint32_t N, uint32_t K,
-                 uint32_t dst_stride) {
+                 uint32_t dst_stride, const Epi ep) {
     constexpr int UN = UNV ? UNV : (M <= 2 ? 2 : 1);
     const uint32_t B = K >> 8, C = K >> 6;  // blocks and 32-byte chunks per row
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
@@ -294,8 +314,10 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const float v = warp_sum(acc[r][m]);
-            if (lane == 0 && row0 + r < N)
+            if (lane == 0 && row0 + r < N) {
                 for (uint32_t o = 0; o < dl.n; ++o) dl.p[o][(size_t)m * dst_stride + row0 + r] = v;
+                if (M == 1 && ep.mode) ep.out[row0 + r] = epilogue_value(ep.mode, v, __ldg(ep.e + row0 + r));
+            }
         }
 }
 
@@ -409,7 +431,20 @@ static inline unsigned gemv_blocks(uint32_t N) {
 // ameva_mmvq_q4_0 / ameva_mmvq_q8_0 [_dump]:
 //   bindings 0 Q, 1 S, 2 AQ, 3 AD, 4 dst f32 [M][dst_stride] (, 5 block sums int32 [M][N][K/32])
 //   push {M (1..8), N, K, dst_stride}
-template <int QBYTES, bool DUMP>
+// Reads the epilogue arguments of the `_ep` entries: bindings e (f32, N) and out (f32, N) after dst, mode in the push
+// word after dst_stride; one activation row only.
+static AcResult read_epilogue(const LaunchArgs& a, uint32_t first_binding, uint32_t mode, uint32_t M, uint32_t N, Epi* ep) {
+    if (M != 1u) return AC_ERR_INVALID_SHAPE;
+    if (mode == 0u || mode > 3u) return AC_ERR_KERNEL_ARG_INVALID;
+    if (a.range[first_binding] < (uint64_t)N * 4u || a.range[first_binding + 1] < (uint64_t)N * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    ep->e = (const float*)a.ptr[first_binding];
+    ep->out = (float*)a.ptr[first_binding + 1];
+    ep->mode = mode;
+    return AC_SUCCESS;
+}
+
+template <int QBYTES, bool DUMP, bool EP = false>
 static AcResult launch_mmvq32(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
     if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
@@ -420,15 +455,24 @@ static AcResult launch_mmvq32(const LaunchArgs& a) {
         (DUMP && a.range[5] < (uint64_t)M * N * U * 4u))
         return AC_ERR_INVALID_BUFFER_SIZE;
     int32_t* sums = DUMP ? (int32_t*)a.ptr[5] : nullptr;
+    Epi ep = {nullptr, nullptr, 0u};
+    if (EP) {
+        const AcResult r = read_epilogue(a, 5, a.push[4], M, N, &ep);
+        if (r != AC_SUCCESS) return r;
+    }
     if (QBYTES == kQ40QBytes) {
         AMV_GEMV_SWITCH(gemv_q4_0_kernel, DUMP, (const uint4*)a.ptr[0], (const uint16_t*)a.ptr[1],
-                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride)
+                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride, ep)
     } else {
         AMV_GEMV_SWITCH(gemv_q8_0_kernel, DUMP, (const u32x8*)a.ptr[0], (const uint16_t*)a.ptr[1],
-                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride)
+                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride, ep)
     }
     return check_launch();
 }
+// ameva_mmvq_q4_0_ep / ameva_mmvq_q8_0_ep: bindings 0 Q, 1 S, 2 AQ, 3 AD, 4 dst, 5 e f32 [N], 6 out f32 [N];
+// push {1, N, K, dst_stride, mode (1 add, 2 silu(v) e, 3 silu(e) v)}
+AcResult launch_mmvq_q4_0_ep(const LaunchArgs& a) { return launch_mmvq32<kQ40QBytes, false, true>(a); }
+AcResult launch_mmvq_q8_0_ep(const LaunchArgs& a) { return launch_mmvq32<kQ80QBytes, false, true>(a); }
 AcResult launch_mmvq_q4_0(const LaunchArgs& a) { return launch_mmvq32<kQ40QBytes, false>(a); }
 AcResult launch_mmvq_q4_0_dump(const LaunchArgs& a) { return launch_mmvq32<kQ40QBytes, true>(a); }
 AcResult launch_mmvq_q8_0(const LaunchArgs& a) { return launch_mmvq32<kQ80QBytes, false>(a); }
@@ -436,7 +480,7 @@ AcResult launch_mmvq_q8_0_dump(const LaunchArgs& a) { return launch_mmvq32<kQ80Q
 
 // ameva_mmvqb_q4_K [_dump]:
 //   bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 dst (, 5 block sums int32 [M][N][K/256][2]);  push {M (1..8), N, K, dst_stride}
-template <bool DUMP, bool PEERS>
+template <bool DUMP, bool PEERS, bool EP = false>
 static AcResult launch_mmvqb(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
     const uint32_t n_peers = PEERS ? a.push[4] : 0u;
@@ -455,6 +499,11 @@ static AcResult launch_mmvqb(const LaunchArgs& a) {
         if (i < n_peers && a.range[5 + i] < need) return AC_ERR_INVALID_BUFFER_SIZE;
     }
     int32_t* sums = DUMP ? (int32_t*)a.ptr[5] : nullptr;
+    Epi ep = {nullptr, nullptr, 0u};
+    if (EP) {
+        const AcResult r = read_epilogue(a, 5, a.push[4], M, N, &ep);
+        if (r != AC_SUCCESS) return r;
+    }
     if (!DUMP && M <= 2u) {
         // Measured on the 28672 x 8192 and 8192 x 28672 projections: one 32-byte chunk per row in flight per lane at 63
         // registers (four blocks = 32 warps per SM) beats two chunks at 96 registers (two blocks): 34.3 vs 39 us. Staging
@@ -463,19 +512,21 @@ static AcResult launch_mmvqb(const LaunchArgs& a) {
         if (M == 1u)
             launch_pdl(gemv_q4_K_kernel<1, 2, false, 1, 4>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
                        (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
-                       dl, sums, N, K, dst_stride);
+                       dl, sums, N, K, dst_stride, ep);
         else
             launch_pdl(gemv_q4_K_kernel<2, 2, false, 1, 3>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
                        (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
-                       dl, sums, N, K, dst_stride);
+                       dl, sums, N, K, dst_stride, ep);
         return check_launch();
     }
     AMV_GEMV_SWITCH(gemv_q4_K_kernel, DUMP, (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2],
-                    (const uint8_t*)a.ptr[3], dl, sums, N, K, dst_stride)
+                    (const uint8_t*)a.ptr[3], dl, sums, N, K, dst_stride, ep)
     return check_launch();
 }
 AcResult launch_mmvqb_q4_K(const LaunchArgs& a) { return launch_mmvqb<false, false>(a); }
 AcResult launch_mmvqb_q4_K_dump(const LaunchArgs& a) { return launch_mmvqb<true, false>(a); }
+// ameva_mmvqb_q4_K_ep: bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 dst, 5 e, 6 out; push {1, N, K, dst_stride, mode}
+AcResult launch_mmvqb_q4_K_ep(const LaunchArgs& a) { return launch_mmvqb<false, false, true>(a); }
 // ameva_mmvqb_q4_K_mp: bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 local dst, 5..11 the same range of up to seven peers' outputs
 // (unused slots repeat binding 4); push {M, N, K, dst_stride, n_peers}: every output row is stored to every destination.
 AcResult launch_mmvqb_q4_K_mp(const LaunchArgs& a) { return launch_mmvqb<false, true>(a); }

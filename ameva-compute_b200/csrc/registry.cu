@@ -35,6 +35,9 @@ AcResult launch_mmvq_q4_0_dump(const LaunchArgs&);
 AcResult launch_mmvq_q8_0(const LaunchArgs&);
 AcResult launch_mmvq_q8_0_dump(const LaunchArgs&);
 AcResult launch_mmvqb_q4_K(const LaunchArgs&);
+AcResult launch_mmvq_q4_0_ep(const LaunchArgs&);
+AcResult launch_mmvq_q8_0_ep(const LaunchArgs&);
+AcResult launch_mmvqb_q4_K_ep(const LaunchArgs&);
 AcResult launch_mmvqb_q4_K_dump(const LaunchArgs&);
 AcResult launch_bitnet_gemv_i2_s(const LaunchArgs&);
 AcResult launch_bitnet_gemv_i2_s_acc(const LaunchArgs&);
@@ -62,6 +65,9 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvq_q8_0", 5, 16, {256, 1, 1}, launch_mmvq_q8_0},
     {"ameva_mmvq_q8_0_dump", 6, 16, {256, 1, 1}, launch_mmvq_q8_0_dump},
     {"ameva_mmvqb_q4_K", 5, 16, {256, 1, 1}, launch_mmvqb_q4_K},
+    {"ameva_mmvq_q4_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q4_0_ep},
+    {"ameva_mmvq_q8_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q8_0_ep},
+    {"ameva_mmvqb_q4_K_ep", 7, 20, {256, 1, 1}, launch_mmvqb_q4_K_ep},
     {"ameva_mmvqb_q4_K_dump", 6, 16, {256, 1, 1}, launch_mmvqb_q4_K_dump},
     {"bitnet_gemv_i2_s_l32w1", 4, 24, {32, 4, 1}, launch_bitnet_gemv_i2_s},
     {"bitnet_gemv_i2_s_l16w2", 4, 24, {16, 8, 1}, launch_bitnet_gemv_i2_s},

@@ -29,6 +29,9 @@ ROUND_NEAREST_EVEN, ROUND_TIES_AWAY = 0, 1
 Q8K_GGML, Q8K_AMEVA = 0, 1
 
 
+EPILOGUE_ADD, EPILOGUE_SWIGLU_GATE, EPILOGUE_SWIGLU_UP = 1, 2, 3
+
+
 class MulMatUnsupported(Exception):
     """The op is outside the contract; the message is the reason (the reference logs it once per (op, type, reason))."""
 
@@ -166,12 +169,17 @@ class MulMat:
         return None
 
     def record(self, batch: rt.Batch, x: rt.Buffer, dst: rt.Buffer, M: int, *, x_offset: int = 0, dst_offset: int = 0,
-               dst_stride: Optional[int] = None, quantize: bool = True, peers=None) -> None:
+               dst_stride: Optional[int] = None, quantize: bool = True, peers=None, epilogue=None) -> None:
         """x: fp32 [M][K] at byte x_offset; dst: fp32 rows dst_stride floats apart at byte dst_offset.
 
         peers: buffers of other ranks (opened with Context.open_ipc) that receive the same output range at the same
         offset and stride: the kernel's epilogue stores every tile to the local dst and to each peer, which is the
-        output exchange of a row-sharded projection fused into the mul_mat (no separate all-gather)."""
+        output exchange of a row-sharded projection fused into the mul_mat (no separate all-gather).
+
+        epilogue: (mode, e, out) with f32 buffers of N elements, M == 1 only: besides dst the kernel writes
+        out = dst + e (EPILOGUE_ADD), silu(dst) * e (EPILOGUE_SWIGLU_GATE) or silu(e) * dst (EPILOGUE_SWIGLU_UP), the
+        fusion the reference's graph engine applies to token-generation MUL_MATs (ggml-ameva.cpp:2272-2279,
+        4345-4378)."""
         if M <= 0 or M > self.max_m:
             raise MulMatUnsupported(f"M={M} outside 1..{self.max_m}")
         ctx, K, N = self.ctx, self.K, self.N
@@ -226,7 +234,9 @@ class MulMat:
                 batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}"),
                                [self.qbind, self.sbind, self.ah, (dst, dst_offset)], [M, N, K, dst_stride], grid)
             return
-        if streamed:
+        if epilogue is not None and (M != 1 or t == GGML_TYPE_I2_S or self.dump or peers):
+            raise MulMatUnsupported("the fused epilogue is built for one activation row of a Q4_0 / Q8_0 / Q4_K product")
+        if streamed and epilogue is None:
             # weight rows staged in shared memory by bulk copies, several stages ahead of the dot products; also carries
             # the output exchange of a row-sharded projection (every output row stored to every rank)
             self.path = "mmvs+peer-stores" if peers else "mmvs"
@@ -252,6 +262,11 @@ class MulMat:
                 if self.dump:
                     per_m = int(np.prod(self._sum_shape(1))) * 4
                     binds.append((self.sums, m0 * per_m))
+                if epilogue is not None:
+                    mode, e_buf, out_buf = epilogue
+                    name += "_ep"
+                    binds += [e_buf, out_buf]
+                    push = push + [int(mode)]
             for b in binds:
                 if isinstance(b, tuple) and b[1] % 64:
                     raise MulMatUnsupported(f"binding offset {b[1]} of {name} is not 64-byte aligned")

@@ -234,3 +234,33 @@ def test_replayed_batch_matches_one_shot_submit(ctx):
         v.destroy()
     mm.destroy()
     w.destroy()
+
+
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
+@pytest.mark.parametrize("mode", [qmm.EPILOGUE_ADD, qmm.EPILOGUE_SWIGLU_GATE, qmm.EPILOGUE_SWIGLU_UP])
+def test_fused_epilogue_of_a_one_row_product(ctx, t, mode):
+    """out = v + e, silu(v) * e or silu(e) * v written next to dst = v (shaders/ameva_mmvq.comp:158-176)."""
+    N, K = 1000, 1024
+    blocks, scale = make_weights(t, N, K, 31)
+    x = make_acts(1, K, 32)
+    e = np.random.default_rng(33).standard_normal(N).astype(np.float32)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    mm = qmm.MulMat(ctx, w, 1)
+    xb, dst, eb, ob, plain = ctx.buffer(data=x), ctx.buffer(N * 4), ctx.buffer(data=e), ctx.buffer(N * 4), ctx.buffer(N * 4)
+    ob.fill(0xFF)
+    mm.run(xb, plain, 1)
+    mm.run(xb, dst, 1, epilogue=(mode, eb, ob))
+    v = dst.read(np.float32)
+    assert np.array_equal(v, plain.read(np.float32))          # the product itself is unchanged
+    silu = lambda a: a / (np.float32(1.0) + np.exp(-a))
+    want = {1: v + e, 2: silu(v) * e, 3: silu(e) * v}[mode]
+    got = ob.read(np.float32)
+    assert np.allclose(got, want, rtol=2e-6, atol=1e-7), np.max(np.abs(got - want))
+    mm2, x2, d2 = qmm.MulMat(ctx, w, 2), ctx.buffer(data=make_acts(2, K, 1)), ctx.buffer(2 * N * 4)
+    with pytest.raises(qmm.MulMatUnsupported):   # one activation row only
+        mm2.run(x2, d2, 2, epilogue=(mode, eb, ob))
+    mm2.destroy()
+    for b in (xb, dst, eb, ob, plain, x2, d2):
+        b.destroy()
+    mm.destroy()
+    w.destroy()
