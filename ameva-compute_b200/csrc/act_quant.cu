@@ -21,6 +21,7 @@ template <bool WRITE_H>
 __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
                                                          uint32_t* __restrict__ ad, __half* __restrict__ ah, uint32_t M,
                                                          uint32_t K, uint32_t src_stride, uint32_t round_mode) {
+    pdl_wait();      // the activations may come from the kernel before (it let this one be scheduled early)
     pdl_trigger();   // the mul_mat behind this kernel may be scheduled; it waits for this grid before reading
     const uint32_t U = K >> 5;
     const uint64_t total = (uint64_t)M * U;
@@ -74,6 +75,7 @@ template <bool WRITE_H>
 __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
                                                          uint8_t* __restrict__ ab, __half* __restrict__ ah, uint32_t M,
                                                          uint32_t K, uint32_t src_stride, uint32_t mode) {
+    pdl_wait();      // the activations may come from the kernel before (it let this one be scheduled early)
     pdl_trigger();   // the mul_mat behind this kernel may be scheduled; it waits for this grid before reading
     const uint32_t B = K >> 8;
     const uint64_t total = (uint64_t)M * B;
@@ -177,6 +179,7 @@ __global__ void __launch_bounds__(256) bitnet_norm_q8_kernel(const float* __rest
                                                              uint32_t* __restrict__ q, uint32_t* __restrict__ act,
                                                              uint2* __restrict__ qeo, uint32_t dim, float eps,
                                                              uint32_t mode, uint32_t do_norm) {
+    pdl_wait();      // the activations may come from the kernel before (it let this one be scheduled early)
     pdl_trigger();   // the mul_mat behind this kernel may be scheduled; it waits for this grid before reading
     __shared__ float red[8];
     __shared__ int redi[8];
@@ -270,7 +273,7 @@ static AcResult launch_quant_a8_t(const LaunchArgs& a) {
     const uint64_t threads = (uint64_t)M * U * 8u;
     const uint64_t blocks = (threads + 255u) / 256u;
     if (blocks > 0x7FFFFFFFull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    quant_q8_0_kernel<WRITE_H><<<(unsigned)blocks, 256, 0, a.stream>>>(
+    launch_pdl(quant_q8_0_kernel<WRITE_H>, dim3((unsigned)blocks), dim3(256), 0, a.stream,
         (const float*)a.ptr[0], (int8_t*)a.ptr[1], (uint32_t*)a.ptr[2], WRITE_H ? (__half*)a.ptr[3] : nullptr, M, K,
         stride, round_mode);
     return check_launch();
@@ -290,7 +293,7 @@ static AcResult launch_quant_a8b_t(const LaunchArgs& a) {
         return AC_ERR_INVALID_BUFFER_SIZE;
     const uint64_t blocks = ((uint64_t)M * B * 32u + 255u) / 256u;
     if (blocks > 0x7FFFFFFFull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    quant_q8_K_kernel<WRITE_H><<<(unsigned)blocks, 256, 0, a.stream>>>(
+    launch_pdl(quant_q8_K_kernel<WRITE_H>, dim3((unsigned)blocks), dim3(256), 0, a.stream,
         (const float*)a.ptr[0], (int8_t*)a.ptr[1], (uint8_t*)a.ptr[2], WRITE_H ? (__half*)a.ptr[3] : nullptr, M, K,
         stride, mode);
     return check_launch();
@@ -310,7 +313,7 @@ AcResult launch_bitnet_norm_q8(const LaunchArgs& a) {
     uint2* qeo = a.range[6] >= (uint64_t)rows * dim * 2u ? (uint2*)a.ptr[6] : nullptr;
     float eps;
     memcpy(&eps, &a.push[1], 4);
-    bitnet_norm_q8_kernel<<<rows, 256, 0, a.stream>>>((const float*)a.ptr[0], (const float*)a.ptr[1],
+    launch_pdl(bitnet_norm_q8_kernel, dim3(rows), dim3(256), 0, a.stream, (const float*)a.ptr[0], (const float*)a.ptr[1],
                                                       (const float*)a.ptr[2], (float*)a.ptr[3], (uint32_t*)a.ptr[4],
                                                       (uint32_t*)a.ptr[5], qeo, dim, eps, mode, do_norm);
     return check_launch();

@@ -52,11 +52,11 @@ enum : uint32_t { DEV_STATUS_OK = 0, DEV_STATUS_WAIT_TIMEOUT = 1, DEV_STATUS_BAD
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------------------------------------------------
-// Programmatic dependent launch. The activation-quantize kernels let the next kernel of the stream be scheduled as soon
-// as all their CTAs have started (pdl_trigger); the mul_mat kernels are launched with the matching attribute
-// (launch_pdl) and call pdl_wait before they touch memory: it returns when the preceding grid has completed and its
-// writes are visible, so only launch latency and set-up overlap. After a kernel that never triggers, or a copy, the
-// dependent simply starts when that work is done.
+// Programmatic dependent launch. The quantize and mul_mat kernels are launched with the attribute (launch_pdl) and begin
+// with pdl_wait, which returns when the preceding grid of the stream has completed and its writes are visible, followed
+// by pdl_trigger, which lets the next kernel of the stream be scheduled once all CTAs of this grid have started. Nothing
+// touches memory before its wait, so only launch latency and set-up overlap. After a kernel that never triggers (the
+// peer barrier), or a copy, the dependent simply starts when that work is done.
 // ---------------------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

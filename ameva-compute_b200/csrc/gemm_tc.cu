@@ -506,6 +506,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     const uint32_t tmem = ctl->tmem_base;       // accumulator: columns 0 .. T-1
     const uint32_t tmem_a = tmem + kTokMax;     // weight operand stages: 32 columns each
     pdl_wait();   // everything above overlapped the tail of the preceding kernel (the activation quantize)
+    pdl_trigger();   // and the kernel behind this one may be scheduled (it waits for this grid before touching memory)
     if (threadIdx.x == 0) trace(p, 1);
 
     // Every tile walks K from its own starting block (a multiple of 4 blocks = one scale group) and wraps around, so

@@ -53,7 +53,8 @@ gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, co
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
-    pdl_wait();   // the quantized activations come from the preceding kernel
+    pdl_wait();      // the quantized activations come from the preceding kernel
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -133,7 +134,8 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
-    pdl_wait();   // the quantized activations come from the preceding kernel
+    pdl_wait();      // the quantized activations come from the preceding kernel
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -215,7 +217,8 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
-    pdl_wait();   // the quantized activations come from the preceding kernel
+    pdl_wait();      // the quantized activations come from the preceding kernel
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -336,7 +339,8 @@ gemv_i2_s_kernel(const uint4* __restrict__ W, const int8_t* __restrict__ AQ, flo
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
-    pdl_wait();   // the quantized activations come from the preceding kernel
+    pdl_wait();      // the quantized activations come from the preceding kernel
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
     int acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)

@@ -214,6 +214,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
     }
     __syncthreads();
     pdl_wait();   // the quantized activations come from the preceding kernel
+    pdl_trigger();
     if (p.act_smem && threadIdx.x == 0) {   // one copy each for the quantized activations and their scales
         mbar_arrive_expect_tx(act_bar, p.aq_bytes + p.ad_bytes);
         bulk_load(smem_u32(s_aq), p.AQ, p.aq_bytes, act_bar);
