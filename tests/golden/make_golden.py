@@ -9,7 +9,7 @@ Sources of truth, none of them this repository's own code:
   * the reference's own I2_S CPU dot kernel (adapters/bitnet/src/cpu/ggml_bitnet_mad.cpp, scalar branch), compiled by
     oracle/Makefile into oracle/_ref/libbitnet_ref.so and called on seeded inputs.
 
-Usage:  python tests/golden/make_golden.py [--reference /root/reference]
+Usage:  python tests/golden/make_golden.py [--reference <checkout of uno-km/ameva-compute>]
 """
 import argparse
 import hashlib
