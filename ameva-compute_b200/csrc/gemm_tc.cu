@@ -640,133 +640,178 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         float* stage_out = reinterpret_cast<float*>(sOut) + warp * 512u;
         bool ok = true;
         Ring sa(S), rr(C::kRawSlots), sr(kScaleSlots);
-        Seg sg;
-        uint32_t it = it_begin, nseg = 0;
         long long w_sc = 0, w_raw = 0, w_empty = 0, w_accum = 0;
-        while (ok && next_seg(it, it_end, KB, sg)) {
-            for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb) {
-                const uint32_t raw_last = min((kb | (C::kGroup - 1u)), sg.kb1 - 1u);   // last K block of this raw group
-                const uint32_t sc_last = min((kb | 3u), sg.kb1 - 1u);
-                if ((kb & 3u) == g) {
-                    const bool tr = threadIdx.x == 0u;
-                    if (tr) trace(p, 1024u + kb);
-                    if (C::kScales) ok = mbar_wait(sc_full + 8u * sr.idx, sr.phase, ctl, status, 0x800u | sr.idx, dg ? &w_sc : nullptr);
-                    ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x900u | rr.idx, dg ? &w_raw : nullptr);
-                    ok = ok && mbar_wait(empty + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx, dg ? &w_empty : nullptr);
-                    if (!ok) break;
-                    if (tr) trace(p, 260u + kb);
-                    tc_fence_after();
-                    uint32_t o[32];
-                    if (!(p.diag & 1u)) {
-                        const uint8_t* raw = sRaw + rr.idx * C::kRawBytes;
-                        const uint8_t* sc = sSc + sr.idx * kScaleBytes;
-                        dequant_half<TYPE>(raw, sc, r, 0u, kb, o);
-                        dequant_half<TYPE>(raw, sc, r, 1u, kb, o + 16);
-                    } else {
+
+        // One K block of segment sg: wait for its packed bytes, its scales and a free operand stage, convert, store to
+        // tensor memory, hand over. Every warp walks all K blocks (the ring counters advance per block); a group converts
+        // the blocks with kb % 4 == g.
+        auto dequant_step = [&](const Seg& sg, uint32_t kb) {
+            const uint32_t raw_last = min((kb | (C::kGroup - 1u)), sg.kb1 - 1u);   // last K block of this raw group
+            const uint32_t sc_last = min((kb | 3u), sg.kb1 - 1u);
+            if ((kb & 3u) == g) {
+                const bool tr = threadIdx.x == 0u;
+                if (tr) trace(p, 1024u + kb);
+                if (C::kScales) ok = mbar_wait(sc_full + 8u * sr.idx, sr.phase, ctl, status, 0x800u | sr.idx, dg ? &w_sc : nullptr);
+                ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x900u | rr.idx, dg ? &w_raw : nullptr);
+                ok = ok && mbar_wait(empty + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x400u | sa.idx, dg ? &w_empty : nullptr);
+                if (!ok) return;
+                if (tr) trace(p, 260u + kb);
+                tc_fence_after();
+                uint32_t o[32];
+                if (!(p.diag & 1u)) {
+                    const uint8_t* raw = sRaw + rr.idx * C::kRawBytes;
+                    const uint8_t* sc = sSc + sr.idx * kScaleBytes;
+                    dequant_half<TYPE>(raw, sc, r, 0u, kb, o);
+                    dequant_half<TYPE>(raw, sc, r, 1u, kb, o + 16);
+                } else {
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = 0u;
-                    }
-                    if (tr) trace(p, 1280u + kb);
-                    tmem_st32(tmem_a + ((q4 * 32u) << 16) + sa.idx * 32u, o);
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (PAIR && rank != 0u)
-                            mbar_arrive_cluster(full_remote + 8u * sa.idx);
-                        else
-                            mbar_arrive(full + 8u * sa.idx);
-                        mbar_arrive(raw_empty + 8u * rr.idx);   // a group meets every raw / scale stage at most once
-                        if (C::kScales) mbar_arrive(sc_empty + 8u * sr.idx);
-                        if (tr) trace(p, 390u + kb);
-                    }
+                    for (int i = 0; i < 32; ++i) o[i] = 0u;
                 }
-                sa.advance();
-                if (kb == raw_last) rr.advance();
-                if (C::kScales && kb == sc_last) sr.advance();
+                if (tr) trace(p, 1280u + kb);
+                tmem_st32(tmem_a + ((q4 * 32u) << 16) + sa.idx * 32u, o);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR && rank != 0u)
+                        mbar_arrive_cluster(full_remote + 8u * sa.idx);
+                    else
+                        mbar_arrive(full + 8u * sa.idx);
+                    mbar_arrive(raw_empty + 8u * rr.idx);   // a group meets every raw / scale stage at most once
+                    if (C::kScales) mbar_arrive(sc_empty + 8u * sr.idx);
+                    if (tr) trace(p, 390u + kb);
+                }
             }
-            // ---- epilogue of the segment: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows) and the 16-column
-            //      chunks w / 4, w / 4 + 4, ..., and sends each 32 x 16 piece out through its own 2 KB staging buffer and
-            //      one TMA store (or TMA add, for a partial sum that is not the first of its tile) per destination ----
+            sa.advance();
+            if (kb == raw_last) rr.advance();
+            if (C::kScales && kb == sc_last) sr.advance();
+        };
+
+        // Epilogue of segment number nseg: warp w reads TMEM lanes 32 (w % 4) .. +31 (its rows) and the 16-column chunks
+        // w / 4, w / 4 + 4, ... into registers, gives the accumulator back to the MMA issuer at once, and then sends each
+        // 32 x 16 piece out through its 2 KB staging buffer and one TMA store (or TMA add, for a partial sum that is not
+        // the first of its tile) per destination.
+        auto epilogue = [&](const Seg& sg, uint32_t nseg) {
             ok = ok && mbar_wait(accum, nseg & 1u, ctl, status, 0x500u, dg ? &w_accum : nullptr) && !ctl->abort;
             if (threadIdx.x == 0) trace(p, 520);
             __syncwarp();
             ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                tc_fence_after();
-                const uint32_t m0 = (sg.tile / p.row_units) * T;
-                const uint32_t n0 = ((sg.tile % p.row_units) * (PAIR ? 2u : 1u) + rank) * kRows;
-                const uint32_t out_row = n0 + eq * 32u + lane;
-                // Partial sums: `later` = the segments of this tile with higher K, which come first in the fixed order.
-                const bool split = sg.kb1 - sg.kb0 != KB;
-                uint32_t later = 0;
-                uint32_t* flag = nullptr;
-                if (split) {
-                    const uint32_t g_end = sg.tile * KB + sg.kb1, t_end = (sg.tile + 1u) * KB;
-                    later = sg.kb1 == KB ? 0u : (t_end - 1u) / p.iters - g_end / p.iters + 1u;
-                    flag = p.flags + ((sg.tile * 2u + rank) * (uint32_t)kDequantWarps + warp);
-                    if (later) {
-                        if (lane == 0) ok = flag_wait(flag, later, ctl, status, 0x540u);
-                        ok = __all_sync(0xffffffffu, ok);
-                        asm volatile("fence.proxy.async;" ::: "memory");
-                    }
-                }
-                for (uint32_t c = cq; c * 16u < T && ok; c += kDequantGroups) {
-                    uint32_t v[16];
-                    tmem_ld16(tmem + ((eq * 32u) << 16) + c * 16u, v);
+            constexpr uint32_t kPieces = kTokMax / 16 / kDequantGroups;   // at most four pieces per warp
+            const uint32_t m0 = (sg.tile / p.row_units) * T;
+            const uint32_t n0 = ((sg.tile % p.row_units) * (PAIR ? 2u : 1u) + rank) * kRows;
+            const uint32_t out_row = n0 + eq * 32u + lane;
+            // Partial sums: `later` = the segments of this tile with higher K, which come first in the fixed order.
+            const bool split = sg.kb1 - sg.kb0 != KB;
+            uint32_t later = 0;
+            uint32_t* flag = nullptr;
+            if (ok && split) {
+                const uint32_t g_end = sg.tile * KB + sg.kb1, t_end = (sg.tile + 1u) * KB;
+                later = sg.kb1 == KB ? 0u : (t_end - 1u) / p.iters - g_end / p.iters + 1u;
+                flag = p.flags + ((sg.tile * 2u + rank) * (uint32_t)kDequantWarps + warp);
+            }
+            bool waited = false, released = false;
+            // Two pieces at a time (register budget); the accumulator goes back to the MMA issuer as soon as the last
+            // piece of this warp is in registers.
 #pragma unroll
-                    for (uint32_t j = 0; j < 16; ++j) {
-                        const uint32_t m = m0 + c * 16u + j;
-                        float y;
-                        if (INT8) {
-                            const float total_scale =
-                                __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
-                            y = __fmul_rn((float)(int)v[j], total_scale);
-                        } else {
-                            y = __uint_as_float(v[j]);
-                        }
-                        if (p.tma_store)
-                            stage_out[j * 32u + lane] = y;
-                        else if (m < p.M && out_row < p.N && !(p.diag & 8u))
-                            p.dst[(size_t)m * p.dst_stride + out_row] = y;
+            for (uint32_t i0 = 0; i0 < kPieces; i0 += 2u) {
+                uint32_t v[2][16];
+                if (ok) {
+                    if (i0 == 0u) tc_fence_after();
+#pragma unroll
+                    for (uint32_t i = 0; i < 2u; ++i)
+                        if ((cq + (i0 + i) * kDequantGroups) * 16u < T)
+                            tmem_ld16(tmem + ((eq * 32u) << 16) + (cq + (i0 + i) * kDequantGroups) * 16u, v[i]);
+                }
+                if (!released && (!ok || (cq + (i0 + 2u) * kDequantGroups) * 16u >= T)) {   // nothing left to read
+                    released = true;
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {   // the accumulator may be overwritten by the next segment
+                        if (PAIR && rank != 0u)
+                            mbar_arrive_cluster(map_to_cta(acc_empty, 0u));
+                        else
+                            mbar_arrive(acc_empty);
                     }
-                    if (p.tma_store && !(p.diag & 8u)) {
-                        fence_async_smem();
-                        __syncwarp();
-                        // rows past M and columns past N are clipped by the tensor map; a piece entirely outside is skipped
-                        if (lane == 0 && n0 + eq * 32u < p.N && m0 + c * 16u < p.M) {
-                            for (uint32_t o = 0; o < p.n_out; ++o) {   // the same piece to every rank's output
-                                if (later)
-                                    tma_add_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u),
-                                               (int)(m0 + c * 16u));
-                                else
-                                    tma_store_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u),
-                                                 (int)(m0 + c * 16u));
+                }
+                if (ok && later && !waited) {   // the earlier partial sums of the tile are in place
+                    waited = true;
+                    if (lane == 0) ok = flag_wait(flag, later, ctl, status, 0x540u);
+                    ok = __all_sync(0xffffffffu, ok);
+                    asm volatile("fence.proxy.async;" ::: "memory");
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < 2u; ++i) {
+                    const uint32_t c = cq + (i0 + i) * kDequantGroups;
+                    if (ok && c * 16u < T) {
+#pragma unroll
+                        for (uint32_t j = 0; j < 16; ++j) {
+                            const uint32_t m = m0 + c * 16u + j;
+                            float y;
+                            if (INT8) {
+                                const float total_scale =
+                                    __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
+                                y = __fmul_rn((float)(int)v[i][j], total_scale);
+                            } else {
+                                y = __uint_as_float(v[i][j]);
                             }
-                            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // buffer reusable
+                            if (p.tma_store)
+                                stage_out[j * 32u + lane] = y;
+                            else if (m < p.M && out_row < p.N && !(p.diag & 8u))
+                                p.dst[(size_t)m * p.dst_stride + out_row] = y;
                         }
-                        __syncwarp();
+                        if (p.tma_store && !(p.diag & 8u)) {
+                            fence_async_smem();
+                            __syncwarp();
+                            // rows past M and columns past N are clipped by the tensor map; a piece entirely outside is
+                            // skipped
+                            if (lane == 0 && n0 + eq * 32u < p.N && m0 + c * 16u < p.M) {
+                                for (uint32_t o = 0; o < p.n_out; ++o) {   // the same piece to every rank's output
+                                    if (later)
+                                        tma_add_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u),
+                                                   (int)(m0 + c * 16u));
+                                    else
+                                        tma_store_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u),
+                                                     (int)(m0 + c * 16u));
+                                }
+                                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // buffer reusable
+                            }
+                            __syncwarp();
+                        }
                     }
                 }
-                if (split && ok && lane == 0) {
-                    if (sg.kb0 != 0u) {   // hand the tile on to the next lower K range once these writes are done
-                        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-                        __threadfence();
-                        asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(later + 1u) : "memory");
-                    } else {
-                        *flag = 0u;       // the tile is complete: leave the flag as the next launch expects it
-                    }
+            }
+            if (!ok) return;
+            if (split && lane == 0) {
+                if (sg.kb0 != 0u) {   // hand the tile on to the next lower K range once these writes are done
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                    __threadfence();
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(later + 1u) : "memory");
+                } else {
+                    *flag = 0u;       // the tile is complete: leave the flag as the next launch expects it
                 }
-                if (threadIdx.x == 0) trace(p, 521);
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {   // the accumulator may be overwritten by the next segment
-                if (PAIR && rank != 0u)
-                    mbar_arrive_cluster(map_to_cta(acc_empty, 0u));
-                else
-                    mbar_arrive(acc_empty);
+            if (threadIdx.x == 0) trace(p, 521);
+        };
+
+        // Segments in order. Before the epilogue of a segment the warps run ahead into the next one by up to S K blocks:
+        // those land in operand stages that the MMAs of the current segment free, so the waits cannot depend on the
+        // epilogue they precede, and the MMA issuer finds work as soon as the accumulator has been read out.
+        Seg cur, nxt;
+        uint32_t it = it_begin, nseg = 0;
+        bool have = next_seg(it, it_end, KB, cur);
+        uint32_t kb = have ? cur.kb0 : 0u;
+        while (have) {
+            for (; kb < cur.kb1 && ok; ++kb) dequant_step(cur, kb);
+            const bool have_next = next_seg(it, it_end, KB, nxt);
+            uint32_t kb_next = have_next ? nxt.kb0 : 0u;
+            if (have_next) {
+                const uint32_t ahead = min(nxt.kb1, nxt.kb0 + S);
+                for (; kb_next < ahead && ok; ++kb_next) dequant_step(nxt, kb_next);
             }
+            epilogue(cur, nseg);
             ++nseg;
+            cur = nxt;
+            kb = kb_next;
+            have = have_next;
         }
         if (p.tma_store && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         if (lane == 0 && q4 == 0u) {
