@@ -1017,8 +1017,12 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
         if (p.tiles >= (uint32_t)resident) {
             p.iters = (uint32_t)(((total + resident - 1) / resident + 3u) & ~3ull);
         } else {
+            // fewer tiles than units: cut every tile in up to four equal K ranges when that fits, else balance the
+            // linear space (a tile then spans two or three units; their partial sums are still combined in order)
             const uint32_t fit = (uint32_t)resident / p.tiles, split = fit < 4u ? fit : 4u;
-            p.iters = split >= 2u ? (((KB + split - 1) / split + 3u) & ~3u) : KB;
+            p.iters = split >= 2u ? (((KB + split - 1) / split + 3u) & ~3u)
+                                  : (uint32_t)(((total + resident - 1) / resident + 3u) & ~3ull);
+            if (p.iters < 8u) p.iters = KB < 8u ? KB : 8u;
         }
         p.units = (uint32_t)((total + p.iters - 1) / p.iters);
         if (p.iters != KB && p.units > (uint32_t)resident) {   // cannot happen by construction; never launch it

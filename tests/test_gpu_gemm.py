@@ -129,3 +129,10 @@ def test_gemm_linearity_property_full_size(ctx):
         b.destroy()
     mm.destroy()
     w.destroy()
+
+
+@pytest.mark.parametrize("t", [Q8_0, Q4_K])
+def test_gemm_tiles_between_half_and_all_units(ctx, t):
+    """45 tiles of 256 rows for ~74 resident CTA pairs: the linear (tile, K block) space is cut into equal ranges, so a
+    tile is produced by two or three units whose partial sums are combined in order (and identically on every run)."""
+    run_gemm(ctx, t, 256, 11520, 2048, seed=17, rows_checked=320)
