@@ -783,7 +783,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             if (split && lane == 0) {
                 if (sg.kb0 != 0u) {   // hand the tile on to the next lower K range once these writes are done
                     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-                    __threadfence();
+                    if (p.n_out > 1u)
+                        __threadfence_system();   // the other ranks' copies must be in place before the next range adds
+                    else
+                        __threadfence();
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(later + 1u) : "memory");
                 } else {
                     *flag = 0u;       // the tile is complete: leave the flag as the next launch expects it
@@ -981,9 +984,11 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     const uint32_t fixed = 1024u + kEpilogueBytes + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + 512u;
 
     // K ranges cut across tiles ("stream" launch, all units resident at once) need the TMA path for the partial sums, a
-    // K that is whole scale groups, exact integer results left alone (I2_S scales per token after the sum), flag space,
-    // and the local output only. Otherwise one tile per unit, as many waves as it takes.
-    bool stream = p.tma_store && !C::kInt8 && (KB & 3u) == 0u && n_peers == 0u && !(diag & 64u) && a.workspace;
+    // K that is whole scale groups, exact integer results left alone (I2_S scales per token after the sum) and flag
+    // space; with peer destinations the partial sums are added into every rank's output (remote adds over NVLink,
+    // ordered by the same local flags behind a system-scope fence). Otherwise one tile per unit, as many waves as it
+    // takes.
+    bool stream = p.tma_store && !C::kInt8 && (KB & 3u) == 0u && !(diag & 64u) && a.workspace;
     const uint32_t forced = diag >> 8;   // diagnostic: bits 8.. force the token tile
     // A single CTA stages all the token rows of its tile itself: 128 of them keep the stage ring deep enough.
     const uint32_t tok_max = pair ? (uint32_t)kTokMax : (uint32_t)kTokMax / 2u;
@@ -1016,6 +1021,10 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
         }
         if (p.tiles >= (uint32_t)resident) {
             p.iters = (uint32_t)(((total + resident - 1) / resident + 3u) & ~3ull);
+        } else if (n_peers) {
+            // few tiles and remote destinations: the ordered remote adds of the split tiles cost more than the idle
+            // units (measured at two ranks on 11008 x 4096 x 512: 77 us split against 62 us whole tiles)
+            p.iters = KB;
         } else {
             // fewer tiles than units: cut every tile in up to four equal K ranges when that fits, else balance the
             // linear space (a tile then spans two or three units; their partial sums are still combined in order)
