@@ -455,8 +455,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     // epilogue warps have read the accumulator out.
     const uint32_t full = smem_u32(bars), empty = full + 8u * 8u, raw_full = empty + 8u * 8u,
                    raw_empty = raw_full + 8u * 4u, sc_full = raw_empty + 8u * 4u, sc_empty = sc_full + 8u * 3u,
-                   accum = sc_empty + 8u * 3u, acc_empty = accum + 8u;
-    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 32);
+                   accum = sc_empty + 8u * 3u, acc_empty = accum + 8u, fwd = acc_empty + 8u;   // fwd: one per epilogue warp
+    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 32 + kDequantWarps);
 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t KB = p.K / C::kBlockK;
@@ -493,6 +493,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         }
         mbar_init(accum, 1u);
         mbar_init(acc_empty, kDequantWarps * (PAIR ? 2u : 1u));
+        for (uint32_t w = 0; w < (uint32_t)kDequantWarps; ++w) mbar_init(fwd + 8u * w, 1u);
         ctl->abort = 0u;
         fence_barrier_init();
     }
@@ -641,6 +642,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         bool ok = true;
         Ring sa(S), rr(C::kRawSlots), sr(kScaleSlots);
         long long w_sc = 0, w_raw = 0, w_empty = 0, w_accum = 0;
+        uint32_t fwd_phase = 0;   // parity of this warp's forwarding barrier
 
         // One K block of segment sg: wait for its packed bytes, its scales and a free operand stage, convert, store to
         // tensor memory, hand over. Every warp walks all K blocks (the ring counters advance per block); a group converts
@@ -708,6 +710,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 later = sg.kb1 == KB ? 0u : (t_end - 1u) / p.iters - g_end / p.iters + 1u;
                 flag = p.flags + ((sg.tile * 2u + rank) * (uint32_t)kDequantWarps + warp);
             }
+            // With other ranks' outputs as destinations the partial sums of a split tile stay in the local output; the
+            // segment that completes the tile forwards the finished pieces (below), so remote traffic stays one store.
+            const uint32_t n_direct = (split && p.n_out > 1u) ? 1u : p.n_out;
             bool waited = false, released = false;
             // Two pieces at a time (register budget); the accumulator goes back to the MMA issuer as soon as the last
             // piece of this warp is in registers.
@@ -764,7 +769,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                             // rows past M and columns past N are clipped by the tensor map; a piece entirely outside is
                             // skipped
                             if (lane == 0 && n0 + eq * 32u < p.N && m0 + c * 16u < p.M) {
-                                for (uint32_t o = 0; o < p.n_out; ++o) {   // the same piece to every rank's output
+                                for (uint32_t o = 0; o < n_direct; ++o) {   // the same piece to every rank's output
                                     if (later)
                                         tma_add_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u),
                                                    (int)(m0 + c * 16u));
@@ -783,13 +788,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             if (split && lane == 0) {
                 if (sg.kb0 != 0u) {   // hand the tile on to the next lower K range once these writes are done
                     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-                    if (p.n_out > 1u)
-                        __threadfence_system();   // the other ranks' copies must be in place before the next range adds
-                    else
-                        __threadfence();
+                    __threadfence();
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(later + 1u) : "memory");
                 } else {
                     *flag = 0u;       // the tile is complete: leave the flag as the next launch expects it
+                }
+            }
+            if (split && sg.kb0 == 0u && p.n_out > 1u && !(p.diag & 8u)) {
+                // This segment completed the tile: read each finished piece back from the local output (after the adds
+                // above have been performed) and store it to the other ranks.
+                if (lane == 0) {
+                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                    __threadfence();
+                }
+                __syncwarp();
+                for (uint32_t c = cq; c * 16u < T && ok; c += kDequantGroups) {
+                    if (n0 + eq * 32u < p.N && m0 + c * 16u < p.M) {
+                        if (lane == 0) {
+                            mbar_arrive_expect_tx(fwd + 8u * warp, 2048u);
+                            tma_load_2d(smem_u32(stage_out), &out_maps.m[0], fwd + 8u * warp, (int)(n0 + eq * 32u),
+                                        (int)(m0 + c * 16u));
+                            ok = mbar_wait(fwd + 8u * warp, fwd_phase, ctl, status, 0x560u);
+                            if (ok) {
+                                for (uint32_t o = 1; o < p.n_out; ++o)
+                                    tma_store_2d(&out_maps.m[o], smem_u32(stage_out), (int)(n0 + eq * 32u),
+                                                 (int)(m0 + c * 16u));
+                                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                            }
+                        }
+                        fwd_phase ^= 1u;
+                        ok = __shfl_sync(0xffffffffu, ok, 0);
+                    }
                 }
             }
             if (threadIdx.x == 0) trace(p, 521);
@@ -985,9 +1014,8 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
 
     // K ranges cut across tiles ("stream" launch, all units resident at once) need the TMA path for the partial sums, a
     // K that is whole scale groups, exact integer results left alone (I2_S scales per token after the sum) and flag
-    // space; with peer destinations the partial sums are added into every rank's output (remote adds over NVLink,
-    // ordered by the same local flags behind a system-scope fence). Otherwise one tile per unit, as many waves as it
-    // takes.
+    // space; with peer destinations the partial sums are combined in the local output and the segment that completes a
+    // tile forwards it to the other ranks. Otherwise one tile per unit, as many waves as it takes.
     bool stream = p.tma_store && !C::kInt8 && (KB & 3u) == 0u && !(diag & 64u) && a.workspace;
     const uint32_t forced = diag >> 8;   // diagnostic: bits 8.. force the token tile
     // A single CTA stages all the token rows of its tile itself: 128 of them keep the stage ring deep enough.
@@ -1021,10 +1049,6 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
         }
         if (p.tiles >= (uint32_t)resident) {
             p.iters = (uint32_t)(((total + resident - 1) / resident + 3u) & ~3ull);
-        } else if (n_peers) {
-            // few tiles and remote destinations: the ordered remote adds of the split tiles cost more than the idle
-            // units (measured at two ranks on 11008 x 4096 x 512: 77 us split against 62 us whole tiles)
-            p.iters = KB;
         } else {
             // fewer tiles than units: cut every tile in up to four equal K ranges when that fits, else balance the
             // linear space (a tile then spans two or three units; their partial sums are still combined in order)
