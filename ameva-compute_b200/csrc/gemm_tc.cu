@@ -429,7 +429,9 @@ __device__ __forceinline__ bool flag_wait(const uint32_t* flag, uint32_t want, C
 }
 
 // ---- the kernel -----------------------------------------------------------------------------------------------------
-template <int TYPE, bool PAIR>
+// PEERS: the launch has other ranks' outputs as destinations (kept out of the single-GPU instantiation, whose main loop
+// would otherwise pay for the forwarding code in registers).
+template <int TYPE, bool PAIR, bool PEERS = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap raw_map,
                const __grid_constant__ CUtensorMap scale_map, const __grid_constant__ OutMaps out_maps,
@@ -712,7 +714,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             }
             // With other ranks' outputs as destinations the partial sums of a split tile stay in the local output; the
             // segment that completes the tile forwards the finished pieces (below), so remote traffic stays one store.
-            const uint32_t n_direct = (split && p.n_out > 1u) ? 1u : p.n_out;
+            const uint32_t n_direct = PEERS ? (split ? 1u : p.n_out) : 1u;
             bool waited = false, released = false;
             // Two pieces at a time (register budget); the accumulator goes back to the MMA issuer as soon as the last
             // piece of this warp is in registers.
@@ -794,7 +796,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     *flag = 0u;       // the tile is complete: leave the flag as the next launch expects it
                 }
             }
-            if (split && sg.kb0 == 0u && p.n_out > 1u && !(p.diag & 8u)) {
+            if (PEERS && split && sg.kb0 == 0u && !(p.diag & 8u)) {
                 // This segment completed the tile: read each finished piece back from the local output (after the adds
                 // above have been performed) and store it to the other ranks.
                 if (lane == 0) {
@@ -972,9 +974,13 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     if (!enc) return AC_ERR_DRIVER_SYMBOL_MISSING;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<TYPE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_tc_kernel<TYPE, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemLimit) != cudaSuccess ||
-            cudaFuncSetAttribute(gemm_tc_kernel<TYPE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            cudaFuncSetAttribute(gemm_tc_kernel<TYPE, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemLimit) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_tc_kernel<TYPE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)kSmemLimit) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_tc_kernel<TYPE, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)kSmemLimit) != cudaSuccess) {
             cudaGetLastError();
             return AC_ERR_INVALID_WORK_GROUP_SIZE;
@@ -1111,10 +1117,13 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    const cudaError_t e = pair ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, true>, act_map, raw_map, scale_map,
-                                                    out_maps, p)
-                               : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, false>, act_map, raw_map, scale_map,
-                                                    out_maps, p);
+    cudaError_t e;
+    if (n_peers)
+        e = pair ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, true, true>, act_map, raw_map, scale_map, out_maps, p)
+                 : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, false, true>, act_map, raw_map, scale_map, out_maps, p);
+    else
+        e = pair ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, true, false>, act_map, raw_map, scale_map, out_maps, p)
+                 : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<TYPE, false, false>, act_map, raw_map, scale_map, out_maps, p);
     if (e != cudaSuccess) {
         cudaGetLastError();
         return AC_ERR_INVALID_WORK_GROUP_SIZE;
