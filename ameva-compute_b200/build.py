@@ -26,6 +26,8 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr",
 ]
+if os.environ.get("AMEVA_GEMM_DIAG") == "1":   # in-kernel diagnostics of the tensor-core GEMM (slower main loop)
+    NVCC_FLAGS.append("-DAMV_GEMM_DIAG=1")
 
 
 def _nvcc() -> str:

@@ -33,6 +33,12 @@
 #include "common.cuh"
 #include "sync_ptx.cuh"
 
+// Diagnostic build (-DAMV_GEMM_DIAG=1): per-stage switches, timeline stamps and wait accounting inside the kernel, driven
+// by the low bits of the diag push word. Off by default: the hooks cost registers in the main loop.
+#ifndef AMV_GEMM_DIAG
+#define AMV_GEMM_DIAG 0
+#endif
+
 namespace amv {
 namespace tc {
 
@@ -374,17 +380,17 @@ struct Params {
 
 // Diagnostic timeline (diag bit 4): CTA (0,0) writes SM clock stamps into the output buffer instead of results.
 __device__ __forceinline__ void trace(const Params& p, uint32_t slot) {
-    if ((p.diag & 16u) && blockIdx.x == 0 && blockIdx.y == 0)
+    if (AMV_GEMM_DIAG && (p.diag & 16u) && blockIdx.x == 0 && blockIdx.y == 0)
         reinterpret_cast<long long*>(p.dst)[slot] = clock64();
 }
 
 __device__ __forceinline__ void trace_val(const Params& p, uint32_t slot, long long v) {
-    if ((p.diag & 16u) && blockIdx.x == 0 && blockIdx.y == 0) reinterpret_cast<long long*>(p.dst)[slot] = v;
+    if (AMV_GEMM_DIAG && (p.diag & 16u) && blockIdx.x == 0 && blockIdx.y == 0) reinterpret_cast<long long*>(p.dst)[slot] = v;
 }
 
 // With the same bit every CTA also records the global nanosecond timer at its start and end (slots 2048 + 2 cta, + 1).
 __device__ __forceinline__ void trace_cta(const Params& p, uint32_t which) {
-    if (p.diag & 16u) {
+    if (AMV_GEMM_DIAG && (p.diag & 16u)) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         reinterpret_cast<unsigned long long*>(p.dst)[2048u + 2u * (blockIdx.y * gridDim.x + blockIdx.x) + which] = t;
@@ -437,6 +443,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                const __grid_constant__ CUtensorMap scale_map, const __grid_constant__ OutMaps out_maps,
                const Params p) {
     using C = Cfg<TYPE>;
+    const uint32_t kdiag = AMV_GEMM_DIAG ? p.diag : 0u;   // the diagnostic switches exist only in a diagnostic build
     constexpr bool INT8 = C::kInt8;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -474,7 +481,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     }
     const uint32_t it_begin = unit * p.iters, it_end = min(it_begin + p.iters, p.tiles * KB);
     uint32_t* status = p.status;
-    const bool dg = (p.diag & 16u) != 0u;   // diagnostic run: account the cycles spent in barrier waits
+    const bool dg = (kdiag & 16u) != 0u;   // diagnostic run: account the cycles spent in barrier waits
     if (threadIdx.x == 0) {
         trace(p, 0);
         trace_cta(p, 0);
@@ -529,7 +536,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, st.advance()) {
                     ok = mbar_wait(empty + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x100u | st.idx, dg ? &w_empty : nullptr);
                     if (!ok) break;
-                    if (p.diag & 2u) {   // diagnostic: no activation traffic
+                    if (kdiag & 2u) {   // diagnostic: no activation traffic
                         if (rank == 0u) mbar_arrive(full + 8u * st.idx);
                         continue;
                     }
@@ -548,7 +555,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 }
             }
             trace_val(p, 1604u, w_empty);
-            if (ctl->abort && !(p.diag & 2u) && rank == 0u) {   // let the copies already requested land before leaving
+            if (ctl->abort && !(kdiag & 2u) && rank == 0u) {   // let the copies already requested land before leaving
                 for (uint32_t i = issued > S ? issued - S : 0; i < issued; ++i)
                     mbar_wait(full + 8u * (i % S), (i / S) & 1u, ctl, status, 0x180u);
             }
@@ -613,7 +620,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     const uint64_t db = make_smem_desc(smem_u32(sB + st.idx * b_bytes));
                     const uint32_t ta = tmem_a + st.idx * 32u;
                     const long long ti = dg ? clock64() : 0;
-                    if (!(p.diag & 4u)) {
+                    if (!(kdiag & 4u)) {
 #pragma unroll
                         for (uint32_t k = 0; k < 4; ++k)   // 32 bytes of K per instruction: 8 TMEM columns / +2 desc units
                             umma_ts<INT8, PAIR>(tmem, ta + 8u * k, db + 2u * k, idesc, (uint32_t)(kb != sg.kb0 || k != 0u));
@@ -662,7 +669,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 if (tr) trace(p, 260u + kb);
                 tc_fence_after();
                 uint32_t o[32];
-                if (!(p.diag & 1u)) {
+                if (!(kdiag & 1u)) {
                     const uint8_t* raw = sRaw + rr.idx * C::kRawBytes;
                     const uint8_t* sc = sSc + sr.idx * kScaleBytes;
                     dequant_half<TYPE>(raw, sc, r, 0u, kb, o);
@@ -762,10 +769,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                             }
                             if (p.tma_store)
                                 stage_out[j * 32u + lane] = y;
-                            else if (m < p.M && out_row < p.N && !(p.diag & 8u))
+                            else if (m < p.M && out_row < p.N && !(kdiag & 8u))
                                 p.dst[(size_t)m * p.dst_stride + out_row] = y;
                         }
-                        if (p.tma_store && !(p.diag & 8u)) {
+                        if (p.tma_store && !(kdiag & 8u)) {
                             fence_async_smem();
                             __syncwarp();
                             // rows past M and columns past N are clipped by the tensor map; a piece entirely outside is
@@ -796,7 +803,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     *flag = 0u;       // the tile is complete: leave the flag as the next launch expects it
                 }
             }
-            if (PEERS && split && sg.kb0 == 0u && !(p.diag & 8u)) {
+            if (PEERS && split && sg.kb0 == 0u && !(kdiag & 8u)) {
                 // This segment completed the tile: read each finished piece back from the local output (after the adds
                 // above have been performed) and store it to the other ranks.
                 if (lane == 0) {
@@ -997,6 +1004,7 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     p.K = K;
     p.dst_stride = dst_stride;
     p.w_scale = w_scale;
+    if (!AMV_GEMM_DIAG && (diag & 31u)) return AC_ERR_FEATURE_NOT_SUPPORTED;   // needs the diagnostic build
     p.diag = diag & 31u;   // bits 5 (single CTAs) and 6 (one tile per unit) are host-side choices
     p.status = a.status;
     p.flags = a.workspace;
