@@ -60,7 +60,7 @@ WORKLOADS = {
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (bytes)
-TRAFFIC = {"cfg2": 58067200, "cfg5-up-m1": 136777216}
+TRAFFIC = {"cfg2": 58200000, "cfg5-up-m1": 136777216}
 GEMV_MAX_M = 8
 
 
