@@ -8,6 +8,7 @@
 //   bitnet_norm_q8   src/shaders/bitnet_norm_q8.comp:51-123                        (norm + per-token absmax)
 #include <cstring>
 
+#include "act_quant.cuh"
 #include "common.cuh"
 
 namespace amv {
@@ -32,26 +33,12 @@ __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict
     const uint32_t u = live ? (uint32_t)(gi - (uint64_t)m * U) : 0u;
     float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
     if (live) x = *reinterpret_cast<const float4*>(src + (size_t)m * src_stride + 32u * u + 4u * sub);
-    float amax = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float d = __fdiv_rn(amax, 127.0f);
-    const float id = d != 0.0f ? __fdiv_rn(1.0f, d) : 0.0f;
-    int q[4];
-    const float v[4] = {__fmul_rn(x.x, id), __fmul_rn(x.y, id), __fmul_rn(x.z, id), __fmul_rn(x.w, id)};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        int r = round_mode ? (int)roundf(v[i]) : __float2int_rn(v[i]);
-        q[i] = max(-127, min(127, r));
-    }
-    int s = q[0] + q[1] + q[2] + q[3];
-#pragma unroll
-    for (int o = 4; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    int q[4], s;
+    float d;
+    quant_unit_q8_0(x, round_mode, q, d, s);
     if (live) {
-        const uint32_t w = (uint32_t)(q[0] & 0xFF) | ((uint32_t)(q[1] & 0xFF) << 8) | ((uint32_t)(q[2] & 0xFF) << 16) |
-                           ((uint32_t)(q[3] & 0xFF) << 24);
-        reinterpret_cast<uint32_t*>(aq + (size_t)m * K + 32u * u)[sub] = w;
-        if (sub == 0) ad[(size_t)m * U + u] = (uint32_t)f2h(d) | ((uint32_t)(s & 0xFFFF) << 16);
+        reinterpret_cast<uint32_t*>(aq + (size_t)m * K + 32u * u)[sub] = pack_q4(q);
+        if (sub == 0) ad[(size_t)m * U + u] = scale_word_q8_0(d, s);
         if (WRITE_H) {   // the tensor-core operand: fp16(q * d) with d the fp16-rounded scale the dot product uses
             const float dh = h2f(f2h(d));
             const __half2 h01 = __floats2half2_rn((float)q[0] * dh, (float)q[1] * dh);
@@ -88,46 +75,9 @@ __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict
     const float4 x0 = *reinterpret_cast<const float4*>(p);
     const float4 x1 = *reinterpret_cast<const float4*>(p + 4);
     const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-    float amax = 0.0f, mx = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const float ax = fabsf(x[i]);
-        if (ax > amax) {
-            amax = ax;
-            mx = x[i];
-        }
-    }
-    // the first element of largest magnitude wins: lower lanes hold lower indices, so on equal magnitude keep the
-    // value that came from the lower lane
-    uint32_t owner = lane;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const float oa = __shfl_xor_sync(0xffffffffu, amax, o);
-        const float om = __shfl_xor_sync(0xffffffffu, mx, o);
-        const uint32_t oo = __shfl_xor_sync(0xffffffffu, owner, o);
-        if (oa > amax || (oa == amax && oo < owner)) {
-            amax = oa;
-            mx = om;
-            owner = oo;
-        }
-    }
     int q[8];
     float d;
-    if (amax == 0.0f) {
-        d = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = 0;
-    } else if (mode == 0u) {
-        const float iscale = __fdiv_rn(-127.0f, mx);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = min(127, __float2int_rn(__fmul_rn(iscale, x[i])));
-        d = __fdiv_rn(1.0f, iscale);
-    } else {
-        d = __fdiv_rn(amax, 127.0f);
-        const float id = __fdiv_rn(1.0f, d);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] = max(-127, min(127, __float2int_rn(__fmul_rn(x[i], id))));
-    }
+    quant_block_q8_K(x, mode, lane, q, d);
     int s = 0;
     uint32_t w0 = 0, w1 = 0;
 #pragma unroll

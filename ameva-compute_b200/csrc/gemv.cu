@@ -11,6 +11,7 @@
 // ameva_mmqb.comp:10-16. With DUMP the exact per-block int32 sums are also written (parity evidence; not a fast path).
 #include <cstring>
 
+#include "act_quant.cuh"
 #include "common.cuh"
 
 namespace amv {
@@ -39,22 +40,88 @@ __device__ __forceinline__ float epilogue_value(uint32_t mode, float v, float e)
     return (e / (1.0f + expf(-e))) * v;
 }
 
+// Activation loads: from global memory through L1 (quantized by the kernel before), or from this CTA's shared memory when
+// the kernel quantized the row itself (FQ).
+template <bool SH, typename T>
+__device__ __forceinline__ T ld_act(const void* p) {
+    if constexpr (SH) return *reinterpret_cast<const T*>(p);
+    else return __ldg(reinterpret_cast<const T*>(p));
+}
+
+// FQ kernels (one activation row): every CTA first quantizes the fp32 row X[0..K) into its own shared memory, with the
+// arithmetic of the stand-alone quantize kernels, and takes the int8 values and scales from there: one launch per
+// projection instead of two. K bytes of values, then the per-32 scale words or the per-256 48-byte records.
+extern __shared__ __align__(16) uint8_t fq_smem[];
+
+__device__ __forceinline__ void fq_quantize_q8_0(const float* __restrict__ X, uint32_t K, uint32_t round_mode) {
+    const uint32_t U = K >> 5, sub = threadIdx.x & 7u;
+    uint32_t* s_ad = reinterpret_cast<uint32_t*>(fq_smem + K);
+    for (uint32_t base = 0; base < U; base += kGemvThreads / 8) {   // 32 units per pass, whole warps stay together
+        const uint32_t u = base + (threadIdx.x >> 3);
+        const bool live = u < U;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live) x = __ldg(reinterpret_cast<const float4*>(X + 32u * u + 4u * sub));
+        int q[4], s;
+        float d;
+        quant_unit_q8_0(x, round_mode, q, d, s);
+        if (live) {
+            reinterpret_cast<uint32_t*>(fq_smem + 32u * u)[sub] = pack_q4(q);
+            if (sub == 0) s_ad[u] = scale_word_q8_0(d, s);
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ void fq_quantize_q8_K(const float* __restrict__ X, uint32_t K, uint32_t mode) {
+    const uint32_t B = K >> 8, lane = threadIdx.x & 31u;
+    uint8_t* s_ab = fq_smem + K;
+    for (uint32_t b = threadIdx.x >> 5; b < B; b += kGemvWarps) {   // one warp per 256-block
+        const float* p = X + 256u * b + 8u * lane;
+        const float4 x0 = __ldg(reinterpret_cast<const float4*>(p)), x1 = __ldg(reinterpret_cast<const float4*>(p + 4));
+        const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        int q[8];
+        float d;
+        quant_block_q8_K(x, mode, lane, q, d);
+        int s = 0;
+        uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            s += q[i] + q[i + 4];
+            w0 |= (uint32_t)(q[i] & 0xFF) << (8 * i);
+            w1 |= (uint32_t)(q[i + 4] & 0xFF) << (8 * i);
+        }
+        *reinterpret_cast<uint2*>(fq_smem + 256u * b + 8u * lane) = make_uint2(w0, w1);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);   // lanes 2j, 2j+1 -> 16-element group j
+        uint8_t* blk = s_ab + (size_t)b * kABBytes;
+        if ((lane & 1u) == 0u) reinterpret_cast<int16_t*>(blk)[lane >> 1] = (int16_t)s;
+        if (lane == 0) *reinterpret_cast<float*>(blk + 32) = d;
+    }
+    __syncthreads();
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Q4_0 x Q8_0.  Q: uint4 [N][U] (byte j: element j low nibble, element j+16 high nibble), S: fp16 [N][U].
 // block: isum = sum nib*q - 8*sum(q); y += float(isum) * d_w * d_a
 // ---------------------------------------------------------------------------------------------------------------------
-template <int M, int R, bool DUMP>
+template <int M, int R, bool DUMP, bool FQ = false>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
                  const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
-                 uint32_t K, uint32_t dst_stride, const Epi ep) {
+                 uint32_t K, uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+    static_assert(!FQ || (M == 1 && !DUMP), "the fused quantize serves one activation row");
     constexpr int UN = M <= 2 ? 4 : 2;
     const uint32_t U = K >> 5;
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
-    if (row0 >= N) return;
-    pdl_wait();      // the quantized activations come from the preceding kernel
+    if (!FQ && row0 >= N) return;
+    pdl_wait();      // the activations come from the preceding kernel
     pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
+    if constexpr (FQ) {
+        fq_quantize_q8_0(X, K, qmode);
+        if (row0 >= N) return;
+        AQ = reinterpret_cast<const int8_t*>(fq_smem);
+        AD = reinterpret_cast<const uint32_t*>(fq_smem + K);
+    }
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -85,8 +152,8 @@ gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, co
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
                     const int8_t* ap = AQ + (size_t)m * K + 32u * u;
-                    const uint4 a0 = ld_cached_u4(ap), a1 = ld_cached_u4(ap + 16);
-                    const uint32_t adw = __ldg(AD + (size_t)m * U + u);
+                    const uint4 a0 = ld_act<FQ, uint4>(ap), a1 = ld_act<FQ, uint4>(ap + 16);
+                    const uint32_t adw = ld_act<FQ, uint32_t>(AD + (size_t)m * U + u);
                     const float da = h2f((uint16_t)(adw & 0xFFFFu));
                     const int sa = (int)(int16_t)(adw >> 16);
 #pragma unroll
@@ -124,18 +191,25 @@ gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, co
 // ---------------------------------------------------------------------------------------------------------------------
 // Q8_0 x Q8_0.  Q: 32 int8 per unit (256-bit loads), S: fp16 [N][U].  y += float(isum) * (d_w * d_a)
 // ---------------------------------------------------------------------------------------------------------------------
-template <int M, int R, bool DUMP>
+template <int M, int R, bool DUMP, bool FQ = false>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
                  const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
-                 uint32_t K, uint32_t dst_stride, const Epi ep) {
+                 uint32_t K, uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+    static_assert(!FQ || (M == 1 && !DUMP), "the fused quantize serves one activation row");
     constexpr int UN = M <= 2 ? 2 : 1;
     const uint32_t U = K >> 5;
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
-    if (row0 >= N) return;
-    pdl_wait();      // the quantized activations come from the preceding kernel
+    if (!FQ && row0 >= N) return;
+    pdl_wait();      // the activations come from the preceding kernel
     pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
+    if constexpr (FQ) {
+        fq_quantize_q8_0(X, K, qmode);
+        if (row0 >= N) return;
+        AQ = reinterpret_cast<const int8_t*>(fq_smem);
+        AD = reinterpret_cast<const uint32_t*>(fq_smem + K);
+    }
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -166,8 +240,8 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
                     const int8_t* ap = AQ + (size_t)m * K + 32u * u;
-                    const uint4 a0 = ld_cached_u4(ap), a1 = ld_cached_u4(ap + 16);
-                    const float da = h2f((uint16_t)(__ldg(AD + (size_t)m * U + u) & 0xFFFFu));
+                    const uint4 a0 = ld_act<FQ, uint4>(ap), a1 = ld_act<FQ, uint4>(ap + 16);
+                    const float da = h2f((uint16_t)(ld_act<FQ, uint32_t>(AD + (size_t)m * U + u) & 0xFFFFu));
 #pragma unroll
                     for (int r = 0; r < R; ++r) {
                         const u32x8& w = wq[i][r];
@@ -207,18 +281,25 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
 //   y += (d*d_a)*float(isum) - (dmin*d_a)*float(mpart)          (block-integer form, ameva_mmqb.comp:10-16)
 // The four lanes of a block are an aligned lane group (DUMP reduces over them).
 // ---------------------------------------------------------------------------------------------------------------------
-template <int M, int R, bool DUMP, int UNV = 0, int MINB = 1>
+template <int M, int R, bool DUMP, int UNV = 0, int MINB = 1, bool FQ = false>
 __global__ void __launch_bounds__(kGemvThreads, MINB)
 gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
                  const uint8_t* __restrict__ AB, const DstList dl, int32_t* __restrict__ sums, uint32_t N, uint32_t K,
-                 uint32_t dst_stride, const Epi ep) {
+                 uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+    static_assert(!FQ || (M == 1 && !DUMP), "the fused quantize serves one activation row");
     constexpr int UN = UNV ? UNV : (M <= 2 ? 2 : 1);
     const uint32_t B = K >> 8, C = K >> 6;  // blocks and 32-byte chunks per row
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
-    if (row0 >= N) return;
-    pdl_wait();      // the quantized activations come from the preceding kernel
+    if (!FQ && row0 >= N) return;
+    pdl_wait();      // the activations come from the preceding kernel
     pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
+    if constexpr (FQ) {
+        fq_quantize_q8_K(X, K, qmode);
+        if (row0 >= N) return;
+        AQ = reinterpret_cast<const int8_t*>(fq_smem);
+        AB = fq_smem + K;
+    }
     float acc[R][M];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -272,11 +353,11 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
 #pragma unroll
                 for (int m = 0; m < M; ++m) {
                     const int8_t* ap = AQ + (size_t)m * K + 64u * c;
-                    const uint4 a0 = ld_cached_u4(ap), a1 = ld_cached_u4(ap + 16), a2 = ld_cached_u4(ap + 32),
-                                a3 = ld_cached_u4(ap + 48);
+                    const uint4 a0 = ld_act<FQ, uint4>(ap), a1 = ld_act<FQ, uint4>(ap + 16),
+                                a2 = ld_act<FQ, uint4>(ap + 32), a3 = ld_act<FQ, uint4>(ap + 48);
                     const uint8_t* ab = AB + ((size_t)m * B + b) * kABBytes;
-                    const uint2 bs = __ldg(reinterpret_cast<const uint2*>(ab + 8u * k));   // bsums[4k .. 4k+3]
-                    const float da = __ldg(reinterpret_cast<const float*>(ab + 32));
+                    const uint2 bs = ld_act<FQ, uint2>(ab + 8u * k);   // bsums[4k .. 4k+3]
+                    const float da = ld_act<FQ, float>(ab + 32);
                     const int bs_lo = (int)(int16_t)(bs.x & 0xFFFFu) + (int)(int16_t)(bs.x >> 16);
                     const int bs_hi = (int)(int16_t)(bs.y & 0xFFFFu) + (int)(int16_t)(bs.y >> 16);
                     const uint32_t al[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
@@ -466,10 +547,10 @@ static AcResult launch_mmvq32(const LaunchArgs& a) {
     }
     if (QBYTES == kQ40QBytes) {
         AMV_GEMV_SWITCH(gemv_q4_0_kernel, DUMP, (const uint4*)a.ptr[0], (const uint16_t*)a.ptr[1],
-                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride, ep)
+                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride, ep, nullptr, 0u)
     } else {
         AMV_GEMV_SWITCH(gemv_q8_0_kernel, DUMP, (const u32x8*)a.ptr[0], (const uint16_t*)a.ptr[1],
-                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride, ep)
+                        (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3], (float*)a.ptr[4], sums, N, K, dst_stride, ep, nullptr, 0u)
     }
     return check_launch();
 }
@@ -516,15 +597,15 @@ static AcResult launch_mmvqb(const LaunchArgs& a) {
         if (M == 1u)
             launch_pdl(gemv_q4_K_kernel<1, 2, false, 1, 4>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
                        (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
-                       dl, sums, N, K, dst_stride, ep);
+                       dl, sums, N, K, dst_stride, ep, nullptr, 0u);
         else
             launch_pdl(gemv_q4_K_kernel<2, 2, false, 1, 3>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
                        (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
-                       dl, sums, N, K, dst_stride, ep);
+                       dl, sums, N, K, dst_stride, ep, nullptr, 0u);
         return check_launch();
     }
     AMV_GEMV_SWITCH(gemv_q4_K_kernel, DUMP, (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2],
-                    (const uint8_t*)a.ptr[3], dl, sums, N, K, dst_stride, ep)
+                    (const uint8_t*)a.ptr[3], dl, sums, N, K, dst_stride, ep, nullptr, 0u)
     return check_launch();
 }
 AcResult launch_mmvqb_q4_K(const LaunchArgs& a) { return launch_mmvqb<false, false>(a); }
@@ -534,6 +615,50 @@ AcResult launch_mmvqb_q4_K_ep(const LaunchArgs& a) { return launch_mmvqb<false, 
 // ameva_mmvqb_q4_K_mp: bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 local dst, 5..11 the same range of up to seven peers' outputs
 // (unused slots repeat binding 4); push {M, N, K, dst_stride, n_peers}: every output row is stored to every destination.
 AcResult launch_mmvqb_q4_K_mp(const LaunchArgs& a) { return launch_mmvqb<false, true>(a); }
+
+// ameva_mmvq_q4_0_fq / ameva_mmvq_q8_0_fq / ameva_mmvqb_q4_K_fq: the activation quantize fused into the GEMV of ONE
+// activation row (one launch per projection instead of two; every CTA quantizes the row into its shared memory).
+//   bindings 0 Q, 1 S, 2 x f32 [K] (16-byte aligned), 3 dst f32 [N]
+//   push {N, K, quantize mode: the round_mode of ameva_quant_a8 (Q4_0 / Q8_0) or the mode of ameva_quant_a8b (Q4_K)}
+// The bits of dst are those of the two-kernel sequence. K is limited to 16384 (the row and its scales live in shared
+// memory, and every CTA repeats the quantize).
+constexpr uint32_t kFusedQuantMaxK = 16384u;
+template <int TYPE>   // 0 Q4_0, 1 Q8_0, 2 Q4_K
+static AcResult launch_fq(const LaunchArgs& a) {
+    const uint32_t N = a.push[0], K = a.push[1], qmode = a.push[2];
+    const uint32_t kmask = TYPE == 2 ? 255u : 31u;
+    if (N == 0 || K == 0 || (K & kmask) || qmode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
+    if (K > kFusedQuantMaxK) return AC_ERR_INVALID_SHAPE;
+    const uint64_t units = TYPE == 2 ? (K >> 8) : (K >> 5);
+    const uint64_t qb = TYPE == 0 ? kQ40QBytes : TYPE == 1 ? kQ80QBytes : kQ4KQBytes, sb = TYPE == 2 ? kQ4KSBytes : 2u;
+    if (a.range[0] < (uint64_t)N * units * qb || a.range[1] < (uint64_t)N * units * sb || a.range[2] < (uint64_t)K * 4u ||
+        a.range[3] < (uint64_t)N * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if ((uintptr_t)a.ptr[2] % 16u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    const Epi ep = {nullptr, nullptr, 0u};
+    const float* x = (const float*)a.ptr[2];
+    const size_t smem = (size_t)K + (TYPE == 2 ? (size_t)units * kABBytes : (size_t)units * 4u);
+    if (TYPE == 0) {
+        launch_pdl(gemv_q4_0_kernel<1, 2, false, true>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), smem, a.stream,
+                   (const uint4*)a.ptr[0], (const uint16_t*)a.ptr[1], nullptr, nullptr, (float*)a.ptr[3], nullptr, N, K,
+                   N, ep, x, qmode);
+    } else if (TYPE == 1) {
+        launch_pdl(gemv_q8_0_kernel<1, 2, false, true>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), smem, a.stream,
+                   (const u32x8*)a.ptr[0], (const uint16_t*)a.ptr[1], nullptr, nullptr, (float*)a.ptr[3], nullptr, N, K,
+                   N, ep, x, qmode);
+    } else {
+        DstList dl;
+        dl.n = 1u;
+        dl.p[0] = (float*)a.ptr[3];
+        for (int i = 1; i < 8; ++i) dl.p[i] = nullptr;
+        launch_pdl(gemv_q4_K_kernel<1, 2, false, 1, 4, true>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), smem, a.stream,
+                   (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], nullptr, nullptr, dl, nullptr, N, K, N, ep, x, qmode);
+    }
+    return check_launch();
+}
+AcResult launch_mmvq_q4_0_fq(const LaunchArgs& a) { return launch_fq<0>(a); }
+AcResult launch_mmvq_q8_0_fq(const LaunchArgs& a) { return launch_fq<1>(a); }
+AcResult launch_mmvqb_q4_K_fq(const LaunchArgs& a) { return launch_fq<2>(a); }
 
 // bitnet_gemv_i2_s_<l32w1|l16w2|l8w4>[_acc]  (argument contract of src/shaders/bitnet_gemv_i2_s.comp:45-80):
 //   bindings 0 packed weights, 1 int8 activations, 2 out f32, 3 act[2] per row {bits of dequant, sum q}

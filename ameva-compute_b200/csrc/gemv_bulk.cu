@@ -14,6 +14,13 @@
 //                                              CTA when they fit 48 KB, else L1-resident) by __dp4a, exact int32
 //                                              per block, scale in fp32, and keep the row sums in registers across the K
 //                                              segments of the row; after the last segment: warp-shuffle sum and store.
+// Two ways of filling a stage. Short rows (a ring of at least six stages of whole rows fits): a stage is G consecutive
+// whole rows, which is one contiguous range of payload and one of scales, two bulk copies issued by one lane; the 16/G
+// groups of G consumer warps take the stages in turn, one row per warp, and the activations are staged by the CTA's own
+// threads with their 16-byte pieces permuted so that every shared-memory load of the dot product is free of bank
+// conflicts (28672 x 8192 Q4_K, M = 1: 26-28 us against 32-34 us of the register-staged kernel and 44 us of the other
+// mode; a plain read of the same bytes takes 22 us). Long rows: a stage is a K segment of one row per consumer warp
+// (R rows per warp), two bulk copies per row.
 // Rows are contiguous in the device layout ([N][K/256] blocks of payload, then the scales), so a row segment is one
 // contiguous, 16-byte-aligned range: no tensor map is needed. Every wait is bounded by a cycle budget (status word
 // DEV_STATUS_WAIT_TIMEOUT -> AC_ERR_LAUNCH_TIMEOUT on the host).
@@ -34,7 +41,7 @@ using namespace ptx;
 
 constexpr int kConsumerWarps = 16;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr uint32_t kMaxStages = 8;
+constexpr uint32_t kMaxStages = 16;
 constexpr uint32_t kSmemLimit = 227 * 1024;
 constexpr uint32_t kSegK = 4096;   // weights per row per stage at most
 
@@ -60,9 +67,14 @@ struct Params {
     uint32_t N, K, dst_stride;
     uint32_t seg_k;       // weights per row per stage (multiple of 256)
     uint32_t stages;
+    uint32_t group_warps; // 0: a stage holds a K segment of one row per consumer warp; G > 0: a stage holds G whole rows
+    uint32_t groups;      //    (one contiguous range: two copies) and the 16/G warp groups take the stages in turn
     uint32_t act_smem;    // 1: the int8 activations and their scales are staged in shared memory once per CTA
-    uint32_t aq_bytes, ad_bytes;   // their sizes (M*K and the scale array), 16-byte multiples
-    uint32_t diag;        // 0 in production; 1: the consumers skip the arithmetic (measures the copy pipeline alone)
+    uint32_t aq_bytes, ad_bytes;   // their sizes (M*act_stride and the scale array), 16-byte multiples
+    uint32_t act_stride;  // bytes between staged activation rows: K, or K rounded up to 512 with whole-row stages
+    uint32_t diag;        // 0 in production; bit 0: the consumers skip the arithmetic (the copy pipeline alone); bit 1: K
+                          // segments per consumer warp even where whole-row stages fit; bit 2: launch without the
+                          // programmatic-dependent-launch attribute
     uint32_t* status;
 };
 
@@ -74,7 +86,19 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
 
 // ---- per-type inner products over one staged row segment --------------------------------------------------------------
 // q, s: the segment of row r in shared memory; k0: first weight of the segment; ks: weights in the segment.
-template <int TYPE, int M, int R>
+// Shared-memory bank conflicts decide this kernel's speed, so both operands are read conflict-free:
+//  - weights arrive by bulk copy in their device layout; a lane's 32-byte chunk is read as two 16-byte halves, and the
+//    upper four lanes of every eight take the halves in the opposite order (each LDS.128 phase of eight lanes then
+//    covers eight different 16-byte bank groups instead of four twice);
+//  - activations staged by the CTA itself (SWZ) are stored with their 16-byte pieces permuted inside each 64 bytes,
+//    piece p at p ^ ((p >> 3) & 3), which spreads the 32- and 64-byte lane strides of the dot products over all banks.
+__device__ __forceinline__ uint32_t swz_piece(uint32_t p) { return p ^ ((p >> 3) & 3u); }
+template <bool SWZ>
+__device__ __forceinline__ uint4 ld_act_piece(const int8_t* AQ, uint32_t piece) {
+    return *reinterpret_cast<const uint4*>(AQ + 16u * (SWZ ? swz_piece(piece) : piece));
+}
+
+template <int TYPE, int M, int R, bool SWZ = false>
 __device__ __forceinline__ void segment_dot(const uint8_t* const (&q)[R], const uint8_t* const (&s)[R], const Params& p,
                                             const int8_t* AQ, const uint8_t* AD, uint32_t k0, uint32_t ks,
                                             uint32_t lane, float (&acc)[R][M]) {
@@ -86,14 +110,21 @@ __device__ __forceinline__ void segment_dot(const uint8_t* const (&q)[R], const 
             float dw[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                w0[r] = *reinterpret_cast<const uint4*>(q[r] + u * QB);
-                if (TYPE == T_Q8_0) w1[r] = *reinterpret_cast<const uint4*>(q[r] + u * QB + 16u);
+                if (TYPE == T_Q8_0) {
+                    const uint32_t h = (u >> 2) & 1u;   // the upper four lanes of eight read the halves swapped
+                    const uint4 x0 = *reinterpret_cast<const uint4*>(q[r] + u * QB + 16u * h);
+                    const uint4 x1 = *reinterpret_cast<const uint4*>(q[r] + u * QB + 16u * (h ^ 1u));
+                    w0[r] = h ? x1 : x0;
+                    w1[r] = h ? x0 : x1;
+                } else {
+                    w0[r] = *reinterpret_cast<const uint4*>(q[r] + u * QB);
+                }
                 dw[r] = h2f(*reinterpret_cast<const uint16_t*>(s[r] + u * 2u));
             }
 #pragma unroll
             for (int m = 0; m < M; ++m) {
-                const uint4* ap = reinterpret_cast<const uint4*>(AQ + (size_t)m * p.K + k0 + 32u * u);
-                const uint4 a0 = ap[0], a1 = ap[1];
+                const uint32_t pc = (m * (SWZ ? p.act_stride : p.K) + k0 + 32u * u) >> 4;
+                const uint4 a0 = ld_act_piece<SWZ>(AQ, pc), a1 = ld_act_piece<SWZ>(AQ, pc + 1u);
                 const uint32_t adw = reinterpret_cast<const uint32_t*>(AD)[(size_t)m * Ufull + u_base + u];
                 const float da = h2f((uint16_t)(adw & 0xFFFFu));
 #pragma unroll
@@ -136,8 +167,11 @@ __device__ __forceinline__ void segment_dot(const uint8_t* const (&q)[R], const 
             float dw[R], dminw[R];
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                wl[r] = *reinterpret_cast<const uint4*>(q[r] + c * 32u);
-                wh[r] = *reinterpret_cast<const uint4*>(q[r] + c * 32u + 16u);
+                const uint32_t h = (c >> 2) & 1u;   // the upper four lanes of eight read the halves swapped
+                const uint4 x0 = *reinterpret_cast<const uint4*>(q[r] + c * 32u + 16u * h);
+                const uint4 x1 = *reinterpret_cast<const uint4*>(q[r] + c * 32u + 16u * (h ^ 1u));
+                wl[r] = h ? x1 : x0;
+                wh[r] = h ? x0 : x1;
                 const uint4 sv = *reinterpret_cast<const uint4*>(s[r] + b * 16u);
                 const uint32_t a = (sv.y >> p16) & 0xFFFFu, bb = (sv.z >> p16) & 0xFFFFu, e = (sv.w >> p16) & 0xFFFFu;
                 const uint32_t scp = k < 2u ? (a & 0x3F3Fu) : ((e & 0x0F0Fu) | ((a >> 2) & 0x3030u));
@@ -151,8 +185,9 @@ __device__ __forceinline__ void segment_dot(const uint8_t* const (&q)[R], const 
             }
 #pragma unroll
             for (int m = 0; m < M; ++m) {
-                const uint4* ap = reinterpret_cast<const uint4*>(AQ + (size_t)m * p.K + k0 + 64u * c);
-                const uint4 a0 = ap[0], a1 = ap[1], a2 = ap[2], a3 = ap[3];
+                const uint32_t pc = (m * (SWZ ? p.act_stride : p.K) + k0 + 64u * c) >> 4;
+                const uint4 a0 = ld_act_piece<SWZ>(AQ, pc), a1 = ld_act_piece<SWZ>(AQ, pc + 1u),
+                            a2 = ld_act_piece<SWZ>(AQ, pc + 2u), a3 = ld_act_piece<SWZ>(AQ, pc + 3u);
                 const uint8_t* ab = AD + ((size_t)m * Bfull + b_base + b) * kABBytes;
                 const uint2 bs = *reinterpret_cast<const uint2*>(ab + 8u * k);   // bsums[4k .. 4k+3]
                 const float da = *reinterpret_cast<const float*>(ab + 32);
@@ -187,6 +222,78 @@ __device__ __forceinline__ void segment_dot(const uint8_t* const (&q)[R], const 
     }
 }
 
+// ---- Q4_K, one whole row in shared memory against activations staged with permuted pieces ---------------------------
+// The same sums as segment_dot, with everything a lane needs addressed in the shared window (32-bit addresses, explicit
+// ld.shared) and every per-lane choice hoisted out of the loop: a lane's chunk index advances by 32, so its position in
+// a 256-block (k), the half it reads first (h) and the permutation of its activation pieces (sw) never change. Lanes
+// with h = 1 read the two 16-byte halves of their chunk in the opposite order and pair them with the activation pieces
+// in the matching order, so no data has to be swapped afterwards (integer sums do not depend on the order).
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 lds64(uint32_t a) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+    return v;
+}
+
+template <int M>
+__device__ __forceinline__ void row_dot_q4k(uint32_t q, uint32_t s, uint32_t aq, uint32_t ad, uint32_t K,
+                                            uint32_t act_stride, uint32_t lane, float (&acc)[M]) {
+    const uint32_t C = K >> 6, B = K >> 8;
+    const uint32_t k = lane & 3u, p16 = 16u * (k & 1u), h = (lane >> 2) & 1u, sw = (lane >> 1) & 3u;
+    const uint32_t wo0 = 16u * h, wo1 = 16u * (h ^ 1u);
+    uint32_t ao[4];
+#pragma unroll
+    for (uint32_t i = 0; i < 4u; ++i) ao[i] = 16u * ((i ^ h) ^ sw);
+    for (uint32_t c = lane; c < C; c += 32u) {
+        const uint4 x0 = lds128(q + 32u * c + wo0), x1 = lds128(q + 32u * c + wo1);
+        const uint4 sv = lds128(s + 16u * (c >> 2));
+        const uint32_t a = (sv.y >> p16) & 0xFFFFu, bb = (sv.z >> p16) & 0xFFFFu, e = (sv.w >> p16) & 0xFFFFu;
+        const uint32_t scp = k < 2u ? (a & 0x3F3Fu) : ((e & 0x0F0Fu) | ((a >> 2) & 0x3030u));
+        const uint32_t mnp = k < 2u ? (bb & 0x3F3Fu) : (((e >> 4) & 0x0F0Fu) | ((bb >> 2) & 0x3030u));
+        const int sc0 = (int)(scp & 0xFFu), sc1 = (int)(scp >> 8), mn0 = (int)(mnp & 0xFFu), mn1 = (int)(mnp >> 8);
+        const float dw = h2f((uint16_t)(sv.x & 0xFFFFu)), dminw = h2f((uint16_t)(sv.x >> 16));
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const uint32_t ab = aq + (uint32_t)m * act_stride + 64u * c;
+            const uint4 A0 = lds128(ab + ao[0]), A1 = lds128(ab + ao[1]), A2 = lds128(ab + ao[2]), A3 = lds128(ab + ao[3]);
+            const uint32_t rec = ad + ((uint32_t)m * B + (c >> 2)) * kABBytes;
+            const uint2 bs = lds64(rec + 8u * k);   // bsums[4k .. 4k+3]
+            const float da = __uint_as_float(lds32(rec + 32u));
+            const int bs_lo = (int)(int16_t)(bs.x & 0xFFFFu) + (int)(int16_t)(bs.x >> 16);
+            const int bs_hi = (int)(int16_t)(bs.y & 0xFFFFu) + (int)(int16_t)(bs.y >> 16);
+            int dlo = 0, dhi = 0;
+            dlo = dp4a_ss(x0.x & 0x0F0F0F0Fu, A0.x, dlo);
+            dlo = dp4a_ss(x0.y & 0x0F0F0F0Fu, A0.y, dlo);
+            dlo = dp4a_ss(x0.z & 0x0F0F0F0Fu, A0.z, dlo);
+            dlo = dp4a_ss(x0.w & 0x0F0F0F0Fu, A0.w, dlo);
+            dlo = dp4a_ss(x1.x & 0x0F0F0F0Fu, A1.x, dlo);
+            dlo = dp4a_ss(x1.y & 0x0F0F0F0Fu, A1.y, dlo);
+            dlo = dp4a_ss(x1.z & 0x0F0F0F0Fu, A1.z, dlo);
+            dlo = dp4a_ss(x1.w & 0x0F0F0F0Fu, A1.w, dlo);
+            dhi = dp4a_ss((x0.x >> 4) & 0x0F0F0F0Fu, A2.x, dhi);
+            dhi = dp4a_ss((x0.y >> 4) & 0x0F0F0F0Fu, A2.y, dhi);
+            dhi = dp4a_ss((x0.z >> 4) & 0x0F0F0F0Fu, A2.z, dhi);
+            dhi = dp4a_ss((x0.w >> 4) & 0x0F0F0F0Fu, A2.w, dhi);
+            dhi = dp4a_ss((x1.x >> 4) & 0x0F0F0F0Fu, A3.x, dhi);
+            dhi = dp4a_ss((x1.y >> 4) & 0x0F0F0F0Fu, A3.y, dhi);
+            dhi = dp4a_ss((x1.z >> 4) & 0x0F0F0F0Fu, A3.z, dhi);
+            dhi = dp4a_ss((x1.w >> 4) & 0x0F0F0F0Fu, A3.w, dhi);
+            const int isum = sc0 * dlo + sc1 * dhi;
+            const int mpart = mn0 * bs_lo + mn1 * bs_hi;
+            acc[m] += (dw * da) * (float)isum - (dminw * da) * (float)mpart;
+        }
+    }
+}
+
 // ---- the kernel -----------------------------------------------------------------------------------------------------
 template <int TYPE, int M, int R>
 __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) {
@@ -194,7 +301,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
     constexpr uint32_t RB = kConsumerWarps * R;   // rows per stage
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t qseg = (p.seg_k >> 8) * C::kQ256, sseg = (p.seg_k >> 8) * C::kS256;   // bytes per row per stage
-    const uint32_t stage_bytes = RB * (qseg + sseg);
+    const uint32_t stage_bytes =
+        p.group_warps ? p.group_warps * (p.K >> 8) * (C::kQ256 + C::kS256) : RB * (qseg + sseg);
     uint8_t* s_aq = smem + p.stages * stage_bytes;            // activations (when staged): int8 [M][K], then scales
     uint8_t* s_ad = s_aq + p.aq_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_ad + p.ad_bytes);
@@ -206,7 +314,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < kMaxStages; ++s) {
             mbar_init(full + 8u * s, 1u);
-            mbar_init(empty + 8u * s, kConsumerWarps);
+            mbar_init(empty + 8u * s, p.group_warps ? p.group_warps : kConsumerWarps);
         }
         mbar_init(act_bar, 1u);
         ctl->abort = 0u;
@@ -215,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
     __syncthreads();
     pdl_wait();   // the quantized activations come from the preceding kernel
     pdl_trigger();
-    if (p.act_smem && threadIdx.x == 0) {   // one copy each for the quantized activations and their scales
+    if (p.act_smem && !p.group_warps && threadIdx.x == 0) {   // one copy each for the quantized activations and their scales
         mbar_arrive_expect_tx(act_bar, p.aq_bytes + p.ad_bytes);
         bulk_load(smem_u32(s_aq), p.AQ, p.aq_bytes, act_bar);
         bulk_load(smem_u32(s_ad), p.AD, p.ad_bytes, act_bar);
@@ -228,6 +336,78 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
     const uint32_t nseg = (p.K + p.seg_k - 1) / p.seg_k;
     const size_t qrow = (size_t)(p.K >> 8) * C::kQ256, srow = (size_t)(p.K >> 8) * C::kS256;   // bytes per weight row
 
+    if (p.group_warps) {
+        // ---- whole rows: stage j of this CTA holds rows (g_begin + j) * G .. + G - 1, consumed by warp group j % groups ----
+        const uint32_t G = p.group_warps;
+        const uint32_t NG = (p.N + G - 1) / G;
+        const uint32_t g_begin = (uint32_t)((uint64_t)NG * blockIdx.x / gridDim.x);
+        const uint32_t g_end = (uint32_t)((uint64_t)NG * (blockIdx.x + 1) / gridDim.x);
+        const uint32_t gq = G * (uint32_t)qrow, gs = G * (uint32_t)srow, gstage = gq + gs;
+        if (p.act_smem) {   // the activations, pieces permuted (swz_piece), and their scale records, by all threads
+            const uint4* ga = reinterpret_cast<const uint4*>(p.AQ);
+            const uint32_t rp = p.K >> 4, sp = p.act_stride >> 4;   // 16-byte pieces per row: source, staged
+            for (uint32_t i = threadIdx.x; i < M * rp; i += kThreads) {
+                const uint32_t m = i / rp, w = i - m * rp;
+                reinterpret_cast<uint4*>(s_aq)[swz_piece(m * sp + w)] = __ldg(ga + i);
+            }
+            const uint4* gd = reinterpret_cast<const uint4*>(p.AD);
+            for (uint32_t i = threadIdx.x; i < (p.ad_bytes >> 4); i += kThreads)
+                reinterpret_cast<uint4*>(s_ad)[i] = __ldg(gd + i);
+            __syncthreads();
+        }
+        if (warp == kConsumerWarps) {
+            if (lane == 0) {
+                Ring st(NS);
+                for (uint32_t g = g_begin; g < g_end; ++g, st.advance()) {
+                    const uint32_t row0 = g * G, rows = min(G, p.N - row0);
+                    if (!mbar_wait(empty + 8u * st.idx, st.phase ^ 1u, ctl, p.status, 0xC00u | st.idx)) break;
+                    mbar_arrive_expect_tx(full + 8u * st.idx, rows * (uint32_t)(qrow + srow));
+                    const uint32_t sq = smem_u32(smem + st.idx * gstage);
+                    bulk_load(sq, p.Q + (size_t)row0 * qrow, rows * (uint32_t)qrow, full + 8u * st.idx);
+                    bulk_load(sq + gq, p.S + (size_t)row0 * srow, rows * (uint32_t)srow, full + 8u * st.idx);
+                }
+            }
+        } else {
+            const uint32_t group = warp / G, wi = warp - group * G;
+            if (group >= p.groups) return;   // (more warp groups than the ring could feed)
+            const bool staged = p.act_smem != 0u;
+            const int8_t* AQ = staged ? reinterpret_cast<const int8_t*>(s_aq) : p.AQ;
+            const uint8_t* AD = staged ? s_ad : p.AD;
+            bool ok = true;
+            for (uint32_t g = g_begin + group; g < g_end && ok; g += p.groups) {
+                const uint32_t j = g - g_begin, idx = j % NS, phase = (j / NS) & 1u;
+                ok = mbar_wait(full + 8u * idx, phase, ctl, p.status, 0xD00u | idx);
+                if (!ok) break;
+                const uint32_t row = g * G + wi;
+                if (row < p.N && !(p.diag & 1u)) {
+                    float acc[1][M];
+#pragma unroll
+                    for (int m = 0; m < M; ++m) acc[0][m] = 0.0f;
+                    const uint8_t* const q[1] = {smem + idx * gstage + wi * (uint32_t)qrow};
+                    const uint8_t* const sc[1] = {smem + idx * gstage + gq + wi * (uint32_t)srow};
+                    if constexpr (TYPE == T_Q4_K) {
+                        if (staged)
+                            row_dot_q4k<M>(smem_u32(q[0]), smem_u32(sc[0]), smem_u32(s_aq), smem_u32(s_ad), p.K,
+                                           p.act_stride, lane, acc[0]);
+                        else
+                            segment_dot<TYPE, M, 1, false>(q, sc, p, AQ, AD, 0u, p.K, lane, acc);
+                    } else {
+                        if (staged) segment_dot<TYPE, M, 1, true>(q, sc, p, AQ, AD, 0u, p.K, lane, acc);
+                        else segment_dot<TYPE, M, 1, false>(q, sc, p, AQ, AD, 0u, p.K, lane, acc);
+                    }
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        const float v = warp_sum(acc[0][m]);
+                        if (lane == 0)
+                            for (uint32_t o = 0; o < p.dl.n; ++o) p.dl.p[o][(size_t)m * p.dst_stride + row] = v;
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + 8u * idx);
+            }
+        }
+        return;
+    }
     if (warp == kConsumerWarps) {
         // ---- producer ----
         Ring st(NS);
@@ -307,19 +487,39 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
 
 // ---- host side ------------------------------------------------------------------------------------------------------
 template <int TYPE, int M, int R>
-static AcResult launch_one(const LaunchArgs& a, Params& p) {
+static AcResult launch_one(const LaunchArgs& a, Params& p, bool whole_rows = false) {
     using C = Cfg<TYPE>;
     constexpr uint32_t RB = kConsumerWarps * R;
     // whole rows per stage while at least three stages fit (then a row block is one contiguous range), else segments
     p.seg_k = (uint64_t)RB * (p.K >> 8) * (C::kQ256 + C::kS256) * 3u <= 200u * 1024u ? p.K : kSegK;
-    const uint32_t stage_bytes = RB * (p.seg_k >> 8) * (C::kQ256 + C::kS256);
+    uint32_t stage_bytes = RB * (p.seg_k >> 8) * (C::kQ256 + C::kS256);
     // activations in shared memory when they take at most 48 KB (they always are 16-byte multiples: K % 256 == 0)
-    const uint32_t aq_bytes = (uint32_t)M * p.K;
+    p.act_stride = whole_rows ? ((p.K + 511u) & ~511u) : p.K;   // (whole rows: the piece permutation is per 512 bytes)
+    const uint32_t aq_bytes = (uint32_t)M * p.act_stride;
     const uint32_t ad_bytes = TYPE == T_Q4_K ? (uint32_t)M * (p.K >> 8) * kABBytes : (uint32_t)M * (p.K >> 5) * 4u;
     p.act_smem = (aq_bytes + ad_bytes <= 48u * 1024u && !((uintptr_t)p.AQ & 15u) && !((uintptr_t)p.AD & 15u)) ? 1u : 0u;
     p.aq_bytes = p.act_smem ? aq_bytes : 0u;
     p.ad_bytes = p.act_smem ? ad_bytes : 0u;
     const uint32_t fixed = p.aq_bytes + p.ad_bytes + (2u * kMaxStages + 1u) * 8u + 64u;
+    // Stages of G whole rows (R == 1 instantiations): the largest G whose ring is deep enough to keep every warp group on
+    // a stage of its own with as many again in flight. A consumer group never runs more than one pass of the ring ahead
+    // of the producer only while the ring is at least as deep as the number of groups (parity waits alias otherwise).
+    p.group_warps = p.groups = 0u;
+    if (R == 1 && whole_rows) {
+        const uint32_t row_bytes = (p.K >> 8) * (C::kQ256 + C::kS256);
+        for (uint32_t G = kConsumerWarps; G >= 1u; G >>= 1) {
+            uint32_t ns = (kSmemLimit - 1024u - fixed) / (G * row_bytes);
+            if (ns > kMaxStages) ns = kMaxStages;
+            const uint32_t groups = kConsumerWarps / G;
+            if (ns >= (2u * groups > 6u ? 2u * groups : 6u)) {
+                p.group_warps = G;
+                p.groups = groups;
+                stage_bytes = G * row_bytes;
+                break;
+            }
+        }
+        if (!p.group_warps) return AC_ERR_INVALID_WORK_GROUP_SIZE;
+    }
     uint32_t stages = (kSmemLimit - 1024u - fixed) / stage_bytes;
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2u) return AC_ERR_INVALID_WORK_GROUP_SIZE;
@@ -334,10 +534,11 @@ static AcResult launch_one(const LaunchArgs& a, Params& p) {
         }
         attr_set = true;
     }
-    const uint32_t NB = (p.N + RB - 1) / RB;
+    const uint32_t NB = p.group_warps ? (p.N + p.group_warps - 1) / p.group_warps : (p.N + RB - 1) / RB;
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
     const uint32_t grid = NB < sms ? NB : sms;
-    launch_pdl(gemv_bulk_kernel<TYPE, M, R>, dim3(grid), dim3(kThreads), smem_bytes, a.stream, p);
+    if (p.diag & 4u) gemv_bulk_kernel<TYPE, M, R><<<grid, kThreads, smem_bytes, a.stream>>>(p);
+    else launch_pdl(gemv_bulk_kernel<TYPE, M, R>, dim3(grid), dim3(kThreads), smem_bytes, a.stream, p);
     return check_launch();
 }
 
@@ -345,6 +546,11 @@ static AcResult launch_one(const LaunchArgs& a, Params& p) {
 template <int TYPE, int M>
 static AcResult launch_m(const LaunchArgs& a, Params& p) {
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
+    // rows short enough for a ring of whole-row stages (two large copies per stage instead of two per row)
+    if (!(p.diag & 2u)) {
+        const AcResult r = launch_one<TYPE, M, 1>(a, p, true);
+        if (r != AC_ERR_INVALID_WORK_GROUP_SIZE) return r;
+    }
     if constexpr (M <= 2 && TYPE != T_Q8_0) {
         if (p.N >= 6u * 2u * kConsumerWarps * sms) return launch_one<TYPE, M, 2>(a, p);
     }

@@ -30,6 +30,7 @@ AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
 AcResult launch_peer_barrier(const LaunchArgs&);
+AcResult launch_read_probe(const LaunchArgs&);
 AcResult launch_mmvq_q4_0(const LaunchArgs&);
 AcResult launch_mmvq_q4_0_dump(const LaunchArgs&);
 AcResult launch_mmvq_q8_0(const LaunchArgs&);
@@ -38,6 +39,9 @@ AcResult launch_mmvqb_q4_K(const LaunchArgs&);
 AcResult launch_mmvq_q4_0_ep(const LaunchArgs&);
 AcResult launch_mmvq_q8_0_ep(const LaunchArgs&);
 AcResult launch_mmvqb_q4_K_ep(const LaunchArgs&);
+AcResult launch_mmvq_q4_0_fq(const LaunchArgs&);
+AcResult launch_mmvq_q8_0_fq(const LaunchArgs&);
+AcResult launch_mmvqb_q4_K_fq(const LaunchArgs&);
 AcResult launch_mmvqb_q4_K_dump(const LaunchArgs&);
 AcResult launch_bitnet_gemv_i2_s(const LaunchArgs&);
 AcResult launch_bitnet_gemv_i2_s_acc(const LaunchArgs&);
@@ -60,6 +64,7 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvs_q8_0", 12, 24, {288, 1, 1}, launch_mmvs_q8_0},
     {"ameva_mmvs_q4_K", 12, 24, {288, 1, 1}, launch_mmvs_q4_K},
     {"ameva_peer_barrier", 8, 12, {32, 1, 1}, launch_peer_barrier},
+    {"ameva_read_probe", 2, 8, {256, 1, 1}, launch_read_probe},
     {"ameva_mmvq_q4_0", 5, 16, {256, 1, 1}, launch_mmvq_q4_0},
     {"ameva_mmvq_q4_0_dump", 6, 16, {256, 1, 1}, launch_mmvq_q4_0_dump},
     {"ameva_mmvq_q8_0", 5, 16, {256, 1, 1}, launch_mmvq_q8_0},
@@ -68,6 +73,9 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvq_q4_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q4_0_ep},
     {"ameva_mmvq_q8_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q8_0_ep},
     {"ameva_mmvqb_q4_K_ep", 7, 20, {256, 1, 1}, launch_mmvqb_q4_K_ep},
+    {"ameva_mmvq_q4_0_fq", 4, 12, {256, 1, 1}, launch_mmvq_q4_0_fq},
+    {"ameva_mmvq_q8_0_fq", 4, 12, {256, 1, 1}, launch_mmvq_q8_0_fq},
+    {"ameva_mmvqb_q4_K_fq", 4, 12, {256, 1, 1}, launch_mmvqb_q4_K_fq},
     {"ameva_mmvqb_q4_K_dump", 6, 16, {256, 1, 1}, launch_mmvqb_q4_K_dump},
     {"bitnet_gemv_i2_s_l32w1", 4, 24, {32, 4, 1}, launch_bitnet_gemv_i2_s},
     {"bitnet_gemv_i2_s_l16w2", 4, 24, {16, 8, 1}, launch_bitnet_gemv_i2_s},

@@ -37,14 +37,11 @@ struct Ctl {             // shared control words
 
 // Bounded wait: false when the CTA is aborting (this or another thread ran out of budget). Waiters other than the MMA
 // issuer back off between polls (BACKOFF): a spinning warp takes issue slots from the warps that share its scheduler.
-template <bool BACKOFF = true>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t* status, uint32_t tag,
-                                          long long* waited = nullptr) {
+// The blocked part of mbar_wait, out of line: the K loops of the callers keep only the first poll and a branch.
+template <bool BACKOFF>
+__device__ __noinline__ bool mbar_wait_blocked(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t* status, uint32_t tag,
+                                               long long* waited) {
     const long long t0 = clock64();
-    if (mbar_try_wait(bar, parity)) {
-        if (waited) *waited += clock64() - t0;
-        return true;
-    }
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if (BACKOFF) __nanosleep(64);
@@ -59,6 +56,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ct
     }
     if (waited) *waited += clock64() - t0;   // diagnostic: cycles this thread spent blocked here
     return true;
+}
+
+template <bool BACKOFF = true>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, Ctl* ctl, uint32_t* status, uint32_t tag,
+                                          long long* waited = nullptr) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_blocked<BACKOFF>(bar, parity, ctl, status, tag, waited);
 }
 
 // Position in a ring of n slots: slot index and the parity of the current pass (no divisions in the K loop).

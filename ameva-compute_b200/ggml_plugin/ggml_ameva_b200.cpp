@@ -300,6 +300,19 @@ bool record_mul_mat(Backend* be, AcCommandBatch* batch, const ggml_tensor* node)
     const uint64_t wtotal = device_bytes(w, &s_off);
     const AcDim3 grid = {1, 1, 1};   // the launchers size their own grids
 
+    // One token of a projection small enough to be launch-bound: one launch that quantizes the row inside the GEMV
+    // (same bits as the two kernels below; the limits are those of qmm.py's MulMat.record).
+    if (M == 1 && K <= 16384u && (uint64_t)N * K <= (64ull << 20) && tensor_offset(x) % 64 == 0 &&
+        tensor_offset(node) % 64 == 0) {
+        AcKernel* k = kernel(be, (std::string(q4k ? "ameva_mmvqb_" : "ameva_mmvq_") + tname + "_fq").c_str());
+        if (!k) return false;
+        AcBufferBinding b[4] = {bind(wb->buf, tensor_offset(w), s_off), bind(wb->buf, tensor_offset(w) + s_off, wtotal - s_off),
+                                bind(xb->buf, tensor_offset(x), (uint64_t)K * 4),
+                                bind(yb->buf, tensor_offset(node), (uint64_t)N * 4)};
+        const uint32_t push[3] = {N, K, 0};   // ties-to-even per-32 / ggml's per-256 convention
+        return ac_runtime_batch_dispatch_bindings(batch, k, b, 4, push, sizeof(push), grid) == AC_SUCCESS;
+    }
+
     // 1. activation quantization (per-32 for Q4_0 / Q8_0, per-256 for Q4_K; fp16 operand too when M > 8)
     {
         std::string name = q4k ? "ameva_quant_a8b" : "ameva_quant_a8";
@@ -322,6 +335,17 @@ bool record_mul_mat(Backend* be, AcCommandBatch* batch, const ggml_tensor* node)
                                 bind(yb->buf, tensor_offset(node), (uint64_t)M * N * 4)};
         const uint32_t push[5] = {M, N, K, N, 0};
         return ac_runtime_batch_dispatch_bindings(batch, k, b, 4, push, sizeof(push), grid) == AC_SUCCESS;
+    }
+    // M <= 8 over short weight rows, with several activation rows or a large matrix: the GEMV that stages whole weight
+    // rows in shared memory (the choice of qmm.py's MulMat.streamed_pays)
+    const uint64_t row_bytes = (uint64_t)(K / 256) * ((w->type == GGML_TYPE_Q8_0 ? 256u : 128u) + 16u);
+    if (M <= 8 && (K % 256) == 0 && row_bytes <= 6400u && (M >= 4 || (uint64_t)N * row_bytes >= (64ull << 20))) {
+        AcKernel* ks = kernel(be, (std::string("ameva_mmvs_") + tname).c_str());
+        if (!ks) return false;
+        const AcBufferBinding y = bind(yb->buf, tensor_offset(node), (uint64_t)M * N * 4);
+        AcBufferBinding b[12] = {Q, S, bind(be->aq, 0, (uint64_t)M * K), bind(be->ad, 0, ad_need), y, y, y, y, y, y, y, y};
+        const uint32_t push[6] = {M, N, K, N, 0, 0};
+        return ac_runtime_batch_dispatch_bindings(batch, ks, b, 12, push, sizeof(push), grid) == AC_SUCCESS;
     }
     AcKernel* k = kernel(be, (std::string(q4k ? "ameva_mmvqb_" : "ameva_mmvq_") + tname).c_str());
     if (!k) return false;

@@ -22,6 +22,10 @@ TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q
 BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128}
 Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128}   # payload bytes per block
 S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16}      # scale bytes per block
+FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in shared memory
+FUSED_QUANT_MAX_ELEMS = 64 << 20    # N*K up to which the fused launch is used (larger ones are not launch-bound)
+STREAMED_MAX_ROW_BYTES = 6400        # packed bytes per weight row up to which the streamed GEMV stages whole rows
+STREAMED_MIN_WEIGHT_BYTES = 64 << 20  # one activation row: weight bytes from which the streamed GEMV is the default
 GEMV_MAX_M = 8   # decode GEMV serves M <= 8 (ggml-ameva.cpp:3607-3804 sends 2 <= M < 8 to the GEMV family as well)
 AB_BYTES = 48
 
@@ -126,9 +130,15 @@ class MulMat:
 
     def __init__(self, ctx: rt.Context, weight, max_m: int, *, round_mode: int = ROUND_NEAREST_EVEN,
                  q8k_mode: int = Q8K_GGML, dump_block_sums: bool = False, exact: bool = False,
-                 streamed: bool = False) -> None:
+                 streamed: Optional[bool] = None, fused_quantize: bool = False) -> None:
         self.ctx = ctx
-        self.streamed = streamed   # M <= 8: stage the weight rows in shared memory by bulk copies (ameva_mmvs_*)
+        # M <= 8: stage the weight rows in shared memory by bulk copies (ameva_mmvs_*). None = where it measures faster
+        # than the register-staged kernels (see streamed_pays); True / False force the choice.
+        self.streamed = streamed
+        # M == 1 of a small projection: one launch that quantizes the row inside the GEMV (ameva_mmv*_fq); same bits.
+        # On request: in replayed batches, where the quantize kernel's launch already overlaps (programmatic dependent
+        # launch), the two kernels measure faster (5.3 vs 6.0 us on 4096 x 4096 Q4_0); it saves a host launch otherwise.
+        self.fused_quantize = fused_quantize
         self.view = weight if isinstance(weight, WeightView) else weight.view(0, weight.N)
         w = self.view.weight
         why = unsupported_reason(w.type, max_m, self.view.rows, w.K)
@@ -168,6 +178,19 @@ class MulMat:
             return (M, self.N, self.K // 256, 2)
         return None
 
+    def streamed_pays(self, M: int) -> bool:
+        """Where the streamed GEMV measured faster than the register-staged one on a B200: rows short enough for a ring
+        of whole-row stages (about 6 KB of packed row: the kernel then issues two large bulk copies per stage and keeps
+        ~150 KB per SM in flight) and either a weight matrix large enough to be bandwidth-bound (28672 x 8192 Q4_K,
+        M = 1: 26-28 us against 32-34 us) or several activation rows (11008 x 4096 Q4_K, M = 8: 30.5 against 40.4 us).
+        Small single-row products are launch-bound and stay on the register-staged kernels (4096 x 4096: 6.0 vs 7.5 us)."""
+        if self.type not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K) or self.K % 256:
+            return False
+        row_bytes = (self.K // 256) * ((256 if self.type == GGML_TYPE_Q8_0 else 128) + 16)
+        if row_bytes > STREAMED_MAX_ROW_BYTES:
+            return False
+        return M >= 4 or self.N * row_bytes >= STREAMED_MIN_WEIGHT_BYTES
+
     def record(self, batch: rt.Batch, x: rt.Buffer, dst: rt.Buffer, M: int, *, x_offset: int = 0, dst_offset: int = 0,
                dst_stride: Optional[int] = None, quantize: bool = True, peers=None, epilogue=None) -> None:
         """x: fp32 [M][K] at byte x_offset; dst: fp32 rows dst_stride floats apart at byte dst_offset.
@@ -186,6 +209,19 @@ class MulMat:
         dst_stride = N if dst_stride is None else dst_stride
         t = self.type
         use_tc = M > GEMV_MAX_M and not self.exact and self.tc_ok
+        peers = list(peers or [])
+        # One activation row of a projection small enough to be launch-bound: the GEMV quantizes the row itself (every
+        # CTA repeats the quantize, so larger projections keep the separate kernel). The scratch AQ/AD stay unwritten.
+        if (quantize and M == 1 and self.fused_quantize and t in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K)
+                and not self.dump and self.streamed is not True and not peers and epilogue is None
+                and K <= FUSED_QUANT_MAX_K and N * K <= FUSED_QUANT_MAX_ELEMS and x_offset % 64 == 0
+                and dst_offset % 64 == 0):
+            fam = "ameva_mmvqb" if t == GGML_TYPE_Q4_K else "ameva_mmvq"
+            mode = self.q8k_mode if t == GGML_TYPE_Q4_K else self.round_mode
+            self.path = "mmvq-fq"
+            batch.dispatch(ctx.kernel(f"{fam}_{TYPE_NAMES[t]}_fq"), [self.qbind, self.sbind, (x, x_offset), (dst, dst_offset)],
+                           [N, K, mode], ((N + 15) // 16, 1, 1))
+            return
         if quantize:
             if t in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
                 binds = [(x, x_offset), self.aq, self.ad] + ([self.ah] if use_tc else [])
@@ -206,13 +242,12 @@ class MulMat:
                 self.sums = ctx.buffer(int(np.prod(self._sum_shape(self.max_m))) * 4)
         # kernel choice by M (ameva_mmq_plan / enc_mul_mat): M <= 8 -> streaming GEMV; larger M -> tcgen05 GEMM; the exact
         # mode (and K that is not a whole number of 128-byte operand rows) walks larger M in chunks of 8 through the GEMV
-        peers = list(peers or [])
         if len(peers) > 7:
             raise MulMatUnsupported("at most 7 peers")
-        # The shared-memory-streamed GEMV carries the peer exchange for every scaled type; on one GPU the
-        # register-staged kernels measure faster (35 vs 45 us on 28672 x 8192 Q4_K), so it runs only on request.
+        # The shared-memory-streamed GEMV carries the peer exchange for every scaled type, so it always runs with peers.
+        want_streamed = self.streamed if self.streamed is not None else (self.streamed_pays(M) and epilogue is None)
         streamed = (not use_tc and M <= GEMV_MAX_M and t != GGML_TYPE_I2_S and K % 256 == 0 and not self.dump
-                    and not self.exact and (self.streamed or bool(peers)))
+                    and not self.exact and (want_streamed or bool(peers)))
         if peers and not (use_tc and t != GGML_TYPE_I2_S) and not streamed:
             raise MulMatUnsupported("the fused peer exchange is built for the tensor-core GEMM of the scaled types and "
                                     "the streamed GEMV (K a multiple of 256)")

@@ -234,6 +234,11 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-replay", action="store_true", help="one host launch per kernel instead of replayed batches")
     ap.add_argument("--no-overlap", action="store_true", help="e2e: copies and compute in sequence on one stream")
+    ap.add_argument("--gemv", choices=["auto", "register", "streamed"], default="auto",
+                    help="M <= 8: register-staged kernels (ameva_mmvq*), the one that stages the weight rows in shared "
+                         "memory (ameva_mmvs_*), or the library's own choice")
+    ap.add_argument("--fused-quantize", action="store_true",
+                    help="M == 1, small projections: quantize inside the GEMV launch (ameva_mmv*_fq)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     name = args.workload
@@ -269,7 +274,8 @@ def main():
     shard_bytes = weight_bytes(t, max(rows, 1), K)
     pool_n = max(2, min(64, -(-2 * L2_BYTES // max(shard_bytes, 1)) + 1))
     weights = [qmm.QuantWeight.from_ggml(ctx, t, my_blocks, rows, K, scale) for _ in range(pool_n)]
-    mms = [qmm.MulMat(ctx, w, M) for w in weights]
+    mms = [qmm.MulMat(ctx, w, M, streamed={"auto": None, "register": False, "streamed": True}[args.gemv],
+                      fused_quantize=args.fused_quantize) for w in weights]
     x_dev = ctx.buffer(data=x)
 
     # Output exchange of the sharded run. "peer": every rank owns a full [M][N] output; the mul_mat's epilogue stores
@@ -299,7 +305,14 @@ def main():
     launches_per_step = [0]
     batch_keep = []
 
+    probe_sink = ctx.buffer(64)
+
     def record_steps(batch, n, first, quantize=True):
+        if quantize == "read-probe":   # a plain read of each step's weight region instead of the step
+            for i in range(n):
+                batch.dispatch(ctx.kernel("ameva_read_probe"), [weights[(first + i) % pool_n].buf, probe_sink], [0, 0],
+                               (1, 1, 1))
+            return
         for i in range(n):
             mm = mms[(first + i) % pool_n]
             before = batch.stats().dispatches if i == 0 else None
@@ -413,7 +426,8 @@ def main():
     roof = None
     if world == 1:
         nprof = args.steps
-        main_s, pb = gpu_steps(nprof, args.warmup + args.steps, 0, quantize=False)
+        # (a step of the fused quantize+GEMV launch is that one kernel: it is timed as it is)
+        main_s, pb = gpu_steps(nprof, args.warmup + args.steps, 0, quantize=mms[0].path == "mmvq-fq")
         if pb:
             pb.destroy()
         main_ns = main_s / nprof * 1e9
@@ -429,6 +443,14 @@ def main():
             roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
                     "traffic": TRAFFIC.get(name), "peak_source": pk["source"] + " copy", "kernel_us": main_ns / 1e3,
                     "quant_us": quant_ns / 1e3}
+            # what a kernel that only reads the same weight regions (ameva_read_probe, same rotation, same timing)
+            # takes: the ramp and the tail of a launch this short keep a pure read well under the copy peak
+            probe_s, pb = gpu_steps(nprof, args.warmup + args.steps, 0, quantize="read-probe")
+            if pb:
+                pb.destroy()
+            roof["read_only_us"] = probe_s / nprof * 1e6
+            roof["read_only_gbs"] = weights[0].buf.size_bytes / (probe_s / nprof) / 1e9
+            roof["frac_of_read_only"] = roof["read_only_us"] / roof["kernel_us"]
 
     # end to end through the public API with host buffers: H2D of the activations, compute, D2H of the result, per step
     x_pin = torch.from_numpy(x).pin_memory()
@@ -576,6 +598,7 @@ def main():
     for w in weights:
         w.destroy()
     x_dev.destroy()
+    probe_sink.destroy()
     if ex:
         ex.destroy()
     else:

@@ -25,7 +25,9 @@ def run_case(ctx, t, M, N, K, seed=0, dump=True, check_strict=True, streamed=Fal
     blocks, scale = make_weights(t, N, K, seed)
     x = make_acts(M, K, seed + 1)
     w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
-    mm = qmm.MulMat(ctx, w, M, dump_block_sums=dump and t != I2_S, streamed=streamed)
+    # the two-kernel sequence (the quantized row lands in the scratch this test reads back); the single launch that
+    # quantizes inside the GEMV is compared with it bit for bit in test_gemv_fused_quantize_same_bits
+    mm = qmm.MulMat(ctx, w, M, dump_block_sums=dump and t != I2_S, streamed=streamed, fused_quantize=False)
     xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
     dst.fill(0xFF)
     mm.run(xb, dst, M)
@@ -264,3 +266,115 @@ def test_fused_epilogue_of_a_one_row_product(ctx, t, mode):
         b.destroy()
     mm.destroy()
     w.destroy()
+
+
+def test_read_probe_kernel(ctx):
+    """The measurement aid that only reads a region: argument checks, and it leaves source and sink untouched."""
+    src, sink, tiny = ctx.buffer(1 << 20), ctx.buffer(64), ctx.buffer(2)
+    data = np.arange(1 << 18, dtype=np.uint32)
+    src.write(data)
+    sink.fill(0)
+    k = ctx.kernel("ameva_read_probe")
+    for push in ([0, 0], [4096, 0], [(1 << 20) - 48, 0]):
+        batch = ctx.batch(4)
+        batch.dispatch(k, [src, sink], push, (1, 1, 1))
+        ev = batch.submit()
+        ev.wait(10_000_000_000)
+        ev.destroy()
+        batch.destroy()
+    assert np.array_equal(src.read(np.uint32), data)
+    assert not sink.read(np.uint32).any()
+    batch = ctx.batch(4)
+    with pytest.raises(rt.AmevaComputeError):      # more bytes than the binding holds
+        batch.dispatch(k, [src, sink], [(1 << 20) + 16, 0], (1, 1, 1))
+        batch.submit().wait()
+    with pytest.raises(rt.AmevaComputeError):      # no room for the sink word
+        batch.dispatch(k, [src, tiny], [0, 0], (1, 1, 1))
+        batch.submit().wait()
+    batch.destroy()
+    for b in (src, sink, tiny):
+        b.destroy()
+
+
+FQ_SHAPES = [(1, 256), (3, 256), (17, 512), (130, 768), (250, 1024), (4096, 4096), (1000, 11008), (33, 16384)]
+
+
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
+@pytest.mark.parametrize("qmode", [0, 1])
+def test_gemv_fused_quantize_same_bits(ctx, t, qmode):
+    """M == 1: the launch that quantizes the row inside the GEMV gives the bits of quantize kernel + GEMV, in both
+    rounding modes of the quantizer, and matches the oracle; K that is a multiple of 32 only (Q4_0 / Q8_0) included."""
+    shapes = FQ_SHAPES + ([(40, 96), (9, 4128)] if t != Q4_K else [])
+    for N, K in shapes:
+        blocks, scale = make_weights(t, N, K, N + K)
+        x = make_acts(1, K, K + 1)
+        x[0, : min(K, 64)] = 0.0                      # an all-zero block: d = 0 path of the quantizer
+        if K >= 512:
+            x[0, 256:260] = [2.5, -2.5, 0.5, 1.5]     # ties, where the two rounding modes differ
+        w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+        kw = dict(round_mode=qmode) if t != Q4_K else dict(q8k_mode=qmode)
+        two = qmm.MulMat(ctx, w, 1, fused_quantize=False, **kw)
+        one = qmm.MulMat(ctx, w, 1, fused_quantize=True, **kw)
+        xb, a, b = ctx.buffer(data=x), ctx.buffer(N * 4), ctx.buffer(N * 4)
+        a.fill(0xFF)
+        b.fill(0xFF)
+        two.run(xb, a, 1)
+        one.run(xb, b, 1)
+        assert (two.path, one.path) == ("mmvq", "mmvq-fq")
+        ya, yb = a.read(np.float32), b.read(np.float32)
+        assert np.array_equal(ya.view(np.uint32), yb.view(np.uint32)), (N, K)
+        okw = dict(round_mode=qmode) if t != Q4_K else dict(q8k_mode=qmode)
+        want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False, **okw)
+        assert max_normalised_error(yb.reshape(1, N), want) <= TOL
+        for v in (xb, a, b):
+            v.destroy()
+        one.destroy()
+        two.destroy()
+        w.destroy()
+
+
+def test_gemv_fused_quantize_limits(ctx):
+    """Rows longer than the shared-memory limit and large projections keep the two-kernel sequence; the kernel itself
+    refuses what it cannot hold."""
+    t, N, K = Q8_0, 8, 32768
+    blocks, scale = make_weights(t, N, K, 1)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    mm = qmm.MulMat(ctx, w, 1, fused_quantize=True)
+    xb, dst = ctx.buffer(data=make_acts(1, K, 2)), ctx.buffer(N * 4)
+    mm.run(xb, dst, 1)
+    assert mm.path == "mmvq"
+    batch = ctx.batch(4)
+    with pytest.raises(rt.AmevaComputeError):
+        batch.dispatch(ctx.kernel("ameva_mmvq_q8_0_fq"), [mm.qbind, mm.sbind, xb, dst], [N, K, 0], (1, 1, 1))
+        batch.submit().wait()
+    with pytest.raises(rt.AmevaComputeError):      # quantize mode out of range
+        batch.dispatch(ctx.kernel("ameva_mmvq_q8_0_fq"), [mm.qbind, mm.sbind, xb, dst], [N, 4096, 2], (1, 1, 1))
+        batch.submit().wait()
+    batch.destroy()
+    for v in (xb, dst):
+        v.destroy()
+    mm.destroy()
+    w.destroy()
+
+
+def test_gemv_default_kernel_choice(ctx):
+    """Without a request the streamed kernel serves several activation rows of short-row weights and large matrices;
+    small single-row products stay on the register-staged kernels. Both agree with the oracle."""
+    cases = [(Q4_K, 8, 272, 4096, "mmvs"), (Q4_K, 3, 272, 4096, "mmvq"), (Q4_K, 1, 272, 4096, "mmvq"),
+             (Q8_0, 4, 130, 2048, "mmvs"), (Q4_0, 8, 96, 512, "mmvs"), (Q4_K, 8, 64, 28672, "mmvq"),
+             (Q4_K, 1, 16384, 8192, "mmvs")]
+    for t, M, N, K, path in cases:
+        blocks, scale = make_weights(t, N, K, N + M)
+        x = make_acts(M, K, K + M)
+        w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+        mm = qmm.MulMat(ctx, w, M)
+        xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+        dst.fill(0xFF)
+        mm.run(xb, dst, M)
+        assert mm.path == path, (t, M, N, K, mm.path)
+        want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+        assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= TOL
+        for v in (xb, dst):
+            v.destroy()
+        mm.destroy()
+        w.destroy()
