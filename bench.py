@@ -59,8 +59,8 @@ WORKLOADS = {
 }
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures summarised under
-# profiles/ (bytes)
-TRAFFIC = {"cfg2": 58200000, "cfg5-up-m1": 136777216}
+# profiles/ (bytes), by workload and kernel path
+TRAFFIC = {("cfg2", "mmtc"): 58200000, ("cfg5-up-m1", "mmvs"): 136000000, ("cfg5-up-m1", "mmvq"): 136777216}
 GEMV_MAX_M = 8
 
 
@@ -436,12 +436,12 @@ def main():
         if unit == "TFLOP/s":
             ach = 2.0 * M * N * K / (main_ns * 1e-9) / 1e12
             roof = {"bound": "tensor", "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
-                    "frac": ach / pk["tflops"], "traffic": TRAFFIC.get(name),
+                    "frac": ach / pk["tflops"], "traffic": TRAFFIC.get((name, mms[0].path)),
                     "peak_source": pk["source"] + " bf16 burst", "kernel_us": main_ns / 1e3, "quant_us": quant_ns / 1e3}
         else:
             ach = algorithmic_bytes(t, M, N, K) / (main_ns * 1e-9) / 1e9
             roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
-                    "traffic": TRAFFIC.get(name), "peak_source": pk["source"] + " copy", "kernel_us": main_ns / 1e3,
+                    "traffic": TRAFFIC.get((name, mms[0].path)), "peak_source": pk["source"] + " copy", "kernel_us": main_ns / 1e3,
                     "quant_us": quant_ns / 1e3}
             # what a kernel that only reads the same weight regions (ameva_read_probe, same rotation, same timing)
             # takes: the ramp and the tail of a launch this short keep a pure read well under the copy peak
