@@ -36,6 +36,21 @@ Q8K_GGML, Q8K_AMEVA = 0, 1
 EPILOGUE_ADD, EPILOGUE_SWIGLU_GATE, EPILOGUE_SWIGLU_UP = 1, 2, 3
 
 
+def streamed_pays(ggml_type: int, M: int, N: int, K: int) -> bool:
+    """Where the streamed GEMV (ameva_mmvs_*) measured faster than the register-staged one on a B200: rows short enough
+    for a ring of whole-row stages (about 6 KB of packed row: the kernel then issues two large bulk copies per stage and
+    keeps ~150 KB per SM in flight) and either a weight matrix large enough to be bandwidth-bound (28672 x 8192 Q4_K,
+    M = 1: 26-28 us against 32-34 us) or several activation rows (11008 x 4096 Q4_K, M = 8: 30.5 against 40.4 us).
+    Small single-row products are launch-bound and stay on the register-staged kernels (4096 x 4096: 6.0 vs 7.5 us);
+    rows longer than the limit would be staged in K segments with two small copies per row, which is slower."""
+    if ggml_type not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K) or K % 256 or not 1 <= M <= GEMV_MAX_M:
+        return False
+    row_bytes = (K // 256) * ((256 if ggml_type == GGML_TYPE_Q8_0 else 128) + 16)
+    if row_bytes > STREAMED_MAX_ROW_BYTES:
+        return False
+    return M >= 4 or N * row_bytes >= STREAMED_MIN_WEIGHT_BYTES
+
+
 class MulMatUnsupported(Exception):
     """The op is outside the contract; the message is the reason (the reference logs it once per (op, type, reason))."""
 
@@ -179,17 +194,7 @@ class MulMat:
         return None
 
     def streamed_pays(self, M: int) -> bool:
-        """Where the streamed GEMV measured faster than the register-staged one on a B200: rows short enough for a ring
-        of whole-row stages (about 6 KB of packed row: the kernel then issues two large bulk copies per stage and keeps
-        ~150 KB per SM in flight) and either a weight matrix large enough to be bandwidth-bound (28672 x 8192 Q4_K,
-        M = 1: 26-28 us against 32-34 us) or several activation rows (11008 x 4096 Q4_K, M = 8: 30.5 against 40.4 us).
-        Small single-row products are launch-bound and stay on the register-staged kernels (4096 x 4096: 6.0 vs 7.5 us)."""
-        if self.type not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K) or self.K % 256:
-            return False
-        row_bytes = (self.K // 256) * ((256 if self.type == GGML_TYPE_Q8_0 else 128) + 16)
-        if row_bytes > STREAMED_MAX_ROW_BYTES:
-            return False
-        return M >= 4 or self.N * row_bytes >= STREAMED_MIN_WEIGHT_BYTES
+        return streamed_pays(self.type, M, self.N, self.K)
 
     def record(self, batch: rt.Batch, x: rt.Buffer, dst: rt.Buffer, M: int, *, x_offset: int = 0, dst_offset: int = 0,
                dst_stride: Optional[int] = None, quantize: bool = True, peers=None, epilogue=None) -> None:

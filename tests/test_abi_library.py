@@ -133,9 +133,26 @@ def test_error_state_first_error_wins_per_generation():
 def test_registry_names():
     names = rt.kernel_names()
     for want in ("ameva_quant_a8", "ameva_quant_a8b", "bitnet_norm_q8", "ameva_mmvq_q4_0", "ameva_mmvq_q8_0",
-                 "ameva_mmvqb_q4_K", "bitnet_gemv_i2_s_l32w1", "bitnet_gemv_i2_s_l16w2_acc"):
+                 "ameva_mmvqb_q4_K", "bitnet_gemv_i2_s_l32w1", "bitnet_gemv_i2_s_l16w2_acc", "ameva_mmvs_q4_K",
+                 "ameva_mmvq_q4_0_fq", "ameva_mmvq_q8_0_fq", "ameva_mmvqb_q4_K_fq", "ameva_read_probe",
+                 "ameva_peer_barrier", "ameva_mmtc_q8_0", "ameva_mmtc_q4_K_mp"):
         assert want in names
     assert len(names) == len(set(names))
+
+
+def test_decode_kernel_choice_policy():
+    """Which M <= 8 products go to the kernel that stages whole weight rows in shared memory (host logic only)."""
+    q = pkg.qmm
+    Q4_0, Q8_0, Q4_K, I2_S = q.GGML_TYPE_Q4_0, q.GGML_TYPE_Q8_0, q.GGML_TYPE_Q4_K, q.GGML_TYPE_I2_S
+    assert q.streamed_pays(Q4_K, 1, 28672, 8192)          # 132 MB of weights, 4.6 KB rows
+    assert not q.streamed_pays(Q4_K, 1, 8192, 28672)      # 16 KB rows do not fit whole-row stages
+    assert not q.streamed_pays(Q4_K, 1, 4096, 4096)       # small single-row product: launch-bound
+    assert not q.streamed_pays(Q4_K, 3, 11008, 4096)
+    assert q.streamed_pays(Q4_K, 4, 11008, 4096) and q.streamed_pays(Q4_K, 8, 64, 256)
+    assert q.streamed_pays(Q8_0, 8, 11008, 4096) and not q.streamed_pays(Q8_0, 8, 4096, 8192)   # 8.7 KB rows
+    assert q.streamed_pays(Q4_0, 1, 32768, 8192) and not q.streamed_pays(Q4_0, 1, 32768, 8192 + 32)   # K % 256
+    assert not q.streamed_pays(I2_S, 8, 6912, 2560)
+    assert not q.streamed_pays(Q4_K, 9, 11008, 4096) and not q.streamed_pays(Q4_K, 0, 11008, 4096)
 
 
 @pytest.mark.parametrize("ggml_type,quant", [(2, oracle.quantize_q4_0), (8, oracle.quantize_q8_0),
