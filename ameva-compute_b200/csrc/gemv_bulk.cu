@@ -16,9 +16,10 @@
 //                                              segments of the row; after the last segment: warp-shuffle sum and store.
 // Two ways of filling a stage. Short rows (a ring of at least six stages of whole rows fits): a stage is G consecutive
 // whole rows, which is one contiguous range of payload and one of scales, two bulk copies issued by one lane; the 16/G
-// groups of G consumer warps take the stages in turn, one row per warp, and the activations are staged by the CTA's own
-// threads with their 16-byte pieces permuted so that every shared-memory load of the dot product is free of bank
-// conflicts (28672 x 8192 Q4_K, M = 1: 26-28 us against 32-34 us of the register-staged kernel and 44 us of the other
+// groups of G consumer warps take the stages in turn, one row per warp (two for large Q4_K matrices at M <= 2), and the
+// activations are staged by the CTA's own threads with their 16-byte pieces permuted so that every shared-memory load
+// of the dot product is free of bank conflicts (28672 x 8192 Q4_K, M = 1: 25-28 us against 32-34 us of the
+// register-staged kernel and 44 us of the other
 // mode; a plain read of the same bytes takes 22 us). Long rows: a stage is a K segment of one row per consumer warp
 // (R rows per warp), two bulk copies per row.
 // Rows are contiguous in the device layout ([N][K/256] blocks of payload, then the scales), so a row segment is one
@@ -74,7 +75,7 @@ struct Params {
     uint32_t act_stride;  // bytes between staged activation rows: K, or K rounded up to 512 with whole-row stages
     uint32_t diag;        // 0 in production; bit 0: the consumers skip the arithmetic (the copy pipeline alone); bit 1: K
                           // segments per consumer warp even where whole-row stages fit; bit 2: launch without the
-                          // programmatic-dependent-launch attribute
+                          // programmatic-dependent-launch attribute; bit 3: two rows per warp in whole-row stages
     uint32_t* status;
 };
 
@@ -244,9 +245,9 @@ __device__ __forceinline__ uint32_t lds32(uint32_t a) {
     return v;
 }
 
-template <int M>
-__device__ __forceinline__ void row_dot_q4k(uint32_t q, uint32_t s, uint32_t aq, uint32_t ad, uint32_t K,
-                                            uint32_t act_stride, uint32_t lane, float (&acc)[M]) {
+template <int M, int RW>
+__device__ __forceinline__ void row_dot_q4k(const uint32_t (&q)[RW], const uint32_t (&s)[RW], uint32_t aq, uint32_t ad,
+                                            uint32_t K, uint32_t act_stride, uint32_t lane, float (&acc)[RW][M]) {
     const uint32_t C = K >> 6, B = K >> 8;
     const uint32_t k = lane & 3u, p16 = 16u * (k & 1u), h = (lane >> 2) & 1u, sw = (lane >> 1) & 3u;
     const uint32_t wo0 = 16u * h, wo1 = 16u * (h ^ 1u);
@@ -254,13 +255,24 @@ __device__ __forceinline__ void row_dot_q4k(uint32_t q, uint32_t s, uint32_t aq,
 #pragma unroll
     for (uint32_t i = 0; i < 4u; ++i) ao[i] = 16u * ((i ^ h) ^ sw);
     for (uint32_t c = lane; c < C; c += 32u) {
-        const uint4 x0 = lds128(q + 32u * c + wo0), x1 = lds128(q + 32u * c + wo1);
-        const uint4 sv = lds128(s + 16u * (c >> 2));
-        const uint32_t a = (sv.y >> p16) & 0xFFFFu, bb = (sv.z >> p16) & 0xFFFFu, e = (sv.w >> p16) & 0xFFFFu;
-        const uint32_t scp = k < 2u ? (a & 0x3F3Fu) : ((e & 0x0F0Fu) | ((a >> 2) & 0x3030u));
-        const uint32_t mnp = k < 2u ? (bb & 0x3F3Fu) : (((e >> 4) & 0x0F0Fu) | ((bb >> 2) & 0x3030u));
-        const int sc0 = (int)(scp & 0xFFu), sc1 = (int)(scp >> 8), mn0 = (int)(mnp & 0xFFu), mn1 = (int)(mnp >> 8);
-        const float dw = h2f((uint16_t)(sv.x & 0xFFFFu)), dminw = h2f((uint16_t)(sv.x >> 16));
+        uint4 x0[RW], x1[RW];
+        int sc0[RW], sc1[RW], mn0[RW], mn1[RW];
+        float dw[RW], dminw[RW];
+#pragma unroll
+        for (int r = 0; r < RW; ++r) {
+            x0[r] = lds128(q[r] + 32u * c + wo0);
+            x1[r] = lds128(q[r] + 32u * c + wo1);
+            const uint4 sv = lds128(s[r] + 16u * (c >> 2));
+            const uint32_t a = (sv.y >> p16) & 0xFFFFu, bb = (sv.z >> p16) & 0xFFFFu, e = (sv.w >> p16) & 0xFFFFu;
+            const uint32_t scp = k < 2u ? (a & 0x3F3Fu) : ((e & 0x0F0Fu) | ((a >> 2) & 0x3030u));
+            const uint32_t mnp = k < 2u ? (bb & 0x3F3Fu) : (((e >> 4) & 0x0F0Fu) | ((bb >> 2) & 0x3030u));
+            sc0[r] = (int)(scp & 0xFFu);
+            sc1[r] = (int)(scp >> 8);
+            mn0[r] = (int)(mnp & 0xFFu);
+            mn1[r] = (int)(mnp >> 8);
+            dw[r] = h2f((uint16_t)(sv.x & 0xFFFFu));
+            dminw[r] = h2f((uint16_t)(sv.x >> 16));
+        }
 #pragma unroll
         for (int m = 0; m < M; ++m) {
             const uint32_t ab = aq + (uint32_t)m * act_stride + 64u * c;
@@ -270,26 +282,29 @@ __device__ __forceinline__ void row_dot_q4k(uint32_t q, uint32_t s, uint32_t aq,
             const float da = __uint_as_float(lds32(rec + 32u));
             const int bs_lo = (int)(int16_t)(bs.x & 0xFFFFu) + (int)(int16_t)(bs.x >> 16);
             const int bs_hi = (int)(int16_t)(bs.y & 0xFFFFu) + (int)(int16_t)(bs.y >> 16);
-            int dlo = 0, dhi = 0;
-            dlo = dp4a_ss(x0.x & 0x0F0F0F0Fu, A0.x, dlo);
-            dlo = dp4a_ss(x0.y & 0x0F0F0F0Fu, A0.y, dlo);
-            dlo = dp4a_ss(x0.z & 0x0F0F0F0Fu, A0.z, dlo);
-            dlo = dp4a_ss(x0.w & 0x0F0F0F0Fu, A0.w, dlo);
-            dlo = dp4a_ss(x1.x & 0x0F0F0F0Fu, A1.x, dlo);
-            dlo = dp4a_ss(x1.y & 0x0F0F0F0Fu, A1.y, dlo);
-            dlo = dp4a_ss(x1.z & 0x0F0F0F0Fu, A1.z, dlo);
-            dlo = dp4a_ss(x1.w & 0x0F0F0F0Fu, A1.w, dlo);
-            dhi = dp4a_ss((x0.x >> 4) & 0x0F0F0F0Fu, A2.x, dhi);
-            dhi = dp4a_ss((x0.y >> 4) & 0x0F0F0F0Fu, A2.y, dhi);
-            dhi = dp4a_ss((x0.z >> 4) & 0x0F0F0F0Fu, A2.z, dhi);
-            dhi = dp4a_ss((x0.w >> 4) & 0x0F0F0F0Fu, A2.w, dhi);
-            dhi = dp4a_ss((x1.x >> 4) & 0x0F0F0F0Fu, A3.x, dhi);
-            dhi = dp4a_ss((x1.y >> 4) & 0x0F0F0F0Fu, A3.y, dhi);
-            dhi = dp4a_ss((x1.z >> 4) & 0x0F0F0F0Fu, A3.z, dhi);
-            dhi = dp4a_ss((x1.w >> 4) & 0x0F0F0F0Fu, A3.w, dhi);
-            const int isum = sc0 * dlo + sc1 * dhi;
-            const int mpart = mn0 * bs_lo + mn1 * bs_hi;
-            acc[m] += (dw * da) * (float)isum - (dminw * da) * (float)mpart;
+#pragma unroll
+            for (int r = 0; r < RW; ++r) {
+                int dlo = 0, dhi = 0;
+                dlo = dp4a_ss(x0[r].x & 0x0F0F0F0Fu, A0.x, dlo);
+                dlo = dp4a_ss(x0[r].y & 0x0F0F0F0Fu, A0.y, dlo);
+                dlo = dp4a_ss(x0[r].z & 0x0F0F0F0Fu, A0.z, dlo);
+                dlo = dp4a_ss(x0[r].w & 0x0F0F0F0Fu, A0.w, dlo);
+                dlo = dp4a_ss(x1[r].x & 0x0F0F0F0Fu, A1.x, dlo);
+                dlo = dp4a_ss(x1[r].y & 0x0F0F0F0Fu, A1.y, dlo);
+                dlo = dp4a_ss(x1[r].z & 0x0F0F0F0Fu, A1.z, dlo);
+                dlo = dp4a_ss(x1[r].w & 0x0F0F0F0Fu, A1.w, dlo);
+                dhi = dp4a_ss((x0[r].x >> 4) & 0x0F0F0F0Fu, A2.x, dhi);
+                dhi = dp4a_ss((x0[r].y >> 4) & 0x0F0F0F0Fu, A2.y, dhi);
+                dhi = dp4a_ss((x0[r].z >> 4) & 0x0F0F0F0Fu, A2.z, dhi);
+                dhi = dp4a_ss((x0[r].w >> 4) & 0x0F0F0F0Fu, A2.w, dhi);
+                dhi = dp4a_ss((x1[r].x >> 4) & 0x0F0F0F0Fu, A3.x, dhi);
+                dhi = dp4a_ss((x1[r].y >> 4) & 0x0F0F0F0Fu, A3.y, dhi);
+                dhi = dp4a_ss((x1[r].z >> 4) & 0x0F0F0F0Fu, A3.z, dhi);
+                dhi = dp4a_ss((x1[r].w >> 4) & 0x0F0F0F0Fu, A3.w, dhi);
+                const int isum = sc0[r] * dlo + sc1[r] * dhi;
+                const int mpart = mn0[r] * bs_lo + mn1[r] * bs_hi;
+                acc[r][m] += (dw[r] * da) * (float)isum - (dminw[r] * da) * (float)mpart;
+            }
         }
     }
 }
@@ -302,7 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t qseg = (p.seg_k >> 8) * C::kQ256, sseg = (p.seg_k >> 8) * C::kS256;   // bytes per row per stage
     const uint32_t stage_bytes =
-        p.group_warps ? p.group_warps * (p.K >> 8) * (C::kQ256 + C::kS256) : RB * (qseg + sseg);
+        p.group_warps ? p.group_warps * R * (p.K >> 8) * (C::kQ256 + C::kS256) : RB * (qseg + sseg);
     uint8_t* s_aq = smem + p.stages * stage_bytes;            // activations (when staged): int8 [M][K], then scales
     uint8_t* s_ad = s_aq + p.aq_bytes;
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_ad + p.ad_bytes);
@@ -337,12 +352,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
     const size_t qrow = (size_t)(p.K >> 8) * C::kQ256, srow = (size_t)(p.K >> 8) * C::kS256;   // bytes per weight row
 
     if (p.group_warps) {
-        // ---- whole rows: stage j of this CTA holds rows (g_begin + j) * G .. + G - 1, consumed by warp group j % groups ----
-        const uint32_t G = p.group_warps;
-        const uint32_t NG = (p.N + G - 1) / G;
+        // ---- whole rows: stage j of this CTA holds rows (g_begin + j) * G * R .. + G * R - 1, consumed by warp group
+        // j % groups, R consecutive rows per warp ----
+        const uint32_t G = p.group_warps, SR = G * R;   // warps per group, rows per stage
+        const uint32_t NG = (p.N + SR - 1) / SR;
         const uint32_t g_begin = (uint32_t)((uint64_t)NG * blockIdx.x / gridDim.x);
         const uint32_t g_end = (uint32_t)((uint64_t)NG * (blockIdx.x + 1) / gridDim.x);
-        const uint32_t gq = G * (uint32_t)qrow, gs = G * (uint32_t)srow, gstage = gq + gs;
+        const uint32_t gq = SR * (uint32_t)qrow, gs = SR * (uint32_t)srow, gstage = gq + gs;
         if (p.act_smem) {   // the activations, pieces permuted (swz_piece), and their scale records, by all threads
             const uint4* ga = reinterpret_cast<const uint4*>(p.AQ);
             const uint32_t rp = p.K >> 4, sp = p.act_stride >> 4;   // 16-byte pieces per row: source, staged
@@ -359,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
             if (lane == 0) {
                 Ring st(NS);
                 for (uint32_t g = g_begin; g < g_end; ++g, st.advance()) {
-                    const uint32_t row0 = g * G, rows = min(G, p.N - row0);
+                    const uint32_t row0 = g * SR, rows = min(SR, p.N - row0);
                     if (!mbar_wait(empty + 8u * st.idx, st.phase ^ 1u, ctl, p.status, 0xC00u | st.idx)) break;
                     mbar_arrive_expect_tx(full + 8u * st.idx, rows * (uint32_t)(qrow + srow));
                     const uint32_t sq = smem_u32(smem + st.idx * gstage);
@@ -378,29 +394,43 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
                 const uint32_t j = g - g_begin, idx = j % NS, phase = (j / NS) & 1u;
                 ok = mbar_wait(full + 8u * idx, phase, ctl, p.status, 0xD00u | idx);
                 if (!ok) break;
-                const uint32_t row = g * G + wi;
-                if (row < p.N && !(p.diag & 1u)) {
-                    float acc[1][M];
+                const uint32_t row = g * SR + wi * R;
+                if (row < p.N && !(p.diag & 1u)) {   // (a row past N next to a valid one computes on stale bytes, unstored)
+                    float acc[R][M];
 #pragma unroll
-                    for (int m = 0; m < M; ++m) acc[0][m] = 0.0f;
-                    const uint8_t* const q[1] = {smem + idx * gstage + wi * (uint32_t)qrow};
-                    const uint8_t* const sc[1] = {smem + idx * gstage + gq + wi * (uint32_t)srow};
-                    if constexpr (TYPE == T_Q4_K) {
-                        if (staged)
-                            row_dot_q4k<M>(smem_u32(q[0]), smem_u32(sc[0]), smem_u32(s_aq), smem_u32(s_ad), p.K,
-                                           p.act_stride, lane, acc[0]);
-                        else
-                            segment_dot<TYPE, M, 1, false>(q, sc, p, AQ, AD, 0u, p.K, lane, acc);
+                    for (int r = 0; r < R; ++r)
+#pragma unroll
+                        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+                    const uint8_t* q[R];
+                    const uint8_t* sc[R];
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        q[r] = smem + idx * gstage + (wi * R + r) * (uint32_t)qrow;
+                        sc[r] = smem + idx * gstage + gq + (wi * R + r) * (uint32_t)srow;
+                    }
+                    if (TYPE == T_Q4_K && staged) {
+                        if constexpr (TYPE == T_Q4_K) {
+                            uint32_t q32[R], s32[R];
+#pragma unroll
+                            for (int r = 0; r < R; ++r) {
+                                q32[r] = smem_u32(q[r]);
+                                s32[r] = smem_u32(sc[r]);
+                            }
+                            row_dot_q4k<M, R>(q32, s32, smem_u32(s_aq), smem_u32(s_ad), p.K, p.act_stride, lane, acc);
+                        }
+                    } else if (staged) {
+                        segment_dot<TYPE, M, R, true>(q, sc, p, AQ, AD, 0u, p.K, lane, acc);
                     } else {
-                        if (staged) segment_dot<TYPE, M, 1, true>(q, sc, p, AQ, AD, 0u, p.K, lane, acc);
-                        else segment_dot<TYPE, M, 1, false>(q, sc, p, AQ, AD, 0u, p.K, lane, acc);
+                        segment_dot<TYPE, M, R, false>(q, sc, p, AQ, AD, 0u, p.K, lane, acc);
                     }
 #pragma unroll
-                    for (int m = 0; m < M; ++m) {
-                        const float v = warp_sum(acc[0][m]);
-                        if (lane == 0)
-                            for (uint32_t o = 0; o < p.dl.n; ++o) p.dl.p[o][(size_t)m * p.dst_stride + row] = v;
-                    }
+                    for (int r = 0; r < R; ++r)
+#pragma unroll
+                        for (int m = 0; m < M; ++m) {
+                            const float v = warp_sum(acc[r][m]);
+                            if (lane == 0 && row + r < p.N)
+                                for (uint32_t o = 0; o < p.dl.n; ++o) p.dl.p[o][(size_t)m * p.dst_stride + row + r] = v;
+                        }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty + 8u * idx);
@@ -505,16 +535,19 @@ static AcResult launch_one(const LaunchArgs& a, Params& p, bool whole_rows = fal
     // a stage of its own with as many again in flight. A consumer group never runs more than one pass of the ring ahead
     // of the producer only while the ring is at least as deep as the number of groups (parity waits alias otherwise).
     p.group_warps = p.groups = 0u;
-    if (R == 1 && whole_rows) {
+    if (whole_rows) {
         const uint32_t row_bytes = (p.K >> 8) * (C::kQ256 + C::kS256);
         for (uint32_t G = kConsumerWarps; G >= 1u; G >>= 1) {
-            uint32_t ns = (kSmemLimit - 1024u - fixed) / (G * row_bytes);
+            uint32_t ns = (kSmemLimit - 1024u - fixed) / (G * R * row_bytes);
             if (ns > kMaxStages) ns = kMaxStages;
             const uint32_t groups = kConsumerWarps / G;
-            if (ns >= (2u * groups > 6u ? 2u * groups : 6u)) {
+            // one row per warp: as many stages in flight as under the consumers; two rows per warp (twice the bytes under
+            // the consumers): at least two stages in flight
+            const uint32_t need = R == 1 ? (2u * groups > 6u ? 2u * groups : 6u) : groups + 2u;
+            if (ns >= need) {
                 p.group_warps = G;
                 p.groups = groups;
-                stage_bytes = G * row_bytes;
+                stage_bytes = G * R * row_bytes;
                 break;
             }
         }
@@ -534,7 +567,7 @@ static AcResult launch_one(const LaunchArgs& a, Params& p, bool whole_rows = fal
         }
         attr_set = true;
     }
-    const uint32_t NB = p.group_warps ? (p.N + p.group_warps - 1) / p.group_warps : (p.N + RB - 1) / RB;
+    const uint32_t NB = p.group_warps ? (p.N + p.group_warps * R - 1) / (p.group_warps * R) : (p.N + RB - 1) / RB;
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
     const uint32_t grid = NB < sms ? NB : sms;
     if (p.diag & 4u) gemv_bulk_kernel<TYPE, M, R><<<grid, kThreads, smem_bytes, a.stream>>>(p);
@@ -548,6 +581,17 @@ static AcResult launch_m(const LaunchArgs& a, Params& p) {
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
     // rows short enough for a ring of whole-row stages (two large copies per stage instead of two per row)
     if (!(p.diag & 2u)) {
+        if constexpr (M <= 2 && TYPE == T_Q4_K) {
+            // Two rows per warp share the activation loads: fewer instructions, but twice the bytes under the consumers
+            // and so a shallower ring. Measured on 28672 x 8192: 25.2 against 26.3 us at M = 1, 30.4 against 35.3 us at
+            // M = 2; on 11008 x 4096 and smaller it loses a few percent, so it serves the large matrices (diag bit 3
+            // forces it).
+            const uint64_t wbytes = (uint64_t)p.N * (p.K >> 8) * (Cfg<TYPE>::kQ256 + Cfg<TYPE>::kS256);
+            if ((p.diag & 8u) || wbytes >= (64ull << 20)) {
+                const AcResult r2 = launch_one<TYPE, M, 2>(a, p, true);
+                if (r2 != AC_ERR_INVALID_WORK_GROUP_SIZE) return r2;
+            }
+        }
         const AcResult r = launch_one<TYPE, M, 1>(a, p, true);
         if (r != AC_ERR_INVALID_WORK_GROUP_SIZE) return r;
     }
