@@ -85,8 +85,18 @@ GGML_PLUGIN = os.path.join(HERE, "libggml-ameva-b200.so")
 GGML_DRIVER = os.path.join(ROOT, "tests", "ggml_shim", "_build", "driver")
 
 
+def reference_root():
+    """A checkout of uno-km/ameva-compute, when one is around: AMEVA_REFERENCE_ROOT, or a directory named `reference`
+    beside this repository."""
+    for cand in (os.environ.get("AMEVA_REFERENCE_ROOT"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.isdir(cand):
+            return cand
+    return None
+
+
 def ggml_include_dir():
-    for cand in (os.environ.get("GGML_INCLUDE_DIR"), "/root/reference/include/ggml"):
+    ref = reference_root()
+    for cand in (os.environ.get("GGML_INCLUDE_DIR"), os.path.join(ref, "include", "ggml") if ref else None):
         if cand and os.path.exists(os.path.join(cand, "ggml-backend-impl.h")):
             return cand
     return None

@@ -22,8 +22,9 @@ template <bool WRITE_H>
 __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
                                                          uint32_t* __restrict__ ad, __half* __restrict__ ah, uint32_t M,
                                                          uint32_t K, uint32_t src_stride, uint32_t round_mode) {
+    pdl_trigger();   // the mul_mat behind this kernel may be scheduled already (it can request its weights meanwhile; it
+                     // waits for this grid before reading the quantized activations)
     pdl_wait();      // the activations may come from the kernel before (it let this one be scheduled early)
-    pdl_trigger();   // the mul_mat behind this kernel may be scheduled; it waits for this grid before reading
     const uint32_t U = K >> 5;
     const uint64_t total = (uint64_t)M * U;
     const uint64_t gi = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3;  // unit index
@@ -62,8 +63,9 @@ template <bool WRITE_H>
 __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
                                                          uint8_t* __restrict__ ab, __half* __restrict__ ah, uint32_t M,
                                                          uint32_t K, uint32_t src_stride, uint32_t mode) {
+    pdl_trigger();   // the mul_mat behind this kernel may be scheduled already (it can request its weights meanwhile; it
+                     // waits for this grid before reading the quantized activations)
     pdl_wait();      // the activations may come from the kernel before (it let this one be scheduled early)
-    pdl_trigger();   // the mul_mat behind this kernel may be scheduled; it waits for this grid before reading
     const uint32_t B = K >> 8;
     const uint64_t total = (uint64_t)M * B;
     const uint64_t gi = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -129,8 +131,9 @@ __global__ void __launch_bounds__(256) bitnet_norm_q8_kernel(const float* __rest
                                                              uint32_t* __restrict__ q, uint32_t* __restrict__ act,
                                                              uint2* __restrict__ qeo, uint32_t dim, float eps,
                                                              uint32_t mode, uint32_t do_norm) {
+    pdl_trigger();   // the mul_mat behind this kernel may be scheduled already (it can request its weights meanwhile; it
+                     // waits for this grid before reading the quantized activations)
     pdl_wait();      // the activations may come from the kernel before (it let this one be scheduled early)
-    pdl_trigger();   // the mul_mat behind this kernel may be scheduled; it waits for this grid before reading
     __shared__ float red[8];
     __shared__ int redi[8];
     const uint32_t row = blockIdx.x, t = threadIdx.x, words = dim >> 2;

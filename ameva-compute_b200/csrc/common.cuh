@@ -7,6 +7,7 @@
 #include <stdint.h>
 
 #include "../../include/ac_runtime_b200.h"
+#include "per_device.h"
 
 namespace amv {
 
@@ -50,7 +51,30 @@ inline AcResult check_launch() {
 // Device status codes written by kernels that give up on a bounded wait (never a trap).
 enum : uint32_t { DEV_STATUS_OK = 0, DEV_STATUS_WAIT_TIMEOUT = 1, DEV_STATUS_BAD_INDEX = 2 };
 
+inline int current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return -1;
+    }
+    return dev;
+}
+
 #ifdef __CUDACC__
+// Raises the dynamic shared-memory limit of `Kernel` on the current device, once per device (the attribute is kept per
+// device, so a second GPU used by the same process needs its own call).
+template <auto* Kernel>
+inline bool ensure_dynamic_smem(int bytes) {
+    static PerDeviceOnce once;
+    return once.run_once(current_device(), [&]() {
+        if (cudaFuncSetAttribute(Kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        return true;
+    });
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Programmatic dependent launch. The quantize and mul_mat kernels are launched with the attribute (launch_pdl) and begin
 // with pdl_wait, which returns when the preceding grid of the stream has completed and its writes are visible, followed

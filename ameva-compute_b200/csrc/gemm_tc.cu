@@ -929,10 +929,10 @@ static uint32_t choose_tok_tile(uint32_t M, uint32_t row_units, int units_reside
 // Units (CTAs, or CTA pairs) of the kernel that the device holds at once.
 template <int TYPE, bool PAIR>
 static int resident_units(uint32_t smem_bytes, int sm_count) {
-    static int cached = 0;
-    static uint32_t cached_smem = 0;
-    if (cached && cached_smem == smem_bytes) return cached;
+    static PerDeviceMemo memo;   // occupancy is a property of (device, kernel, shared-memory size)
+    const int dev = current_device();
     int n = 0;
+    if (memo.get(dev, smem_bytes, &n)) return n;
     if (PAIR) {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
@@ -959,8 +959,7 @@ static int resident_units(uint32_t smem_bytes, int sm_count) {
         }
         n = per_sm * sm_count;
     }
-    cached = n;
-    cached_smem = smem_bytes;
+    if (n > 0) memo.put(dev, smem_bytes, n);
     return n;
 }
 
@@ -979,21 +978,11 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
         return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return AC_ERR_DRIVER_SYMBOL_MISSING;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel<TYPE, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kSmemLimit) != cudaSuccess ||
-            cudaFuncSetAttribute(gemm_tc_kernel<TYPE, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kSmemLimit) != cudaSuccess ||
-            cudaFuncSetAttribute(gemm_tc_kernel<TYPE, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kSmemLimit) != cudaSuccess ||
-            cudaFuncSetAttribute(gemm_tc_kernel<TYPE, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kSmemLimit) != cudaSuccess) {
-            cudaGetLastError();
-            return AC_ERR_INVALID_WORK_GROUP_SIZE;
-        }
-        attr_set = true;
-    }
+    if (!ensure_dynamic_smem<gemm_tc_kernel<TYPE, false, false>>((int)kSmemLimit) ||
+        !ensure_dynamic_smem<gemm_tc_kernel<TYPE, true, false>>((int)kSmemLimit) ||
+        !ensure_dynamic_smem<gemm_tc_kernel<TYPE, false, true>>((int)kSmemLimit) ||
+        !ensure_dynamic_smem<gemm_tc_kernel<TYPE, true, true>>((int)kSmemLimit))
+        return AC_ERR_INVALID_WORK_GROUP_SIZE;
 
     Params p;
     memset(&p, 0, sizeof(p));

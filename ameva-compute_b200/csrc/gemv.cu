@@ -104,36 +104,23 @@ __device__ __forceinline__ void fq_quantize_q8_K(const float* __restrict__ X, ui
 // block: isum = sum nib*q - 8*sum(q); y += float(isum) * d_w * d_a
 // ---------------------------------------------------------------------------------------------------------------------
 template <int M, int R, bool DUMP, bool FQ = false>
-__global__ void __launch_bounds__(kGemvThreads)
-gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
-                 const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
-                 uint32_t K, uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+__device__ __forceinline__ void
+gemv_q4_0_body(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
+               const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
+               uint32_t K, uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode,
+               const uint32_t warp) {
     static_assert(!FQ || (M == 1 && !DUMP), "the fused quantize serves one activation row");
     constexpr int UN = M <= 2 ? 4 : 2;
     const uint32_t U = K >> 5;
-    const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    const uint32_t lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (!FQ && row0 >= N) return;
-    pdl_wait();      // the activations come from the preceding kernel
-    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
-    if constexpr (FQ) {
-        fq_quantize_q8_0(X, K, qmode);
-        if (row0 >= N) return;
-        AQ = reinterpret_cast<const int8_t*>(fq_smem);
-        AD = reinterpret_cast<const uint32_t*>(fq_smem + K);
-    }
-    float acc[R][M];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
     size_t rbase[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) rbase[r] = (size_t)min(row0 + r, N - 1) * U;
-
-    for (uint32_t u0 = lane; u0 < U; u0 += 32 * UN) {
-        uint4 wq[UN][R];
-        uint16_t ws[UN][R];
+    uint4 wq[UN][R];
+    uint16_t ws[UN][R];
+    auto load_weights = [&](uint32_t u0) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t u = u0 + 32 * i;
@@ -145,6 +132,25 @@ gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, co
                 }
             }
         }
+    };
+    // The weights do not depend on the kernel before this one: the first chunks are requested before the wait for it, so
+    // their HBM latency overlaps that kernel's tail (and, with FQ, the quantization of the row below).
+    load_weights(lane);
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching what it wrote)
+    pdl_wait();      // the activations come from the preceding kernel
+    if constexpr (FQ) {
+        fq_quantize_q8_0(X, K, qmode);
+        if (row0 >= N) return;
+        AQ = reinterpret_cast<const int8_t*>(fq_smem);
+        AD = reinterpret_cast<const uint32_t*>(fq_smem + K);
+    }
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+
+    for (uint32_t u0 = lane; u0 < U;) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t u = u0 + 32 * i;
@@ -175,6 +181,8 @@ gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, co
                 }
             }
         }
+        u0 += 32 * UN;
+        if (u0 < U) load_weights(u0);
     }
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -188,40 +196,36 @@ gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, co
         }
 }
 
+template <int M, int R, bool DUMP, bool FQ = false>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_q4_0_kernel(const uint4* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
+                 const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
+                 uint32_t K, uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+    gemv_q4_0_body<M, R, DUMP, FQ>(Q, S, AQ, AD, dst, sums, N, K, dst_stride, ep, X, qmode,
+                                   (blockIdx.x * kGemvThreads + threadIdx.x) >> 5);
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Q8_0 x Q8_0.  Q: 32 int8 per unit (256-bit loads), S: fp16 [N][U].  y += float(isum) * (d_w * d_a)
 // ---------------------------------------------------------------------------------------------------------------------
 template <int M, int R, bool DUMP, bool FQ = false>
-__global__ void __launch_bounds__(kGemvThreads)
-gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
-                 const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
-                 uint32_t K, uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+__device__ __forceinline__ void
+gemv_q8_0_body(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
+               const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
+               uint32_t K, uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode,
+               const uint32_t warp) {
     static_assert(!FQ || (M == 1 && !DUMP), "the fused quantize serves one activation row");
     constexpr int UN = M <= 2 ? 2 : 1;
     const uint32_t U = K >> 5;
-    const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    const uint32_t lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (!FQ && row0 >= N) return;
-    pdl_wait();      // the activations come from the preceding kernel
-    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
-    if constexpr (FQ) {
-        fq_quantize_q8_0(X, K, qmode);
-        if (row0 >= N) return;
-        AQ = reinterpret_cast<const int8_t*>(fq_smem);
-        AD = reinterpret_cast<const uint32_t*>(fq_smem + K);
-    }
-    float acc[R][M];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
     size_t rbase[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) rbase[r] = (size_t)min(row0 + r, N - 1) * U;
-
-    for (uint32_t u0 = lane; u0 < U; u0 += 32 * UN) {
-        u32x8 wq[UN][R];
-        uint16_t ws[UN][R];
+    u32x8 wq[UN][R];
+    uint16_t ws[UN][R];
+    auto load_weights = [&](uint32_t u0) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t u = u0 + 32 * i;
@@ -233,6 +237,23 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
                 }
             }
         }
+    };
+    load_weights(lane);   // before the wait: the weights do not depend on the kernel before this one
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching what it wrote)
+    pdl_wait();      // the activations come from the preceding kernel
+    if constexpr (FQ) {
+        fq_quantize_q8_0(X, K, qmode);
+        if (row0 >= N) return;
+        AQ = reinterpret_cast<const int8_t*>(fq_smem);
+        AD = reinterpret_cast<const uint32_t*>(fq_smem + K);
+    }
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+
+    for (uint32_t u0 = lane; u0 < U;) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t u = u0 + 32 * i;
@@ -260,6 +281,8 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
                 }
             }
         }
+        u0 += 32 * UN;
+        if (u0 < U) load_weights(u0);
     }
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -273,6 +296,15 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
         }
 }
 
+template <int M, int R, bool DUMP, bool FQ = false>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, const int8_t* __restrict__ AQ,
+                 const uint32_t* __restrict__ AD, float* __restrict__ dst, int32_t* __restrict__ sums, uint32_t N,
+                 uint32_t K, uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+    gemv_q8_0_body<M, R, DUMP, FQ>(Q, S, AQ, AD, dst, sums, N, K, dst_stride, ep, X, qmode,
+                                   (blockIdx.x * kGemvThreads + threadIdx.x) >> 5);
+}
+
 // ---------------------------------------------------------------------------------------------------------------------
 // Q4_K x Q8_K.  Q: 128 B per 256-block, S: 16 B per block (fp16 d, fp16 dmin, scales[12]).
 // A lane takes a 32-byte chunk = qs[32k .. 32k+31] of a block (k = 0..3): the low nibbles are the 32 weights of
@@ -281,30 +313,17 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
 //   y += (d*d_a)*float(isum) - (dmin*d_a)*float(mpart)          (block-integer form, ameva_mmqb.comp:10-16)
 // The four lanes of a block are an aligned lane group (DUMP reduces over them).
 // ---------------------------------------------------------------------------------------------------------------------
-template <int M, int R, bool DUMP, int UNV = 0, int MINB = 1, bool FQ = false>
-__global__ void __launch_bounds__(kGemvThreads, MINB)
-gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
-                 const uint8_t* __restrict__ AB, const DstList dl, int32_t* __restrict__ sums, uint32_t N, uint32_t K,
-                 uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+template <int M, int R, bool DUMP, int UNV = 0, bool FQ = false>
+__device__ __forceinline__ void
+gemv_q4_K_body(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
+               const uint8_t* __restrict__ AB, const DstList& dl, int32_t* __restrict__ sums, uint32_t N, uint32_t K,
+               uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode, const uint32_t warp) {
     static_assert(!FQ || (M == 1 && !DUMP), "the fused quantize serves one activation row");
     constexpr int UN = UNV ? UNV : (M <= 2 ? 2 : 1);
     const uint32_t B = K >> 8, C = K >> 6;  // blocks and 32-byte chunks per row
-    const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
+    const uint32_t lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (!FQ && row0 >= N) return;
-    pdl_wait();      // the activations come from the preceding kernel
-    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
-    if constexpr (FQ) {
-        fq_quantize_q8_K(X, K, qmode);
-        if (row0 >= N) return;
-        AQ = reinterpret_cast<const int8_t*>(fq_smem);
-        AB = fq_smem + K;
-    }
-    float acc[R][M];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
     const u32x8* qrow[R];
     const uint4* srow[R];
 #pragma unroll
@@ -313,10 +332,9 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
         qrow[r] = Q + blk * 4u;
         srow[r] = S + blk;
     }
-
-    for (uint32_t c0 = lane; c0 < C; c0 += 32 * UN) {
-        u32x8 wq[UN][R];
-        uint4 wsc[UN][R];
+    u32x8 wq[UN][R];
+    uint4 wsc[UN][R];
+    auto load_weights = [&](uint32_t c0) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t c = c0 + 32 * i;
@@ -328,6 +346,23 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
                 }
             }
         }
+    };
+    load_weights(lane);   // before the wait: the weights do not depend on the kernel before this one
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching what it wrote)
+    pdl_wait();      // the activations come from the preceding kernel
+    if constexpr (FQ) {
+        fq_quantize_q8_K(X, K, qmode);
+        if (row0 >= N) return;
+        AQ = reinterpret_cast<const int8_t*>(fq_smem);
+        AB = fq_smem + K;
+    }
+    float acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
+
+    for (uint32_t c0 = lane; c0 < C;) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t c = c0 + 32 * i;
@@ -392,6 +427,8 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
                 }
             }
         }
+        c0 += 32 * UN;
+        if (c0 < C) load_weights(c0);
     }
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -403,6 +440,59 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
                 if (M == 1 && ep.mode) ep.out[row0 + r] = epilogue_value(ep.mode, v, __ldg(ep.e + row0 + r));
             }
         }
+}
+
+template <int M, int R, bool DUMP, int UNV = 0, int MINB = 1, bool FQ = false>
+__global__ void __launch_bounds__(kGemvThreads, MINB)
+gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
+                 const uint8_t* __restrict__ AB, const DstList dl, int32_t* __restrict__ sums, uint32_t N, uint32_t K,
+                 uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
+    gemv_q4_K_body<M, R, DUMP, UNV, FQ>(Q, S, AQ, AB, dl, sums, N, K, dst_stride, ep, X, qmode,
+                                        (blockIdx.x * kGemvThreads + threadIdx.x) >> 5);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Grouped launch: one activation row against up to four weight matrices of the same type and K (the q / k / v or the
+// gate / up projections of a decoder layer, which share src1), one launch. The fp32 row is quantized once per CTA in
+// shared memory (the FQ path) and every warp serves R rows of one of the matrices: the rows of all matrices form one
+// row space, `row_end` holding the running totals. Results are those of the separate launches, bit for bit.
+// ---------------------------------------------------------------------------------------------------------------------
+struct WeightGroup {
+    const void* Q[4];
+    const void* S[4];
+    float* dst[4];
+    uint32_t row_end[4];   // rows of matrices 0..j, each matrix a multiple of 2 rows
+    uint32_t count;
+};
+
+template <int TYPE>   // 0 Q4_0, 1 Q8_0, 2 Q4_K
+__global__ void __launch_bounds__(kGemvThreads, TYPE == 2 ? 3 : 1)
+gemv_group_fq_kernel(const WeightGroup g, const float* __restrict__ X, uint32_t K, uint32_t qmode) {
+    const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5;
+    uint32_t row = warp * 2u, j = 0, start = 0;
+    const uint32_t total = g.row_end[g.count - 1];
+    if (row >= total) row = total - 2u;   // (idle warps of the last CTA repeat its last row pair: they must reach the barrier)
+#pragma unroll
+    for (uint32_t i = 0; i < 3u; ++i)
+        if (i + 1u < g.count && row >= g.row_end[i]) {
+            j = i + 1u;
+            start = g.row_end[i];
+        }
+    const uint32_t N = g.row_end[j] - start, w = (row - start) >> 1;
+    const Epi ep = {nullptr, nullptr, 0u};
+    if constexpr (TYPE == 0) {
+        gemv_q4_0_body<1, 2, false, true>((const uint4*)g.Q[j], (const uint16_t*)g.S[j], nullptr, nullptr, g.dst[j], nullptr,
+                                          N, K, N, ep, X, qmode, w);
+    } else if constexpr (TYPE == 1) {
+        gemv_q8_0_body<1, 2, false, true>((const u32x8*)g.Q[j], (const uint16_t*)g.S[j], nullptr, nullptr, g.dst[j], nullptr,
+                                          N, K, N, ep, X, qmode, w);
+    } else {
+        DstList dl;
+        dl.n = 1u;
+        dl.p[0] = g.dst[j];
+        gemv_q4_K_body<1, 2, false, 1, true>((const u32x8*)g.Q[j], (const uint4*)g.S[j], nullptr, nullptr, dl, nullptr, N, K,
+                                             N, ep, X, qmode, w);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -420,19 +510,11 @@ gemv_i2_s_kernel(const uint4* __restrict__ W, const int8_t* __restrict__ AQ, flo
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5, lane = threadIdx.x & 31u;
     const uint32_t row0 = warp * R;
     if (row0 >= N) return;
-    pdl_wait();      // the quantized activations come from the preceding kernel
-    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
-    int acc[R][M];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int m = 0; m < M; ++m) acc[r][m] = 0;
     size_t rbase[R];
 #pragma unroll
     for (int r = 0; r < R; ++r) rbase[r] = (size_t)min(row0 + r, N - 1) * C;
-
-    for (uint32_t c0 = lane; c0 < C; c0 += 32 * UN) {
-        uint4 wq[UN][R];
+    uint4 wq[UN][R];
+    auto load_weights = [&](uint32_t c0) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t c = c0 + 32 * i;
@@ -441,6 +523,17 @@ gemv_i2_s_kernel(const uint4* __restrict__ W, const int8_t* __restrict__ AQ, flo
                 for (int r = 0; r < R; ++r) wq[i][r] = ld_stream_u4(W + rbase[r] + c);
             }
         }
+    };
+    load_weights(lane);   // before the wait: the weights do not depend on the kernel before this one
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching what it wrote)
+    pdl_wait();      // the quantized activations come from the preceding kernel
+    int acc[R][M];
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0;
+
+    for (uint32_t c0 = lane; c0 < C;) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t c = c0 + 32 * i;
@@ -469,6 +562,8 @@ gemv_i2_s_kernel(const uint4* __restrict__ W, const int8_t* __restrict__ AQ, flo
                 }
             }
         }
+        c0 += 32 * UN;
+        if (c0 < C) load_weights(c0);
     }
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -656,6 +751,49 @@ static AcResult launch_fq(const LaunchArgs& a) {
     }
     return check_launch();
 }
+// ameva_mmvqg_q4_0_fq / ameva_mmvqg_q8_0_fq / ameva_mmvqgb_q4_K_fq: ONE activation row against up to four weight
+// matrices of the same type and K in one launch (the q / k / v or gate / up projections of a decoder layer share src1;
+// the reference quantizes such a src1 once, ggml-ameva.cpp:2154-2158, 2738-2749, and still launches per projection).
+//   bindings (Q, S, dst f32 [N_j]) of matrix 0, 1, 2, 3 (unused slots repeat matrix 0), then 12: x f32 [K]
+//   push {K, quantize mode, count (1..4), N_0, N_1, N_2, N_3}     every N_j a multiple of 2
+// The bits of every dst are those of the separate ameva_mmv*_fq launches.
+template <int TYPE>
+static AcResult launch_group_fq(const LaunchArgs& a) {
+    const uint32_t K = a.push[0], qmode = a.push[1], count = a.push[2];
+    const uint32_t kmask = TYPE == 2 ? 255u : 31u;
+    if (count == 0 || count > 4u || K == 0 || (K & kmask) || qmode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
+    if (K > kFusedQuantMaxK) return AC_ERR_INVALID_SHAPE;
+    const uint64_t units = TYPE == 2 ? (K >> 8) : (K >> 5);
+    const uint64_t qb = TYPE == 0 ? kQ40QBytes : TYPE == 1 ? kQ80QBytes : kQ4KQBytes, sb = TYPE == 2 ? kQ4KSBytes : 2u;
+    WeightGroup g;
+    memset(&g, 0, sizeof(g));
+    g.count = count;
+    uint64_t rows = 0;
+    for (uint32_t j = 0; j < count; ++j) {
+        const uint32_t N = a.push[3 + j];
+        if (N == 0 || (N & 1u)) return AC_ERR_KERNEL_ARG_INVALID;
+        if (a.range[3 * j] < (uint64_t)N * units * qb || a.range[3 * j + 1] < (uint64_t)N * units * sb ||
+            a.range[3 * j + 2] < (uint64_t)N * 4u)
+            return AC_ERR_INVALID_BUFFER_SIZE;
+        if (((uintptr_t)a.ptr[3 * j] & 31u) || ((uintptr_t)a.ptr[3 * j + 1] & 15u)) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+        g.Q[j] = a.ptr[3 * j];
+        g.S[j] = a.ptr[3 * j + 1];
+        g.dst[j] = (float*)a.ptr[3 * j + 2];
+        rows += N;
+        if (rows > 0x7fffffffull) return AC_ERR_INVALID_SHAPE;
+        g.row_end[j] = (uint32_t)rows;
+    }
+    for (uint32_t j = count; j < 4u; ++j) g.row_end[j] = (uint32_t)rows;
+    if (a.range[12] < (uint64_t)K * 4u) return AC_ERR_INVALID_BUFFER_SIZE;
+    if ((uintptr_t)a.ptr[12] % 16u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    const size_t smem = (size_t)K + (TYPE == 2 ? (size_t)units * kABBytes : (size_t)units * 4u);
+    launch_pdl(gemv_group_fq_kernel<TYPE>, dim3(gemv_blocks<2>((uint32_t)rows)), dim3(kGemvThreads), smem, a.stream, g,
+               (const float*)a.ptr[12], K, qmode);
+    return check_launch();
+}
+AcResult launch_mmvqg_q4_0_fq(const LaunchArgs& a) { return launch_group_fq<0>(a); }
+AcResult launch_mmvqg_q8_0_fq(const LaunchArgs& a) { return launch_group_fq<1>(a); }
+AcResult launch_mmvqgb_q4_K_fq(const LaunchArgs& a) { return launch_group_fq<2>(a); }
 AcResult launch_mmvq_q4_0_fq(const LaunchArgs& a) { return launch_fq<0>(a); }
 AcResult launch_mmvq_q8_0_fq(const LaunchArgs& a) { return launch_fq<1>(a); }
 AcResult launch_mmvqb_q4_K_fq(const LaunchArgs& a) { return launch_fq<2>(a); }

@@ -558,15 +558,7 @@ static AcResult launch_one(const LaunchArgs& a, Params& p, bool whole_rows = fal
     if (stages < 2u) return AC_ERR_INVALID_WORK_GROUP_SIZE;
     p.stages = stages;
     const uint32_t smem_bytes = stages * stage_bytes + fixed;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(gemv_bulk_kernel<TYPE, M, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)kSmemLimit) != cudaSuccess) {
-            cudaGetLastError();
-            return AC_ERR_INVALID_WORK_GROUP_SIZE;
-        }
-        attr_set = true;
-    }
+    if (!ensure_dynamic_smem<gemv_bulk_kernel<TYPE, M, R>>((int)kSmemLimit)) return AC_ERR_INVALID_WORK_GROUP_SIZE;
     const uint32_t NB = p.group_warps ? (p.N + p.group_warps * R - 1) / (p.group_warps * R) : (p.N + RB - 1) / RB;
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
     const uint32_t grid = NB < sms ? NB : sms;

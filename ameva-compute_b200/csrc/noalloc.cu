@@ -63,7 +63,11 @@ AcResult scratch_for_current_device(uint8_t** out) {
 // w_scales: one fp16 per 32 weights, both row-major over [N][K/32]), quantizing x per 32 values on the fly exactly as
 // the regular path does. All pointers are device addresses on the current device; x rows are x_stride floats apart
 // (a multiple of 4), dst rows dst_stride floats apart. The work is enqueued on `stream` (a cudaStream_t; NULL is the
-// default stream) and not waited for.
+// default stream) and not waited for. The kernels read x and w_payload with 16-byte loads, w_scales with 2-byte loads
+// and write dst as floats: x and w_payload must be 16-byte aligned, w_scales 2-byte and dst 4-byte aligned, otherwise
+// the call is refused with AC_ERR_BUFFER_ALIGNMENT_INVALID before anything is launched (a misaligned device load would
+// be a fault on the GPU, not an error code). The scratch used is the array of the device that is current at the call,
+// which must be the device `stream` belongs to.
 //
 // The first call on each device looks up the scratch array's address (and may load the module): make that call before
 // starting any stream capture. The function calls no cudaMalloc, cudaFree or allocating library routine.
@@ -73,6 +77,8 @@ extern "C" AcResult ac_b200_mul_mat_q4_0_static(void* stream, const void* w_payl
     if (!w_payload || !w_scales || !x || !dst) return AC_ERR_NULL_POINTER;
     if (M == 0 || N == 0 || K == 0 || (K & 31u) || x_stride < K || (x_stride & 3u) || dst_stride < N || round_mode > 1u)
         return AC_ERR_KERNEL_ARG_INVALID;
+    if (((uintptr_t)x & 15u) || ((uintptr_t)w_payload & 15u) || ((uintptr_t)w_scales & 1u) || ((uintptr_t)dst & 3u))
+        return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     if (M > kMaxRows || K > kMaxK) {
         const size_t want = (size_t)M * K + (size_t)M * (K / 32) * 4;
         ac_runtime_set_error((int32_t)AC_ERR_INVALID_SHAPE, AMEVA_BACKEND_OP_DISPATCH, 0, want, kScratchBytes);

@@ -43,6 +43,9 @@ AcResult launch_mmvq_q4_0_fq(const LaunchArgs&);
 AcResult launch_mmvq_q8_0_fq(const LaunchArgs&);
 AcResult launch_mmvqb_q4_K_fq(const LaunchArgs&);
 AcResult launch_mmvqb_q4_K_dump(const LaunchArgs&);
+AcResult launch_mmvqg_q4_0_fq(const LaunchArgs&);
+AcResult launch_mmvqg_q8_0_fq(const LaunchArgs&);
+AcResult launch_mmvqgb_q4_K_fq(const LaunchArgs&);
 AcResult launch_bitnet_gemv_i2_s(const LaunchArgs&);
 AcResult launch_bitnet_gemv_i2_s_acc(const LaunchArgs&);
 
@@ -77,6 +80,9 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvq_q8_0_fq", 4, 12, {256, 1, 1}, launch_mmvq_q8_0_fq},
     {"ameva_mmvqb_q4_K_fq", 4, 12, {256, 1, 1}, launch_mmvqb_q4_K_fq},
     {"ameva_mmvqb_q4_K_dump", 6, 16, {256, 1, 1}, launch_mmvqb_q4_K_dump},
+    {"ameva_mmvqg_q4_0_fq", 13, 28, {256, 1, 1}, launch_mmvqg_q4_0_fq},
+    {"ameva_mmvqg_q8_0_fq", 13, 28, {256, 1, 1}, launch_mmvqg_q8_0_fq},
+    {"ameva_mmvqgb_q4_K_fq", 13, 28, {256, 1, 1}, launch_mmvqgb_q4_K_fq},
     {"bitnet_gemv_i2_s_l32w1", 4, 24, {32, 4, 1}, launch_bitnet_gemv_i2_s},
     {"bitnet_gemv_i2_s_l16w2", 4, 24, {16, 8, 1}, launch_bitnet_gemv_i2_s},
     {"bitnet_gemv_i2_s_l8w4", 4, 24, {8, 16, 1}, launch_bitnet_gemv_i2_s},

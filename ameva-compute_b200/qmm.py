@@ -352,6 +352,72 @@ class MulMat:
                 b.destroy()
 
 
+class MulMatGroup:
+    """One activation row against several weight matrices that share it (the q / k / v or the gate / up projections of a
+    decoder layer), as ONE launch: the row is quantized once per CTA inside the kernel and every output is bit-equal to
+    the separate launches. The reference quantizes such a shared src1 once and reuses it
+    (adapters/llama/ggml-ameva/ggml-ameva.cpp:2154-2158, 2738-2749); on B200 the launches themselves are what a small
+    projection pays for, so they are merged too. Up to four matrices of one type and K, every N a multiple of 2,
+    K <= FUSED_QUANT_MAX_K; anything else is refused (callers fall back to one MulMat per matrix)."""
+
+    def __init__(self, ctx: rt.Context, weights, *, round_mode: int = ROUND_NEAREST_EVEN, q8k_mode: int = Q8K_GGML) -> None:
+        views = [w if isinstance(w, WeightView) else w.view(0, w.N) for w in weights]
+        if not 1 <= len(views) <= 4:
+            raise MulMatUnsupported("a group holds one to four weight matrices")
+        t, K = views[0].weight.type, views[0].weight.K
+        if t not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K):
+            raise MulMatUnsupported("grouped launches are built for Q4_0 / Q8_0 / Q4_K")
+        for v in views:
+            if v.weight.type != t or v.weight.K != K:
+                raise MulMatUnsupported("the matrices of a group share the type and K")
+            why = unsupported_reason(t, 1, v.rows, K)
+            if why:
+                raise MulMatUnsupported(why)
+            if v.rows % 2:
+                raise MulMatUnsupported("grouped launches need an even number of weight rows per matrix")
+        if K > FUSED_QUANT_MAX_K:
+            raise MulMatUnsupported(f"K={K} above {FUSED_QUANT_MAX_K}: the quantized row does not fit shared memory")
+        self.ctx, self.type, self.K, self.views = ctx, t, K, views
+        self.mode = q8k_mode if t == GGML_TYPE_Q4_K else round_mode
+        self.binds = [_bindings_for(v) for v in views]
+        self.path = "mmvqg-fq"
+
+    def record(self, batch: rt.Batch, x: rt.Buffer, dsts, *, x_offset: int = 0, dst_offsets=None) -> None:
+        """x: fp32 [K] at byte x_offset (64-byte aligned); dsts[j]: fp32 [N_j] at byte dst_offsets[j]."""
+        if len(dsts) != len(self.views):
+            raise MulMatUnsupported("one destination per matrix")
+        offs = list(dst_offsets or [0] * len(dsts))
+        if x_offset % 64 or any(o % 64 for o in offs):
+            raise MulMatUnsupported("binding offsets must be 64-byte aligned")
+        binds = []
+        for j in range(4):
+            jj = j if j < len(self.views) else 0
+            q, s_ = self.binds[jj]
+            binds += [q, s_, (dsts[jj], offs[jj], self.views[jj].rows * 4)]
+        binds.append((x, x_offset, self.K * 4))
+        ns = [v.rows for v in self.views] + [0] * (4 - len(self.views))
+        fam = "ameva_mmvqgb" if self.type == GGML_TYPE_Q4_K else "ameva_mmvqg"
+        total = sum(v.rows for v in self.views)
+        batch.dispatch(self.ctx.kernel(f"{fam}_{TYPE_NAMES[self.type]}_fq"), binds,
+                       [self.K, self.mode, len(self.views)] + ns, ((total + 15) // 16, 1, 1))
+
+    def run(self, x: rt.Buffer, dsts, **kw) -> float:
+        batch = self.ctx.batch(8)
+        try:
+            self.record(batch, x, dsts, **kw)
+            ev = batch.submit()
+            try:
+                ev.wait()
+                return ev.gpu_duration_us()
+            finally:
+                ev.destroy()
+        finally:
+            batch.destroy()
+
+    def destroy(self) -> None:
+        pass
+
+
 def q8_0_blocks_from_scratch(q: np.ndarray, d_bits: np.ndarray) -> np.ndarray:
     """Reassembles ggml Q8_0 block bytes (fp16 d + 32 int8) from the SoA scratch, for byte comparison with a CPU
     quantizer."""

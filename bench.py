@@ -5,22 +5,29 @@
 
 A step is one pass of the hot path over one batch of synthetic input: on-the-fly activation quantization followed by
 the quantized mul_mat. The default workload is benchmark configuration 2 (Q8_0 x Q8_0 prefill GEMM, W 11008 x 4096,
-M = 512 tokens); `--workload` selects another configuration (cfg1, cfg3-*, cfg4-*, cfg5-*).
+M = 512 tokens), the configuration the M = 512 half of the metric is quoted on; the line also carries a `decode` object
+(the M = 1 half of the metric: configuration 1, the largest decode shape and the grouped q/k/v launch) and a `sharded`
+object (the row-sharded configuration-5 shapes at this number of GPUs). `--workload` makes another configuration the
+primary one (cfg1, cfg3-*, cfg4-*, cfg5-*).
 
-Timing: W >= 3 untimed warm-up steps, then exactly K steps recorded into one batch on the runtime's stream and timed
-with CUDA events on that stream, bracketed by a barrier and a device synchronize, max over ranks. Every step reads a
-different copy of the weights from a rotating pool larger than L2. `value` is the device-resident throughput; `e2e` goes
-through the same public API with host buffers (pinned), the host->device copy of the activations and the device->host
-copy of the result inside the timed region.
+Timing: W >= 3 untimed warm-up steps, then exactly K steps on the runtime's stream, timed with CUDA events on that
+stream, bracketed by a barrier and a device synchronize, max over ranks. Every step reads a different copy of the
+weights from a rotating pool larger than L2. On one GPU the steps are replayed from instantiated batches (CUDA graphs);
+`value` is the device-resident throughput; `e2e` goes through the same public API with pinned host buffers, the
+host->device copy of the activations and the device->host copy of the result inside the timed region.
 
-With N > 1 (launched by torch.distributed.run) the weight rows are sharded over the ranks (strong scaling: the total
-work is fixed). Every rank owns a full [M][N] output shared with the other ranks over CUDA IPC; the mul_mat's epilogue
-stores the rank's rows into every rank's output over NVLink and a flag barrier kernel closes the step, so the exchange
-is part of this library's kernels and of the timed region. Kernels without that epilogue (I2_S) fall
-back to an NCCL all-gather of the fp32 output plus a permute, also inside the timed region.
+With N > 1 (launched by torch.distributed.run):
+  * the primary workload runs data-parallel over tokens: every rank holds the whole weight matrix and processes its own
+    batch of M tokens, no exchange ("scaling": "weak"; a 47 MB matrix is not worth sharding, a step takes ~50 us);
+  * the `sharded` object holds the shapes that are row-sharded over the ranks (configuration 5): every rank computes
+    its slice of the output features and the ranks assemble the full [M][N] fp32 output on every rank, inside the timed
+    region (strong scaling). `--exchange` selects how: "copy" (each rank's column block is pushed to the peers by the
+    copy engines over NVLink, pipelined against the mul_mat of the next token chunk, closed by a flag barrier kernel),
+    "fused" (the mul_mat kernels' epilogues store to every rank's output) or "nccl" (all-gather + permute).
 
 `--impl reference` times the CPU implementation of the same path (the oracle: a C restatement of the ggml CPU
-arithmetic, or for I2_S the reference's own CPU kernel) on the host cores, on a bounded sample of the workload.
+arithmetic, or for I2_S the reference's own CPU kernel) on the host cores, on a bounded sample of the workload; under
+torch.distributed.run rank 0 alone runs it, with all host threads.
 """
 from __future__ import annotations
 
@@ -42,10 +49,12 @@ sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 Q4_0, Q8_0, Q4_K, I2_S = 2, 8, 12, 36
 WORKLOADS = {
-    # name: (type, M, N, K, weight std, description)
+    # name: (type, M, N (a tuple: several matrices sharing the activation row, one launch), K, weight std, description)
     "cfg1": (Q4_0, 1, 4096, 4096, 0.02, "Q4_0 x Q8_0 decode GEMV 4096x4096 M=1"),
     "cfg2": (Q8_0, 512, 11008, 4096, 0.02, "Q8_0 x Q8_0 prefill GEMM 11008x4096 M=512"),
     "cfg3-qkvo-m1": (Q4_K, 1, 4096, 4096, 0.02, "Q4_K x Q8_K 4096x4096 M=1"),
+    "cfg3-qkv-m1": (Q4_K, 1, (4096, 4096, 4096), 4096, 0.02, "Q4_K x Q8_K q,k,v 3 x 4096x4096 M=1, one launch"),
+    "cfg3-gateup-m1": (Q4_K, 1, (11008, 11008), 4096, 0.02, "Q4_K x Q8_K gate,up 2 x 11008x4096 M=1, one launch"),
     "cfg3-gate-m1": (Q4_K, 1, 11008, 4096, 0.02, "Q4_K x Q8_K 11008x4096 M=1"),
     "cfg3-down-m1": (Q4_K, 1, 4096, 11008, 0.02, "Q4_K x Q8_K 4096x11008 M=1"),
     "cfg3-gate-m8": (Q4_K, 8, 11008, 4096, 0.02, "Q4_K x Q8_K 11008x4096 M=8"),
@@ -57,6 +66,8 @@ WORKLOADS = {
     "cfg5-down-m1": (Q4_K, 1, 8192, 28672, 0.01, "Q4_K x Q8_K 8192x28672 M=1"),
     "cfg5-up-m2048": (Q4_K, 2048, 28672, 8192, 0.01, "Q4_K x Q8_K 28672x8192 M=2048"),
 }
+DECODE_LINES = ("cfg1", "cfg3-qkv-m1", "cfg5-up-m1")      # the M = 1 half of the metric, in the default line
+SHARDED_LINES = ("cfg5-up-m2048", "cfg5-up-m1")           # the row-sharded shapes, in every line
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (bytes), by workload and kernel path
@@ -72,13 +83,18 @@ def peaks():
     return {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
 
 
+def n_list(N):
+    return list(N) if isinstance(N, (tuple, list)) else [N]
+
+
 def weight_bytes(t, N, K):
-    return {Q4_0: 18 * N * K // 32, Q8_0: 34 * N * K // 32, Q4_K: 144 * N * K // 256, I2_S: N * K // 4}[t]
+    n = sum(n_list(N))
+    return {Q4_0: 18 * n * K // 32, Q8_0: 34 * n * K // 32, Q4_K: 144 * n * K // 256, I2_S: n * K // 4}[t]
 
 
 def algorithmic_bytes(t, M, N, K):
     """packed weights (incl. scales) + fp32 activations read + fp32 output written, per pass."""
-    return weight_bytes(t, N, K) + 4 * M * K + 4 * M * N
+    return weight_bytes(t, N, K) + 4 * M * K + 4 * M * sum(n_list(N))
 
 
 class ClockSampler:
@@ -136,84 +152,109 @@ def cpu_threads():
 
 
 def make_inputs(t, M, N, K, std, seed=0):
+    """Weights (one ggml block array per matrix of the workload), per-tensor scale, activations."""
     from helpers import make_acts, make_weights
-    blocks, scale = make_weights(t, N, K, seed, std)
+    blocks, scale = [], 1.0
+    for j, n in enumerate(n_list(N)):
+        b, scale = make_weights(t, n, K, seed + 7 * j, std)
+        blocks.append(b)
     return blocks, scale, make_acts(M, K, seed + 1)
 
 
-def cpu_pass(t, blocks, scale, x, N, K, nthreads=0):
-    """One pass of the path on the CPU (quantize activations + mul_mat); returns seconds."""
+def cpu_pass(t, blocks_list, scale, x, N, K, nthreads):
+    """One pass of the path on the CPU (quantize activations once + one mul_mat per matrix); returns seconds."""
     import oracle
     M = x.shape[0]
     t0 = time.perf_counter()
     if t in (Q4_0, Q8_0):
         aq = oracle.quantize_q8_0(x)
-        (oracle.mul_mat_q4_0_q8_0 if t == Q4_0 else oracle.mul_mat_q8_0_q8_0)(blocks, aq, M, N, K, False, nthreads)
+        for blocks, n in zip(blocks_list, n_list(N)):
+            (oracle.mul_mat_q4_0_q8_0 if t == Q4_0 else oracle.mul_mat_q8_0_q8_0)(blocks, aq, M, n, K, False, nthreads)
     elif t == Q4_K:
-        oracle.mul_mat_q4_K_q8_K(blocks, oracle.quantize_q8_K(x), M, N, K, False, nthreads)
+        aq = oracle.quantize_q8_K(x)
+        for blocks, n in zip(blocks_list, n_list(N)):
+            oracle.mul_mat_q4_K_q8_K(blocks, aq, M, n, K, False, nthreads)
     else:
         q, dq, _ = oracle.quantize_i8_token(x)
-        if oracle.ref_available() and M == 1:   # the reference's own kernel (single vector per call)
-            y = oracle.ref_vec_dot_i2_i8_s(blocks, q[0], N, K)
-            y *= np.float32(dq[0]) * np.float32(scale)
-        else:
-            oracle.mul_mat_i2_s_i8(blocks, scale, q, dq, M, N, K, nthreads)
+        for blocks, n in zip(blocks_list, n_list(N)):
+            if oracle.ref_available() and M == 1:   # the reference's own kernel (single vector per call)
+                y = oracle.ref_vec_dot_i2_i8_s(blocks, q[0], n, K)
+                y *= np.float32(dq[0]) * np.float32(scale)
+            else:
+                oracle.mul_mat_i2_s_i8(blocks, scale, q, dq, M, n, K, nthreads)
     return time.perf_counter() - t0
 
 
 def unit_value(unit, t, M, N, K, seconds):
     if unit == "TFLOP/s":
-        return 2.0 * M * N * K / seconds / 1e12
+        return 2.0 * M * sum(n_list(N)) * K / seconds / 1e12
     return algorithmic_bytes(t, M, N, K) / seconds / 1e9
 
 
-def run_cpu_baseline(t, M, N, K, blocks, scale, x, unit, budget_s=15.0):
+def cpu_kind(t, M):
+    import oracle
+    return "reference" if (t == I2_S and M == 1 and oracle.ref_available()) else "port"
+
+
+def cpu_build_note():
+    import oracle
+    return oracle.build_flavour() if hasattr(oracle, "build_flavour") else "portable -O3 build"
+
+
+def run_cpu_baseline(t, M, N, K, blocks, scale, x, unit, budget_s=12.0):
     """Times the CPU path on a bounded sample: the first Ms token rows, Ms sized from a probe so the timed pass costs
     roughly budget_s. Returns the cpu_baseline object."""
     import oracle
-    kind = "reference" if (t == I2_S and M == 1 and oracle.ref_available()) else "port"
-    cores = 1 if kind == "reference" else min(cpu_threads(), oracle.num_threads())
-    probe_m = 1
-    dt = cpu_pass(t, blocks, scale, x[:probe_m], N, K)
-    dt = min(dt, cpu_pass(t, blocks, scale, x[:probe_m], N, K))
-    ms = int(max(1, min(M, budget_s / max(dt, 1e-6))))
-    if ms > 1:
-        dt = cpu_pass(t, blocks, scale, x[:ms], N, K)
-    else:
-        reps = int(max(1, min(200, budget_s / max(dt, 1e-6))))
-        dt = min(cpu_pass(t, blocks, scale, x[:1], N, K) for _ in range(min(reps, 20)))
+    kind = cpu_kind(t, M)
+    cores = 1 if kind == "reference" else cpu_threads()
+    with oracle.timing_build():
+        dt = min(cpu_pass(t, blocks, scale, x[:1], N, K, cores) for _ in range(2))
+        ms = int(max(1, min(M, budget_s / max(dt, 1e-6))))
+        if ms > 1:
+            dt = cpu_pass(t, blocks, scale, x[:ms], N, K, cores)
+        else:
+            reps = int(max(1, min(20, budget_s / max(dt, 1e-6))))
+            dt = min(cpu_pass(t, blocks, scale, x[:1], N, K, cores) for _ in range(reps))
+        note = cpu_build_note()
     return {"value": unit_value(unit, t, ms, N, K, dt), "unit": unit, "cores": cores, "kind": kind,
-            "sample": f"{ms} of {M} token rows x all {N} weight rows, one pass, {dt * 1e3:.1f} ms"}
+            "sample": f"{ms} of {M} token rows x all {sum(n_list(N))} weight rows, one pass, {dt * 1e3:.1f} ms", "build": note}
+
+
+def workload_config(name):
+    t, M, N, K, std, desc = WORKLOADS[name]
+    return {"workload": f"{name}: {desc}", "M": M, "N": sum(n_list(N)), "K": K}
 
 
 def reference_arm(args, name):
     t, M, N, K, std, desc = WORKLOADS[name]
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     unit = "TFLOP/s" if M > GEMV_MAX_M else "GB/s"
     import oracle
     blocks, scale, x = make_inputs(t, M, N, K, std)
-    probe = min(cpu_pass(t, blocks, scale, x[:1], N, K) for _ in range(2))
-    per_step_budget = max(0.5, 60.0 / max(1, args.steps + args.warmup))
-    ms = int(max(1, min(M, per_step_budget / max(probe, 1e-6))))
-    for _ in range(args.warmup):
-        cpu_pass(t, blocks, scale, x[:ms], N, K)
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        cpu_pass(t, blocks, scale, x[:ms], N, K)
-    dt = (time.perf_counter() - t0) / args.steps
+    kind = cpu_kind(t, M)
+    cores = 1 if kind == "reference" else cpu_threads()   # explicit: launchers set OMP_NUM_THREADS=1 for their ranks
+    with oracle.timing_build():
+        probe = min(cpu_pass(t, blocks, scale, x[:1], N, K, cores) for _ in range(2))
+        per_step_budget = max(0.5, 60.0 / max(1, args.steps + args.warmup))
+        ms = int(max(1, min(M, per_step_budget / max(probe, 1e-6))))
+        for _ in range(args.warmup):
+            cpu_pass(t, blocks, scale, x[:ms], N, K, cores)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            cpu_pass(t, blocks, scale, x[:ms], N, K, cores)
+        dt = (time.perf_counter() - t0) / args.steps
+        note = cpu_build_note()
     val = unit_value(unit, t, ms, N, K, dt)
-    kind = "reference" if (t == I2_S and ms == 1 and oracle.ref_available()) else "port"
-    cores = 1 if kind == "reference" else min(cpu_threads(), oracle.num_threads())
-    sample = f"{ms} of {M} token rows x all {N} weight rows per step"
+    sample = f"{ms} of {M} token rows x all {sum(n_list(N))} weight rows per step"
+    detail = {"sample": sample, "host": ("CPU restatement of the ggml CPU arithmetic" if kind == "port" else
+                                         "reference's own ggml_vec_dot_i2_i8_s (scalar branch)") + ", " + note}
     print(json.dumps({
         "impl": "reference", "metric": metric_name(name), "value": val, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": f"{name}: {desc}", "sample": sample, "host": "CPU restatement of the ggml CPU arithmetic"
-                   if kind == "port" else "reference's own ggml_vec_dot_i2_i8_s (scalar branch)"},
-        "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": kind, "sample": sample},
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 dot, fp32 accumulate", "data": "synthetic",
+        "config": workload_config(name), "config_detail": detail,
+        "cpu_baseline": {"value": val, "unit": unit, "cores": cores, "kind": kind, "sample": sample, "build": note},
         "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -224,6 +265,447 @@ def metric_name(name):
         f"quant mul_mat GB/s (% of HBM) at M={M}"
 
 
+class Env:
+    """What every measurement shares: the process's rank, the runtime context, its stream as a torch stream."""
+
+    def __init__(self, args):
+        import torch
+        self.args, self.torch = args, torch
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        torch.cuda.set_device(self.local_rank)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
+        self.pkg = importlib.import_module("ameva-compute_b200")
+        self.rt, self.qmm, self.shard = self.pkg.runtime, self.pkg.qmm, self.pkg.shard
+        self.ctx = self.rt.init()
+        self.stream = torch.cuda.ExternalStream(self.ctx.stream, device=torch.device("cuda", self.local_rank))
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+        self.ctx.synchronize()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, seconds):
+        if self.dist is None:
+            return seconds
+        tt = self.torch.tensor([seconds], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(tt, op=self.dist.ReduceOp.MAX)
+        return float(tt.item())
+
+
+class Measurement:
+    """One workload on this process's GPU. mode: "single" (one GPU), "replicas" (N > 1, every rank the whole matrix and
+    its own tokens, no exchange) or "sharded" (N > 1, weight rows split over the ranks, output assembled on every rank)."""
+
+    def __init__(self, env: Env, name: str, mode: str):
+        self.env, self.name, self.mode = env, name, mode
+        args, rt, qmm, shard, ctx = env.args, env.rt, env.qmm, env.shard, env.ctx
+        t, M, N, K, std, desc = WORKLOADS[name]
+        self.t, self.M, self.N, self.K, self.desc = t, M, N, K, desc
+        self.grouped = isinstance(N, tuple)
+        self.Ntot = sum(n_list(N))
+        self.unit = "TFLOP/s" if M > GEMV_MAX_M else "GB/s"
+        world, rank = (env.world, env.rank) if mode == "sharded" else (1, 0)
+        self.blocks, self.scale, self.x = make_inputs(t, M, N, K, std)
+        if mode == "replicas":   # every rank its own batch of tokens
+            from helpers import make_acts
+            self.x = make_acts(M, K, 1 + env.rank)
+        if self.grouped and mode == "sharded":
+            raise SystemExit("grouped workloads are not sharded")
+        n0 = n_list(N)[0]
+        self.parts = shard.partition_rows(n0, world)
+        self.row0, self.rows = self.parts[rank]
+        self.pad = shard.padded_rows(n0, world)
+        # rotating pool of weight copies larger than L2, so that no step finds its weights cached
+        if self.grouped:
+            my_blocks = self.blocks
+            self.shard_bytes = weight_bytes(t, N, K)
+        else:
+            per_row = self.blocks[0].reshape(n0, -1).shape[1]
+            my_blocks = [self.blocks[0].reshape(n0, per_row)[self.row0:self.row0 + self.rows]]
+            self.shard_bytes = weight_bytes(t, max(self.rows, 1), K)
+        self.pool_n = max(2, min(64, -(-2 * L2_BYTES // max(self.shard_bytes, 1)) + 1))
+        streamed = {"auto": None, "register": False, "streamed": True}[args.gemv]
+        self.weights, self.mms = [], []
+        for _ in range(self.pool_n):
+            if self.grouped:
+                ws = [qmm.QuantWeight.from_ggml(ctx, t, b, n, K, self.scale) for b, n in zip(my_blocks, n_list(N))]
+                self.weights.append(ws)
+                self.mms.append(qmm.MulMatGroup(ctx, ws))
+            else:
+                w = qmm.QuantWeight.from_ggml(ctx, t, my_blocks[0], self.rows, K, self.scale)
+                self.weights.append([w])
+                self.mms.append(qmm.MulMat(ctx, w, M, streamed=streamed, fused_quantize=not args.no_fused_quantize))
+        self.x_dev = ctx.buffer(data=self.x)
+        self.probe_sink = ctx.buffer(64)
+        self.launches_per_step = 0
+        self.replay_cache = {}
+        self.keep = []
+        # output exchange of the sharded run
+        self.exchange = "none"
+        self.ex = None
+        self.gathered_t = self.out_full_t = self.out_local_t = None
+        tc_path = (not self.grouped) and M > GEMV_MAX_M and self.mms[0].tc_ok
+        if mode == "sharded" and world > 1:
+            want = args.exchange
+            fused_ok = t != I2_S and (tc_path or (M <= GEMV_MAX_M and K % 256 == 0))
+            if want == "fused" and not fused_ok:
+                want = "nccl"
+            self.exchange = want
+        if self.exchange in ("fused", "copy"):
+            self.ex = qmm.PeerExchange(ctx, rank, world, M * n0 * 4)
+            handles = [None] * world
+            env.dist.all_gather_object(handles, self.ex.handles())
+            self.ex.connect(handles)
+            self.out_buf, self.out_off, self.out_stride, self.out_cols = self.ex.out, self.row0 * 4, n0, n0
+        elif self.grouped:
+            self.out_bufs = [ctx.buffer(n * 4) for n in n_list(N)]
+            self.out_buf, self.out_off, self.out_stride, self.out_cols = self.out_bufs[0], 0, n_list(N)[0], n_list(N)[0]
+        else:
+            self.out_buf, self.out_off, self.out_stride, self.out_cols = ctx.buffer(M * self.pad * 4), 0, self.pad, self.pad
+        if self.exchange == "nccl":
+            torch = env.torch
+            self.out_local_t = torch.empty((M, self.pad), dtype=torch.float32, device="cuda")
+            self.out_buf.destroy()
+            self.out_buf = ctx.import_buffer(self.out_local_t.data_ptr(), self.out_local_t.numel() * 4)
+            self.gathered_t = torch.empty((world, M, self.pad), dtype=torch.float32, device="cuda")
+            self.out_full_t = torch.empty((M, n0), dtype=torch.float32, device="cuda")
+        self.world, self.rank = world, rank
+        self.exchange_on = True
+
+    # ---- recording -------------------------------------------------------------------------------------------------
+    def path(self):
+        return self.mms[0].path
+
+    def record_steps(self, batch, n, first, quantize=True):
+        ctx = self.env.ctx
+        if quantize == "read-probe":   # a plain read of each step's weight region instead of the step
+            for i in range(n):
+                for w in self.weights[(first + i) % self.pool_n]:
+                    batch.dispatch(ctx.kernel("ameva_read_probe"), [w.buf, self.probe_sink], [0, 0], (1, 1, 1))
+            return
+        for i in range(n):
+            mm = self.mms[(first + i) % self.pool_n]
+            before = batch.stats().dispatches if i == 0 else None
+            if self.grouped:
+                mm.record(batch, self.x_dev, self.out_bufs)
+            else:
+                mm.record(batch, self.x_dev, self.out_buf, self.M, dst_offset=self.out_off, dst_stride=self.out_stride,
+                          quantize=quantize,
+                          peers=self.ex.peers if (self.ex and self.exchange == "fused" and self.exchange_on) else None)
+            if self.ex and self.exchange == "copy" and self.exchange_on:
+                self.ex.record_push(batch, self.M, self.row0, self.rows)
+            if self.ex and self.exchange_on:
+                self.ex.record_barrier(batch)
+            if i == 0 and quantize is True:
+                self.launches_per_step = batch.stats().dispatches - before
+
+    def use_replay(self):
+        return self.exchange in ("none", "fused") and not self.env.args.no_replay
+
+    def replay_batches(self, quantize, rem):
+        """(graph of pool_n consecutive steps, graph of the first `rem` steps): every step count replays."""
+        ctx = self.env.ctx
+        key = (quantize, 0, self.exchange_on)
+        if key not in self.replay_cache:
+            rb = ctx.batch(max(64, self.pool_n * 70), 0)
+            self.record_steps(rb, self.pool_n, 0, quantize)
+            rb.instantiate()
+            self.replay_cache[key] = rb
+        tail = None
+        if rem:
+            key_t = (quantize, rem, self.exchange_on)
+            if key_t not in self.replay_cache:
+                tb = ctx.batch(max(64, rem * 70), 0)
+                self.record_steps(tb, rem, 0, quantize)
+                tb.instantiate()
+                self.replay_cache[key_t] = tb
+            tail = self.replay_cache[key_t]
+        return self.replay_cache[key], tail
+
+    def gpu_steps(self, n, first, quantize=True):
+        """n steps on the device; returns the GPU seconds by CUDA events on the runtime's stream."""
+        env, torch, ctx = self.env, self.env.torch, self.env.ctx
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if self.use_replay():
+            full, rem = divmod(n, self.pool_n)
+            rb, tail = self.replay_batches(quantize, rem)   # instantiated before the timed region
+            evs = []
+            with torch.cuda.stream(env.stream):
+                start.record()
+                for _ in range(full):
+                    evs.append(rb.replay())
+                if tail is not None:
+                    evs.append(tail.replay())
+                end.record()
+            for ev in evs:
+                ev.wait(600_000_000_000)
+                ev.destroy()
+            end.synchronize()
+            return start.elapsed_time(end) / 1e3
+        if self.exchange != "nccl":
+            per_batch = max(1, min(n, 60000 // 70))   # a batch holds at most 65536 dispatches
+            done, pending = 0, []
+            with torch.cuda.stream(env.stream):
+                start.record()
+                while done < n:   # every batch is recorded and submitted before the first wait: the GPU never idles
+                    cnt = min(per_batch, n - done)
+                    batch = ctx.batch(max(64, cnt * 70), 0)
+                    self.record_steps(batch, cnt, first + done, quantize)
+                    pending.append((batch, batch.submit()))
+                    done += cnt
+                end.record()
+            for bt, ev in pending:
+                ev.wait(600_000_000_000)
+                ev.destroy()
+                bt.destroy()
+            end.synchronize()
+            return start.elapsed_time(end) / 1e3
+        # all-gather exchange: compute on the runtime's stream, then the NCCL all-gather and the permute, in stream order
+        dist, shard = env.dist, env.shard
+        with torch.cuda.stream(env.stream):
+            start.record()
+            for i in range(n):
+                batch = ctx.batch(128, 0)
+                self.record_steps(batch, 1, first + i)
+                batch.flush()
+                dist.all_gather_into_tensor(self.gathered_t.view(self.world * self.M, self.pad), self.out_local_t)
+                shard.assemble(self.gathered_t, self.parts, self.M, n_list(self.N)[0], self.out_full_t)
+                self.keep.append(batch)
+            end.record()
+            end.synchronize()
+        for b_ in self.keep:
+            b_.destroy()
+        self.keep.clear()
+        return start.elapsed_time(end) / 1e3
+
+    # ---- the measurements ------------------------------------------------------------------------------------------
+    def timed(self, steps, warmup):
+        env = self.env
+        self.gpu_steps(warmup, 0)
+        env.barrier()
+        gpu_s = self.gpu_steps(steps, warmup)
+        env.barrier()
+        return env.max_over_ranks(gpu_s)
+
+    def roofline(self, steps, warmup, step_s):
+        """Average launch duration of the dominant kernel, live: the mul_mat kernel alone (activations already quantized
+        by the steps before), the same rotation of weight copies, back to back on the launching stream between two CUDA
+        events; the quantize kernel's share is the rest of a step. A step that is one launch is timed as it is."""
+        one_launch = self.path() in ("mmvq-fq", "mmvqg-fq")
+        main_s = self.gpu_steps(steps, warmup + steps, quantize=True if one_launch else False)
+        main_ns = main_s / steps * 1e9
+        quant_ns = max(0.0, step_s * 1e9 - main_ns)
+        pk = peaks()
+        t, M, N, K = self.t, self.M, self.N, self.K
+        if self.unit == "TFLOP/s":
+            ach = 2.0 * M * self.Ntot * K / (main_ns * 1e-9) / 1e12
+            return {"bound": "tensor", "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
+                    "frac": ach / pk["tflops"], "traffic": TRAFFIC.get((self.name, self.path())),
+                    "peak_source": pk["source"] + " bf16 burst", "kernel_us": main_ns / 1e3, "quant_us": quant_ns / 1e3}
+        ach = algorithmic_bytes(t, M, N, K) / (main_ns * 1e-9) / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
+                "traffic": TRAFFIC.get((self.name, self.path())), "peak_source": pk["source"] + " copy",
+                "kernel_us": main_ns / 1e3, "quant_us": quant_ns / 1e3}
+        # what a kernel that only reads the same weight regions takes (same rotation, same timing): the ramp and the tail
+        # of a launch this short keep a pure read well under the copy peak
+        probe_s = self.gpu_steps(steps, warmup + steps, quantize="read-probe")
+        roof["read_only_us"] = probe_s / steps * 1e6
+        roof["read_only_gbs"] = sum(w.buf.size_bytes for w in self.weights[0]) / (probe_s / steps) / 1e9
+        roof["frac_of_read_only"] = roof["read_only_us"] / roof["kernel_us"]
+        return roof
+
+    def read_result(self):
+        """The last step's output on the host, [M][columns]."""
+        if self.grouped:
+            return np.concatenate([b.read(np.float32) for b in self.out_bufs]).reshape(1, -1)
+        if self.exchange == "nccl":
+            return self.out_full_t.cpu().numpy()
+        return self.out_buf.read(np.float32, self.M * self.out_cols).reshape(self.M, self.out_cols)
+
+    def parity(self, got):
+        """First token rows x a sample of weight rows of the first and, when sharded, also of the last rank's shard, so a
+        wrong kernel or exchange cannot post a number."""
+        from helpers import max_normalised_error, oracle_mul_mat
+        t, K = self.t, self.K
+        ms = min(self.M, 4)
+        worst = 0.0
+        if self.grouped:
+            col = 0
+            for blocks, n in zip(self.blocks, n_list(self.N)):
+                ns = min(n, 256)
+                per_row = blocks.reshape(n, -1).shape[1]
+                want, _, _ = oracle_mul_mat(t, np.ascontiguousarray(blocks.reshape(n, per_row)[:ns]), self.scale,
+                                            self.x[:ms], ns, K, want_sums=False)
+                worst = max(worst, max_normalised_error(got[:ms, col:col + ns], want))
+                col += n
+            return worst
+        n0 = n_list(self.N)[0]
+        allb = self.blocks[0].reshape(n0, -1)
+        full = self.exchange != "none"
+        spans = [(self.row0, min(self.rows, 512), self.row0 if full else 0)]
+        if full:
+            lr0, lrows = self.parts[-1]
+            spans.append((lr0, min(lrows, 256), lr0))
+        for g_row0, g_n, col0 in spans:
+            want, _, _ = oracle_mul_mat(t, np.ascontiguousarray(allb[g_row0:g_row0 + g_n]), self.scale, self.x[:ms], g_n,
+                                        K, want_sums=False)
+            worst = max(worst, max_normalised_error(got[:ms, col0:col0 + g_n], want))
+        return worst
+
+    def e2e(self, steps):
+        """End to end through the public API with host buffers: H2D of the activations, compute, D2H of the result, per
+        step. One GPU per rank, software-pipelined when a step moves at least 1 MB: the activations of step i+1 travel
+        host->device and the result of step i-1 device->host on two copy streams while step i computes (double-buffered
+        device input and output imported into the runtime; events order the three streams)."""
+        env, torch, ctx = self.env, self.env.torch, self.env.ctx
+        M, K = self.M, self.K
+        x_pin = torch.from_numpy(self.x).pin_memory()
+        d2h_bytes = M * self.out_cols * 4 if not self.grouped else self.Ntot * 4
+        y_pin = torch.empty((M, d2h_bytes // 4 // M), dtype=torch.float32).pin_memory()
+        overlap = (self.exchange == "none" and not self.grouped and not env.args.no_overlap
+                   and self.x.nbytes + d2h_bytes >= (1 << 20))
+        if not overlap:
+            mode = "sequential on the runtime's stream"
+
+            def run(n, first):
+                with torch.cuda.stream(env.stream):
+                    for i in range(n):
+                        self.x_dev.write_async(x_pin.data_ptr(), self.x.nbytes)
+                        batch = ctx.batch(128, 0)
+                        self.record_steps(batch, 1, first + i)
+                        batch.flush()
+                        self.keep.append(batch)
+                        if self.exchange == "nccl":
+                            env.dist.all_gather_into_tensor(self.gathered_t.view(self.world * M, self.pad), self.out_local_t)
+                            env.shard.assemble(self.gathered_t, self.parts, M, n_list(self.N)[0], self.out_full_t)
+                        if self.grouped:
+                            off = 0
+                            for b_, n_ in zip(self.out_bufs, n_list(self.N)):
+                                b_.read_async(y_pin.data_ptr() + off, n_ * 4)
+                                off += n_ * 4
+                        else:
+                            self.out_buf.read_async(y_pin.data_ptr(), d2h_bytes)
+                ctx.synchronize()
+                for bb in self.keep:
+                    bb.destroy()
+                self.keep.clear()
+            cleanup = []
+        else:
+            mode = "pipelined: H2D, compute and D2H of neighbouring steps overlap on three streams"
+            NBUF = 2
+            x_t = [torch.empty((M, K), dtype=torch.float32, device="cuda") for _ in range(NBUF)]
+            o_t = [torch.empty((M, self.out_cols), dtype=torch.float32, device="cuda") for _ in range(NBUF)]
+            x_b = [ctx.import_buffer(tt_.data_ptr(), tt_.numel() * 4) for tt_ in x_t]
+            o_b = [ctx.import_buffer(tt_.data_ptr(), tt_.numel() * 4) for tt_ in o_t]
+            y_pins = [y_pin] + [torch.empty((M, self.out_cols), dtype=torch.float32).pin_memory() for _ in range(NBUF - 1)]
+            s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+            cleanup = x_b + o_b
+
+            def run(n, first):
+                ev_cmp, ev_out = [None] * NBUF, [None] * NBUF
+                for i in range(n):
+                    b_ = i % NBUF
+                    with torch.cuda.stream(s_in):
+                        if ev_cmp[b_] is not None:
+                            s_in.wait_event(ev_cmp[b_])          # the step that last read this input buffer has finished
+                        x_t[b_].copy_(x_pin, non_blocking=True)
+                        ev_in = torch.cuda.Event()
+                        ev_in.record(s_in)
+                    with torch.cuda.stream(env.stream):
+                        env.stream.wait_event(ev_in)
+                        if ev_out[b_] is not None:
+                            env.stream.wait_event(ev_out[b_])    # the result that last used this output buffer is on the host
+                        batch = ctx.batch(128, 0)
+                        self.mms[(first + i) % self.pool_n].record(batch, x_b[b_], o_b[b_], M, dst_stride=self.out_stride)
+                        batch.flush()
+                        self.keep.append(batch)
+                        ev_cmp[b_] = torch.cuda.Event()
+                        ev_cmp[b_].record(env.stream)
+                    with torch.cuda.stream(s_out):
+                        s_out.wait_event(ev_cmp[b_])
+                        y_pins[b_].copy_(o_t[b_], non_blocking=True)
+                        ev_out[b_] = torch.cuda.Event()
+                        ev_out[b_].record(s_out)
+                torch.cuda.synchronize()
+                ctx.synchronize()
+                for bb in self.keep:
+                    bb.destroy()
+                self.keep.clear()
+
+        run(3, 0)
+        env.barrier()
+        t0 = time.perf_counter()
+        run(steps, 3)
+        env.barrier()
+        e2e_s = env.max_over_ranks(time.perf_counter() - t0)
+        for ib in cleanup:
+            ib.destroy()
+        units = self.world_units()
+        return {"value": unit_value(self.unit, self.t, self.M * units, self.N, self.K, e2e_s / steps), "unit": self.unit,
+                "h2d_bytes_per_step": int(self.x.nbytes), "d2h_bytes_per_step": int(d2h_bytes),
+                "ms_per_step": e2e_s / steps * 1e3, "mode": mode}, y_pin.numpy()
+
+    def world_units(self):
+        """How many independent batches one step of the whole job processes (replicas: one per rank)."""
+        return self.env.world if self.mode == "replicas" else 1
+
+    def destroy(self):
+        for rb in self.replay_cache.values():
+            rb.destroy()
+        for mm in self.mms:
+            mm.destroy()
+        for ws in self.weights:
+            for w in ws:
+                w.destroy()
+        self.x_dev.destroy()
+        self.probe_sink.destroy()
+        if self.ex:
+            self.ex.destroy()
+        elif self.grouped:
+            for b in self.out_bufs:
+                b.destroy()
+        else:
+            self.out_buf.destroy()
+
+
+def sub_line(env, name, mode, steps, warmup, want_roof):
+    """A compact record of one more workload for the `decode` / `sharded` objects of the line."""
+    m = Measurement(env, name, mode)
+    try:
+        step_s = m.timed(steps, warmup) / steps
+        t, M, N, K = m.t, m.M, m.N, m.K
+        rec = {"workload": f"{name}: {m.desc}", "value": unit_value(m.unit, t, M, N, K, step_s), "unit": m.unit,
+               "ms_per_step": step_s * 1e3, "steps": steps, "path": m.path(), "exchange": m.exchange}
+        if want_roof and env.world == 1:
+            r = m.roofline(steps, warmup, step_s)
+            rec.update({k: r[k] for k in ("kernel_us", "frac", "achieved", "peak", "bound") if k in r})
+            for k in ("read_only_us", "frac_of_read_only"):
+                if k in r:
+                    rec[k] = r[k]
+        if mode == "sharded" and env.world > 1:
+            # what crossed NVLink per rank and direction in a step: every other rank's share of the fp32 output comes in
+            n0 = n_list(N)[0]
+            in_bytes = 4 * M * (n0 - m.rows)
+            rec["nvlink_in_bytes_per_rank"] = int(in_bytes)
+            rec["nvlink_in_gbs_per_rank"] = in_bytes / step_s / 1e9
+            m.exchange_on = False      # the same kernels on the rank's slice without the exchange: what the exchange costs
+            rec["kernel_only_ms_per_step"] = m.timed(steps, warmup) / steps * 1e3
+            m.exchange_on = True
+        if env.rank == 0:
+            rec["parity_max_normalised_error"] = m.parity(m.read_result())
+        return rec
+    finally:
+        env.barrier()
+        m.destroy()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -232,13 +714,19 @@ def main():
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="leave the `decode` object out of the line")
+    ap.add_argument("--no-sharded", action="store_true", help="leave the `sharded` object out of the line")
+    ap.add_argument("--sharded-primary", action="store_true",
+                    help="N > 1: row-shard the primary workload too (strong scaling) instead of token-parallel replicas")
+    ap.add_argument("--exchange", choices=["copy", "fused", "nccl"], default="copy",
+                    help="how the ranks of a row-sharded mul_mat assemble the output (see the module docstring)")
     ap.add_argument("--no-replay", action="store_true", help="one host launch per kernel instead of replayed batches")
     ap.add_argument("--no-overlap", action="store_true", help="e2e: copies and compute in sequence on one stream")
     ap.add_argument("--gemv", choices=["auto", "register", "streamed"], default="auto",
                     help="M <= 8: register-staged kernels (ameva_mmvq*), the one that stages the weight rows in shared "
                          "memory (ameva_mmvs_*), or the library's own choice")
-    ap.add_argument("--fused-quantize", action="store_true",
-                    help="M == 1, small projections: quantize inside the GEMV launch (ameva_mmv*_fq)")
+    ap.add_argument("--no-fused-quantize", action="store_true",
+                    help="M == 1, small projections: keep the separate quantize kernel (default: one launch, ameva_mmv*_fq)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     name = args.workload
@@ -246,366 +734,78 @@ def main():
         reference_arm(args, name)
         return
 
+    env = Env(args)
+    world, rank = env.world, env.rank
     t, M, N, K, std, desc = WORKLOADS[name]
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    import torch
-    torch.cuda.set_device(local_rank)
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    mode = "single" if world == 1 else ("sharded" if args.sharded_primary else "replicas")
+    m = Measurement(env, name, mode)
+    units = m.world_units()
 
-    pkg = importlib.import_module("ameva-compute_b200")
-    rt, qmm, shard = pkg.runtime, pkg.qmm, pkg.shard
-    ctx = rt.init()
-    ext_stream = torch.cuda.ExternalStream(ctx.stream, device=torch.device("cuda", local_rank))
-
-    unit = "TFLOP/s" if M > GEMV_MAX_M else "GB/s"
-    blocks, scale, x = make_inputs(t, M, N, K, std)
-    parts = shard.partition_rows(N, world)
-    row0, rows = parts[rank]
-    pad = shard.padded_rows(N, world)
-    per_row = blocks.reshape(N, -1).shape[1]
-    my_blocks = blocks.reshape(N, per_row)[row0:row0 + rows]
-
-    # rotating pool of weight copies larger than L2, so that no step finds its weights cached
-    shard_bytes = weight_bytes(t, max(rows, 1), K)
-    pool_n = max(2, min(64, -(-2 * L2_BYTES // max(shard_bytes, 1)) + 1))
-    weights = [qmm.QuantWeight.from_ggml(ctx, t, my_blocks, rows, K, scale) for _ in range(pool_n)]
-    mms = [qmm.MulMat(ctx, w, M, streamed={"auto": None, "register": False, "streamed": True}[args.gemv],
-                      fused_quantize=args.fused_quantize) for w in weights]
-    x_dev = ctx.buffer(data=x)
-
-    # Output exchange of the sharded run. "peer": every rank owns a full [M][N] output; the mul_mat's epilogue stores
-    # its rows into every rank's output over NVLink and a flag barrier closes the step (all inside this library's
-    # kernels). "allgather": [M][rows] shards + NCCL all-gather + permute, for the kernels without the fused epilogue.
-    tc_path = M > GEMV_MAX_M and mms[0].tc_ok
-    exchange = "none"
-    if world > 1:
-        exchange = "peer" if (t != I2_S and (tc_path or (M <= GEMV_MAX_M and K % 256 == 0))) else "allgather"
-    ex = None
-    if exchange == "peer":
-        ex = qmm.PeerExchange(ctx, rank, world, M * N * 4)
-        handles = [None] * world
-        dist.all_gather_object(handles, ex.handles())
-        ex.connect(handles)
-        out_buf, out_off, out_stride, out_cols = ex.out, row0 * 4, N, N
-    else:
-        out_buf, out_off, out_stride, out_cols = ctx.buffer(M * pad * 4), 0, pad, pad
-    gathered_t = out_full_t = out_local_t = None
-    if exchange == "allgather":
-        out_local_t = torch.empty((M, pad), dtype=torch.float32, device="cuda")
-        out_buf.destroy()
-        out_buf = ctx.import_buffer(out_local_t.data_ptr(), out_local_t.numel() * 4)
-        gathered_t = torch.empty((world, M, pad), dtype=torch.float32, device="cuda")
-        out_full_t = torch.empty((M, N), dtype=torch.float32, device="cuda")
-
-    launches_per_step = [0]
-    batch_keep = []
-
-    probe_sink = ctx.buffer(64)
-
-    def record_steps(batch, n, first, quantize=True):
-        if quantize == "read-probe":   # a plain read of each step's weight region instead of the step
-            for i in range(n):
-                batch.dispatch(ctx.kernel("ameva_read_probe"), [weights[(first + i) % pool_n].buf, probe_sink], [0, 0],
-                               (1, 1, 1))
-            return
-        for i in range(n):
-            mm = mms[(first + i) % pool_n]
-            before = batch.stats().dispatches if i == 0 else None
-            mm.record(batch, x_dev, out_buf, M, dst_offset=out_off, dst_stride=out_stride, quantize=quantize,
-                      peers=ex.peers if ex else None)
-            if ex:
-                ex.record_barrier(batch)
-            if i == 0 and quantize:
-                launches_per_step[0] = batch.stats().dispatches - before
-
-    # The steps are replayed from instantiated batches (CUDA graphs of pool_n consecutive steps, one per weight copy;
-    # with peers each step ends in the flag barrier kernel, which counts its own epochs), so that a step of a few
-    # microseconds is not bounded by one host launch per kernel; the timed region is bracketed by CUDA events on the
-    # runtime's stream.
-    use_replay = exchange != "allgather" and not args.no_replay
-    replay_cache = {}
-
-    def replay_batch(quantize):
-        if quantize not in replay_cache:
-            rb = ctx.batch(max(64, pool_n * 70), 0)
-            record_steps(rb, pool_n, 0, quantize)
-            rb.instantiate()
-            replay_cache[quantize] = rb
-        return replay_cache[quantize]
-
-    def gpu_steps(n, first, flags=0, quantize=True):
-        """n steps on the device; returns (gpu seconds by CUDA events on the runtime's stream, last batch)."""
-        if use_replay and not flags:
-            full, rem = divmod(n, pool_n)
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            rb = replay_batch(quantize) if full else None
-            tail = None
-            if rem:
-                tail = ctx.batch(max(64, rem * 70), 0)
-                record_steps(tail, rem, 0, quantize)
-            evs = []
-            with torch.cuda.stream(ext_stream):
-                start.record()
-                for _ in range(full):
-                    evs.append(rb.replay())
-                if tail:
-                    evs.append(tail.submit())
-                end.record()
-            for ev in evs:
-                ev.wait(600_000_000_000)
-                ev.destroy()
-            end.synchronize()
-            return start.elapsed_time(end) / 1e3, tail
-        if exchange != "allgather":
-            per_batch = n if flags else max(1, min(n, 60000 // 70))   # a batch holds at most 65536 dispatches
-            gpu_s, done, batch = 0.0, 0, None
-            pending = []
-            while done < n:   # every batch is recorded and submitted before the first wait: the GPU never idles
-                cnt = min(per_batch, n - done)
-                batch = ctx.batch(max(64, cnt * 70), flags)
-                record_steps(batch, cnt, first + done, quantize)
-                pending.append((batch, batch.submit()))
-                done += cnt
-            for bt, ev in pending:
-                ev.wait(600_000_000_000)
-                gpu_s += ev.timing()[1] / 1e9
-                ev.destroy()
-                if bt is not batch:
-                    bt.destroy()
-            return gpu_s, batch
-        # all-gather exchange: compute on the runtime's stream, then the NCCL all-gather and the permute, in stream order
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with torch.cuda.stream(ext_stream):
-            start.record()
-            for i in range(n):
-                batch = ctx.batch(128, 0)
-                record_steps(batch, 1, first + i)
-                batch.flush()
-                dist.all_gather_into_tensor(gathered_t.view(world * M, pad), out_local_t)
-                shard.assemble(gathered_t, parts, M, N, out_full_t)
-                batch_keep.append(batch)
-            end.record()
-            end.synchronize()
-        for b_ in batch_keep:
-            b_.destroy()
-        batch_keep.clear()
-        return start.elapsed_time(end) / 1e3, None
-
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        ctx.synchronize()
-        torch.cuda.synchronize()
-
-    # warm-up
-    _, b = gpu_steps(args.warmup, 0)
-    if b:
-        b.destroy()
-    sampler = ClockSampler(local_rank)
-    barrier()
+    sampler = ClockSampler(env.local_rank)
+    m.gpu_steps(args.warmup, 0)
+    env.barrier()
     sampler.start()
     t_wall0 = time.perf_counter()
-    gpu_s, b = gpu_steps(args.steps, args.warmup)
-    barrier()
+    gpu_s = m.gpu_steps(args.steps, args.warmup)
+    env.barrier()
     wall_s = time.perf_counter() - t_wall0
-    if b:
-        b.destroy()
-    if dist is not None:
-        tt = torch.tensor([gpu_s], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        gpu_s = float(tt.item())
+    gpu_s = env.max_over_ranks(gpu_s)
+    step_s = gpu_s / args.steps
 
-    # average launch duration of the dominant kernel, live: the mul_mat kernel(s) alone (activations already quantized
-    # by the steps above), the same rotation of weight copies, back to back on the launching stream between two CUDA
-    # events; the quantize kernel's share is the rest of a step
-    roof = None
-    if world == 1:
-        nprof = args.steps
-        # (a step of the fused quantize+GEMV launch is that one kernel: it is timed as it is)
-        main_s, pb = gpu_steps(nprof, args.warmup + args.steps, 0, quantize=mms[0].path == "mmvq-fq")
-        if pb:
-            pb.destroy()
-        main_ns = main_s / nprof * 1e9
-        quant_ns = max(0.0, gpu_s / args.steps * 1e9 - main_ns)
-        pk = peaks()
-        if unit == "TFLOP/s":
-            ach = 2.0 * M * N * K / (main_ns * 1e-9) / 1e12
-            roof = {"bound": "tensor", "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
-                    "frac": ach / pk["tflops"], "traffic": TRAFFIC.get((name, mms[0].path)),
-                    "peak_source": pk["source"] + " bf16 burst", "kernel_us": main_ns / 1e3, "quant_us": quant_ns / 1e3}
-        else:
-            ach = algorithmic_bytes(t, M, N, K) / (main_ns * 1e-9) / 1e9
-            roof = {"bound": "hbm", "achieved": ach, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": ach / pk["hbm_gbs"],
-                    "traffic": TRAFFIC.get((name, mms[0].path)), "peak_source": pk["source"] + " copy", "kernel_us": main_ns / 1e3,
-                    "quant_us": quant_ns / 1e3}
-            # what a kernel that only reads the same weight regions (ameva_read_probe, same rotation, same timing)
-            # takes: the ramp and the tail of a launch this short keep a pure read well under the copy peak
-            probe_s, pb = gpu_steps(nprof, args.warmup + args.steps, 0, quantize="read-probe")
-            if pb:
-                pb.destroy()
-            roof["read_only_us"] = probe_s / nprof * 1e6
-            roof["read_only_gbs"] = weights[0].buf.size_bytes / (probe_s / nprof) / 1e9
-            roof["frac_of_read_only"] = roof["read_only_us"] / roof["kernel_us"]
-
-    # end to end through the public API with host buffers: H2D of the activations, compute, D2H of the result, per step
-    x_pin = torch.from_numpy(x).pin_memory()
-    d2h_bytes = M * out_cols * 4
-    y_pin = torch.empty((M, out_cols), dtype=torch.float32).pin_memory()
-    e2e_steps = args.steps
-
-    def e2e_run(n, first):
-        with torch.cuda.stream(ext_stream):
-            for i in range(n):
-                x_dev.write_async(x_pin.data_ptr(), x.nbytes)
-                batch = ctx.batch(128, 0)
-                record_steps(batch, 1, first + i)
-                batch.flush()
-                batch_keep.append(batch)
-                if exchange == "allgather":
-                    dist.all_gather_into_tensor(gathered_t.view(world * M, pad), out_local_t)
-                    shard.assemble(gathered_t, parts, M, N, out_full_t)
-                out_buf.read_async(y_pin.data_ptr(), d2h_bytes)
-        ctx.synchronize()
-        for bb in batch_keep:
-            bb.destroy()
-        batch_keep.clear()
-
-    # One GPU: the same per-step work, software-pipelined. The activations of step i+1 travel host->device and the result
-    # of step i-1 device->host on two copy streams while step i computes (double-buffered device input and output,
-    # imported into the runtime with ac_b200_buffer_import; events order the three streams).
-    e2e_mode = "sequential on the runtime's stream"
-    overlap = exchange == "none" and not args.no_overlap and x.nbytes + d2h_bytes >= (1 << 20)   # else host-bound
-    if overlap:
-        e2e_mode = "pipelined: H2D, compute and D2H of neighbouring steps overlap on three streams"
-        NBUF = 2
-        x_t = [torch.empty((M, K), dtype=torch.float32, device="cuda") for _ in range(NBUF)]
-        o_t = [torch.empty((M, out_cols), dtype=torch.float32, device="cuda") for _ in range(NBUF)]
-        x_b = [ctx.import_buffer(tt_.data_ptr(), tt_.numel() * 4) for tt_ in x_t]
-        o_b = [ctx.import_buffer(tt_.data_ptr(), tt_.numel() * 4) for tt_ in o_t]
-        y_pins = [y_pin] + [torch.empty((M, out_cols), dtype=torch.float32).pin_memory() for _ in range(NBUF - 1)]
-        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-
-        def e2e_run(n, first):   # noqa: F811
-            ev_cmp, ev_out = [None] * NBUF, [None] * NBUF
-            for i in range(n):
-                b_ = i % NBUF
-                with torch.cuda.stream(s_in):
-                    if ev_cmp[b_] is not None:
-                        s_in.wait_event(ev_cmp[b_])          # the step that last read this input buffer has finished
-                    x_t[b_].copy_(x_pin, non_blocking=True)
-                    ev_in = torch.cuda.Event()
-                    ev_in.record(s_in)
-                with torch.cuda.stream(ext_stream):
-                    ext_stream.wait_event(ev_in)
-                    if ev_out[b_] is not None:
-                        ext_stream.wait_event(ev_out[b_])    # the result that last used this output buffer is on the host
-                    batch = ctx.batch(128, 0)
-                    mms[(first + i) % pool_n].record(batch, x_b[b_], o_b[b_], M, dst_stride=out_stride)
-                    batch.flush()
-                    batch_keep.append(batch)
-                    ev_cmp[b_] = torch.cuda.Event()
-                    ev_cmp[b_].record(ext_stream)
-                with torch.cuda.stream(s_out):
-                    s_out.wait_event(ev_cmp[b_])
-                    y_pins[b_].copy_(o_t[b_], non_blocking=True)
-                    ev_out[b_] = torch.cuda.Event()
-                    ev_out[b_].record(s_out)
-            torch.cuda.synchronize()
-            ctx.synchronize()
-            for bb in batch_keep:
-                bb.destroy()
-            batch_keep.clear()
-
-    e2e_run(3, 0)
-    barrier()
-    t0 = time.perf_counter()
-    e2e_run(e2e_steps, 3)
-    barrier()
-    e2e_s = time.perf_counter() - t0
+    roof = m.roofline(args.steps, args.warmup, step_s) if world == 1 else None
+    e2e, y_host = m.e2e(args.steps)
     clocks = sampler.stop()
-    if dist is not None:
-        tt = torch.tensor([e2e_s], dtype=torch.float64, device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        e2e_s = float(tt.item())
+    check = m.parity(y_host) if rank == 0 and m.rows else None
 
-    # parity spot check of what was timed (rank 0): first token rows x a sample of weight rows of the first and, when
-    # sharded with the peer exchange, also of the last rank's shard, so a wrong kernel or exchange cannot post a number
-    check = None
-    if rank == 0 and rows:
-        from helpers import max_normalised_error, oracle_mul_mat
-        ms, ns = min(M, 4), min(rows, 512)
-        got_all = y_pin.numpy()
-        spans = [(row0, ns, 0 if exchange != "peer" else row0)]
-        if exchange == "peer":
-            lr0, lrows = parts[-1]
-            spans.append((lr0, min(lrows, 256), lr0))
-        check = 0.0
-        allb = blocks.reshape(N, per_row)
-        for g_row0, g_n, col0 in spans:
-            want, _, _ = oracle_mul_mat(t, np.ascontiguousarray(allb[g_row0:g_row0 + g_n]), scale, x[:ms], g_n, K,
-                                        want_sums=False)
-            check = max(check, max_normalised_error(got_all[:ms, col0:col0 + g_n], want))
+    decode = sharded = None
+    sub_steps = max(20, min(args.steps, 200))
+    if not args.no_decode and world == 1 and name == "cfg2":
+        decode = {w: sub_line(env, w, "single", sub_steps, 5, True) for w in DECODE_LINES}
+    if not args.no_sharded and name == "cfg2":
+        sharded = {w: sub_line(env, w, "sharded" if world > 1 else "single", max(10, min(sub_steps, 50)) if
+                               WORKLOADS[w][1] > GEMV_MAX_M else sub_steps, 3, False) for w in SHARDED_LINES}
 
     if rank == 0:
-        par = {"none": "single GPU",
-               "peer": f"weight rows sharded over {world} ranks; the GEMM/GEMV epilogue stores each rank's rows into every "
-                       "rank's [M][N] output over NVLink (peer memory) and a flag barrier kernel closes every step; no "
-                       "collective library in the data path",
-               "allgather": f"weight rows sharded over {world} ranks, NCCL all-gather of the fp32 output + permute inside "
-                            "the timed region"}[exchange]
+        par = {"single": "single GPU",
+               "replicas": f"data-parallel over tokens: {world} ranks, each with the whole weight matrix and its own batch of "
+                           f"{M} tokens, no exchange",
+               "sharded": f"weight rows sharded over {world} ranks, output assembled on every rank ({m.exchange})"}[mode]
+        detail = ({"l2": f"rotating pool of {m.pool_n} weight copies ({m.pool_n * m.shard_bytes / 1e6:.0f} MB > L2) per rank",
+                    "parallelism": par, "path": m.path(),
+                    "launch": f"replayed batches (CUDA graphs of {m.pool_n} steps + one of the remainder)" if
+                    m.use_replay() else "one host launch per kernel"})
         line = {
-            "metric": metric_name(name), "value": unit_value(unit, t, M, N, K, gpu_s / args.steps), "unit": unit,
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": gpu_s / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "metric": metric_name(name), "value": unit_value(m.unit, t, M * units, N, K, step_s), "unit": m.unit,
+            "n_gpus": env.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3,
+            "higher_is_better": True, "scaling": "strong" if mode == "sharded" else "weak", "vs_baseline": None,
             "dtype": {"mmtc": "int8 (tcgen05 kind::i8, int32 accumulate)" if t == I2_S else
                       "f16 (tcgen05 kind::f16 on dequantized fp16 operands, fp32 accumulate in TMEM)"}.get(
-                          mms[0].path.split("+")[0], "int8 (dp4a, int32 per block, fp32 scale-accumulate)"),
+                          m.path().split("+")[0], "int8 (dp4a, int32 per block, fp32 scale-accumulate)"),
             "data": "synthetic",
-            "config": {"workload": f"{name}: {desc}", "M": M, "N": N, "K": K,
-                       "l2": f"rotating pool of {pool_n} weight copies ({pool_n * shard_bytes / 1e6:.0f} MB > L2) per rank",
-                       "parallelism": par, "path": mms[0].path,
-                       "launch": f"replayed batches (CUDA graphs of {pool_n} steps)" if use_replay else
-                                 "one host launch per kernel"},
+            "config": workload_config(name), "config_detail": detail,
             "wall_ms_per_step": wall_s / args.steps * 1e3,
-            "gpu_launches": launches_per_step[0] * args.steps,
-            "e2e": {"value": unit_value(unit, t, M, N, K, e2e_s / e2e_steps), "unit": unit,
-                    "h2d_bytes_per_step": int(x.nbytes), "d2h_bytes_per_step": int(d2h_bytes),
-                    "ms_per_step": e2e_s / e2e_steps * 1e3, "mode": e2e_mode},
+            "gpu_launches": m.launches_per_step * args.steps,
+            "e2e": e2e,
             "clocks": clocks,
             "parity_max_normalised_error": check,
         }
         if roof:
             line["roofline"] = roof
+        if decode:
+            line["decode"] = decode
+        if sharded:
+            line["sharded"] = sharded
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = run_cpu_baseline(t, M, N, K, blocks, scale, x, unit)
+            line["cpu_baseline"] = run_cpu_baseline(t, M, N, K, m.blocks, m.scale, m.x, m.unit)
         print(json.dumps(line), flush=True)
 
-    if dist is not None:   # nobody unmaps a buffer a peer may still be writing; and never hang after the line is out
+    if env.dist is not None:   # nobody unmaps a buffer a peer may still be writing; and never hang after the line is out
         threading.Timer(60.0, lambda: os._exit(0)).start()
-        barrier()
-    for rb in replay_cache.values():
-        rb.destroy()
-    if overlap:
-        for ib in x_b + o_b:
-            ib.destroy()
-    for mm in mms:
-        mm.destroy()
-    for w in weights:
-        w.destroy()
-    x_dev.destroy()
-    probe_sink.destroy()
-    if ex:
-        ex.destroy()
-    else:
-        out_buf.destroy()
-    ctx.destroy()
-    if dist is not None:
-        dist.destroy_process_group()
+        env.barrier()
+    m.destroy()
+    env.ctx.destroy()
+    if env.dist is not None:
+        env.dist.destroy_process_group()
         os._exit(0)
 
 

@@ -356,8 +356,10 @@ AcResult ac_b200_repack_from_device(uint32_t ggml_type, const void* device_layou
  * meant for hosts that must not allocate where they call from (real-time callbacks, fixed-budget plugins, sandboxes
  * that forbid allocation after start-up). Limits: M <= 8 and K <= 32768, otherwise AC_ERR_INVALID_SHAPE; the array
  * (294 912 bytes) stays resident on every GPU that loads the library. All pointers are device addresses on the current
- * device; the work is enqueued on `stream` (cudaStream_t, NULL = default stream) and not waited for. The first call on a
- * device also looks the array up and should come before any stream capture. Every call reuses the same array, so calls
+ * device (the one `stream` belongs to: the scratch used is the array of the device current at the call); x and
+ * w_payload must be 16-byte aligned, w_scales 2-byte and dst 4-byte aligned, otherwise the call is refused with
+ * AC_ERR_BUFFER_ALIGNMENT_INVALID and nothing is launched. The work is enqueued on `stream` (cudaStream_t, NULL = default
+ * stream) and not waited for. The first call on a device also looks the array up and should come before any stream capture. Every call reuses the same array, so calls
  * whose GPU work may overlap must be serialised by the caller. */
 AcResult ac_b200_mul_mat_q4_0_static(void* stream, const void* w_payload, const void* w_scales, const float* x,
                                      uint32_t x_stride, float* dst, uint32_t dst_stride, uint32_t M, uint32_t N,

@@ -29,13 +29,17 @@ def build(force: bool = False) -> None:
     src = os.path.join(_HERE, "oracle.c")
     if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
         subprocess.run(["make", "-s", "-C", _HERE, "all"], check=True)
-    if not os.path.exists(_REF_PATH):
-        subprocess.run(["make", "-s", "-C", _HERE, "ref"], check=False)
+    ref_root = os.environ.get("AMEVA_REFERENCE_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    if not os.path.exists(_REF_PATH) and os.path.isdir(ref_root):
+        subprocess.run(["make", "-s", "-C", _HERE, "ref", f"REFERENCE_ROOT={ref_root}"], check=False)
 
 
 def _load():
     build()
-    lib = C.CDLL(_LIB_PATH)
+    return _bind(C.CDLL(_LIB_PATH))
+
+
+def _bind(lib):
     vp, i64, i32, f32p = C.c_void_p, C.c_int64, C.c_int, C.c_void_p
     lib.orc_fp16_to_fp32.restype = C.c_float
     lib.orc_fp16_to_fp32.argtypes = [C.c_uint16]
@@ -62,6 +66,59 @@ def _load():
 
 
 _lib = None
+_native = None
+_native_note = "portable build (-O3, no -march)"
+
+
+def _native_path() -> str:
+    """The timing build is specific to the CPU it was compiled on (-march=native): the file name carries a digest of the
+    CPU's feature flags, so a file brought from another machine is never loaded."""
+    import hashlib
+    flags = ""
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("flags"):
+                flags = line
+                break
+    except OSError:
+        pass
+    return os.path.join(_HERE, "_native", f"liboracle_native_{hashlib.sha1(flags.encode()).hexdigest()[:12]}.so")
+
+
+class timing_build:
+    """Context manager for the CPU-baseline timing legs of bench.py: inside it the oracle's functions run from a second
+    build of the same oracle.c with -march=native (vectorised integer loops; -ffp-contract=off kept), compiled on this
+    machine on first use. Parity tests never use it: they run the portable build, whose fp32 expressions evaluate as
+    written. When the native build cannot be made (no compiler), the portable build is timed and says so."""
+
+    def __enter__(self):
+        global _lib, _native, _native_note
+        self.saved = lib()
+        if _native is None:
+            path = _native_path()
+            if not os.path.exists(path):
+                subprocess.run(["make", "-s", "-C", _HERE, "native", f"NATIVE_OUT={path}"], check=False)
+            if os.path.exists(path):
+                try:
+                    _native = _bind(C.CDLL(path))
+                except OSError:
+                    _native = None
+        if _native is not None:
+            _lib = _native
+            _native_note = "native build (-O3 -march=native) of the same source"
+        else:
+            _native_note = "portable build (-O3, no -march)"
+        return self
+
+    def __exit__(self, *exc):
+        global _lib
+        _lib = self.saved
+        return False
+
+
+def build_flavour() -> str:
+    """Which build the last timing_build() ran."""
+    return _native_note
 
 
 def lib():

@@ -27,7 +27,8 @@ sys.path.insert(0, ROOT)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("AMEVA_REFERENCE_ROOT"), required="AMEVA_REFERENCE_ROOT" not in os.environ,
+                    help="a checkout of uno-km/ameva-compute (or the AMEVA_REFERENCE_ROOT environment variable)")
     args = ap.parse_args()
 
     import gguf

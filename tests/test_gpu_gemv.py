@@ -378,3 +378,69 @@ def test_gemv_default_kernel_choice(ctx):
             v.destroy()
         mm.destroy()
         w.destroy()
+
+
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
+@pytest.mark.parametrize("ns,K", [((64, 32, 32), 512), ((4096, 1024, 1024), 4096), ((350, 2), 1024), ((10, 6, 2, 30), 256),
+                                  ((128,), 2048)])
+def test_grouped_launch_of_projections_sharing_the_activation_row(ctx, t, ns, K):
+    """q / k / v (or gate / up) of one activation row as ONE launch: every output carries the bits of its own separate
+    quantize-in-GEMV launch, and matches the oracle. Ragged group sizes, a group of one and of four included."""
+    x = make_acts(1, K, 77)
+    x[0, :32] = 0.0
+    xb = ctx.buffer(data=x)
+    ws, blocks_all = [], []
+    for j, N in enumerate(ns):
+        blocks, scale = make_weights(t, N, K, 100 + j)
+        blocks_all.append(blocks)
+        ws.append(qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale))
+    outs = [ctx.buffer(N * 4) for N in ns]
+    for o in outs:
+        o.fill(0xFF)
+    grp = qmm.MulMatGroup(ctx, ws)
+    grp.run(xb, outs)
+    for j, N in enumerate(ns):
+        got = outs[j].read(np.float32)
+        one = qmm.MulMat(ctx, ws[j], 1, fused_quantize=True)
+        ref = ctx.buffer(N * 4)
+        one.run(xb, ref, 1)
+        assert one.path == "mmvq-fq"
+        assert np.array_equal(got.view(np.uint32), ref.read(np.uint32)), (j, N)
+        want, _, _ = oracle_mul_mat(t, blocks_all[j], 1.0, x, N, K, want_sums=False)
+        assert max_normalised_error(got.reshape(1, N), want) <= TOL
+        ref.destroy()
+        one.destroy()
+    for b in outs + [xb]:
+        b.destroy()
+    for w in ws:
+        w.destroy()
+
+
+def test_grouped_launch_refusals(ctx):
+    blocks, _ = make_weights(Q4_0, 6, 256, 1)
+    w = qmm.QuantWeight.from_ggml(ctx, Q4_0, blocks, 6, 256)
+    blocks2, _ = make_weights(Q8_0, 6, 256, 1)
+    w2 = qmm.QuantWeight.from_ggml(ctx, Q8_0, blocks2, 6, 256)
+    blocks3, _ = make_weights(Q4_0, 5, 256, 1)
+    w3 = qmm.QuantWeight.from_ggml(ctx, Q4_0, blocks3, 5, 256)
+    with pytest.raises(qmm.MulMatUnsupported):
+        qmm.MulMatGroup(ctx, [w, w2])                 # mixed types
+    with pytest.raises(qmm.MulMatUnsupported):
+        qmm.MulMatGroup(ctx, [w, w3])                 # odd row count
+    with pytest.raises(qmm.MulMatUnsupported):
+        qmm.MulMatGroup(ctx, [w] * 5)                 # more than four
+    # the launcher itself: odd N, count 0, K above the shared-memory limit
+    xb, dst = ctx.buffer(256 * 4), ctx.buffer(64)
+    grp = qmm.MulMatGroup(ctx, [w])
+    q, s_ = grp.binds[0]
+    binds = [q, s_, dst] * 4 + [xb]
+    for push in ([256, 0, 1, 5, 0, 0, 0], [256, 0, 0, 6, 0, 0, 0], [256, 2, 1, 6, 0, 0, 0], [32768, 0, 1, 6, 0, 0, 0]):
+        batch = ctx.batch(4)
+        with pytest.raises(rt.AmevaComputeError):
+            batch.dispatch(ctx.kernel("ameva_mmvqg_q4_0_fq"), binds, push, (1, 1, 1))
+            batch.submit().wait()
+        batch.destroy()
+    for b in (xb, dst):
+        b.destroy()
+    for v in (w, w2, w3):
+        v.destroy()
