@@ -18,10 +18,9 @@ namespace amv {
 //   d = amax / 127 (f32); id = d ? 1/d : 0; q = clamp(round(x*id), +-127); stored d = fp16(d) (what the dot uses).
 //   round_mode 0 = ties-to-even (reference shaders, ggml SIMD quantizers), 1 = ties-away (ggml quantize_row_q8_0_ref).
 // ---------------------------------------------------------------------------------------------------------------------
-template <bool WRITE_H>
 __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
-                                                         uint32_t* __restrict__ ad, __half* __restrict__ ah, uint32_t M,
-                                                         uint32_t K, uint32_t src_stride, uint32_t round_mode) {
+                                                         uint32_t* __restrict__ ad, uint32_t M, uint32_t K,
+                                                         uint32_t src_stride, uint32_t round_mode) {
     pdl_trigger();   // the mul_mat behind this kernel may be scheduled already (it can request its weights meanwhile; it
                      // waits for this grid before reading the quantized activations)
     pdl_wait();      // the activations may come from the kernel before (it let this one be scheduled early)
@@ -40,15 +39,6 @@ __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict
     if (live) {
         reinterpret_cast<uint32_t*>(aq + (size_t)m * K + 32u * u)[sub] = pack_q4(q);
         if (sub == 0) ad[(size_t)m * U + u] = scale_word_q8_0(d, s);
-        if (WRITE_H) {   // the tensor-core operand: fp16(q * d) with d the fp16-rounded scale the dot product uses
-            const float dh = h2f(f2h(d));
-            const __half2 h01 = __floats2half2_rn((float)q[0] * dh, (float)q[1] * dh);
-            const __half2 h23 = __floats2half2_rn((float)q[2] * dh, (float)q[3] * dh);
-            uint2 o;
-            o.x = *reinterpret_cast<const uint32_t*>(&h01);
-            o.y = *reinterpret_cast<const uint32_t*>(&h23);
-            *reinterpret_cast<uint2*>(ah + (size_t)m * K + 32u * u + 4u * sub) = o;
-        }
     }
 }
 
@@ -59,10 +49,9 @@ __global__ void __launch_bounds__(256) quant_q8_0_kernel(const float* __restrict
 //   mode 1 (ameva_quant_a8b.comp): d = amax/127, q = clamp(roundEven(x * (1/d)), +-127).
 //   bsums[j] = sum of q over elements 16j..16j+15.
 // ---------------------------------------------------------------------------------------------------------------------
-template <bool WRITE_H>
 __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
-                                                         uint8_t* __restrict__ ab, __half* __restrict__ ah, uint32_t M,
-                                                         uint32_t K, uint32_t src_stride, uint32_t mode) {
+                                                         uint8_t* __restrict__ ab, uint32_t M, uint32_t K,
+                                                         uint32_t src_stride, uint32_t mode) {
     pdl_trigger();   // the mul_mat behind this kernel may be scheduled already (it can request its weights meanwhile; it
                      // waits for this grid before reading the quantized activations)
     pdl_wait();      // the activations may come from the kernel before (it let this one be scheduled early)
@@ -89,15 +78,6 @@ __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict
         w1 |= (uint32_t)(q[i + 4] & 0xFF) << (8 * i);
     }
     *reinterpret_cast<uint2*>(aq + (size_t)m * K + 256u * b + 8u * lane) = make_uint2(w0, w1);
-    if (WRITE_H) {   // the tensor-core operand: fp16(q * d)
-        uint32_t o[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const __half2 hh = __floats2half2_rn((float)q[2 * i] * d, (float)q[2 * i + 1] * d);
-            o[i] = *reinterpret_cast<const uint32_t*>(&hh);
-        }
-        *reinterpret_cast<uint4*>(ah + (size_t)m * K + 256u * b + 8u * lane) = make_uint4(o[0], o[1], o[2], o[3]);
-    }
     s += __shfl_xor_sync(0xffffffffu, s, 1);  // lanes 2j, 2j+1 -> 16-element group j
     uint8_t* blk = ab + ((size_t)m * B + b) * kABBytes;
     if ((lane & 1u) == 0u) reinterpret_cast<int16_t*>(blk)[lane >> 1] = (int16_t)s;
@@ -105,6 +85,108 @@ __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict
         *reinterpret_cast<float*>(blk + 32) = d;
         *reinterpret_cast<uint32_t*>(blk + 36) = 0u;
         *reinterpret_cast<uint2*>(blk + 40) = make_uint2(0u, 0u);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The quantizers of the tensor-core GEMM (more than 8 token rows): one CTA per token row. Besides AQ and the block scales
+// (the same bytes as the kernels above) they write the GEMM's activation operand AH = fp16(q * d * s_m) and AE[m] = 1 / s_m,
+// where s_m is a power of two that brings the row's largest magnitude into [1, 2). fp16 has five exponent bits: without
+// the factor a row of small activations (|x| ~ 1e-4) would land among fp16 subnormals and a row of large ones (> 65504)
+// would overflow, although the integer path they stand in for is scale-invariant. The factor is exact (a power of two)
+// and the GEMM's epilogue multiplies it back per token row.
+//   SCHEME 0: per-32 (Q8_0) scales, `mode` = round_mode; SCHEME 1: per-256 (Q8_K), `mode` as ameva_quant_a8b.
+// ---------------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float block_max_256(float v, float* red) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) r = fmaxf(r, red[i]);
+    return r;
+}
+
+template <int SCHEME>
+__global__ void __launch_bounds__(256) quant_rows_f16_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
+                                                             uint8_t* __restrict__ ad, __half* __restrict__ ah,
+                                                             float* __restrict__ ae, uint32_t K, uint32_t src_stride,
+                                                             uint32_t mode) {
+    pdl_trigger();   // the GEMM behind this kernel may be scheduled already; it waits for this grid before reading
+    pdl_wait();      // the activations may come from the kernel before
+    __shared__ float red[8];
+    const uint32_t m = blockIdx.x, t = threadIdx.x, lane = t & 31u;
+    const float* row = src + (size_t)m * src_stride;
+    float amax = 0.0f;
+    for (uint32_t i = t; i < (K >> 2); i += 256u) {
+        const float4 v = *reinterpret_cast<const float4*>(row + 4u * i);
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    amax = block_max_256(amax, red);
+    // s = 2^-floor(log2(amax)); rows that are all zero (or not finite) keep s = 1
+    int e = 0;
+    if (amax > 0.0f && amax <= 3.4e38f) e = min(126, max(-126, ilogbf(amax)));
+    const float s = __int_as_float((127 - e) << 23), inv = __int_as_float((127 + e) << 23);
+    if (t == 0) ae[m] = inv;
+
+    if constexpr (SCHEME == 0) {
+        const uint32_t U = K >> 5, sub = t & 7u;
+        uint32_t* adw = reinterpret_cast<uint32_t*>(ad);
+        for (uint32_t base = 0; base < U; base += 32u) {   // 32 units per pass; whole warps stay together
+            const uint32_t u = base + (t >> 3);
+            const bool live = u < U;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (live) x = *reinterpret_cast<const float4*>(row + 32u * u + 4u * sub);   // (second read: L1 / L2)
+            int q[4], sum;
+            float d;
+            quant_unit_q8_0(x, mode, q, d, sum);
+            if (live) {
+                reinterpret_cast<uint32_t*>(aq + (size_t)m * K + 32u * u)[sub] = pack_q4(q);
+                if (sub == 0) adw[(size_t)m * U + u] = scale_word_q8_0(d, sum);
+                const float dh = __fmul_rn(h2f(f2h(d)), s);   // the fp16-rounded scale the dot product uses, times 2^-e
+                const __half2 h01 = __floats2half2_rn((float)q[0] * dh, (float)q[1] * dh);
+                const __half2 h23 = __floats2half2_rn((float)q[2] * dh, (float)q[3] * dh);
+                uint2 o;
+                o.x = *reinterpret_cast<const uint32_t*>(&h01);
+                o.y = *reinterpret_cast<const uint32_t*>(&h23);
+                *reinterpret_cast<uint2*>(ah + (size_t)m * K + 32u * u + 4u * sub) = o;
+            }
+        }
+    } else {
+        const uint32_t B = K >> 8;
+        for (uint32_t b = t >> 5; b < B; b += 8u) {   // one warp per 256-block
+            const float* p = row + 256u * b + 8u * lane;
+            const float4 x0 = *reinterpret_cast<const float4*>(p), x1 = *reinterpret_cast<const float4*>(p + 4);
+            const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            int q[8];
+            float d;
+            quant_block_q8_K(x, mode, lane, q, d);
+            int sum = 0;
+            uint32_t w0 = 0, w1 = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                sum += q[i] + q[i + 4];
+                w0 |= (uint32_t)(q[i] & 0xFF) << (8 * i);
+                w1 |= (uint32_t)(q[i + 4] & 0xFF) << (8 * i);
+            }
+            *reinterpret_cast<uint2*>(aq + (size_t)m * K + 256u * b + 8u * lane) = make_uint2(w0, w1);
+            const float ds = __fmul_rn(d, s);
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const __half2 hh = __floats2half2_rn((float)q[2 * i] * ds, (float)q[2 * i + 1] * ds);
+                o[i] = *reinterpret_cast<const uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(ah + (size_t)m * K + 256u * b + 8u * lane) = make_uint4(o[0], o[1], o[2], o[3]);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);  // lanes 2j, 2j+1 -> 16-element group j
+            uint8_t* blk = ad + ((size_t)m * B + b) * kABBytes;
+            if ((lane & 1u) == 0u) reinterpret_cast<int16_t*>(blk)[lane >> 1] = (int16_t)sum;
+            if (lane == 0) {
+                *reinterpret_cast<float*>(blk + 32) = d;
+                *reinterpret_cast<uint32_t*>(blk + 36) = 0u;
+                *reinterpret_cast<uint2*>(blk + 40) = make_uint2(0u, 0u);
+            }
+        }
     }
 }
 
@@ -214,45 +296,58 @@ __global__ void __launch_bounds__(256) bitnet_norm_q8_kernel(const float* __rest
 // launchers
 // ---------------------------------------------------------------------------------------------------------------------
 // ameva_quant_a8: bindings 0 src f32, 1 AQ, 2 AD; push {M, K, src_stride (floats), round_mode}
-// ameva_quant_a8_f16: the same plus binding 3 AH, fp16 [M][K] = fp16(q * d), the activation operand of ameva_mmtc_*
-template <bool WRITE_H>
-static AcResult launch_quant_a8_t(const LaunchArgs& a) {
+AcResult launch_quant_a8(const LaunchArgs& a) {
     const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], round_mode = a.push[3];
     if (M == 0 || K == 0 || (K & 31u) || stride < K || (stride & 3u) || round_mode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
     const uint64_t U = K >> 5;
     if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || a.range[1] < (uint64_t)M * K ||
-        a.range[2] < (uint64_t)M * U * 4u || (WRITE_H && a.range[3] < (uint64_t)M * K * 2u))
+        a.range[2] < (uint64_t)M * U * 4u)
         return AC_ERR_INVALID_BUFFER_SIZE;
+    if ((uintptr_t)a.ptr[0] & 15u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     const uint64_t threads = (uint64_t)M * U * 8u;
     const uint64_t blocks = (threads + 255u) / 256u;
     if (blocks > 0x7FFFFFFFull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    launch_pdl(quant_q8_0_kernel<WRITE_H>, dim3((unsigned)blocks), dim3(256), 0, a.stream,
-        (const float*)a.ptr[0], (int8_t*)a.ptr[1], (uint32_t*)a.ptr[2], WRITE_H ? (__half*)a.ptr[3] : nullptr, M, K,
-        stride, round_mode);
+    launch_pdl(quant_q8_0_kernel, dim3((unsigned)blocks), dim3(256), 0, a.stream, (const float*)a.ptr[0],
+               (int8_t*)a.ptr[1], (uint32_t*)a.ptr[2], M, K, stride, round_mode);
     return check_launch();
 }
-AcResult launch_quant_a8(const LaunchArgs& a) { return launch_quant_a8_t<false>(a); }
-AcResult launch_quant_a8_f16(const LaunchArgs& a) { return launch_quant_a8_t<true>(a); }
 
 // ameva_quant_a8b: bindings 0 src f32, 1 AQ, 2 AB; push {M, K, src_stride (floats), mode}
-// ameva_quant_a8b_f16: the same plus binding 3 AH, fp16 [M][K] = fp16(q * d)
-template <bool WRITE_H>
-static AcResult launch_quant_a8b_t(const LaunchArgs& a) {
+AcResult launch_quant_a8b(const LaunchArgs& a) {
     const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], mode = a.push[3];
     if (M == 0 || K == 0 || (K & 255u) || stride < K || (stride & 3u) || mode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
     const uint64_t B = K >> 8;
     if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || a.range[1] < (uint64_t)M * K ||
-        a.range[2] < (uint64_t)M * B * kABBytes || (WRITE_H && a.range[3] < (uint64_t)M * K * 2u))
+        a.range[2] < (uint64_t)M * B * kABBytes)
         return AC_ERR_INVALID_BUFFER_SIZE;
+    if ((uintptr_t)a.ptr[0] & 15u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     const uint64_t blocks = ((uint64_t)M * B * 32u + 255u) / 256u;
     if (blocks > 0x7FFFFFFFull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    launch_pdl(quant_q8_K_kernel<WRITE_H>, dim3((unsigned)blocks), dim3(256), 0, a.stream,
-        (const float*)a.ptr[0], (int8_t*)a.ptr[1], (uint8_t*)a.ptr[2], WRITE_H ? (__half*)a.ptr[3] : nullptr, M, K,
-        stride, mode);
+    launch_pdl(quant_q8_K_kernel, dim3((unsigned)blocks), dim3(256), 0, a.stream, (const float*)a.ptr[0],
+               (int8_t*)a.ptr[1], (uint8_t*)a.ptr[2], M, K, stride, mode);
     return check_launch();
 }
-AcResult launch_quant_a8b(const LaunchArgs& a) { return launch_quant_a8b_t<false>(a); }
-AcResult launch_quant_a8b_f16(const LaunchArgs& a) { return launch_quant_a8b_t<true>(a); }
+
+// ameva_quant_a8_f16 / ameva_quant_a8b_f16: the quantizers in front of ameva_mmtc_* (more than 8 token rows).
+//   bindings 0 src f32, 1 AQ, 2 AD (per-32 scale words) or AB (per-256 records), 3 AH fp16 [M][K] = fp16(q * d * s_m),
+//            4 AE f32 [M] = 1 / s_m (s_m the power of two that brings row m's largest magnitude into [1, 2))
+//   push {M, K, src_stride (floats), round_mode / mode}
+template <int SCHEME>
+static AcResult launch_quant_rows(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], mode = a.push[3];
+    const uint32_t kmask = SCHEME ? 255u : 31u;
+    if (M == 0 || K == 0 || (K & kmask) || stride < K || (stride & 3u) || mode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t scale_bytes = SCHEME ? (uint64_t)M * (K >> 8) * kABBytes : (uint64_t)M * (K >> 5) * 4u;
+    if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || a.range[1] < (uint64_t)M * K || a.range[2] < scale_bytes ||
+        a.range[3] < (uint64_t)M * K * 2u || a.range[4] < (uint64_t)M * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if (((uintptr_t)a.ptr[0] & 15u) || ((uintptr_t)a.ptr[3] & 15u)) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    launch_pdl(quant_rows_f16_kernel<SCHEME>, dim3(M), dim3(256), 0, a.stream, (const float*)a.ptr[0], (int8_t*)a.ptr[1],
+               (uint8_t*)a.ptr[2], (__half*)a.ptr[3], (float*)a.ptr[4], K, stride, mode);
+    return check_launch();
+}
+AcResult launch_quant_a8_f16(const LaunchArgs& a) { return launch_quant_rows<0>(a); }
+AcResult launch_quant_a8b_f16(const LaunchArgs& a) { return launch_quant_rows<1>(a); }
 
 // bitnet_norm_q8: bindings 0 a, 1 b, 2 w, 3 y, 4 q, 5 act, 6 qeo; push {dim, eps_bits, mode, do_norm}; grid.x = rows
 // (argument contract of src/shaders/bitnet_norm_q8.comp:20-44, extended from one row to grid.x rows).

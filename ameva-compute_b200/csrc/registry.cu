@@ -52,16 +52,16 @@ AcResult launch_bitnet_gemv_i2_s_acc(const LaunchArgs&);
 static const KernelEntry kTable[] = {
     {"ameva_quant_a8", 3, 16, {256, 1, 1}, launch_quant_a8},
     {"ameva_quant_a8b", 3, 16, {256, 1, 1}, launch_quant_a8b},
-    {"ameva_quant_a8_f16", 4, 16, {256, 1, 1}, launch_quant_a8_f16},
-    {"ameva_quant_a8b_f16", 4, 16, {256, 1, 1}, launch_quant_a8b_f16},
+    {"ameva_quant_a8_f16", 5, 16, {256, 1, 1}, launch_quant_a8_f16},
+    {"ameva_quant_a8b_f16", 5, 16, {256, 1, 1}, launch_quant_a8b_f16},
     {"bitnet_norm_q8", 7, 16, {256, 1, 1}, launch_bitnet_norm_q8},
-    {"ameva_mmtc_q4_0", 4, 20, {320, 1, 1}, launch_mmtc_q4_0},
-    {"ameva_mmtc_q8_0", 4, 20, {320, 1, 1}, launch_mmtc_q8_0},
-    {"ameva_mmtc_q4_K", 4, 20, {320, 1, 1}, launch_mmtc_q4_K},
+    {"ameva_mmtc_q4_0", 5, 24, {320, 1, 1}, launch_mmtc_q4_0},
+    {"ameva_mmtc_q8_0", 5, 24, {320, 1, 1}, launch_mmtc_q8_0},
+    {"ameva_mmtc_q4_K", 5, 24, {320, 1, 1}, launch_mmtc_q4_K},
     {"bitnet_gemm_i2_s", 4, 24, {320, 1, 1}, launch_bitnet_gemm_i2_s},
-    {"ameva_mmtc_q4_0_mp", 11, 24, {608, 1, 1}, launch_mmtc_q4_0_mp},
-    {"ameva_mmtc_q8_0_mp", 11, 24, {608, 1, 1}, launch_mmtc_q8_0_mp},
-    {"ameva_mmtc_q4_K_mp", 11, 24, {608, 1, 1}, launch_mmtc_q4_K_mp},
+    {"ameva_mmtc_q4_0_mp", 12, 28, {608, 1, 1}, launch_mmtc_q4_0_mp},
+    {"ameva_mmtc_q8_0_mp", 12, 28, {608, 1, 1}, launch_mmtc_q8_0_mp},
+    {"ameva_mmtc_q4_K_mp", 12, 28, {608, 1, 1}, launch_mmtc_q4_K_mp},
     {"ameva_mmvqb_q4_K_mp", 12, 20, {256, 1, 1}, launch_mmvqb_q4_K_mp},
     {"ameva_mmvs_q4_0", 12, 24, {288, 1, 1}, launch_mmvs_q4_0},
     {"ameva_mmvs_q8_0", 12, 24, {288, 1, 1}, launch_mmvs_q8_0},

@@ -16,8 +16,10 @@
 //   - props: async = false, host_buffer = false, events = false (ggml-ameva-device.cpp:271-281).
 // Scope: MUL_MAT with a Q4_0 / Q8_0 / Q4_K src0 (2-D, contiguous) and f32 src1 / dst, plus the no-op view nodes. Other
 // ops are reported unsupported, which is how the scheduler keeps them on another backend.
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -87,7 +89,56 @@ uint64_t device_bytes(const ggml_tensor* t, uint64_t* s_off) {
 struct BufferCtx {
     AcBuffer* buf = nullptr;
     size_t size = 0;
+    // per repacked weight (by its offset in the buffer): the power of two the tensor-core GEMM scales the weights by
+    // while dequantizing them to fp16 (ameva_mmtc_* push word w_exp), computed from the block scales at upload
+    std::map<size_t, int> w_exp;
 };
+
+float half_bits_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {   // subnormal: normalise
+            int e = -1;
+            uint32_t m = man;
+            do {
+                m <<= 1;
+                ++e;
+            } while (!(m & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3FFu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7F800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112u) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+// w_exp of a weight tensor from its ggml blocks: an upper bound of |w| per block from the scale fields alone (Q4_0
+// 8 |d|, Q8_0 127 |d|, Q4_K 945 |d| + 63 |dmin|), the largest over the tensor brought into [1, 2); limited to -14..15.
+int weight_exponent(enum ggml_type type, const uint8_t* blocks, size_t nbytes) {
+    const size_t bb = type == GGML_TYPE_Q4_0 ? 18 : (type == GGML_TYPE_Q8_0 ? 34 : 144);
+    float top = 0.0f;
+    for (size_t o = 0; o + bb <= nbytes; o += bb) {
+        uint16_t h0, h1;
+        memcpy(&h0, blocks + o, 2);
+        memcpy(&h1, blocks + o + 2, 2);
+        const float d = fabsf(half_bits_to_float(h0));
+        float bound = type == GGML_TYPE_Q4_0 ? 8.0f * d : (type == GGML_TYPE_Q8_0 ? 127.0f * d
+                                                          : 945.0f * d + 63.0f * fabsf(half_bits_to_float(h1)));
+        if (bound > top && bound <= 3.0e38f) top = bound;
+    }
+    if (!(top > 0.0f)) return 0;
+    int e = 0;
+    frexpf(top, &e);          // top = m * 2^e, m in [0.5, 1)  ->  floor(log2(top)) = e - 1
+    const int w = -(e - 1);
+    return w < -14 ? -14 : (w > 15 ? 15 : w);
+}
 
 size_t tensor_offset(const ggml_tensor* t) { return (size_t)((const char*)t->data - kBase); }
 
@@ -134,6 +185,7 @@ void buffer_set_tensor(ggml_backend_buffer_t buffer, ggml_tensor* tensor, const 
     AcResult rc = ac_b200_repack_to_device((uint32_t)tensor->type, src, rows, k, dev.data());
     if (rc == AC_SUCCESS) rc = ac_runtime_buffer_write(b->buf, tensor_offset(tensor), dev.data(), total);
     if (rc != AC_SUCCESS) die("set_tensor", rc);
+    b->w_exp[tensor_offset(tensor)] = weight_exponent(tensor->type, (const uint8_t*)src, nbytes);
 }
 
 void buffer_get_tensor(ggml_backend_buffer_t buffer, const ggml_tensor* tensor, void* data, size_t offset, size_t size) {
@@ -220,7 +272,8 @@ struct Backend {
     AcBuffer* aq = nullptr;   // int8 [M][K]
     AcBuffer* ad = nullptr;   // per-block activation scales (u32 per 32 / 48 B per 256)
     AcBuffer* ah = nullptr;   // fp16 [M][K], the tensor-core operand (M > 8)
-    size_t aq_bytes = 0, ad_bytes = 0, ah_bytes = 0;
+    AcBuffer* ae = nullptr;   // f32 [M], the per-row range factors of that operand
+    size_t aq_bytes = 0, ad_bytes = 0, ah_bytes = 0, ae_bytes = 0;
 };
 
 AcKernel* kernel(Backend* be, const char* name) {
@@ -232,9 +285,17 @@ AcKernel* kernel(Backend* be, const char* name) {
     return k;
 }
 
+// Called before a batch is begun (nothing retains the old buffer then), with the largest need over the graph's nodes, as
+// the reference sizes its scratch before recording (ggml-ameva.cpp:5382-5422).
 bool grow(AcBuffer** buf, size_t* have, size_t need) {
     if (*have >= need) return true;
-    if (*buf) ac_runtime_buffer_destroy(*buf);
+    if (*buf) {
+        const AcResult rc = ac_runtime_buffer_destroy(*buf);
+        if (rc != AC_SUCCESS) {
+            fprintf(stderr, "ggml-ameva-b200: scratch buffer still in use (AcResult %d)\n", (int)rc);
+            return false;
+        }
+    }
     *buf = nullptr;
     *have = 0;
     AcBufferDesc d = {AC_ABI_VERSION, (uint32_t)sizeof(AcBufferDesc), need, AC_BUFFER_USAGE_STORAGE, 0};
@@ -290,9 +351,6 @@ bool record_mul_mat(Backend* be, AcCommandBatch* batch, const ggml_tensor* node)
     const char* tname = w->type == GGML_TYPE_Q4_0 ? "q4_0" : (w->type == GGML_TYPE_Q8_0 ? "q8_0" : "q4_K");
     const bool tc = M > 8 && (K % 256) == 0;
     const uint64_t ad_need = q4k ? (uint64_t)M * (K / 256) * 48u : (uint64_t)M * (K / 32) * 4u;
-    if (!grow(&be->aq, &be->aq_bytes, (size_t)M * K) || !grow(&be->ad, &be->ad_bytes, (size_t)ad_need) ||
-        (tc && !grow(&be->ah, &be->ah_bytes, (size_t)M * K * 2)))
-        return false;
     BufferCtx* wb = (BufferCtx*)w->buffer->context;
     BufferCtx* xb = (BufferCtx*)(x->view_src ? x->view_src : x)->buffer->context;
     BufferCtx* yb = (BufferCtx*)(node->view_src ? node->view_src : node)->buffer->context;
@@ -319,10 +377,10 @@ bool record_mul_mat(Backend* be, AcCommandBatch* batch, const ggml_tensor* node)
         if (tc) name += "_f16";
         AcKernel* k = kernel(be, name.c_str());
         if (!k) return false;
-        AcBufferBinding b[4] = {bind(xb->buf, tensor_offset(x), (uint64_t)M * K * 4), bind(be->aq, 0, (uint64_t)M * K),
-                                bind(be->ad, 0, ad_need), bind(be->ah, 0, (uint64_t)M * K * 2)};
+        AcBufferBinding b[5] = {bind(xb->buf, tensor_offset(x), (uint64_t)M * K * 4), bind(be->aq, 0, (uint64_t)M * K),
+                                bind(be->ad, 0, ad_need), bind(be->ah, 0, (uint64_t)M * K * 2), bind(be->ae, 0, (uint64_t)M * 4)};
         const uint32_t push[4] = {M, K, K, 0};   // ties-to-even per-32 / ggml's per-256 convention
-        if (ac_runtime_batch_dispatch_bindings(batch, k, b, tc ? 4 : 3, push, sizeof(push), grid) != AC_SUCCESS)
+        if (ac_runtime_batch_dispatch_bindings(batch, k, b, tc ? 5 : 3, push, sizeof(push), grid) != AC_SUCCESS)
             return false;
         ac_runtime_batch_barrier(batch);
     }
@@ -331,10 +389,11 @@ bool record_mul_mat(Backend* be, AcCommandBatch* batch, const ggml_tensor* node)
     if (tc) {
         AcKernel* k = kernel(be, (std::string("ameva_mmtc_") + tname).c_str());
         if (!k) return false;
-        AcBufferBinding b[4] = {Q, S, bind(be->ah, 0, (uint64_t)M * K * 2),
-                                bind(yb->buf, tensor_offset(node), (uint64_t)M * N * 4)};
-        const uint32_t push[5] = {M, N, K, N, 0};
-        return ac_runtime_batch_dispatch_bindings(batch, k, b, 4, push, sizeof(push), grid) == AC_SUCCESS;
+        AcBufferBinding b[5] = {Q, S, bind(be->ah, 0, (uint64_t)M * K * 2),
+                                bind(yb->buf, tensor_offset(node), (uint64_t)M * N * 4), bind(be->ae, 0, (uint64_t)M * 4)};
+        auto it = wb->w_exp.find(tensor_offset(w));
+        const uint32_t push[6] = {M, N, K, N, 0, (uint32_t)(it == wb->w_exp.end() ? 0 : it->second)};
+        return ac_runtime_batch_dispatch_bindings(batch, k, b, 5, push, sizeof(push), grid) == AC_SUCCESS;
     }
     // M <= 8 over short weight rows, with several activation rows or a large matrix: the GEMV that stages whole weight
     // rows in shared memory (the choice of qmm.py's MulMat.streamed_pays)
@@ -368,7 +427,7 @@ void backend_free(ggml_backend_t backend) {
     {
         std::lock_guard<std::mutex> lock(plugin().mutex);
         for (auto& kv : be->kernels) ac_runtime_kernel_destroy(kv.second);
-        for (AcBuffer* b : {be->aq, be->ad, be->ah})
+        for (AcBuffer* b : {be->aq, be->ad, be->ah, be->ae})
             if (b) ac_runtime_buffer_destroy(b);
     }
     delete be;
@@ -387,6 +446,23 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
             return GGML_STATUS_FAILED;
         }
     }
+    // scratch for the quantized activations: the largest need over all nodes, reserved before anything is recorded
+    size_t aq_need = 0, ad_need = 0, ah_need = 0, ae_need = 0;
+    for (int i = 0; i < n; ++i) {
+        const ggml_tensor* node = ggml_graph_node(cgraph, i);
+        if (node->op != GGML_OP_MUL_MAT) continue;
+        const ggml_tensor *w = node->src[0], *x = node->src[1];
+        const size_t K = (size_t)w->ne[0], M = (size_t)x->ne[1];
+        aq_need = std::max(aq_need, M * K);
+        ad_need = std::max(ad_need, w->type == GGML_TYPE_Q4_K ? M * (K / 256) * 48u : M * (K / 32) * 4u);
+        if (M > 8 && K % 256 == 0) {
+            ah_need = std::max(ah_need, M * K * 2);
+            ae_need = std::max(ae_need, M * 4);
+        }
+    }
+    if ((aq_need && !grow(&be->aq, &be->aq_bytes, aq_need)) || (ad_need && !grow(&be->ad, &be->ad_bytes, ad_need)) ||
+        (ah_need && !grow(&be->ah, &be->ah_bytes, ah_need)) || (ae_need && !grow(&be->ae, &be->ae_bytes, ae_need)))
+        return GGML_STATUS_ALLOC_FAILED;
     AcCommandBatch* batch = nullptr;
     AcBatchDesc bd = {AC_ABI_VERSION, (uint32_t)sizeof(AcBatchDesc), 4096u, 0u};
     if (ac_runtime_batch_begin_ex(context(), &bd, &batch) != AC_SUCCESS) return GGML_STATUS_ALLOC_FAILED;

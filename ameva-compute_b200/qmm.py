@@ -51,6 +51,28 @@ def streamed_pays(ggml_type: int, M: int, N: int, K: int) -> bool:
     return M >= 4 or N * row_bytes >= STREAMED_MIN_WEIGHT_BYTES
 
 
+def weight_exponent(ggml_type: int, blocks: np.ndarray, N: int, K: int) -> int:
+    """w_exp of the tensor-core GEMM: the power of two that brings the largest weight magnitude of the tensor into
+    [1, 2) when the weights are dequantized to fp16 (the GEMM multiplies the block scales by 2^w_exp and its epilogue
+    takes the factor out again). Computed once per tensor at upload from the block scale fields alone, as an upper bound
+    of |w|: Q4_0 8 |d|, Q8_0 127 |d|, Q4_K 945 |d| + 63 |dmin|. Limited to [-14, 15] (2^w_exp is an fp16 number)."""
+    if ggml_type not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K):
+        return 0
+    nblk = N * (K // BLOCK[ggml_type])
+    raw = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(nblk, -1)
+    d = np.abs(np.ascontiguousarray(raw[:, 0:2]).view(np.float16).astype(np.float32))[:, 0]
+    if ggml_type == GGML_TYPE_Q4_K:
+        dmin = np.abs(np.ascontiguousarray(raw[:, 2:4]).view(np.float16).astype(np.float32))[:, 0]
+        bound = d * 945.0 + dmin * 63.0
+    else:
+        bound = d * (8.0 if ggml_type == GGML_TYPE_Q4_0 else 127.0)
+    bound = bound[np.isfinite(bound)]
+    top = float(bound.max()) if bound.size else 0.0
+    if not top > 0.0:
+        return 0
+    return int(min(15, max(-14, -int(np.floor(np.log2(top))))))
+
+
 class MulMatUnsupported(Exception):
     """The op is outside the contract; the message is the reason (the reference logs it once per (op, type, reason))."""
 
@@ -83,8 +105,9 @@ class QuantWeight:
     uploaded bytes exactly, whole or by row range (read-back guarantee of tests/ameva_qmm_check.cpp:184-196)."""
 
     def __init__(self, ctx: rt.Context, ggml_type: int, N: int, K: int, buf: rt.Buffer, s_off: int,
-                 scale: float = 1.0) -> None:
+                 scale: float = 1.0, w_exp: int = 0) -> None:
         self.ctx, self.type, self.N, self.K, self.buf, self.s_off, self.scale = ctx, ggml_type, N, K, buf, s_off, scale
+        self.w_exp = w_exp   # see weight_exponent
 
     @classmethod
     def from_ggml(cls, ctx: rt.Context, ggml_type: int, blocks: np.ndarray, N: int, K: int,
@@ -97,7 +120,7 @@ class QuantWeight:
             raise MulMatUnsupported(f"expected {rt.ggml_nbytes(ggml_type, N, K)} bytes of ggml blocks, got {blocks.size}")
         total, s_off = rt.device_layout(ggml_type, N, K)
         dev = rt.repack_to_device(ggml_type, blocks, N, K)
-        return cls(ctx, ggml_type, N, K, ctx.buffer(total, dev), s_off, scale)
+        return cls(ctx, ggml_type, N, K, ctx.buffer(total, dev), s_off, scale, weight_exponent(ggml_type, blocks, N, K))
 
     def to_ggml(self, row0: int = 0, rows: Optional[int] = None) -> np.ndarray:
         rows = self.N - row0 if rows is None else rows
@@ -176,15 +199,16 @@ class MulMat:
             self.ad = ctx.buffer(max_m * 8)
             self.y = ctx.buffer(max_m * K * 4)     # bitnet_norm_q8 writes the fp32 activations it quantized
             self.qeo = ctx.buffer(64)              # emulated-dot operand: not produced (range too small on purpose)
-        self.ah = None
+        self.ah = self.ae = None
         if max_m > GEMV_MAX_M and not self.exact and self.tc_ok and self.type != GGML_TYPE_I2_S:
-            self.ah = ctx.buffer(max_m * K * 2)    # fp16(q * d): the activation operand of the tensor-core GEMM
+            self.ah = ctx.buffer(max_m * K * 2)    # fp16(q * d * s_m): the activation operand of the tensor-core GEMM
+            self.ae = ctx.buffer(max_m * 4)        # 1 / s_m per token row (power-of-two range factors, see act_quant.cu)
         self.sums = None
         self.path = ""
 
     # -- scratch accounting (graph_compute reserves the max over nodes, ggml-ameva.cpp:5382-5422)
     def scratch_bytes(self) -> int:
-        return self.aq.size_bytes + self.ad.size_bytes + (self.ah.size_bytes if self.ah else 0)
+        return self.aq.size_bytes + self.ad.size_bytes + (self.ah.size_bytes + self.ae.size_bytes if self.ah else 0)
 
     def _sum_shape(self, M: int):
         if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
@@ -229,11 +253,11 @@ class MulMat:
             return
         if quantize:
             if t in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
-                binds = [(x, x_offset), self.aq, self.ad] + ([self.ah] if use_tc else [])
+                binds = [(x, x_offset), self.aq, self.ad] + ([self.ah, self.ae] if use_tc else [])
                 batch.dispatch(ctx.kernel("ameva_quant_a8_f16" if use_tc else "ameva_quant_a8"), binds,
                                [M, K, K, self.round_mode], ((M * (K // 32) * 8 + 255) // 256, 1, 1))
             elif t == GGML_TYPE_Q4_K:
-                binds = [(x, x_offset), self.aq, self.ad] + ([self.ah] if use_tc else [])
+                binds = [(x, x_offset), self.aq, self.ad] + ([self.ah, self.ae] if use_tc else [])
                 batch.dispatch(ctx.kernel("ameva_quant_a8b_f16" if use_tc else "ameva_quant_a8b"), binds,
                                [M, K, K, self.q8k_mode], ((M * (K // 256) * 32 + 255) // 256, 1, 1))
             else:
@@ -259,12 +283,13 @@ class MulMat:
         if use_tc:
             self.path = "mmtc"
             grid = ((M + 255) // 256, (N + 127) // 128, 1)
+            w_exp = (int(self.view.weight.w_exp) & 0xFFFFFFFF) if t != GGML_TYPE_I2_S else 0
             if peers:
                 self.path = "mmtc+peer-stores"
                 outs = [(dst, dst_offset)] + [(pb, dst_offset) for pb in peers]
                 outs += [(dst, dst_offset)] * (8 - len(outs))
-                batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}_mp"), [self.qbind, self.sbind, self.ah] + outs,
-                               [M, N, K, dst_stride, 0, len(peers)], grid)
+                batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}_mp"), [self.qbind, self.sbind, self.ah] + outs + [self.ae],
+                               [M, N, K, dst_stride, 0, len(peers), w_exp], grid)
                 return
             if t == GGML_TYPE_I2_S:
                 push = [M, N, K, dst_stride, int(np.float32(self.view.weight.scale).view(np.uint32))]
@@ -272,7 +297,8 @@ class MulMat:
                                grid)
             else:
                 batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}"),
-                               [self.qbind, self.sbind, self.ah, (dst, dst_offset)], [M, N, K, dst_stride], grid)
+                               [self.qbind, self.sbind, self.ah, (dst, dst_offset), self.ae],
+                               [M, N, K, dst_stride, 0, w_exp], grid)
             return
         if epilogue is not None and (M != 1 or t == GGML_TYPE_I2_S or self.dump or peers):
             raise MulMatUnsupported("the fused epilogue is built for one activation row of a Q4_0 / Q8_0 / Q4_K product")
@@ -346,7 +372,7 @@ class MulMat:
         return q, act[:, 0].copy().view(np.float32), act[:, 1].copy().view(np.int32)
 
     def destroy(self) -> None:
-        for name in ("aq", "ad", "ah", "y", "qeo", "sums"):
+        for name in ("aq", "ad", "ah", "ae", "y", "qeo", "sums"):
             b = getattr(self, name, None)
             if b is not None:
                 b.destroy()

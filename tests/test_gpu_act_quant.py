@@ -3,7 +3,7 @@ import numpy as np
 import pytest
 
 import oracle
-from conftest import load_pkg
+from conftest import GOLDEN, load_pkg
 
 pytestmark = pytest.mark.gpu
 pkg = load_pkg()
@@ -146,5 +146,32 @@ def test_quant_argument_errors_are_explicit(ctx):
     with pytest.raises(rt.AmevaComputeError) as e:
         ctx.dispatch(k, [xb, aq], [1, 1024, 1024, 0])          # wrong binding count
     assert e.value.code == rt.AC_ERR_KERNEL_ARG_INVALID
+    for b in (xb, aq, ad):
+        b.destroy()
+
+
+def test_quantizers_against_frozen_known_answers(ctx):
+    """The CUDA quantizers against the frozen known-answer vectors of tests/golden/q8_K_kat.npz (hand-built edge blocks
+    and seeded rows; expected bytes from an independent numpy statement of ggml's published algorithms), not only against
+    the oracle: Q8_K in ggml's convention (mode 0) and Q8_0 with ties to even (round_mode 0)."""
+    import os
+    z = np.load(os.path.join(GOLDEN, "q8_K_kat.npz"))
+    x = np.ascontiguousarray(z["x"])
+    M, K = x.shape
+    xb, aq, ab = ctx.buffer(data=x), ctx.buffer(M * K), ctx.buffer(M * (K // 256) * 48)
+    ctx.dispatch(ctx.kernel("ameva_quant_a8b"), [xb, aq, ab], [M, K, K, 0], ((M * (K // 256) * 32 + 255) // 256, 1, 1))
+    q = aq.read(np.int8).reshape(M, K)
+    raw = ab.read(np.uint8).reshape(M, K // 256, 48)
+    bsums = np.ascontiguousarray(raw[:, :, :32]).view(np.int16)
+    d = np.ascontiguousarray(raw[:, :, 32:36]).view(np.float32)[..., 0]
+    assert np.array_equal(qmm.q8_K_blocks_from_scratch(q, d, bsums), z["q8_K"])
+    for b in (xb, aq, ab):
+        b.destroy()
+    x0 = np.ascontiguousarray(z["x_q8_0"])
+    xb, aq, ad = ctx.buffer(data=x0), ctx.buffer(M * K), ctx.buffer(M * (K // 32) * 4)
+    ctx.dispatch(ctx.kernel("ameva_quant_a8"), [xb, aq, ad], [M, K, K, 0], ((M * (K // 32) * 8 + 255) // 256, 1, 1))
+    q = aq.read(np.int8).reshape(M, K)
+    adw = ad.read(np.uint32).reshape(M, K // 32)
+    assert np.array_equal(qmm.q8_0_blocks_from_scratch(q, (adw & 0xFFFF).astype(np.uint16)), z["q8_0_even"])
     for b in (xb, aq, ad):
         b.destroy()

@@ -136,3 +136,72 @@ def test_gemm_tiles_between_half_and_all_units(ctx, t):
     """45 tiles of 256 rows for ~74 resident CTA pairs: the linear (tile, K block) space is cut into equal ranges, so a
     tile is produced by two or three units whose partial sums are combined in order (and identically on every run)."""
     run_gemm(ctx, t, 256, 11520, 2048, seed=17, rows_checked=320)
+
+
+@pytest.mark.parametrize("t", [Q8_0, Q4_0, Q4_K])
+@pytest.mark.parametrize("x_scale,w_std", [(1e-4, 0.02), (1e4, 0.02), (1.0, 1e-4), (1e-4, 1e-4), (3e4, 30.0), (1e-6, 0.02)])
+def test_gemm_tc_keeps_its_tolerance_across_operand_magnitudes(ctx, t, x_scale, w_std):
+    """The integer CPU path is scale-invariant; fp16 operands are not (subnormals below 6.1e-5, overflow above 65504).
+    The tensor-core path folds a power of two per token row into the activation operand and one per tensor into the
+    weight operand and takes them out in the epilogue, so activations of magnitude 1e-6 .. 3e4 and weights of standard
+    deviation 1e-4 .. 30 must meet the same 1e-3 gate as the N(0,1) x N(0,0.02) case (int8 reference form:
+    tests/ameva_qmm_check.cpp:63-79, 205-217 of the reference)."""
+    M, N, K = 64, 384, 1024
+    blocks, scale = make_weights(t, N, K, 11, std=w_std)
+    x = make_acts(M, K, 12) * np.float32(x_scale)
+    x[3] *= np.float32(1e-3)          # rows of very different magnitude in one call: the factor is per row
+    x[5] *= np.float32(50.0) if x_scale < 1e3 else np.float32(1.0)
+    x[7] = 0.0
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    mm.run(xb, dst, M)
+    assert mm.path == "mmtc"
+    y = dst.read(np.float32).reshape(M, N)
+    want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+    assert np.isfinite(y).all()
+    assert not y[7].any()
+    # per token row, so that a large row cannot hide a small one
+    for m in range(M):
+        ref = np.abs(want[m]).max()
+        if ref > 0:
+            err = np.abs(y[m].astype(np.float64) - want[m]).max() / ref
+            assert err <= TOL, (m, err)
+    for b in (xb, dst):
+        b.destroy()
+    mm.destroy()
+    w.destroy()
+
+
+def test_exact_path_block_sums_at_config2_size(ctx):
+    """`exact=True` at configuration-2 size: every M walks the dp4a kernels in chunks of 8 rows, the per-block int32 sums
+    are those of the CPU path bit for bit (checked on a sample of weight rows) and the fp32 output meets the gate."""
+    t, M, N, K = Q8_0, 512, 11008, 4096
+    rows = 96
+    blocks, scale = make_weights(t, N, K, 0)
+    x = make_acts(M, K, 1)
+    idx = np.sort(np.random.default_rng(3).choice(N, rows, replace=False))
+    sub = np.ascontiguousarray(np.asarray(blocks).reshape(N, -1)[idx])
+    w_all = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    w_sub = qmm.QuantWeight.from_ggml(ctx, t, sub, rows, K, scale)
+    xb = ctx.buffer(data=x)
+    # the whole matrix without the dump (M * N * K / 32 sums would be 2.9 GB), the sampled rows with it
+    mm = qmm.MulMat(ctx, w_all, M, exact=True)
+    dst = ctx.buffer(M * N * 4)
+    mm.run(xb, dst, M)
+    assert mm.path == "mmvq-chunks"
+    y = dst.read(np.float32).reshape(M, N)
+    mm_s = qmm.MulMat(ctx, w_sub, M, dump_block_sums=True)
+    dst_s = ctx.buffer(M * rows * 4)
+    mm_s.run(xb, dst_s, M)
+    want, sums, _ = oracle_mul_mat(t, sub, scale, x, rows, K, want_sums=True)
+    assert np.array_equal(mm_s.read_block_sums(M), sums)
+    ys = dst_s.read(np.float32).reshape(M, rows)
+    assert np.array_equal(ys.view(np.uint32), y[:, idx].view(np.uint32)), "same kernels, same bits, with or without the dump"
+    assert max_normalised_error(ys, want) <= 1e-5
+    for b in (xb, dst, dst_s):
+        b.destroy()
+    mm.destroy()
+    mm_s.destroy()
+    w_all.destroy()
+    w_sub.destroy()

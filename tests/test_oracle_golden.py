@@ -125,3 +125,31 @@ def test_i2s_live_reference_kernel():
     assert np.array_equal(acc[0].astype(np.float32), ref)
     total = np.float32(dq[0]) * np.float32(scale)
     assert np.array_equal(y[0], ref * total)
+
+
+def test_q8_K_and_q8_0_even_known_answers():
+    """The Q8_K row quantizer (ggml convention) and the per-32 quantizer with ties to even against frozen known-answer
+    vectors: hand-built blocks (all zero, single maximum, negative maximum, equal magnitudes of both signs, exact .5 ties,
+    values landing on +-127, tiny and huge magnitudes) and seeded rows. The expected bytes come from an independent numpy
+    statement of ggml's published quantize_row_q8_K_ref / quantize_row_q8_0 (tests/golden/make_q8_K_kat.py), not from
+    ggml itself, which is not available where this is built: the restatement is pinned against a second statement,
+    parity with a real ggml build stays unpinned."""
+    z = np.load(_g("q8_K_kat.npz"))
+    got = oracle.quantize_q8_K(z["x"], oracle.Q8K_GGML)
+    assert np.array_equal(got, z["q8_K"])
+    assert np.array_equal(oracle.quantize_q8_0(z["x_q8_0"], oracle.ROUND_NEAREST_EVEN), z["q8_0_even"])
+    # spot facts of the convention, readable without the file
+    blk = got.reshape(-1, 292)
+    d = np.ascontiguousarray(blk[:, :4]).view(np.float32)[:, 0]
+    q = blk[:, 4:260].view(np.int8)
+    assert d[0] == 0 and not q[0].any()                    # all-zero block
+    assert d[1] < 0 and q[1, 37] == -127                   # positive maximum: iscale negative, q = -127, d negative
+    assert d[2] > 0 and q[2, 200] == -127                  # negative maximum: q = -127 as well, d positive
+    assert q[3, 5] == -127 and q[3, 9] == 127              # equal magnitudes: the first one sets the sign
+    assert q[4, 5] == -127 and q[4, 9] == 127
+    # max = -127 -> iscale = 1: x = k + 0.5 rounds to the even neighbour
+    x5 = z["x"].reshape(-1, 256)[5]
+    ties = np.abs(x5 - np.trunc(x5)) == 0.5
+    assert ties.sum() > 100 and np.array_equal(q[5][ties], np.rint(x5[ties]).astype(np.int8))
+    bs = np.ascontiguousarray(blk[:, 260:]).view(np.int16)
+    assert np.array_equal(bs, q.reshape(-1, 16, 16).astype(np.int32).sum(axis=2).astype(np.int16))
