@@ -3,7 +3,8 @@
     python ameva-compute_b200/build.py [--force] [--verbose]
 
 Outputs (git-ignored, next to this file):
-    libac_runtime_b200.so   the ac_runtime C ABI + every built-in kernel
+    libac_runtime_b200.so   the ac_runtime C ABI + every built-in kernel (and the link libac_runtime.so.2 to it, the
+                            file name hosts built against the reference's runtime load)
     libamuda_b200.so        the legacy amuda host API + ac_ops_bitnet_gemv_i2_s_exact
     libggml-ameva-b200.so   the ggml backend plugin, only where ggml's headers are available (GGML_INCLUDE_DIR, or the
                             headers vendored by a checkout of the reference); with it the test harness
@@ -69,6 +70,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if force or procs or _stale(LIB, objs):
         cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", LIB] + objs
         subprocess.run(cmd, check=True)
+    # the name a host linked against the reference's runtime asks the loader for (DT_NEEDED libac_runtime.so.2)
+    alias = os.path.join(HERE, "libac_runtime.so.2")
+    if not os.path.islink(alias) or os.readlink(alias) != os.path.basename(LIB):
+        if os.path.lexists(alias):
+            os.remove(alias)
+        os.symlink(os.path.basename(LIB), alias)
     # the legacy host API is a library of its own: its type names collide with the opaque handles of the ac_runtime ABI
     shim = os.path.join(CSRC, "amuda_shim.cu")
     if force or _stale(LEGACY_LIB, [shim, os.path.join(ROOT, "include", "amuda_b200.h")]):

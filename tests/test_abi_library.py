@@ -28,6 +28,18 @@ def test_library_loads_and_exports_every_declared_symbol():
     assert lib.ac_runtime_abi_version() == 0x00020400
 
 
+def test_library_is_reachable_under_the_reference_runtime_name():
+    """A host linked against the reference's runtime asks the loader for libac_runtime.so.2: the build leaves that name
+    next to the library."""
+    alias = os.path.join(os.path.dirname(rt.LIB_PATH), "libac_runtime.so.2")
+    if not os.path.lexists(alias):
+        pytest.skip("the alias is made by the build step on the machine that builds")
+    lib = C.CDLL(alias)
+    lib.ac_runtime_abi_version.restype = C.c_uint32
+    assert lib.ac_runtime_abi_version() == 0x00020400
+    assert os.path.realpath(alias) == os.path.realpath(rt.LIB_PATH)
+
+
 # The 40 facts the reference records for its ABI (docs/abi/ac_runtime_layout.txt; arm64 LP64, identical on x86-64): what a
 # host compiled against the reference's own headers assumes about every descriptor.
 REFERENCE_LAYOUT = """
