@@ -17,6 +17,17 @@ namespace amv {
 // device status words. Launchers validate shapes and ranges and return an AcResult: they never fall back to another
 // implementation.
 // ---------------------------------------------------------------------------------------------------------------------
+// Side queues of a context: streams for copy-engine transfers that run beside the context's own stream (the output
+// exchange of a row-sharded mul_mat). Created on first use; a launcher forks them off the main stream with `fork`, the
+// join launcher makes the main stream wait for every `done` event recorded since.
+struct SideQueues {
+    cudaStream_t stream[8];
+    cudaEvent_t done[8];
+    cudaEvent_t fork;
+    bool ready;        // streams and events exist
+    bool pending[8];   // work was queued on stream i since the last join
+};
+
 struct LaunchArgs {
     cudaStream_t stream;
     uint32_t binding_count;
@@ -28,6 +39,7 @@ struct LaunchArgs {
     int sm_count;
     uint32_t* workspace;      // device words owned by the context, zero between launches (cross-CTA sequence flags)
     uint64_t workspace_bytes;
+    SideQueues* side;         // the context's side queues (copy launchers)
 };
 
 typedef AcResult (*LaunchFn)(const LaunchArgs&);

@@ -762,6 +762,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 for (uint32_t i = 0; i < 2u; ++i) {
                     const uint32_t c = cq + (i0 + i) * kDequantGroups;
                     if (ok && c * 16u < T) {
+                        // lane j holds the factor of the piece's token row j (scaled types): one load per piece, handed
+                        // round by shuffles in the loop below
+                        float unscale = 1.0f;
+                        if (!INT8) unscale = __ldg(p.row_unscale + min(m0 + c * 16u + (lane & 15u), p.M - 1u)) * p.w_unmul;
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j) {
                             const uint32_t m = m0 + c * 16u + j;
@@ -771,7 +775,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                                     __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
                                 y = __fmul_rn((float)(int)v[i][j], total_scale);
                             } else {   // undo the two power-of-two factors of the fp16 operands (exact)
-                                y = __uint_as_float(v[i][j]) * (__ldg(p.row_unscale + min(m, p.M - 1u)) * p.w_unmul);
+                                y = __uint_as_float(v[i][j]) * __shfl_sync(0xffffffffu, unscale, j);
                             }
                             if (p.tma_store)
                                 stage_out[j * 32u + lane] = y;

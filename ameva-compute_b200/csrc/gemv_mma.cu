@@ -1,0 +1,318 @@
+// Decode GEMV for 2..8 activation rows over Q4_K weights on the warp-level integer tensor instruction.
+//
+// With several activation rows the dp4a kernels stop being bound by HBM: every weight word is multiplied into each row
+// by its own dp4a, and the activation operands are re-read from shared memory for every weight row (11008 x 4096, M = 8:
+// 30 us against 4 us of HBM time). Here a warp owns 16 consecutive weight rows and feeds mma.sync.m16n8k32 (u8 x s8 ->
+// s32): the 16 weight rows are the instruction's M, the (up to) 8 activation rows its N, one 32-weight sub-block its K.
+// One instruction replaces 32 warp-wide dp4a, the activations are read once per 16 weight rows, and the kernel is back
+// at the memory roofline. The sums are the same exact integers as on the dp4a path.
+//
+//   One persistent CTA of 16 warps per SM. The warps work on 16 / KS groups of 16 weight rows at a time ("a set"), KS
+//   warps splitting the K of a group between them (KS = 16 whenever a row has at least 16 blocks); their partial fp32
+//   sums are added through shared memory at the end of the set. Sets are dealt to the CTAs in equal contiguous shares.
+//   Weights: straight from global memory into the instruction's fragment layout, no shared-memory stage: lane (g, t)
+//   (g = lane / 4, t = lane % 4) loads the 8 bytes [8t, 8t + 8) of each 32-byte chunk qs[32k' ..] of rows g and g + 8. A
+//   chunk's low nibbles are sub-block 2k', its high nibbles sub-block 2k' + 1; the lane's first word fills the k slots
+//   4t..4t+3 of the A fragment, the second the slots 16+4t..: a permutation of k, applied to the activations as well
+//   (one 8-byte shared-memory load per sub-block), which an integer sum does not see. The next 256-block's bytes are
+//   requested before the current one is multiplied, the first one before the wait for the preceding kernel.
+//   Activations (int8, written by ameva_quant_a8b) are staged once per CTA, rows K + 32 bytes apart (conflict-free
+//   8-byte loads across the 8 rows), followed by one row of zeros that stands for the tokens M..7 of the instruction. Per 256-block and token the 8 sub-block sums of q (for the
+//   mins) and the scale d are staged next to them.
+//   Per block:  isum = sum_j sc_j * mma_j      mpart = sum_j m_j * bsum_j     y += (d d_a) isum - (dmin d_a) mpart
+//
+// Reference kernels replaced: adapters/llama/ggml-ameva/shaders/ameva_qmv.comp:65-252 (2 <= M < 8, COLS = 8) and
+// ameva_mmqb.comp:10-16 (the block-integer product form).
+#include <cstring>
+
+#include "common.cuh"
+
+namespace amv {
+namespace gm {
+
+constexpr int kThreads = 512;
+constexpr int kWarps = 16;
+constexpr uint32_t kActPad = 32;                 // bytes added to an activation row: rows land 32 bytes apart mod 128
+constexpr uint32_t kSmemLimit = 200u * 1024u;
+
+struct Params {
+    const uint8_t* Q;     // 128 B per 256-block, [N][B]
+    const uint4* S;       // 16 B per 256-block: fp16 d, fp16 dmin, scales[12]
+    const int8_t* AQ;     // int8 [M][K]
+    const uint8_t* AB;    // 48-byte records [M][B]: int16 bsums[16], float d
+    float* dst;
+    uint32_t M, N, K, dst_stride;
+};
+
+__device__ __forceinline__ uint2 ld_stream_u2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+
+// D (16 x 8, s32) = A (16 x 32, u8, row) * B (32 x 8, s8, col), accumulator zero
+__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+__device__ __forceinline__ int dp2a_lo(uint32_t a16x2, uint32_t b8x4, int c) {
+    int d;
+    asm("dp2a.lo.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a16x2), "r"(b8x4), "r"(c));
+    return d;
+}
+__device__ __forceinline__ int dp2a_hi(uint32_t a16x2, uint32_t b8x4, int c) {
+    int d;
+    asm("dp2a.hi.s32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a16x2), "r"(b8x4), "r"(c));
+    return d;
+}
+
+struct BlockRegs {
+    uint2 w[2][4];    // [row g / g + 8][chunk k']: this lane's 8 bytes
+    uint4 s[2];       // the two rows' scale records
+};
+
+// One CTA per SM, 16 warps. A "set" is RG = 16 / KS groups of 16 weight rows; the KS warps of a group split its K between
+// them. The sets are dealt to the CTAs in equal contiguous shares (every SM gets within one set of the same work: no
+// partial last wave), and a CTA walks its sets with the next 256-block of weights always in flight.
+template <int KS>
+__global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params p) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t K = p.K, B = K >> 8, astride = K + kActPad, MR = p.M + 1u;   // staged rows: M tokens + one of zeros
+    int8_t* s_act = reinterpret_cast<int8_t*>(smem);                         // [M + 1][K + 32]
+    int16_t* s_sub = reinterpret_cast<int16_t*>(smem + MR * astride);         // [M + 1][B][8] sub-block sums of q
+    float* s_da = reinterpret_cast<float*>(smem + MR * astride + MR * B * 16u);   // [M + 1][B]
+    float* s_red = s_da + MR * B;                                            // [2][16 warps][16 rows][8 tokens]
+
+    constexpr uint32_t RG = kWarps / KS;
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t rg = warp / KS, ks = warp % KS;
+    const uint32_t groups = (p.N + 15u) >> 4, n_sets = (groups + RG - 1u) / RG;
+    const uint32_t set_begin = (uint32_t)((uint64_t)n_sets * blockIdx.x / gridDim.x);
+    const uint32_t set_end = (uint32_t)((uint64_t)n_sets * (blockIdx.x + 1u) / gridDim.x);
+    const uint32_t nb = (B + KS - 1) / KS, b_begin = min(B, ks * nb), b_end = min(B, b_begin + nb);
+    const uint32_t my_blocks = b_end - b_begin;
+
+    // this lane's two weight rows of set `set` (clamped into the matrix; rows past N are computed and not stored)
+    auto row_ptrs = [&](uint32_t set, const uint8_t*& qa, const uint8_t*& qb, const uint4*& sa, const uint4*& sb) {
+        const uint32_t row0 = (set * RG + rg) * 16u;
+        const uint32_t ra = min(row0 + g, p.N - 1u), rb = min(row0 + g + 8u, p.N - 1u);
+        qa = p.Q + (size_t)ra * B * 128u + 8u * t;
+        qb = p.Q + (size_t)rb * B * 128u + 8u * t;
+        sa = p.S + (size_t)ra * B;
+        sb = p.S + (size_t)rb * B;
+    };
+    auto load_block = [&](const uint8_t* qa, const uint8_t* qb, const uint4* sa, const uint4* sb, uint32_t b, BlockRegs& r) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            r.w[0][k] = ld_stream_u2(qa + (size_t)b * 128u + 32u * k);
+            r.w[1][k] = ld_stream_u2(qb + (size_t)b * 128u + 32u * k);
+        }
+        r.s[0] = ld_cached_u4(sa + b);
+        r.s[1] = ld_cached_u4(sb + b);
+    };
+
+    const uint8_t *qa, *qb;
+    const uint4 *sa, *sb;
+    BlockRegs cur, nxt;
+    const bool work = set_begin < set_end && my_blocks > 0u;
+    if (work) {   // the weights do not depend on the kernel before this one: requested before the wait for it
+        row_ptrs(set_begin, qa, qb, sa, sb);
+        load_block(qa, qb, sa, sb, b_begin, cur);
+    }
+    pdl_trigger();
+    pdl_wait();
+
+    // ---- stage the quantized activations and their per-block records; row M is zeros (tokens M..7 of the instruction) ----
+    {
+        const uint32_t pieces = K >> 4;   // 16-byte pieces per activation row
+        for (uint32_t i = threadIdx.x; i < MR * pieces; i += kThreads) {
+            const uint32_t m = i / pieces, w = i - m * pieces;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (m < p.M) v = __ldg(reinterpret_cast<const uint4*>(p.AQ + (size_t)m * K) + w);
+            *reinterpret_cast<uint4*>(s_act + m * astride + 16u * w) = v;
+        }
+        for (uint32_t i = threadIdx.x; i < MR * B; i += kThreads) {
+            const uint32_t m = i / B, b = i - m * B;
+            uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
+            float d = 0.0f;
+            if (m < p.M) {
+                const uint8_t* rec = p.AB + ((size_t)m * B + b) * kABBytes;
+                lo = __ldg(reinterpret_cast<const uint4*>(rec));
+                hi = __ldg(reinterpret_cast<const uint4*>(rec + 16));
+                d = __ldg(reinterpret_cast<const float*>(rec + 32));
+            }
+            // bsums[2j] + bsums[2j + 1] = the sum of q over sub-block j (|sum| <= 32 * 127: fits int16)
+            const uint32_t in[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+            uint32_t out[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int s0 = (int)(int16_t)(in[2 * j] & 0xFFFFu) + (int)(int16_t)(in[2 * j] >> 16);
+                const int s1 = (int)(int16_t)(in[2 * j + 1] & 0xFFFFu) + (int)(int16_t)(in[2 * j + 1] >> 16);
+                out[j] = ((uint32_t)s0 & 0xFFFFu) | ((uint32_t)s1 << 16);
+            }
+            *reinterpret_cast<uint4*>(s_sub + (size_t)i * 8u) = make_uint4(out[0], out[1], out[2], out[3]);
+            s_da[i] = d;
+        }
+    }
+    __syncthreads();
+
+    // token n of the instruction reads staged row min(n, M): rows past M are the zero row
+    const uint32_t tok_b = min(g, p.M), tok0 = min(2u * t, p.M), tok1 = min(2u * t + 1u, p.M);
+    const int8_t* a_lane = s_act + tok_b * astride + 8u * t;   // this lane's k slots of the B fragment
+    const int16_t* sub0 = s_sub + (size_t)tok0 * B * 8u;
+    const int16_t* sub1 = s_sub + (size_t)tok1 * B * 8u;
+    const float* da0p = s_da + tok0 * B;
+    const float* da1p = s_da + tok1 * B;
+
+    uint32_t parity = 0;
+    for (uint32_t set = set_begin; set < set_end; ++set) {
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // (row g, token 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
+        for (uint32_t b = b_begin; b < b_end; ++b) {
+            if (b + 1u < b_end) {
+                load_block(qa, qb, sa, sb, b + 1u, nxt);
+            } else if (set + 1u < set_end) {   // the first block of the next set
+                row_ptrs(set + 1u, qa, qb, sa, sb);
+                load_block(qa, qb, sa, sb, b_begin, nxt);
+            }
+            // 6-bit scales and mins of the 8 sub-blocks, four to a word, per row
+            uint32_t sc[2][2], mn[2][2];
+            float dw[2], dmin[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const uint4 s = cur.s[r];
+                sc[r][0] = s.y & 0x3F3F3F3Fu;
+                mn[r][0] = s.z & 0x3F3F3F3Fu;
+                sc[r][1] = (s.w & 0x0F0F0F0Fu) | ((s.y >> 2) & 0x30303030u);
+                mn[r][1] = ((s.w >> 4) & 0x0F0F0F0Fu) | ((s.z >> 2) & 0x30303030u);
+                dw[r] = h2f((uint16_t)(s.x & 0xFFFFu));
+                dmin[r] = h2f((uint16_t)(s.x >> 16));
+            }
+            int isum[4] = {0, 0, 0, 0};
+            const int8_t* ab = a_lane + 256u * b;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int j = 2 * k + h;   // sub-block
+                    const uint2 bv = *reinterpret_cast<const uint2*>(ab + 32 * j);
+                    const uint32_t a0 = (cur.w[0][k].x >> (4 * h)) & 0x0F0F0F0Fu, a1 = (cur.w[1][k].x >> (4 * h)) & 0x0F0F0F0Fu;
+                    const uint32_t a2 = (cur.w[0][k].y >> (4 * h)) & 0x0F0F0F0Fu, a3 = (cur.w[1][k].y >> (4 * h)) & 0x0F0F0F0Fu;
+                    int c[4];
+                    mma_u8s8(c, a0, a1, a2, a3, bv.x, bv.y);
+                    const int s0 = (int)((sc[0][j >> 2] >> (8 * (j & 3))) & 0xFFu), s1 = (int)((sc[1][j >> 2] >> (8 * (j & 3))) & 0xFFu);
+                    isum[0] += s0 * c[0];
+                    isum[1] += s0 * c[1];
+                    isum[2] += s1 * c[2];
+                    isum[3] += s1 * c[3];
+                }
+            }
+            // mins: sum_j m_j * (sum of q over sub-block j), tokens 2t and 2t + 1
+            const uint4 u0 = *reinterpret_cast<const uint4*>(sub0 + (size_t)b * 8u);
+            const uint4 u1 = *reinterpret_cast<const uint4*>(sub1 + (size_t)b * 8u);
+            const float da0 = da0p[b], da1 = da1p[b];
+            int mp[4];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                int m0 = dp2a_lo(u0.x, mn[r][0], 0), m1 = dp2a_lo(u1.x, mn[r][0], 0);
+                m0 = dp2a_hi(u0.y, mn[r][0], m0);
+                m1 = dp2a_hi(u1.y, mn[r][0], m1);
+                m0 = dp2a_lo(u0.z, mn[r][1], m0);
+                m1 = dp2a_lo(u1.z, mn[r][1], m1);
+                m0 = dp2a_hi(u0.w, mn[r][1], m0);
+                m1 = dp2a_hi(u1.w, mn[r][1], m1);
+                mp[2 * r] = m0;
+                mp[2 * r + 1] = m1;
+            }
+            acc[0] += (dw[0] * da0) * (float)isum[0] - (dmin[0] * da0) * (float)mp[0];
+            acc[1] += (dw[0] * da1) * (float)isum[1] - (dmin[0] * da1) * (float)mp[1];
+            acc[2] += (dw[1] * da0) * (float)isum[2] - (dmin[1] * da0) * (float)mp[2];
+            acc[3] += (dw[1] * da1) * (float)isum[3] - (dmin[1] * da1) * (float)mp[3];
+            cur = nxt;
+        }
+        // ---- add the KS partial sums of every row group of the set and store; the two halves of s_red alternate, so
+        //      one barrier per set is enough (a half is rewritten two sets later, after the barrier in between) ----
+        float* red = s_red + parity * (kWarps * 128u) + warp * 128u;
+        red[g * 8u + 2u * t] = acc[0];
+        red[g * 8u + 2u * t + 1u] = acc[1];
+        red[(g + 8u) * 8u + 2u * t] = acc[2];
+        red[(g + 8u) * 8u + 2u * t + 1u] = acc[3];
+        __syncthreads();
+        const float* rd = s_red + parity * (kWarps * 128u);
+        // thread -> (token m, row of the set): rows contiguous, so the stores of a token are contiguous
+        for (uint32_t i = threadIdx.x; i < RG * 16u * p.M; i += kThreads) {
+            const uint32_t m = i / (RG * 16u), rr = i - m * (RG * 16u), grp = rr >> 4, r = rr & 15u;
+            const uint32_t row = (set * RG + grp) * 16u + r;
+            if (row < p.N) {
+                float v = 0.0f;
+#pragma unroll
+                for (int s = 0; s < KS; ++s) v += rd[(grp * KS + s) * 128u + r * 8u + m];
+                p.dst[(size_t)m * p.dst_stride + row] = v;
+            }
+        }
+        parity ^= 1u;
+    }
+}
+
+template <int KS>
+static AcResult launch_ks(const LaunchArgs& a, const Params& p, uint32_t smem_bytes) {
+    if (!ensure_dynamic_smem<gemv_mma_q4k_kernel<KS>>((int)kSmemLimit)) return AC_ERR_INVALID_WORK_GROUP_SIZE;
+    const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
+    const uint32_t groups = (p.N + 15u) / 16u, rg = kWarps / KS, n_sets = (groups + rg - 1u) / rg;
+    launch_pdl(gemv_mma_q4k_kernel<KS>, dim3(n_sets < sms ? n_sets : sms), dim3(kThreads), smem_bytes, a.stream, p);
+    return check_launch();
+}
+
+}  // namespace gm
+
+// Shared-memory bytes of ameva_mmvm_q4_K: the activations of M token rows plus a row of zeros, their per-block records
+// and two sets of partial sums. The kernel serves the (M, K) for which this fits 200 KB.
+static uint32_t mmvm_smem_bytes(uint32_t M, uint32_t K) {
+    const uint32_t B = K >> 8, MR = M + 1u;
+    return MR * (K + gm::kActPad) + MR * B * 16u + MR * B * 4u + 2u * gm::kWarps * 128u * 4u;
+}
+
+// ameva_mmvm_q4_K: bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 dst f32 [M][dst_stride];  push {M (1..8), N, K (% 256), dst_stride}
+// (M + 1) (K + 32) bytes of activations must fit shared memory (M = 8: K <= 20480; M = 1: any K of the configurations);
+// beyond that AC_ERR_INVALID_SHAPE (callers keep the dp4a kernels there).
+AcResult launch_mmvm_q4_K(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
+    if (N == 0 || K == 0 || (K & 255u) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t B = K >> 8;
+    if (a.range[0] < (uint64_t)N * B * kQ4KQBytes || a.range[1] < (uint64_t)N * B * kQ4KSBytes ||
+        a.range[2] < (uint64_t)M * K || a.range[3] < (uint64_t)M * B * kABBytes ||
+        a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if (((uintptr_t)a.ptr[0] & 15u) || ((uintptr_t)a.ptr[1] & 15u) || ((uintptr_t)a.ptr[2] & 15u) ||
+        ((uintptr_t)a.ptr[3] & 15u))
+        return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    if ((uint64_t)(M + 1u) * (K + gm::kActPad) > gm::kSmemLimit) return AC_ERR_INVALID_SHAPE;
+    const uint32_t smem = mmvm_smem_bytes(M, K);
+    if (smem > gm::kSmemLimit) return AC_ERR_INVALID_SHAPE;
+    gm::Params p;
+    p.Q = (const uint8_t*)a.ptr[0];
+    p.S = (const uint4*)a.ptr[1];
+    p.AQ = (const int8_t*)a.ptr[2];
+    p.AB = (const uint8_t*)a.ptr[3];
+    p.dst = (float*)a.ptr[4];
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.dst_stride = dst_stride;
+    // K split: the 16 warps of a CTA work on as few row groups at a time as the 256-blocks of a row allow (one block
+    // per warp at least), which keeps the sets small and the shares of the SMs even
+    uint32_t ks = 16;
+    while (ks > 1u && ks > B) ks >>= 1;
+    switch (ks) {
+        case 1: return gm::launch_ks<1>(a, p, smem);
+        case 2: return gm::launch_ks<2>(a, p, smem);
+        case 4: return gm::launch_ks<4>(a, p, smem);
+        case 8: return gm::launch_ks<8>(a, p, smem);
+        default: return gm::launch_ks<16>(a, p, smem);
+    }
+}
+
+}  // namespace amv

@@ -26,10 +26,14 @@ AcResult launch_mmtc_q4_0_mp(const LaunchArgs&);
 AcResult launch_mmtc_q8_0_mp(const LaunchArgs&);
 AcResult launch_mmtc_q4_K_mp(const LaunchArgs&);
 AcResult launch_mmvqb_q4_K_mp(const LaunchArgs&);
+AcResult launch_mmvm_q4_K(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
 AcResult launch_peer_barrier(const LaunchArgs&);
+AcResult launch_peer_push_barrier(const LaunchArgs&);
+AcResult launch_peer_copy(const LaunchArgs&);
+AcResult launch_peer_join(const LaunchArgs&);
 AcResult launch_read_probe(const LaunchArgs&);
 AcResult launch_mmvq_q4_0(const LaunchArgs&);
 AcResult launch_mmvq_q4_0_dump(const LaunchArgs&);
@@ -63,10 +67,14 @@ static const KernelEntry kTable[] = {
     {"ameva_mmtc_q8_0_mp", 12, 28, {608, 1, 1}, launch_mmtc_q8_0_mp},
     {"ameva_mmtc_q4_K_mp", 12, 28, {608, 1, 1}, launch_mmtc_q4_K_mp},
     {"ameva_mmvqb_q4_K_mp", 12, 20, {256, 1, 1}, launch_mmvqb_q4_K_mp},
+    {"ameva_mmvm_q4_K", 5, 16, {256, 1, 1}, launch_mmvm_q4_K},
     {"ameva_mmvs_q4_0", 12, 24, {288, 1, 1}, launch_mmvs_q4_0},
     {"ameva_mmvs_q8_0", 12, 24, {288, 1, 1}, launch_mmvs_q8_0},
     {"ameva_mmvs_q4_K", 12, 24, {288, 1, 1}, launch_mmvs_q4_K},
     {"ameva_peer_barrier", 8, 12, {32, 1, 1}, launch_peer_barrier},
+    {"ameva_peer_push_barrier", 16, 28, {256, 1, 1}, launch_peer_push_barrier},
+    {"ameva_peer_copy", 8, 16, {1, 1, 1}, launch_peer_copy},
+    {"ameva_peer_join", 1, 0, {1, 1, 1}, launch_peer_join},
     {"ameva_read_probe", 2, 8, {256, 1, 1}, launch_read_probe},
     {"ameva_mmvq_q4_0", 5, 16, {256, 1, 1}, launch_mmvq_q4_0},
     {"ameva_mmvq_q4_0_dump", 6, 16, {256, 1, 1}, launch_mmvq_q4_0_dump},

@@ -46,6 +46,7 @@ struct AcContext {
     uint32_t* workspace;    // kWorkspaceBytes of zeroed device memory for the kernels' cross-CTA flags
     uint32_t live_buffers, live_kernels, live_events, live_batches;
     uint64_t id;
+    SideQueues side;        // copy queues beside the stream, created by the first launcher that needs them
 };
 
 struct AcBuffer {
@@ -184,6 +185,7 @@ AcResult launch_record(AcContext* ctx, const KernelEntry* e, uint32_t nbind, voi
     a.sm_count = ctx->prop.multiProcessorCount;
     a.workspace = ctx->workspace;
     a.workspace_bytes = kWorkspaceBytes;
+    a.side = &ctx->side;
     return e->launch(a);
 }
 
@@ -369,6 +371,14 @@ AcResult ac_runtime_context_destroy(AcContext* ctx) {
     if (ctx->live_buffers || ctx->live_kernels || ctx->live_events || ctx->live_batches) return AC_ERR_RESOURCE_IN_USE;
     DeviceGuard g(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    if (ctx->side.ready) {
+        for (int i = 0; i < 8; ++i) {
+            cudaStreamSynchronize(ctx->side.stream[i]);
+            cudaStreamDestroy(ctx->side.stream[i]);
+            cudaEventDestroy(ctx->side.done[i]);
+        }
+        cudaEventDestroy(ctx->side.fork);
+    }
     cudaStreamDestroy(ctx->stream);
     cudaFreeHost(ctx->status_host);
     cudaFree(ctx->workspace);

@@ -26,6 +26,15 @@ FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in
 FUSED_QUANT_MAX_ELEMS = 64 << 20    # N*K up to which the fused launch is used (larger ones are not launch-bound)
 STREAMED_MAX_ROW_BYTES = 6400        # packed bytes per weight row up to which the streamed GEMV stages whole rows
 STREAMED_MIN_WEIGHT_BYTES = 64 << 20  # one activation row: weight bytes from which the streamed GEMV is the default
+
+
+def mma_gemv_fits(M: int, K: int) -> bool:
+    """Q4_K, M <= 8: whether ameva_mmvm_q4_K can hold the M activation rows (plus one row of zeros), their per-block
+    records and its partial sums in 200 KB of shared memory (M = 8: K <= 20480)."""
+    rows = M + 1
+    return K % 256 == 0 and rows * (K + 32) + rows * (K // 256) * 20 + 16384 <= 200 * 1024
+
+
 GEMV_MAX_M = 8   # decode GEMV serves M <= 8 (ggml-ameva.cpp:3607-3804 sends 2 <= M < 8 to the GEMV family as well)
 AB_BYTES = 48
 
@@ -168,8 +177,11 @@ class MulMat:
 
     def __init__(self, ctx: rt.Context, weight, max_m: int, *, round_mode: int = ROUND_NEAREST_EVEN,
                  q8k_mode: int = Q8K_GGML, dump_block_sums: bool = False, exact: bool = False,
-                 streamed: Optional[bool] = None, fused_quantize: bool = False) -> None:
+                 streamed: Optional[bool] = None, fused_quantize: bool = False, mma: Optional[bool] = None) -> None:
         self.ctx = ctx
+        # M <= 8 over Q4_K: the GEMV on the warp-level integer tensor instruction (ameva_mmvm_q4_K). None = with 2..8
+        # activation rows wherever they fit; True also takes a single row; False never.
+        self.mma = mma
         # M <= 8: stage the weight rows in shared memory by bulk copies (ameva_mmvs_*). None = where it measures faster
         # than the register-staged kernels (see streamed_pays); True / False force the choice.
         self.streamed = streamed
@@ -302,6 +314,16 @@ class MulMat:
             return
         if epilogue is not None and (M != 1 or t == GGML_TYPE_I2_S or self.dump or peers):
             raise MulMatUnsupported("the fused epilogue is built for one activation row of a Q4_0 / Q8_0 / Q4_K product")
+        use_mma = (t == GGML_TYPE_Q4_K and (2 if self.mma is None else 1) <= M <= GEMV_MAX_M and mma_gemv_fits(M, K)
+                   and not self.dump and not peers and epilogue is None and self.mma is not False
+                   and self.streamed is not True)
+        if self.mma is True and not use_mma and not use_tc:
+            raise MulMatUnsupported("ameva_mmvm_q4_K serves Q4_K with up to 8 activation rows that fit shared memory")
+        if use_mma and not use_tc:
+            self.path = "mmvm"
+            batch.dispatch(ctx.kernel("ameva_mmvm_q4_K"), [self.qbind, self.sbind, self.aq, self.ad, (dst, dst_offset)],
+                           [M, N, K, dst_stride], ((N + 15) // 16, 1, 1))
+            return
         if streamed and epilogue is None:
             # weight rows staged in shared memory by bulk copies, several stages ahead of the dot products; also carries
             # the output exchange of a row-sharded projection (every output row stored to every rank)
@@ -340,7 +362,7 @@ class MulMat:
 
     def run(self, x: rt.Buffer, dst: rt.Buffer, M: int, **kw) -> float:
         """Record, submit, wait. Returns the GPU time of the batch in microseconds."""
-        batch = self.ctx.batch(64)
+        batch = self.ctx.batch(64 + (M + GEMV_MAX_M - 1) // GEMV_MAX_M)   # (the exact path walks M in chunks of 8 rows)
         try:
             self.record(batch, x, dst, M, **kw)
             ev = batch.submit()
@@ -470,16 +492,22 @@ class PeerExchange:
     """The output side of a row-sharded mul_mat on the ranks of one box (one process per GPU).
 
     Every rank owns a full [M][N] fp32 output and a small flag array, both exported to the other ranks
-    (``handles()`` -> exchange with any out-of-band channel -> ``connect()``). ``MulMat.record(..., peers=ex.peers)``
-    then stores each rank's rows into every rank's output, and ``record_barrier`` appends the cross-GPU barrier after
-    which the local output is complete. No collective library is involved in the data path."""
+    (``handles()`` -> exchange with any out-of-band channel -> ``connect()``). Three ways to assemble the output, none of
+    them with a collective library in the data path:
+      * fused: ``MulMat.record(..., peers=ex.peers)`` stores each rank's rows into every rank's output from the kernel's
+        epilogue; ``record_barrier`` appends the cross-GPU barrier after which the local output is complete;
+      * decode sizes (M <= 8): the mul_mat writes locally and ``record_push`` appends one kernel that copies the rank's
+        slice to every peer and is the barrier as well;
+      * prefill sizes: the mul_mat runs in chunks of token rows; after each chunk ``record_copy`` hands the rank's column
+        block of those rows to the copy engines (one queue per peer, beside the compute stream), so the transfer of a
+        chunk overlaps the mul_mat of the next; ``record_join`` + ``record_barrier`` close the step."""
 
     def __init__(self, ctx: rt.Context, rank: int, world: int, out_bytes: int) -> None:
         if not 2 <= world <= 8 or not 0 <= rank < world:
             raise MulMatUnsupported("PeerExchange needs 2..8 ranks")
         self.ctx, self.rank, self.world = ctx, rank, world
         self.out = ctx.buffer(out_bytes)
-        self.flags = ctx.buffer(256)
+        self.flags = ctx.buffer(512)     # words 0..63: ameva_peer_barrier; words 64..127: ameva_peer_push_barrier
         self.flags.fill(0)
         self.epoch = 0
         self.peer_out, self.peer_flags = {}, {}
@@ -492,16 +520,39 @@ class PeerExchange:
         for r, (oh, fh, nbytes) in enumerate(all_handles):
             if r != self.rank:
                 self.peer_out[r] = self.ctx.open_ipc(oh, nbytes)
-                self.peer_flags[r] = self.ctx.open_ipc(fh, 256)
+                self.peer_flags[r] = self.ctx.open_ipc(fh, 512)
 
     @property
     def peers(self):
         return [self.peer_out[r] for r in sorted(self.peer_out)]
 
+    def _by_rank(self, own, others, offset=0, size=None):
+        return [((own if r == self.rank or r >= self.world else others[r]), offset, size) for r in range(8)]
+
     def record_barrier(self, batch: rt.Batch) -> None:
         """The kernel counts its own uses (epoch 0), so a recorded step can be replayed."""
-        slots = [self.flags if r == self.rank or r >= self.world else self.peer_flags[r] for r in range(8)]
-        batch.dispatch(self.ctx.kernel("ameva_peer_barrier"), slots, [self.rank, self.world, 0], (1, 1, 1))
+        batch.dispatch(self.ctx.kernel("ameva_peer_barrier"), self._by_rank(self.flags, self.peer_flags, 0, 256),
+                       [self.rank, self.world, 0], (1, 1, 1))
+
+    def record_push(self, batch: rt.Batch, M: int, stride: int, row0: int, rows: int) -> None:
+        """M <= 8: copy rows [row0, row0 + rows) of every token row of the local output to all peers and wait until the
+        peers' slices have arrived (one kernel; `stride` = floats between token rows)."""
+        binds = self._by_rank(self.flags, self.peer_flags, 256, 256) + self._by_rank(self.out, self.peer_out)
+        batch.dispatch(self.ctx.kernel("ameva_peer_push_barrier"), binds,
+                       [self.rank, self.world, 0, M, stride, row0, rows], (self.world - 1, 1, 1))
+
+    def record_copy(self, batch: rt.Batch, m0: int, mc: int, stride: int, row0: int, rows: int) -> None:
+        """Token rows [m0, m0 + mc): queue the copy of this rank's column block to every peer on the copy engines."""
+        off = (m0 * stride + row0) * 4
+        if off % 64:
+            raise MulMatUnsupported("the column block of a rank must start on a 64-byte boundary")
+        size = ((mc - 1) * stride + rows) * 4
+        peers = self.peers
+        binds = [(self.out, off, size)] + [(p, off, size) for p in peers] + [(self.out, off, size)] * (7 - len(peers))
+        batch.dispatch(self.ctx.kernel("ameva_peer_copy"), binds, [mc, rows * 4, stride * 4, len(peers)], (1, 1, 1))
+
+    def record_join(self, batch: rt.Batch) -> None:
+        batch.dispatch(self.ctx.kernel("ameva_peer_join"), [(self.flags, 0, 64)], [], (1, 1, 1))
 
     def destroy(self) -> None:
         for b in list(self.peer_out.values()) + list(self.peer_flags.values()) + [self.out, self.flags]:

@@ -331,7 +331,8 @@ class Measurement:
             my_blocks = [self.blocks[0].reshape(n0, per_row)[self.row0:self.row0 + self.rows]]
             self.shard_bytes = weight_bytes(t, max(self.rows, 1), K)
         self.pool_n = max(2, min(64, -(-2 * L2_BYTES // max(self.shard_bytes, 1)) + 1))
-        streamed = {"auto": None, "register": False, "streamed": True}[args.gemv]
+        streamed = {"auto": None, "register": False, "streamed": True, "mma": None}[args.gemv]
+        mma = {"auto": None, "register": False, "streamed": False, "mma": True}[args.gemv]
         self.weights, self.mms = [], []
         for _ in range(self.pool_n):
             if self.grouped:
@@ -341,7 +342,8 @@ class Measurement:
             else:
                 w = qmm.QuantWeight.from_ggml(ctx, t, my_blocks[0], self.rows, K, self.scale)
                 self.weights.append([w])
-                self.mms.append(qmm.MulMat(ctx, w, M, streamed=streamed, fused_quantize=not args.no_fused_quantize))
+                self.mms.append(qmm.MulMat(ctx, w, M, streamed=streamed, mma=mma if t == Q4_K else None,
+                                           fused_quantize=args.fused_quantize and mma is not True))
         self.x_dev = ctx.buffer(data=self.x)
         self.probe_sink = ctx.buffer(64)
         self.launches_per_step = 0
@@ -395,18 +397,32 @@ class Measurement:
             before = batch.stats().dispatches if i == 0 else None
             if self.grouped:
                 mm.record(batch, self.x_dev, self.out_bufs)
-            else:
-                mm.record(batch, self.x_dev, self.out_buf, self.M, dst_offset=self.out_off, dst_stride=self.out_stride,
-                          quantize=quantize,
-                          peers=self.ex.peers if (self.ex and self.exchange == "fused" and self.exchange_on) else None)
-            if self.ex and self.exchange == "copy" and self.exchange_on:
-                self.ex.record_push(batch, self.M, self.row0, self.rows)
-            if self.ex and self.exchange_on:
+            elif self.ex and self.exchange == "copy" and self.exchange_on and self.M > GEMV_MAX_M:
+                # chunks of token rows: the copy engines move chunk c to the peers while the tensor cores compute c + 1
+                chunk = self.env.args.chunk_tokens
+                for m0 in range(0, self.M, chunk):
+                    mc = min(chunk, self.M - m0)
+                    mm.record(batch, self.x_dev, self.out_buf, mc, x_offset=m0 * self.K * 4,
+                              dst_offset=self.out_off + m0 * self.out_stride * 4, dst_stride=self.out_stride,
+                              quantize=quantize)
+                    self.ex.record_copy(batch, m0, mc, self.out_stride, self.row0, self.rows)
+                self.ex.record_join(batch)
                 self.ex.record_barrier(batch)
+            else:
+                fused = self.ex and self.exchange == "fused" and self.exchange_on
+                mm.record(batch, self.x_dev, self.out_buf, self.M, dst_offset=self.out_off, dst_stride=self.out_stride,
+                          quantize=quantize, peers=self.ex.peers if fused else None)
+                if self.ex and self.exchange == "copy" and self.exchange_on:
+                    self.ex.record_push(batch, self.M, self.out_stride, self.row0, self.rows)   # push + barrier
+                elif fused:
+                    self.ex.record_barrier(batch)
             if i == 0 and quantize is True:
                 self.launches_per_step = batch.stats().dispatches - before
 
     def use_replay(self):
+        # (the copy exchange forks copy queues off the stream at record time; its steps are submitted, not replayed)
+        if self.exchange == "copy":
+            return self.M <= GEMV_MAX_M and not self.env.args.no_replay
         return self.exchange in ("none", "fused") and not self.env.args.no_replay
 
     def replay_batches(self, quantize, rem):
@@ -720,13 +736,16 @@ def main():
                     help="N > 1: row-shard the primary workload too (strong scaling) instead of token-parallel replicas")
     ap.add_argument("--exchange", choices=["copy", "fused", "nccl"], default="copy",
                     help="how the ranks of a row-sharded mul_mat assemble the output (see the module docstring)")
+    ap.add_argument("--chunk-tokens", type=int, default=256,
+                    help="copy exchange, more than 8 token rows: token rows per mul_mat + copy chunk")
     ap.add_argument("--no-replay", action="store_true", help="one host launch per kernel instead of replayed batches")
     ap.add_argument("--no-overlap", action="store_true", help="e2e: copies and compute in sequence on one stream")
-    ap.add_argument("--gemv", choices=["auto", "register", "streamed"], default="auto",
+    ap.add_argument("--gemv", choices=["auto", "register", "streamed", "mma"], default="auto",
                     help="M <= 8: register-staged kernels (ameva_mmvq*), the one that stages the weight rows in shared "
                          "memory (ameva_mmvs_*), or the library's own choice")
-    ap.add_argument("--no-fused-quantize", action="store_true",
-                    help="M == 1, small projections: keep the separate quantize kernel (default: one launch, ameva_mmv*_fq)")
+    ap.add_argument("--fused-quantize", action="store_true",
+                    help="M == 1, small projections: quantize inside the GEMV launch (ameva_mmv*_fq); in replayed batches "
+                         "the two-kernel sequence measures as fast, it saves a host launch otherwise")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     name = args.workload
@@ -758,7 +777,7 @@ def main():
     check = m.parity(y_host) if rank == 0 and m.rows else None
 
     decode = sharded = None
-    sub_steps = max(20, min(args.steps, 200))
+    sub_steps = 200   # (decode steps take microseconds: enough of them to amortise the replay launches, whatever --steps is)
     if not args.no_decode and world == 1 and name == "cfg2":
         decode = {w: sub_line(env, w, "single", sub_steps, 5, True) for w in DECODE_LINES}
     if not args.no_sharded and name == "cfg2":

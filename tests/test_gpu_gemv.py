@@ -33,7 +33,12 @@ def run_case(ctx, t, M, N, K, seed=0, dump=True, check_strict=True, streamed=Fal
     mm.run(xb, dst, M)
     y = dst.read(np.float32).reshape(M, N)
     # the shared-memory-streamed kernel runs on request, for the scaled types and K % 256 == 0, and never with the dump
-    assert mm.path == ("mmvs" if (streamed and t != I2_S and K % 256 == 0 and not dump) else "mmvq")
+    if streamed and t != I2_S and K % 256 == 0 and not dump:
+        assert mm.path == "mmvs"
+    elif t == Q4_K and 2 <= M <= 8 and not dump and qmm.mma_gemv_fits(M, K):
+        assert mm.path == "mmvm"      # Q4_K with several activation rows: the integer tensor instruction
+    else:
+        assert mm.path == "mmvq"
     want, sums, aq = oracle_mul_mat(t, blocks, scale, x, N, K)
     # 1. activation quantization: bytes equal
     if t in (Q4_0, Q8_0):
@@ -358,9 +363,10 @@ def test_gemv_fused_quantize_limits(ctx):
 
 
 def test_gemv_default_kernel_choice(ctx):
-    """Without a request the streamed kernel serves several activation rows of short-row weights and large matrices;
-    small single-row products stay on the register-staged kernels. Both agree with the oracle."""
-    cases = [(Q4_K, 8, 272, 4096, "mmvs"), (Q4_K, 3, 272, 4096, "mmvq"), (Q4_K, 1, 272, 4096, "mmvq"),
+    """Without a request: Q4_K with 2..8 activation rows runs on the integer tensor instruction, the streamed kernel
+    serves several activation rows of the other types' short-row weights and large matrices, small single-row products
+    stay on the register-staged kernels. All agree with the oracle."""
+    cases = [(Q4_K, 8, 272, 4096, "mmvm"), (Q4_K, 3, 272, 4096, "mmvm"), (Q4_K, 1, 272, 4096, "mmvq"),
              (Q8_0, 4, 130, 2048, "mmvs"), (Q4_0, 8, 96, 512, "mmvs"), (Q4_K, 8, 64, 28672, "mmvq"),
              (Q4_K, 1, 16384, 8192, "mmvs")]
     for t, M, N, K, path in cases:
@@ -444,3 +450,60 @@ def test_grouped_launch_refusals(ctx):
         b.destroy()
     for v in (w, w2, w3):
         v.destroy()
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 11008, 4096), (2, 4096, 4096), (5, 272, 1024), (8, 40, 256), (3, 17, 512),
+                                   (8, 4096, 11008), (7, 1000, 8192), (4, 16, 22528), (1, 4096, 4096), (1, 2000, 28672),
+                                   (6, 50, 2048), (8, 3000, 768)])
+def test_gemv_on_the_integer_tensor_instruction(ctx, M, N, K):
+    """Q4_K with up to 8 activation rows on mma.sync (ameva_mmvm_q4_K): the integer sums are exact, so the output must
+    agree with the dp4a kernel to fp32 summation order (a few ulp) and with the oracle within the path's tolerance; ragged
+    N (not a multiple of 16), every K split (1, 2, 4, 8, 16 warps per row group), rows whose blocks do not divide evenly
+    among the warps, and the configuration-3 shapes at full size."""
+    blocks, scale = make_weights(Q4_K, N, K, N + K)
+    x = make_acts(M, K, M)
+    w = qmm.QuantWeight.from_ggml(ctx, Q4_K, blocks, N, K, scale)
+    a, b = qmm.MulMat(ctx, w, M, mma=True, fused_quantize=False), qmm.MulMat(ctx, w, M, mma=False, streamed=False)
+    xb, ya, yb = ctx.buffer(data=x), ctx.buffer(M * N * 4), ctx.buffer(M * N * 4)
+    ya.fill(0xFF)
+    a.run(xb, ya, M)
+    b.run(xb, yb, M)
+    assert (a.path, b.path) == ("mmvm", "mmvq")
+    got, ref = ya.read(np.float32).reshape(M, N), yb.read(np.float32).reshape(M, N)
+    assert np.isfinite(got).all()
+    assert max_normalised_error(got, ref) <= 2e-6
+    want, _, _ = oracle_mul_mat(Q4_K, blocks, scale, x, N, K, want_sums=False)
+    assert max_normalised_error(got, want) <= TOL
+    ref64, norm = oracle.mul_mat_f64(dequantize(Q4_K, blocks, scale, N, K), _dequant_acts(Q4_K, oracle.quantize_q8_K(x), M, K))
+    assert np.max(np.abs(got - ref64) / np.maximum(norm, 1e-30)) <= STRICT_TOL
+    for v in (xb, ya, yb):
+        v.destroy()
+    a.destroy()
+    b.destroy()
+    w.destroy()
+
+
+def test_gemv_mma_limits(ctx):
+    K = 28672
+    blocks, scale = make_weights(Q4_K, 16, K, 1)
+    w = qmm.QuantWeight.from_ggml(ctx, Q4_K, blocks, 16, K, scale)
+    assert qmm.mma_gemv_fits(1, K) and qmm.mma_gemv_fits(5, K) and not qmm.mma_gemv_fits(8, K)
+    assert qmm.mma_gemv_fits(8, 20480) and not qmm.mma_gemv_fits(8, 20736)
+    with pytest.raises(qmm.MulMatUnsupported):      # 8 token rows of this K are beyond what shared memory holds
+        mm = qmm.MulMat(ctx, w, 8, mma=True)
+        xb, dst = ctx.buffer(8 * K * 4), ctx.buffer(8 * 16 * 4)
+        mm.run(xb, dst, 8)
+    mm = qmm.MulMat(ctx, w, 8)                       # the default keeps them on the other kernels
+    xb, dst = ctx.buffer(data=make_acts(8, K, 2)), ctx.buffer(8 * 16 * 4)
+    mm.run(xb, dst, 8)
+    assert mm.path in ("mmvq", "mmvs")
+    batch = ctx.batch(4)
+    with pytest.raises(rt.AmevaComputeError) as e:   # and the launcher itself refuses it
+        batch.dispatch(ctx.kernel("ameva_mmvm_q4_K"), [mm.qbind, mm.sbind, mm.aq, mm.ad, dst], [8, 16, K, 16], (1, 1, 1))
+        batch.submit().wait()
+    assert e.value.code == rt.AC_ERR_INVALID_SHAPE
+    batch.destroy()
+    for v in (xb, dst):
+        v.destroy()
+    mm.destroy()
+    w.destroy()
