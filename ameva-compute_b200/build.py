@@ -22,7 +22,7 @@ ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libac_runtime_b200.so")
 LEGACY_LIB = os.path.join(HERE, "libamuda_b200.so")
 
-RUNTIME_SOURCES = ["runtime.cu", "registry.cu", "act_quant.cu", "gemv.cu", "gemv_bulk.cu", "gemv_mma.cu", "gemm_tc.cu", "noalloc.cu",
+RUNTIME_SOURCES = ["runtime.cu", "registry.cu", "act_quant.cu", "gemv.cu", "gemv_bulk.cu", "gemv_mma.cu", "elementwise.cu", "gemm_tc.cu", "noalloc.cu",
                    "peer_sync.cu", "read_probe.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -97,51 +97,66 @@ __global__ void __launch_bounds__(256) quant_q8_K_kernel(const float* __restrict
 // and the GEMM's epilogue multiplies it back per token row.
 //   SCHEME 0: per-32 (Q8_0) scales, `mode` = round_mode; SCHEME 1: per-256 (Q8_K), `mode` as ameva_quant_a8b.
 // ---------------------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float block_max_256(float v, float* red) {
+// Row maximum over a CTA of `WARPS` warps; every thread gets the result.
+template <int WARPS>
+__device__ __forceinline__ float block_max(float v, float* red) {
     v = warp_max(v);
     if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
     __syncthreads();
     float r = red[0];
 #pragma unroll
-    for (int i = 1; i < 8; ++i) r = fmaxf(r, red[i]);
+    for (int i = 1; i < WARPS; ++i) r = fmaxf(r, red[i]);
     return r;
 }
 
-template <int SCHEME>
-__global__ void __launch_bounds__(256) quant_rows_f16_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
-                                                             uint8_t* __restrict__ ad, __half* __restrict__ ah,
-                                                             float* __restrict__ ae, uint32_t K, uint32_t src_stride,
-                                                             uint32_t mode) {
+// s = 2^-floor(log2(amax)) and its inverse; rows that are all zero (or not finite) keep s = 1
+__device__ __forceinline__ void row_factor(float amax, float& s, float& inv) {
+    int e = 0;
+    if (amax > 0.0f && amax <= 3.4e38f) e = min(126, max(-126, ilogbf(amax)));
+    s = __int_as_float((127 - e) << 23);
+    inv = __int_as_float((127 + e) << 23);
+}
+
+constexpr int kRowThreads = 512;
+
+// The row is read once: a thread keeps its J pieces in registers across the row maximum (J = pieces per thread, a
+// template parameter so that they are registers). SCHEME 0: a piece is one float4, piece i = t + 512 j, eight
+// consecutive lanes hold one 32-unit; SCHEME 1: a piece is 8 consecutive floats, piece i = t + 512 j, a warp holds one
+// 256-block.
+template <int SCHEME, int J>
+__global__ void __launch_bounds__(kRowThreads) quant_rows_f16_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
+                                                                     uint8_t* __restrict__ ad, __half* __restrict__ ah,
+                                                                     float* __restrict__ ae, uint32_t K,
+                                                                     uint32_t src_stride, uint32_t mode) {
     pdl_trigger();   // the GEMM behind this kernel may be scheduled already; it waits for this grid before reading
     pdl_wait();      // the activations may come from the kernel before
-    __shared__ float red[8];
+    __shared__ float red[kRowThreads / 32];
     const uint32_t m = blockIdx.x, t = threadIdx.x, lane = t & 31u;
     const float* row = src + (size_t)m * src_stride;
     float amax = 0.0f;
-    for (uint32_t i = t; i < (K >> 2); i += 256u) {
-        const float4 v = *reinterpret_cast<const float4*>(row + 4u * i);
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-    }
-    amax = block_max_256(amax, red);
-    // s = 2^-floor(log2(amax)); rows that are all zero (or not finite) keep s = 1
-    int e = 0;
-    if (amax > 0.0f && amax <= 3.4e38f) e = min(126, max(-126, ilogbf(amax)));
-    const float s = __int_as_float((127 - e) << 23), inv = __int_as_float((127 + e) << 23);
-    if (t == 0) ae[m] = inv;
-
     if constexpr (SCHEME == 0) {
-        const uint32_t U = K >> 5, sub = t & 7u;
+        const uint32_t P = K >> 2, U = K >> 5, sub = t & 7u;
+        float4 v[J];
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const uint32_t i = t + (uint32_t)kRowThreads * j;
+            v[j] = i < P ? *reinterpret_cast<const float4*>(row + 4u * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
+        }
+        amax = block_max<kRowThreads / 32>(amax, red);
+        float s, inv;
+        row_factor(amax, s, inv);
+        if (t == 0) ae[m] = inv;
         uint32_t* adw = reinterpret_cast<uint32_t*>(ad);
-        for (uint32_t base = 0; base < U; base += 32u) {   // 32 units per pass; whole warps stay together
-            const uint32_t u = base + (t >> 3);
-            const bool live = u < U;
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (live) x = *reinterpret_cast<const float4*>(row + 32u * u + 4u * sub);   // (second read: L1 / L2)
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const uint32_t i = t + (uint32_t)kRowThreads * j, u = i >> 3;
+            const bool live = i < P;   // (P is a multiple of 8: the eight lanes of a unit are live together)
             int q[4], sum;
             float d;
-            quant_unit_q8_0(x, mode, q, d, sum);
+            quant_unit_q8_0(v[j], mode, q, d, sum);
             if (live) {
-                reinterpret_cast<uint32_t*>(aq + (size_t)m * K + 32u * u)[sub] = pack_q4(q);
+                reinterpret_cast<uint32_t*>(aq + (size_t)m * K)[i] = pack_q4(q);
                 if (sub == 0) adw[(size_t)m * U + u] = scale_word_q8_0(d, sum);
                 const float dh = __fmul_rn(h2f(f2h(d)), s);   // the fp16-rounded scale the dot product uses, times 2^-e
                 const __half2 h01 = __floats2half2_rn((float)q[0] * dh, (float)q[1] * dh);
@@ -149,18 +164,37 @@ __global__ void __launch_bounds__(256) quant_rows_f16_kernel(const float* __rest
                 uint2 o;
                 o.x = *reinterpret_cast<const uint32_t*>(&h01);
                 o.y = *reinterpret_cast<const uint32_t*>(&h23);
-                *reinterpret_cast<uint2*>(ah + (size_t)m * K + 32u * u + 4u * sub) = o;
+                *reinterpret_cast<uint2*>(ah + (size_t)m * K + 4u * i) = o;
             }
         }
     } else {
         const uint32_t B = K >> 8;
-        for (uint32_t b = t >> 5; b < B; b += 8u) {   // one warp per 256-block
-            const float* p = row + 256u * b + 8u * lane;
-            const float4 x0 = *reinterpret_cast<const float4*>(p), x1 = *reinterpret_cast<const float4*>(p + 4);
-            const float x[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+        float x[J][8];
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const uint32_t b = (t >> 5) + (uint32_t)(kRowThreads / 32) * j;   // this warp's block
+            float4 x0 = make_float4(0.f, 0.f, 0.f, 0.f), x1 = x0;
+            if (b < B) {
+                const float* p = row + 256u * b + 8u * lane;
+                x0 = *reinterpret_cast<const float4*>(p);
+                x1 = *reinterpret_cast<const float4*>(p + 4);
+            }
+            x[j][0] = x0.x; x[j][1] = x0.y; x[j][2] = x0.z; x[j][3] = x0.w;
+            x[j][4] = x1.x; x[j][5] = x1.y; x[j][6] = x1.z; x[j][7] = x1.w;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[j][i]));
+        }
+        amax = block_max<kRowThreads / 32>(amax, red);
+        float s, inv;
+        row_factor(amax, s, inv);
+        if (t == 0) ae[m] = inv;
+#pragma unroll
+        for (int j = 0; j < J; ++j) {
+            const uint32_t b = (t >> 5) + (uint32_t)(kRowThreads / 32) * j;
+            if (b >= B) continue;   // whole warps leave together
             int q[8];
             float d;
-            quant_block_q8_K(x, mode, lane, q, d);
+            quant_block_q8_K(x[j], mode, lane, q, d);
             int sum = 0;
             uint32_t w0 = 0, w1 = 0;
 #pragma unroll
@@ -331,7 +365,13 @@ AcResult launch_quant_a8b(const LaunchArgs& a) {
 // ameva_quant_a8_f16 / ameva_quant_a8b_f16: the quantizers in front of ameva_mmtc_* (more than 8 token rows).
 //   bindings 0 src f32, 1 AQ, 2 AD (per-32 scale words) or AB (per-256 records), 3 AH fp16 [M][K] = fp16(q * d * s_m),
 //            4 AE f32 [M] = 1 / s_m (s_m the power of two that brings row m's largest magnitude into [1, 2))
-//   push {M, K, src_stride (floats), round_mode / mode}
+//   push {M, K, src_stride (floats), round_mode / mode};  K <= 32768
+template <int SCHEME, int J>
+static void launch_rows_j(const LaunchArgs& a, uint32_t M, uint32_t K, uint32_t stride, uint32_t mode) {
+    launch_pdl(quant_rows_f16_kernel<SCHEME, J>, dim3(M), dim3(kRowThreads), 0, a.stream, (const float*)a.ptr[0],
+               (int8_t*)a.ptr[1], (uint8_t*)a.ptr[2], (__half*)a.ptr[3], (float*)a.ptr[4], K, stride, mode);
+}
+
 template <int SCHEME>
 static AcResult launch_quant_rows(const LaunchArgs& a) {
     const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], mode = a.push[3];
@@ -342,8 +382,14 @@ static AcResult launch_quant_rows(const LaunchArgs& a) {
         a.range[3] < (uint64_t)M * K * 2u || a.range[4] < (uint64_t)M * 4u)
         return AC_ERR_INVALID_BUFFER_SIZE;
     if (((uintptr_t)a.ptr[0] & 15u) || ((uintptr_t)a.ptr[3] & 15u)) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
-    launch_pdl(quant_rows_f16_kernel<SCHEME>, dim3(M), dim3(256), 0, a.stream, (const float*)a.ptr[0], (int8_t*)a.ptr[1],
-               (uint8_t*)a.ptr[2], (__half*)a.ptr[3], (float*)a.ptr[4], K, stride, mode);
+    // pieces per thread: a row of K floats over 512 threads, 4 (per-32) or 8 (per-256) floats to a piece
+    const uint32_t per_thread = (K + (SCHEME ? 4095u : 2047u)) / (SCHEME ? 4096u : 2048u);
+    if (per_thread <= 1) launch_rows_j<SCHEME, 1>(a, M, K, stride, mode);
+    else if (per_thread <= 2) launch_rows_j<SCHEME, 2>(a, M, K, stride, mode);
+    else if (per_thread <= 4) launch_rows_j<SCHEME, 4>(a, M, K, stride, mode);
+    else if (per_thread <= 8) launch_rows_j<SCHEME, 8>(a, M, K, stride, mode);
+    else if (per_thread <= 16 && SCHEME == 0) launch_rows_j<SCHEME, (SCHEME == 0 ? 16 : 8)>(a, M, K, stride, mode);
+    else return AC_ERR_INVALID_SHAPE;   // K above 32768: beyond the rows this kernel keeps in registers
     return check_launch();
 }
 AcResult launch_quant_a8_f16(const LaunchArgs& a) { return launch_quant_rows<0>(a); }

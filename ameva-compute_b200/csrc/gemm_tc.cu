@@ -274,17 +274,14 @@ __device__ __forceinline__ uint4 raw_chunk(const uint8_t* raw, uint32_t r, uint3
 
 // ---- dequantization of (row r, half h) of one K block: 32 fp16 (or 64 int8) values = 16 TMEM columns -----------------
 // The lanes of a warp are 32 consecutive rows reading the same chunk index, which the swizzle spreads over all banks.
-// wmul: the power of two (2^w_exp, chosen by the host from the tensor's largest magnitude) that brings the weights into
-// fp16's comfortable range; applied to the block scale, so it costs one multiply per 32 weights and no precision.
 template <int TYPE>
 __device__ __forceinline__ void dequant_half(const uint8_t* raw, const uint8_t* sc, uint32_t r, uint32_t h, uint32_t kb,
-                                             float wmul, uint32_t* o) {
+                                             uint32_t* o) {
     if constexpr (TYPE == T_Q8_0) {
         // raw row: 2 K blocks x 64 B; this half: 32 int8 = chunks 4 (kb % 2) + 2h, +1; scale of unit 2 (kb % 4) + h
         const uint32_t c0 = 4u * (kb & 1u) + 2u * h;
         const uint4 q0 = raw_chunk(raw, r, c0), q1 = raw_chunk(raw, r, c0 + 1u);
-        const __half2 d2 = __hmul2(__half2half2(*reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + h) * 2u)),
-                                   __float2half2_rn(wmul));
+        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + h) * 2u));
         const __half2 bias = __float2half2_rn(1152.0f);   // 1024 (magic) + 128 (bytes are q + 128 after the xor)
         const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
 #pragma unroll
@@ -297,8 +294,7 @@ __device__ __forceinline__ void dequant_half(const uint8_t* raw, const uint8_t* 
     } else if constexpr (TYPE == T_Q4_0) {
         // raw row: 4 K blocks x 32 B; this half: one unit of 16 B (byte j = weight j low nibble, weight j + 16 high)
         const uint4 q = raw_chunk(raw, r, 2u * (kb & 3u) + h);
-        const __half2 d2 = __hmul2(__half2half2(*reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + h) * 2u)),
-                                   __float2half2_rn(wmul));
+        const __half2 d2 = __half2half2(*reinterpret_cast<const __half*>(sc + r * 16u + ((kb & 3u) * 2u + h) * 2u));
         const __half2 bias = __float2half2_rn(1032.0f);   // 1024 (magic) + 8 (the nibble offset)
         const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -327,8 +323,8 @@ __device__ __forceinline__ void dequant_half(const uint8_t* raw, const uint8_t* 
             scp = (e & 0x0F0Fu) | ((a >> 2) & 0x3030u);
             mnp = ((e >> 4) & 0x0F0Fu) | ((b >> 2) & 0x3030u);
         }
-        const float dl = h2f((uint16_t)(s.x & 0xFFFFu)) * (float)((scp >> (8u * h)) & 0xFFu) * wmul;
-        const float ml = h2f((uint16_t)(s.x >> 16)) * (float)((mnp >> (8u * h)) & 0xFFu) * wmul;
+        const float dl = h2f((uint16_t)(s.x & 0xFFFFu)) * (float)((scp >> (8u * h)) & 0xFFu);
+        const float ml = h2f((uint16_t)(s.x >> 16)) * (float)((mnp >> (8u * h)) & 0xFFu);
         // One byte permute puts a nibble (as a byte 0..15) into mantissa bits 16..19 of the float 0x3F000000 = 0.5, which
         // then reads 0.5 + q / 256. One fp32 fma gives q dl - ml to about 21 bits (the constant 128 dl costs three of the
         // 24), and one rounding makes the fp16 operand.
@@ -379,7 +375,6 @@ struct Params {
     uint32_t* flags;          // per (tile, CTA of the pair, epilogue warp) sequence words, zero between launches
     float w_scale;
     const float* row_unscale; // scaled types: per token row, the factor the activation quantizer divided out (AE)
-    float w_mul, w_unmul;     // scaled types: 2^w_exp applied to the weights while dequantizing, and 2^-w_exp
     uint32_t diag;
     uint32_t* status;
 };
@@ -678,8 +673,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 if (!(kdiag & 1u)) {
                     const uint8_t* raw = sRaw + rr.idx * C::kRawBytes;
                     const uint8_t* sc = sSc + sr.idx * kScaleBytes;
-                    dequant_half<TYPE>(raw, sc, r, 0u, kb, p.w_mul, o);
-                    dequant_half<TYPE>(raw, sc, r, 1u, kb, p.w_mul, o + 16);
+                    dequant_half<TYPE>(raw, sc, r, 0u, kb, o);
+                    dequant_half<TYPE>(raw, sc, r, 1u, kb, o + 16);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = 0u;
@@ -765,7 +760,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                         // lane j holds the factor of the piece's token row j (scaled types): one load per piece, handed
                         // round by shuffles in the loop below
                         float unscale = 1.0f;
-                        if (!INT8) unscale = __ldg(p.row_unscale + min(m0 + c * 16u + (lane & 15u), p.M - 1u)) * p.w_unmul;
+                        if (!INT8) unscale = __ldg(p.row_unscale + min(m0 + c * 16u + (lane & 15u), p.M - 1u));
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j) {
                             const uint32_t m = m0 + c * 16u + j;
@@ -774,7 +769,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                                 const float total_scale =
                                     __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
                                 y = __fmul_rn((float)(int)v[i][j], total_scale);
-                            } else {   // undo the two power-of-two factors of the fp16 operands (exact)
+                            } else {   // undo the power-of-two factor of the token row's fp16 operand (exact)
                                 y = __uint_as_float(v[i][j]) * __shfl_sync(0xffffffffu, unscale, j);
                             }
                             if (p.tma_store)
@@ -977,8 +972,7 @@ template <int TYPE>
 static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, const void* act, uint64_t act_range,
                        void* dstp, uint64_t dst_range, const void* actscale, uint32_t M, uint32_t N, uint32_t K,
                        uint32_t dst_stride, float w_scale, uint32_t diag, const void* row_unscale, uint64_t unscale_range,
-                       int32_t w_exp, uint32_t n_peers = 0, void* const* peer_dst = nullptr,
-                       const uint64_t* peer_range = nullptr) {
+                       uint32_t n_peers = 0, void* const* peer_dst = nullptr, const uint64_t* peer_range = nullptr) {
     using C = Cfg<TYPE>;
     constexpr uint32_t esz = C::kInt8 ? 1u : 2u;
     if (M == 0 || N == 0 || K == 0 || (K % C::kBlockK) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
@@ -986,7 +980,6 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     if (act_range < (uint64_t)M * K * esz || dst_range < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
         return AC_ERR_INVALID_BUFFER_SIZE;
     if (C::kScales && (!row_unscale || unscale_range < (uint64_t)M * 4u)) return AC_ERR_INVALID_BUFFER_SIZE;
-    if (w_exp < -14 || w_exp > 15) return AC_ERR_KERNEL_ARG_INVALID;   // 2^w_exp must be a normal fp16 number
     if (((uintptr_t)act & 15u) || ((uintptr_t)Qp & 15u) || (C::kScales && ((uintptr_t)Sp & 15u)))
         return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     EncodeTiledFn enc = encode_fn();
@@ -1007,8 +1000,6 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     p.dst_stride = dst_stride;
     p.w_scale = w_scale;
     p.row_unscale = (const float*)row_unscale;
-    p.w_mul = ldexpf(1.0f, w_exp);
-    p.w_unmul = ldexpf(1.0f, -w_exp);
     if (!AMV_GEMM_DIAG && (diag & 31u)) return AC_ERR_FEATURE_NOT_SUPPORTED;   // needs the diagnostic build
     p.diag = diag & 31u;   // bits 5 (single CTAs) and 6 (one tile per unit) are host-side choices
     p.status = a.status;
@@ -1148,9 +1139,10 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
 
 // ameva_mmtc_<q4_0|q8_0|q4_K>: bindings 0 Q, 1 S, 2 AH (fp16 activations [M][K], written by ameva_quant_a8_f16 /
 // ameva_quant_a8b_f16), 3 dst f32 [M][dst_stride], 4 AE f32 [M] (the per-row factors of the same quantize kernel);
-// push {M, N, K (% 256), dst_stride, diag, w_exp}: w_exp (a signed word, -14..15) scales the weights by 2^w_exp while
-// they are dequantized to fp16, chosen by the host so that the tensor's largest magnitude lands in [1, 2); the epilogue
-// multiplies both factors back, so dst is unaffected except that small and large magnitudes keep their precision.
+// push {M, N, K (% 256), dst_stride, diag}. The activation operand carries a power-of-two factor per token row (small
+// and large activations keep their precision in fp16) that the epilogue multiplies back out with AE. The weights are
+// dequantized to fp16 as they are: tensors whose magnitudes fp16 does not hold comfortably are kept off this kernel by
+// the host (ac_b200_weight_exponent + AC_B200_PLAN_WEIGHT_RANGE, which selects the exact integer path).
 // diag (0 in production; results are meaningless otherwise) switches one pipeline stage off for profiling:
 // 1 = no weight dequantization, 2 = no activation TMA, 4 = no MMA, 8 = no output stores; bits 8.. force the token tile.
 template <int TYPE, uint32_t QB, uint32_t SB, uint32_t BLK>
@@ -1160,11 +1152,11 @@ static AcResult launch_mmtc(const LaunchArgs& a) {
     const uint64_t nblk = (uint64_t)N * (K / BLK);
     if (a.range[0] < nblk * QB || a.range[1] < nblk * SB) return AC_ERR_INVALID_BUFFER_SIZE;
     return tc::launch<TYPE>(a, a.ptr[0], a.ptr[1], a.ptr[2], a.range[2], a.ptr[3], a.range[3], nullptr, M, N, K,
-                            dst_stride, 1.0f, a.push[4], a.ptr[4], a.range[4], (int32_t)a.push[5]);
+                            dst_stride, 1.0f, a.push[4], a.ptr[4], a.range[4]);
 }
 // ameva_mmtc_<type>_mp: the same with the output exchange of a row-sharded mul_mat fused into the epilogue: bindings
 // 0 Q, 1 S, 2 AH, 3 local dst, 4..10 the same range of up to seven peers' outputs (unused slots repeat binding 3), 11 AE;
-// push {M, N, K, dst_stride, diag, n_peers, w_exp}. Every tile is sent with one TMA store per destination.
+// push {M, N, K, dst_stride, diag, n_peers}. Every tile is sent with one TMA store per destination.
 template <int TYPE, uint32_t QB, uint32_t SB, uint32_t BLK>
 static AcResult launch_mmtc_mp(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3], n_peers = a.push[5];
@@ -1172,8 +1164,7 @@ static AcResult launch_mmtc_mp(const LaunchArgs& a) {
     const uint64_t nblk = (uint64_t)N * (K / BLK);
     if (a.range[0] < nblk * QB || a.range[1] < nblk * SB) return AC_ERR_INVALID_BUFFER_SIZE;
     return tc::launch<TYPE>(a, a.ptr[0], a.ptr[1], a.ptr[2], a.range[2], a.ptr[3], a.range[3], nullptr, M, N, K,
-                            dst_stride, 1.0f, a.push[4], a.ptr[11], a.range[11], (int32_t)a.push[6], n_peers, &a.ptr[4],
-                            &a.range[4]);
+                            dst_stride, 1.0f, a.push[4], a.ptr[11], a.range[11], n_peers, &a.ptr[4], &a.range[4]);
 }
 AcResult launch_mmtc_q4_0_mp(const LaunchArgs& a) { return launch_mmtc_mp<tc::T_Q4_0, 16, 2, 32>(a); }
 AcResult launch_mmtc_q8_0_mp(const LaunchArgs& a) { return launch_mmtc_mp<tc::T_Q8_0, 32, 2, 32>(a); }
@@ -1191,7 +1182,7 @@ AcResult launch_bitnet_gemm_i2_s(const LaunchArgs& a) {
     float w_scale;
     memcpy(&w_scale, &a.push[4], 4);
     return tc::launch<tc::T_I2_S>(a, a.ptr[0], nullptr, a.ptr[1], a.range[1], a.ptr[2], a.range[2], a.ptr[3], M, N, K,
-                                  dst_stride, w_scale, a.push[5], nullptr, 0, 0);
+                                  dst_stride, w_scale, a.push[5], nullptr, 0);
 }
 
 }  // namespace amv

@@ -10,12 +10,14 @@
 //   One persistent CTA of 16 warps per SM. The warps work on 16 / KS groups of 16 weight rows at a time ("a set"), KS
 //   warps splitting the K of a group between them (KS = 16 whenever a row has at least 16 blocks); their partial fp32
 //   sums are added through shared memory at the end of the set. Sets are dealt to the CTAs in equal contiguous shares.
-//   Weights: straight from global memory into the instruction's fragment layout, no shared-memory stage: lane (g, t)
-//   (g = lane / 4, t = lane % 4) loads the 8 bytes [8t, 8t + 8) of each 32-byte chunk qs[32k' ..] of rows g and g + 8. A
-//   chunk's low nibbles are sub-block 2k', its high nibbles sub-block 2k' + 1; the lane's first word fills the k slots
-//   4t..4t+3 of the A fragment, the second the slots 16+4t..: a permutation of k, applied to the activations as well
-//   (one 8-byte shared-memory load per sub-block), which an integer sum does not see. The next 256-block's bytes are
-//   requested before the current one is multiplied, the first one before the wait for the preceding kernel.
+//   Weights: every warp stages the 256-blocks of its 16 rows in a private shared-memory ring with cp.async (rows 160
+//   bytes apart, so the fragment loads below are free of bank conflicts), several blocks ahead of the one it multiplies
+//   and the first ones before the wait for the preceding kernel: with one block in flight per warp the kernel ran at
+//   the latency of a load per block (11008 x 4096, M = 8: 13 us), not at the bandwidth of the memory.
+//   Fragments: lane (g, t) (g = lane / 4, t = lane % 4) reads the 8 bytes [8t, 8t + 8) of each 32-byte chunk qs[32k' ..]
+//   of rows g and g + 8. A chunk's low nibbles are sub-block 2k', its high nibbles sub-block 2k' + 1; the lane's first
+//   word fills the k slots 4t..4t+3 of the A fragment, the second the slots 16+4t..: a permutation of k, applied to the
+//   activations as well (one 8-byte shared-memory load per sub-block), which an integer sum does not see.
 //   Activations (int8, written by ameva_quant_a8b) are staged once per CTA, rows K + 32 bytes apart (conflict-free
 //   8-byte loads across the 8 rows), followed by one row of zeros that stands for the tokens M..7 of the instruction. Per 256-block and token the 8 sub-block sums of q (for the
 //   mins) and the scale d are staged next to them.
@@ -33,7 +35,7 @@ namespace gm {
 constexpr int kThreads = 512;
 constexpr int kWarps = 16;
 constexpr uint32_t kActPad = 32;                 // bytes added to an activation row: rows land 32 bytes apart mod 128
-constexpr uint32_t kSmemLimit = 200u * 1024u;
+constexpr uint32_t kSmemLimit = 227u * 1024u;
 
 struct Params {
     const uint8_t* Q;     // 128 B per 256-block, [N][B]
@@ -69,22 +71,35 @@ __device__ __forceinline__ int dp2a_hi(uint32_t a16x2, uint32_t b8x4, int c) {
     return d;
 }
 
-struct BlockRegs {
-    uint2 w[2][4];    // [row g / g + 8][chunk k']: this lane's 8 bytes
-    uint4 s[2];       // the two rows' scale records
-};
+constexpr uint32_t kRowPitch = 160;                       // bytes between the staged rows of a 256-block (128 + 32)
+constexpr uint32_t kStageBytes = 16u * kRowPitch + 16u * 16u;   // 16 rows of payload + 16 scale records = 2816
+constexpr uint32_t kMaxDepth = 6;
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 // One CTA per SM, 16 warps. A "set" is RG = 16 / KS groups of 16 weight rows; the KS warps of a group split its K between
 // them. The sets are dealt to the CTAs in equal contiguous shares (every SM gets within one set of the same work: no
-// partial last wave), and a CTA walks its sets with the next 256-block of weights always in flight.
+// partial last wave). A warp's work is a flat sequence of items (set, 256-block of its K share); it keeps a private ring
+// of `depth` staged items in shared memory, filled by cp.async (16 bytes per lane and instruction, no registers held),
+// depth - 1 items ahead of the one being multiplied: the bytes in flight per SM are bounded by shared memory.
 template <int KS>
-__global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params p) {
+__global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params p, const uint32_t depth) {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t K = p.K, B = K >> 8, astride = K + kActPad, MR = p.M + 1u;   // staged rows: M tokens + one of zeros
     int8_t* s_act = reinterpret_cast<int8_t*>(smem);                         // [M + 1][K + 32]
     int16_t* s_sub = reinterpret_cast<int16_t*>(smem + MR * astride);         // [M + 1][B][8] sub-block sums of q
     float* s_da = reinterpret_cast<float*>(smem + MR * astride + MR * B * 16u);   // [M + 1][B]
     float* s_red = s_da + MR * B;                                            // [2][16 warps][16 rows][8 tokens]
+    uint8_t* s_ring = reinterpret_cast<uint8_t*>(s_red + 2u * kWarps * 128u);   // [16 warps][depth][kStageBytes]
+    s_ring += (16u - (smem_addr(s_ring) & 15u)) & 15u;
 
     constexpr uint32_t RG = kWarps / KS;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u, g = lane >> 2, t = lane & 3u;
@@ -94,34 +109,29 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
     const uint32_t set_end = (uint32_t)((uint64_t)n_sets * (blockIdx.x + 1u) / gridDim.x);
     const uint32_t nb = (B + KS - 1) / KS, b_begin = min(B, ks * nb), b_end = min(B, b_begin + nb);
     const uint32_t my_blocks = b_end - b_begin;
+    const uint32_t n_items = (set_end - set_begin) * my_blocks;
+    const uint32_t ring = smem_addr(s_ring) + warp * depth * kStageBytes;
 
-    // this lane's two weight rows of set `set` (clamped into the matrix; rows past N are computed and not stored)
-    auto row_ptrs = [&](uint32_t set, const uint8_t*& qa, const uint8_t*& qb, const uint4*& sa, const uint4*& sb) {
-        const uint32_t row0 = (set * RG + rg) * 16u;
-        const uint32_t ra = min(row0 + g, p.N - 1u), rb = min(row0 + g + 8u, p.N - 1u);
-        qa = p.Q + (size_t)ra * B * 128u + 8u * t;
-        qb = p.Q + (size_t)rb * B * 128u + 8u * t;
-        sa = p.S + (size_t)ra * B;
-        sb = p.S + (size_t)rb * B;
-    };
-    auto load_block = [&](const uint8_t* qa, const uint8_t* qb, const uint4* sa, const uint4* sb, uint32_t b, BlockRegs& r) {
+    // item -> (set, block); the lane's share of the copy: payload pieces lane, lane + 32, + 64, + 96 of the 16 x 8 pieces
+    // (row = piece / 8, 16-byte column = piece % 8), and the scale record of row `lane` for lanes 0..15
+    auto issue = [&](uint32_t item) {
+        if (item < n_items) {
+            const uint32_t set = set_begin + item / my_blocks, b = b_begin + item % my_blocks;
+            const uint32_t row0 = (set * RG + rg) * 16u;
+            const uint32_t st = ring + (item % depth) * kStageBytes;
+            const uint32_t col = lane & 7u;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            r.w[0][k] = ld_stream_u2(qa + (size_t)b * 128u + 32u * k);
-            r.w[1][k] = ld_stream_u2(qb + (size_t)b * 128u + 32u * k);
+            for (uint32_t i = 0; i < 4u; ++i) {
+                const uint32_t r = (lane >> 3) + 4u * i, row = min(row0 + r, p.N - 1u);
+                cp_async_16(st + r * kRowPitch + col * 16u, p.Q + ((size_t)row * B + b) * 128u + col * 16u);
+            }
+            if (lane < 16u) cp_async_16(st + 16u * kRowPitch + lane * 16u, p.S + (size_t)min(row0 + lane, p.N - 1u) * B + b);
         }
-        r.s[0] = ld_cached_u4(sa + b);
-        r.s[1] = ld_cached_u4(sb + b);
+        cp_async_commit();   // (an empty group when the sequence has ended keeps the group count in step)
     };
 
-    const uint8_t *qa, *qb;
-    const uint4 *sa, *sb;
-    BlockRegs cur, nxt;
-    const bool work = set_begin < set_end && my_blocks > 0u;
-    if (work) {   // the weights do not depend on the kernel before this one: requested before the wait for it
-        row_ptrs(set_begin, qa, qb, sa, sb);
-        load_block(qa, qb, sa, sb, b_begin, cur);
-    }
+    // the weights do not depend on the kernel before this one: the ring is filled before the wait for it
+    for (uint32_t i = 0; i + 1u < depth; ++i) issue(i);
     pdl_trigger();
     pdl_wait();
 
@@ -167,22 +177,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
     const float* da0p = s_da + tok0 * B;
     const float* da1p = s_da + tok1 * B;
 
-    uint32_t parity = 0;
+    uint32_t parity = 0, item = 0;
     for (uint32_t set = set_begin; set < set_end; ++set) {
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // (row g, token 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
-        for (uint32_t b = b_begin; b < b_end; ++b) {
-            if (b + 1u < b_end) {
-                load_block(qa, qb, sa, sb, b + 1u, nxt);
-            } else if (set + 1u < set_end) {   // the first block of the next set
-                row_ptrs(set + 1u, qa, qb, sa, sb);
-                load_block(qa, qb, sa, sb, b_begin, nxt);
+        for (uint32_t b = b_begin; b < b_end; ++b, ++item) {
+            // item's copies have landed when at most depth - 2 newer groups are pending
+            switch (depth) {
+                case 2: cp_async_wait<0>(); break;
+                case 3: cp_async_wait<1>(); break;
+                case 4: cp_async_wait<2>(); break;
+                case 5: cp_async_wait<3>(); break;
+                default: cp_async_wait<4>(); break;
             }
+            __syncwarp();
+            // (every lane is past the previous item, whose stage is the one item + depth - 1 goes to: refill it now)
+            issue(item + depth - 1u);
+            const uint8_t* st = s_ring + ((size_t)warp * depth + item % depth) * kStageBytes;
             // 6-bit scales and mins of the 8 sub-blocks, four to a word, per row
             uint32_t sc[2][2], mn[2][2];
             float dw[2], dmin[2];
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
-                const uint4 s = cur.s[r];
+                const uint4 s = *reinterpret_cast<const uint4*>(st + 16u * kRowPitch + (g + 8u * r) * 16u);
                 sc[r][0] = s.y & 0x3F3F3F3Fu;
                 mn[r][0] = s.z & 0x3F3F3F3Fu;
                 sc[r][1] = (s.w & 0x0F0F0F0Fu) | ((s.y >> 2) & 0x30303030u);
@@ -192,14 +208,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
             }
             int isum[4] = {0, 0, 0, 0};
             const int8_t* ab = a_lane + 256u * b;
+            const uint8_t* wa = st + g * kRowPitch + 8u * t;            // row g: this lane's 8 bytes of each 32-byte chunk
+            const uint8_t* wb = wa + 8u * kRowPitch;                    // row g + 8
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
+                const uint2 va = *reinterpret_cast<const uint2*>(wa + 32 * k), vb = *reinterpret_cast<const uint2*>(wb + 32 * k);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int j = 2 * k + h;   // sub-block
                     const uint2 bv = *reinterpret_cast<const uint2*>(ab + 32 * j);
-                    const uint32_t a0 = (cur.w[0][k].x >> (4 * h)) & 0x0F0F0F0Fu, a1 = (cur.w[1][k].x >> (4 * h)) & 0x0F0F0F0Fu;
-                    const uint32_t a2 = (cur.w[0][k].y >> (4 * h)) & 0x0F0F0F0Fu, a3 = (cur.w[1][k].y >> (4 * h)) & 0x0F0F0F0Fu;
+                    const uint32_t a0 = (va.x >> (4 * h)) & 0x0F0F0F0Fu, a1 = (vb.x >> (4 * h)) & 0x0F0F0F0Fu;
+                    const uint32_t a2 = (va.y >> (4 * h)) & 0x0F0F0F0Fu, a3 = (vb.y >> (4 * h)) & 0x0F0F0F0Fu;
                     int c[4];
                     mma_u8s8(c, a0, a1, a2, a3, bv.x, bv.y);
                     const int s0 = (int)((sc[0][j >> 2] >> (8 * (j & 3))) & 0xFFu), s1 = (int)((sc[1][j >> 2] >> (8 * (j & 3))) & 0xFFu);
@@ -230,7 +249,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
             acc[1] += (dw[0] * da1) * (float)isum[1] - (dmin[0] * da1) * (float)mp[1];
             acc[2] += (dw[1] * da0) * (float)isum[2] - (dmin[1] * da0) * (float)mp[2];
             acc[3] += (dw[1] * da1) * (float)isum[3] - (dmin[1] * da1) * (float)mp[3];
-            cur = nxt;
         }
         // ---- add the KS partial sums of every row group of the set and store; the two halves of s_red alternate, so
         //      one barrier per set is enough (a half is rewritten two sets later, after the barrier in between) ----
@@ -254,29 +272,37 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
         }
         parity ^= 1u;
     }
+    cp_async_wait<0>();   // (only empty groups can be pending here)
 }
 
 template <int KS>
-static AcResult launch_ks(const LaunchArgs& a, const Params& p, uint32_t smem_bytes) {
+static AcResult launch_ks(const LaunchArgs& a, const Params& p, uint32_t smem_bytes, uint32_t depth) {
     if (!ensure_dynamic_smem<gemv_mma_q4k_kernel<KS>>((int)kSmemLimit)) return AC_ERR_INVALID_WORK_GROUP_SIZE;
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
     const uint32_t groups = (p.N + 15u) / 16u, rg = kWarps / KS, n_sets = (groups + rg - 1u) / rg;
-    launch_pdl(gemv_mma_q4k_kernel<KS>, dim3(n_sets < sms ? n_sets : sms), dim3(kThreads), smem_bytes, a.stream, p);
+    launch_pdl(gemv_mma_q4k_kernel<KS>, dim3(n_sets < sms ? n_sets : sms), dim3(kThreads), smem_bytes, a.stream, p, depth);
     return check_launch();
 }
 
 }  // namespace gm
 
-// Shared-memory bytes of ameva_mmvm_q4_K: the activations of M token rows plus a row of zeros, their per-block records
-// and two sets of partial sums. The kernel serves the (M, K) for which this fits 200 KB.
-static uint32_t mmvm_smem_bytes(uint32_t M, uint32_t K) {
+// Shared-memory bytes of ameva_mmvm_q4_K before the weight rings: the activations of M token rows plus a row of zeros,
+// their per-block records and two sets of partial sums. What is left of 227 KB holds the 16 warps' rings: the kernel
+// serves the (M, K) for which at least two stages per warp fit (M = 8: K <= 12800; M = 1: K <= 65536).
+static uint32_t mmvm_fixed_bytes(uint32_t M, uint32_t K) {
     const uint32_t B = K >> 8, MR = M + 1u;
-    return MR * (K + gm::kActPad) + MR * B * 16u + MR * B * 4u + 2u * gm::kWarps * 128u * 4u;
+    return MR * (K + gm::kActPad) + MR * B * 16u + MR * B * 4u + 2u * gm::kWarps * 128u * 4u + 16u;
+}
+static uint32_t mmvm_depth(uint32_t M, uint32_t K) {
+    const uint32_t fixed = mmvm_fixed_bytes(M, K);
+    if (fixed >= gm::kSmemLimit) return 0;
+    const uint32_t d = (gm::kSmemLimit - fixed) / (gm::kWarps * gm::kStageBytes);
+    return d > gm::kMaxDepth ? gm::kMaxDepth : d;
 }
 
 // ameva_mmvm_q4_K: bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 dst f32 [M][dst_stride];  push {M (1..8), N, K (% 256), dst_stride}
-// (M + 1) (K + 32) bytes of activations must fit shared memory (M = 8: K <= 20480; M = 1: any K of the configurations);
-// beyond that AC_ERR_INVALID_SHAPE (callers keep the dp4a kernels there).
+// (M + 1) (K + 32) bytes of activations and two ring stages per warp must fit shared memory (M = 8: K <= 12800; M = 1:
+// K <= 65536); beyond that AC_ERR_INVALID_SHAPE (callers keep the dp4a kernels there).
 AcResult launch_mmvm_q4_K(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
     if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
@@ -290,8 +316,9 @@ AcResult launch_mmvm_q4_K(const LaunchArgs& a) {
         ((uintptr_t)a.ptr[3] & 15u))
         return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     if ((uint64_t)(M + 1u) * (K + gm::kActPad) > gm::kSmemLimit) return AC_ERR_INVALID_SHAPE;
-    const uint32_t smem = mmvm_smem_bytes(M, K);
-    if (smem > gm::kSmemLimit) return AC_ERR_INVALID_SHAPE;
+    const uint32_t depth = mmvm_depth(M, K);
+    if (depth < 2u) return AC_ERR_INVALID_SHAPE;
+    const uint32_t smem = mmvm_fixed_bytes(M, K) + depth * gm::kWarps * gm::kStageBytes;
     gm::Params p;
     p.Q = (const uint8_t*)a.ptr[0];
     p.S = (const uint4*)a.ptr[1];
@@ -307,11 +334,11 @@ AcResult launch_mmvm_q4_K(const LaunchArgs& a) {
     uint32_t ks = 16;
     while (ks > 1u && ks > B) ks >>= 1;
     switch (ks) {
-        case 1: return gm::launch_ks<1>(a, p, smem);
-        case 2: return gm::launch_ks<2>(a, p, smem);
-        case 4: return gm::launch_ks<4>(a, p, smem);
-        case 8: return gm::launch_ks<8>(a, p, smem);
-        default: return gm::launch_ks<16>(a, p, smem);
+        case 1: return gm::launch_ks<1>(a, p, smem, depth);
+        case 2: return gm::launch_ks<2>(a, p, smem, depth);
+        case 4: return gm::launch_ks<4>(a, p, smem, depth);
+        case 8: return gm::launch_ks<8>(a, p, smem, depth);
+        default: return gm::launch_ks<16>(a, p, smem, depth);
     }
 }
 

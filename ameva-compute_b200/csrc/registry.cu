@@ -7,6 +7,7 @@
 // (adapters/bitnet/src/core/ac_bitnet_engine.cpp:253-288) can dispatch them unchanged; the ameva_* names follow the
 // reference's families (quant_a8, quant_a8b, mmvq, mmvqb, mmq) with this library's own binding / push contracts,
 // documented at each launcher.
+#include <cmath>
 #include <cstring>
 
 #include "common.cuh"
@@ -27,6 +28,10 @@ AcResult launch_mmtc_q8_0_mp(const LaunchArgs&);
 AcResult launch_mmtc_q4_K_mp(const LaunchArgs&);
 AcResult launch_mmvqb_q4_K_mp(const LaunchArgs&);
 AcResult launch_mmvm_q4_K(const LaunchArgs&);
+AcResult launch_add_f32(const LaunchArgs&);
+AcResult launch_mul_f32(const LaunchArgs&);
+AcResult launch_swiglu_f32(const LaunchArgs&);
+AcResult launch_rms_norm_f32(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
@@ -59,15 +64,19 @@ static const KernelEntry kTable[] = {
     {"ameva_quant_a8_f16", 5, 16, {256, 1, 1}, launch_quant_a8_f16},
     {"ameva_quant_a8b_f16", 5, 16, {256, 1, 1}, launch_quant_a8b_f16},
     {"bitnet_norm_q8", 7, 16, {256, 1, 1}, launch_bitnet_norm_q8},
-    {"ameva_mmtc_q4_0", 5, 24, {320, 1, 1}, launch_mmtc_q4_0},
-    {"ameva_mmtc_q8_0", 5, 24, {320, 1, 1}, launch_mmtc_q8_0},
-    {"ameva_mmtc_q4_K", 5, 24, {320, 1, 1}, launch_mmtc_q4_K},
+    {"ameva_mmtc_q4_0", 5, 20, {320, 1, 1}, launch_mmtc_q4_0},
+    {"ameva_mmtc_q8_0", 5, 20, {320, 1, 1}, launch_mmtc_q8_0},
+    {"ameva_mmtc_q4_K", 5, 20, {320, 1, 1}, launch_mmtc_q4_K},
     {"bitnet_gemm_i2_s", 4, 24, {320, 1, 1}, launch_bitnet_gemm_i2_s},
-    {"ameva_mmtc_q4_0_mp", 12, 28, {608, 1, 1}, launch_mmtc_q4_0_mp},
-    {"ameva_mmtc_q8_0_mp", 12, 28, {608, 1, 1}, launch_mmtc_q8_0_mp},
-    {"ameva_mmtc_q4_K_mp", 12, 28, {608, 1, 1}, launch_mmtc_q4_K_mp},
+    {"ameva_mmtc_q4_0_mp", 12, 24, {608, 1, 1}, launch_mmtc_q4_0_mp},
+    {"ameva_mmtc_q8_0_mp", 12, 24, {608, 1, 1}, launch_mmtc_q8_0_mp},
+    {"ameva_mmtc_q4_K_mp", 12, 24, {608, 1, 1}, launch_mmtc_q4_K_mp},
     {"ameva_mmvqb_q4_K_mp", 12, 20, {256, 1, 1}, launch_mmvqb_q4_K_mp},
-    {"ameva_mmvm_q4_K", 5, 16, {256, 1, 1}, launch_mmvm_q4_K},
+    {"ameva_mmvm_q4_K", 5, 16, {512, 1, 1}, launch_mmvm_q4_K},
+    {"ameva_add_f32", 3, 12, {256, 1, 1}, launch_add_f32},
+    {"ameva_mul_f32", 3, 12, {256, 1, 1}, launch_mul_f32},
+    {"ameva_swiglu_f32", 3, 4, {256, 1, 1}, launch_swiglu_f32},
+    {"ameva_rms_norm_f32", 3, 16, {256, 1, 1}, launch_rms_norm_f32},
     {"ameva_mmvs_q4_0", 12, 24, {288, 1, 1}, launch_mmvs_q4_0},
     {"ameva_mmvs_q8_0", 12, 24, {288, 1, 1}, launch_mmvs_q8_0},
     {"ameva_mmvs_q4_K", 12, 24, {288, 1, 1}, launch_mmvs_q4_K},
@@ -129,6 +138,141 @@ bool codec_for(uint32_t type, Codec* c) {
 }  // namespace
 
 static uint64_t align64(uint64_t v) { return (v + 63u) & ~(uint64_t)63u; }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// The kernel choice, in one place for every host of the library (the Python mirror, the ggml plugin): what the reference
+// decides in mul_mat_qmm_reason / ameva_mmq_plan / ameva_qmv_choice (adapters/llama/ggml-ameva/ggml-ameva.cpp:1326-1377,
+// 2486-2503, 2986) from the shape alone. The thresholds are measurements on a B200 (noted at each line).
+// ---------------------------------------------------------------------------------------------------------------------
+static bool mmvm_fits(uint64_t M, uint64_t K) {   // shared memory of ameva_mmvm_q4_K (gemv_mma.cu): two ring stages per warp
+    const uint64_t rows = M + 1;
+    return (K % 256) == 0 && rows * (K + 32) + rows * (K / 256) * 20 + 16384 + 16 + 2u * 16u * 2816u <= 227u * 1024u;
+}
+
+extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, uint64_t K, uint32_t flags,
+                                         uint32_t* out_path) {
+    if (!out_path) return AC_ERR_NULL_POINTER;
+    *out_path = AC_B200_PATH_NONE;
+    if (flags & ~(AC_B200_PLAN_EXACT | AC_B200_PLAN_HOST_LAUNCH | AC_B200_PLAN_PEERS | AC_B200_PLAN_WEIGHT_RANGE))
+        return AC_ERR_INVALID_ARGUMENT;
+    const uint64_t blk = type == 2 || type == 8 ? 32 : type == 12 ? 256 : type == 36 ? 128 : 0;
+    if (!blk) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    if (M == 0 || N == 0 || K == 0 || (K % blk) || N * K >= (1ull << 32) || M * (N > K ? N : K) >= (1ull << 32))
+        return AC_ERR_INVALID_SHAPE;
+    // (a weight tensor whose magnitudes fp16 does not hold comfortably stays on the integer kernels at every M)
+    const bool exact = (flags & (AC_B200_PLAN_EXACT | AC_B200_PLAN_WEIGHT_RANGE)) != 0, peers = (flags & AC_B200_PLAN_PEERS) != 0;
+    // more than 8 activation rows: the tensor-core GEMM (whole 128-byte operand rows: K % 256, I2_S K % 128); callers
+    // that need the exact per-block integer sums, or a K it cannot take, walk the rows in chunks of 8 through the GEMV
+    if (M > 8) {
+        const bool tc_ok = type == 36 ? (K % 128) == 0 : (K % 256) == 0;
+        if (tc_ok && !exact) {
+            if (peers && type == 36) return AC_ERR_FEATURE_NOT_SUPPORTED;
+            *out_path = AC_B200_PATH_GEMM_TC;
+            return AC_SUCCESS;
+        }
+        if (peers) return AC_ERR_FEATURE_NOT_SUPPORTED;
+        *out_path = AC_B200_PATH_GEMV;
+        return AC_SUCCESS;
+    }
+    if (type == 36) {
+        if (peers) return AC_ERR_FEATURE_NOT_SUPPORTED;
+        *out_path = AC_B200_PATH_GEMV;
+        return AC_SUCCESS;
+    }
+    const uint64_t row_bytes = (K / 256) * ((type == 8 ? 256u : 128u) + 16u);
+    const bool streamed_ok = (K % 256) == 0;
+    if (peers) {   // the streamed kernel carries the fused peer stores of every scaled type
+        if (!streamed_ok) return AC_ERR_FEATURE_NOT_SUPPORTED;
+        *out_path = AC_B200_PATH_GEMV_STREAMED;
+        return AC_SUCCESS;
+    }
+    // Q4_K with several activation rows: the integer tensor instruction (11008 x 4096, M = 8: 13.6 us against 30.4 us
+    // of the streamed dp4a kernel and 40 us of the register-staged one)
+    if (type == 12 && M >= 2 && mmvm_fits(M, K)) {
+        *out_path = AC_B200_PATH_GEMV_MMA;
+        return AC_SUCCESS;
+    }
+    // rows short enough for a ring of whole-row stages, and either several activation rows or a matrix large enough to
+    // be bandwidth-bound (28672 x 8192 Q4_K, M = 1: 26-28 us against 32-34 us register-staged)
+    if (streamed_ok && row_bytes <= 6400u && (M >= 4 || N * row_bytes >= (64ull << 20))) {
+        *out_path = AC_B200_PATH_GEMV_STREAMED;
+        return AC_SUCCESS;
+    }
+    // one activation row of a projection small enough to be launch-bound, launched from the host one kernel at a time:
+    // quantize inside the GEMV launch (in replayed batches the two kernels overlap and measure as fast)
+    if ((flags & AC_B200_PLAN_HOST_LAUNCH) && M == 1 && K <= 16384u && N * K <= (64ull << 20)) {
+        *out_path = AC_B200_PATH_GEMV_FQ;
+        return AC_SUCCESS;
+    }
+    *out_path = AC_B200_PATH_GEMV;
+    return AC_SUCCESS;
+}
+
+// The magnitude of a weight tensor as a power of two: w_exp brings an upper bound of the tensor's largest |w| (from the
+// block scale fields alone: Q4_0 8 |d|, Q8_0 127 |d|, Q4_K 945 |d| + 63 |dmin|) into [1, 2), limited to -30..30. The
+// tensor-core GEMM dequantizes weights to fp16, whose normal range is 2^-14 .. 2^15: hosts compute this once per tensor
+// at upload and keep tensors with AC_B200_WEIGHT_RANGE_EXTREME(w_exp) on the integer kernels. Other types: 0.
+static float half_to_float(uint16_t h) {
+    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {
+            int e = -1;
+            uint32_t m = man;
+            do {
+                m <<= 1;
+                ++e;
+            } while (!(m & 0x400u));
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3FFu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7F800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112u) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+extern "C" AcResult ac_b200_weight_exponent(uint32_t type, const void* ggml_blocks, uint64_t rows, uint64_t k,
+                                            int32_t* out_w_exp) {
+    if (!out_w_exp) return AC_ERR_NULL_POINTER;
+    *out_w_exp = 0;
+    if (type == 36) return AC_SUCCESS;
+    Codec c;
+    if (!codec_for(type, &c)) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    if (!ggml_blocks) return AC_ERR_NULL_POINTER;
+    if (k % c.blk) return AC_ERR_INVALID_SHAPE;
+    const uint8_t* b = (const uint8_t*)ggml_blocks;
+    const uint64_t nblk = rows * (k / c.blk);
+    float top = 0.0f;
+    for (uint64_t i = 0; i < nblk; ++i, b += c.blk_bytes) {
+        uint16_t h0, h1;
+        memcpy(&h0, b, 2);
+        memcpy(&h1, b + 2, 2);
+        float d = half_to_float(h0);
+        d = d < 0 ? -d : d;
+        float bound;
+        if (type == 2) {
+            bound = 8.0f * d;
+        } else if (type == 8) {
+            bound = 127.0f * d;
+        } else {
+            float m = half_to_float(h1);
+            bound = 945.0f * d + 63.0f * (m < 0 ? -m : m);
+        }
+        if (bound > top && bound <= 3.0e38f) top = bound;
+    }
+    if (!(top > 0.0f)) return AC_SUCCESS;
+    int e = 0;
+    (void)frexpf(top, &e);   // top = m 2^e with m in [0.5, 1): floor(log2(top)) = e - 1
+    const int w = -(e - 1);
+    *out_w_exp = w < -30 ? -30 : (w > 30 ? 30 : w);
+    return AC_SUCCESS;
+}
 
 extern "C" AcResult ac_b200_device_layout(uint32_t type, uint64_t rows, uint64_t k, uint64_t* out_total_bytes,
                                           uint64_t* out_scale_offset) {

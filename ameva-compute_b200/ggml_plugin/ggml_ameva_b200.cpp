@@ -1,25 +1,35 @@
-// ggml backend plugin over libac_runtime_b200.so: the quantized MUL_MAT of a ggml graph on B200.
+// ggml backend plugin over libac_runtime_b200.so: the quantized MUL_MAT of a ggml graph, and the f32 row ops between two
+// of them, on B200.
 //
 // Exports ggml_backend_init() / ggml_backend_score() with C linkage, as the reference's plugin does
-// (adapters/llama/ggml-ameva/ggml-ameva.cpp:5693-5707), and fills the registry / device / buffer-type / buffer / backend
-// tables of ggml's backend interface (ggml-backend-impl.h, API version 2). It is compiled against the ggml headers of the
-// host application (llama.cpp b8471 / ggml 0.9.8 is what the reference builds with); none of ggml is part of this
-// repository. Behaviour kept from the reference plugin:
+// (adapters/llama/ggml-ameva/ggml-ameva.cpp:5693-5707), the ggml_backend_ameva_* helper surface of its public header
+// (ggml-ameva.h:19-98: lifecycle, counters, host-side failure injection) and fills the registry / device / buffer-type /
+// buffer / backend tables of ggml's backend interface (ggml-backend-impl.h, API version 2). It is compiled against the
+// ggml headers of the host application (llama.cpp b8471 / ggml 0.9.8 is what the reference builds with); none of ggml is
+// part of this repository. Behaviour kept from the reference plugin:
 //   - buffer type: alignment 64, not host memory (weights live in a device layout), alloc size = the device layout's
 //     size for repacked weights, ggml_nbytes otherwise (ggml-ameva-buffer.cpp:662-696);
 //   - set_tensor repacks Q4_0 / Q8_0 / Q4_K matrices into the device regions, get_tensor returns the uploaded ggml
-//     bytes, partial ranges included (tests/ameva_qmm_check.cpp:184-196); ggml has no error return there, so a failed
-//     transfer aborts (ggml-ameva-buffer.cpp:196-219);
+//     bytes, partial ranges and row-range views included (tests/ameva_qmm_check.cpp:103-127, 184-196); ggml has no error
+//     return there, so a failed transfer aborts (ggml-ameva-buffer.cpp:196-219);
+//   - a MUL_MAT whose src0 is a range of rows of a repacked weight runs on that range (ggml-ameva.cpp:1332-1338);
 //   - supports_buft = the own buffer type only, so the scheduler copies foreign inputs in (ggml-ameva-device.cpp:314-317);
 //   - graph_compute checks every node first and returns GGML_STATUS_FAILED without recording anything when one cannot
-//     run (ggml-ameva.cpp:5330-5341); it returns after completion (synchronize = NULL); calls are serialised by a mutex;
+//     run (ggml-ameva.cpp:5330-5341); the scratch for quantized activations is reserved as the largest need over all
+//     nodes before anything is recorded (:5382-5422); consecutive MUL_MATs that share src1 quantize it once
+//     (:2154-2158, 2738-2749), and for one activation row they become one launch; a one-row MUL_MAT followed by its ADD or
+//     SWIGLU consumer, and RMS_NORM followed by its MUL, run as one kernel (ameva_find_fusion, :4345-4378); the whole
+//     graph is one batch, and the call returns after completion (synchronize = NULL); calls are serialised by a mutex;
 //   - props: async = false, host_buffer = false, events = false (ggml-ameva-device.cpp:271-281).
-// Scope: MUL_MAT with a Q4_0 / Q8_0 / Q4_K src0 (2-D, contiguous) and f32 src1 / dst, plus the no-op view nodes. Other
-// ops are reported unsupported, which is how the scheduler keeps them on another backend.
+// The kernel choice per MUL_MAT is the library's (ac_b200_mul_mat_plan), not a second copy of it.
+// Scope: MUL_MAT with a Q4_0 / Q8_0 / Q4_K src0 (2-D, contiguous, or a row range of one) and f32 src1 / dst; ADD and MUL
+// of f32 rows (same shape, or src1 one row); GLU in its split SWIGLU form; RMS_NORM over f32 rows; the no-op view nodes.
+// Other ops are reported unsupported, which is how the scheduler keeps them on another backend.
+#include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
-#include <algorithm>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -32,6 +42,7 @@
 
 // The C ABI of libac_runtime_b200.so. (Its header shares no names with ggml's.)
 #include "../../include/ac_runtime_b200.h"
+#include "../../include/ggml_ameva_b200.h"
 
 namespace {
 
@@ -43,6 +54,14 @@ char* const kBase = reinterpret_cast<char*>(0x1000);   // tensor->data = kBase +
     abort();
 }
 
+struct Counters {
+    std::atomic<int64_t> supports_query{0}, supported_op{0}, gpu_op{0}, mul_mat{0}, ctx_create{0}, ctx_destroy{0},
+        kernel_create{0}, kernel_destroy{0}, buffer_create{0}, buffer_destroy{0}, event_create{0}, event_destroy{0},
+        repacked_tensors{0}, repacked_bytes{0}, qmv{0}, mmq{0}, mmqb{0}, fused_pairs{0};
+};
+Counters g_count;
+std::atomic<int> g_fail{AMEVA_FAIL_NONE};
+
 struct Plugin {                 // one per process
     std::mutex mutex;
     AcContext* ctx = nullptr;
@@ -50,6 +69,7 @@ struct Plugin {                 // one per process
     ggml_backend_reg reg{};
     ggml_backend_device dev{};
     ggml_backend_buffer_type buft{};
+    int live_backends = 0, live_buffers = 0;
 };
 Plugin& plugin() {
     static Plugin p;
@@ -62,6 +82,7 @@ AcContext* context() {          // created on first use (the loader probes the r
         AcContextDesc d = {AC_ABI_VERSION, (uint32_t)sizeof(AcContextDesc), AC_BACKEND_CUDA, 0};
         const AcResult rc = ac_runtime_context_create(&d, &p.ctx);
         if (rc != AC_SUCCESS) return nullptr;
+        g_count.ctx_create++;
         char nm[128] = {0};
         ac_runtime_context_get_device_name(p.ctx, nm, sizeof(nm));
         p.name = nm;
@@ -70,11 +91,14 @@ AcContext* context() {          // created on first use (the loader probes the r
 }
 
 bool repacked_type(enum ggml_type t) { return t == GGML_TYPE_Q4_0 || t == GGML_TYPE_Q8_0 || t == GGML_TYPE_Q4_K; }
+uint32_t block_elems(enum ggml_type t) { return t == GGML_TYPE_Q4_K ? 256u : 32u; }
+uint32_t payload_bytes(enum ggml_type t) { return t == GGML_TYPE_Q4_0 ? 16u : (t == GGML_TYPE_Q8_0 ? 32u : 128u); }
+uint32_t scale_bytes(enum ggml_type t) { return t == GGML_TYPE_Q4_K ? 16u : 2u; }
 
-// A weight this backend keeps in its device layout: a supported quantized type, plain 2-D, contiguous, whole 256-blocks
-// for Q4_K / whole 32-blocks otherwise (ggml guarantees the latter by construction).
+// A weight this backend keeps in its device layout: a supported quantized type, plain 2-D, contiguous, not a view.
 bool is_repacked_weight(const ggml_tensor* t) {
-    return t && repacked_type(t->type) && t->ne[2] == 1 && t->ne[3] == 1 && ggml_is_contiguous(t) && t->view_src == nullptr;
+    return t && repacked_type(t->type) && t->ne[2] == 1 && t->ne[3] == 1 && ggml_is_contiguous(t) && t->view_src == nullptr &&
+           t->ne[0] % block_elems(t->type) == 0;
 }
 
 uint64_t device_bytes(const ggml_tensor* t, uint64_t* s_off) {
@@ -89,63 +113,33 @@ uint64_t device_bytes(const ggml_tensor* t, uint64_t* s_off) {
 struct BufferCtx {
     AcBuffer* buf = nullptr;
     size_t size = 0;
-    // per repacked weight (by its offset in the buffer): the power of two the tensor-core GEMM scales the weights by
-    // while dequantizing them to fp16 (ameva_mmtc_* push word w_exp), computed from the block scales at upload
+    // per repacked weight (by its offset in the buffer): the tensor's magnitude as a power of two, from its block scales
+    // at upload (ac_b200_weight_exponent); tensors fp16 does not hold comfortably stay off the tensor-core kernel
     std::map<size_t, int> w_exp;
 };
 
-float half_bits_to_float(uint16_t h) {
-    const uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1Fu, man = h & 0x3FFu;
-    uint32_t bits;
-    if (exp == 0) {
-        if (man == 0) {
-            bits = sign;
-        } else {   // subnormal: normalise
-            int e = -1;
-            uint32_t m = man;
-            do {
-                m <<= 1;
-                ++e;
-            } while (!(m & 0x400u));
-            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | ((m & 0x3FFu) << 13);
-        }
-    } else if (exp == 31) {
-        bits = sign | 0x7F800000u | (man << 13);
-    } else {
-        bits = sign | ((exp + 112u) << 23) | (man << 13);
-    }
-    float f;
-    memcpy(&f, &bits, 4);
-    return f;
-}
-
-// w_exp of a weight tensor from its ggml blocks: an upper bound of |w| per block from the scale fields alone (Q4_0
-// 8 |d|, Q8_0 127 |d|, Q4_K 945 |d| + 63 |dmin|), the largest over the tensor brought into [1, 2); limited to -14..15.
-int weight_exponent(enum ggml_type type, const uint8_t* blocks, size_t nbytes) {
-    const size_t bb = type == GGML_TYPE_Q4_0 ? 18 : (type == GGML_TYPE_Q8_0 ? 34 : 144);
-    float top = 0.0f;
-    for (size_t o = 0; o + bb <= nbytes; o += bb) {
-        uint16_t h0, h1;
-        memcpy(&h0, blocks + o, 2);
-        memcpy(&h1, blocks + o + 2, 2);
-        const float d = fabsf(half_bits_to_float(h0));
-        float bound = type == GGML_TYPE_Q4_0 ? 8.0f * d : (type == GGML_TYPE_Q8_0 ? 127.0f * d
-                                                          : 945.0f * d + 63.0f * fabsf(half_bits_to_float(h1)));
-        if (bound > top && bound <= 3.0e38f) top = bound;
-    }
-    if (!(top > 0.0f)) return 0;
-    int e = 0;
-    frexpf(top, &e);          // top = m * 2^e, m in [0.5, 1)  ->  floor(log2(top)) = e - 1
-    const int w = -(e - 1);
-    return w < -14 ? -14 : (w > 15 ? 15 : w);
-}
-
 size_t tensor_offset(const ggml_tensor* t) { return (size_t)((const char*)t->data - kBase); }
+
+// The repacked weight a tensor is, or is a byte range of: the tensor itself, or its view_src when that is a repacked
+// weight (ggml sets a view's data to the base's data + view_offs). extra = where the tensor starts inside the base, in
+// bytes of the ggml layout.
+const ggml_tensor* repacked_base(const ggml_tensor* t, size_t* extra) {
+    if (is_repacked_weight(t)) {
+        *extra = 0;
+        return t;
+    }
+    if (t && t->view_src && is_repacked_weight(t->view_src)) {
+        *extra = t->view_offs;
+        return t->view_src;
+    }
+    return nullptr;
+}
 
 void buffer_free(ggml_backend_buffer_t buffer) {
     BufferCtx* b = (BufferCtx*)buffer->context;
     std::lock_guard<std::mutex> lock(plugin().mutex);
-    if (b->buf) ac_runtime_buffer_destroy(b->buf);
+    if (b->buf && ac_runtime_buffer_destroy(b->buf) == AC_SUCCESS) g_count.buffer_destroy++;
+    plugin().live_buffers--;
     delete b;
 }
 
@@ -164,43 +158,59 @@ void buffer_memset_tensor(ggml_backend_buffer_t buffer, ggml_tensor* tensor, uin
 void buffer_set_tensor(ggml_backend_buffer_t buffer, ggml_tensor* tensor, const void* data, size_t offset, size_t size) {
     BufferCtx* b = (BufferCtx*)buffer->context;
     std::lock_guard<std::mutex> lock(plugin().mutex);
-    if (!is_repacked_weight(tensor)) {
+    size_t extra = 0;
+    const ggml_tensor* base = repacked_base(tensor, &extra);
+    if (!base) {
         const AcResult rc = ac_runtime_buffer_write(b->buf, tensor_offset(tensor) + offset, data, size);
         if (rc != AC_SUCCESS) die("buffer_write", rc);
         return;
     }
-    const size_t nbytes = ggml_nbytes(tensor);
-    const uint64_t rows = (uint64_t)tensor->ne[1], k = (uint64_t)tensor->ne[0];
-    const uint64_t total = device_bytes(tensor, nullptr);
+    offset += extra;   // a view of a repacked weight: a byte range of the base's ggml image
+    const size_t nbytes = ggml_nbytes(base);
+    if (offset > nbytes || size > nbytes - offset) die("set_tensor range", AC_ERR_INVALID_BUFFER_SIZE);
+    const uint64_t rows = (uint64_t)base->ne[1], k = (uint64_t)base->ne[0];
+    const uint64_t total = device_bytes(base, nullptr);
     std::vector<uint8_t> dev(total), blocks;
     const void* src = data;
+    const bool first_upload = b->w_exp.find(tensor_offset(base)) == b->w_exp.end();
     if (offset != 0 || size != nbytes) {   // a partial range: patch the ggml image of what is on the device
         blocks.resize(nbytes);
-        AcResult rc = ac_runtime_buffer_read(b->buf, tensor_offset(tensor), dev.data(), total);
-        if (rc == AC_SUCCESS) rc = ac_b200_repack_from_device((uint32_t)tensor->type, dev.data(), rows, k, blocks.data());
+        AcResult rc = ac_runtime_buffer_read(b->buf, tensor_offset(base), dev.data(), total);
+        if (rc == AC_SUCCESS) rc = ac_b200_repack_from_device((uint32_t)base->type, dev.data(), rows, k, blocks.data());
         if (rc != AC_SUCCESS) die("partial set_tensor read-back", rc);
         memcpy(blocks.data() + offset, data, size);
         src = blocks.data();
     }
-    AcResult rc = ac_b200_repack_to_device((uint32_t)tensor->type, src, rows, k, dev.data());
-    if (rc == AC_SUCCESS) rc = ac_runtime_buffer_write(b->buf, tensor_offset(tensor), dev.data(), total);
+    AcResult rc = ac_b200_repack_to_device((uint32_t)base->type, src, rows, k, dev.data());
+    if (rc == AC_SUCCESS) rc = ac_runtime_buffer_write(b->buf, tensor_offset(base), dev.data(), total);
+    int32_t w_exp = 0;
+    if (rc == AC_SUCCESS) rc = ac_b200_weight_exponent((uint32_t)base->type, src, rows, k, &w_exp);
     if (rc != AC_SUCCESS) die("set_tensor", rc);
-    b->w_exp[tensor_offset(tensor)] = weight_exponent(tensor->type, (const uint8_t*)src, nbytes);
+    b->w_exp[tensor_offset(base)] = w_exp;
+    if (first_upload) {
+        g_count.repacked_tensors++;
+        g_count.repacked_bytes += (int64_t)total;
+    }
 }
 
 void buffer_get_tensor(ggml_backend_buffer_t buffer, const ggml_tensor* tensor, void* data, size_t offset, size_t size) {
     BufferCtx* b = (BufferCtx*)buffer->context;
     std::lock_guard<std::mutex> lock(plugin().mutex);
-    if (!is_repacked_weight(tensor)) {
+    size_t extra = 0;
+    const ggml_tensor* base = repacked_base(tensor, &extra);
+    if (!base) {
         const AcResult rc = ac_runtime_buffer_read(b->buf, tensor_offset(tensor) + offset, data, size);
         if (rc != AC_SUCCESS) die("buffer_read", rc);
         return;
     }
-    const uint64_t rows = (uint64_t)tensor->ne[1], k = (uint64_t)tensor->ne[0];
-    const uint64_t total = device_bytes(tensor, nullptr);
-    std::vector<uint8_t> dev(total), blocks(ggml_nbytes(tensor));
-    AcResult rc = ac_runtime_buffer_read(b->buf, tensor_offset(tensor), dev.data(), total);
-    if (rc == AC_SUCCESS) rc = ac_b200_repack_from_device((uint32_t)tensor->type, dev.data(), rows, k, blocks.data());
+    offset += extra;
+    const size_t nbytes = ggml_nbytes(base);
+    if (offset > nbytes || size > nbytes - offset) die("get_tensor range", AC_ERR_INVALID_BUFFER_SIZE);
+    const uint64_t rows = (uint64_t)base->ne[1], k = (uint64_t)base->ne[0];
+    const uint64_t total = device_bytes(base, nullptr);
+    std::vector<uint8_t> dev(total), blocks(nbytes);
+    AcResult rc = ac_runtime_buffer_read(b->buf, tensor_offset(base), dev.data(), total);
+    if (rc == AC_SUCCESS) rc = ac_b200_repack_from_device((uint32_t)base->type, dev.data(), rows, k, blocks.data());
     if (rc != AC_SUCCESS) die("get_tensor", rc);
     memcpy(data, blocks.data() + offset, size);
 }
@@ -227,7 +237,7 @@ ggml_backend_buffer_i buffer_iface() {
 }
 
 // ---- buffer type ------------------------------------------------------------------------------------------------------
-const char* buft_get_name(ggml_backend_buffer_type_t) { return "AMEVA_B200"; }
+const char* buft_get_name(ggml_backend_buffer_type_t) { return GGML_AMEVA_B200_NAME; }
 
 ggml_backend_buffer_t buft_alloc_buffer(ggml_backend_buffer_type_t buft, size_t size) {
     std::lock_guard<std::mutex> lock(plugin().mutex);
@@ -241,12 +251,15 @@ ggml_backend_buffer_t buft_alloc_buffer(ggml_backend_buffer_type_t buft, size_t 
         delete b;
         return nullptr;   // ggml reports the allocation failure
     }
+    g_count.buffer_create++;
+    plugin().live_buffers++;
     return ggml_backend_buffer_init(buft, buffer_iface(), b, size);
 }
 
 size_t buft_get_alignment(ggml_backend_buffer_type_t) { return kAlign; }
 
 size_t buft_get_max_size(ggml_backend_buffer_type_t) {
+    std::lock_guard<std::mutex> lock(plugin().mutex);
     AcContext* ctx = context();
     AcDeviceLimits lim;
     memset(&lim, 0, sizeof(lim));
@@ -281,12 +294,12 @@ AcKernel* kernel(Backend* be, const char* name) {
     if (it != be->kernels.end()) return it->second;
     AcKernel* k = nullptr;
     if (ac_runtime_kernel_create_builtin(context(), name, &k) != AC_SUCCESS) return nullptr;
+    g_count.kernel_create++;
     be->kernels[name] = k;
     return k;
 }
 
-// Called before a batch is begun (nothing retains the old buffer then), with the largest need over the graph's nodes, as
-// the reference sizes its scratch before recording (ggml-ameva.cpp:5382-5422).
+// Called before a batch is begun (nothing retains the old buffer then), with the largest need over the graph's nodes.
 bool grow(AcBuffer** buf, size_t* have, size_t need) {
     if (*have >= need) return true;
     if (*buf) {
@@ -295,11 +308,13 @@ bool grow(AcBuffer** buf, size_t* have, size_t need) {
             fprintf(stderr, "ggml-ameva-b200: scratch buffer still in use (AcResult %d)\n", (int)rc);
             return false;
         }
+        g_count.buffer_destroy++;
     }
     *buf = nullptr;
     *have = 0;
     AcBufferDesc d = {AC_ABI_VERSION, (uint32_t)sizeof(AcBufferDesc), need, AC_BUFFER_USAGE_STORAGE, 0};
     if (ac_runtime_buffer_create(context(), &d, buf) != AC_SUCCESS) return false;
+    g_count.buffer_create++;
     *have = need;
     return true;
 }
@@ -313,138 +328,395 @@ bool own_buffer(const ggml_tensor* t) {
     const ggml_tensor* base = t->view_src ? t->view_src : t;
     return base->buffer && base->buffer->buft == &plugin().buft;
 }
+BufferCtx* buffer_of(const ggml_tensor* t) { return (BufferCtx*)(t->view_src ? t->view_src : t)->buffer->context; }
+
+bool is_f32_rows(const ggml_tensor* t) {   // f32, rows contiguous and packed ([ne1 * ne2 * ne3][ne0])
+    return t && t->type == GGML_TYPE_F32 && ggml_is_contiguous(t);
+}
+int64_t n_rows(const ggml_tensor* t) { return t->ne[1] * t->ne[2] * t->ne[3]; }
+int64_t n_elems(const ggml_tensor* t) { return t->ne[0] * n_rows(t); }
+
+bool overlap(const ggml_tensor* a, const ggml_tensor* b) {
+    if (!a || !b || !a->data || !b->data || buffer_of(a) != buffer_of(b)) return false;
+    const char *a0 = (const char*)a->data, *b0 = (const char*)b->data;
+    return a0 < b0 + ggml_nbytes(b) && b0 < a0 + ggml_nbytes(a);
+}
+bool same_elements(const ggml_tensor* a, const ggml_tensor* b) {   // an in-place result
+    return a->data == b->data && buffer_of(a) == buffer_of(b) && ggml_nbytes(a) == ggml_nbytes(b);
+}
+
+// A MUL_MAT's weight operand resolved to device addresses: the whole repacked tensor or a range of its rows.
+struct WeightRef {
+    BufferCtx* buf;
+    uint64_t q_off, q_range, s_off, s_range;   // byte ranges of the payload and scale regions inside the buffer
+    uint32_t N, K;
+    enum ggml_type type;
+};
 
 // Why a MUL_MAT node cannot run here; NULL when it can (the reference's mul_mat_qmm_reason, ggml-ameva.cpp:1326-1377,
-// reduced to this backend's kernels).
-const char* mul_mat_reason(const ggml_tensor* node) {
+// reduced to this backend's kernels). With `out`, also resolves the weight operand and the kernel family.
+const char* mul_mat_reason(const ggml_tensor* node, WeightRef* out = nullptr, uint32_t* out_path = nullptr) {
     const ggml_tensor *w = node->src[0], *x = node->src[1];
     if (!w || !x) return "missing operand";
-    if (!is_repacked_weight(w)) return "src0 is not a 2-D contiguous Q4_0 / Q8_0 / Q4_K matrix";
-    if (!own_buffer(w) || !own_buffer(x) || !own_buffer(node)) return "an operand is not in an AMEVA_B200 buffer";
+    size_t extra = 0;
+    const ggml_tensor* base = repacked_base(w, &extra);
+    if (!base) return "src0 is not a 2-D contiguous Q4_0 / Q8_0 / Q4_K matrix (or a row range of one)";
+    uint64_t row0 = 0;
+    if (w != base) {   // rows [row0, row0 + ne1) of the base: same K, same row pitch, whole rows
+        if (w->type != base->type || w->ne[0] != base->ne[0] || w->ne[2] != 1 || w->ne[3] != 1 || w->nb[0] != base->nb[0] ||
+            w->nb[1] != base->nb[1] || extra % base->nb[1])
+            return "src0 views a repacked weight but is not a range of its rows";
+        row0 = extra / base->nb[1];
+        if (row0 + (uint64_t)w->ne[1] > (uint64_t)base->ne[1]) return "row range outside the weight";
+    }
+    if (!own_buffer(base) || !own_buffer(x) || !own_buffer(node)) return "an operand is not in an AMEVA_B200 buffer";
     if (x->type != GGML_TYPE_F32 || node->type != GGML_TYPE_F32) return "src1 / dst are not f32";
     if (!ggml_is_contiguous(x) || !ggml_is_contiguous(node)) return "src1 / dst are not contiguous";
     if (x->ne[2] != 1 || x->ne[3] != 1 || node->ne[2] != 1 || node->ne[3] != 1) return "batched (3-D / 4-D) operands";
     if (x->ne[0] != w->ne[0] || node->ne[0] != w->ne[1] || node->ne[1] != x->ne[1]) return "shape mismatch";
-    if (w->ne[0] % (w->type == GGML_TYPE_Q4_K ? 256 : 32)) return "K is not whole quantization blocks";
-    if (tensor_offset(w) % kAlign || tensor_offset(x) % kAlign || tensor_offset(node) % kAlign) return "unaligned tensor";
-    // more than 8 activation rows with a K the tensor-core kernel cannot take run as chunks of 8 rows through the GEMV:
-    // the chunks' scratch and output offsets (8 K, K, 32 N bytes) must keep the 64-byte binding alignment
-    if (x->ne[1] > 8 && w->ne[0] % 256 && (w->ne[0] % 64 || (32 * w->ne[1]) % 64)) return "chunked M > 8 needs K % 64 == 0, N % 2 == 0";
+    const uint64_t K = (uint64_t)w->ne[0], N = (uint64_t)w->ne[1], M = (uint64_t)x->ne[1];
+    const uint64_t nblk_row = K / block_elems(w->type);
+    uint64_t s_off = 0;
+    device_bytes(base, &s_off);
+    const uint64_t q_off = tensor_offset(base) + row0 * nblk_row * payload_bytes(w->type);
+    const uint64_t sc_off = tensor_offset(base) + s_off + row0 * nblk_row * scale_bytes(w->type);
+    if (q_off % kAlign || sc_off % kAlign) return "the row range does not start on a 64-byte boundary of the device layout";
+    if (tensor_offset(x) % kAlign || tensor_offset(node) % kAlign) return "unaligned tensor";
+    BufferCtx* wb = buffer_of(base);
+    auto it = wb->w_exp.find(tensor_offset(base));
+    const int w_exp = it == wb->w_exp.end() ? 0 : it->second;
+    uint32_t path = AC_B200_PATH_NONE;
+    const uint32_t flags = AC_B200_PLAN_HOST_LAUNCH | (AC_B200_WEIGHT_RANGE_EXTREME(w_exp) ? AC_B200_PLAN_WEIGHT_RANGE : 0u);
+    if (ac_b200_mul_mat_plan((uint32_t)w->type, M, N, K, flags, &path) != AC_SUCCESS) return "shape outside the kernels' contract";
+    // more than 8 activation rows on the GEMV family run as chunks of 8 rows: the chunks' scratch and output offsets
+    // (8 K, 8 scale rows, 32 N bytes) must keep the 64-byte binding alignment
+    if (M > 8 && path == AC_B200_PATH_GEMV && (K % 64 || (32 * N) % 64)) return "chunked M > 8 needs K % 64 == 0, N % 2 == 0";
+    if (out) {
+        out->buf = wb;
+        out->q_off = q_off;
+        out->q_range = N * nblk_row * payload_bytes(w->type);
+        out->s_off = sc_off;
+        out->s_range = N * nblk_row * scale_bytes(w->type);
+        out->N = (uint32_t)N;
+        out->K = (uint32_t)K;
+        out->type = w->type;
+    }
+    if (out_path) *out_path = path;
     return nullptr;
 }
 
-bool node_supported(const ggml_tensor* node) {
-    if (is_view_op(node->op)) return true;
-    return node->op == GGML_OP_MUL_MAT && mul_mat_reason(node) == nullptr;
+bool binary_supported(const ggml_tensor* node) {   // ADD / MUL of f32 rows: same shape, or src1 one row of the same width
+    const ggml_tensor *a = node->src[0], *b = node->src[1];
+    if (!a || !b || !is_f32_rows(a) || !is_f32_rows(b) || !is_f32_rows(node)) return false;
+    if (a->ne[0] != node->ne[0] || n_rows(a) != n_rows(node) || b->ne[0] != a->ne[0]) return false;
+    const int64_t br = n_rows(b);
+    return br >= 1 && (br == 1 || br == n_rows(a));
+}
+bool glu_supported(const ggml_tensor* node) {      // the split SWIGLU: silu(src0) * src1
+    const ggml_tensor *a = node->src[0], *b = node->src[1];
+    return a && b && node->op_params[0] == (int32_t)GGML_GLU_OP_SWIGLU && node->op_params[1] == 0 && is_f32_rows(a) &&
+           is_f32_rows(b) && is_f32_rows(node) && n_elems(a) == n_elems(b) && n_elems(a) == n_elems(node);
+}
+bool rms_norm_supported(const ggml_tensor* node) {
+    const ggml_tensor* a = node->src[0];
+    return a && is_f32_rows(a) && is_f32_rows(node) && n_elems(a) == n_elems(node) && a->ne[0] == node->ne[0];
+}
+
+// shapes and types only (at planning time tensors may not be allocated yet)
+bool op_supported_static(const ggml_tensor* op) {
+    if (is_view_op(op->op)) return true;
+    switch (op->op) {
+        case GGML_OP_MUL_MAT: {
+            const ggml_tensor *w = op->src[0], *x = op->src[1];
+            if (!w || !x || !repacked_type(w->type) || w->ne[2] != 1 || w->ne[3] != 1 || x->type != GGML_TYPE_F32 ||
+                op->type != GGML_TYPE_F32 || x->ne[2] != 1 || x->ne[3] != 1 || !ggml_is_contiguous(x) ||
+                w->ne[0] % block_elems(w->type))
+                return false;
+            uint32_t path = 0;
+            return ac_b200_mul_mat_plan((uint32_t)w->type, (uint64_t)x->ne[1], (uint64_t)w->ne[1], (uint64_t)w->ne[0],
+                                        AC_B200_PLAN_HOST_LAUNCH, &path) == AC_SUCCESS;
+        }
+        case GGML_OP_ADD:
+        case GGML_OP_MUL: return binary_supported(op);
+        case GGML_OP_GLU: return glu_supported(op);
+        case GGML_OP_RMS_NORM: return rms_norm_supported(op);
+        default: return false;
+    }
+}
+
+const char* node_reason(const ggml_tensor* node) {
+    if (is_view_op(node->op)) return nullptr;
+    if (node->op == GGML_OP_MUL_MAT) return mul_mat_reason(node);
+    if (!op_supported_static(node)) return "op, type or shape not built";
+    for (int i = 0; i < GGML_MAX_SRC && node->src[i]; ++i)
+        if (!own_buffer(node->src[i]) || tensor_offset(node->src[i]) % kAlign)
+            return "an operand is not in an AMEVA_B200 buffer (or unaligned)";
+    if (!own_buffer(node) || tensor_offset(node) % kAlign) return "dst is not in an AMEVA_B200 buffer (or unaligned)";
+    return nullptr;
 }
 
 AcBufferBinding bind(AcBuffer* b, uint64_t off, uint64_t range) {
     AcBufferBinding r = {b, off, range};
     return r;
 }
+AcBufferBinding bind_tensor(const ggml_tensor* t) { return bind(buffer_of(t)->buf, tensor_offset(t), ggml_nbytes(t)); }
 
-// Records quantize + mul_mat of one node: the sequence of ameva-compute_b200/qmm.py MulMat.record.
-bool record_mul_mat(Backend* be, AcCommandBatch* batch, const ggml_tensor* node) {
-    const ggml_tensor *w = node->src[0], *x = node->src[1];
-    const uint32_t K = (uint32_t)w->ne[0], N = (uint32_t)w->ne[1], M = (uint32_t)x->ne[1];
-    const bool q4k = w->type == GGML_TYPE_Q4_K;
-    const char* tname = w->type == GGML_TYPE_Q4_0 ? "q4_0" : (w->type == GGML_TYPE_Q8_0 ? "q8_0" : "q4_K");
-    const bool tc = M > 8 && (K % 256) == 0;
-    const uint64_t ad_need = q4k ? (uint64_t)M * (K / 256) * 48u : (uint64_t)M * (K / 32) * 4u;
-    BufferCtx* wb = (BufferCtx*)w->buffer->context;
-    BufferCtx* xb = (BufferCtx*)(x->view_src ? x->view_src : x)->buffer->context;
-    BufferCtx* yb = (BufferCtx*)(node->view_src ? node->view_src : node)->buffer->context;
-    uint64_t s_off = 0;
-    const uint64_t wtotal = device_bytes(w, &s_off);
-    const AcDim3 grid = {1, 1, 1};   // the launchers size their own grids
+// What graph_compute remembers while it records one graph.
+struct Recorder {
+    Backend* be = nullptr;
+    AcCommandBatch* batch = nullptr;
+    // the activation rows last quantized into the scratch (reused by the next MUL_MAT with the same src1 and scheme)
+    const void* q_data = nullptr;
+    uint32_t q_M = 0, q_K = 0;
+    int q_scheme = -1;   // 0 per-32, 1 per-256; +2 when the fp16 operand was written too
+    int64_t gpu_ops = 0, mul_mats = 0, mmq = 0, mmqb = 0, fused = 0;
+};
 
-    // One token of a projection small enough to be launch-bound: one launch that quantizes the row inside the GEMV
-    // (same bits as the two kernels below; the limits are those of qmm.py's MulMat.record).
-    if (M == 1 && K <= 16384u && (uint64_t)N * K <= (64ull << 20) && tensor_offset(x) % 64 == 0 &&
-        tensor_offset(node) % 64 == 0) {
-        AcKernel* k = kernel(be, (std::string(q4k ? "ameva_mmvqb_" : "ameva_mmvq_") + tname + "_fq").c_str());
-        if (!k) return false;
-        AcBufferBinding b[4] = {bind(wb->buf, tensor_offset(w), s_off), bind(wb->buf, tensor_offset(w) + s_off, wtotal - s_off),
-                                bind(xb->buf, tensor_offset(x), (uint64_t)K * 4),
-                                bind(yb->buf, tensor_offset(node), (uint64_t)N * 4)};
-        const uint32_t push[3] = {N, K, 0};   // ties-to-even per-32 / ggml's per-256 convention
-        return ac_runtime_batch_dispatch_bindings(batch, k, b, 4, push, sizeof(push), grid) == AC_SUCCESS;
-    }
-
-    // 1. activation quantization (per-32 for Q4_0 / Q8_0, per-256 for Q4_K; fp16 operand too when M > 8)
-    {
-        std::string name = q4k ? "ameva_quant_a8b" : "ameva_quant_a8";
-        if (tc) name += "_f16";
-        AcKernel* k = kernel(be, name.c_str());
-        if (!k) return false;
-        AcBufferBinding b[5] = {bind(xb->buf, tensor_offset(x), (uint64_t)M * K * 4), bind(be->aq, 0, (uint64_t)M * K),
-                                bind(be->ad, 0, ad_need), bind(be->ah, 0, (uint64_t)M * K * 2), bind(be->ae, 0, (uint64_t)M * 4)};
-        const uint32_t push[4] = {M, K, K, 0};   // ties-to-even per-32 / ggml's per-256 convention
-        if (ac_runtime_batch_dispatch_bindings(batch, k, b, tc ? 5 : 3, push, sizeof(push), grid) != AC_SUCCESS)
-            return false;
-        ac_runtime_batch_barrier(batch);
-    }
-    const AcBufferBinding Q = bind(wb->buf, tensor_offset(w), s_off), S = bind(wb->buf, tensor_offset(w) + s_off, wtotal - s_off);
-    // 2. the product: tensor-core GEMM for M > 8, streaming GEMV (in chunks of 8 rows when K rules the GEMM out) else
-    if (tc) {
-        AcKernel* k = kernel(be, (std::string("ameva_mmtc_") + tname).c_str());
-        if (!k) return false;
-        AcBufferBinding b[5] = {Q, S, bind(be->ah, 0, (uint64_t)M * K * 2),
-                                bind(yb->buf, tensor_offset(node), (uint64_t)M * N * 4), bind(be->ae, 0, (uint64_t)M * 4)};
-        auto it = wb->w_exp.find(tensor_offset(w));
-        const uint32_t push[6] = {M, N, K, N, 0, (uint32_t)(it == wb->w_exp.end() ? 0 : it->second)};
-        return ac_runtime_batch_dispatch_bindings(batch, k, b, 5, push, sizeof(push), grid) == AC_SUCCESS;
-    }
-    // M <= 8 over short weight rows, with several activation rows or a large matrix: the GEMV that stages whole weight
-    // rows in shared memory (the choice of qmm.py's MulMat.streamed_pays)
-    const uint64_t row_bytes = (uint64_t)(K / 256) * ((w->type == GGML_TYPE_Q8_0 ? 256u : 128u) + 16u);
-    if (M <= 8 && (K % 256) == 0 && row_bytes <= 6400u && (M >= 4 || (uint64_t)N * row_bytes >= (64ull << 20))) {
-        AcKernel* ks = kernel(be, (std::string("ameva_mmvs_") + tname).c_str());
-        if (!ks) return false;
-        const AcBufferBinding y = bind(yb->buf, tensor_offset(node), (uint64_t)M * N * 4);
-        AcBufferBinding b[12] = {Q, S, bind(be->aq, 0, (uint64_t)M * K), bind(be->ad, 0, ad_need), y, y, y, y, y, y, y, y};
-        const uint32_t push[6] = {M, N, K, N, 0, 0};
-        return ac_runtime_batch_dispatch_bindings(batch, ks, b, 12, push, sizeof(push), grid) == AC_SUCCESS;
-    }
-    AcKernel* k = kernel(be, (std::string(q4k ? "ameva_mmvqb_" : "ameva_mmvq_") + tname).c_str());
+bool dispatch(Recorder& r, const char* name, const AcBufferBinding* b, uint32_t nb, const uint32_t* push, size_t push_bytes) {
+    AcKernel* k = kernel(r.be, name);
     if (!k) return false;
-    for (uint32_t m0 = 0; m0 < M; m0 += 8) {
-        const uint32_t mc = M - m0 < 8 ? M - m0 : 8;
-        const uint64_t ad_row = q4k ? (uint64_t)(K / 256) * 48u : (uint64_t)(K / 32) * 4u;
-        AcBufferBinding b[5] = {Q, S, bind(be->aq, (uint64_t)m0 * K, (uint64_t)mc * K),
-                                bind(be->ad, m0 * ad_row, mc * ad_row),
-                                bind(yb->buf, tensor_offset(node) + (uint64_t)m0 * N * 4, (uint64_t)mc * N * 4)};
-        const uint32_t push[4] = {mc, N, K, N};
-        if (ac_runtime_batch_dispatch_bindings(batch, k, b, 5, push, sizeof(push), grid) != AC_SUCCESS) return false;
-    }
+    const AcDim3 grid = {1, 1, 1};   // the launchers size their own grids
+    return ac_runtime_batch_dispatch_bindings(r.batch, k, b, nb, push, push_bytes, grid) == AC_SUCCESS;
+}
+
+const char* type_name(enum ggml_type t) { return t == GGML_TYPE_Q4_0 ? "q4_0" : (t == GGML_TYPE_Q8_0 ? "q8_0" : "q4_K"); }
+
+// activation quantization into the scratch, unless the same rows are there already
+bool record_quantize(Recorder& r, const ggml_tensor* x, enum ggml_type wtype, uint32_t M, uint32_t K, bool tc) {
+    const bool q4k = wtype == GGML_TYPE_Q4_K;
+    const int scheme = (q4k ? 1 : 0) + (tc ? 2 : 0);
+    if (r.q_data == x->data && r.q_M == M && r.q_K == K && (r.q_scheme == scheme || r.q_scheme == scheme + 2)) return true;
+    const uint64_t ad_need = q4k ? (uint64_t)M * (K / 256) * 48u : (uint64_t)M * (K / 32) * 4u;
+    std::string name = q4k ? "ameva_quant_a8b" : "ameva_quant_a8";
+    if (tc) name += "_f16";
+    AcBufferBinding b[5] = {bind(buffer_of(x)->buf, tensor_offset(x), (uint64_t)M * K * 4), bind(r.be->aq, 0, (uint64_t)M * K),
+                            bind(r.be->ad, 0, ad_need), bind(r.be->ah, 0, (uint64_t)M * K * 2),
+                            bind(r.be->ae, 0, (uint64_t)M * 4)};
+    const uint32_t push[4] = {M, K, K, 0};   // ties-to-even per-32 / ggml's per-256 convention
+    if (!dispatch(r, name.c_str(), b, tc ? 5 : 3, push, sizeof(push))) return false;
+    ac_runtime_batch_barrier(r.batch);
+    r.q_data = x->data;
+    r.q_M = M;
+    r.q_K = K;
+    r.q_scheme = scheme;
     return true;
 }
 
-const char* backend_get_name(ggml_backend_t) { return "AMEVA_B200"; }
+// Epilogue of a one-row MUL_MAT fused with the node that consumes it (AmevaEpilogue, ggml-ameva.cpp:2272-2279).
+struct Epilogue {
+    uint32_t mode = 0;   // 1 out = v + e, 2 out = silu(v) * e, 3 out = silu(e) * v
+    const ggml_tensor* e = nullptr;
+    const ggml_tensor* out = nullptr;
+};
+
+// Whether n1 consumes the one-row product n0 in a way the GEMV's epilogue computes (ameva_find_fusion, :4345-4378).
+Epilogue find_epilogue(const ggml_tensor* n0, const ggml_tensor* n1) {
+    Epilogue f;
+    if (!n1 || n0->op != GGML_OP_MUL_MAT || n0->src[1]->ne[1] != 1) return f;
+    const int64_t N = n0->ne[0];
+    if (n1->op != GGML_OP_ADD && n1->op != GGML_OP_GLU) return f;
+    if (node_reason(n1)) return f;
+    if (!is_f32_rows(n1) || n_elems(n1) != N) return f;
+    const ggml_tensor* other = n1->src[0] == n0 ? n1->src[1] : (n1->src[1] == n0 ? n1->src[0] : nullptr);
+    if (!other || other == n0 || n_elems(other) != N) return f;
+    // the activation row is read by every CTA: the fused output must not overlap it at all; it may overlap the product
+    // or the other operand only as the same elements (in place)
+    if (overlap(n1, n0->src[1])) return f;
+    if (overlap(n1, n0) && !same_elements(n1, n0)) return f;
+    if (overlap(n1, other) && !same_elements(n1, other)) return f;
+    if (n1->op == GGML_OP_ADD) f.mode = 1;
+    else f.mode = n1->src[0] == n0 ? 2u : 3u;
+    f.e = other;
+    f.out = n1;
+    return f;
+}
+
+// quantize + mul_mat of one node
+bool record_mul_mat(Recorder& r, const ggml_tensor* node, const Epilogue& ep) {
+    WeightRef w;
+    uint32_t path = 0;
+    if (mul_mat_reason(node, &w, &path)) return false;
+    const ggml_tensor* x = node->src[1];
+    const uint32_t K = w.K, N = w.N, M = (uint32_t)x->ne[1];
+    const bool q4k = w.type == GGML_TYPE_Q4_K;
+    const char* tname = type_name(w.type);
+    const uint64_t ad_need = q4k ? (uint64_t)M * (K / 256) * 48u : (uint64_t)M * (K / 32) * 4u;
+    const AcBufferBinding Q = bind(w.buf->buf, w.q_off, w.q_range), S = bind(w.buf->buf, w.s_off, w.s_range);
+    const AcBufferBinding X = bind_tensor(x), Y = bind_tensor(node);
+    r.mul_mats++;
+    if (ep.mode) path = AC_B200_PATH_GEMV;   // the fused consumers live on the register-staged one-row kernels
+    if (path != AC_B200_PATH_GEMM_TC) {
+        r.mmq++;
+        if (q4k) r.mmqb++;
+    }
+    switch (path) {
+        case AC_B200_PATH_GEMV_FQ: {   // one launch that quantizes the row inside the GEMV
+            AcBufferBinding b[4] = {Q, S, X, Y};
+            const uint32_t push[3] = {N, K, 0};   // ties-to-even per-32 / ggml's per-256 convention
+            return dispatch(r, (std::string(q4k ? "ameva_mmvqb_" : "ameva_mmvq_") + tname + "_fq").c_str(), b, 4, push,
+                            sizeof(push));
+        }
+        case AC_B200_PATH_GEMM_TC: {
+            if (!record_quantize(r, x, w.type, M, K, true)) return false;
+            AcBufferBinding b[5] = {Q, S, bind(r.be->ah, 0, (uint64_t)M * K * 2), Y, bind(r.be->ae, 0, (uint64_t)M * 4)};
+            const uint32_t push[5] = {M, N, K, N, 0};
+            return dispatch(r, (std::string("ameva_mmtc_") + tname).c_str(), b, 5, push, sizeof(push));
+        }
+        case AC_B200_PATH_GEMV_MMA: {
+            if (!record_quantize(r, x, w.type, M, K, false)) return false;
+            AcBufferBinding b[5] = {Q, S, bind(r.be->aq, 0, (uint64_t)M * K), bind(r.be->ad, 0, ad_need), Y};
+            const uint32_t push[4] = {M, N, K, N};
+            return dispatch(r, "ameva_mmvm_q4_K", b, 5, push, sizeof(push));
+        }
+        case AC_B200_PATH_GEMV_STREAMED: {
+            if (!record_quantize(r, x, w.type, M, K, false)) return false;
+            AcBufferBinding b[12] = {Q, S, bind(r.be->aq, 0, (uint64_t)M * K), bind(r.be->ad, 0, ad_need), Y, Y, Y, Y, Y, Y, Y, Y};
+            const uint32_t push[6] = {M, N, K, N, 0, 0};
+            return dispatch(r, (std::string("ameva_mmvs_") + tname).c_str(), b, 12, push, sizeof(push));
+        }
+        case AC_B200_PATH_GEMV: {
+            if (!record_quantize(r, x, w.type, M, K, false)) return false;
+            std::string name = std::string(q4k ? "ameva_mmvqb_" : "ameva_mmvq_") + tname;
+            if (ep.mode) {
+                AcBufferBinding b[7] = {Q, S, bind(r.be->aq, 0, (uint64_t)K), bind(r.be->ad, 0, ad_need), Y, bind_tensor(ep.e),
+                                        bind_tensor(ep.out)};
+                const uint32_t push[5] = {1, N, K, N, ep.mode};
+                return dispatch(r, (name + "_ep").c_str(), b, 7, push, sizeof(push));
+            }
+            const uint64_t ad_row = q4k ? (uint64_t)(K / 256) * 48u : (uint64_t)(K / 32) * 4u;
+            for (uint32_t m0 = 0; m0 < M; m0 += 8) {   // chunks of 8 rows
+                const uint32_t mc = M - m0 < 8 ? M - m0 : 8;
+                AcBufferBinding b[5] = {Q, S, bind(r.be->aq, (uint64_t)m0 * K, (uint64_t)mc * K),
+                                        bind(r.be->ad, m0 * ad_row, mc * ad_row),
+                                        bind(buffer_of(node)->buf, tensor_offset(node) + (uint64_t)m0 * N * 4, (uint64_t)mc * N * 4)};
+                const uint32_t push[4] = {mc, N, K, N};
+                if (!dispatch(r, name.c_str(), b, 5, push, sizeof(push))) return false;
+            }
+            return true;
+        }
+        default: return false;
+    }
+}
+
+// Consecutive one-row MUL_MATs that share src1 (q / k / v; gate / up) as one launch. nodes[0..count) are the MUL_MATs.
+bool record_group(Recorder& r, const ggml_tensor* const* nodes, uint32_t count) {
+    WeightRef w[4];
+    for (uint32_t j = 0; j < count; ++j)
+        if (mul_mat_reason(nodes[j], &w[j])) return false;
+    const bool q4k = w[0].type == GGML_TYPE_Q4_K;
+    AcBufferBinding b[13];
+    uint32_t push[7] = {w[0].K, 0, count, 0, 0, 0, 0};
+    for (uint32_t j = 0; j < 4; ++j) {
+        const uint32_t jj = j < count ? j : 0;
+        b[3 * j] = bind(w[jj].buf->buf, w[jj].q_off, w[jj].q_range);
+        b[3 * j + 1] = bind(w[jj].buf->buf, w[jj].s_off, w[jj].s_range);
+        b[3 * j + 2] = bind_tensor(nodes[jj]);
+        if (j < count) push[3 + j] = w[j].N;
+    }
+    b[12] = bind_tensor(nodes[0]->src[1]);
+    r.mul_mats += count;
+    r.mmq += count;
+    if (q4k) r.mmqb += count;
+    r.fused += count - 1;
+    return dispatch(r, (std::string(q4k ? "ameva_mmvqgb_" : "ameva_mmvqg_") + type_name(w[0].type) + "_fq").c_str(), b, 13, push,
+                    sizeof(push));
+}
+
+// Can node b join the group that starts with node a? (one activation row, the same src1, type and K, an even N, the
+// one-launch path for the shape, outputs that do not overlap the shared activation row or each other)
+bool groups_with(const ggml_tensor* a, const ggml_tensor* b) {
+    if (b->op != GGML_OP_MUL_MAT) return false;
+    WeightRef wa, wb;
+    uint32_t pa = 0, pb = 0;
+    if (mul_mat_reason(a, &wa, &pa) || mul_mat_reason(b, &wb, &pb)) return false;
+    return pa == AC_B200_PATH_GEMV_FQ && pb == AC_B200_PATH_GEMV_FQ && a->src[1]->data == b->src[1]->data &&
+           buffer_of(a->src[1]) == buffer_of(b->src[1]) && a->src[1]->ne[1] == 1 && b->src[1]->ne[1] == 1 && wa.type == wb.type &&
+           wa.K == wb.K && wa.N % 2 == 0 && wb.N % 2 == 0 && !overlap(b, a->src[1]) && !overlap(a, a->src[1]) && !overlap(a, b);
+}
+
+bool record_elementwise(Recorder& r, const ggml_tensor* node, const ggml_tensor* fused_mul) {
+    switch (node->op) {
+        case GGML_OP_ADD:
+        case GGML_OP_MUL: {
+            AcBufferBinding b[3] = {bind_tensor(node->src[0]), bind_tensor(node->src[1]), bind_tensor(node)};
+            const uint32_t push[3] = {(uint32_t)n_rows(node), (uint32_t)node->ne[0], (uint32_t)n_rows(node->src[1])};
+            return dispatch(r, node->op == GGML_OP_ADD ? "ameva_add_f32" : "ameva_mul_f32", b, 3, push, sizeof(push));
+        }
+        case GGML_OP_GLU: {
+            AcBufferBinding b[3] = {bind_tensor(node->src[0]), bind_tensor(node->src[1]), bind_tensor(node)};
+            const uint32_t push[1] = {(uint32_t)n_elems(node)};
+            return dispatch(r, "ameva_swiglu_f32", b, 3, push, sizeof(push));
+        }
+        case GGML_OP_RMS_NORM: {
+            // alone, or with the MUL by a weight row that follows it (one kernel writes the MUL's output)
+            const ggml_tensor* wt = nullptr;
+            const ggml_tensor* out = node;
+            if (fused_mul) {
+                wt = fused_mul->src[0] == node ? fused_mul->src[1] : fused_mul->src[0];
+                out = fused_mul;
+            }
+            AcBufferBinding b[3] = {bind_tensor(node->src[0]), wt ? bind_tensor(wt) : bind_tensor(node->src[0]), bind_tensor(out)};
+            uint32_t push[4] = {(uint32_t)n_rows(node), (uint32_t)node->ne[0], 0, wt ? 1u : 0u};
+            memcpy(&push[2], &node->op_params[0], 4);   // eps
+            return dispatch(r, "ameva_rms_norm_f32", b, 3, push, sizeof(push));
+        }
+        default: return false;
+    }
+}
+
+// RMS_NORM followed by MUL with a weight row of the same width (the RMS_NORM + MUL pair of ameva_find_fusion)
+bool rms_mul_pair(const ggml_tensor* n0, const ggml_tensor* n1) {
+    if (!n1 || n0->op != GGML_OP_RMS_NORM || n1->op != GGML_OP_MUL || node_reason(n1)) return false;
+    const ggml_tensor* wt = n1->src[0] == n0 ? n1->src[1] : (n1->src[1] == n0 ? n1->src[0] : nullptr);
+    if (!wt || wt == n0 || n_rows(wt) != 1 || wt->ne[0] != n0->ne[0] || n_elems(n1) != n_elems(n0)) return false;
+    if (overlap(n1, wt)) return false;
+    if (overlap(n1, n0->src[0]) && !same_elements(n1, n0->src[0])) return false;
+    return true;
+}
+
+const char* backend_get_name(ggml_backend_t) { return GGML_AMEVA_B200_NAME; }
 
 void backend_free(ggml_backend_t backend) {
     Backend* be = (Backend*)backend->context;
     {
         std::lock_guard<std::mutex> lock(plugin().mutex);
-        for (auto& kv : be->kernels) ac_runtime_kernel_destroy(kv.second);
+        for (auto& kv : be->kernels)
+            if (ac_runtime_kernel_destroy(kv.second) == AC_SUCCESS) g_count.kernel_destroy++;
         for (AcBuffer* b : {be->aq, be->ad, be->ah, be->ae})
-            if (b) ac_runtime_buffer_destroy(b);
+            if (b && ac_runtime_buffer_destroy(b) == AC_SUCCESS) g_count.buffer_destroy++;
+        plugin().live_backends--;
     }
     delete be;
     delete backend;
 }
 
+int next_compute_node(ggml_cgraph* g, int i, int n) {   // the first node after i that computes something, or -1
+    for (int j = i + 1; j < n; ++j) {
+        const ggml_tensor* t = ggml_graph_node(g, j);
+        if (!is_view_op(t->op) && !ggml_is_empty(t)) return j;
+    }
+    return -1;
+}
+
 enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgraph) {
     Backend* be = (Backend*)backend->context;
     std::lock_guard<std::mutex> lock(plugin().mutex);
+    const int fi = g_fail.load();
     const int n = ggml_graph_n_nodes(cgraph);
+    int work = 0;
     for (int i = 0; i < n; ++i) {   // every node first: nothing is recorded if one cannot run
         const ggml_tensor* node = ggml_graph_node(cgraph, i);
-        if (!node_supported(node)) {
-            fprintf(stderr, "ggml-ameva-b200: node %d (%s, %s) cannot run here: %s\n", i, ggml_op_name(node->op), node->name,
-                    node->op == GGML_OP_MUL_MAT ? mul_mat_reason(node) : "op not built");
+        if (const char* why = node_reason(node)) {
+            fprintf(stderr, "ggml-ameva-b200: node %d (%s, %s) cannot run here: %s\n", i, ggml_op_name(node->op), node->name, why);
             return GGML_STATUS_FAILED;
         }
+        if (!is_view_op(node->op) && !ggml_is_empty(node)) ++work;
+    }
+    if (work == 0) return GGML_STATUS_SUCCESS;
+    if (fi == AMEVA_FAIL_TENSOR_RANGE_OOB || fi == AMEVA_FAIL_MAP_SRC0 || fi == AMEVA_FAIL_MAP_SRC1 || fi == AMEVA_FAIL_MAP_DST ||
+        fi == AMEVA_FAIL_OFFSET_OVERFLOW || fi == AMEVA_FAIL_FLUSH_SRC0 || fi == AMEVA_FAIL_FLUSH_SRC1) {
+        fprintf(stderr, "ggml-ameva-b200 [FAILURE_INJECTION]: point %d triggered while binding\n", fi);
+        return GGML_STATUS_FAILED;
     }
     // scratch for the quantized activations: the largest need over all nodes, reserved before anything is recorded
     size_t aq_need = 0, ad_need = 0, ah_need = 0, ae_need = 0;
@@ -463,21 +735,103 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
     if ((aq_need && !grow(&be->aq, &be->aq_bytes, aq_need)) || (ad_need && !grow(&be->ad, &be->ad_bytes, ad_need)) ||
         (ah_need && !grow(&be->ah, &be->ah_bytes, ah_need)) || (ae_need && !grow(&be->ae, &be->ae_bytes, ae_need)))
         return GGML_STATUS_ALLOC_FAILED;
-    AcCommandBatch* batch = nullptr;
-    AcBatchDesc bd = {AC_ABI_VERSION, (uint32_t)sizeof(AcBatchDesc), 4096u, 0u};
-    if (ac_runtime_batch_begin_ex(context(), &bd, &batch) != AC_SUCCESS) return GGML_STATUS_ALLOC_FAILED;
+    Recorder r;
+    r.be = be;
+    AcBatchDesc bd = {AC_ABI_VERSION, (uint32_t)sizeof(AcBatchDesc), 16384u, 0u};
+    if (ac_runtime_batch_begin_ex(context(), &bd, &r.batch) != AC_SUCCESS) return GGML_STATUS_ALLOC_FAILED;
     bool ok = true;
-    for (int i = 0; i < n && ok; ++i) {
+    for (int i = 0; i < n && ok;) {
         const ggml_tensor* node = ggml_graph_node(cgraph, i);
-        if (node->op == GGML_OP_MUL_MAT) {
-            ok = record_mul_mat(be, batch, node);
-            ac_runtime_batch_barrier(batch);
+        if (is_view_op(node->op) || ggml_is_empty(node)) {
+            ++i;
+            continue;
         }
+        const int j = next_compute_node(cgraph, i, n);
+        const ggml_tensor* next = j >= 0 ? ggml_graph_node(cgraph, j) : nullptr;
+        int consumed_upto = i;   // index of the last node this step computes
+        if (node->op == GGML_OP_MUL_MAT) {
+            // a run of one-row MUL_MATs sharing src1: one launch (up to four)
+            const ggml_tensor* grp[4] = {node, nullptr, nullptr, nullptr};
+            uint32_t count = 1;
+            int last = i;
+            for (int jj = j; jj >= 0 && count < 4 && groups_with(node, ggml_graph_node(cgraph, jj));
+                 jj = next_compute_node(cgraph, jj, n)) {
+                bool clash = false;   // no member may write what another member writes
+                for (uint32_t q = 1; q < count && !clash; ++q) clash = overlap(ggml_graph_node(cgraph, jj), grp[q]);
+                if (clash) break;
+                grp[count++] = ggml_graph_node(cgraph, jj);
+                last = jj;
+            }
+            if (count > 1) {
+                ok = record_group(r, grp, count);   // (quantizes inside the kernel: the scratch holds nothing of this src1)
+                r.gpu_ops += count;
+                consumed_upto = last;
+            } else {
+                const Epilogue ep = find_epilogue(node, next);
+                ok = record_mul_mat(r, node, ep);
+                r.gpu_ops += 1;
+                if (ep.mode) {
+                    r.gpu_ops += 1;
+                    r.fused += 1;
+                    consumed_upto = j;
+                }
+            }
+        } else if (node->op == GGML_OP_RMS_NORM && rms_mul_pair(node, next)) {
+            ok = record_elementwise(r, node, next);
+            r.gpu_ops += 2;
+            r.fused += 1;
+            consumed_upto = j;
+        } else {
+            ok = record_elementwise(r, node, nullptr);
+            r.gpu_ops += 1;
+        }
+        // a node that wrote over the rows whose quantized form sits in the scratch invalidates it
+        for (int q = i; q <= consumed_upto && r.q_data; ++q) {
+            const ggml_tensor* t = ggml_graph_node(cgraph, q);
+            if (is_view_op(t->op)) continue;
+            const char* d0 = (const char*)t->data;
+            const char* x0 = (const char*)r.q_data;
+            if (d0 < x0 + (size_t)r.q_M * r.q_K * 4 && x0 < d0 + ggml_nbytes(t)) r.q_data = nullptr;
+        }
+        ac_runtime_batch_barrier(r.batch);
+        i = consumed_upto + 1;
     }
-    if (ok) ok = ac_runtime_batch_submit(batch, nullptr) == AC_SUCCESS;   // blocks until the GPU finished
-    else ac_runtime_batch_abort(batch);
-    ac_runtime_batch_destroy(batch);
-    return ok ? GGML_STATUS_SUCCESS : GGML_STATUS_FAILED;
+    if (ok && fi == AMEVA_FAIL_DISPATCH) {
+        fprintf(stderr, "ggml-ameva-b200 [FAILURE_INJECTION]: DISPATCH_FAIL triggered\n");
+        ok = false;
+    }
+    if (!ok) {
+        ac_runtime_batch_abort(r.batch);
+        ac_runtime_batch_destroy(r.batch);
+        return GGML_STATUS_FAILED;
+    }
+    AcEvent* ev = nullptr;
+    AcResult rc = ac_runtime_batch_submit(r.batch, &ev);
+    if (rc == AC_SUCCESS && ev) {
+        g_count.event_create++;
+        rc = ac_runtime_event_wait(ev, fi == AMEVA_FAIL_WAIT_TIMEOUT ? 1ull : 600ull * 1000000000ull);
+        if (fi == AMEVA_FAIL_WAIT_TIMEOUT) {
+            // the injected 1 ns limit has run out (or the work was already done): the graph is reported failed either way,
+            // after the work has finished, so that nothing is still writing when the caller looks at its tensors
+            fprintf(stderr, "ggml-ameva-b200 [FAILURE_INJECTION]: WAIT_TIMEOUT triggered\n");
+            ac_runtime_event_wait(ev, 600ull * 1000000000ull);
+            rc = AC_ERR_LAUNCH_TIMEOUT;
+        }
+        if (ac_runtime_event_destroy(ev) == AC_SUCCESS) g_count.event_destroy++;
+    }
+    ac_runtime_batch_destroy(r.batch);
+    if (rc == AC_SUCCESS && fi == AMEVA_FAIL_INVALIDATE_DST) {
+        fprintf(stderr, "ggml-ameva-b200 [FAILURE_INJECTION]: INVALIDATE_DST_FAIL triggered\n");
+        rc = AC_ERR_BUFFER_NOT_MAPPED;
+    }
+    if (rc != AC_SUCCESS) return GGML_STATUS_FAILED;
+    g_count.gpu_op += r.gpu_ops;
+    g_count.mul_mat += r.mul_mats;
+    g_count.qmv += r.mul_mats;
+    g_count.mmq += r.mmq;
+    g_count.mmqb += r.mmqb;
+    g_count.fused_pairs += r.fused;
+    return GGML_STATUS_SUCCESS;
 }
 
 ggml_guid_t backend_guid() {
@@ -486,7 +840,7 @@ ggml_guid_t backend_guid() {
 }
 
 // ---- device -----------------------------------------------------------------------------------------------------------
-const char* dev_get_name(ggml_backend_dev_t) { return "AMEVA_B200_0"; }
+const char* dev_get_name(ggml_backend_dev_t) { return GGML_AMEVA_B200_DEVICE_NAME; }
 const char* dev_get_description(ggml_backend_dev_t) {
     std::lock_guard<std::mutex> lock(plugin().mutex);
     return context() ? plugin().name.c_str() : "NVIDIA B200 (context unavailable)";
@@ -519,6 +873,7 @@ ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char*) {
     {
         std::lock_guard<std::mutex> lock(plugin().mutex);
         if (!context()) return nullptr;
+        plugin().live_backends++;
     }
     ggml_backend* b = new ggml_backend();
     memset(&b->iface, 0, sizeof(b->iface));
@@ -532,22 +887,19 @@ ggml_backend_t dev_init_backend(ggml_backend_dev_t dev, const char*) {
     return b;
 }
 bool dev_supports_op(ggml_backend_dev_t, const ggml_tensor* op) {
-    if (is_view_op(op->op)) return true;
-    if (op->op != GGML_OP_MUL_MAT) return false;
-    // at planning time tensors may not be allocated yet: judge types and shapes only
-    const ggml_tensor *w = op->src[0], *x = op->src[1];
-    return w && x && repacked_type(w->type) && w->ne[2] == 1 && w->ne[3] == 1 && x->type == GGML_TYPE_F32 &&
-           op->type == GGML_TYPE_F32 && x->ne[2] == 1 && x->ne[3] == 1 && ggml_is_contiguous(w) && ggml_is_contiguous(x) &&
-           w->ne[0] % (w->type == GGML_TYPE_Q4_K ? 256 : 32) == 0;
+    g_count.supports_query++;
+    const bool yes = op_supported_static(op);
+    if (yes) g_count.supported_op++;
+    return yes;
 }
 bool dev_supports_buft(ggml_backend_dev_t, ggml_backend_buffer_type_t buft) { return buft == &plugin().buft; }
 bool dev_offload_op(ggml_backend_dev_t, const ggml_tensor*) { return false; }
 
 // ---- registry ---------------------------------------------------------------------------------------------------------
-const char* reg_get_name(ggml_backend_reg_t) { return "AMEVA_B200"; }
+const char* reg_get_name(ggml_backend_reg_t) { return GGML_AMEVA_B200_NAME; }
 size_t reg_get_device_count(ggml_backend_reg_t) { return 1; }
 ggml_backend_dev_t reg_get_device(ggml_backend_reg_t, size_t index) { return index == 0 ? &plugin().dev : nullptr; }
-void* reg_get_proc_address(ggml_backend_reg_t, const char*) { return nullptr; }
+void* reg_get_proc_address(ggml_backend_reg_t, const char* name);
 
 ggml_backend_reg_t registry() {
     Plugin& p = plugin();
@@ -589,6 +941,75 @@ ggml_backend_reg_t registry() {
 
 extern "C" {
 
+// ggml's struct layouts and enum values, read through the loaded ggml's own accessors, against the headers this file was
+// compiled with (the vtables of ggml-backend-impl.h are not versioned: ggml-ameva-device.cpp:408-414).
+const char* ggml_backend_ameva_abi_check(void) {
+    static std::once_flag once;
+    static char msg[320];
+    static const char* result = nullptr;
+    std::call_once(once, [] {
+        const char* what = nullptr;
+        Plugin& p = plugin();
+        registry();
+        ggml_backend pb = {};
+        pb.device = &p.dev;
+        ggml_backend_buffer_type pbt = {};
+        pbt.device = &p.dev;
+        ggml_backend_buffer pbuf = {};
+        pbuf.buft = &pbt;
+        pbuf.size = 0x5A17;
+        ggml_backend_device pd = {};
+        pd.reg = &p.reg;
+        if (ggml_backend_get_device(&pb) != &p.dev) what = "struct ggml_backend (ggml_backend_i member count)";
+        else if (ggml_backend_buffer_get_size(&pbuf) != 0x5A17 || ggml_backend_buffer_get_type(&pbuf) != &pbt)
+            what = "struct ggml_backend_buffer (ggml_backend_buffer_i member count)";
+        else if (ggml_backend_buft_get_device(&pbt) != &p.dev) what = "struct ggml_backend_buffer_type";
+        else if (ggml_backend_dev_backend_reg(&pd) != &p.reg) what = "struct ggml_backend_device";
+        static const struct {
+            enum ggml_op op;
+            const char* name;
+        } kOps[] = {{GGML_OP_NONE, "NONE"},       {GGML_OP_ADD, "ADD"},         {GGML_OP_MUL, "MUL"},   {GGML_OP_RMS_NORM, "RMS_NORM"},
+                    {GGML_OP_MUL_MAT, "MUL_MAT"}, {GGML_OP_RESHAPE, "RESHAPE"}, {GGML_OP_VIEW, "VIEW"}, {GGML_OP_PERMUTE, "PERMUTE"},
+                    {GGML_OP_TRANSPOSE, "TRANSPOSE"}, {GGML_OP_GLU, "GLU"}};
+        static const struct {
+            enum ggml_type type;
+            const char* name;
+        } kTypes[] = {{GGML_TYPE_F32, "f32"}, {GGML_TYPE_Q4_0, "q4_0"}, {GGML_TYPE_Q8_0, "q8_0"}, {GGML_TYPE_Q4_K, "q4_K"}};
+        for (const auto& o : kOps)
+            if (!what && strcmp(ggml_op_name(o.op), o.name) != 0) what = "enum ggml_op";
+        for (const auto& t : kTypes)
+            if (!what && strcmp(ggml_type_name(t.type), t.name) != 0) what = "enum ggml_type";
+        if (!what) {   // struct ggml_tensor: a MUL_MAT node built by the loaded ggml, read back with this file's layout
+            ggml_init_params ip = {8 * ggml_tensor_overhead(), nullptr, true};
+            ggml_context* tctx = ggml_init(ip);
+            if (!tctx) {
+                what = "ggml_init for the tensor layout probe";
+            } else {
+                ggml_tensor* a = ggml_new_tensor_2d(tctx, GGML_TYPE_F32, 8, 3);
+                ggml_tensor* b = ggml_new_tensor_2d(tctx, GGML_TYPE_F32, 8, 2);
+                ggml_tensor* c = ggml_mul_mat(tctx, a, b);
+                if (!c || c->op != GGML_OP_MUL_MAT || c->src[0] != a || c->src[1] != b || c->type != GGML_TYPE_F32 || c->ne[0] != 3 ||
+                    c->ne[1] != 2 || a->nb[1] != 32 || ggml_nbytes(c) != 24)
+                    what = "struct ggml_tensor";
+                char probe_name[512];
+                memset(probe_name, 'n', sizeof(probe_name) - 1);
+                probe_name[sizeof(probe_name) - 1] = 0;
+                if (!what && strlen(ggml_get_name(ggml_set_name(c, probe_name))) != sizeof(c->name) - 1)
+                    what = "struct ggml_tensor (GGML_MAX_NAME)";
+                ggml_free(tctx);
+            }
+        }
+        if (what) {
+            snprintf(msg, sizeof(msg),
+                     "ABI mismatch with the loaded ggml: %s differs from the ggml headers libggml-ameva-b200.so was compiled "
+                     "with (offsetof(ggml_backend, device)=%zu). Rebuild it against the ggml of the program that loads it.",
+                     what, offsetof(ggml_backend, device));
+            result = msg;
+        }
+    });
+    return result;
+}
+
 // NULL tells the loader the backend cannot be used (it prints "failed to initialize backend from <path>").
 GGML_BACKEND_API ggml_backend_reg_t ggml_backend_init(void) {
     if (ac_runtime_abi_version() != AC_ABI_VERSION) {
@@ -596,9 +1017,129 @@ GGML_BACKEND_API ggml_backend_reg_t ggml_backend_init(void) {
                 ac_runtime_abi_version(), (unsigned)AC_ABI_VERSION);
         return nullptr;
     }
+    if (const char* why = ggml_backend_ameva_abi_check()) {
+        fprintf(stderr, "ggml-ameva-b200: refusing to load: %s\n", why);
+        return nullptr;
+    }
     return registry();
 }
 
 GGML_BACKEND_API int ggml_backend_score(void) { return 100; }
 
+ggml_backend_reg_t ggml_backend_ameva_reg(void) { return registry(); }
+
+ggml_backend_t ggml_backend_ameva_init(size_t dev_num) {
+    if (dev_num != 0 || ggml_backend_ameva_abi_check()) return nullptr;
+    registry();
+    return dev_init_backend(&plugin().dev, nullptr);
+}
+
+bool ggml_backend_is_ameva(ggml_backend_t backend) { return backend && ggml_guid_matches(backend->guid, backend_guid()); }
+
+ggml_backend_buffer_type_t ggml_backend_ameva_buffer_type(size_t dev_num) {
+    if (dev_num != 0) return nullptr;
+    registry();
+    return &plugin().buft;
+}
+
+void ggml_backend_ameva_register(void) {
+    if (const char* why = ggml_backend_ameva_abi_check()) {
+        fprintf(stderr, "ggml-ameva-b200: not registering the backend: %s\n", why);
+        return;
+    }
+    ggml_backend_register(ggml_backend_ameva_reg());
+}
+
+void ggml_backend_ameva_teardown(void) {
+    Plugin& p = plugin();
+    std::lock_guard<std::mutex> lock(p.mutex);
+    if (!p.ctx) return;
+    if (p.live_backends || p.live_buffers) {
+        fprintf(stderr, "ggml-ameva-b200: teardown with %d backend(s) and %d buffer(s) alive: context kept\n", p.live_backends,
+                p.live_buffers);
+        return;
+    }
+    const AcResult rc = ac_runtime_context_destroy(p.ctx);
+    if (rc != AC_SUCCESS) {
+        fprintf(stderr, "ggml-ameva-b200: context destroy failed (AcResult %d): something still owns runtime objects\n", (int)rc);
+        return;
+    }
+    g_count.ctx_destroy++;
+    p.ctx = nullptr;
+}
+
+int64_t ggml_backend_ameva_get_supports_query_count(void) { return g_count.supports_query.load(); }
+int64_t ggml_backend_ameva_get_supported_op_count(void) { return g_count.supported_op.load(); }
+int64_t ggml_backend_ameva_get_gpu_op_count(void) { return g_count.gpu_op.load(); }
+int64_t ggml_backend_ameva_get_q5_0_cpu_dequant_count(void) { return 0; }
+int64_t ggml_backend_ameva_get_f32_gpu_sgemm_dispatch_count(void) { return g_count.mul_mat.load(); }
+int64_t ggml_backend_ameva_get_context_create_count(void) { return g_count.ctx_create.load(); }
+int64_t ggml_backend_ameva_get_context_destroy_count(void) { return g_count.ctx_destroy.load(); }
+int64_t ggml_backend_ameva_get_kernel_create_count(void) { return g_count.kernel_create.load(); }
+int64_t ggml_backend_ameva_get_kernel_destroy_count(void) { return g_count.kernel_destroy.load(); }
+int64_t ggml_backend_ameva_get_buffer_create_count(void) { return g_count.buffer_create.load(); }
+int64_t ggml_backend_ameva_get_buffer_destroy_count(void) { return g_count.buffer_destroy.load(); }
+int64_t ggml_backend_ameva_get_event_create_count(void) { return g_count.event_create.load(); }
+int64_t ggml_backend_ameva_get_event_destroy_count(void) { return g_count.event_destroy.load(); }
+int64_t ggml_backend_ameva_get_q5_0_staging_alloc_count(void) { return 0; }
+int64_t ggml_backend_ameva_get_q5_0_staging_free_count(void) { return 0; }
+int64_t ggml_backend_ameva_get_repacked_tensor_count(void) { return g_count.repacked_tensors.load(); }
+int64_t ggml_backend_ameva_get_repacked_bytes(void) { return g_count.repacked_bytes.load(); }
+int64_t ggml_backend_ameva_get_qmv_mul_mat_count(void) { return g_count.qmv.load(); }
+int64_t ggml_backend_ameva_get_mmq_mul_mat_count(void) { return g_count.mmq.load(); }
+int64_t ggml_backend_ameva_get_mmqb_mul_mat_count(void) { return g_count.mmqb.load(); }
+int64_t ggml_backend_ameva_get_fused_pair_count(void) { return g_count.fused_pairs.load(); }
+const char* ggml_backend_ameva_get_build_commit(void) {
+#ifdef AMEVA_B200_BUILD_COMMIT
+    return AMEVA_B200_BUILD_COMMIT;
+#else
+    return "unknown";
+#endif
+}
+void ggml_backend_ameva_reset_counters(void) {
+    // activity counters only; the repacked tensor and byte counts describe stored weights (ggml-ameva-device.cpp:129-145)
+    g_count.supports_query = 0;
+    g_count.supported_op = 0;
+    g_count.gpu_op = 0;
+    g_count.mul_mat = 0;
+    g_count.buffer_create = 0;
+    g_count.buffer_destroy = 0;
+    g_count.event_create = 0;
+    g_count.event_destroy = 0;
+    g_count.qmv = 0;
+    g_count.mmq = 0;
+    g_count.mmqb = 0;
+    g_count.fused_pairs = 0;
+}
+
+void ggml_backend_ameva_set_failure_injection(AmevaFailureInjectionPoint point) { g_fail.store((int)point); }
+AmevaFailureInjectionPoint ggml_backend_ameva_get_failure_injection(void) { return (AmevaFailureInjectionPoint)g_fail.load(); }
+
 }  // extern "C"
+
+namespace {
+struct ProcEntry {
+    const char* name;
+    void* fn;
+};
+void* reg_get_proc_address(ggml_backend_reg_t, const char* name) {
+    static const ProcEntry table[] = {
+        {"ggml_backend_ameva_get_gpu_op_count", (void*)ggml_backend_ameva_get_gpu_op_count},
+        {"ggml_backend_ameva_get_fused_pair_count", (void*)ggml_backend_ameva_get_fused_pair_count},
+        {"ggml_backend_ameva_get_qmv_mul_mat_count", (void*)ggml_backend_ameva_get_qmv_mul_mat_count},
+        {"ggml_backend_ameva_get_mmq_mul_mat_count", (void*)ggml_backend_ameva_get_mmq_mul_mat_count},
+        {"ggml_backend_ameva_get_mmqb_mul_mat_count", (void*)ggml_backend_ameva_get_mmqb_mul_mat_count},
+        {"ggml_backend_ameva_get_repacked_tensor_count", (void*)ggml_backend_ameva_get_repacked_tensor_count},
+        {"ggml_backend_ameva_get_repacked_bytes", (void*)ggml_backend_ameva_get_repacked_bytes},
+        {"ggml_backend_ameva_reset_counters", (void*)ggml_backend_ameva_reset_counters},
+        {"ggml_backend_ameva_set_failure_injection", (void*)ggml_backend_ameva_set_failure_injection},
+        {"ggml_backend_ameva_get_failure_injection", (void*)ggml_backend_ameva_get_failure_injection},
+        {"ggml_backend_ameva_teardown", (void*)ggml_backend_ameva_teardown},
+        {"ggml_backend_ameva_abi_check", (void*)ggml_backend_ameva_abi_check},
+    };
+    if (!name) return nullptr;
+    for (const ProcEntry& e : table)
+        if (strcmp(e.name, name) == 0) return e.fn;
+    return nullptr;
+}
+}  // namespace

@@ -23,16 +23,13 @@ BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_
 Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128}   # payload bytes per block
 S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16}      # scale bytes per block
 FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in shared memory
-FUSED_QUANT_MAX_ELEMS = 64 << 20    # N*K up to which the fused launch is used (larger ones are not launch-bound)
-STREAMED_MAX_ROW_BYTES = 6400        # packed bytes per weight row up to which the streamed GEMV stages whole rows
-STREAMED_MIN_WEIGHT_BYTES = 64 << 20  # one activation row: weight bytes from which the streamed GEMV is the default
 
 
 def mma_gemv_fits(M: int, K: int) -> bool:
     """Q4_K, M <= 8: whether ameva_mmvm_q4_K can hold the M activation rows (plus one row of zeros), their per-block
-    records and its partial sums in 200 KB of shared memory (M = 8: K <= 20480)."""
+    records, its partial sums and two ring stages per warp in 227 KB of shared memory (M = 8: K <= 12800)."""
     rows = M + 1
-    return K % 256 == 0 and rows * (K + 32) + rows * (K // 256) * 20 + 16384 <= 200 * 1024
+    return K % 256 == 0 and rows * (K + 32) + rows * (K // 256) * 20 + 16384 + 16 + 2 * 16 * 2816 <= 227 * 1024
 
 
 GEMV_MAX_M = 8   # decode GEMV serves M <= 8 (ggml-ameva.cpp:3607-3804 sends 2 <= M < 8 to the GEMV family as well)
@@ -45,41 +42,25 @@ Q8K_GGML, Q8K_AMEVA = 0, 1
 EPILOGUE_ADD, EPILOGUE_SWIGLU_GATE, EPILOGUE_SWIGLU_UP = 1, 2, 3
 
 
+def plan(ggml_type: int, M: int, N: int, K: int, flags: int = 0) -> int:
+    """The library's kernel choice for a shape (rt.PATH_*), or rt.PATH_NONE for a shape outside the contract. The policy
+    itself lives in the C library (ac_b200_mul_mat_plan), shared with the ggml plugin."""
+    try:
+        return rt.mul_mat_plan(ggml_type, M, N, K, flags)
+    except rt.AmevaComputeError:
+        return rt.PATH_NONE
+
+
 def streamed_pays(ggml_type: int, M: int, N: int, K: int) -> bool:
-    """Where the streamed GEMV (ameva_mmvs_*) measured faster than the register-staged one on a B200: rows short enough
-    for a ring of whole-row stages (about 6 KB of packed row: the kernel then issues two large bulk copies per stage and
-    keeps ~150 KB per SM in flight) and either a weight matrix large enough to be bandwidth-bound (28672 x 8192 Q4_K,
-    M = 1: 26-28 us against 32-34 us) or several activation rows (11008 x 4096 Q4_K, M = 8: 30.5 against 40.4 us).
-    Small single-row products are launch-bound and stay on the register-staged kernels (4096 x 4096: 6.0 vs 7.5 us);
-    rows longer than the limit would be staged in K segments with two small copies per row, which is slower."""
-    if ggml_type not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K) or K % 256 or not 1 <= M <= GEMV_MAX_M:
-        return False
-    row_bytes = (K // 256) * ((256 if ggml_type == GGML_TYPE_Q8_0 else 128) + 16)
-    if row_bytes > STREAMED_MAX_ROW_BYTES:
-        return False
-    return M >= 4 or N * row_bytes >= STREAMED_MIN_WEIGHT_BYTES
+    """Whether the library's policy sends this decode shape to the streamed GEMV (ameva_mmvs_*)."""
+    return 1 <= M <= GEMV_MAX_M and plan(ggml_type, M, N, K) == rt.PATH_GEMV_STREAMED
 
 
 def weight_exponent(ggml_type: int, blocks: np.ndarray, N: int, K: int) -> int:
-    """w_exp of the tensor-core GEMM: the power of two that brings the largest weight magnitude of the tensor into
-    [1, 2) when the weights are dequantized to fp16 (the GEMM multiplies the block scales by 2^w_exp and its epilogue
-    takes the factor out again). Computed once per tensor at upload from the block scale fields alone, as an upper bound
-    of |w|: Q4_0 8 |d|, Q8_0 127 |d|, Q4_K 945 |d| + 63 |dmin|. Limited to [-14, 15] (2^w_exp is an fp16 number)."""
-    if ggml_type not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K):
-        return 0
-    nblk = N * (K // BLOCK[ggml_type])
-    raw = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(nblk, -1)
-    d = np.abs(np.ascontiguousarray(raw[:, 0:2]).view(np.float16).astype(np.float32))[:, 0]
-    if ggml_type == GGML_TYPE_Q4_K:
-        dmin = np.abs(np.ascontiguousarray(raw[:, 2:4]).view(np.float16).astype(np.float32))[:, 0]
-        bound = d * 945.0 + dmin * 63.0
-    else:
-        bound = d * (8.0 if ggml_type == GGML_TYPE_Q4_0 else 127.0)
-    bound = bound[np.isfinite(bound)]
-    top = float(bound.max()) if bound.size else 0.0
-    if not top > 0.0:
-        return 0
-    return int(min(15, max(-14, -int(np.floor(np.log2(top))))))
+    """The magnitude of a weight tensor as a power of two (2^w_exp brings its largest |w| into [1, 2)), computed once per
+    tensor at upload (ac_b200_weight_exponent). The tensor-core GEMM dequantizes weights to fp16: tensors whose magnitudes
+    fp16 does not hold comfortably (rt.weight_range_extreme) stay on the integer kernels at every M."""
+    return rt.weight_exponent(ggml_type, blocks, N, K)
 
 
 class MulMatUnsupported(Exception):
@@ -117,6 +98,7 @@ class QuantWeight:
                  scale: float = 1.0, w_exp: int = 0) -> None:
         self.ctx, self.type, self.N, self.K, self.buf, self.s_off, self.scale = ctx, ggml_type, N, K, buf, s_off, scale
         self.w_exp = w_exp   # see weight_exponent
+        self.fp16_ok = not rt.weight_range_extreme(w_exp)
 
     @classmethod
     def from_ggml(cls, ctx: rt.Context, ggml_type: int, blocks: np.ndarray, N: int, K: int,
@@ -196,8 +178,9 @@ class MulMat:
             raise MulMatUnsupported(why)
         self.type, self.N, self.K, self.max_m = w.type, self.view.rows, w.K, max_m
         self.round_mode, self.q8k_mode, self.dump = round_mode, q8k_mode, dump_block_sums
-        # exact = keep every M on the dp4a kernels (exact per-block int32 sums); otherwise M > 8 runs on tensor cores
-        self.exact = exact or dump_block_sums
+        # exact = keep every M on the dp4a kernels (exact per-block int32 sums); otherwise M > 8 runs on tensor cores,
+        # unless the weights' magnitudes are outside what their fp16 form holds comfortably
+        self.exact = exact or dump_block_sums or not w.fp16_ok
         # the GEMM stages weights and scales with TMA: whole 128-byte operand rows, whole 16-byte scale groups per row
         self.tc_ok = self.K % (128 if self.type == GGML_TYPE_I2_S else 256) == 0
         self.qbind, self.sbind = _bindings_for(self.view)
@@ -255,7 +238,7 @@ class MulMat:
         # CTA repeats the quantize, so larger projections keep the separate kernel). The scratch AQ/AD stay unwritten.
         if (quantize and M == 1 and self.fused_quantize and t in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K)
                 and not self.dump and self.streamed is not True and not peers and epilogue is None
-                and K <= FUSED_QUANT_MAX_K and N * K <= FUSED_QUANT_MAX_ELEMS and x_offset % 64 == 0
+                and plan(t, 1, N, K, rt.PLAN_HOST_LAUNCH) == rt.PATH_GEMV_FQ and x_offset % 64 == 0
                 and dst_offset % 64 == 0):
             fam = "ameva_mmvqb" if t == GGML_TYPE_Q4_K else "ameva_mmvq"
             mode = self.q8k_mode if t == GGML_TYPE_Q4_K else self.round_mode
@@ -295,13 +278,12 @@ class MulMat:
         if use_tc:
             self.path = "mmtc"
             grid = ((M + 255) // 256, (N + 127) // 128, 1)
-            w_exp = (int(self.view.weight.w_exp) & 0xFFFFFFFF) if t != GGML_TYPE_I2_S else 0
             if peers:
                 self.path = "mmtc+peer-stores"
                 outs = [(dst, dst_offset)] + [(pb, dst_offset) for pb in peers]
                 outs += [(dst, dst_offset)] * (8 - len(outs))
                 batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}_mp"), [self.qbind, self.sbind, self.ah] + outs + [self.ae],
-                               [M, N, K, dst_stride, 0, len(peers), w_exp], grid)
+                               [M, N, K, dst_stride, 0, len(peers)], grid)
                 return
             if t == GGML_TYPE_I2_S:
                 push = [M, N, K, dst_stride, int(np.float32(self.view.weight.scale).view(np.uint32))]
@@ -310,13 +292,13 @@ class MulMat:
             else:
                 batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}"),
                                [self.qbind, self.sbind, self.ah, (dst, dst_offset), self.ae],
-                               [M, N, K, dst_stride, 0, w_exp], grid)
+                               [M, N, K, dst_stride], grid)
             return
         if epilogue is not None and (M != 1 or t == GGML_TYPE_I2_S or self.dump or peers):
             raise MulMatUnsupported("the fused epilogue is built for one activation row of a Q4_0 / Q8_0 / Q4_K product")
-        use_mma = (t == GGML_TYPE_Q4_K and (2 if self.mma is None else 1) <= M <= GEMV_MAX_M and mma_gemv_fits(M, K)
-                   and not self.dump and not peers and epilogue is None and self.mma is not False
-                   and self.streamed is not True)
+        use_mma = (t == GGML_TYPE_Q4_K and 1 <= M <= GEMV_MAX_M and mma_gemv_fits(M, K) and not self.dump and not peers
+                   and epilogue is None and self.streamed is not True
+                   and (self.mma is True or (self.mma is None and plan(t, M, N, K) == rt.PATH_GEMV_MMA)))
         if self.mma is True and not use_mma and not use_tc:
             raise MulMatUnsupported("ameva_mmvm_q4_K serves Q4_K with up to 8 activation rows that fit shared memory")
         if use_mma and not use_tc:

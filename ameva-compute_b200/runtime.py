@@ -132,7 +132,8 @@ EXPORTED_SYMBOLS = [
     "ac_runtime_get_generation_ctx", "ac_runtime_reset_error_state_ctx", "ac_runtime_kernel_create_builtin",
     "ac_b200_kernel_count", "ac_b200_kernel_name", "ac_b200_context_get_stream", "ac_b200_buffer_import",
     "ac_b200_buffer_export_ipc", "ac_b200_buffer_open_ipc", "ac_b200_buffer_write_async", "ac_b200_buffer_read_async", "ac_b200_context_synchronize", "ac_b200_batch_instantiate", "ac_b200_batch_replay",
-    "ac_b200_device_layout", "ac_b200_repack_to_device", "ac_b200_repack_from_device",
+    "ac_b200_device_layout", "ac_b200_repack_to_device", "ac_b200_repack_from_device", "ac_b200_mul_mat_plan",
+    "ac_b200_weight_exponent",
     "ac_b200_mul_mat_q4_0_static",
 ]
 
@@ -216,6 +217,8 @@ def load_library() -> C.CDLL:
         "ac_b200_batch_replay": (C.c_int, [vp, C.POINTER(vp)]),
         "ac_b200_device_layout": (C.c_int, [u32, u64, u64, P(u64), P(u64)]),
         "ac_b200_mul_mat_q4_0_static": (C.c_int, [vp, vp, vp, vp, u32, vp, u32, u32, u32, u32, u32]),
+        "ac_b200_mul_mat_plan": (C.c_int, [u32, u64, u64, u64, u32, P(u32)]),
+        "ac_b200_weight_exponent": (C.c_int, [u32, vp, u64, u64, P(C.c_int32)]),
         "ac_b200_repack_to_device": (C.c_int, [u32, vp, u64, u64, vp]),
         "ac_b200_repack_from_device": (C.c_int, [u32, vp, u64, u64, vp]),
     }
@@ -546,6 +549,30 @@ def device_layout(ggml_type: int, rows: int, k: int) -> Tuple[int, int]:
     total, soff = C.c_uint64(0), C.c_uint64(0)
     _check(load_library().ac_b200_device_layout(ggml_type, rows, k, C.byref(total), C.byref(soff)), "device_layout")
     return total.value, soff.value
+
+
+PATH_NONE, PATH_GEMV, PATH_GEMV_FQ, PATH_GEMV_STREAMED, PATH_GEMV_MMA, PATH_GEMM_TC = range(6)
+PLAN_EXACT, PLAN_HOST_LAUNCH, PLAN_PEERS, PLAN_WEIGHT_RANGE = 1, 2, 4, 8
+
+
+def weight_range_extreme(w_exp: int) -> bool:
+    """AC_B200_WEIGHT_RANGE_EXTREME: the tensor's largest magnitude is below 2^-7 or at least 2^14."""
+    return w_exp > 7 or w_exp < -13
+
+
+def mul_mat_plan(ggml_type: int, M: int, N: int, K: int, flags: int = 0) -> int:
+    """The kernel family the library chooses for this shape (ac_b200_mul_mat_plan); raises for shapes outside the
+    contract."""
+    out = C.c_uint32(0)
+    _check(load_library().ac_b200_mul_mat_plan(ggml_type, M, N, K, flags, C.byref(out)), "mul_mat_plan")
+    return out.value
+
+
+def weight_exponent(ggml_type: int, blocks: np.ndarray, rows: int, k: int) -> int:
+    blocks = np.ascontiguousarray(blocks, dtype=np.uint8)
+    out = C.c_int32(0)
+    _check(load_library().ac_b200_weight_exponent(ggml_type, blocks.ctypes.data, rows, k, C.byref(out)), "weight_exponent")
+    return out.value
 
 
 def repack_to_device(ggml_type: int, blocks: np.ndarray, rows: int, k: int) -> np.ndarray:

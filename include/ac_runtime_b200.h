@@ -349,6 +349,32 @@ AcResult ac_b200_repack_to_device(uint32_t ggml_type, const void* ggml_blocks, u
 AcResult ac_b200_repack_from_device(uint32_t ggml_type, const void* device_layout, uint64_t rows, uint64_t k,
                                     void* ggml_blocks);
 
+/* The kernel family a quantized MUL_MAT of a given shape runs on: the one policy every host of this library follows (what
+ * the reference decides in mul_mat_qmm_reason / ameva_mmq_plan / ameva_qmv_choice, adapters/llama/ggml-ameva/
+ * ggml-ameva.cpp:1326-1377, 2486-2503, 2986). ggml_type as above; M activation rows, N weight rows, K. Shapes outside the
+ * contract answer AC_ERR_INVALID_SHAPE / AC_ERR_FEATURE_NOT_SUPPORTED with *out_path = AC_B200_PATH_NONE: there is no
+ * other implementation to fall to. Pure host function. */
+#define AC_B200_PATH_NONE 0u
+#define AC_B200_PATH_GEMV 1u          /* ameva_mmvq_* / ameva_mmvqb_* / bitnet_gemv_i2_s_*; M > 8 in chunks of 8 rows */
+#define AC_B200_PATH_GEMV_FQ 2u       /* ameva_mmv*_fq: one activation row quantized inside the GEMV launch */
+#define AC_B200_PATH_GEMV_STREAMED 3u /* ameva_mmvs_*: weight rows staged in shared memory by bulk copies */
+#define AC_B200_PATH_GEMV_MMA 4u      /* ameva_mmvm_q4_K: up to 8 rows on the integer tensor instruction */
+#define AC_B200_PATH_GEMM_TC 5u       /* ameva_mmtc_* / bitnet_gemm_i2_s: tcgen05 GEMM */
+#define AC_B200_PLAN_EXACT 1u         /* the caller needs the exact per-block integer sums at every M */
+#define AC_B200_PLAN_HOST_LAUNCH 2u   /* kernels are launched one by one from the host (not replayed batches) */
+#define AC_B200_PLAN_PEERS 4u         /* the kernel also stores to other ranks' outputs */
+#define AC_B200_PLAN_WEIGHT_RANGE 8u  /* AC_B200_WEIGHT_RANGE_EXTREME holds for the weight tensor: integer kernels only */
+AcResult ac_b200_mul_mat_plan(uint32_t ggml_type, uint64_t M, uint64_t N, uint64_t K, uint32_t flags, uint32_t* out_path);
+
+/* The magnitude of a weight tensor given as ggml blocks, as a power of two: 2^w_exp brings an upper bound of its largest
+ * |w| into [1, 2) (-30..30; 0 for I2_S). The tensor-core GEMM dequantizes weights to fp16; a tensor whose largest
+ * magnitude is below 2^-7 or at least 2^14 would lose its small weights to fp16 subnormals or overflow, so hosts compute
+ * this once per tensor at upload and pass AC_B200_PLAN_WEIGHT_RANGE for such tensors (they then run on the integer
+ * kernels at every M, which are scale-invariant). Host function. */
+#define AC_B200_WEIGHT_RANGE_EXTREME(w_exp) ((w_exp) > 7 || (w_exp) < -13)
+AcResult ac_b200_weight_exponent(uint32_t ggml_type, const void* ggml_blocks, uint64_t rows, uint64_t k,
+                                 int32_t* out_w_exp);
+
 /* Decode mul_mat for callers that cannot allocate. No counterpart in the reference.
  * Q4_0 weights (device layout: w_payload 16 bytes and w_scales one fp16 per 32 weights, row-major over [N][K/32]) times
  * fp32 activations x[M][K], quantized per 32 values on the fly, into dst[M][N] (fp32). The scratch for the quantized

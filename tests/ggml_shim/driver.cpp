@@ -1,13 +1,19 @@
 // Test harness for the ggml backend plugin (libggml-ameva-b200.so). It stands in for the host application: a minimal
-// ggml-base (the six functions the plugin calls, restated for the four tensor types of the test) and a driver that walks
+// ggml-base (the functions the plugin calls, restated for the tensor types and ops of the tests) and a driver that walks
 // the plugin's tables the way ggml's loader, allocator and scheduler do. Built against the host's ggml headers; not part
 // of the product.
 //
-//   driver probe                                   registry / device / buffer-type facts, no device needed
+//   driver probe                                   registry / device / buffer-type facts and the ABI self-check, no device
 //   driver mulmat <type> <M> <N> <K> <w.bin> <x.bin> <y.bin>
 //                                                  uploads ggml blocks + f32 activations, runs a one-node MUL_MAT graph,
 //                                                  writes y; also checks weight read-back (whole, partial), a partial
 //                                                  set_tensor, and that a graph with an unsupported node is refused
+//   driver layer <type> <K> <Nq> <Nkv> <Nff> <M2> <dir>
+//                                                  a decoder-layer-shaped graph of one activation row (q / k / v sharing
+//                                                  src1, o + residual ADD, gate / up + SWIGLU, RMS_NORM + MUL, a row-range
+//                                                  view of a weight) followed by a graph with M2 activation rows that
+//                                                  needs larger scratch; counters, host-side failure injection, teardown.
+//                                                  Inputs are read from <dir>, outputs written there.
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -17,6 +23,8 @@
 #include "ggml-backend-impl.h"
 #include "ggml-backend.h"
 #include "ggml.h"
+
+#include "../../include/ggml_ameva_b200.h"
 
 struct ggml_cgraph {
     int n_nodes;
@@ -33,6 +41,11 @@ static void traits(enum ggml_type t, size_t* type_size, int64_t* blck) {
     }
 }
 
+// ---- the stand-in for ggml-base ---------------------------------------------------------------------------------------
+struct ggml_context {
+    std::vector<ggml_tensor*> tensors;
+};
+
 extern "C" {
 size_t ggml_nbytes(const ggml_tensor* t) {
     size_t ts;
@@ -47,7 +60,32 @@ bool ggml_is_contiguous(const ggml_tensor* t) {
     return t->nb[0] == ts && t->nb[1] == ts * (size_t)(t->ne[0] / bs) && t->nb[2] == t->nb[1] * (size_t)t->ne[1] &&
            t->nb[3] == t->nb[2] * (size_t)t->ne[2];
 }
-const char* ggml_op_name(enum ggml_op op) { return op == GGML_OP_MUL_MAT ? "MUL_MAT" : (op == GGML_OP_ADD ? "ADD" : "OP"); }
+bool ggml_is_empty(const ggml_tensor* t) { return t->ne[0] == 0 || t->ne[1] == 0 || t->ne[2] == 0 || t->ne[3] == 0; }
+const char* ggml_op_name(enum ggml_op op) {
+    switch (op) {
+        case GGML_OP_NONE: return "NONE";
+        case GGML_OP_ADD: return "ADD";
+        case GGML_OP_MUL: return "MUL";
+        case GGML_OP_RMS_NORM: return "RMS_NORM";
+        case GGML_OP_MUL_MAT: return "MUL_MAT";
+        case GGML_OP_RESHAPE: return "RESHAPE";
+        case GGML_OP_VIEW: return "VIEW";
+        case GGML_OP_PERMUTE: return "PERMUTE";
+        case GGML_OP_TRANSPOSE: return "TRANSPOSE";
+        case GGML_OP_GLU: return "GLU";
+        case GGML_OP_SUB: return "SUB";
+        default: return "OP";
+    }
+}
+const char* ggml_type_name(enum ggml_type t) {
+    switch (t) {
+        case GGML_TYPE_F32: return "f32";
+        case GGML_TYPE_Q4_0: return "q4_0";
+        case GGML_TYPE_Q8_0: return "q8_0";
+        case GGML_TYPE_Q4_K: return "q4_K";
+        default: return "?";
+    }
+}
 int ggml_graph_n_nodes(ggml_cgraph* g) { return g->n_nodes; }
 ggml_tensor* ggml_graph_node(ggml_cgraph* g, int i) { return g->nodes[i < 0 ? g->n_nodes + i : i]; }
 ggml_backend_buffer_t ggml_backend_buffer_init(ggml_backend_buffer_type_t buft, ggml_backend_buffer_i iface, void* context,
@@ -60,8 +98,46 @@ ggml_backend_buffer_t ggml_backend_buffer_init(ggml_backend_buffer_type_t buft, 
     b->usage = GGML_BACKEND_BUFFER_USAGE_ANY;
     return b;
 }
-ggml_backend_reg_t ggml_backend_init(void);
-int ggml_backend_score(void);
+bool ggml_guid_matches(ggml_guid_t a, ggml_guid_t b) { return memcmp(a, b, sizeof(ggml_guid)) == 0; }
+static ggml_backend_reg_t g_registered = nullptr;
+void ggml_backend_register(ggml_backend_reg_t reg) { g_registered = reg; }
+ggml_backend_dev_t ggml_backend_get_device(ggml_backend_t backend) { return backend->device; }
+size_t ggml_backend_buffer_get_size(ggml_backend_buffer_t buffer) { return buffer->size; }
+ggml_backend_buffer_type_t ggml_backend_buffer_get_type(ggml_backend_buffer_t buffer) { return buffer->buft; }
+ggml_backend_dev_t ggml_backend_buft_get_device(ggml_backend_buffer_type_t buft) { return buft->device; }
+ggml_backend_reg_t ggml_backend_dev_backend_reg(ggml_backend_dev_t device) { return device->reg; }
+size_t ggml_tensor_overhead(void) { return sizeof(ggml_tensor) + 32; }
+ggml_context* ggml_init(ggml_init_params) { return new ggml_context(); }
+void ggml_free(ggml_context* ctx) {
+    if (!ctx) return;
+    for (ggml_tensor* t : ctx->tensors) delete t;
+    delete ctx;
+}
+ggml_tensor* ggml_new_tensor_2d(ggml_context* ctx, enum ggml_type type, int64_t ne0, int64_t ne1) {
+    ggml_tensor* t = new ggml_tensor();
+    memset(t, 0, sizeof(*t));
+    size_t ts;
+    int64_t bs;
+    traits(type, &ts, &bs);
+    t->type = type;
+    t->ne[0] = ne0; t->ne[1] = ne1; t->ne[2] = 1; t->ne[3] = 1;
+    t->nb[0] = ts; t->nb[1] = ts * (size_t)(ne0 / bs); t->nb[2] = t->nb[1] * (size_t)ne1; t->nb[3] = t->nb[2];
+    ctx->tensors.push_back(t);
+    return t;
+}
+ggml_tensor* ggml_mul_mat(ggml_context* ctx, ggml_tensor* a, ggml_tensor* b) {
+    ggml_tensor* c = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, a->ne[1], b->ne[1]);
+    c->op = GGML_OP_MUL_MAT;
+    c->src[0] = a;
+    c->src[1] = b;
+    return c;
+}
+ggml_tensor* ggml_set_name(ggml_tensor* t, const char* name) {
+    strncpy(t->name, name, sizeof(t->name) - 1);
+    t->name[sizeof(t->name) - 1] = 0;
+    return t;
+}
+const char* ggml_get_name(const ggml_tensor* t) { return t->name; }
 }
 
 #define CHECK(c)                                                                   \
@@ -84,9 +160,9 @@ static void shape(ggml_tensor* t, enum ggml_type type, int64_t ne0, int64_t ne1,
     snprintf(t->name, sizeof(t->name), "%s", name);
 }
 
-static std::vector<uint8_t> slurp(const char* path) {
-    FILE* f = fopen(path, "rb");
-    if (!f) { perror(path); exit(2); }
+static std::vector<uint8_t> slurp(const std::string& path) {
+    FILE* f = fopen(path.c_str(), "rb");
+    if (!f) { perror(path.c_str()); exit(2); }
     fseek(f, 0, SEEK_END);
     long n = ftell(f);
     fseek(f, 0, SEEK_SET);
@@ -95,29 +171,41 @@ static std::vector<uint8_t> slurp(const char* path) {
     fclose(f);
     return v;
 }
+static bool dump(const std::string& path, const void* p, size_t n) {
+    FILE* f = fopen(path.c_str(), "wb");
+    if (!f) return false;
+    const bool ok = fwrite(p, 1, n, f) == n;
+    fclose(f);
+    return ok;
+}
 
-int main(int argc, char** argv) {
-    CHECK(argc >= 2);
-    ggml_backend_reg_t reg = ggml_backend_init();
-    CHECK(reg != nullptr);
-    CHECK(reg->api_version == GGML_BACKEND_API_VERSION);
-    CHECK(ggml_backend_score() == 100);
-    CHECK(reg->iface.get_device_count(reg) == 1);
-    ggml_backend_dev_t dev = reg->iface.get_device(reg, 0);
-    CHECK(dev && dev->reg == reg && reg->iface.get_device(reg, 1) == nullptr);
-    ggml_backend_buffer_type_t buft = dev->iface.get_buffer_type(dev);
-    CHECK(buft && buft->device == dev);
-    CHECK(buft->iface.get_alignment(buft) == 64);
-    CHECK(!buft->iface.is_host(buft));
-    CHECK(dev->iface.supports_buft(dev, buft));
-    ggml_backend_buffer_type other{};
-    CHECK(!dev->iface.supports_buft(dev, &other));
-    CHECK(dev->iface.get_type(dev) == GGML_BACKEND_DEVICE_TYPE_GPU);
-    printf("registry %s device %s buffer-type %s\n", reg->iface.get_name(reg), dev->iface.get_name(dev),
-           buft->iface.get_name(buft));
-    if (std::string(argv[1]) == "probe") return 0;
+// what ggml's allocator does: every tensor padded to the buffer type's alignment, one buffer
+struct Arena {
+    ggml_backend_buffer_type_t buft;
+    std::vector<ggml_tensor*> tensors;
+    std::vector<size_t> offsets;
+    size_t total = 0;
+    ggml_backend_buffer_t buf = nullptr;
+    void add(ggml_tensor* t) {
+        tensors.push_back(t);
+        offsets.push_back(total);
+        total += (buft->iface.get_alloc_size(buft, t) + 63) & ~(size_t)63;
+    }
+    bool commit() {
+        buf = buft->iface.alloc_buffer(buft, total);
+        if (!buf) return false;
+        char* base = (char*)buf->iface.get_base(buf);
+        for (size_t i = 0; i < tensors.size(); ++i) {
+            tensors[i]->buffer = buf;
+            tensors[i]->data = base + offsets[i];
+        }
+        buf->iface.clear(buf, 0);
+        return true;
+    }
+};
 
-    CHECK(std::string(argv[1]) == "mulmat" && argc == 9);
+static int run_mulmat(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) {
+    CHECK(argc == 9);
     const enum ggml_type type = (enum ggml_type)atoi(argv[2]);
     const int64_t M = atoll(argv[3]), N = atoll(argv[4]), K = atoll(argv[5]);
     std::vector<uint8_t> wbytes = slurp(argv[6]), xbytes = slurp(argv[7]);
@@ -128,25 +216,22 @@ int main(int argc, char** argv) {
     printf("device: %s\n", props.description);
     ggml_backend_t backend = dev->iface.init_backend(dev, nullptr);
     CHECK(backend && backend->iface.graph_compute && backend->iface.synchronize == nullptr);
+    CHECK(ggml_backend_is_ameva(backend));
 
     ggml_tensor w, x, y, bad;
     shape(&w, type, K, N, "weight");
     shape(&x, GGML_TYPE_F32, K, M, "activations");
     shape(&y, GGML_TYPE_F32, N, M, "result");
-    shape(&bad, GGML_TYPE_F32, N, M, "sum");
+    shape(&bad, GGML_TYPE_F32, N, M, "difference");
     CHECK(wbytes.size() == ggml_nbytes(&w) && xbytes.size() == ggml_nbytes(&x));
     CHECK(buft->iface.get_alloc_size(buft, &w) >= ggml_nbytes(&w));
     CHECK(buft->iface.get_alloc_size(buft, &x) == ggml_nbytes(&x));
-    // what ggml's allocator does: pad every tensor to the alignment, one buffer
-    auto pad = [](size_t v) { return (v + 63) & ~(size_t)63; };
-    const size_t ow = 0, ox = ow + pad(buft->iface.get_alloc_size(buft, &w)), oy = ox + pad(ggml_nbytes(&x)),
-                 total = oy + pad(ggml_nbytes(&y));
-    ggml_backend_buffer_t buf = buft->iface.alloc_buffer(buft, total);
-    CHECK(buf != nullptr);
-    char* base = (char*)buf->iface.get_base(buf);
-    w.buffer = x.buffer = y.buffer = buf;
-    w.data = base + ow; x.data = base + ox; y.data = base + oy;
-    buf->iface.clear(buf, 0);
+    Arena ar{buft};
+    ar.add(&w);
+    ar.add(&x);
+    ar.add(&y);
+    CHECK(ar.commit());
+    ggml_backend_buffer_t buf = ar.buf;
     buf->iface.set_tensor(buf, &w, wbytes.data(), 0, wbytes.size());
     buf->iface.set_tensor(buf, &x, xbytes.data(), 0, xbytes.size());
 
@@ -175,12 +260,10 @@ int main(int argc, char** argv) {
     CHECK(backend->iface.graph_compute(backend, &graph) == GGML_STATUS_SUCCESS);
     std::vector<uint8_t> out(ggml_nbytes(&y));
     buf->iface.get_tensor(buf, &y, out.data(), 0, out.size());
-    FILE* f = fopen(argv[8], "wb");
-    CHECK(f && fwrite(out.data(), 1, out.size(), f) == out.size());
-    fclose(f);
+    CHECK(dump(argv[8], out.data(), out.size()));
 
     // a graph with a node this backend cannot run is refused as a whole: the result buffer stays untouched
-    bad.op = GGML_OP_ADD;
+    bad.op = GGML_OP_SUB;
     bad.src[0] = &y;
     bad.src[1] = &y;
     bad.buffer = buf;
@@ -188,7 +271,9 @@ int main(int argc, char** argv) {
     CHECK(!dev->iface.supports_op(dev, &bad));
     buf->iface.memset_tensor(buf, &y, 0xEE, 0, ggml_nbytes(&y));
     graph.n_nodes = 2;
+    const int64_t ops_before = ggml_backend_ameva_get_gpu_op_count();
     CHECK(backend->iface.graph_compute(backend, &graph) == GGML_STATUS_FAILED);
+    CHECK(ggml_backend_ameva_get_gpu_op_count() == ops_before);
     std::vector<uint8_t> after(ggml_nbytes(&y));
     buf->iface.get_tensor(buf, &y, after.data(), 0, after.size());
     for (uint8_t v : after) CHECK(v == 0xEE);
@@ -196,6 +281,220 @@ int main(int argc, char** argv) {
     buf->iface.free_buffer(buf);
     delete buf;
     backend->iface.free(backend);
+    ggml_backend_ameva_teardown();
+    CHECK(ggml_backend_ameva_get_context_destroy_count() == ggml_backend_ameva_get_context_create_count());
     printf("ok\n");
     return 0;
+}
+
+static ggml_tensor* op2(ggml_tensor* t, enum ggml_op op, ggml_tensor* a, ggml_tensor* b) {
+    t->op = op;
+    t->src[0] = a;
+    t->src[1] = b;
+    return t;
+}
+
+static int run_layer(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) {
+    CHECK(argc == 9);
+    const enum ggml_type type = (enum ggml_type)atoi(argv[2]);
+    const int64_t K = atoll(argv[3]), Nq = atoll(argv[4]), Nkv = atoll(argv[5]), Nff = atoll(argv[6]), M2 = atoll(argv[7]);
+    const std::string dir = argv[8];
+    auto in = [&](const char* n) { return slurp(dir + "/" + n); };
+    auto out = [&](ggml_backend_buffer_t buf, ggml_tensor* t, const char* n) {
+        std::vector<uint8_t> v(ggml_nbytes(t));
+        buf->iface.get_tensor(buf, t, v.data(), 0, v.size());
+        return dump(dir + "/" + n, v.data(), v.size());
+    };
+    ggml_backend_t backend = ggml_backend_ameva_init(0);
+    CHECK(backend && ggml_backend_is_ameva(backend));
+    CHECK(ggml_backend_ameva_init(1) == nullptr);
+    CHECK(ggml_backend_ameva_buffer_type(0) == buft && ggml_backend_ameva_reg() == dev->reg);
+
+    // weights: q (Nq rows), k, v (Nkv rows), o (K rows), gate / up (Nff rows), all over K; activations x (1 x K), a second
+    // activation row `res` (K), the RMS weight row (K), x2 (M2 x K)
+    ggml_tensor wq, wk, wv, wo, wg, wu, x, res, rw, x2;
+    shape(&wq, type, K, Nq, "wq");
+    shape(&wk, type, K, Nkv, "wk");
+    shape(&wv, type, K, Nkv, "wv");
+    shape(&wo, type, K, K, "wo");
+    shape(&wg, type, K, Nff, "w_gate");
+    shape(&wu, type, K, Nff, "w_up");
+    shape(&x, GGML_TYPE_F32, K, 1, "x");
+    shape(&res, GGML_TYPE_F32, K, 1, "residual");
+    shape(&rw, GGML_TYPE_F32, K, 1, "rms_weight");
+    shape(&x2, GGML_TYPE_F32, K, M2, "x2");
+    // results
+    ggml_tensor rn, xn, q, k, v, o, o_res, gate, up, act, wq_rows, qv, y2;
+    shape(&rn, GGML_TYPE_F32, K, 1, "rms_norm");
+    shape(&xn, GGML_TYPE_F32, K, 1, "x_normed");
+    shape(&q, GGML_TYPE_F32, Nq, 1, "q");
+    shape(&k, GGML_TYPE_F32, Nkv, 1, "k");
+    shape(&v, GGML_TYPE_F32, Nkv, 1, "v");
+    shape(&o, GGML_TYPE_F32, K, 1, "o");
+    shape(&o_res, GGML_TYPE_F32, K, 1, "o_plus_residual");
+    shape(&gate, GGML_TYPE_F32, Nff, 1, "gate");
+    shape(&up, GGML_TYPE_F32, Nff, 1, "up");
+    shape(&act, GGML_TYPE_F32, Nff, 1, "swiglu");
+    // rows [Nq / 2, Nq) of wq, as a view (what ggml_view_2d makes): same K, same row pitch, data = base + offset
+    shape(&wq_rows, type, K, Nq - Nq / 2, "wq_rows");
+    shape(&qv, GGML_TYPE_F32, Nq - Nq / 2, 1, "q_of_row_range");
+    shape(&y2, GGML_TYPE_F32, Nq, M2, "y2");
+
+    Arena ar{buft};
+    for (ggml_tensor* t : {&wq, &wk, &wv, &wo, &wg, &wu, &x, &res, &rw, &x2, &rn, &xn, &q, &k, &v, &o, &o_res, &gate, &up, &act, &qv, &y2})
+        ar.add(t);
+    CHECK(ar.commit());
+    ggml_backend_buffer_t buf = ar.buf;
+    wq_rows.view_src = &wq;
+    wq_rows.view_offs = (size_t)(Nq / 2) * wq.nb[1];
+    wq_rows.buffer = buf;
+    wq_rows.data = (char*)wq.data + wq_rows.view_offs;
+    wq_rows.op = GGML_OP_VIEW;
+    wq_rows.src[0] = &wq;
+
+    const int64_t repacked_before = ggml_backend_ameva_get_repacked_tensor_count();
+    struct { ggml_tensor* t; const char* file; } uploads[] = {{&wq, "wq.bin"}, {&wk, "wk.bin"}, {&wv, "wv.bin"}, {&wo, "wo.bin"},
+                                                              {&wg, "wg.bin"}, {&wu, "wu.bin"}, {&x, "x.bin"},   {&res, "res.bin"},
+                                                              {&rw, "rw.bin"}, {&x2, "x2.bin"}};
+    for (auto& u : uploads) {
+        std::vector<uint8_t> bytes = in(u.file);
+        CHECK(bytes.size() == ggml_nbytes(u.t));
+        buf->iface.set_tensor(buf, u.t, bytes.data(), 0, bytes.size());
+    }
+    CHECK(ggml_backend_ameva_get_repacked_tensor_count() == repacked_before + 6);
+    CHECK(ggml_backend_ameva_get_repacked_bytes() > 0);
+    // the view reads back the bytes of its rows
+    {
+        std::vector<uint8_t> all = in("wq.bin"), part(ggml_nbytes(&wq_rows));
+        buf->iface.get_tensor(buf, &wq_rows, part.data(), 0, part.size());
+        CHECK(memcmp(part.data(), all.data() + wq_rows.view_offs, part.size()) == 0);
+    }
+
+    // ---- graph 1: one activation row through a decoder-layer-shaped graph ----
+    op2(&rn, GGML_OP_RMS_NORM, &x, nullptr);
+    const float eps = 1e-5f;
+    memcpy(&rn.op_params[0], &eps, 4);
+    op2(&xn, GGML_OP_MUL, &rn, &rw);
+    op2(&q, GGML_OP_MUL_MAT, &wq, &xn);
+    op2(&k, GGML_OP_MUL_MAT, &wk, &xn);
+    op2(&v, GGML_OP_MUL_MAT, &wv, &xn);
+    op2(&o, GGML_OP_MUL_MAT, &wo, &res);   // another activation row: not part of the q / k / v group
+    op2(&o_res, GGML_OP_ADD, &o, &x);      // its consumer: computed by the same launch
+    op2(&gate, GGML_OP_MUL_MAT, &wg, &xn);
+    op2(&up, GGML_OP_MUL_MAT, &wu, &xn);
+    op2(&act, GGML_OP_GLU, &gate, &up);
+    act.op_params[0] = (int32_t)GGML_GLU_OP_SWIGLU;
+    act.op_params[1] = 0;
+    op2(&qv, GGML_OP_MUL_MAT, &wq_rows, &xn);
+    ggml_tensor* nodes1[] = {&rn, &xn, &q, &k, &v, &o, &o_res, &gate, &up, &act, &wq_rows, &qv};
+    const int n1 = (int)(sizeof(nodes1) / sizeof(nodes1[0]));
+    for (ggml_tensor* t : nodes1) CHECK(dev->iface.supports_op(dev, t));
+    ggml_cgraph g1 = {n1, nodes1};
+    ggml_backend_ameva_reset_counters();
+    CHECK(backend->iface.graph_compute(backend, &g1) == GGML_STATUS_SUCCESS);
+    printf("COUNTER gpu_op %lld\n", (long long)ggml_backend_ameva_get_gpu_op_count());
+    printf("COUNTER mul_mat %lld\n", (long long)ggml_backend_ameva_get_f32_gpu_sgemm_dispatch_count());
+    printf("COUNTER fused_pair %lld\n", (long long)ggml_backend_ameva_get_fused_pair_count());
+    printf("COUNTER qmv %lld\n", (long long)ggml_backend_ameva_get_qmv_mul_mat_count());
+    printf("COUNTER mmq %lld\n", (long long)ggml_backend_ameva_get_mmq_mul_mat_count());
+    printf("COUNTER mmqb %lld\n", (long long)ggml_backend_ameva_get_mmqb_mul_mat_count());
+    CHECK(ggml_backend_ameva_get_gpu_op_count() == 11);   // every node but the view
+    CHECK(ggml_backend_ameva_get_f32_gpu_sgemm_dispatch_count() == 7 && ggml_backend_ameva_get_qmv_mul_mat_count() == 7);
+    CHECK(ggml_backend_ameva_get_q5_0_cpu_dequant_count() == 0);
+    CHECK(out(buf, &xn, "xn.out") && out(buf, &q, "q.out") && out(buf, &k, "k.out") && out(buf, &v, "v.out") &&
+          out(buf, &o_res, "o_res.out") && out(buf, &act, "act.out") && out(buf, &qv, "qv.out") && out(buf, &gate, "gate.out"));
+
+    // ---- graph 2: more activation rows than graph 1 reserved scratch for, and two nodes sharing src1 ----
+    ggml_tensor y2b;
+    shape(&y2b, GGML_TYPE_F32, Nq, M2, "y2_again");
+    y2b.buffer = buf;
+    y2b.data = y2.data;   // the second product overwrites the first: same src1, quantized once
+    op2(&y2, GGML_OP_MUL_MAT, &wq, &x2);
+    op2(&y2b, GGML_OP_MUL_MAT, &wq, &x2);
+    ggml_tensor* nodes2[] = {&y2, &y2b};
+    ggml_cgraph g2 = {2, nodes2};
+    CHECK(backend->iface.graph_compute(backend, &g2) == GGML_STATUS_SUCCESS);
+    CHECK(ggml_backend_ameva_get_gpu_op_count() == 13);
+    CHECK(out(buf, &y2, "y2.out"));
+    // and graph 1 again after the scratch grew
+    CHECK(backend->iface.graph_compute(backend, &g1) == GGML_STATUS_SUCCESS);
+    CHECK(out(buf, &q, "q_again.out"));
+
+    // ---- host-side failure injection: FAILED, and the op counter does not move (tests/test_amuda_ggml_backend.cpp:211-251) ----
+    int gates = 0;
+    for (int point = AMEVA_FAIL_MAP_SRC0; point <= AMEVA_FAIL_TENSOR_RANGE_OOB; ++point) {
+        const int64_t before = ggml_backend_ameva_get_gpu_op_count();
+        ggml_backend_ameva_set_failure_injection((AmevaFailureInjectionPoint)point);
+        CHECK(ggml_backend_ameva_get_failure_injection() == (AmevaFailureInjectionPoint)point);
+        const enum ggml_status st = backend->iface.graph_compute(backend, &g1);
+        const bool ok = st == GGML_STATUS_FAILED && ggml_backend_ameva_get_gpu_op_count() == before;
+        printf("GATE_%02d: %s\n", point, ok ? "PASS" : "FAIL");
+        gates += ok;
+    }
+    ggml_backend_ameva_set_failure_injection(AMEVA_FAIL_NONE);
+    printf("FAILURE_GATES=%d/10\n", gates);
+    CHECK(gates == 10);
+    CHECK(backend->iface.graph_compute(backend, &g1) == GGML_STATUS_SUCCESS);   // and the backend still works
+
+    // ---- registration and teardown ----
+    ggml_backend_ameva_register();
+    CHECK(g_registered == dev->reg);
+    CHECK(dev->reg->iface.get_proc_address(dev->reg, "ggml_backend_ameva_get_gpu_op_count") == (void*)ggml_backend_ameva_get_gpu_op_count);
+    CHECK(dev->reg->iface.get_proc_address(dev->reg, "no_such_function") == nullptr);
+    ggml_backend_ameva_teardown();   // refused while a backend and a buffer are alive
+    CHECK(ggml_backend_ameva_get_context_destroy_count() == 0);
+    buf->iface.free_buffer(buf);
+    delete buf;
+    backend->iface.free(backend);
+    ggml_backend_ameva_teardown();
+    CHECK(ggml_backend_ameva_get_context_destroy_count() == 1 && ggml_backend_ameva_get_context_create_count() == 1);
+    CHECK(ggml_backend_ameva_get_kernel_create_count() == ggml_backend_ameva_get_kernel_destroy_count());
+    printf("ok\n");
+    return 0;
+}
+
+int main(int argc, char** argv) {
+    CHECK(argc >= 2);
+    CHECK(ggml_backend_ameva_abi_check() == nullptr);
+    ggml_backend_reg_t reg = ggml_backend_init();
+    CHECK(reg != nullptr);
+    CHECK(reg->api_version == GGML_BACKEND_API_VERSION);
+    CHECK(ggml_backend_score() == 100);
+    CHECK(reg->iface.get_device_count(reg) == 1);
+    ggml_backend_dev_t dev = reg->iface.get_device(reg, 0);
+    CHECK(dev && dev->reg == reg && reg->iface.get_device(reg, 1) == nullptr);
+    ggml_backend_buffer_type_t buft = dev->iface.get_buffer_type(dev);
+    CHECK(buft && buft->device == dev);
+    CHECK(buft->iface.get_alignment(buft) == 64);
+    CHECK(!buft->iface.is_host(buft));
+    CHECK(dev->iface.supports_buft(dev, buft));
+    ggml_backend_buffer_type other{};
+    CHECK(!dev->iface.supports_buft(dev, &other));
+    CHECK(dev->iface.get_type(dev) == GGML_BACKEND_DEVICE_TYPE_GPU);
+    printf("registry %s device %s buffer-type %s\n", reg->iface.get_name(reg), dev->iface.get_name(dev),
+           buft->iface.get_name(buft));
+    if (std::string(argv[1]) == "probe") {
+        // what the scheduler asks at planning time, without a device: types and shapes only
+        ggml_tensor w, x, y, a, b, c;
+        shape(&w, GGML_TYPE_Q4_K, 512, 64, "w");
+        shape(&x, GGML_TYPE_F32, 512, 3, "x");
+        shape(&y, GGML_TYPE_F32, 64, 3, "y");
+        op2(&y, GGML_OP_MUL_MAT, &w, &x);
+        CHECK(dev->iface.supports_op(dev, &y));
+        shape(&a, GGML_TYPE_F32, 64, 3, "a");
+        shape(&b, GGML_TYPE_F32, 64, 1, "b");
+        shape(&c, GGML_TYPE_F32, 64, 3, "c");
+        op2(&c, GGML_OP_ADD, &a, &b);
+        CHECK(dev->iface.supports_op(dev, &c));
+        c.op = GGML_OP_SUB;
+        CHECK(!dev->iface.supports_op(dev, &c));
+        CHECK(ggml_backend_ameva_get_supports_query_count() == 3 && ggml_backend_ameva_get_supported_op_count() == 2);
+        CHECK(ggml_backend_ameva_get_context_create_count() == 0);   // nothing above touched the device
+        printf("build %s\n", ggml_backend_ameva_get_build_commit());
+        return 0;
+    }
+    if (std::string(argv[1]) == "mulmat") return run_mulmat(argc, argv, dev, buft);
+    if (std::string(argv[1]) == "layer") return run_layer(argc, argv, dev, buft);
+    fprintf(stderr, "driver: unknown mode %s\n", argv[1]);
+    return 2;
 }

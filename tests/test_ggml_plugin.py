@@ -44,3 +44,61 @@ def test_mul_mat_graph_through_the_plugin(t, M, N, K):
         y = np.fromfile(yp, np.float32).reshape(M, N)
     want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
     assert max_normalised_error(y, want) <= 1e-3
+
+
+def _silu(v):
+    return v / (1.0 + np.exp(-v.astype(np.float64)))
+
+
+@needs_plugin
+@pytest.mark.gpu
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
+def test_decoder_layer_graph_counters_failure_injection_and_teardown(t):
+    """A decoder-layer-shaped graph of one activation row through the plugin: RMS_NORM + MUL as one kernel, q / k / v as
+    one launch (they share src1), o with its residual ADD fused, gate / up as one launch, the split SWIGLU, a MUL_MAT on a
+    row-range view of a weight; then a graph with more activation rows (larger scratch, two nodes sharing src1) and the
+    first graph again. Every output is checked against the CPU oracle; the plugin's counters say what ran (5 nodes
+    computed by the launch of an earlier node); the ten host-side failure-injection points each fail the graph without
+    moving the op counter; teardown destroys the runtime context once nothing owns objects any more."""
+    K, Nq, Nkv, Nff, M2 = 1024, 512, 128, 768, 33
+    rng = np.random.default_rng(5)
+    ws = {n: make_weights(t, N, K, s)[0] for n, N, s in (("wq", Nq, 1), ("wk", Nkv, 2), ("wv", Nkv, 3), ("wo", K, 4),
+                                                         ("wg", Nff, 5), ("wu", Nff, 6))}
+    x = make_acts(1, K, 7)
+    res = make_acts(1, K, 8)
+    rw = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    x2 = make_acts(M2, K, 9)
+    with tempfile.TemporaryDirectory() as d:
+        for n, b in ws.items():
+            np.asarray(b, np.uint8).tofile(os.path.join(d, n + ".bin"))
+        for n, a in (("x", x), ("res", res), ("rw", rw), ("x2", x2)):
+            a.tofile(os.path.join(d, n + ".bin"))
+        r = subprocess.run([DRIVER, "layer", str(t), str(K), str(Nq), str(Nkv), str(Nff), str(M2), d], capture_output=True,
+                           text=True)
+        assert r.returncode == 0, r.stdout + r.stderr
+        assert r.stdout.strip().endswith("ok") and "FAILURE_GATES=10/10" in r.stdout
+        counters = dict(l.split()[1:3] for l in r.stdout.splitlines() if l.startswith("COUNTER"))
+        got = {n: np.fromfile(os.path.join(d, n + ".out"), np.float32) for n in
+               ("xn", "q", "k", "v", "o_res", "act", "qv", "gate", "y2", "q_again")}
+    assert counters["gpu_op"] == "11" and counters["mul_mat"] == "7" and counters["fused_pair"] == "5"
+    assert counters["mmq"] == "7" and counters["mmqb"] == ("7" if t == Q4_K else "0")
+    # expected values: fp64 RMS norm as ggml's CPU backend accumulates it, then the quantized products of the oracle
+    x64 = x[0].astype(np.float64)
+    xn = ((x64 / np.sqrt(np.mean(x64 * x64) + 1e-5)).astype(np.float32) * rw).astype(np.float32)
+    assert np.max(np.abs(got["xn"] - xn)) <= 2e-6 * np.max(np.abs(xn))
+    xin = got["xn"].reshape(1, K)      # the products are checked on the activations the device produced
+
+    def mm(name, N, acts):
+        y, _, _ = oracle_mul_mat(t, ws[name], 1.0, acts, N, K, want_sums=False)
+        return y
+
+    for name, wname, N in (("q", "wq", Nq), ("k", "wk", Nkv), ("v", "wv", Nkv), ("gate", "wg", Nff)):
+        assert max_normalised_error(got[name].reshape(1, N), mm(wname, N, xin)) <= 1e-3, name
+    assert np.array_equal(got["qv"], got["q"][Nq // 2:]), "the row-range view computes the same rows"
+    assert np.array_equal(got["q_again"], got["q"]), "the same graph after the scratch grew"
+    o = mm("wo", K, res)
+    assert max_normalised_error(got["o_res"].reshape(1, K), o + x) <= 1e-3
+    up = mm("wu", Nff, xin)
+    act = (_silu(got["gate"]) * up[0]).astype(np.float32)
+    assert max_normalised_error(got["act"].reshape(1, Nff), act.reshape(1, Nff)) <= 1e-3
+    assert max_normalised_error(got["y2"].reshape(M2, Nq), mm("wq", Nq, x2)) <= 1e-3
