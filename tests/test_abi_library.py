@@ -147,24 +147,48 @@ def test_registry_names():
     for want in ("ameva_quant_a8", "ameva_quant_a8b", "bitnet_norm_q8", "ameva_mmvq_q4_0", "ameva_mmvq_q8_0",
                  "ameva_mmvqb_q4_K", "bitnet_gemv_i2_s_l32w1", "bitnet_gemv_i2_s_l16w2_acc", "ameva_mmvs_q4_K",
                  "ameva_mmvq_q4_0_fq", "ameva_mmvq_q8_0_fq", "ameva_mmvqb_q4_K_fq", "ameva_read_probe",
-                 "ameva_peer_barrier", "ameva_mmtc_q8_0", "ameva_mmtc_q4_K_mp"):
+                 "ameva_peer_barrier", "ameva_mmtc_q8_0", "ameva_mmtc_q4_K_mp", "ameva_mmvm_q4_K", "ameva_mmvqgb_q4_K_fq",
+                 "ameva_peer_push_barrier", "ameva_peer_copy", "ameva_peer_join", "ameva_add_f32", "ameva_rms_norm_f32"):
         assert want in names
     assert len(names) == len(set(names))
 
 
-def test_decode_kernel_choice_policy():
-    """Which M <= 8 products go to the kernel that stages whole weight rows in shared memory (host logic only)."""
+def test_kernel_choice_policy():
+    """The one kernel-choice policy of the library (ac_b200_mul_mat_plan, shared by the Python mirror and the ggml plugin):
+    which family a shape runs on, which flags change it, what is outside the contract (host logic only)."""
     q = pkg.qmm
     Q4_0, Q8_0, Q4_K, I2_S = q.GGML_TYPE_Q4_0, q.GGML_TYPE_Q8_0, q.GGML_TYPE_Q4_K, q.GGML_TYPE_I2_S
-    assert q.streamed_pays(Q4_K, 1, 28672, 8192)          # 132 MB of weights, 4.6 KB rows
-    assert not q.streamed_pays(Q4_K, 1, 8192, 28672)      # 16 KB rows do not fit whole-row stages
-    assert not q.streamed_pays(Q4_K, 1, 4096, 4096)       # small single-row product: launch-bound
-    assert not q.streamed_pays(Q4_K, 3, 11008, 4096)
-    assert q.streamed_pays(Q4_K, 4, 11008, 4096) and q.streamed_pays(Q4_K, 8, 64, 256)
-    assert q.streamed_pays(Q8_0, 8, 11008, 4096) and not q.streamed_pays(Q8_0, 8, 4096, 8192)   # 8.7 KB rows
-    assert q.streamed_pays(Q4_0, 1, 32768, 8192) and not q.streamed_pays(Q4_0, 1, 32768, 8192 + 32)   # K % 256
-    assert not q.streamed_pays(I2_S, 8, 6912, 2560)
-    assert not q.streamed_pays(Q4_K, 9, 11008, 4096) and not q.streamed_pays(Q4_K, 0, 11008, 4096)
+    GEMV, FQ, STREAMED, MMA, TC = rt.PATH_GEMV, rt.PATH_GEMV_FQ, rt.PATH_GEMV_STREAMED, rt.PATH_GEMV_MMA, rt.PATH_GEMM_TC
+    table = [
+        (Q4_K, 1, 28672, 8192, 0, STREAMED),          # 132 MB of weights, 4.6 KB rows: whole-row stages
+        (Q4_K, 1, 8192, 28672, 0, GEMV),              # 16 KB rows do not fit whole-row stages
+        (Q4_K, 1, 4096, 4096, 0, GEMV),               # small single-row product: launch-bound
+        (Q4_K, 1, 4096, 4096, rt.PLAN_HOST_LAUNCH, FQ),   # ... launched from the host: quantize inside the GEMV launch
+        (Q4_K, 3, 11008, 4096, 0, MMA), (Q4_K, 8, 11008, 4096, 0, MMA), (Q4_K, 2, 64, 256, 0, MMA),
+        (Q4_K, 8, 64, 28672, 0, GEMV),                # 8 rows of this K do not fit the tensor-instruction kernel
+        (Q8_0, 8, 11008, 4096, 0, STREAMED), (Q8_0, 8, 4096, 8192, 0, GEMV),   # 8.7 KB rows
+        (Q4_0, 1, 32768, 8192, 0, STREAMED), (Q4_0, 1, 32768, 8192 + 32, 0, GEMV),   # K % 256
+        (Q4_0, 4, 130, 2048, 0, STREAMED),
+        (I2_S, 8, 6912, 2560, 0, GEMV), (I2_S, 128, 6912, 2560, 0, TC),
+        (Q8_0, 512, 11008, 4096, 0, TC), (Q4_K, 9, 11008, 4096, 0, TC),
+        (Q8_0, 512, 11008, 4096, rt.PLAN_EXACT, GEMV),            # exact per-block sums: chunks of 8 rows on dp4a
+        (Q8_0, 512, 11008, 4096, rt.PLAN_WEIGHT_RANGE, GEMV),     # weights fp16 does not hold: integer kernels
+        (Q4_0, 33, 96, 96, 0, GEMV),                              # K the GEMM cannot take
+        (Q4_K, 4, 11008, 4096, rt.PLAN_PEERS, STREAMED), (Q8_0, 512, 11008, 4096, rt.PLAN_PEERS, TC),
+    ]
+    for t, M, N, K, flags, want in table:
+        assert q.plan(t, M, N, K, flags) == want, (t, M, N, K, flags)
+    assert q.streamed_pays(Q4_K, 1, 28672, 8192) and not q.streamed_pays(Q4_K, 1, 4096, 4096)
+    # outside the contract: an explicit error, never another implementation
+    for t, M, N, K, flags, code in ((Q4_K, 0, 16, 256, 0, rt.AC_ERR_INVALID_SHAPE), (Q4_K, 1, 16, 384, 0, rt.AC_ERR_INVALID_SHAPE),
+                                    (14, 1, 16, 256, 0, rt.AC_ERR_FEATURE_NOT_SUPPORTED),
+                                    (I2_S, 4, 640, 2560, rt.PLAN_PEERS, rt.AC_ERR_FEATURE_NOT_SUPPORTED),
+                                    (Q4_K, 1, 16, 256, 64, rt.AC_ERR_INVALID_ARGUMENT)):
+        with pytest.raises(rt.AmevaComputeError) as e:
+            rt.mul_mat_plan(t, M, N, K, flags)
+        assert e.value.code == code
+        assert q.plan(t, M, N, K, flags) == rt.PATH_NONE
+    assert rt.weight_range_extreme(8) and rt.weight_range_extreme(-14) and not rt.weight_range_extreme(4)
 
 
 @pytest.mark.parametrize("ggml_type,quant", [(2, oracle.quantize_q4_0), (8, oracle.quantize_q8_0),
