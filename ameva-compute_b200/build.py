@@ -6,6 +6,8 @@ Outputs (git-ignored, next to this file):
     libac_runtime_b200.so   the ac_runtime C ABI + every built-in kernel (and the link libac_runtime.so.2 to it, the
                             file name hosts built against the reference's runtime load)
     libamuda_b200.so        the legacy amuda host API + ac_ops_bitnet_gemv_i2_s_exact
+    libac_b200_measure.so   measurement aids that are not runtime kernels (the read-only probe bench.py times); adds
+                            them to the runtime's kernel table on request (ac_b200_measure_register)
     libggml-ameva-b200.so   the ggml backend plugin, only where ggml's headers are available (GGML_INCLUDE_DIR, or the
                             headers vendored by a checkout of the reference); with it the test harness
                             tests/ggml_shim/_build/driver
@@ -21,9 +23,10 @@ CSRC = os.path.join(HERE, "csrc")
 ROOT = os.path.dirname(HERE)
 LIB = os.path.join(HERE, "libac_runtime_b200.so")
 LEGACY_LIB = os.path.join(HERE, "libamuda_b200.so")
+MEASURE_LIB = os.path.join(HERE, "libac_b200_measure.so")
 
 RUNTIME_SOURCES = ["runtime.cu", "registry.cu", "act_quant.cu", "gemv.cu", "gemv_bulk.cu", "gemv_mma.cu", "elementwise.cu", "gemm_tc.cu", "noalloc.cu",
-                   "peer_sync.cu", "read_probe.cu"]
+                   "peer_sync.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr",
@@ -83,6 +86,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0 or verbose:
             sys.stderr.write(f"--- nvcc amuda_shim.cu ---\n{r.stdout}\n")
+        if r.returncode != 0:
+            raise RuntimeError("nvcc failed")
+    probe = os.path.join(CSRC, "measure", "read_probe.cu")
+    if force or _stale(MEASURE_LIB, [probe, LIB] + headers):
+        cmd = [_nvcc()] + NVCC_FLAGS + ["-shared", probe, "-o", MEASURE_LIB, "-L", HERE, "-lac_runtime_b200",
+                                        "-Xlinker", "-rpath=$ORIGIN"]
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0 or verbose:
+            sys.stderr.write(f"--- nvcc measure/read_probe.cu ---\n{r.stdout}\n")
         if r.returncode != 0:
             raise RuntimeError("nvcc failed")
     return LIB

@@ -49,12 +49,14 @@ struct KernelEntry {
     uint32_t binding_count;
     uint32_t push_bytes;
     AcDim3 local_size;
-    LaunchFn launch;
+    LaunchFn launch;               // built-in kernels
+    AcB200LaunchFn ext = nullptr;  // kernels added by ac_b200_kernel_register (launch is null)
 };
 
 const KernelEntry* find_kernel(const char* name);
 uint32_t kernel_count();
 const KernelEntry* kernel_at(uint32_t i);
+AcResult register_kernel(const char* name, uint32_t binding_count, uint32_t push_bytes, AcB200LaunchFn fn);
 
 inline AcResult check_launch() {
     return cudaGetLastError() == cudaSuccess ? AC_SUCCESS : AC_ERR_INVALID_WORK_GROUP_SIZE;

@@ -57,6 +57,7 @@ constexpr uint32_t kTmemCols = 512;  // 256 accumulator columns + 8 x 32 operand
 constexpr int kScaleSlots = 3;
 constexpr uint32_t kEpilogueBytes = kDequantWarps * 2048u;   // one 32 x 16 fp32 staging buffer per epilogue warp
 constexpr uint32_t kScaleBytes = kRows * 16;        // 2 KB: 16 bytes of scales per row per 256 weights
+constexpr uint32_t kUnscaleBytes = kDequantWarps * 256u;   // per epilogue warp: the row factors of its (up to) 64 tokens
 constexpr uint32_t kSmemLimit = 227 * 1024;
 
 enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_I2_S = 36 };
@@ -458,7 +459,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     uint8_t* sOut = sB + S * b_bytes;                                 // 16 x 2 KB epilogue staging
     uint8_t* sRaw = sOut + kEpilogueBytes;                            // kRawSlots x 16 KB
     uint8_t* sSc = sRaw + C::kRawSlots * C::kRawBytes;                // kScaleSlots x 2 KB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sSc + kScaleSlots * kScaleBytes);
+    uint8_t* sUn = sSc + kScaleSlots * kScaleBytes;                   // kDequantWarps x 256 B row factors
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sUn + kUnscaleBytes);
     // full[s]: the four arrivals of the dequant group that wrote TMEM stage s (of each CTA of a pair) + the activation
     // TMA's arrival and bytes for shared-memory stage s; empty[s]: one tcgen05.commit when the MMAs that read stage s
     // have finished (delivered to both CTAs of a pair); accum: the MMAs of a segment have finished; acc_empty: the
@@ -649,6 +651,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         const uint32_t eq = q4, cq = g;   // epilogue: TMEM lane quarter, column-chunk phase
         const uint32_t full_remote = (PAIR && rank != 0u) ? map_to_cta(full, 0u) : 0u;
         float* stage_out = reinterpret_cast<float*>(sOut) + warp * 512u;
+        float* my_unscale = reinterpret_cast<float*>(sUn) + warp * 64u;
         bool ok = true;
         Ring sa(S), rr(C::kRawSlots), sr(kScaleSlots);
         long long w_sc = 0, w_raw = 0, w_empty = 0, w_accum = 0;
@@ -705,6 +708,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         auto epilogue = [&](const Seg& sg, uint32_t nseg) {
             ok = ok && mbar_wait(accum, nseg & 1u, ctl, status, 0x500u, dg ? &w_accum : nullptr) && !ctl->abort;
             if (threadIdx.x == 0) trace(p, 520);
+            if (!INT8) asm volatile("cp.async.wait_all;" ::: "memory");   // the row factors requested by fetch_unscale
             __syncwarp();
             ok = __all_sync(0xffffffffu, ok);
             constexpr uint32_t kPieces = kTokMax / 16 / kDequantGroups;   // at most four pieces per warp
@@ -757,10 +761,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 for (uint32_t i = 0; i < 2u; ++i) {
                     const uint32_t c = cq + (i0 + i) * kDequantGroups;
                     if (ok && c * 16u < T) {
-                        // lane j holds the factor of the piece's token row j (scaled types): one load per piece, handed
-                        // round by shuffles in the loop below
-                        float unscale = 1.0f;
-                        if (!INT8) unscale = __ldg(p.row_unscale + min(m0 + c * 16u + (lane & 15u), p.M - 1u));
+                        // the factors of the piece's 16 token rows (scaled types): the same for every lane, fetched into
+                        // shared memory while the segment's K blocks were converted
+                        float un[16];
+                        if (!INT8) {
+#pragma unroll
+                            for (uint32_t j4 = 0; j4 < 4; ++j4) {
+                                const float4 f = *reinterpret_cast<const float4*>(my_unscale + (i0 + i) * 16u + 4u * j4);
+                                un[4 * j4] = f.x, un[4 * j4 + 1] = f.y, un[4 * j4 + 2] = f.z, un[4 * j4 + 3] = f.w;
+                            }
+                        }
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j) {
                             const uint32_t m = m0 + c * 16u + j;
@@ -770,7 +780,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                                     __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
                                 y = __fmul_rn((float)(int)v[i][j], total_scale);
                             } else {   // undo the power-of-two factor of the token row's fp16 operand (exact)
-                                y = __uint_as_float(v[i][j]) * __shfl_sync(0xffffffffu, unscale, j);
+                                y = __uint_as_float(v[i][j]) * un[j];
                             }
                             if (p.tma_store)
                                 stage_out[j * 32u + lane] = y;
@@ -838,6 +848,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
             if (threadIdx.x == 0) trace(p, 521);
         };
 
+        // The row factors the epilogue of segment sg multiplies back in: piece i of this warp covers token rows
+        // m0 + 16 (cq + 4 i) .. + 15. Asynchronous 4-byte copies into the warp's own 256 bytes (two per lane), requested
+        // when the segment becomes the current one and waited for at its epilogue, so their latency is never on the path
+        // between the last MMA and the stores. Rows past M read row M - 1 (their outputs are clipped).
+        auto fetch_unscale = [&](const Seg& sg) {
+            if (INT8) return;
+            const uint32_t m0 = (sg.tile / p.row_units) * T;
+#pragma unroll
+            for (uint32_t h = 0; h < 2u; ++h) {
+                const uint32_t e = lane + 32u * h, m = m0 + (cq + (e >> 4) * kDequantGroups) * 16u + (e & 15u);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(my_unscale + e)),
+                             "l"(p.row_unscale + min(m, p.M - 1u)) : "memory");
+            }
+        };
+
         // Segments in order. Before the epilogue of a segment the warps run ahead into the next one by up to S K blocks:
         // those land in operand stages that the MMAs of the current segment free, so the waits cannot depend on the
         // epilogue they precede, and the MMA issuer finds work as soon as the accumulator has been read out.
@@ -846,6 +871,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         bool have = next_seg(it, it_end, KB, cur);
         uint32_t kb = have ? cur.kb0 : 0u;
         while (have) {
+            fetch_unscale(cur);
             for (; kb < cur.kb1 && ok; ++kb) dequant_step(cur, kb);
             const bool have_next = next_seg(it, it_end, KB, nxt);
             uint32_t kb_next = have_next ? nxt.kb0 : 0u;
@@ -1020,7 +1046,7 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     p.row_units = (N + unit_rows - 1) / unit_rows;
     const uint32_t KB = K / C::kBlockK;
     const int sm_count = a.sm_count > 0 ? a.sm_count : 148;
-    const uint32_t fixed = 1024u + kEpilogueBytes + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + 512u;
+    const uint32_t fixed = 1024u + kEpilogueBytes + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + kUnscaleBytes + 512u;
 
     // K ranges cut across tiles ("stream" launch, all units resident at once) need the TMA path for the partial sums, a
     // K that is whole scale groups, exact integer results left alone (I2_S scales per token after the sum) and flag

@@ -9,6 +9,8 @@
 // documented at each launcher.
 #include <cmath>
 #include <cstring>
+#include <mutex>
+#include <string>
 
 #include "common.cuh"
 
@@ -39,7 +41,6 @@ AcResult launch_peer_barrier(const LaunchArgs&);
 AcResult launch_peer_push_barrier(const LaunchArgs&);
 AcResult launch_peer_copy(const LaunchArgs&);
 AcResult launch_peer_join(const LaunchArgs&);
-AcResult launch_read_probe(const LaunchArgs&);
 AcResult launch_mmvq_q4_0(const LaunchArgs&);
 AcResult launch_mmvq_q4_0_dump(const LaunchArgs&);
 AcResult launch_mmvq_q8_0(const LaunchArgs&);
@@ -84,7 +85,6 @@ static const KernelEntry kTable[] = {
     {"ameva_peer_push_barrier", 16, 28, {256, 1, 1}, launch_peer_push_barrier},
     {"ameva_peer_copy", 8, 16, {1, 1, 1}, launch_peer_copy},
     {"ameva_peer_join", 1, 0, {1, 1, 1}, launch_peer_join},
-    {"ameva_read_probe", 2, 8, {256, 1, 1}, launch_read_probe},
     {"ameva_mmvq_q4_0", 5, 16, {256, 1, 1}, launch_mmvq_q4_0},
     {"ameva_mmvq_q4_0_dump", 6, 16, {256, 1, 1}, launch_mmvq_q4_0_dump},
     {"ameva_mmvq_q8_0", 5, 16, {256, 1, 1}, launch_mmvq_q8_0},
@@ -108,13 +108,44 @@ static const KernelEntry kTable[] = {
     {"bitnet_gemv_i2_s_l8w4_acc", 4, 24, {8, 16, 1}, launch_bitnet_gemv_i2_s_acc},
 };
 
-uint32_t kernel_count() { return (uint32_t)(sizeof(kTable) / sizeof(kTable[0])); }
-const KernelEntry* kernel_at(uint32_t i) { return i < kernel_count() ? &kTable[i] : nullptr; }
+// Kernels added at run time by ac_b200_kernel_register (measurement aids, a host's own kernels). The entries live for
+// the life of the process at fixed addresses (kernels keep a pointer to theirs), so the table is a fixed array.
+static constexpr uint32_t kBuiltin = (uint32_t)(sizeof(kTable) / sizeof(kTable[0]));
+static constexpr uint32_t kMaxRegistered = 32;
+static KernelEntry g_registered[kMaxRegistered];
+static std::string g_registered_name[kMaxRegistered];
+static uint32_t g_registered_count = 0;
+static std::mutex g_registered_mutex;
+
+static uint32_t registered_count() {
+    std::lock_guard<std::mutex> lock(g_registered_mutex);
+    return g_registered_count;
+}
+
+uint32_t kernel_count() { return kBuiltin + registered_count(); }
+const KernelEntry* kernel_at(uint32_t i) {
+    if (i < kBuiltin) return &kTable[i];
+    return i - kBuiltin < registered_count() ? &g_registered[i - kBuiltin] : nullptr;
+}
 const KernelEntry* find_kernel(const char* name) {
     if (!name) return nullptr;
-    for (uint32_t i = 0; i < kernel_count(); ++i)
-        if (strcmp(kTable[i].name, name) == 0) return &kTable[i];
+    for (uint32_t i = 0, n = kernel_count(); i < n; ++i)
+        if (strcmp(kernel_at(i)->name, name) == 0) return kernel_at(i);
     return nullptr;
+}
+
+AcResult register_kernel(const char* name, uint32_t binding_count, uint32_t push_bytes, AcB200LaunchFn fn) {
+    if (!name || !fn) return AC_ERR_NULL_POINTER;
+    if (!name[0] || strlen(name) > 63u || binding_count == 0 || binding_count > 16u || push_bytes > 128u || (push_bytes & 3u))
+        return AC_ERR_INVALID_ARGUMENT;
+    if (find_kernel(name)) return AC_ERR_RESOURCE_IN_USE;   // names are unique, built-in ones included
+    std::lock_guard<std::mutex> lock(g_registered_mutex);
+    if (g_registered_count == kMaxRegistered) return AC_ERR_OUT_OF_HOST_MEMORY;
+    const uint32_t i = g_registered_count;
+    g_registered_name[i] = name;
+    g_registered[i] = KernelEntry{g_registered_name[i].c_str(), binding_count, push_bytes, {1, 1, 1}, nullptr, fn};
+    g_registered_count = i + 1;
+    return AC_SUCCESS;
 }
 
 }  // namespace amv

@@ -171,6 +171,18 @@ AcResult wait_cuda_event(AcContext* ctx, cudaEvent_t ev, uint64_t timeout_ns) {
 
 AcResult launch_record(AcContext* ctx, const KernelEntry* e, uint32_t nbind, void* const* ptrs, const uint64_t* ranges,
                        const uint32_t* push, AcDim3 grid) {
+    if (!e->launch) {   // a registered kernel: the public form of the same arguments
+        AcB200Launch l;
+        l.stream = ctx->stream;
+        l.binding_count = nbind;
+        l.ptr = ptrs;
+        l.range = ranges;
+        l.push = push;
+        l.push_bytes = e->push_bytes;
+        l.sm_count = ctx->prop.multiProcessorCount;
+        l.grid = grid;
+        return e->ext(&l);
+    }
     LaunchArgs a;
     memset(&a, 0, sizeof(a));
     a.stream = ctx->stream;
@@ -760,6 +772,9 @@ AcResult ac_runtime_kernel_get_push_constant_size(const AcKernel* kernel, size_t
 }
 
 uint32_t ac_b200_kernel_count(void) { return kernel_count(); }
+AcResult ac_b200_kernel_register(const char* name, uint32_t binding_count, uint32_t push_constant_size, AcB200LaunchFn fn) {
+    return register_kernel(name, binding_count, push_constant_size, fn);
+}
 const char* ac_b200_kernel_name(uint32_t index) {
     const KernelEntry* e = kernel_at(index);
     return e ? e->name : nullptr;

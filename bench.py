@@ -32,6 +32,7 @@ torch.distributed.run rank 0 alone runs it, with all host threads.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import importlib
 import json
 import os
@@ -283,6 +284,12 @@ class Env:
         self.pkg = importlib.import_module("ameva-compute_b200")
         self.rt, self.qmm, self.shard = self.pkg.runtime, self.pkg.qmm, self.pkg.shard
         self.ctx = self.rt.init()
+        # the read-only probe is a measurement aid, not a runtime kernel: its own library adds it to the kernel table
+        self.rt.load_library()
+        measure = ctypes.CDLL(os.path.join(os.path.dirname(self.rt.LIB_PATH), "libac_b200_measure.so"), mode=ctypes.RTLD_GLOBAL)
+        rc = measure.ac_b200_measure_register()
+        if rc != 0:
+            raise RuntimeError(f"ac_b200_measure_register failed with {rc}")
         self.stream = torch.cuda.ExternalStream(self.ctx.stream, device=torch.device("cuda", self.local_rank))
 
     def barrier(self):
@@ -390,7 +397,7 @@ class Measurement:
         if quantize == "read-probe":   # a plain read of each step's weight region instead of the step
             for i in range(n):
                 for w in self.weights[(first + i) % self.pool_n]:
-                    batch.dispatch(ctx.kernel("ameva_read_probe"), [w.buf, self.probe_sink], [0, 0], (1, 1, 1))
+                    batch.dispatch(ctx.kernel("measure_read_probe"), [w.buf, self.probe_sink], [0, 0], (1, 1, 1))
             return
         for i in range(n):
             mm = self.mms[(first + i) % self.pool_n]

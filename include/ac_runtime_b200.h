@@ -311,6 +311,25 @@ AcResult ac_runtime_kernel_create_builtin(AcContext* ctx, const char* kernel_nam
 /* Registry enumeration: number of built-in kernels and the name of entry i (NULL when out of range). */
 uint32_t ac_b200_kernel_count(void);
 const char* ac_b200_kernel_name(uint32_t index);
+/* A host's own kernel under a name of its choosing, dispatched like the built-in ones (batches, replay, events). The
+ * reference takes caller kernels as SPIR-V / OpenCL source in AcKernelCreateInfo (ac_runtime.h:560-600); here the caller
+ * brings a compiled launcher. fn runs on the recording thread with the device current, must only enqueue work on
+ * `stream` (it may be in graph capture) and returns AC_SUCCESS or the error the dispatch reports. `ptr[i]` is binding
+ * i's device address with its offset applied, `range[i]` the bytes available there; `push` holds push_bytes / 4 words
+ * (zero-filled past what the dispatch supplied). Names are unique for the life of the process (built-in names
+ * included): AC_ERR_RESOURCE_IN_USE for a duplicate. 1..16 bindings, push_constant_size <= 128 and a multiple of 4. */
+typedef struct AcB200Launch {
+    void* stream; /* cudaStream_t */
+    uint32_t binding_count;
+    void* const* ptr;
+    const uint64_t* range;
+    const uint32_t* push;
+    uint32_t push_bytes;
+    int32_t sm_count;
+    AcDim3 grid; /* as given by the dispatch; the launcher is free to size its own grid */
+} AcB200Launch;
+typedef AcResult (*AcB200LaunchFn)(const AcB200Launch* launch);
+AcResult ac_b200_kernel_register(const char* name, uint32_t binding_count, uint32_t push_constant_size, AcB200LaunchFn fn);
 /* The context's CUDA stream (a cudaStream_t), for callers that time or order their own work against it. */
 AcResult ac_b200_context_get_stream(const AcContext* ctx, void** out_stream);
 /* Wrap device memory owned by the caller (e.g. a framework allocator) as a buffer; destroy does not free it. */

@@ -146,11 +146,34 @@ def test_registry_names():
     names = rt.kernel_names()
     for want in ("ameva_quant_a8", "ameva_quant_a8b", "bitnet_norm_q8", "ameva_mmvq_q4_0", "ameva_mmvq_q8_0",
                  "ameva_mmvqb_q4_K", "bitnet_gemv_i2_s_l32w1", "bitnet_gemv_i2_s_l16w2_acc", "ameva_mmvs_q4_K",
-                 "ameva_mmvq_q4_0_fq", "ameva_mmvq_q8_0_fq", "ameva_mmvqb_q4_K_fq", "ameva_read_probe",
+                 "ameva_mmvq_q4_0_fq", "ameva_mmvq_q8_0_fq", "ameva_mmvqb_q4_K_fq",
                  "ameva_peer_barrier", "ameva_mmtc_q8_0", "ameva_mmtc_q4_K_mp", "ameva_mmvm_q4_K", "ameva_mmvqgb_q4_K_fq",
                  "ameva_peer_push_barrier", "ameva_peer_copy", "ameva_peer_join", "ameva_add_f32", "ameva_rms_norm_f32"):
         assert want in names
     assert len(names) == len(set(names))
+
+
+def test_kernel_registration_hook():
+    """ac_b200_kernel_register (host logic only, nothing is launched): argument checks, unique names, the registered
+    kernel listed after the built-in ones; measurement aids are not built in."""
+    import ctypes as C
+    lib = rt.load_library()
+    assert "ameva_read_probe" not in rt.kernel_names() and "measure_read_probe" not in rt.kernel_names()
+    launcher_t = C.CFUNCTYPE(C.c_int, C.c_void_p)
+    keep = launcher_t(lambda launch: 0)
+    test_kernel_registration_hook.keep = keep          # the table keeps the pointer for the life of the process
+    fn = C.cast(keep, C.c_void_p)
+    before = rt.kernel_names()
+    assert lib.ac_b200_kernel_register(None, 1, 0, fn) == rt.AC_ERR_NULL_POINTER
+    assert lib.ac_b200_kernel_register(b"host_kernel", 1, 0, None) == rt.AC_ERR_NULL_POINTER
+    for name, nb, push in ((b"", 1, 0), (b"k" * 64, 1, 0), (b"host_kernel", 0, 0), (b"host_kernel", 17, 0),
+                           (b"host_kernel", 1, 132), (b"host_kernel", 1, 6)):
+        assert lib.ac_b200_kernel_register(name, nb, push, fn) == rt.AC_ERR_INVALID_ARGUMENT
+    assert lib.ac_b200_kernel_register(b"ameva_quant_a8", 3, 16, fn) == rt.AC_ERR_RESOURCE_IN_USE
+    assert rt.kernel_names() == before
+    assert lib.ac_b200_kernel_register(b"host_kernel", 2, 8, fn) == 0
+    assert lib.ac_b200_kernel_register(b"host_kernel", 2, 8, fn) == rt.AC_ERR_RESOURCE_IN_USE
+    assert rt.kernel_names() == before + ["host_kernel"]
 
 
 def test_kernel_choice_policy():
