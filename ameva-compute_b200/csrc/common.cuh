@@ -90,6 +90,51 @@ inline bool ensure_dynamic_smem(int bytes) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// Timeline build (-DAMV_TRACE=1): thread 0 of the first kTraceCtas CTAs of an instrumented kernel records the global
+// nanosecond timer at up to 16 points of each launch (a ring of 64 launches per CTA), read back with
+// ac_b200_trace_read_<file> (AMV_TRACE_READER: the stamps are kept per translation unit). Off by default: production
+// kernels carry none of it.
+#ifndef AMV_TRACE
+#define AMV_TRACE 0
+#endif
+#if AMV_TRACE
+constexpr uint32_t kTraceCtas = 256, kTraceLaunches = 64, kTraceStamps = 16;
+static __device__ unsigned long long g_trace[kTraceCtas * kTraceLaunches * kTraceStamps];
+static __device__ unsigned int g_trace_count[kTraceCtas];
+__device__ __forceinline__ uint32_t trace_begin(uint32_t cta) {   // thread 0 only; returns the slot of this launch
+    if (cta >= kTraceCtas) return 0xFFFFFFFFu;
+    const uint32_t n = g_trace_count[cta];
+    g_trace_count[cta] = n + 1u;
+    return (cta * kTraceLaunches + (n % kTraceLaunches)) * kTraceStamps;
+}
+__device__ __forceinline__ void trace_stamp(uint32_t slot, uint32_t i) {
+    if (slot == 0xFFFFFFFFu) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_trace[slot + i] = t;
+}
+#define AMV_TRACE_BEGIN(cta) uint32_t amv_trace_slot = 0xFFFFFFFFu; if (threadIdx.x == 0) amv_trace_slot = trace_begin(cta);
+#define AMV_TRACE_STAMP(i) if (threadIdx.x == 0) trace_stamp(amv_trace_slot, i);
+// for kernels whose roles live in different threads: thread 0 publishes the slot in shared memory (after a barrier the
+// kernel already has), any one thread of a role stamps
+#define AMV_TRACE_SHARE(var) if (threadIdx.x == 0) var = amv_trace_slot;
+#define AMV_TRACE_STAMP_AT(var, i) trace_stamp(var, i);
+// copies the stamps ([cta][launch % 64][16] nanosecond timers) and the per-CTA launch counts of this file's kernels out
+#define AMV_TRACE_READER(file)                                                                             \
+    extern "C" int ac_b200_trace_read_##file(unsigned long long* stamps, unsigned int* counts) {            \
+        if (cudaDeviceSynchronize() != cudaSuccess) return -1;                                              \
+        if (cudaMemcpyFromSymbol(stamps, amv::g_trace, sizeof(amv::g_trace)) != cudaSuccess) return -2;     \
+        if (cudaMemcpyFromSymbol(counts, amv::g_trace_count, sizeof(amv::g_trace_count)) != cudaSuccess) return -3; \
+        return 0;                                                                                           \
+    }
+#else
+#define AMV_TRACE_BEGIN(cta)
+#define AMV_TRACE_STAMP(i)
+#define AMV_TRACE_SHARE(var)
+#define AMV_TRACE_STAMP_AT(var, i)
+#define AMV_TRACE_READER(file)
+#endif
+
 // Programmatic dependent launch. The quantize and mul_mat kernels are launched with the attribute (launch_pdl) and begin
 // with pdl_wait, which returns when the preceding grid of the stream has completed and its writes are visible, followed
 // by pdl_trigger, which lets the next kernel of the stream be scheduled once all CTAs of this grid have started. Nothing

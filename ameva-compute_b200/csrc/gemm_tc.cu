@@ -38,6 +38,12 @@
 #ifndef AMV_GEMM_DIAG
 #define AMV_GEMM_DIAG 0
 #endif
+// How the epilogue of the kernel with one accumulator reads the per-row factors: 1 = one broadcast shared-memory load
+// per element (configuration 2: 50.9 us), 0 = four 16-byte loads per piece into registers (54.0 us), 2 = one load per
+// lane and a shuffle per element (53.6 us): the extra live registers of 0 and 2 cost the conversion loop its schedule.
+#ifndef AMV_EPI_VARIANT
+#define AMV_EPI_VARIANT 1
+#endif
 
 namespace amv {
 namespace tc {
@@ -755,7 +761,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     waited = true;
                     if (lane == 0) ok = flag_wait(flag, later, ctl, status, 0x540u);
                     ok = __all_sync(0xffffffffu, ok);
-                    asm volatile("fence.proxy.async;" ::: "memory");
+                    if (p.tma_store)
+                        asm volatile("fence.proxy.async;" ::: "memory");
+                    else
+                        __threadfence();
                 }
 #pragma unroll
                 for (uint32_t i = 0; i < 2u; ++i) {
@@ -763,6 +772,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     if (ok && c * 16u < T) {
                         // the factors of the piece's 16 token rows (scaled types): the same for every lane, fetched into
                         // shared memory while the segment's K blocks were converted
+#if AMV_EPI_VARIANT == 0
                         float un[16];
                         if (!INT8) {
 #pragma unroll
@@ -771,6 +781,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                                 un[4 * j4] = f.x, un[4 * j4 + 1] = f.y, un[4 * j4 + 2] = f.z, un[4 * j4 + 3] = f.w;
                             }
                         }
+#endif
 #pragma unroll
                         for (uint32_t j = 0; j < 16; ++j) {
                             const uint32_t m = m0 + c * 16u + j;
@@ -780,12 +791,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                                     __fmul_rn(__uint_as_float(__ldg(p.act + 2u * min(m, p.M - 1u))), p.w_scale);
                                 y = __fmul_rn((float)(int)v[i][j], total_scale);
                             } else {   // undo the power-of-two factor of the token row's fp16 operand (exact)
+#if AMV_EPI_VARIANT == 0
                                 y = __uint_as_float(v[i][j]) * un[j];
+#elif AMV_EPI_VARIANT == 1
+                                y = __uint_as_float(v[i][j]) * my_unscale[(i0 + i) * 16u + j];
+#else
+                                y = __uint_as_float(v[i][j]) * __shfl_sync(0xffffffffu, my_unscale[(i0 + i) * 16u + (lane & 15u)], j);
+#endif
                             }
-                            if (p.tma_store)
+                            if (p.tma_store) {
                                 stage_out[j * 32u + lane] = y;
-                            else if (m < p.M && out_row < p.N && !(kdiag & 8u))
-                                p.dst[(size_t)m * p.dst_stride + out_row] = y;
+                            } else if (m < p.M && out_row < p.N && !(kdiag & 8u)) {
+                                // the lanes of the warp are 32 consecutive weight rows: one 128-byte line per token
+                                float* out = p.dst + (size_t)m * p.dst_stride + out_row;
+                                if (later)
+                                    atomicAdd(out, y);   // (result unused: a reduction at the memory side, in flag order)
+                                else
+                                    *out = y;
+                            }
                         }
                         if (p.tma_store && !(kdiag & 8u)) {
                             fence_async_smem();
@@ -809,9 +832,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 }
             }
             if (!ok) return;
+            if (split && !p.tma_store) {   // every lane's stores and adds are performed before lane 0 publishes the flag
+                __threadfence();
+                __syncwarp();
+            }
             if (split && lane == 0) {
                 if (sg.kb0 != 0u) {   // hand the tile on to the next lower K range once these writes are done
-                    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+                    if (p.tma_store) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
                     __threadfence();
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(later + 1u) : "memory");
                 } else {
@@ -905,6 +932,386 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     }
 }
 
+// ---- the wide kernel: two accumulators per CTA pair ------------------------------------------------------------------
+// The kernel above converts every weight tile once per 256 tokens, and the conversion (CUDA cores) takes about as long
+// as the MMAs it feeds: the tensor pipe waits half the time. Here a CTA pair works on 2 x T tokens (T <= 256) at once:
+// the accumulator fills the whole tensor memory (columns 0..T-1: tokens m0.., columns 256..256+T-1: tokens m0 + T..), the
+// converted weights go to shared memory instead (a ring of 128 rows x 64 fp16 = one K block, in the 128-byte swizzle the
+// activation stages have), and every converted block feeds eight MMAs instead of four: the conversion work per flop halves.
+//   warp 16     activation TMA: per K block the CTA's halves of both token ranges (2 x T/2 rows x 128 B), ring of 3;
+//   warp 18     packed weights and block scales, as above (ring of 3 raw stages);
+//   warps 0-15  four groups taking K blocks in turn (group g: kb % 4 == g, a K block of MMAs lasts twice as long here, so
+//               a ring of four stages hides a conversion step as the eight stages above do); one weight row per thread,
+//               64 weights = 128 bytes = eight 16-byte shared-memory stores, then a proxy fence and
+//               one arrival per warp on the leader CTA's barrier; after a segment they are the epilogue: tcgen05.ld,
+//               the row factor, and plain stores (a warp writes one 128-byte line per token);
+//   warp 17     of the even CTA issues, per K block, 4 k-steps x 2 accumulators of tcgen05.mma.cta_group::2 with both
+//               operands in shared memory.
+// Scaled types only (Q4_0, Q8_0, Q4_K), CTA pairs only, local output only.
+constexpr int kWideAStages = 4;                       // ring depth >= number of groups (see the kernel above)
+constexpr int kWideBStages = 4;                       // at most; the host takes as many as fit (3 with T = 256)
+constexpr uint32_t kWideABytes = kRows * kRowBytes;   // 16 KB: 128 rows x 64 fp16
+constexpr uint32_t kWideRawSlots = 3;
+constexpr uint32_t kWideUnscaleBytes = kDequantWarps * 512u;   // per epilogue warp: the row factors of its 8 x 16 tokens
+constexpr uint32_t kWideAccCols = 256;                // column of the second accumulator
+
+// Both operands from shared memory, issued by one thread of the even CTA for the pair.
+__device__ __forceinline__ void umma_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(acc)
+        : "memory");
+}
+// Arrival on a barrier of the other CTA that hands over shared memory written by this thread's warp: cluster-scope release.
+__device__ __forceinline__ void mbar_arrive_cluster_release(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap raw_map,
+                    const __grid_constant__ CUtensorMap scale_map, const __grid_constant__ OutMaps out_maps,
+                    const Params p) {
+    using C = Cfg<TYPE>;
+    static_assert(!C::kInt8 && C::kScales, "scaled types only");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* base = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    const uint32_t rank = cluster_ctarank(), unit = blockIdx.x >> 1;
+    const uint32_t T = p.tok_tile, Th = T / 2u, b_bytes = Th * kRowBytes;   // T tokens per accumulator, Th staged per CTA
+    const uint32_t SB = p.b_stages;                                   // activation stages (3 or 4)
+    uint8_t* sB = base;                                               // SB x 2 x Th*128 B
+    uint8_t* sA = sB + SB * 2u * b_bytes;                             // kWideAStages x 16 KB
+    uint8_t* sRaw = sA + kWideAStages * kWideABytes;                  // kWideRawSlots x 16 KB
+    uint8_t* sSc = sRaw + kWideRawSlots * C::kRawBytes;               // kScaleSlots x 2 KB
+    uint8_t* sUn = sSc + kScaleSlots * kScaleBytes;                   // 16 x 512 B row factors
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sUn + kWideUnscaleBytes);
+    // a_full[s]: the arrivals of the group that wrote weight stage s in both CTAs; a_empty[s] / b_empty[s]: one
+    // tcgen05.commit (to both CTAs) when the MMAs that read the stage have finished; b_full[s]: the activation bytes of
+    // both CTAs; accum / acc_empty as above.
+    const uint32_t a_full = smem_u32(bars), a_empty = a_full + 8u * 4u, b_full = a_empty + 8u * 4u, b_empty = b_full + 8u * 4u,
+                   raw_full = b_empty + 8u * 4u, raw_empty = raw_full + 8u * 4u, sc_full = raw_empty + 8u * 4u,
+                   sc_empty = sc_full + 8u * 4u, accum = sc_empty + 8u * 4u, acc_empty = accum + 8u;
+    Ctl* ctl = reinterpret_cast<Ctl*>(bars + 32 + kDequantWarps);
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t KB = p.K / C::kBlockK;
+    {   // the carve-up must fit the dynamic shared memory of this launch (the same in every CTA: uniform exit)
+        uint32_t dyn;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        const uint32_t need = (uint32_t)(reinterpret_cast<uint8_t*>(ctl + 1) - smem_raw);
+        if (need > dyn || T > (uint32_t)kTokMax || (T & 31u) || T == 0u || SB < 2u || SB > (uint32_t)kWideBStages) {
+            if (threadIdx.x == 0 && atomicCAS(p.status, DEV_STATUS_OK, DEV_STATUS_BAD_INDEX) == DEV_STATUS_OK)
+                p.status[1] = 0xA10u | (need > dyn ? 1u : 2u);
+            return;
+        }
+    }
+    const uint32_t it_begin = unit * p.iters, it_end = min(it_begin + p.iters, p.tiles * KB);
+    uint32_t* status = p.status;
+    AMV_TRACE_BEGIN(blockIdx.x)
+    AMV_TRACE_STAMP(0)
+    AMV_TRACE_SHARE(ctl->trace_slot)
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < 4u; ++s) {
+            mbar_init(a_full + 8u * s, kGroupWarps * 2u);
+            mbar_init(a_empty + 8u * s, 1u);
+            mbar_init(b_full + 8u * s, 1u);
+            mbar_init(b_empty + 8u * s, 1u);
+            mbar_init(raw_full + 8u * s, 1u);
+            mbar_init(raw_empty + 8u * s, kGroupWarps * C::kGroup);        // every K block of the stage, per warp
+            mbar_init(sc_full + 8u * s, 1u);
+            mbar_init(sc_empty + 8u * s, kDequantWarps);                   // the 4 K blocks of a scale group
+        }
+        mbar_init(accum, 1u);
+        mbar_init(acc_empty, kDequantWarps * 2u);
+        ctl->abort = 0u;
+        fence_barrier_init();
+    }
+    if (warp == kWarpMma) tmem_alloc<true>(smem_u32(&ctl->tmem_base), kTmemCols);
+    tc_fence_before();
+    cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem = ctl->tmem_base;
+    pdl_wait();
+    pdl_trigger();
+    AMV_TRACE_STAMP(1)
+
+    auto rot_of = [&](uint32_t tile) -> uint32_t { return (KB & 3u) ? 0u : 4u * ((tile * 5u) % (KB >> 2)); };
+
+    if (warp == kWarpAct) {
+        if (lane == 0) {
+            Ring st(SB);
+            Seg sg;
+            uint32_t it = it_begin, issued = 0;
+            bool ok = true;
+            while (ok && next_seg(it, it_end, KB, sg)) {
+                const uint32_t m0 = (sg.tile / p.row_units) * 2u * T, rot = rot_of(sg.tile);
+                for (uint32_t kb = sg.kb0; kb < sg.kb1; ++kb, st.advance()) {
+                    ok = mbar_wait(b_empty + 8u * st.idx, st.phase ^ 1u, ctl, status, 0x110u | st.idx);
+                    if (!ok) break;
+                    const uint32_t kbr = kb + rot < KB ? kb + rot : kb + rot - KB;
+                    const uint32_t bar = map_to_cta(b_full + 8u * st.idx, 0u);
+                    if (rank == 0u) mbar_arrive_expect_tx(b_full + 8u * st.idx, 4u * b_bytes);
+                    uint8_t* dst = sB + st.idx * 2u * b_bytes;
+                    tma_load_2d_pair(smem_u32(dst), &act_map, bar, (int)(kbr * C::kBlockK), (int)(m0 + rank * Th));
+                    tma_load_2d_pair(smem_u32(dst + b_bytes), &act_map, bar, (int)(kbr * C::kBlockK),
+                                     (int)(m0 + T + rank * Th));
+                    ++issued;
+                }
+            }
+            if (ctl->abort && rank == 0u) {   // let the copies already requested land before leaving
+                for (uint32_t i = issued > SB ? issued - SB : 0; i < issued; ++i)
+                    mbar_wait(b_full + 8u * (i % SB), (i / SB) & 1u, ctl, status, 0x190u);
+            }
+        }
+    } else if (warp == kWarpRaw) {
+        if (lane == 0) {
+            Ring rr(kWideRawSlots), sr(kScaleSlots);
+            Seg sg;
+            uint32_t it = it_begin, groups = 0;
+            bool ok = true;
+            while (ok && next_seg(it, it_end, KB, sg)) {
+                const uint32_t n0 = ((sg.tile % p.row_units) * 2u + rank) * kRows, rot = rot_of(sg.tile);
+                for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb) {
+                    const uint32_t kbr = kb + rot < KB ? kb + rot : kb + rot - KB;
+                    if ((kb & 3u) == 0u) {
+                        ok = mbar_wait(sc_empty + 8u * sr.idx, sr.phase ^ 1u, ctl, status, 0x610u | sr.idx);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(sc_full + 8u * sr.idx, kScaleBytes);
+                        tma_load_2d(smem_u32(sSc + sr.idx * kScaleBytes), &scale_map, sc_full + 8u * sr.idx,
+                                    (int)((kbr >> 2) * 16u), (int)n0);
+                        sr.advance();
+                    }
+                    if ((kb & (C::kGroup - 1u)) == 0u) {
+                        ok = mbar_wait(raw_empty + 8u * rr.idx, rr.phase ^ 1u, ctl, status, 0x710u | rr.idx);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(raw_full + 8u * rr.idx, C::kRawBytes);
+                        tma_load_2d(smem_u32(sRaw + rr.idx * C::kRawBytes), &raw_map, raw_full + 8u * rr.idx,
+                                    (int)((kbr / C::kGroup) * 128u), (int)n0);
+                        ++groups;
+                        rr.advance();
+                    }
+                }
+            }
+            if (ctl->abort) {
+                for (uint32_t i = groups > kWideRawSlots ? groups - kWideRawSlots : 0; i < groups; ++i)
+                    mbar_wait(raw_full + 8u * (i % kWideRawSlots), (i / kWideRawSlots) & 1u, ctl, status, 0x790u);
+            }
+        }
+    } else if (warp == kWarpMma) {
+        if (lane == 0 && rank == 0u) {
+            const uint32_t idesc = make_idesc(1u, 0u, T, 2u * kRows);
+            Ring sa(kWideAStages), sb(SB);
+            Seg sg;
+            uint32_t it = it_begin, nseg = 0;
+            bool ok = true;
+            while (ok && next_seg(it, it_end, KB, sg)) {
+                if (nseg) ok = mbar_wait<false>(acc_empty, (nseg - 1u) & 1u, ctl, status, 0x290u);
+                for (uint32_t kb = sg.kb0; kb < sg.kb1 && ok; ++kb, sb.advance()) {
+                    ok = mbar_wait<false>(b_full + 8u * sb.idx, sb.phase, ctl, status, 0x210u | sb.idx);
+                    if (!ok) break;
+                    const uint64_t db0 = make_smem_desc(smem_u32(sB + sb.idx * 2u * b_bytes));
+                    const uint64_t db1 = make_smem_desc(smem_u32(sB + sb.idx * 2u * b_bytes + b_bytes));
+                    ok = mbar_wait<false>(a_full + 8u * sa.idx, sa.phase, ctl, status, 0x220u | sa.idx);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t da = make_smem_desc(smem_u32(sA + sa.idx * kWideABytes));
+                    if (kb == sg.kb0 && nseg < 2u) { AMV_TRACE_STAMP_AT(ctl->trace_slot, 2u + 5u * nseg) }
+#pragma unroll
+                    for (uint32_t k = 0; k < 4u; ++k) {   // 16 fp16 of K per instruction: 32 bytes = +2 descriptor units
+                        const uint32_t acc = (uint32_t)(kb != sg.kb0 || k != 0u);
+                        umma_ss_pair(tmem, da + 2u * k, db0 + 2u * k, idesc, acc);
+                        umma_ss_pair(tmem + kWideAccCols, da + 2u * k, db1 + 2u * k, idesc, acc);
+                    }
+                    umma_commit<true>(a_empty + 8u * sa.idx);
+                    sa.advance();
+                    umma_commit<true>(b_empty + 8u * sb.idx);
+                }
+                if (!ok) ctl->abort = 1u;
+                umma_commit<true>(accum);
+                if (nseg < 2u) { AMV_TRACE_STAMP_AT(ctl->trace_slot, 3u + 5u * nseg) }
+                ++nseg;
+            }
+        }
+    } else {
+        const uint32_t g = warp >> 2, q4 = warp & 3u, r = q4 * 32u + lane;
+        const uint32_t eq = q4, cq = g;
+        const uint32_t a_full_leader = rank != 0u ? map_to_cta(a_full, 0u) : 0u;
+        float* my_unscale = reinterpret_cast<float*>(sUn) + warp * 128u;
+        bool ok = true;
+        Ring sa(kWideAStages), rr(kWideRawSlots), sr(kScaleSlots);
+        const uint32_t a_row = r * kRowBytes, a_xor = r & 7u;   // this thread's row in a weight stage, its swizzle term
+
+        // One K block of segment sg. Every warp walks all of them (the ring counters advance per block); group g converts
+        // the ones with kb % 4 == g.
+        auto dequant_step = [&](const Seg& sg, uint32_t kb) {
+            const uint32_t raw_last = min((kb | (C::kGroup - 1u)), sg.kb1 - 1u);
+            const uint32_t sc_last = min((kb | 3u), sg.kb1 - 1u);
+            if ((kb & 3u) == g) {
+                ok = mbar_wait(sc_full + 8u * sr.idx, sr.phase, ctl, status, 0x810u | sr.idx);
+                ok = ok && mbar_wait(raw_full + 8u * rr.idx, rr.phase, ctl, status, 0x910u | rr.idx);
+                ok = ok && mbar_wait(a_empty + 8u * sa.idx, sa.phase ^ 1u, ctl, status, 0x410u | sa.idx);
+                if (!ok) return;
+                tc_fence_after();   // the MMAs that read this stage are behind the barrier
+                const uint8_t* raw = sRaw + rr.idx * C::kRawBytes;
+                const uint8_t* sc = sSc + sr.idx * kScaleBytes;
+                uint8_t* arow = sA + sa.idx * kWideABytes + a_row;
+#pragma unroll
+                for (uint32_t h = 0; h < 2u; ++h) {
+                    uint32_t o[16];
+                    dequant_half<TYPE>(raw, sc, r, h, kb, o);
+#pragma unroll
+                    for (uint32_t c = 0; c < 4u; ++c)
+                        *reinterpret_cast<uint4*>(arow + (((4u * h + c) ^ a_xor) << 4)) =
+                            make_uint4(o[4 * c], o[4 * c + 1], o[4 * c + 2], o[4 * c + 3]);
+                }
+                fence_async_smem();   // the tensor core reads the stage through the async proxy
+                __syncwarp();
+                if (lane == 0) {
+                    if (rank != 0u)
+                        mbar_arrive_cluster_release(a_full_leader + 8u * sa.idx);
+                    else
+                        mbar_arrive(a_full + 8u * sa.idx);
+                    mbar_arrive(raw_empty + 8u * rr.idx);
+                    mbar_arrive(sc_empty + 8u * sr.idx);
+                }
+            }
+            sa.advance();
+            if (kb == raw_last) rr.advance();
+            if (kb == sc_last) sr.advance();
+        };
+
+        // Row factors of the segment's tokens for this warp's pieces: piece i (0..7) is accumulator i / 4, 16-column chunk
+        // cq + 4 (i % 4). Four asynchronous 4-byte copies per lane, waited for at the epilogue.
+        auto fetch_unscale = [&](const Seg& sg) {
+            const uint32_t m0 = (sg.tile / p.row_units) * 2u * T;
+#pragma unroll
+            for (uint32_t q = 0; q < 4u; ++q) {
+                const uint32_t e = lane + 32u * q, i = e >> 4;
+                const uint32_t m = m0 + (i >> 2) * T + (cq + (i & 3u) * kDequantGroups) * 16u + (e & 15u);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(my_unscale + e)),
+                             "l"(p.row_unscale + min(m, p.M - 1u)) : "memory");
+            }
+        };
+
+        auto epilogue = [&](const Seg& sg, uint32_t nseg) {
+            ok = ok && mbar_wait(accum, nseg & 1u, ctl, status, 0x510u) && !ctl->abort;
+            if (nseg < 2u) { AMV_TRACE_STAMP(4u + 5u * nseg) }
+            asm volatile("cp.async.wait_all;" ::: "memory");
+            __syncwarp();
+            ok = __all_sync(0xffffffffu, ok);
+            constexpr uint32_t kPieces = 2u * kTokMax / 16 / kDequantGroups;   // eight pieces per warp at most
+            const uint32_t m0 = (sg.tile / p.row_units) * 2u * T;
+            const uint32_t n0 = ((sg.tile % p.row_units) * 2u + rank) * kRows;
+            const uint32_t out_row = n0 + eq * 32u + lane;
+            const bool split = sg.kb1 - sg.kb0 != KB;
+            uint32_t later = 0;
+            uint32_t* flag = nullptr;
+            if (ok && split) {
+                const uint32_t g_end = sg.tile * KB + sg.kb1, t_end = (sg.tile + 1u) * KB;
+                later = sg.kb1 == KB ? 0u : (t_end - 1u) / p.iters - g_end / p.iters + 1u;
+                flag = p.flags + ((sg.tile * 2u + rank) * (uint32_t)kDequantWarps + warp);
+            }
+            bool waited = false, released = false;
+            // piece i: accumulator i / 4, chunk c = cq + 4 (i % 4); it exists when 16 c < T
+            auto chunk_of = [&](uint32_t i) -> uint32_t { return cq + (i & 3u) * kDequantGroups; };
+#pragma unroll
+            for (uint32_t i0 = 0; i0 < kPieces; i0 += 2u) {
+                uint32_t v[2][16];
+                if (ok) {
+                    if (i0 == 0u) tc_fence_after();
+#pragma unroll
+                    for (uint32_t i = 0; i < 2u; ++i)
+                        if (chunk_of(i0 + i) * 16u < T)
+                            tmem_ld16(tmem + ((eq * 32u) << 16) + ((i0 + i) >> 2) * kWideAccCols + chunk_of(i0 + i) * 16u, v[i]);
+                }
+                bool more = false;   // pieces of this warp still in tensor memory
+#pragma unroll
+                for (uint32_t i = i0 + 2u; i < kPieces; ++i) more = more || chunk_of(i) * 16u < T;
+                if (!released && (!ok || !more)) {
+                    released = true;
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (rank != 0u)
+                            mbar_arrive_cluster(map_to_cta(acc_empty, 0u));
+                        else
+                            mbar_arrive(acc_empty);
+                    }
+                }
+                if (ok && later && !waited) {   // the earlier partial sums of the tile are in place
+                    waited = true;
+                    if (lane == 0) ok = flag_wait(flag, later, ctl, status, 0x550u);
+                    ok = __all_sync(0xffffffffu, ok);
+                    __threadfence();
+                    if (nseg < 2u) { AMV_TRACE_STAMP(5u + 5u * nseg) }
+                }
+#pragma unroll
+                for (uint32_t i = 0; i < 2u; ++i) {
+                    const uint32_t c = chunk_of(i0 + i), mp = m0 + ((i0 + i) >> 2) * T + c * 16u;   // first token of the piece
+                    if (ok && c * 16u < T && out_row < p.N) {
+                        float* out = p.dst + (size_t)mp * p.dst_stride + out_row;
+#pragma unroll
+                        for (uint32_t j4 = 0; j4 < 4; ++j4) {
+                            const float4 f = *reinterpret_cast<const float4*>(my_unscale + (i0 + i) * 16u + 4u * j4);
+                            const float un[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+                            for (uint32_t jj = 0; jj < 4; ++jj) {
+                                const uint32_t j = 4u * j4 + jj;
+                                const float y = __uint_as_float(v[i][j]) * un[jj];
+                                if (mp + j < p.M) {
+                                    if (later)
+                                        atomicAdd(out + (size_t)j * p.dst_stride, y);   // (a reduction at the memory side)
+                                    else
+                                        out[(size_t)j * p.dst_stride] = y;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            if (!ok) return;
+            if (split) {   // every lane's stores and adds are performed before lane 0 publishes the flag
+                __threadfence();
+                __syncwarp();
+            }
+            if (split && lane == 0) {
+                if (sg.kb0 != 0u) {
+                    __threadfence();
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(later + 1u) : "memory");
+                } else {
+                    *flag = 0u;
+                }
+            }
+            if (nseg < 2u) { AMV_TRACE_STAMP(6u + 5u * nseg) }
+        };
+
+        Seg cur, nxt;
+        uint32_t it = it_begin, nseg = 0;
+        bool have = next_seg(it, it_end, KB, cur);
+        uint32_t kb = have ? cur.kb0 : 0u;
+        while (have) {
+            fetch_unscale(cur);
+            for (; kb < cur.kb1 && ok; ++kb) dequant_step(cur, kb);
+            const bool have_next = next_seg(it, it_end, KB, nxt);
+            uint32_t kb_next = have_next ? nxt.kb0 : 0u;
+            if (have_next) {   // run ahead by the depth of the weight ring (stages the current segment's MMAs free)
+                const uint32_t ahead = min(nxt.kb1, nxt.kb0 + (uint32_t)kWideAStages);
+                for (; kb_next < ahead && ok; ++kb_next) dequant_step(nxt, kb_next);
+            }
+            epilogue(cur, nseg);
+            ++nseg;
+            cur = nxt;
+            kb = kb_next;
+            have = have_next;
+        }
+    }
+    tc_fence_before();
+    cluster_sync();
+    if (warp == kWarpMma) tmem_dealloc<true>(tmem, kTmemCols);
+    AMV_TRACE_STAMP(12)
+}
+
 // ---- host side ------------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -994,6 +1401,127 @@ static int resident_units(uint32_t smem_bytes, int sm_count) {
     return n;
 }
 
+// Shared memory of the wide kernel: everything but the activation ring, then the ring for T tokens per accumulator.
+template <int TYPE>
+static uint32_t wide_smem_bytes(uint32_t T, uint32_t b_stages) {
+    using C = Cfg<TYPE>;
+    return 1024u + kWideAStages * kWideABytes + kWideRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + kWideUnscaleBytes +
+           512u + b_stages * 2u * (T / 2u) * kRowBytes;
+}
+
+template <int TYPE>
+static int resident_wide_units(uint32_t smem_bytes, int sm_count) {
+    static PerDeviceMemo memo;
+    const int dev = current_device();
+    int n = 0;
+    if (memo.get(dev, smem_bytes, &n)) return n;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * sm_count);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_wide_kernel<TYPE>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    if (n > 0) memo.put(dev, smem_bytes, n);
+    return n;
+}
+
+// The wide kernel's launch: token tiles of up to 512 (two accumulators of T <= 256), 256 weight rows per CTA pair, the
+// same linear (tile, K block) schedule as the kernel above. Arguments were validated by the caller.
+template <int TYPE>
+static AcResult launch_wide(const LaunchArgs& a, EncodeTiledFn enc, const void* Qp, const void* Sp, const void* act,
+                            void* dstp, uint32_t M, uint32_t N, uint32_t K, uint32_t dst_stride, const void* row_unscale,
+                            uint32_t diag) {
+    using C = Cfg<TYPE>;
+    if (!ensure_dynamic_smem<gemm_tc_wide_kernel<TYPE>>((int)kSmemLimit)) return AC_ERR_INVALID_WORK_GROUP_SIZE;
+    Params p;
+    memset(&p, 0, sizeof(p));
+    p.dst = (float*)dstp;
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.dst_stride = dst_stride;
+    p.w_scale = 1.0f;
+    p.row_unscale = (const float*)row_unscale;
+    p.status = a.status;
+    p.flags = a.workspace;
+    p.n_out = 1u;
+    const uint32_t KB = K / C::kBlockK;
+    const int sm_count = a.sm_count > 0 ? a.sm_count : 148;
+    p.row_units = (N + 2u * kRows - 1) / (2u * kRows);
+    const uint32_t j = (M + 2u * kTokMax - 1) / (2u * kTokMax);
+    const uint32_t tile_tok = (((M + j - 1) / j) + 63u) & ~63u;   // tokens per tile: two accumulators of tile_tok / 2
+    p.tok_tile = tile_tok / 2u;
+    p.b_stages = wide_smem_bytes<TYPE>(p.tok_tile, kWideBStages) <= kSmemLimit ? kWideBStages : kWideBStages - 1;
+    p.tiles = p.row_units * ((M + tile_tok - 1) / tile_tok);
+    p.iters = KB;
+    p.units = p.tiles;
+    const uint32_t smem_bytes = wide_smem_bytes<TYPE>(p.tok_tile, p.b_stages);
+    if (smem_bytes > kSmemLimit) return AC_ERR_INVALID_WORK_GROUP_SIZE;
+    const uint64_t total = (uint64_t)p.tiles * KB;
+    const int resident = resident_wide_units<TYPE>(smem_bytes, sm_count);
+    if ((KB & 3u) == 0u && !(diag & 64u) && a.workspace && resident >= 1 && total <= 0x7fffffffull &&
+        (uint64_t)p.tiles * 2u * kDequantWarps * 4u <= a.workspace_bytes) {
+        // K ranges cut across tiles, every unit resident at once (see the schedule of the kernel above)
+        uint32_t iters;
+        if (p.tiles >= (uint32_t)resident) {
+            iters = (uint32_t)(((total + resident - 1) / resident + 3u) & ~3ull);
+        } else {
+            const uint32_t fit = (uint32_t)resident / p.tiles, split = fit < 4u ? fit : 4u;
+            iters = split >= 2u ? (((KB + split - 1) / split + 3u) & ~3u)
+                                : (uint32_t)(((total + resident - 1) / resident + 3u) & ~3ull);
+            if (iters < 8u) iters = KB < 8u ? KB : 8u;
+        }
+        const uint32_t units = (uint32_t)((total + iters - 1) / iters);
+        if (iters == KB || units <= (uint32_t)resident) {
+            p.iters = iters;
+            p.units = units;
+        }
+    }
+    CUtensorMap act_map, raw_map, scale_map;
+    OutMaps out_maps;
+    memset(&out_maps, 0, sizeof(out_maps));
+    const uint64_t row_bytes = (uint64_t)KB * C::kRawRow, srow = (uint64_t)(K >> 8) * 16u;
+    if (!encode_2d(enc, &act_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, act, K, M, (uint64_t)K * 2u, C::kBlockK, p.tok_tile / 2u,
+                   CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_2d(enc, &raw_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Qp, row_bytes, N, row_bytes, 128, kRows,
+                   CU_TENSOR_MAP_SWIZZLE_128B) ||
+        !encode_2d(enc, &scale_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Sp, srow, N, srow, 16, kRows, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return AC_ERR_INVALID_ARGUMENT;
+    for (uint32_t o = 0; o < 8u; ++o) out_maps.m[o] = raw_map;   // (unused: the epilogue stores from registers)
+    const uint64_t ctas = (uint64_t)p.units * 2u;
+    if (ctas > 0x7fffffffull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem_bytes;
+    cfg.stream = a.stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    if (cudaLaunchKernelEx(&cfg, gemm_tc_wide_kernel<TYPE>, act_map, raw_map, scale_map, out_maps, p) != cudaSuccess) {
+        cudaGetLastError();
+        return AC_ERR_INVALID_WORK_GROUP_SIZE;
+    }
+    return check_launch();
+}
+
 template <int TYPE>
 static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, const void* act, uint64_t act_range,
                        void* dstp, uint64_t dst_range, const void* actscale, uint32_t M, uint32_t N, uint32_t K,
@@ -1010,6 +1538,12 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
         return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     EncodeTiledFn enc = encode_fn();
     if (!enc) return AC_ERR_DRIVER_SYMBOL_MISSING;
+    // More than 256 token rows of a scaled type, local output: the kernel with two accumulators per CTA pair, which
+    // converts every weight tile once per 512 tokens (diag bit 7 keeps the launch on the kernel with one accumulator).
+    if constexpr (C::kScales) {
+        if (M > (uint32_t)kTokMax && N > (uint32_t)kRows && n_peers == 0 && !(diag & (128u | 32u | 31u)) && !(diag >> 8))
+            return launch_wide<TYPE>(a, enc, Qp, Sp, act, dstp, M, N, K, dst_stride, row_unscale, diag);
+    }
     if (!ensure_dynamic_smem<gemm_tc_kernel<TYPE, false, false>>((int)kSmemLimit) ||
         !ensure_dynamic_smem<gemm_tc_kernel<TYPE, true, false>>((int)kSmemLimit) ||
         !ensure_dynamic_smem<gemm_tc_kernel<TYPE, false, true>>((int)kSmemLimit) ||
@@ -1027,13 +1561,18 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     p.w_scale = w_scale;
     p.row_unscale = (const float*)row_unscale;
     if (!AMV_GEMM_DIAG && (diag & 31u)) return AC_ERR_FEATURE_NOT_SUPPORTED;   // needs the diagnostic build
-    p.diag = diag & 31u;   // bits 5 (single CTAs) and 6 (one tile per unit) are host-side choices
+    p.diag = diag & 31u;   // bits 5 (single CTAs), 6 (one tile per unit), 7 (one accumulator) are host-side choices
     p.status = a.status;
     p.flags = a.workspace;
-    p.tma_store = ((dst_stride & 3u) == 0u && ((uintptr_t)dstp & 15u) == 0u) ? 1u : 0u;
+    // Output: every 32 x 16 piece goes through a staging buffer and one TMA store (or TMA add, for the partial sums of a
+    // split tile) per destination, which needs 16-byte aligned rows; otherwise plain stores from the epilogue's registers
+    // (a warp writes one 128-byte line per token; partial sums are added at the memory side), which measured slower
+    // (configuration 2: 57.5 against 50.3 us).
+    const bool tma_ok = (dst_stride & 3u) == 0u && ((uintptr_t)dstp & 15u) == 0u;
+    p.tma_store = tma_ok ? 1u : 0u;
     p.n_out = 1u + n_peers;
     if (n_peers) {   // the exchange goes through TMA stores: every destination must qualify
-        if (n_peers > 7u || !p.tma_store) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+        if (n_peers > 7u || !tma_ok) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
         for (uint32_t i = 0; i < n_peers; ++i)
             if (((uintptr_t)peer_dst[i] & 15u) || peer_range[i] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
                 return AC_ERR_INVALID_BUFFER_SIZE;
@@ -1048,11 +1587,10 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     const int sm_count = a.sm_count > 0 ? a.sm_count : 148;
     const uint32_t fixed = 1024u + kEpilogueBytes + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + kUnscaleBytes + 512u;
 
-    // K ranges cut across tiles ("stream" launch, all units resident at once) need the TMA path for the partial sums, a
-    // K that is whole scale groups, exact integer results left alone (I2_S scales per token after the sum) and flag
+    // K ranges cut across tiles ("stream" launch, all units resident at once) need a K that is whole scale groups, exact integer results left alone (I2_S scales per token after the sum) and flag
     // space; with peer destinations the partial sums are combined in the local output and the segment that completes a
     // tile forwards it to the other ranks. Otherwise one tile per unit, as many waves as it takes.
-    bool stream = p.tma_store && !C::kInt8 && (KB & 3u) == 0u && !(diag & 64u) && a.workspace;
+    bool stream = !C::kInt8 && (KB & 3u) == 0u && !(diag & 64u) && a.workspace;
     const uint32_t forced = diag >> 8;   // diagnostic: bits 8.. force the token tile
     // A single CTA stages all the token rows of its tile itself: 128 of them keep the stage ring deep enough.
     const uint32_t tok_max = pair ? (uint32_t)kTokMax : (uint32_t)kTokMax / 2u;
@@ -1212,3 +1750,5 @@ AcResult launch_bitnet_gemm_i2_s(const LaunchArgs& a) {
 }
 
 }  // namespace amv
+
+AMV_TRACE_READER(gemm_tc)

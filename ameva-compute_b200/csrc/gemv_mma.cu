@@ -131,9 +131,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
     };
 
     // the weights do not depend on the kernel before this one: the ring is filled before the wait for it
+    AMV_TRACE_BEGIN(blockIdx.x)
+    AMV_TRACE_STAMP(0)
     for (uint32_t i = 0; i + 1u < depth; ++i) issue(i);
     pdl_trigger();
+    AMV_TRACE_STAMP(1)
     pdl_wait();
+    AMV_TRACE_STAMP(2)
 
     // ---- stage the quantized activations and their per-block records; row M is zeros (tokens M..7 of the instruction) ----
     {
@@ -168,6 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
         }
     }
     __syncthreads();
+    AMV_TRACE_STAMP(3)
 
     // token n of the instruction reads staged row min(n, M): rows past M are the zero row
     const uint32_t tok_b = min(g, p.M), tok0 = min(2u * t, p.M), tok1 = min(2u * t + 1u, p.M);
@@ -179,6 +184,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
 
     uint32_t parity = 0, item = 0;
     for (uint32_t set = set_begin; set < set_end; ++set) {
+        if (set == set_begin + 1u) { AMV_TRACE_STAMP(4) }
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // (row g, token 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
         for (uint32_t b = b_begin; b < b_end; ++b, ++item) {
             // item's copies have landed when at most depth - 2 newer groups are pending
@@ -273,6 +279,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
         parity ^= 1u;
     }
     cp_async_wait<0>();   // (only empty groups can be pending here)
+    AMV_TRACE_STAMP(5)
 }
 
 template <int KS>
@@ -343,3 +350,5 @@ AcResult launch_mmvm_q4_K(const LaunchArgs& a) {
 }
 
 }  // namespace amv
+
+AMV_TRACE_READER(gemv_mma)

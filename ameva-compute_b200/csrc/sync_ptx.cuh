@@ -33,6 +33,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 struct Ctl {             // shared control words
     uint32_t tmem_base;
     volatile uint32_t abort;
+    uint32_t trace_slot;   // timeline build only
 };
 
 // Bounded wait: false when the CTA is aborting (this or another thread ran out of budget). Waiters other than the MMA

@@ -159,8 +159,12 @@ class MulMat:
 
     def __init__(self, ctx: rt.Context, weight, max_m: int, *, round_mode: int = ROUND_NEAREST_EVEN,
                  q8k_mode: int = Q8K_GGML, dump_block_sums: bool = False, exact: bool = False,
-                 streamed: Optional[bool] = None, fused_quantize: bool = False, mma: Optional[bool] = None) -> None:
+                 streamed: Optional[bool] = None, fused_quantize: bool = False, mma: Optional[bool] = None,
+                 gemm_flags: int = 0) -> None:
         self.ctx = ctx
+        # launch switches of the tensor-core GEMM (rt.GEMM_ONE_TILE_PER_UNIT for hosts that share the GPU with other
+        # work, rt.GEMM_ONE_ACCUMULATOR to keep M > 256 on the kernel with one accumulator per CTA pair)
+        self.gemm_flags = gemm_flags
         # M <= 8 over Q4_K: the GEMV on the warp-level integer tensor instruction (ameva_mmvm_q4_K). None = with 2..8
         # activation rows wherever they fit; True also takes a single row; False never.
         self.mma = mma
@@ -283,7 +287,7 @@ class MulMat:
                 outs = [(dst, dst_offset)] + [(pb, dst_offset) for pb in peers]
                 outs += [(dst, dst_offset)] * (8 - len(outs))
                 batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}_mp"), [self.qbind, self.sbind, self.ah] + outs + [self.ae],
-                               [M, N, K, dst_stride, 0, len(peers)], grid)
+                               [M, N, K, dst_stride, self.gemm_flags, len(peers)], grid)
                 return
             if t == GGML_TYPE_I2_S:
                 push = [M, N, K, dst_stride, int(np.float32(self.view.weight.scale).view(np.uint32))]
@@ -292,7 +296,7 @@ class MulMat:
             else:
                 batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}"),
                                [self.qbind, self.sbind, self.ah, (dst, dst_offset), self.ae],
-                               [M, N, K, dst_stride], grid)
+                               [M, N, K, dst_stride, self.gemm_flags], grid)
             return
         if epilogue is not None and (M != 1 or t == GGML_TYPE_I2_S or self.dump or peers):
             raise MulMatUnsupported("the fused epilogue is built for one activation row of a Q4_0 / Q8_0 / Q4_K product")

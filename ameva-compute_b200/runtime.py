@@ -556,6 +556,9 @@ PATH_NONE, PATH_GEMV, PATH_GEMV_FQ, PATH_GEMV_STREAMED, PATH_GEMV_MMA, PATH_GEMM
 PLAN_EXACT, PLAN_HOST_LAUNCH, PLAN_PEERS, PLAN_WEIGHT_RANGE = 1, 2, 4, 8
 
 
+GEMM_ONE_TILE_PER_UNIT, GEMM_ONE_ACCUMULATOR = 64, 128   # AC_B200_GEMM_* launch switches of ameva_mmtc_* (push word 4)
+
+
 def weight_range_extreme(w_exp: int) -> bool:
     """AC_B200_WEIGHT_RANGE_EXTREME: the tensor's largest magnitude is below 2^-7 or at least 2^14."""
     return w_exp > 7 or w_exp < -13

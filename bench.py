@@ -350,7 +350,8 @@ class Measurement:
                 w = qmm.QuantWeight.from_ggml(ctx, t, my_blocks[0], self.rows, K, self.scale)
                 self.weights.append([w])
                 self.mms.append(qmm.MulMat(ctx, w, M, streamed=streamed, mma=mma if t == Q4_K else None,
-                                           fused_quantize=args.fused_quantize and mma is not True))
+                                           fused_quantize=args.fused_quantize and mma is not True,
+                                           gemm_flags=args.gemm_flags))
         self.x_dev = ctx.buffer(data=self.x)
         self.probe_sink = ctx.buffer(64)
         self.launches_per_step = 0
@@ -747,6 +748,8 @@ def main():
                     help="copy exchange, more than 8 token rows: token rows per mul_mat + copy chunk")
     ap.add_argument("--no-replay", action="store_true", help="one host launch per kernel instead of replayed batches")
     ap.add_argument("--no-overlap", action="store_true", help="e2e: copies and compute in sequence on one stream")
+    ap.add_argument("--gemm-flags", type=int, default=0,
+                    help="launch switches of the tensor-core GEMM (64: one tile per unit, 128: one accumulator per CTA pair)")
     ap.add_argument("--gemv", choices=["auto", "register", "streamed", "mma"], default="auto",
                     help="M <= 8: register-staged kernels (ameva_mmvq*), the one that stages the weight rows in shared "
                          "memory (ameva_mmvs_*), or the library's own choice")

@@ -311,6 +311,15 @@ AcResult ac_runtime_kernel_create_builtin(AcContext* ctx, const char* kernel_nam
 /* Registry enumeration: number of built-in kernels and the name of entry i (NULL when out of range). */
 uint32_t ac_b200_kernel_count(void);
 const char* ac_b200_kernel_name(uint32_t index);
+/* Launch switches of the tensor-core GEMM kernels ameva_mmtc_<type>[_mp] and bitnet_gemm_i2_s (their last-but-one /
+ * fifth push word; 0 = the default schedule).
+ *   ONE_TILE_PER_UNIT  every CTA (pair) computes whole output tiles, as many waves as it takes. The default schedule
+ *                      cuts K ranges across tiles and has units wait (bounded, about a second, then
+ *                      AC_ERR_LAUNCH_TIMEOUT) for partial sums of other units of the same launch, which assumes the
+ *                      launch has the whole GPU: a host that shares the device with other contexts or streams sets this.
+ *   ONE_ACCUMULATOR    keep launches of more than 256 token rows on the kernel with one accumulator per CTA pair. */
+#define AC_B200_GEMM_ONE_TILE_PER_UNIT 64u
+#define AC_B200_GEMM_ONE_ACCUMULATOR 128u
 /* A host's own kernel under a name of its choosing, dispatched like the built-in ones (batches, replay, events). The
  * reference takes caller kernels as SPIR-V / OpenCL source in AcKernelCreateInfo (ac_runtime.h:560-600); here the caller
  * brings a compiled launcher. fn runs on the recording thread with the device current, must only enqueue work on

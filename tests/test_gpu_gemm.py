@@ -207,3 +207,33 @@ def test_exact_path_block_sums_at_config2_size(ctx):
     mm_s.destroy()
     w_all.destroy()
     w_sub.destroy()
+
+
+@pytest.mark.parametrize("t", [Q8_0, Q4_0, Q4_K])
+@pytest.mark.parametrize("M,N,K", [(257, 384, 512), (300, 129, 256), (384, 1000, 1024), (512, 256, 2048), (513, 640, 768),
+                                   (700, 2000, 512), (1025, 300, 1024), (448, 5120, 256)])
+def test_gemm_two_accumulators_per_cta_pair(ctx, t, M, N, K):
+    """More than 256 token rows run on the kernel that keeps two accumulators per CTA pair (every weight tile converted
+    once per 512 tokens): ragged M (the second accumulator partly or wholly past M), N that is not whole 256-row units, K
+    of one to thirty-two K blocks, tiles cut across units; against the oracle, and against the kernel with one
+    accumulator (the same fp16 operands and fp32 accumulation, so they agree to summation order)."""
+    if t == Q4_K and K % 256:
+        K = (K // 256 + 1) * 256
+    run_gemm(ctx, t, M, N, K, seed=M + N + 7)
+    blocks, scale = make_weights(t, N, K, 3)
+    x = make_acts(M, K, 4)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    xb = ctx.buffer(data=x)
+    ys = []
+    for flags in (0, rt.GEMM_ONE_ACCUMULATOR, rt.GEMM_ONE_TILE_PER_UNIT):
+        mm = qmm.MulMat(ctx, w, M, gemm_flags=flags)
+        dst = ctx.buffer(M * N * 4)
+        dst.fill(0xFF)
+        mm.run(xb, dst, M)
+        ys.append(dst.read(np.float32).reshape(M, N))
+        dst.destroy()
+        mm.destroy()
+    assert np.isfinite(ys[0]).all()
+    assert max_normalised_error(ys[0], ys[1]) <= 1e-5 and max_normalised_error(ys[0], ys[2]) <= 1e-5
+    xb.destroy()
+    w.destroy()
