@@ -35,6 +35,8 @@ if os.environ.get("AMEVA_GEMM_DIAG") == "1":   # in-kernel diagnostics of the te
     NVCC_FLAGS.append("-DAMV_GEMM_DIAG=1")
 if os.environ.get("AMEVA_EPI_VARIANT"):
     NVCC_FLAGS.append("-DAMV_EPI_VARIANT=" + os.environ["AMEVA_EPI_VARIANT"])
+if os.environ.get("AMEVA_WIDE_EPI"):
+    NVCC_FLAGS.append("-DAMV_WIDE_EPI=" + os.environ["AMEVA_WIDE_EPI"])
 if os.environ.get("AMEVA_TRACE") == "1":       # per-CTA timeline stamps in the instrumented GEMV kernels (ac_b200_trace_read_*)
     NVCC_FLAGS.append("-DAMV_TRACE=1")
 

@@ -44,6 +44,14 @@
 #ifndef AMV_EPI_VARIANT
 #define AMV_EPI_VARIANT 1
 #endif
+// Output path of the kernel with two accumulators: 2 = every 32 x 8 piece transposed through shared memory and sent with
+// one TMA store (TMA add for partial sums); 1 = the same staging, then 16-byte stores (16-byte reductions). Both drain
+// a 128 x 512 accumulator in about 10 us, which is the rate at which an SM writes to memory (about 26 GB/s per SM; the
+// loads from tensor memory take a quarter of a microsecond per warp and pair of pieces); 28672 x 8192, M = 2048 measured
+// 736 us with 2 and 774 us with 1.
+#ifndef AMV_WIDE_EPI
+#define AMV_WIDE_EPI 2
+#endif
 
 namespace amv {
 namespace tc {
@@ -207,6 +215,14 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
         : "r"(taddr)
         : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// 8 consecutive 32-bit columns of this thread's TMEM lane; the caller waits (tcgen05.wait::ld) after its last load.
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 
 // 16 consecutive 32-bit columns of this thread's TMEM lane.
@@ -524,8 +540,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;       // accumulator: columns 0 .. T-1
     const uint32_t tmem_a = tmem + kTokMax;     // weight operand stages: 32 columns each
-    pdl_wait();   // everything above overlapped the tail of the preceding kernel (the activation quantize)
-    pdl_trigger();   // and the kernel behind this one may be scheduled (it waits for this grid before touching memory)
+    // Only the activations (and their row factors) come from the kernel before this one (the activation quantize): the
+    // activation warp and the conversion warps wait for it where they first need them; the packed weights are fetched
+    // and the first stages converted while that kernel is still running.
+    pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching memory)
     if (threadIdx.x == 0) trace(p, 1);
 
     // Every tile walks K from its own starting block (a multiple of 4 blocks = one scale group) and wraps around, so
@@ -535,6 +553,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     if (warp == kWarpAct) {
         // ---- activation TMA: token rows m0 .. m0+T-1 (rows past M read as zero), K block kb ----
         if (lane == 0) {
+            pdl_wait();
             Ring st(S);
             Seg sg;
             uint32_t it = it_begin, issued = 0;
@@ -897,7 +916,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         uint32_t it = it_begin, nseg = 0;
         bool have = next_seg(it, it_end, KB, cur);
         uint32_t kb = have ? cur.kb0 : 0u;
+        bool waited_for_grid = false;
         while (have) {
+            if (!waited_for_grid) {   // fill the operand ring, then wait for the kernel that wrote the row factors
+                const uint32_t pre = min(cur.kb1, kb + S);
+                for (; kb < pre && ok; ++kb) dequant_step(cur, kb);
+                pdl_wait();
+                waited_for_grid = true;
+            }
             fetch_unscale(cur);
             for (; kb < cur.kb1 && ok; ++kb) dequant_step(cur, kb);
             const bool have_next = next_seg(it, it_end, KB, nxt);
@@ -951,8 +977,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
 constexpr int kWideAStages = 4;                       // ring depth >= number of groups (see the kernel above)
 constexpr int kWideBStages = 4;                       // at most; the host takes as many as fit (3 with T = 256)
 constexpr uint32_t kWideABytes = kRows * kRowBytes;   // 16 KB: 128 rows x 64 fp16
-constexpr uint32_t kWideRawSlots = 3;
-constexpr uint32_t kWideUnscaleBytes = kDequantWarps * 512u;   // per epilogue warp: the row factors of its 8 x 16 tokens
+constexpr uint32_t kWideRawSlots = 2;                 // 2 x 4 (Q4) or 2 x 2 (Q8_0) K blocks of packed weights
+constexpr uint32_t kWideEpiBytes = kDequantWarps * 1024u;   // one 32 x 8 fp32 staging buffer per epilogue warp
+constexpr uint32_t kWideUnscaleBytes = kDequantWarps * 512u;   // per epilogue warp: the row factors of its 16 x 8 tokens
 constexpr uint32_t kWideAccCols = 256;                // column of the second accumulator
 
 // Both operands from shared memory, issued by one thread of the even CTA for the pair.
@@ -982,7 +1009,8 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
     const uint32_t SB = p.b_stages;                                   // activation stages (3 or 4)
     uint8_t* sB = base;                                               // SB x 2 x Th*128 B
     uint8_t* sA = sB + SB * 2u * b_bytes;                             // kWideAStages x 16 KB
-    uint8_t* sRaw = sA + kWideAStages * kWideABytes;                  // kWideRawSlots x 16 KB
+    uint8_t* sOut = sA + kWideAStages * kWideABytes;                  // 16 x 1 KB epilogue staging
+    uint8_t* sRaw = sOut + kWideEpiBytes;                             // kWideRawSlots x 16 KB
     uint8_t* sSc = sRaw + kWideRawSlots * C::kRawBytes;               // kScaleSlots x 2 KB
     uint8_t* sUn = sSc + kScaleSlots * kScaleBytes;                   // 16 x 512 B row factors
     uint64_t* bars = reinterpret_cast<uint64_t*>(sUn + kWideUnscaleBytes);
@@ -1032,7 +1060,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
     cluster_sync();
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
-    pdl_wait();
+    // Only the activations (and their row factors) come from the kernel before this one: the activation warp and the
+    // conversion warps wait for it where they first need them; the packed weights are fetched and the first stages
+    // converted while that kernel is still running.
     pdl_trigger();
     AMV_TRACE_STAMP(1)
 
@@ -1040,6 +1070,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
 
     if (warp == kWarpAct) {
         if (lane == 0) {
+            pdl_wait();
             Ring st(SB);
             Seg sg;
             uint32_t it = it_begin, issued = 0;
@@ -1137,6 +1168,7 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
         const uint32_t g = warp >> 2, q4 = warp & 3u, r = q4 * 32u + lane;
         const uint32_t eq = q4, cq = g;
         const uint32_t a_full_leader = rank != 0u ? map_to_cta(a_full, 0u) : 0u;
+        float* stage_out = reinterpret_cast<float*>(sOut) + warp * 256u;
         float* my_unscale = reinterpret_cast<float*>(sUn) + warp * 128u;
         bool ok = true;
         Ring sa(kWideAStages), rr(kWideRawSlots), sr(kScaleSlots);
@@ -1181,14 +1213,14 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
             if (kb == sc_last) sr.advance();
         };
 
-        // Row factors of the segment's tokens for this warp's pieces: piece i (0..7) is accumulator i / 4, 16-column chunk
-        // cq + 4 (i % 4). Four asynchronous 4-byte copies per lane, waited for at the epilogue.
+        // Row factors of the segment's tokens for this warp's pieces: piece i (0..15) is accumulator i / 8, 8-column chunk
+        // cq + 4 (i % 8). Four asynchronous 4-byte copies per lane, waited for at the epilogue.
         auto fetch_unscale = [&](const Seg& sg) {
             const uint32_t m0 = (sg.tile / p.row_units) * 2u * T;
 #pragma unroll
             for (uint32_t q = 0; q < 4u; ++q) {
-                const uint32_t e = lane + 32u * q, i = e >> 4;
-                const uint32_t m = m0 + (i >> 2) * T + (cq + (i & 3u) * kDequantGroups) * 16u + (e & 15u);
+                const uint32_t e = lane + 32u * q, i = e >> 3;
+                const uint32_t m = m0 + (i >> 3) * T + (cq + (i & 7u) * kDequantGroups) * 8u + (e & 7u);
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(my_unscale + e)),
                              "l"(p.row_unscale + min(m, p.M - 1u)) : "memory");
             }
@@ -1200,10 +1232,9 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
             asm volatile("cp.async.wait_all;" ::: "memory");
             __syncwarp();
             ok = __all_sync(0xffffffffu, ok);
-            constexpr uint32_t kPieces = 2u * kTokMax / 16 / kDequantGroups;   // eight pieces per warp at most
+            constexpr uint32_t kPieces = 2u * kTokMax / 8 / kDequantGroups;   // sixteen 32 x 8 pieces per warp at most
             const uint32_t m0 = (sg.tile / p.row_units) * 2u * T;
             const uint32_t n0 = ((sg.tile % p.row_units) * 2u + rank) * kRows;
-            const uint32_t out_row = n0 + eq * 32u + lane;
             const bool split = sg.kb1 - sg.kb0 != KB;
             uint32_t later = 0;
             uint32_t* flag = nullptr;
@@ -1213,21 +1244,23 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
                 flag = p.flags + ((sg.tile * 2u + rank) * (uint32_t)kDequantWarps + warp);
             }
             bool waited = false, released = false;
-            // piece i: accumulator i / 4, chunk c = cq + 4 (i % 4); it exists when 16 c < T
-            auto chunk_of = [&](uint32_t i) -> uint32_t { return cq + (i & 3u) * kDequantGroups; };
+            // piece i: accumulator i / 8, chunk c = cq + 4 (i % 8); it exists when 8 c < T
+            auto chunk_of = [&](uint32_t i) -> uint32_t { return cq + (i & 7u) * kDequantGroups; };
 #pragma unroll
             for (uint32_t i0 = 0; i0 < kPieces; i0 += 2u) {
-                uint32_t v[2][16];
+                uint32_t v[2][8];
                 if (ok) {
                     if (i0 == 0u) tc_fence_after();
 #pragma unroll
                     for (uint32_t i = 0; i < 2u; ++i)
-                        if (chunk_of(i0 + i) * 16u < T)
-                            tmem_ld16(tmem + ((eq * 32u) << 16) + ((i0 + i) >> 2) * kWideAccCols + chunk_of(i0 + i) * 16u, v[i]);
+                        if (chunk_of(i0 + i) * 8u < T)
+                            tmem_ld8(tmem + ((eq * 32u) << 16) + ((i0 + i) >> 3) * kWideAccCols + chunk_of(i0 + i) * 8u, v[i]);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (i0 == 0u && nseg == 0u) { AMV_TRACE_STAMP(13) }
                 }
                 bool more = false;   // pieces of this warp still in tensor memory
 #pragma unroll
-                for (uint32_t i = i0 + 2u; i < kPieces; ++i) more = more || chunk_of(i) * 16u < T;
+                for (uint32_t i = i0 + 2u; i < kPieces; ++i) more = more || chunk_of(i) * 8u < T;
                 if (!released && (!ok || !more)) {
                     released = true;
                     tc_fence_before();
@@ -1238,35 +1271,56 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
                         else
                             mbar_arrive(acc_empty);
                     }
+                    if (nseg == 0u) { AMV_TRACE_STAMP(14) }
                 }
+                if (i0 == 2u && nseg == 0u) { AMV_TRACE_STAMP(15) }
                 if (ok && later && !waited) {   // the earlier partial sums of the tile are in place
                     waited = true;
                     if (lane == 0) ok = flag_wait(flag, later, ctl, status, 0x550u);
                     ok = __all_sync(0xffffffffu, ok);
+#if AMV_WIDE_EPI == 2
+                    asm volatile("fence.proxy.async;" ::: "memory");
+#else
                     __threadfence();
+#endif
                     if (nseg < 2u) { AMV_TRACE_STAMP(5u + 5u * nseg) }
                 }
 #pragma unroll
                 for (uint32_t i = 0; i < 2u; ++i) {
-                    const uint32_t c = chunk_of(i0 + i), mp = m0 + ((i0 + i) >> 2) * T + c * 16u;   // first token of the piece
-                    if (ok && c * 16u < T && out_row < p.N) {
-                        float* out = p.dst + (size_t)mp * p.dst_stride + out_row;
+                    const uint32_t c = chunk_of(i0 + i), mp = m0 + ((i0 + i) >> 3) * T + c * 8u;   // first token of the piece
+                    if (ok && c * 8u < T) {
+                        // transpose through the staging buffer: token j of the piece = 32 consecutive floats (one line)
 #pragma unroll
-                        for (uint32_t j4 = 0; j4 < 4; ++j4) {
-                            const float4 f = *reinterpret_cast<const float4*>(my_unscale + (i0 + i) * 16u + 4u * j4);
-                            const float un[4] = {f.x, f.y, f.z, f.w};
+                        for (uint32_t j = 0; j < 8; ++j)
+                            stage_out[j * 32u + lane] = __uint_as_float(v[i][j]) * my_unscale[(i0 + i) * 8u + j];
+#if AMV_WIDE_EPI == 2
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0 && n0 + eq * 32u < p.N && mp < p.M) {   // clipped at M and N by the tensor map
+                            if (later)
+                                tma_add_2d(&out_maps.m[0], smem_u32(stage_out), (int)(n0 + eq * 32u), (int)mp);
+                            else
+                                tma_store_2d(&out_maps.m[0], smem_u32(stage_out), (int)(n0 + eq * 32u), (int)mp);
+                            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        }
+                        __syncwarp();
+#else
+                        __syncwarp();
+                        // a lane takes 16 bytes of two token rows: eight lanes cover a row's 128 bytes, the warp four rows
 #pragma unroll
-                            for (uint32_t jj = 0; jj < 4; ++jj) {
-                                const uint32_t j = 4u * j4 + jj;
-                                const float y = __uint_as_float(v[i][j]) * un[jj];
-                                if (mp + j < p.M) {
-                                    if (later)
-                                        atomicAdd(out + (size_t)j * p.dst_stride, y);   // (a reduction at the memory side)
-                                    else
-                                        out[(size_t)j * p.dst_stride] = y;
-                                }
+                        for (uint32_t jh = 0; jh < 2u; ++jh) {
+                            const uint32_t j = (lane >> 3) + 4u * jh, n = n0 + eq * 32u + 4u * (lane & 7u);
+                            const float4 val = *reinterpret_cast<const float4*>(stage_out + j * 32u + 4u * (lane & 7u));
+                            if (mp + j < p.M && n < p.N) {   // (N is a multiple of 4 here)
+                                float4* out = reinterpret_cast<float4*>(p.dst + (size_t)(mp + j) * p.dst_stride + n);
+                                if (later)
+                                    atomicAdd(out, val);   // (result unused: a reduction at the memory side, in flag order)
+                                else
+                                    *out = val;
                             }
                         }
+                        __syncwarp();
+#endif
                     }
                 }
             }
@@ -1290,7 +1344,14 @@ gemm_tc_wide_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_co
         uint32_t it = it_begin, nseg = 0;
         bool have = next_seg(it, it_end, KB, cur);
         uint32_t kb = have ? cur.kb0 : 0u;
+        bool waited_for_grid = false;
         while (have) {
+            if (!waited_for_grid) {   // fill the weight ring, then wait for the kernel that wrote the row factors
+                const uint32_t pre = min(cur.kb1, kb + (uint32_t)kWideAStages);
+                for (; kb < pre && ok; ++kb) dequant_step(cur, kb);
+                pdl_wait();
+                waited_for_grid = true;
+            }
             fetch_unscale(cur);
             for (; kb < cur.kb1 && ok; ++kb) dequant_step(cur, kb);
             const bool have_next = next_seg(it, it_end, KB, nxt);
@@ -1405,7 +1466,7 @@ static int resident_units(uint32_t smem_bytes, int sm_count) {
 template <int TYPE>
 static uint32_t wide_smem_bytes(uint32_t T, uint32_t b_stages) {
     using C = Cfg<TYPE>;
-    return 1024u + kWideAStages * kWideABytes + kWideRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + kWideUnscaleBytes +
+    return 1024u + kWideAStages * kWideABytes + kWideEpiBytes + kWideRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + kWideUnscaleBytes +
            512u + b_stages * 2u * (T / 2u) * kRowBytes;
 }
 
@@ -1497,7 +1558,10 @@ static AcResult launch_wide(const LaunchArgs& a, EncodeTiledFn enc, const void* 
                    CU_TENSOR_MAP_SWIZZLE_128B) ||
         !encode_2d(enc, &scale_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Sp, srow, N, srow, 16, kRows, CU_TENSOR_MAP_SWIZZLE_NONE))
         return AC_ERR_INVALID_ARGUMENT;
-    for (uint32_t o = 0; o < 8u; ++o) out_maps.m[o] = raw_map;   // (unused: the epilogue stores from registers)
+    for (uint32_t o = 0; o < 8u; ++o) out_maps.m[o] = raw_map;
+    if (AMV_WIDE_EPI == 2 && !encode_2d(enc, &out_maps.m[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dstp, N, M,
+                                        (uint64_t)dst_stride * 4u, 32, 8, CU_TENSOR_MAP_SWIZZLE_NONE))
+        return AC_ERR_INVALID_ARGUMENT;
     const uint64_t ctas = (uint64_t)p.units * 2u;
     if (ctas > 0x7fffffffull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
     cudaLaunchConfig_t cfg;
@@ -1541,7 +1605,16 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     // More than 256 token rows of a scaled type, local output: the kernel with two accumulators per CTA pair, which
     // converts every weight tile once per 512 tokens (diag bit 7 keeps the launch on the kernel with one accumulator).
     if constexpr (C::kScales) {
-        if (M > (uint32_t)kTokMax && N > (uint32_t)kRows && n_peers == 0 && !(diag & (128u | 32u | 31u)) && !(diag >> 8))
+        // (its epilogue writes 16 bytes at a time: rows of the output 16-byte aligned, N a multiple of 4)
+        // It pays when every CTA pair gets at least two whole 256 x 512 tiles: its accumulators fill the tensor memory,
+        // so the 10 us an SM needs to write a tile out are not overlapped with MMAs, and a tile cut across units is
+        // written twice (28672 x 8192, M = 2048: 736 against 929 us; 11008 x 4096, M = 512, where 43 tiles are cut
+        // across 74 pairs: 52.7 against 48.4 us). diag bit 8 takes it regardless.
+        const uint64_t wide_tiles = (uint64_t)((N + 2u * kRows - 1) / (2u * kRows)) * ((M + 2u * kTokMax - 1) / (2u * kTokMax));
+        const uint64_t pairs = (uint64_t)(a.sm_count > 0 ? a.sm_count : 148) / 2u;
+        if (M > (uint32_t)kTokMax && N > (uint32_t)kRows && n_peers == 0 && !(diag & (128u | 32u | 31u)) && !(diag >> 9) &&
+            (wide_tiles >= 2u * pairs || (diag & 256u)) &&
+            (dst_stride & 3u) == 0u && ((uintptr_t)dstp & 15u) == 0u && (N & 3u) == 0u)
             return launch_wide<TYPE>(a, enc, Qp, Sp, act, dstp, M, N, K, dst_stride, row_unscale, diag);
     }
     if (!ensure_dynamic_smem<gemm_tc_kernel<TYPE, false, false>>((int)kSmemLimit) ||
@@ -1591,7 +1664,7 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     // space; with peer destinations the partial sums are combined in the local output and the segment that completes a
     // tile forwards it to the other ranks. Otherwise one tile per unit, as many waves as it takes.
     bool stream = !C::kInt8 && (KB & 3u) == 0u && !(diag & 64u) && a.workspace;
-    const uint32_t forced = diag >> 8;   // diagnostic: bits 8.. force the token tile
+    const uint32_t forced = diag >> 9;   // diagnostic: bits 9.. force the token tile
     // A single CTA stages all the token rows of its tile itself: 128 of them keep the stage ring deep enough.
     const uint32_t tok_max = pair ? (uint32_t)kTokMax : (uint32_t)kTokMax / 2u;
     int resident = 0;
@@ -1708,7 +1781,7 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
 // dequantized to fp16 as they are: tensors whose magnitudes fp16 does not hold comfortably are kept off this kernel by
 // the host (ac_b200_weight_exponent + AC_B200_PLAN_WEIGHT_RANGE, which selects the exact integer path).
 // diag (0 in production; results are meaningless otherwise) switches one pipeline stage off for profiling:
-// 1 = no weight dequantization, 2 = no activation TMA, 4 = no MMA, 8 = no output stores; bits 8.. force the token tile.
+// 1 = no weight dequantization, 2 = no activation TMA, 4 = no MMA, 8 = no output stores; bits 9.. force the token tile.
 template <int TYPE, uint32_t QB, uint32_t SB, uint32_t BLK>
 static AcResult launch_mmtc(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];

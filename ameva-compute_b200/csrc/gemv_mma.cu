@@ -10,10 +10,13 @@
 //   One persistent CTA of 16 warps per SM. The warps work on 16 / KS groups of 16 weight rows at a time ("a set"), KS
 //   warps splitting the K of a group between them (KS = 16 whenever a row has at least 16 blocks); their partial fp32
 //   sums are added through shared memory at the end of the set. Sets are dealt to the CTAs in equal contiguous shares.
-//   Weights: every warp stages the 256-blocks of its 16 rows in a private shared-memory ring with cp.async (rows 160
-//   bytes apart, so the fragment loads below are free of bank conflicts), several blocks ahead of the one it multiplies
-//   and the first ones before the wait for the preceding kernel: with one block in flight per warp the kernel ran at
-//   the latency of a load per block (11008 x 4096, M = 8: 13 us), not at the bandwidth of the memory.
+//   Weights: every warp stages the 256-blocks of its 16 rows in a private shared-memory ring with cp.async (the 16-byte
+//   pieces of a row XOR-swizzled by the row, so the fragment loads below are free of bank conflicts), several blocks
+//   ahead of the one it multiplies and the first ones before the wait for the preceding kernel: with one block in flight
+//   per warp the kernel ran at the latency of a load per block (11008 x 4096, M = 8: 13 us), not at the bandwidth of the
+//   memory. Where the activations are small (few rows, short K) the CTA has 8 warps and at most half of an SM's shared
+//   memory and registers: the CTAs of the next launch of the stream become resident beside it and fetch their first
+//   blocks while this launch is still computing, instead of starting from an idle memory system when it ends.
 //   Fragments: lane (g, t) (g = lane / 4, t = lane % 4) reads the 8 bytes [8t, 8t + 8) of each 32-byte chunk qs[32k' ..]
 //   of rows g and g + 8. A chunk's low nibbles are sub-block 2k', its high nibbles sub-block 2k' + 1; the lane's first
 //   word fills the k slots 4t..4t+3 of the A fragment, the second the slots 16+4t..: a permutation of k, applied to the
@@ -32,8 +35,7 @@
 namespace amv {
 namespace gm {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = 16;
+constexpr int kMaxWarps = 16;
 constexpr uint32_t kActPad = 32;                 // bytes added to an activation row: rows land 32 bytes apart mod 128
 constexpr uint32_t kSmemLimit = 227u * 1024u;
 
@@ -71,9 +73,10 @@ __device__ __forceinline__ int dp2a_hi(uint32_t a16x2, uint32_t b8x4, int c) {
     return d;
 }
 
-constexpr uint32_t kRowPitch = 160;                       // bytes between the staged rows of a 256-block (128 + 32)
-constexpr uint32_t kStageBytes = 16u * kRowPitch + 16u * 16u;   // 16 rows of payload + 16 scale records = 2816
-constexpr uint32_t kMaxDepth = 6;
+constexpr uint32_t kRowPitch = 128;                       // a staged row of a 256-block: eight 16-byte pieces, piece c at c ^ (row % 8)
+constexpr uint32_t kStageBytes = 16u * kRowPitch + 16u * 16u;   // 16 rows of payload + 16 scale records = 2304
+constexpr uint32_t kMaxDepth = 8;
+constexpr uint32_t kHalfSmem = 113u * 1024u;              // two CTAs of this size share an SM
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
@@ -85,20 +88,21 @@ __device__ __forceinline__ void cp_async_wait() {
 }
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-// One CTA per SM, 16 warps. A "set" is RG = 16 / KS groups of 16 weight rows; the KS warps of a group split its K between
-// them. The sets are dealt to the CTAs in equal contiguous shares (every SM gets within one set of the same work: no
-// partial last wave). A warp's work is a flat sequence of items (set, 256-block of its K share); it keeps a private ring
-// of `depth` staged items in shared memory, filled by cp.async (16 bytes per lane and instruction, no registers held),
-// depth - 1 items ahead of the one being multiplied: the bytes in flight per SM are bounded by shared memory.
-template <int KS>
-__global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params p, const uint32_t depth) {
+// One CTA per SM, WARPS warps. A "set" is RG = WARPS / KS groups of 16 weight rows; the KS warps of a group split its K
+// between them. The sets are dealt to the CTAs in equal contiguous shares (every SM gets within one set of the same work:
+// no partial last wave). A warp's work is a flat sequence of items (set, 256-block of its K share); it keeps a private
+// ring of `depth` staged items in shared memory, filled by cp.async (16 bytes per lane and instruction, no registers
+// held), depth - 1 items ahead of the one being multiplied: the bytes in flight per SM are bounded by shared memory.
+template <int KS, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemv_mma_q4k_kernel(const Params p, const uint32_t depth) {
+    constexpr uint32_t kWarps = WARPS, kThreads = WARPS * 32;
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t K = p.K, B = K >> 8, astride = K + kActPad, MR = p.M + 1u;   // staged rows: M tokens + one of zeros
     int8_t* s_act = reinterpret_cast<int8_t*>(smem);                         // [M + 1][K + 32]
     int16_t* s_sub = reinterpret_cast<int16_t*>(smem + MR * astride);         // [M + 1][B][8] sub-block sums of q
     float* s_da = reinterpret_cast<float*>(smem + MR * astride + MR * B * 16u);   // [M + 1][B]
-    float* s_red = s_da + MR * B;                                            // [2][16 warps][16 rows][8 tokens]
-    uint8_t* s_ring = reinterpret_cast<uint8_t*>(s_red + 2u * kWarps * 128u);   // [16 warps][depth][kStageBytes]
+    float* s_red = s_da + MR * B;                                            // [2][WARPS][16 rows][8 tokens]
+    uint8_t* s_ring = reinterpret_cast<uint8_t*>(s_red + 2u * kWarps * 128u);   // [WARPS][depth][kStageBytes]
     s_ring += (16u - (smem_addr(s_ring) & 15u)) & 15u;
 
     constexpr uint32_t RG = kWarps / KS;
@@ -123,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
 #pragma unroll
             for (uint32_t i = 0; i < 4u; ++i) {
                 const uint32_t r = (lane >> 3) + 4u * i, row = min(row0 + r, p.N - 1u);
-                cp_async_16(st + r * kRowPitch + col * 16u, p.Q + ((size_t)row * B + b) * 128u + col * 16u);
+                cp_async_16(st + r * kRowPitch + ((col ^ (r & 7u)) << 4), p.Q + ((size_t)row * B + b) * 128u + col * 16u);
             }
             if (lane < 16u) cp_async_16(st + 16u * kRowPitch + lane * 16u, p.S + (size_t)min(row0 + lane, p.N - 1u) * B + b);
         }
@@ -139,15 +143,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
     pdl_wait();
     AMV_TRACE_STAMP(2)
 
-    // ---- stage the quantized activations and their per-block records; row M is zeros (tokens M..7 of the instruction) ----
+    // ---- stage the quantized activations (asynchronous copies: one round trip for all of them) and their per-block
+    //      records; row M is zeros (tokens M..7 of the instruction) ----
     {
         const uint32_t pieces = K >> 4;   // 16-byte pieces per activation row
-        for (uint32_t i = threadIdx.x; i < MR * pieces; i += kThreads) {
+        for (uint32_t i = threadIdx.x; i < p.M * pieces; i += kThreads) {
             const uint32_t m = i / pieces, w = i - m * pieces;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (m < p.M) v = __ldg(reinterpret_cast<const uint4*>(p.AQ + (size_t)m * K) + w);
-            *reinterpret_cast<uint4*>(s_act + m * astride + 16u * w) = v;
+            cp_async_16(smem_addr(s_act + m * astride + 16u * w), p.AQ + (size_t)m * K + 16u * w);
         }
+        cp_async_commit();
+        for (uint32_t w = threadIdx.x; w < pieces; w += kThreads)
+            *reinterpret_cast<uint4*>(s_act + p.M * astride + 16u * w) = make_uint4(0u, 0u, 0u, 0u);
         for (uint32_t i = threadIdx.x; i < MR * B; i += kThreads) {
             const uint32_t m = i / B, b = i - m * B;
             uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
@@ -170,6 +176,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
             *reinterpret_cast<uint4*>(s_sub + (size_t)i * 8u) = make_uint4(out[0], out[1], out[2], out[3]);
             s_da[i] = d;
         }
+        cp_async_wait<0>();   // the activations (and the blocks requested before them)
     }
     __syncthreads();
     AMV_TRACE_STAMP(3)
@@ -214,11 +221,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
             }
             int isum[4] = {0, 0, 0, 0};
             const int8_t* ab = a_lane + 256u * b;
-            const uint8_t* wa = st + g * kRowPitch + 8u * t;            // row g: this lane's 8 bytes of each 32-byte chunk
-            const uint8_t* wb = wa + 8u * kRowPitch;                    // row g + 8
+            // rows g and g + 8 (the same swizzle term): this lane's 8 bytes of each 32-byte chunk = half (t & 1) of the
+            // 16-byte piece 2k + t / 2, which sits at piece position (2k + t / 2) ^ g
+            const uint8_t* wa = st + g * kRowPitch + 8u * (t & 1u);
+            const uint8_t* wb = wa + 8u * kRowPitch;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const uint2 va = *reinterpret_cast<const uint2*>(wa + 32 * k), vb = *reinterpret_cast<const uint2*>(wb + 32 * k);
+                const uint32_t po = ((2u * (uint32_t)k + (t >> 1)) ^ g) << 4;
+                const uint2 va = *reinterpret_cast<const uint2*>(wa + po), vb = *reinterpret_cast<const uint2*>(wb + po);
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int j = 2 * k + h;   // sub-block
@@ -282,33 +292,42 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_mma_q4k_kernel(const Params 
     AMV_TRACE_STAMP(5)
 }
 
-template <int KS>
+template <int KS, int WARPS>
 static AcResult launch_ks(const LaunchArgs& a, const Params& p, uint32_t smem_bytes, uint32_t depth) {
-    if (!ensure_dynamic_smem<gemv_mma_q4k_kernel<KS>>((int)kSmemLimit)) return AC_ERR_INVALID_WORK_GROUP_SIZE;
+    if (!ensure_dynamic_smem<gemv_mma_q4k_kernel<KS, WARPS>>((int)kSmemLimit)) return AC_ERR_INVALID_WORK_GROUP_SIZE;
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
-    const uint32_t groups = (p.N + 15u) / 16u, rg = kWarps / KS, n_sets = (groups + rg - 1u) / rg;
-    launch_pdl(gemv_mma_q4k_kernel<KS>, dim3(n_sets < sms ? n_sets : sms), dim3(kThreads), smem_bytes, a.stream, p, depth);
+    const uint32_t groups = (p.N + 15u) / 16u, rg = WARPS / KS, n_sets = (groups + rg - 1u) / rg;
+    launch_pdl(gemv_mma_q4k_kernel<KS, WARPS>, dim3(n_sets < sms ? n_sets : sms), dim3(WARPS * 32), smem_bytes, a.stream, p,
+               depth);
     return check_launch();
 }
 
 }  // namespace gm
 
 // Shared-memory bytes of ameva_mmvm_q4_K before the weight rings: the activations of M token rows plus a row of zeros,
-// their per-block records and two sets of partial sums. What is left of 227 KB holds the 16 warps' rings: the kernel
-// serves the (M, K) for which at least two stages per warp fit (M = 8: K <= 12800; M = 1: K <= 65536).
-static uint32_t mmvm_fixed_bytes(uint32_t M, uint32_t K) {
+// their per-block records and two sets of partial sums.
+static uint32_t mmvm_fixed_bytes(uint32_t M, uint32_t K, uint32_t warps) {
     const uint32_t B = K >> 8, MR = M + 1u;
-    return MR * (K + gm::kActPad) + MR * B * 16u + MR * B * 4u + 2u * gm::kWarps * 128u * 4u + 16u;
+    return MR * (K + gm::kActPad) + MR * B * 16u + MR * B * 4u + 2u * warps * 128u * 4u + 16u;
 }
-static uint32_t mmvm_depth(uint32_t M, uint32_t K) {
-    const uint32_t fixed = mmvm_fixed_bytes(M, K);
-    if (fixed >= gm::kSmemLimit) return 0;
-    const uint32_t d = (gm::kSmemLimit - fixed) / (gm::kWarps * gm::kStageBytes);
-    return d > gm::kMaxDepth ? gm::kMaxDepth : d;
+// The launch shape: 8 warps in at most half an SM's shared memory when at least four ring stages per warp fit there (so
+// that two launches overlap on an SM), else 16 warps in all of it; the kernel serves the (M, K) for which the second
+// form has at least two stages per warp (M = 8: K <= 14592; M = 1: K <= 65536). depth = 0: does not fit.
+static void mmvm_shape(uint32_t M, uint32_t K, uint32_t* warps, uint32_t* depth) {
+    *warps = 8u;
+    const uint32_t f8 = mmvm_fixed_bytes(M, K, 8u);
+    uint32_t d = f8 < gm::kHalfSmem ? (gm::kHalfSmem - f8) / (8u * gm::kStageBytes) : 0u;
+    if (d < 4u) {
+        *warps = 16u;
+        const uint32_t f16 = mmvm_fixed_bytes(M, K, 16u);
+        d = f16 < gm::kSmemLimit ? (gm::kSmemLimit - f16) / (16u * gm::kStageBytes) : 0u;
+        if (d < 2u) d = 0u;
+    }
+    *depth = d > gm::kMaxDepth ? gm::kMaxDepth : d;
 }
 
 // ameva_mmvm_q4_K: bindings 0 Q, 1 S, 2 AQ, 3 AB, 4 dst f32 [M][dst_stride];  push {M (1..8), N, K (% 256), dst_stride}
-// (M + 1) (K + 32) bytes of activations and two ring stages per warp must fit shared memory (M = 8: K <= 12800; M = 1:
+// (M + 1) (K + 32) bytes of activations and two ring stages per warp must fit shared memory (M = 8: K <= 14592; M = 1:
 // K <= 65536); beyond that AC_ERR_INVALID_SHAPE (callers keep the dp4a kernels there).
 AcResult launch_mmvm_q4_K(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
@@ -323,9 +342,10 @@ AcResult launch_mmvm_q4_K(const LaunchArgs& a) {
         ((uintptr_t)a.ptr[3] & 15u))
         return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     if ((uint64_t)(M + 1u) * (K + gm::kActPad) > gm::kSmemLimit) return AC_ERR_INVALID_SHAPE;
-    const uint32_t depth = mmvm_depth(M, K);
+    uint32_t warps, depth;
+    mmvm_shape(M, K, &warps, &depth);
     if (depth < 2u) return AC_ERR_INVALID_SHAPE;
-    const uint32_t smem = mmvm_fixed_bytes(M, K) + depth * gm::kWarps * gm::kStageBytes;
+    const uint32_t smem = mmvm_fixed_bytes(M, K, warps) + depth * warps * gm::kStageBytes;
     gm::Params p;
     p.Q = (const uint8_t*)a.ptr[0];
     p.S = (const uint4*)a.ptr[1];
@@ -336,16 +356,24 @@ AcResult launch_mmvm_q4_K(const LaunchArgs& a) {
     p.N = N;
     p.K = K;
     p.dst_stride = dst_stride;
-    // K split: the 16 warps of a CTA work on as few row groups at a time as the 256-blocks of a row allow (one block
-    // per warp at least), which keeps the sets small and the shares of the SMs even
-    uint32_t ks = 16;
+    // K split: the warps of a CTA work on as few row groups at a time as the 256-blocks of a row allow (one block per
+    // warp at least), which keeps the sets small and the shares of the SMs even
+    uint32_t ks = warps;
     while (ks > 1u && ks > B) ks >>= 1;
+    if (warps == 8u) {
+        switch (ks) {
+            case 1: return gm::launch_ks<1, 8>(a, p, smem, depth);
+            case 2: return gm::launch_ks<2, 8>(a, p, smem, depth);
+            case 4: return gm::launch_ks<4, 8>(a, p, smem, depth);
+            default: return gm::launch_ks<8, 8>(a, p, smem, depth);
+        }
+    }
     switch (ks) {
-        case 1: return gm::launch_ks<1>(a, p, smem, depth);
-        case 2: return gm::launch_ks<2>(a, p, smem, depth);
-        case 4: return gm::launch_ks<4>(a, p, smem, depth);
-        case 8: return gm::launch_ks<8>(a, p, smem, depth);
-        default: return gm::launch_ks<16>(a, p, smem, depth);
+        case 1: return gm::launch_ks<1, 16>(a, p, smem, depth);
+        case 2: return gm::launch_ks<2, 16>(a, p, smem, depth);
+        case 4: return gm::launch_ks<4, 16>(a, p, smem, depth);
+        case 8: return gm::launch_ks<8, 16>(a, p, smem, depth);
+        default: return gm::launch_ks<16, 16>(a, p, smem, depth);
     }
 }
 

@@ -177,7 +177,7 @@ static uint64_t align64(uint64_t v) { return (v + 63u) & ~(uint64_t)63u; }
 // ---------------------------------------------------------------------------------------------------------------------
 static bool mmvm_fits(uint64_t M, uint64_t K) {   // shared memory of ameva_mmvm_q4_K (gemv_mma.cu): two ring stages per warp
     const uint64_t rows = M + 1;
-    return (K % 256) == 0 && rows * (K + 32) + rows * (K / 256) * 20 + 16384 + 16 + 2u * 16u * 2816u <= 227u * 1024u;
+    return (K % 256) == 0 && rows * (K + 32) + rows * (K / 256) * 20 + 16384 + 16 + 2u * 16u * 2304u <= 227u * 1024u;
 }
 
 extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, uint64_t K, uint32_t flags,

@@ -27,9 +27,9 @@ FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in
 
 def mma_gemv_fits(M: int, K: int) -> bool:
     """Q4_K, M <= 8: whether ameva_mmvm_q4_K can hold the M activation rows (plus one row of zeros), their per-block
-    records, its partial sums and two ring stages per warp in 227 KB of shared memory (M = 8: K <= 12800)."""
+    records, its partial sums and two ring stages per warp in 227 KB of shared memory (M = 8: K <= 14592)."""
     rows = M + 1
-    return K % 256 == 0 and rows * (K + 32) + rows * (K // 256) * 20 + 16384 + 16 + 2 * 16 * 2816 <= 227 * 1024
+    return K % 256 == 0 and rows * (K + 32) + rows * (K // 256) * 20 + 16384 + 16 + 2 * 16 * 2304 <= 227 * 1024
 
 
 GEMV_MAX_M = 8   # decode GEMV serves M <= 8 (ggml-ameva.cpp:3607-3804 sends 2 <= M < 8 to the GEMV family as well)

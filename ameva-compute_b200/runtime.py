@@ -556,7 +556,7 @@ PATH_NONE, PATH_GEMV, PATH_GEMV_FQ, PATH_GEMV_STREAMED, PATH_GEMV_MMA, PATH_GEMM
 PLAN_EXACT, PLAN_HOST_LAUNCH, PLAN_PEERS, PLAN_WEIGHT_RANGE = 1, 2, 4, 8
 
 
-GEMM_ONE_TILE_PER_UNIT, GEMM_ONE_ACCUMULATOR = 64, 128   # AC_B200_GEMM_* launch switches of ameva_mmtc_* (push word 4)
+GEMM_ONE_TILE_PER_UNIT, GEMM_ONE_ACCUMULATOR, GEMM_TWO_ACCUMULATORS = 64, 128, 256   # AC_B200_GEMM_* launch switches of ameva_mmtc_* (push word 4)
 
 
 def weight_range_extreme(w_exp: int) -> bool:

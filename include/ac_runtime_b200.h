@@ -317,9 +317,13 @@ const char* ac_b200_kernel_name(uint32_t index);
  *                      cuts K ranges across tiles and has units wait (bounded, about a second, then
  *                      AC_ERR_LAUNCH_TIMEOUT) for partial sums of other units of the same launch, which assumes the
  *                      launch has the whole GPU: a host that shares the device with other contexts or streams sets this.
- *   ONE_ACCUMULATOR    keep launches of more than 256 token rows on the kernel with one accumulator per CTA pair. */
+ *   ONE_ACCUMULATOR    keep launches of more than 256 token rows on the kernel with one accumulator per CTA pair.
+ *   TWO_ACCUMULATORS   take the kernel with two accumulators per CTA pair (weights converted once per 512 token rows)
+ *                      for every launch of more than 256 token rows; by default only where every CTA pair gets at
+ *                      least two whole 256 x 512 output tiles. */
 #define AC_B200_GEMM_ONE_TILE_PER_UNIT 64u
 #define AC_B200_GEMM_ONE_ACCUMULATOR 128u
+#define AC_B200_GEMM_TWO_ACCUMULATORS 256u
 /* A host's own kernel under a name of its choosing, dispatched like the built-in ones (batches, replay, events). The
  * reference takes caller kernels as SPIR-V / OpenCL source in AcKernelCreateInfo (ac_runtime.h:560-600); here the caller
  * brings a compiled launcher. fn runs on the recording thread with the device current, must only enqueue work on

@@ -219,13 +219,12 @@ def test_gemm_two_accumulators_per_cta_pair(ctx, t, M, N, K):
     accumulator (the same fp16 operands and fp32 accumulation, so they agree to summation order)."""
     if t == Q4_K and K % 256:
         K = (K // 256 + 1) * 256
-    run_gemm(ctx, t, M, N, K, seed=M + N + 7)
     blocks, scale = make_weights(t, N, K, 3)
     x = make_acts(M, K, 4)
     w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
     xb = ctx.buffer(data=x)
     ys = []
-    for flags in (0, rt.GEMM_ONE_ACCUMULATOR, rt.GEMM_ONE_TILE_PER_UNIT):
+    for flags in (rt.GEMM_TWO_ACCUMULATORS, rt.GEMM_ONE_ACCUMULATOR, rt.GEMM_TWO_ACCUMULATORS | rt.GEMM_ONE_TILE_PER_UNIT):
         mm = qmm.MulMat(ctx, w, M, gemm_flags=flags)
         dst = ctx.buffer(M * N * 4)
         dst.fill(0xFF)
@@ -234,6 +233,8 @@ def test_gemm_two_accumulators_per_cta_pair(ctx, t, M, N, K):
         dst.destroy()
         mm.destroy()
     assert np.isfinite(ys[0]).all()
+    want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+    assert max_normalised_error(ys[0], want) <= TOL
     assert max_normalised_error(ys[0], ys[1]) <= 1e-5 and max_normalised_error(ys[0], ys[2]) <= 1e-5
     xb.destroy()
     w.destroy()

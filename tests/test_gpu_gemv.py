@@ -498,7 +498,7 @@ def test_gemv_mma_limits(ctx):
     blocks, scale = make_weights(Q4_K, 16, K, 1)
     w = qmm.QuantWeight.from_ggml(ctx, Q4_K, blocks, 16, K, scale)
     assert qmm.mma_gemv_fits(1, K) and qmm.mma_gemv_fits(2, K) and not qmm.mma_gemv_fits(4, K) and not qmm.mma_gemv_fits(8, K)
-    assert qmm.mma_gemv_fits(8, 12800) and not qmm.mma_gemv_fits(8, 13056)
+    assert qmm.mma_gemv_fits(8, 14592) and not qmm.mma_gemv_fits(8, 14848)
     xb, dst = ctx.buffer(data=make_acts(8, K, 2)), ctx.buffer(8 * 16 * 4)
     forced = qmm.MulMat(ctx, w, 8, mma=True)
     with pytest.raises(qmm.MulMatUnsupported):      # 8 token rows of this K are beyond what shared memory holds
