@@ -57,6 +57,9 @@ const KernelEntry* find_kernel(const char* name);
 uint32_t kernel_count();
 const KernelEntry* kernel_at(uint32_t i);
 AcResult register_kernel(const char* name, uint32_t binding_count, uint32_t push_bytes, AcB200LaunchFn fn);
+// repack.cu: the ggml -> device-regions permutation of blocks [first, first + nblk) of a tensor, from staged ggml bytes
+AcResult launch_repack(cudaStream_t stream, uint32_t type, const void* src, void* q_region, void* s_region, uint64_t first,
+                       uint64_t nblk);
 
 inline AcResult check_launch() {
     return cudaGetLastError() == cudaSuccess ? AC_SUCCESS : AC_ERR_INVALID_WORK_GROUP_SIZE;

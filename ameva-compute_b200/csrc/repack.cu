@@ -1,0 +1,85 @@
+// Device-side repack of ggml weight blocks into the device regions (payloads first, padded to 64 bytes, then the scale
+// fields), fed from pinned staging chunks.
+//
+// The reference repacks on the CPU while uploading (adapters/llama/ggml-ameva/ggml-ameva-buffer.cpp:300-330 stages
+// chunks, ggml-ameva-repack.cpp:82-247 permutes). Here the CPU only copies the caller's ggml bytes into one of two
+// pinned chunks; the chunk travels host -> device asynchronously and a kernel does the permutation at memory speed while
+// the CPU fills the other chunk. The permutation is a pure byte move, so reading the regions back through
+// ac_b200_repack_from_device returns the uploaded bytes exactly.
+#include <cstring>
+
+#include "common.cuh"
+
+namespace amv {
+
+struct RepackCodec {
+    uint32_t blk_bytes, q_off, q_bytes, s_off, s_bytes;   // placement of the payload / scale fields inside a ggml block
+};
+
+constexpr uint32_t kRepackTile = 256;   // blocks per CTA: 256 x 18, 34 or 144 bytes are whole 16-byte pieces
+
+// One CTA moves kRepackTile consecutive blocks: the tile's bytes are loaded into shared memory with coalesced 16-byte
+// loads (a tile starts on a 16-byte boundary of the staging chunk), then every thread assembles 16-byte payload pieces
+// (fields sit on 2-byte boundaries inside a block) and 2-byte scale pieces and stores them coalesced.
+__global__ void __launch_bounds__(256) repack_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst_q,
+                                                     uint8_t* __restrict__ dst_s, uint64_t nblk, const RepackCodec c) {
+    extern __shared__ __align__(16) uint8_t tile[];
+    const uint64_t b0 = (uint64_t)blockIdx.x * kRepackTile;
+    const uint32_t nb = (uint32_t)min((uint64_t)kRepackTile, nblk - b0);
+    const uint32_t bytes = nb * c.blk_bytes;
+    const uint8_t* s = src + b0 * c.blk_bytes;
+    for (uint32_t i = threadIdx.x * 16u; i < bytes; i += 256u * 16u) {
+        if (i + 16u <= bytes) {
+            *reinterpret_cast<uint4*>(tile + i) = *reinterpret_cast<const uint4*>(s + i);
+        } else {   // the ragged end of the last tile
+            for (uint32_t j = i; j < bytes; ++j) tile[j] = s[j];
+        }
+    }
+    __syncthreads();
+    const uint32_t q_pieces = nb * (c.q_bytes / 16u), per_blk = c.q_bytes / 16u;
+    uint8_t* q = dst_q + b0 * c.q_bytes;
+    for (uint32_t p = threadIdx.x; p < q_pieces; p += 256u) {
+        const uint32_t blk = p / per_blk, part = p - blk * per_blk;
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(tile + blk * c.blk_bytes + c.q_off + part * 16u);
+        uint4 v;
+        v.x = h[0] | ((uint32_t)h[1] << 16);
+        v.y = h[2] | ((uint32_t)h[3] << 16);
+        v.z = h[4] | ((uint32_t)h[5] << 16);
+        v.w = h[6] | ((uint32_t)h[7] << 16);
+        *reinterpret_cast<uint4*>(q + (size_t)p * 16u) = v;
+    }
+    const uint32_t s_halves = nb * (c.s_bytes / 2u), per_blk_s = c.s_bytes / 2u;
+    uint16_t* sc = reinterpret_cast<uint16_t*>(dst_s + b0 * c.s_bytes);
+    for (uint32_t p = threadIdx.x; p < s_halves; p += 256u) {
+        const uint32_t blk = p / per_blk_s, part = p - blk * per_blk_s;
+        sc[p] = *reinterpret_cast<const uint16_t*>(tile + blk * c.blk_bytes + c.s_off + part * 2u);
+    }
+}
+
+static bool repack_codec(uint32_t type, RepackCodec* c, uint32_t* blk) {
+    switch (type) {
+        case 2: *c = {18, 2, 16, 0, 2}; *blk = 32; return true;        // Q4_0: d@0, qs[16]@2
+        case 8: *c = {34, 2, 32, 0, 2}; *blk = 32; return true;        // Q8_0: d@0, qs[32]@2
+        case 12: *c = {144, 16, 128, 0, 16}; *blk = 256; return true;  // Q4_K: d, dmin, scales[12] @0, qs[128]@16
+        default: return false;
+    }
+}
+
+// Launches the permutation of `nblk` blocks that start at block `first` of the tensor: src = the staged ggml bytes of
+// those blocks (16-byte aligned), q_region / s_region = the start of the tensor's payload / scale regions.
+AcResult launch_repack(cudaStream_t stream, uint32_t type, const void* src, void* q_region, void* s_region,
+                       uint64_t first, uint64_t nblk) {
+    RepackCodec c;
+    uint32_t blk;
+    if (!repack_codec(type, &c, &blk)) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    if (nblk == 0) return AC_SUCCESS;
+    if (((uintptr_t)src & 15u) || ((uintptr_t)q_region & 15u) || ((uintptr_t)s_region & 1u) || (first % kRepackTile))
+        return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    const uint64_t tiles = (nblk + kRepackTile - 1) / kRepackTile;
+    if (tiles > 0x7fffffffull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
+    repack_kernel<<<(unsigned)tiles, 256, kRepackTile * c.blk_bytes, stream>>>(
+        (const uint8_t*)src, (uint8_t*)q_region + first * c.q_bytes, (uint8_t*)s_region + first * c.s_bytes, nblk, c);
+    return check_launch();
+}
+
+}  // namespace amv

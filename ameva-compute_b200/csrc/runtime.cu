@@ -47,6 +47,11 @@ struct AcContext {
     uint32_t live_buffers, live_kernels, live_events, live_batches;
     uint64_t id;
     SideQueues side;        // copy queues beside the stream, created by the first launcher that needs them
+    // weight upload (ac_b200_weight_upload): two pinned host chunks and two device chunks, created by the first upload
+    void* up_pinned[2];
+    void* up_dev[2];
+    cudaEvent_t up_done[2];
+    bool up_used[2], up_ready;
 };
 
 struct AcBuffer {
@@ -390,6 +395,13 @@ AcResult ac_runtime_context_destroy(AcContext* ctx) {
             cudaEventDestroy(ctx->side.done[i]);
         }
         cudaEventDestroy(ctx->side.fork);
+    }
+    if (ctx->up_ready) {
+        for (int i = 0; i < 2; ++i) {
+            cudaFreeHost(ctx->up_pinned[i]);
+            cudaFree(ctx->up_dev[i]);
+            cudaEventDestroy(ctx->up_done[i]);
+        }
     }
     cudaStreamDestroy(ctx->stream);
     cudaFreeHost(ctx->status_host);
@@ -778,6 +790,73 @@ AcResult ac_b200_kernel_register(const char* name, uint32_t binding_count, uint3
 const char* ac_b200_kernel_name(uint32_t index) {
     const KernelEntry* e = kernel_at(index);
     return e ? e->name : nullptr;
+}
+
+// ---- weight upload with the repack on the device ----------------------------------------------------------------------
+static constexpr size_t kUploadChunk = 32u << 20;   // bytes of ggml blocks per staging chunk
+
+AcResult ac_b200_weight_upload(AcBuffer* buf, size_t offset, uint32_t type, const void* ggml_blocks, uint64_t rows,
+                               uint64_t k) {
+    if (!buf_ok(buf)) return AC_ERR_INVALID_ARGUMENT;
+    if (!ggml_blocks) return AC_ERR_NULL_POINTER;
+    uint64_t total = 0, s_off = 0;
+    AcResult rc = ac_b200_device_layout(type, rows, k, &total, &s_off);
+    if (rc != AC_SUCCESS) return rc;
+    if (offset % 64u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    if (offset > buf->size || total > buf->size - offset) return AC_ERR_INVALID_BUFFER_SIZE;
+    if (type == 36u) return ac_runtime_buffer_write(buf, offset, ggml_blocks, (size_t)total);   // I2_S: dense already
+    const uint32_t blk_bytes = type == 2u ? 18u : type == 8u ? 34u : 144u, blk = type == 12u ? 256u : 32u;
+    const uint64_t nblk = rows * (k / blk);
+    AcContext* ctx = buf->ctx;
+    DeviceGuard g(ctx->device);
+    if (!ctx->up_ready) {
+        bool ok = true;
+        for (int i = 0; i < 2 && ok; ++i)
+            ok = cudaMallocHost(&ctx->up_pinned[i], kUploadChunk) == cudaSuccess &&
+                 cudaMalloc(&ctx->up_dev[i], kUploadChunk) == cudaSuccess &&
+                 cudaEventCreateWithFlags(&ctx->up_done[i], cudaEventDisableTiming) == cudaSuccess;
+        if (!ok) {   // (what was created is released here: the staging either exists whole or not at all)
+            cudaGetLastError();
+            for (int i = 0; i < 2; ++i) {
+                if (ctx->up_pinned[i]) cudaFreeHost(ctx->up_pinned[i]);
+                if (ctx->up_dev[i]) cudaFree(ctx->up_dev[i]);
+                if (ctx->up_done[i]) cudaEventDestroy(ctx->up_done[i]);
+                ctx->up_pinned[i] = ctx->up_dev[i] = nullptr;
+                ctx->up_done[i] = nullptr;
+            }
+            cudaGetLastError();
+            return fail(ctx, AC_ERR_OUT_OF_DEVICE_MEMORY, AMEVA_BACKEND_OP_COPY_HTOD, 0, kUploadChunk, 0);
+        }
+        ctx->up_used[0] = ctx->up_used[1] = false;
+        ctx->up_ready = true;
+    }
+    // whole tiles of 256 blocks per chunk, so every chunk starts where a CTA of the repack kernel starts
+    const uint64_t chunk_blocks = (kUploadChunk / blk_bytes) / 256u * 256u;
+    char* base = (char*)buf->dptr + offset;
+    const char* src = (const char*)ggml_blocks;
+    int c = 0;
+    for (uint64_t first = 0; first < nblk; first += chunk_blocks, c ^= 1) {
+        const uint64_t n = nblk - first < chunk_blocks ? nblk - first : chunk_blocks;
+        if (ctx->up_used[c] && cudaEventSynchronize(ctx->up_done[c]) != cudaSuccess) {   // the chunk's last use is over
+            cudaGetLastError();
+            return fail(ctx, AC_ERR_DRIVER_CRASH_OR_LOST, AMEVA_BACKEND_OP_COPY_HTOD, offset, (size_t)total, buf->size);
+        }
+        memcpy(ctx->up_pinned[c], src + first * blk_bytes, (size_t)(n * blk_bytes));
+        if (cudaMemcpyAsync(ctx->up_dev[c], ctx->up_pinned[c], (size_t)(n * blk_bytes), cudaMemcpyHostToDevice,
+                            ctx->stream) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(ctx, AC_ERR_DRIVER_CRASH_OR_LOST, AMEVA_BACKEND_OP_COPY_HTOD, offset, (size_t)total, buf->size);
+        }
+        rc = amv::launch_repack(ctx->stream, type, ctx->up_dev[c], base, base + s_off, first, n);
+        if (rc != AC_SUCCESS) return rc;
+        cudaEventRecord(ctx->up_done[c], ctx->stream);
+        ctx->up_used[c] = true;
+    }
+    if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ctx, AC_ERR_DRIVER_CRASH_OR_LOST, AMEVA_BACKEND_OP_COPY_HTOD, offset, (size_t)total, buf->size);
+    }
+    return AC_SUCCESS;
 }
 
 // ---- dispatch and events --------------------------------------------------------------------------------------------

@@ -170,10 +170,11 @@ void buffer_set_tensor(ggml_backend_buffer_t buffer, ggml_tensor* tensor, const 
     if (offset > nbytes || size > nbytes - offset) die("set_tensor range", AC_ERR_INVALID_BUFFER_SIZE);
     const uint64_t rows = (uint64_t)base->ne[1], k = (uint64_t)base->ne[0];
     const uint64_t total = device_bytes(base, nullptr);
-    std::vector<uint8_t> dev(total), blocks;
+    std::vector<uint8_t> blocks;
     const void* src = data;
     const bool first_upload = b->w_exp.find(tensor_offset(base)) == b->w_exp.end();
     if (offset != 0 || size != nbytes) {   // a partial range: patch the ggml image of what is on the device
+        std::vector<uint8_t> dev(total);
         blocks.resize(nbytes);
         AcResult rc = ac_runtime_buffer_read(b->buf, tensor_offset(base), dev.data(), total);
         if (rc == AC_SUCCESS) rc = ac_b200_repack_from_device((uint32_t)base->type, dev.data(), rows, k, blocks.data());
@@ -181,8 +182,9 @@ void buffer_set_tensor(ggml_backend_buffer_t buffer, ggml_tensor* tensor, const 
         memcpy(blocks.data() + offset, data, size);
         src = blocks.data();
     }
-    AcResult rc = ac_b200_repack_to_device((uint32_t)base->type, src, rows, k, dev.data());
-    if (rc == AC_SUCCESS) rc = ac_runtime_buffer_write(b->buf, tensor_offset(base), dev.data(), total);
+    // the ggml -> regions permutation runs on the device, fed from the runtime's pinned staging chunks
+    // (ggml-ameva-buffer.cpp:300-330 stages chunks and repacks on the CPU)
+    AcResult rc = ac_b200_weight_upload(b->buf, tensor_offset(base), (uint32_t)base->type, src, rows, k);
     int32_t w_exp = 0;
     if (rc == AC_SUCCESS) rc = ac_b200_weight_exponent((uint32_t)base->type, src, rows, k, &w_exp);
     if (rc != AC_SUCCESS) die("set_tensor", rc);

@@ -102,7 +102,10 @@ class QuantWeight:
 
     @classmethod
     def from_ggml(cls, ctx: rt.Context, ggml_type: int, blocks: np.ndarray, N: int, K: int,
-                  scale: float = 1.0) -> "QuantWeight":
+                  scale: float = 1.0, host_repack: bool = False) -> "QuantWeight":
+        """Uploads ggml blocks into the device regions. The permutation runs on the device, fed from pinned staging
+        chunks (ac_b200_weight_upload); host_repack=True permutes on the CPU first (ac_b200_repack_to_device) and
+        writes the result, which is what a caller with its own staging does. Both leave the same bytes."""
         why = unsupported_reason(ggml_type, 1, N, K)
         if why:
             raise MulMatUnsupported(why)
@@ -110,8 +113,17 @@ class QuantWeight:
         if blocks.size != rt.ggml_nbytes(ggml_type, N, K):
             raise MulMatUnsupported(f"expected {rt.ggml_nbytes(ggml_type, N, K)} bytes of ggml blocks, got {blocks.size}")
         total, s_off = rt.device_layout(ggml_type, N, K)
-        dev = rt.repack_to_device(ggml_type, blocks, N, K)
-        return cls(ctx, ggml_type, N, K, ctx.buffer(total, dev), s_off, scale, weight_exponent(ggml_type, blocks, N, K))
+        w_exp = weight_exponent(ggml_type, blocks, N, K)
+        if host_repack:
+            buf = ctx.buffer(total, rt.repack_to_device(ggml_type, blocks, N, K))
+        else:
+            buf = ctx.buffer(total)
+            try:
+                buf.upload_weight(ggml_type, blocks, N, K)
+            except Exception:
+                buf.destroy()
+                raise
+        return cls(ctx, ggml_type, N, K, buf, s_off, scale, w_exp)
 
     def to_ggml(self, row0: int = 0, rows: Optional[int] = None) -> np.ndarray:
         rows = self.N - row0 if rows is None else rows

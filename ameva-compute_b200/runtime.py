@@ -130,7 +130,7 @@ EXPORTED_SYMBOLS = [
     "ac_runtime_get_generation", "ac_runtime_reset_error_state", "ac_runtime_set_error_ctx",
     "ac_runtime_get_error_state_ctx", "ac_runtime_consume_error_ctx", "ac_runtime_advance_generation_ctx",
     "ac_runtime_get_generation_ctx", "ac_runtime_reset_error_state_ctx", "ac_runtime_kernel_create_builtin",
-    "ac_b200_kernel_count", "ac_b200_kernel_name", "ac_b200_kernel_register", "ac_b200_context_get_stream", "ac_b200_buffer_import",
+    "ac_b200_kernel_count", "ac_b200_kernel_name", "ac_b200_kernel_register", "ac_b200_weight_upload", "ac_b200_context_get_stream", "ac_b200_buffer_import",
     "ac_b200_buffer_export_ipc", "ac_b200_buffer_open_ipc", "ac_b200_buffer_write_async", "ac_b200_buffer_read_async", "ac_b200_context_synchronize", "ac_b200_batch_instantiate", "ac_b200_batch_replay",
     "ac_b200_device_layout", "ac_b200_repack_to_device", "ac_b200_repack_from_device", "ac_b200_mul_mat_plan",
     "ac_b200_weight_exponent",
@@ -207,6 +207,7 @@ def load_library() -> C.CDLL:
         "ac_b200_kernel_count": (u32, []),
         "ac_b200_kernel_name": (C.c_char_p, [u32]),
         "ac_b200_kernel_register": (C.c_int, [C.c_char_p, u32, u32, C.c_void_p]),
+        "ac_b200_weight_upload": (C.c_int, [vp, sz, u32, vp, u64, u64]),
         "ac_b200_context_get_stream": (C.c_int, [vp, P(vp)]),
         "ac_b200_buffer_import": (C.c_int, [vp, vp, sz, P(vp)]),
         "ac_b200_buffer_export_ipc": (C.c_int, [vp, vp]),
@@ -300,6 +301,11 @@ class Buffer:
 
     def read_async(self, host, nbytes: int, offset: int = 0) -> None:
         _check(load_library().ac_b200_buffer_read_async(self._h, offset, _host_ptr(host), nbytes), "read_async")
+
+    def upload_weight(self, ggml_type: int, blocks: np.ndarray, rows: int, k: int, offset: int = 0) -> None:
+        """ggml blocks -> the device regions at byte `offset` (a multiple of 64), permuted on the device."""
+        blocks = np.ascontiguousarray(blocks, dtype=np.uint8).reshape(-1)
+        _check(load_library().ac_b200_weight_upload(self._h, offset, ggml_type, _host_ptr(blocks), rows, k), "weight_upload")
 
     def export_ipc(self) -> bytes:
         """64-byte handle another rank of the same box opens with Context.open_ipc."""

@@ -42,3 +42,30 @@ def assemble(gathered, parts: List[Tuple[int, int]], M: int, N: int, out) -> Non
     for r, (row0, rows) in enumerate(parts):
         if rows:
             out[:, row0:row0 + rows].copy_(gathered[r, :, :rows])
+
+
+def token_chunks(M: int, chunk: int) -> List[Tuple[int, int]]:
+    """[(m0, rows)]: the token rows of a prefill batch in chunks; the mul_mat of chunk c + 1 runs while the copy engines
+    send chunk c's columns to the other ranks."""
+    if M <= 0 or chunk <= 0:
+        raise ValueError("M and chunk must be positive")
+    return [(m0, min(chunk, M - m0)) for m0 in range(0, M, chunk)]
+
+
+def exchange_plan(M: int, N: int, world: int, rank: int, chunk: int, stride: int = 0):
+    """The copies rank `rank` queues to give every other rank its column block of the [M][stride] fp32 output (stride = 0:
+    N): one entry per (token chunk, peer) = (peer, byte offset of the block's first element in both outputs, rows, width
+    in bytes, pitch in bytes). The same offset applies on both sides: every rank holds the whole [M][stride] output and
+    owns the columns partition_rows gives it. A rank without rows sends nothing."""
+    stride = stride or N
+    if stride < N:
+        raise ValueError("stride smaller than N")
+    row0, rows = partition_rows(N, world)[rank]
+    plan = []
+    if rows == 0:
+        return plan
+    for m0, mc in token_chunks(M, chunk):
+        for peer in range(world):
+            if peer != rank:
+                plan.append((peer, (m0 * stride + row0) * 4, mc, rows * 4, stride * 4))
+    return plan

@@ -202,6 +202,12 @@ def cpu_build_note():
     return oracle.build_flavour() if hasattr(oracle, "build_flavour") else "portable -O3 build"
 
 
+def parity_ties(t, x):
+    from helpers import count_rounding_ties
+    return {"convention": "nearest-even" if t != I2_S else "half-away (the scheme's only one)",
+            "exact_half_values": count_rounding_ties(t, x), "values": int(x.size)}
+
+
 def run_cpu_baseline(t, M, N, K, blocks, scale, x, unit, budget_s=12.0):
     """Times the CPU path on a bounded sample: the first Ms token rows, Ms sized from a probe so the timed pass costs
     roughly budget_s. Returns the cpu_baseline object."""
@@ -433,33 +439,39 @@ class Measurement:
             return self.M <= GEMV_MAX_M and not self.env.args.no_replay
         return self.exchange in ("none", "fused") and not self.env.args.no_replay
 
-    def replay_batches(self, quantize, rem):
-        """(graph of pool_n consecutive steps, graph of the first `rem` steps): every step count replays."""
+    def graph_steps(self, n):
+        """Steps per instantiated batch: all n of a short run in one (no launch of a graph inside the timed region but
+        the first), else a multiple of the pool that keeps a graph at a few hundred launches."""
+        if n <= 128:
+            return n
+        return self.pool_n * max(1, 96 // self.pool_n)
+
+    def replay_batches(self, quantize, g, rem):
+        """(graph of g consecutive steps, graph of the first `rem` steps): every step count replays. The steps of a graph
+        cycle through the pool of weight copies."""
         ctx = self.env.ctx
-        key = (quantize, 0, self.exchange_on)
-        if key not in self.replay_cache:
-            rb = ctx.batch(max(64, self.pool_n * 70), 0)
-            self.record_steps(rb, self.pool_n, 0, quantize)
-            rb.instantiate()
-            self.replay_cache[key] = rb
-        tail = None
-        if rem:
-            key_t = (quantize, rem, self.exchange_on)
-            if key_t not in self.replay_cache:
-                tb = ctx.batch(max(64, rem * 70), 0)
-                self.record_steps(tb, rem, 0, quantize)
-                tb.instantiate()
-                self.replay_cache[key_t] = tb
-            tail = self.replay_cache[key_t]
-        return self.replay_cache[key], tail
+        out = []
+        for cnt in (g, rem):
+            if not cnt:
+                out.append(None)
+                continue
+            key = (quantize, cnt, self.exchange_on)
+            if key not in self.replay_cache:
+                rb = ctx.batch(max(64, cnt * 70), 0)
+                self.record_steps(rb, cnt, 0, quantize)
+                rb.instantiate()
+                self.replay_cache[key] = rb
+            out.append(self.replay_cache[key])
+        return out[0], out[1]
 
     def gpu_steps(self, n, first, quantize=True):
         """n steps on the device; returns the GPU seconds by CUDA events on the runtime's stream."""
         env, torch, ctx = self.env, self.env.torch, self.env.ctx
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if self.use_replay():
-            full, rem = divmod(n, self.pool_n)
-            rb, tail = self.replay_batches(quantize, rem)   # instantiated before the timed region
+            g = self.graph_steps(n)
+            full, rem = divmod(n, g)
+            rb, tail = self.replay_batches(quantize, g, rem)   # instantiated before the timed region
             evs = []
             with torch.cuda.stream(env.stream):
                 start.record()
@@ -724,6 +736,7 @@ def sub_line(env, name, mode, steps, warmup, want_roof):
             m.exchange_on = True
         if env.rank == 0:
             rec["parity_max_normalised_error"] = m.parity(m.read_result())
+            rec["parity_rounding_ties"] = parity_ties(m.t, m.x)
         return rec
     finally:
         env.barrier()
@@ -801,7 +814,7 @@ def main():
                "sharded": f"weight rows sharded over {world} ranks, output assembled on every rank ({m.exchange})"}[mode]
         detail = ({"l2": f"rotating pool of {m.pool_n} weight copies ({m.pool_n * m.shard_bytes / 1e6:.0f} MB > L2) per rank",
                     "parallelism": par, "path": m.path(),
-                    "launch": f"replayed batches (CUDA graphs of {m.pool_n} steps + one of the remainder)" if
+                    "launch": f"replayed batches (CUDA graphs of {m.graph_steps(args.steps)} steps, cycling the pool, + one of the remainder)" if
                     m.use_replay() else "one host launch per kernel"})
         line = {
             "metric": metric_name(name), "value": unit_value(m.unit, t, M * units, N, K, step_s), "unit": m.unit,
@@ -817,6 +830,9 @@ def main():
             "e2e": e2e,
             "clocks": clocks,
             "parity_max_normalised_error": check,
+            # exact .5 values in this input's activation quantization (where nearest-even and half-away differ; the
+            # kernels and the oracle share one switch, default nearest-even)
+            "parity_rounding_ties": parity_ties(t, m.x),
         }
         if roof:
             line["roofline"] = roof

@@ -324,6 +324,15 @@ const char* ac_b200_kernel_name(uint32_t index);
 #define AC_B200_GEMM_ONE_TILE_PER_UNIT 64u
 #define AC_B200_GEMM_ONE_ACCUMULATOR 128u
 #define AC_B200_GEMM_TWO_ACCUMULATORS 256u
+/* Upload of a weight tensor with the ggml -> device-regions permutation done on the device: the caller's ggml blocks
+ * (rows x k weights of `type`, ggml_nbytes bytes) are copied through two pinned staging chunks of the context (created
+ * by the first upload: 2 x 32 MB pinned + 2 x 32 MB device) and permuted by a kernel while the CPU fills the other
+ * chunk; returns when the regions at byte `offset` (a multiple of 64) of `buf` are complete. Same bytes as
+ * ac_b200_repack_to_device + ac_runtime_buffer_write (the reference repacks on the CPU while uploading,
+ * adapters/llama/ggml-ameva/ggml-ameva-buffer.cpp:300-330), so ac_b200_repack_from_device still returns the uploaded
+ * blocks exactly. */
+AcResult ac_b200_weight_upload(AcBuffer* buf, size_t offset, uint32_t type, const void* ggml_blocks, uint64_t rows,
+                               uint64_t k);
 /* A host's own kernel under a name of its choosing, dispatched like the built-in ones (batches, replay, events). The
  * reference takes caller kernels as SPIR-V / OpenCL source in AcKernelCreateInfo (ac_runtime.h:560-600); here the caller
  * brings a compiled launcher. fn runs on the recording thread with the device current, must only enqueue work on

@@ -41,6 +41,29 @@ def oracle_mul_mat(ggml_type, blocks, scale, x, N, K, round_mode=0, q8k_mode=0, 
     return y, acc, (q, dq, sm)
 
 
+def count_rounding_ties(ggml_type, x):
+    """How many activation values of x land on an exact .5 before rounding in the quantizer of this weight type's
+    activation scheme (per-32 Q8_0: v = x * (1 / (amax / 127)); per-256 Q8_K: v = x * (-127 / max), max the signed value
+    of largest magnitude): the values on which round-to-nearest-even and round-half-away differ, so a "bit-equal"
+    verdict holds for the stated convention only where this is not 0. The per-token BitNet scheme has one convention."""
+    x = np.ascontiguousarray(x, np.float32)
+    if ggml_type in (Q4_0, Q8_0):
+        b = x.reshape(-1, 32)
+        d = (np.max(np.abs(b), axis=1, keepdims=True) / np.float32(127.0)).astype(np.float32)
+        inv = np.where(d > 0, np.float32(1.0) / np.where(d > 0, d, np.float32(1.0)), np.float32(0.0)).astype(np.float32)
+        v = (b * inv).astype(np.float32)
+    elif ggml_type == Q4_K:
+        b = x.reshape(-1, 256)
+        idx = np.argmax(np.abs(b), axis=1)
+        mx = b[np.arange(b.shape[0]), idx][:, None]
+        inv = np.where(mx != 0, np.float32(-127.0) / np.where(mx != 0, mx, np.float32(1.0)), np.float32(0.0)).astype(np.float32)
+        v = (b * inv).astype(np.float32)
+    else:
+        return 0
+    a = np.abs(v)
+    return int(np.count_nonzero(a - np.floor(a) == np.float32(0.5)))
+
+
 def max_normalised_error(y, ref):
     ref = np.asarray(ref, np.float64)
     return float(np.max(np.abs(np.asarray(y, np.float64) - ref)) / max(np.max(np.abs(ref)), 1e-30))

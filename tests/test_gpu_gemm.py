@@ -9,7 +9,8 @@ import pytest
 
 import oracle
 from conftest import load_pkg
-from helpers import I2_S, Q4_0, Q4_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+from helpers import (I2_S, Q4_0, Q4_K, Q8_0, count_rounding_ties, make_acts, make_weights, max_normalised_error,
+                     oracle_mul_mat)
 
 pytestmark = pytest.mark.gpu
 pkg = load_pkg()
@@ -91,7 +92,9 @@ def test_exact_path_block_sums_at_prefill_m(ctx, t):
 def test_config2_q8_0_prefill_full_size(ctx):
     """Configuration 2: W 11008 x 4096 Q8_0, M = 512; oracle on 384 seeded weight rows x all 512 tokens."""
     err = run_gemm(ctx, Q8_0, 512, 11008, 4096, seed=0, rows_checked=384)
-    print("config 2 max normalised error", err)
+    ties = count_rounding_ties(Q8_0, make_acts(512, 4096, 1))
+    print("config 2 max normalised error", err, "| exact .5 values in the activation quantization:", ties,
+          "of", 512 * 4096, "(bit-equal quantized bytes under round-to-nearest-even, the default of kernels and oracle)")
 
 
 @pytest.mark.parametrize("N,K", [(4096, 4096), (11008, 4096), (4096, 11008)])
