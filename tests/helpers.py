@@ -45,7 +45,7 @@ def count_rounding_ties(ggml_type, x):
     """How many activation values of x land on an exact .5 before rounding in the quantizer of this weight type's
     activation scheme (per-32 Q8_0: v = x * (1 / (amax / 127)); per-256 Q8_K: v = x * (-127 / max), max the signed value
     of largest magnitude): the values on which round-to-nearest-even and round-half-away differ, so a "bit-equal"
-    verdict holds for the stated convention only where this is not 0. The per-token BitNet scheme has one convention."""
+    result holds for the stated convention only where this is not 0. The per-token BitNet scheme has one convention."""
     x = np.ascontiguousarray(x, np.float32)
     if ggml_type in (Q4_0, Q8_0):
         b = x.reshape(-1, 32)
