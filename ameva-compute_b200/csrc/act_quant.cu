@@ -123,14 +123,37 @@ constexpr int kRowThreads = 512;
 // template parameter so that they are registers). SCHEME 0: a piece is one float4, piece i = t + 512 j, eight
 // consecutive lanes hold one 32-unit; SCHEME 1: a piece is 8 consecutive floats, piece i = t + 512 j, a warp holds one
 // 256-block.
-template <int SCHEME, int J>
+// NORM: the row is RMS-normalised first (ggml's rms_norm: squares summed in double, y = x / sqrt(mean + eps), then the
+// optional MUL by a weight row), the f32 result is written to `norm_y` and it is that result which is quantized: one
+// kernel instead of RMS_NORM (+ MUL) and the quantize of the MUL_MAT behind it. ah == nullptr: no fp16 operand (M <= 8).
+struct NormArgs {
+    const float* w;   // weight row [K], or nullptr
+    float* y;         // f32 [M][K]
+    float eps;
+};
+
+// Sum over a CTA of `WARPS` warps in double; every thread gets the result.
+template <int WARPS>
+__device__ __forceinline__ double block_sum_f64(double v, double* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double r = 0.0;
+#pragma unroll
+    for (int i = 0; i < WARPS; ++i) r += red[i];
+    return r;
+}
+
+template <int SCHEME, int J, bool NORM = false>
 __global__ void __launch_bounds__(kRowThreads) quant_rows_f16_kernel(const float* __restrict__ src, int8_t* __restrict__ aq,
                                                                      uint8_t* __restrict__ ad, __half* __restrict__ ah,
                                                                      float* __restrict__ ae, uint32_t K,
-                                                                     uint32_t src_stride, uint32_t mode) {
+                                                                     uint32_t src_stride, uint32_t mode, const NormArgs na) {
     pdl_trigger();   // the GEMM behind this kernel may be scheduled already; it waits for this grid before reading
     pdl_wait();      // the activations may come from the kernel before
     __shared__ float red[kRowThreads / 32];
+    __shared__ double red64[NORM ? kRowThreads / 32 : 1];
     const uint32_t m = blockIdx.x, t = threadIdx.x, lane = t & 31u;
     const float* row = src + (size_t)m * src_stride;
     float amax = 0.0f;
@@ -141,12 +164,38 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_f16_kernel(const float
         for (int j = 0; j < J; ++j) {
             const uint32_t i = t + (uint32_t)kRowThreads * j;
             v[j] = i < P ? *reinterpret_cast<const float4*>(row + 4u * i) : make_float4(0.f, 0.f, 0.f, 0.f);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
         }
+        if constexpr (NORM) {
+            double ss = 0.0;
+#pragma unroll
+            for (int j = 0; j < J; ++j)
+                ss += (double)__fmul_rn(v[j].x, v[j].x) + (double)__fmul_rn(v[j].y, v[j].y) +
+                      (double)__fmul_rn(v[j].z, v[j].z) + (double)__fmul_rn(v[j].w, v[j].w);
+            ss = block_sum_f64<kRowThreads / 32>(ss, red64);
+            const float mean = (float)(ss / (double)K);
+            const float scale = __fdiv_rn(1.0f, sqrtf(mean + na.eps));
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                const uint32_t i = t + (uint32_t)kRowThreads * j;
+                if (i < P) {
+                    float4 y = make_float4(__fmul_rn(v[j].x, scale), __fmul_rn(v[j].y, scale), __fmul_rn(v[j].z, scale),
+                                           __fmul_rn(v[j].w, scale));
+                    if (na.w) {
+                        const float4 w4 = __ldg(reinterpret_cast<const float4*>(na.w + 4u * i));
+                        y = make_float4(__fmul_rn(y.x, w4.x), __fmul_rn(y.y, w4.y), __fmul_rn(y.z, w4.z), __fmul_rn(y.w, w4.w));
+                    }
+                    *reinterpret_cast<float4*>(na.y + (size_t)m * K + 4u * i) = y;
+                    v[j] = y;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < J; ++j)
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));
         amax = block_max<kRowThreads / 32>(amax, red);
         float s, inv;
         row_factor(amax, s, inv);
-        if (t == 0) ae[m] = inv;
+        if (t == 0 && ae) ae[m] = inv;
         uint32_t* adw = reinterpret_cast<uint32_t*>(ad);
 #pragma unroll
         for (int j = 0; j < J; ++j) {
@@ -158,13 +207,15 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_f16_kernel(const float
             if (live) {
                 reinterpret_cast<uint32_t*>(aq + (size_t)m * K)[i] = pack_q4(q);
                 if (sub == 0) adw[(size_t)m * U + u] = scale_word_q8_0(d, sum);
-                const float dh = __fmul_rn(h2f(f2h(d)), s);   // the fp16-rounded scale the dot product uses, times 2^-e
-                const __half2 h01 = __floats2half2_rn((float)q[0] * dh, (float)q[1] * dh);
-                const __half2 h23 = __floats2half2_rn((float)q[2] * dh, (float)q[3] * dh);
-                uint2 o;
-                o.x = *reinterpret_cast<const uint32_t*>(&h01);
-                o.y = *reinterpret_cast<const uint32_t*>(&h23);
-                *reinterpret_cast<uint2*>(ah + (size_t)m * K + 4u * i) = o;
+                if (ah) {
+                    const float dh = __fmul_rn(h2f(f2h(d)), s);   // the fp16-rounded scale the dot product uses, times 2^-e
+                    const __half2 h01 = __floats2half2_rn((float)q[0] * dh, (float)q[1] * dh);
+                    const __half2 h23 = __floats2half2_rn((float)q[2] * dh, (float)q[3] * dh);
+                    uint2 o;
+                    o.x = *reinterpret_cast<const uint32_t*>(&h01);
+                    o.y = *reinterpret_cast<const uint32_t*>(&h23);
+                    *reinterpret_cast<uint2*>(ah + (size_t)m * K + 4u * i) = o;
+                }
             }
         }
     } else {
@@ -181,13 +232,48 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_f16_kernel(const float
             }
             x[j][0] = x0.x; x[j][1] = x0.y; x[j][2] = x0.z; x[j][3] = x0.w;
             x[j][4] = x1.x; x[j][5] = x1.y; x[j][6] = x1.z; x[j][7] = x1.w;
+        }
+        if constexpr (NORM) {
+            double ss = 0.0;
+#pragma unroll
+            for (int j = 0; j < J; ++j)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss += (double)__fmul_rn(x[j][i], x[j][i]);
+            ss = block_sum_f64<kRowThreads / 32>(ss, red64);
+            const float mean = (float)(ss / (double)K);
+            const float scale = __fdiv_rn(1.0f, sqrtf(mean + na.eps));
+#pragma unroll
+            for (int j = 0; j < J; ++j) {
+                const uint32_t b = (t >> 5) + (uint32_t)(kRowThreads / 32) * j;
+                if (b < B) {
+                    const uint32_t c0 = 256u * b + 8u * lane;
+                    float wv[8];
+                    if (na.w) {
+                        const float4 w0 = __ldg(reinterpret_cast<const float4*>(na.w + c0));
+                        const float4 w1 = __ldg(reinterpret_cast<const float4*>(na.w + c0 + 4));
+                        wv[0] = w0.x; wv[1] = w0.y; wv[2] = w0.z; wv[3] = w0.w;
+                        wv[4] = w1.x; wv[5] = w1.y; wv[6] = w1.z; wv[7] = w1.w;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float y = __fmul_rn(x[j][i], scale);
+                        if (na.w) y = __fmul_rn(y, wv[i]);
+                        x[j][i] = y;
+                    }
+                    float* yo = na.y + (size_t)m * K + c0;
+                    *reinterpret_cast<float4*>(yo) = make_float4(x[j][0], x[j][1], x[j][2], x[j][3]);
+                    *reinterpret_cast<float4*>(yo + 4) = make_float4(x[j][4], x[j][5], x[j][6], x[j][7]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < J; ++j)
 #pragma unroll
             for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(x[j][i]));
-        }
         amax = block_max<kRowThreads / 32>(amax, red);
         float s, inv;
         row_factor(amax, s, inv);
-        if (t == 0) ae[m] = inv;
+        if (t == 0 && ae) ae[m] = inv;
 #pragma unroll
         for (int j = 0; j < J; ++j) {
             const uint32_t b = (t >> 5) + (uint32_t)(kRowThreads / 32) * j;
@@ -204,14 +290,16 @@ __global__ void __launch_bounds__(kRowThreads) quant_rows_f16_kernel(const float
                 w1 |= (uint32_t)(q[i + 4] & 0xFF) << (8 * i);
             }
             *reinterpret_cast<uint2*>(aq + (size_t)m * K + 256u * b + 8u * lane) = make_uint2(w0, w1);
-            const float ds = __fmul_rn(d, s);
-            uint32_t o[4];
+            if (ah) {
+                const float ds = __fmul_rn(d, s);
+                uint32_t o[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const __half2 hh = __floats2half2_rn((float)q[2 * i] * ds, (float)q[2 * i + 1] * ds);
-                o[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                for (int i = 0; i < 4; ++i) {
+                    const __half2 hh = __floats2half2_rn((float)q[2 * i] * ds, (float)q[2 * i + 1] * ds);
+                    o[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                }
+                *reinterpret_cast<uint4*>(ah + (size_t)m * K + 256u * b + 8u * lane) = make_uint4(o[0], o[1], o[2], o[3]);
             }
-            *reinterpret_cast<uint4*>(ah + (size_t)m * K + 256u * b + 8u * lane) = make_uint4(o[0], o[1], o[2], o[3]);
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);  // lanes 2j, 2j+1 -> 16-element group j
             uint8_t* blk = ad + ((size_t)m * B + b) * kABBytes;
             if ((lane & 1u) == 0u) reinterpret_cast<int16_t*>(blk)[lane >> 1] = (int16_t)sum;
@@ -366,10 +454,26 @@ AcResult launch_quant_a8b(const LaunchArgs& a) {
 //   bindings 0 src f32, 1 AQ, 2 AD (per-32 scale words) or AB (per-256 records), 3 AH fp16 [M][K] = fp16(q * d * s_m),
 //            4 AE f32 [M] = 1 / s_m (s_m the power of two that brings row m's largest magnitude into [1, 2))
 //   push {M, K, src_stride (floats), round_mode / mode};  K <= 32768
-template <int SCHEME, int J>
-static void launch_rows_j(const LaunchArgs& a, uint32_t M, uint32_t K, uint32_t stride, uint32_t mode) {
-    launch_pdl(quant_rows_f16_kernel<SCHEME, J>, dim3(M), dim3(kRowThreads), 0, a.stream, (const float*)a.ptr[0],
-               (int8_t*)a.ptr[1], (uint8_t*)a.ptr[2], (__half*)a.ptr[3], (float*)a.ptr[4], K, stride, mode);
+template <int SCHEME, int J, bool NORM>
+static void launch_rows_j(const LaunchArgs& a, const float* src, int8_t* aq, uint8_t* ad, __half* ah, float* ae, uint32_t M,
+                          uint32_t K, uint32_t stride, uint32_t mode, const NormArgs& na) {
+    launch_pdl(quant_rows_f16_kernel<SCHEME, J, NORM>, dim3(M), dim3(kRowThreads), 0, a.stream, src, aq, ad, ah, ae, K, stride,
+               mode, na);
+}
+
+// pieces per thread: a row of K floats over 512 threads, 4 (per-32) or 8 (per-256) floats to a piece
+template <int SCHEME, bool NORM>
+static AcResult launch_rows(const LaunchArgs& a, const float* src, int8_t* aq, uint8_t* ad, __half* ah, float* ae, uint32_t M,
+                            uint32_t K, uint32_t stride, uint32_t mode, const NormArgs& na) {
+    const uint32_t per_thread = (K + (SCHEME ? 4095u : 2047u)) / (SCHEME ? 4096u : 2048u);
+    if (per_thread <= 1) launch_rows_j<SCHEME, 1, NORM>(a, src, aq, ad, ah, ae, M, K, stride, mode, na);
+    else if (per_thread <= 2) launch_rows_j<SCHEME, 2, NORM>(a, src, aq, ad, ah, ae, M, K, stride, mode, na);
+    else if (per_thread <= 4) launch_rows_j<SCHEME, 4, NORM>(a, src, aq, ad, ah, ae, M, K, stride, mode, na);
+    else if (per_thread <= 8) launch_rows_j<SCHEME, 8, NORM>(a, src, aq, ad, ah, ae, M, K, stride, mode, na);
+    else if (per_thread <= 16 && SCHEME == 0)
+        launch_rows_j<SCHEME, (SCHEME == 0 ? 16 : 8), NORM>(a, src, aq, ad, ah, ae, M, K, stride, mode, na);
+    else return AC_ERR_INVALID_SHAPE;   // K above 32768: beyond the rows this kernel keeps in registers
+    return check_launch();
 }
 
 template <int SCHEME>
@@ -382,18 +486,44 @@ static AcResult launch_quant_rows(const LaunchArgs& a) {
         a.range[3] < (uint64_t)M * K * 2u || a.range[4] < (uint64_t)M * 4u)
         return AC_ERR_INVALID_BUFFER_SIZE;
     if (((uintptr_t)a.ptr[0] & 15u) || ((uintptr_t)a.ptr[3] & 15u)) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
-    // pieces per thread: a row of K floats over 512 threads, 4 (per-32) or 8 (per-256) floats to a piece
-    const uint32_t per_thread = (K + (SCHEME ? 4095u : 2047u)) / (SCHEME ? 4096u : 2048u);
-    if (per_thread <= 1) launch_rows_j<SCHEME, 1>(a, M, K, stride, mode);
-    else if (per_thread <= 2) launch_rows_j<SCHEME, 2>(a, M, K, stride, mode);
-    else if (per_thread <= 4) launch_rows_j<SCHEME, 4>(a, M, K, stride, mode);
-    else if (per_thread <= 8) launch_rows_j<SCHEME, 8>(a, M, K, stride, mode);
-    else if (per_thread <= 16 && SCHEME == 0) launch_rows_j<SCHEME, (SCHEME == 0 ? 16 : 8)>(a, M, K, stride, mode);
-    else return AC_ERR_INVALID_SHAPE;   // K above 32768: beyond the rows this kernel keeps in registers
-    return check_launch();
+    const NormArgs na = {nullptr, nullptr, 0.0f};
+    return launch_rows<SCHEME, false>(a, (const float*)a.ptr[0], (int8_t*)a.ptr[1], (uint8_t*)a.ptr[2], (__half*)a.ptr[3],
+                                      (float*)a.ptr[4], M, K, stride, mode, na);
 }
 AcResult launch_quant_a8_f16(const LaunchArgs& a) { return launch_quant_rows<0>(a); }
 AcResult launch_quant_a8b_f16(const LaunchArgs& a) { return launch_quant_rows<1>(a); }
+
+// ameva_rms_norm_quant_a8 / ameva_rms_norm_quant_a8b: RMS norm (+ MUL by a weight row) and the activation quantize of
+// the MUL_MAT that consumes it, one kernel (the reference fuses RMS_NORM + MUL, ggml-ameva.cpp:4347-4357, and norm +
+// quantize for BitNet, src/shaders/bitnet_norm_q8.comp; here for the per-32 / per-256 schemes).
+//   bindings 0 x f32 [M][src_stride], 1 w f32 [K] (any buffer when has_weight = 0), 2 y f32 [M][K] (the normalised rows:
+//            what RMS_NORM (+ MUL) writes), 3 AQ, 4 AD or AB, 5 AH, 6 AE (any buffers when write_h = 0)
+//   push {M, K (<= 32768), src_stride, round_mode / mode, eps (float bits), has_weight, write_h}
+// AQ / AD / AB are the bytes ameva_quant_a8 / a8b produce from y.
+template <int SCHEME>
+static AcResult launch_rms_norm_quant(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], K = a.push[1], stride = a.push[2], mode = a.push[3], has_w = a.push[5], write_h = a.push[6];
+    const uint32_t kmask = SCHEME ? 255u : 31u;
+    if (M == 0 || K == 0 || (K & kmask) || stride < K || (stride & 3u) || mode > 1u || has_w > 1u || write_h > 1u)
+        return AC_ERR_KERNEL_ARG_INVALID;
+    float eps;
+    memcpy(&eps, &a.push[4], 4);
+    if (!(eps >= 0.0f)) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t scale_bytes = SCHEME ? (uint64_t)M * (K >> 8) * kABBytes : (uint64_t)M * (K >> 5) * 4u;
+    if (a.range[0] < ((uint64_t)(M - 1) * stride + K) * 4u || (has_w && a.range[1] < (uint64_t)K * 4u) ||
+        a.range[2] < (uint64_t)M * K * 4u || a.range[3] < (uint64_t)M * K || a.range[4] < scale_bytes ||
+        (write_h && (a.range[5] < (uint64_t)M * K * 2u || a.range[6] < (uint64_t)M * 4u)))
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if (((uintptr_t)a.ptr[0] & 15u) || ((uintptr_t)a.ptr[1] & 15u) || ((uintptr_t)a.ptr[2] & 15u) ||
+        (write_h && ((uintptr_t)a.ptr[5] & 15u)))
+        return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    const NormArgs na = {has_w ? (const float*)a.ptr[1] : nullptr, (float*)a.ptr[2], eps};
+    return launch_rows<SCHEME, true>(a, (const float*)a.ptr[0], (int8_t*)a.ptr[3], (uint8_t*)a.ptr[4],
+                                     write_h ? (__half*)a.ptr[5] : nullptr, write_h ? (float*)a.ptr[6] : nullptr, M, K, stride,
+                                     mode, na);
+}
+AcResult launch_rms_norm_quant_a8(const LaunchArgs& a) { return launch_rms_norm_quant<0>(a); }
+AcResult launch_rms_norm_quant_a8b(const LaunchArgs& a) { return launch_rms_norm_quant<1>(a); }
 
 // bitnet_norm_q8: bindings 0 a, 1 b, 2 w, 3 y, 4 q, 5 act, 6 qeo; push {dim, eps_bits, mode, do_norm}; grid.x = rows
 // (argument contract of src/shaders/bitnet_norm_q8.comp:20-44, extended from one row to grid.x rows).

@@ -506,6 +506,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     }
     const uint32_t it_begin = unit * p.iters, it_end = min(it_begin + p.iters, p.tiles * KB);
     uint32_t* status = p.status;
+    AMV_TRACE_BEGIN(blockIdx.x)
+    AMV_TRACE_STAMP(0)
+    AMV_TRACE_SHARE(ctl->trace_slot)
     const bool dg = (kdiag & 16u) != 0u;   // diagnostic run: account the cycles spent in barrier waits
     if (threadIdx.x == 0) {
         trace(p, 0);
@@ -647,6 +650,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     tc_fence_after();
                     const uint64_t db = make_smem_desc(smem_u32(sB + st.idx * b_bytes));
                     const uint32_t ta = tmem_a + st.idx * 32u;
+                    if (kb == sg.kb0 && nseg < 2u) { AMV_TRACE_STAMP_AT(ctl->trace_slot, 2u + 5u * nseg) }
                     const long long ti = dg ? clock64() : 0;
                     if (!(kdiag & 4u)) {
 #pragma unroll
@@ -658,6 +662,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 }
                 if (!ok) ctl->abort = 1u;   // visible to whoever passes the accumulator barrier below
                 umma_commit<PAIR>(accum);
+                if (nseg < 2u) { AMV_TRACE_STAMP_AT(ctl->trace_slot, 3u + 5u * nseg) }
                 ++nseg;
             }
             trace_val(p, 1600u, w_full);
@@ -956,6 +961,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
         trace(p, 522);
         trace_cta(p, 1);
     }
+    AMV_TRACE_STAMP(12)
 }
 
 // ---- the wide kernel: two accumulators per CTA pair ------------------------------------------------------------------

@@ -453,9 +453,11 @@ gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Grouped launch: one activation row against up to four weight matrices of the same type and K (the q / k / v or the
-// gate / up projections of a decoder layer, which share src1), one launch. The fp32 row is quantized once per CTA in
-// shared memory (the FQ path) and every warp serves R rows of one of the matrices: the rows of all matrices form one
-// row space, `row_end` holding the running totals. Results are those of the separate launches, bit for bit.
+// gate / up projections of a decoder layer, which share src1), one launch. Every warp serves R rows of one of the
+// matrices: the rows of all matrices form one row space, `row_end` holding the running totals. FQ: the fp32 row is
+// quantized by every CTA in its shared memory (one launch in all: what a host that launches kernel by kernel wants);
+// otherwise the row was quantized once by the kernel before (ameva_quant_a8 / a8b), which is faster on the device
+// (4096-wide q/k/v of Q4_K: 13.1 us with FQ). Results are those of the separate launches, bit for bit.
 // ---------------------------------------------------------------------------------------------------------------------
 struct WeightGroup {
     const void* Q[4];
@@ -465,13 +467,17 @@ struct WeightGroup {
     uint32_t count;
 };
 
-template <int TYPE>   // 0 Q4_0, 1 Q8_0, 2 Q4_K
+template <int TYPE, bool FQ>   // 0 Q4_0, 1 Q8_0, 2 Q4_K
 __global__ void __launch_bounds__(kGemvThreads, TYPE == 2 ? 3 : 1)
-gemv_group_fq_kernel(const WeightGroup g, const float* __restrict__ X, uint32_t K, uint32_t qmode) {
+gemv_group_kernel(const WeightGroup g, const float* __restrict__ X, const int8_t* __restrict__ AQ,
+                  const void* __restrict__ AD, uint32_t K, uint32_t qmode) {
     const uint32_t warp = (blockIdx.x * kGemvThreads + threadIdx.x) >> 5;
     uint32_t row = warp * 2u, j = 0, start = 0;
     const uint32_t total = g.row_end[g.count - 1];
-    if (row >= total) row = total - 2u;   // (idle warps of the last CTA repeat its last row pair: they must reach the barrier)
+    if (row >= total) {
+        if (!FQ) return;
+        row = total - 2u;   // (idle warps of the last CTA repeat its last row pair: they must reach the quantize barrier)
+    }
 #pragma unroll
     for (uint32_t i = 0; i < 3u; ++i)
         if (i + 1u < g.count && row >= g.row_end[i]) {
@@ -481,17 +487,17 @@ gemv_group_fq_kernel(const WeightGroup g, const float* __restrict__ X, uint32_t 
     const uint32_t N = g.row_end[j] - start, w = (row - start) >> 1;
     const Epi ep = {nullptr, nullptr, 0u};
     if constexpr (TYPE == 0) {
-        gemv_q4_0_body<1, 2, false, true>((const uint4*)g.Q[j], (const uint16_t*)g.S[j], nullptr, nullptr, g.dst[j], nullptr,
-                                          N, K, N, ep, X, qmode, w);
+        gemv_q4_0_body<1, 2, false, FQ>((const uint4*)g.Q[j], (const uint16_t*)g.S[j], AQ, (const uint32_t*)AD, g.dst[j],
+                                        nullptr, N, K, N, ep, X, qmode, w);
     } else if constexpr (TYPE == 1) {
-        gemv_q8_0_body<1, 2, false, true>((const u32x8*)g.Q[j], (const uint16_t*)g.S[j], nullptr, nullptr, g.dst[j], nullptr,
-                                          N, K, N, ep, X, qmode, w);
+        gemv_q8_0_body<1, 2, false, FQ>((const u32x8*)g.Q[j], (const uint16_t*)g.S[j], AQ, (const uint32_t*)AD, g.dst[j],
+                                        nullptr, N, K, N, ep, X, qmode, w);
     } else {
         DstList dl;
         dl.n = 1u;
         dl.p[0] = g.dst[j];
-        gemv_q4_K_body<1, 2, false, 1, true>((const u32x8*)g.Q[j], (const uint4*)g.S[j], nullptr, nullptr, dl, nullptr, N, K,
-                                             N, ep, X, qmode, w);
+        gemv_q4_K_body<1, 2, false, 1, FQ>((const u32x8*)g.Q[j], (const uint4*)g.S[j], AQ, (const uint8_t*)AD, dl, nullptr, N,
+                                           K, N, ep, X, qmode, w);
     }
 }
 
@@ -757,12 +763,15 @@ static AcResult launch_fq(const LaunchArgs& a) {
 //   bindings (Q, S, dst f32 [N_j]) of matrix 0, 1, 2, 3 (unused slots repeat matrix 0), then 12: x f32 [K]
 //   push {K, quantize mode, count (1..4), N_0, N_1, N_2, N_3}     every N_j a multiple of 2
 // The bits of every dst are those of the separate ameva_mmv*_fq launches.
-template <int TYPE>
-static AcResult launch_group_fq(const LaunchArgs& a) {
+// ameva_mmvqg_q4_0 / ameva_mmvqg_q8_0 / ameva_mmvqgb_q4_K: the same launch over a row that the quantize kernel before it
+// has quantized once:  bindings (Q, S, dst) x 4 as above, then 12: AQ int8 [K], 13: AD (per-32 scale words) or AB (per-256
+// records);  push {K, 0, count, N_0 .. N_3}. The bits of every dst are those of the separate ameva_mmvq* launches.
+template <int TYPE, bool FQ>
+static AcResult launch_group(const LaunchArgs& a) {
     const uint32_t K = a.push[0], qmode = a.push[1], count = a.push[2];
     const uint32_t kmask = TYPE == 2 ? 255u : 31u;
     if (count == 0 || count > 4u || K == 0 || (K & kmask) || qmode > 1u) return AC_ERR_KERNEL_ARG_INVALID;
-    if (K > kFusedQuantMaxK) return AC_ERR_INVALID_SHAPE;
+    if (FQ && K > kFusedQuantMaxK) return AC_ERR_INVALID_SHAPE;
     const uint64_t units = TYPE == 2 ? (K >> 8) : (K >> 5);
     const uint64_t qb = TYPE == 0 ? kQ40QBytes : TYPE == 1 ? kQ80QBytes : kQ4KQBytes, sb = TYPE == 2 ? kQ4KSBytes : 2u;
     WeightGroup g;
@@ -784,16 +793,27 @@ static AcResult launch_group_fq(const LaunchArgs& a) {
         g.row_end[j] = (uint32_t)rows;
     }
     for (uint32_t j = count; j < 4u; ++j) g.row_end[j] = (uint32_t)rows;
-    if (a.range[12] < (uint64_t)K * 4u) return AC_ERR_INVALID_BUFFER_SIZE;
-    if ((uintptr_t)a.ptr[12] % 16u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
-    const size_t smem = (size_t)K + (TYPE == 2 ? (size_t)units * kABBytes : (size_t)units * 4u);
-    launch_pdl(gemv_group_fq_kernel<TYPE>, dim3(gemv_blocks<2>((uint32_t)rows)), dim3(kGemvThreads), smem, a.stream, g,
-               (const float*)a.ptr[12], K, qmode);
+    if (FQ) {
+        if (a.range[12] < (uint64_t)K * 4u) return AC_ERR_INVALID_BUFFER_SIZE;
+        if ((uintptr_t)a.ptr[12] % 16u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+        const size_t smem = (size_t)K + (TYPE == 2 ? (size_t)units * kABBytes : (size_t)units * 4u);
+        launch_pdl(gemv_group_kernel<TYPE, true>, dim3(gemv_blocks<2>((uint32_t)rows)), dim3(kGemvThreads), smem, a.stream, g,
+                   (const float*)a.ptr[12], (const int8_t*)nullptr, (const void*)nullptr, K, qmode);
+    } else {
+        if (a.range[12] < (uint64_t)K || a.range[13] < units * (TYPE == 2 ? (uint64_t)kABBytes : 4u))
+            return AC_ERR_INVALID_BUFFER_SIZE;
+        if (((uintptr_t)a.ptr[12] & 15u) || ((uintptr_t)a.ptr[13] & 15u)) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+        launch_pdl(gemv_group_kernel<TYPE, false>, dim3(gemv_blocks<2>((uint32_t)rows)), dim3(kGemvThreads), 0, a.stream, g,
+                   (const float*)nullptr, (const int8_t*)a.ptr[12], (const void*)a.ptr[13], K, 0u);
+    }
     return check_launch();
 }
-AcResult launch_mmvqg_q4_0_fq(const LaunchArgs& a) { return launch_group_fq<0>(a); }
-AcResult launch_mmvqg_q8_0_fq(const LaunchArgs& a) { return launch_group_fq<1>(a); }
-AcResult launch_mmvqgb_q4_K_fq(const LaunchArgs& a) { return launch_group_fq<2>(a); }
+AcResult launch_mmvqg_q4_0_fq(const LaunchArgs& a) { return launch_group<0, true>(a); }
+AcResult launch_mmvqg_q8_0_fq(const LaunchArgs& a) { return launch_group<1, true>(a); }
+AcResult launch_mmvqgb_q4_K_fq(const LaunchArgs& a) { return launch_group<2, true>(a); }
+AcResult launch_mmvqg_q4_0(const LaunchArgs& a) { return launch_group<0, false>(a); }
+AcResult launch_mmvqg_q8_0(const LaunchArgs& a) { return launch_group<1, false>(a); }
+AcResult launch_mmvqgb_q4_K(const LaunchArgs& a) { return launch_group<2, false>(a); }
 AcResult launch_mmvq_q4_0_fq(const LaunchArgs& a) { return launch_fq<0>(a); }
 AcResult launch_mmvq_q8_0_fq(const LaunchArgs& a) { return launch_fq<1>(a); }
 AcResult launch_mmvqb_q4_K_fq(const LaunchArgs& a) { return launch_fq<2>(a); }

@@ -20,6 +20,8 @@ AcResult launch_quant_a8(const LaunchArgs&);
 AcResult launch_quant_a8b(const LaunchArgs&);
 AcResult launch_quant_a8_f16(const LaunchArgs&);
 AcResult launch_quant_a8b_f16(const LaunchArgs&);
+AcResult launch_rms_norm_quant_a8(const LaunchArgs&);
+AcResult launch_rms_norm_quant_a8b(const LaunchArgs&);
 AcResult launch_bitnet_norm_q8(const LaunchArgs&);
 AcResult launch_mmtc_q4_0(const LaunchArgs&);
 AcResult launch_mmtc_q8_0(const LaunchArgs&);
@@ -56,6 +58,9 @@ AcResult launch_mmvqb_q4_K_dump(const LaunchArgs&);
 AcResult launch_mmvqg_q4_0_fq(const LaunchArgs&);
 AcResult launch_mmvqg_q8_0_fq(const LaunchArgs&);
 AcResult launch_mmvqgb_q4_K_fq(const LaunchArgs&);
+AcResult launch_mmvqg_q4_0(const LaunchArgs&);
+AcResult launch_mmvqg_q8_0(const LaunchArgs&);
+AcResult launch_mmvqgb_q4_K(const LaunchArgs&);
 AcResult launch_bitnet_gemv_i2_s(const LaunchArgs&);
 AcResult launch_bitnet_gemv_i2_s_acc(const LaunchArgs&);
 
@@ -64,6 +69,8 @@ static const KernelEntry kTable[] = {
     {"ameva_quant_a8b", 3, 16, {256, 1, 1}, launch_quant_a8b},
     {"ameva_quant_a8_f16", 5, 16, {256, 1, 1}, launch_quant_a8_f16},
     {"ameva_quant_a8b_f16", 5, 16, {256, 1, 1}, launch_quant_a8b_f16},
+    {"ameva_rms_norm_quant_a8", 7, 28, {512, 1, 1}, launch_rms_norm_quant_a8},
+    {"ameva_rms_norm_quant_a8b", 7, 28, {512, 1, 1}, launch_rms_norm_quant_a8b},
     {"bitnet_norm_q8", 7, 16, {256, 1, 1}, launch_bitnet_norm_q8},
     {"ameva_mmtc_q4_0", 5, 20, {320, 1, 1}, launch_mmtc_q4_0},
     {"ameva_mmtc_q8_0", 5, 20, {320, 1, 1}, launch_mmtc_q8_0},
@@ -100,6 +107,9 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvqg_q4_0_fq", 13, 28, {256, 1, 1}, launch_mmvqg_q4_0_fq},
     {"ameva_mmvqg_q8_0_fq", 13, 28, {256, 1, 1}, launch_mmvqg_q8_0_fq},
     {"ameva_mmvqgb_q4_K_fq", 13, 28, {256, 1, 1}, launch_mmvqgb_q4_K_fq},
+    {"ameva_mmvqg_q4_0", 14, 28, {256, 1, 1}, launch_mmvqg_q4_0},
+    {"ameva_mmvqg_q8_0", 14, 28, {256, 1, 1}, launch_mmvqg_q8_0},
+    {"ameva_mmvqgb_q4_K", 14, 28, {256, 1, 1}, launch_mmvqgb_q4_K},
     {"bitnet_gemv_i2_s_l32w1", 4, 24, {32, 4, 1}, launch_bitnet_gemv_i2_s},
     {"bitnet_gemv_i2_s_l16w2", 4, 24, {16, 8, 1}, launch_bitnet_gemv_i2_s},
     {"bitnet_gemv_i2_s_l8w4", 4, 24, {8, 16, 1}, launch_bitnet_gemv_i2_s},

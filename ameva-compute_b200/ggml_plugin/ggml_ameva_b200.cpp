@@ -474,6 +474,12 @@ struct Recorder {
     int64_t gpu_ops = 0, mul_mats = 0, mmq = 0, mmqb = 0, fused = 0;
 };
 
+struct QuantizedRows {
+    const void* data = nullptr;
+    uint32_t M = 0, K = 0;
+    int scheme = -1;
+};
+
 bool dispatch(Recorder& r, const char* name, const AcBufferBinding* b, uint32_t nb, const uint32_t* push, size_t push_bytes) {
     AcKernel* k = kernel(r.be, name);
     if (!k) return false;
@@ -547,6 +553,9 @@ bool record_mul_mat(Recorder& r, const ggml_tensor* node, const Epilogue& ep) {
     const AcBufferBinding X = bind_tensor(x), Y = bind_tensor(node);
     r.mul_mats++;
     if (ep.mode) path = AC_B200_PATH_GEMV;   // the fused consumers live on the register-staged one-row kernels
+    // the row sits quantized in the scratch already (the fused RMS norm + quantize, or an earlier MUL_MAT on it)
+    if (path == AC_B200_PATH_GEMV_FQ && r.q_data == x->data && r.q_M == M && r.q_K == K && (r.q_scheme & 1) == (q4k ? 1 : 0))
+        path = AC_B200_PATH_GEMV;
     if (path != AC_B200_PATH_GEMM_TC) {
         r.mmq++;
         if (q4k) r.mmqb++;
@@ -615,13 +624,23 @@ bool record_group(Recorder& r, const ggml_tensor* const* nodes, uint32_t count) 
         b[3 * j + 2] = bind_tensor(nodes[jj]);
         if (j < count) push[3 + j] = w[j].N;
     }
-    b[12] = bind_tensor(nodes[0]->src[1]);
     r.mul_mats += count;
     r.mmq += count;
     if (q4k) r.mmqb += count;
     r.fused += count - 1;
-    return dispatch(r, (std::string(q4k ? "ameva_mmvqgb_" : "ameva_mmvqg_") + type_name(w[0].type) + "_fq").c_str(), b, 13, push,
-                    sizeof(push));
+    const ggml_tensor* x = nodes[0]->src[1];
+    const std::string name = std::string(q4k ? "ameva_mmvqgb_" : "ameva_mmvqg_") + type_name(w[0].type);
+    // the row is in the scratch already (the fused RMS norm + quantize wrote it, or an earlier MUL_MAT): no quantize
+    // inside the launch
+    if (r.q_data == x->data && r.q_M == 1 && r.q_K == w[0].K && (r.q_scheme & 1) == (q4k ? 1 : 0)) {
+        AcBufferBinding bb[14];
+        for (int i = 0; i < 12; ++i) bb[i] = b[i];
+        bb[12] = bind(r.be->aq, 0, w[0].K);
+        bb[13] = bind(r.be->ad, 0, q4k ? (uint64_t)(w[0].K / 256) * 48u : (uint64_t)(w[0].K / 32) * 4u);
+        return dispatch(r, name.c_str(), bb, 14, push, sizeof(push));
+    }
+    b[12] = bind_tensor(x);
+    return dispatch(r, (name + "_fq").c_str(), b, 13, push, sizeof(push));
 }
 
 // Can node b join the group that starts with node a? (one activation row, the same src1, type and K, an even N, the
@@ -673,6 +692,37 @@ bool rms_mul_pair(const ggml_tensor* n0, const ggml_tensor* n1) {
     if (!wt || wt == n0 || n_rows(wt) != 1 || wt->ne[0] != n0->ne[0] || n_elems(n1) != n_elems(n0)) return false;
     if (overlap(n1, wt)) return false;
     if (overlap(n1, n0->src[0]) && !same_elements(n1, n0->src[0])) return false;
+    return true;
+}
+
+// RMS_NORM (+ the MUL by a weight row) whose result is the activation of the MUL_MAT `consumer`: one kernel writes the
+// normalised rows and their quantized form into the scratch (ameva_rms_norm_quant_a8 / a8b), so the MUL_MAT (or the
+// grouped launch it starts) finds its activations quantized. False when the pattern does not apply (nothing recorded).
+bool record_norm_quantize(Recorder& r, const ggml_tensor* node, const ggml_tensor* fused_mul, const ggml_tensor* consumer,
+                          QuantizedRows* fresh) {
+    const ggml_tensor* out = fused_mul ? fused_mul : node;
+    if (!consumer || consumer->op != GGML_OP_MUL_MAT || consumer->src[1] != out) return false;
+    WeightRef w;
+    uint32_t path = 0;
+    if (mul_mat_reason(consumer, &w, &path)) return false;
+    const uint32_t M = (uint32_t)n_rows(out), K = (uint32_t)out->ne[0];
+    if (K != w.K || K > 32768u || (uint64_t)n_rows(out) != (uint64_t)out->ne[1] || !ggml_is_contiguous(node->src[0])) return false;
+    const bool q4k = w.type == GGML_TYPE_Q4_K, tc = path == AC_B200_PATH_GEMM_TC;
+    if (path == AC_B200_PATH_GEMV && M > 8) return false;   // the exact chunked path quantizes per chunk layout as usual
+    const ggml_tensor* wt = nullptr;
+    if (fused_mul) wt = fused_mul->src[0] == node ? fused_mul->src[1] : fused_mul->src[0];
+    const uint64_t ad_need = q4k ? (uint64_t)M * (K / 256) * 48u : (uint64_t)M * (K / 32) * 4u;
+    AcBufferBinding b[7] = {bind_tensor(node->src[0]), wt ? bind_tensor(wt) : bind_tensor(node->src[0]), bind_tensor(out),
+                            bind(r.be->aq, 0, (uint64_t)M * K), bind(r.be->ad, 0, ad_need),
+                            tc ? bind(r.be->ah, 0, (uint64_t)M * K * 2) : bind(r.be->aq, 0, (uint64_t)M * K),
+                            tc ? bind(r.be->ae, 0, (uint64_t)M * 4) : bind(r.be->aq, 0, (uint64_t)M * K)};
+    uint32_t push[7] = {M, K, K, 0, 0, wt ? 1u : 0u, tc ? 1u : 0u};
+    memcpy(&push[4], &node->op_params[0], 4);   // eps
+    if (!dispatch(r, q4k ? "ameva_rms_norm_quant_a8b" : "ameva_rms_norm_quant_a8", b, 7, push, sizeof(push))) return false;
+    fresh->data = out->data;
+    fresh->M = M;
+    fresh->K = K;
+    fresh->scheme = (q4k ? 1 : 0) + (tc ? 2 : 0);
     return true;
 }
 
@@ -751,6 +801,7 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
         const int j = next_compute_node(cgraph, i, n);
         const ggml_tensor* next = j >= 0 ? ggml_graph_node(cgraph, j) : nullptr;
         int consumed_upto = i;   // index of the last node this step computes
+        QuantizedRows fresh;     // rows this step itself quantized into the scratch while producing them
         if (node->op == GGML_OP_MUL_MAT) {
             // a run of one-row MUL_MATs sharing src1: one launch (up to four)
             const ggml_tensor* grp[4] = {node, nullptr, nullptr, nullptr};
@@ -778,11 +829,17 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
                     consumed_upto = j;
                 }
             }
-        } else if (node->op == GGML_OP_RMS_NORM && rms_mul_pair(node, next)) {
-            ok = record_elementwise(r, node, next);
-            r.gpu_ops += 2;
-            r.fused += 1;
-            consumed_upto = j;
+        } else if (node->op == GGML_OP_RMS_NORM) {
+            const bool pair = rms_mul_pair(node, next);
+            // the MUL_MAT that consumes the result (the next computing node): its quantize joins this launch
+            const int jc = next_compute_node(cgraph, pair ? j : i, n);
+            const ggml_tensor* consumer = jc >= 0 ? ggml_graph_node(cgraph, jc) : nullptr;
+            if (!record_norm_quantize(r, node, pair ? next : nullptr, consumer, &fresh)) ok = record_elementwise(r, node, pair ? next : nullptr);
+            r.gpu_ops += pair ? 2 : 1;
+            if (pair) {
+                r.fused += 1;
+                consumed_upto = j;
+            }
         } else {
             ok = record_elementwise(r, node, nullptr);
             r.gpu_ops += 1;
@@ -794,6 +851,12 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
             const char* d0 = (const char*)t->data;
             const char* x0 = (const char*)r.q_data;
             if (d0 < x0 + (size_t)r.q_M * r.q_K * 4 && x0 < d0 + ggml_nbytes(t)) r.q_data = nullptr;
+        }
+        if (fresh.data) {
+            r.q_data = fresh.data;
+            r.q_M = fresh.M;
+            r.q_K = fresh.K;
+            r.q_scheme = fresh.scheme;
         }
         ac_runtime_batch_barrier(r.batch);
         i = consumed_upto + 1;

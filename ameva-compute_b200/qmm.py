@@ -162,6 +162,22 @@ def _bindings_for(view: WeightView):
     return (w.buf, qo, view.rows * nblk_row * qb), (w.buf, so, view.rows * nblk_row * sb)
 
 
+def _record_rms_norm_quantize(ctx, batch, ggml_type, M, K, x, y, aq, ad, ah, ae, mode, eps, weight, x_offset, y_offset,
+                              w_offset):
+    """ameva_rms_norm_quant_a8 / a8b: y = rms_norm(x) [* weight] written as f32, and y quantized into (aq, ad[, ah, ae])."""
+    if ggml_type not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K):
+        raise MulMatUnsupported("the fused RMS norm + quantize serves the per-32 and per-256 activation schemes")
+    if K > 32768:
+        raise MulMatUnsupported("the fused RMS norm + quantize keeps a row in registers: K <= 32768")
+    name = "ameva_rms_norm_quant_a8b" if ggml_type == GGML_TYPE_Q4_K else "ameva_rms_norm_quant_a8"
+    wb = (weight, w_offset, K * 4) if weight is not None else (x, x_offset)
+    write_h = ah is not None
+    binds = [(x, x_offset), wb, (y, y_offset, M * K * 4), aq, ad, ah if write_h else aq, ae if write_h else aq]
+    push = [M, K, K, mode, int(np.float32(eps).view(np.uint32)), 1 if weight is not None else 0, 1 if write_h else 0]
+    batch.dispatch(ctx.kernel(name), binds, push, (M, 1, 1))
+    batch.barrier()
+
+
 class MulMat:
     """dst[M][N] (fp32) = activations[M][K] (fp32) x weight[N][K]^T for one weight (or row range) and a maximum M.
 
@@ -376,6 +392,18 @@ class MulMat:
         shp = self._sum_shape(M)
         return self.sums.read(np.int32, int(np.prod(shp))).reshape(shp)
 
+    def record_rms_norm_quantize(self, batch: rt.Batch, x: rt.Buffer, y: rt.Buffer, M: int, *, eps: float,
+                                 weight: Optional[rt.Buffer] = None, x_offset: int = 0, y_offset: int = 0,
+                                 w_offset: int = 0) -> None:
+        """RMS norm of M rows of x (times the weight row, if given) written to y, and y quantized into this product's
+        scratch by the same kernel: follow with ``record(batch, y, dst, M, quantize=False)``. Replaces RMS_NORM (+ MUL)
+        and the quantize kernel of the MUL_MAT that consumes the result (three launches become one)."""
+        use_tc = M > GEMV_MAX_M and not self.exact and self.tc_ok
+        mode = self.q8k_mode if self.type == GGML_TYPE_Q4_K else self.round_mode
+        _record_rms_norm_quantize(self.ctx, batch, self.type, M, self.K, x, y, self.aq, self.ad,
+                                  self.ah if use_tc else None, self.ae if use_tc else None, mode, eps, weight, x_offset,
+                                  y_offset, w_offset)
+
     def read_quantized(self, M: int):
         """The activation scratch of the last run, in oracle-comparable form."""
         K = self.K
@@ -400,13 +428,15 @@ class MulMat:
 
 class MulMatGroup:
     """One activation row against several weight matrices that share it (the q / k / v or the gate / up projections of a
-    decoder layer), as ONE launch: the row is quantized once per CTA inside the kernel and every output is bit-equal to
-    the separate launches. The reference quantizes such a shared src1 once and reuses it
-    (adapters/llama/ggml-ameva/ggml-ameva.cpp:2154-2158, 2738-2749); on B200 the launches themselves are what a small
-    projection pays for, so they are merged too. Up to four matrices of one type and K, every N a multiple of 2,
-    K <= FUSED_QUANT_MAX_K; anything else is refused (callers fall back to one MulMat per matrix)."""
+    decoder layer), as ONE launch, every output bit-equal to the separate launches. The reference quantizes such a shared
+    src1 once and reuses it (adapters/llama/ggml-ameva/ggml-ameva.cpp:2154-2158, 2738-2749); on B200 the launches
+    themselves are what a small projection pays for, so they are merged too. fused_quantize=True: the row is quantized
+    by every CTA inside that launch (one launch in all, K <= FUSED_QUANT_MAX_K: for hosts that launch kernel by kernel);
+    False: the quantize kernel runs once before it (faster on the device, any K). Up to four matrices of one type and K,
+    every N a multiple of 2; anything else is refused (callers fall back to one MulMat per matrix)."""
 
-    def __init__(self, ctx: rt.Context, weights, *, round_mode: int = ROUND_NEAREST_EVEN, q8k_mode: int = Q8K_GGML) -> None:
+    def __init__(self, ctx: rt.Context, weights, *, round_mode: int = ROUND_NEAREST_EVEN, q8k_mode: int = Q8K_GGML,
+                 fused_quantize: bool = True) -> None:
         views = [w if isinstance(w, WeightView) else w.view(0, w.N) for w in weights]
         if not 1 <= len(views) <= 4:
             raise MulMatUnsupported("a group holds one to four weight matrices")
@@ -421,15 +451,22 @@ class MulMatGroup:
                 raise MulMatUnsupported(why)
             if v.rows % 2:
                 raise MulMatUnsupported("grouped launches need an even number of weight rows per matrix")
-        if K > FUSED_QUANT_MAX_K:
+        if fused_quantize and K > FUSED_QUANT_MAX_K:
             raise MulMatUnsupported(f"K={K} above {FUSED_QUANT_MAX_K}: the quantized row does not fit shared memory")
         self.ctx, self.type, self.K, self.views = ctx, t, K, views
         self.mode = q8k_mode if t == GGML_TYPE_Q4_K else round_mode
         self.binds = [_bindings_for(v) for v in views]
-        self.path = "mmvqg-fq"
+        self.fq = fused_quantize
+        self.path = "mmvqg-fq" if fused_quantize else "mmvqg"
+        self.aq = self.ad = None
+        if not fused_quantize:
+            self.aq = ctx.buffer(K)
+            self.ad = ctx.buffer((K // 256) * AB_BYTES if t == GGML_TYPE_Q4_K else (K // 32) * 4)
 
-    def record(self, batch: rt.Batch, x: rt.Buffer, dsts, *, x_offset: int = 0, dst_offsets=None) -> None:
-        """x: fp32 [K] at byte x_offset (64-byte aligned); dsts[j]: fp32 [N_j] at byte dst_offsets[j]."""
+    def record(self, batch: rt.Batch, x: rt.Buffer, dsts, *, x_offset: int = 0, dst_offsets=None,
+               quantize: bool = True) -> None:
+        """x: fp32 [K] at byte x_offset (64-byte aligned); dsts[j]: fp32 [N_j] at byte dst_offsets[j]. quantize=False
+        (two-kernel form only) reuses the row quantized by the previous record."""
         if len(dsts) != len(self.views):
             raise MulMatUnsupported("one destination per matrix")
         offs = list(dst_offsets or [0] * len(dsts))
@@ -440,12 +477,32 @@ class MulMatGroup:
             jj = j if j < len(self.views) else 0
             q, s_ = self.binds[jj]
             binds += [q, s_, (dsts[jj], offs[jj], self.views[jj].rows * 4)]
-        binds.append((x, x_offset, self.K * 4))
         ns = [v.rows for v in self.views] + [0] * (4 - len(self.views))
         fam = "ameva_mmvqgb" if self.type == GGML_TYPE_Q4_K else "ameva_mmvqg"
         total = sum(v.rows for v in self.views)
-        batch.dispatch(self.ctx.kernel(f"{fam}_{TYPE_NAMES[self.type]}_fq"), binds,
-                       [self.K, self.mode, len(self.views)] + ns, ((total + 15) // 16, 1, 1))
+        if self.fq:
+            binds.append((x, x_offset, self.K * 4))
+            batch.dispatch(self.ctx.kernel(f"{fam}_{TYPE_NAMES[self.type]}_fq"), binds,
+                           [self.K, self.mode, len(self.views)] + ns, ((total + 15) // 16, 1, 1))
+            return
+        if quantize:
+            qk = "ameva_quant_a8b" if self.type == GGML_TYPE_Q4_K else "ameva_quant_a8"
+            batch.dispatch(self.ctx.kernel(qk), [(x, x_offset, self.K * 4), self.aq, self.ad],
+                           [1, self.K, self.K, self.mode], (1, 1, 1))
+            batch.barrier()
+        binds += [self.aq, self.ad]
+        batch.dispatch(self.ctx.kernel(f"{fam}_{TYPE_NAMES[self.type]}"), binds, [self.K, 0, len(self.views)] + ns,
+                       ((total + 15) // 16, 1, 1))
+
+    def record_rms_norm_quantize(self, batch: rt.Batch, x: rt.Buffer, y: rt.Buffer, *, eps: float,
+                                 weight: Optional[rt.Buffer] = None, x_offset: int = 0, y_offset: int = 0,
+                                 w_offset: int = 0) -> None:
+        """The row's RMS norm (times the weight row) written to y and quantized into the group's scratch in one kernel
+        (two-kernel form only): follow with ``record(batch, y, dsts, quantize=False)``."""
+        if self.fq:
+            raise MulMatUnsupported("the group quantizes inside its launch: build it with fused_quantize=False")
+        _record_rms_norm_quantize(self.ctx, batch, self.type, 1, self.K, x, y, self.aq, self.ad, None, None, self.mode, eps,
+                                  weight, x_offset, y_offset, w_offset)
 
     def run(self, x: rt.Buffer, dsts, **kw) -> float:
         batch = self.ctx.batch(8)
@@ -461,7 +518,10 @@ class MulMatGroup:
             batch.destroy()
 
     def destroy(self) -> None:
-        pass
+        for b in (self.aq, self.ad):
+            if b is not None:
+                b.destroy()
+        self.aq = self.ad = None
 
 
 def q8_0_blocks_from_scratch(q: np.ndarray, d_bits: np.ndarray) -> np.ndarray:

@@ -147,7 +147,7 @@ def test_registry_names():
     for want in ("ameva_quant_a8", "ameva_quant_a8b", "bitnet_norm_q8", "ameva_mmvq_q4_0", "ameva_mmvq_q8_0",
                  "ameva_mmvqb_q4_K", "bitnet_gemv_i2_s_l32w1", "bitnet_gemv_i2_s_l16w2_acc", "ameva_mmvs_q4_K",
                  "ameva_mmvq_q4_0_fq", "ameva_mmvq_q8_0_fq", "ameva_mmvqb_q4_K_fq",
-                 "ameva_peer_barrier", "ameva_mmtc_q8_0", "ameva_mmtc_q4_K_mp", "ameva_mmvm_q4_K", "ameva_mmvqgb_q4_K_fq",
+                 "ameva_peer_barrier", "ameva_mmtc_q8_0", "ameva_mmtc_q4_K_mp", "ameva_mmvm_q4_K", "ameva_rms_norm_quant_a8", "ameva_rms_norm_quant_a8b", "ameva_mmvqgb_q4_K_fq", "ameva_mmvqgb_q4_K", "ameva_mmvqg_q8_0",
                  "ameva_peer_push_barrier", "ameva_peer_copy", "ameva_peer_join", "ameva_add_f32", "ameva_rms_norm_f32"):
         assert want in names
     assert len(names) == len(set(names))

@@ -4,6 +4,7 @@ import pytest
 
 import oracle
 from conftest import GOLDEN, load_pkg
+from helpers import Q4_0, Q4_K, Q8_0, make_weights
 
 pytestmark = pytest.mark.gpu
 pkg = load_pkg()
@@ -175,3 +176,85 @@ def test_quantizers_against_frozen_known_answers(ctx):
     assert np.array_equal(qmm.q8_0_blocks_from_scratch(q, (adw & 0xFFFF).astype(np.uint16)), z["q8_0_even"])
     for b in (xb, aq, ad):
         b.destroy()
+
+
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
+@pytest.mark.parametrize("M,N,K,with_weight", [(1, 64, 4096, True), (1, 130, 2560, False), (5, 32, 1024, True),
+                                               (33, 128, 2048, True), (1, 16, 32768, True), (300, 256, 512, False)])
+def test_rms_norm_fused_with_the_quantize(ctx, t, M, N, K, with_weight):
+    """RMS norm (+ MUL by a weight row) and the activation quantize of the MUL_MAT behind it as ONE kernel
+    (ameva_rms_norm_quant_a8 / a8b): y against ggml's CPU arithmetic (squares summed in double), the quantized scratch
+    bit-equal to the oracle's quantization of the y the kernel wrote, and the product through that scratch equal to the
+    product of the separate kernels on the same y."""
+    if t == Q4_K and K % 256:
+        K = (K // 256 + 1) * 256
+    rng = np.random.default_rng(M + K)
+    x = (rng.standard_normal((M, K)) * rng.uniform(0.05, 20.0, (M, 1))).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    eps = 1e-5
+    blocks, scale = make_weights(t, N, K, 3)
+    wt = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, scale)
+    mm = qmm.MulMat(ctx, wt, M)
+    xb, wb, yb, dst, dst2 = ctx.buffer(data=x), ctx.buffer(data=w), ctx.buffer(M * K * 4), ctx.buffer(M * N * 4), ctx.buffer(M * N * 4)
+    batch = ctx.batch(16)
+    mm.record_rms_norm_quantize(batch, xb, yb, M, eps=eps, weight=wb if with_weight else None)
+    mm.record(batch, yb, dst, M, quantize=False)
+    ev = batch.submit()
+    ev.wait()
+    ev.destroy()
+    batch.destroy()
+    y = yb.read(np.float32).reshape(M, K)
+    x64 = x.astype(np.float64)
+    ss = np.sum((x * x).astype(np.float64), axis=1, keepdims=True)            # float products, summed in double
+    mean = (ss / K).astype(np.float32)
+    sc = (np.float32(1.0) / np.sqrt(mean + np.float32(eps))).astype(np.float32)
+    want_y = (x * sc).astype(np.float32)
+    if with_weight:
+        want_y = (want_y * w).astype(np.float32)
+    assert np.max(np.abs(y - want_y) / np.max(np.abs(want_y), axis=1, keepdims=True)) <= 3e-7
+    assert np.max(np.abs(y - (x64 / np.sqrt(np.mean(x64 * x64, axis=1, keepdims=True) + eps)) * (w if with_weight else 1.0))
+                  / np.max(np.abs(want_y), axis=1, keepdims=True)) <= 3e-6
+    if t in (Q4_0, Q8_0):
+        q, dbits, _ = mm.read_quantized(M)
+        assert np.array_equal(qmm.q8_0_blocks_from_scratch(q, dbits), oracle.quantize_q8_0(y))
+    else:
+        q, d, bs = mm.read_quantized(M)
+        assert np.array_equal(qmm.q8_K_blocks_from_scratch(q, d, bs), oracle.quantize_q8_K(y))
+    got = dst.read(np.float32)
+    mm.run(yb, dst2, M)                                  # the separate quantize kernel on the same y
+    assert np.array_equal(got.view(np.uint32), dst2.read(np.uint32))
+    for b in (xb, wb, yb, dst, dst2):
+        b.destroy()
+    mm.destroy()
+    wt.destroy()
+
+
+def test_rms_norm_quantize_feeds_a_grouped_launch(ctx):
+    K, ns = 2048, (256, 64, 64)
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    w = (1.0 + 0.1 * rng.standard_normal(K)).astype(np.float32)
+    ws = [qmm.QuantWeight.from_ggml(ctx, Q4_K, make_weights(Q4_K, n, K, 20 + j)[0], n, K) for j, n in enumerate(ns)]
+    grp = qmm.MulMatGroup(ctx, ws, fused_quantize=False)
+    xb, wb, yb = ctx.buffer(data=x), ctx.buffer(data=w), ctx.buffer(K * 4)
+    outs, refs = [ctx.buffer(n * 4) for n in ns], [ctx.buffer(n * 4) for n in ns]
+    batch = ctx.batch(16)
+    grp.record_rms_norm_quantize(batch, xb, yb, eps=1e-6, weight=wb)
+    grp.record(batch, yb, outs, quantize=False)
+    ev = batch.submit()
+    ev.wait()
+    ev.destroy()
+    batch.destroy()
+    grp.run(yb, refs)                                    # quantize kernel + grouped launch on the same y
+    for o, r in zip(outs, refs):
+        assert np.array_equal(o.read(np.uint32), r.read(np.uint32))
+    fq, spare = qmm.MulMatGroup(ctx, ws), ctx.batch(4)
+    with pytest.raises(qmm.MulMatUnsupported):      # a group that quantizes inside its launch has no scratch to fill
+        fq.record_rms_norm_quantize(spare, xb, yb, eps=1e-6)
+    spare.destroy()
+    fq.destroy()
+    for b in [xb, wb, yb] + outs + refs:
+        b.destroy()
+    grp.destroy()
+    for v in ws:
+        v.destroy()

@@ -413,6 +413,13 @@ def test_grouped_launch_of_projections_sharing_the_activation_row(ctx, t, ns, K)
         o.fill(0xFF)
     grp = qmm.MulMatGroup(ctx, ws)
     grp.run(xb, outs)
+    # the same group with the row quantized once by the kernel before the grouped launch
+    outs2 = [ctx.buffer(N * 4) for N in ns]
+    for o in outs2:
+        o.fill(0xFF)
+    grp2 = qmm.MulMatGroup(ctx, ws, fused_quantize=False)
+    grp2.run(xb, outs2)
+    assert (grp.path, grp2.path) == ("mmvqg-fq", "mmvqg")
     for j, N in enumerate(ns):
         got = outs[j].read(np.float32)
         one = qmm.MulMat(ctx, ws[j], 1, fused_quantize=True)
@@ -420,11 +427,15 @@ def test_grouped_launch_of_projections_sharing_the_activation_row(ctx, t, ns, K)
         one.run(xb, ref, 1)
         assert one.path == "mmvq-fq"
         assert np.array_equal(got.view(np.uint32), ref.read(np.uint32)), (j, N)
+        assert np.array_equal(outs2[j].read(np.uint32), ref.read(np.uint32)), (j, N)
         want, _, _ = oracle_mul_mat(t, blocks_all[j], 1.0, x, N, K, want_sums=False)
         assert max_normalised_error(got.reshape(1, N), want) <= TOL
         ref.destroy()
         one.destroy()
     grp.destroy()
+    grp2.destroy()
+    for b in outs2:
+        b.destroy()
     for b in outs + [xb]:
         b.destroy()
     for w in ws:
