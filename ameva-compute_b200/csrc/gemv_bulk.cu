@@ -337,7 +337,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
     }
     __syncthreads();
     pdl_wait();   // the quantized activations come from the preceding kernel
-    pdl_trigger();
+    // No early launch trigger here: the kernel behind this one becomes schedulable when this grid's CTAs exit. With
+    // the trigger at this point, the CTAs of the next launch of this kernel in a replayed chain (mul_mat, quantize,
+    // mul_mat, ...) became resident while this grid was still running, and such chains ended in a launch failure on
+    // 28672 x 8192 Q4_K; without the overlap of two generations of this kernel they run.
     if (p.act_smem && !p.group_warps && threadIdx.x == 0) {   // one copy each for the quantized activations and their scales
         mbar_arrive_expect_tx(act_bar, p.aq_bytes + p.ad_bytes);
         bulk_load(smem_u32(s_aq), p.AQ, p.aq_bytes, act_bar);
@@ -391,7 +394,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_bulk_kernel(const Params p) 
             const uint8_t* AD = staged ? s_ad : p.AD;
             bool ok = true;
             for (uint32_t g = g_begin + group; g < g_end && ok; g += p.groups) {
-                const uint32_t j = g - g_begin, idx = j % NS, phase = (j / NS) & 1u;
+                const uint32_t j = g - g_begin, idx = j % NS, pass = j / NS, phase = pass & 1u;
+                // A parity wait cannot tell pass n from pass n - 2, and this group last waited on another slot: a copy
+                // of the pass before that completes late (bulk copies finish in no fixed order) would look like this
+                // pass complete. The slot's previous pass having been consumed rules that out, and it always has been
+                // by the time this pass is requested, so this wait does not block.
+                if (pass) ok = mbar_wait(empty + 8u * idx, phase ^ 1u, ctl, p.status, 0xD80u | idx);
+                if (!ok) break;
                 ok = mbar_wait(full + 8u * idx, phase, ctl, p.status, 0xD00u | idx);
                 if (!ok) break;
                 const uint32_t row = g * SR + wi * R;

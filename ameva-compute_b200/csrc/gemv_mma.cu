@@ -116,24 +116,31 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemv_mma_q4k_k
     const uint32_t n_items = (set_end - set_begin) * my_blocks;
     const uint32_t ring = smem_addr(s_ring) + warp * depth * kStageBytes;
 
-    // item -> (set, block); the lane's share of the copy: payload pieces lane, lane + 32, + 64, + 96 of the 16 x 8 pieces
-    // (row = piece / 8, 16-byte column = piece % 8), and the scale record of row `lane` for lanes 0..15
-    auto issue = [&](uint32_t item) {
-        if (item < n_items) {
-            const uint32_t set = set_begin + item / my_blocks, b = b_begin + item % my_blocks;
-            const uint32_t row0 = (set * RG + rg) * 16u;
-            const uint32_t st = ring + (item % depth) * kStageBytes;
-            const uint32_t col = lane & 7u;
+    // The items are requested in order, so the request side keeps its own (set, block, ring slot) counters instead of
+    // dividing the item number. The lane's share of a copy: payload pieces lane, lane + 32, + 64, + 96 of the 16 x 8
+    // pieces (row = piece / 8, 16-byte column = piece % 8), and the scale record of row `lane` for lanes 0..15.
+    uint32_t iss_item = 0, iss_set = set_begin, iss_b = b_begin, iss_slot = 0;
+    const uint32_t col = lane & 7u, r_lo = lane >> 3;
+    auto issue = [&](uint32_t) {
+        if (iss_item < n_items) {
+            const uint32_t row0 = (iss_set * RG + rg) * 16u;
+            const uint32_t st = ring + iss_slot * kStageBytes;
+            const uint8_t* qb = p.Q + (size_t)iss_b * 128u + col * 16u;
 #pragma unroll
             for (uint32_t i = 0; i < 4u; ++i) {
-                const uint32_t r = (lane >> 3) + 4u * i, row = min(row0 + r, p.N - 1u);
-                cp_async_16(st + r * kRowPitch + ((col ^ (r & 7u)) << 4), p.Q + ((size_t)row * B + b) * 128u + col * 16u);
+                const uint32_t r = r_lo + 4u * i, row = min(row0 + r, p.N - 1u);
+                cp_async_16(st + r * kRowPitch + ((col ^ (r & 7u)) << 4), qb + (size_t)row * B * 128u);
             }
-            if (lane < 16u) cp_async_16(st + 16u * kRowPitch + lane * 16u, p.S + (size_t)min(row0 + lane, p.N - 1u) * B + b);
+            if (lane < 16u) cp_async_16(st + 16u * kRowPitch + lane * 16u, p.S + (size_t)min(row0 + lane, p.N - 1u) * B + iss_b);
+            ++iss_item;
+            if (++iss_slot == depth) iss_slot = 0;
+            if (++iss_b == b_end) {
+                iss_b = b_begin;
+                ++iss_set;
+            }
         }
         cp_async_commit();   // (an empty group when the sequence has ended keeps the group count in step)
     };
-
     // the weights do not depend on the kernel before this one: the ring is filled before the wait for it
     AMV_TRACE_BEGIN(blockIdx.x)
     AMV_TRACE_STAMP(0)
@@ -189,7 +196,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemv_mma_q4k_k
     const float* da0p = s_da + tok0 * B;
     const float* da1p = s_da + tok1 * B;
 
-    uint32_t parity = 0, item = 0;
+    uint32_t parity = 0, item = 0, slot = 0;
     for (uint32_t set = set_begin; set < set_end; ++set) {
         if (set == set_begin + 1u) { AMV_TRACE_STAMP(4) }
         float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};   // (row g, token 2t), (g, 2t+1), (g+8, 2t), (g+8, 2t+1)
@@ -205,7 +212,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 2 : 1) gemv_mma_q4k_k
             __syncwarp();
             // (every lane is past the previous item, whose stage is the one item + depth - 1 goes to: refill it now)
             issue(item + depth - 1u);
-            const uint8_t* st = s_ring + ((size_t)warp * depth + item % depth) * kStageBytes;
+            const uint8_t* st = s_ring + ((size_t)warp * depth + slot) * kStageBytes;
+            if (++slot == depth) slot = 0;
             // 6-bit scales and mins of the 8 sub-blocks, four to a word, per row
             uint32_t sc[2][2], mn[2][2];
             float dw[2], dmin[2];
