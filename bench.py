@@ -475,8 +475,10 @@ class Measurement:
             rb, tail = self.replay_batches(quantize, g, rem)   # instantiated before the timed region
             evs = []
             with torch.cuda.stream(env.stream):
-                if lead_in:   # an untimed replay just ahead: the timed one is enqueued while the GPU is still busy,
-                    evs.append((rb if full else tail).replay())   # so no launch bubble sits behind the start event
+                # untimed replays just ahead: the timed ones are enqueued while the GPU is still busy, so no launch
+                # bubble sits behind the start event, and a short run starts as far into a busy period as a long one
+                for _ in range(int(lead_in)):
+                    evs.append((rb if full else tail).replay())
                 start.record()
                 for _ in range(full):
                     evs.append(rb.replay())
@@ -525,14 +527,30 @@ class Measurement:
         return start.elapsed_time(end) / 1e3
 
     # ---- the measurements ------------------------------------------------------------------------------------------
+    def lead_in_replays(self, steps):
+        """Untimed replays of the timed graph enqueued directly ahead of the start event: about `lead_in_ms` of GPU work
+        (from the step time of the untimed first launch of the graphs), at least one."""
+        est = getattr(self, "step_estimate_s", None)
+        ms = float(os.environ.get("AMEVA_BENCH_LEAD_IN_MS", "8"))
+        if not est or ms <= 0:
+            return 1
+        g = self.graph_steps(steps)
+        per_replay = est * (g if steps >= g else steps)
+        return max(1, min(64, int(ms * 1e-3 / per_replay + 0.5)))
+
     def timed(self, steps, warmup):
         env = self.env
         self.gpu_steps(warmup, 0)
         if self.use_replay():   # the graphs of the timed run have been launched once before it is timed
-            self.gpu_steps(steps, warmup)
+            self.step_estimate_s = self.gpu_steps(steps, warmup) / steps
         env.barrier()
-        gpu_s = self.gpu_steps(steps, warmup, lead_in=True)
+        lead = self.lead_in_replays(steps) if self.use_replay() else 0
+        t0 = time.perf_counter()
+        gpu_s = self.gpu_steps(steps, warmup, lead_in=lead)
         env.barrier()
+        g = self.graph_steps(steps)
+        self.wall_steps = steps + lead * (g if steps >= g else steps)   # steps the host clock below covers
+        self.wall_s = time.perf_counter() - t0
         return env.max_over_ranks(gpu_s)
 
     def roofline(self, steps, warmup, step_s):
@@ -542,7 +560,8 @@ class Measurement:
         one_launch = self.path() in ("mmvq-fq", "mmvqg-fq")
         if self.use_replay():
             self.gpu_steps(steps, warmup + steps, quantize=True if one_launch else False)   # first launch of its graphs
-        main_s = self.gpu_steps(steps, warmup + steps, quantize=True if one_launch else False, lead_in=True)
+        main_s = self.gpu_steps(steps, warmup + steps, quantize=True if one_launch else False,
+                                lead_in=self.lead_in_replays(steps))
         main_ns = main_s / steps * 1e9
         quant_ns = max(0.0, step_s * 1e9 - main_ns)
         pk = peaks()
@@ -560,7 +579,7 @@ class Measurement:
         # of a launch this short keep a pure read well under the copy peak
         if self.use_replay():
             self.gpu_steps(steps, warmup + steps, quantize="read-probe")
-        probe_s = self.gpu_steps(steps, warmup + steps, quantize="read-probe", lead_in=True)
+        probe_s = self.gpu_steps(steps, warmup + steps, quantize="read-probe", lead_in=self.lead_in_replays(steps))
         roof["read_only_us"] = probe_s / steps * 1e6
         roof["read_only_gbs"] = sum(w.buf.size_bytes for w in self.weights[0]) / (probe_s / steps) / 1e9
         roof["frac_of_read_only"] = roof["read_only_us"] / roof["kernel_us"]
@@ -793,14 +812,8 @@ def main():
     units = m.world_units()
 
     sampler = ClockSampler(env.local_rank)
-    m.gpu_steps(args.warmup, 0)
-    env.barrier()
     sampler.start()
-    t_wall0 = time.perf_counter()
-    gpu_s = m.gpu_steps(args.steps, args.warmup)
-    env.barrier()
-    wall_s = time.perf_counter() - t_wall0
-    gpu_s = env.max_over_ranks(gpu_s)
+    gpu_s = m.timed(args.steps, args.warmup)   # warm-up, first launch of the timed graphs, then the timed region
     step_s = gpu_s / args.steps
 
     roof = m.roofline(args.steps, args.warmup, step_s) if world == 1 else None
@@ -823,7 +836,7 @@ def main():
                "sharded": f"weight rows sharded over {world} ranks, output assembled on every rank ({m.exchange})"}[mode]
         detail = ({"l2": f"rotating pool of {m.pool_n} weight copies ({m.pool_n * m.shard_bytes / 1e6:.0f} MB > L2) per rank",
                     "parallelism": par, "path": m.path(),
-                    "launch": f"replayed batches (CUDA graphs of {m.graph_steps(args.steps)} steps, cycling the pool, + one of the remainder; one untimed replay is enqueued just ahead of the start event so that the timed graphs are submitted while the GPU is busy)" if
+                    "launch": f"replayed batches (CUDA graphs of {m.graph_steps(args.steps)} steps, cycling the pool, + one of the remainder; the graphs are launched once untimed, and untimed replays (about 8 ms of them) are enqueued just ahead of the start event so that the timed ones are submitted while the GPU is busy)" if
                     m.use_replay() else "one host launch per kernel"})
         line = {
             "metric": metric_name(name), "value": unit_value(m.unit, t, M * units, N, K, step_s), "unit": m.unit,
@@ -834,7 +847,7 @@ def main():
                           m.path().split("+")[0], "int8 (dp4a, int32 per block, fp32 scale-accumulate)"),
             "data": "synthetic",
             "config": workload_config(name), "config_detail": detail,
-            "wall_ms_per_step": wall_s / args.steps * 1e3,
+            "wall_ms_per_step": m.wall_s / m.wall_steps * 1e3,
             "gpu_launches": m.launches_per_step * args.steps,
             "e2e": e2e,
             "clocks": clocks,
