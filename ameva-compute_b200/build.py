@@ -26,7 +26,7 @@ LEGACY_LIB = os.path.join(HERE, "libamuda_b200.so")
 MEASURE_LIB = os.path.join(HERE, "libac_b200_measure.so")
 
 RUNTIME_SOURCES = ["runtime.cu", "registry.cu", "act_quant.cu", "gemv.cu", "gemv_bulk.cu", "gemv_mma.cu", "elementwise.cu", "gemm_tc.cu", "noalloc.cu",
-                   "peer_sync.cu", "repack.cu"]
+                   "peer_sync.cu", "repack.cu", "gguf_load.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr",
@@ -58,6 +58,7 @@ def _stale(target: str, deps: list[str]) -> bool:
 def build(force: bool = False, verbose: bool = False) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(ROOT, "include", "ac_runtime_b200.h"))
+    headers.append(os.path.join(ROOT, "include", "amuda_gguf_b200.h"))
     objs = []
     os.makedirs(os.path.join(HERE, "build"), exist_ok=True)
     procs = []
