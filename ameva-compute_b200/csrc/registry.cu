@@ -36,6 +36,13 @@ AcResult launch_add_f32(const LaunchArgs&);
 AcResult launch_mul_f32(const LaunchArgs&);
 AcResult launch_swiglu_f32(const LaunchArgs&);
 AcResult launch_rms_norm_f32(const LaunchArgs&);
+AcResult launch_rope(const LaunchArgs&);
+AcResult launch_rope_f16(const LaunchArgs&);
+AcResult launch_get_rows(const LaunchArgs&);
+AcResult launch_set_rows(const LaunchArgs&);
+AcResult launch_soft_max(const LaunchArgs&);
+AcResult launch_gemv_f16(const LaunchArgs&);
+AcResult launch_flash_attn(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
@@ -85,6 +92,17 @@ static const KernelEntry kTable[] = {
     {"ameva_mul_f32", 3, 12, {256, 1, 1}, launch_mul_f32},
     {"ameva_swiglu_f32", 3, 4, {256, 1, 1}, launch_swiglu_f32},
     {"ameva_rms_norm_f32", 3, 16, {256, 1, 1}, launch_rms_norm_f32},
+    // the reference's own names, binding counts, push sizes and local sizes (ggml_ameva_kernels_spv.h:145036-145054,
+    // bitnet_kernels_spv.h:3712-3714)
+    {"ameva_rope", 4, 92, {256, 1, 1}, launch_rope},
+    {"ameva_rope_f16", 4, 92, {256, 1, 1}, launch_rope_f16},
+    {"ameva_get_rows", 4, 76, {256, 1, 1}, launch_get_rows},
+    {"ameva_set_rows", 4, 88, {256, 1, 1}, launch_set_rows},
+    {"ameva_soft_max", 3, 80, {128, 1, 1}, launch_soft_max},
+    {"ameva_flash_attn", 6, 124, {128, 1, 1}, launch_flash_attn},
+    {"bitnet_gemv_f16_w1", 3, 12, {32, 4, 1}, launch_gemv_f16},
+    {"bitnet_gemv_f16_w2", 3, 12, {32, 4, 1}, launch_gemv_f16},
+    {"bitnet_gemv_f16_w4", 3, 12, {32, 4, 1}, launch_gemv_f16},
     {"ameva_mmvs_q4_0", 12, 24, {288, 1, 1}, launch_mmvs_q4_0},
     {"ameva_mmvs_q8_0", 12, 24, {288, 1, 1}, launch_mmvs_q8_0},
     {"ameva_mmvs_q4_K", 12, 24, {288, 1, 1}, launch_mmvs_q4_K},
