@@ -435,154 +435,237 @@ struct FlashArgs {
 
 constexpr int kFaWarps = 4;
 
-template <int D, int GMAX>
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(src)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kFaHeads = 8;   // query heads per KV head a CTA carries (rows 0..7 of the 16-row MMA tile; 8..15 stay zero)
+
+// the warps' K and V tiles; after the last block the same memory holds the warps' results for the merge
+template <int D>
+constexpr size_t flash_smem_bytes() {
+    constexpr size_t tiles = 2 * sizeof(__half) * kFaWarps * 32 * D, merge = sizeof(float) * kFaWarps * kFaHeads * (D + 2);
+    return tiles > merge ? tiles : merge;
+}
+
+// 32 rows of D halves from global memory (row r at base + r * stride) into a warp's shared-memory tile, two (D = 128)
+// whole rows per warp instruction; rows from `rows` on are zero-filled. The 16-byte pieces of row r are stored at
+// piece ^ (r mod pieces per row): the eight row addresses of an ldmatrix then fall into eight different bank groups.
+template <int D>
+__device__ __forceinline__ void stage_rows(__half (*tile)[D], const __half* base, uint64_t stride, uint32_t rows,
+                                           uint32_t lane) {
+    constexpr uint32_t P = D / 8;
+#pragma unroll 8
+    for (uint32_t i = lane; i < 32u * P; i += 32u) {
+        const uint32_t row = i / P, piece = i - row * P;
+        __half* dst = &tile[row][8u * (piece ^ (row & (P - 1u)))];
+        if (row < rows) cp_async16(dst, base + row * stride + 8u * piece);
+        else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    cp_async_commit();
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"((uint32_t)__cvta_generic_to_shared(smem_row)));
+}
+// D (16 x 8, fp32) += A (16 x 16, f16, rows 8..15 zero: a1 = a3 = 0) * B (16 x 8, f16)
+__device__ __forceinline__ void mma_16816_top(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+// Both products run on the tensor cores (mma.sync m16n8k16, f16 operands, fp32 accumulate): the scalar form of this
+// kernel needed about 4000 instructions per 32 keys and was bound by instruction issue at a quarter of the HBM rate.
+// The up to eight query heads of a KV head are rows 0..7 of the 16-row tile. Scores: A = Q (f16, kept in registers for
+// the whole kernel), B = the staged K rows (ldmatrix). The score accumulators already have the A-fragment layout of
+// the second product, P V, whose B fragments are the staged V rows through ldmatrix.trans. Q and the probabilities
+// are rounded to f16 (ggml's CPU kernel rounds Q to f16 as well and accumulates V in f16; here accumulation is fp32).
+template <int D>
 __global__ void __launch_bounds__(kFaWarps * 32) flash_decode_kernel(const float* __restrict__ q, const __half* __restrict__ k,
                                                                      const __half* __restrict__ v,
                                                                      const __half* __restrict__ mask, float* __restrict__ o,
                                                                      float* __restrict__ part, const FlashArgs pc,
                                                                      uint32_t n_splits) {
-    constexpr int C = D / 32;                 // output columns (and V elements) per lane
-    __shared__ __align__(16) float s_q[GMAX][D];
-    __shared__ float s_acc[kFaWarps][GMAX][D + 2];   // per warp: D accumulators, then maximum and sum
+    constexpr int KS = D / 16;                // k-steps of the score product
+    constexpr int NT = D / 8;                 // n-tiles of the output
+    constexpr uint32_t P = D / 8;             // 16-byte pieces per K or V row
+    extern __shared__ __align__(16) uint8_t fa_smem[];
+    float (*s_acc)[kFaHeads][D + 2] = reinterpret_cast<float (*)[kFaHeads][D + 2]>(fa_smem);   // per warp: D sums, max, sum
+    uint8_t* tiles = fa_smem;                                                                  // (used before s_acc)
     pdl_trigger();
     pdl_wait();
     const uint32_t z = blockIdx.x, hkv = blockIdx.y, iq1 = blockIdx.z;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    __half (*s_k)[D] = reinterpret_cast<__half (*)[D]>(tiles + sizeof(__half) * 32 * D * (2 * warp));       // this warp's
+    __half (*s_v)[D] = reinterpret_cast<__half (*)[D]>(tiles + sizeof(__half) * 32 * D * (2 * warp + 1));   // K and V tile
     const uint32_t G = pc.n_head / pc.n_head_kv, h0 = hkv * G;
-    for (uint32_t i = threadIdx.x; i < GMAX * D; i += kFaWarps * 32) {
-        const uint32_t g = i / D, d = i - g * D;
-        s_q[g][d] = g < G ? q[pc.q_off + (uint64_t)iq1 * pc.q_s1 + (uint64_t)(h0 + g) * pc.q_s2 + d] : 0.0f;
-    }
-    __syncthreads();
-    const float scale = u2f(pc.scale), softcap = u2f(pc.softcap);
+    const float ninf = __uint_as_float(0xFF800000u);
     const uint32_t key_begin = z * pc.split_keys, key_end = min(pc.n_kv, key_begin + pc.split_keys);
     const __half* kbase = k + pc.k_off + (uint64_t)hkv * pc.k_s2;
     const __half* vbase = v + pc.v_off + (uint64_t)hkv * pc.v_s2;
-    float acc[GMAX][C], m_run[GMAX], l_run[GMAX];
-#pragma unroll
-    for (int g = 0; g < GMAX; ++g) {
-        m_run[g] = __uint_as_float(0xFF800000u);
-        l_run[g] = 0.0f;
-#pragma unroll
-        for (int c = 0; c < C; ++c) acc[g][c] = 0.0f;
+    uint32_t k0 = key_begin + warp * 32u;
+    // the first block's K and V are requested before anything else
+    if (k0 < key_end) {
+        stage_rows<D>(s_k, kbase + (uint64_t)k0 * pc.k_s1, pc.k_s1, min(32u, key_end - k0), lane);
+        stage_rows<D>(s_v, vbase + (uint64_t)k0 * pc.v_s1, pc.v_s1, min(32u, key_end - k0), lane);
     }
-    for (uint32_t k0 = key_begin + warp * 32u; k0 < key_end; k0 += kFaWarps * 32u) {
-        const uint32_t key = k0 + lane;
-        const bool live = key < key_end;
-        float s[GMAX];
+    // this thread's share of the A fragments of Q: head g = lane / 4, columns 16 ks + 2 (lane % 4) + {0, 1} and + 8
+    const uint32_t g = lane >> 2, t4 = lane & 3u;
+    const bool head = g < G;
+    uint32_t qa[KS][2];
+    {
+        const float* qrow = q + pc.q_off + (uint64_t)iq1 * pc.q_s1 + (uint64_t)(h0 + (head ? g : 0u)) * pc.q_s2;
 #pragma unroll
-        for (int g = 0; g < GMAX; ++g) s[g] = 0.0f;
-        if (live) {
-            const uint4* krow = reinterpret_cast<const uint4*>(kbase + (uint64_t)key * pc.k_s1);
-#pragma unroll 4
-            for (int p = 0; p < D / 8; ++p) {
-                const uint4 w = ld_stream_u4(krow + p);
-                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-                const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-                const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
-                const float2 e = __half22float2(*reinterpret_cast<const __half2*>(&w.w));
+        for (int ks = 0; ks < KS; ++ks) {
+            const uint32_t c = 16u * ks + 2u * t4;
+            qa[ks][0] = head ? pack_h2(qrow[c], qrow[c + 1u]) : 0u;
+            qa[ks][1] = head ? pack_h2(qrow[c + 8u], qrow[c + 9u]) : 0u;
+        }
+    }
+    const float scale = u2f(pc.scale), softcap = u2f(pc.softcap);
+    float oc[NT][4];
 #pragma unroll
-                for (int g = 0; g < GMAX; ++g) {
-                    const float4 q0 = *reinterpret_cast<const float4*>(&s_q[g][8 * p]);
-                    const float4 q1 = *reinterpret_cast<const float4*>(&s_q[g][8 * p + 4]);
-                    float t = s[g];
-                    t = fmaf(a.x, q0.x, t);
-                    t = fmaf(a.y, q0.y, t);
-                    t = fmaf(b.x, q0.z, t);
-                    t = fmaf(b.y, q0.w, t);
-                    t = fmaf(c.x, q1.x, t);
-                    t = fmaf(c.y, q1.y, t);
-                    t = fmaf(e.x, q1.z, t);
-                    t = fmaf(e.y, q1.w, t);
-                    s[g] = t;
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oc[nt][j] = 0.0f;
+    float m_run = ninf, l_run = 0.0f;
+    const __half* mrow = mask + pc.m_off + (uint64_t)iq1 * pc.m_s1 + (uint64_t)((h0 + (head ? g : 0u)) % (pc.has_mask ? pc.m_ne2 : 1u)) * pc.m_s2;
+    // ldmatrix row addresses of this lane: matrix lane / 8, row lane % 8
+    const uint32_t lm_row = (lane & 7u) + ((lane >> 4) << 3), lm_hi = (lane >> 3) & 1u;   // K: key within 16, upper d half
+    const uint32_t lv_row = (lane & 7u) + (((lane >> 3) & 1u) << 3), lv_nt = lane >> 4;    // V: key within 16, second n-tile
+    // Per block of 32 keys: K(b) and V(b) are in flight when the block starts; K(b + 1) is requested as soon as the
+    // scores are formed, V(b + 1) after the P V product: a tile is always on its way while the warp computes.
+    for (; k0 < key_end; k0 += kFaWarps * 32u) {
+        const uint32_t next = k0 + kFaWarps * 32u;
+        const bool more = next < key_end;
+        cp_async_wait_group<1>();   // K(b) has landed (V(b) may still be on its way)
+        __syncwarp();
+        float sc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sc[nt][j] = 0.0f;
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {          // pairs of n-tiles: keys 16 np .. 16 np + 15
+            const uint32_t key = 16u * np + lm_row;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t b[4];
+                ldmatrix_x4(b, &s_k[key][8u * ((2u * ks + lm_hi) ^ (key & (P - 1u)))]);
+                mma_16816_top(sc[2 * np], qa[ks][0], qa[ks][1], b[0], b[1]);
+                mma_16816_top(sc[2 * np + 1], qa[ks][0], qa[ks][1], b[2], b[3]);
+            }
+        }
+        __syncwarp();   // every lane has read the K tile: it may be refilled
+        if (more) stage_rows<D>(s_k, kbase + (uint64_t)next * pc.k_s1, pc.k_s1, min(32u, key_end - next), lane);
+        else cp_async_commit();   // (an empty group keeps the count of the waits below)
+        // this thread's eight scores: head g, keys k0 + 8 nt + 2 t4 + {0, 1}
+        float x[4][2], bm = ninf;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const uint32_t key = k0 + 8u * nt + 2u * t4 + j;
+                float xv = ninf;
+                if (head && key < key_end) {
+                    xv = sc[nt][j] * scale;
+                    if (softcap != 0.0f) xv = softcap * tanhf(xv / softcap);
+                    if (pc.has_mask) xv += __half2float(mrow[key]);
                 }
+                x[nt][j] = xv;
+                bm = fmaxf(bm, xv);
+            }
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+        const float m_new = fmaxf(m_run, bm);
+        // nothing but masked keys so far: the maximum stays -inf and nothing is added
+        const float factor = m_new == ninf ? 1.0f : expf(m_run - m_new);
+        float ps = 0.0f;
+        uint32_t pa[2][2];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const float p0 = x[nt][0] == ninf ? 0.0f : expf(x[nt][0] - m_new);
+            const float p1 = x[nt][1] == ninf ? 0.0f : expf(x[nt][1] - m_new);
+            ps += p0 + p1;
+            pa[nt >> 1][nt & 1] = pack_h2(p0, p1);
+        }
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run = l_run * factor + ps;
+        m_run = m_new;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            oc[nt][0] *= factor;
+            oc[nt][1] *= factor;
+        }
+        cp_async_wait_group<1>();   // V(b) has landed (K(b + 1) may still be on its way)
+        __syncwarp();
+        // rows past the last key are zeros and their probabilities are 0
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {     // pairs of output n-tiles: columns 16 np .. 16 np + 15
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {      // keys 16 kk .. 16 kk + 15
+                const uint32_t key = 16u * kk + lv_row;
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, &s_v[key][8u * ((2u * np + lv_nt) ^ (key & (P - 1u)))]);
+                mma_16816_top(oc[2 * np], pa[kk][0], pa[kk][1], b[0], b[1]);
+                mma_16816_top(oc[2 * np + 1], pa[kk][0], pa[kk][1], b[2], b[3]);
             }
         }
-        float p_l[GMAX];
-#pragma unroll
-        for (int g = 0; g < GMAX; ++g) {
-            float x = __uint_as_float(0xFF800000u);
-            if (live && g < (int)G) {
-                x = s[g] * scale;
-                if (softcap != 0.0f) x = softcap * tanhf(x / softcap);
-                if (pc.has_mask)
-                    x += __half2float(mask[pc.m_off + (uint64_t)iq1 * pc.m_s1 + (uint64_t)((h0 + g) % pc.m_ne2) * pc.m_s2 + key]);
-            }
-            float bm = x;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, off));
-            const float m_new = fmaxf(m_run[g], bm);
-            // nothing but masked keys so far: the maximum stays -inf and nothing is added
-            const float factor = m_new == __uint_as_float(0xFF800000u) ? 1.0f : expf(m_run[g] - m_new);
-            const float p = (x == __uint_as_float(0xFF800000u)) ? 0.0f : expf(x - m_new);
-            float ps = p;
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
-            l_run[g] = l_run[g] * factor + ps;
-            m_run[g] = m_new;
-            p_l[g] = p;
-#pragma unroll
-            for (int c = 0; c < C; ++c) acc[g][c] *= factor;
-        }
-        const uint32_t nk = min(32u, key_end - k0);
-        for (uint32_t kk = 0; kk < nk; ++kk) {
-            const __half* vrow = vbase + (uint64_t)(k0 + kk) * pc.v_s1 + lane * C;
-            float vf[C];
-            if constexpr (C == 2) {
-                const float2 t = __half22float2(*reinterpret_cast<const __half2*>(vrow));
-                vf[0] = t.x;
-                vf[1] = t.y;
-            } else if constexpr (C == 4) {
-                const uint2 w = *reinterpret_cast<const uint2*>(vrow);
-                const float2 t0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-                const float2 t1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-                vf[0] = t0.x; vf[1] = t0.y; vf[2] = t1.x; vf[3] = t1.y;
-            } else {
-                const uint4 w = *reinterpret_cast<const uint4*>(vrow);
-                const float2 t0 = __half22float2(*reinterpret_cast<const __half2*>(&w.x));
-                const float2 t1 = __half22float2(*reinterpret_cast<const __half2*>(&w.y));
-                const float2 t2 = __half22float2(*reinterpret_cast<const __half2*>(&w.z));
-                const float2 t3 = __half22float2(*reinterpret_cast<const __half2*>(&w.w));
-                vf[0] = t0.x; vf[1] = t0.y; vf[2] = t1.x; vf[3] = t1.y; vf[4] = t2.x; vf[5] = t2.y; vf[6] = t3.x; vf[7] = t3.y;
-            }
-#pragma unroll
-            for (int g = 0; g < GMAX; ++g) {
-                const float pg = __shfl_sync(0xffffffffu, p_l[g], kk);
-#pragma unroll
-                for (int c = 0; c < C; ++c) acc[g][c] = fmaf(pg, vf[c], acc[g][c]);
-            }
-        }
+        __syncwarp();   // every lane has read the V tile
+        if (more) stage_rows<D>(s_v, vbase + (uint64_t)next * pc.v_s1, pc.v_s1, min(32u, key_end - next), lane);
+        else cp_async_commit();
     }
-    // merge the warps of the CTA
+    cp_async_wait_group<0>();
+    __syncthreads();   // every warp is done with its tiles: the memory is reused for the merge
+    // merge the warps of the CTA: thread (g, t4) holds columns 8 nt + 2 t4 + {0, 1} of head g
+    if (head) {
 #pragma unroll
-    for (int g = 0; g < GMAX; ++g) {
-#pragma unroll
-        for (int c = 0; c < C; ++c) s_acc[warp][g][lane * C + c] = acc[g][c];
-        if (lane == 0) {
-            s_acc[warp][g][D] = m_run[g];
-            s_acc[warp][g][D + 1] = l_run[g];
+        for (int nt = 0; nt < NT; ++nt) {
+            s_acc[warp][g][8 * nt + 2 * t4] = oc[nt][0];
+            s_acc[warp][g][8 * nt + 2 * t4 + 1] = oc[nt][1];
+        }
+        if (t4 == 0) {
+            s_acc[warp][g][D] = m_run;
+            s_acc[warp][g][D + 1] = l_run;
         }
     }
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < G * D; i += kFaWarps * 32) {
-        const uint32_t g = i / D, d = i - g * D;
-        float mx = __uint_as_float(0xFF800000u);
+        const uint32_t gg = i / D, d = i - gg * D;
+        float mx = ninf;
 #pragma unroll
-        for (int w = 0; w < kFaWarps; ++w) mx = fmaxf(mx, s_acc[w][g][D]);
+        for (int w = 0; w < kFaWarps; ++w) mx = fmaxf(mx, s_acc[w][gg][D]);
         float num = 0.0f, den = 0.0f;
 #pragma unroll
         for (int w = 0; w < kFaWarps; ++w) {
-            const float mw = s_acc[w][g][D];
-            const float f = mw == __uint_as_float(0xFF800000u) ? 0.0f : expf(mw - mx);
-            num = fmaf(s_acc[w][g][d], f, num);
-            den = fmaf(s_acc[w][g][D + 1], f, den);
+            const float mw = s_acc[w][gg][D];
+            const float f = mw == ninf ? 0.0f : expf(mw - mx);
+            num = fmaf(s_acc[w][gg][d], f, num);
+            den = fmaf(s_acc[w][gg][D + 1], f, den);
         }
-        const uint64_t r = (uint64_t)iq1 * pc.n_head + h0 + g;   // output row
+        const uint64_t r = (uint64_t)iq1 * pc.n_head + h0 + gg;   // output row
         if (n_splits == 1u) {
             o[pc.o_off + r * D + d] = num / den;
         } else {
-            float* pr = part + pc.part_off + ((uint64_t)z * pc.n_q * pc.n_head + r) * (D + 2);
-            pr[2 + d] = num;
+            float* pr = part + pc.part_off + ((uint64_t)z * pc.n_q * pc.n_head + r) * (D + 4);   // max, sum, 2 unused, D sums
+            pr[4 + d] = num;
             if (d == 0) {
                 pr[0] = mx;
                 pr[1] = den;
@@ -591,42 +674,84 @@ __global__ void __launch_bounds__(kFaWarps * 32) flash_decode_kernel(const float
     }
 }
 
-// one thread per output element: merges the partial results of the key splits
-__global__ void __launch_bounds__(256) flash_combine_kernel(const float* __restrict__ part, float* __restrict__ o,
+// merges the partial results of the key splits: one CTA per output row; the splits' maxima and sums are read in parallel,
+// then every thread sums its columns over the splits (independent, coalesced loads)
+constexpr uint32_t kFaMaxSplits = 1024;
+__global__ void __launch_bounds__(128) flash_combine_kernel(const float* __restrict__ part, float* __restrict__ o,
                                                             uint32_t D, uint32_t rows, uint32_t n_splits, uint32_t part_off,
                                                             uint32_t o_off) {
+    __shared__ float s_f[kFaMaxSplits];   // exp(m_z - max) per split
+    __shared__ float s_red[4];
     pdl_trigger();
     pdl_wait();
-    const uint64_t i = linear_id();
-    if (i >= (uint64_t)rows * D) return;
-    const uint32_t r = (uint32_t)(i / D), d = (uint32_t)(i - (uint64_t)r * D);
-    float mx = __uint_as_float(0xFF800000u);
-    for (uint32_t z = 0; z < n_splits; ++z) mx = fmaxf(mx, part[part_off + ((uint64_t)z * rows + r) * (D + 2)]);
-    float num = 0.0f, den = 0.0f;
-    for (uint32_t z = 0; z < n_splits; ++z) {
-        const float* pr = part + part_off + ((uint64_t)z * rows + r) * (D + 2);
-        const float f = pr[0] == __uint_as_float(0xFF800000u) ? 0.0f : expf(pr[0] - mx);
-        num = fmaf(pr[2 + d], f, num);
-        den = fmaf(pr[1], f, den);
+    const uint32_t r = blockIdx.x, t = threadIdx.x;
+    const float ninf = __uint_as_float(0xFF800000u);
+    const float* base = part + part_off + (uint64_t)r * (D + 4);
+    const uint64_t zs = (uint64_t)rows * (D + 4);   // floats between two splits of a row
+    float mx = ninf;
+    for (uint32_t z = t; z < n_splits; z += 128u) {
+        const float m = base[z * zs];
+        s_f[z] = m;
+        mx = fmaxf(mx, m);
     }
-    o[o_off + (uint64_t)r * D + d] = num / den;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if ((t & 31u) == 0) s_red[t >> 5] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    __syncthreads();
+    float den = 0.0f;
+    for (uint32_t z = t; z < n_splits; z += 128u) {
+        const float f = s_f[z] == ninf ? 0.0f : expf(s_f[z] - mx);
+        s_f[z] = f;
+        den = fmaf(base[z * zs + 1], f, den);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) den += __shfl_xor_sync(0xffffffffu, den, off);
+    if ((t & 31u) == 0) s_red[t >> 5] = den;
+    __syncthreads();
+    den = (s_red[0] + s_red[1]) + (s_red[2] + s_red[3]);
+    // columns: D / 4 float4 columns x (128 / (D / 4)) groups of splits, then the groups are added in shared memory
+    __shared__ float4 s_part[128];
+    const uint32_t cols = D >> 2, groups = 128u / cols, col = t % cols, grp = t / cols;
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (uint32_t z = grp; z < n_splits; z += groups) {
+        const float4 x = *reinterpret_cast<const float4*>(base + z * zs + 4 + 4u * col);
+        const float f = s_f[z];
+        num.x = fmaf(x.x, f, num.x);
+        num.y = fmaf(x.y, f, num.y);
+        num.z = fmaf(x.z, f, num.z);
+        num.w = fmaf(x.w, f, num.w);
+    }
+    s_part[t] = num;
+    __syncthreads();
+    if (grp == 0) {
+        for (uint32_t gI = 1; gI < groups; ++gI) {
+            const float4 x = s_part[gI * cols + col];
+            num.x += x.x;
+            num.y += x.y;
+            num.z += x.z;
+            num.w += x.w;
+        }
+        *reinterpret_cast<float4*>(o + o_off + (uint64_t)r * D + 4u * col) =
+            make_float4(num.x / den, num.y / den, num.z / den, num.w / den);
+    }
 }
 
 template <int D>
-static void launch_flash_d(const LaunchArgs& a, const FlashArgs& pc, uint32_t G, uint32_t n_splits) {
+static bool launch_flash_d(const LaunchArgs& a, const FlashArgs& pc, uint32_t n_splits) {
+    constexpr size_t smem = flash_smem_bytes<D>();
+    if (!ensure_dynamic_smem<flash_decode_kernel<D>>((int)smem)) return false;
     const dim3 grid(n_splits, pc.n_head_kv, pc.n_q), block(kFaWarps * 32);
-    const float* q = (const float*)a.ptr[0];
-    const __half *k = (const __half*)a.ptr[1], *v = (const __half*)a.ptr[2], *m = (const __half*)a.ptr[3];
-    float *o = (float*)a.ptr[4], *part = (float*)a.ptr[5];
-    if (G == 1u) launch_pdl(flash_decode_kernel<D, 1>, grid, block, 0, a.stream, q, k, v, m, o, part, pc, n_splits);
-    else if (G == 2u) launch_pdl(flash_decode_kernel<D, 2>, grid, block, 0, a.stream, q, k, v, m, o, part, pc, n_splits);
-    else if (G <= 4u) launch_pdl(flash_decode_kernel<D, 4>, grid, block, 0, a.stream, q, k, v, m, o, part, pc, n_splits);
-    else launch_pdl(flash_decode_kernel<D, 8>, grid, block, 0, a.stream, q, k, v, m, o, part, pc, n_splits);
+    launch_pdl(flash_decode_kernel<D>, grid, block, smem, a.stream, (const float*)a.ptr[0], (const __half*)a.ptr[1],
+               (const __half*)a.ptr[2], (const __half*)a.ptr[3], (float*)a.ptr[4], (float*)a.ptr[5], pc, n_splits);
+    return true;
 }
 
 // ameva_flash_attn: bindings 0 q f32, 1 k f16, 2 v f16, 3 mask f16 (any range when has_mask = 0), 4 dst f32,
 // 5 scratch for the key splits (any range >= 4 bytes: the launcher uses as many splits as it holds, each taking
-// n_q * n_head * (DV + 2) floats from part_off); push = the reference's 31 words (ameva_flash_attn.comp:46-58) with
+// n_q * n_head * (DV + 4) floats from part_off); push = the reference's 31 words (ameva_flash_attn.comp:46-58) with
 // kv_types 0x11 (f16, f16); split_keys is chosen here (the pushed value is ignored), tile_base must be 0.
 AcResult launch_flash_attn(const LaunchArgs& a) {
     FlashArgs pc;
@@ -636,7 +761,7 @@ AcResult launch_flash_attn(const LaunchArgs& a) {
         return AC_ERR_KERNEL_ARG_INVALID;
     const uint32_t G = pc.n_head / pc.n_head_kv;
     if (pc.D != pc.DV || (pc.D != 64u && pc.D != 128u && pc.D != 256u) || pc.kv_types != 0x11u || u2f_host(pc.max_bias) != 0.0f ||
-        G > 8u)
+        G > (uint32_t)kFaHeads)
         return AC_ERR_FEATURE_NOT_SUPPORTED;
     if ((pc.k_off | pc.k_s1 | pc.k_s2 | pc.v_off | pc.v_s1 | pc.v_s2) & 7u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     if (((uintptr_t)a.ptr[1] | (uintptr_t)a.ptr[2]) & 15u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
@@ -648,27 +773,33 @@ AcResult launch_flash_attn(const LaunchArgs& a) {
                                                 pc.m_s1, pc.m_s2, 0u) * 2u) ||
         a.range[4] < ((uint64_t)pc.o_off + rows * pc.D) * 4u)
         return AC_ERR_INVALID_BUFFER_SIZE;
-    // key splits: about two CTAs per SM, at least 128 keys each, as many as the scratch holds
+    // key splits: one wave of CTAs (as many as are resident at once), at least 128 keys (one block of 32 per warp) each,
+    // as many as the scratch holds
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
     const uint64_t ctas = (uint64_t)pc.n_head_kv * pc.n_q;
-    uint32_t n_splits = (uint32_t)((2u * sms + ctas - 1u) / ctas);
+    const size_t smem = pc.D == 64u ? flash_smem_bytes<64>() : pc.D == 128u ? flash_smem_bytes<128>() : flash_smem_bytes<256>();
+    uint32_t per_sm = (uint32_t)((227u * 1024u) / (smem + 1024u));
+    if (per_sm > 4u) per_sm = 4u;
+    if (per_sm < 1u) per_sm = 1u;
+    uint32_t n_splits = (uint32_t)(((uint64_t)per_sm * sms) / ctas);
     const uint32_t max_by_keys = (pc.n_kv + 127u) / 128u;
     if (n_splits > max_by_keys) n_splits = max_by_keys;
-    const uint64_t per_split = rows * (pc.D + 2u) * 4u;
+    const uint64_t per_split = rows * (pc.D + 4u) * 4u;
     const uint64_t room = a.range[5] > (uint64_t)pc.part_off * 4u ? a.range[5] - (uint64_t)pc.part_off * 4u : 0u;
     if ((uint64_t)n_splits * per_split > room) n_splits = (uint32_t)(room / per_split);
+    // (the merge of the splits reads and writes 16 bytes at a time)
+    if (((uintptr_t)a.ptr[5] | (uintptr_t)a.ptr[4]) & 15u || ((pc.part_off | pc.o_off) & 3u)) n_splits = 1u;
     if (n_splits < 2u) n_splits = 1u;
-    if (n_splits > 65535u) n_splits = 65535u;
+    if (n_splits > kFaMaxSplits) n_splits = kFaMaxSplits;
     pc.split_keys = ((pc.n_kv + n_splits - 1u) / n_splits + 31u) & ~31u;
     n_splits = (pc.n_kv + pc.split_keys - 1u) / pc.split_keys;
-    if (pc.D == 64u) launch_flash_d<64>(a, pc, G, n_splits);
-    else if (pc.D == 128u) launch_flash_d<128>(a, pc, G, n_splits);
-    else launch_flash_d<256>(a, pc, G, n_splits);
+    const bool fits = pc.D == 64u ? launch_flash_d<64>(a, pc, n_splits)
+                      : pc.D == 128u ? launch_flash_d<128>(a, pc, n_splits) : launch_flash_d<256>(a, pc, n_splits);
+    if (!fits) return AC_ERR_INVALID_WORK_GROUP_SIZE;
     AcResult rc = check_launch();
     if (rc != AC_SUCCESS || n_splits == 1u) return rc;
-    const uint64_t total = rows * pc.D;
-    launch_pdl(flash_combine_kernel, dim3((unsigned)((total + 255u) / 256u)), dim3(256), 0, a.stream, (const float*)a.ptr[5],
-               (float*)a.ptr[4], pc.D, (uint32_t)rows, n_splits, pc.part_off, pc.o_off);
+    launch_pdl(flash_combine_kernel, dim3((unsigned)rows), dim3(128), 0, a.stream, (const float*)a.ptr[5], (float*)a.ptr[4],
+               pc.D, (uint32_t)rows, n_splits, pc.part_off, pc.o_off);
     return check_launch();
 }
 

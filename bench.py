@@ -771,6 +771,90 @@ def sub_line(env, name, mode, steps, warmup, want_roof):
         m.destroy()
 
 
+def layer_op_lines(env, steps=3):
+    """The HBM-bound ops next to the mul_mat in a decoder (1 GPU): the f16 LM-head GEMV (BitNet-2B: 128256 x 2560) and
+    token-generation attention over an f16 KV cache (32 heads on 8 KV heads of 128, one cache per layer, the layers'
+    caches together larger than L2). Replayed batches of one launch per layer, CUDA events on the launching stream;
+    `frac` is algorithmic bytes / time over the measured copy bandwidth."""
+    import struct
+    torch, ctx = env.torch, env.ctx
+    pk = peaks()
+
+    def fbits(v):
+        return struct.unpack("<I", struct.pack("<f", float(v)))[0]
+
+    def timed(record, launches):
+        batch = ctx.batch(4 * launches + 8, 0)
+        record(batch)
+        batch.instantiate()
+        secs = None
+        try:
+            for it in range(2 + steps):
+                start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(env.stream):
+                    lead = batch.replay()
+                    start.record()
+                    evs = [batch.replay() for _ in range(steps)]
+                    end.record()
+                for ev in [lead] + evs:
+                    ev.wait(600_000_000_000)
+                    ev.destroy()
+                end.synchronize()
+                secs = start.elapsed_time(end) / 1e3 / (steps * launches)
+        finally:
+            batch.destroy()
+        return secs
+
+    out = {}
+    rng = np.random.default_rng(0)
+    # ---- LM head: one buffer of 657 MB, read once per launch ----
+    n_rows, n_in, launches = 128256, 2560, 8
+    W = (rng.standard_normal((n_rows, n_in), dtype=np.float32) * 0.02).astype(np.float16)
+    x = rng.standard_normal(n_in).astype(np.float32)
+    wb, xb, yb = ctx.buffer(data=W), ctx.buffer(data=x), ctx.buffer(n_rows * 4)
+    kern = ctx.kernel("bitnet_gemv_f16_w4")
+    s = timed(lambda b: [b.dispatch(kern, [wb, xb, yb], [n_in, n_rows, 0], (1, 1, 1)) for _ in range(launches)], launches)
+    y = yb.read(np.float32)
+    rows = rng.integers(0, n_rows, 512)
+    want = W[rows].astype(np.float64) @ x.astype(np.float64)
+    norm = np.abs(W[rows].astype(np.float64)) @ np.abs(x.astype(np.float64))
+    nbytes = n_rows * n_in * 2 + n_in * 4 + n_rows * 4
+    out["lm_head_f16"] = {"workload": f"f16 GEMV {n_rows}x{n_in} M=1 (bitnet_gemv_f16)", "us": s * 1e6,
+                          "achieved": nbytes / s / 1e9, "unit": "GB/s", "peak": pk["hbm_gbs"], "frac": nbytes / s / 1e9 / pk["hbm_gbs"],
+                          "parity_max_normalised_error": float(np.max(np.abs(y[rows] - want) / norm))}
+    for b in (wb, xb, yb):
+        b.destroy()
+    del W
+    # ---- attention at token generation ----
+    D, n_head, n_head_kv, n_q = 128, 32, 8, 1
+    fk = ctx.kernel("ameva_flash_attn")
+    for label, n_kv, layers in (("flash_decode_4k", 4096, 32), ("flash_decode_32k", 32768, 4)):
+        kv = (rng.standard_normal((n_head_kv, n_kv, D), dtype=np.float32)).astype(np.float16)
+        ks = [ctx.buffer(data=kv) for _ in range(layers)]
+        vs = [ctx.buffer(data=kv[::-1].copy()) for _ in range(layers)]
+        q = rng.standard_normal((n_head, n_q, D)).astype(np.float32)
+        mask = np.zeros((n_q, n_kv), np.float16)
+        qb, mb, ob, pb = ctx.buffer(data=q), ctx.buffer(data=mask), ctx.buffer(n_q * n_head * D * 4), ctx.buffer(16 << 20)
+        push = [D, D, n_kv, n_q, n_head, n_head_kv, 0x11, 1, 0, D, D * n_q, 0, D, D * n_kv, 0, D, D * n_kv, 0, n_kv, 0,
+                1, 0, fbits(1.0 / np.sqrt(D)), 0, 0, 0, 0, 0, 0, 0, 0]
+        s = timed(lambda b: [b.dispatch(fk, [qb, ks[i], vs[i], mb, ob, pb], push, (1, 1, 1)) for i in range(layers)], layers)
+        got = ob.read(np.float32).reshape(n_q, n_head, D)
+        kd, vd = kv.astype(np.float64), kv[::-1].astype(np.float64)
+        worst = 0.0
+        for h in (0, 13, 31):
+            sc = (q[h, 0].astype(np.float64) @ kd[h // 4].T) / np.sqrt(D)
+            p = np.exp(sc - sc.max())
+            worst = max(worst, float(np.max(np.abs(got[0, h] - (p @ vd[h // 4]) / p.sum()))))
+        nbytes = 2 * n_head_kv * n_kv * D * 2 + n_kv * 2 + q.nbytes + n_q * n_head * D * 4
+        out[label] = {"workload": f"attention, 1 query x {n_kv} cached positions, {n_head} heads on {n_head_kv} KV heads of {D}, "
+                                  f"f16 cache, {layers} caches in rotation ({layers * 2 * kv.nbytes / 1e6:.0f} MB)",
+                      "us": s * 1e6, "achieved": nbytes / s / 1e9, "unit": "GB/s", "peak": pk["hbm_gbs"],
+                      "frac": nbytes / s / 1e9 / pk["hbm_gbs"], "launches_per_step": 2, "parity_max_abs_error": worst}
+        for b in ks + vs + [qb, mb, ob, pb]:
+            b.destroy()
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -781,6 +865,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="leave the `decode` object out of the line")
     ap.add_argument("--no-sharded", action="store_true", help="leave the `sharded` object out of the line")
+    ap.add_argument("--no-layer-ops", action="store_true", help="leave the `layer_ops` object out of the line")
     ap.add_argument("--sharded-primary", action="store_true",
                     help="N > 1: row-shard the primary workload too (strong scaling) instead of token-parallel replicas")
     ap.add_argument("--exchange", choices=["copy", "fused", "nccl"], default="copy",
@@ -828,6 +913,12 @@ def main():
     if not args.no_sharded and name == "cfg2":
         sharded = {w: sub_line(env, w, "sharded" if world > 1 else "single", max(10, min(sub_steps, 50)) if
                                WORKLOADS[w][1] > GEMV_MAX_M else sub_steps, 3, False) for w in SHARDED_LINES}
+    layer_ops = None
+    if not args.no_layer_ops and world == 1 and name == "cfg2":
+        try:
+            layer_ops = layer_op_lines(env)
+        except Exception as e:   # (an aid beside the metric: its failure is reported, the line still goes out)
+            layer_ops = {"error": repr(e)}
 
     if rank == 0:
         par = {"single": "single GPU",
@@ -862,6 +953,8 @@ def main():
             line["decode"] = decode
         if sharded:
             line["sharded"] = sharded
+        if layer_ops:
+            line["layer_ops"] = layer_ops
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = run_cpu_baseline(t, M, N, K, m.blocks, m.scale, m.x, m.unit)
         print(json.dumps(line), flush=True)

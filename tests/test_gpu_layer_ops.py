@@ -302,7 +302,8 @@ def test_flash_attn_decode(ctx, D, n_head, n_head_kv, n_kv, n_q, masked, softcap
                                                                        m_pitch=m_pitch))
     got = ob.read(np.float32).reshape(n_q, n_head, D)
     want = ops.flash_attn_ext(q, k, v, mask[:, :n_kv] if masked else None, scale, softcap)
-    assert np.max(np.abs(got - want)) <= 2e-5 * max(1.0, float(np.max(np.abs(want))))
+    # queries and probabilities enter the tensor cores as f16 (ggml's CPU kernel rounds the queries to f16 too)
+    assert np.max(np.abs(got - want)) <= 2e-3 * max(1.0, float(np.max(np.abs(want))))
     for b in {qb, kb, vb, mb, ob, pb}:
         b.destroy()
 
