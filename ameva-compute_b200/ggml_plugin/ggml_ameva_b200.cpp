@@ -289,6 +289,9 @@ struct Backend {
     AcBuffer* ah = nullptr;   // fp16 [M][K], the tensor-core operand (M > 8)
     AcBuffer* ae = nullptr;   // f32 [M], the per-row range factors of that operand
     size_t aq_bytes = 0, ad_bytes = 0, ah_bytes = 0, ae_bytes = 0;
+    AcBuffer* op_status = nullptr;   // {count, lowest node} of refused GET_ROWS / SET_ROWS indices
+    AcBuffer* fa_part = nullptr;     // partial results of the key splits of FLASH_ATTN_EXT
+    size_t op_status_bytes = 0, fa_part_bytes = 0;
 };
 
 AcKernel* kernel(Backend* be, const char* name) {
@@ -424,6 +427,148 @@ bool rms_norm_supported(const ggml_tensor* node) {
     return a && is_f32_rows(a) && is_f32_rows(node) && n_elems(a) == n_elems(node) && a->ne[0] == node->ne[0];
 }
 
+// ---- the ops around the mul_mats of a decoder layer: ROPE, GET_ROWS, SET_ROWS, SOFT_MAX, FLASH_ATTN_EXT -------------------
+// They run under the reference's kernel contracts (ggml-ameva.cpp:3965-3995 enc_rope, :4037-4060 enc_set_rows,
+// :4113-4135 enc_get_rows, enc_soft_max, enc_flash_attn): strides in elements of the tensor's type, a tensor that does
+// not start on a 64-byte boundary of its buffer is bound from the boundary below with its element offset in the push
+// constants.
+size_t elem_size(enum ggml_type t) {
+    switch (t) {
+        case GGML_TYPE_F32: case GGML_TYPE_I32: return 4;
+        case GGML_TYPE_F16: return 2;
+        case GGML_TYPE_I64: return 8;
+        default: return 0;
+    }
+}
+bool elem_strides(const ggml_tensor* t, size_t es) {   // element 0 stride = one element, the others whole elements in 32 bits
+    if (!t || !es || t->nb[0] != es) return false;
+    for (int i = 1; i < 4; ++i)
+        if (t->nb[i] % es || t->nb[i] / es > 0xFFFFFFFFull) return false;
+    return true;
+}
+uint32_t st(const ggml_tensor* t, int i, size_t es) { return (uint32_t)(t->nb[i] / es); }
+
+bool is_layer_op(enum ggml_op op) {
+    return op == GGML_OP_ROPE || op == GGML_OP_GET_ROWS || op == GGML_OP_SET_ROWS || op == GGML_OP_SOFT_MAX ||
+           op == GGML_OP_FLASH_ATTN_EXT;
+}
+float param_f32(const ggml_tensor* t, int i) {
+    float f;
+    memcpy(&f, &t->op_params[i], 4);
+    return f;
+}
+
+const char* layer_op_static_reason(const ggml_tensor* node) {
+    const ggml_tensor *a = node->src[0], *b = node->src[1];
+    switch (node->op) {
+        case GGML_OP_ROPE: {
+            if (!a || !b || (a->type != GGML_TYPE_F32 && a->type != GGML_TYPE_F16) || node->type != a->type) return "rope: f32 or f16 only";
+            const size_t es = elem_size(a->type);
+            if (!elem_strides(a, es) || !elem_strides(node, es)) return "rope: strides are not whole elements";
+            if (b->type != GGML_TYPE_I32 || b->ne[0] < a->ne[2] || b->nb[0] != 4) return "rope: positions are not i32 [ne2]";
+            const int n_dims = node->op_params[1], mode = node->op_params[2];
+            if (mode != 0 && mode != 2) return "rope: only the NORMAL and NEOX modes";
+            if (n_dims < 0 || n_dims > a->ne[0] || (n_dims & 1) || (a->ne[0] & 1)) return "rope: n_dims";
+            if (node->src[2] && (node->src[2]->type != GGML_TYPE_F32 || node->src[2]->ne[0] < n_dims / 2)) return "rope: frequency factors";
+            for (int i = 0; i < 4; ++i)
+                if (a->ne[i] != node->ne[i]) return "rope: shape";
+            return nullptr;
+        }
+        case GGML_OP_GET_ROWS: {
+            if (!a || !b || (a->type != GGML_TYPE_F32 && a->type != GGML_TYPE_F16) || node->type != GGML_TYPE_F32) return "get_rows: f32 / f16 rows to f32";
+            if (b->type != GGML_TYPE_I32 || !elem_strides(b, 4) || !elem_strides(a, elem_size(a->type)) || !elem_strides(node, 4))
+                return "get_rows: indices are not i32 or strides are not whole elements";
+            if (node->ne[0] != a->ne[0] || node->ne[1] != b->ne[0] || node->ne[2] != b->ne[1] || node->ne[3] != b->ne[2]) return "get_rows: shape";
+            return nullptr;
+        }
+        case GGML_OP_SET_ROWS: {
+            if (!a || !b || a->type != GGML_TYPE_F32 || (node->type != GGML_TYPE_F32 && node->type != GGML_TYPE_F16)) return "set_rows: f32 rows to f32 / f16";
+            if ((b->type != GGML_TYPE_I64 && b->type != GGML_TYPE_I32) || b->nb[0] != elem_size(b->type) || b->nb[1] % 4 || b->nb[2] % 4)
+                return "set_rows: indices";
+            if (!elem_strides(a, 4) || !elem_strides(node, elem_size(node->type))) return "set_rows: strides are not whole elements";
+            if (a->ne[0] != node->ne[0] || a->ne[2] != node->ne[2] || a->ne[3] != node->ne[3] || b->ne[0] != a->ne[1] || !b->ne[1] || !b->ne[2])
+                return "set_rows: shape";
+            return nullptr;
+        }
+        case GGML_OP_SOFT_MAX: {
+            if (!a || a->type != GGML_TYPE_F32 || node->type != GGML_TYPE_F32 || !elem_strides(a, 4) || !elem_strides(node, 4)) return "soft_max: f32 only";
+            if (node->src[2]) return "soft_max: attention sinks";
+            if (param_f32(node, 1) != 0.0f) return "soft_max: ALiBi bias";
+            if (b) {
+                if ((b->type != GGML_TYPE_F32 && b->type != GGML_TYPE_F16) || !elem_strides(b, elem_size(b->type))) return "soft_max: mask type";
+                if (b->ne[0] != a->ne[0] || b->ne[1] < a->ne[1] || !b->ne[2] || !b->ne[3] || a->ne[2] % b->ne[2] || a->ne[3] % b->ne[3])
+                    return "soft_max: mask shape";
+            }
+            return nullptr;
+        }
+        case GGML_OP_FLASH_ATTN_EXT: {
+            const ggml_tensor *k = node->src[1], *v = node->src[2], *m = node->src[3];
+            if (!a || !k || !v || a->type != GGML_TYPE_F32 || k->type != GGML_TYPE_F16 || v->type != GGML_TYPE_F16 ||
+                node->type != GGML_TYPE_F32)
+                return "flash_attn: f32 queries on an f16 cache only";
+            if (node->src[4]) return "flash_attn: attention sinks";
+            if (param_f32(node, 1) != 0.0f) return "flash_attn: ALiBi bias";
+            const int64_t D = a->ne[0];
+            if ((D != 64 && D != 128 && D != 256) || k->ne[0] != D || v->ne[0] != D) return "flash_attn: head size";
+            if (a->ne[3] != 1 || k->ne[3] != 1 || v->ne[3] != 1 || k->ne[1] != v->ne[1] || k->ne[2] != v->ne[2] || !k->ne[2] ||
+                a->ne[2] % k->ne[2] || a->ne[2] / k->ne[2] > 8)
+                return "flash_attn: head grouping";
+            if (!elem_strides(a, 4) || !elem_strides(k, 2) || !elem_strides(v, 2) || !ggml_is_contiguous(node)) return "flash_attn: strides";
+            if ((k->nb[1] | k->nb[2] | v->nb[1] | v->nb[2]) % 16) return "flash_attn: cache rows are not 16-byte aligned";
+            if (node->ne[0] != D || node->ne[1] != a->ne[2] || node->ne[2] != a->ne[1]) return "flash_attn: result shape";
+            if (m && (m->type != GGML_TYPE_F16 || !elem_strides(m, 2) || m->ne[0] < k->ne[1] || m->ne[1] < a->ne[1] || !m->ne[2] || m->ne[3] != 1))
+                return "flash_attn: mask";
+            return nullptr;
+        }
+        default: return "op has no encoder";
+    }
+}
+
+AcBufferBinding bind(AcBuffer* b, uint64_t off, uint64_t range);
+
+// a tensor bound from the 64-byte boundary below it; elem = where the tensor starts inside the binding, in elements
+struct ElemBind {
+    AcBufferBinding b;
+    uint32_t elem;
+};
+bool bind_elems(const ggml_tensor* t, size_t es, ElemBind* out) {
+    const size_t off = tensor_offset(t), base = off & ~(size_t)(kAlign - 1), rem = off - base;
+    if (rem % es) return false;
+    out->b = bind(buffer_of(t)->buf, base, rem + ggml_nbytes(t));
+    out->elem = (uint32_t)(rem / es);
+    return true;
+}
+
+const char* layer_op_reason(const ggml_tensor* node) {
+    if (const char* why = layer_op_static_reason(node)) return why;
+    for (int i = 0; i < GGML_MAX_SRC; ++i) {
+        const ggml_tensor* t = node->src[i];
+        if (!t) continue;
+        if (!own_buffer(t)) return "an operand is not in an AMEVA_B200 buffer";
+        if (tensor_offset(t) % elem_size(t->type)) return "an operand does not start on an element boundary";
+    }
+    if (!own_buffer(node) || tensor_offset(node) % elem_size(node->type)) return "dst is not in an AMEVA_B200 buffer";
+    if (node->op == GGML_OP_FLASH_ATTN_EXT && (tensor_offset(node->src[1]) % 16 || tensor_offset(node->src[2]) % 16 || tensor_offset(node) % 16))
+        return "flash_attn: cache or result not 16-byte aligned";
+    return nullptr;
+}
+
+uint32_t f32_bits(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    return u;
+}
+
+// ggml_rope_yarn_corr_dims (ggml.c): the pair indices between which YaRN blends interpolation and extrapolation
+void rope_corr_dims(int n_dims, int n_ctx_orig, float freq_base, float beta_fast, float beta_slow, float dims[2]) {
+    auto corr_dim = [&](float n_rot) {
+        return n_dims * logf(n_ctx_orig / (n_rot * 2.0f * 3.14159265358979323846f)) / (2.0f * logf(freq_base));
+    };
+    const float start = floorf(corr_dim(beta_fast)), end = ceilf(corr_dim(beta_slow));
+    dims[0] = std::max(0.0f, start);
+    dims[1] = std::min((float)(n_dims - 1), end);
+}
+
 // shapes and types only (at planning time tensors may not be allocated yet)
 bool op_supported_static(const ggml_tensor* op) {
     if (is_view_op(op->op)) return true;
@@ -442,13 +587,14 @@ bool op_supported_static(const ggml_tensor* op) {
         case GGML_OP_MUL: return binary_supported(op);
         case GGML_OP_GLU: return glu_supported(op);
         case GGML_OP_RMS_NORM: return rms_norm_supported(op);
-        default: return false;
+        default: return is_layer_op(op->op) && !layer_op_static_reason(op);
     }
 }
 
 const char* node_reason(const ggml_tensor* node) {
     if (is_view_op(node->op)) return nullptr;
     if (node->op == GGML_OP_MUL_MAT) return mul_mat_reason(node);
+    if (is_layer_op(node->op)) return layer_op_reason(node);
     if (!op_supported_static(node)) return "op, type or shape not built";
     for (int i = 0; i < GGML_MAX_SRC && node->src[i]; ++i)
         if (!own_buffer(node->src[i]) || tensor_offset(node->src[i]) % kAlign)
@@ -472,6 +618,7 @@ struct Recorder {
     uint32_t q_M = 0, q_K = 0;
     int q_scheme = -1;   // 0 per-32, 1 per-256; +2 when the fp16 operand was written too
     int64_t gpu_ops = 0, mul_mats = 0, mmq = 0, mmqb = 0, fused = 0;
+    bool rows_ops = false;   // a GET_ROWS / SET_ROWS was recorded: the index status is read after the batch
 };
 
 struct QuantizedRows {
@@ -685,6 +832,93 @@ bool record_elementwise(Recorder& r, const ggml_tensor* node, const ggml_tensor*
     }
 }
 
+// ROPE, GET_ROWS, SET_ROWS, SOFT_MAX, FLASH_ATTN_EXT: push constants as the reference's encoders build them
+bool record_layer_op(Recorder& r, const ggml_tensor* node, int node_index) {
+    const ggml_tensor *a = node->src[0], *b = node->src[1];
+    const AcBufferBinding status = bind(r.be->op_status, 0, 256);
+    switch (node->op) {
+        case GGML_OP_ROPE: {
+            const ggml_tensor* ff = node->src[2];
+            const size_t es = elem_size(a->type);
+            ElemBind ba, bp, bf, bd;
+            if (!bind_elems(a, es, &ba) || !bind_elems(b, 4, &bp) || !bind_elems(ff ? ff : b, 4, &bf) || !bind_elems(node, es, &bd)) return false;
+            const int n_dims = node->op_params[1], mode = node->op_params[2], n_ctx_orig = node->op_params[4];
+            const float freq_base = param_f32(node, 5), freq_scale = param_f32(node, 6), ext_factor = param_f32(node, 7),
+                        attn_factor = param_f32(node, 8), beta_fast = param_f32(node, 9), beta_slow = param_f32(node, 10);
+            float corr[2];
+            rope_corr_dims(n_dims, n_ctx_orig, freq_base, beta_fast, beta_slow, corr);
+            const float theta_scale = n_dims > 0 ? powf(freq_base, -2.0f / n_dims) : 1.0f;
+            const uint32_t pc[23] = {(uint32_t)node->ne[0], (uint32_t)node->ne[1], (uint32_t)node->ne[2], (uint32_t)node->ne[3],
+                                     ba.elem, st(a, 1, es), st(a, 2, es), st(a, 3, es),
+                                     bd.elem, st(node, 1, es), st(node, 2, es), st(node, 3, es),
+                                     bp.elem, ff ? bf.elem : 0u, (uint32_t)n_dims, mode == 2 ? 1u : 0u,
+                                     ff ? 1u : 0u, f32_bits(theta_scale), f32_bits(freq_scale), f32_bits(ext_factor),
+                                     f32_bits(attn_factor), f32_bits(corr[0]), f32_bits(corr[1])};
+            const AcBufferBinding bb[4] = {ba.b, bp.b, bf.b, bd.b};
+            return dispatch(r, a->type == GGML_TYPE_F16 ? "ameva_rope_f16" : "ameva_rope", bb, 4, pc, sizeof(pc));
+        }
+        case GGML_OP_GET_ROWS: {
+            const size_t es = elem_size(a->type);
+            ElemBind ba, bi, bd;
+            if (!bind_elems(a, es, &ba) || !bind_elems(b, 4, &bi) || !bind_elems(node, 4, &bd)) return false;
+            const uint32_t pc[19] = {(uint32_t)node->ne[0], (uint32_t)b->ne[0], (uint32_t)b->ne[1], (uint32_t)b->ne[2],
+                                     ba.elem, st(a, 1, es), st(a, 2, es), st(a, 3, es),
+                                     bi.elem, st(b, 0, 4), st(b, 1, 4), st(b, 2, 4),
+                                     bd.elem, st(node, 1, 4), st(node, 2, 4), st(node, 3, 4),
+                                     a->type == GGML_TYPE_F16 ? 1u : 0u, (uint32_t)a->ne[1], (uint32_t)node_index};
+            const AcBufferBinding bb[4] = {ba.b, bi.b, status, bd.b};
+            r.rows_ops = true;
+            return dispatch(r, "ameva_get_rows", bb, 4, pc, sizeof(pc));
+        }
+        case GGML_OP_SET_ROWS: {
+            const size_t es = elem_size(node->type);
+            ElemBind ba, bi, bd;
+            if (!bind_elems(a, 4, &ba) || !bind_elems(b, 4, &bi) || !bind_elems(node, es, &bd)) return false;
+            const uint32_t pc[22] = {(uint32_t)a->ne[0], (uint32_t)a->ne[1], (uint32_t)a->ne[2], (uint32_t)a->ne[3],
+                                     ba.elem, st(a, 1, 4), st(a, 2, 4), st(a, 3, 4),
+                                     bi.elem, (uint32_t)(b->nb[0] / 4), (uint32_t)(b->nb[1] / 4), (uint32_t)(b->nb[2] / 4),
+                                     (uint32_t)b->ne[1], (uint32_t)b->ne[2], b->type == GGML_TYPE_I64 ? 1u : 0u, (uint32_t)node->ne[1],
+                                     bd.elem, st(node, 1, es), st(node, 2, es), st(node, 3, es),
+                                     node->type == GGML_TYPE_F16 ? 1u : 0u, (uint32_t)node_index};
+            const AcBufferBinding bb[4] = {ba.b, bi.b, status, bd.b};
+            r.rows_ops = true;
+            return dispatch(r, "ameva_set_rows", bb, 4, pc, sizeof(pc));
+        }
+        case GGML_OP_SOFT_MAX: {
+            const size_t ms = b ? elem_size(b->type) : 4;
+            ElemBind ba, bd, bm;
+            if (!bind_elems(a, 4, &ba) || !bind_elems(node, 4, &bd) || !bind_elems(b ? b : a, ms, &bm)) return false;
+            const uint32_t nrows = (uint32_t)(node->ne[1] * node->ne[2] * node->ne[3]);
+            const uint32_t pc[20] = {(uint32_t)node->ne[0], (uint32_t)node->ne[1], (uint32_t)node->ne[2], nrows,
+                                     ba.elem, st(a, 1, 4), st(a, 2, 4), st(a, 3, 4),
+                                     bd.elem, st(node, 1, 4), st(node, 2, 4), st(node, 3, 4),
+                                     f32_bits(param_f32(node, 0)),
+                                     b ? (b->type == GGML_TYPE_F16 ? 2u : 1u) : 0u, b ? bm.elem : 0u, b ? st(b, 1, ms) : 0u,
+                                     b ? st(b, 2, ms) : 0u, b ? st(b, 3, ms) : 0u, b ? (uint32_t)b->ne[2] : 1u, b ? (uint32_t)b->ne[3] : 1u};
+            const AcBufferBinding bb[3] = {ba.b, bd.b, bm.b};
+            return dispatch(r, "ameva_soft_max", bb, 3, pc, sizeof(pc));
+        }
+        case GGML_OP_FLASH_ATTN_EXT: {
+            const ggml_tensor *k = node->src[1], *v = node->src[2], *m = node->src[3];
+            ElemBind bq, bk, bv, bm, bo;
+            if (!bind_elems(a, 4, &bq) || !bind_elems(k, 2, &bk) || !bind_elems(v, 2, &bv) || !bind_elems(m ? m : a, m ? 2 : 4, &bm) ||
+                !bind_elems(node, 4, &bo))
+                return false;
+            const uint32_t D = (uint32_t)a->ne[0];
+            const uint32_t pc[31] = {D, D, (uint32_t)k->ne[1], (uint32_t)a->ne[1],
+                                     (uint32_t)a->ne[2], (uint32_t)k->ne[2], 0x11u, m ? 1u : 0u,
+                                     bq.elem, st(a, 1, 4), st(a, 2, 4), bk.elem,
+                                     st(k, 1, 2), st(k, 2, 2), bv.elem, st(v, 1, 2),
+                                     st(v, 2, 2), m ? bm.elem : 0u, m ? st(m, 1, 2) : 0u, m ? st(m, 2, 2) : 0u,
+                                     m ? (uint32_t)m->ne[2] : 1u, bo.elem, f32_bits(param_f32(node, 0)), f32_bits(param_f32(node, 2)),
+                                     0u, 0u, 0u, 0u, 0u, 0u, 0u};
+            const AcBufferBinding bb[6] = {bq.b, bk.b, bv.b, bm.b, bo.b, bind(r.be->fa_part, 0, r.be->fa_part_bytes)};
+            return dispatch(r, "ameva_flash_attn", bb, 6, pc, sizeof(pc));
+        }
+        default: return false;
+    }
+}
+
 // RMS_NORM followed by MUL with a weight row of the same width (the RMS_NORM + MUL pair of ameva_find_fusion)
 bool rms_mul_pair(const ggml_tensor* n0, const ggml_tensor* n1) {
     if (!n1 || n0->op != GGML_OP_RMS_NORM || n1->op != GGML_OP_MUL || node_reason(n1)) return false;
@@ -734,7 +968,7 @@ void backend_free(ggml_backend_t backend) {
         std::lock_guard<std::mutex> lock(plugin().mutex);
         for (auto& kv : be->kernels)
             if (ac_runtime_kernel_destroy(kv.second) == AC_SUCCESS) g_count.kernel_destroy++;
-        for (AcBuffer* b : {be->aq, be->ad, be->ah, be->ae})
+        for (AcBuffer* b : {be->aq, be->ad, be->ah, be->ae, be->op_status, be->fa_part})
             if (b && ac_runtime_buffer_destroy(b) == AC_SUCCESS) g_count.buffer_destroy++;
         plugin().live_backends--;
     }
@@ -787,6 +1021,13 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
     if ((aq_need && !grow(&be->aq, &be->aq_bytes, aq_need)) || (ad_need && !grow(&be->ad, &be->ad_bytes, ad_need)) ||
         (ah_need && !grow(&be->ah, &be->ah_bytes, ah_need)) || (ae_need && !grow(&be->ae, &be->ae_bytes, ae_need)))
         return GGML_STATUS_ALLOC_FAILED;
+    bool layer_ops = false;
+    for (int i = 0; i < n && !layer_ops; ++i) layer_ops = is_layer_op(ggml_graph_node(cgraph, i)->op);
+    if (layer_ops) {
+        if (!grow(&be->op_status, &be->op_status_bytes, 256) || !grow(&be->fa_part, &be->fa_part_bytes, 8u << 20)) return GGML_STATUS_ALLOC_FAILED;
+        const uint32_t clear[2] = {0u, 0xFFFFFFFFu};
+        if (ac_runtime_buffer_write(be->op_status, 0, clear, sizeof(clear)) != AC_SUCCESS) return GGML_STATUS_FAILED;
+    }
     Recorder r;
     r.be = be;
     AcBatchDesc bd = {AC_ABI_VERSION, (uint32_t)sizeof(AcBatchDesc), 16384u, 0u};
@@ -840,6 +1081,9 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
                 r.fused += 1;
                 consumed_upto = j;
             }
+        } else if (is_layer_op(node->op)) {
+            ok = record_layer_op(r, node, i);
+            r.gpu_ops += 1;
         } else {
             ok = record_elementwise(r, node, nullptr);
             r.gpu_ops += 1;
@@ -885,6 +1129,14 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
         if (ac_runtime_event_destroy(ev) == AC_SUCCESS) g_count.event_destroy++;
     }
     ac_runtime_batch_destroy(r.batch);
+    if (rc == AC_SUCCESS && r.rows_ops) {   // an index outside its table or cache fails the graph (ggml asserts on the CPU)
+        uint32_t st2[2] = {0u, 0u};
+        rc = ac_runtime_buffer_read(be->op_status, 0, st2, sizeof(st2));
+        if (rc == AC_SUCCESS && st2[0]) {
+            fprintf(stderr, "ggml-ameva-b200: %u row indices out of range, first at node %u\n", st2[0], st2[1]);
+            rc = AC_ERR_KERNEL_ARG_INVALID;
+        }
+    }
     if (rc == AC_SUCCESS && fi == AMEVA_FAIL_INVALIDATE_DST) {
         fprintf(stderr, "ggml-ameva-b200 [FAILURE_INJECTION]: INVALIDATE_DST_FAIL triggered\n");
         rc = AC_ERR_BUFFER_NOT_MAPPED;
@@ -1035,11 +1287,13 @@ const char* ggml_backend_ameva_abi_check(void) {
             const char* name;
         } kOps[] = {{GGML_OP_NONE, "NONE"},       {GGML_OP_ADD, "ADD"},         {GGML_OP_MUL, "MUL"},   {GGML_OP_RMS_NORM, "RMS_NORM"},
                     {GGML_OP_MUL_MAT, "MUL_MAT"}, {GGML_OP_RESHAPE, "RESHAPE"}, {GGML_OP_VIEW, "VIEW"}, {GGML_OP_PERMUTE, "PERMUTE"},
-                    {GGML_OP_TRANSPOSE, "TRANSPOSE"}, {GGML_OP_GLU, "GLU"}};
+                    {GGML_OP_TRANSPOSE, "TRANSPOSE"}, {GGML_OP_GLU, "GLU"}, {GGML_OP_ROPE, "ROPE"}, {GGML_OP_GET_ROWS, "GET_ROWS"},
+                    {GGML_OP_SET_ROWS, "SET_ROWS"}, {GGML_OP_SOFT_MAX, "SOFT_MAX"}, {GGML_OP_FLASH_ATTN_EXT, "FLASH_ATTN_EXT"}};
         static const struct {
             enum ggml_type type;
             const char* name;
-        } kTypes[] = {{GGML_TYPE_F32, "f32"}, {GGML_TYPE_Q4_0, "q4_0"}, {GGML_TYPE_Q8_0, "q8_0"}, {GGML_TYPE_Q4_K, "q4_K"}};
+        } kTypes[] = {{GGML_TYPE_F32, "f32"}, {GGML_TYPE_Q4_0, "q4_0"}, {GGML_TYPE_Q8_0, "q8_0"}, {GGML_TYPE_Q4_K, "q4_K"},
+                      {GGML_TYPE_F16, "f16"}, {GGML_TYPE_I32, "i32"}, {GGML_TYPE_I64, "i64"}};
         for (const auto& o : kOps)
             if (!what && strcmp(ggml_op_name(o.op), o.name) != 0) what = "enum ggml_op";
         for (const auto& t : kTypes)

@@ -31,7 +31,8 @@ def rope_yarn_corr_dims(n_dims: int, n_ctx_orig: int, freq_base: float, beta_fas
 
 def rope_theta_scale(freq_base: float, n_dims: int):
     """powf(freq_base, -2.0f / n_dims), the factor between the angles of neighbouring pairs."""
-    return f32(np.power(f32(freq_base), f32(-2.0) / f32(n_dims))) if n_dims > 0 else f32(1.0)
+    # (libm's powf is correctly rounded: the double result rounded once stands in for it)
+    return f32(math.pow(float(f32(freq_base)), float(f32(-2.0) / f32(n_dims)))) if n_dims > 0 else f32(1.0)
 
 
 def rope(x, pos, n_dims: int, neox: bool, freq_base: float, freq_scale: float = 1.0, ext_factor: float = 0.0,

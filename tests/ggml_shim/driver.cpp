@@ -14,6 +14,7 @@
 //                                                  view of a weight) followed by a graph with M2 activation rows that
 //                                                  needs larger scratch; counters, host-side failure injection, teardown.
 //                                                  Inputs are read from <dir>, outputs written there.
+#include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -37,6 +38,9 @@ static void traits(enum ggml_type t, size_t* type_size, int64_t* blck) {
         case GGML_TYPE_Q4_0: *type_size = 18; *blck = 32; break;
         case GGML_TYPE_Q8_0: *type_size = 34; *blck = 32; break;
         case GGML_TYPE_Q4_K: *type_size = 144; *blck = 256; break;
+        case GGML_TYPE_F16: *type_size = 2; *blck = 1; break;
+        case GGML_TYPE_I32: *type_size = 4; *blck = 1; break;
+        case GGML_TYPE_I64: *type_size = 8; *blck = 1; break;
         default: fprintf(stderr, "shim: type %d not in the test set\n", (int)t); abort();
     }
 }
@@ -51,6 +55,11 @@ size_t ggml_nbytes(const ggml_tensor* t) {
     size_t ts;
     int64_t bs;
     traits(t->type, &ts, &bs);
+    if (bs == 1) {   // as ggml: the span from the first to the last element, whatever the strides
+        size_t n = ts;
+        for (int i = 0; i < 4; ++i) n += (size_t)(t->ne[i] - 1) * t->nb[i];
+        return n;
+    }
     return (size_t)(t->ne[0] / bs) * ts * (size_t)(t->ne[1] * t->ne[2] * t->ne[3]);
 }
 bool ggml_is_contiguous(const ggml_tensor* t) {
@@ -74,6 +83,11 @@ const char* ggml_op_name(enum ggml_op op) {
         case GGML_OP_TRANSPOSE: return "TRANSPOSE";
         case GGML_OP_GLU: return "GLU";
         case GGML_OP_SUB: return "SUB";
+        case GGML_OP_ROPE: return "ROPE";
+        case GGML_OP_GET_ROWS: return "GET_ROWS";
+        case GGML_OP_SET_ROWS: return "SET_ROWS";
+        case GGML_OP_SOFT_MAX: return "SOFT_MAX";
+        case GGML_OP_FLASH_ATTN_EXT: return "FLASH_ATTN_EXT";
         default: return "OP";
     }
 }
@@ -83,6 +97,9 @@ const char* ggml_type_name(enum ggml_type t) {
         case GGML_TYPE_Q4_0: return "q4_0";
         case GGML_TYPE_Q8_0: return "q8_0";
         case GGML_TYPE_Q4_K: return "q4_K";
+        case GGML_TYPE_F16: return "f16";
+        case GGML_TYPE_I32: return "i32";
+        case GGML_TYPE_I64: return "i64";
         default: return "?";
     }
 }
@@ -453,6 +470,147 @@ static int run_layer(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend
     return 0;
 }
 
+// a contiguous tensor of up to three dimensions
+static void shape3(ggml_tensor* t, enum ggml_type type, int64_t ne0, int64_t ne1, int64_t ne2, const char* name) {
+    shape(t, type, ne0, ne1, name);
+    t->ne[2] = ne2;
+    t->nb[3] = t->nb[2] * (size_t)ne2;
+}
+// a strided view of `base` starting `offs` bytes in
+static void view3(ggml_tensor* t, ggml_tensor* base, int64_t ne0, int64_t ne1, int64_t ne2, size_t nb1, size_t nb2, size_t offs,
+                  enum ggml_op op, const char* name) {
+    shape3(t, base->type, ne0, ne1, ne2, name);
+    t->nb[1] = nb1;
+    t->nb[2] = nb2;
+    t->nb[3] = nb2 * (size_t)ne2;
+    t->view_src = base;
+    t->view_offs = offs;
+    t->buffer = base->buffer;
+    t->data = (char*)base->data + offs;
+    t->op = op;
+    t->src[0] = base;
+}
+
+// The ops around the mul_mats of a decoder layer, as llama.cpp strings them: token embedding (GET_ROWS), ROPE on the new
+// queries and keys, the KV-cache write (SET_ROWS into f16 caches), attention of the new tokens over the cache
+// (FLASH_ATTN_EXT on strided views of the caches) and a masked SOFT_MAX; then the same graph with a cache slot out of
+// range, which must fail.
+static int run_attn(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) {
+    CHECK(argc == 11);
+    const int64_t D = atoll(argv[2]), n_head = atoll(argv[3]), n_head_kv = atoll(argv[4]), n_ctx = atoll(argv[5]),
+                  n_kv = atoll(argv[6]), n_tok = atoll(argv[7]), n_vocab = atoll(argv[8]), n_embd = atoll(argv[9]);
+    const std::string dir = argv[10];
+    auto in = [&](const char* n) { return slurp(dir + "/" + n); };
+    ggml_backend_t backend = ggml_backend_ameva_init(0);
+    CHECK(backend);
+    const int64_t kvw = D * n_head_kv;   // floats of one cache row
+    ggml_tensor emb, tok, q, kcur, vcur, kcache, vcache, pos, slots, mask, sc, smask;
+    shape(&emb, GGML_TYPE_F16, n_embd, n_vocab, "token_embd");
+    shape(&tok, GGML_TYPE_I32, n_tok, 1, "tokens");
+    shape3(&q, GGML_TYPE_F32, D, n_head, n_tok, "q");
+    shape3(&kcur, GGML_TYPE_F32, D, n_head_kv, n_tok, "k_cur");
+    shape(&vcur, GGML_TYPE_F32, kvw, n_tok, "v_cur");
+    shape(&kcache, GGML_TYPE_F16, kvw, n_ctx, "cache_k");
+    shape(&vcache, GGML_TYPE_F16, kvw, n_ctx, "cache_v");
+    shape(&pos, GGML_TYPE_I32, n_tok, 1, "pos");
+    shape(&slots, GGML_TYPE_I64, n_tok, 1, "slots");
+    shape(&mask, GGML_TYPE_F16, n_kv, n_tok, "kq_mask");
+    shape3(&sc, GGML_TYPE_F32, n_kv, n_tok, n_head, "scores");
+    shape(&smask, GGML_TYPE_F32, n_kv, n_tok, "scores_mask");
+    ggml_tensor x, q_rope, k_rope, attn, sm;
+    shape(&x, GGML_TYPE_F32, n_embd, n_tok, "inp_embd");
+    shape3(&q_rope, GGML_TYPE_F32, D, n_head, n_tok, "q_rope");
+    shape3(&k_rope, GGML_TYPE_F32, D, n_head_kv, n_tok, "k_rope");
+    shape3(&attn, GGML_TYPE_F32, D, n_head, n_tok, "kqv");
+    shape3(&sm, GGML_TYPE_F32, n_kv, n_tok, n_head, "soft_max");
+    Arena ar{buft};
+    for (ggml_tensor* t : {&emb, &tok, &q, &kcur, &vcur, &kcache, &vcache, &pos, &slots, &mask, &sc, &smask, &x, &q_rope, &k_rope,
+                           &attn, &sm})
+        ar.add(t);
+    CHECK(ar.commit());
+    ggml_backend_buffer_t buf = ar.buf;
+    struct { ggml_tensor* t; const char* file; } uploads[] = {
+        {&emb, "emb.bin"}, {&tok, "tok.bin"}, {&q, "q.bin"}, {&kcur, "kcur.bin"}, {&vcur, "vcur.bin"}, {&kcache, "kcache.bin"},
+        {&vcache, "vcache.bin"}, {&pos, "pos.bin"}, {&slots, "slots.bin"}, {&mask, "mask.bin"}, {&sc, "sc.bin"}, {&smask, "smask.bin"}};
+    for (auto& u : uploads) {
+        std::vector<uint8_t> bytes = in(u.file);
+        CHECK(bytes.size() == ggml_nbytes(u.t));
+        buf->iface.set_tensor(buf, u.t, bytes.data(), 0, bytes.size());
+    }
+    // the graph
+    op2(&x, GGML_OP_GET_ROWS, &emb, &tok);
+    auto rope = [&](ggml_tensor* t, ggml_tensor* a) {
+        op2(t, GGML_OP_ROPE, a, &pos);
+        const float freq_base = 10000.0f, one = 1.0f, zero = 0.0f, bf = 32.0f, bs = 1.0f;
+        t->op_params[1] = (int32_t)D;
+        t->op_params[2] = 2;       // NEOX
+        t->op_params[4] = 4096;
+        memcpy(&t->op_params[5], &freq_base, 4);
+        memcpy(&t->op_params[6], &one, 4);
+        memcpy(&t->op_params[7], &zero, 4);
+        memcpy(&t->op_params[8], &one, 4);
+        memcpy(&t->op_params[9], &bf, 4);
+        memcpy(&t->op_params[10], &bs, 4);
+    };
+    rope(&q_rope, &q);
+    rope(&k_rope, &kcur);
+    ggml_tensor k_rows, kset, vset, q_perm, k_view, v_view;
+    view3(&k_rows, &k_rope, kvw, n_tok, 1, (size_t)kvw * 4, (size_t)kvw * n_tok * 4, 0, GGML_OP_RESHAPE, "k_rope_rows");
+    // SET_ROWS: the node is a view of the cache it writes
+    view3(&kset, &kcache, kvw, n_ctx, 1, kcache.nb[1], kcache.nb[2], 0, GGML_OP_SET_ROWS, "cache_k_set");
+    kset.src[0] = &k_rows;
+    kset.src[1] = &slots;
+    view3(&vset, &vcache, kvw, n_ctx, 1, vcache.nb[1], vcache.nb[2], 0, GGML_OP_SET_ROWS, "cache_v_set");
+    vset.src[0] = &vcur;
+    vset.src[1] = &slots;
+    // attention operands: q [D, n_tok, n_head] (a permutation of q_rope), the first n_kv rows of the caches by KV head
+    view3(&q_perm, &q_rope, D, n_tok, n_head, (size_t)D * n_head * 4, (size_t)D * 4, 0, GGML_OP_PERMUTE, "q_perm");
+    view3(&k_view, &kcache, D, n_kv, n_head_kv, kcache.nb[1], (size_t)D * 2, 0, GGML_OP_VIEW, "k_view");
+    view3(&v_view, &vcache, D, n_kv, n_head_kv, vcache.nb[1], (size_t)D * 2, 0, GGML_OP_VIEW, "v_view");
+    op2(&attn, GGML_OP_FLASH_ATTN_EXT, &q_perm, &k_view);
+    attn.src[2] = &v_view;
+    attn.src[3] = &mask;
+    const float scale = 1.0f / sqrtf((float)D), zero = 0.0f;
+    memcpy(&attn.op_params[0], &scale, 4);
+    memcpy(&attn.op_params[1], &zero, 4);
+    memcpy(&attn.op_params[2], &zero, 4);
+    op2(&sm, GGML_OP_SOFT_MAX, &sc, &smask);
+    memcpy(&sm.op_params[0], &scale, 4);
+    memcpy(&sm.op_params[1], &zero, 4);
+    ggml_tensor* nodes[] = {&x, &q_rope, &k_rope, &k_rows, &kset, &vset, &q_perm, &k_view, &v_view, &attn, &sm};
+    const int n = (int)(sizeof(nodes) / sizeof(nodes[0]));
+    for (ggml_tensor* t : nodes) CHECK(dev->iface.supports_op(dev, t));
+    ggml_cgraph g = {n, nodes};
+    ggml_backend_ameva_reset_counters();
+    CHECK(backend->iface.graph_compute(backend, &g) == GGML_STATUS_SUCCESS);
+    printf("COUNTER gpu_op %lld\n", (long long)ggml_backend_ameva_get_gpu_op_count());
+    auto out = [&](ggml_tensor* t, const char* name) {
+        std::vector<uint8_t> v(ggml_nbytes(t));
+        buf->iface.get_tensor(buf, t, v.data(), 0, v.size());
+        return dump(dir + "/" + name, v.data(), v.size());
+    };
+    CHECK(out(&x, "x.out") && out(&q_rope, "q_rope.out") && out(&k_rope, "k_rope.out") && out(&kcache, "kcache.out") &&
+          out(&vcache, "vcache.out") && out(&attn, "attn.out") && out(&sm, "sm.out"));
+    // a cache slot past the cache: the graph fails and the op counter does not move
+    {
+        std::vector<uint8_t> bytes = in("slots.bin");
+        int64_t bad = n_ctx;
+        memcpy(bytes.data(), &bad, 8);
+        buf->iface.set_tensor(buf, &slots, bytes.data(), 0, bytes.size());
+        const int64_t before = ggml_backend_ameva_get_gpu_op_count();
+        CHECK(backend->iface.graph_compute(backend, &g) == GGML_STATUS_FAILED);
+        CHECK(ggml_backend_ameva_get_gpu_op_count() == before);
+    }
+    // an op outside the set is refused at planning time
+    sm.op_params[1] = 0x41000000;   // max_bias 8.0: ALiBi
+    CHECK(!dev->iface.supports_op(dev, &sm));
+    buf->iface.free_buffer(buf);
+    backend->iface.free(backend);
+    ggml_backend_ameva_teardown();
+    printf("ok\n");
+    return 0;
+}
+
 int main(int argc, char** argv) {
     CHECK(argc >= 2);
     CHECK(ggml_backend_ameva_abi_check() == nullptr);
@@ -495,6 +653,7 @@ int main(int argc, char** argv) {
     }
     if (std::string(argv[1]) == "mulmat") return run_mulmat(argc, argv, dev, buft);
     if (std::string(argv[1]) == "layer") return run_layer(argc, argv, dev, buft);
+    if (std::string(argv[1]) == "attn") return run_attn(argc, argv, dev, buft);
     fprintf(stderr, "driver: unknown mode %s\n", argv[1]);
     return 2;
 }

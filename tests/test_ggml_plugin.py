@@ -102,3 +102,61 @@ def test_decoder_layer_graph_counters_failure_injection_and_teardown(t):
     act = (_silu(got["gate"]) * up[0]).astype(np.float32)
     assert max_normalised_error(got["act"].reshape(1, Nff), act.reshape(1, Nff)) <= 1e-3
     assert max_normalised_error(got["y2"].reshape(M2, Nq), mm("wq", Nq, x2)) <= 1e-3
+
+
+@needs_plugin
+@pytest.mark.gpu
+@pytest.mark.parametrize("D,n_head,n_head_kv,n_kv,n_tok", [(128, 32, 8, 1024, 1), (64, 20, 5, 300, 3)])
+def test_attention_side_of_a_decoder_layer_through_the_plugin(D, n_head, n_head_kv, n_kv, n_tok):
+    """Token embedding (GET_ROWS from an f16 table), ROPE on new queries and keys, the KV-cache write (SET_ROWS into f16
+    caches with i64 slots), attention over strided views of the caches (FLASH_ATTN_EXT) and a masked SOFT_MAX as one graph
+    through the plugin; every result against the numpy restatement of ggml's ops. The driver then repeats the graph with a
+    cache slot out of range (the graph must fail and count nothing) and asks for an op outside the set."""
+    from oracle import layer_ops as ops
+    n_ctx, n_vocab, n_embd = n_kv + 64, 500, 256
+    kvw = D * n_head_kv
+    rng = np.random.default_rng(D + n_tok)
+    emb = rng.standard_normal((n_vocab, n_embd)).astype(np.float16)
+    tok = rng.integers(0, n_vocab, n_tok).astype(np.int32)
+    q = rng.standard_normal((n_tok, n_head, D)).astype(np.float32)
+    kcur = rng.standard_normal((n_tok, n_head_kv, D)).astype(np.float32)
+    vcur = rng.standard_normal((n_tok, kvw)).astype(np.float32)
+    kcache = rng.standard_normal((n_ctx, kvw)).astype(np.float16)
+    vcache = rng.standard_normal((n_ctx, kvw)).astype(np.float16)
+    first = n_kv - n_tok
+    pos = np.arange(first, n_kv, dtype=np.int32)
+    slots = np.arange(first, n_kv, dtype=np.int64)
+    mask = np.zeros((n_tok, n_kv), np.float16)
+    for i in range(n_tok):
+        mask[i, first + i + 1:] = -np.inf
+    sc = (rng.standard_normal((n_head, n_tok, n_kv)) * 3).astype(np.float32)
+    smask = mask.astype(np.float32)
+    with tempfile.TemporaryDirectory() as d:
+        for name, a in (("emb", emb), ("tok", tok), ("q", q), ("kcur", kcur), ("vcur", vcur), ("kcache", kcache),
+                        ("vcache", vcache), ("pos", pos), ("slots", slots), ("mask", mask), ("sc", sc), ("smask", smask)):
+            a.tofile(os.path.join(d, name + ".bin"))
+        r = subprocess.run([DRIVER, "attn", str(D), str(n_head), str(n_head_kv), str(n_ctx), str(n_kv), str(n_tok), str(n_vocab),
+                            str(n_embd), d], capture_output=True, text=True)
+        assert r.returncode == 0, r.stdout + r.stderr
+        assert r.stdout.strip().endswith("ok") and "COUNTER gpu_op 7" in r.stdout
+        assert "row indices out of range" in r.stderr
+        load = lambda n, dt: np.fromfile(os.path.join(d, n + ".out"), dt)
+        x, q_rope, k_rope = load("x", np.float32), load("q_rope", np.float32), load("k_rope", np.float32)
+        kc, vc = load("kcache", np.float16).reshape(n_ctx, kvw), load("vcache", np.float16).reshape(n_ctx, kvw)
+        attn, sm = load("attn", np.float32).reshape(n_tok, n_head, D), load("sm", np.float32).reshape(n_head, n_tok, n_kv)
+    assert np.array_equal(x.reshape(n_tok, n_embd), emb[tok].astype(np.float32))
+    want_q = ops.rope(q[None], pos, D, True, 10000.0)[0]
+    want_k = ops.rope(kcur[None], pos, D, True, 10000.0)[0]
+    assert np.max(np.abs(q_rope.reshape(q.shape) - want_q)) <= 4e-6 * np.max(np.abs(q))
+    assert np.max(np.abs(k_rope.reshape(kcur.shape) - want_k)) <= 4e-6 * np.max(np.abs(kcur))
+    # the caches: the device's own rotated keys, rounded to f16, in the slots; every other row untouched
+    want_kc, want_vc = kcache.copy(), vcache.copy()
+    want_kc[slots] = k_rope.reshape(n_tok, kvw).astype(np.float16)
+    want_vc[slots] = vcur.astype(np.float16)
+    assert np.array_equal(kc, want_kc) and np.array_equal(vc, want_vc)
+    k3 = kc[:n_kv].reshape(n_kv, n_head_kv, D).transpose(1, 0, 2)
+    v3 = vc[:n_kv].reshape(n_kv, n_head_kv, D).transpose(1, 0, 2)
+    want_attn = ops.flash_attn_ext(q_rope.reshape(q.shape).transpose(1, 0, 2), k3, v3, mask, 1.0 / np.sqrt(D))
+    assert np.max(np.abs(attn - want_attn)) <= 2e-3 * max(1.0, float(np.max(np.abs(want_attn))))
+    want_sm = ops.soft_max(sc[None], 1.0 / np.sqrt(np.float32(D)), smask[None, None])[0]
+    assert np.max(np.abs(sm - want_sm)) <= 2e-6
