@@ -8,6 +8,7 @@
 // reference's families (quant_a8, quant_a8b, mmvq, mmvqb, mmq) with this library's own binding / push contracts,
 // documented at each launcher.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -185,16 +186,77 @@ AcResult register_kernel(const char* name, uint32_t binding_count, uint32_t push
 namespace {
 struct Codec {
     uint32_t blk, blk_bytes, q_off, q_bytes, s_off, s_bytes;  // payload / scale field placement inside a ggml block
+    uint32_t xcode;   // 0: the payload bytes are moved; 1 (Q5_0) / 2 (IQ4_NL): the payload is decoded to 32 int8 (see below)
 };
 bool codec_for(uint32_t type, Codec* c) {
     switch (type) {
-        case 2: *c = {32, 18, 2, 16, 0, 2}; return true;      // Q4_0: d@0, qs[16]@2
-        case 8: *c = {32, 34, 2, 32, 0, 2}; return true;      // Q8_0: d@0, qs[32]@2
-        case 12: *c = {256, 144, 16, 128, 0, 16}; return true;  // Q4_K: d, dmin, scales[12] @0, qs[128]@16
+        case 2: *c = {32, 18, 2, 16, 0, 2, 0}; return true;      // Q4_0: d@0, qs[16]@2
+        case 8: *c = {32, 34, 2, 32, 0, 2, 0}; return true;      // Q8_0: d@0, qs[32]@2
+        case 12: *c = {256, 144, 16, 128, 0, 16, 0}; return true;  // Q4_K: d, dmin, scales[12] @0, qs[128]@16
+        case 6: *c = {32, 22, 2, 32, 0, 2, 1}; return true;      // Q5_0: d@0, qh[4]@2, qs[16]@6 -> Q8_0 regions
+        case 20: *c = {32, 18, 2, 32, 0, 2, 2}; return true;     // IQ4_NL: d@0, qs[16]@2 -> Q8_0 regions
         default: return false;
     }
 }
+
+// Weight types kept on the device as another type's regions. A Q5_0 weight is d * (q5 - 16) and an IQ4_NL weight is
+// d * kvalues[q4] with integer table values: both are d * (an int8), which is exactly a Q8_0 block with the same fp16 d.
+// Their products with Q8_0 activations, sum(q_w * q_a) * (d_w * d_a) per block, are then the Q8_0 kernels' arithmetic
+// on the same integers (ggml_vec_dot_q5_0_q8_0 and ggml_vec_dot_iq4_nl_q8_0 form the same sums), at 34 instead of 22 /
+// 18 bytes per block on the device. The decode is inverted exactly when the tensor is read back.
+const int8_t kIq4nlValues[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // 32 int8 of one ggml block
+    if (xcode == 1) {
+        uint32_t qh;
+        memcpy(&qh, blk + 2, 4);
+        const uint8_t* qs = blk + 6;
+        for (int j = 0; j < 16; ++j) {
+            out[j] = (int8_t)(((qs[j] & 0x0F) | (((qh >> j) & 1u) << 4)) - 16);
+            out[j + 16] = (int8_t)(((qs[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4)) - 16);
+        }
+    } else {
+        const uint8_t* qs = blk + 2;
+        for (int j = 0; j < 16; ++j) {
+            out[j] = kIq4nlValues[qs[j] & 0x0F];
+            out[j + 16] = kIq4nlValues[qs[j] >> 4];
+        }
+    }
+}
+void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inverse (values no block decodes to, as in
+    if (xcode == 1) {                                                   // regions never written: the nearest code)
+        uint32_t qh = 0;
+        uint8_t* qs = blk + 6;
+        for (int j = 0; j < 16; ++j) {
+            int a = in[j] + 16, b = in[j + 16] + 16;
+            a = a < 0 ? 0 : (a > 31 ? 31 : a);
+            b = b < 0 ? 0 : (b > 31 ? 31 : b);
+            qs[j] = (uint8_t)((a & 0x0F) | ((b & 0x0F) << 4));
+            qh |= (uint32_t)(a >> 4) << j;
+            qh |= (uint32_t)(b >> 4) << (j + 16);
+        }
+        memcpy(blk + 2, &qh, 4);
+        return;
+    }
+    uint8_t* qs = blk + 2;
+    auto nearest = [](int v) {
+        int best = 0;
+        for (int t = 1; t < 16; ++t)
+            if (abs(kIq4nlValues[t] - v) < abs(kIq4nlValues[best] - v)) best = t;
+        return best;
+    };
+    for (int j = 0; j < 16; ++j) qs[j] = (uint8_t)(nearest(in[j]) | (nearest(in[j + 16]) << 4));
+}
 }  // namespace
+
+// The type whose kernels and device regions serve a weight type (itself, or Q8_0 for the decoded types); 0 = not built.
+extern "C" uint32_t ac_b200_device_type(uint32_t ggml_type) {
+    switch (ggml_type) {
+        case 2: case 8: case 12: case 36: return ggml_type;
+        case 6: case 20: return 8;
+        default: return 0;
+    }
+}
 
 static uint64_t align64(uint64_t v) { return (v + 63u) & ~(uint64_t)63u; }
 
@@ -210,6 +272,7 @@ static bool mmvm_fits(uint64_t M, uint64_t K) {   // shared memory of ameva_mmvm
 
 extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, uint64_t K, uint32_t flags,
                                          uint32_t* out_path) {
+    if (type == 6 || type == 20) type = 8;   // kept on the device as Q8_0 regions (ac_b200_device_type)
     if (!out_path) return AC_ERR_NULL_POINTER;
     *out_path = AC_B200_PATH_NONE;
     if (flags & ~(AC_B200_PLAN_EXACT | AC_B200_PLAN_HOST_LAUNCH | AC_B200_PLAN_PEERS | AC_B200_PLAN_WEIGHT_RANGE))
@@ -317,8 +380,10 @@ extern "C" AcResult ac_b200_weight_exponent(uint32_t type, const void* ggml_bloc
         float bound;
         if (type == 2) {
             bound = 8.0f * d;
-        } else if (type == 8) {
+        } else if (type == 8 || type == 20) {
             bound = 127.0f * d;
+        } else if (type == 6) {
+            bound = 16.0f * d;
         } else {
             float m = half_to_float(h1);
             bound = 945.0f * d + 63.0f * (m < 0 ? -m : m);
@@ -368,7 +433,8 @@ extern "C" AcResult ac_b200_repack_to_device(uint32_t type, const void* src, uin
     uint8_t* q = (uint8_t*)dst;
     uint8_t* sc = q + align64(nblk * c.q_bytes);
     for (uint64_t i = 0; i < nblk; ++i) {
-        memcpy(q + i * c.q_bytes, s + i * c.blk_bytes + c.q_off, c.q_bytes);
+        if (c.xcode) decode_block(c.xcode, s + i * c.blk_bytes, (int8_t*)(q + i * c.q_bytes));
+        else memcpy(q + i * c.q_bytes, s + i * c.blk_bytes + c.q_off, c.q_bytes);
         memcpy(sc + i * c.s_bytes, s + i * c.blk_bytes + c.s_off, c.s_bytes);
     }
     return AC_SUCCESS;
@@ -389,7 +455,11 @@ extern "C" AcResult ac_b200_repack_from_device(uint32_t type, const void* src, u
     const uint8_t* sc = q + align64(nblk * c.q_bytes);
     uint8_t* d = (uint8_t*)dst;
     for (uint64_t i = 0; i < nblk; ++i) {
-        memcpy(d + i * c.blk_bytes + c.q_off, q + i * c.q_bytes, c.q_bytes);
+        if (c.xcode) {
+            encode_block(c.xcode, (const int8_t*)(q + i * c.q_bytes), d + i * c.blk_bytes);
+        } else {
+            memcpy(d + i * c.blk_bytes + c.q_off, q + i * c.q_bytes, c.q_bytes);
+        }
         memcpy(d + i * c.blk_bytes + c.s_off, sc + i * c.s_bytes, c.s_bytes);
     }
     return AC_SUCCESS;

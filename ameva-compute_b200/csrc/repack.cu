@@ -4,8 +4,9 @@
 // The reference repacks on the CPU while uploading (adapters/llama/ggml-ameva/ggml-ameva-buffer.cpp:300-330 stages
 // chunks, ggml-ameva-repack.cpp:82-247 permutes). Here the CPU only copies the caller's ggml bytes into one of two
 // pinned chunks; the chunk travels host -> device asynchronously and a kernel does the permutation at memory speed while
-// the CPU fills the other chunk. The permutation is a pure byte move, so reading the regions back through
-// ac_b200_repack_from_device returns the uploaded bytes exactly.
+// the CPU fills the other chunk. The permutation is a pure byte move (Q5_0 and IQ4_NL: an exactly invertible decode of
+// the payload to int8, which makes them Q8_0 blocks), so reading the regions back through ac_b200_repack_from_device
+// returns the uploaded bytes exactly.
 #include <cstring>
 
 #include "common.cuh"
@@ -14,7 +15,35 @@ namespace amv {
 
 struct RepackCodec {
     uint32_t blk_bytes, q_off, q_bytes, s_off, s_bytes;   // placement of the payload / scale fields inside a ggml block
+    uint32_t xcode;   // 1 (Q5_0) / 2 (IQ4_NL): the payload is decoded to 32 int8, the block becomes a Q8_0 block
 };
+
+// IQ4_NL's sixteen values (ggml's kvalues_iq4nl)
+__constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
+
+// sixteen decoded weights of a Q5_0 / IQ4_NL block: `part` 0 = elements 0..15 (low nibbles), 1 = elements 16..31
+__device__ __forceinline__ uint4 decode_piece(uint32_t xcode, const uint8_t* blk, uint32_t part) {
+    uint32_t w[4] = {0u, 0u, 0u, 0u};
+    if (xcode == 1u) {
+        const uint16_t* h = reinterpret_cast<const uint16_t*>(blk + 2);
+        const uint32_t qh = (h[0] | ((uint32_t)h[1] << 16)) >> (16u * part);
+        const uint8_t* qs = blk + 6;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t nib = part ? (qs[j] >> 4) : (qs[j] & 0x0Fu);
+            const int v = (int)(nib | (((qh >> j) & 1u) << 4)) - 16;
+            w[j >> 2] |= (uint32_t)(v & 0xFF) << (8 * (j & 3));
+        }
+    } else {
+        const uint8_t* qs = blk + 2;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int v = c_iq4nl[part ? (qs[j] >> 4) : (qs[j] & 0x0Fu)];
+            w[j >> 2] |= (uint32_t)(v & 0xFF) << (8 * (j & 3));
+        }
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
 
 constexpr uint32_t kRepackTile = 256;   // blocks per CTA: 256 x 18, 34 or 144 bytes are whole 16-byte pieces
 
@@ -40,12 +69,16 @@ __global__ void __launch_bounds__(256) repack_kernel(const uint8_t* __restrict__
     uint8_t* q = dst_q + b0 * c.q_bytes;
     for (uint32_t p = threadIdx.x; p < q_pieces; p += 256u) {
         const uint32_t blk = p / per_blk, part = p - blk * per_blk;
-        const uint16_t* h = reinterpret_cast<const uint16_t*>(tile + blk * c.blk_bytes + c.q_off + part * 16u);
         uint4 v;
-        v.x = h[0] | ((uint32_t)h[1] << 16);
-        v.y = h[2] | ((uint32_t)h[3] << 16);
-        v.z = h[4] | ((uint32_t)h[5] << 16);
-        v.w = h[6] | ((uint32_t)h[7] << 16);
+        if (c.xcode) {
+            v = decode_piece(c.xcode, tile + blk * c.blk_bytes, part);
+        } else {
+            const uint16_t* h = reinterpret_cast<const uint16_t*>(tile + blk * c.blk_bytes + c.q_off + part * 16u);
+            v.x = h[0] | ((uint32_t)h[1] << 16);
+            v.y = h[2] | ((uint32_t)h[3] << 16);
+            v.z = h[4] | ((uint32_t)h[5] << 16);
+            v.w = h[6] | ((uint32_t)h[7] << 16);
+        }
         *reinterpret_cast<uint4*>(q + (size_t)p * 16u) = v;
     }
     const uint32_t s_halves = nb * (c.s_bytes / 2u), per_blk_s = c.s_bytes / 2u;
@@ -58,9 +91,11 @@ __global__ void __launch_bounds__(256) repack_kernel(const uint8_t* __restrict__
 
 static bool repack_codec(uint32_t type, RepackCodec* c, uint32_t* blk) {
     switch (type) {
-        case 2: *c = {18, 2, 16, 0, 2}; *blk = 32; return true;        // Q4_0: d@0, qs[16]@2
-        case 8: *c = {34, 2, 32, 0, 2}; *blk = 32; return true;        // Q8_0: d@0, qs[32]@2
-        case 12: *c = {144, 16, 128, 0, 16}; *blk = 256; return true;  // Q4_K: d, dmin, scales[12] @0, qs[128]@16
+        case 2: *c = {18, 2, 16, 0, 2, 0}; *blk = 32; return true;        // Q4_0: d@0, qs[16]@2
+        case 8: *c = {34, 2, 32, 0, 2, 0}; *blk = 32; return true;        // Q8_0: d@0, qs[32]@2
+        case 12: *c = {144, 16, 128, 0, 16, 0}; *blk = 256; return true;  // Q4_K: d, dmin, scales[12] @0, qs[128]@16
+        case 6: *c = {22, 2, 32, 0, 2, 1}; *blk = 32; return true;        // Q5_0: d@0, qh[4]@2, qs[16]@6, decoded
+        case 20: *c = {18, 2, 32, 0, 2, 2}; *blk = 32; return true;       // IQ4_NL: d@0, qs[16]@2, decoded
         default: return false;
     }
 }

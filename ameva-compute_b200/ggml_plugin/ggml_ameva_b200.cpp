@@ -90,9 +90,18 @@ AcContext* context() {          // created on first use (the loader probes the r
     return p.ctx;
 }
 
-bool repacked_type(enum ggml_type t) { return t == GGML_TYPE_Q4_0 || t == GGML_TYPE_Q8_0 || t == GGML_TYPE_Q4_K; }
+// Q5_0 and IQ4_NL weights are d * int8: they live on the device as Q8_0 regions and run on the Q8_0 kernels
+// (ac_b200_device_type); what is uploaded and read back keeps the tensor's own type.
+enum ggml_type dev_type(enum ggml_type t) { return (t == GGML_TYPE_Q5_0 || t == GGML_TYPE_IQ4_NL) ? GGML_TYPE_Q8_0 : t; }
+bool repacked_type(enum ggml_type t) {
+    t = dev_type(t);
+    return t == GGML_TYPE_Q4_0 || t == GGML_TYPE_Q8_0 || t == GGML_TYPE_Q4_K;
+}
 uint32_t block_elems(enum ggml_type t) { return t == GGML_TYPE_Q4_K ? 256u : 32u; }
-uint32_t payload_bytes(enum ggml_type t) { return t == GGML_TYPE_Q4_0 ? 16u : (t == GGML_TYPE_Q8_0 ? 32u : 128u); }
+uint32_t payload_bytes(enum ggml_type t) {   // of the device regions
+    t = dev_type(t);
+    return t == GGML_TYPE_Q4_0 ? 16u : (t == GGML_TYPE_Q8_0 ? 32u : 128u);
+}
 uint32_t scale_bytes(enum ggml_type t) { return t == GGML_TYPE_Q4_K ? 16u : 2u; }
 
 // A weight this backend keeps in its device layout: a supported quantized type, plain 2-D, contiguous, not a view.
@@ -404,7 +413,7 @@ const char* mul_mat_reason(const ggml_tensor* node, WeightRef* out = nullptr, ui
         out->s_range = N * nblk_row * scale_bytes(w->type);
         out->N = (uint32_t)N;
         out->K = (uint32_t)K;
-        out->type = w->type;
+        out->type = dev_type(w->type);
     }
     if (out_path) *out_path = path;
     return nullptr;

@@ -18,6 +18,9 @@ import numpy as np
 from . import runtime as rt
 
 GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_I2_S = 2, 8, 12, 36
+# kept on the device as Q8_0 regions: d * (q5 - 16) and d * kvalues_iq4nl[q4] are d * int8 (registry.cu, decode_block)
+GGML_TYPE_Q5_0, GGML_TYPE_IQ4_NL = 6, 20
+DEVICE_TYPE = {GGML_TYPE_Q5_0: GGML_TYPE_Q8_0, GGML_TYPE_IQ4_NL: GGML_TYPE_Q8_0}
 TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s"}
 BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128}
 Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128}   # payload bytes per block
@@ -69,6 +72,7 @@ class MulMatUnsupported(Exception):
 
 def unsupported_reason(ggml_type: int, M: int, N: int, K: int) -> Optional[str]:
     """Shape contract (mul_mat_qmm_reason, ggml-ameva.cpp:1326-1377, narrowed to the four types built here)."""
+    ggml_type = DEVICE_TYPE.get(ggml_type, ggml_type)
     if ggml_type not in TYPE_NAMES:
         return f"weight type {ggml_type} not built"
     if M <= 0 or N <= 0 or K <= 0:
@@ -96,6 +100,8 @@ class QuantWeight:
 
     def __init__(self, ctx: rt.Context, ggml_type: int, N: int, K: int, buf: rt.Buffer, s_off: int,
                  scale: float = 1.0, w_exp: int = 0) -> None:
+        self.ggml_type = ggml_type                          # what was uploaded and what to_ggml returns
+        ggml_type = DEVICE_TYPE.get(ggml_type, ggml_type)   # the type whose regions and kernels serve it
         self.ctx, self.type, self.N, self.K, self.buf, self.s_off, self.scale = ctx, ggml_type, N, K, buf, s_off, scale
         self.w_exp = w_exp   # see weight_exponent
         self.fp16_ok = not rt.weight_range_extreme(w_exp)
@@ -135,7 +141,7 @@ class QuantWeight:
         s = self.buf.read(np.uint8, rows * nblk_row * sb, self.s_off + row0 * nblk_row * sb)
         pad = (-q.size) % 64   # the codec expects the payload region padded to 64 bytes before the scales
         dev = np.concatenate([q, np.zeros(pad, np.uint8), s])
-        return rt.repack_from_device(self.type, dev, rows, self.K)
+        return rt.repack_from_device(self.ggml_type, dev, rows, self.K)
 
     def view(self, row0: int, rows: int) -> WeightView:
         if row0 < 0 or rows <= 0 or row0 + rows > self.N:

@@ -132,7 +132,7 @@ EXPORTED_SYMBOLS = [
     "ac_runtime_get_generation_ctx", "ac_runtime_reset_error_state_ctx", "ac_runtime_kernel_create_builtin",
     "ac_b200_kernel_count", "ac_b200_kernel_name", "ac_b200_kernel_register", "ac_b200_weight_upload", "ac_b200_context_get_stream", "ac_b200_buffer_import",
     "ac_b200_buffer_export_ipc", "ac_b200_buffer_open_ipc", "ac_b200_buffer_write_async", "ac_b200_buffer_read_async", "ac_b200_context_synchronize", "ac_b200_batch_instantiate", "ac_b200_batch_replay",
-    "ac_b200_device_layout", "ac_b200_repack_to_device", "ac_b200_repack_from_device", "ac_b200_mul_mat_plan",
+    "ac_b200_device_layout", "ac_b200_device_type", "ac_b200_repack_to_device", "ac_b200_repack_from_device", "ac_b200_mul_mat_plan",
     "ac_b200_weight_exponent",
     "ac_b200_mul_mat_q4_0_static",
 ]
@@ -218,6 +218,7 @@ def load_library() -> C.CDLL:
         "ac_b200_batch_instantiate": (C.c_int, [vp]),
         "ac_b200_batch_replay": (C.c_int, [vp, C.POINTER(vp)]),
         "ac_b200_device_layout": (C.c_int, [u32, u64, u64, P(u64), P(u64)]),
+        "ac_b200_device_type": (u32, [u32]),
         "ac_b200_mul_mat_q4_0_static": (C.c_int, [vp, vp, vp, vp, u32, vp, u32, u32, u32, u32, u32]),
         "ac_b200_mul_mat_plan": (C.c_int, [u32, u64, u64, u64, u32, P(u32)]),
         "ac_b200_weight_exponent": (C.c_int, [u32, vp, u64, u64, P(C.c_int32)]),
@@ -543,7 +544,7 @@ def init(*, backend: int = AC_BACKEND_CUDA) -> Context:
     return Context(out.value)
 
 
-_GGML_BLOCK = {2: (32, 18), 8: (32, 34), 12: (256, 144), 36: (4, 1)}  # type id -> (elements, bytes) per block
+_GGML_BLOCK = {2: (32, 18), 6: (32, 22), 8: (32, 34), 12: (256, 144), 20: (32, 18), 36: (4, 1)}  # type id -> (elements, bytes) per block
 
 
 def ggml_nbytes(ggml_type: int, rows: int, k: int) -> int:

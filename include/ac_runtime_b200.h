@@ -387,6 +387,12 @@ AcResult ac_b200_batch_replay(AcCommandBatch* batch, AcEvent** out_completion_ev
 AcResult ac_b200_device_layout(uint32_t ggml_type, uint64_t rows, uint64_t k, uint64_t* out_total_bytes,
                                uint64_t* out_scale_offset);
 AcResult ac_b200_repack_to_device(uint32_t ggml_type, const void* ggml_blocks, uint64_t rows, uint64_t k, void* dst);
+/* Q5_0 (6) and IQ4_NL (20) are accepted by the layout, repack, upload, exponent and plan functions as well: their weights
+ * are d * (an int8), so they are kept as Q8_0 regions (the payload decoded exactly at upload, re-encoded exactly at
+ * read-back) and served by the Q8_0 kernels: ac_b200_device_type answers which type's kernels and regions serve a
+ * weight type (the type itself, 8 for these two, 0 when the type is not built). The reference's repacked family lists
+ * both (adapters/llama/ggml-ameva/ggml-ameva-repack.cpp:21-28). */
+uint32_t ac_b200_device_type(uint32_t ggml_type);
 AcResult ac_b200_repack_from_device(uint32_t ggml_type, const void* device_layout, uint64_t rows, uint64_t k,
                                     void* ggml_blocks);
 

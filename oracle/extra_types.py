@@ -1,0 +1,78 @@
+"""Q5_0 and IQ4_NL weights for the parity tests (numpy): packers, the decode to integers, and the rewrite as Q8_0 blocks.
+
+TEST INFRASTRUCTURE ONLY. Both types are d * (an int8 per weight) with one fp16 d per 32 weights (ggml-common.h block_q5_0:
+d, qh[4], qs[16]; block_iq4_nl: d, qs[16] with kvalues_iq4nl), and their dot products with Q8_0 activations form
+sum(q_w * q_a) * (d_w * d_a) per block (ggml_vec_dot_q5_0_q8_0 / ggml_vec_dot_iq4_nl_q8_0, generic branches), which is the
+Q8_0 x Q8_0 arithmetic on the same integers: the oracle's mul_mat for them is mul_mat_q8_0_q8_0 over `to_q8_0`. The decode
+is pinned against gguf-py's dequantizers in tests/test_oracle_golden.py. The Q5_0 packer follows ggml's
+quantize_row_q5_0_ref; for IQ4_NL any valid packer serves (weights are inputs of the path): nearest table value under
+d = amax / 127.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+Q5_0, IQ4_NL = 6, 20
+BLOCK_BYTES = {Q5_0: 22, IQ4_NL: 18}
+KVALUES_IQ4NL = np.array([-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113], np.int8)
+
+
+def quantize_q5_0(w) -> np.ndarray:
+    x = np.ascontiguousarray(w, np.float32).reshape(-1, 32)
+    idx = np.argmax(np.abs(x), axis=1)
+    mx = x[np.arange(x.shape[0]), idx]
+    d = (mx / np.float32(-16.0)).astype(np.float32)
+    inv = np.where(d != 0, np.float32(1.0) / np.where(d != 0, d, np.float32(1.0)), np.float32(0.0)).astype(np.float32)
+    q = np.minimum(31, ((x * inv[:, None]).astype(np.float32) + np.float32(16.5)).astype(np.int8).astype(np.int32)) & 0x1F
+    out = np.zeros((x.shape[0], 22), np.uint8)
+    out[:, 0:2] = d.astype(np.float16).view(np.uint8).reshape(-1, 2)
+    lo, hi = q[:, :16], q[:, 16:]
+    out[:, 6:22] = ((lo & 0x0F) | ((hi & 0x0F) << 4)).astype(np.uint8)
+    qh = np.zeros(x.shape[0], np.uint32)
+    for j in range(16):
+        qh |= ((lo[:, j] >> 4).astype(np.uint32) << np.uint32(j)) | ((hi[:, j] >> 4).astype(np.uint32) << np.uint32(j + 16))
+    out[:, 2:6] = qh.view(np.uint8).reshape(-1, 4)
+    return out.reshape(-1)
+
+
+def quantize_iq4_nl(w) -> np.ndarray:
+    x = np.ascontiguousarray(w, np.float32).reshape(-1, 32)
+    d = (np.max(np.abs(x), axis=1) / np.float32(127.0)).astype(np.float16)
+    df = d.astype(np.float32)
+    t = x / np.where(df != 0, df, np.float32(1.0))[:, None]
+    q = np.argmin(np.abs(t[:, :, None] - KVALUES_IQ4NL.astype(np.float32)[None, None, :]), axis=2).astype(np.uint8)
+    out = np.zeros((x.shape[0], 18), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:18] = q[:, :16] | (q[:, 16:] << 4)
+    return out.reshape(-1)
+
+
+def decode(ggml_type: int, blocks):
+    """(d fp16 [n], q int8 [n][32]) of n blocks."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, BLOCK_BYTES[ggml_type])
+    d = b[:, 0:2].copy().view(np.float16).reshape(-1)
+    if ggml_type == Q5_0:
+        qh = b[:, 2:6].copy().view(np.uint32).reshape(-1)
+        qs = b[:, 6:22].astype(np.int32)
+        j = np.arange(16, dtype=np.uint32)
+        lo = (qs & 0x0F) | ((((qh[:, None] >> j[None, :]) & 1).astype(np.int32)) << 4)
+        hi = (qs >> 4) | ((((qh[:, None] >> (j[None, :] + np.uint32(16))) & 1).astype(np.int32)) << 4)
+        q = np.concatenate([lo, hi], axis=1) - 16
+    else:
+        qs = b[:, 2:18]
+        q = np.concatenate([KVALUES_IQ4NL[qs & 0x0F], KVALUES_IQ4NL[qs >> 4]], axis=1)
+    return d, q.astype(np.int8)
+
+
+def to_q8_0(ggml_type: int, blocks) -> np.ndarray:
+    """The same weights as Q8_0 blocks (fp16 d, 32 int8): what the device keeps."""
+    d, q = decode(ggml_type, blocks)
+    out = np.zeros((d.size, 34), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:34] = q.view(np.uint8)
+    return out.reshape(-1)
+
+
+def dequantize(ggml_type: int, blocks) -> np.ndarray:
+    d, q = decode(ggml_type, blocks)
+    return (d.astype(np.float32)[:, None] * q.astype(np.float32)).reshape(-1)

@@ -3,9 +3,11 @@ configurations, quantized on the CPU by the oracle (weights are inputs of the pa
 import numpy as np
 
 import oracle
+from oracle import extra_types
 
 Q4_0, Q8_0, Q4_K, I2_S = 2, 8, 12, 36
-WEIGHT_STD = {Q4_0: 0.02, Q8_0: 0.02, Q4_K: 0.02, I2_S: 1.0}
+Q5_0, IQ4_NL = 6, 20   # kept on the device as Q8_0 regions (oracle/extra_types.py)
+WEIGHT_STD = {Q4_0: 0.02, Q8_0: 0.02, Q4_K: 0.02, I2_S: 1.0, Q5_0: 0.02, IQ4_NL: 0.02}
 
 
 def make_weights(ggml_type, N, K, seed=0, std=None):
@@ -17,6 +19,10 @@ def make_weights(ggml_type, N, K, seed=0, std=None):
         return oracle.quantize_q8_0(w, oracle.ROUND_TIES_AWAY), 1.0
     if ggml_type == Q4_K:
         return oracle.quantize_q4_K(w), 1.0
+    if ggml_type == Q5_0:
+        return extra_types.quantize_q5_0(w), 1.0
+    if ggml_type == IQ4_NL:
+        return extra_types.quantize_iq4_nl(w), 1.0
     return oracle.quantize_i2_s(w)
 
 
@@ -27,6 +33,8 @@ def make_acts(M, K, seed=1):
 def oracle_mul_mat(ggml_type, blocks, scale, x, N, K, round_mode=0, q8k_mode=0, want_sums=True):
     """Returns (dst fp32 [M][N], exact integer sums, quantized activations as the oracle made them)."""
     M = x.shape[0]
+    if ggml_type in (Q5_0, IQ4_NL):   # the same integers and scales as Q8_0 blocks: the Q8_0 x Q8_0 arithmetic
+        blocks, ggml_type = extra_types.to_q8_0(ggml_type, blocks), Q8_0
     if ggml_type in (Q4_0, Q8_0):
         aq = oracle.quantize_q8_0(x, round_mode)
         fn = oracle.mul_mat_q4_0_q8_0 if ggml_type == Q4_0 else oracle.mul_mat_q8_0_q8_0

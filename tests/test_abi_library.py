@@ -214,6 +214,27 @@ def test_kernel_choice_policy():
     assert rt.weight_range_extreme(8) and rt.weight_range_extreme(-14) and not rt.weight_range_extreme(4)
 
 
+def test_q5_0_and_iq4_nl_become_q8_0_regions():
+    """The two types kept as another type's regions: the CPU codec writes exactly the Q8_0 image of the same weights and
+    reads the uploaded bytes back; the plan and the layout answer as for Q8_0."""
+    from oracle import extra_types as et
+    lib = rt.load_library()
+    lib.ac_b200_device_type.restype = C.c_uint32
+    assert [lib.ac_b200_device_type(t) for t in (2, 8, 12, 36, 6, 20, 14)] == [2, 8, 12, 36, 8, 8, 0]
+    rng = np.random.default_rng(4)
+    w = (rng.standard_normal((5, 512)) * 0.02).astype(np.float32)
+    for t, pack in ((et.Q5_0, et.quantize_q5_0), (et.IQ4_NL, et.quantize_iq4_nl)):
+        blocks = pack(w)
+        assert rt.device_layout(t, 5, 512) == rt.device_layout(8, 5, 512)
+        dev = rt.repack_to_device(t, blocks, 5, 512)
+        assert np.array_equal(dev, rt.repack_to_device(8, et.to_q8_0(t, blocks), 5, 512))
+        assert np.array_equal(rt.repack_from_device(t, dev, 5, 512), blocks)
+        assert rt.mul_mat_plan(t, 1, 4096, 4096, 0) == rt.mul_mat_plan(8, 1, 4096, 4096, 0)
+        assert rt.mul_mat_plan(t, 512, 11008, 4096, 0) == rt.PATH_GEMM_TC
+        assert pkg.qmm.unsupported_reason(t, 1, 64, 512) is None and "block" in pkg.qmm.unsupported_reason(t, 1, 64, 48)
+        assert rt.weight_exponent(t, blocks, 5, 512) == rt.weight_exponent(8, et.to_q8_0(t, blocks), 5, 512) + (3 if t == et.Q5_0 else 0)   # |w| <= 16 |d| against 127 |d|
+
+
 @pytest.mark.parametrize("ggml_type,quant", [(2, oracle.quantize_q4_0), (8, oracle.quantize_q8_0),
                                              (12, oracle.quantize_q4_K)])
 def test_weight_codec_round_trip(ggml_type, quant):

@@ -66,6 +66,19 @@ LLAMA_KV = [("general.architecture", STR, "llama"), ("llama.context_length", U32
             ("llama.rope.dimension_count", U32, 64), ("general.name", STR, "tiny")]
 
 
+def test_the_library_exports_what_the_header_declares():
+    import ctypes
+    import re
+    from conftest import ROOT
+    header = open(os.path.join(ROOT, "include", "amuda_gguf_b200.h")).read()
+    declared = set(re.findall(r"\b(ac_(?:gguf|b200_gguf)_[a-z0-9_]+)\s*\(", header))
+    assert declared == {"ac_gguf_open", "ac_gguf_get_tensor", "ac_gguf_get_tensor_scale", "ac_gguf_close",
+                        "ac_b200_gguf_tensor_size", "ac_b200_gguf_device_size", "ac_b200_gguf_upload_tensor"}
+    lib = ctypes.CDLL(rt.LIB_PATH)
+    for name in declared:
+        assert hasattr(lib, name), name
+
+
 def test_tensor_sizes_follow_the_block_table_and_the_i2s_trailer():
     table = {0: (1, 4), 1: (1, 2), 2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 9: (32, 40),
              10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210), 15: (256, 292)}

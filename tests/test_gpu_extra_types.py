@@ -1,0 +1,66 @@
+"""Q5_0 and IQ4_NL weights: uploaded as they are, kept on the device as Q8_0 regions (both are d * int8 per weight), read
+back byte-exact, multiplied by the Q8_0 kernels. Reference: the repacked family of the reference's plugin
+(adapters/llama/ggml-ameva/ggml-ameva-repack.cpp:21-28 lists q5_0 and iq4_nl); arithmetic of ggml_vec_dot_q5_0_q8_0 /
+ggml_vec_dot_iq4_nl_q8_0 (sum(q_w q_a) * (d_w d_a) per block), restated in oracle/extra_types.py."""
+import numpy as np
+import pytest
+
+from conftest import load_pkg
+from helpers import IQ4_NL, Q5_0, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+from oracle import extra_types
+
+pytestmark = pytest.mark.gpu
+pkg = load_pkg()
+rt, qmm = pkg.runtime, pkg.qmm
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = rt.init()
+    yield c
+    c.destroy()
+
+
+@pytest.mark.parametrize("t", [Q5_0, IQ4_NL])
+@pytest.mark.parametrize("N,K", [(96, 1024), (1000, 4096), (3, 32)])
+def test_upload_keeps_q8_0_regions_and_reads_back_the_uploaded_bytes(ctx, t, N, K):
+    blocks, _ = make_weights(t, N, K, N)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K)
+    assert w.type == Q8_0 and w.ggml_type == t
+    assert np.array_equal(w.to_ggml(), blocks)
+    if N > 2:
+        per_row = blocks.size // N
+        assert np.array_equal(w.to_ggml(1, N - 2), blocks[per_row:(N - 1) * per_row])
+    # the device holds exactly the Q8_0 image of the same weights
+    want = rt.repack_to_device(Q8_0, extra_types.to_q8_0(t, blocks), N, K)
+    host = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, host_repack=True)
+    nq, ns = N * (K // 32) * 32, N * (K // 32) * 2      # payload and scale regions (the padding between them is not data)
+    try:
+        for wt in (w, host):
+            got = wt.buf.read(np.uint8, want.size)
+            assert np.array_equal(got[:nq], want[:nq]) and np.array_equal(got[w.s_off:w.s_off + ns], want[w.s_off:w.s_off + ns])
+    finally:
+        w.destroy()
+        host.destroy()
+
+
+@pytest.mark.parametrize("t", [Q5_0, IQ4_NL])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (4, 512, 1024), (33, 768, 2048), (300, 1024, 4096)])
+def test_mul_mat_on_the_q8_0_kernels(ctx, t, M, N, K):
+    blocks, scale = make_weights(t, N, K, M)
+    x = make_acts(M, K, M + 1)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    mm.run(xb, dst, M)
+    got = dst.read(np.float32).reshape(M, N)
+    want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+    assert max_normalised_error(got, want) <= 1e-3
+    # and bit-equal to the same product over the weights uploaded as Q8_0
+    w8 = qmm.QuantWeight.from_ggml(ctx, Q8_0, extra_types.to_q8_0(t, blocks), N, K)
+    mm8 = qmm.MulMat(ctx, w8, M)
+    dst8 = ctx.buffer(M * N * 4)
+    mm8.run(xb, dst8, M)
+    assert np.array_equal(dst8.read(np.float32).reshape(M, N), got)
+    for o in (mm, mm8, xb, dst, dst8, w, w8):
+        o.destroy()

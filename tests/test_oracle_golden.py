@@ -153,3 +153,24 @@ def test_q8_K_and_q8_0_even_known_answers():
     assert ties.sum() > 100 and np.array_equal(q[5][ties], np.rint(x5[ties]).astype(np.int8))
     bs = np.ascontiguousarray(blk[:, 260:]).view(np.int16)
     assert np.array_equal(bs, q.reshape(-1, 16, 16).astype(np.int32).sum(axis=2).astype(np.int16))
+
+
+def test_q5_0_and_iq4_nl_decode_equals_gguf_py():
+    """The decode the device layout of these two types rests on (d * int8 per weight), against gguf-py's dequantizers; the
+    Q5_0 packer against gguf-py's quantizer."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    from oracle import extra_types as et
+    rng = np.random.default_rng(11)
+    w = (rng.standard_normal((64, 256)) * 0.05).astype(np.float32)
+    w[0, :32] = 0.0          # a block of zeros
+    w[1, 5] = -3.0           # the largest magnitude negative: d > 0
+    for t, qt, pack in ((et.Q5_0, gguf.GGMLQuantizationType.Q5_0, et.quantize_q5_0),
+                        (et.IQ4_NL, gguf.GGMLQuantizationType.IQ4_NL, et.quantize_iq4_nl)):
+        blocks = pack(w)
+        want = quants.dequantize(blocks.reshape(64, -1), qt).reshape(-1)
+        assert np.array_equal(et.dequantize(t, blocks), want)
+        d, q = et.decode(t, blocks)
+        q8 = et.to_q8_0(t, blocks).reshape(-1, 34)
+        assert np.array_equal(q8[:, 2:].view(np.int8), q) and np.array_equal(q8[:, :2].copy().view(np.float16).reshape(-1), d)
+    assert np.array_equal(et.quantize_q5_0(w), quants.quantize(w, gguf.GGMLQuantizationType.Q5_0).reshape(-1))
