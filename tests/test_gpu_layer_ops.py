@@ -282,6 +282,7 @@ def _flash_push(D, n_kv, n_q, n_head, n_head_kv, has_mask, scale, softcap=0.0, m
     (256, 8, 8, 100, 1, False, 30.0, 8 << 20),     # one split, no mask, soft-capped scores
     (128, 28, 4, 2048, 2, True, 0.0, 64),          # scratch too small for splits: every CTA walks all keys
     (128, 64, 8, 333, 1, False, 0.0, 8 << 20),     # eight heads per KV head
+    (128, 32, 8, 32768, 1, True, 0.0, 16 << 20),   # a long context: 134 MB of cache, many key splits
 ])
 def test_flash_attn_decode(ctx, D, n_head, n_head_kv, n_kv, n_q, masked, softcap, scratch):
     rng = np.random.default_rng(D + n_kv)
