@@ -542,7 +542,8 @@ class Measurement:
         env = self.env
         self.gpu_steps(warmup, 0)
         if self.use_replay():   # the graphs of the timed run have been launched once before it is timed
-            self.step_estimate_s = self.gpu_steps(steps, warmup) / steps
+            # (the same estimate on every rank: ranks that exchange outputs must enqueue the same number of replays)
+            self.step_estimate_s = env.max_over_ranks(self.gpu_steps(steps, warmup) / steps)
         env.barrier()
         lead = self.lead_in_replays(steps) if self.use_replay() else 0
         t0 = time.perf_counter()
@@ -868,7 +869,7 @@ def main():
     ap.add_argument("--no-layer-ops", action="store_true", help="leave the `layer_ops` object out of the line")
     ap.add_argument("--sharded-primary", action="store_true",
                     help="N > 1: row-shard the primary workload too (strong scaling) instead of token-parallel replicas")
-    ap.add_argument("--exchange", choices=["copy", "fused", "nccl"], default="copy",
+    ap.add_argument("--exchange", choices=["copy", "fused", "nccl"], default="fused",
                     help="how the ranks of a row-sharded mul_mat assemble the output (see the module docstring)")
     ap.add_argument("--chunk-tokens", type=int, default=256,
                     help="copy exchange, more than 8 token rows: token rows per mul_mat + copy chunk")
