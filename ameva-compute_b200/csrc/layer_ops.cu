@@ -238,6 +238,63 @@ AcResult launch_set_rows(const LaunchArgs& a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// CPY / CONT / DUP between f32 and f16, any strides and shapes with the same element count: element k of the source in
+// row-major order of its own shape goes to element k of the destination in row-major order of the destination shape
+// (ggml_compute_forward_dup). Quantized sources (src_type 2, 3: the shift of a quantized KV cache) are not taken.
+// ---------------------------------------------------------------------------------------------------------------------
+struct CpyArgs {
+    uint32_t a_ne0, a_ne1, a_ne2, a_ne3;
+    uint32_t a_off, a_s0, a_s1, a_s2;
+    uint32_t a_s3, d_ne0, d_ne1, d_ne2;
+    uint32_t d_off, d_s0, d_s1, d_s2;
+    uint32_t d_s3, src_type, dst_f16;
+};
+
+__global__ void __launch_bounds__(256) cpy_kernel(const void* __restrict__ a, void* __restrict__ d, const CpyArgs pc) {
+    pdl_trigger();
+    pdl_wait();
+    const uint64_t k = linear_id();
+    if (k >= (uint64_t)pc.a_ne0 * pc.a_ne1 * pc.a_ne2 * pc.a_ne3) return;
+    uint64_t t = k;
+    const uint32_t a0 = (uint32_t)(t % pc.a_ne0);
+    t /= pc.a_ne0;
+    const uint32_t a1 = (uint32_t)(t % pc.a_ne1);
+    t /= pc.a_ne1;
+    const uint32_t a2 = (uint32_t)(t % pc.a_ne2), a3 = (uint32_t)(t / pc.a_ne2);
+    t = k;
+    const uint32_t b0 = (uint32_t)(t % pc.d_ne0);
+    t /= pc.d_ne0;
+    const uint32_t b1 = (uint32_t)(t % pc.d_ne1);
+    t /= pc.d_ne1;
+    const uint32_t b2 = (uint32_t)(t % pc.d_ne2), b3 = (uint32_t)(t / pc.d_ne2);
+    const uint64_t si = pc.a_off + (uint64_t)a0 * pc.a_s0 + (uint64_t)a1 * pc.a_s1 + (uint64_t)a2 * pc.a_s2 + (uint64_t)a3 * pc.a_s3;
+    const uint64_t di = pc.d_off + (uint64_t)b0 * pc.d_s0 + (uint64_t)b1 * pc.d_s1 + (uint64_t)b2 * pc.d_s2 + (uint64_t)b3 * pc.d_s3;
+    const float v = pc.src_type ? __half2float(((const __half*)a)[si]) : ((const float*)a)[si];
+    if (pc.dst_f16) ((__half*)d)[di] = __float2half_rn(v);
+    else ((float*)d)[di] = v;
+}
+
+// ameva_cpy: bindings 0 source, 1 destination; push = CpyArgs (19 words, ameva_cpy.comp:15-21). The destination's last
+// extent follows from the element count.
+AcResult launch_cpy(const LaunchArgs& a) {
+    CpyArgs pc;
+    memcpy(&pc, a.push, sizeof(pc));
+    if (!pc.a_ne0 || !pc.a_ne1 || !pc.a_ne2 || !pc.a_ne3 || !pc.d_ne0 || !pc.d_ne1 || !pc.d_ne2 || pc.dst_f16 > 1u)
+        return AC_ERR_KERNEL_ARG_INVALID;
+    if (pc.src_type > 1u) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    const uint64_t total = (uint64_t)pc.a_ne0 * pc.a_ne1 * pc.a_ne2 * pc.a_ne3, d012 = (uint64_t)pc.d_ne0 * pc.d_ne1 * pc.d_ne2;
+    if (total % d012) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t d_ne3 = total / d012;
+    const uint64_t src_span = (uint64_t)pc.a_off + (uint64_t)(pc.a_ne0 - 1u) * pc.a_s0 + (uint64_t)(pc.a_ne1 - 1u) * pc.a_s1 +
+                              (uint64_t)(pc.a_ne2 - 1u) * pc.a_s2 + (uint64_t)(pc.a_ne3 - 1u) * pc.a_s3 + 1u;
+    const uint64_t dst_span = (uint64_t)pc.d_off + (uint64_t)(pc.d_ne0 - 1u) * pc.d_s0 + (uint64_t)(pc.d_ne1 - 1u) * pc.d_s1 +
+                              (uint64_t)(pc.d_ne2 - 1u) * pc.d_s2 + (d_ne3 - 1u) * pc.d_s3 + 1u;
+    if (a.range[0] < src_span * (pc.src_type ? 2u : 4u) || a.range[1] < dst_span * (pc.dst_f16 ? 2u : 4u)) return AC_ERR_INVALID_BUFFER_SIZE;
+    launch_pdl(cpy_kernel, dim3((unsigned)((total + 255u) / 256u)), dim3(256), 0, a.stream, (const void*)a.ptr[0], (void*)a.ptr[1], pc);
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
 // SOFT_MAX per row of ne0 elements: x = a * scale (+ mask), y = exp(x - max x) / sum exp(x - max x); mask 1 = f32,
 // 2 = f16, with the row length and row count of a, repeated over dimensions 2 and 3. One CTA per row; a thread writes
 // only the elements it read itself and only after the reductions, so the result may lie in place of the source.

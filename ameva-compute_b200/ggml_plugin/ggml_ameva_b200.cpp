@@ -455,11 +455,17 @@ bool elem_strides(const ggml_tensor* t, size_t es) {   // element 0 stride = one
         if (t->nb[i] % es || t->nb[i] / es > 0xFFFFFFFFull) return false;
     return true;
 }
+bool whole_elem_strides(const ggml_tensor* t, size_t es) {   // any layout whose strides are whole elements (a transposed view)
+    if (!t || !es) return false;
+    for (int i = 0; i < 4; ++i)
+        if (t->nb[i] % es || t->nb[i] / es > 0xFFFFFFFFull) return false;
+    return true;
+}
 uint32_t st(const ggml_tensor* t, int i, size_t es) { return (uint32_t)(t->nb[i] / es); }
 
 bool is_layer_op(enum ggml_op op) {
     return op == GGML_OP_ROPE || op == GGML_OP_GET_ROWS || op == GGML_OP_SET_ROWS || op == GGML_OP_SOFT_MAX ||
-           op == GGML_OP_FLASH_ATTN_EXT;
+           op == GGML_OP_FLASH_ATTN_EXT || op == GGML_OP_CPY || op == GGML_OP_CONT || op == GGML_OP_DUP;
 }
 float param_f32(const ggml_tensor* t, int i) {
     float f;
@@ -481,6 +487,15 @@ const char* layer_op_static_reason(const ggml_tensor* node) {
             if (node->src[2] && (node->src[2]->type != GGML_TYPE_F32 || node->src[2]->ne[0] < n_dims / 2)) return "rope: frequency factors";
             for (int i = 0; i < 4; ++i)
                 if (a->ne[i] != node->ne[i]) return "rope: shape";
+            return nullptr;
+        }
+        case GGML_OP_CPY:
+        case GGML_OP_CONT:
+        case GGML_OP_DUP: {
+            if (!a || (a->type != GGML_TYPE_F32 && a->type != GGML_TYPE_F16) || (node->type != GGML_TYPE_F32 && node->type != GGML_TYPE_F16))
+                return "cpy: between f32 and f16 only";
+            if (!whole_elem_strides(a, elem_size(a->type)) || !whole_elem_strides(node, elem_size(node->type))) return "cpy: strides are not whole elements";
+            if (a->ne[0] * a->ne[1] * a->ne[2] * a->ne[3] != node->ne[0] * node->ne[1] * node->ne[2] * node->ne[3]) return "cpy: element counts differ";
             return nullptr;
         }
         case GGML_OP_GET_ROWS: {
@@ -865,6 +880,20 @@ bool record_layer_op(Recorder& r, const ggml_tensor* node, int node_index) {
                                      f32_bits(attn_factor), f32_bits(corr[0]), f32_bits(corr[1])};
             const AcBufferBinding bb[4] = {ba.b, bp.b, bf.b, bd.b};
             return dispatch(r, a->type == GGML_TYPE_F16 ? "ameva_rope_f16" : "ameva_rope", bb, 4, pc, sizeof(pc));
+        }
+        case GGML_OP_CPY:
+        case GGML_OP_CONT:
+        case GGML_OP_DUP: {
+            const size_t es = elem_size(a->type), ds = elem_size(node->type);
+            ElemBind ba, bd;
+            if (!bind_elems(a, es, &ba) || !bind_elems(node, ds, &bd)) return false;
+            const uint32_t pc[19] = {(uint32_t)a->ne[0], (uint32_t)a->ne[1], (uint32_t)a->ne[2], (uint32_t)a->ne[3],
+                                     ba.elem, st(a, 0, es), st(a, 1, es), st(a, 2, es),
+                                     st(a, 3, es), (uint32_t)node->ne[0], (uint32_t)node->ne[1], (uint32_t)node->ne[2],
+                                     bd.elem, st(node, 0, ds), st(node, 1, ds), st(node, 2, ds),
+                                     st(node, 3, ds), a->type == GGML_TYPE_F16 ? 1u : 0u, node->type == GGML_TYPE_F16 ? 1u : 0u};
+            const AcBufferBinding bb[2] = {ba.b, bd.b};
+            return dispatch(r, "ameva_cpy", bb, 2, pc, sizeof(pc));
         }
         case GGML_OP_GET_ROWS: {
             const size_t es = elem_size(a->type);
@@ -1297,7 +1326,8 @@ const char* ggml_backend_ameva_abi_check(void) {
         } kOps[] = {{GGML_OP_NONE, "NONE"},       {GGML_OP_ADD, "ADD"},         {GGML_OP_MUL, "MUL"},   {GGML_OP_RMS_NORM, "RMS_NORM"},
                     {GGML_OP_MUL_MAT, "MUL_MAT"}, {GGML_OP_RESHAPE, "RESHAPE"}, {GGML_OP_VIEW, "VIEW"}, {GGML_OP_PERMUTE, "PERMUTE"},
                     {GGML_OP_TRANSPOSE, "TRANSPOSE"}, {GGML_OP_GLU, "GLU"}, {GGML_OP_ROPE, "ROPE"}, {GGML_OP_GET_ROWS, "GET_ROWS"},
-                    {GGML_OP_SET_ROWS, "SET_ROWS"}, {GGML_OP_SOFT_MAX, "SOFT_MAX"}, {GGML_OP_FLASH_ATTN_EXT, "FLASH_ATTN_EXT"}};
+                    {GGML_OP_SET_ROWS, "SET_ROWS"}, {GGML_OP_SOFT_MAX, "SOFT_MAX"}, {GGML_OP_FLASH_ATTN_EXT, "FLASH_ATTN_EXT"},
+                    {GGML_OP_CPY, "CPY"}, {GGML_OP_CONT, "CONT"}, {GGML_OP_DUP, "DUP"}};
         static const struct {
             enum ggml_type type;
             const char* name;

@@ -85,6 +85,9 @@ const char* ggml_op_name(enum ggml_op op) {
         case GGML_OP_TRANSPOSE: return "TRANSPOSE";
         case GGML_OP_GLU: return "GLU";
         case GGML_OP_SUB: return "SUB";
+        case GGML_OP_CPY: return "CPY";
+        case GGML_OP_CONT: return "CONT";
+        case GGML_OP_DUP: return "DUP";
         case GGML_OP_ROPE: return "ROPE";
         case GGML_OP_GET_ROWS: return "GET_ROWS";
         case GGML_OP_SET_ROWS: return "SET_ROWS";
@@ -533,6 +536,7 @@ static int run_attn(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_
         ar.add(t);
     CHECK(ar.commit());
     ggml_backend_buffer_t buf = ar.buf;
+    Arena ar2{buft};   // a second buffer of the same type, for the results of the copies below
     struct { ggml_tensor* t; const char* file; } uploads[] = {
         {&emb, "emb.bin"}, {&tok, "tok.bin"}, {&q, "q.bin"}, {&kcur, "kcur.bin"}, {&vcur, "vcur.bin"}, {&kcache, "kcache.bin"},
         {&vcache, "vcache.bin"}, {&pos, "pos.bin"}, {&slots, "slots.bin"}, {&mask, "mask.bin"}, {&sc, "sc.bin"}, {&smask, "smask.bin"}};
@@ -581,7 +585,16 @@ static int run_attn(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_
     op2(&sm, GGML_OP_SOFT_MAX, &sc, &smask);
     memcpy(&sm.op_params[0], &scale, 4);
     memcpy(&sm.op_params[1], &zero, 4);
-    ggml_tensor* nodes[] = {&x, &q_rope, &k_rope, &k_rows, &kset, &vset, &q_perm, &k_view, &v_view, &attn, &sm};
+    // CONT of the permuted queries (a gather into [D, n_tok, n_head] order) and a CPY of the new values to f16
+    ggml_tensor q_cont, v_f16;
+    shape3(&q_cont, GGML_TYPE_F32, D, n_tok, n_head, "q_cont");
+    shape(&v_f16, GGML_TYPE_F16, kvw, n_tok, "v_cur_f16");
+    ar2.add(&q_cont);
+    ar2.add(&v_f16);
+    CHECK(ar2.commit());
+    op2(&q_cont, GGML_OP_CONT, &q_perm, nullptr);
+    op2(&v_f16, GGML_OP_CPY, &vcur, &v_f16);
+    ggml_tensor* nodes[] = {&x, &q_rope, &k_rope, &k_rows, &kset, &vset, &q_perm, &k_view, &v_view, &attn, &sm, &q_cont, &v_f16};
     const int n = (int)(sizeof(nodes) / sizeof(nodes[0]));
     for (ggml_tensor* t : nodes) CHECK(dev->iface.supports_op(dev, t));
     ggml_cgraph g = {n, nodes};
@@ -593,6 +606,12 @@ static int run_attn(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_
         buf->iface.get_tensor(buf, t, v.data(), 0, v.size());
         return dump(dir + "/" + name, v.data(), v.size());
     };
+    {
+        std::vector<uint8_t> v1(ggml_nbytes(&q_cont)), v2(ggml_nbytes(&v_f16));
+        ar2.buf->iface.get_tensor(ar2.buf, &q_cont, v1.data(), 0, v1.size());
+        ar2.buf->iface.get_tensor(ar2.buf, &v_f16, v2.data(), 0, v2.size());
+        CHECK(dump(dir + "/q_cont.out", v1.data(), v1.size()) && dump(dir + "/v_f16.out", v2.data(), v2.size()));
+    }
     CHECK(out(&x, "x.out") && out(&q_rope, "q_rope.out") && out(&k_rope, "k_rope.out") && out(&kcache, "kcache.out") &&
           out(&vcache, "vcache.out") && out(&attn, "attn.out") && out(&sm, "sm.out"));
     // a cache slot past the cache: the graph fails and the op counter does not move
@@ -608,6 +627,7 @@ static int run_attn(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_
     // an op outside the set is refused at planning time
     sm.op_params[1] = 0x41000000;   // max_bias 8.0: ALiBi
     CHECK(!dev->iface.supports_op(dev, &sm));
+    ar2.buf->iface.free_buffer(ar2.buf);
     buf->iface.free_buffer(buf);
     backend->iface.free(backend);
     ggml_backend_ameva_teardown();

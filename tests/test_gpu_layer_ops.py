@@ -325,3 +325,28 @@ def test_flash_attn_refusals(ctx):
         with pytest.raises(rt.AmevaComputeError, match=code):
             _run(ctx, "ameva_flash_attn", [b, b, b, b, b, b], push)
     b.destroy()
+
+
+# ---- CPY / CONT ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("src_dt,dst_dt", [(np.float32, np.float32), (np.float32, np.float16), (np.float16, np.float32),
+                                           (np.float16, np.float16)])
+def test_cpy_gathers_a_transposed_view_into_another_shape(ctx, src_dt, dst_dt):
+    """Element k of the source in row-major order of its own (here transposed) shape goes to element k of the destination
+    in row-major order of the destination's shape (ggml_compute_forward_dup): CONT of a transpose, reshaped on the way."""
+    ne1, ne0 = 37, 48                          # the stored array is [ne1][ne0]; the view transposes it
+    rng = np.random.default_rng(13)
+    a = rng.standard_normal((3, ne1, ne0)).astype(src_dt)
+    ab, db = ctx.buffer(data=a), ctx.buffer(a.size * np.dtype(dst_dt).itemsize + 64)
+    # source view: ne = [ne1, ne0, 3] with strides (ne0, 1, ne0 * ne1); destination: contiguous [3 * ne0 * ne1 / 16][16] + offset 8
+    push = [ne1, ne0, 3, 1, 0, ne0, 1, ne0 * ne1, ne0 * ne1 * 3, 16, ne0 * ne1 * 3 // 16, 1, 8, 1, 16, ne0 * ne1 * 3,
+            ne0 * ne1 * 3, int(src_dt == np.float16), int(dst_dt == np.float16)]
+    _run(ctx, "ameva_cpy", [ab, db], push)
+    got = db.read(dst_dt)[8:8 + a.size]
+    want = a.transpose(0, 2, 1).reshape(-1).astype(dst_dt)
+    assert np.array_equal(got, want)
+    with pytest.raises(rt.AmevaComputeError, match="FEATURE_NOT_SUPPORTED"):
+        _run(ctx, "ameva_cpy", [ab, db], push[:17] + [2, 0])       # a quantized source
+    with pytest.raises(rt.AmevaComputeError, match="KERNEL_ARG_INVALID"):
+        _run(ctx, "ameva_cpy", [ab, db], push[:9] + [7] + push[10:])   # element counts that do not divide
+    ab.destroy()
+    db.destroy()
