@@ -238,6 +238,69 @@ AcResult launch_set_rows(const LaunchArgs& a) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
+// Element-wise f32 ops, same shape in and out, dimension 0 contiguous (SCALE and ggml's unary ops). The op codes and the
+// formulas are the reference shader's (ameva_unary.comp:4-6, 52-73), which are ggml's (ggml-cpu vec.h / unary-ops.cpp)
+// evaluated in fp32; GELU is the formula itself, not ggml's f16 lookup table.
+// ---------------------------------------------------------------------------------------------------------------------
+struct UnaryArgs {
+    uint32_t ne0, ne1, ne2, ne3;
+    uint32_t a_off, a_s1, a_s2, a_s3;
+    uint32_t d_off, d_s1, d_s2, d_s3;
+    uint32_t op, p0, p1;
+};
+
+__global__ void __launch_bounds__(256) unary_kernel(const float* a, float* d, const UnaryArgs pc) {
+    pdl_trigger();
+    pdl_wait();
+    const uint64_t i = linear_id();
+    if (i >= (uint64_t)pc.ne0 * pc.ne1 * pc.ne2 * pc.ne3) return;
+    uint64_t t = i;
+    const uint32_t i0 = (uint32_t)(t % pc.ne0);
+    t /= pc.ne0;
+    const uint32_t i1 = (uint32_t)(t % pc.ne1);
+    t /= pc.ne1;
+    const uint32_t i2 = (uint32_t)(t % pc.ne2), i3 = (uint32_t)(t / pc.ne2);
+    const float x = a[pc.a_off + i0 + (uint64_t)i1 * pc.a_s1 + (uint64_t)i2 * pc.a_s2 + (uint64_t)i3 * pc.a_s3];
+    const float p0 = u2f(pc.p0), p1 = u2f(pc.p1);
+    float r;
+    switch (pc.op) {
+        case 0u: r = x * p0 + p1; break;                                                    // SCALE
+        case 1u: r = tanhf(x); break;
+        case 2u: r = x / (1.0f + expf(-x)); break;                                          // SILU
+        case 3u: r = 0.5f * x * (1.0f + tanhf(0.79788456080286535588f * x * (1.0f + 0.044715f * x * x))); break;   // GELU
+        case 4u: r = 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f)); break;          // GELU_ERF
+        case 5u: r = x * (1.0f / (1.0f + expf(-1.702f * x))); break;                        // GELU_QUICK
+        case 6u: r = fmaxf(x, 0.0f); break;
+        case 7u: r = 1.0f / (1.0f + expf(-x)); break;                                       // SIGMOID
+        case 8u: r = -x; break;
+        case 9u: r = x * x; break;
+        case 10u: r = sqrtf(x); break;
+        case 11u: r = expf(x); break;
+        case 13u: r = sinf(x); break;
+        case 14u: r = cosf(x); break;
+        case 15u: r = fmaxf(x, 0.0f) + p0 * fminf(x, 0.0f); break;                          // LEAKY_RELU
+        case 16u: r = x > 0.0f ? 1.0f : (x < 0.0f ? -1.0f : 0.0f); break;                   // SGN
+        case 17u: r = x > 0.0f ? 1.0f : 0.0f; break;                                        // STEP
+        case 18u: r = floorf(x); break;
+        default: r = fabsf(x); break;                                                       // 12 ABS
+    }
+    d[pc.d_off + i0 + (uint64_t)i1 * pc.d_s1 + (uint64_t)i2 * pc.d_s2 + (uint64_t)i3 * pc.d_s3] = r;
+}
+
+// ameva_unary: bindings 0 source f32, 1 destination f32 (may be the source); push = UnaryArgs (15 words)
+AcResult launch_unary(const LaunchArgs& a) {
+    UnaryArgs pc;
+    memcpy(&pc, a.push, sizeof(pc));
+    if (!pc.ne0 || !pc.ne1 || !pc.ne2 || !pc.ne3 || pc.op > 18u) return AC_ERR_KERNEL_ARG_INVALID;
+    if (a.range[0] < span_elems(pc.a_off, pc.ne0, pc.ne1, pc.ne2, pc.ne3, pc.a_s1, pc.a_s2, pc.a_s3) * 4u ||
+        a.range[1] < span_elems(pc.d_off, pc.ne0, pc.ne1, pc.ne2, pc.ne3, pc.d_s1, pc.d_s2, pc.d_s3) * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    const uint64_t total = (uint64_t)pc.ne0 * pc.ne1 * pc.ne2 * pc.ne3;
+    launch_pdl(unary_kernel, dim3((unsigned)((total + 255u) / 256u)), dim3(256), 0, a.stream, (const float*)a.ptr[0], (float*)a.ptr[1], pc);
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
 // CPY / CONT / DUP between f32 and f16, any strides and shapes with the same element count: element k of the source in
 // row-major order of its own shape goes to element k of the destination in row-major order of the destination shape
 // (ggml_compute_forward_dup). Quantized sources (src_type 2, 3: the shift of a quantized KV cache) are not taken.

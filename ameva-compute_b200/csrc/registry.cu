@@ -45,6 +45,7 @@ AcResult launch_soft_max(const LaunchArgs&);
 AcResult launch_gemv_f16(const LaunchArgs&);
 AcResult launch_flash_attn(const LaunchArgs&);
 AcResult launch_cpy(const LaunchArgs&);
+AcResult launch_unary(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
@@ -103,6 +104,7 @@ static const KernelEntry kTable[] = {
     {"ameva_soft_max", 3, 80, {128, 1, 1}, launch_soft_max},
     {"ameva_flash_attn", 6, 124, {128, 1, 1}, launch_flash_attn},
     {"ameva_cpy", 2, 76, {256, 1, 1}, launch_cpy},
+    {"ameva_unary", 2, 60, {256, 1, 1}, launch_unary},
     {"bitnet_gemv_f16_w1", 3, 12, {32, 4, 1}, launch_gemv_f16},
     {"bitnet_gemv_f16_w2", 3, 12, {32, 4, 1}, launch_gemv_f16},
     {"bitnet_gemv_f16_w4", 3, 12, {32, 4, 1}, launch_gemv_f16},

@@ -463,7 +463,42 @@ bool whole_elem_strides(const ggml_tensor* t, size_t es) {   // any layout whose
 }
 uint32_t st(const ggml_tensor* t, int i, size_t es) { return (uint32_t)(t->nb[i] / es); }
 
+// the op code of ameva_unary for a node (ameva_unary.comp:4-6), -1 when the kernel has none
+int unary_code(const ggml_tensor* node) {
+    switch (node->op) {
+        case GGML_OP_SCALE: return 0;
+        case GGML_OP_SQR: return 9;
+        case GGML_OP_SQRT: return 10;
+        case GGML_OP_SIN: return 13;
+        case GGML_OP_COS: return 14;
+        case GGML_OP_LEAKY_RELU: return 15;
+        case GGML_OP_UNARY:
+            switch ((enum ggml_unary_op)node->op_params[0]) {
+                case GGML_UNARY_OP_TANH: return 1;
+                case GGML_UNARY_OP_SILU: return 2;
+                case GGML_UNARY_OP_GELU: return 3;
+                case GGML_UNARY_OP_GELU_ERF: return 4;
+                case GGML_UNARY_OP_GELU_QUICK: return 5;
+                case GGML_UNARY_OP_RELU: return 6;
+                case GGML_UNARY_OP_SIGMOID: return 7;
+                case GGML_UNARY_OP_NEG: return 8;
+                case GGML_UNARY_OP_EXP: return 11;
+                case GGML_UNARY_OP_ABS: return 12;
+                case GGML_UNARY_OP_SGN: return 16;
+                case GGML_UNARY_OP_STEP: return 17;
+                case GGML_UNARY_OP_FLOOR: return 18;
+                default: return -1;
+            }
+        default: return -1;
+    }
+}
+bool is_unary_like(enum ggml_op op) {
+    return op == GGML_OP_SCALE || op == GGML_OP_UNARY || op == GGML_OP_SQR || op == GGML_OP_SQRT || op == GGML_OP_SIN ||
+           op == GGML_OP_COS || op == GGML_OP_LEAKY_RELU;
+}
+
 bool is_layer_op(enum ggml_op op) {
+    if (is_unary_like(op)) return true;
     return op == GGML_OP_ROPE || op == GGML_OP_GET_ROWS || op == GGML_OP_SET_ROWS || op == GGML_OP_SOFT_MAX ||
            op == GGML_OP_FLASH_ATTN_EXT || op == GGML_OP_CPY || op == GGML_OP_CONT || op == GGML_OP_DUP;
 }
@@ -475,6 +510,13 @@ float param_f32(const ggml_tensor* t, int i) {
 
 const char* layer_op_static_reason(const ggml_tensor* node) {
     const ggml_tensor *a = node->src[0], *b = node->src[1];
+    if (is_unary_like(node->op)) {
+        if (unary_code(node) < 0) return "unary op without a kernel";
+        if (!a || a->type != GGML_TYPE_F32 || node->type != GGML_TYPE_F32 || !elem_strides(a, 4) || !elem_strides(node, 4)) return "unary: f32 rows only";
+        for (int i = 0; i < 4; ++i)
+            if (a->ne[i] != node->ne[i]) return "unary: shape";
+        return nullptr;
+    }
     switch (node->op) {
         case GGML_OP_ROPE: {
             if (!a || !b || (a->type != GGML_TYPE_F32 && a->type != GGML_TYPE_F16) || node->type != a->type) return "rope: f32 or f16 only";
@@ -860,6 +902,22 @@ bool record_elementwise(Recorder& r, const ggml_tensor* node, const ggml_tensor*
 bool record_layer_op(Recorder& r, const ggml_tensor* node, int node_index) {
     const ggml_tensor *a = node->src[0], *b = node->src[1];
     const AcBufferBinding status = bind(r.be->op_status, 0, 256);
+    if (is_unary_like(node->op)) {
+        ElemBind ba, bd;
+        if (!bind_elems(a, 4, &ba) || !bind_elems(node, 4, &bd)) return false;
+        uint32_t p0 = 0, p1 = 0;
+        if (node->op == GGML_OP_SCALE) {
+            p0 = f32_bits(param_f32(node, 0));
+            p1 = f32_bits(param_f32(node, 1));
+        } else if (node->op == GGML_OP_LEAKY_RELU) {
+            p0 = f32_bits(param_f32(node, 0));
+        }
+        const uint32_t pc[15] = {(uint32_t)node->ne[0], (uint32_t)node->ne[1], (uint32_t)node->ne[2], (uint32_t)node->ne[3],
+                                 ba.elem, st(a, 1, 4), st(a, 2, 4), st(a, 3, 4), bd.elem, st(node, 1, 4), st(node, 2, 4),
+                                 st(node, 3, 4), (uint32_t)unary_code(node), p0, p1};
+        const AcBufferBinding bb[2] = {ba.b, bd.b};
+        return dispatch(r, "ameva_unary", bb, 2, pc, sizeof(pc));
+    }
     switch (node->op) {
         case GGML_OP_ROPE: {
             const ggml_tensor* ff = node->src[2];
@@ -1327,7 +1385,8 @@ const char* ggml_backend_ameva_abi_check(void) {
                     {GGML_OP_MUL_MAT, "MUL_MAT"}, {GGML_OP_RESHAPE, "RESHAPE"}, {GGML_OP_VIEW, "VIEW"}, {GGML_OP_PERMUTE, "PERMUTE"},
                     {GGML_OP_TRANSPOSE, "TRANSPOSE"}, {GGML_OP_GLU, "GLU"}, {GGML_OP_ROPE, "ROPE"}, {GGML_OP_GET_ROWS, "GET_ROWS"},
                     {GGML_OP_SET_ROWS, "SET_ROWS"}, {GGML_OP_SOFT_MAX, "SOFT_MAX"}, {GGML_OP_FLASH_ATTN_EXT, "FLASH_ATTN_EXT"},
-                    {GGML_OP_CPY, "CPY"}, {GGML_OP_CONT, "CONT"}, {GGML_OP_DUP, "DUP"}};
+                    {GGML_OP_CPY, "CPY"}, {GGML_OP_CONT, "CONT"}, {GGML_OP_DUP, "DUP"}, {GGML_OP_SCALE, "SCALE"},
+                    {GGML_OP_UNARY, "UNARY"}, {GGML_OP_SQR, "SQR"}};
         static const struct {
             enum ggml_type type;
             const char* name;

@@ -85,6 +85,9 @@ const char* ggml_op_name(enum ggml_op op) {
         case GGML_OP_TRANSPOSE: return "TRANSPOSE";
         case GGML_OP_GLU: return "GLU";
         case GGML_OP_SUB: return "SUB";
+        case GGML_OP_SCALE: return "SCALE";
+        case GGML_OP_UNARY: return "UNARY";
+        case GGML_OP_SQR: return "SQR";
         case GGML_OP_CPY: return "CPY";
         case GGML_OP_CONT: return "CONT";
         case GGML_OP_DUP: return "DUP";
@@ -594,7 +597,22 @@ static int run_attn(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_
     CHECK(ar2.commit());
     op2(&q_cont, GGML_OP_CONT, &q_perm, nullptr);
     op2(&v_f16, GGML_OP_CPY, &vcur, &v_f16);
-    ggml_tensor* nodes[] = {&x, &q_rope, &k_rope, &k_rows, &kset, &vset, &q_perm, &k_view, &v_view, &attn, &sm, &q_cont, &v_f16};
+    // SCALE with a bias, in place of nothing (own result), and SILU on the embedded rows
+    ggml_tensor x_scaled, x_silu;
+    shape(&x_scaled, GGML_TYPE_F32, n_embd, n_tok, "x_scaled");
+    shape(&x_silu, GGML_TYPE_F32, n_embd, n_tok, "x_silu");
+    Arena ar3{buft};
+    ar3.add(&x_scaled);
+    ar3.add(&x_silu);
+    CHECK(ar3.commit());
+    op2(&x_scaled, GGML_OP_SCALE, &x, nullptr);
+    const float sc_s = 0.125f, sc_b = -0.5f;
+    memcpy(&x_scaled.op_params[0], &sc_s, 4);
+    memcpy(&x_scaled.op_params[1], &sc_b, 4);
+    op2(&x_silu, GGML_OP_UNARY, &x, nullptr);
+    x_silu.op_params[0] = (int32_t)GGML_UNARY_OP_SILU;
+    ggml_tensor* nodes[] = {&x, &q_rope, &k_rope, &k_rows, &kset, &vset, &q_perm, &k_view, &v_view, &attn, &sm, &q_cont, &v_f16,
+                            &x_scaled, &x_silu};
     const int n = (int)(sizeof(nodes) / sizeof(nodes[0]));
     for (ggml_tensor* t : nodes) CHECK(dev->iface.supports_op(dev, t));
     ggml_cgraph g = {n, nodes};
@@ -611,6 +629,15 @@ static int run_attn(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_
         ar2.buf->iface.get_tensor(ar2.buf, &q_cont, v1.data(), 0, v1.size());
         ar2.buf->iface.get_tensor(ar2.buf, &v_f16, v2.data(), 0, v2.size());
         CHECK(dump(dir + "/q_cont.out", v1.data(), v1.size()) && dump(dir + "/v_f16.out", v2.data(), v2.size()));
+        std::vector<uint8_t> v3(ggml_nbytes(&x_scaled)), v4(ggml_nbytes(&x_silu));
+        ar3.buf->iface.get_tensor(ar3.buf, &x_scaled, v3.data(), 0, v3.size());
+        ar3.buf->iface.get_tensor(ar3.buf, &x_silu, v4.data(), 0, v4.size());
+        CHECK(dump(dir + "/x_scaled.out", v3.data(), v3.size()) && dump(dir + "/x_silu.out", v4.data(), v4.size()));
+    }
+    {   // a unary op the kernel has no code for is refused at planning time
+        ggml_tensor t = x_silu;
+        t.op_params[0] = (int32_t)GGML_UNARY_OP_ELU;
+        CHECK(!dev->iface.supports_op(dev, &t));
     }
     CHECK(out(&x, "x.out") && out(&q_rope, "q_rope.out") && out(&k_rope, "k_rope.out") && out(&kcache, "kcache.out") &&
           out(&vcache, "vcache.out") && out(&attn, "attn.out") && out(&sm, "sm.out"));
@@ -627,6 +654,7 @@ static int run_attn(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_
     // an op outside the set is refused at planning time
     sm.op_params[1] = 0x41000000;   // max_bias 8.0: ALiBi
     CHECK(!dev->iface.supports_op(dev, &sm));
+    ar3.buf->iface.free_buffer(ar3.buf);
     ar2.buf->iface.free_buffer(ar2.buf);
     buf->iface.free_buffer(buf);
     backend->iface.free(backend);

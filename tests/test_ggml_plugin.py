@@ -138,13 +138,14 @@ def test_attention_side_of_a_decoder_layer_through_the_plugin(D, n_head, n_head_
         r = subprocess.run([DRIVER, "attn", str(D), str(n_head), str(n_head_kv), str(n_ctx), str(n_kv), str(n_tok), str(n_vocab),
                             str(n_embd), d], capture_output=True, text=True)
         assert r.returncode == 0, r.stdout + r.stderr
-        assert r.stdout.strip().endswith("ok") and "COUNTER gpu_op 9" in r.stdout
+        assert r.stdout.strip().endswith("ok") and "COUNTER gpu_op 11" in r.stdout
         assert "row indices out of range" in r.stderr
         load = lambda n, dt: np.fromfile(os.path.join(d, n + ".out"), dt)
         x, q_rope, k_rope = load("x", np.float32), load("q_rope", np.float32), load("k_rope", np.float32)
         kc, vc = load("kcache", np.float16).reshape(n_ctx, kvw), load("vcache", np.float16).reshape(n_ctx, kvw)
         attn, sm = load("attn", np.float32).reshape(n_tok, n_head, D), load("sm", np.float32).reshape(n_head, n_tok, n_kv)
         q_cont, v_f16 = load("q_cont", np.float32).reshape(n_head, n_tok, D), load("v_f16", np.float16).reshape(n_tok, kvw)
+        x_scaled, x_silu = load("x_scaled", np.float32), load("x_silu", np.float32)
     assert np.array_equal(x.reshape(n_tok, n_embd), emb[tok].astype(np.float32))
     want_q = ops.rope(q[None], pos, D, True, 10000.0)[0]
     want_k = ops.rope(kcur[None], pos, D, True, 10000.0)[0]
@@ -161,5 +162,8 @@ def test_attention_side_of_a_decoder_layer_through_the_plugin(D, n_head, n_head_
     assert np.max(np.abs(attn - want_attn)) <= 2e-3 * max(1.0, float(np.max(np.abs(want_attn))))
     # CONT of the permuted queries (the device's own rotated values, gathered) and the CPY to f16
     assert np.array_equal(q_cont, q_rope.reshape(q.shape).transpose(1, 0, 2)) and np.array_equal(v_f16, vcur.astype(np.float16))
+    xe = emb[tok].astype(np.float32).reshape(-1)
+    assert np.array_equal(x_scaled, xe * np.float32(0.125) + np.float32(-0.5))      # SCALE with its bias (exact: a power of two)
+    assert np.max(np.abs(x_silu - xe / (1.0 + np.exp(-xe.astype(np.float64))))) <= 1e-6
     want_sm = ops.soft_max(sc[None], 1.0 / np.sqrt(np.float32(D)), smask[None, None])[0]
     assert np.max(np.abs(sm - want_sm)) <= 2e-6

@@ -350,3 +350,36 @@ def test_cpy_gathers_a_transposed_view_into_another_shape(ctx, src_dt, dst_dt):
         _run(ctx, "ameva_cpy", [ab, db], push[:9] + [7] + push[10:])   # element counts that do not divide
     ab.destroy()
     db.destroy()
+
+
+# ---- SCALE and the unary ops ----------------------------------------------------------------------------------------------
+def test_unary_ops_follow_the_cpu_formulas(ctx):
+    """Every op code of ameva_unary (ameva_unary.comp:4-6) against numpy in fp64, on a strided view and in place."""
+    from math import erf
+    rng = np.random.default_rng(17)
+    rows, cols, pitch = 9, 130, 160
+    a = (rng.standard_normal((rows, pitch)) * 3).astype(np.float32)
+    x = a[:, :cols].astype(np.float64)
+    sig = lambda v: 1.0 / (1.0 + np.exp(-v))
+    want = {0: x * 0.75 + 0.5, 1: np.tanh(x), 2: x * sig(x), 3: 0.5 * x * (1 + np.tanh(0.7978845608028654 * x * (1 + 0.044715 * x * x))),
+            4: 0.5 * x * (1 + np.vectorize(erf)(x * 0.7071067811865476)), 5: x * sig(1.702 * x), 6: np.maximum(x, 0), 7: sig(x), 8: -x,
+            9: x * x, 10: np.sqrt(np.abs(x)), 11: np.exp(x), 12: np.abs(x), 13: np.sin(x), 14: np.cos(x),
+            15: np.maximum(x, 0) + 0.1 * np.minimum(x, 0), 16: np.sign(x), 17: (x > 0).astype(np.float64), 18: np.floor(x)}
+    ab, db = ctx.buffer(data=a), ctx.buffer(rows * cols * 4)
+    for op, w in want.items():
+        src = np.abs(a) if op == 10 else a
+        ab.write(src)
+        p0 = {0: 0.75, 15: 0.1}.get(op, 0.0)
+        push = [cols, rows, 1, 1, 0, pitch, pitch * rows, pitch * rows, 0, cols, cols * rows, cols * rows, op, fbits(p0), fbits(0.5)]
+        _run(ctx, "ameva_unary", [ab, db], push)
+        got = db.read(np.float32).reshape(rows, cols)
+        assert np.max(np.abs(got - w) / np.maximum(1.0, np.abs(w))) <= 2e-6, op
+        if op in (0, 2):    # in place on the strided source
+            push[8:12] = [0, pitch, pitch * rows, pitch * rows]
+            _run(ctx, "ameva_unary", [ab, ab], push)
+            back = ab.read(np.float32).reshape(rows, pitch)
+            assert np.array_equal(back[:, :cols], got) and np.array_equal(back[:, cols:], src[:, cols:])
+    with pytest.raises(rt.AmevaComputeError, match="KERNEL_ARG_INVALID"):
+        _run(ctx, "ameva_unary", [ab, db], [cols, rows, 1, 1, 0, pitch, 0, 0, 0, cols, 0, 0, 19, 0, 0])
+    ab.destroy()
+    db.destroy()
