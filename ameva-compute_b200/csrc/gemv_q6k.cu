@@ -1,0 +1,95 @@
+// Q6_K x Q8_K mul_mat for up to 8 activation rows (token generation; more rows run in chunks of 8).
+//
+// A Q6_K weight is d * scale[e / 16] * (q6 - 32) with 6-bit q6 split over ql / qh (ggml-common.h block_q6_K: ql[128],
+// qh[64], scales[16] int8, d fp16: 210 bytes per 256 weights). The upload decodes q6 - 32 to int8 in element order and
+// keeps the scale bytes (registry.cu decode_q6_K; 274 bytes per block on the device), so the kernel reads a 16-weight
+// group with one 16-byte load and multiplies it with the int8 activations by four dp4a:
+//   y[m][n] = sum_blocks (d_w * d_a) * sum_{g < 16} scale[g] * sum_{i < 16} (q6 - 32)[16 g + i] * q8[16 g + i]
+// which is ggml_vec_dot_q6_K_q8_K's arithmetic (generic branch: aux32 += scale * (q8 * (q6 - 32)), sumf += d * aux32)
+// with the integers exact and the fp32 products summed per lane and then over the warp (ggml sums per block in lane
+// order 0..7; the results agree to fp32 rounding). The reference serves Q6_K through its f32 GEMV with the weights
+// decoded in the shader (adapters/llama/ggml-ameva/shaders/ameva_qdecode.glsl, decode of type 14;
+// ggml-ameva-repack.cpp:21-28 lists q6_K in the repacked family).
+//
+// One warp per weight row, eight rows per CTA; a lane walks the row's 16-weight groups with stride 32, so a warp's loads
+// are 512 contiguous bytes; weights bypass L1, which keeps the activation rows. Bound by HBM: 274 bytes per 256 weights.
+#include "common.cuh"
+
+namespace amv {
+
+constexpr int kQ6Warps = 8;
+constexpr uint32_t kQ6ScaleBytes = 18;   // 16 int8 sub-block scales + fp16 d, as in the ggml block
+
+template <int M>
+__global__ void __launch_bounds__(kQ6Warps * 32) gemv_q6k_kernel(const uint8_t* __restrict__ Q, const uint8_t* __restrict__ S,
+                                                                 const int8_t* __restrict__ AQ, const uint8_t* __restrict__ AB,
+                                                                 float* __restrict__ dst, uint32_t N, uint32_t K,
+                                                                 uint32_t dst_stride) {
+    pdl_wait();
+    pdl_trigger();
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row = blockIdx.x * kQ6Warps + warp;
+    if (row >= N) return;
+    const uint32_t B = K >> 8, groups = K >> 4;
+    const uint4* q = reinterpret_cast<const uint4*>(Q + (size_t)row * K);
+    const uint8_t* s = S + (size_t)row * B * kQ6ScaleBytes;
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+#pragma unroll 4
+    for (uint32_t gi = lane; gi < groups; gi += 32u) {
+        const uint4 w = ld_stream_u4(q + gi);
+        const uint32_t blk = gi >> 4, g = gi & 15u;
+        const uint8_t* rec = s + blk * kQ6ScaleBytes;
+        const int sc = (int)(int8_t)rec[g];
+        const float dw = h2f((uint16_t)(rec[16] | ((uint32_t)rec[17] << 8)));
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const uint4 a = *reinterpret_cast<const uint4*>(AQ + (size_t)m * K + 16u * gi);
+            int t = dp4a_ss(w.x, a.x, 0);
+            t = dp4a_ss(w.y, a.y, t);
+            t = dp4a_ss(w.z, a.z, t);
+            t = dp4a_ss(w.w, a.w, t);
+            const float da = *reinterpret_cast<const float*>(AB + ((size_t)m * B + blk) * kABBytes + 32);
+            acc[m] = fmaf(dw * da, (float)(sc * t), acc[m]);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const float v = warp_sum(acc[m]);
+        if (lane == 0) dst[(size_t)m * dst_stride + row] = v;
+    }
+}
+
+template <int M>
+static void launch_q6k_m(const LaunchArgs& a, uint32_t N, uint32_t K, uint32_t dst_stride) {
+    launch_pdl(gemv_q6k_kernel<M>, dim3((N + kQ6Warps - 1) / kQ6Warps), dim3(kQ6Warps * 32), 0, a.stream,
+               (const uint8_t*)a.ptr[0], (const uint8_t*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
+               (float*)a.ptr[4], N, K, dst_stride);
+}
+
+// ameva_mmvqb_q6_K: bindings 0 Q (int8 [N][K], the decoded weights), 1 S (18-byte records [N][K/256]), 2 AQ int8 [M][K],
+// 3 AB (48-byte Q8_K records [M][K/256]), 4 dst f32 [M][dst_stride]; push {M (1..8), N, K (% 256), dst_stride}
+AcResult launch_mmvqb_q6_K(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
+    if (N == 0 || K == 0 || (K & 255u) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t B = K >> 8;
+    if (a.range[0] < (uint64_t)N * K || a.range[1] < (uint64_t)N * B * kQ6ScaleBytes || a.range[2] < (uint64_t)M * K ||
+        a.range[3] < (uint64_t)M * B * kABBytes || a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if (((uintptr_t)a.ptr[0] | (uintptr_t)a.ptr[2]) & 15u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    switch (M) {
+        case 1: launch_q6k_m<1>(a, N, K, dst_stride); break;
+        case 2: launch_q6k_m<2>(a, N, K, dst_stride); break;
+        case 3: launch_q6k_m<3>(a, N, K, dst_stride); break;
+        case 4: launch_q6k_m<4>(a, N, K, dst_stride); break;
+        case 5: launch_q6k_m<5>(a, N, K, dst_stride); break;
+        case 6: launch_q6k_m<6>(a, N, K, dst_stride); break;
+        case 7: launch_q6k_m<7>(a, N, K, dst_stride); break;
+        default: launch_q6k_m<8>(a, N, K, dst_stride); break;
+    }
+    return check_launch();
+}
+
+}  // namespace amv

@@ -46,6 +46,7 @@ AcResult launch_gemv_f16(const LaunchArgs&);
 AcResult launch_flash_attn(const LaunchArgs&);
 AcResult launch_cpy(const LaunchArgs&);
 AcResult launch_unary(const LaunchArgs&);
+AcResult launch_mmvqb_q6_K(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
@@ -120,6 +121,7 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvq_q8_0", 5, 16, {256, 1, 1}, launch_mmvq_q8_0},
     {"ameva_mmvq_q8_0_dump", 6, 16, {256, 1, 1}, launch_mmvq_q8_0_dump},
     {"ameva_mmvqb_q4_K", 5, 16, {256, 1, 1}, launch_mmvqb_q4_K},
+    {"ameva_mmvqb_q6_K", 5, 16, {256, 1, 1}, launch_mmvqb_q6_K},
     {"ameva_mmvq_q4_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q4_0_ep},
     {"ameva_mmvq_q8_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q8_0_ep},
     {"ameva_mmvqb_q4_K_ep", 7, 20, {256, 1, 1}, launch_mmvqb_q4_K_ep},
@@ -199,6 +201,7 @@ bool codec_for(uint32_t type, Codec* c) {
         case 12: *c = {256, 144, 16, 128, 0, 16, 0}; return true;  // Q4_K: d, dmin, scales[12] @0, qs[128]@16
         case 6: *c = {32, 22, 2, 32, 0, 2, 1}; return true;      // Q5_0: d@0, qh[4]@2, qs[16]@6 -> Q8_0 regions
         case 20: *c = {32, 18, 2, 32, 0, 2, 2}; return true;     // IQ4_NL: d@0, qs[16]@2 -> Q8_0 regions
+        case 14: *c = {256, 210, 0, 256, 192, 18, 3}; return true;  // Q6_K: ql[128]@0, qh[64]@128, scales[16]@192, d@208
         default: return false;
     }
 }
@@ -210,8 +213,35 @@ bool codec_for(uint32_t type, Codec* c) {
 // 18 bytes per block on the device. The decode is inverted exactly when the tensor is read back.
 const int8_t kIq4nlValues[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 13, 25, 38, 53, 69, 89, 113};
 
-void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // 32 int8 of one ggml block
-    if (xcode == 1) {
+// Q6_K (xcode 3): the 6-bit weights of a block, q - 32, as 256 int8 in element order (element e has scale e / 16);
+// the 16 int8 sub-block scales and the fp16 d keep their bytes. 274 instead of 210 bytes per block on the device, in
+// exchange for a dot product that is four dp4a per 16 weights with nothing to unpack.
+void decode_q6_K(const uint8_t* blk, int8_t* out) {
+    const uint8_t *ql = blk, *qh = blk + 128;
+    for (int h = 0; h < 2; ++h, ql += 64, qh += 32, out += 128)
+        for (int l = 0; l < 32; ++l) {
+            out[l] = (int8_t)(((ql[l] & 0x0F) | (((qh[l] >> 0) & 3) << 4)) - 32);
+            out[l + 32] = (int8_t)(((ql[l + 32] & 0x0F) | (((qh[l] >> 2) & 3) << 4)) - 32);
+            out[l + 64] = (int8_t)(((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32);
+            out[l + 96] = (int8_t)(((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32);
+        }
+}
+void encode_q6_K(const int8_t* in, uint8_t* blk) {
+    uint8_t *ql = blk, *qh = blk + 128;
+    for (int h = 0; h < 2; ++h, ql += 64, qh += 32, in += 128)
+        for (int l = 0; l < 32; ++l) {
+            int q[4] = {in[l] + 32, in[l + 32] + 32, in[l + 64] + 32, in[l + 96] + 32};
+            for (int& v : q) v = v < 0 ? 0 : (v > 63 ? 63 : v);
+            ql[l] = (uint8_t)((q[0] & 0x0F) | ((q[2] & 0x0F) << 4));
+            ql[l + 32] = (uint8_t)((q[1] & 0x0F) | ((q[3] & 0x0F) << 4));
+            qh[l] = (uint8_t)((q[0] >> 4) | ((q[1] >> 4) << 2) | ((q[2] >> 4) << 4) | ((q[3] >> 4) << 6));
+        }
+}
+
+void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // the int8 weights of one ggml block
+    if (xcode == 3) {
+        decode_q6_K(blk, out);
+    } else if (xcode == 1) {
         uint32_t qh;
         memcpy(&qh, blk + 2, 4);
         const uint8_t* qs = blk + 6;
@@ -228,7 +258,11 @@ void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // 32 int
     }
 }
 void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inverse (values no block decodes to, as in
-    if (xcode == 1) {                                                   // regions never written: the nearest code)
+    if (xcode == 3) {                                                   // regions never written: the nearest code)
+        encode_q6_K(in, blk);
+        return;
+    }
+    if (xcode == 1) {
         uint32_t qh = 0;
         uint8_t* qs = blk + 6;
         for (int j = 0; j < 16; ++j) {
@@ -256,7 +290,7 @@ void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inv
 // The type whose kernels and device regions serve a weight type (itself, or Q8_0 for the decoded types); 0 = not built.
 extern "C" uint32_t ac_b200_device_type(uint32_t ggml_type) {
     switch (ggml_type) {
-        case 2: case 8: case 12: case 36: return ggml_type;
+        case 2: case 8: case 12: case 14: case 36: return ggml_type;
         case 6: case 20: return 8;
         default: return 0;
     }
@@ -281,8 +315,13 @@ extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, 
     *out_path = AC_B200_PATH_NONE;
     if (flags & ~(AC_B200_PLAN_EXACT | AC_B200_PLAN_HOST_LAUNCH | AC_B200_PLAN_PEERS | AC_B200_PLAN_WEIGHT_RANGE))
         return AC_ERR_INVALID_ARGUMENT;
-    const uint64_t blk = type == 2 || type == 8 ? 32 : type == 12 ? 256 : type == 36 ? 128 : 0;
+    const uint64_t blk = type == 2 || type == 8 ? 32 : (type == 12 || type == 14) ? 256 : type == 36 ? 128 : 0;
     if (!blk) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    if (type == 14) {   // Q6_K: one kernel, ameva_mmvqb_q6_K; more than 8 activation rows run in chunks of 8
+        if (M == 0 || N == 0 || K == 0 || K % blk) return AC_ERR_INVALID_SHAPE;
+        *out_path = AC_B200_PATH_GEMV;
+        return AC_SUCCESS;
+    }
     if (M == 0 || N == 0 || K == 0 || (K % blk) || N * K >= (1ull << 32) || M * (N > K ? N : K) >= (1ull << 32))
         return AC_ERR_INVALID_SHAPE;
     // (a weight tensor whose magnitudes fp16 does not hold comfortably stays on the integer kernels at every M)
@@ -388,6 +427,11 @@ extern "C" AcResult ac_b200_weight_exponent(uint32_t type, const void* ggml_bloc
             bound = 127.0f * d;
         } else if (type == 6) {
             bound = 16.0f * d;
+        } else if (type == 14) {   // |scale| <= 128, |q - 32| <= 32; d sits at byte 208 of the block
+            uint16_t hd;
+            memcpy(&hd, b + 208, 2);
+            const float dd = half_to_float(hd);
+            bound = 4096.0f * (dd < 0 ? -dd : dd);
         } else {
             float m = half_to_float(h1);
             bound = 945.0f * d + 63.0f * (m < 0 ? -m : m);

@@ -24,7 +24,19 @@ __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 
 // sixteen decoded weights of a Q5_0 / IQ4_NL block: `part` 0 = elements 0..15 (low nibbles), 1 = elements 16..31
 __device__ __forceinline__ uint4 decode_piece(uint32_t xcode, const uint8_t* blk, uint32_t part) {
     uint32_t w[4] = {0u, 0u, 0u, 0u};
-    if (xcode == 1u) {
+    if (xcode == 3u) {
+        // Q6_K: piece `part` (0..15) = elements 16 part .. 16 part + 15 of the block: half h = part / 8, quarter
+        // qr = (part % 8) / 2 (which nibble of which ql byte, which two bits of qh), l = 16 (part % 2) + j
+        const uint32_t h = part >> 3, qr = (part & 7u) >> 1, l0 = 16u * (part & 1u);
+        const uint8_t* ql = blk + 64u * h + l0 + ((qr & 1u) ? 32u : 0u);
+        const uint8_t* qh = blk + 128u + 32u * h + l0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t nib = qr >= 2u ? (ql[j] >> 4) : (ql[j] & 0x0Fu);
+            const int v = (int)(nib | (((qh[j] >> (2u * qr)) & 3u) << 4)) - 32;
+            w[j >> 2] |= (uint32_t)(v & 0xFF) << (8 * (j & 3));
+        }
+    } else if (xcode == 1u) {
         const uint16_t* h = reinterpret_cast<const uint16_t*>(blk + 2);
         const uint32_t qh = (h[0] | ((uint32_t)h[1] << 16)) >> (16u * part);
         const uint8_t* qs = blk + 6;
@@ -45,7 +57,7 @@ __device__ __forceinline__ uint4 decode_piece(uint32_t xcode, const uint8_t* blk
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-constexpr uint32_t kRepackTile = 256;   // blocks per CTA: 256 x 18, 34 or 144 bytes are whole 16-byte pieces
+constexpr uint32_t kRepackTile = 256;   // blocks per CTA: 256 x 18, 22, 34, 144 or 210 bytes are whole 16-byte pieces
 
 // One CTA moves kRepackTile consecutive blocks: the tile's bytes are loaded into shared memory with coalesced 16-byte
 // loads (a tile starts on a 16-byte boundary of the staging chunk), then every thread assembles 16-byte payload pieces
@@ -96,6 +108,7 @@ static bool repack_codec(uint32_t type, RepackCodec* c, uint32_t* blk) {
         case 12: *c = {144, 16, 128, 0, 16, 0}; *blk = 256; return true;  // Q4_K: d, dmin, scales[12] @0, qs[128]@16
         case 6: *c = {22, 2, 32, 0, 2, 1}; *blk = 32; return true;        // Q5_0: d@0, qh[4]@2, qs[16]@6, decoded
         case 20: *c = {18, 2, 32, 0, 2, 2}; *blk = 32; return true;       // IQ4_NL: d@0, qs[16]@2, decoded
+        case 14: *c = {210, 0, 256, 192, 18, 3}; *blk = 256; return true; // Q6_K: ql, qh decoded to 256 int8; scales[16] + d kept
         default: return false;
     }
 }
@@ -112,6 +125,7 @@ AcResult launch_repack(cudaStream_t stream, uint32_t type, const void* src, void
         return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     const uint64_t tiles = (nblk + kRepackTile - 1) / kRepackTile;
     if (tiles > 0x7fffffffull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
+    if (!ensure_dynamic_smem<repack_kernel>(kRepackTile * 210)) return AC_ERR_INVALID_WORK_GROUP_SIZE;   // (Q6_K tiles: 52.5 KB)
     repack_kernel<<<(unsigned)tiles, 256, kRepackTile * c.blk_bytes, stream>>>(
         (const uint8_t*)src, (uint8_t*)q_region + first * c.q_bytes, (uint8_t*)s_region + first * c.s_bytes, nblk, c);
     return check_launch();

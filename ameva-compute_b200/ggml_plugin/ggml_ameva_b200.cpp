@@ -95,14 +95,16 @@ AcContext* context() {          // created on first use (the loader probes the r
 enum ggml_type dev_type(enum ggml_type t) { return (t == GGML_TYPE_Q5_0 || t == GGML_TYPE_IQ4_NL) ? GGML_TYPE_Q8_0 : t; }
 bool repacked_type(enum ggml_type t) {
     t = dev_type(t);
-    return t == GGML_TYPE_Q4_0 || t == GGML_TYPE_Q8_0 || t == GGML_TYPE_Q4_K;
+    return t == GGML_TYPE_Q4_0 || t == GGML_TYPE_Q8_0 || t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K;
 }
-uint32_t block_elems(enum ggml_type t) { return t == GGML_TYPE_Q4_K ? 256u : 32u; }
+// activations quantized per 256 (Q8_K records) and the ameva_mmvqb kernel family
+bool per_256(enum ggml_type t) { return t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K; }
+uint32_t block_elems(enum ggml_type t) { return per_256(t) ? 256u : 32u; }
 uint32_t payload_bytes(enum ggml_type t) {   // of the device regions
     t = dev_type(t);
-    return t == GGML_TYPE_Q4_0 ? 16u : (t == GGML_TYPE_Q8_0 ? 32u : 128u);
+    return t == GGML_TYPE_Q4_0 ? 16u : (t == GGML_TYPE_Q8_0 ? 32u : (t == GGML_TYPE_Q6_K ? 256u : 128u));
 }
-uint32_t scale_bytes(enum ggml_type t) { return t == GGML_TYPE_Q4_K ? 16u : 2u; }
+uint32_t scale_bytes(enum ggml_type t) { return t == GGML_TYPE_Q4_K ? 16u : (t == GGML_TYPE_Q6_K ? 18u : 2u); }
 
 // A weight this backend keeps in its device layout: a supported quantized type, plain 2-D, contiguous, not a view.
 bool is_repacked_weight(const ggml_tensor* t) {
@@ -700,11 +702,13 @@ bool dispatch(Recorder& r, const char* name, const AcBufferBinding* b, uint32_t 
     return ac_runtime_batch_dispatch_bindings(r.batch, k, b, nb, push, push_bytes, grid) == AC_SUCCESS;
 }
 
-const char* type_name(enum ggml_type t) { return t == GGML_TYPE_Q4_0 ? "q4_0" : (t == GGML_TYPE_Q8_0 ? "q8_0" : "q4_K"); }
+const char* type_name(enum ggml_type t) {
+    return t == GGML_TYPE_Q4_0 ? "q4_0" : (t == GGML_TYPE_Q8_0 ? "q8_0" : (t == GGML_TYPE_Q6_K ? "q6_K" : "q4_K"));
+}
 
 // activation quantization into the scratch, unless the same rows are there already
 bool record_quantize(Recorder& r, const ggml_tensor* x, enum ggml_type wtype, uint32_t M, uint32_t K, bool tc) {
-    const bool q4k = wtype == GGML_TYPE_Q4_K;
+    const bool q4k = per_256(wtype);
     const int scheme = (q4k ? 1 : 0) + (tc ? 2 : 0);
     if (r.q_data == x->data && r.q_M == M && r.q_K == K && (r.q_scheme == scheme || r.q_scheme == scheme + 2)) return true;
     const uint64_t ad_need = q4k ? (uint64_t)M * (K / 256) * 48u : (uint64_t)M * (K / 32) * 4u;
@@ -734,6 +738,7 @@ struct Epilogue {
 Epilogue find_epilogue(const ggml_tensor* n0, const ggml_tensor* n1) {
     Epilogue f;
     if (!n1 || n0->op != GGML_OP_MUL_MAT || n0->src[1]->ne[1] != 1) return f;
+    if (n0->src[0]->type == GGML_TYPE_Q6_K) return f;   // (its one kernel has no fused consumer)
     const int64_t N = n0->ne[0];
     if (n1->op != GGML_OP_ADD && n1->op != GGML_OP_GLU) return f;
     if (node_reason(n1)) return f;
@@ -759,7 +764,7 @@ bool record_mul_mat(Recorder& r, const ggml_tensor* node, const Epilogue& ep) {
     if (mul_mat_reason(node, &w, &path)) return false;
     const ggml_tensor* x = node->src[1];
     const uint32_t K = w.K, N = w.N, M = (uint32_t)x->ne[1];
-    const bool q4k = w.type == GGML_TYPE_Q4_K;
+    const bool q4k = per_256(w.type);
     const char* tname = type_name(w.type);
     const uint64_t ad_need = q4k ? (uint64_t)M * (K / 256) * 48u : (uint64_t)M * (K / 32) * 4u;
     const AcBufferBinding Q = bind(w.buf->buf, w.q_off, w.q_range), S = bind(w.buf->buf, w.s_off, w.s_range);
@@ -827,7 +832,7 @@ bool record_group(Recorder& r, const ggml_tensor* const* nodes, uint32_t count) 
     WeightRef w[4];
     for (uint32_t j = 0; j < count; ++j)
         if (mul_mat_reason(nodes[j], &w[j])) return false;
-    const bool q4k = w[0].type == GGML_TYPE_Q4_K;
+    const bool q4k = per_256(w[0].type);
     AcBufferBinding b[13];
     uint32_t push[7] = {w[0].K, 0, count, 0, 0, 0, 0};
     for (uint32_t j = 0; j < 4; ++j) {
@@ -1037,7 +1042,7 @@ bool record_norm_quantize(Recorder& r, const ggml_tensor* node, const ggml_tenso
     if (mul_mat_reason(consumer, &w, &path)) return false;
     const uint32_t M = (uint32_t)n_rows(out), K = (uint32_t)out->ne[0];
     if (K != w.K || K > 32768u || (uint64_t)n_rows(out) != (uint64_t)out->ne[1] || !ggml_is_contiguous(node->src[0])) return false;
-    const bool q4k = w.type == GGML_TYPE_Q4_K, tc = path == AC_B200_PATH_GEMM_TC;
+    const bool q4k = per_256(w.type), tc = path == AC_B200_PATH_GEMM_TC;
     if (path == AC_B200_PATH_GEMV && M > 8) return false;   // the exact chunked path quantizes per chunk layout as usual
     const ggml_tensor* wt = nullptr;
     if (fused_mul) wt = fused_mul->src[0] == node ? fused_mul->src[1] : fused_mul->src[0];
@@ -1108,7 +1113,7 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
         const ggml_tensor *w = node->src[0], *x = node->src[1];
         const size_t K = (size_t)w->ne[0], M = (size_t)x->ne[1];
         aq_need = std::max(aq_need, M * K);
-        ad_need = std::max(ad_need, w->type == GGML_TYPE_Q4_K ? M * (K / 256) * 48u : M * (K / 32) * 4u);
+        ad_need = std::max(ad_need, per_256(w->type) ? M * (K / 256) * 48u : M * (K / 32) * 4u);
         if (M > 8 && K % 256 == 0) {
             ah_need = std::max(ah_need, M * K * 2);
             ae_need = std::max(ae_need, M * 4);
@@ -1391,7 +1396,7 @@ const char* ggml_backend_ameva_abi_check(void) {
             enum ggml_type type;
             const char* name;
         } kTypes[] = {{GGML_TYPE_F32, "f32"}, {GGML_TYPE_Q4_0, "q4_0"}, {GGML_TYPE_Q8_0, "q8_0"}, {GGML_TYPE_Q4_K, "q4_K"},
-                      {GGML_TYPE_F16, "f16"}, {GGML_TYPE_I32, "i32"}, {GGML_TYPE_I64, "i64"}};
+                      {GGML_TYPE_F16, "f16"}, {GGML_TYPE_I32, "i32"}, {GGML_TYPE_I64, "i64"}, {GGML_TYPE_Q6_K, "q6_K"}};
         for (const auto& o : kOps)
             if (!what && strcmp(ggml_op_name(o.op), o.name) != 0) what = "enum ggml_op";
         for (const auto& t : kTypes)

@@ -21,10 +21,15 @@ GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_I2_S = 2, 8, 12, 36
 # kept on the device as Q8_0 regions: d * (q5 - 16) and d * kvalues_iq4nl[q4] are d * int8 (registry.cu, decode_block)
 GGML_TYPE_Q5_0, GGML_TYPE_IQ4_NL = 6, 20
 DEVICE_TYPE = {GGML_TYPE_Q5_0: GGML_TYPE_Q8_0, GGML_TYPE_IQ4_NL: GGML_TYPE_Q8_0}
-TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s"}
-BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128}
-Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128}   # payload bytes per block
-S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16}      # scale bytes per block
+# Q6_K: the 6-bit weights decoded to int8 at upload (256 payload bytes per block), scales[16] + d kept (18 bytes); one
+# kernel, ameva_mmvqb_q6_K, over Q8_K activations; more than 8 activation rows run in chunks of 8 (gemv_q6k.cu)
+GGML_TYPE_Q6_K = 14
+TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s",
+              GGML_TYPE_Q6_K: "q6_K"}
+BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128, GGML_TYPE_Q6_K: 256}
+Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128, GGML_TYPE_Q6_K: 256}   # payload bytes per block
+S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16, GGML_TYPE_Q6_K: 18}      # scale bytes per block
+PER_256 = (GGML_TYPE_Q4_K, GGML_TYPE_Q6_K)   # types whose activations are quantized per 256 (Q8_K records)
 FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in shared memory
 
 
@@ -215,10 +220,12 @@ class MulMat:
         if why:
             raise MulMatUnsupported(why)
         self.type, self.N, self.K, self.max_m = w.type, self.view.rows, w.K, max_m
+        if w.type == GGML_TYPE_Q6_K and dump_block_sums:
+            raise MulMatUnsupported("no kernel writes the per-block sums of a Q6_K product")
         self.round_mode, self.q8k_mode, self.dump = round_mode, q8k_mode, dump_block_sums
         # exact = keep every M on the dp4a kernels (exact per-block int32 sums); otherwise M > 8 runs on tensor cores,
         # unless the weights' magnitudes are outside what their fp16 form holds comfortably
-        self.exact = exact or dump_block_sums or not w.fp16_ok
+        self.exact = exact or dump_block_sums or not w.fp16_ok or w.type == GGML_TYPE_Q6_K   # (Q6_K has no GEMM form)
         # the GEMM stages weights and scales with TMA: whole 128-byte operand rows, whole 16-byte scale groups per row
         self.tc_ok = self.K % (128 if self.type == GGML_TYPE_I2_S else 256) == 0
         self.qbind, self.sbind = _bindings_for(self.view)
@@ -226,7 +233,7 @@ class MulMat:
         self.aq = ctx.buffer(max_m * K)
         if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
             self.ad = ctx.buffer(max_m * (K // 32) * 4)
-        elif self.type == GGML_TYPE_Q4_K:
+        elif self.type in PER_256:
             self.ad = ctx.buffer(max_m * (K // 256) * AB_BYTES)
         else:
             self.ad = ctx.buffer(max_m * 8)
@@ -289,7 +296,7 @@ class MulMat:
                 binds = [(x, x_offset), self.aq, self.ad] + ([self.ah, self.ae] if use_tc else [])
                 batch.dispatch(ctx.kernel("ameva_quant_a8_f16" if use_tc else "ameva_quant_a8"), binds,
                                [M, K, K, self.round_mode], ((M * (K // 32) * 8 + 255) // 256, 1, 1))
-            elif t == GGML_TYPE_Q4_K:
+            elif t in PER_256:
                 binds = [(x, x_offset), self.aq, self.ad] + ([self.ah, self.ae] if use_tc else [])
                 batch.dispatch(ctx.kernel("ameva_quant_a8b_f16" if use_tc else "ameva_quant_a8b"), binds,
                                [M, K, K, self.q8k_mode], ((M * (K // 256) * 32 + 255) // 256, 1, 1))
@@ -308,7 +315,7 @@ class MulMat:
             raise MulMatUnsupported("at most 7 peers")
         # The shared-memory-streamed GEMV carries the peer exchange for every scaled type, so it always runs with peers.
         want_streamed = self.streamed if self.streamed is not None else (self.streamed_pays(M) and epilogue is None)
-        streamed = (not use_tc and M <= GEMV_MAX_M and t != GGML_TYPE_I2_S and K % 256 == 0 and not self.dump
+        streamed = (not use_tc and M <= GEMV_MAX_M and t not in (GGML_TYPE_I2_S, GGML_TYPE_Q6_K) and K % 256 == 0 and not self.dump
                     and not self.exact and (want_streamed or bool(peers)))
         if peers and not (use_tc and t != GGML_TYPE_I2_S) and not streamed:
             raise MulMatUnsupported("the fused peer exchange is built for the tensor-core GEMM of the scaled types and "
@@ -332,7 +339,7 @@ class MulMat:
                                [self.qbind, self.sbind, self.ah, (dst, dst_offset), self.ae],
                                [M, N, K, dst_stride, self.gemm_flags], grid)
             return
-        if epilogue is not None and (M != 1 or t == GGML_TYPE_I2_S or self.dump or peers):
+        if epilogue is not None and (M != 1 or t in (GGML_TYPE_I2_S, GGML_TYPE_Q6_K) or self.dump or peers):
             raise MulMatUnsupported("the fused epilogue is built for one activation row of a Q4_0 / Q8_0 / Q4_K product")
         use_mma = (t == GGML_TYPE_Q4_K and 1 <= M <= GEMV_MAX_M and mma_gemv_fits(M, K) and not self.dump and not peers
                    and epilogue is None and self.streamed is not True
@@ -362,10 +369,10 @@ class MulMat:
                 push = [K, N, int(np.float32(self.view.weight.scale).view(np.uint32)), 0, mc, dst_stride]
                 binds = [self.qbind, (self.aq, m0 * K), (dst, d_off), (self.ad, m0 * 8)]
             else:
-                fam = "ameva_mmvqb" if t == GGML_TYPE_Q4_K else "ameva_mmvq"
+                fam = "ameva_mmvqb" if t in PER_256 else "ameva_mmvq"
                 name = f"{fam}_{TYPE_NAMES[t]}" + ("_dump" if self.dump else "")
                 push = [mc, N, K, dst_stride]
-                per_row = (K // 32) * 4 if t != GGML_TYPE_Q4_K else (K // 256) * AB_BYTES
+                per_row = (K // 32) * 4 if t not in PER_256 else (K // 256) * AB_BYTES
                 binds = [self.qbind, self.sbind, (self.aq, m0 * K), (self.ad, m0 * per_row), (dst, d_off)]
                 if self.dump:
                     per_m = int(np.prod(self._sum_shape(1))) * 4
@@ -417,7 +424,7 @@ class MulMat:
         if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
             ad = self.ad.read(np.uint32, M * (K // 32)).reshape(M, K // 32)
             return q, (ad & 0xFFFF).astype(np.uint16), (ad >> 16).astype(np.uint16).view(np.int16)
-        if self.type == GGML_TYPE_Q4_K:
+        if self.type in PER_256:
             ab = self.ad.read(np.uint8, M * (K // 256) * AB_BYTES).reshape(M, K // 256, AB_BYTES)
             bsums = np.ascontiguousarray(ab[:, :, :32]).view(np.int16)
             d = np.ascontiguousarray(ab[:, :, 32:36]).view(np.float32)[..., 0]

@@ -76,3 +76,74 @@ def to_q8_0(ggml_type: int, blocks) -> np.ndarray:
 def dequantize(ggml_type: int, blocks) -> np.ndarray:
     d, q = decode(ggml_type, blocks)
     return (d.astype(np.float32)[:, None] * q.astype(np.float32)).reshape(-1)
+
+
+# ---- Q6_K --------------------------------------------------------------------------------------------------------------
+# ggml-common.h block_q6_K: ql[128] (low 4 bits), qh[64] (high 2 bits), scales[16] int8, d fp16 = 210 bytes per 256
+# weights; weight e = d * scales[e / 16] * (q6[e] - 32), elements in the order of ggml's dequantize_row_q6_K (pinned
+# against gguf-py's dequantizer in tests/test_oracle_golden.py). The dot product follows ggml_vec_dot_q6_K_q8_K's generic
+# branch: per block aux = sum_g scales[g] * sum_i (q6 - 32) * q8 (exact integers), sumf += (d6 * d8) * aux.
+Q6_K = 14
+BLOCK_BYTES[Q6_K] = 210
+
+
+def quantize_q6_K(w) -> np.ndarray:
+    """A valid packer (weights are inputs of the path): per 16 weights scale = amax / 31, d = the largest scale / 127."""
+    x = np.ascontiguousarray(w, np.float32).reshape(-1, 16, 16)           # [block][group][16]
+    gs = np.max(np.abs(x), axis=2) / np.float32(31.0)
+    d = (np.max(gs, axis=1) / np.float32(127.0)).astype(np.float16)
+    df = d.astype(np.float32)
+    sc = np.where(df[:, None] > 0, np.rint(gs / np.where(df > 0, df, 1.0)[:, None]), 0).clip(0, 127).astype(np.int8)
+    eff = df[:, None] * sc.astype(np.float32)
+    q = np.where(eff[:, :, None] > 0, np.rint(x / np.where(eff > 0, eff, 1.0)[:, :, None]), 0).clip(-32, 31).astype(np.int32) + 32
+    q = q.reshape(-1, 2, 4, 32)                                            # [block][half][quarter][l]
+    out = np.zeros((q.shape[0], 210), np.uint8)
+    for h in range(2):
+        q1, q2, q3, q4 = q[:, h, 0], q[:, h, 1], q[:, h, 2], q[:, h, 3]
+        out[:, 64 * h:64 * h + 32] = (q1 & 0x0F) | ((q3 & 0x0F) << 4)
+        out[:, 64 * h + 32:64 * h + 64] = (q2 & 0x0F) | ((q4 & 0x0F) << 4)
+        out[:, 128 + 32 * h:128 + 32 * h + 32] = (q1 >> 4) | ((q2 >> 4) << 2) | ((q3 >> 4) << 4) | ((q4 >> 4) << 6)
+    out[:, 192:208] = sc.view(np.uint8)
+    out[:, 208:210] = d.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
+
+
+def decode_q6_K(blocks):
+    """(d fp16 [n], scales int8 [n][16], q - 32 as int8 [n][256] in element order) of n blocks."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, 210)
+    ql, qh = b[:, :128].astype(np.int32), b[:, 128:192].astype(np.int32)
+    q = np.zeros((b.shape[0], 256), np.int32)
+    for h in range(2):
+        lo, hi, hh = ql[:, 64 * h:64 * h + 32], ql[:, 64 * h + 32:64 * h + 64], qh[:, 32 * h:32 * h + 32]
+        base = 128 * h
+        q[:, base:base + 32] = (lo & 0x0F) | (((hh >> 0) & 3) << 4)
+        q[:, base + 32:base + 64] = (hi & 0x0F) | (((hh >> 2) & 3) << 4)
+        q[:, base + 64:base + 96] = (lo >> 4) | (((hh >> 4) & 3) << 4)
+        q[:, base + 96:base + 128] = (hi >> 4) | (((hh >> 6) & 3) << 4)
+    d = b[:, 208:210].copy().view(np.float16).reshape(-1)
+    return d, b[:, 192:208].copy().view(np.int8), (q - 32).astype(np.int8)
+
+
+def dequantize_q6_K(blocks) -> np.ndarray:
+    d, sc, q = decode_q6_K(blocks)
+    scale = (d.astype(np.float32)[:, None] * sc.astype(np.float32))           # d * scales[g], rounded to fp32 as in ggml
+    return (np.repeat(scale, 16, axis=1) * q.astype(np.float32)).reshape(-1)
+
+
+def mul_mat_q6_K_q8_K(W, A, M: int, N: int, K: int) -> np.ndarray:
+    """W: Q6_K blocks [N][K/256]; A: Q8_K blocks [M][K/256] (292 bytes: fp32 d, 256 int8, 16 int16 sums) -> fp32 [M][N]."""
+    B = K // 256
+    d6, sc, q6 = decode_q6_K(W)
+    d6, sc, q6 = d6.reshape(N, B).astype(np.float32), sc.reshape(N, B, 16).astype(np.int64), q6.reshape(N, B, 16, 16).astype(np.int64)
+    a = np.ascontiguousarray(A, np.uint8).reshape(M, B, 292)
+    d8 = a[:, :, 0:4].copy().view(np.float32).reshape(M, B)
+    q8 = a[:, :, 4:260].copy().view(np.int8).reshape(M, B, 16, 16).astype(np.int64)
+    out = np.zeros((M, N), np.float32)
+    for m in range(M):
+        aux = np.einsum("nbg,nbgi,bgi->nb", sc, q6, q8[m])                   # exact integers
+        terms = ((d6 * d8[m][None, :]).astype(np.float32) * aux.astype(np.float32)).astype(np.float32)
+        acc = np.zeros(N, np.float32)
+        for b in range(B):                                                   # sumf += d * aux, block by block
+            acc = (acc + terms[:, b]).astype(np.float32)
+        out[m] = acc
+    return out

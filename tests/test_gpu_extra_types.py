@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from conftest import load_pkg
-from helpers import IQ4_NL, Q5_0, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+from helpers import IQ4_NL, Q5_0, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
 from oracle import extra_types
 
 pytestmark = pytest.mark.gpu
@@ -63,4 +63,44 @@ def test_mul_mat_on_the_q8_0_kernels(ctx, t, M, N, K):
     mm8.run(xb, dst8, M)
     assert np.array_equal(dst8.read(np.float32).reshape(M, N), got)
     for o in (mm, mm8, xb, dst, dst8, w, w8):
+        o.destroy()
+
+
+@pytest.mark.parametrize("N,K", [(96, 1024), (1000, 4096), (3, 256)])
+def test_q6_K_upload_decodes_to_int8_and_reads_back_the_uploaded_bytes(ctx, N, K):
+    blocks, _ = make_weights(Q6_K, N, K, N)
+    w = qmm.QuantWeight.from_ggml(ctx, Q6_K, blocks, N, K)
+    host = qmm.QuantWeight.from_ggml(ctx, Q6_K, blocks, N, K, host_repack=True)
+    try:
+        assert np.array_equal(w.to_ggml(), blocks) and np.array_equal(host.to_ggml(), blocks)
+        d, sc, q = extra_types.decode_q6_K(blocks)
+        nq = N * K
+        for wt in (w, host):
+            assert np.array_equal(wt.buf.read(np.int8, nq), q.reshape(-1))                      # q6 - 32 in element order
+            rec = wt.buf.read(np.uint8, N * (K // 256) * 18, wt.s_off).reshape(-1, 18)
+            assert np.array_equal(rec[:, :16].view(np.int8), sc) and np.array_equal(rec[:, 16:].copy().view(np.float16).reshape(-1), d)
+        if N > 2:
+            per_row = blocks.size // N
+            assert np.array_equal(w.to_ggml(1, N - 2), blocks[per_row:(N - 1) * per_row])
+    finally:
+        w.destroy()
+        host.destroy()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (1, 1000, 14336), (4, 512, 1024), (8, 130, 2048), (33, 768, 2048)])
+def test_q6_K_mul_mat(ctx, M, N, K):
+    """Q6_K x Q8_K on its own kernel (ameva_mmvqb_q6_K); more than 8 activation rows in chunks of 8. Against the numpy
+    restatement of ggml_vec_dot_q6_K_q8_K (exact integers, fp32 per block), normalised error <= 1e-3."""
+    blocks, scale = make_weights(Q6_K, N, K, M)
+    x = make_acts(M, K, M + 1)
+    w = qmm.QuantWeight.from_ggml(ctx, Q6_K, blocks, N, K)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    mm.run(xb, dst, M)
+    assert mm.path in ("mmvq", "mmvq-chunks")
+    want, _, _ = oracle_mul_mat(Q6_K, blocks, scale, x, N, K, want_sums=False)
+    assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
+    with pytest.raises(qmm.MulMatUnsupported):
+        qmm.MulMat(ctx, w, M, dump_block_sums=True)
+    for o in (mm, xb, dst, w):
         o.destroy()

@@ -174,3 +174,20 @@ def test_q5_0_and_iq4_nl_decode_equals_gguf_py():
         q8 = et.to_q8_0(t, blocks).reshape(-1, 34)
         assert np.array_equal(q8[:, 2:].view(np.int8), q) and np.array_equal(q8[:, :2].copy().view(np.float16).reshape(-1), d)
     assert np.array_equal(et.quantize_q5_0(w), quants.quantize(w, gguf.GGMLQuantizationType.Q5_0).reshape(-1))
+
+
+def test_q6_K_decode_equals_gguf_py():
+    """The decode the Q6_K device layout rests on (q6 - 32 as int8 in element order, scale e / 16) against gguf-py's
+    dequantizer, on packed weights and on random block bytes."""
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    from oracle import extra_types as et
+    rng = np.random.default_rng(12)
+    w = (rng.standard_normal((16, 512)) * 0.05).astype(np.float32)
+    w[0, :256] = 0.0
+    blocks = et.quantize_q6_K(w)
+    assert np.array_equal(et.dequantize_q6_K(blocks), quants.dequantize(blocks.reshape(16, -1), gguf.GGMLQuantizationType.Q6_K).reshape(-1))
+    assert np.max(np.abs(et.dequantize_q6_K(blocks).reshape(16, 512) - w)) <= 0.02 * np.max(np.abs(w))
+    raw = rng.integers(0, 256, (8, 210), dtype=np.uint8)
+    raw[:, 208], raw[:, 209] = 0, 0x1C           # a small positive fp16 d
+    assert np.array_equal(et.dequantize_q6_K(raw.reshape(-1)), quants.dequantize(raw, gguf.GGMLQuantizationType.Q6_K).reshape(-1))
