@@ -20,6 +20,26 @@ namespace amv {
 constexpr int kQ6Warps = 8;
 constexpr uint32_t kQ6ScaleBytes = 18;   // 16 int8 sub-block scales + fp16 d, as in the ggml block
 
+// one 16-weight group of a row against the M activation rows
+template <int M>
+__device__ __forceinline__ void group_dot(const uint4 w, uint32_t gi, const uint8_t* s, const int8_t* __restrict__ AQ,
+                                          const uint8_t* __restrict__ AB, uint32_t K, uint32_t B, float (&acc)[M]) {
+    const uint32_t blk = gi >> 4, g = gi & 15u;
+    const uint8_t* rec = s + blk * kQ6ScaleBytes;
+    const int sc = (int)(int8_t)rec[g];
+    const float dw = h2f((uint16_t)(rec[16] | ((uint32_t)rec[17] << 8)));
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const uint4 a = *reinterpret_cast<const uint4*>(AQ + (size_t)m * K + 16u * gi);
+        int t = dp4a_ss(w.x, a.x, 0);
+        t = dp4a_ss(w.y, a.y, t);
+        t = dp4a_ss(w.z, a.z, t);
+        t = dp4a_ss(w.w, a.w, t);
+        const float da = *reinterpret_cast<const float*>(AB + ((size_t)m * B + blk) * kABBytes + 32);
+        acc[m] = fmaf(dw * da, (float)(sc * t), acc[m]);
+    }
+}
+
 template <int M>
 __global__ void __launch_bounds__(kQ6Warps * 32) gemv_q6k_kernel(const uint8_t* __restrict__ Q, const uint8_t* __restrict__ S,
                                                                  const int8_t* __restrict__ AQ, const uint8_t* __restrict__ AB,
@@ -32,28 +52,36 @@ __global__ void __launch_bounds__(kQ6Warps * 32) gemv_q6k_kernel(const uint8_t* 
     if (row >= N) return;
     const uint32_t B = K >> 8, groups = K >> 4;
     const uint4* q = reinterpret_cast<const uint4*>(Q + (size_t)row * K);
-    const uint8_t* s = S + (size_t)row * B * kQ6ScaleBytes;
+    // the row's scale records go to shared memory first (2-byte loads, all in flight at once): inside the loop only the
+    // weight loads wait for HBM
+    extern __shared__ __align__(16) uint8_t q6_smem[];
+    uint8_t* s = q6_smem + (size_t)warp * B * kQ6ScaleBytes;
+    {
+        const uint16_t* src = reinterpret_cast<const uint16_t*>(S + (size_t)row * B * kQ6ScaleBytes);
+        uint16_t* dstp = reinterpret_cast<uint16_t*>(s);
+        for (uint32_t i = lane; i < B * (kQ6ScaleBytes / 2u); i += 32u) dstp[i] = __ldg(src + i);
+        __syncwarp();
+    }
     float acc[M];
 #pragma unroll
     for (int m = 0; m < M; ++m) acc[m] = 0.0f;
-#pragma unroll 4
-    for (uint32_t gi = lane; gi < groups; gi += 32u) {
-        const uint4 w = ld_stream_u4(q + gi);
-        const uint32_t blk = gi >> 4, g = gi & 15u;
-        const uint8_t* rec = s + blk * kQ6ScaleBytes;
-        const int sc = (int)(int8_t)rec[g];
-        const float dw = h2f((uint16_t)(rec[16] | ((uint32_t)rec[17] << 8)));
+    // eight, then four groups per lane and step: that many independent 16-byte loads in flight before the first is used
+    uint32_t gi = lane;
+    for (; gi + 32u * 7u < groups; gi += 32u * 8u) {
+        uint4 w[8];
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            const uint4 a = *reinterpret_cast<const uint4*>(AQ + (size_t)m * K + 16u * gi);
-            int t = dp4a_ss(w.x, a.x, 0);
-            t = dp4a_ss(w.y, a.y, t);
-            t = dp4a_ss(w.z, a.z, t);
-            t = dp4a_ss(w.w, a.w, t);
-            const float da = *reinterpret_cast<const float*>(AB + ((size_t)m * B + blk) * kABBytes + 32);
-            acc[m] = fmaf(dw * da, (float)(sc * t), acc[m]);
-        }
+        for (uint32_t u = 0; u < 8u; ++u) w[u] = ld_stream_u4(q + gi + 32u * u);
+#pragma unroll
+        for (uint32_t u = 0; u < 8u; ++u) group_dot<M>(w[u], gi + 32u * u, s, AQ, AB, K, B, acc);
     }
+    for (; gi + 32u * 3u < groups; gi += 32u * 4u) {
+        uint4 w[4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u) w[u] = ld_stream_u4(q + gi + 32u * u);
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u) group_dot<M>(w[u], gi + 32u * u, s, AQ, AB, K, B, acc);
+    }
+    for (; gi < groups; gi += 32u) group_dot<M>(ld_stream_u4(q + gi), gi, s, AQ, AB, K, B, acc);
 #pragma unroll
     for (int m = 0; m < M; ++m) {
         const float v = warp_sum(acc[m]);
@@ -63,17 +91,18 @@ __global__ void __launch_bounds__(kQ6Warps * 32) gemv_q6k_kernel(const uint8_t* 
 
 template <int M>
 static void launch_q6k_m(const LaunchArgs& a, uint32_t N, uint32_t K, uint32_t dst_stride) {
-    launch_pdl(gemv_q6k_kernel<M>, dim3((N + kQ6Warps - 1) / kQ6Warps), dim3(kQ6Warps * 32), 0, a.stream,
+    const size_t smem = (size_t)kQ6Warps * (K >> 8) * kQ6ScaleBytes;   // (K <= 65536: at most 36 KB)
+    launch_pdl(gemv_q6k_kernel<M>, dim3((N + kQ6Warps - 1) / kQ6Warps), dim3(kQ6Warps * 32), smem, a.stream,
                (const uint8_t*)a.ptr[0], (const uint8_t*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
                (float*)a.ptr[4], N, K, dst_stride);
 }
 
 // ameva_mmvqb_q6_K: bindings 0 Q (int8 [N][K], the decoded weights), 1 S (18-byte records [N][K/256]), 2 AQ int8 [M][K],
-// 3 AB (48-byte Q8_K records [M][K/256]), 4 dst f32 [M][dst_stride]; push {M (1..8), N, K (% 256), dst_stride}
+// 3 AB (48-byte Q8_K records [M][K/256]), 4 dst f32 [M][dst_stride]; push {M (1..8), N, K (% 256, <= 65536), dst_stride}
 AcResult launch_mmvqb_q6_K(const LaunchArgs& a) {
     const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
     if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
-    if (N == 0 || K == 0 || (K & 255u) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    if (N == 0 || K == 0 || (K & 255u) || K > 65536u || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
     const uint64_t B = K >> 8;
     if (a.range[0] < (uint64_t)N * K || a.range[1] < (uint64_t)N * B * kQ6ScaleBytes || a.range[2] < (uint64_t)M * K ||
         a.range[3] < (uint64_t)M * B * kABBytes || a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)

@@ -48,7 +48,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "tests"))
 
-Q4_0, Q8_0, Q4_K, I2_S = 2, 8, 12, 36
+Q4_0, Q8_0, Q4_K, I2_S, Q6_K = 2, 8, 12, 36, 14
 WORKLOADS = {
     # name: (type, M, N (a tuple: several matrices sharing the activation row, one launch), K, weight std, description)
     "cfg1": (Q4_0, 1, 4096, 4096, 0.02, "Q4_0 x Q8_0 decode GEMV 4096x4096 M=1"),
@@ -66,6 +66,8 @@ WORKLOADS = {
     "cfg5-up-m1": (Q4_K, 1, 28672, 8192, 0.01, "Q4_K x Q8_K 28672x8192 M=1"),
     "cfg5-down-m1": (Q4_K, 1, 8192, 28672, 0.01, "Q4_K x Q8_K 8192x28672 M=1"),
     "cfg5-up-m2048": (Q4_K, 2048, 28672, 8192, 0.01, "Q4_K x Q8_K 28672x8192 M=2048"),
+    # not a BASELINE configuration: the Q6_K tensors a Q4_K_M model file carries (ffn_down of a llama-3-8B layer)
+    "q6k-down-m1": (Q6_K, 1, 4096, 14336, 0.02, "Q6_K x Q8_K 4096x14336 M=1"),
 }
 DECODE_LINES = ("cfg1", "cfg3-qkv-m1", "cfg5-up-m1")      # the M = 1 half of the metric, in the default line
 SHARDED_LINES = ("cfg5-up-m2048", "cfg5-up-m1")           # the row-sharded shapes, in every line
@@ -91,7 +93,9 @@ def n_list(N):
 
 def weight_bytes(t, N, K):
     n = sum(n_list(N))
-    return {Q4_0: 18 * n * K // 32, Q8_0: 34 * n * K // 32, Q4_K: 144 * n * K // 256, I2_S: n * K // 4}[t]
+    # (Q6_K: the 274 bytes per block the device layout holds; the ggml block has 210)
+    return {Q4_0: 18 * n * K // 32, Q8_0: 34 * n * K // 32, Q4_K: 144 * n * K // 256, I2_S: n * K // 4,
+            Q6_K: 274 * n * K // 256}[t]
 
 
 def algorithmic_bytes(t, M, N, K):
@@ -176,6 +180,11 @@ def cpu_pass(t, blocks_list, scale, x, N, K, nthreads):
         aq = oracle.quantize_q8_K(x)
         for blocks, n in zip(blocks_list, n_list(N)):
             oracle.mul_mat_q4_K_q8_K(blocks, aq, M, n, K, False, nthreads)
+    elif t == Q6_K:   # (the numpy restatement: one thread)
+        from oracle import extra_types
+        aq = oracle.quantize_q8_K(x)
+        for blocks, n in zip(blocks_list, n_list(N)):
+            extra_types.mul_mat_q6_K_q8_K(blocks, aq, M, n, K)
     else:
         q, dq, _ = oracle.quantize_i8_token(x)
         for blocks, n in zip(blocks_list, n_list(N)):
