@@ -1,4 +1,5 @@
-// Q6_K x Q8_K mul_mat for up to 8 activation rows (token generation; more rows run in chunks of 8).
+// Q6_K x Q8_K (and, below, Q5_K x Q8_K) mul_mat for up to 8 activation rows (token generation; more rows run in chunks
+// of 8).
 //
 // A Q6_K weight is d * scale[e / 16] * (q6 - 32) with 6-bit q6 split over ql / qh (ggml-common.h block_q6_K: ql[128],
 // qh[64], scales[16] int8, d fp16: 210 bytes per 256 weights). The upload decodes q6 - 32 to int8 in element order and
@@ -117,6 +118,115 @@ AcResult launch_mmvqb_q6_K(const LaunchArgs& a) {
         case 6: launch_q6k_m<6>(a, N, K, dst_stride); break;
         case 7: launch_q6k_m<7>(a, N, K, dst_stride); break;
         default: launch_q6k_m<8>(a, N, K, dst_stride); break;
+    }
+    return check_launch();
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Q5_K x Q8_K, the same way: a Q5_K weight is d * sc[j] * q5 - dmin * m[j] for sub-block j = e / 32 (ggml-common.h
+// block_q5_K: d, dmin, scales[12] with packed 6-bit sc / m, qh[32], qs[128]: 176 bytes per 256 weights). The upload
+// decodes q5 (0..31) to bytes in element order and keeps the first 16 bytes of the block as the scale record (the
+// record of Q4_K), 272 bytes per block on the device.
+//   y[m][n] = sum_blocks d_a * ( d * sum_j sc[j] * sum_i q5 * q8  -  dmin * sum_j m[j] * bsum(j) )
+// as ggml_vec_dot_q5_K_q8_K (generic branch) forms it; a lane takes 16 weights (half a sub-block) with the Q8_K half-sum
+// of the same 16 activations for the min term.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int M>
+__device__ __forceinline__ void group_dot_q5(const uint4 w, uint32_t gi, const uint8_t* s, const int8_t* __restrict__ AQ,
+                                             const uint8_t* __restrict__ AB, uint32_t K, uint32_t B, float (&acc)[M]) {
+    const uint32_t blk = gi >> 4, g = gi & 15u, j = g >> 1;
+    const uint8_t* rec = s + blk * 16u;
+    const uint32_t hd = *reinterpret_cast<const uint32_t*>(rec);
+    const uint8_t* sm = rec + 4;
+    int sc, mn;   // get_scale_min_k4
+    if (j < 4u) {
+        sc = sm[j] & 63;
+        mn = sm[j + 4u] & 63;
+    } else {
+        sc = (sm[j + 4u] & 0x0F) | ((sm[j - 4u] >> 6) << 4);
+        mn = (sm[j + 4u] >> 4) | ((sm[j] >> 6) << 4);
+    }
+    const float dw = h2f((uint16_t)(hd & 0xFFFFu)), dmin = h2f((uint16_t)(hd >> 16));
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const uint4 a = *reinterpret_cast<const uint4*>(AQ + (size_t)m * K + 16u * gi);
+        int t = dp4a_ss(w.x, a.x, 0);
+        t = dp4a_ss(w.y, a.y, t);
+        t = dp4a_ss(w.z, a.z, t);
+        t = dp4a_ss(w.w, a.w, t);
+        const uint8_t* ab = AB + ((size_t)m * B + blk) * kABBytes;
+        const float da = *reinterpret_cast<const float*>(ab + 32);
+        const int bs = (int)reinterpret_cast<const int16_t*>(ab)[g];
+        acc[m] += (dw * da) * (float)(sc * t) - (dmin * da) * (float)(mn * bs);
+    }
+}
+
+template <int M>
+__global__ void __launch_bounds__(kQ6Warps * 32) gemv_q5k_kernel(const uint8_t* __restrict__ Q, const uint8_t* __restrict__ S,
+                                                                 const int8_t* __restrict__ AQ, const uint8_t* __restrict__ AB,
+                                                                 float* __restrict__ dst, uint32_t N, uint32_t K,
+                                                                 uint32_t dst_stride) {
+    pdl_wait();
+    pdl_trigger();
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row = blockIdx.x * kQ6Warps + warp;
+    if (row >= N) return;
+    const uint32_t B = K >> 8, groups = K >> 4;
+    const uint4* q = reinterpret_cast<const uint4*>(Q + (size_t)row * K);
+    extern __shared__ __align__(16) uint8_t q5_smem[];
+    uint8_t* s = q5_smem + (size_t)warp * B * 16u;
+    {   // the row's scale records (16 bytes per block), all loads in flight at once
+        const uint4* src = reinterpret_cast<const uint4*>(S + (size_t)row * B * 16u);
+        for (uint32_t i = lane; i < B; i += 32u) reinterpret_cast<uint4*>(s)[i] = __ldg(src + i);
+        __syncwarp();
+    }
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+    uint32_t gi = lane;
+    for (; gi + 32u * 3u < groups; gi += 32u * 4u) {
+        uint4 w[4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u) w[u] = ld_stream_u4(q + gi + 32u * u);
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u) group_dot_q5<M>(w[u], gi + 32u * u, s, AQ, AB, K, B, acc);
+    }
+    for (; gi < groups; gi += 32u) group_dot_q5<M>(ld_stream_u4(q + gi), gi, s, AQ, AB, K, B, acc);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const float v = warp_sum(acc[m]);
+        if (lane == 0) dst[(size_t)m * dst_stride + row] = v;
+    }
+}
+
+template <int M>
+static void launch_q5k_m(const LaunchArgs& a, uint32_t N, uint32_t K, uint32_t dst_stride) {
+    const size_t smem = (size_t)kQ6Warps * (K >> 8) * 16u;
+    launch_pdl(gemv_q5k_kernel<M>, dim3((N + kQ6Warps - 1) / kQ6Warps), dim3(kQ6Warps * 32), smem, a.stream,
+               (const uint8_t*)a.ptr[0], (const uint8_t*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
+               (float*)a.ptr[4], N, K, dst_stride);
+}
+
+// ameva_mmvqb_q5_K: bindings 0 Q (bytes [N][K], q5 decoded at upload), 1 S (16-byte records [N][K/256]: d, dmin, packed
+// scales), 2 AQ int8 [M][K], 3 AB (48-byte Q8_K records), 4 dst f32; push {M (1..8), N, K (% 256, <= 65536), dst_stride}
+AcResult launch_mmvqb_q5_K(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
+    if (N == 0 || K == 0 || (K & 255u) || K > 65536u || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t B = K >> 8;
+    if (a.range[0] < (uint64_t)N * K || a.range[1] < (uint64_t)N * B * 16u || a.range[2] < (uint64_t)M * K ||
+        a.range[3] < (uint64_t)M * B * kABBytes || a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if (((uintptr_t)a.ptr[0] | (uintptr_t)a.ptr[1] | (uintptr_t)a.ptr[2]) & 15u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    switch (M) {
+        case 1: launch_q5k_m<1>(a, N, K, dst_stride); break;
+        case 2: launch_q5k_m<2>(a, N, K, dst_stride); break;
+        case 3: launch_q5k_m<3>(a, N, K, dst_stride); break;
+        case 4: launch_q5k_m<4>(a, N, K, dst_stride); break;
+        case 5: launch_q5k_m<5>(a, N, K, dst_stride); break;
+        case 6: launch_q5k_m<6>(a, N, K, dst_stride); break;
+        case 7: launch_q5k_m<7>(a, N, K, dst_stride); break;
+        default: launch_q5k_m<8>(a, N, K, dst_stride); break;
     }
     return check_launch();
 }

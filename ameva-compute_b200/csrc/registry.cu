@@ -47,6 +47,7 @@ AcResult launch_flash_attn(const LaunchArgs&);
 AcResult launch_cpy(const LaunchArgs&);
 AcResult launch_unary(const LaunchArgs&);
 AcResult launch_mmvqb_q6_K(const LaunchArgs&);
+AcResult launch_mmvqb_q5_K(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
@@ -122,6 +123,7 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvq_q8_0_dump", 6, 16, {256, 1, 1}, launch_mmvq_q8_0_dump},
     {"ameva_mmvqb_q4_K", 5, 16, {256, 1, 1}, launch_mmvqb_q4_K},
     {"ameva_mmvqb_q6_K", 5, 16, {256, 1, 1}, launch_mmvqb_q6_K},
+    {"ameva_mmvqb_q5_K", 5, 16, {256, 1, 1}, launch_mmvqb_q5_K},
     {"ameva_mmvq_q4_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q4_0_ep},
     {"ameva_mmvq_q8_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q8_0_ep},
     {"ameva_mmvqb_q4_K_ep", 7, 20, {256, 1, 1}, launch_mmvqb_q4_K_ep},
@@ -202,6 +204,7 @@ bool codec_for(uint32_t type, Codec* c) {
         case 6: *c = {32, 22, 2, 32, 0, 2, 1}; return true;      // Q5_0: d@0, qh[4]@2, qs[16]@6 -> Q8_0 regions
         case 20: *c = {32, 18, 2, 32, 0, 2, 2}; return true;     // IQ4_NL: d@0, qs[16]@2 -> Q8_0 regions
         case 14: *c = {256, 210, 0, 256, 192, 18, 3}; return true;  // Q6_K: ql[128]@0, qh[64]@128, scales[16]@192, d@208
+        case 13: *c = {256, 176, 16, 256, 0, 16, 4}; return true;   // Q5_K: d, dmin, scales[12] @0, qh[32]@16, qs[128]@48
         default: return false;
     }
 }
@@ -238,8 +241,33 @@ void encode_q6_K(const int8_t* in, uint8_t* blk) {
         }
 }
 
+// Q5_K (xcode 4): the 5-bit weights q5 (0..31) as 256 bytes in element order (element e belongs to sub-block e / 32);
+// the block's first 16 bytes (d, dmin, the packed 6-bit scales and mins) are its scale record, as for Q4_K.
+void decode_q5_K(const uint8_t* blk, int8_t* out) {
+    const uint8_t *qh = blk + 16, *qs = blk + 48;
+    for (int j = 0; j < 4; ++j, qs += 32, out += 64)
+        for (int l = 0; l < 32; ++l) {
+            out[l] = (int8_t)((qs[l] & 0x0F) + (((qh[l] >> (2 * j)) & 1) << 4));
+            out[l + 32] = (int8_t)((qs[l] >> 4) + (((qh[l] >> (2 * j + 1)) & 1) << 4));
+        }
+}
+void encode_q5_K(const int8_t* in, uint8_t* blk) {
+    uint8_t *qh = blk + 16, *qs = blk + 48;
+    memset(qh, 0, 32);
+    for (int j = 0; j < 4; ++j, qs += 32, in += 64)
+        for (int l = 0; l < 32; ++l) {
+            int a = in[l], b = in[l + 32];
+            a = a < 0 ? 0 : (a > 31 ? 31 : a);
+            b = b < 0 ? 0 : (b > 31 ? 31 : b);
+            qs[l] = (uint8_t)((a & 0x0F) | ((b & 0x0F) << 4));
+            qh[l] |= (uint8_t)(((a >> 4) << (2 * j)) | ((b >> 4) << (2 * j + 1)));
+        }
+}
+
 void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // the int8 weights of one ggml block
-    if (xcode == 3) {
+    if (xcode == 4) {
+        decode_q5_K(blk, out);
+    } else if (xcode == 3) {
         decode_q6_K(blk, out);
     } else if (xcode == 1) {
         uint32_t qh;
@@ -260,6 +288,10 @@ void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // the in
 void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inverse (values no block decodes to, as in
     if (xcode == 3) {                                                   // regions never written: the nearest code)
         encode_q6_K(in, blk);
+        return;
+    }
+    if (xcode == 4) {
+        encode_q5_K(in, blk);
         return;
     }
     if (xcode == 1) {
@@ -290,7 +322,7 @@ void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inv
 // The type whose kernels and device regions serve a weight type (itself, or Q8_0 for the decoded types); 0 = not built.
 extern "C" uint32_t ac_b200_device_type(uint32_t ggml_type) {
     switch (ggml_type) {
-        case 2: case 8: case 12: case 14: case 36: return ggml_type;
+        case 2: case 8: case 12: case 13: case 14: case 36: return ggml_type;
         case 6: case 20: return 8;
         default: return 0;
     }
@@ -315,9 +347,9 @@ extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, 
     *out_path = AC_B200_PATH_NONE;
     if (flags & ~(AC_B200_PLAN_EXACT | AC_B200_PLAN_HOST_LAUNCH | AC_B200_PLAN_PEERS | AC_B200_PLAN_WEIGHT_RANGE))
         return AC_ERR_INVALID_ARGUMENT;
-    const uint64_t blk = type == 2 || type == 8 ? 32 : (type == 12 || type == 14) ? 256 : type == 36 ? 128 : 0;
+    const uint64_t blk = type == 2 || type == 8 ? 32 : (type == 12 || type == 13 || type == 14) ? 256 : type == 36 ? 128 : 0;
     if (!blk) return AC_ERR_FEATURE_NOT_SUPPORTED;
-    if (type == 14) {   // Q6_K: one kernel, ameva_mmvqb_q6_K; more than 8 activation rows run in chunks of 8
+    if (type == 14 || type == 13) {   // Q6_K, Q5_K: one kernel each (ameva_mmvqb_q6_K / _q5_K); more than 8 rows in chunks of 8
         if (M == 0 || N == 0 || K == 0 || K % blk) return AC_ERR_INVALID_SHAPE;
         *out_path = AC_B200_PATH_GEMV;
         return AC_SUCCESS;
@@ -427,6 +459,9 @@ extern "C" AcResult ac_b200_weight_exponent(uint32_t type, const void* ggml_bloc
             bound = 127.0f * d;
         } else if (type == 6) {
             bound = 16.0f * d;
+        } else if (type == 13) {   // 6-bit scales and mins, 5-bit weights
+            const float m = half_to_float(h1);
+            bound = 1953.0f * d + 63.0f * (m < 0 ? -m : m);
         } else if (type == 14) {   // |scale| <= 128, |q - 32| <= 32; d sits at byte 208 of the block
             uint16_t hd;
             memcpy(&hd, b + 208, 2);

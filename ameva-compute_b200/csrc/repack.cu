@@ -24,7 +24,19 @@ __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 
 // sixteen decoded weights of a Q5_0 / IQ4_NL block: `part` 0 = elements 0..15 (low nibbles), 1 = elements 16..31
 __device__ __forceinline__ uint4 decode_piece(uint32_t xcode, const uint8_t* blk, uint32_t part) {
     uint32_t w[4] = {0u, 0u, 0u, 0u};
-    if (xcode == 3u) {
+    if (xcode == 4u) {
+        // Q5_K: piece `part` (0..15) = elements 16 part .. 16 part + 15: j = part / 4 (64 elements), half = (part / 2) % 2
+        // (low or high nibble), l = 16 (part % 2) + i
+        const uint32_t j = part >> 2, half = (part >> 1) & 1u, l0 = 16u * (part & 1u);
+        const uint8_t* qs = blk + 48u + 32u * j + l0;
+        const uint8_t* qh = blk + 16u + l0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t nib = half ? (qs[i] >> 4) : (qs[i] & 0x0Fu);
+            const uint32_t v = nib | (((qh[i] >> (2u * j + half)) & 1u) << 4);
+            w[i >> 2] |= v << (8 * (i & 3));
+        }
+    } else if (xcode == 3u) {
         // Q6_K: piece `part` (0..15) = elements 16 part .. 16 part + 15 of the block: half h = part / 8, quarter
         // qr = (part % 8) / 2 (which nibble of which ql byte, which two bits of qh), l = 16 (part % 2) + j
         const uint32_t h = part >> 3, qr = (part & 7u) >> 1, l0 = 16u * (part & 1u);
@@ -109,6 +121,7 @@ static bool repack_codec(uint32_t type, RepackCodec* c, uint32_t* blk) {
         case 6: *c = {22, 2, 32, 0, 2, 1}; *blk = 32; return true;        // Q5_0: d@0, qh[4]@2, qs[16]@6, decoded
         case 20: *c = {18, 2, 32, 0, 2, 2}; *blk = 32; return true;       // IQ4_NL: d@0, qs[16]@2, decoded
         case 14: *c = {210, 0, 256, 192, 18, 3}; *blk = 256; return true; // Q6_K: ql, qh decoded to 256 int8; scales[16] + d kept
+        case 13: *c = {176, 16, 256, 0, 16, 4}; *blk = 256; return true;  // Q5_K: qh, qs decoded to 256 bytes; d, dmin, scales kept
         default: return false;
     }
 }

@@ -24,12 +24,17 @@ DEVICE_TYPE = {GGML_TYPE_Q5_0: GGML_TYPE_Q8_0, GGML_TYPE_IQ4_NL: GGML_TYPE_Q8_0}
 # Q6_K: the 6-bit weights decoded to int8 at upload (256 payload bytes per block), scales[16] + d kept (18 bytes); one
 # kernel, ameva_mmvqb_q6_K, over Q8_K activations; more than 8 activation rows run in chunks of 8 (gemv_q6k.cu)
 GGML_TYPE_Q6_K = 14
+# Q5_K likewise: q5 decoded to bytes (256 per block), the block's first 16 bytes (d, dmin, packed scales) kept as the
+# scale record; ameva_mmvqb_q5_K
+GGML_TYPE_Q5_K = 13
+BYTE_DECODED = (GGML_TYPE_Q6_K, GGML_TYPE_Q5_K)   # one GEMV kernel each, no tensor-core form, no fused variants
 TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s",
-              GGML_TYPE_Q6_K: "q6_K"}
-BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128, GGML_TYPE_Q6_K: 256}
-Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128, GGML_TYPE_Q6_K: 256}   # payload bytes per block
-S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16, GGML_TYPE_Q6_K: 18}      # scale bytes per block
-PER_256 = (GGML_TYPE_Q4_K, GGML_TYPE_Q6_K)   # types whose activations are quantized per 256 (Q8_K records)
+              GGML_TYPE_Q6_K: "q6_K", GGML_TYPE_Q5_K: "q5_K"}
+BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128, GGML_TYPE_Q6_K: 256,
+         GGML_TYPE_Q5_K: 256}
+Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128, GGML_TYPE_Q6_K: 256, GGML_TYPE_Q5_K: 256}   # payload bytes per block
+S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16, GGML_TYPE_Q6_K: 18, GGML_TYPE_Q5_K: 16}       # scale bytes per block
+PER_256 = (GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_Q5_K)   # types whose activations are quantized per 256 (Q8_K records)
 FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in shared memory
 
 
@@ -220,12 +225,12 @@ class MulMat:
         if why:
             raise MulMatUnsupported(why)
         self.type, self.N, self.K, self.max_m = w.type, self.view.rows, w.K, max_m
-        if w.type == GGML_TYPE_Q6_K and dump_block_sums:
-            raise MulMatUnsupported("no kernel writes the per-block sums of a Q6_K product")
+        if w.type in BYTE_DECODED and dump_block_sums:
+            raise MulMatUnsupported("no kernel writes the per-block sums of a Q6_K / Q5_K product")
         self.round_mode, self.q8k_mode, self.dump = round_mode, q8k_mode, dump_block_sums
         # exact = keep every M on the dp4a kernels (exact per-block int32 sums); otherwise M > 8 runs on tensor cores,
         # unless the weights' magnitudes are outside what their fp16 form holds comfortably
-        self.exact = exact or dump_block_sums or not w.fp16_ok or w.type == GGML_TYPE_Q6_K   # (Q6_K has no GEMM form)
+        self.exact = exact or dump_block_sums or not w.fp16_ok or w.type in BYTE_DECODED   # (no GEMM form)
         # the GEMM stages weights and scales with TMA: whole 128-byte operand rows, whole 16-byte scale groups per row
         self.tc_ok = self.K % (128 if self.type == GGML_TYPE_I2_S else 256) == 0
         self.qbind, self.sbind = _bindings_for(self.view)
@@ -315,7 +320,7 @@ class MulMat:
             raise MulMatUnsupported("at most 7 peers")
         # The shared-memory-streamed GEMV carries the peer exchange for every scaled type, so it always runs with peers.
         want_streamed = self.streamed if self.streamed is not None else (self.streamed_pays(M) and epilogue is None)
-        streamed = (not use_tc and M <= GEMV_MAX_M and t not in (GGML_TYPE_I2_S, GGML_TYPE_Q6_K) and K % 256 == 0 and not self.dump
+        streamed = (not use_tc and M <= GEMV_MAX_M and t != GGML_TYPE_I2_S and t not in BYTE_DECODED and K % 256 == 0 and not self.dump
                     and not self.exact and (want_streamed or bool(peers)))
         if peers and not (use_tc and t != GGML_TYPE_I2_S) and not streamed:
             raise MulMatUnsupported("the fused peer exchange is built for the tensor-core GEMM of the scaled types and "
@@ -339,7 +344,7 @@ class MulMat:
                                [self.qbind, self.sbind, self.ah, (dst, dst_offset), self.ae],
                                [M, N, K, dst_stride, self.gemm_flags], grid)
             return
-        if epilogue is not None and (M != 1 or t in (GGML_TYPE_I2_S, GGML_TYPE_Q6_K) or self.dump or peers):
+        if epilogue is not None and (M != 1 or t == GGML_TYPE_I2_S or t in BYTE_DECODED or self.dump or peers):
             raise MulMatUnsupported("the fused epilogue is built for one activation row of a Q4_0 / Q8_0 / Q4_K product")
         use_mma = (t == GGML_TYPE_Q4_K and 1 <= M <= GEMV_MAX_M and mma_gemv_fits(M, K) and not self.dump and not peers
                    and epilogue is None and self.streamed is not True

@@ -147,3 +147,102 @@ def mul_mat_q6_K_q8_K(W, A, M: int, N: int, K: int) -> np.ndarray:
             acc = (acc + terms[:, b]).astype(np.float32)
         out[m] = acc
     return out
+
+
+# ---- Q5_K --------------------------------------------------------------------------------------------------------------
+# ggml-common.h block_q5_K: d, dmin (fp16), scales[12] (eight 6-bit scales and eight 6-bit mins, packed as in Q4_K),
+# qh[32], qs[128] = 176 bytes per 256 weights; weight e = d * sc[e / 32] * q5[e] - dmin * m[e / 32], elements in the order
+# of ggml's dequantize_row_q5_K (pinned against gguf-py's dequantizer). The dot product follows ggml_vec_dot_q5_K_q8_K's
+# generic branch: per block sumi = sum_j sc[j] * sum_i q5 * q8 (exact), sumf += d * d8 * sumi - dmin * d8 * sum_j m[j] * bsum(j).
+Q5_K = 13
+BLOCK_BYTES[Q5_K] = 176
+
+
+def _pack_scales_k4(sc, mn) -> np.ndarray:
+    """Eight 6-bit scales and mins [n][8] into ggml's 12 bytes (the inverse of get_scale_min_k4)."""
+    sc, mn = sc.astype(np.uint8), mn.astype(np.uint8)
+    out = np.zeros((sc.shape[0], 12), np.uint8)
+    out[:, 0:4] = (sc[:, 0:4] & 63) | ((sc[:, 4:8] >> 4) << 6)
+    out[:, 4:8] = (mn[:, 0:4] & 63) | ((mn[:, 4:8] >> 4) << 6)
+    out[:, 8:12] = (sc[:, 4:8] & 0x0F) | ((mn[:, 4:8] & 0x0F) << 4)
+    return out
+
+
+def _unpack_scales_k4(s12):
+    s12 = s12.astype(np.int32)
+    sc, mn = np.zeros((s12.shape[0], 8), np.int32), np.zeros((s12.shape[0], 8), np.int32)
+    sc[:, 0:4], mn[:, 0:4] = s12[:, 0:4] & 63, s12[:, 4:8] & 63
+    sc[:, 4:8] = (s12[:, 8:12] & 0x0F) | ((s12[:, 0:4] >> 6) << 4)
+    mn[:, 4:8] = (s12[:, 8:12] >> 4) | ((s12[:, 4:8] >> 6) << 4)
+    return sc, mn
+
+
+def quantize_q5_K(w) -> np.ndarray:
+    """A valid packer: per 32 weights min / range -> 6-bit m and sc under d = max range / (63 * 31), dmin = max -min / 63."""
+    x = np.ascontiguousarray(w, np.float32).reshape(-1, 8, 32)
+    lo = np.minimum(x.min(axis=2), 0.0)
+    rng = x.max(axis=2) - lo
+    d = (rng.max(axis=1) / np.float32(63.0 * 31.0)).astype(np.float16)
+    dmin = ((-lo).max(axis=1) / np.float32(63.0)).astype(np.float16)
+    df, mf = d.astype(np.float32), dmin.astype(np.float32)
+    sc = np.where(df[:, None] > 0, np.ceil(rng / 31.0 / np.where(df > 0, df, 1.0)[:, None]), 0).clip(0, 63).astype(np.int32)
+    mn = np.where(mf[:, None] > 0, np.rint(-lo / np.where(mf > 0, mf, 1.0)[:, None]), 0).clip(0, 63).astype(np.int32)
+    eff = df[:, None] * sc
+    q = np.where(eff[:, :, None] > 0, np.rint((x + (mf[:, None] * mn)[:, :, None]) / np.where(eff > 0, eff, 1.0)[:, :, None]), 0)
+    q = q.clip(0, 31).astype(np.int32).reshape(-1, 4, 2, 32)              # [block][j][half][l]
+    out = np.zeros((q.shape[0], 176), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(-1, 2)
+    out[:, 4:16] = _pack_scales_k4(sc, mn)
+    qh = np.zeros((q.shape[0], 32), np.int32)
+    for j in range(4):
+        a, b = q[:, j, 0], q[:, j, 1]
+        out[:, 48 + 32 * j:48 + 32 * j + 32] = (a & 0x0F) | ((b & 0x0F) << 4)
+        qh |= ((a >> 4) << (2 * j)) | ((b >> 4) << (2 * j + 1))
+    out[:, 16:48] = qh.astype(np.uint8)
+    return out.reshape(-1)
+
+
+def decode_q5_K(blocks):
+    """(d, dmin fp16 [n], sc, m int [n][8], q5 as uint8 [n][256] in element order) of n blocks."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, 176)
+    d = b[:, 0:2].copy().view(np.float16).reshape(-1)
+    dmin = b[:, 2:4].copy().view(np.float16).reshape(-1)
+    sc, mn = _unpack_scales_k4(b[:, 4:16])
+    qh, qs = b[:, 16:48].astype(np.int32), b[:, 48:176].astype(np.int32)
+    q = np.zeros((b.shape[0], 256), np.int32)
+    for j in range(4):
+        s = qs[:, 32 * j:32 * j + 32]
+        q[:, 64 * j:64 * j + 32] = (s & 0x0F) | (((qh >> (2 * j)) & 1) << 4)
+        q[:, 64 * j + 32:64 * j + 64] = (s >> 4) | (((qh >> (2 * j + 1)) & 1) << 4)
+    return d, dmin, sc, mn, q.astype(np.uint8)
+
+
+def dequantize_q5_K(blocks) -> np.ndarray:
+    d, dmin, sc, mn, q = decode_q5_K(blocks)
+    d1 = (d.astype(np.float32)[:, None] * sc.astype(np.float32))
+    m1 = (dmin.astype(np.float32)[:, None] * mn.astype(np.float32))
+    return (np.repeat(d1, 32, axis=1) * q.astype(np.float32) - np.repeat(m1, 32, axis=1)).astype(np.float32).reshape(-1)
+
+
+def mul_mat_q5_K_q8_K(W, A, M: int, N: int, K: int) -> np.ndarray:
+    B = K // 256
+    d, dmin, sc, mn, q5 = decode_q5_K(W)
+    d, dmin = d.reshape(N, B).astype(np.float32), dmin.reshape(N, B).astype(np.float32)
+    sc, mn = sc.reshape(N, B, 8).astype(np.int64), mn.reshape(N, B, 8).astype(np.int64)
+    q5 = q5.reshape(N, B, 8, 32).astype(np.int64)
+    a = np.ascontiguousarray(A, np.uint8).reshape(M, B, 292)
+    d8 = a[:, :, 0:4].copy().view(np.float32).reshape(M, B)
+    q8 = a[:, :, 4:260].copy().view(np.int8).reshape(M, B, 8, 32).astype(np.int64)
+    bsum = a[:, :, 260:292].copy().view(np.int16).reshape(M, B, 8, 2).astype(np.int64).sum(axis=3)
+    out = np.zeros((M, N), np.float32)
+    for m in range(M):
+        sumi = np.einsum("nbj,nbji,bji->nb", sc, q5, q8[m])
+        summ = np.einsum("nbj,bj->nb", mn, bsum[m])
+        terms = ((d * d8[m][None, :]).astype(np.float32) * sumi.astype(np.float32) -
+                 (dmin * d8[m][None, :]).astype(np.float32) * summ.astype(np.float32)).astype(np.float32)
+        acc = np.zeros(N, np.float32)
+        for b in range(B):
+            acc = (acc + terms[:, b]).astype(np.float32)
+        out[m] = acc
+    return out

@@ -191,3 +191,18 @@ def test_q6_K_decode_equals_gguf_py():
     raw = rng.integers(0, 256, (8, 210), dtype=np.uint8)
     raw[:, 208], raw[:, 209] = 0, 0x1C           # a small positive fp16 d
     assert np.array_equal(et.dequantize_q6_K(raw.reshape(-1)), quants.dequantize(raw, gguf.GGMLQuantizationType.Q6_K).reshape(-1))
+
+
+def test_q5_K_decode_equals_gguf_py():
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    from oracle import extra_types as et
+    rng = np.random.default_rng(13)
+    w = (rng.standard_normal((16, 512)) * 0.05).astype(np.float32)
+    w[0, :256] = 0.0
+    blocks = et.quantize_q5_K(w)
+    assert np.array_equal(et.dequantize_q5_K(blocks), quants.dequantize(blocks.reshape(16, -1), gguf.GGMLQuantizationType.Q5_K).reshape(-1))
+    assert np.max(np.abs(et.dequantize_q5_K(blocks).reshape(16, 512) - w)) <= 0.05 * np.max(np.abs(w))
+    raw = rng.integers(0, 256, (8, 176), dtype=np.uint8)
+    raw[:, 0], raw[:, 1], raw[:, 2], raw[:, 3] = 0, 0x1C, 0, 0x18      # small positive fp16 d and dmin
+    assert np.array_equal(et.dequantize_q5_K(raw.reshape(-1)), quants.dequantize(raw, gguf.GGMLQuantizationType.Q5_K).reshape(-1))
