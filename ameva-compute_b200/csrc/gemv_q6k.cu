@@ -231,4 +231,101 @@ AcResult launch_mmvqb_q5_K(const LaunchArgs& a) {
     return check_launch();
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// IQ4_XS x Q8_K: a weight is d * (ls[e / 32] - 32) * kvalues_iq4nl[q4] (ggml-common.h block_iq4_xs: d, scales_h,
+// scales_l[4], qs[128]: 136 bytes per 256 weights; ls is 6 bits: four from scales_l, two from scales_h). The upload
+// decodes kvalues[q4] to int8 in element order and keeps the first 8 bytes of the block as the scale record (264 bytes
+// per block on the device). y = sum_blocks (d * d_a) * sum_ib (ls[ib] - 32) * sum_i kv * q8, as
+// ggml_vec_dot_iq4_xs_q8_K forms it.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int M>
+__device__ __forceinline__ void group_dot_iq4xs(const uint4 w, uint32_t gi, const uint8_t* s, const int8_t* __restrict__ AQ,
+                                                const uint8_t* __restrict__ AB, uint32_t K, uint32_t B, float (&acc)[M]) {
+    const uint32_t blk = gi >> 4, ib = (gi & 15u) >> 1;
+    const uint2 rec = *reinterpret_cast<const uint2*>(s + blk * 8u);   // d | scales_h << 16, scales_l[0..3]
+    const uint32_t lo = (rec.y >> (4u * ib)) & 0x0Fu, hi = ((rec.x >> 16) >> (2u * ib)) & 3u;
+    const int ls = (int)(lo | (hi << 4)) - 32;
+    const float dw = h2f((uint16_t)(rec.x & 0xFFFFu));
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const uint4 a = *reinterpret_cast<const uint4*>(AQ + (size_t)m * K + 16u * gi);
+        int t = dp4a_ss(w.x, a.x, 0);
+        t = dp4a_ss(w.y, a.y, t);
+        t = dp4a_ss(w.z, a.z, t);
+        t = dp4a_ss(w.w, a.w, t);
+        const float da = *reinterpret_cast<const float*>(AB + ((size_t)m * B + blk) * kABBytes + 32);
+        acc[m] = fmaf(dw * da, (float)(ls * t), acc[m]);
+    }
+}
+
+template <int M>
+__global__ void __launch_bounds__(kQ6Warps * 32) gemv_iq4xs_kernel(const uint8_t* __restrict__ Q, const uint8_t* __restrict__ S,
+                                                                   const int8_t* __restrict__ AQ, const uint8_t* __restrict__ AB,
+                                                                   float* __restrict__ dst, uint32_t N, uint32_t K,
+                                                                   uint32_t dst_stride) {
+    pdl_wait();
+    pdl_trigger();
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row = blockIdx.x * kQ6Warps + warp;
+    if (row >= N) return;
+    const uint32_t B = K >> 8, groups = K >> 4;
+    const uint4* q = reinterpret_cast<const uint4*>(Q + (size_t)row * K);
+    extern __shared__ __align__(16) uint8_t iq_smem[];
+    uint8_t* s = iq_smem + (size_t)warp * B * 8u;
+    {   // the row's scale records (8 bytes per block)
+        const uint2* src = reinterpret_cast<const uint2*>(S + (size_t)row * B * 8u);
+        for (uint32_t i = lane; i < B; i += 32u) reinterpret_cast<uint2*>(s)[i] = __ldg(src + i);
+        __syncwarp();
+    }
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+    uint32_t gi = lane;
+    for (; gi + 32u * 3u < groups; gi += 32u * 4u) {
+        uint4 w[4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u) w[u] = ld_stream_u4(q + gi + 32u * u);
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u) group_dot_iq4xs<M>(w[u], gi + 32u * u, s, AQ, AB, K, B, acc);
+    }
+    for (; gi < groups; gi += 32u) group_dot_iq4xs<M>(ld_stream_u4(q + gi), gi, s, AQ, AB, K, B, acc);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const float v = warp_sum(acc[m]);
+        if (lane == 0) dst[(size_t)m * dst_stride + row] = v;
+    }
+}
+
+template <int M>
+static void launch_iq4xs_m(const LaunchArgs& a, uint32_t N, uint32_t K, uint32_t dst_stride) {
+    const size_t smem = (size_t)kQ6Warps * (K >> 8) * 8u;
+    launch_pdl(gemv_iq4xs_kernel<M>, dim3((N + kQ6Warps - 1) / kQ6Warps), dim3(kQ6Warps * 32), smem, a.stream,
+               (const uint8_t*)a.ptr[0], (const uint8_t*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
+               (float*)a.ptr[4], N, K, dst_stride);
+}
+
+// ameva_mmvqb_iq4_xs: bindings 0 Q (int8 [N][K], kvalues decoded at upload), 1 S (8-byte records [N][K/256]: d, scales_h,
+// scales_l), 2 AQ int8 [M][K], 3 AB (48-byte Q8_K records), 4 dst f32; push {M (1..8), N, K (% 256, <= 65536), dst_stride}
+AcResult launch_mmvqb_iq4_xs(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
+    if (N == 0 || K == 0 || (K & 255u) || K > 65536u || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t B = K >> 8;
+    if (a.range[0] < (uint64_t)N * K || a.range[1] < (uint64_t)N * B * 8u || a.range[2] < (uint64_t)M * K ||
+        a.range[3] < (uint64_t)M * B * kABBytes || a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if ((((uintptr_t)a.ptr[0] | (uintptr_t)a.ptr[2]) & 15u) || ((uintptr_t)a.ptr[1] & 7u)) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    switch (M) {
+        case 1: launch_iq4xs_m<1>(a, N, K, dst_stride); break;
+        case 2: launch_iq4xs_m<2>(a, N, K, dst_stride); break;
+        case 3: launch_iq4xs_m<3>(a, N, K, dst_stride); break;
+        case 4: launch_iq4xs_m<4>(a, N, K, dst_stride); break;
+        case 5: launch_iq4xs_m<5>(a, N, K, dst_stride); break;
+        case 6: launch_iq4xs_m<6>(a, N, K, dst_stride); break;
+        case 7: launch_iq4xs_m<7>(a, N, K, dst_stride); break;
+        default: launch_iq4xs_m<8>(a, N, K, dst_stride); break;
+    }
+    return check_launch();
+}
+
 }  // namespace amv

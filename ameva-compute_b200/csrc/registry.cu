@@ -48,6 +48,7 @@ AcResult launch_cpy(const LaunchArgs&);
 AcResult launch_unary(const LaunchArgs&);
 AcResult launch_mmvqb_q6_K(const LaunchArgs&);
 AcResult launch_mmvqb_q5_K(const LaunchArgs&);
+AcResult launch_mmvqb_iq4_xs(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
@@ -124,6 +125,7 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvqb_q4_K", 5, 16, {256, 1, 1}, launch_mmvqb_q4_K},
     {"ameva_mmvqb_q6_K", 5, 16, {256, 1, 1}, launch_mmvqb_q6_K},
     {"ameva_mmvqb_q5_K", 5, 16, {256, 1, 1}, launch_mmvqb_q5_K},
+    {"ameva_mmvqb_iq4_xs", 5, 16, {256, 1, 1}, launch_mmvqb_iq4_xs},
     {"ameva_mmvq_q4_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q4_0_ep},
     {"ameva_mmvq_q8_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q8_0_ep},
     {"ameva_mmvqb_q4_K_ep", 7, 20, {256, 1, 1}, launch_mmvqb_q4_K_ep},
@@ -205,6 +207,7 @@ bool codec_for(uint32_t type, Codec* c) {
         case 20: *c = {32, 18, 2, 32, 0, 2, 2}; return true;     // IQ4_NL: d@0, qs[16]@2 -> Q8_0 regions
         case 14: *c = {256, 210, 0, 256, 192, 18, 3}; return true;  // Q6_K: ql[128]@0, qh[64]@128, scales[16]@192, d@208
         case 13: *c = {256, 176, 16, 256, 0, 16, 4}; return true;   // Q5_K: d, dmin, scales[12] @0, qh[32]@16, qs[128]@48
+        case 23: *c = {256, 136, 8, 256, 0, 8, 5}; return true;     // IQ4_XS: d, scales_h, scales_l[4] @0, qs[128]@8
         default: return false;
     }
 }
@@ -264,8 +267,32 @@ void encode_q5_K(const int8_t* in, uint8_t* blk) {
         }
 }
 
+// IQ4_XS (xcode 5): kvalues_iq4nl[q4] as 256 int8 in element order (sub-block ib = e / 32 holds qs[16 ib .. 16 ib + 15]:
+// low nibbles first, then high nibbles); the block's first 8 bytes (d, scales_h, scales_l[4]) are its scale record.
+void decode_iq4_xs(const uint8_t* blk, int8_t* out) {
+    const uint8_t* qs = blk + 8;
+    for (int ib = 0; ib < 8; ++ib, qs += 16, out += 32)
+        for (int j = 0; j < 16; ++j) {
+            out[j] = kIq4nlValues[qs[j] & 0x0F];
+            out[j + 16] = kIq4nlValues[qs[j] >> 4];
+        }
+}
+void encode_iq4_xs(const int8_t* in, uint8_t* blk) {
+    auto nearest = [](int v) {
+        int best = 0;
+        for (int t = 1; t < 16; ++t)
+            if (abs(kIq4nlValues[t] - v) < abs(kIq4nlValues[best] - v)) best = t;
+        return best;
+    };
+    uint8_t* qs = blk + 8;
+    for (int ib = 0; ib < 8; ++ib, qs += 16, in += 32)
+        for (int j = 0; j < 16; ++j) qs[j] = (uint8_t)(nearest(in[j]) | (nearest(in[j + 16]) << 4));
+}
+
 void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // the int8 weights of one ggml block
-    if (xcode == 4) {
+    if (xcode == 5) {
+        decode_iq4_xs(blk, out);
+    } else if (xcode == 4) {
         decode_q5_K(blk, out);
     } else if (xcode == 3) {
         decode_q6_K(blk, out);
@@ -292,6 +319,10 @@ void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inv
     }
     if (xcode == 4) {
         encode_q5_K(in, blk);
+        return;
+    }
+    if (xcode == 5) {
+        encode_iq4_xs(in, blk);
         return;
     }
     if (xcode == 1) {
@@ -322,7 +353,7 @@ void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inv
 // The type whose kernels and device regions serve a weight type (itself, or Q8_0 for the decoded types); 0 = not built.
 extern "C" uint32_t ac_b200_device_type(uint32_t ggml_type) {
     switch (ggml_type) {
-        case 2: case 8: case 12: case 13: case 14: case 36: return ggml_type;
+        case 2: case 8: case 12: case 13: case 14: case 23: case 36: return ggml_type;
         case 6: case 20: return 8;
         default: return 0;
     }
@@ -347,9 +378,9 @@ extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, 
     *out_path = AC_B200_PATH_NONE;
     if (flags & ~(AC_B200_PLAN_EXACT | AC_B200_PLAN_HOST_LAUNCH | AC_B200_PLAN_PEERS | AC_B200_PLAN_WEIGHT_RANGE))
         return AC_ERR_INVALID_ARGUMENT;
-    const uint64_t blk = type == 2 || type == 8 ? 32 : (type == 12 || type == 13 || type == 14) ? 256 : type == 36 ? 128 : 0;
+    const uint64_t blk = type == 2 || type == 8 ? 32 : (type == 12 || type == 13 || type == 14 || type == 23) ? 256 : type == 36 ? 128 : 0;
     if (!blk) return AC_ERR_FEATURE_NOT_SUPPORTED;
-    if (type == 14 || type == 13) {   // Q6_K, Q5_K: one kernel each (ameva_mmvqb_q6_K / _q5_K); more than 8 rows in chunks of 8
+    if (type == 14 || type == 13 || type == 23) {   // Q6_K, Q5_K, IQ4_XS: one kernel each (ameva_mmvqb_*); more than 8 rows in chunks of 8
         if (M == 0 || N == 0 || K == 0 || K % blk) return AC_ERR_INVALID_SHAPE;
         *out_path = AC_B200_PATH_GEMV;
         return AC_SUCCESS;
@@ -459,6 +490,8 @@ extern "C" AcResult ac_b200_weight_exponent(uint32_t type, const void* ggml_bloc
             bound = 127.0f * d;
         } else if (type == 6) {
             bound = 16.0f * d;
+        } else if (type == 23) {   // |ls - 32| <= 32, |kvalue| <= 127
+            bound = 4064.0f * d;
         } else if (type == 13) {   // 6-bit scales and mins, 5-bit weights
             const float m = half_to_float(h1);
             bound = 1953.0f * d + 63.0f * (m < 0 ? -m : m);

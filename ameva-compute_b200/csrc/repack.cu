@@ -24,7 +24,15 @@ __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 
 // sixteen decoded weights of a Q5_0 / IQ4_NL block: `part` 0 = elements 0..15 (low nibbles), 1 = elements 16..31
 __device__ __forceinline__ uint4 decode_piece(uint32_t xcode, const uint8_t* blk, uint32_t part) {
     uint32_t w[4] = {0u, 0u, 0u, 0u};
-    if (xcode == 4u) {
+    if (xcode == 5u) {
+        // IQ4_XS: piece `part` (0..15): sub-block ib = part / 2, low (part even) or high nibbles of qs[16 ib .. 16 ib + 15]
+        const uint8_t* qs = blk + 8u + 16u * (part >> 1);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int v = c_iq4nl[(part & 1u) ? (qs[i] >> 4) : (qs[i] & 0x0Fu)];
+            w[i >> 2] |= (uint32_t)(v & 0xFF) << (8 * (i & 3));
+        }
+    } else if (xcode == 4u) {
         // Q5_K: piece `part` (0..15) = elements 16 part .. 16 part + 15: j = part / 4 (64 elements), half = (part / 2) % 2
         // (low or high nibble), l = 16 (part % 2) + i
         const uint32_t j = part >> 2, half = (part >> 1) & 1u, l0 = 16u * (part & 1u);
@@ -122,6 +130,7 @@ static bool repack_codec(uint32_t type, RepackCodec* c, uint32_t* blk) {
         case 20: *c = {18, 2, 32, 0, 2, 2}; *blk = 32; return true;       // IQ4_NL: d@0, qs[16]@2, decoded
         case 14: *c = {210, 0, 256, 192, 18, 3}; *blk = 256; return true; // Q6_K: ql, qh decoded to 256 int8; scales[16] + d kept
         case 13: *c = {176, 16, 256, 0, 16, 4}; *blk = 256; return true;  // Q5_K: qh, qs decoded to 256 bytes; d, dmin, scales kept
+        case 23: *c = {136, 8, 256, 0, 8, 5}; *blk = 256; return true;    // IQ4_XS: qs decoded to 256 int8; d, scales_h, scales_l kept
         default: return false;
     }
 }

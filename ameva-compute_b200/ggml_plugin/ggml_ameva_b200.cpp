@@ -95,18 +95,21 @@ AcContext* context() {          // created on first use (the loader probes the r
 enum ggml_type dev_type(enum ggml_type t) { return (t == GGML_TYPE_Q5_0 || t == GGML_TYPE_IQ4_NL) ? GGML_TYPE_Q8_0 : t; }
 bool repacked_type(enum ggml_type t) {
     t = dev_type(t);
-    return t == GGML_TYPE_Q4_0 || t == GGML_TYPE_Q8_0 || t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K;
+    return t == GGML_TYPE_Q4_0 || t == GGML_TYPE_Q8_0 || t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K ||
+           t == GGML_TYPE_IQ4_XS;
 }
 // activations quantized per 256 (Q8_K records) and the ameva_mmvqb kernel family
-bool per_256(enum ggml_type t) { return t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K; }
+bool per_256(enum ggml_type t) { return t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K || t == GGML_TYPE_IQ4_XS; }
 // types with one GEMV kernel each (weights decoded to bytes at upload): no fused, grouped or tensor-core variants
-bool byte_decoded(enum ggml_type t) { return t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K; }
+bool byte_decoded(enum ggml_type t) { return t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K || t == GGML_TYPE_IQ4_XS; }
 uint32_t block_elems(enum ggml_type t) { return per_256(t) ? 256u : 32u; }
 uint32_t payload_bytes(enum ggml_type t) {   // of the device regions
     t = dev_type(t);
     return t == GGML_TYPE_Q4_0 ? 16u : (t == GGML_TYPE_Q8_0 ? 32u : (byte_decoded(t) ? 256u : 128u));
 }
-uint32_t scale_bytes(enum ggml_type t) { return (t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q5_K) ? 16u : (t == GGML_TYPE_Q6_K ? 18u : 2u); }
+uint32_t scale_bytes(enum ggml_type t) {
+    return (t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q5_K) ? 16u : (t == GGML_TYPE_Q6_K ? 18u : (t == GGML_TYPE_IQ4_XS ? 8u : 2u));
+}
 
 // A weight this backend keeps in its device layout: a supported quantized type, plain 2-D, contiguous, not a view.
 bool is_repacked_weight(const ggml_tensor* t) {
@@ -705,7 +708,7 @@ bool dispatch(Recorder& r, const char* name, const AcBufferBinding* b, uint32_t 
 }
 
 const char* type_name(enum ggml_type t) {
-    return t == GGML_TYPE_Q4_0 ? "q4_0" : (t == GGML_TYPE_Q8_0 ? "q8_0" : (t == GGML_TYPE_Q6_K ? "q6_K" : (t == GGML_TYPE_Q5_K ? "q5_K" : "q4_K")));
+    return t == GGML_TYPE_Q4_0 ? "q4_0" : (t == GGML_TYPE_Q8_0 ? "q8_0" : (t == GGML_TYPE_Q6_K ? "q6_K" : (t == GGML_TYPE_Q5_K ? "q5_K" : (t == GGML_TYPE_IQ4_XS ? "iq4_xs" : "q4_K"))));
 }
 
 // activation quantization into the scratch, unless the same rows are there already
@@ -1398,7 +1401,7 @@ const char* ggml_backend_ameva_abi_check(void) {
             enum ggml_type type;
             const char* name;
         } kTypes[] = {{GGML_TYPE_F32, "f32"}, {GGML_TYPE_Q4_0, "q4_0"}, {GGML_TYPE_Q8_0, "q8_0"}, {GGML_TYPE_Q4_K, "q4_K"},
-                      {GGML_TYPE_F16, "f16"}, {GGML_TYPE_I32, "i32"}, {GGML_TYPE_I64, "i64"}, {GGML_TYPE_Q6_K, "q6_K"}, {GGML_TYPE_Q5_K, "q5_K"}};
+                      {GGML_TYPE_F16, "f16"}, {GGML_TYPE_I32, "i32"}, {GGML_TYPE_I64, "i64"}, {GGML_TYPE_Q6_K, "q6_K"}, {GGML_TYPE_Q5_K, "q5_K"}, {GGML_TYPE_IQ4_XS, "iq4_xs"}};
         for (const auto& o : kOps)
             if (!what && strcmp(ggml_op_name(o.op), o.name) != 0) what = "enum ggml_op";
         for (const auto& t : kTypes)

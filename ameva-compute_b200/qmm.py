@@ -27,14 +27,18 @@ GGML_TYPE_Q6_K = 14
 # Q5_K likewise: q5 decoded to bytes (256 per block), the block's first 16 bytes (d, dmin, packed scales) kept as the
 # scale record; ameva_mmvqb_q5_K
 GGML_TYPE_Q5_K = 13
-BYTE_DECODED = (GGML_TYPE_Q6_K, GGML_TYPE_Q5_K)   # one GEMV kernel each, no tensor-core form, no fused variants
+# IQ4_XS: kvalues_iq4nl[q4] decoded to int8, the block's first 8 bytes (d, scales_h, scales_l) kept; ameva_mmvqb_iq4_xs
+GGML_TYPE_IQ4_XS = 23
+BYTE_DECODED = (GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS)   # one GEMV kernel each, no tensor-core form, no fused variants
 TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s",
-              GGML_TYPE_Q6_K: "q6_K", GGML_TYPE_Q5_K: "q5_K"}
+              GGML_TYPE_Q6_K: "q6_K", GGML_TYPE_Q5_K: "q5_K", GGML_TYPE_IQ4_XS: "iq4_xs"}
 BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128, GGML_TYPE_Q6_K: 256,
-         GGML_TYPE_Q5_K: 256}
-Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128, GGML_TYPE_Q6_K: 256, GGML_TYPE_Q5_K: 256}   # payload bytes per block
-S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16, GGML_TYPE_Q6_K: 18, GGML_TYPE_Q5_K: 16}       # scale bytes per block
-PER_256 = (GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_Q5_K)   # types whose activations are quantized per 256 (Q8_K records)
+         GGML_TYPE_Q5_K: 256, GGML_TYPE_IQ4_XS: 256}
+Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128, GGML_TYPE_Q6_K: 256, GGML_TYPE_Q5_K: 256,
+           GGML_TYPE_IQ4_XS: 256}   # payload bytes per block
+S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16, GGML_TYPE_Q6_K: 18, GGML_TYPE_Q5_K: 16,
+           GGML_TYPE_IQ4_XS: 8}     # scale bytes per block
+PER_256 = (GGML_TYPE_Q4_K,) + BYTE_DECODED   # types whose activations are quantized per 256 (Q8_K records)
 FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in shared memory
 
 

@@ -395,7 +395,8 @@ AcResult ac_b200_repack_to_device(uint32_t ggml_type, const void* ggml_blocks, u
  * the 6-bit weights decoded to int8 (q - 32, 256 bytes per block, element order), its scale region the block's 16 int8
  * sub-block scales and fp16 d as they are (18 bytes per block); kernel ameva_mmvqb_q6_K, any M in chunks of 8 rows
  * (ac_b200_mul_mat_plan answers AC_B200_PATH_GEMV). Q5_K (13) likewise: q5 (0..31) as 256 bytes per block, the block's
- * first 16 bytes (d, dmin, packed scales) as its scale record; kernel ameva_mmvqb_q5_K. */
+ * first 16 bytes (d, dmin, packed scales) as its scale record; kernel ameva_mmvqb_q5_K. IQ4_XS (23): kvalues_iq4nl[q4]
+ * as 256 int8 per block, the block's first 8 bytes (d, scales_h, scales_l) as its scale record; ameva_mmvqb_iq4_xs. */
 uint32_t ac_b200_device_type(uint32_t ggml_type);
 AcResult ac_b200_repack_from_device(uint32_t ggml_type, const void* device_layout, uint64_t rows, uint64_t k,
                                     void* ggml_blocks);

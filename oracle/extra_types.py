@@ -246,3 +246,74 @@ def mul_mat_q5_K_q8_K(W, A, M: int, N: int, K: int) -> np.ndarray:
             acc = (acc + terms[:, b]).astype(np.float32)
         out[m] = acc
     return out
+
+
+# ---- IQ4_XS ------------------------------------------------------------------------------------------------------------
+# ggml-common.h block_iq4_xs: d fp16, scales_h u16, scales_l[4], qs[128] = 136 bytes per 256 weights; sub-block ib = e / 32
+# has the 6-bit ls = scales_l nibble ib | (two bits of scales_h) << 4; weight e = d * (ls - 32) * kvalues_iq4nl[q4] (the low
+# nibbles of qs[16 ib ..] are the first 16 elements of the sub-block, the high nibbles the next 16; pinned against gguf-py).
+# ggml_vec_dot_iq4_xs_q8_K: per block sumf += d * d8 * sum_ib (ls - 32) * sum_i kv * q8.
+IQ4_XS = 23
+BLOCK_BYTES[IQ4_XS] = 136
+
+
+def quantize_iq4_xs(w) -> np.ndarray:
+    """A valid packer: per 32 weights amax / 127 -> 6-bit scale under d = max / 31, nearest table value."""
+    x = np.ascontiguousarray(w, np.float32).reshape(-1, 8, 32)
+    gs = np.max(np.abs(x), axis=2) / np.float32(127.0)
+    d = (np.max(gs, axis=1) / np.float32(31.0)).astype(np.float16)
+    df = d.astype(np.float32)
+    ls = np.where(df[:, None] > 0, np.ceil(gs / np.where(df > 0, df, 1.0)[:, None]), 0).clip(0, 31).astype(np.int32) + 32
+    eff = df[:, None] * (ls - 32)
+    t = x / np.where(eff > 0, eff, 1.0)[:, :, None]
+    q = np.argmin(np.abs(t[..., None] - KVALUES_IQ4NL.astype(np.float32)), axis=-1).astype(np.uint8)     # [n][8][32]
+    q = np.where(eff[:, :, None] > 0, q, 8).astype(np.uint8)                                             # (kvalues[8] = 1)
+    out = np.zeros((x.shape[0], 136), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(-1, 2)
+    sh = np.zeros(x.shape[0], np.uint16)
+    for ib in range(8):
+        sh |= ((ls[:, ib] >> 4).astype(np.uint16) << np.uint16(2 * ib))
+        out[:, 4 + ib // 2] |= ((ls[:, ib] & 0x0F) << (4 * (ib % 2))).astype(np.uint8)
+        out[:, 8 + 16 * ib:8 + 16 * ib + 16] = q[:, ib, :16] | (q[:, ib, 16:] << 4)
+    out[:, 2:4] = sh.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
+
+
+def decode_iq4_xs(blocks):
+    """(d fp16 [n], ls - 32 as int [n][8], kvalues[q4] as int8 [n][256] in element order) of n blocks."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, 136)
+    d = b[:, 0:2].copy().view(np.float16).reshape(-1)
+    sh = b[:, 2:4].copy().view(np.uint16).reshape(-1).astype(np.int32)
+    sl = b[:, 4:8].astype(np.int32)
+    ls = np.zeros((b.shape[0], 8), np.int32)
+    q = np.zeros((b.shape[0], 256), np.int8)
+    for ib in range(8):
+        ls[:, ib] = ((sl[:, ib // 2] >> (4 * (ib % 2))) & 0x0F) | (((sh >> (2 * ib)) & 3) << 4)
+        qs = b[:, 8 + 16 * ib:8 + 16 * ib + 16]
+        q[:, 32 * ib:32 * ib + 16] = KVALUES_IQ4NL[qs & 0x0F]
+        q[:, 32 * ib + 16:32 * ib + 32] = KVALUES_IQ4NL[qs >> 4]
+    return d, ls - 32, q
+
+
+def dequantize_iq4_xs(blocks) -> np.ndarray:
+    d, ls, q = decode_iq4_xs(blocks)
+    dl = (d.astype(np.float32)[:, None] * ls.astype(np.float32))
+    return (np.repeat(dl, 32, axis=1) * q.astype(np.float32)).reshape(-1)
+
+
+def mul_mat_iq4_xs_q8_K(W, A, M: int, N: int, K: int) -> np.ndarray:
+    B = K // 256
+    d, ls, q = decode_iq4_xs(W)
+    d, ls, q = d.reshape(N, B).astype(np.float32), ls.reshape(N, B, 8).astype(np.int64), q.reshape(N, B, 8, 32).astype(np.int64)
+    a = np.ascontiguousarray(A, np.uint8).reshape(M, B, 292)
+    d8 = a[:, :, 0:4].copy().view(np.float32).reshape(M, B)
+    q8 = a[:, :, 4:260].copy().view(np.int8).reshape(M, B, 8, 32).astype(np.int64)
+    out = np.zeros((M, N), np.float32)
+    for m in range(M):
+        sumi = np.einsum("nbj,nbji,bji->nb", ls, q, q8[m])
+        terms = ((d * d8[m][None, :]).astype(np.float32) * sumi.astype(np.float32)).astype(np.float32)
+        acc = np.zeros(N, np.float32)
+        for b in range(B):
+            acc = (acc + terms[:, b]).astype(np.float32)
+        out[m] = acc
+    return out

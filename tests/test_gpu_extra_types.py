@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from conftest import load_pkg
-from helpers import IQ4_NL, Q5_0, Q5_K, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+from helpers import IQ4_NL, IQ4_XS, Q5_0, Q5_K, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
 from oracle import extra_types
 
 pytestmark = pytest.mark.gpu
@@ -133,6 +133,38 @@ def test_q5_K_mul_mat(ctx, M, N, K):
     xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
     mm.run(xb, dst, M)
     want, _, _ = oracle_mul_mat(Q5_K, blocks, scale, x, N, K, want_sums=False)
+    assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
+    for o in (mm, xb, dst, w):
+        o.destroy()
+
+
+@pytest.mark.parametrize("N,K", [(96, 1024), (1000, 4096), (3, 256)])
+def test_iq4_xs_upload_decodes_to_int8_and_reads_back_the_uploaded_bytes(ctx, N, K):
+    blocks, _ = make_weights(IQ4_XS, N, K, N)
+    w = qmm.QuantWeight.from_ggml(ctx, IQ4_XS, blocks, N, K)
+    host = qmm.QuantWeight.from_ggml(ctx, IQ4_XS, blocks, N, K, host_repack=True)
+    try:
+        assert np.array_equal(w.to_ggml(), blocks) and np.array_equal(host.to_ggml(), blocks)
+        q = extra_types.decode_iq4_xs(blocks)[2]
+        rec_want = blocks.reshape(-1, 136)[:, :8]
+        for wt in (w, host):
+            assert np.array_equal(wt.buf.read(np.int8, N * K), q.reshape(-1))
+            assert np.array_equal(wt.buf.read(np.uint8, N * (K // 256) * 8, wt.s_off).reshape(-1, 8), rec_want)
+    finally:
+        w.destroy()
+        host.destroy()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (1, 1000, 14336), (4, 512, 1024), (8, 130, 2048), (33, 768, 2048)])
+def test_iq4_xs_mul_mat(ctx, M, N, K):
+    """IQ4_XS x Q8_K on its own kernel (ameva_mmvqb_iq4_xs), against the numpy restatement of ggml_vec_dot_iq4_xs_q8_K."""
+    blocks, scale = make_weights(IQ4_XS, N, K, M)
+    x = make_acts(M, K, M + 1)
+    w = qmm.QuantWeight.from_ggml(ctx, IQ4_XS, blocks, N, K)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    mm.run(xb, dst, M)
+    want, _, _ = oracle_mul_mat(IQ4_XS, blocks, scale, x, N, K, want_sums=False)
     assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
     for o in (mm, xb, dst, w):
         o.destroy()

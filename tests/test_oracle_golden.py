@@ -206,3 +206,17 @@ def test_q5_K_decode_equals_gguf_py():
     raw = rng.integers(0, 256, (8, 176), dtype=np.uint8)
     raw[:, 0], raw[:, 1], raw[:, 2], raw[:, 3] = 0, 0x1C, 0, 0x18      # small positive fp16 d and dmin
     assert np.array_equal(et.dequantize_q5_K(raw.reshape(-1)), quants.dequantize(raw, gguf.GGMLQuantizationType.Q5_K).reshape(-1))
+
+
+def test_iq4_xs_decode_equals_gguf_py():
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    from oracle import extra_types as et
+    rng = np.random.default_rng(14)
+    w = (rng.standard_normal((16, 512)) * 0.05).astype(np.float32)
+    w[0, :256] = 0.0
+    blocks = et.quantize_iq4_xs(w)
+    assert np.array_equal(et.dequantize_iq4_xs(blocks), quants.dequantize(blocks.reshape(16, -1), gguf.GGMLQuantizationType.IQ4_XS).reshape(-1))
+    raw = rng.integers(0, 256, (8, 136), dtype=np.uint8)
+    raw[:, 0], raw[:, 1] = 0, 0x1C
+    assert np.array_equal(et.dequantize_iq4_xs(raw.reshape(-1)), quants.dequantize(raw, gguf.GGMLQuantizationType.IQ4_XS).reshape(-1))
