@@ -328,4 +328,88 @@ AcResult launch_mmvqb_iq4_xs(const LaunchArgs& a) {
     return check_launch();
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Q4_1 / Q5_1 x Q8_0-with-sums (ggml's Q8_1): a weight is d * q + m per 32 (q = 0..15 / 0..31), so
+//   y = sum_blocks (d_w * d_a) * sum_i q * q8 + m_w * (d_a * sum_i q8)
+// as ggml_vec_dot_q4_1_q8_1 / _q5_1_q8_1 form it (there d_a * sum q8 is the fp16 field s of the Q8_1 block; here it is
+// the product of the activation record's fp16 d and int16 sum in fp32). The upload decodes q to bytes (32 per block) and
+// keeps (d, m) as a 4-byte record; one kernel serves both types.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int M>
+__global__ void __launch_bounds__(kQ6Warps * 32) gemv_q41_kernel(const uint8_t* __restrict__ Q, const uint32_t* __restrict__ S,
+                                                                 const int8_t* __restrict__ AQ, const uint32_t* __restrict__ AD,
+                                                                 float* __restrict__ dst, uint32_t N, uint32_t K,
+                                                                 uint32_t dst_stride) {
+    pdl_wait();
+    pdl_trigger();
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row = blockIdx.x * kQ6Warps + warp;
+    if (row >= N) return;
+    const uint32_t U = K >> 5, groups = K >> 4;
+    const uint4* q = reinterpret_cast<const uint4*>(Q + (size_t)row * K);
+    extern __shared__ __align__(16) uint8_t q41_smem[];
+    uint32_t* s = reinterpret_cast<uint32_t*>(q41_smem) + (size_t)warp * U;
+    for (uint32_t i = lane; i < U; i += 32u) s[i] = __ldg(S + (size_t)row * U + i);
+    __syncwarp();
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+#pragma unroll 4
+    for (uint32_t gi = lane; gi < groups; gi += 32u) {
+        const uint4 w = ld_stream_u4(q + gi);
+        const uint32_t u = gi >> 1, rec = s[u];
+        const float dw = h2f((uint16_t)(rec & 0xFFFFu)), mw = (gi & 1u) ? 0.0f : h2f((uint16_t)(rec >> 16));
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            const uint4 a = *reinterpret_cast<const uint4*>(AQ + (size_t)m * K + 16u * gi);
+            int t = dp4a_ss(w.x, a.x, 0);
+            t = dp4a_ss(w.y, a.y, t);
+            t = dp4a_ss(w.z, a.z, t);
+            t = dp4a_ss(w.w, a.w, t);
+            const uint32_t adw = AD[(size_t)m * U + u];
+            const float da = h2f((uint16_t)(adw & 0xFFFFu));
+            acc[m] += (dw * da) * (float)t + mw * (da * (float)(int)(int16_t)(adw >> 16));
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const float v = warp_sum(acc[m]);
+        if (lane == 0) dst[(size_t)m * dst_stride + row] = v;
+    }
+}
+
+template <int M>
+static void launch_q41_m(const LaunchArgs& a, uint32_t N, uint32_t K, uint32_t dst_stride) {
+    const size_t smem = (size_t)kQ6Warps * (K >> 5) * 4u;
+    launch_pdl(gemv_q41_kernel<M>, dim3((N + kQ6Warps - 1) / kQ6Warps), dim3(kQ6Warps * 32), smem, a.stream,
+               (const uint8_t*)a.ptr[0], (const uint32_t*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint32_t*)a.ptr[3],
+               (float*)a.ptr[4], N, K, dst_stride);
+}
+
+// ameva_mmvq_q4_1 / ameva_mmvq_q5_1: bindings 0 Q (bytes [N][K], q decoded at upload), 1 S (u32 [N][K/32]: fp16 d | fp16 m
+// << 16), 2 AQ int8 [M][K], 3 AD (u32 [M][K/32]: fp16 d | int16 sum << 16), 4 dst f32;
+// push {M (1..8), N, K (% 32, <= 32768), dst_stride}
+AcResult launch_mmvq_q4_1(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
+    if (N == 0 || K == 0 || (K & 31u) || K > 32768u || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t U = K >> 5;
+    if (a.range[0] < (uint64_t)N * K || a.range[1] < (uint64_t)N * U * 4u || a.range[2] < (uint64_t)M * K ||
+        a.range[3] < (uint64_t)M * U * 4u || a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if ((((uintptr_t)a.ptr[0] | (uintptr_t)a.ptr[2]) & 15u) || (((uintptr_t)a.ptr[1] | (uintptr_t)a.ptr[3]) & 3u))
+        return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    switch (M) {
+        case 1: launch_q41_m<1>(a, N, K, dst_stride); break;
+        case 2: launch_q41_m<2>(a, N, K, dst_stride); break;
+        case 3: launch_q41_m<3>(a, N, K, dst_stride); break;
+        case 4: launch_q41_m<4>(a, N, K, dst_stride); break;
+        case 5: launch_q41_m<5>(a, N, K, dst_stride); break;
+        case 6: launch_q41_m<6>(a, N, K, dst_stride); break;
+        case 7: launch_q41_m<7>(a, N, K, dst_stride); break;
+        default: launch_q41_m<8>(a, N, K, dst_stride); break;
+    }
+    return check_launch();
+}
+
 }  // namespace amv

@@ -49,6 +49,7 @@ AcResult launch_unary(const LaunchArgs&);
 AcResult launch_mmvqb_q6_K(const LaunchArgs&);
 AcResult launch_mmvqb_q5_K(const LaunchArgs&);
 AcResult launch_mmvqb_iq4_xs(const LaunchArgs&);
+AcResult launch_mmvq_q4_1(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
@@ -126,6 +127,8 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvqb_q6_K", 5, 16, {256, 1, 1}, launch_mmvqb_q6_K},
     {"ameva_mmvqb_q5_K", 5, 16, {256, 1, 1}, launch_mmvqb_q5_K},
     {"ameva_mmvqb_iq4_xs", 5, 16, {256, 1, 1}, launch_mmvqb_iq4_xs},
+    {"ameva_mmvq_q4_1", 5, 16, {256, 1, 1}, launch_mmvq_q4_1},
+    {"ameva_mmvq_q5_1", 5, 16, {256, 1, 1}, launch_mmvq_q4_1},
     {"ameva_mmvq_q4_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q4_0_ep},
     {"ameva_mmvq_q8_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q8_0_ep},
     {"ameva_mmvqb_q4_K_ep", 7, 20, {256, 1, 1}, launch_mmvqb_q4_K_ep},
@@ -208,6 +211,8 @@ bool codec_for(uint32_t type, Codec* c) {
         case 14: *c = {256, 210, 0, 256, 192, 18, 3}; return true;  // Q6_K: ql[128]@0, qh[64]@128, scales[16]@192, d@208
         case 13: *c = {256, 176, 16, 256, 0, 16, 4}; return true;   // Q5_K: d, dmin, scales[12] @0, qh[32]@16, qs[128]@48
         case 23: *c = {256, 136, 8, 256, 0, 8, 5}; return true;     // IQ4_XS: d, scales_h, scales_l[4] @0, qs[128]@8
+        case 3: *c = {32, 20, 4, 32, 0, 4, 6}; return true;         // Q4_1: d, m @0, qs[16]@4
+        case 7: *c = {32, 24, 4, 32, 0, 4, 7}; return true;         // Q5_1: d, m @0, qh[4]@4, qs[16]@8
         default: return false;
     }
 }
@@ -289,8 +294,36 @@ void encode_iq4_xs(const int8_t* in, uint8_t* blk) {
         for (int j = 0; j < 16; ++j) qs[j] = (uint8_t)(nearest(in[j]) | (nearest(in[j + 16]) << 4));
 }
 
+// Q4_1 (xcode 6) / Q5_1 (xcode 7): weight = d * q + m with q = 0..15 / 0..31 (ggml-common.h block_q4_1: d, m, qs[16];
+// block_q5_1: d, m, qh[4], qs[16]); q as 32 bytes in element order (low nibbles first), the 4 bytes (d, m) as the record.
+void decode_q4_1(uint32_t xcode, const uint8_t* blk, int8_t* out) {
+    uint32_t qh = 0;
+    const uint8_t* qs = blk + (xcode == 7 ? 8 : 4);
+    if (xcode == 7) memcpy(&qh, blk + 4, 4);
+    for (int j = 0; j < 16; ++j) {
+        out[j] = (int8_t)((qs[j] & 0x0F) | (((qh >> j) & 1u) << 4));
+        out[j + 16] = (int8_t)((qs[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4));
+    }
+}
+void encode_q4_1(uint32_t xcode, const int8_t* in, uint8_t* blk) {
+    const int top = xcode == 7 ? 31 : 15;
+    uint32_t qh = 0;
+    uint8_t* qs = blk + (xcode == 7 ? 8 : 4);
+    for (int j = 0; j < 16; ++j) {
+        int a = in[j], b = in[j + 16];
+        a = a < 0 ? 0 : (a > top ? top : a);
+        b = b < 0 ? 0 : (b > top ? top : b);
+        qs[j] = (uint8_t)((a & 0x0F) | ((b & 0x0F) << 4));
+        qh |= (uint32_t)(a >> 4) << j;
+        qh |= (uint32_t)(b >> 4) << (j + 16);
+    }
+    if (xcode == 7) memcpy(blk + 4, &qh, 4);
+}
+
 void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // the int8 weights of one ggml block
-    if (xcode == 5) {
+    if (xcode == 6 || xcode == 7) {
+        decode_q4_1(xcode, blk, out);
+    } else if (xcode == 5) {
         decode_iq4_xs(blk, out);
     } else if (xcode == 4) {
         decode_q5_K(blk, out);
@@ -325,6 +358,10 @@ void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inv
         encode_iq4_xs(in, blk);
         return;
     }
+    if (xcode == 6 || xcode == 7) {
+        encode_q4_1(xcode, in, blk);
+        return;
+    }
     if (xcode == 1) {
         uint32_t qh = 0;
         uint8_t* qs = blk + 6;
@@ -353,7 +390,7 @@ void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inv
 // The type whose kernels and device regions serve a weight type (itself, or Q8_0 for the decoded types); 0 = not built.
 extern "C" uint32_t ac_b200_device_type(uint32_t ggml_type) {
     switch (ggml_type) {
-        case 2: case 8: case 12: case 13: case 14: case 23: case 36: return ggml_type;
+        case 2: case 3: case 7: case 8: case 12: case 13: case 14: case 23: case 36: return ggml_type;
         case 6: case 20: return 8;
         default: return 0;
     }
@@ -378,9 +415,9 @@ extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, 
     *out_path = AC_B200_PATH_NONE;
     if (flags & ~(AC_B200_PLAN_EXACT | AC_B200_PLAN_HOST_LAUNCH | AC_B200_PLAN_PEERS | AC_B200_PLAN_WEIGHT_RANGE))
         return AC_ERR_INVALID_ARGUMENT;
-    const uint64_t blk = type == 2 || type == 8 ? 32 : (type == 12 || type == 13 || type == 14 || type == 23) ? 256 : type == 36 ? 128 : 0;
+    const uint64_t blk = (type == 2 || type == 8 || type == 3 || type == 7) ? 32 : (type == 12 || type == 13 || type == 14 || type == 23) ? 256 : type == 36 ? 128 : 0;
     if (!blk) return AC_ERR_FEATURE_NOT_SUPPORTED;
-    if (type == 14 || type == 13 || type == 23) {   // Q6_K, Q5_K, IQ4_XS: one kernel each (ameva_mmvqb_*); more than 8 rows in chunks of 8
+    if (type == 14 || type == 13 || type == 23 || type == 3 || type == 7) {   // Q6_K, Q5_K, IQ4_XS, Q4_1, Q5_1: one kernel each; more than 8 rows in chunks of 8
         if (M == 0 || N == 0 || K == 0 || K % blk) return AC_ERR_INVALID_SHAPE;
         *out_path = AC_B200_PATH_GEMV;
         return AC_SUCCESS;
@@ -490,6 +527,9 @@ extern "C" AcResult ac_b200_weight_exponent(uint32_t type, const void* ggml_bloc
             bound = 127.0f * d;
         } else if (type == 6) {
             bound = 16.0f * d;
+        } else if (type == 3 || type == 7) {   // d * q + m
+            const float m = half_to_float(h1);
+            bound = (type == 3 ? 15.0f : 31.0f) * d + (m < 0 ? -m : m);
         } else if (type == 23) {   // |ls - 32| <= 32, |kvalue| <= 127
             bound = 4064.0f * d;
         } else if (type == 13) {   // 6-bit scales and mins, 5-bit weights

@@ -24,7 +24,20 @@ __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 
 // sixteen decoded weights of a Q5_0 / IQ4_NL block: `part` 0 = elements 0..15 (low nibbles), 1 = elements 16..31
 __device__ __forceinline__ uint4 decode_piece(uint32_t xcode, const uint8_t* blk, uint32_t part) {
     uint32_t w[4] = {0u, 0u, 0u, 0u};
-    if (xcode == 5u) {
+    if (xcode == 6u || xcode == 7u) {
+        // Q4_1 / Q5_1: `part` 0 = elements 0..15 (low nibbles), 1 = elements 16..31 (high nibbles); Q5_1 adds bit 4 from qh
+        uint32_t qh = 0;
+        const uint8_t* qs = blk + (xcode == 7u ? 8u : 4u);
+        if (xcode == 7u) {
+            const uint16_t* h = reinterpret_cast<const uint16_t*>(blk + 4);
+            qh = (h[0] | ((uint32_t)h[1] << 16)) >> (16u * part);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint32_t nib = part ? (qs[i] >> 4) : (qs[i] & 0x0Fu);
+            w[i >> 2] |= (nib | (((qh >> i) & 1u) << 4)) << (8 * (i & 3));
+        }
+    } else if (xcode == 5u) {
         // IQ4_XS: piece `part` (0..15): sub-block ib = part / 2, low (part even) or high nibbles of qs[16 ib .. 16 ib + 15]
         const uint8_t* qs = blk + 8u + 16u * (part >> 1);
 #pragma unroll
@@ -131,6 +144,8 @@ static bool repack_codec(uint32_t type, RepackCodec* c, uint32_t* blk) {
         case 14: *c = {210, 0, 256, 192, 18, 3}; *blk = 256; return true; // Q6_K: ql, qh decoded to 256 int8; scales[16] + d kept
         case 13: *c = {176, 16, 256, 0, 16, 4}; *blk = 256; return true;  // Q5_K: qh, qs decoded to 256 bytes; d, dmin, scales kept
         case 23: *c = {136, 8, 256, 0, 8, 5}; *blk = 256; return true;    // IQ4_XS: qs decoded to 256 int8; d, scales_h, scales_l kept
+        case 3: *c = {20, 4, 32, 0, 4, 6}; *blk = 32; return true;        // Q4_1: qs decoded to 32 bytes; d, m kept
+        case 7: *c = {24, 4, 32, 0, 4, 7}; *blk = 32; return true;        // Q5_1: qh, qs decoded to 32 bytes; d, m kept
         default: return false;
     }
 }

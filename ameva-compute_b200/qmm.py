@@ -29,16 +29,21 @@ GGML_TYPE_Q6_K = 14
 GGML_TYPE_Q5_K = 13
 # IQ4_XS: kvalues_iq4nl[q4] decoded to int8, the block's first 8 bytes (d, scales_h, scales_l) kept; ameva_mmvqb_iq4_xs
 GGML_TYPE_IQ4_XS = 23
-BYTE_DECODED = (GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS)   # one GEMV kernel each, no tensor-core form, no fused variants
+# Q4_1 / Q5_1 (d * q + m per 32): q decoded to bytes, (d, m) kept as a 4-byte record; ameva_mmvq_q4_1 / _q5_1 over the
+# per-32 activations (whose records carry the sum of q8 the m term needs)
+GGML_TYPE_Q4_1, GGML_TYPE_Q5_1 = 3, 7
+BYTE_DECODED = (GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS, GGML_TYPE_Q4_1, GGML_TYPE_Q5_1)   # one GEMV kernel each, no tensor-core form, no fused variants
 TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s",
-              GGML_TYPE_Q6_K: "q6_K", GGML_TYPE_Q5_K: "q5_K", GGML_TYPE_IQ4_XS: "iq4_xs"}
+              GGML_TYPE_Q6_K: "q6_K", GGML_TYPE_Q5_K: "q5_K", GGML_TYPE_IQ4_XS: "iq4_xs", GGML_TYPE_Q4_1: "q4_1",
+              GGML_TYPE_Q5_1: "q5_1"}
 BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128, GGML_TYPE_Q6_K: 256,
-         GGML_TYPE_Q5_K: 256, GGML_TYPE_IQ4_XS: 256}
+         GGML_TYPE_Q5_K: 256, GGML_TYPE_IQ4_XS: 256, GGML_TYPE_Q4_1: 32, GGML_TYPE_Q5_1: 32}
 Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128, GGML_TYPE_Q6_K: 256, GGML_TYPE_Q5_K: 256,
-           GGML_TYPE_IQ4_XS: 256}   # payload bytes per block
+           GGML_TYPE_IQ4_XS: 256, GGML_TYPE_Q4_1: 32, GGML_TYPE_Q5_1: 32}   # payload bytes per block
 S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16, GGML_TYPE_Q6_K: 18, GGML_TYPE_Q5_K: 16,
-           GGML_TYPE_IQ4_XS: 8}     # scale bytes per block
-PER_256 = (GGML_TYPE_Q4_K,) + BYTE_DECODED   # types whose activations are quantized per 256 (Q8_K records)
+           GGML_TYPE_IQ4_XS: 8, GGML_TYPE_Q4_1: 4, GGML_TYPE_Q5_1: 4}     # scale bytes per block
+PER_256 = (GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS)   # types whose activations are quantized per 256 (Q8_K records)
+PER_32 = (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_1, GGML_TYPE_Q5_1)         # per 32 (fp16 d | int16 sum per block)
 FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in shared memory
 
 
@@ -240,7 +245,7 @@ class MulMat:
         self.qbind, self.sbind = _bindings_for(self.view)
         K = self.K
         self.aq = ctx.buffer(max_m * K)
-        if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
+        if self.type in PER_32:
             self.ad = ctx.buffer(max_m * (K // 32) * 4)
         elif self.type in PER_256:
             self.ad = ctx.buffer(max_m * (K // 256) * AB_BYTES)
@@ -301,7 +306,7 @@ class MulMat:
                            [N, K, mode], ((N + 15) // 16, 1, 1))
             return
         if quantize:
-            if t in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
+            if t in PER_32:
                 binds = [(x, x_offset), self.aq, self.ad] + ([self.ah, self.ae] if use_tc else [])
                 batch.dispatch(ctx.kernel("ameva_quant_a8_f16" if use_tc else "ameva_quant_a8"), binds,
                                [M, K, K, self.round_mode], ((M * (K // 32) * 8 + 255) // 256, 1, 1))
@@ -430,7 +435,7 @@ class MulMat:
         """The activation scratch of the last run, in oracle-comparable form."""
         K = self.K
         q = self.aq.read(np.int8, M * K).reshape(M, K)
-        if self.type in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0):
+        if self.type in PER_32:
             ad = self.ad.read(np.uint32, M * (K // 32)).reshape(M, K // 32)
             return q, (ad & 0xFFFF).astype(np.uint16), (ad >> 16).astype(np.uint16).view(np.int16)
         if self.type in PER_256:

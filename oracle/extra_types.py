@@ -317,3 +317,76 @@ def mul_mat_iq4_xs_q8_K(W, A, M: int, N: int, K: int) -> np.ndarray:
             acc = (acc + terms[:, b]).astype(np.float32)
         out[m] = acc
     return out
+
+
+# ---- Q4_1 / Q5_1 -----------------------------------------------------------------------------------------------------------
+# ggml-common.h block_q4_1: d, m fp16, qs[16] (20 bytes); block_q5_1: d, m, qh[4], qs[16] (24 bytes); weight = d * q + m,
+# low nibbles = elements 0..15, high nibbles = 16..31 (Q5_1: bit 4 from qh). ggml_vec_dot_q4_1_q8_1 / _q5_1_q8_1:
+# sumf += (d_w * d_a) * sum q * q8 + m_w * s_a with s_a = d_a * sum q8 (an fp16 field of the Q8_1 block in ggml; here the
+# product of the Q8_0 block's fp16 d and the exact integer sum, in fp32: the two differ by the fp16 rounding of s_a).
+Q4_1, Q5_1 = 3, 7
+BLOCK_BYTES[Q4_1], BLOCK_BYTES[Q5_1] = 20, 24
+
+
+def quantize_q4_1(w, bits: int = 4) -> np.ndarray:
+    """ggml's quantize_row_q4_1_ref / q5_1_ref: d = (max - min) / (2^bits - 1), m = min, q = (int)((x - min) / d + 0.5)."""
+    top = (1 << bits) - 1
+    x = np.ascontiguousarray(w, np.float32).reshape(-1, 32)
+    mn, mx = x.min(axis=1), x.max(axis=1)
+    d = ((mx - mn) / np.float32(top)).astype(np.float32)
+    inv = np.where(d != 0, np.float32(1.0) / np.where(d != 0, d, np.float32(1.0)), np.float32(0.0)).astype(np.float32)
+    q = np.minimum(top, (((x - mn[:, None]) * inv[:, None]).astype(np.float32) + np.float32(0.5)).astype(np.int32)).astype(np.int32)
+    nb = 20 if bits == 4 else 24
+    out = np.zeros((x.shape[0], nb), np.uint8)
+    out[:, 0:2] = d.astype(np.float16).view(np.uint8).reshape(-1, 2)
+    out[:, 2:4] = mn.astype(np.float16).view(np.uint8).reshape(-1, 2)
+    lo, hi = q[:, :16], q[:, 16:]
+    out[:, nb - 16:nb] = ((lo & 0x0F) | ((hi & 0x0F) << 4)).astype(np.uint8)
+    if bits == 5:
+        qh = np.zeros(x.shape[0], np.uint32)
+        for j in range(16):
+            qh |= ((lo[:, j] >> 4).astype(np.uint32) << np.uint32(j)) | ((hi[:, j] >> 4).astype(np.uint32) << np.uint32(j + 16))
+        out[:, 4:8] = qh.view(np.uint8).reshape(-1, 4)
+    return out.reshape(-1)
+
+
+def quantize_q5_1(w) -> np.ndarray:
+    return quantize_q4_1(w, 5)
+
+
+def decode_q4_1(ggml_type: int, blocks):
+    """(d, m fp16 [n], q uint8 [n][32]) of n blocks."""
+    nb = BLOCK_BYTES[ggml_type]
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, nb)
+    d = b[:, 0:2].copy().view(np.float16).reshape(-1)
+    m = b[:, 2:4].copy().view(np.float16).reshape(-1)
+    qs = b[:, nb - 16:nb].astype(np.int32)
+    lo, hi = qs & 0x0F, qs >> 4
+    if ggml_type == Q5_1:
+        qh = b[:, 4:8].copy().view(np.uint32).reshape(-1)
+        j = np.arange(16, dtype=np.uint32)
+        lo = lo | (((qh[:, None] >> j[None, :]) & 1).astype(np.int32) << 4)
+        hi = hi | (((qh[:, None] >> (j[None, :] + np.uint32(16))) & 1).astype(np.int32) << 4)
+    return d, m, np.concatenate([lo, hi], axis=1).astype(np.uint8)
+
+
+def dequantize_q4_1(ggml_type: int, blocks) -> np.ndarray:
+    d, m, q = decode_q4_1(ggml_type, blocks)
+    return (d.astype(np.float32)[:, None] * q.astype(np.float32) + m.astype(np.float32)[:, None]).astype(np.float32).reshape(-1)
+
+
+def mul_mat_q4_1_q8_0(ggml_type: int, W, A, M: int, N: int, K: int) -> np.ndarray:
+    """W: Q4_1 / Q5_1 blocks [N][K/32]; A: Q8_0 blocks [M][K/32] (34 bytes: fp16 d, 32 int8) -> fp32 [M][N]."""
+    U = K // 32
+    d, mw, q = decode_q4_1(ggml_type, W)
+    d, mw, q = d.reshape(N, U).astype(np.float32), mw.reshape(N, U).astype(np.float32), q.reshape(N, U, 32).astype(np.int64)
+    a = np.ascontiguousarray(A, np.uint8).reshape(M, U, 34)
+    da = a[:, :, 0:2].copy().view(np.float16).reshape(M, U).astype(np.float32)
+    q8 = a[:, :, 2:34].copy().view(np.int8).reshape(M, U, 32).astype(np.int64)
+    out = np.zeros((M, N), np.float32)
+    for m in range(M):
+        sumi = np.einsum("nui,ui->nu", q, q8[m]).astype(np.float32)
+        s_a = (da[m] * q8[m].sum(axis=1).astype(np.float32)).astype(np.float32)
+        terms = ((d * da[m][None, :]).astype(np.float32) * sumi + mw * s_a[None, :]).astype(np.float32)
+        out[m] = terms.astype(np.float64).sum(axis=1).astype(np.float32)
+    return out

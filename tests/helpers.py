@@ -8,7 +8,8 @@ from oracle import extra_types
 Q4_0, Q8_0, Q4_K, I2_S = 2, 8, 12, 36
 Q5_0, IQ4_NL = 6, 20   # kept on the device as Q8_0 regions (oracle/extra_types.py)
 Q6_K, Q5_K, IQ4_XS = 14, 13, 23    # decoded to bytes at upload, a kernel of their own over Q8_K activations
-WEIGHT_STD = {Q4_0: 0.02, Q8_0: 0.02, Q4_K: 0.02, I2_S: 1.0, Q5_0: 0.02, IQ4_NL: 0.02, Q6_K: 0.02, Q5_K: 0.02, IQ4_XS: 0.02}
+Q4_1, Q5_1 = 3, 7                  # likewise, over the per-32 activations
+WEIGHT_STD = {Q4_0: 0.02, Q8_0: 0.02, Q4_K: 0.02, I2_S: 1.0, Q5_0: 0.02, IQ4_NL: 0.02, Q6_K: 0.02, Q5_K: 0.02, IQ4_XS: 0.02, Q4_1: 0.02, Q5_1: 0.02}
 
 
 def make_weights(ggml_type, N, K, seed=0, std=None):
@@ -30,6 +31,8 @@ def make_weights(ggml_type, N, K, seed=0, std=None):
         return extra_types.quantize_q5_K(w), 1.0
     if ggml_type == IQ4_XS:
         return extra_types.quantize_iq4_xs(w), 1.0
+    if ggml_type in (Q4_1, Q5_1):
+        return extra_types.quantize_q4_1(w, 4 if ggml_type == Q4_1 else 5), 1.0
     return oracle.quantize_i2_s(w)
 
 
@@ -42,6 +45,9 @@ def oracle_mul_mat(ggml_type, blocks, scale, x, N, K, round_mode=0, q8k_mode=0, 
     M = x.shape[0]
     if ggml_type in (Q5_0, IQ4_NL):   # the same integers and scales as Q8_0 blocks: the Q8_0 x Q8_0 arithmetic
         blocks, ggml_type = extra_types.to_q8_0(ggml_type, blocks), Q8_0
+    if ggml_type in (Q4_1, Q5_1):
+        aq = oracle.quantize_q8_0(x, round_mode)
+        return extra_types.mul_mat_q4_1_q8_0(ggml_type, blocks, aq, M, N, K), None, aq
     if ggml_type in (Q4_0, Q8_0):
         aq = oracle.quantize_q8_0(x, round_mode)
         fn = oracle.mul_mat_q4_0_q8_0 if ggml_type == Q4_0 else oracle.mul_mat_q8_0_q8_0

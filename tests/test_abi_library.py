@@ -220,7 +220,7 @@ def test_q5_0_and_iq4_nl_become_q8_0_regions():
     from oracle import extra_types as et
     lib = rt.load_library()
     lib.ac_b200_device_type.restype = C.c_uint32
-    assert [lib.ac_b200_device_type(t) for t in (2, 8, 12, 36, 6, 20, 14, 13, 23, 10)] == [2, 8, 12, 36, 8, 8, 14, 13, 23, 0]
+    assert [lib.ac_b200_device_type(t) for t in (2, 8, 12, 36, 6, 20, 14, 13, 23, 3, 7, 10)] == [2, 8, 12, 36, 8, 8, 14, 13, 23, 3, 7, 0]
     rng = np.random.default_rng(4)
     w = (rng.standard_normal((5, 512)) * 0.02).astype(np.float32)
     for t, pack in ((et.Q5_0, et.quantize_q5_0), (et.IQ4_NL, et.quantize_iq4_nl)):

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from conftest import load_pkg
-from helpers import IQ4_NL, IQ4_XS, Q5_0, Q5_K, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+from helpers import IQ4_NL, IQ4_XS, Q4_1, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
 from oracle import extra_types
 
 pytestmark = pytest.mark.gpu
@@ -168,3 +168,29 @@ def test_iq4_xs_mul_mat(ctx, M, N, K):
     assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
     for o in (mm, xb, dst, w):
         o.destroy()
+
+
+@pytest.mark.parametrize("t", [Q4_1, Q5_1])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (3, 1000, 96), (8, 130, 2048), (33, 768, 2048)])
+def test_q4_1_and_q5_1(ctx, t, M, N, K):
+    """d * q + m weights: q decoded to bytes and (d, m) kept at upload, read-back byte-exact, ameva_mmvq_q4_1 / _q5_1 over the
+    per-32 activations against the numpy restatement of ggml_vec_dot_q4_1_q8_1 / _q5_1_q8_1."""
+    blocks, scale = make_weights(t, N, K, M)
+    x = make_acts(M, K, M + 1)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K)
+    host = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, host_repack=True)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    try:
+        assert np.array_equal(w.to_ggml(), blocks) and np.array_equal(host.to_ggml(), blocks)
+        d, m, q = extra_types.decode_q4_1(t, blocks)
+        for wt in (w, host):
+            assert np.array_equal(wt.buf.read(np.uint8, N * K), q.reshape(-1))
+            rec = wt.buf.read(np.uint16, N * (K // 32) * 2, wt.s_off).reshape(-1, 2)
+            assert np.array_equal(rec[:, 0], d.view(np.uint16)) and np.array_equal(rec[:, 1], m.view(np.uint16))
+        mm.run(xb, dst, M)
+        want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+        assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
+    finally:
+        for o in (mm, xb, dst, w, host):
+            o.destroy()

@@ -220,3 +220,16 @@ def test_iq4_xs_decode_equals_gguf_py():
     raw = rng.integers(0, 256, (8, 136), dtype=np.uint8)
     raw[:, 0], raw[:, 1] = 0, 0x1C
     assert np.array_equal(et.dequantize_iq4_xs(raw.reshape(-1)), quants.dequantize(raw, gguf.GGMLQuantizationType.IQ4_XS).reshape(-1))
+
+
+def test_q4_1_and_q5_1_equal_gguf_py():
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    from oracle import extra_types as et
+    rng = np.random.default_rng(15)
+    w = (rng.standard_normal((16, 256)) * 0.05).astype(np.float32)
+    w[0, :32] = 0.0
+    for t, qt, bits in ((et.Q4_1, gguf.GGMLQuantizationType.Q4_1, 4), (et.Q5_1, gguf.GGMLQuantizationType.Q5_1, 5)):
+        blocks = et.quantize_q4_1(w, bits)
+        assert np.array_equal(blocks, quants.quantize(w, qt).reshape(-1))
+        assert np.array_equal(et.dequantize_q4_1(t, blocks), quants.dequantize(blocks.reshape(16, -1), qt).reshape(-1))
