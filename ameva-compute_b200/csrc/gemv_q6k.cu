@@ -412,4 +412,127 @@ AcResult launch_mmvq_q4_1(const LaunchArgs& a) {
     return check_launch();
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Q3_K and Q2_K x Q8_K. Q3_K: a weight is d * (scale[e / 16] - 32) * q3, q3 = -4..3 from two bits of qs and one of hmask,
+// scale six bits packed in scales[12] (ggml-common.h block_q3_K: hmask[32], qs[64], scales[12], d: 110 bytes per 256
+// weights); the upload decodes q3 to int8 and keeps scales[12] + d as a 14-byte record. Q2_K: d * (sc[e / 16] & 15) * q2
+// - dmin * (sc[e / 16] >> 4), q2 = 0..3 (block_q2_K: scales[16], qs[64], d, dmin: 84 bytes); the upload decodes q2 to
+// bytes and keeps scales[16], d, dmin as a 20-byte record. Sums as ggml_vec_dot_q3_K_q8_K / _q2_K_q8_K (generic branch)
+// form them; Q2_K's min term uses the Q8_K sum of the same 16 activations. KIND 3 / 2 selects the type.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int M, int KIND>
+__device__ __forceinline__ void group_dot_q23(const uint4 w, uint32_t gi, const uint8_t* s, const int8_t* __restrict__ AQ,
+                                              const uint8_t* __restrict__ AB, uint32_t K, uint32_t B, float (&acc)[M]) {
+    constexpr uint32_t kRec = KIND == 3 ? 14u : 20u;
+    const uint32_t blk = gi >> 4, g = gi & 15u;
+    const uint8_t* rec = s + blk * kRec;
+    int sc, mn = 0;
+    float dw, dmin = 0.0f;
+    if (KIND == 3) {
+        const uint32_t lo = g < 8u ? (rec[g] & 0x0Fu) : (rec[g - 8u] >> 4);
+        const uint32_t hi = (rec[8u + (g & 3u)] >> (2u * (g >> 2))) & 3u;
+        sc = (int)(lo | (hi << 4)) - 32;
+        dw = h2f((uint16_t)(rec[12] | ((uint32_t)rec[13] << 8)));
+    } else {
+        sc = rec[g] & 0x0F;
+        mn = rec[g] >> 4;
+        dw = h2f((uint16_t)(rec[16] | ((uint32_t)rec[17] << 8)));
+        dmin = h2f((uint16_t)(rec[18] | ((uint32_t)rec[19] << 8)));
+    }
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const uint4 a = *reinterpret_cast<const uint4*>(AQ + (size_t)m * K + 16u * gi);
+        int t = dp4a_ss(w.x, a.x, 0);
+        t = dp4a_ss(w.y, a.y, t);
+        t = dp4a_ss(w.z, a.z, t);
+        t = dp4a_ss(w.w, a.w, t);
+        const uint8_t* ab = AB + ((size_t)m * B + blk) * kABBytes;
+        const float da = *reinterpret_cast<const float*>(ab + 32);
+        if (KIND == 3) {
+            acc[m] = fmaf(dw * da, (float)(sc * t), acc[m]);
+        } else {
+            const int bs = (int)reinterpret_cast<const int16_t*>(ab)[g];
+            acc[m] += (dw * da) * (float)(sc * t) - (dmin * da) * (float)(mn * bs);
+        }
+    }
+}
+
+template <int M, int KIND>
+__global__ void __launch_bounds__(kQ6Warps * 32) gemv_q23k_kernel(const uint8_t* __restrict__ Q, const uint8_t* __restrict__ S,
+                                                                  const int8_t* __restrict__ AQ, const uint8_t* __restrict__ AB,
+                                                                  float* __restrict__ dst, uint32_t N, uint32_t K,
+                                                                  uint32_t dst_stride) {
+    constexpr uint32_t kRec = KIND == 3 ? 14u : 20u;
+    pdl_wait();
+    pdl_trigger();
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t row = blockIdx.x * kQ6Warps + warp;
+    if (row >= N) return;
+    const uint32_t B = K >> 8, groups = K >> 4;
+    const uint4* q = reinterpret_cast<const uint4*>(Q + (size_t)row * K);
+    extern __shared__ __align__(16) uint8_t q23_smem[];
+    uint8_t* s = q23_smem + (size_t)warp * B * kRec;
+    {   // the row's scale records, by 2-byte loads (a record is 14 or 20 bytes)
+        const uint16_t* src = reinterpret_cast<const uint16_t*>(S + (size_t)row * B * kRec);
+        uint16_t* dstp = reinterpret_cast<uint16_t*>(s);
+        for (uint32_t i = lane; i < B * (kRec / 2u); i += 32u) dstp[i] = __ldg(src + i);
+        __syncwarp();
+    }
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+    uint32_t gi = lane;
+    for (; gi + 32u * 3u < groups; gi += 32u * 4u) {
+        uint4 w[4];
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u) w[u] = ld_stream_u4(q + gi + 32u * u);
+#pragma unroll
+        for (uint32_t u = 0; u < 4u; ++u) group_dot_q23<M, KIND>(w[u], gi + 32u * u, s, AQ, AB, K, B, acc);
+    }
+    for (; gi < groups; gi += 32u) group_dot_q23<M, KIND>(ld_stream_u4(q + gi), gi, s, AQ, AB, K, B, acc);
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+        const float v = warp_sum(acc[m]);
+        if (lane == 0) dst[(size_t)m * dst_stride + row] = v;
+    }
+}
+
+template <int M, int KIND>
+static void launch_q23k_m(const LaunchArgs& a, uint32_t N, uint32_t K, uint32_t dst_stride) {
+    const size_t smem = (size_t)kQ6Warps * (K >> 8) * (KIND == 3 ? 14u : 20u);   // (K <= 65536: at most 40 KB)
+    launch_pdl(gemv_q23k_kernel<M, KIND>, dim3((N + kQ6Warps - 1) / kQ6Warps), dim3(kQ6Warps * 32), smem, a.stream,
+               (const uint8_t*)a.ptr[0], (const uint8_t*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
+               (float*)a.ptr[4], N, K, dst_stride);
+}
+
+template <int KIND>
+static AcResult launch_q23k(const LaunchArgs& a) {
+    constexpr uint32_t kRec = KIND == 3 ? 14u : 20u;
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (M == 0 || M > 8) return AC_ERR_INVALID_SHAPE;
+    if (N == 0 || K == 0 || (K & 255u) || K > 65536u || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t B = K >> 8;
+    if (a.range[0] < (uint64_t)N * K || a.range[1] < (uint64_t)N * B * kRec || a.range[2] < (uint64_t)M * K ||
+        a.range[3] < (uint64_t)M * B * kABBytes || a.range[4] < ((uint64_t)(M - 1) * dst_stride + N) * 4u)
+        return AC_ERR_INVALID_BUFFER_SIZE;
+    if ((((uintptr_t)a.ptr[0] | (uintptr_t)a.ptr[2]) & 15u) || ((uintptr_t)a.ptr[1] & 1u)) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    switch (M) {
+        case 1: launch_q23k_m<1, KIND>(a, N, K, dst_stride); break;
+        case 2: launch_q23k_m<2, KIND>(a, N, K, dst_stride); break;
+        case 3: launch_q23k_m<3, KIND>(a, N, K, dst_stride); break;
+        case 4: launch_q23k_m<4, KIND>(a, N, K, dst_stride); break;
+        case 5: launch_q23k_m<5, KIND>(a, N, K, dst_stride); break;
+        case 6: launch_q23k_m<6, KIND>(a, N, K, dst_stride); break;
+        case 7: launch_q23k_m<7, KIND>(a, N, K, dst_stride); break;
+        default: launch_q23k_m<8, KIND>(a, N, K, dst_stride); break;
+    }
+    return check_launch();
+}
+
+// ameva_mmvqb_q3_K: bindings 0 Q (int8 [N][K], q3 decoded at upload), 1 S (14-byte records [N][K/256]: scales[12], d),
+// 2 AQ int8 [M][K], 3 AB (48-byte Q8_K records), 4 dst f32; push {M (1..8), N, K (% 256, <= 65536), dst_stride}
+AcResult launch_mmvqb_q3_K(const LaunchArgs& a) { return launch_q23k<3>(a); }
+// ameva_mmvqb_q2_K: the same with Q bytes 0..3 and 20-byte records (scales[16], d, dmin)
+AcResult launch_mmvqb_q2_K(const LaunchArgs& a) { return launch_q23k<2>(a); }
+
 }  // namespace amv

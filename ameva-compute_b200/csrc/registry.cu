@@ -50,6 +50,8 @@ AcResult launch_mmvqb_q6_K(const LaunchArgs&);
 AcResult launch_mmvqb_q5_K(const LaunchArgs&);
 AcResult launch_mmvqb_iq4_xs(const LaunchArgs&);
 AcResult launch_mmvq_q4_1(const LaunchArgs&);
+AcResult launch_mmvqb_q3_K(const LaunchArgs&);
+AcResult launch_mmvqb_q2_K(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
 AcResult launch_mmvs_q4_K(const LaunchArgs&);
@@ -127,6 +129,8 @@ static const KernelEntry kTable[] = {
     {"ameva_mmvqb_q6_K", 5, 16, {256, 1, 1}, launch_mmvqb_q6_K},
     {"ameva_mmvqb_q5_K", 5, 16, {256, 1, 1}, launch_mmvqb_q5_K},
     {"ameva_mmvqb_iq4_xs", 5, 16, {256, 1, 1}, launch_mmvqb_iq4_xs},
+    {"ameva_mmvqb_q3_K", 5, 16, {256, 1, 1}, launch_mmvqb_q3_K},
+    {"ameva_mmvqb_q2_K", 5, 16, {256, 1, 1}, launch_mmvqb_q2_K},
     {"ameva_mmvq_q4_1", 5, 16, {256, 1, 1}, launch_mmvq_q4_1},
     {"ameva_mmvq_q5_1", 5, 16, {256, 1, 1}, launch_mmvq_q4_1},
     {"ameva_mmvq_q4_0_ep", 7, 20, {256, 1, 1}, launch_mmvq_q4_0_ep},
@@ -211,6 +215,8 @@ bool codec_for(uint32_t type, Codec* c) {
         case 14: *c = {256, 210, 0, 256, 192, 18, 3}; return true;  // Q6_K: ql[128]@0, qh[64]@128, scales[16]@192, d@208
         case 13: *c = {256, 176, 16, 256, 0, 16, 4}; return true;   // Q5_K: d, dmin, scales[12] @0, qh[32]@16, qs[128]@48
         case 23: *c = {256, 136, 8, 256, 0, 8, 5}; return true;     // IQ4_XS: d, scales_h, scales_l[4] @0, qs[128]@8
+        case 11: *c = {256, 110, 0, 256, 96, 14, 8}; return true;   // Q3_K: hmask[32]@0, qs[64]@32, scales[12]@96, d@108
+        case 10: *c = {256, 84, 16, 256, 0, 20, 9}; return true;    // Q2_K: scales[16]@0, qs[64]@16, d@80, dmin@82 (record: 16 + 4 bytes)
         case 3: *c = {32, 20, 4, 32, 0, 4, 6}; return true;         // Q4_1: d, m @0, qs[16]@4
         case 7: *c = {32, 24, 4, 32, 0, 4, 7}; return true;         // Q5_1: d, m @0, qh[4]@4, qs[16]@8
         default: return false;
@@ -320,8 +326,37 @@ void encode_q4_1(uint32_t xcode, const int8_t* in, uint8_t* blk) {
     if (xcode == 7) memcpy(blk + 4, &qh, 4);
 }
 
+// Q3_K (xcode 8): q3 = (two bits of qs) - (hmask bit ? 0 : 4), -4..3, as 256 int8 in element order (element e: byte
+// qs[32 (e / 128) + e % 32], shift 2 ((e % 128) / 32), hmask[e % 32] bit e / 32); scales[12] + d kept (14 bytes).
+// Q2_K (xcode 9): q2 = two bits of qs (0..3) the same way; the record is scales[16] followed by d, dmin (20 bytes).
+void decode_q23_K(uint32_t xcode, const uint8_t* blk, int8_t* out) {
+    const uint8_t* qs = blk + (xcode == 8 ? 32 : 16);
+    for (int e = 0; e < 256; ++e) {
+        const int v = (qs[32 * (e >> 7) + (e & 31)] >> (2 * ((e & 127) >> 5))) & 3;
+        out[e] = (int8_t)(xcode == 8 ? v - (((blk[e & 31] >> (e >> 5)) & 1) ? 0 : 4) : v);
+    }
+}
+void encode_q23_K(uint32_t xcode, const int8_t* in, uint8_t* blk) {
+    uint8_t* qs = blk + (xcode == 8 ? 32 : 16);
+    memset(qs, 0, 64);
+    if (xcode == 8) memset(blk, 0, 32);
+    for (int e = 0; e < 256; ++e) {
+        int v = in[e];
+        if (xcode == 8) {
+            v = v < -4 ? -4 : (v > 3 ? 3 : v);
+            if (v >= 0) blk[e & 31] |= (uint8_t)(1u << (e >> 5));
+            else v += 4;
+        } else {
+            v = v < 0 ? 0 : (v > 3 ? 3 : v);
+        }
+        qs[32 * (e >> 7) + (e & 31)] |= (uint8_t)(v << (2 * ((e & 127) >> 5)));
+    }
+}
+
 void decode_block(uint32_t xcode, const uint8_t* blk, int8_t* out) {   // the int8 weights of one ggml block
-    if (xcode == 6 || xcode == 7) {
+    if (xcode == 8 || xcode == 9) {
+        decode_q23_K(xcode, blk, out);
+    } else if (xcode == 6 || xcode == 7) {
         decode_q4_1(xcode, blk, out);
     } else if (xcode == 5) {
         decode_iq4_xs(blk, out);
@@ -362,6 +397,10 @@ void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inv
         encode_q4_1(xcode, in, blk);
         return;
     }
+    if (xcode == 8 || xcode == 9) {
+        encode_q23_K(xcode, in, blk);
+        return;
+    }
     if (xcode == 1) {
         uint32_t qh = 0;
         uint8_t* qs = blk + 6;
@@ -390,7 +429,7 @@ void encode_block(uint32_t xcode, const int8_t* in, uint8_t* blk) {   // the inv
 // The type whose kernels and device regions serve a weight type (itself, or Q8_0 for the decoded types); 0 = not built.
 extern "C" uint32_t ac_b200_device_type(uint32_t ggml_type) {
     switch (ggml_type) {
-        case 2: case 3: case 7: case 8: case 12: case 13: case 14: case 23: case 36: return ggml_type;
+        case 2: case 3: case 7: case 8: case 10: case 11: case 12: case 13: case 14: case 23: case 36: return ggml_type;
         case 6: case 20: return 8;
         default: return 0;
     }
@@ -415,9 +454,9 @@ extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, 
     *out_path = AC_B200_PATH_NONE;
     if (flags & ~(AC_B200_PLAN_EXACT | AC_B200_PLAN_HOST_LAUNCH | AC_B200_PLAN_PEERS | AC_B200_PLAN_WEIGHT_RANGE))
         return AC_ERR_INVALID_ARGUMENT;
-    const uint64_t blk = (type == 2 || type == 8 || type == 3 || type == 7) ? 32 : (type == 12 || type == 13 || type == 14 || type == 23) ? 256 : type == 36 ? 128 : 0;
+    const uint64_t blk = (type == 2 || type == 8 || type == 3 || type == 7) ? 32 : (type == 12 || type == 13 || type == 14 || type == 23 || type == 10 || type == 11) ? 256 : type == 36 ? 128 : 0;
     if (!blk) return AC_ERR_FEATURE_NOT_SUPPORTED;
-    if (type == 14 || type == 13 || type == 23 || type == 3 || type == 7) {   // Q6_K, Q5_K, IQ4_XS, Q4_1, Q5_1: one kernel each; more than 8 rows in chunks of 8
+    if (type == 14 || type == 13 || type == 23 || type == 3 || type == 7 || type == 10 || type == 11) {   // Q6_K, Q5_K, IQ4_XS, Q4_1, Q5_1, Q3_K, Q2_K: one kernel each; more than 8 rows in chunks of 8
         if (M == 0 || N == 0 || K == 0 || K % blk) return AC_ERR_INVALID_SHAPE;
         *out_path = AC_B200_PATH_GEMV;
         return AC_SUCCESS;
@@ -527,6 +566,17 @@ extern "C" AcResult ac_b200_weight_exponent(uint32_t type, const void* ggml_bloc
             bound = 127.0f * d;
         } else if (type == 6) {
             bound = 16.0f * d;
+        } else if (type == 11) {   // |scale - 32| <= 32, |q3| <= 4; d at byte 108
+            uint16_t hd;
+            memcpy(&hd, b + 108, 2);
+            const float dd = half_to_float(hd);
+            bound = 128.0f * (dd < 0 ? -dd : dd);
+        } else if (type == 10) {   // sc <= 15, q2 <= 3, min <= 15; d at byte 80, dmin at 82
+            uint16_t hd, hm;
+            memcpy(&hd, b + 80, 2);
+            memcpy(&hm, b + 82, 2);
+            const float dd = half_to_float(hd), mm = half_to_float(hm);
+            bound = 45.0f * (dd < 0 ? -dd : dd) + 15.0f * (mm < 0 ? -mm : mm);
         } else if (type == 3 || type == 7) {   // d * q + m
             const float m = half_to_float(h1);
             bound = (type == 3 ? 15.0f : 31.0f) * d + (m < 0 ? -m : m);
@@ -591,7 +641,12 @@ extern "C" AcResult ac_b200_repack_to_device(uint32_t type, const void* src, uin
     for (uint64_t i = 0; i < nblk; ++i) {
         if (c.xcode) decode_block(c.xcode, s + i * c.blk_bytes, (int8_t*)(q + i * c.q_bytes));
         else memcpy(q + i * c.q_bytes, s + i * c.blk_bytes + c.q_off, c.q_bytes);
-        memcpy(sc + i * c.s_bytes, s + i * c.blk_bytes + c.s_off, c.s_bytes);
+        if (c.xcode == 9) {   // Q2_K: scales[16] at the start of the block, d and dmin at its end
+            memcpy(sc + i * c.s_bytes, s + i * c.blk_bytes, 16);
+            memcpy(sc + i * c.s_bytes + 16, s + i * c.blk_bytes + 80, 4);
+        } else {
+            memcpy(sc + i * c.s_bytes, s + i * c.blk_bytes + c.s_off, c.s_bytes);
+        }
     }
     return AC_SUCCESS;
 }
@@ -616,7 +671,12 @@ extern "C" AcResult ac_b200_repack_from_device(uint32_t type, const void* src, u
         } else {
             memcpy(d + i * c.blk_bytes + c.q_off, q + i * c.q_bytes, c.q_bytes);
         }
-        memcpy(d + i * c.blk_bytes + c.s_off, sc + i * c.s_bytes, c.s_bytes);
+        if (c.xcode == 9) {
+            memcpy(d + i * c.blk_bytes, sc + i * c.s_bytes, 16);
+            memcpy(d + i * c.blk_bytes + 80, sc + i * c.s_bytes + 16, 4);
+        } else {
+            memcpy(d + i * c.blk_bytes + c.s_off, sc + i * c.s_bytes, c.s_bytes);
+        }
     }
     return AC_SUCCESS;
 }

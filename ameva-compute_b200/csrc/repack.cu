@@ -24,7 +24,19 @@ __constant__ int8_t c_iq4nl[16] = {-127, -104, -83, -65, -49, -35, -22, -10, 1, 
 // sixteen decoded weights of a Q5_0 / IQ4_NL block: `part` 0 = elements 0..15 (low nibbles), 1 = elements 16..31
 __device__ __forceinline__ uint4 decode_piece(uint32_t xcode, const uint8_t* blk, uint32_t part) {
     uint32_t w[4] = {0u, 0u, 0u, 0u};
-    if (xcode == 6u || xcode == 7u) {
+    if (xcode == 8u || xcode == 9u) {
+        // Q3_K / Q2_K: piece `part` (0..15) = elements 16 part ..: byte qs[32 (part / 8) + 16 (part % 2) + i], shift
+        // 2 ((part % 8) / 2); Q3_K subtracts 4 where the hmask bit (part / 2) of hmask[16 (part % 2) + i] is clear
+        const uint8_t* qs = blk + (xcode == 8u ? 32u : 16u) + 32u * (part >> 3) + 16u * (part & 1u);
+        const uint8_t* hm = blk + 16u * (part & 1u);
+        const uint32_t shift = 2u * ((part & 7u) >> 1), bit = part >> 1;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            int v = (int)((qs[i] >> shift) & 3u);
+            if (xcode == 8u && !((hm[i] >> bit) & 1u)) v -= 4;
+            w[i >> 2] |= (uint32_t)(v & 0xFF) << (8 * (i & 3));
+        }
+    } else if (xcode == 6u || xcode == 7u) {
         // Q4_1 / Q5_1: `part` 0 = elements 0..15 (low nibbles), 1 = elements 16..31 (high nibbles); Q5_1 adds bit 4 from qh
         uint32_t qh = 0;
         const uint8_t* qs = blk + (xcode == 7u ? 8u : 4u);
@@ -130,7 +142,9 @@ __global__ void __launch_bounds__(256) repack_kernel(const uint8_t* __restrict__
     uint16_t* sc = reinterpret_cast<uint16_t*>(dst_s + b0 * c.s_bytes);
     for (uint32_t p = threadIdx.x; p < s_halves; p += 256u) {
         const uint32_t blk = p / per_blk_s, part = p - blk * per_blk_s;
-        sc[p] = *reinterpret_cast<const uint16_t*>(tile + blk * c.blk_bytes + c.s_off + part * 2u);
+        // (Q2_K's record is two slices of the block: scales[16] at its start, d and dmin at bytes 80..83)
+        const uint32_t so = (c.xcode == 9u && part >= 8u) ? 64u + part * 2u : c.s_off + part * 2u;
+        sc[p] = *reinterpret_cast<const uint16_t*>(tile + blk * c.blk_bytes + so);
     }
 }
 
@@ -144,6 +158,8 @@ static bool repack_codec(uint32_t type, RepackCodec* c, uint32_t* blk) {
         case 14: *c = {210, 0, 256, 192, 18, 3}; *blk = 256; return true; // Q6_K: ql, qh decoded to 256 int8; scales[16] + d kept
         case 13: *c = {176, 16, 256, 0, 16, 4}; *blk = 256; return true;  // Q5_K: qh, qs decoded to 256 bytes; d, dmin, scales kept
         case 23: *c = {136, 8, 256, 0, 8, 5}; *blk = 256; return true;    // IQ4_XS: qs decoded to 256 int8; d, scales_h, scales_l kept
+        case 11: *c = {110, 0, 256, 96, 14, 8}; *blk = 256; return true;  // Q3_K: hmask, qs decoded to 256 int8; scales[12] + d kept
+        case 10: *c = {84, 16, 256, 0, 20, 9}; *blk = 256; return true;   // Q2_K: qs decoded to 256 bytes; scales[16], d, dmin kept
         case 3: *c = {20, 4, 32, 0, 4, 6}; *blk = 32; return true;        // Q4_1: qs decoded to 32 bytes; d, m kept
         case 7: *c = {24, 4, 32, 0, 4, 7}; *blk = 32; return true;        // Q5_1: qh, qs decoded to 32 bytes; d, m kept
         default: return false;

@@ -805,8 +805,8 @@ AcResult ac_b200_weight_upload(AcBuffer* buf, size_t offset, uint32_t type, cons
     if (offset % 64u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
     if (offset > buf->size || total > buf->size - offset) return AC_ERR_INVALID_BUFFER_SIZE;
     if (type == 36u) return ac_runtime_buffer_write(buf, offset, ggml_blocks, (size_t)total);   // I2_S: dense already
-    const uint32_t blk_bytes = (type == 2u || type == 20u) ? 18u : type == 8u ? 34u : type == 6u ? 22u : type == 3u ? 20u : type == 7u ? 24u : type == 14u ? 210u : type == 13u ? 176u : type == 23u ? 136u : 144u;
-    const uint32_t blk = (type == 12u || type == 13u || type == 14u || type == 23u) ? 256u : 32u;
+    const uint32_t blk_bytes = (type == 2u || type == 20u) ? 18u : type == 8u ? 34u : type == 6u ? 22u : type == 3u ? 20u : type == 7u ? 24u : type == 14u ? 210u : type == 13u ? 176u : type == 23u ? 136u : type == 11u ? 110u : type == 10u ? 84u : 144u;
+    const uint32_t blk = (type == 12u || type == 13u || type == 14u || type == 23u || type == 10u || type == 11u) ? 256u : 32u;
     const uint64_t nblk = rows * (k / blk);
     AcContext* ctx = buf->ctx;
     DeviceGuard g(ctx->device);

@@ -96,13 +96,17 @@ enum ggml_type dev_type(enum ggml_type t) { return (t == GGML_TYPE_Q5_0 || t == 
 bool repacked_type(enum ggml_type t) {
     t = dev_type(t);
     return t == GGML_TYPE_Q4_0 || t == GGML_TYPE_Q8_0 || t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K ||
-           t == GGML_TYPE_IQ4_XS || t == GGML_TYPE_Q4_1 || t == GGML_TYPE_Q5_1;
+           t == GGML_TYPE_IQ4_XS || t == GGML_TYPE_Q4_1 || t == GGML_TYPE_Q5_1 || t == GGML_TYPE_Q3_K || t == GGML_TYPE_Q2_K;
 }
 // activations quantized per 256 (Q8_K records) and the ameva_mmvqb kernel family
-bool per_256(enum ggml_type t) { return t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K || t == GGML_TYPE_IQ4_XS; }
+bool per_256(enum ggml_type t) {
+    return t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K || t == GGML_TYPE_IQ4_XS || t == GGML_TYPE_Q3_K ||
+           t == GGML_TYPE_Q2_K;
+}
 // types with one GEMV kernel each (weights decoded to bytes at upload): no fused, grouped or tensor-core variants
 bool byte_decoded(enum ggml_type t) {
-    return t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K || t == GGML_TYPE_IQ4_XS || t == GGML_TYPE_Q4_1 || t == GGML_TYPE_Q5_1;
+    return t == GGML_TYPE_Q6_K || t == GGML_TYPE_Q5_K || t == GGML_TYPE_IQ4_XS || t == GGML_TYPE_Q4_1 || t == GGML_TYPE_Q5_1 ||
+           t == GGML_TYPE_Q3_K || t == GGML_TYPE_Q2_K;
 }
 uint32_t block_elems(enum ggml_type t) { return per_256(t) ? 256u : 32u; }
 uint32_t payload_bytes(enum ggml_type t) {   // of the device regions
@@ -112,6 +116,8 @@ uint32_t payload_bytes(enum ggml_type t) {   // of the device regions
 }
 uint32_t scale_bytes(enum ggml_type t) {
     if (t == GGML_TYPE_Q4_1 || t == GGML_TYPE_Q5_1) return 4u;
+    if (t == GGML_TYPE_Q3_K) return 14u;
+    if (t == GGML_TYPE_Q2_K) return 20u;
     return (t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q5_K) ? 16u : (t == GGML_TYPE_Q6_K ? 18u : (t == GGML_TYPE_IQ4_XS ? 8u : 2u));
 }
 
@@ -714,6 +720,8 @@ bool dispatch(Recorder& r, const char* name, const AcBufferBinding* b, uint32_t 
 const char* type_name(enum ggml_type t) {
     if (t == GGML_TYPE_Q4_1) return "q4_1";
     if (t == GGML_TYPE_Q5_1) return "q5_1";
+    if (t == GGML_TYPE_Q3_K) return "q3_K";
+    if (t == GGML_TYPE_Q2_K) return "q2_K";
     return t == GGML_TYPE_Q4_0 ? "q4_0" : (t == GGML_TYPE_Q8_0 ? "q8_0" : (t == GGML_TYPE_Q6_K ? "q6_K" : (t == GGML_TYPE_Q5_K ? "q5_K" : (t == GGML_TYPE_IQ4_XS ? "iq4_xs" : "q4_K"))));
 }
 
@@ -1407,7 +1415,7 @@ const char* ggml_backend_ameva_abi_check(void) {
             enum ggml_type type;
             const char* name;
         } kTypes[] = {{GGML_TYPE_F32, "f32"}, {GGML_TYPE_Q4_0, "q4_0"}, {GGML_TYPE_Q8_0, "q8_0"}, {GGML_TYPE_Q4_K, "q4_K"},
-                      {GGML_TYPE_F16, "f16"}, {GGML_TYPE_I32, "i32"}, {GGML_TYPE_I64, "i64"}, {GGML_TYPE_Q6_K, "q6_K"}, {GGML_TYPE_Q5_K, "q5_K"}, {GGML_TYPE_IQ4_XS, "iq4_xs"}, {GGML_TYPE_Q4_1, "q4_1"}, {GGML_TYPE_Q5_1, "q5_1"}};
+                      {GGML_TYPE_F16, "f16"}, {GGML_TYPE_I32, "i32"}, {GGML_TYPE_I64, "i64"}, {GGML_TYPE_Q6_K, "q6_K"}, {GGML_TYPE_Q5_K, "q5_K"}, {GGML_TYPE_IQ4_XS, "iq4_xs"}, {GGML_TYPE_Q4_1, "q4_1"}, {GGML_TYPE_Q5_1, "q5_1"}, {GGML_TYPE_Q3_K, "q3_K"}, {GGML_TYPE_Q2_K, "q2_K"}};
         for (const auto& o : kOps)
             if (!what && strcmp(ggml_op_name(o.op), o.name) != 0) what = "enum ggml_op";
         for (const auto& t : kTypes)

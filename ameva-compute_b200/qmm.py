@@ -32,17 +32,24 @@ GGML_TYPE_IQ4_XS = 23
 # Q4_1 / Q5_1 (d * q + m per 32): q decoded to bytes, (d, m) kept as a 4-byte record; ameva_mmvq_q4_1 / _q5_1 over the
 # per-32 activations (whose records carry the sum of q8 the m term needs)
 GGML_TYPE_Q4_1, GGML_TYPE_Q5_1 = 3, 7
-BYTE_DECODED = (GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS, GGML_TYPE_Q4_1, GGML_TYPE_Q5_1)   # one GEMV kernel each, no tensor-core form, no fused variants
+# Q3_K / Q2_K: q3 (-4..3) / q2 (0..3) decoded to bytes; scales[12] + d (14 bytes) / scales[16], d, dmin (20 bytes) kept;
+# ameva_mmvqb_q3_K / _q2_K
+GGML_TYPE_Q2_K, GGML_TYPE_Q3_K = 10, 11
+BYTE_DECODED = (GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS, GGML_TYPE_Q4_1, GGML_TYPE_Q5_1, GGML_TYPE_Q3_K,
+                GGML_TYPE_Q2_K)   # one GEMV kernel each, no tensor-core form, no fused variants
 TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s",
               GGML_TYPE_Q6_K: "q6_K", GGML_TYPE_Q5_K: "q5_K", GGML_TYPE_IQ4_XS: "iq4_xs", GGML_TYPE_Q4_1: "q4_1",
-              GGML_TYPE_Q5_1: "q5_1"}
+              GGML_TYPE_Q5_1: "q5_1", GGML_TYPE_Q3_K: "q3_K", GGML_TYPE_Q2_K: "q2_K"}
 BLOCK = {GGML_TYPE_Q4_0: 32, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 256, GGML_TYPE_I2_S: 128, GGML_TYPE_Q6_K: 256,
-         GGML_TYPE_Q5_K: 256, GGML_TYPE_IQ4_XS: 256, GGML_TYPE_Q4_1: 32, GGML_TYPE_Q5_1: 32}
+         GGML_TYPE_Q5_K: 256, GGML_TYPE_IQ4_XS: 256, GGML_TYPE_Q4_1: 32, GGML_TYPE_Q5_1: 32, GGML_TYPE_Q3_K: 256,
+         GGML_TYPE_Q2_K: 256}
 Q_BYTES = {GGML_TYPE_Q4_0: 16, GGML_TYPE_Q8_0: 32, GGML_TYPE_Q4_K: 128, GGML_TYPE_Q6_K: 256, GGML_TYPE_Q5_K: 256,
-           GGML_TYPE_IQ4_XS: 256, GGML_TYPE_Q4_1: 32, GGML_TYPE_Q5_1: 32}   # payload bytes per block
+           GGML_TYPE_IQ4_XS: 256, GGML_TYPE_Q4_1: 32, GGML_TYPE_Q5_1: 32, GGML_TYPE_Q3_K: 256,
+           GGML_TYPE_Q2_K: 256}   # payload bytes per block
 S_BYTES = {GGML_TYPE_Q4_0: 2, GGML_TYPE_Q8_0: 2, GGML_TYPE_Q4_K: 16, GGML_TYPE_Q6_K: 18, GGML_TYPE_Q5_K: 16,
-           GGML_TYPE_IQ4_XS: 8, GGML_TYPE_Q4_1: 4, GGML_TYPE_Q5_1: 4}     # scale bytes per block
-PER_256 = (GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS)   # types whose activations are quantized per 256 (Q8_K records)
+           GGML_TYPE_IQ4_XS: 8, GGML_TYPE_Q4_1: 4, GGML_TYPE_Q5_1: 4, GGML_TYPE_Q3_K: 14,
+           GGML_TYPE_Q2_K: 20}     # scale bytes per block
+PER_256 = (GGML_TYPE_Q4_K, GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS, GGML_TYPE_Q3_K, GGML_TYPE_Q2_K)   # types whose activations are quantized per 256 (Q8_K records)
 PER_32 = (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_1, GGML_TYPE_Q5_1)         # per 32 (fp16 d | int16 sum per block)
 FUSED_QUANT_MAX_K = 16384          # the fused kernels keep the quantized row in shared memory
 

@@ -544,7 +544,7 @@ def init(*, backend: int = AC_BACKEND_CUDA) -> Context:
     return Context(out.value)
 
 
-_GGML_BLOCK = {2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 12: (256, 144), 13: (256, 176), 14: (256, 210), 20: (32, 18), 23: (256, 136), 36: (4, 1)}  # type id -> (elements, bytes) per block
+_GGML_BLOCK = {2: (32, 18), 3: (32, 20), 6: (32, 22), 7: (32, 24), 8: (32, 34), 10: (256, 84), 11: (256, 110), 12: (256, 144), 13: (256, 176), 14: (256, 210), 20: (32, 18), 23: (256, 136), 36: (4, 1)}  # type id -> (elements, bytes) per block
 
 
 def ggml_nbytes(ggml_type: int, rows: int, k: int) -> int:

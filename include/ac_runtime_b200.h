@@ -397,7 +397,9 @@ AcResult ac_b200_repack_to_device(uint32_t ggml_type, const void* ggml_blocks, u
  * (ac_b200_mul_mat_plan answers AC_B200_PATH_GEMV). Q5_K (13) likewise: q5 (0..31) as 256 bytes per block, the block's
  * first 16 bytes (d, dmin, packed scales) as its scale record; kernel ameva_mmvqb_q5_K. IQ4_XS (23): kvalues_iq4nl[q4]
  * as 256 int8 per block, the block's first 8 bytes (d, scales_h, scales_l) as its scale record; ameva_mmvqb_iq4_xs.
- * Q4_1 (3) / Q5_1 (7): q as 32 bytes per block, (d, m) as a 4-byte record; ameva_mmvq_q4_1 / ameva_mmvq_q5_1. */
+ * Q4_1 (3) / Q5_1 (7): q as 32 bytes per block, (d, m) as a 4-byte record; ameva_mmvq_q4_1 / ameva_mmvq_q5_1.
+ * Q3_K (11): q3 (-4..3) as 256 int8 per block, scales[12] + d as a 14-byte record; ameva_mmvqb_q3_K. Q2_K (10): q2 (0..3)
+ * as 256 bytes per block, scales[16] + d + dmin as a 20-byte record; ameva_mmvqb_q2_K. */
 uint32_t ac_b200_device_type(uint32_t ggml_type);
 AcResult ac_b200_repack_from_device(uint32_t ggml_type, const void* device_layout, uint64_t rows, uint64_t k,
                                     void* ggml_blocks);

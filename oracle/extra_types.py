@@ -390,3 +390,155 @@ def mul_mat_q4_1_q8_0(ggml_type: int, W, A, M: int, N: int, K: int) -> np.ndarra
         terms = ((d * da[m][None, :]).astype(np.float32) * sumi + mw * s_a[None, :]).astype(np.float32)
         out[m] = terms.astype(np.float64).sum(axis=1).astype(np.float32)
     return out
+
+
+# ---- Q3_K / Q2_K -----------------------------------------------------------------------------------------------------------
+# ggml-common.h block_q3_K: hmask[32], qs[64], scales[12], d fp16 = 110 bytes per 256 weights; weight e = d * (sc[e / 16] - 32)
+# * q3 with q3 = ((qs[32 (e / 128) + e % 32] >> 2 ((e % 128) / 32)) & 3) - (hmask[e % 32] bit (e / 32) ? 0 : 4) and the
+# 6-bit sc[g] = nibble (g < 8: low of scales[g], else high of scales[g - 8]) | ((scales[8 + g % 4] >> 2 (g / 4)) & 3) << 4
+# (dequantize_row_q3_K's aux / kmask shuffle written per scale). ggml_vec_dot_q3_K_q8_K: sumf += d * d8 * sum_g (sc - 32) *
+# sum_i q3 * q8.
+# block_q2_K: scales[16], qs[64], d, dmin fp16 = 84 bytes; weight e = d * (scales[e / 16] & 15) * q2 - dmin * (scales[e / 16]
+# >> 4), q2 from qs as above. ggml_vec_dot_q2_K_q8_K: sumf += d * d8 * sum_g sc * sum_i q2 * q8 - dmin * d8 * sum_g mn * bsum_g.
+Q2_K, Q3_K = 10, 11
+BLOCK_BYTES[Q3_K], BLOCK_BYTES[Q2_K] = 110, 84
+
+
+def _pack_two_bits(v) -> np.ndarray:
+    """v [n][256] (0..3) -> qs [n][64]: element e in byte 32 (e / 128) + e % 32 at shift 2 ((e % 128) / 32)."""
+    v = v.reshape(-1, 2, 4, 32).astype(np.uint8)
+    qs = np.zeros((v.shape[0], 2, 32), np.uint8)
+    for j in range(4):
+        qs |= v[:, :, j, :] << np.uint8(2 * j)
+    return qs.reshape(-1, 64)
+
+
+def _unpack_two_bits(qs) -> np.ndarray:
+    qs = qs.reshape(-1, 2, 1, 32)
+    return ((qs >> (2 * np.arange(4, dtype=np.uint8)).reshape(1, 1, 4, 1)) & 3).reshape(-1, 256)
+
+
+def quantize_q3_K(w) -> np.ndarray:
+    """A valid packer: per 16 weights amax / 4 -> 6-bit scale (stored + 32) under d = max / 31, q3 = round(x / (d sc))."""
+    x = np.ascontiguousarray(w, np.float32).reshape(-1, 16, 16)
+    gs = np.max(np.abs(x), axis=2) / np.float32(4.0)
+    d = (np.max(gs, axis=1) / np.float32(31.0)).astype(np.float16)
+    df = d.astype(np.float32)
+    sc = np.where(df[:, None] > 0, np.ceil(gs / np.where(df > 0, df, 1.0)[:, None]), 0).clip(0, 31).astype(np.int32)
+    eff = df[:, None] * sc
+    q = np.where(eff[:, :, None] > 0, np.rint(x / np.where(eff > 0, eff, 1.0)[:, :, None]), 0).clip(-4, 3).astype(np.int32)
+    q = q.reshape(-1, 256)
+    n = q.shape[0]
+    out = np.zeros((n, 110), np.uint8)
+    hm = (q >= 0).reshape(n, 8, 32)
+    for j in range(8):
+        out[:, 0:32] |= (hm[:, j, :].astype(np.uint8) << np.uint8(j))
+    out[:, 32:96] = _pack_two_bits(np.where(q >= 0, q, q + 4))
+    st = sc + 32
+    for g in range(16):
+        out[:, 96 + (g & 7)] |= ((st[:, g] & 0x0F) << (4 * (g >> 3))).astype(np.uint8)
+        out[:, 104 + (g & 3)] |= ((st[:, g] >> 4) << (2 * (g >> 2))).astype(np.uint8)
+    out[:, 108:110] = d.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
+
+
+def decode_q3_K(blocks):
+    """(d fp16 [n], sc - 32 as int [n][16], q3 int8 [n][256] in element order) of n blocks."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, 110)
+    n = b.shape[0]
+    d = b[:, 108:110].copy().view(np.float16).reshape(-1)
+    s = b[:, 96:108].astype(np.int32)
+    sc = np.zeros((n, 16), np.int32)
+    for g in range(16):
+        lo = (s[:, g] & 0x0F) if g < 8 else (s[:, g - 8] >> 4)
+        sc[:, g] = lo | (((s[:, 8 + (g & 3)] >> (2 * (g >> 2))) & 3) << 4)
+    q = _unpack_two_bits(b[:, 32:96]).astype(np.int32)
+    hbit = ((b[:, 0:32].reshape(n, 1, 32) >> np.arange(8, dtype=np.uint8).reshape(1, 8, 1)) & 1).reshape(n, 256)
+    return d, sc - 32, (q - np.where(hbit != 0, 0, 4)).astype(np.int8)
+
+
+def dequantize_q3_K(blocks) -> np.ndarray:
+    d, sc, q = decode_q3_K(blocks)
+    dl = d.astype(np.float32)[:, None] * sc.astype(np.float32)
+    return (np.repeat(dl, 16, axis=1) * q.astype(np.float32)).reshape(-1)
+
+
+def quantize_q2_K(w) -> np.ndarray:
+    """A valid packer: per 16 weights min -> 4-bit m under dmin, (max - min) / 3 -> 4-bit sc under d, q2 nearest."""
+    x = np.ascontiguousarray(w, np.float32).reshape(-1, 16, 16)
+    lo = np.minimum(x.min(axis=2), 0.0)
+    step = (x.max(axis=2) - lo) / np.float32(3.0)
+    d = (step.max(axis=1) / np.float32(15.0)).astype(np.float16)
+    dmin = ((-lo).max(axis=1) / np.float32(15.0)).astype(np.float16)
+    df, mf = d.astype(np.float32), dmin.astype(np.float32)
+    sc = np.where(df[:, None] > 0, np.ceil(step / np.where(df > 0, df, 1.0)[:, None]), 0).clip(0, 15).astype(np.int32)
+    mn = np.where(mf[:, None] > 0, np.rint(-lo / np.where(mf > 0, mf, 1.0)[:, None]), 0).clip(0, 15).astype(np.int32)
+    eff, off = df[:, None] * sc, mf[:, None] * mn
+    q = np.where(eff[:, :, None] > 0, np.rint((x + off[:, :, None]) / np.where(eff > 0, eff, 1.0)[:, :, None]), 0)
+    q = q.clip(0, 3).astype(np.uint8).reshape(-1, 256)
+    out = np.zeros((q.shape[0], 84), np.uint8)
+    out[:, 0:16] = (sc | (mn << 4)).astype(np.uint8)
+    out[:, 16:80] = _pack_two_bits(q)
+    out[:, 80:82] = d.view(np.uint8).reshape(-1, 2)
+    out[:, 82:84] = dmin.view(np.uint8).reshape(-1, 2)
+    return out.reshape(-1)
+
+
+def decode_q2_K(blocks):
+    """(d, dmin fp16 [n], sc, mn int [n][16], q2 uint8 [n][256] in element order) of n blocks."""
+    b = np.ascontiguousarray(blocks, np.uint8).reshape(-1, 84)
+    d = b[:, 80:82].copy().view(np.float16).reshape(-1)
+    dmin = b[:, 82:84].copy().view(np.float16).reshape(-1)
+    s = b[:, 0:16].astype(np.int32)
+    return d, dmin, s & 0x0F, s >> 4, _unpack_two_bits(b[:, 16:80]).astype(np.uint8)
+
+
+def dequantize_q2_K(blocks) -> np.ndarray:
+    d, dmin, sc, mn, q = decode_q2_K(blocks)
+    dl = d.astype(np.float32)[:, None] * sc.astype(np.float32)
+    ml = dmin.astype(np.float32)[:, None] * mn.astype(np.float32)
+    return (np.repeat(dl, 16, axis=1) * q.astype(np.float32) - np.repeat(ml, 16, axis=1)).astype(np.float32).reshape(-1)
+
+
+def _q8_K_fields(A, M: int, B: int):
+    a = np.ascontiguousarray(A, np.uint8).reshape(M, B, 292)
+    d8 = a[:, :, 0:4].copy().view(np.float32).reshape(M, B)
+    q8 = a[:, :, 4:260].copy().view(np.int8).reshape(M, B, 16, 16).astype(np.int64)
+    bsum = a[:, :, 260:292].copy().view(np.int16).reshape(M, B, 16).astype(np.int64)
+    return d8, q8, bsum
+
+
+def mul_mat_q3_K_q8_K(W, A, M: int, N: int, K: int) -> np.ndarray:
+    B = K // 256
+    d, sc, q = decode_q3_K(W)
+    d, sc, q = d.reshape(N, B).astype(np.float32), sc.reshape(N, B, 16).astype(np.int64), q.reshape(N, B, 16, 16).astype(np.int64)
+    d8, q8, _ = _q8_K_fields(A, M, B)
+    out = np.zeros((M, N), np.float32)
+    for m in range(M):
+        sumi = np.einsum("nbg,nbgi,bgi->nb", sc, q, q8[m])
+        terms = ((d * d8[m][None, :]).astype(np.float32) * sumi.astype(np.float32)).astype(np.float32)
+        acc = np.zeros(N, np.float32)
+        for b in range(B):
+            acc = (acc + terms[:, b]).astype(np.float32)
+        out[m] = acc
+    return out
+
+
+def mul_mat_q2_K_q8_K(W, A, M: int, N: int, K: int) -> np.ndarray:
+    B = K // 256
+    d, dmin, sc, mn, q = decode_q2_K(W)
+    d, dmin = d.reshape(N, B).astype(np.float32), dmin.reshape(N, B).astype(np.float32)
+    sc, mn = sc.reshape(N, B, 16).astype(np.int64), mn.reshape(N, B, 16).astype(np.int64)
+    q = q.reshape(N, B, 16, 16).astype(np.int64)
+    d8, q8, bsum = _q8_K_fields(A, M, B)
+    out = np.zeros((M, N), np.float32)
+    for m in range(M):
+        sumi = np.einsum("nbg,nbgi,bgi->nb", sc, q, q8[m])
+        summ = np.einsum("nbg,bg->nb", mn, bsum[m])
+        terms = ((d * d8[m][None, :]).astype(np.float32) * sumi.astype(np.float32) -
+                 (dmin * d8[m][None, :]).astype(np.float32) * summ.astype(np.float32)).astype(np.float32)
+        acc = np.zeros(N, np.float32)
+        for b in range(B):
+            acc = (acc + terms[:, b]).astype(np.float32)
+        out[m] = acc
+    return out

@@ -41,6 +41,8 @@ static void traits(enum ggml_type t, size_t* type_size, int64_t* blck) {
         case GGML_TYPE_Q6_K: *type_size = 210; *blck = 256; break;
         case GGML_TYPE_Q5_K: *type_size = 176; *blck = 256; break;
         case GGML_TYPE_IQ4_XS: *type_size = 136; *blck = 256; break;
+        case GGML_TYPE_Q3_K: *type_size = 110; *blck = 256; break;
+        case GGML_TYPE_Q2_K: *type_size = 84; *blck = 256; break;
         case GGML_TYPE_Q4_1: *type_size = 20; *blck = 32; break;
         case GGML_TYPE_Q5_1: *type_size = 24; *blck = 32; break;
         case GGML_TYPE_Q5_0: *type_size = 22; *blck = 32; break;
@@ -113,6 +115,8 @@ const char* ggml_type_name(enum ggml_type t) {
         case GGML_TYPE_Q6_K: return "q6_K";
         case GGML_TYPE_Q5_K: return "q5_K";
         case GGML_TYPE_IQ4_XS: return "iq4_xs";
+        case GGML_TYPE_Q3_K: return "q3_K";
+        case GGML_TYPE_Q2_K: return "q2_K";
         case GGML_TYPE_Q4_1: return "q4_1";
         case GGML_TYPE_Q5_1: return "q5_1";
         case GGML_TYPE_Q5_0: return "q5_0";

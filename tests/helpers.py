@@ -9,7 +9,8 @@ Q4_0, Q8_0, Q4_K, I2_S = 2, 8, 12, 36
 Q5_0, IQ4_NL = 6, 20   # kept on the device as Q8_0 regions (oracle/extra_types.py)
 Q6_K, Q5_K, IQ4_XS = 14, 13, 23    # decoded to bytes at upload, a kernel of their own over Q8_K activations
 Q4_1, Q5_1 = 3, 7                  # likewise, over the per-32 activations
-WEIGHT_STD = {Q4_0: 0.02, Q8_0: 0.02, Q4_K: 0.02, I2_S: 1.0, Q5_0: 0.02, IQ4_NL: 0.02, Q6_K: 0.02, Q5_K: 0.02, IQ4_XS: 0.02, Q4_1: 0.02, Q5_1: 0.02}
+Q2_K, Q3_K = 10, 11                # likewise, over Q8_K activations
+WEIGHT_STD = {Q4_0: 0.02, Q8_0: 0.02, Q4_K: 0.02, I2_S: 1.0, Q5_0: 0.02, IQ4_NL: 0.02, Q6_K: 0.02, Q5_K: 0.02, IQ4_XS: 0.02, Q4_1: 0.02, Q5_1: 0.02, Q2_K: 0.02, Q3_K: 0.02}
 
 
 def make_weights(ggml_type, N, K, seed=0, std=None):
@@ -31,6 +32,10 @@ def make_weights(ggml_type, N, K, seed=0, std=None):
         return extra_types.quantize_q5_K(w), 1.0
     if ggml_type == IQ4_XS:
         return extra_types.quantize_iq4_xs(w), 1.0
+    if ggml_type == Q3_K:
+        return extra_types.quantize_q3_K(w), 1.0
+    if ggml_type == Q2_K:
+        return extra_types.quantize_q2_K(w), 1.0
     if ggml_type in (Q4_1, Q5_1):
         return extra_types.quantize_q4_1(w, 4 if ggml_type == Q4_1 else 5), 1.0
     return oracle.quantize_i2_s(w)
@@ -57,10 +62,11 @@ def oracle_mul_mat(ggml_type, blocks, scale, x, N, K, round_mode=0, q8k_mode=0, 
         aq = oracle.quantize_q8_K(x, q8k_mode)
         y, sums = oracle.mul_mat_q4_K_q8_K(blocks, aq, M, N, K, want_sums)
         return y, sums, aq
-    if ggml_type in (Q6_K, Q5_K, IQ4_XS):
+    if ggml_type in (Q6_K, Q5_K, IQ4_XS, Q3_K, Q2_K):
         aq = oracle.quantize_q8_K(x, q8k_mode)
         fn = {Q6_K: extra_types.mul_mat_q6_K_q8_K, Q5_K: extra_types.mul_mat_q5_K_q8_K,
-              IQ4_XS: extra_types.mul_mat_iq4_xs_q8_K}[ggml_type]
+              IQ4_XS: extra_types.mul_mat_iq4_xs_q8_K, Q3_K: extra_types.mul_mat_q3_K_q8_K,
+              Q2_K: extra_types.mul_mat_q2_K_q8_K}[ggml_type]
         return fn(blocks, aq, M, N, K), None, aq
     q, dq, sm = oracle.quantize_i8_token(x)
     y, acc = oracle.mul_mat_i2_s_i8(blocks, scale, q, dq, M, N, K)

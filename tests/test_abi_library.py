@@ -204,7 +204,7 @@ def test_kernel_choice_policy():
     assert q.streamed_pays(Q4_K, 1, 28672, 8192) and not q.streamed_pays(Q4_K, 1, 4096, 4096)
     # outside the contract: an explicit error, never another implementation
     for t, M, N, K, flags, code in ((Q4_K, 0, 16, 256, 0, rt.AC_ERR_INVALID_SHAPE), (Q4_K, 1, 16, 384, 0, rt.AC_ERR_INVALID_SHAPE),
-                                    (10, 1, 16, 256, 0, rt.AC_ERR_FEATURE_NOT_SUPPORTED),
+                                    (16, 1, 16, 256, 0, rt.AC_ERR_FEATURE_NOT_SUPPORTED),
                                     (I2_S, 4, 640, 2560, rt.PLAN_PEERS, rt.AC_ERR_FEATURE_NOT_SUPPORTED),
                                     (Q4_K, 1, 16, 256, 64, rt.AC_ERR_INVALID_ARGUMENT)):
         with pytest.raises(rt.AmevaComputeError) as e:
@@ -220,7 +220,7 @@ def test_q5_0_and_iq4_nl_become_q8_0_regions():
     from oracle import extra_types as et
     lib = rt.load_library()
     lib.ac_b200_device_type.restype = C.c_uint32
-    assert [lib.ac_b200_device_type(t) for t in (2, 8, 12, 36, 6, 20, 14, 13, 23, 3, 7, 10)] == [2, 8, 12, 36, 8, 8, 14, 13, 23, 3, 7, 0]
+    assert [lib.ac_b200_device_type(t) for t in (2, 8, 12, 36, 6, 20, 14, 13, 23, 3, 7, 10, 11, 16)] == [2, 8, 12, 36, 8, 8, 14, 13, 23, 3, 7, 10, 11, 0]
     rng = np.random.default_rng(4)
     w = (rng.standard_normal((5, 512)) * 0.02).astype(np.float32)
     for t, pack in ((et.Q5_0, et.quantize_q5_0), (et.IQ4_NL, et.quantize_iq4_nl)):
@@ -258,6 +258,6 @@ def test_shape_contract_reasons():
     q = pkg.qmm
     assert q.unsupported_reason(2, 1, 4096, 4096) is None
     assert "block" in q.unsupported_reason(12, 1, 16, 384)
-    assert "not built" in q.unsupported_reason(10, 1, 16, 256)
+    assert "not built" in q.unsupported_reason(16, 1, 16, 256)
     assert q.unsupported_reason(36, 1, 640, 2560) is None
     assert "empty" in q.unsupported_reason(2, 0, 16, 256)

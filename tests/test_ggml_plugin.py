@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from conftest import ROOT
-from helpers import IQ4_NL, IQ4_XS, Q4_0, Q4_1, Q4_K, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+from helpers import IQ4_NL, IQ4_XS, Q2_K, Q3_K, Q4_0, Q4_1, Q4_K, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
 
 DRIVER = os.path.join(ROOT, "tests", "ggml_shim", "_build", "driver")
 PLUGIN = os.path.join(ROOT, "ameva-compute_b200", "libggml-ameva-b200.so")
@@ -27,10 +27,10 @@ def test_plugin_exports_and_registry_facts():
 
 @needs_plugin
 @pytest.mark.gpu
-@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K, Q5_0, IQ4_NL, Q6_K, Q5_K, IQ4_XS, Q4_1, Q5_1])
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K, Q5_0, IQ4_NL, Q6_K, Q5_K, IQ4_XS, Q4_1, Q5_1, Q3_K, Q2_K])
 @pytest.mark.parametrize("M,N,K", [(1, 384, 1024), (8, 130, 512), (33, 256, 768), (12, 96, 128)])
 def test_mul_mat_graph_through_the_plugin(t, M, N, K):
-    if t in (Q4_K, Q6_K, Q5_K, IQ4_XS) and K % 256:
+    if t in (Q4_K, Q6_K, Q5_K, IQ4_XS, Q3_K, Q2_K) and K % 256:
         K = 256
     blocks, scale = make_weights(t, N, K, 21)
     x = make_acts(M, K, 22)

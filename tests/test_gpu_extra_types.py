@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from conftest import load_pkg
-from helpers import IQ4_NL, IQ4_XS, Q4_1, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
+from helpers import IQ4_NL, IQ4_XS, Q2_K, Q3_K, Q4_1, Q5_0, Q5_1, Q5_K, Q6_K, Q8_0, make_acts, make_weights, max_normalised_error, oracle_mul_mat
 from oracle import extra_types
 
 pytestmark = pytest.mark.gpu
@@ -188,6 +188,37 @@ def test_q4_1_and_q5_1(ctx, t, M, N, K):
             assert np.array_equal(wt.buf.read(np.uint8, N * K), q.reshape(-1))
             rec = wt.buf.read(np.uint16, N * (K // 32) * 2, wt.s_off).reshape(-1, 2)
             assert np.array_equal(rec[:, 0], d.view(np.uint16)) and np.array_equal(rec[:, 1], m.view(np.uint16))
+        mm.run(xb, dst, M)
+        want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+        assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
+    finally:
+        for o in (mm, xb, dst, w, host):
+            o.destroy()
+
+
+@pytest.mark.parametrize("t", [Q3_K, Q2_K])
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (1, 1000, 14336), (3, 3, 256), (8, 130, 2048), (33, 768, 2048)])
+def test_q3_K_and_q2_K(ctx, t, M, N, K):
+    """Two- and three-bit K-quants: q decoded to bytes and the scale record kept at upload (on the device and by the host
+    codec alike), read-back byte-exact, ameva_mmvqb_q3_K / _q2_K over Q8_K activations against the numpy restatement of
+    ggml_vec_dot_q3_K_q8_K / _q2_K_q8_K."""
+    blocks, scale = make_weights(t, N, K, M)
+    x = make_acts(M, K, M + 1)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K)
+    host = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K, host_repack=True)
+    mm = qmm.MulMat(ctx, w, M)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    try:
+        assert np.array_equal(w.to_ggml(), blocks) and np.array_equal(host.to_ggml(), blocks)
+        raw = blocks.reshape(-1, 110 if t == Q3_K else 84)
+        if t == Q3_K:
+            q, rec_want = extra_types.decode_q3_K(blocks)[2].view(np.uint8), raw[:, 96:110]
+        else:
+            q, rec_want = extra_types.decode_q2_K(blocks)[4], np.concatenate([raw[:, 0:16], raw[:, 80:84]], axis=1)
+        rb = rec_want.shape[1]
+        for wt in (w, host):
+            assert np.array_equal(wt.buf.read(np.uint8, N * K), q.reshape(-1))
+            assert np.array_equal(wt.buf.read(np.uint8, N * (K // 256) * rb, wt.s_off).reshape(-1, rb), rec_want)
         mm.run(xb, dst, M)
         want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
         assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3

@@ -193,9 +193,9 @@ def test_row_range_view_matches_full(ctx):
 
 def test_unsupported_is_an_explicit_error_not_a_fallback(ctx):
     with pytest.raises(qmm.MulMatUnsupported):
-        qmm.QuantWeight.from_ggml(ctx, 10, np.zeros(84, np.uint8), 1, 256)         # Q2_K: not built
+        qmm.QuantWeight.from_ggml(ctx, 16, np.zeros(66, np.uint8), 1, 256)         # IQ2_XXS: not built
     with pytest.raises(rt.AmevaComputeError) as e:
-        ctx.kernel("ameva_mmvq_q2_K")
+        ctx.kernel("ameva_mmvq_iq2_xxs")
     assert e.value.code == rt.AC_ERR_KERNEL_NOT_FOUND
     blocks, _ = make_weights(Q4_0, 8, 256, 0)
     w = qmm.QuantWeight.from_ggml(ctx, Q4_0, blocks, 8, 256)

@@ -233,3 +233,21 @@ def test_q4_1_and_q5_1_equal_gguf_py():
         blocks = et.quantize_q4_1(w, bits)
         assert np.array_equal(blocks, quants.quantize(w, qt).reshape(-1))
         assert np.array_equal(et.dequantize_q4_1(t, blocks), quants.dequantize(blocks.reshape(16, -1), qt).reshape(-1))
+
+
+def test_q3_K_and_q2_K_decode_equal_gguf_py():
+    gguf = pytest.importorskip("gguf")
+    from gguf import quants
+    from oracle import extra_types as et
+    rng = np.random.default_rng(16)
+    w = (rng.standard_normal((16, 512)) * 0.05).astype(np.float32)
+    w[0, :256] = 0.0
+    for quantize, dequantize, qt, nbytes, halves in (
+            (et.quantize_q3_K, et.dequantize_q3_K, gguf.GGMLQuantizationType.Q3_K, 110, (108,)),
+            (et.quantize_q2_K, et.dequantize_q2_K, gguf.GGMLQuantizationType.Q2_K, 84, (80, 82))):
+        blocks = quantize(w)
+        assert np.array_equal(dequantize(blocks), quants.dequantize(blocks.reshape(16, -1), qt).reshape(-1))
+        raw = rng.integers(0, 256, (8, nbytes), dtype=np.uint8)    # every bit pattern of the packed fields
+        for h in halves:
+            raw[:, h], raw[:, h + 1] = 0, 0x1C                     # (a finite fp16 scale)
+        assert np.array_equal(dequantize(raw.reshape(-1)), quants.dequantize(raw, qt).reshape(-1))
