@@ -74,19 +74,25 @@ constexpr uint32_t kScaleBytes = kRows * 16;        // 2 KB: 16 bytes of scales 
 constexpr uint32_t kUnscaleBytes = kDequantWarps * 256u;   // per epilogue warp: the row factors of its (up to) 64 tokens
 constexpr uint32_t kSmemLimit = 227 * 1024;
 
-enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_I2_S = 36 };
+// T_B8: the types whose codes the upload decodes to one byte per weight (Q6_K, Q5_K, IQ4_XS, Q3_K, Q2_K, Q4_1, Q5_1): the
+// payload is laid out like Q8_0's, the scale operand is a table of fp16 pairs (scale, offset) per 16 weights that
+// ameva_mmtc_scales writes from the type's scale records (w = scale * q + offset).
+enum { T_Q4_0 = 2, T_Q8_0 = 8, T_Q4_K = 12, T_I2_S = 36, T_B8 = 100 };
 
 template <int TYPE>
 struct Cfg {
     static constexpr bool kInt8 = TYPE == T_I2_S;
     static constexpr bool kScales = TYPE != T_I2_S;
     static constexpr uint32_t kBlockK = kInt8 ? 128u : 64u;                 // K elements per K block
-    static constexpr uint32_t kRawRow = TYPE == T_Q8_0 ? 64u : 32u;         // packed bytes per row per K block
+    static constexpr uint32_t kRawRow = (TYPE == T_Q8_0 || TYPE == T_B8) ? 64u : 32u;   // packed bytes per row per K block
     // A raw stage is one TMA box of 128 rows x 128 contiguous bytes (a full L2 line per row, 128B-swizzled in shared
     // memory): kGroup K blocks of packed weights.
     static constexpr uint32_t kGroup = 128u / kRawRow;
     static constexpr uint32_t kRawBytes = kRows * 128u;
-    static constexpr uint32_t kRawSlots = TYPE == T_Q8_0 ? 4u : 3u;
+    static constexpr uint32_t kRawSlots = (TYPE == T_Q8_0 || TYPE == T_B8) ? 4u : 3u;
+    static constexpr uint32_t kScaleRow = TYPE == T_B8 ? 64u : 16u;         // scale bytes per row per 256 weights
+    static constexpr uint32_t kScaleStage = kRows * kScaleRow;
+    static constexpr bool kWide = TYPE != T_B8;                             // the kernel with two accumulators serves it
 };
 
 // ---- PTX wrappers (barriers, bounded waits and ring counters come from sync_ptx.cuh) -----------------------------------
@@ -299,8 +305,26 @@ __device__ __forceinline__ uint4 raw_chunk(const uint8_t* raw, uint32_t r, uint3
 // The lanes of a warp are 32 consecutive rows reading the same chunk index, which the swizzle spreads over all banks.
 template <int TYPE>
 __device__ __forceinline__ void dequant_half(const uint8_t* raw, const uint8_t* sc, uint32_t r, uint32_t h, uint32_t kb,
-                                             uint32_t* o) {
-    if constexpr (TYPE == T_Q8_0) {
+                                             uint32_t* o, uint32_t b8_signed = 0u) {
+    if constexpr (TYPE == T_B8) {
+        // raw row as Q8_0's; scale row: 64 bytes per 256 weights = fp16 pairs (s, o) of the 16 groups of 16 weights; this
+        // half holds groups 4 (kb % 4) + 2h and + 1. Stored bytes are q (0..255) or, signed, q as int8 (xor 0x80 = q + 128).
+        const uint32_t c0 = 4u * (kb & 1u) + 2u * h;
+        const uint4 q0 = raw_chunk(raw, r, c0), q1 = raw_chunk(raw, r, c0 + 1u);
+        const uint2 so = *reinterpret_cast<const uint2*>(sc + r * 64u + (kb & 3u) * 16u + h * 8u);
+        const __half2 p0 = *reinterpret_cast<const __half2*>(&so.x), p1 = *reinterpret_cast<const __half2*>(&so.y);
+        const __half2 s0 = __low2half2(p0), o0 = __high2half2(p0), s1 = __low2half2(p1), o1 = __high2half2(p1);
+        const uint32_t flip = b8_signed ? 0x80808080u : 0u;
+        const __half2 bias = __float2half2_rn(b8_signed ? 1152.0f : 1024.0f);   // the fp16 magic 1024 (+ 128)
+        const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            __half2 lo, hi;
+            bytes_to_h2(w[i] ^ flip, lo, hi);
+            o[2 * i] = pack_h2(__hfma2(__hsub2(lo, bias), i < 4 ? s0 : s1, i < 4 ? o0 : o1));
+            o[2 * i + 1] = pack_h2(__hfma2(__hsub2(hi, bias), i < 4 ? s0 : s1, i < 4 ? o0 : o1));
+        }
+    } else if constexpr (TYPE == T_Q8_0) {
         // raw row: 2 K blocks x 64 B; this half: 32 int8 = chunks 4 (kb % 2) + 2h, +1; scale of unit 2 (kb % 4) + h
         const uint32_t c0 = 4u * (kb & 1u) + 2u * h;
         const uint4 q0 = raw_chunk(raw, r, c0), q1 = raw_chunk(raw, r, c0 + 1u);
@@ -397,6 +421,7 @@ struct Params {
     uint32_t iters, units;    // K blocks per unit in the linear (tile, K block) space; number of units launched
     uint32_t* flags;          // per (tile, CTA of the pair, epilogue warp) sequence words, zero between launches
     float w_scale;
+    uint32_t b8_signed;       // T_B8: the payload bytes are int8 (1) or 0..255 (0)
     const float* row_unscale; // scaled types: per token row, the factor the activation quantizer divided out (AE)
     uint32_t diag;
     uint32_t* status;
@@ -481,7 +506,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
     uint8_t* sOut = sB + S * b_bytes;                                 // 16 x 2 KB epilogue staging
     uint8_t* sRaw = sOut + kEpilogueBytes;                            // kRawSlots x 16 KB
     uint8_t* sSc = sRaw + C::kRawSlots * C::kRawBytes;                // kScaleSlots x 2 KB
-    uint8_t* sUn = sSc + kScaleSlots * kScaleBytes;                   // kDequantWarps x 256 B row factors
+    uint8_t* sUn = sSc + kScaleSlots * C::kScaleStage;                // kDequantWarps x 256 B row factors
     uint64_t* bars = reinterpret_cast<uint64_t*>(sUn + kUnscaleBytes);
     // full[s]: the four arrivals of the dequant group that wrote TMEM stage s (of each CTA of a pair) + the activation
     // TMA's arrival and bytes for shared-memory stage s; empty[s]: one tcgen05.commit when the MMAs that read stage s
@@ -607,9 +632,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                     if (C::kScales && (kb & 3u) == 0u) {
                         ok = mbar_wait(sc_empty + 8u * sr.idx, sr.phase ^ 1u, ctl, status, 0x600u | sr.idx, dg ? &w_sc : nullptr);
                         if (!ok) break;
-                        mbar_arrive_expect_tx(sc_full + 8u * sr.idx, kScaleBytes);
-                        tma_load_2d(smem_u32(sSc + sr.idx * kScaleBytes), &scale_map, sc_full + 8u * sr.idx,
-                                    (int)((kbr >> 2) * 16u), (int)n0);
+                        mbar_arrive_expect_tx(sc_full + 8u * sr.idx, C::kScaleStage);
+                        tma_load_2d(smem_u32(sSc + sr.idx * C::kScaleStage), &scale_map, sc_full + 8u * sr.idx,
+                                    (int)((kbr >> 2) * C::kScaleRow), (int)n0);
                         sr.advance();
                     }
                     if ((kb & (C::kGroup - 1u)) == 0u) {
@@ -705,9 +730,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap act_map, const __grid_constan
                 uint32_t o[32];
                 if (!(kdiag & 1u)) {
                     const uint8_t* raw = sRaw + rr.idx * C::kRawBytes;
-                    const uint8_t* sc = sSc + sr.idx * kScaleBytes;
-                    dequant_half<TYPE>(raw, sc, r, 0u, kb, o);
-                    dequant_half<TYPE>(raw, sc, r, 1u, kb, o + 16);
+                    const uint8_t* sc = sSc + sr.idx * C::kScaleStage;
+                    dequant_half<TYPE>(raw, sc, r, 0u, kb, o, p.b8_signed);
+                    dequant_half<TYPE>(raw, sc, r, 1u, kb, o + 16, p.b8_signed);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] = 0u;
@@ -1596,7 +1621,8 @@ template <int TYPE>
 static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, const void* act, uint64_t act_range,
                        void* dstp, uint64_t dst_range, const void* actscale, uint32_t M, uint32_t N, uint32_t K,
                        uint32_t dst_stride, float w_scale, uint32_t diag, const void* row_unscale, uint64_t unscale_range,
-                       uint32_t n_peers = 0, void* const* peer_dst = nullptr, const uint64_t* peer_range = nullptr) {
+                       uint32_t n_peers = 0, void* const* peer_dst = nullptr, const uint64_t* peer_range = nullptr,
+                       uint32_t b8_signed = 0) {
     using C = Cfg<TYPE>;
     constexpr uint32_t esz = C::kInt8 ? 1u : 2u;
     if (M == 0 || N == 0 || K == 0 || (K % C::kBlockK) || dst_stride < N) return AC_ERR_KERNEL_ARG_INVALID;
@@ -1610,7 +1636,7 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     if (!enc) return AC_ERR_DRIVER_SYMBOL_MISSING;
     // More than 256 token rows of a scaled type, local output: the kernel with two accumulators per CTA pair, which
     // converts every weight tile once per 512 tokens (diag bit 7 keeps the launch on the kernel with one accumulator).
-    if constexpr (C::kScales) {
+    if constexpr (C::kScales && C::kWide) {
         // (its epilogue writes 16 bytes at a time: rows of the output 16-byte aligned, N a multiple of 4)
         // It pays when every CTA pair gets at least two whole 256 x 512 tiles: its accumulators fill the tensor memory,
         // so the 10 us an SM needs to write a tile out are not overlapped with MMAs, and a tile cut across units is
@@ -1638,6 +1664,7 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     p.K = K;
     p.dst_stride = dst_stride;
     p.w_scale = w_scale;
+    p.b8_signed = b8_signed;
     p.row_unscale = (const float*)row_unscale;
     if (!AMV_GEMM_DIAG && (diag & 31u)) return AC_ERR_FEATURE_NOT_SUPPORTED;   // needs the diagnostic build
     p.diag = diag & 31u;   // bits 5 (single CTAs), 6 (one tile per unit), 7 (one accumulator) are host-side choices
@@ -1664,7 +1691,7 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
     p.row_units = (N + unit_rows - 1) / unit_rows;
     const uint32_t KB = K / C::kBlockK;
     const int sm_count = a.sm_count > 0 ? a.sm_count : 148;
-    const uint32_t fixed = 1024u + kEpilogueBytes + C::kRawSlots * C::kRawBytes + kScaleSlots * kScaleBytes + kUnscaleBytes + 512u;
+    const uint32_t fixed = 1024u + kEpilogueBytes + C::kRawSlots * C::kRawBytes + kScaleSlots * C::kScaleStage + kUnscaleBytes + 512u;
 
     // K ranges cut across tiles ("stream" launch, all units resident at once) need a K that is whole scale groups, exact integer results left alone (I2_S scales per token after the sum) and flag
     // space; with peer destinations the partial sums are combined in the local output and the segment that completes a
@@ -1730,8 +1757,8 @@ static AcResult launch(const LaunchArgs& a, const void* Qp, const void* Sp, cons
                    CU_TENSOR_MAP_SWIZZLE_128B))
         return AC_ERR_INVALID_ARGUMENT;
     if (C::kScales) {
-        const uint64_t srow = (uint64_t)(K >> 8) * 16u;   // 16 bytes of scales per 256 weights
-        if (!encode_2d(enc, &scale_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Sp, srow, N, srow, 16, kRows,
+        const uint64_t srow = (uint64_t)(K >> 8) * C::kScaleRow;   // 16 (T_B8: 64) bytes of scales per 256 weights
+        if (!encode_2d(enc, &scale_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, Sp, srow, N, srow, C::kScaleRow, kRows,
                        CU_TENSOR_MAP_SWIZZLE_NONE))
             return AC_ERR_INVALID_ARGUMENT;
     } else {
@@ -1815,6 +1842,17 @@ AcResult launch_mmtc_q4_K_mp(const LaunchArgs& a) { return launch_mmtc_mp<tc::T_
 AcResult launch_mmtc_q4_0(const LaunchArgs& a) { return launch_mmtc<tc::T_Q4_0, 16, 2, 32>(a); }
 AcResult launch_mmtc_q8_0(const LaunchArgs& a) { return launch_mmtc<tc::T_Q8_0, 32, 2, 32>(a); }
 AcResult launch_mmtc_q4_K(const LaunchArgs& a) { return launch_mmtc<tc::T_Q4_K, 128, 16, 256>(a); }
+
+// ameva_mmtc_b8: the types decoded to one byte per weight. Bindings 0 Q (bytes [N][K]), 1 H (fp16 pairs (scale, offset) per
+// 16 weights, [N][K / 16], written by ameva_mmtc_scales), 2 AH, 3 dst, 4 AE; push {M, N, K (% 256), dst_stride, diag,
+// signed (1: the bytes are int8)}
+AcResult launch_mmtc_b8(const LaunchArgs& a) {
+    const uint32_t M = a.push[0], N = a.push[1], K = a.push[2], dst_stride = a.push[3];
+    if (K == 0 || (K & 255u) || a.push[5] > 1u) return AC_ERR_KERNEL_ARG_INVALID;
+    if (a.range[0] < (uint64_t)N * K || a.range[1] < (uint64_t)N * (K >> 4) * 4u) return AC_ERR_INVALID_BUFFER_SIZE;
+    return tc::launch<tc::T_B8>(a, a.ptr[0], a.ptr[1], a.ptr[2], a.range[2], a.ptr[3], a.range[3], nullptr, M, N, K,
+                                dst_stride, 1.0f, a.push[4], a.ptr[4], a.range[4], 0, nullptr, nullptr, a.push[5]);
+}
 
 // bitnet_gemm_i2_s: bindings 0 packed weights, 1 int8 activations [M][K], 2 dst f32 [M][dst_stride], 3 act[2] per row
 // {bits of dequant, sum q};  push {M, N, K (% 128), dst_stride, weight_scale_bits, diag}

@@ -535,4 +535,88 @@ AcResult launch_mmvqb_q3_K(const LaunchArgs& a) { return launch_q23k<3>(a); }
 // ameva_mmvqb_q2_K: the same with Q bytes 0..3 and 20-byte records (scales[16], d, dmin)
 AcResult launch_mmvqb_q2_K(const LaunchArgs& a) { return launch_q23k<2>(a); }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Scale table of the tensor-core GEMM for the types above (ameva_mmtc_b8): per 16 weights an fp16 pair (s, o) with
+// w = s * q + o for the stored byte q, decoded from the type's scale records: Q6_K s = d * scale[g]; Q5_K s = d * sc[g / 2],
+// o = -dmin * m[g / 2]; IQ4_XS s = d * (ls[g / 2] - 32); Q3_K s = d * (scale6[g] - 32); Q2_K s = d * (scales[g] & 15),
+// o = -dmin * (scales[g] >> 4); Q4_1 / Q5_1 s = d, o = m of the 32-weight block g / 2. The products are exact in fp32
+// (an fp16 times at most 6 bits) and rounded once to fp16. One thread per 256 weights; it runs once per weight (the
+// host keeps the table) or once per prompt, and moves 64 bytes per 256 weights.
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) mmtc_scales_kernel(const uint8_t* __restrict__ S, uint32_t* __restrict__ H, uint32_t type,
+                                                          uint64_t blocks) {
+    pdl_wait();
+    pdl_trigger();
+    const uint64_t b = (uint64_t)blockIdx.x * 256u + threadIdx.x;
+    if (b >= blocks) return;
+    const uint32_t rec_bytes = type == 14u ? 18u : type == 13u ? 16u : type == 23u ? 8u : type == 11u ? 14u : type == 10u ? 20u : 32u;
+    const uint8_t* rec = S + b * rec_bytes;
+    auto half_at = [&](uint32_t off) { return h2f((uint16_t)(rec[off] | ((uint32_t)rec[off + 1u] << 8))); };
+    uint32_t out[16];
+#pragma unroll
+    for (uint32_t g = 0; g < 16u; ++g) {
+        float sv = 0.0f, ov = 0.0f;
+        if (type == 14u) {
+            sv = half_at(16) * (float)(int8_t)rec[g];
+        } else if (type == 13u) {
+            const uint32_t j = g >> 1;
+            const uint8_t* sm = rec + 4;
+            int sc, mn;
+            if (j < 4u) {
+                sc = sm[j] & 63;
+                mn = sm[j + 4u] & 63;
+            } else {
+                sc = (sm[j + 4u] & 0x0F) | ((sm[j - 4u] >> 6) << 4);
+                mn = (sm[j + 4u] >> 4) | ((sm[j] >> 6) << 4);
+            }
+            sv = half_at(0) * (float)sc;
+            ov = -(half_at(2) * (float)mn);
+        } else if (type == 23u) {
+            const uint32_t ib = g >> 1, sh = rec[2] | ((uint32_t)rec[3] << 8);
+            const uint32_t lo = (rec[4u + (ib >> 1)] >> (4u * (ib & 1u))) & 0x0Fu, hi = (sh >> (2u * ib)) & 3u;
+            sv = half_at(0) * (float)((int)(lo | (hi << 4)) - 32);
+        } else if (type == 11u) {
+            const uint32_t lo = g < 8u ? (rec[g] & 0x0Fu) : (rec[g - 8u] >> 4);
+            const uint32_t hi = (rec[8u + (g & 3u)] >> (2u * (g >> 2))) & 3u;
+            sv = half_at(12) * (float)((int)(lo | (hi << 4)) - 32);
+        } else if (type == 10u) {
+            sv = half_at(16) * (float)(rec[g] & 0x0F);
+            ov = -(half_at(18) * (float)(rec[g] >> 4));
+        } else {   // Q4_1 / Q5_1: eight (d, m) records per 256 weights
+            sv = half_at(4u * (g >> 1));
+            ov = half_at(4u * (g >> 1) + 2u);
+        }
+        const __half2 pr = __floats2half2_rn(sv, ov);
+        out[g] = *reinterpret_cast<const uint32_t*>(&pr);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(H + b * 16u);
+#pragma unroll
+    for (uint32_t i = 0; i < 4u; ++i) dst[i] = make_uint4(out[4 * i], out[4 * i + 1], out[4 * i + 2], out[4 * i + 3]);
+}
+
+// ameva_mmtc_scales: bindings 0 S (the weight's scale records), 1 H (fp16 pairs, 64 bytes per 256 weights);
+// push {device type (14, 13, 23, 11, 10, 3, 7), N, K (% 256)}
+AcResult launch_mmtc_scales(const LaunchArgs& a) {
+    const uint32_t type = a.push[0], N = a.push[1], K = a.push[2];
+    uint32_t rec;
+    switch (type) {
+        case 14: rec = 18; break;
+        case 13: rec = 16; break;
+        case 23: rec = 8; break;
+        case 11: rec = 14; break;
+        case 10: rec = 20; break;
+        case 3: case 7: rec = 32; break;
+        default: return AC_ERR_FEATURE_NOT_SUPPORTED;
+    }
+    if (N == 0 || K == 0 || (K & 255u)) return AC_ERR_KERNEL_ARG_INVALID;
+    const uint64_t blocks = (uint64_t)N * (K >> 8);
+    if (a.range[0] < blocks * rec || a.range[1] < blocks * 64u) return AC_ERR_INVALID_BUFFER_SIZE;
+    if ((uintptr_t)a.ptr[1] & 15u) return AC_ERR_BUFFER_ALIGNMENT_INVALID;
+    const uint64_t grid = (blocks + 255u) / 256u;
+    if (grid > 0x7fffffffull) return AC_ERR_INVALID_WORK_ITEM_DIMS;
+    launch_pdl(mmtc_scales_kernel, dim3((unsigned)grid), dim3(256), 0, a.stream, (const uint8_t*)a.ptr[0], (uint32_t*)a.ptr[1],
+               type, blocks);
+    return check_launch();
+}
+
 }  // namespace amv

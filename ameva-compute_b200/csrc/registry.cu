@@ -51,6 +51,8 @@ AcResult launch_mmvqb_q5_K(const LaunchArgs&);
 AcResult launch_mmvqb_iq4_xs(const LaunchArgs&);
 AcResult launch_mmvq_q4_1(const LaunchArgs&);
 AcResult launch_mmvqb_q3_K(const LaunchArgs&);
+AcResult launch_mmtc_scales(const LaunchArgs&);
+AcResult launch_mmtc_b8(const LaunchArgs&);
 AcResult launch_mmvqb_q2_K(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
 AcResult launch_mmvs_q8_0(const LaunchArgs&);
@@ -92,6 +94,8 @@ static const KernelEntry kTable[] = {
     {"ameva_mmtc_q8_0", 5, 20, {320, 1, 1}, launch_mmtc_q8_0},
     {"ameva_mmtc_q4_K", 5, 20, {320, 1, 1}, launch_mmtc_q4_K},
     {"bitnet_gemm_i2_s", 4, 24, {320, 1, 1}, launch_bitnet_gemm_i2_s},
+    {"ameva_mmtc_b8", 5, 24, {608, 1, 1}, launch_mmtc_b8},
+    {"ameva_mmtc_scales", 2, 12, {256, 1, 1}, launch_mmtc_scales},
     {"ameva_mmtc_q4_0_mp", 12, 24, {608, 1, 1}, launch_mmtc_q4_0_mp},
     {"ameva_mmtc_q8_0_mp", 12, 24, {608, 1, 1}, launch_mmtc_q8_0_mp},
     {"ameva_mmtc_q4_K_mp", 12, 24, {608, 1, 1}, launch_mmtc_q4_K_mp},
@@ -456,9 +460,13 @@ extern "C" AcResult ac_b200_mul_mat_plan(uint32_t type, uint64_t M, uint64_t N, 
         return AC_ERR_INVALID_ARGUMENT;
     const uint64_t blk = (type == 2 || type == 8 || type == 3 || type == 7) ? 32 : (type == 12 || type == 13 || type == 14 || type == 23 || type == 10 || type == 11) ? 256 : type == 36 ? 128 : 0;
     if (!blk) return AC_ERR_FEATURE_NOT_SUPPORTED;
-    if (type == 14 || type == 13 || type == 23 || type == 3 || type == 7 || type == 10 || type == 11) {   // Q6_K, Q5_K, IQ4_XS, Q4_1, Q5_1, Q3_K, Q2_K: one kernel each; more than 8 rows in chunks of 8
+    if (type == 14 || type == 13 || type == 23 || type == 3 || type == 7 || type == 10 || type == 11) {   // Q6_K, Q5_K, IQ4_XS, Q4_1, Q5_1, Q3_K, Q2_K: one GEMV kernel each
         if (M == 0 || N == 0 || K == 0 || K % blk) return AC_ERR_INVALID_SHAPE;
-        *out_path = AC_B200_PATH_GEMV;
+        if (flags & AC_B200_PLAN_PEERS) return AC_ERR_FEATURE_NOT_SUPPORTED;
+        // more than 8 rows: ameva_mmtc_b8 over the scale table of ameva_mmtc_scales (K % 256), unless exact results are
+        // asked for or the weights' magnitudes are outside what fp16 holds comfortably
+        const bool exact = (flags & (AC_B200_PLAN_EXACT | AC_B200_PLAN_WEIGHT_RANGE)) != 0;
+        *out_path = (M > 8 && (K % 256) == 0 && !exact && N * K < (1ull << 32)) ? AC_B200_PATH_GEMM_TC : AC_B200_PATH_GEMV;
         return AC_SUCCESS;
     }
     if (M == 0 || N == 0 || K == 0 || (K % blk) || N * K >= (1ull << 32) || M * (N > K ? N : K) >= (1ull << 32))

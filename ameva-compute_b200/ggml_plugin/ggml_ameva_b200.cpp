@@ -314,7 +314,8 @@ struct Backend {
     AcBuffer* ad = nullptr;   // per-block activation scales (u32 per 32 / 48 B per 256)
     AcBuffer* ah = nullptr;   // fp16 [M][K], the tensor-core operand (M > 8)
     AcBuffer* ae = nullptr;   // f32 [M], the per-row range factors of that operand
-    size_t aq_bytes = 0, ad_bytes = 0, ah_bytes = 0, ae_bytes = 0;
+    AcBuffer* gh = nullptr;   // fp16 (scale, offset) per 16 weights: the scale table of ameva_mmtc_b8, rewritten per MUL_MAT
+    size_t aq_bytes = 0, ad_bytes = 0, ah_bytes = 0, ae_bytes = 0, gh_bytes = 0;
     AcBuffer* op_status = nullptr;   // {count, lowest node} of refused GET_ROWS / SET_ROWS indices
     AcBuffer* fa_part = nullptr;     // partial results of the key splits of FLASH_ATTN_EXT
     size_t op_status_bytes = 0, fa_part_bytes = 0;
@@ -806,6 +807,21 @@ bool record_mul_mat(Recorder& r, const ggml_tensor* node, const Epilogue& ep) {
         }
         case AC_B200_PATH_GEMM_TC: {
             if (!record_quantize(r, x, w.type, M, K, true)) return false;
+            if (byte_decoded(w.type)) {
+                // the types decoded to bytes share one kernel, which reads (scale, offset) per 16 weights from a table
+                // that ameva_mmtc_scales writes from the weight's scale records (64 bytes per 256 weights)
+                const AcBufferBinding H = bind(r.be->gh, 0, (uint64_t)N * (K / 16) * 4);
+                AcBufferBinding sb[2] = {S, H};
+                const uint32_t spush[3] = {(uint32_t)w.type, N, K};
+                if (!dispatch(r, "ameva_mmtc_scales", sb, 2, spush, sizeof(spush))) return false;
+                ac_runtime_batch_barrier(r.batch);
+                const bool is_signed = w.type == GGML_TYPE_Q6_K || w.type == GGML_TYPE_IQ4_XS || w.type == GGML_TYPE_Q3_K;
+                AcBufferBinding b8[5] = {Q, H, bind(r.be->ah, 0, (uint64_t)M * K * 2), Y, bind(r.be->ae, 0, (uint64_t)M * 4)};
+                const uint32_t push8[6] = {M, N, K, N, 0, is_signed ? 1u : 0u};
+                if (!dispatch(r, "ameva_mmtc_b8", b8, 5, push8, sizeof(push8))) return false;
+                ac_runtime_batch_barrier(r.batch);   // the next product's table may overwrite this one
+                return true;
+            }
             AcBufferBinding b[5] = {Q, S, bind(r.be->ah, 0, (uint64_t)M * K * 2), Y, bind(r.be->ae, 0, (uint64_t)M * 4)};
             const uint32_t push[5] = {M, N, K, N, 0};
             return dispatch(r, (std::string("ameva_mmtc_") + tname).c_str(), b, 5, push, sizeof(push));
@@ -1088,7 +1104,7 @@ void backend_free(ggml_backend_t backend) {
         std::lock_guard<std::mutex> lock(plugin().mutex);
         for (auto& kv : be->kernels)
             if (ac_runtime_kernel_destroy(kv.second) == AC_SUCCESS) g_count.kernel_destroy++;
-        for (AcBuffer* b : {be->aq, be->ad, be->ah, be->ae, be->op_status, be->fa_part})
+        for (AcBuffer* b : {be->aq, be->ad, be->ah, be->ae, be->gh, be->op_status, be->fa_part})
             if (b && ac_runtime_buffer_destroy(b) == AC_SUCCESS) g_count.buffer_destroy++;
         plugin().live_backends--;
     }
@@ -1125,7 +1141,7 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
         return GGML_STATUS_FAILED;
     }
     // scratch for the quantized activations: the largest need over all nodes, reserved before anything is recorded
-    size_t aq_need = 0, ad_need = 0, ah_need = 0, ae_need = 0;
+    size_t aq_need = 0, ad_need = 0, ah_need = 0, ae_need = 0, gh_need = 0;
     for (int i = 0; i < n; ++i) {
         const ggml_tensor* node = ggml_graph_node(cgraph, i);
         if (node->op != GGML_OP_MUL_MAT) continue;
@@ -1136,10 +1152,12 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
         if (M > 8 && K % 256 == 0) {
             ah_need = std::max(ah_need, M * K * 2);
             ae_need = std::max(ae_need, M * 4);
+            if (byte_decoded(w->type)) gh_need = std::max(gh_need, (size_t)w->ne[1] * (K / 16) * 4);
         }
     }
     if ((aq_need && !grow(&be->aq, &be->aq_bytes, aq_need)) || (ad_need && !grow(&be->ad, &be->ad_bytes, ad_need)) ||
-        (ah_need && !grow(&be->ah, &be->ah_bytes, ah_need)) || (ae_need && !grow(&be->ae, &be->ae_bytes, ae_need)))
+        (ah_need && !grow(&be->ah, &be->ah_bytes, ah_need)) || (ae_need && !grow(&be->ae, &be->ae_bytes, ae_need)) ||
+        (gh_need && !grow(&be->gh, &be->gh_bytes, gh_need)))
         return GGML_STATUS_ALLOC_FAILED;
     bool layer_ops = false;
     for (int i = 0; i < n && !layer_ops; ++i) layer_ops = is_layer_op(ggml_graph_node(cgraph, i)->op);

@@ -22,7 +22,7 @@ GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K, GGML_TYPE_I2_S = 2, 8, 12, 36
 GGML_TYPE_Q5_0, GGML_TYPE_IQ4_NL = 6, 20
 DEVICE_TYPE = {GGML_TYPE_Q5_0: GGML_TYPE_Q8_0, GGML_TYPE_IQ4_NL: GGML_TYPE_Q8_0}
 # Q6_K: the 6-bit weights decoded to int8 at upload (256 payload bytes per block), scales[16] + d kept (18 bytes); one
-# kernel, ameva_mmvqb_q6_K, over Q8_K activations; more than 8 activation rows run in chunks of 8 (gemv_q6k.cu)
+# kernel, ameva_mmvqb_q6_K, over Q8_K activations (gemv_q6k.cu); more than 8 activation rows: ameva_mmtc_b8
 GGML_TYPE_Q6_K = 14
 # Q5_K likewise: q5 decoded to bytes (256 per block), the block's first 16 bytes (d, dmin, packed scales) kept as the
 # scale record; ameva_mmvqb_q5_K
@@ -36,7 +36,8 @@ GGML_TYPE_Q4_1, GGML_TYPE_Q5_1 = 3, 7
 # ameva_mmvqb_q3_K / _q2_K
 GGML_TYPE_Q2_K, GGML_TYPE_Q3_K = 10, 11
 BYTE_DECODED = (GGML_TYPE_Q6_K, GGML_TYPE_Q5_K, GGML_TYPE_IQ4_XS, GGML_TYPE_Q4_1, GGML_TYPE_Q5_1, GGML_TYPE_Q3_K,
-                GGML_TYPE_Q2_K)   # one GEMV kernel each, no tensor-core form, no fused variants
+                GGML_TYPE_Q2_K)   # one GEMV kernel each, one tensor-core kernel for all (ameva_mmtc_b8), no fused variants
+BYTE_SIGNED = (GGML_TYPE_Q6_K, GGML_TYPE_IQ4_XS, GGML_TYPE_Q3_K)   # payload bytes are int8 (the others: 0..255)
 TYPE_NAMES = {GGML_TYPE_Q4_0: "q4_0", GGML_TYPE_Q8_0: "q8_0", GGML_TYPE_Q4_K: "q4_K", GGML_TYPE_I2_S: "i2_s",
               GGML_TYPE_Q6_K: "q6_K", GGML_TYPE_Q5_K: "q5_K", GGML_TYPE_IQ4_XS: "iq4_xs", GGML_TYPE_Q4_1: "q4_1",
               GGML_TYPE_Q5_1: "q5_1", GGML_TYPE_Q3_K: "q3_K", GGML_TYPE_Q2_K: "q2_K"}
@@ -246,7 +247,7 @@ class MulMat:
         self.round_mode, self.q8k_mode, self.dump = round_mode, q8k_mode, dump_block_sums
         # exact = keep every M on the dp4a kernels (exact per-block int32 sums); otherwise M > 8 runs on tensor cores,
         # unless the weights' magnitudes are outside what their fp16 form holds comfortably
-        self.exact = exact or dump_block_sums or not w.fp16_ok or w.type in BYTE_DECODED   # (no GEMM form)
+        self.exact = exact or dump_block_sums or not w.fp16_ok
         # the GEMM stages weights and scales with TMA: whole 128-byte operand rows, whole 16-byte scale groups per row
         self.tc_ok = self.K % (128 if self.type == GGML_TYPE_I2_S else 256) == 0
         self.qbind, self.sbind = _bindings_for(self.view)
@@ -264,6 +265,22 @@ class MulMat:
         if max_m > GEMV_MAX_M and not self.exact and self.tc_ok and self.type != GGML_TYPE_I2_S:
             self.ah = ctx.buffer(max_m * K * 2)    # fp16(q * d * s_m): the activation operand of the tensor-core GEMM
             self.ae = ctx.buffer(max_m * 4)        # 1 / s_m per token row (power-of-two range factors, see act_quant.cu)
+        # the byte-decoded types' GEMM reads an fp16 (scale, offset) pair per 16 weights: written once, here, from the
+        # weight's scale records (64 bytes per 256 weights)
+        self.h = None
+        if self.ah is not None and self.type in BYTE_DECODED:
+            self.h = ctx.buffer(self.N * (K // 16) * 4)
+            batch = ctx.batch(4)
+            try:
+                batch.dispatch(ctx.kernel("ameva_mmtc_scales"), [self.sbind, self.h], [self.type, self.N, K],
+                               ((self.N * (K // 256) + 255) // 256, 1, 1))
+                ev = batch.submit()
+                try:
+                    ev.wait()
+                finally:
+                    ev.destroy()
+            finally:
+                batch.destroy()
         self.sums = None
         self.path = ""
 
@@ -338,7 +355,7 @@ class MulMat:
         want_streamed = self.streamed if self.streamed is not None else (self.streamed_pays(M) and epilogue is None)
         streamed = (not use_tc and M <= GEMV_MAX_M and t != GGML_TYPE_I2_S and t not in BYTE_DECODED and K % 256 == 0 and not self.dump
                     and not self.exact and (want_streamed or bool(peers)))
-        if peers and not (use_tc and t != GGML_TYPE_I2_S) and not streamed:
+        if peers and not (use_tc and t != GGML_TYPE_I2_S and t not in BYTE_DECODED) and not streamed:
             raise MulMatUnsupported("the fused peer exchange is built for the tensor-core GEMM of the scaled types and "
                                     "the streamed GEMV (K a multiple of 256)")
         if use_tc:
@@ -351,7 +368,10 @@ class MulMat:
                 batch.dispatch(ctx.kernel(f"ameva_mmtc_{TYPE_NAMES[t]}_mp"), [self.qbind, self.sbind, self.ah] + outs + [self.ae],
                                [M, N, K, dst_stride, self.gemm_flags, len(peers)], grid)
                 return
-            if t == GGML_TYPE_I2_S:
+            if t in BYTE_DECODED:
+                batch.dispatch(ctx.kernel("ameva_mmtc_b8"), [self.qbind, self.h, self.ah, (dst, dst_offset), self.ae],
+                               [M, N, K, dst_stride, self.gemm_flags, 1 if t in BYTE_SIGNED else 0], grid)
+            elif t == GGML_TYPE_I2_S:
                 push = [M, N, K, dst_stride, int(np.float32(self.view.weight.scale).view(np.uint32))]
                 batch.dispatch(ctx.kernel("bitnet_gemm_i2_s"), [self.qbind, self.aq, (dst, dst_offset), self.ad], push,
                                grid)
@@ -454,7 +474,7 @@ class MulMat:
         return q, act[:, 0].copy().view(np.float32), act[:, 1].copy().view(np.int32)
 
     def destroy(self) -> None:
-        for name in ("aq", "ad", "ah", "ae", "y", "qeo", "sums"):
+        for name in ("aq", "ad", "ah", "ae", "h", "y", "qeo", "sums"):
             b = getattr(self, name, None)
             if b is not None:
                 b.destroy()

@@ -399,7 +399,9 @@ AcResult ac_b200_repack_to_device(uint32_t ggml_type, const void* ggml_blocks, u
  * as 256 int8 per block, the block's first 8 bytes (d, scales_h, scales_l) as its scale record; ameva_mmvqb_iq4_xs.
  * Q4_1 (3) / Q5_1 (7): q as 32 bytes per block, (d, m) as a 4-byte record; ameva_mmvq_q4_1 / ameva_mmvq_q5_1.
  * Q3_K (11): q3 (-4..3) as 256 int8 per block, scales[12] + d as a 14-byte record; ameva_mmvqb_q3_K. Q2_K (10): q2 (0..3)
- * as 256 bytes per block, scales[16] + d + dmin as a 20-byte record; ameva_mmvqb_q2_K. */
+ * as 256 bytes per block, scales[16] + d + dmin as a 20-byte record; ameva_mmvqb_q2_K.
+ * More than 8 activation rows of these seven types (K % 256 == 0): ac_b200_mul_mat_plan answers AC_B200_PATH_GEMM_TC,
+ * which for them is ameva_mmtc_scales (scale records -> fp16 (scale, offset) per 16 weights) + ameva_mmtc_b8. */
 uint32_t ac_b200_device_type(uint32_t ggml_type);
 AcResult ac_b200_repack_from_device(uint32_t ggml_type, const void* device_layout, uint64_t rows, uint64_t k,
                                     void* ggml_blocks);

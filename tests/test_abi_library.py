@@ -197,6 +197,8 @@ def test_kernel_choice_policy():
         (Q8_0, 512, 11008, 4096, rt.PLAN_EXACT, GEMV),            # exact per-block sums: chunks of 8 rows on dp4a
         (Q8_0, 512, 11008, 4096, rt.PLAN_WEIGHT_RANGE, GEMV),     # weights fp16 does not hold: integer kernels
         (Q4_0, 33, 96, 96, 0, GEMV),                              # K the GEMM cannot take
+        (14, 8, 4096, 14336, 0, GEMV), (14, 9, 4096, 14336, 0, TC), (10, 512, 4096, 4096, 0, TC), (3, 64, 128, 256, 0, TC),   # decoded to bytes
+        (3, 64, 128, 96, 0, GEMV), (13, 64, 4096, 4096, rt.PLAN_EXACT, GEMV), (23, 64, 4096, 4096, rt.PLAN_WEIGHT_RANGE, GEMV),
         (Q4_K, 4, 11008, 4096, rt.PLAN_PEERS, STREAMED), (Q8_0, 512, 11008, 4096, rt.PLAN_PEERS, TC),
     ]
     for t, M, N, K, flags, want in table:

@@ -97,7 +97,7 @@ def test_q6_K_mul_mat(ctx, M, N, K):
     mm = qmm.MulMat(ctx, w, M)
     xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
     mm.run(xb, dst, M)
-    assert mm.path in ("mmvq", "mmvq-chunks")
+    assert mm.path in ("mmvq", "mmtc")
     want, _, _ = oracle_mul_mat(Q6_K, blocks, scale, x, N, K, want_sums=False)
     assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
     with pytest.raises(qmm.MulMatUnsupported):
@@ -225,3 +225,70 @@ def test_q3_K_and_q2_K(ctx, t, M, N, K):
     finally:
         for o in (mm, xb, dst, w, host):
             o.destroy()
+
+
+@pytest.mark.parametrize("t", [Q6_K, Q5_K, IQ4_XS, Q3_K, Q2_K, Q4_1, Q5_1])
+@pytest.mark.parametrize("M,N,K", [(33, 768, 2048), (200, 300, 1024), (520, 1000, 4096), (9, 128, 256)])
+def test_byte_decoded_prompt_runs_on_the_tensor_cores(ctx, t, M, N, K):
+    """More than 8 activation rows of a byte-decoded type: ameva_mmtc_b8 over the (scale, offset) table that
+    ameva_mmtc_scales writes from the scale records, within the fp16-operand tolerance of the oracle's product; the
+    exact mode keeps the same rows on the GEMV in chunks of 8."""
+    blocks, scale = make_weights(t, N, K, M)
+    x = make_acts(M, K, M + 1)
+    w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K)
+    mm, ex = qmm.MulMat(ctx, w, M), qmm.MulMat(ctx, w, M, exact=True)
+    xb, dst = ctx.buffer(data=x), ctx.buffer(M * N * 4)
+    try:
+        want, _, _ = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+        mm.run(xb, dst, M)
+        assert mm.path == "mmtc"
+        assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
+        ex.run(xb, dst, M)
+        assert ex.path == "mmvq-chunks"
+        assert max_normalised_error(dst.read(np.float32).reshape(M, N), want) <= 1e-3
+        mm.run(xb, dst, 8)      # the same object serves token generation on the GEMV
+        assert mm.path == "mmvq"
+        assert max_normalised_error(dst.read(np.float32)[:8 * N].reshape(8, N), want[:8]) <= 1e-3
+    finally:
+        for o in (mm, ex, xb, dst, w):
+            o.destroy()
+
+
+def test_gemm_scale_table_holds_the_decoded_scales(ctx):
+    """ameva_mmtc_scales: per 16 weights fp16 (scale, offset) with w = scale * q + offset, equal to the oracle's decode of
+    the scale records rounded once to fp16."""
+    N, K = 24, 512
+    for t in (Q6_K, Q5_K, IQ4_XS, Q3_K, Q2_K, Q4_1, Q5_1):
+        blocks, _ = make_weights(t, N, K, t)
+        w = qmm.QuantWeight.from_ggml(ctx, t, blocks, N, K)
+        mm = qmm.MulMat(ctx, w, 16)
+        try:
+            got = mm.h.read(np.float16, N * (K // 16) * 2).reshape(-1, 2).astype(np.float32)
+            if t == Q6_K:
+                d, sc, _ = extra_types.decode_q6_K(blocks)
+                s, o = d.astype(np.float32)[:, None] * sc.astype(np.float32), None
+            elif t == Q5_K:
+                d, dmin, sc, mn, _ = extra_types.decode_q5_K(blocks)
+                s = np.repeat(d.astype(np.float32)[:, None] * sc.astype(np.float32), 2, axis=1)
+                o = -np.repeat(dmin.astype(np.float32)[:, None] * mn.astype(np.float32), 2, axis=1)
+            elif t == IQ4_XS:
+                d, ls, _ = extra_types.decode_iq4_xs(blocks)
+                s, o = np.repeat(d.astype(np.float32)[:, None] * ls.astype(np.float32), 2, axis=1), None
+            elif t == Q3_K:
+                d, sc, _ = extra_types.decode_q3_K(blocks)
+                s, o = d.astype(np.float32)[:, None] * sc.astype(np.float32), None
+            elif t == Q2_K:
+                d, dmin, sc, mn, _ = extra_types.decode_q2_K(blocks)
+                s = d.astype(np.float32)[:, None] * sc.astype(np.float32)
+                o = -(dmin.astype(np.float32)[:, None] * mn.astype(np.float32))
+            else:
+                raw = blocks.reshape(-1, 20 if t == Q4_1 else 24)
+                dm = raw[:, 0:4].copy().view(np.float16).astype(np.float32)
+                s, o = np.repeat(dm[:, 0:1], 2, axis=1), np.repeat(dm[:, 1:2], 2, axis=1)
+            s = s.reshape(-1)
+            o = np.zeros_like(s) if o is None else o.reshape(-1)
+            assert np.array_equal(got[:, 0], s.astype(np.float16).astype(np.float32))
+            assert np.array_equal(got[:, 1], o.astype(np.float16).astype(np.float32))
+        finally:
+            mm.destroy()
+            w.destroy()
