@@ -537,7 +537,7 @@ AcResult launch_gemv_f16(const LaunchArgs& a) {
 // round by shuffles, so the V rows are read coalesced. The warps of a CTA, then the splits (ameva_fa_combine's job in
 // the reference: a second kernel here too) are merged with the usual maximum / sum rescaling. The work is bound by
 // reading the KV cache from HBM: n_kv * n_head_kv * (D + DV) * 2 bytes per query position.
-// Prompts (n_q > 1) are computed one query position per CTA: correct, K and V re-read per position.
+// Prompts (n_q > 1, D <= 128): 16 / G query positions per CTA (flash_tile_kernel below); D = 256: one position per CTA.
 // Not taken: ALiBi (max_bias != 0), f32 or quantized K / V, G > 8, D != DV: refused with AC_ERR_FEATURE_NOT_SUPPORTED
 // (the host keeps such nodes on its other path).
 // ---------------------------------------------------------------------------------------------------------------------
@@ -566,6 +566,11 @@ __device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.w
 constexpr int kFaHeads = 8;   // query heads per KV head a CTA carries (rows 0..7 of the 16-row MMA tile; 8..15 stay zero)
 
 // the warps' K and V tiles; after the last block the same memory holds the warps' results for the merge
+template <int D>
+constexpr size_t flash_tile_smem_bytes() {   // the kernel for prompts merges sixteen rows per warp
+    constexpr size_t tiles = 2 * sizeof(__half) * kFaWarps * 32 * D, merge = sizeof(float) * kFaWarps * 16 * (D + 2);
+    return tiles > merge ? tiles : merge;
+}
 template <int D>
 constexpr size_t flash_smem_bytes() {
     constexpr size_t tiles = 2 * sizeof(__half) * kFaWarps * 32 * D, merge = sizeof(float) * kFaWarps * kFaHeads * (D + 2);
@@ -794,6 +799,209 @@ __global__ void __launch_bounds__(kFaWarps * 32) flash_decode_kernel(const float
     }
 }
 
+// D (16 x 8, fp32) += A (16 x 16, f16) * B (16 x 8, f16), all sixteen rows
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Prompts (n_q > 1): the sixteen rows of the MMA tile are QT = 16 / G consecutive query positions x the G heads of the KV
+// head (row r: position q0 + r / G, head h0 + r % G), so a CTA reads its K and V rows once for QT positions instead of
+// once per position, and both halves of the tile carry work. Everything else (key splits, staging, online softmax per
+// row, the merge of the warps and of the splits) is the kernel above with two rows per thread (g and g + 8).
+template <int D>
+__global__ void __launch_bounds__(kFaWarps * 32) flash_tile_kernel(const float* __restrict__ q, const __half* __restrict__ k,
+                                                                   const __half* __restrict__ v,
+                                                                   const __half* __restrict__ mask, float* __restrict__ o,
+                                                                   float* __restrict__ part, const FlashArgs pc,
+                                                                   uint32_t n_splits) {
+    constexpr int KS = D / 16, NT = D / 8;
+    constexpr uint32_t P = D / 8;
+    extern __shared__ __align__(16) uint8_t fa_smem[];
+    float (*s_acc)[16][D + 2] = reinterpret_cast<float (*)[16][D + 2]>(fa_smem);   // per warp and row: D sums, max, sum
+    uint8_t* tiles = fa_smem;
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t z = blockIdx.x, hkv = blockIdx.y;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    __half (*s_k)[D] = reinterpret_cast<__half (*)[D]>(tiles + sizeof(__half) * 32 * D * (2 * warp));
+    __half (*s_v)[D] = reinterpret_cast<__half (*)[D]>(tiles + sizeof(__half) * 32 * D * (2 * warp + 1));
+    const uint32_t G = pc.n_head / pc.n_head_kv, h0 = hkv * G, QT = 16u / G, q0 = blockIdx.z * QT;
+    const float ninf = __uint_as_float(0xFF800000u);
+    const uint32_t key_begin = z * pc.split_keys, key_end = min(pc.n_kv, key_begin + pc.split_keys);
+    const __half* kbase = k + pc.k_off + (uint64_t)hkv * pc.k_s2;
+    const __half* vbase = v + pc.v_off + (uint64_t)hkv * pc.v_s2;
+    uint32_t k0 = key_begin + warp * 32u;
+    if (k0 < key_end) {
+        stage_rows<D>(s_k, kbase + (uint64_t)k0 * pc.k_s1, pc.k_s1, min(32u, key_end - k0), lane);
+        stage_rows<D>(s_v, vbase + (uint64_t)k0 * pc.v_s1, pc.v_s1, min(32u, key_end - k0), lane);
+    }
+    const uint32_t g = lane >> 2, t4 = lane & 3u;
+    // this thread's two rows: r = g and g + 8
+    uint32_t iq[2], hd[2];
+    bool valid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t r = g + 8u * h;
+        iq[h] = q0 + r / G;
+        hd[h] = h0 + r % G;
+        valid[h] = r < QT * G && iq[h] < pc.n_q;
+    }
+    uint32_t qa[KS][4];   // a0 (row g, columns c, c + 1), a1 (row g + 8), a2 (row g, c + 8, c + 9), a3 (row g + 8)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float* qrow = q + pc.q_off + (uint64_t)(valid[h] ? iq[h] : 0u) * pc.q_s1 + (uint64_t)(valid[h] ? hd[h] : h0) * pc.q_s2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const uint32_t c = 16u * ks + 2u * t4;
+            qa[ks][h] = valid[h] ? pack_h2(qrow[c], qrow[c + 1u]) : 0u;
+            qa[ks][2 + h] = valid[h] ? pack_h2(qrow[c + 8u], qrow[c + 9u]) : 0u;
+        }
+    }
+    const float scale = u2f(pc.scale), softcap = u2f(pc.softcap);
+    float oc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oc[nt][j] = 0.0f;
+    float m_run[2] = {ninf, ninf}, l_run[2] = {0.0f, 0.0f};
+    const __half* mrow[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+        mrow[h] = mask + pc.m_off + (uint64_t)(valid[h] ? iq[h] : 0u) * pc.m_s1 +
+                  (uint64_t)((valid[h] ? hd[h] : h0) % (pc.has_mask ? pc.m_ne2 : 1u)) * pc.m_s2;
+    const uint32_t lm_row = (lane & 7u) + ((lane >> 4) << 3), lm_hi = (lane >> 3) & 1u;
+    const uint32_t lv_row = (lane & 7u) + (((lane >> 3) & 1u) << 3), lv_nt = lane >> 4;
+    for (; k0 < key_end; k0 += kFaWarps * 32u) {
+        const uint32_t next = k0 + kFaWarps * 32u;
+        const bool more = next < key_end;
+        cp_async_wait_group<1>();
+        __syncwarp();
+        float sc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) sc[nt][j] = 0.0f;
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+            const uint32_t key = 16u * np + lm_row;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+                uint32_t b[4];
+                ldmatrix_x4(b, &s_k[key][8u * ((2u * ks + lm_hi) ^ (key & (P - 1u)))]);
+                mma_16816(sc[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
+                mma_16816(sc[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        if (more) stage_rows<D>(s_k, kbase + (uint64_t)next * pc.k_s1, pc.k_s1, min(32u, key_end - next), lane);
+        else cp_async_commit();
+        uint32_t pa[2][4];   // the probabilities as A fragments of the second product, per 16 keys
+        float factor[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float x[4][2], bm = ninf;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const uint32_t key = k0 + 8u * nt + 2u * t4 + j;
+                    float xv = ninf;
+                    if (valid[h] && key < key_end) {
+                        xv = sc[nt][2 * h + j] * scale;
+                        if (softcap != 0.0f) xv = softcap * tanhf(xv / softcap);
+                        if (pc.has_mask) xv += __half2float(mrow[h][key]);
+                    }
+                    x[nt][j] = xv;
+                    bm = fmaxf(bm, xv);
+                }
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+            const float m_new = fmaxf(m_run[h], bm);
+            factor[h] = m_new == ninf ? 1.0f : expf(m_run[h] - m_new);
+            float ps = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const float p0 = x[nt][0] == ninf ? 0.0f : expf(x[nt][0] - m_new);
+                const float p1 = x[nt][1] == ninf ? 0.0f : expf(x[nt][1] - m_new);
+                ps += p0 + p1;
+                pa[nt >> 1][2 * (nt & 1) + h] = pack_h2(p0, p1);   // a0 / a1: keys 2 t4 + {0, 1}; a2 / a3: + 8
+            }
+            ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+            l_run[h] = l_run[h] * factor[h] + ps;
+            m_run[h] = m_new;
+        }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            oc[nt][0] *= factor[0];
+            oc[nt][1] *= factor[0];
+            oc[nt][2] *= factor[1];
+            oc[nt][3] *= factor[1];
+        }
+        cp_async_wait_group<1>();
+        __syncwarp();
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+                const uint32_t key = 16u * kk + lv_row;
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, &s_v[key][8u * ((2u * np + lv_nt) ^ (key & (P - 1u)))]);
+                mma_16816(oc[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[0], b[1]);
+                mma_16816(oc[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        if (more) stage_rows<D>(s_v, vbase + (uint64_t)next * pc.v_s1, pc.v_s1, min(32u, key_end - next), lane);
+        else cp_async_commit();
+    }
+    cp_async_wait_group<0>();
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t r = g + 8u * h;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            s_acc[warp][r][8 * nt + 2 * t4] = oc[nt][2 * h];
+            s_acc[warp][r][8 * nt + 2 * t4 + 1] = oc[nt][2 * h + 1];
+        }
+        if (t4 == 0) {
+            s_acc[warp][r][D] = m_run[h];
+            s_acc[warp][r][D + 1] = l_run[h];
+        }
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < QT * G * D; i += kFaWarps * 32) {
+        const uint32_t r = i / D, d = i - r * D, pos = q0 + r / G;
+        if (pos >= pc.n_q) break;   // (rows are ordered by position)
+        float mx = ninf;
+#pragma unroll
+        for (int w = 0; w < kFaWarps; ++w) mx = fmaxf(mx, s_acc[w][r][D]);
+        float num = 0.0f, den = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kFaWarps; ++w) {
+            const float mw = s_acc[w][r][D];
+            const float f = mw == ninf ? 0.0f : expf(mw - mx);
+            num = fmaf(s_acc[w][r][d], f, num);
+            den = fmaf(s_acc[w][r][D + 1], f, den);
+        }
+        const uint64_t orow = (uint64_t)pos * pc.n_head + h0 + r % G;
+        if (n_splits == 1u) {
+            o[pc.o_off + orow * D + d] = num / den;
+        } else {
+            float* pr = part + pc.part_off + ((uint64_t)z * pc.n_q * pc.n_head + orow) * (D + 4);
+            pr[4 + d] = num;
+            if (d == 0) {
+                pr[0] = mx;
+                pr[1] = den;
+            }
+        }
+    }
+}
+
 // merges the partial results of the key splits: one CTA per output row; the splits' maxima and sums are read in parallel,
 // then every thread sums its columns over the splits (independent, coalesced loads)
 constexpr uint32_t kFaMaxSplits = 1024;
@@ -860,6 +1068,16 @@ __global__ void __launch_bounds__(128) flash_combine_kernel(const float* __restr
 }
 
 template <int D>
+static bool launch_flash_tile_d(const LaunchArgs& a, const FlashArgs& pc, uint32_t n_splits, uint32_t q_tiles) {
+    constexpr size_t smem = flash_tile_smem_bytes<D>();
+    if (!ensure_dynamic_smem<flash_tile_kernel<D>>((int)smem)) return false;
+    const dim3 grid(n_splits, pc.n_head_kv, q_tiles), block(kFaWarps * 32);
+    launch_pdl(flash_tile_kernel<D>, grid, block, smem, a.stream, (const float*)a.ptr[0], (const __half*)a.ptr[1],
+               (const __half*)a.ptr[2], (const __half*)a.ptr[3], (float*)a.ptr[4], (float*)a.ptr[5], pc, n_splits);
+    return true;
+}
+
+template <int D>
 static bool launch_flash_d(const LaunchArgs& a, const FlashArgs& pc, uint32_t n_splits) {
     constexpr size_t smem = flash_smem_bytes<D>();
     if (!ensure_dynamic_smem<flash_decode_kernel<D>>((int)smem)) return false;
@@ -896,8 +1114,14 @@ AcResult launch_flash_attn(const LaunchArgs& a) {
     // key splits: one wave of CTAs (as many as are resident at once), at least 128 keys (one block of 32 per warp) each,
     // as many as the scratch holds
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
-    const uint64_t ctas = (uint64_t)pc.n_head_kv * pc.n_q;
-    const size_t smem = pc.D == 64u ? flash_smem_bytes<64>() : pc.D == 128u ? flash_smem_bytes<128>() : flash_smem_bytes<256>();
+    // prompts: 16 / G query positions per CTA (D = 256 would not keep two rows' fragments in registers)
+    const uint32_t QT = 16u / G;
+    const bool tile = pc.n_q > 1u && QT >= 2u && pc.D <= 128u;
+    const uint32_t q_tiles = tile ? (pc.n_q + QT - 1u) / QT : pc.n_q;
+    const uint64_t ctas = (uint64_t)pc.n_head_kv * q_tiles;
+    if (q_tiles > 65535u) return AC_ERR_INVALID_WORK_ITEM_DIMS;
+    const size_t smem = tile ? (pc.D == 64u ? flash_tile_smem_bytes<64>() : flash_tile_smem_bytes<128>())
+                             : pc.D == 64u ? flash_smem_bytes<64>() : pc.D == 128u ? flash_smem_bytes<128>() : flash_smem_bytes<256>();
     uint32_t per_sm = (uint32_t)((227u * 1024u) / (smem + 1024u));
     if (per_sm > 4u) per_sm = 4u;
     if (per_sm < 1u) per_sm = 1u;
@@ -913,7 +1137,9 @@ AcResult launch_flash_attn(const LaunchArgs& a) {
     if (n_splits > kFaMaxSplits) n_splits = kFaMaxSplits;
     pc.split_keys = ((pc.n_kv + n_splits - 1u) / n_splits + 31u) & ~31u;
     n_splits = (pc.n_kv + pc.split_keys - 1u) / pc.split_keys;
-    const bool fits = pc.D == 64u ? launch_flash_d<64>(a, pc, n_splits)
+    const bool fits = tile ? (pc.D == 64u ? launch_flash_tile_d<64>(a, pc, n_splits, q_tiles)
+                                          : launch_flash_tile_d<128>(a, pc, n_splits, q_tiles))
+                      : pc.D == 64u ? launch_flash_d<64>(a, pc, n_splits)
                       : pc.D == 128u ? launch_flash_d<128>(a, pc, n_splits) : launch_flash_d<256>(a, pc, n_splits);
     if (!fits) return AC_ERR_INVALID_WORK_GROUP_SIZE;
     AcResult rc = check_launch();

@@ -283,6 +283,11 @@ def _flash_push(D, n_kv, n_q, n_head, n_head_kv, has_mask, scale, softcap=0.0, m
     (128, 28, 4, 2048, 2, True, 0.0, 64),          # scratch too small for splits: every CTA walks all keys
     (128, 64, 8, 333, 1, False, 0.0, 8 << 20),     # eight heads per KV head
     (128, 32, 8, 32768, 1, True, 0.0, 16 << 20),   # a long context: 134 MB of cache, many key splits
+    (128, 32, 8, 512, 512, True, 0.0, 16 << 20),   # a prompt of 512 tokens: four positions x four heads per CTA
+    (64, 12, 12, 300, 77, True, 0.0, 8 << 20),     # no grouping: sixteen positions per CTA, a ragged last tile
+    (128, 24, 8, 200, 50, False, 0.0, 64),         # three heads per KV head: five positions per CTA, one row idle
+    (128, 64, 8, 256, 9, True, 0.0, 8 << 20),      # eight heads per KV head: two positions per CTA
+    (256, 8, 4, 128, 5, True, 0.0, 8 << 20),       # D = 256 prompts stay on one position per CTA
 ])
 def test_flash_attn_decode(ctx, D, n_head, n_head_kv, n_kv, n_q, masked, softcap, scratch):
     rng = np.random.default_rng(D + n_kv)
