@@ -1002,6 +1002,234 @@ __global__ void __launch_bounds__(kFaWarps * 32) flash_tile_kernel(const float* 
     }
 }
 
+// Longer prompts (n_q * G > 16): the four warps of a CTA share every staged K / V tile and own sixteen rows each, so a
+// CTA carries 64 rows = 64 / G query positions x G heads and a tile is fetched once for all of them (a quarter of the
+// traffic between L2 and shared memory of the kernel above, which bounded it). Tiles of 32 keys are double-buffered
+// (the next tile's copies are in flight while this one is multiplied). A warp whose rows are all masked for a tile (the
+// upper triangle of a causal prompt) skips the tile's arithmetic. No merge between warps: a thread holds the maximum,
+// the sum and its columns of two rows from the first key to the last and writes them out itself.
+template <int D>
+__global__ void __launch_bounds__(kFaWarps * 32, 3) flash_prompt_kernel(const float* __restrict__ q, const __half* __restrict__ k,
+                                                                     const __half* __restrict__ v,
+                                                                     const __half* __restrict__ mask, float* __restrict__ o,
+                                                                     float* __restrict__ part, const FlashArgs pc,
+                                                                     uint32_t n_splits) {
+    constexpr int KS = D / 16, NT = D / 8;
+    constexpr uint32_t P = D / 8;
+    extern __shared__ __align__(16) uint8_t fa_smem[];
+    typedef __half (*Tile)[D];
+    pdl_trigger();
+    pdl_wait();
+    const uint32_t z = blockIdx.x, hkv = blockIdx.y;
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t G = pc.n_head / pc.n_head_kv, h0 = hkv * G, QT = 64u / G, q0 = blockIdx.z * QT;
+    const float ninf = __uint_as_float(0xFF800000u);
+    const uint32_t key_begin = z * pc.split_keys, key_end = min(pc.n_kv, key_begin + pc.split_keys);
+    const __half* kbase = k + pc.k_off + (uint64_t)hkv * pc.k_s2;
+    const __half* vbase = v + pc.v_off + (uint64_t)hkv * pc.v_s2;
+    // stage s: K tile, then V tile (32 x D halves each)
+    auto tile_k = [&](uint32_t st) { return reinterpret_cast<Tile>(fa_smem + sizeof(__half) * 32 * D * (2 * st)); };
+    auto tile_v = [&](uint32_t st) { return reinterpret_cast<Tile>(fa_smem + sizeof(__half) * 32 * D * (2 * st + 1)); };
+    auto stage = [&](uint32_t st, uint32_t key0) {   // the whole CTA copies one K and one V tile; one commit group
+        const uint32_t rows = min(32u, key_end - key0);
+        Tile tk = tile_k(st), tv = tile_v(st);
+#pragma unroll 4
+        for (uint32_t i = threadIdx.x; i < 32u * P; i += kFaWarps * 32u) {
+            const uint32_t row = i / P, piece = i - row * P, col = 8u * (piece ^ (row & (P - 1u)));
+            if (row < rows) {
+                cp_async16(&tk[row][col], kbase + (uint64_t)(key0 + row) * pc.k_s1 + 8u * piece);
+                cp_async16(&tv[row][col], vbase + (uint64_t)(key0 + row) * pc.v_s1 + 8u * piece);
+            } else {
+                *reinterpret_cast<uint4*>(&tk[row][col]) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(&tv[row][col]) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        cp_async_commit();
+    };
+    if (key_begin < key_end) stage(0u, key_begin);
+    const uint32_t g = lane >> 2, t4 = lane & 3u;
+    uint32_t iq[2], hd[2];
+    bool valid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t r = 16u * warp + g + 8u * h;   // row of the CTA
+        iq[h] = q0 + r / G;
+        hd[h] = h0 + r % G;
+        valid[h] = r < QT * G && iq[h] < pc.n_q;
+    }
+    uint32_t qa[KS][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float* qrow = q + pc.q_off + (uint64_t)(valid[h] ? iq[h] : 0u) * pc.q_s1 + (uint64_t)(valid[h] ? hd[h] : h0) * pc.q_s2;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            const uint32_t c = 16u * ks + 2u * t4;
+            qa[ks][h] = valid[h] ? pack_h2(qrow[c], qrow[c + 1u]) : 0u;
+            qa[ks][2 + h] = valid[h] ? pack_h2(qrow[c + 8u], qrow[c + 9u]) : 0u;
+        }
+    }
+    const float scale = u2f(pc.scale), softcap = u2f(pc.softcap);
+    float oc[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) oc[nt][j] = 0.0f;
+    float m_run[2] = {ninf, ninf}, l_run[2] = {0.0f, 0.0f};
+    const __half* mrow[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+        mrow[h] = mask + pc.m_off + (uint64_t)(valid[h] ? iq[h] : 0u) * pc.m_s1 +
+                  (uint64_t)((valid[h] ? hd[h] : h0) % (pc.has_mask ? pc.m_ne2 : 1u)) * pc.m_s2;
+    const uint32_t lm_row = (lane & 7u) + ((lane >> 4) << 3), lm_hi = (lane >> 3) & 1u;
+    const uint32_t lv_row = (lane & 7u) + (((lane >> 3) & 1u) << 3), lv_nt = lane >> 4;
+    // This thread's mask values of a tile: rows g, g + 8, keys k0 + 8 nt + 2 t4 + {0, 1}, as pairs of halves; -inf for
+    // keys past the end and for idle rows. They are fetched one tile ahead, so the loads' latency is not waited for.
+    const bool m_pairs = ((((uintptr_t)mrow[0]) | ((uintptr_t)mrow[1])) & 3u) == 0u;
+    auto load_mask = [&](uint32_t key0, uint32_t (&raw)[2][4]) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const uint32_t key = key0 + 8u * nt + 2u * t4;
+                uint32_t w = 0xFC00FC00u;   // (-inf, -inf)
+                if (valid[h] && key < key_end) {
+                    if (!pc.has_mask) {
+                        w = key + 1u < key_end ? 0u : 0xFC000000u;
+                    } else if (m_pairs && key + 1u < key_end) {
+                        w = *reinterpret_cast<const uint32_t*>(mrow[h] + key);
+                    } else {
+                        const uint32_t lo = *reinterpret_cast<const uint16_t*>(mrow[h] + key);
+                        const uint32_t hi = key + 1u < key_end ? *reinterpret_cast<const uint16_t*>(mrow[h] + key + 1u) : 0xFC00u;
+                        w = lo | (hi << 16);
+                    }
+                }
+                raw[h][nt] = w;
+            }
+    };
+    uint32_t m_next[2][4];
+    load_mask(key_begin, m_next);
+    uint32_t st = 0;
+    for (uint32_t k0 = key_begin; k0 < key_end; k0 += 32u, st ^= 1u) {
+        const uint32_t next = k0 + 32u;
+        if (next < key_end) stage(st ^ 1u, next);   // (that buffer was released by the barrier that ended the last tile)
+        else cp_async_commit();
+        float mk[2][4][2];
+        bool any = false;
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&m_next[h][nt]));
+                mk[h][nt][0] = f.x;
+                mk[h][nt][1] = f.y;
+                any = any || f.x != ninf || f.y != ninf;
+            }
+        if (next < key_end) load_mask(next, m_next);
+        const bool work = __any_sync(0xffffffffu, any);
+        cp_async_wait_group<1>();   // this tile has landed (the next one may be on its way)
+        __syncthreads();
+        if (work) {
+            Tile s_k = tile_k(st), s_v = tile_v(st);
+            float sc[4][4];
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) sc[nt][j] = 0.0f;
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
+                const uint32_t key = 16u * np + lm_row;
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, &s_k[key][8u * ((2u * ks + lm_hi) ^ (key & (P - 1u)))]);
+                    mma_16816(sc[2 * np], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[0], b[1]);
+                    mma_16816(sc[2 * np + 1], qa[ks][0], qa[ks][1], qa[ks][2], qa[ks][3], b[2], b[3]);
+                }
+            }
+            uint32_t pa[2][4];
+            float factor[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                float x[4][2], bm = ninf;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        float xv = ninf;
+                        if (mk[h][nt][j] != ninf) {
+                            xv = sc[nt][2 * h + j] * scale;
+                            if (softcap != 0.0f) xv = softcap * tanhf(xv / softcap);
+                            xv += mk[h][nt][j];
+                        }
+                        x[nt][j] = xv;
+                        bm = fmaxf(bm, xv);
+                    }
+                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+                const float m_new = fmaxf(m_run[h], bm);
+                factor[h] = m_new == ninf ? 1.0f : expf(m_run[h] - m_new);
+                float ps = 0.0f;
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt) {
+                    const float p0 = x[nt][0] == ninf ? 0.0f : expf(x[nt][0] - m_new);
+                    const float p1 = x[nt][1] == ninf ? 0.0f : expf(x[nt][1] - m_new);
+                    ps += p0 + p1;
+                    pa[nt >> 1][2 * (nt & 1) + h] = pack_h2(p0, p1);
+                }
+                ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+                ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+                l_run[h] = l_run[h] * factor[h] + ps;
+                m_run[h] = m_new;
+            }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                oc[nt][0] *= factor[0];
+                oc[nt][1] *= factor[0];
+                oc[nt][2] *= factor[1];
+                oc[nt][3] *= factor[1];
+            }
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    const uint32_t key = 16u * kk + lv_row;
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, &s_v[key][8u * ((2u * np + lv_nt) ^ (key & (P - 1u)))]);
+                    mma_16816(oc[2 * np], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[0], b[1]);
+                    mma_16816(oc[2 * np + 1], pa[kk][0], pa[kk][1], pa[kk][2], pa[kk][3], b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();   // every warp is done with this stage: the tile after next may overwrite it
+    }
+    cp_async_wait_group<0>();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (!valid[h]) continue;
+        const uint64_t orow = (uint64_t)iq[h] * pc.n_head + hd[h];
+        if (n_splits == 1u) {
+            float* dst = o + pc.o_off + orow * D + 2u * t4;
+            const float inv = 1.0f / l_run[h];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                dst[8 * nt] = oc[nt][2 * h] * inv;
+                dst[8 * nt + 1] = oc[nt][2 * h + 1] * inv;
+            }
+        } else {
+            float* pr = part + pc.part_off + ((uint64_t)z * pc.n_q * pc.n_head + orow) * (D + 4);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                pr[4 + 8 * nt + 2 * t4] = oc[nt][2 * h];
+                pr[4 + 8 * nt + 2 * t4 + 1] = oc[nt][2 * h + 1];
+            }
+            if (t4 == 0) {
+                pr[0] = m_run[h];
+                pr[1] = l_run[h];
+            }
+        }
+    }
+}
+
 // merges the partial results of the key splits: one CTA per output row; the splits' maxima and sums are read in parallel,
 // then every thread sums its columns over the splits (independent, coalesced loads)
 constexpr uint32_t kFaMaxSplits = 1024;
@@ -1078,6 +1306,15 @@ static bool launch_flash_tile_d(const LaunchArgs& a, const FlashArgs& pc, uint32
 }
 
 template <int D>
+static bool launch_flash_prompt_d(const LaunchArgs& a, const FlashArgs& pc, uint32_t n_splits, uint32_t q_tiles) {
+    constexpr size_t smem = 4 * sizeof(__half) * 32 * D;   // two stages of a K and a V tile
+    const dim3 grid(n_splits, pc.n_head_kv, q_tiles), block(kFaWarps * 32);
+    launch_pdl(flash_prompt_kernel<D>, grid, block, smem, a.stream, (const float*)a.ptr[0], (const __half*)a.ptr[1],
+               (const __half*)a.ptr[2], (const __half*)a.ptr[3], (float*)a.ptr[4], (float*)a.ptr[5], pc, n_splits);
+    return true;
+}
+
+template <int D>
 static bool launch_flash_d(const LaunchArgs& a, const FlashArgs& pc, uint32_t n_splits) {
     constexpr size_t smem = flash_smem_bytes<D>();
     if (!ensure_dynamic_smem<flash_decode_kernel<D>>((int)smem)) return false;
@@ -1115,12 +1352,15 @@ AcResult launch_flash_attn(const LaunchArgs& a) {
     // as many as the scratch holds
     const uint32_t sms = a.sm_count > 0 ? (uint32_t)a.sm_count : 148u;
     // prompts: 16 / G query positions per CTA (D = 256 would not keep two rows' fragments in registers)
-    const uint32_t QT = 16u / G;
-    const bool tile = pc.n_q > 1u && QT >= 2u && pc.D <= 128u;
-    const uint32_t q_tiles = tile ? (pc.n_q + QT - 1u) / QT : pc.n_q;
+    // (more than one such tile's worth of rows: 64 / G positions per CTA, the warps sharing the staged tiles)
+    const bool prompt = pc.n_q > 1u && pc.D <= 128u && (uint64_t)pc.n_q * G > 16u;
+    const uint32_t QT = prompt ? 64u / G : 16u / G;
+    const bool tile = !prompt && pc.n_q > 1u && QT >= 2u && pc.D <= 128u;
+    const uint32_t q_tiles = (tile || prompt) ? (pc.n_q + QT - 1u) / QT : pc.n_q;
     const uint64_t ctas = (uint64_t)pc.n_head_kv * q_tiles;
     if (q_tiles > 65535u) return AC_ERR_INVALID_WORK_ITEM_DIMS;
-    const size_t smem = tile ? (pc.D == 64u ? flash_tile_smem_bytes<64>() : flash_tile_smem_bytes<128>())
+    const size_t smem = prompt ? (size_t)8u * 32u * pc.D
+                        : tile ? (pc.D == 64u ? flash_tile_smem_bytes<64>() : flash_tile_smem_bytes<128>())
                              : pc.D == 64u ? flash_smem_bytes<64>() : pc.D == 128u ? flash_smem_bytes<128>() : flash_smem_bytes<256>();
     uint32_t per_sm = (uint32_t)((227u * 1024u) / (smem + 1024u));
     if (per_sm > 4u) per_sm = 4u;
@@ -1137,7 +1377,9 @@ AcResult launch_flash_attn(const LaunchArgs& a) {
     if (n_splits > kFaMaxSplits) n_splits = kFaMaxSplits;
     pc.split_keys = ((pc.n_kv + n_splits - 1u) / n_splits + 31u) & ~31u;
     n_splits = (pc.n_kv + pc.split_keys - 1u) / pc.split_keys;
-    const bool fits = tile ? (pc.D == 64u ? launch_flash_tile_d<64>(a, pc, n_splits, q_tiles)
+    const bool fits = prompt ? (pc.D == 64u ? launch_flash_prompt_d<64>(a, pc, n_splits, q_tiles)
+                                            : launch_flash_prompt_d<128>(a, pc, n_splits, q_tiles))
+                      : tile ? (pc.D == 64u ? launch_flash_tile_d<64>(a, pc, n_splits, q_tiles)
                                           : launch_flash_tile_d<128>(a, pc, n_splits, q_tiles))
                       : pc.D == 64u ? launch_flash_d<64>(a, pc, n_splits)
                       : pc.D == 128u ? launch_flash_d<128>(a, pc, n_splits) : launch_flash_d<256>(a, pc, n_splits);

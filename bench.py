@@ -68,6 +68,7 @@ WORKLOADS = {
     "cfg5-up-m2048": (Q4_K, 2048, 28672, 8192, 0.01, "Q4_K x Q8_K 28672x8192 M=2048"),
     # not a BASELINE configuration: the Q6_K tensors a Q4_K_M model file carries (ffn_down of a llama-3-8B layer)
     "q6k-down-m1": (Q6_K, 1, 4096, 14336, 0.02, "Q6_K x Q8_K 4096x14336 M=1"),
+    "q6k-down-m512": (Q6_K, 512, 4096, 14336, 0.02, "Q6_K x Q8_K 4096x14336 M=512 (ameva_mmtc_b8)"),
 }
 DECODE_LINES = ("cfg1", "cfg3-qkv-m1", "cfg5-up-m1")      # the M = 1 half of the metric, in the default line
 SHARDED_LINES = ("cfg5-up-m2048", "cfg5-up-m1")           # the row-sharded shapes, in every line
@@ -862,6 +863,30 @@ def layer_op_lines(env, steps=3):
                       "frac": nbytes / s / 1e9 / pk["hbm_gbs"], "launches_per_step": 2, "parity_max_abs_error": worst}
         for b in ks + vs + [qb, mb, ob, pb]:
             b.destroy()
+    # ---- attention over a prompt: 512 positions against themselves under a causal mask (tensor-bound, mma.sync) ----
+    n_q = n_kv = 512
+    kv = (rng.standard_normal((n_head_kv, n_kv, D), dtype=np.float32)).astype(np.float16)
+    q = rng.standard_normal((n_head, n_q, D)).astype(np.float32)
+    mask = np.triu(np.full((n_q, n_kv), -np.inf, np.float16), 1)
+    kb, vb, qb, mb = ctx.buffer(data=kv), ctx.buffer(data=kv[::-1].copy()), ctx.buffer(data=q), ctx.buffer(data=mask)
+    ob, pb = ctx.buffer(n_q * n_head * D * 4), ctx.buffer(16 << 20)
+    push = [D, D, n_kv, n_q, n_head, n_head_kv, 0x11, 1, 0, D, D * n_q, 0, D, D * n_kv, 0, D, D * n_kv, 0, n_kv, 0,
+            1, 0, fbits(1.0 / np.sqrt(D)), 0, 0, 0, 0, 0, 0, 0, 0]
+    s = timed(lambda b: [b.dispatch(fk, [qb, kb, vb, mb, ob, pb], push, (1, 1, 1)) for _ in range(4)], 4)
+    got = ob.read(np.float32).reshape(n_q, n_head, D)
+    kd, vd = kv.astype(np.float64), kv[::-1].astype(np.float64)
+    worst = 0.0
+    for h, i in ((0, 0), (13, 200), (31, 511)):
+        sc = (q[h, i].astype(np.float64) @ kd[h // 4, :i + 1].T) / np.sqrt(D)
+        p = np.exp(sc - sc.max())
+        worst = max(worst, float(np.max(np.abs(got[i, h] - (p @ vd[h // 4, :i + 1]) / p.sum()))))
+    flops = 4.0 * n_head * D * (n_q * (n_q + 1) / 2)     # the unmasked half of both products
+    out["flash_prompt_512"] = {"workload": f"attention, {n_q} query positions x {n_kv} keys, causal, {n_head} heads on "
+                                           f"{n_head_kv} KV heads of {D}, f16 K / V", "us": s * 1e6,
+                               "achieved": flops / s / 1e12, "unit": "TFLOP/s (unmasked products)",
+                               "parity_max_abs_error": worst}
+    for b in (kb, vb, qb, mb, ob, pb):
+        b.destroy()
     return out
 
 

@@ -288,6 +288,11 @@ def _flash_push(D, n_kv, n_q, n_head, n_head_kv, has_mask, scale, softcap=0.0, m
     (128, 24, 8, 200, 50, False, 0.0, 64),         # three heads per KV head: five positions per CTA, one row idle
     (128, 64, 8, 256, 9, True, 0.0, 8 << 20),      # eight heads per KV head: two positions per CTA
     (256, 8, 4, 128, 5, True, 0.0, 8 << 20),       # D = 256 prompts stay on one position per CTA
+    (64, 4, 4, 100, 16, True, 0.0, 8 << 20),       # sixteen positions of ungrouped heads: one 16-row tile per KV head
+    (128, 16, 2, 150, 2, True, 0.0, 8 << 20),      # two positions x eight heads: one 16-row tile
+    (128, 8, 2, 4096, 20, True, 0.0, 8 << 20),     # a short prompt against a long cache: the 64-row kernel with key splits
+    (128, 32, 8, 1500, 200, True, 30.0, 16 << 20), # a chunk of a prompt appended to a cache, soft-capped
+    (128, 32, 8, 2048, 512, True, 0.0, 16 << 20),  # 512 positions appended to 1536 cached ones (the profiled case)
 ])
 def test_flash_attn_decode(ctx, D, n_head, n_head_kv, n_kv, n_q, masked, softcap, scratch):
     rng = np.random.default_rng(D + n_kv)
