@@ -26,7 +26,7 @@ LEGACY_LIB = os.path.join(HERE, "libamuda_b200.so")
 MEASURE_LIB = os.path.join(HERE, "libac_b200_measure.so")
 
 RUNTIME_SOURCES = ["runtime.cu", "registry.cu", "act_quant.cu", "gemv.cu", "gemv_bulk.cu", "gemv_mma.cu", "elementwise.cu", "gemm_tc.cu", "noalloc.cu",
-                   "peer_sync.cu", "repack.cu", "gguf_load.cu", "layer_ops.cu", "gemv_q6k.cu"]
+                   "peer_sync.cu", "repack.cu", "gguf_load.cu", "layer_ops.cu", "gemv_q6k.cu", "kv_quant_ops.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "--expt-relaxed-constexpr",

@@ -303,7 +303,9 @@ AcResult launch_unary(const LaunchArgs& a) {
 // ---------------------------------------------------------------------------------------------------------------------
 // CPY / CONT / DUP between f32 and f16, any strides and shapes with the same element count: element k of the source in
 // row-major order of its own shape goes to element k of the destination in row-major order of the destination shape
-// (ggml_compute_forward_dup). Quantized sources (src_type 2, 3: the shift of a quantized KV cache) are not taken.
+// (ggml_compute_forward_dup). src_type 2 / 3: a q8_0 / q4_0 source in ggml's block layout (the shift of a quantized KV
+// cache casts K to f32), addressed in bytes: a_off and a_s1..a_s3 are bytes, a_s0 is the block size (34 / 18); element a0
+// of a row is value a0 % 32 of block a0 / 32, dequantized as ggml does ((q - 8) * d, q * d).
 // ---------------------------------------------------------------------------------------------------------------------
 struct CpyArgs {
     uint32_t a_ne0, a_ne1, a_ne2, a_ne3;
@@ -330,9 +332,23 @@ __global__ void __launch_bounds__(256) cpy_kernel(const void* __restrict__ a, vo
     const uint32_t b1 = (uint32_t)(t % pc.d_ne1);
     t /= pc.d_ne1;
     const uint32_t b2 = (uint32_t)(t % pc.d_ne2), b3 = (uint32_t)(t / pc.d_ne2);
-    const uint64_t si = pc.a_off + (uint64_t)a0 * pc.a_s0 + (uint64_t)a1 * pc.a_s1 + (uint64_t)a2 * pc.a_s2 + (uint64_t)a3 * pc.a_s3;
     const uint64_t di = pc.d_off + (uint64_t)b0 * pc.d_s0 + (uint64_t)b1 * pc.d_s1 + (uint64_t)b2 * pc.d_s2 + (uint64_t)b3 * pc.d_s3;
-    const float v = pc.src_type ? __half2float(((const __half*)a)[si]) : ((const float*)a)[si];
+    float v;
+    if (pc.src_type >= 2u) {
+        const uint8_t* blk = (const uint8_t*)a + pc.a_off + (uint64_t)(a0 >> 5) * pc.a_s0 + (uint64_t)a1 * pc.a_s1 +
+                             (uint64_t)a2 * pc.a_s2 + (uint64_t)a3 * pc.a_s3;
+        const float dd = __half2float(*reinterpret_cast<const __half*>(blk));
+        const uint32_t j = a0 & 31u;
+        if (pc.src_type == 2u) {
+            v = __fmul_rn((float)(int8_t)blk[2u + j], dd);
+        } else {
+            const uint32_t byte = blk[2u + (j & 15u)];
+            v = __fmul_rn((float)((int)(j < 16u ? (byte & 0x0Fu) : (byte >> 4)) - 8), dd);
+        }
+    } else {
+        const uint64_t si = pc.a_off + (uint64_t)a0 * pc.a_s0 + (uint64_t)a1 * pc.a_s1 + (uint64_t)a2 * pc.a_s2 + (uint64_t)a3 * pc.a_s3;
+        v = pc.src_type ? __half2float(((const __half*)a)[si]) : ((const float*)a)[si];
+    }
     if (pc.dst_f16) ((__half*)d)[di] = __float2half_rn(v);
     else ((float*)d)[di] = v;
 }
@@ -344,15 +360,20 @@ AcResult launch_cpy(const LaunchArgs& a) {
     memcpy(&pc, a.push, sizeof(pc));
     if (!pc.a_ne0 || !pc.a_ne1 || !pc.a_ne2 || !pc.a_ne3 || !pc.d_ne0 || !pc.d_ne1 || !pc.d_ne2 || pc.dst_f16 > 1u)
         return AC_ERR_KERNEL_ARG_INVALID;
-    if (pc.src_type > 1u) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    if (pc.src_type > 3u) return AC_ERR_FEATURE_NOT_SUPPORTED;
+    const bool sq = pc.src_type >= 2u;
+    if (sq && ((pc.a_ne0 & 31u) || pc.a_s0 != (pc.src_type == 2u ? 34u : 18u) || ((pc.a_off | pc.a_s1 | pc.a_s2 | pc.a_s3) & 1u)))
+        return AC_ERR_KERNEL_ARG_INVALID;
     const uint64_t total = (uint64_t)pc.a_ne0 * pc.a_ne1 * pc.a_ne2 * pc.a_ne3, d012 = (uint64_t)pc.d_ne0 * pc.d_ne1 * pc.d_ne2;
     if (total % d012) return AC_ERR_KERNEL_ARG_INVALID;
     const uint64_t d_ne3 = total / d012;
-    const uint64_t src_span = (uint64_t)pc.a_off + (uint64_t)(pc.a_ne0 - 1u) * pc.a_s0 + (uint64_t)(pc.a_ne1 - 1u) * pc.a_s1 +
-                              (uint64_t)(pc.a_ne2 - 1u) * pc.a_s2 + (uint64_t)(pc.a_ne3 - 1u) * pc.a_s3 + 1u;
+    const uint64_t src_span = sq ? (uint64_t)pc.a_off + (uint64_t)(pc.a_ne0 >> 5) * pc.a_s0 + (uint64_t)(pc.a_ne1 - 1u) * pc.a_s1 +
+                                       (uint64_t)(pc.a_ne2 - 1u) * pc.a_s2 + (uint64_t)(pc.a_ne3 - 1u) * pc.a_s3
+                                 : (uint64_t)pc.a_off + (uint64_t)(pc.a_ne0 - 1u) * pc.a_s0 + (uint64_t)(pc.a_ne1 - 1u) * pc.a_s1 +
+                                       (uint64_t)(pc.a_ne2 - 1u) * pc.a_s2 + (uint64_t)(pc.a_ne3 - 1u) * pc.a_s3 + 1u;
     const uint64_t dst_span = (uint64_t)pc.d_off + (uint64_t)(pc.d_ne0 - 1u) * pc.d_s0 + (uint64_t)(pc.d_ne1 - 1u) * pc.d_s1 +
                               (uint64_t)(pc.d_ne2 - 1u) * pc.d_s2 + (d_ne3 - 1u) * pc.d_s3 + 1u;
-    if (a.range[0] < src_span * (pc.src_type ? 2u : 4u) || a.range[1] < dst_span * (pc.dst_f16 ? 2u : 4u)) return AC_ERR_INVALID_BUFFER_SIZE;
+    if (a.range[0] < src_span * (sq ? 1u : pc.src_type ? 2u : 4u) || a.range[1] < dst_span * (pc.dst_f16 ? 2u : 4u)) return AC_ERR_INVALID_BUFFER_SIZE;
     launch_pdl(cpy_kernel, dim3((unsigned)((total + 255u) / 256u)), dim3(256), 0, a.stream, (const void*)a.ptr[0], (void*)a.ptr[1], pc);
     return check_launch();
 }

@@ -52,6 +52,17 @@ AcResult launch_mmvqb_iq4_xs(const LaunchArgs&);
 AcResult launch_mmvq_q4_1(const LaunchArgs&);
 AcResult launch_mmvqb_q3_K(const LaunchArgs&);
 AcResult launch_mmtc_scales(const LaunchArgs&);
+AcResult launch_set_rows_q8_0(const LaunchArgs&);
+AcResult launch_set_rows_q4_0(const LaunchArgs&);
+AcResult launch_get_rows_q4_0_rp(const LaunchArgs&);
+AcResult launch_get_rows_q8_0_rp(const LaunchArgs&);
+AcResult launch_get_rows_q4_k_rp(const LaunchArgs&);
+AcResult launch_get_rows_q5_k_rp(const LaunchArgs&);
+AcResult launch_get_rows_q6_k_rp(const LaunchArgs&);
+AcResult launch_get_rows_iq4_xs_rp(const LaunchArgs&);
+AcResult launch_get_rows_q3_k_rp(const LaunchArgs&);
+AcResult launch_get_rows_q2_k_rp(const LaunchArgs&);
+AcResult launch_get_rows_q4_1_rp(const LaunchArgs&);
 AcResult launch_mmtc_b8(const LaunchArgs&);
 AcResult launch_mmvqb_q2_K(const LaunchArgs&);
 AcResult launch_mmvs_q4_0(const LaunchArgs&);
@@ -111,6 +122,20 @@ static const KernelEntry kTable[] = {
     {"ameva_rope_f16", 4, 92, {256, 1, 1}, launch_rope_f16},
     {"ameva_get_rows", 4, 76, {256, 1, 1}, launch_get_rows},
     {"ameva_set_rows", 4, 88, {256, 1, 1}, launch_set_rows},
+    {"ameva_set_rows_q8_0", 4, 84, {64, 1, 1}, launch_set_rows_q8_0},
+    {"ameva_set_rows_q4_0", 4, 84, {64, 1, 1}, launch_set_rows_q4_0},
+    {"ameva_get_rows_q4_0_rp", 4, 100, {256, 1, 1}, launch_get_rows_q4_0_rp},
+    {"ameva_get_rows_q5_0_rp", 4, 100, {256, 1, 1}, launch_get_rows_q8_0_rp},    // (a Q5_0 table is kept as Q8_0 regions)
+    {"ameva_get_rows_q8_0_rp", 4, 100, {256, 1, 1}, launch_get_rows_q8_0_rp},
+    {"ameva_get_rows_iq4_nl_rp", 4, 100, {256, 1, 1}, launch_get_rows_q8_0_rp},  // (likewise)
+    {"ameva_get_rows_q6_k_rp", 4, 100, {256, 1, 1}, launch_get_rows_q6_k_rp},
+    {"ameva_get_rows_q4_k_rp", 4, 100, {256, 1, 1}, launch_get_rows_q4_k_rp},
+    {"ameva_get_rows_q5_k_rp", 4, 100, {256, 1, 1}, launch_get_rows_q5_k_rp},
+    {"ameva_get_rows_iq4_xs_rp", 4, 100, {256, 1, 1}, launch_get_rows_iq4_xs_rp},
+    {"ameva_get_rows_q3_k_rp", 4, 100, {256, 1, 1}, launch_get_rows_q3_k_rp},
+    {"ameva_get_rows_q2_k_rp", 4, 100, {256, 1, 1}, launch_get_rows_q2_k_rp},
+    {"ameva_get_rows_q4_1_rp", 4, 100, {256, 1, 1}, launch_get_rows_q4_1_rp},
+    {"ameva_get_rows_q5_1_rp", 4, 100, {256, 1, 1}, launch_get_rows_q4_1_rp},
     {"ameva_soft_max", 3, 80, {128, 1, 1}, launch_soft_max},
     {"ameva_flash_attn", 6, 124, {128, 1, 1}, launch_flash_attn},
     {"ameva_cpy", 2, 76, {256, 1, 1}, launch_cpy},

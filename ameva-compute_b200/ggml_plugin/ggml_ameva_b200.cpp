@@ -27,6 +27,7 @@
 // Other ops are reported unsupported, which is how the scheduler keeps them on another backend.
 #include <algorithm>
 #include <atomic>
+#include <cctype>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -559,6 +560,14 @@ const char* layer_op_static_reason(const ggml_tensor* node) {
             return nullptr;
         }
         case GGML_OP_GET_ROWS: {
+            if (a && b && is_repacked_weight(a)) {   // a quantized table kept in the device weight layout (token embeddings)
+                if (node->type != GGML_TYPE_F32 || b->type != GGML_TYPE_I32 || !elem_strides(b, 4) || !elem_strides(node, 4))
+                    return "get_rows: quantized table to f32 with i32 indices";
+                if (b->ne[1] != 1 || b->ne[2] != 1 || node->ne[0] != a->ne[0] || node->ne[1] != b->ne[0] || node->ne[2] != 1 ||
+                    node->ne[3] != 1)
+                    return "get_rows: a quantized table is looked up with one row of indices";
+                return nullptr;
+            }
             if (!a || !b || (a->type != GGML_TYPE_F32 && a->type != GGML_TYPE_F16) || node->type != GGML_TYPE_F32) return "get_rows: f32 / f16 rows to f32";
             if (b->type != GGML_TYPE_I32 || !elem_strides(b, 4) || !elem_strides(a, elem_size(a->type)) || !elem_strides(node, 4))
                 return "get_rows: indices are not i32 or strides are not whole elements";
@@ -629,7 +638,11 @@ const char* layer_op_reason(const ggml_tensor* node) {
         const ggml_tensor* t = node->src[i];
         if (!t) continue;
         if (!own_buffer(t)) return "an operand is not in an AMEVA_B200 buffer";
-        if (tensor_offset(t) % elem_size(t->type)) return "an operand does not start on an element boundary";
+        if (node->op == GGML_OP_GET_ROWS && i == 0 && is_repacked_weight(t)) {
+            if (tensor_offset(t) % kAlign) return "get_rows: the table does not start on a 64-byte boundary";
+            continue;
+        }
+        if (!elem_size(t->type) || tensor_offset(t) % elem_size(t->type)) return "an operand does not start on an element boundary";
     }
     if (!own_buffer(node) || tensor_offset(node) % elem_size(node->type)) return "dst is not in an AMEVA_B200 buffer";
     if (node->op == GGML_OP_FLASH_ATTN_EXT && (tensor_offset(node->src[1]) % 16 || tensor_offset(node->src[2]) % 16 || tensor_offset(node) % 16))
@@ -994,6 +1007,25 @@ bool record_layer_op(Recorder& r, const ggml_tensor* node, int node_index) {
             return dispatch(r, "ameva_cpy", bb, 2, pc, sizeof(pc));
         }
         case GGML_OP_GET_ROWS: {
+            if (is_repacked_weight(a)) {
+                // ameva_get_rows_<type>_rp: the table in the device layout (payload region, scale region at s_off)
+                ElemBind bi, bd;
+                if (!bind_elems(b, 4, &bi) || !bind_elems(node, 4, &bd)) return false;
+                uint64_t s_off = 0;
+                const uint64_t total = device_bytes(a, &s_off);
+                const uint64_t nblk_row = (uint64_t)a->ne[0] / block_elems(a->type);
+                const uint64_t q_row = nblk_row * payload_bytes(a->type), s_row = nblk_row * scale_bytes(dev_type(a->type));
+                if (s_off > 0xFFFFFFFFull || q_row > 0xFFFFFFFFull) return false;
+                const uint32_t pc[25] = {(uint32_t)node->ne[0], (uint32_t)b->ne[0], 1u, 1u, 0u, 0u, 0u, 0u,
+                                         bi.elem, st(b, 0, 4), 0u, 0u, bd.elem, st(node, 1, 4), st(node, 2, 4), st(node, 3, 4),
+                                         (uint32_t)a->ne[1], (uint32_t)node_index, 0u, (uint32_t)a->ne[1],
+                                         0u, (uint32_t)s_off, (uint32_t)q_row, 0u, (uint32_t)s_row};
+                const AcBufferBinding bb[4] = {bind(buffer_of(a)->buf, tensor_offset(a), total), bi.b, status, bd.b};
+                std::string name = std::string("ameva_get_rows_") + type_name(dev_type(a->type)) + "_rp";
+                for (char& ch : name) ch = (char)tolower((unsigned char)ch);
+                r.rows_ops = true;
+                return dispatch(r, name.c_str(), bb, 4, pc, sizeof(pc));
+            }
             const size_t es = elem_size(a->type);
             ElemBind ba, bi, bd;
             if (!bind_elems(a, es, &ba) || !bind_elems(b, 4, &bi) || !bind_elems(node, 4, &bd)) return false;

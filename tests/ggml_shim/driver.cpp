@@ -515,6 +515,49 @@ static void view3(ggml_tensor* t, ggml_tensor* base, int64_t ne0, int64_t ne1, i
     t->src[0] = base;
 }
 
+// GET_ROWS from a quantized table uploaded like any weight (token embeddings): getrows <type> <rows> <nc> <n_idx> <dir>
+// reads table.bin (ggml blocks) and idx.bin (i32), writes rows.bin (f32); an index outside the table must fail the graph.
+static int run_getrows(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) {
+    CHECK(argc == 7);
+    const enum ggml_type type = (enum ggml_type)atoi(argv[2]);
+    const int64_t rows = atoll(argv[3]), nc = atoll(argv[4]), n_idx = atoll(argv[5]);
+    const std::string dir = argv[6];
+    std::vector<uint8_t> tbytes = slurp(dir + "/table.bin"), ibytes = slurp(dir + "/idx.bin");
+    ggml_backend_t backend = dev->iface.init_backend(dev, nullptr);
+    CHECK(backend);
+    ggml_tensor table, idx, out;
+    shape(&table, type, nc, rows, "token_embd");
+    shape(&idx, GGML_TYPE_I32, n_idx, 1, "tokens");
+    shape(&out, GGML_TYPE_F32, nc, n_idx, "inp_embd");
+    CHECK(tbytes.size() == ggml_nbytes(&table) && ibytes.size() == ggml_nbytes(&idx));
+    Arena ar{buft};
+    ar.add(&table);
+    ar.add(&idx);
+    ar.add(&out);
+    CHECK(ar.commit());
+    ggml_backend_buffer_t buf = ar.buf;
+    buf->iface.set_tensor(buf, &table, tbytes.data(), 0, tbytes.size());
+    buf->iface.set_tensor(buf, &idx, ibytes.data(), 0, ibytes.size());
+    out.op = GGML_OP_GET_ROWS;
+    out.src[0] = &table;
+    out.src[1] = &idx;
+    CHECK(dev->iface.supports_op(dev, &out));
+    ggml_tensor* nodes[1] = {&out};
+    ggml_cgraph graph = {1, nodes};
+    CHECK(backend->iface.graph_compute(backend, &graph) == GGML_STATUS_SUCCESS);
+    std::vector<uint8_t> res(ggml_nbytes(&out));
+    buf->iface.get_tensor(buf, &out, res.data(), 0, res.size());
+    CHECK(dump((dir + "/rows.bin").c_str(), res.data(), res.size()));
+    int32_t bad = (int32_t)rows;
+    buf->iface.set_tensor(buf, &idx, &bad, 4, 4);
+    CHECK(backend->iface.graph_compute(backend, &graph) == GGML_STATUS_FAILED);
+    buf->iface.free_buffer(buf);
+    delete buf;
+    backend->iface.free(backend);
+    printf("ok\n");
+    return 0;
+}
+
 // The ops around the mul_mats of a decoder layer, as llama.cpp strings them: token embedding (GET_ROWS), ROPE on the new
 // queries and keys, the KV-cache write (SET_ROWS into f16 caches), attention of the new tokens over the cache
 // (FLASH_ATTN_EXT on strided views of the caches) and a masked SOFT_MAX; then the same graph with a cache slot out of
@@ -720,6 +763,7 @@ int main(int argc, char** argv) {
     if (std::string(argv[1]) == "mulmat") return run_mulmat(argc, argv, dev, buft);
     if (std::string(argv[1]) == "layer") return run_layer(argc, argv, dev, buft);
     if (std::string(argv[1]) == "attn") return run_attn(argc, argv, dev, buft);
+    if (std::string(argv[1]) == "getrows") return run_getrows(argc, argv, dev, buft);
     fprintf(stderr, "driver: unknown mode %s\n", argv[1]);
     return 2;
 }

@@ -167,3 +167,28 @@ def test_attention_side_of_a_decoder_layer_through_the_plugin(D, n_head, n_head_
     assert np.max(np.abs(x_silu - xe / (1.0 + np.exp(-xe.astype(np.float64))))) <= 1e-6
     want_sm = ops.soft_max(sc[None], 1.0 / np.sqrt(np.float32(D)), smask[None, None])[0]
     assert np.max(np.abs(sm - want_sm)) <= 2e-6
+
+
+@needs_plugin
+@pytest.mark.gpu
+@pytest.mark.parametrize("t", [Q4_0, Q5_0, Q8_0, Q6_K, Q4_K, IQ4_XS, Q2_K, Q5_1])
+def test_token_embedding_lookup_from_a_quantized_table(t):
+    """GET_ROWS whose src0 is a quantized matrix uploaded like any weight (ameva_get_rows_<type>_rp on the device layout):
+    the rows are ggml's dequantized rows bit for bit; an index outside the table fails the graph."""
+    import oracle
+    from oracle import extra_types
+    rows, nc, n_idx = 300, 512, 23
+    blocks, _ = make_weights(t, rows, nc, 3)
+    deq = {Q4_0: oracle.dequantize_q4_0, Q8_0: oracle.dequantize_q8_0, Q4_K: oracle.dequantize_q4_K,
+           Q5_0: lambda b: extra_types.dequantize(Q5_0, b), Q6_K: extra_types.dequantize_q6_K,
+           IQ4_XS: extra_types.dequantize_iq4_xs, Q2_K: extra_types.dequantize_q2_K,
+           Q5_1: lambda b: extra_types.dequantize_q4_1(Q5_1, b)}[t]
+    table = np.asarray(deq(blocks), np.float32).reshape(rows, nc)
+    idx = np.random.default_rng(t).integers(0, rows, n_idx).astype(np.int32)
+    with tempfile.TemporaryDirectory() as d:
+        np.asarray(blocks, np.uint8).tofile(os.path.join(d, "table.bin"))
+        idx.tofile(os.path.join(d, "idx.bin"))
+        r = subprocess.run([DRIVER, "getrows", str(t), str(rows), str(nc), str(n_idx), d], capture_output=True, text=True)
+        assert r.returncode == 0, r.stdout + r.stderr
+        got = np.fromfile(os.path.join(d, "rows.bin"), np.float32).reshape(n_idx, nc)
+    assert np.array_equal(got, table[idx])

@@ -355,7 +355,7 @@ def test_cpy_gathers_a_transposed_view_into_another_shape(ctx, src_dt, dst_dt):
     want = a.transpose(0, 2, 1).reshape(-1).astype(dst_dt)
     assert np.array_equal(got, want)
     with pytest.raises(rt.AmevaComputeError, match="FEATURE_NOT_SUPPORTED"):
-        _run(ctx, "ameva_cpy", [ab, db], push[:17] + [2, 0])       # a quantized source
+        _run(ctx, "ameva_cpy", [ab, db], push[:17] + [4, 0])       # a source type without a kernel
     with pytest.raises(rt.AmevaComputeError, match="KERNEL_ARG_INVALID"):
         _run(ctx, "ameva_cpy", [ab, db], push[:9] + [7] + push[10:])   # element counts that do not divide
     ab.destroy()
