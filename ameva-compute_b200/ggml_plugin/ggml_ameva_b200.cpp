@@ -122,10 +122,35 @@ uint32_t scale_bytes(enum ggml_type t) {
     return (t == GGML_TYPE_Q4_K || t == GGML_TYPE_Q5_K) ? 16u : (t == GGML_TYPE_Q6_K ? 18u : (t == GGML_TYPE_IQ4_XS ? 8u : 2u));
 }
 
-// A weight this backend keeps in its device layout: a supported quantized type, plain 2-D, contiguous, not a view.
-bool is_repacked_weight(const ggml_tensor* t) {
+// A tensor that can be kept in the device weight layout: a supported quantized type, plain 2-D, contiguous, not a view.
+bool repackable(const ggml_tensor* t) {
     return t && repacked_type(t->type) && t->ne[2] == 1 && t->ne[3] == 1 && ggml_is_contiguous(t) && t->view_src == nullptr &&
            t->ne[0] % block_elems(t->type) == 0;
+}
+bool repack_all() {   // AMEVA_B200_REPACK_ALL=1: every such tensor, whatever its buffer's usage (hosts that set the usage late)
+    static const bool on = [] {
+        const char* e = getenv("AMEVA_B200_REPACK_ALL");
+        return e && e[0] == '1';
+    }();
+    return on;
+}
+// A weight this backend keeps in its device layout: such a tensor in a buffer whose usage is WEIGHTS (the rule of the
+// reference, ggml-ameva-buffer.cpp:392-394). A quantized tensor anywhere else (a q8_0 / q4_0 KV cache) keeps ggml's
+// block layout.
+bool is_repacked_weight(const ggml_tensor* t) {
+    return repackable(t) && (repack_all() || (t->buffer && ggml_backend_buffer_get_usage(t->buffer) == GGML_BACKEND_BUFFER_USAGE_WEIGHTS));
+}
+// q8_0 / q4_0 data in ggml's block layout (a quantized KV cache, or a view of one)
+bool is_kvq(const ggml_tensor* t) {
+    if (!t || (t->type != GGML_TYPE_Q8_0 && t->type != GGML_TYPE_Q4_0)) return false;
+    return !is_repacked_weight(t) && !(t->view_src && is_repacked_weight(t->view_src));
+}
+uint32_t kvq_block_bytes(enum ggml_type t) { return t == GGML_TYPE_Q8_0 ? 34u : 18u; }
+bool kvq_rows(const ggml_tensor* t) {   // whole blocks along dimension 0, the other strides even and within 32 bits
+    if (t->ne[0] % 32 || t->nb[0] != kvq_block_bytes(t->type)) return false;
+    for (int i = 1; i < 4; ++i)
+        if (t->nb[i] % 2 || t->nb[i] > 0xFFFFFFFFull) return false;
+    return true;
 }
 
 uint64_t device_bytes(const ggml_tensor* t, uint64_t* s_off) {
@@ -299,7 +324,7 @@ size_t buft_get_max_size(ggml_backend_buffer_type_t) {
 }
 
 size_t buft_get_alloc_size(ggml_backend_buffer_type_t, const ggml_tensor* tensor) {
-    if (is_repacked_weight(tensor)) {
+    if (repackable(tensor)) {   // (asked before the tensor has a buffer: room for either layout)
         const size_t dev = (size_t)device_bytes(tensor, nullptr), nb = ggml_nbytes(tensor);
         return dev > nb ? dev : nb;   // the device layout pads the payload region to 64 bytes
     }
@@ -315,6 +340,8 @@ struct Backend {
     AcBuffer* ad = nullptr;   // per-block activation scales (u32 per 32 / 48 B per 256)
     AcBuffer* ah = nullptr;   // fp16 [M][K], the tensor-core operand (M > 8)
     AcBuffer* ae = nullptr;   // f32 [M], the per-row range factors of that operand
+    AcBuffer* kv_f16[2] = {nullptr, nullptr};   // a quantized K / V view dequantized to f16 for FLASH_ATTN_EXT
+    size_t kv_f16_bytes[2] = {0, 0};
     AcBuffer* gh = nullptr;   // fp16 (scale, offset) per 16 weights: the scale table of ameva_mmtc_b8, rewritten per MUL_MAT
     size_t aq_bytes = 0, ad_bytes = 0, ah_bytes = 0, ae_bytes = 0, gh_bytes = 0;
     AcBuffer* op_status = nullptr;   // {count, lowest node} of refused GET_ROWS / SET_ROWS indices
@@ -553,6 +580,17 @@ const char* layer_op_static_reason(const ggml_tensor* node) {
         case GGML_OP_CPY:
         case GGML_OP_CONT:
         case GGML_OP_DUP: {
+            if (a && is_kvq(node)) {   // f32 -> q8_0 / q4_0 of the same shape (the KV-cache shift writes the rotated K back)
+                if (a->type != GGML_TYPE_F32 || !(a->ne[0] == node->ne[0] && a->ne[1] == node->ne[1] && a->ne[2] == node->ne[2] && a->ne[3] == node->ne[3])) return "cpy: to a quantized type from f32 of the same shape only";
+                if (!elem_strides(a, 4) || !kvq_rows(node)) return "cpy: to a quantized type: rows are not whole blocks";
+                return nullptr;
+            }
+            if (a && is_kvq(a)) {      // q8_0 / q4_0 -> f32 / f16 (the shift casts K to f32)
+                if (node->type != GGML_TYPE_F32 && node->type != GGML_TYPE_F16) return "cpy: from a quantized type to f32 / f16 only";
+                if (!kvq_rows(a) || !whole_elem_strides(node, elem_size(node->type))) return "cpy: from a quantized type: rows are not whole blocks";
+                if (a->ne[0] * a->ne[1] * a->ne[2] * a->ne[3] != node->ne[0] * node->ne[1] * node->ne[2] * node->ne[3]) return "cpy: element counts differ";
+                return nullptr;
+            }
             if (!a || (a->type != GGML_TYPE_F32 && a->type != GGML_TYPE_F16) || (node->type != GGML_TYPE_F32 && node->type != GGML_TYPE_F16))
                 return "cpy: between f32 and f16 only";
             if (!whole_elem_strides(a, elem_size(a->type)) || !whole_elem_strides(node, elem_size(node->type))) return "cpy: strides are not whole elements";
@@ -575,6 +613,14 @@ const char* layer_op_static_reason(const ggml_tensor* node) {
             return nullptr;
         }
         case GGML_OP_SET_ROWS: {
+            if (a && b && is_kvq(node)) {   // the write of a quantized KV cache
+                if (a->type != GGML_TYPE_F32 || !elem_strides(a, 4) || !kvq_rows(node)) return "set_rows: f32 rows to whole q8_0 / q4_0 blocks";
+                if ((b->type != GGML_TYPE_I64 && b->type != GGML_TYPE_I32) || b->nb[0] != elem_size(b->type) || b->nb[1] % 4 || b->nb[2] % 4)
+                    return "set_rows: indices";
+                if (a->ne[0] != node->ne[0] || a->ne[2] != node->ne[2] || a->ne[3] != node->ne[3] || b->ne[0] != a->ne[1] || !b->ne[1] || !b->ne[2])
+                    return "set_rows: shape";
+                return nullptr;
+            }
             if (!a || !b || a->type != GGML_TYPE_F32 || (node->type != GGML_TYPE_F32 && node->type != GGML_TYPE_F16)) return "set_rows: f32 rows to f32 / f16";
             if ((b->type != GGML_TYPE_I64 && b->type != GGML_TYPE_I32) || b->nb[0] != elem_size(b->type) || b->nb[1] % 4 || b->nb[2] % 4)
                 return "set_rows: indices";
@@ -596,9 +642,10 @@ const char* layer_op_static_reason(const ggml_tensor* node) {
         }
         case GGML_OP_FLASH_ATTN_EXT: {
             const ggml_tensor *k = node->src[1], *v = node->src[2], *m = node->src[3];
-            if (!a || !k || !v || a->type != GGML_TYPE_F32 || k->type != GGML_TYPE_F16 || v->type != GGML_TYPE_F16 ||
+            const bool kq = k && is_kvq(k), vq = v && is_kvq(v);   // (dequantized to f16 scratch before the attention kernel)
+            if (!a || !k || !v || a->type != GGML_TYPE_F32 || (k->type != GGML_TYPE_F16 && !kq) || (v->type != GGML_TYPE_F16 && !vq) ||
                 node->type != GGML_TYPE_F32)
-                return "flash_attn: f32 queries on an f16 cache only";
+                return "flash_attn: f32 queries on an f16 / q8_0 / q4_0 cache only";
             if (node->src[4]) return "flash_attn: attention sinks";
             if (param_f32(node, 1) != 0.0f) return "flash_attn: ALiBi bias";
             const int64_t D = a->ne[0];
@@ -606,8 +653,10 @@ const char* layer_op_static_reason(const ggml_tensor* node) {
             if (a->ne[3] != 1 || k->ne[3] != 1 || v->ne[3] != 1 || k->ne[1] != v->ne[1] || k->ne[2] != v->ne[2] || !k->ne[2] ||
                 a->ne[2] % k->ne[2] || a->ne[2] / k->ne[2] > 8)
                 return "flash_attn: head grouping";
-            if (!elem_strides(a, 4) || !elem_strides(k, 2) || !elem_strides(v, 2) || !ggml_is_contiguous(node)) return "flash_attn: strides";
-            if ((k->nb[1] | k->nb[2] | v->nb[1] | v->nb[2]) % 16) return "flash_attn: cache rows are not 16-byte aligned";
+            if (!elem_strides(a, 4) || !(kq ? kvq_rows(k) : elem_strides(k, 2)) || !(vq ? kvq_rows(v) : elem_strides(v, 2)) ||
+                !ggml_is_contiguous(node))
+                return "flash_attn: strides";
+            if ((!kq && (k->nb[1] | k->nb[2]) % 16) || (!vq && (v->nb[1] | v->nb[2]) % 16)) return "flash_attn: cache rows are not 16-byte aligned";
             if (node->ne[0] != D || node->ne[1] != a->ne[2] || node->ne[2] != a->ne[1]) return "flash_attn: result shape";
             if (m && (m->type != GGML_TYPE_F16 || !elem_strides(m, 2) || m->ne[0] < k->ne[1] || m->ne[1] < a->ne[1] || !m->ne[2] || m->ne[3] != 1))
                 return "flash_attn: mask";
@@ -642,10 +691,16 @@ const char* layer_op_reason(const ggml_tensor* node) {
             if (tensor_offset(t) % kAlign) return "get_rows: the table does not start on a 64-byte boundary";
             continue;
         }
+        if (is_kvq(t)) {
+            if (tensor_offset(t) % 2) return "a quantized operand does not start on an even byte";
+            continue;
+        }
         if (!elem_size(t->type) || tensor_offset(t) % elem_size(t->type)) return "an operand does not start on an element boundary";
     }
-    if (!own_buffer(node) || tensor_offset(node) % elem_size(node->type)) return "dst is not in an AMEVA_B200 buffer";
-    if (node->op == GGML_OP_FLASH_ATTN_EXT && (tensor_offset(node->src[1]) % 16 || tensor_offset(node->src[2]) % 16 || tensor_offset(node) % 16))
+    if (!own_buffer(node) || (is_kvq(node) ? tensor_offset(node) % 2 : (!elem_size(node->type) || tensor_offset(node) % elem_size(node->type))))
+        return "dst is not in an AMEVA_B200 buffer";
+    if (node->op == GGML_OP_FLASH_ATTN_EXT && ((!is_kvq(node->src[1]) && tensor_offset(node->src[1]) % 16) ||
+                                               (!is_kvq(node->src[2]) && tensor_offset(node->src[2]) % 16) || tensor_offset(node) % 16))
         return "flash_attn: cache or result not 16-byte aligned";
     return nullptr;
 }
@@ -952,6 +1007,25 @@ bool record_elementwise(Recorder& r, const ggml_tensor* node, const ggml_tensor*
 }
 
 // ROPE, GET_ROWS, SET_ROWS, SOFT_MAX, FLASH_ATTN_EXT: push constants as the reference's encoders build them
+// f32 rows -> q8_0 / q4_0 blocks with ameva_set_rows_q8_0 / _q4_0: SET_ROWS (idx given) or a same-shape CPY (idx == nullptr);
+// the reference's enc_store_quantized (ggml-ameva.cpp:4008-4036)
+bool record_store_quantized(Recorder& r, const ggml_tensor* node, const ggml_tensor* a, const ggml_tensor* idx,
+                            const AcBufferBinding& status, int node_index) {
+    ElemBind ba, bi, bd;
+    if (!bind_elems(a, 4, &ba) || !bind_elems(node, 2, &bd) || (idx && !bind_elems(idx, 4, &bi))) return false;
+    if (!idx) bi = ba;   // binding 1 is not read in identity mode
+    const uint32_t mode = !idx ? 0u : (idx->type == GGML_TYPE_I64 ? 2u : 1u);
+    const uint32_t pc[21] = {(uint32_t)(a->ne[0] / 32), (uint32_t)a->ne[1], (uint32_t)a->ne[2], (uint32_t)a->ne[3],
+                             ba.elem, st(a, 1, 4), st(a, 2, 4), st(a, 3, 4),
+                             idx ? bi.elem : 0u, idx ? (uint32_t)(idx->nb[0] / 4) : 0u, idx ? (uint32_t)(idx->nb[1] / 4) : 0u,
+                             idx ? (uint32_t)(idx->nb[2] / 4) : 0u, idx ? (uint32_t)idx->ne[1] : 1u, idx ? (uint32_t)idx->ne[2] : 1u,
+                             mode, (uint32_t)node->ne[1],
+                             bd.elem * 2u, (uint32_t)node->nb[1], (uint32_t)node->nb[2], (uint32_t)node->nb[3], (uint32_t)node_index};
+    const AcBufferBinding bb[4] = {ba.b, bi.b, status, bd.b};
+    if (idx) r.rows_ops = true;
+    return dispatch(r, node->type == GGML_TYPE_Q8_0 ? "ameva_set_rows_q8_0" : "ameva_set_rows_q4_0", bb, 4, pc, sizeof(pc));
+}
+
 bool record_layer_op(Recorder& r, const ggml_tensor* node, int node_index) {
     const ggml_tensor *a = node->src[0], *b = node->src[1];
     const AcBufferBinding status = bind(r.be->op_status, 0, 256);
@@ -995,6 +1069,19 @@ bool record_layer_op(Recorder& r, const ggml_tensor* node, int node_index) {
         case GGML_OP_CPY:
         case GGML_OP_CONT:
         case GGML_OP_DUP: {
+            if (is_kvq(node)) return record_store_quantized(r, node, a, nullptr, status, node_index);
+            if (is_kvq(a)) {   // addressed in bytes: offset and strides in bytes, a_s0 = the block size
+                const size_t ds = elem_size(node->type);
+                ElemBind ba, bd;
+                if (!bind_elems(a, 2, &ba) || !bind_elems(node, ds, &bd)) return false;
+                const uint32_t pc[19] = {(uint32_t)a->ne[0], (uint32_t)a->ne[1], (uint32_t)a->ne[2], (uint32_t)a->ne[3],
+                                         ba.elem * 2u, (uint32_t)a->nb[0], (uint32_t)a->nb[1], (uint32_t)a->nb[2],
+                                         (uint32_t)a->nb[3], (uint32_t)node->ne[0], (uint32_t)node->ne[1], (uint32_t)node->ne[2],
+                                         bd.elem, st(node, 0, ds), st(node, 1, ds), st(node, 2, ds),
+                                         st(node, 3, ds), a->type == GGML_TYPE_Q8_0 ? 2u : 3u, node->type == GGML_TYPE_F16 ? 1u : 0u};
+                const AcBufferBinding bb[2] = {ba.b, bd.b};
+                return dispatch(r, "ameva_cpy", bb, 2, pc, sizeof(pc));
+            }
             const size_t es = elem_size(a->type), ds = elem_size(node->type);
             ElemBind ba, bd;
             if (!bind_elems(a, es, &ba) || !bind_elems(node, ds, &bd)) return false;
@@ -1039,6 +1126,7 @@ bool record_layer_op(Recorder& r, const ggml_tensor* node, int node_index) {
             return dispatch(r, "ameva_get_rows", bb, 4, pc, sizeof(pc));
         }
         case GGML_OP_SET_ROWS: {
+            if (is_kvq(node)) return record_store_quantized(r, node, a, b, status, node_index);
             const size_t es = elem_size(node->type);
             ElemBind ba, bi, bd;
             if (!bind_elems(a, 4, &ba) || !bind_elems(b, 4, &bi) || !bind_elems(node, es, &bd)) return false;
@@ -1069,15 +1157,42 @@ bool record_layer_op(Recorder& r, const ggml_tensor* node, int node_index) {
         case GGML_OP_FLASH_ATTN_EXT: {
             const ggml_tensor *k = node->src[1], *v = node->src[2], *m = node->src[3];
             ElemBind bq, bk, bv, bm, bo;
-            if (!bind_elems(a, 4, &bq) || !bind_elems(k, 2, &bk) || !bind_elems(v, 2, &bv) || !bind_elems(m ? m : a, m ? 2 : 4, &bm) ||
-                !bind_elems(node, 4, &bo))
-                return false;
+            if (!bind_elems(a, 4, &bq) || !bind_elems(m ? m : a, m ? 2 : 4, &bm) || !bind_elems(node, 4, &bo)) return false;
             const uint32_t D = (uint32_t)a->ne[0];
+            // a q8_0 / q4_0 cache is dequantized into f16 scratch [n_head_kv][n_kv][D] first (ameva_cpy from the quantized
+            // view), and the attention kernel reads the scratch: one pass more over the cache than a kernel that decodes
+            // the blocks itself would need
+            uint32_t ks1 = 0, ks2 = 0, vs1 = 0, vs2 = 0;
+            auto operand = [&](const ggml_tensor* t, AcBuffer* scratch, ElemBind* out, uint32_t* s1, uint32_t* s2) -> bool {
+                if (!is_kvq(t)) {
+                    if (!bind_elems(t, 2, out)) return false;
+                    *s1 = st(t, 1, 2);
+                    *s2 = st(t, 2, 2);
+                    return true;
+                }
+                ElemBind src;
+                if (!bind_elems(t, 2, &src)) return false;
+                const uint64_t bytes = (uint64_t)t->ne[0] * t->ne[1] * t->ne[2] * 2u;
+                const uint32_t cp[19] = {(uint32_t)t->ne[0], (uint32_t)t->ne[1], (uint32_t)t->ne[2], 1u,
+                                         src.elem * 2u, (uint32_t)t->nb[0], (uint32_t)t->nb[1], (uint32_t)t->nb[2],
+                                         (uint32_t)t->nb[3], (uint32_t)t->ne[0], (uint32_t)t->ne[1], (uint32_t)t->ne[2],
+                                         0u, 1u, (uint32_t)t->ne[0], (uint32_t)(t->ne[0] * t->ne[1]),
+                                         (uint32_t)(t->ne[0] * t->ne[1] * t->ne[2]), t->type == GGML_TYPE_Q8_0 ? 2u : 3u, 1u};
+                const AcBufferBinding cb[2] = {src.b, bind(scratch, 0, bytes)};
+                if (!dispatch(r, "ameva_cpy", cb, 2, cp, sizeof(cp))) return false;
+                out->b = bind(scratch, 0, bytes);
+                out->elem = 0;
+                *s1 = (uint32_t)t->ne[0];
+                *s2 = (uint32_t)(t->ne[0] * t->ne[1]);
+                return true;
+            };
+            if (!operand(k, r.be->kv_f16[0], &bk, &ks1, &ks2) || !operand(v, r.be->kv_f16[1], &bv, &vs1, &vs2)) return false;
+            if (is_kvq(k) || is_kvq(v)) ac_runtime_batch_barrier(r.batch);
             const uint32_t pc[31] = {D, D, (uint32_t)k->ne[1], (uint32_t)a->ne[1],
                                      (uint32_t)a->ne[2], (uint32_t)k->ne[2], 0x11u, m ? 1u : 0u,
                                      bq.elem, st(a, 1, 4), st(a, 2, 4), bk.elem,
-                                     st(k, 1, 2), st(k, 2, 2), bv.elem, st(v, 1, 2),
-                                     st(v, 2, 2), m ? bm.elem : 0u, m ? st(m, 1, 2) : 0u, m ? st(m, 2, 2) : 0u,
+                                     ks1, ks2, bv.elem, vs1,
+                                     vs2, m ? bm.elem : 0u, m ? st(m, 1, 2) : 0u, m ? st(m, 2, 2) : 0u,
                                      m ? (uint32_t)m->ne[2] : 1u, bo.elem, f32_bits(param_f32(node, 0)), f32_bits(param_f32(node, 2)),
                                      0u, 0u, 0u, 0u, 0u, 0u, 0u};
             const AcBufferBinding bb[6] = {bq.b, bk.b, bv.b, bm.b, bo.b, bind(r.be->fa_part, 0, r.be->fa_part_bytes)};
@@ -1136,7 +1251,7 @@ void backend_free(ggml_backend_t backend) {
         std::lock_guard<std::mutex> lock(plugin().mutex);
         for (auto& kv : be->kernels)
             if (ac_runtime_kernel_destroy(kv.second) == AC_SUCCESS) g_count.kernel_destroy++;
-        for (AcBuffer* b : {be->aq, be->ad, be->ah, be->ae, be->gh, be->op_status, be->fa_part})
+        for (AcBuffer* b : {be->aq, be->ad, be->ah, be->ae, be->gh, be->op_status, be->fa_part, be->kv_f16[0], be->kv_f16[1]})
             if (b && ac_runtime_buffer_destroy(b) == AC_SUCCESS) g_count.buffer_destroy++;
         plugin().live_backends--;
     }
@@ -1191,6 +1306,17 @@ enum ggml_status backend_graph_compute(ggml_backend_t backend, ggml_cgraph* cgra
         (ah_need && !grow(&be->ah, &be->ah_bytes, ah_need)) || (ae_need && !grow(&be->ae, &be->ae_bytes, ae_need)) ||
         (gh_need && !grow(&be->gh, &be->gh_bytes, gh_need)))
         return GGML_STATUS_ALLOC_FAILED;
+    size_t kvf_need[2] = {0, 0};
+    for (int i = 0; i < n; ++i) {
+        const ggml_tensor* node = ggml_graph_node(cgraph, i);
+        if (node->op != GGML_OP_FLASH_ATTN_EXT) continue;
+        for (int j = 0; j < 2; ++j) {
+            const ggml_tensor* t = node->src[1 + j];
+            if (t && is_kvq(t)) kvf_need[j] = std::max(kvf_need[j], (size_t)(t->ne[0] * t->ne[1] * t->ne[2] * 2));
+        }
+    }
+    for (int j = 0; j < 2; ++j)
+        if (kvf_need[j] && !grow(&be->kv_f16[j], &be->kv_f16_bytes[j], kvf_need[j])) return GGML_STATUS_ALLOC_FAILED;
     bool layer_ops = false;
     for (int i = 0; i < n && !layer_ops; ++i) layer_ops = is_layer_op(ggml_graph_node(cgraph, i)->op);
     if (layer_ops) {
@@ -1445,10 +1571,12 @@ const char* ggml_backend_ameva_abi_check(void) {
         ggml_backend_buffer pbuf = {};
         pbuf.buft = &pbt;
         pbuf.size = 0x5A17;
+        pbuf.usage = GGML_BACKEND_BUFFER_USAGE_WEIGHTS;
         ggml_backend_device pd = {};
         pd.reg = &p.reg;
         if (ggml_backend_get_device(&pb) != &p.dev) what = "struct ggml_backend (ggml_backend_i member count)";
-        else if (ggml_backend_buffer_get_size(&pbuf) != 0x5A17 || ggml_backend_buffer_get_type(&pbuf) != &pbt)
+        else if (ggml_backend_buffer_get_size(&pbuf) != 0x5A17 || ggml_backend_buffer_get_type(&pbuf) != &pbt ||
+                 ggml_backend_buffer_get_usage(&pbuf) != GGML_BACKEND_BUFFER_USAGE_WEIGHTS)
             what = "struct ggml_backend_buffer (ggml_backend_buffer_i member count)";
         else if (ggml_backend_buft_get_device(&pbt) != &p.dev) what = "struct ggml_backend_buffer_type";
         else if (ggml_backend_dev_backend_reg(&pd) != &p.reg) what = "struct ggml_backend_device";

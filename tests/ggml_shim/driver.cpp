@@ -144,6 +144,7 @@ static ggml_backend_reg_t g_registered = nullptr;
 void ggml_backend_register(ggml_backend_reg_t reg) { g_registered = reg; }
 ggml_backend_dev_t ggml_backend_get_device(ggml_backend_t backend) { return backend->device; }
 size_t ggml_backend_buffer_get_size(ggml_backend_buffer_t buffer) { return buffer->size; }
+enum ggml_backend_buffer_usage ggml_backend_buffer_get_usage(ggml_backend_buffer_t buffer) { return buffer->usage; }
 ggml_backend_buffer_type_t ggml_backend_buffer_get_type(ggml_backend_buffer_t buffer) { return buffer->buft; }
 ggml_backend_dev_t ggml_backend_buft_get_device(ggml_backend_buffer_type_t buft) { return buft->device; }
 ggml_backend_reg_t ggml_backend_dev_backend_reg(ggml_backend_dev_t device) { return device->reg; }
@@ -227,6 +228,7 @@ struct Arena {
     std::vector<size_t> offsets;
     size_t total = 0;
     ggml_backend_buffer_t buf = nullptr;
+    bool weights = true;   // the usage llama.cpp gives the buffers it loads the model into; false: a compute / cache buffer
     void add(ggml_tensor* t) {
         tensors.push_back(t);
         offsets.push_back(total);
@@ -235,6 +237,7 @@ struct Arena {
     bool commit() {
         buf = buft->iface.alloc_buffer(buft, total);
         if (!buf) return false;
+        buf->usage = weights ? GGML_BACKEND_BUFFER_USAGE_WEIGHTS : GGML_BACKEND_BUFFER_USAGE_ANY;
         char* base = (char*)buf->iface.get_base(buf);
         for (size_t i = 0; i < tensors.size(); ++i) {
             tensors[i]->buffer = buf;
@@ -515,6 +518,87 @@ static void view3(ggml_tensor* t, ggml_tensor* base, int64_t ne0, int64_t ne1, i
     t->src[0] = base;
 }
 
+// A quantized KV cache (q8_0 / q4_0 tensors in a buffer whose usage is not WEIGHTS keep ggml's block layout):
+// kvq <type> <D> <n_head> <n_head_kv> <n_ctx> <n_kv> <n_tok> <dir>. SET_ROWS of the new keys / values into the caches,
+// FLASH_ATTN_EXT over strided views of them, CPY of the key view to f32 and CPY of the new keys to a quantized tensor of
+// the same shape. Reads q.bin, kcur.bin, vcur.bin, kcache.bin, vcache.bin (ggml blocks), slots.bin, mask.bin; writes
+// attn.out, kcache.out, vcache.out (ggml blocks), kdeq.out, kcur_q.out.
+static int run_kvq(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) {
+    CHECK(argc == 10);
+    const enum ggml_type type = (enum ggml_type)atoi(argv[2]);
+    const int64_t D = atoll(argv[3]), n_head = atoll(argv[4]), n_head_kv = atoll(argv[5]), n_ctx = atoll(argv[6]),
+                  n_kv = atoll(argv[7]), n_tok = atoll(argv[8]);
+    const std::string dir = argv[9];
+    auto in = [&](const char* n) { return slurp(dir + "/" + n); };
+    ggml_backend_t backend = dev->iface.init_backend(dev, nullptr);
+    CHECK(backend);
+    const int64_t kvw = D * n_head_kv;
+    ggml_tensor q, kcur, vcur, kcache, vcache, slots, mask, attn, kdeq, kcur_q;
+    shape3(&q, GGML_TYPE_F32, D, n_tok, n_head, "q");
+    shape(&kcur, GGML_TYPE_F32, kvw, n_tok, "k_cur");
+    shape(&vcur, GGML_TYPE_F32, kvw, n_tok, "v_cur");
+    shape(&kcache, type, kvw, n_ctx, "cache_k");
+    shape(&vcache, type, kvw, n_ctx, "cache_v");
+    shape(&slots, GGML_TYPE_I64, n_tok, 1, "slots");
+    shape(&mask, GGML_TYPE_F16, n_kv, n_tok, "kq_mask");
+    shape3(&attn, GGML_TYPE_F32, D, n_head, n_tok, "kqv");
+    shape3(&kdeq, GGML_TYPE_F32, D, n_kv, n_head_kv, "k_f32");
+    shape(&kcur_q, type, kvw, n_tok, "k_cur_q");
+    Arena ar{buft};
+    ar.weights = false;   // a cache / compute buffer: quantized tensors stay in ggml's layout
+    for (ggml_tensor* t : {&q, &kcur, &vcur, &kcache, &vcache, &slots, &mask, &attn, &kdeq, &kcur_q}) ar.add(t);
+    CHECK(ar.commit());
+    ggml_backend_buffer_t buf = ar.buf;
+    struct { ggml_tensor* t; const char* file; } uploads[] = {{&q, "q.bin"}, {&kcur, "kcur.bin"}, {&vcur, "vcur.bin"},
+        {&kcache, "kcache.bin"}, {&vcache, "vcache.bin"}, {&slots, "slots.bin"}, {&mask, "mask.bin"}};
+    for (auto& u : uploads) {
+        std::vector<uint8_t> bytes = in(u.file);
+        CHECK(bytes.size() == ggml_nbytes(u.t));
+        buf->iface.set_tensor(buf, u.t, bytes.data(), 0, bytes.size());
+    }
+    {   // the cache is not repacked: its bytes read back as they were written, also from an odd range
+        std::vector<uint8_t> want = in("kcache.bin"), got(want.size());
+        buf->iface.get_tensor(buf, &kcache, got.data(), 0, got.size());
+        CHECK(got == want);
+    }
+    ggml_tensor kset, vset, k_view, v_view;
+    view3(&kset, &kcache, kvw, n_ctx, 1, kcache.nb[1], kcache.nb[2], 0, GGML_OP_SET_ROWS, "cache_k_set");
+    kset.src[0] = &kcur;
+    kset.src[1] = &slots;
+    view3(&vset, &vcache, kvw, n_ctx, 1, vcache.nb[1], vcache.nb[2], 0, GGML_OP_SET_ROWS, "cache_v_set");
+    vset.src[0] = &vcur;
+    vset.src[1] = &slots;
+    const size_t head_bytes = (size_t)(D / 32) * kcache.nb[0];
+    view3(&k_view, &kcache, D, n_kv, n_head_kv, kcache.nb[1], head_bytes, 0, GGML_OP_VIEW, "k_view");
+    view3(&v_view, &vcache, D, n_kv, n_head_kv, vcache.nb[1], head_bytes, 0, GGML_OP_VIEW, "v_view");
+    op2(&attn, GGML_OP_FLASH_ATTN_EXT, &q, &k_view);
+    attn.src[2] = &v_view;
+    attn.src[3] = &mask;
+    const float scale = 1.0f / sqrtf((float)D), zero = 0.0f;
+    memcpy(&attn.op_params[0], &scale, 4);
+    memcpy(&attn.op_params[1], &zero, 4);
+    memcpy(&attn.op_params[2], &zero, 4);
+    op2(&kdeq, GGML_OP_CPY, &k_view, &kdeq);
+    op2(&kcur_q, GGML_OP_CPY, &kcur, &kcur_q);
+    ggml_tensor* nodes[] = {&kset, &vset, &k_view, &v_view, &attn, &kdeq, &kcur_q};
+    const int n = (int)(sizeof(nodes) / sizeof(nodes[0]));
+    for (ggml_tensor* t : nodes) CHECK(dev->iface.supports_op(dev, t));
+    ggml_cgraph g = {n, nodes};
+    CHECK(backend->iface.graph_compute(backend, &g) == GGML_STATUS_SUCCESS);
+    auto out = [&](ggml_tensor* t, const char* name) {
+        std::vector<uint8_t> v(ggml_nbytes(t));
+        buf->iface.get_tensor(buf, t, v.data(), 0, v.size());
+        return dump(dir + "/" + name, v.data(), v.size());
+    };
+    CHECK(out(&attn, "attn.out") && out(&kcache, "kcache.out") && out(&vcache, "vcache.out") && out(&kdeq, "kdeq.out") &&
+          out(&kcur_q, "kcur_q.out"));
+    buf->iface.free_buffer(buf);
+    delete buf;
+    backend->iface.free(backend);
+    printf("ok\n");
+    return 0;
+}
+
 // GET_ROWS from a quantized table uploaded like any weight (token embeddings): getrows <type> <rows> <nc> <n_idx> <dir>
 // reads table.bin (ggml blocks) and idx.bin (i32), writes rows.bin (f32); an index outside the table must fail the graph.
 static int run_getrows(int argc, char** argv, ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) {
@@ -764,6 +848,7 @@ int main(int argc, char** argv) {
     if (std::string(argv[1]) == "layer") return run_layer(argc, argv, dev, buft);
     if (std::string(argv[1]) == "attn") return run_attn(argc, argv, dev, buft);
     if (std::string(argv[1]) == "getrows") return run_getrows(argc, argv, dev, buft);
+    if (std::string(argv[1]) == "kvq") return run_kvq(argc, argv, dev, buft);
     fprintf(stderr, "driver: unknown mode %s\n", argv[1]);
     return 2;
 }

@@ -192,3 +192,50 @@ def test_token_embedding_lookup_from_a_quantized_table(t):
         assert r.returncode == 0, r.stdout + r.stderr
         got = np.fromfile(os.path.join(d, "rows.bin"), np.float32).reshape(n_idx, nc)
     assert np.array_equal(got, table[idx])
+
+
+@needs_plugin
+@pytest.mark.gpu
+@pytest.mark.parametrize("kind,t,bs", [("q8_0", Q8_0, 34), ("q4_0", Q4_0, 18)])
+def test_quantized_kv_cache_through_the_plugin(kind, t, bs):
+    """A q8_0 / q4_0 KV cache in a buffer that does not hold weights keeps ggml's block layout: SET_ROWS quantizes the new
+    rows into it (bytes equal to ggml's quantizers), FLASH_ATTN_EXT reads it (dequantized to f16 scratch first), CPY
+    dequantizes a strided view of it and quantizes f32 rows of the same shape."""
+    import oracle
+    from oracle import layer_ops as ops
+    D, n_head, n_head_kv, n_ctx, n_kv, n_tok = 128, 8, 2, 96, 80, 5
+    kvw = D * n_head_kv
+    rng = np.random.default_rng(41)
+    quant = (lambda x: oracle.quantize_q8_0(x, oracle.ROUND_NEAREST_EVEN)) if kind == "q8_0" else oracle.quantize_q4_0
+    deq = oracle.dequantize_q8_0 if kind == "q8_0" else oracle.dequantize_q4_0
+    q = rng.standard_normal((n_head, n_tok, D)).astype(np.float32)
+    kcur = rng.standard_normal((n_tok, kvw)).astype(np.float32)
+    vcur = rng.standard_normal((n_tok, kvw)).astype(np.float32)
+    row_bytes = kvw // 32 * bs
+    kcache = np.asarray(quant(rng.standard_normal((n_ctx, kvw)).astype(np.float32)), np.uint8).reshape(n_ctx, row_bytes)
+    vcache = np.asarray(quant(rng.standard_normal((n_ctx, kvw)).astype(np.float32)), np.uint8).reshape(n_ctx, row_bytes)
+    slots = np.arange(n_kv - n_tok, n_kv, dtype=np.int64)
+    mask = np.zeros((n_tok, n_kv), np.float16)
+    for i in range(n_tok):
+        mask[i, n_kv - n_tok + i + 1:] = -np.inf
+    with tempfile.TemporaryDirectory() as d:
+        for name, arr in (("q", q), ("kcur", kcur), ("vcur", vcur), ("kcache", kcache), ("vcache", vcache), ("slots", slots),
+                          ("mask", mask)):
+            arr.tofile(os.path.join(d, name + ".bin"))
+        r = subprocess.run([DRIVER, "kvq", str(t), str(D), str(n_head), str(n_head_kv), str(n_ctx), str(n_kv), str(n_tok), d],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stdout + r.stderr
+        load = lambda n, dt: np.fromfile(os.path.join(d, n + ".out"), dt)
+        attn = load("attn", np.float32).reshape(n_tok, n_head, D)
+        k_after, v_after = load("kcache", np.uint8).reshape(n_ctx, row_bytes), load("vcache", np.uint8).reshape(n_ctx, row_bytes)
+        kdeq, kcur_q = load("kdeq", np.float32).reshape(n_head_kv, n_kv, D), load("kcur_q", np.uint8)
+    want_k, want_v = kcache.copy(), vcache.copy()
+    want_k[slots] = np.asarray(quant(kcur), np.uint8).reshape(n_tok, row_bytes)
+    want_v[slots] = np.asarray(quant(vcur), np.uint8).reshape(n_tok, row_bytes)
+    assert np.array_equal(k_after, want_k) and np.array_equal(v_after, want_v)
+    assert np.array_equal(kcur_q, np.asarray(quant(kcur), np.uint8).reshape(-1))
+    kf = np.asarray(deq(want_k.reshape(-1)), np.float32).reshape(n_ctx, n_head_kv, D)[:n_kv].transpose(1, 0, 2)
+    vf = np.asarray(deq(want_v.reshape(-1)), np.float32).reshape(n_ctx, n_head_kv, D)[:n_kv].transpose(1, 0, 2)
+    assert np.array_equal(kdeq, kf)
+    want = ops.flash_attn_ext(q, kf.astype(np.float16), vf.astype(np.float16), mask, 1.0 / np.sqrt(D))
+    assert np.max(np.abs(attn - want)) <= 2e-3 * max(1.0, float(np.max(np.abs(want))))
