@@ -76,7 +76,7 @@ L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (bytes), by workload and kernel path
 TRAFFIC = {("cfg2", "mmtc"): 57000000, ("cfg5-up-m2048", "mmtc"): 785200000, ("cfg3-gate-m8", "mmvm"): 25424896,
-           ("cfg5-up-m1", "mmvs"): 136000000, ("cfg5-up-m1", "mmvq"): 136777216}
+           ("cfg5-up-m1", "mmvs"): 136000000, ("cfg5-up-m1", "mmvq"): 136777216, ("q6k-down-m512", "mmtc"): 101992192}
 GEMV_MAX_M = 8
 
 
