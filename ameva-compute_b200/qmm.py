@@ -198,11 +198,11 @@ def _bindings_for(view: WeightView):
 def _record_rms_norm_quantize(ctx, batch, ggml_type, M, K, x, y, aq, ad, ah, ae, mode, eps, weight, x_offset, y_offset,
                               w_offset):
     """ameva_rms_norm_quant_a8 / a8b: y = rms_norm(x) [* weight] written as f32, and y quantized into (aq, ad[, ah, ae])."""
-    if ggml_type not in (GGML_TYPE_Q4_0, GGML_TYPE_Q8_0, GGML_TYPE_Q4_K):
+    if ggml_type not in PER_32 and ggml_type not in PER_256:
         raise MulMatUnsupported("the fused RMS norm + quantize serves the per-32 and per-256 activation schemes")
     if K > 32768:
         raise MulMatUnsupported("the fused RMS norm + quantize keeps a row in registers: K <= 32768")
-    name = "ameva_rms_norm_quant_a8b" if ggml_type == GGML_TYPE_Q4_K else "ameva_rms_norm_quant_a8"
+    name = "ameva_rms_norm_quant_a8b" if ggml_type in PER_256 else "ameva_rms_norm_quant_a8"
     wb = (weight, w_offset, K * 4) if weight is not None else (x, x_offset)
     write_h = ah is not None
     binds = [(x, x_offset), wb, (y, y_offset, M * K * 4), aq, ad, ah if write_h else aq, ae if write_h else aq]
@@ -453,7 +453,7 @@ class MulMat:
         scratch by the same kernel: follow with ``record(batch, y, dst, M, quantize=False)``. Replaces RMS_NORM (+ MUL)
         and the quantize kernel of the MUL_MAT that consumes the result (three launches become one)."""
         use_tc = M > GEMV_MAX_M and not self.exact and self.tc_ok
-        mode = self.q8k_mode if self.type == GGML_TYPE_Q4_K else self.round_mode
+        mode = self.q8k_mode if self.type in PER_256 else self.round_mode
         _record_rms_norm_quantize(self.ctx, batch, self.type, M, self.K, x, y, self.aq, self.ad,
                                   self.ah if use_tc else None, self.ae if use_tc else None, mode, eps, weight, x_offset,
                                   y_offset, w_offset)

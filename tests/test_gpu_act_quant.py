@@ -4,7 +4,7 @@ import pytest
 
 import oracle
 from conftest import GOLDEN, load_pkg
-from helpers import Q4_0, Q4_K, Q8_0, make_weights
+from helpers import Q4_0, Q4_K, Q8_0, make_weights, Q6_K, Q5_1, Q2_K
 
 pytestmark = pytest.mark.gpu
 pkg = load_pkg()
@@ -178,7 +178,7 @@ def test_quantizers_against_frozen_known_answers(ctx):
         b.destroy()
 
 
-@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K])
+@pytest.mark.parametrize("t", [Q4_0, Q8_0, Q4_K, Q6_K, Q5_1, Q2_K])
 @pytest.mark.parametrize("M,N,K,with_weight", [(1, 64, 4096, True), (1, 130, 2560, False), (5, 32, 1024, True),
                                                (33, 128, 2048, True), (1, 16, 32768, True), (300, 256, 512, False)])
 def test_rms_norm_fused_with_the_quantize(ctx, t, M, N, K, with_weight):
@@ -186,7 +186,7 @@ def test_rms_norm_fused_with_the_quantize(ctx, t, M, N, K, with_weight):
     (ameva_rms_norm_quant_a8 / a8b): y against ggml's CPU arithmetic (squares summed in double), the quantized scratch
     bit-equal to the oracle's quantization of the y the kernel wrote, and the product through that scratch equal to the
     product of the separate kernels on the same y."""
-    if t == Q4_K and K % 256:
+    if t in (Q4_K, Q6_K, Q2_K) and K % 256:
         K = (K // 256 + 1) * 256
     rng = np.random.default_rng(M + K)
     x = (rng.standard_normal((M, K)) * rng.uniform(0.05, 20.0, (M, 1))).astype(np.float32)
@@ -214,7 +214,7 @@ def test_rms_norm_fused_with_the_quantize(ctx, t, M, N, K, with_weight):
     assert np.max(np.abs(y - want_y) / np.max(np.abs(want_y), axis=1, keepdims=True)) <= 3e-7
     assert np.max(np.abs(y - (x64 / np.sqrt(np.mean(x64 * x64, axis=1, keepdims=True) + eps)) * (w if with_weight else 1.0))
                   / np.max(np.abs(want_y), axis=1, keepdims=True)) <= 3e-6
-    if t in (Q4_0, Q8_0):
+    if t in (Q4_0, Q8_0, Q5_1):
         q, dbits, _ = mm.read_quantized(M)
         assert np.array_equal(qmm.q8_0_blocks_from_scratch(q, dbits), oracle.quantize_q8_0(y))
     else:
