@@ -1043,7 +1043,9 @@ __global__ void __launch_bounds__(kFaWarps * 32, 3) flash_prompt_kernel(const fl
     pdl_wait();
     const uint32_t z = blockIdx.x, hkv = blockIdx.y;
     const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
-    const uint32_t G = pc.n_head / pc.n_head_kv, h0 = hkv * G, QT = 64u / G, q0 = blockIdx.z * QT;
+    const uint32_t G = pc.n_head / pc.n_head_kv, h0 = hkv * G, QT = 64u / G;
+    // the last positions first: under a causal mask they have the most unmasked keys, and the grid is dealt in order
+    const uint32_t q0 = (gridDim.z - 1u - blockIdx.z) * QT;
     const float ninf = __uint_as_float(0xFF800000u);
     const uint32_t key_begin = z * pc.split_keys, key_end = min(pc.n_kv, key_begin + pc.split_keys);
     const __half* kbase = k + pc.k_off + (uint64_t)hkv * pc.k_s2;
