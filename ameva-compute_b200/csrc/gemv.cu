@@ -313,7 +313,7 @@ gemv_q8_0_kernel(const u32x8* __restrict__ Q, const uint16_t* __restrict__ S, co
 //   y += (d*d_a)*float(isum) - (dmin*d_a)*float(mpart)          (block-integer form, ameva_mmqb.comp:10-16)
 // The four lanes of a block are an aligned lane group (DUMP reduces over them).
 // ---------------------------------------------------------------------------------------------------------------------
-template <int M, int R, bool DUMP, int UNV = 0, bool FQ = false>
+template <int M, int R, bool DUMP, int UNV = 0, bool FQ = false, bool PF = false>
 __device__ __forceinline__ void
 gemv_q4_K_body(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
                const uint8_t* __restrict__ AB, const DstList& dl, int32_t* __restrict__ sums, uint32_t N, uint32_t K,
@@ -334,20 +334,28 @@ gemv_q4_K_body(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const i
     }
     u32x8 wq[UN][R];
     uint4 wsc[UN][R];
-    auto load_weights = [&](uint32_t c0) {
+    // PF: the weights of the next step are requested before this step's arithmetic (a second register set), so a warp has
+    // two steps of loads in flight instead of one
+    u32x8 nq[PF ? UN : 1][PF ? R : 1];
+    uint4 nsc[PF ? UN : 1][PF ? R : 1];
+    auto load_into = [&](auto& dq, auto& ds, uint32_t c0) {
 #pragma unroll
         for (int i = 0; i < UN; ++i) {
             const uint32_t c = c0 + 32 * i;
             if (c < C) {
 #pragma unroll
                 for (int r = 0; r < R; ++r) {
-                    wq[i][r] = ld_stream_u8(qrow[r] + c);
-                    wsc[i][r] = ld_cached_u4(srow[r] + (c >> 2));  // shared by the 4 lanes of the block
+                    dq[i][r] = ld_stream_u8(qrow[r] + c);
+                    ds[i][r] = ld_cached_u4(srow[r] + (c >> 2));  // shared by the 4 lanes of the block
                 }
             }
         }
     };
+    auto load_weights = [&](uint32_t c0) { load_into(wq, wsc, c0); };
     load_weights(lane);   // before the wait: the weights do not depend on the kernel before this one
+    if constexpr (PF) {   // (two steps: a row of 4096 weights is then wholly in flight before the wait)
+        if (lane + 32 * UN < C) load_into(nq, nsc, lane + 32 * UN);
+    }
     pdl_trigger();   // the kernel behind this one may be scheduled (it waits for this grid before touching what it wrote)
     pdl_wait();      // the activations come from the preceding kernel
     if constexpr (FQ) {
@@ -428,7 +436,18 @@ gemv_q4_K_body(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const i
             }
         }
         c0 += 32 * UN;
-        if (c0 < C) load_weights(c0);
+        if constexpr (PF) {
+#pragma unroll
+            for (int i = 0; i < UN; ++i)
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    wq[i][r] = nq[i][r];
+                    wsc[i][r] = nsc[i][r];
+                }
+            if (c0 + 32 * UN < C) load_into(nq, nsc, c0 + 32 * UN);   // in flight during the next step's arithmetic
+        } else {
+            if (c0 < C) load_weights(c0);
+        }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -442,12 +461,12 @@ gemv_q4_K_body(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const i
         }
 }
 
-template <int M, int R, bool DUMP, int UNV = 0, int MINB = 1, bool FQ = false>
+template <int M, int R, bool DUMP, int UNV = 0, int MINB = 1, bool FQ = false, bool PF = false>
 __global__ void __launch_bounds__(kGemvThreads, MINB)
 gemv_q4_K_kernel(const u32x8* __restrict__ Q, const uint4* __restrict__ S, const int8_t* __restrict__ AQ,
                  const uint8_t* __restrict__ AB, const DstList dl, int32_t* __restrict__ sums, uint32_t N, uint32_t K,
                  uint32_t dst_stride, const Epi ep, const float* __restrict__ X, uint32_t qmode) {
-    gemv_q4_K_body<M, R, DUMP, UNV, FQ>(Q, S, AQ, AB, dl, sums, N, K, dst_stride, ep, X, qmode,
+    gemv_q4_K_body<M, R, DUMP, UNV, FQ, PF>(Q, S, AQ, AB, dl, sums, N, K, dst_stride, ep, X, qmode,
                                         (blockIdx.x * kGemvThreads + threadIdx.x) >> 5);
 }
 
@@ -496,6 +515,8 @@ gemv_group_kernel(const WeightGroup g, const float* __restrict__ X, const int8_t
         DstList dl;
         dl.n = 1u;
         dl.p[0] = g.dst[j];
+        // (the variant with the next step's weights in flight, see launch_mmvqb, measured slower here: three 4096 x 4096
+        // matrices in one launch 12.5 against 11.0 us)
         gemv_q4_K_body<1, 2, false, 1, FQ>((const u32x8*)g.Q[j], (const uint4*)g.S[j], AQ, (const uint8_t*)AD, dl, nullptr, N,
                                            K, N, ep, X, qmode, w);
     }
@@ -695,7 +716,16 @@ static AcResult launch_mmvqb(const LaunchArgs& a) {
         // registers (four blocks = 32 warps per SM) beats two chunks at 96 registers (two blocks): 34.3 vs 39 us. Staging
         // the stream through shared memory was also tried and is slower on this kernel: cp.async prefetch four steps
         // ahead 41 us, bulk copies into a persistent CTA (gemv_bulk.cu) 45 us.
-        if (M == 1u)
+        // A matrix below 64 MB is not bandwidth-bound at one row (a launch takes 5-15 us, of which 3.5 are the floor of a
+        // dependent launch): there the variant that requests two steps of weights before the wait for the preceding
+        // kernel and keeps the next step's loads in flight during the arithmetic wins (4096 x 14336: 14.7 -> 11.7 us,
+        // 4096 x 4096: 5.5 -> 4.6 us) at three instead of four blocks per SM; on 132 MB matrices the four blocks win
+        // (8192 x 28672: 28.3 against 41.0 us).
+        if (M == 1u && (uint64_t)N * B * (kQ4KQBytes + kQ4KSBytes) < (64ull << 20))
+            launch_pdl(gemv_q4_K_kernel<1, 2, false, 1, 3, false, true>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
+                       (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
+                       dl, sums, N, K, dst_stride, ep, nullptr, 0u);
+        else if (M == 1u)
             launch_pdl(gemv_q4_K_kernel<1, 2, false, 1, 4>, dim3(gemv_blocks<2>(N)), dim3(kGemvThreads), 0, a.stream,
                        (const u32x8*)a.ptr[0], (const uint4*)a.ptr[1], (const int8_t*)a.ptr[2], (const uint8_t*)a.ptr[3],
                        dl, sums, N, K, dst_stride, ep, nullptr, 0u);

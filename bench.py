@@ -70,7 +70,7 @@ WORKLOADS = {
     "q6k-down-m1": (Q6_K, 1, 4096, 14336, 0.02, "Q6_K x Q8_K 4096x14336 M=1"),
     "q6k-down-m512": (Q6_K, 512, 4096, 14336, 0.02, "Q6_K x Q8_K 4096x14336 M=512 (ameva_mmtc_b8)"),
 }
-DECODE_LINES = ("cfg1", "cfg3-qkv-m1", "cfg5-up-m1")      # the M = 1 half of the metric, in the default line
+DECODE_LINES = ("cfg1", "cfg3-qkv-m1", "cfg3-down-m1", "cfg5-up-m1")      # the M = 1 half of the metric, in the default line
 SHARDED_LINES = ("cfg5-up-m2048", "cfg5-up-m1")           # the row-sharded shapes, in every line
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of the dominant kernel per launch, from the ncu captures summarised under
