@@ -251,3 +251,24 @@ def test_q3_K_and_q2_K_decode_equal_gguf_py():
         for h in halves:
             raw[:, h], raw[:, h + 1] = 0, 0x1C                     # (a finite fp16 scale)
         assert np.array_equal(dequantize(raw.reshape(-1)), quants.dequantize(raw, qt).reshape(-1))
+
+
+def test_products_of_the_added_types_agree_with_their_dequantized_operands():
+    """The numpy restatements of ggml_vec_dot_<type>_q8_K / _q8_1 (block-integer sums times block scales) against the
+    plain product of the dequantized weights and the dequantized activations in fp64: the two are the same real number
+    per output, so they agree to fp32 summation error. This ties every product formula to the decode that gguf-py pins."""
+    from helpers import (IQ4_XS, Q2_K, Q3_K, Q4_1, Q5_1, Q5_K, Q6_K, make_acts, make_weights, max_normalised_error,
+                         oracle_mul_mat)
+    from oracle import extra_types as et
+    deq = {Q6_K: et.dequantize_q6_K, Q5_K: et.dequantize_q5_K, IQ4_XS: et.dequantize_iq4_xs, Q3_K: et.dequantize_q3_K,
+           Q2_K: et.dequantize_q2_K, Q4_1: lambda b: et.dequantize_q4_1(Q4_1, b), Q5_1: lambda b: et.dequantize_q4_1(Q5_1, b)}
+    M, N, K = 3, 24, 1024
+    x = make_acts(M, K, 9)
+    for t, fn in deq.items():
+        blocks, scale = make_weights(t, N, K, t)
+        y, _, aq = oracle_mul_mat(t, blocks, scale, x, N, K, want_sums=False)
+        w = np.asarray(fn(blocks), np.float64).reshape(N, K)
+        a = np.asarray((oracle.dequantize_q8_0 if t in (Q4_1, Q5_1) else oracle.dequantize_q8_K)(aq), np.float64).reshape(M, K)
+        want = a @ w.T
+        norm = np.abs(a) @ np.abs(w).T
+        assert float(np.max(np.abs(np.asarray(y, np.float64) - want) / norm)) <= 2e-6, t
